@@ -1,0 +1,325 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-group kernels on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+A step is one launch of the headline fused group, cast_fp16(tanh((X + bias) * 0.5)) with X fp32 [64,1024,1024]
+and bias [1024] broadcast on the last axis, through the group's C-ABI entry point.  With N > 1 (one process per
+GPU under torch.distributed.run) every rank runs the same group on its own shard-sized copy (weak scaling, the
+group shards on axis 0 with no communication); the reported value is the whole-job GB/s over the slowest rank.
+One JSON line is printed by rank 0.  `--impl reference` times the CPU restatement of the reference's x86 path on
+the host cores instead (rank 0 only).
+"""
+import argparse
+import ctypes
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HEADLINE_SHAPE = (64, 1024, 1024)
+METRIC = "fused-group HBM throughput"
+UNIT = "GB/s"
+
+
+def measured_peak_gbs():
+    """(HBM GB/s used as the roofline denominator, where it came from)."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index, period_s=0.02):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop_evt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def _sample(self):
+        nv = self.nv
+        self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+        try:
+            mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+        except Exception:
+            mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+        names = {
+            0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+            0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost",
+        }
+        for bit, name in names.items():
+            if mask & bit:
+                self.reasons.add(name)
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self._stop_evt.is_set():
+            try:
+                self._sample()
+            except Exception:
+                break
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        med = int(np.median(self.samples)) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def cpu_reference_run(steps, warmup):
+    """Times the CPU restatement of the reference's x86 path on the headline group, all host threads."""
+    from oracle import x86_oracle
+    from cinn_b200 import workloads as W
+    threads = x86_oracle.num_threads()
+    w = W.bias_scale_tanh_cast(HEADLINE_SHAPE)
+    x, bias = w.inputs
+    for _ in range(max(warmup, 1)):
+        x86_oracle.bias_scale_tanh_f16(x, bias, 0.5, 0.0, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        x86_oracle.bias_scale_tanh_f16(x, bias, 0.5, 0.0, threads=threads)
+    dt = (time.perf_counter() - t0) / steps
+    return w.algorithmic_bytes() / dt / 1e9, dt * 1e3, threads
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    steps = min(args.steps, 10)
+    warm = min(args.warmup, 2)
+    gbs, ms, threads = cpu_reference_run(steps, warm)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "bias_scale_tanh_cast X f32[64,1024,1024] + bias[1024] -> f16", "elements": 67108864},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": "full headline group per step, OpenMP over rows, %d threads" % threads},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "elements_per_s": 67108864 / (ms * 1e-3),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def time_group(group, tensors_sets, iters, warmup, torch):
+    """Average device time (ms) of one launch of `group`, rotating through the given argument sets."""
+    stream = torch.cuda.current_stream()
+    sp = ctypes.c_void_p(stream.cuda_stream)
+    bound = [group.bind(ts) for ts in tensors_sets]
+    for i in range(warmup):
+        pods, _ = bound[i % len(bound)]
+        group.run_entry(pods, len(tensors_sets[0]), sp)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(iters):
+        pods, _ = bound[i % len(bound)]
+        group.run_entry(pods, len(tensors_sets[0]), sp)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def side_groups(torch, dev, peak, only=None):
+    """Per-group throughput of the other fused groups (device-resident inputs, kernel time only)."""
+    import cinn_b200
+    from cinn_b200 import workloads as W
+    out = {}
+
+    def dev_inputs(w, reps):
+        sets = []
+        for _ in range(reps):
+            ins = [torch.from_numpy(a).to(dev) for a in w.inputs]
+            o = torch.empty(w.out_shape, dtype={np.dtype(np.float32): torch.float32,
+                                                np.dtype(np.float16): torch.float16}[np.dtype(w.out_dtype)], device=dev)
+            sets.append(ins + [o])
+        return sets
+
+    plan = [
+        ("add_relu_1x3x224x224", lambda: W.add_relu((1, 3, 224, 224)), 4, "L2-resident (1.8 MB): launch-latency-bound"),
+        ("add_relu_stacked_256x3x224x224", lambda: W.add_relu((256, 3, 224, 224), name="fn_add_relu_stacked"), 2,
+         "256 stacked copies so that the working set exceeds L2"),
+        ("reduce_sum_axis2_128x1024x1024", lambda: W.reduce_sum_last((128, 1024, 1024)), 1, ""),
+        ("reduce_max_axis0_128x1024x1024", lambda: W.reduce_max_first((128, 1024, 1024)), 1, ""),
+        ("softmax_f32_16384x4096", lambda: W.softmax((16384, 4096)), 2, ""),
+        ("softmax_f16_16384x4096", lambda: W.softmax((16384, 4096), half=True), 2, ""),
+        ("layer_norm_f32_16384x4096", lambda: W.layer_norm((16384, 4096)), 2, ""),
+        ("layer_norm_f16_16384x4096", lambda: W.layer_norm((16384, 4096), half=True), 2, ""),
+        ("bn_relu_f32_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112)), 1, ""),
+        ("bn_relu_f16_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112), half=True), 1, ""),
+    ]
+    for name, make, reps, note in plan:
+        if only and not any(o in name for o in only):
+            continue
+        w = make()
+        g = cinn_b200.FusedGroup(w.desc)
+        sets = dev_inputs(w, reps)
+        ms = time_group(g, sets, iters=30, warmup=5, torch=torch)
+        gbs = g.algorithmic_bytes / (ms * 1e-3) / 1e9
+        out[name] = {"ms": round(ms, 5), "GB/s": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                     "elements_per_s": g.elements / (ms * 1e-3), "kernels": g.kernel_names(),
+                     "bytes": g.algorithmic_bytes}
+        if note:
+            out[name]["note"] = note
+        g.release()
+        del sets
+        torch.cuda.empty_cache()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-side-groups", action="store_true", help="skip the per-group table of the other configs")
+    ap.add_argument("--only", nargs="*", default=None, help="side groups whose name contains one of these")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    import cinn_b200
+    from cinn_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the fused-group kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    warmup = max(args.warmup, 3)
+    peak, peak_src = measured_peak_gbs()
+
+    # Headline group.  Two argument sets (2 x 403 MB) so that consecutive launches never touch the same lines;
+    # each set is itself larger than the 126 MB L2.
+    w = W.bias_scale_tanh_cast(HEADLINE_SHAPE)
+    g = cinn_b200.FusedGroup(w.desc)
+    x_host = torch.from_numpy(w.inputs[0]).pin_memory()
+    bias_host = torch.from_numpy(w.inputs[1]).pin_memory()
+    out_host = torch.empty(w.out_shape, dtype=torch.float16).pin_memory()
+    sets = []
+    for _ in range(2):
+        sets.append([x_host.to(dev, non_blocking=True), bias_host.to(dev, non_blocking=True),
+                     torch.empty(w.out_shape, dtype=torch.float16, device=dev)])
+    torch.cuda.synchronize()
+
+    stream = torch.cuda.current_stream()
+    sp = ctypes.c_void_p(stream.cuda_stream)
+    bound = [g.bind(ts) for ts in sets]
+    for i in range(warmup):
+        g.run_entry(bound[i % 2][0], 3, sp)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches0 = cinn_b200.lib().cinn_b200_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for i in range(args.steps):
+        g.run_entry(bound[i % 2][0], 3, sp)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    launches = cinn_b200.lib().cinn_b200_launch_count() - launches0
+    clocks = sampler.stop()
+    total_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    bytes_per_launch = g.algorithmic_bytes
+    value = bytes_per_launch * world / (ms_per_step * 1e-3) / 1e9
+    per_gpu = value / world
+
+    # End to end through the host-buffer entry point: pinned host inputs -> device -> kernel -> pinned host output.
+    e2e_steps = max(3, min(args.steps, 20))
+    host_arrays = [x_host, bias_host, out_host]
+    for _ in range(3):
+        g.run_host(host_arrays, device=local_rank)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        g.run_host(host_arrays, device=local_rank)
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = bytes_per_launch * world / (e2e_ms * 1e-3) / 1e9
+
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "bias_scale_tanh_cast X f32[64,1024,1024] + bias[1024] -> f16 (per GPU)",
+                   "elements": g.elements, "bytes_per_launch": bytes_per_launch,
+                   "l2": "inputs (268 MB) larger than L2; two argument sets alternated",
+                   "sharding": "axis 0, no collective; each rank runs the full-size group (weak scaling)"},
+        "elements_per_s": g.elements * world / (ms_per_step * 1e-3),
+        "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
+                     "frac": round(per_gpu / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "kernel": g.kernel_names()[0]},
+        "e2e": {"value": round(e2e_value, 3), "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": int(x_host.numel() * 4 + bias_host.numel() * 4),
+                "d2h_bytes_per_step": int(out_host.numel() * 2), "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    g.release()
+    del sets, bound
+    torch.cuda.empty_cache()
+
+    if rank == 0 and not args.no_cpu_baseline:
+        gbs, ms, threads = cpu_reference_run(steps=3, warmup=1)
+        line["cpu_baseline"] = {"value": round(gbs, 3), "unit": UNIT, "cores": threads, "kind": "port", "ms": ms,
+                                "sample": "full headline group, 3 passes, OpenMP over rows, %d threads" % threads}
+    if rank == 0 and world == 1 and not args.no_side_groups:
+        line["groups"] = side_groups(torch, dev, peak, args.only)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

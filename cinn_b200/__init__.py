@@ -1,0 +1,3 @@
+"""B200-native kernels for CINN's fused op groups behind the CINN runtime ABI."""
+from ._lib import CinnB200Error, lib  # noqa: F401
+from .runtime import FusedGroup  # noqa: F401

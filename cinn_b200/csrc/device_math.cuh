@@ -1,0 +1,174 @@
+// Device-side arithmetic and memory helpers shared by all fused-group kernels.
+//
+// The scalar formulas restate what CINN's x86 path computes (that path is the parity target), not
+// what CUDA's libm would: tanh is the two-branch exp formula, rsqrt is 1/sqrt, max/min are
+// compare+select.  The translation units that include this file are compiled with -fmad=false so
+// that a*b+c is fused only where fmaf() is written; division and sqrt are the IEEE-rounded forms
+// (nvcc defaults -prec-div=true -prec-sqrt=true, no fast-math, no flush-to-zero).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace cinn_b200 {
+
+// cinn/backends/llvm/codegen_llvm.cc:310-340: fcmp ogt/olt + select.
+__device__ __forceinline__ float x86_max(float a, float b) { return a > b ? a : b; }
+__device__ __forceinline__ float x86_min(float a, float b) { return a < b ? a : b; }
+
+// cinn/backends/llvm/llvm_intrin_rule.h:136-154.  Both branches evaluate exp(-2|x|); the negative
+// branch (e-1)/(e+1) is the exact negation of (1-e)/(1+e).
+__device__ __forceinline__ float x86_tanh(float x) {
+  if (x >= 0.0f) {
+    float e = expf(-2.0f * x);
+    return (1.0f - e) / (1.0f + e);
+  } else {
+    float e = expf(2.0f * x);
+    return (e - 1.0f) / (e + 1.0f);
+  }
+}
+// cinn/backends/llvm/llvm_intrin_rule.h:105-113.
+__device__ __forceinline__ float x86_rsqrt(float x) { return 1.0f / sqrtf(x); }
+// cinn/lang/builtin.h:79-82.
+__device__ __forceinline__ float x86_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// ---- 128-bit global memory access -------------------------------------------------------------
+// Inputs of these groups are read once and outputs written once, so both use the streaming
+// (evict-first) cache policy; small broadcast operands use the default policy and stay in L1/L2.
+__device__ __forceinline__ uint4 ld_stream16(const void* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ void st_stream16(void* p, uint4 v) { __stcs(reinterpret_cast<uint4*>(p), v); }
+__device__ __forceinline__ uint2 ld_stream8(const void* p) { return __ldcs(reinterpret_cast<const uint2*>(p)); }
+__device__ __forceinline__ void st_stream8(void* p, uint2 v) { __stcs(reinterpret_cast<uint2*>(p), v); }
+__device__ __forceinline__ uint4 ld_keep16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+__device__ __forceinline__ void unpack4(uint4 u, float (&f)[4]) {
+  f[0] = __uint_as_float(u.x);
+  f[1] = __uint_as_float(u.y);
+  f[2] = __uint_as_float(u.z);
+  f[3] = __uint_as_float(u.w);
+}
+__device__ __forceinline__ uint4 pack4(const float (&f)[4]) {
+  return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+// fp16 pairs: fpext is exact, fptrunc is round-to-nearest-even (cinn/backends/llvm/codegen_llvm.cc:454-455).
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void unpack_h2(uint32_t u, float& lo, float& hi) {
+  __half2 h = *reinterpret_cast<__half2*>(&u);
+  float2 f  = __half22float2(h);
+  lo        = f.x;
+  hi        = f.y;
+}
+__device__ __forceinline__ void unpack8h(uint4 u, float (&f)[8]) {
+  unpack_h2(u.x, f[0], f[1]);
+  unpack_h2(u.y, f[2], f[3]);
+  unpack_h2(u.z, f[4], f[5]);
+  unpack_h2(u.w, f[6], f[7]);
+}
+__device__ __forceinline__ uint4 pack8h(const float (&f)[8]) {
+  return make_uint4(pack_h2(f[0], f[1]), pack_h2(f[2], f[3]), pack_h2(f[4], f[5]), pack_h2(f[6], f[7]));
+}
+__device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void unpack_bf2(uint32_t u, float& lo, float& hi) {
+  lo = __uint_as_float(u << 16);
+  hi = __uint_as_float(u & 0xffff0000u);
+}
+
+// Element type traits: how many elements a 16-byte vector holds and how to convert it to/from fp32.
+template <typename T>
+struct Io;
+template <>
+struct Io<float> {
+  static constexpr int kVec = 4;
+  __device__ static __forceinline__ void unpack(uint4 u, float* f) {
+    f[0] = __uint_as_float(u.x);
+    f[1] = __uint_as_float(u.y);
+    f[2] = __uint_as_float(u.z);
+    f[3] = __uint_as_float(u.w);
+  }
+  __device__ static __forceinline__ uint4 pack(const float* f) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+  __device__ static __forceinline__ float load1(const float* p) { return *p; }
+  __device__ static __forceinline__ void store1(float* p, float v) { *p = v; }
+};
+template <>
+struct Io<__half> {
+  static constexpr int kVec = 8;
+  __device__ static __forceinline__ void unpack(uint4 u, float* f) {
+    unpack_h2(u.x, f[0], f[1]);
+    unpack_h2(u.y, f[2], f[3]);
+    unpack_h2(u.z, f[4], f[5]);
+    unpack_h2(u.w, f[6], f[7]);
+  }
+  __device__ static __forceinline__ uint4 pack(const float* f) {
+    return make_uint4(pack_h2(f[0], f[1]), pack_h2(f[2], f[3]), pack_h2(f[4], f[5]), pack_h2(f[6], f[7]));
+  }
+  __device__ static __forceinline__ float load1(const __half* p) { return __half2float(*p); }
+  __device__ static __forceinline__ void store1(__half* p, float v) { *p = __float2half_rn(v); }
+};
+template <>
+struct Io<__nv_bfloat16> {
+  static constexpr int kVec = 8;
+  __device__ static __forceinline__ void unpack(uint4 u, float* f) {
+    unpack_bf2(u.x, f[0], f[1]);
+    unpack_bf2(u.y, f[2], f[3]);
+    unpack_bf2(u.z, f[4], f[5]);
+    unpack_bf2(u.w, f[6], f[7]);
+  }
+  __device__ static __forceinline__ uint4 pack(const float* f) {
+    return make_uint4(pack_bf2(f[0], f[1]), pack_bf2(f[2], f[3]), pack_bf2(f[4], f[5]), pack_bf2(f[6], f[7]));
+  }
+  __device__ static __forceinline__ float load1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  __device__ static __forceinline__ void store1(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+// ---- warp / CTA reductions ---------------------------------------------------------------------
+struct SumOp {
+  __device__ static __forceinline__ float identity() { return 0.0f; }
+  __device__ static __forceinline__ float apply(float a, float b) { return a + b; }
+};
+struct ProdOp {
+  __device__ static __forceinline__ float identity() { return 1.0f; }
+  __device__ static __forceinline__ float apply(float a, float b) { return a * b; }
+};
+// cinn/lang/builtin.cc:123-143: the initial value of max is lowest() (= -FLT_MAX), not -inf.
+struct MaxOp {
+  __device__ static __forceinline__ float identity() { return -3.402823466e+38f; }
+  __device__ static __forceinline__ float apply(float a, float b) { return x86_max(a, b); }
+};
+struct MinOp {
+  __device__ static __forceinline__ float identity() { return 3.402823466e+38f; }
+  __device__ static __forceinline__ float apply(float a, float b) { return x86_min(a, b); }
+};
+
+template <class Op>
+__device__ __forceinline__ float warp_allreduce(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// All threads of the CTA get the result.  `scratch` holds at least 32 floats of shared memory and may
+// be reused after the call returns (a trailing barrier is included).
+template <class Op>
+__device__ __forceinline__ float cta_allreduce(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+  v = warp_allreduce<Op>(v);
+  if (nwarps == 1) return v;
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = lane < nwarps ? scratch[lane] : Op::identity();
+  r       = warp_allreduce<Op>(r);
+  __syncthreads();
+  return r;
+}
+
+}  // namespace cinn_b200

@@ -1,0 +1,633 @@
+// Pattern matcher: fused group -> launch plan over the prebuilt kernels.
+//
+// This is "dispatch point #1": where the reference turns a Graph::Group into generated CUDA through
+// OpLowerer::Lower (cinn/hlir/framework/op_lowering.cc:48-162) and CodegenAndJit
+// (cinn/hlir/framework/parallel_compiler.cc:151-199), this file recognises the group's expression and picks a
+// hand-written kernel plus its launch shape.  What each recognised expression computes is defined by the op
+// semantics cited next to each matcher.
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <functional>
+#include <set>
+#include <sstream>
+
+#include "group_desc.h"
+
+namespace cinn_b200 {
+namespace {
+
+int64_t CeilDiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
+int64_t RoundUp(int64_t a, int64_t b) { return CeilDiv(a, b) * b; }
+
+struct Matcher {
+  const GroupDesc& g;
+  const DeviceInfo& dev;
+  std::string* err;
+  std::map<std::string, const OpDesc*> producer;
+  std::map<std::string, int> input_index;
+  std::map<std::string, TensorDesc> values;  // every value with inferred dtype/shape
+
+  Matcher(const GroupDesc& g_, const DeviceInfo& d, std::string* e) : g(g_), dev(d), err(e) {
+    for (size_t i = 0; i < g.inputs.size(); ++i) {
+      input_index[g.inputs[i].name] = (int)i;
+      values[g.inputs[i].name]      = g.inputs[i];
+    }
+    for (auto& op : g.ops) producer[op.output] = &op;
+  }
+
+  bool Fail(const std::string& m) {
+    if (err) *err = "group '" + g.name + "': " + m;
+    return false;
+  }
+
+  // ---- attribute access ----------------------------------------------------------------------
+  static bool HasAttr(const OpDesc& op, const char* k) { return op.attrs.count(k) != 0; }
+  static std::string AttrS(const OpDesc& op, const char* k, const std::string& dflt) {
+    auto it = op.attrs.find(k);
+    return it == op.attrs.end() ? dflt : it->second;
+  }
+  static double AttrF(const OpDesc& op, const char* k, double dflt) {
+    auto it = op.attrs.find(k);
+    return it == op.attrs.end() ? dflt : atof(it->second.c_str());
+  }
+  static int64_t AttrI(const OpDesc& op, const char* k, int64_t dflt) {
+    auto it = op.attrs.find(k);
+    return it == op.attrs.end() ? dflt : atoll(it->second.c_str());
+  }
+  static bool AttrB(const OpDesc& op, const char* k, bool dflt) {
+    auto it = op.attrs.find(k);
+    if (it == op.attrs.end()) return dflt;
+    return it->second == "1" || it->second == "true" || it->second == "True";
+  }
+  static std::vector<int64_t> AttrList(const OpDesc& op, const char* k) {
+    std::vector<int64_t> out;
+    auto it = op.attrs.find(k);
+    if (it == op.attrs.end()) return out;
+    std::string cur;
+    for (char c : it->second + ",") {
+      if (c == ',') {
+        if (!cur.empty()) out.push_back(atoll(cur.c_str()));
+        cur.clear();
+      } else if (c != '[' && c != ']' && c != ' ') {
+        cur.push_back(c);
+      }
+    }
+    return out;
+  }
+
+  const OpDesc* Producer(const std::string& v) const {
+    auto it = producer.find(v);
+    return it == producer.end() ? nullptr : it->second;
+  }
+  // The op producing `v` if it has the given type, else nullptr.
+  const OpDesc* ProducerOfType(const std::string& v, const char* type) const {
+    const OpDesc* p = Producer(v);
+    return (p && p->type == type) ? p : nullptr;
+  }
+  int InputIndex(const std::string& v) const {
+    auto it = input_index.find(v);
+    return it == input_index.end() ? -1 : it->second;
+  }
+
+  // ---- common pieces of a plan ---------------------------------------------------------------
+  std::unique_ptr<CompiledGroup> NewPlan(const char* pattern) {
+    auto p     = std::make_unique<CompiledGroup>();
+    p->name    = g.name;
+    p->pattern = pattern;
+    p->inputs  = g.inputs;
+    p->outputs = g.outputs;
+    for (auto& t : g.inputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
+    for (auto& t : g.outputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
+    p->elements = g.outputs[0].numel();
+    return p;
+  }
+  static ArgSpec In(int i) {
+    ArgSpec a;
+    a.kind  = ArgSpec::kInput;
+    a.index = i;
+    return a;
+  }
+  static ArgSpec Out(int i) {
+    ArgSpec a;
+    a.kind  = ArgSpec::kOutput;
+    a.index = i;
+    return a;
+  }
+  static ArgSpec Scratch(int64_t offset) {
+    ArgSpec a;
+    a.kind   = ArgSpec::kScratch;
+    a.ivalue = offset;
+    return a;
+  }
+  static ArgSpec I(int64_t v) {
+    ArgSpec a;
+    a.kind   = ArgSpec::kInt;
+    a.ivalue = v;
+    return a;
+  }
+  static ArgSpec F(double v) {
+    ArgSpec a;
+    a.kind   = ArgSpec::kFloat;
+    a.fvalue = v;
+    return a;
+  }
+  static ArgSpec Aligned(bool static_ok, std::vector<int> ins, std::vector<int> outs) {
+    ArgSpec a;
+    a.kind            = ArgSpec::kAligned;
+    a.ivalue          = static_ok ? 1 : 0;
+    a.aligned_inputs  = std::move(ins);
+    a.aligned_outputs = std::move(outs);
+    return a;
+  }
+  bool Kernel(LaunchStep* s, const std::string& name) {
+    s->kernel = FindKernel(name);
+    if (!s->kernel) return Fail("kernel '" + name + "' is not in the library");
+    return true;
+  }
+
+  // ---- relu(elementwise_add(%0,%1)), fp32, equal shapes --------------------------------------
+  // cinn/hlir/pe/broadcast.cc:216-273, cinn/hlir/pe/nn.cc:61-64.
+  std::unique_ptr<CompiledGroup> MatchAddRelu(const std::string& expr) {
+    if (expr != "relu(elementwise_add(%0,%1))" && expr != "relu(elementwise_add(%1,%0))") return nullptr;
+    if (g.inputs.size() != 2) return nullptr;
+    const auto &a = g.inputs[0], &b = g.inputs[1], &o = g.outputs[0];
+    if (a.dtype != DType::kFloat32 || b.dtype != DType::kFloat32 || o.dtype != DType::kFloat32) return nullptr;
+    if (a.shape != b.shape || a.numel() != o.numel()) return nullptr;
+    auto p    = NewPlan("ew_add_relu");
+    int64_t n = o.numel();
+    LaunchStep s;
+    if (!Kernel(&s, "ew_add_relu_f32")) return nullptr;
+    s.block[0] = 256;
+    s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(CeilDiv(n, 4), 256), dev.sm_count * 32));
+    s.args     = {In(0), In(1), Out(0), I(n), Aligned(true, {0, 1}, {0})};
+    p->steps.push_back(s);
+    return p;
+  }
+
+  // ---- cast(tanh(scale(elementwise_add(%0,%1)))) with %1 a vector on the last axis ------------
+  // cinn/hlir/pe/broadcast.cc:35-273 (axis = -1 or ndim-1), cinn/hlir/op/elementwise.cc:149-163,
+  // cinn/backends/llvm/llvm_intrin_rule.h:136-154, cinn/hlir/pe/elementwise.cc:213-217.
+  std::unique_ptr<CompiledGroup> MatchBiasScaleTanhCast(const std::string& expr) {
+    bool with_cast = expr == "cast(tanh(scale(elementwise_add(%0,%1))))";
+    if (!with_cast && expr != "tanh(scale(elementwise_add(%0,%1)))") return nullptr;
+    if (g.inputs.size() != 2) return nullptr;
+    const auto &x = g.inputs[0], &bias = g.inputs[1], &o = g.outputs[0];
+    if (x.dtype != DType::kFloat32 || bias.dtype != DType::kFloat32) return nullptr;
+    if (x.shape.empty() || o.numel() != x.numel()) return nullptr;
+    const int64_t cols = x.shape.back();
+    if (!(bias.shape.size() == 1 && bias.shape[0] == cols)) return nullptr;
+    const OpDesc* top   = Producer(o.name);
+    const OpDesc* tanh  = with_cast ? Producer(top->inputs[0]) : top;
+    const OpDesc* scale = Producer(tanh->inputs[0]);
+    const OpDesc* add   = Producer(scale->inputs[0]);
+    int64_t axis        = AttrI(*add, "axis", -1);
+    if (!(axis == -1 || axis == (int64_t)x.shape.size() - 1)) return nullptr;
+    if (!AttrB(*scale, "bias_after_scale", true)) return nullptr;
+    const char* suffix = nullptr;
+    if (with_cast) {
+      DType want = DTypeFromName(AttrS(*top, "dtype", "float32"));
+      if (want != o.dtype) {
+        Fail("cast dtype attribute does not match the output tensor's dtype");
+        return nullptr;
+      }
+    }
+    switch (o.dtype) {
+      case DType::kFloat16: suffix = "f16"; break;
+      case DType::kBFloat16: suffix = "bf16"; break;
+      case DType::kFloat32: suffix = "f32"; break;
+      default: return nullptr;
+    }
+    auto p    = NewPlan("ew_bias_scale_tanh_cast");
+    int64_t n = x.numel();
+    LaunchStep s;
+    if (!Kernel(&s, std::string("ew_bias_scale_tanh_cast_f32_") + suffix)) return nullptr;
+    s.block[0] = 256;
+    s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(CeilDiv(n, 8), 512), dev.sm_count * 32));
+    s.args     = {In(0), In(1), Out(0), I(n), I(cols), Aligned(cols % 8 == 0, {0, 1}, {0}),
+                  F((float)AttrF(*scale, "scale", 1.0)), F((float)AttrF(*scale, "bias", 0.0))};
+    p->steps.push_back(s);
+    return p;
+  }
+
+  // ---- [cast(] [relu(] batch_norm(x, scale, bias, mean, variance) [)] [)] on NCHW ---------------
+  // cinn/hlir/pe/nn.cc:700-721; argument order cinn/frontend/net_builder.cc:764-801.  The op itself is fp32
+  // only (cinn/hlir/op/nn.cc:1078-1082); 16-bit storage is expressed as cast(..(cast(%0),..)).
+  std::unique_ptr<CompiledGroup> MatchBatchNorm(const std::string& expr) {
+    bool relu = false, half = false;
+    if (expr == "relu(batch_norm(%0,%1,%2,%3,%4))") {
+      relu = true;
+    } else if (expr == "batch_norm(%0,%1,%2,%3,%4)") {
+    } else if (expr == "cast(relu(batch_norm(cast(%0),%1,%2,%3,%4)))") {
+      relu = half = true;
+    } else if (expr == "cast(batch_norm(cast(%0),%1,%2,%3,%4))") {
+      half = true;
+    } else {
+      return nullptr;
+    }
+    if (g.inputs.size() != 5) return nullptr;
+    const auto &x = g.inputs[0], &o = g.outputs[0];
+    if (x.shape.size() != 4 || o.shape != x.shape) return nullptr;
+    if (half ? (x.dtype != DType::kFloat16 || o.dtype != DType::kFloat16)
+             : (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32))
+      return nullptr;
+    const int64_t N = x.shape[0], C = x.shape[1], HW = x.shape[2] * x.shape[3];
+    for (int i = 1; i < 5; ++i) {
+      if (g.inputs[i].dtype != DType::kFloat32 || g.inputs[i].shape != std::vector<int64_t>{C}) {
+        Fail("batch_norm parameters must be float32 vectors of length C");
+        return nullptr;
+      }
+    }
+    const OpDesc* bn = nullptr;
+    for (auto& op : g.ops)
+      if (op.type == "batch_norm") bn = &op;
+    std::string layout = AttrS(*bn, "data_layout", "NCHW");
+    if (layout != "NCHW") {
+      Fail("batch_norm layout '" + layout + "' has no prebuilt kernel (NCHW only)");
+      return nullptr;
+    }
+    const double eps = (float)AttrF(*bn, "epsilon", 1e-5);
+    auto p           = NewPlan(relu ? "ew_bn_relu_nchw" : "ew_bn_nchw");
+    const int V      = half ? 8 : 4;
+    const int64_t planes = N * C;
+    // A CTA takes about 1024 vectors of one plane; small problems get more, smaller chunks to fill the SMs.
+    const int64_t units = HW % V == 0 ? HW / V : HW;
+    int64_t chunks      = std::max<int64_t>(1, (units + 512) / 1024);
+    while (planes * chunks < (int64_t)dev.sm_count * 4 && units / (chunks * 2) >= 256) chunks *= 2;
+    LaunchStep s;
+    if (!Kernel(&s, std::string(relu ? "ew_bn_relu_nchw_" : "ew_bn_nchw_") + (half ? "f16" : "f32"))) return nullptr;
+    s.block[0] = 256;
+    s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(planes * chunks, (int64_t)dev.sm_count * 64));
+    s.args     = {In(0), In(1), In(2), In(3), In(4), Out(0), I(planes), I(C), I(HW), I(chunks),
+                  Aligned(HW % V == 0, {0}, {0}), F(eps)};
+    p->steps.push_back(s);
+    return p;
+  }
+
+  // ---- reduce_{sum,prod,max,min}(%0) -----------------------------------------------------------
+  // cinn/hlir/op/reduction.cc:49-158 (dim normalisation: negative dims wrap, empty = all), cinn/hlir/pe/reduction.cc.
+  static bool ReduceView(const std::vector<int64_t>& shape, std::vector<int64_t> dims, int64_t* outer, int64_t* r,
+                         int64_t* inner) {
+    const int nd = (int)shape.size();
+    if (dims.empty())
+      for (int i = 0; i < nd; ++i) dims.push_back(i);
+    for (auto& d : dims)
+      if (d < 0) d += nd;
+    std::sort(dims.begin(), dims.end());
+    dims.erase(std::unique(dims.begin(), dims.end()), dims.end());
+    for (auto d : dims)
+      if (d < 0 || d >= nd) return false;
+    // Drop extent-1 axes from consideration, then the reduced axes must be contiguous.
+    std::vector<int> kind;  // 0 keep, 1 reduce, per non-unit axis
+    std::vector<int64_t> ext;
+    for (int i = 0; i < nd; ++i) {
+      if (shape[i] == 1) continue;
+      kind.push_back(std::binary_search(dims.begin(), dims.end(), (int64_t)i) ? 1 : 0);
+      ext.push_back(shape[i]);
+    }
+    *outer = *r = *inner = 1;
+    int state            = 0;  // 0 outer, 1 reduce, 2 inner
+    for (size_t i = 0; i < kind.size(); ++i) {
+      if (kind[i] == 1) {
+        if (state == 2) return false;
+        state = 1;
+        *r *= ext[i];
+      } else {
+        if (state == 1) state = 2;
+        if (state == 0) *outer *= ext[i];
+        else *inner *= ext[i];
+      }
+    }
+    return true;
+  }
+
+  bool PlanReduce(CompiledGroup* p, const char* opname, int64_t outer, int64_t r, int64_t inner, ArgSpec src,
+                  ArgSpec dst, std::vector<int> src_in_for_align) {
+    const int sms = dev.sm_count;
+    if (inner == 1) {
+      const int64_t rows = outer;
+      const bool vec     = r % 4 == 0;
+      if (r <= 2048) {
+        int iters = 1;
+        while (iters * 128 < r) iters *= 2;
+        LaunchStep s;
+        if (!Kernel(&s, "row_reduce_warp" + std::to_string(iters) + "_" + opname + "_f32")) return false;
+        s.block[0] = 256;
+        s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(rows, 8), (int64_t)sms * 64));
+        s.args     = {src, dst, I(rows), I(r), Aligned(vec, src_in_for_align, {})};
+        p->steps.push_back(s);
+        return true;
+      }
+      const unsigned block = r >= 16384 ? 512 : 256;
+      if (rows >= (int64_t)sms * 2 || r < 32768) {
+        LaunchStep s;
+        if (!Kernel(&s, std::string("row_reduce_cta_") + opname + "_f32")) return false;
+        s.block[0] = block;
+        s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(rows, (int64_t)sms * 32));
+        s.args     = {src, dst, I(rows), I(r), I(1), I(RoundUp(r, 4)), Aligned(vec, src_in_for_align, {})};
+        p->steps.push_back(s);
+        return true;
+      }
+      if (rows * 8 >= sms) {
+        // A cluster of 8 CTAs per row merges partials through distributed shared memory: one launch.
+        const int64_t csize = 8;
+        LaunchStep s;
+        if (!Kernel(&s, std::string("row_reduce_cluster_") + opname + "_f32")) return false;
+        s.block[0] = 512;
+        s.cluster  = (unsigned)csize;
+        s.grid[0]  = (unsigned)(std::min<int64_t>(rows, std::max<int64_t>(1, (int64_t)sms * 2 / csize)) * csize);
+        s.args     = {src, dst, I(rows), I(r), I(RoundUp(CeilDiv(r, csize), 4)), Aligned(vec, src_in_for_align, {})};
+        p->steps.push_back(s);
+        return true;
+      }
+      // Few, very long rows: split every row over many CTAs into scratch partials, then finish.
+      int64_t splits = std::min<int64_t>(CeilDiv((int64_t)sms * 4, rows), std::max<int64_t>(1, r / 8192));
+      splits         = std::min<int64_t>(splits, 2048);
+      const int64_t seg = RoundUp(CeilDiv(r, splits), 4);
+      splits            = CeilDiv(r, seg);
+      const int64_t scratch_off = p->scratch_bytes;
+      p->scratch_bytes += (size_t)RoundUp(rows * splits * 4, 256);
+      LaunchStep s1;
+      if (!Kernel(&s1, std::string("row_reduce_cta_") + opname + "_f32")) return false;
+      s1.block[0] = 512;
+      s1.grid[0]  = (unsigned)(rows * splits);
+      s1.args = {src, Scratch(scratch_off), I(rows), I(r), I(splits), I(seg), Aligned(vec, src_in_for_align, {})};
+      p->steps.push_back(s1);
+      // The partials of a sum are summed; of max/min/prod combined with the same op.
+      return PlanReduceFinishRows(p, opname, rows, splits, Scratch(scratch_off), dst);
+    }
+    // inner > 1: column reduction.
+    const bool vec       = inner % 4 == 0;
+    const int64_t cols   = vec ? inner / 4 : inner;
+    const int64_t thr    = cols * outer;
+    int64_t splits       = 1;
+    if (thr < (int64_t)sms * 1024 && r >= 64) {
+      splits = std::min<int64_t>(r / 32, CeilDiv((int64_t)sms * 2048, thr));
+      splits = std::max<int64_t>(1, std::min<int64_t>(splits, 1024));
+    }
+    const int64_t rows_per_split = CeilDiv(r, splits);
+    splits                       = CeilDiv(r, rows_per_split);
+    const unsigned block         = cols >= 256 ? 256 : (cols >= 128 ? 128 : 64);
+    LaunchStep s;
+    if (!Kernel(&s, std::string("col_reduce_") + opname + "_f32")) return false;
+    s.block[0] = block;
+    s.grid[0]  = (unsigned)CeilDiv(cols, block);
+    s.grid[1]  = (unsigned)std::min<int64_t>(outer, 65535);
+    s.grid[2]  = (unsigned)splits;
+    if (splits == 1) {
+      std::vector<int> outs;
+      ArgSpec al = Aligned(vec, src_in_for_align, {});
+      if (dst.kind == ArgSpec::kOutput) al.aligned_outputs.push_back(dst.index);
+      s.args = {src, dst, I(outer), I(r), I(inner), I(rows_per_split), al};
+      p->steps.push_back(s);
+      return true;
+    }
+    const int64_t scratch_off = p->scratch_bytes;
+    p->scratch_bytes += (size_t)RoundUp(splits * outer * inner * 4, 256);
+    // Scratch is 256-byte aligned; the partial of split k starts at k*outer*inner floats, which keeps 16-byte
+    // alignment only when outer*inner % 4 == 0 (true when inner % 4 == 0).
+    s.args = {src, Scratch(scratch_off), I(outer), I(r), I(inner), I(rows_per_split),
+              Aligned(vec, src_in_for_align, {})};
+    p->steps.push_back(s);
+    const int64_t oi = outer * inner;
+    return PlanReduce(p, opname, 1, splits, oi, Scratch(scratch_off), dst, {});
+  }
+
+  bool PlanReduceFinishRows(CompiledGroup* p, const char* opname, int64_t rows, int64_t splits, ArgSpec src,
+                            ArgSpec dst) {
+    return PlanReduce(p, opname, rows, splits, 1, src, dst, {});
+  }
+
+  std::unique_ptr<CompiledGroup> MatchReduce(const std::string& expr) {
+    static const std::map<std::string, const char*> kinds = {
+        {"reduce_sum(%0)", "sum"}, {"reduce_prod(%0)", "prod"}, {"reduce_max(%0)", "max"}, {"reduce_min(%0)", "min"}};
+    auto it = kinds.find(expr);
+    if (it == kinds.end()) return nullptr;
+    const auto &x = g.inputs[0], &o = g.outputs[0];
+    if (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32) {
+      Fail("reductions are prebuilt for float32 only");
+      return nullptr;
+    }
+    const OpDesc* op = Producer(o.name);
+    int64_t outer, r, inner;
+    if (!ReduceView(x.shape, AttrList(*op, "dim"), &outer, &r, &inner)) {
+      Fail("reduce over non-adjacent axes has no prebuilt kernel");
+      return nullptr;
+    }
+    if (o.numel() != outer * inner) {
+      Fail("reduce output has " + std::to_string(o.numel()) + " elements, expected " + std::to_string(outer * inner));
+      return nullptr;
+    }
+    auto p      = NewPlan(inner == 1 ? "row_reduce" : "col_reduce");
+    p->elements = x.numel();
+    if (!PlanReduce(p.get(), it->second, outer, r, inner, In(0), Out(0), {0})) return nullptr;
+    return p;
+  }
+
+  // ---- row normalisation ---------------------------------------------------------------------
+  bool PlanRowNorm(CompiledGroup* p, bool layernorm, bool half, int64_t rows, int64_t cols, double eps, int x_in,
+                   int gamma_in, int beta_in) {
+    const int V        = half ? 8 : 4;
+    const char* tname  = half ? "f16" : "f32";
+    const int sms      = dev.sm_count;
+    const int64_t nvec = cols / V;
+    auto cluster_step  = [&](LaunchStep* s) -> bool {
+      const int64_t cap = 48 * 1024;  // floats of dynamic shared memory per CTA (192 KiB)
+      int64_t csize     = 1;
+      while (csize < 8 && CeilDiv(cols, csize) > cap) csize *= 2;
+      if (CeilDiv(cols, csize) > cap)
+        return Fail("row of " + std::to_string(cols) + " elements exceeds the cluster capacity of " +
+                    std::to_string(8 * cap));
+      const int64_t seg = CeilDiv(cols, csize);
+      if (!Kernel(s, std::string("rownorm_cluster_") + tname)) return false;
+      s->block[0] = 512;
+      s->cluster  = (unsigned)csize;
+      s->dyn_smem = (size_t)seg * 4;
+      const int64_t per_sm = std::max<int64_t>(1, std::min<int64_t>(4, (200 * 1024) / (seg * 4 + 1024)));
+      const int64_t ncl    = std::max<int64_t>(1, std::min<int64_t>(rows, (int64_t)sms * per_sm / csize));
+      s->grid[0]           = (unsigned)(ncl * csize);
+      s->args = {In(x_in), layernorm ? In(gamma_in) : In(x_in), layernorm ? In(beta_in) : In(x_in), Out(0), I(rows),
+                 I(cols), I(seg), I(layernorm ? 1 : 0), F(eps)};
+      return true;
+    };
+    LaunchStep slow;
+    if (!cluster_step(&slow)) return false;
+    if (cols % V == 0 && nvec <= 4096) {
+      int G = 32;
+      if (nvec > 128) G = 128;
+      if (nvec > 512) G = 256;
+      if (nvec > 1024) G = 512;
+      if (nvec > 2048) G = 1024;
+      int vpt = 1;
+      while (G * vpt < nvec) vpt *= 2;
+      LaunchStep s;
+      std::string name = std::string(layernorm ? "layernorm_row_" : "softmax_row_") + tname + "_g" +
+                         std::to_string(G) + "_v" + std::to_string(vpt);
+      if (!Kernel(&s, name)) return false;
+      if (G == 32) {
+        s.block[0] = 256;
+        s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(rows, 8), (int64_t)sms * 16));
+      } else {
+        s.block[0] = G;
+        s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(rows, (int64_t)sms * (2048 / G) * 2));
+      }
+      if (layernorm)
+        s.args = {In(x_in), In(gamma_in), In(beta_in), Out(0), I(rows), I(cols), F(eps)};
+      else
+        s.args = {In(x_in), Out(0), I(rows), I(cols)};
+      p->steps.push_back(s);
+      // Register-resident rows need 16-byte aligned buffers; otherwise the cluster kernel takes over.
+      p->aligned_inputs  = layernorm ? std::vector<int>{x_in, gamma_in, beta_in} : std::vector<int>{x_in};
+      p->aligned_outputs = {0};
+      p->steps_unaligned.push_back(slow);
+    } else {
+      p->steps.push_back(slow);
+    }
+    return true;
+  }
+
+  // softmax op along the last axis: cinn/hlir/pe/nn.cc:755-796 (exp(x)/sum exp(x)); 16-bit storage as
+  // cast(softmax(cast(%0))).  Also the decomposed "fast" form of cinn/frontend/decomposer/activation.cc:70-118:
+  // divide(exp(x), broadcast_to(reduce_sum(exp(x)))).
+  std::unique_ptr<CompiledGroup> MatchSoftmax(const std::string& expr) {
+    bool half = false;
+    if (expr == "softmax(%0)" || expr == "divide(exp(%0),broadcast_to(reduce_sum(exp(%0))))") {
+    } else if (expr == "cast(softmax(cast(%0)))" ||
+               expr == "cast(divide(exp(cast(%0)),broadcast_to(reduce_sum(exp(cast(%0))))))") {
+      half = true;
+    } else {
+      return nullptr;
+    }
+    const auto &x = g.inputs[0], &o = g.outputs[0];
+    if (x.shape.empty() || o.shape != x.shape) return nullptr;
+    if (half ? (x.dtype != DType::kFloat16 || o.dtype != DType::kFloat16)
+             : (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32))
+      return nullptr;
+    const int nd = (int)x.shape.size();
+    for (auto& op : g.ops) {
+      if (op.type == "softmax") {
+        int64_t axis = AttrI(op, "axis", -1);
+        auto axes    = AttrList(op, "axes");
+        if (!axes.empty()) axis = axes[0];
+        if (axes.size() > 1 || !(axis == -1 || axis == nd - 1)) {
+          Fail("softmax is prebuilt for the last axis only");
+          return nullptr;
+        }
+      } else if (op.type == "reduce_sum") {
+        auto dims = AttrList(op, "dim");
+        if (dims.size() != 1 || !(dims[0] == -1 || dims[0] == nd - 1)) {
+          Fail("decomposed softmax must reduce the last axis");
+          return nullptr;
+        }
+      }
+    }
+    const int64_t cols = x.shape.back(), rows = x.numel() / std::max<int64_t>(cols, 1);
+    auto p = NewPlan("softmax_row");
+    if (!PlanRowNorm(p.get(), false, half, rows, cols, 0.0, 0, 0, 0)) return nullptr;
+    return p;
+  }
+
+  // layer_norm composition over [rows, cols] (cinn/frontend/op_mappers/paddle/layer_norm.cc:84-139 with
+  // rsqrt+multiply): inputs x, gamma, beta.  The expression below is what LayerNormExpr() prints for the op
+  // sequence built by the frontend helper; constants are checked against the shapes.
+  static std::string LayerNormExpr(bool half) {
+    const std::string x    = half ? "cast(%0)" : "%0";
+    const std::string n    = "fill_constant()";
+    const std::string mean = "divide(reduce_sum(" + x + ")," + n + ")";
+    const std::string m2   = "divide(reduce_sum(elementwise_mul(" + x + ",identity(" + x + ")))," + n + ")";
+    const std::string var  = "max(subtract(" + m2 + ",elementwise_mul(" + mean + ",identity(" + mean + "))),fill_constant())";
+    const std::string rstd = "rsqrt(elementwise_add(" + var + ",fill_constant()))";
+    const std::string xn   = "elementwise_mul(subtract(" + x + ",broadcast_to(" + mean + ")),broadcast_to(" + rstd + "))";
+    const std::string y    = "elementwise_add(elementwise_mul(" + xn + ",broadcast_to(%1)),broadcast_to(%2))";
+    return half ? "cast(" + y + ")" : y;
+  }
+
+  std::unique_ptr<CompiledGroup> MatchLayerNorm(const std::string& expr) {
+    bool half = false;
+    if (expr == LayerNormExpr(false)) {
+    } else if (expr == LayerNormExpr(true)) {
+      half = true;
+    } else {
+      return nullptr;
+    }
+    if (g.inputs.size() != 3) return nullptr;
+    const auto &x = g.inputs[0], &gamma = g.inputs[1], &beta = g.inputs[2], &o = g.outputs[0];
+    if (x.shape.size() != 2 || o.shape != x.shape) return nullptr;
+    if (half ? (x.dtype != DType::kFloat16 || o.dtype != DType::kFloat16)
+             : (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32))
+      return nullptr;
+    const int64_t rows = x.shape[0], cols = x.shape[1];
+    if (gamma.dtype != DType::kFloat32 || beta.dtype != DType::kFloat32 || gamma.shape != std::vector<int64_t>{cols} ||
+        beta.shape != std::vector<int64_t>{cols}) {
+      Fail("layer_norm gamma/beta must be float32 vectors of the row length");
+      return nullptr;
+    }
+    // Constants: the element count, zero and epsilon, identified by the op that consumes them.
+    double eps = -1.0;
+    for (auto& op : g.ops) {
+      if (op.type == "divide") {
+        const OpDesc* c = ProducerOfType(op.inputs[1], "fill_constant");
+        if (!c || AttrF(*c, "value", 0) != (double)cols) {
+          Fail("layer_norm divisor constant is not the row length");
+          return nullptr;
+        }
+      } else if (op.type == "max") {
+        const OpDesc* c = ProducerOfType(op.inputs[1], "fill_constant");
+        if (!c || AttrF(*c, "value", 1) != 0.0) {
+          Fail("layer_norm variance clamp constant is not 0");
+          return nullptr;
+        }
+      } else if (op.type == "elementwise_add") {
+        const OpDesc* c = ProducerOfType(op.inputs[1], "fill_constant");
+        if (c) eps = (float)AttrF(*c, "value", 0);
+      } else if (op.type == "reduce_sum") {
+        auto dims = AttrList(op, "dim");
+        if (dims.size() != 1 || !(dims[0] == 1 || dims[0] == -1)) {
+          Fail("layer_norm reductions must be over axis 1");
+          return nullptr;
+        }
+      }
+    }
+    if (eps < 0) {
+      Fail("layer_norm epsilon constant not found");
+      return nullptr;
+    }
+    auto p = NewPlan("layernorm_row");
+    if (!PlanRowNorm(p.get(), true, half, rows, cols, eps, 0, 1, 2)) return nullptr;
+    return p;
+  }
+
+  std::unique_ptr<CompiledGroup> Run() {
+    if (g.outputs.size() != 1) {
+      Fail("groups with " + std::to_string(g.outputs.size()) + " outputs have no prebuilt kernel");
+      return nullptr;
+    }
+    std::string e;
+    std::string expr = CanonicalExpr(g, &e);
+    if (expr.empty()) {
+      Fail(e);
+      return nullptr;
+    }
+    if (err) err->clear();
+    typedef std::unique_ptr<CompiledGroup> (Matcher::*Fn)(const std::string&);
+    const Fn fns[] = {&Matcher::MatchAddRelu, &Matcher::MatchBiasScaleTanhCast, &Matcher::MatchBatchNorm,
+                      &Matcher::MatchReduce,  &Matcher::MatchSoftmax,           &Matcher::MatchLayerNorm};
+    for (Fn f : fns) {
+      auto p = (this->*f)(expr);
+      if (p) return p;
+      if (err && !err->empty()) return nullptr;  // a matcher recognised the form but rejected its details
+    }
+    Fail("no prebuilt sm_100a kernel matches expression " + expr);
+    return nullptr;
+  }
+};
+
+}  // namespace
+
+std::unique_ptr<CompiledGroup> CompileGroup(const GroupDesc& g, const DeviceInfo& dev, std::string* err) {
+  std::string local;
+  Matcher m(g, dev, err ? err : &local);
+  return m.Run();
+}
+
+}  // namespace cinn_b200

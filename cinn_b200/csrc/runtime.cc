@@ -1,0 +1,549 @@
+// C-ABI launch layer: kernel table, launch primitive, fused-group registry and entry points.
+//
+// It takes the place of cinn/runtime/cuda/cuda_util.cc:78-118 (cinn_call_cuda_kernel), of the per-group host
+// stubs the reference JIT-compiles (cinn/backends/codegen_cuda_host.cc:35-170: unpack the pod array, call the
+// launch primitive with the kernel handle and its grid/block) and of the name -> function lookup used to
+// build Instructions (cinn/backends/llvm/execution_engine.cc:221-230).
+#include <cuda_runtime.h>
+
+#include <array>
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+#include <utility>
+
+#include "../../include/cinn_b200.h"
+#include "group_desc.h"
+
+namespace cinn_b200 {
+
+// ---- kernel table ---------------------------------------------------------------------------------
+static std::vector<KernelEntry>& Table() {
+  static std::vector<KernelEntry> t;
+  return t;
+}
+int RegisterKernel(const char* name, const void* fn, int num_params, int max_threads) {
+  Table().push_back(KernelEntry{name, fn, num_params, max_threads});
+  return (int)Table().size() - 1;
+}
+const KernelEntry* FindKernel(const std::string& name) {
+  for (auto& e : Table())
+    if (name == e.name) return &e;
+  return nullptr;
+}
+const KernelEntry* FindKernelByFn(const void* fn) {
+  for (auto& e : Table())
+    if (e.fn == fn) return &e;
+  return nullptr;
+}
+const std::vector<KernelEntry>& AllKernels() { return Table(); }
+
+// ---- errors ---------------------------------------------------------------------------------------
+static thread_local std::string tls_error;
+
+static int SetError(int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  tls_error = buf;
+  if (getenv("CINN_B200_VERBOSE")) fprintf(stderr, "[cinn_b200] error %d: %s\n", code, buf);
+  return code;
+}
+
+static void FatalIfRequested() {
+  if (getenv("CINN_B200_ABORT_ON_ERROR")) {
+    fprintf(stderr, "[cinn_b200] fatal: %s\n", tls_error.c_str());
+    abort();
+  }
+}
+
+static std::atomic<long long> g_launches{0};
+
+// ---- options ----------------------------------------------------------------------------------------
+static std::mutex g_mu;
+static int g_opt_sm_count = 0;  // 0: query the device, or 148 without one
+
+static DeviceInfo CurrentDeviceInfo() {
+  DeviceInfo d;
+  if (g_opt_sm_count > 0) {
+    d.sm_count = g_opt_sm_count;
+    return d;
+  }
+  int count = 0;
+  if (cudaGetDeviceCount(&count) == cudaSuccess && count > 0) {
+    int dev = 0, sms = 0, smem = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+      d.sm_count = sms;
+    if (cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) == cudaSuccess && smem > 0)
+      d.max_smem_optin = smem;
+  } else {
+    (void)cudaGetLastError();  // no driver / no device: planning proceeds with the B200 defaults
+  }
+  return d;
+}
+
+// ---- launch primitive -------------------------------------------------------------------------------
+static int LaunchKernel(const void* kernel_fn, void* v_args, int num_args, int gx, int gy, int gz, int bx, int by,
+                        int bz, unsigned cluster_x, size_t dyn_smem, void* stream) {
+  if (!kernel_fn || (!v_args && num_args > 0) || num_args < 0 || num_args > 64)
+    return SetError(CINN_B200_EINVAL, "cinn_call_cuda_kernel: bad kernel handle or argument array (num_args=%d)",
+                    num_args);
+  const KernelEntry* entry = FindKernelByFn(kernel_fn);
+  if (!entry) return SetError(CINN_B200_ENOTFOUND, "cinn_call_cuda_kernel: %p is not a kernel of this library", kernel_fn);
+  if (num_args != entry->num_params)
+    return SetError(CINN_B200_EINVAL, "kernel %s takes %d parameters, got %d", entry->name, entry->num_params, num_args);
+  if (gx <= 0 || gy <= 0 || gz <= 0 || bx <= 0 || by <= 0 || bz <= 0 ||
+      (long long)bx * by * bz > entry->max_threads)
+    return SetError(CINN_B200_EINVAL, "kernel %s: bad launch shape grid=(%d,%d,%d) block=(%d,%d,%d), max %d threads",
+                    entry->name, gx, gy, gz, bx, by, bz, entry->max_threads);
+  // cuda_util.cc:94-104: a buffer passes the address of its `memory` field, anything else its payload address.
+  void* params[64];
+  cinn_pod_value_t* args = static_cast<cinn_pod_value_t*>(v_args);
+  for (int i = 0; i < num_args; ++i) {
+    if (args[i].type_code_ == CINN_POD_BUFFERP) {
+      cinn_buffer_t* b = static_cast<cinn_buffer_t*>(args[i].value_.v_handle);
+      if (!b) return SetError(CINN_B200_EINVAL, "kernel %s: argument %d is a null cinn_buffer_t*", entry->name, i);
+      params[i] = &b->memory;
+    } else {
+      params[i] = &args[i].value_;
+    }
+  }
+  if (dyn_smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel_fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem);
+    if (e != cudaSuccess)
+      return SetError(CINN_B200_ECUDA, "kernel %s: cannot reserve %zu bytes of shared memory: %s", entry->name,
+                      dyn_smem, cudaGetErrorString(e));
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim          = dim3(gx, gy, gz);
+  cfg.blockDim         = dim3(bx, by, bz);
+  cfg.dynamicSmemBytes = dyn_smem;
+  cfg.stream           = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  if (cluster_x > 1) {
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster_x;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs                = attr;
+    cfg.numAttrs             = 1;
+  }
+  cudaError_t e = cudaLaunchKernelExC(&cfg, kernel_fn, params);
+  if (e != cudaSuccess)
+    return SetError(CINN_B200_ECUDA, "launch of %s grid=(%d,%d,%d) block=(%d,%d,%d) cluster=%u smem=%zu failed: %s",
+                    entry->name, gx, gy, gz, bx, by, bz, cluster_x, dyn_smem, cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return CINN_B200_OK;
+}
+
+// ---- group registry ---------------------------------------------------------------------------------
+constexpr int kMaxGroups = 1024;
+
+struct HostStaging {
+  void* dev        = nullptr;
+  size_t bytes     = 0;
+  cudaStream_t s   = nullptr;
+};
+
+struct GroupSlot {
+  std::unique_ptr<CompiledGroup> plan;
+  std::unordered_map<int, void*> scratch;        // device ordinal -> scratch buffer
+  std::unordered_map<int, HostStaging> staging;  // device ordinal -> staging for run_host
+};
+
+static GroupSlot g_slots[kMaxGroups];
+static std::unordered_map<std::string, int> g_slot_of_name;
+
+static int RunSlot(int slot, void* pod_args, int num_args, void* stream);
+
+template <int I>
+static void Trampoline(void* args, int32_t num_args, void* stream) {
+  if (RunSlot(I, args, num_args, stream) != CINN_B200_OK) FatalIfRequested();
+}
+
+template <int... Is>
+static constexpr std::array<lower_func_ptr_g, sizeof...(Is)> MakeTrampolines(std::integer_sequence<int, Is...>) {
+  return {{&Trampoline<Is>...}};
+}
+static const std::array<lower_func_ptr_g, kMaxGroups> g_trampolines =
+    MakeTrampolines(std::make_integer_sequence<int, kMaxGroups>());
+
+static bool IsAligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int TypeMatches(const cinn_buffer_t* b, DType t) {
+  const int code = (int)b->type.code, bits = b->type.bits;
+  switch (t) {
+    case DType::kFloat32: return code == cinn_type_float && bits == 32;
+    case DType::kFloat16: return code == cinn_type_float && bits == 16;
+    case DType::kBFloat16: return code == cinn_type_bfloat && bits == 16;
+    case DType::kFloat64: return code == cinn_type_float && bits == 64;
+    case DType::kInt32: return code == cinn_type_int && bits == 32;
+    case DType::kInt64: return code == cinn_type_int && bits == 64;
+    case DType::kBool: return code == cinn_type_int && bits == 1;
+    case DType::kUInt8: return code == cinn_type_uint && bits == 8;
+    default: return 0;
+  }
+}
+
+// Checks the pod array against the compiled group and returns the buffers (inputs then outputs).
+static int CheckArgs(const CompiledGroup& plan, void* pod_args, int num_args, std::vector<cinn_buffer_t*>* bufs) {
+  const int n_in = (int)plan.inputs.size(), n_out = (int)plan.outputs.size();
+  if (!pod_args) return SetError(CINN_B200_EINVAL, "group %s: null argument array", plan.name.c_str());
+  if (num_args != n_in + n_out)
+    return SetError(CINN_B200_EINVAL, "group %s takes %d inputs + %d outputs, got %d arguments", plan.name.c_str(),
+                    n_in, n_out, num_args);
+  cinn_pod_value_t* args = static_cast<cinn_pod_value_t*>(pod_args);
+  bufs->resize(num_args);
+  for (int i = 0; i < num_args; ++i) {
+    const TensorDesc& t = i < n_in ? plan.inputs[i] : plan.outputs[i - n_in];
+    if (args[i].type_code_ != CINN_POD_BUFFERP)
+      return SetError(CINN_B200_EINVAL, "group %s: argument %d (%s) has type code %d, expected a cinn_buffer_t* (7)",
+                      plan.name.c_str(), i, t.name.c_str(), args[i].type_code_);
+    cinn_buffer_t* b = static_cast<cinn_buffer_t*>(args[i].value_.v_handle);
+    if (!b || !b->memory)
+      return SetError(CINN_B200_EINVAL, "group %s: argument %d (%s) has no memory", plan.name.c_str(), i,
+                      t.name.c_str());
+    if (!TypeMatches(b, t.dtype))
+      return SetError(CINN_B200_ESHAPE, "group %s: argument %d (%s) has type code %d/%d bits, compiled for %s",
+                      plan.name.c_str(), i, t.name.c_str(), (int)b->type.code, (int)b->type.bits, DTypeName(t.dtype));
+    if (b->dimensions < 0 || b->dimensions > CINN_BUFFER_MAX_DIMS)
+      return SetError(CINN_B200_ESHAPE, "group %s: argument %d (%s) has %d dimensions", plan.name.c_str(), i,
+                      t.name.c_str(), b->dimensions);
+    long long numel = 1;
+    for (int d = 0; d < b->dimensions; ++d) numel *= b->dims[d];
+    if (numel != t.numel())
+      return SetError(CINN_B200_ESHAPE, "group %s: argument %d (%s) has %lld elements, compiled for %lld",
+                      plan.name.c_str(), i, t.name.c_str(), numel, (long long)t.numel());
+    (*bufs)[i] = b;
+  }
+  return CINN_B200_OK;
+}
+
+static int RunPlan(GroupSlot& slot, const std::vector<cinn_buffer_t*>& bufs, void* stream) {
+  const CompiledGroup& plan = *slot.plan;
+  const int n_in            = (int)plan.inputs.size();
+  // Device scratch (split reductions only), one buffer per device, allocated on first use.
+  uint8_t* scratch = nullptr;
+  if (plan.scratch_bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaGetDevice failed");
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = slot.scratch.find(dev);
+    if (it == slot.scratch.end()) {
+      void* p       = nullptr;
+      cudaError_t e = cudaMalloc(&p, plan.scratch_bytes);
+      if (e != cudaSuccess)
+        return SetError(CINN_B200_ECUDA, "group %s: cudaMalloc of %zu scratch bytes failed: %s", plan.name.c_str(),
+                        plan.scratch_bytes, cudaGetErrorString(e));
+      it = slot.scratch.emplace(dev, p).first;
+    }
+    scratch = static_cast<uint8_t*>(it->second);
+  }
+  const std::vector<LaunchStep>* steps = &plan.steps;
+  if (!plan.steps_unaligned.empty()) {
+    bool ok = true;
+    for (int i : plan.aligned_inputs) ok = ok && IsAligned16(bufs[i]->memory);
+    for (int i : plan.aligned_outputs) ok = ok && IsAligned16(bufs[n_in + i]->memory);
+    if (!ok) steps = &plan.steps_unaligned;
+  }
+  for (const LaunchStep& s : *steps) {
+    cinn_pod_value_t pods[64];
+    cinn_buffer_t scratch_bufs[8];
+    int n_scratch = 0;
+    const int n   = (int)s.args.size();
+    for (int i = 0; i < n; ++i) {
+      const ArgSpec& a = s.args[i];
+      switch (a.kind) {
+        case ArgSpec::kInput:
+          pods[i].type_code_      = CINN_POD_BUFFERP;
+          pods[i].value_.v_handle = bufs[a.index];
+          break;
+        case ArgSpec::kOutput:
+          pods[i].type_code_      = CINN_POD_BUFFERP;
+          pods[i].value_.v_handle = bufs[n_in + a.index];
+          break;
+        case ArgSpec::kScratch: {
+          if (n_scratch >= 8) return SetError(CINN_B200_EINVAL, "too many scratch arguments");
+          cinn_buffer_t* sb = &scratch_bufs[n_scratch++];
+          memset(sb, 0, sizeof(*sb));
+          sb->memory              = scratch + a.ivalue;
+          pods[i].type_code_      = CINN_POD_BUFFERP;
+          pods[i].value_.v_handle = sb;
+          break;
+        }
+        case ArgSpec::kInt:
+          pods[i].type_code_     = CINN_POD_INT64;
+          pods[i].value_.v_int64 = a.ivalue;
+          break;
+        case ArgSpec::kFloat:
+          pods[i].type_code_       = CINN_POD_DOUBLE;
+          pods[i].value_.v_float64 = a.fvalue;
+          break;
+        case ArgSpec::kAligned: {
+          bool ok = a.ivalue != 0;
+          for (int k : a.aligned_inputs) ok = ok && IsAligned16(bufs[k]->memory);
+          for (int k : a.aligned_outputs) ok = ok && IsAligned16(bufs[n_in + k]->memory);
+          pods[i].type_code_     = CINN_POD_INT64;
+          pods[i].value_.v_int64 = ok ? 1 : 0;
+          break;
+        }
+      }
+    }
+    int rc = LaunchKernel(s.kernel->fn, pods, n, s.grid[0], s.grid[1], s.grid[2], s.block[0], s.block[1], s.block[2],
+                          s.cluster, s.dyn_smem, stream);
+    if (rc != CINN_B200_OK) return rc;
+  }
+  return CINN_B200_OK;
+}
+
+static int RunSlot(int slot_index, void* pod_args, int num_args, void* stream) {
+  GroupSlot& slot = g_slots[slot_index];
+  if (!slot.plan) return SetError(CINN_B200_ENOTFOUND, "entry point %d is not bound to a compiled group", slot_index);
+  std::vector<cinn_buffer_t*> bufs;
+  int rc = CheckArgs(*slot.plan, pod_args, num_args, &bufs);
+  if (rc != CINN_B200_OK) return rc;
+  return RunPlan(slot, bufs, stream);
+}
+
+static int SlotOf(const char* fn_name) {
+  if (!fn_name) return -1;
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_slot_of_name.find(fn_name);
+  return it == g_slot_of_name.end() ? -1 : it->second;
+}
+
+static void FreeSlotResources(GroupSlot& s) {
+  for (auto& kv : s.scratch) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(kv.first);
+    cudaFree(kv.second);
+    cudaSetDevice(prev);
+  }
+  for (auto& kv : s.staging) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(kv.first);
+    if (kv.second.dev) cudaFree(kv.second.dev);
+    if (kv.second.s) cudaStreamDestroy(kv.second.s);
+    cudaSetDevice(prev);
+  }
+  s.scratch.clear();
+  s.staging.clear();
+  s.plan.reset();
+}
+
+}  // namespace cinn_b200
+
+using namespace cinn_b200;
+
+extern "C" {
+
+const char* cinn_b200_last_error(void) { return tls_error.c_str(); }
+
+void cinn_call_cuda_kernel(void* kernel_fn, void* v_args, int num_args, int grid_x, int grid_y, int grid_z,
+                           int block_x, int block_y, int block_z, void* stream) {
+  if (LaunchKernel(kernel_fn, v_args, num_args, grid_x, grid_y, grid_z, block_x, block_y, block_z, 0, 0, stream) !=
+      CINN_B200_OK)
+    FatalIfRequested();
+}
+
+int cinn_b200_call_cuda_kernel_ex(void* kernel_fn, void* v_args, int num_args, int grid_x, int grid_y, int grid_z,
+                                  int block_x, int block_y, int block_z, unsigned cluster_x, size_t dyn_smem,
+                                  void* stream) {
+  return LaunchKernel(kernel_fn, v_args, num_args, grid_x, grid_y, grid_z, block_x, block_y, block_z, cluster_x,
+                      dyn_smem, stream);
+}
+
+void* cinn_b200_get_kernel(const char* kernel_name) {
+  const KernelEntry* e = kernel_name ? FindKernel(kernel_name) : nullptr;
+  if (!e) {
+    SetError(CINN_B200_ENOTFOUND, "no kernel named '%s'", kernel_name ? kernel_name : "(null)");
+    return nullptr;
+  }
+  return const_cast<void*>(e->fn);
+}
+
+int cinn_b200_num_kernels(void) { return (int)AllKernels().size(); }
+
+const char* cinn_b200_kernel_name(int index) {
+  if (index < 0 || index >= (int)AllKernels().size()) return nullptr;
+  return AllKernels()[index].name;
+}
+
+int cinn_b200_kernel_num_params(const char* kernel_name) {
+  const KernelEntry* e = kernel_name ? FindKernel(kernel_name) : nullptr;
+  if (!e) return SetError(CINN_B200_ENOTFOUND, "no kernel named '%s'", kernel_name ? kernel_name : "(null)");
+  return e->num_params;
+}
+
+long long cinn_b200_launch_count(void) { return g_launches.load(); }
+
+int cinn_b200_compile_group(const char* group_desc, lower_func_ptr_g* fn_out) {
+  if (!group_desc) return SetError(CINN_B200_EINVAL, "null group description");
+  GroupDesc g;
+  std::string err;
+  if (!ParseGroupDesc(group_desc, &g, &err)) return SetError(CINN_B200_EINVAL, "%s", err.c_str());
+  DeviceInfo dev = CurrentDeviceInfo();
+  auto plan      = CompileGroup(g, dev, &err);
+  if (!plan) return SetError(CINN_B200_ENOMATCH, "%s", err.c_str());
+  std::lock_guard<std::mutex> lk(g_mu);
+  int slot = -1;
+  auto it  = g_slot_of_name.find(g.name);
+  if (it != g_slot_of_name.end()) {
+    slot = it->second;
+    FreeSlotResources(g_slots[slot]);
+  } else {
+    for (int i = 0; i < kMaxGroups; ++i)
+      if (!g_slots[i].plan) {
+        slot = i;
+        break;
+      }
+    if (slot < 0) return SetError(CINN_B200_ENOSPACE, "all %d entry points are in use; release some groups", kMaxGroups);
+    g_slot_of_name[g.name] = slot;
+  }
+  g_slots[slot].plan = std::move(plan);
+  if (fn_out) *fn_out = g_trampolines[slot];
+  return CINN_B200_OK;
+}
+
+lower_func_ptr_g cinn_b200_lookup(const char* fn_name) {
+  int slot = SlotOf(fn_name);
+  if (slot < 0) {
+    SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+    return nullptr;
+  }
+  return g_trampolines[slot];
+}
+
+int cinn_b200_release_group(const char* fn_name) {
+  int slot = SlotOf(fn_name);
+  if (slot < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  std::lock_guard<std::mutex> lk(g_mu);
+  FreeSlotResources(g_slots[slot]);
+  g_slot_of_name.erase(fn_name);
+  return CINN_B200_OK;
+}
+
+int cinn_b200_group_run(const char* fn_name, void* pod_args, int num_args, void* stream) {
+  int slot = SlotOf(fn_name);
+  if (slot < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  return RunSlot(slot, pod_args, num_args, stream);
+}
+
+static int CopyOut(const std::string& s, char* out, size_t len) {
+  if (!out || len == 0) return CINN_B200_OK;
+  if (s.size() + 1 > len) return SetError(CINN_B200_ENOSPACE, "caller buffer of %zu bytes is too small for %zu", len, s.size() + 1);
+  memcpy(out, s.c_str(), s.size() + 1);
+  return CINN_B200_OK;
+}
+
+int cinn_b200_group_info(const char* fn_name, char* pattern, size_t pattern_len, long long* algorithmic_bytes,
+                         long long* elements, int* launches, long long* scratch_bytes) {
+  int slot = SlotOf(fn_name);
+  if (slot < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  const CompiledGroup& p = *g_slots[slot].plan;
+  if (algorithmic_bytes) *algorithmic_bytes = p.algorithmic_bytes;
+  if (elements) *elements = p.elements;
+  if (launches) *launches = (int)p.steps.size();
+  if (scratch_bytes) *scratch_bytes = (long long)p.scratch_bytes;
+  return CopyOut(p.pattern, pattern, pattern_len);
+}
+
+int cinn_b200_group_kernel(const char* fn_name, int step, char* name, size_t name_len) {
+  int slot = SlotOf(fn_name);
+  if (slot < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  const CompiledGroup& p = *g_slots[slot].plan;
+  if (step < 0 || step >= (int)p.steps.size()) return SetError(CINN_B200_EINVAL, "group %s has %zu launch steps", fn_name, p.steps.size());
+  return CopyOut(p.steps[step].kernel->name, name, name_len);
+}
+
+int cinn_b200_canonical_expr(const char* group_desc, char* out, size_t out_len) {
+  if (!group_desc) return SetError(CINN_B200_EINVAL, "null group description");
+  GroupDesc g;
+  std::string err;
+  if (!ParseGroupDesc(group_desc, &g, &err)) return SetError(CINN_B200_EINVAL, "%s", err.c_str());
+  std::string e = CanonicalExpr(g, &err);
+  if (e.empty()) return SetError(CINN_B200_EINVAL, "%s", err.c_str());
+  return CopyOut(e, out, out_len);
+}
+
+int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, int device) {
+  int slot_index = SlotOf(fn_name);
+  if (slot_index < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  GroupSlot& slot           = g_slots[slot_index];
+  const CompiledGroup& plan = *slot.plan;
+  std::vector<cinn_buffer_t*> host;
+  int rc = CheckArgs(plan, pod_args, num_args, &host);
+  if (rc != CINN_B200_OK) return rc;
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
+  // One staging allocation per (group, device): [inputs..., outputs...] each 256-byte aligned.
+  const int n_in = (int)plan.inputs.size();
+  std::vector<size_t> offs(num_args), sizes(num_args);
+  size_t total = 0;
+  for (int i = 0; i < num_args; ++i) {
+    const TensorDesc& t = i < n_in ? plan.inputs[i] : plan.outputs[i - n_in];
+    sizes[i]            = (size_t)t.numel() * DTypeBytes(t.dtype);
+    offs[i]             = total;
+    total += (sizes[i] + 255) / 256 * 256;
+  }
+  HostStaging* st = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    st = &slot.staging[device];
+  }
+  if (st->bytes < total) {
+    if (st->dev) cudaFree(st->dev);
+    st->dev = nullptr;
+    e       = cudaMalloc(&st->dev, total);
+    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaMalloc of %zu staging bytes: %s", total, cudaGetErrorString(e));
+    st->bytes = total;
+  }
+  if (!st->s) {
+    e = cudaStreamCreateWithFlags(&st->s, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
+  }
+  std::vector<cinn_buffer_t> dev_bufs(num_args);
+  std::vector<cinn_pod_value_t> dev_pods(num_args);
+  for (int i = 0; i < num_args; ++i) {
+    dev_bufs[i]                  = *host[i];
+    dev_bufs[i].memory           = static_cast<uint8_t*>(st->dev) + offs[i];
+    dev_bufs[i].external_malloc  = nullptr;
+    dev_bufs[i].external_free    = nullptr;
+    dev_pods[i].type_code_       = CINN_POD_BUFFERP;
+    dev_pods[i].value_.v_handle  = &dev_bufs[i];
+  }
+  for (int i = 0; i < n_in; ++i) {
+    e = cudaMemcpyAsync(dev_bufs[i].memory, host[i]->memory, sizes[i], cudaMemcpyHostToDevice, st->s);
+    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "host->device copy of %s: %s", plan.inputs[i].name.c_str(), cudaGetErrorString(e));
+  }
+  rc = RunSlot(slot_index, dev_pods.data(), num_args, st->s);
+  if (rc != CINN_B200_OK) return rc;
+  for (int i = n_in; i < num_args; ++i) {
+    e = cudaMemcpyAsync(host[i]->memory, dev_bufs[i].memory, sizes[i], cudaMemcpyDeviceToHost, st->s);
+    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "device->host copy of %s: %s", plan.outputs[i - n_in].name.c_str(), cudaGetErrorString(e));
+  }
+  e = cudaStreamSynchronize(st->s);
+  if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "group %s: %s", plan.name.c_str(), cudaGetErrorString(e));
+  return CINN_B200_OK;
+}
+
+int cinn_b200_set_option(const char* key, long long value) {
+  if (!key) return SetError(CINN_B200_EINVAL, "null option key");
+  if (!strcmp(key, "sm_count")) {
+    g_opt_sm_count = (int)value;
+    return CINN_B200_OK;
+  }
+  return SetError(CINN_B200_ENOTFOUND, "unknown option '%s'", key);
+}
+
+}  // extern "C"

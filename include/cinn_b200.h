@@ -1,0 +1,117 @@
+/*
+ * C ABI of the B200 fused-group kernel library (libcinn_b200.so).
+ *
+ * The library is a drop-in for one path of CINN: the kernels it generates at run time for HLIR fused op
+ * groups (elementwise / broadcast / reduction), the host stubs that launch them, and the launch primitive.
+ * Everything crosses this boundary as plain pointers and sizes; the argument structures are the
+ * reference's own (see cinn_runtime_abi.h).  No function here throws; functions returning int give 0 on
+ * success and a negative CINN_B200_E* code otherwise, with a message available from cinn_b200_last_error().
+ *
+ * Each declaration names the reference interface it replaces (paths are inside the CINN project).
+ */
+#ifndef CINN_B200_H_
+#define CINN_B200_H_
+
+#include "cinn_runtime_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CINN_B200_OK 0
+#define CINN_B200_EINVAL (-1)     /* malformed argument (null pointer, wrong count, wrong type tag) */
+#define CINN_B200_ENOMATCH (-2)   /* no prebuilt kernel covers the group (there is no fallback) */
+#define CINN_B200_ENOTFOUND (-3)  /* unknown function or kernel name */
+#define CINN_B200_ECUDA (-4)      /* a CUDA runtime call failed */
+#define CINN_B200_ESHAPE (-5)     /* a buffer's type or element count differs from the compiled group's */
+#define CINN_B200_ENOSPACE (-6)   /* table full / caller buffer too small */
+
+/* Message of the most recent failure on the calling thread ("" if none).  The pointer stays valid until the
+ * next failing call on the same thread.  Replaces the reference's LOG(FATAL)/abort convention
+ * (cinn/backends/cuda_util.h:30-45) with a status + message. */
+const char* cinn_b200_last_error(void);
+
+/* ---- launch primitive ----------------------------------------------------------------------------- */
+
+/*
+ * Same name, signature and argument unpacking as cinn/runtime/cuda/cuda_util.h:75-84 (implementation
+ * cinn/runtime/cuda/cuda_util.cc:78-118): v_args is a cinn_pod_value_t[num_args]; a buffer argument
+ * contributes the address of its `memory` field as the kernel parameter, any other argument the address
+ * of its 8-byte payload.  kernel_fn is a handle from cinn_b200_get_kernel() (the reference passes a
+ * CUfunction published as "<fn>_kernel_ptr_", cinn/backends/compiler.cc:133-140).  Dynamic shared memory
+ * is 0 as in the reference.  Failures are reported through cinn_b200_last_error() and, when the
+ * environment variable CINN_B200_ABORT_ON_ERROR is set, abort() like the reference does.
+ */
+void cinn_call_cuda_kernel(void* kernel_fn, void* v_args, int num_args, int grid_x, int grid_y, int grid_z,
+                           int block_x, int block_y, int block_z, void* stream);
+
+/* The same with a status result, a thread-block-cluster width (0 = none) and dynamic shared memory. */
+int cinn_b200_call_cuda_kernel_ex(void* kernel_fn, void* v_args, int num_args, int grid_x, int grid_y, int grid_z,
+                                  int block_x, int block_y, int block_z, unsigned cluster_x, size_t dyn_smem,
+                                  void* stream);
+
+/*
+ * Prebuilt-kernel table.  Replaces CUDAModule::GetFunction (cinn/runtime/cuda/cuda_module.cc:73-101) and
+ * the JIT symbol registration of cinn/runtime/cuda/cuda_intrinsics.cc:404-418: kernels are compiled
+ * offline for sm_100a and found by name.
+ */
+void* cinn_b200_get_kernel(const char* kernel_name);
+int cinn_b200_num_kernels(void);
+const char* cinn_b200_kernel_name(int index);
+int cinn_b200_kernel_num_params(const char* kernel_name);
+
+/* Number of kernel launches issued by this library in the calling process so far. */
+long long cinn_b200_launch_count(void);
+
+/* ---- fused groups ------------------------------------------------------------------------------- */
+
+/*
+ * Compile one fused group, given in the text form documented in INTEGRATION.md ("group/input/op/output"
+ * lines), to a launch plan over the prebuilt kernels and bind it to an entry point of the reference's
+ * type lower_func_ptr_g (cinn/runtime/cinn_runtime.h:497-499).  Replaces, for the groups it covers,
+ * ParallelCompiler::Task::Lowering + CodegenAndJit (cinn/hlir/framework/parallel_compiler.cc:123-199).
+ * The entry point takes cinn_pod_value_t[num_args] = the group's inputs then outputs, each a
+ * cinn_buffer_t* holding device memory (cinn/hlir/framework/instruction.cc:81-105), and a CUstream.
+ * Compiling the same name again replaces the earlier plan.  Needs no GPU.
+ */
+int cinn_b200_compile_group(const char* group_desc, lower_func_ptr_g* fn_out);
+
+/* By-name lookup, as backends::ExecutionEngine::Lookup (cinn/backends/llvm/execution_engine.cc:221-230)
+ * does for Instruction construction (cinn/hlir/framework/parallel_compiler.cc:201-217). NULL if unknown. */
+lower_func_ptr_g cinn_b200_lookup(const char* fn_name);
+
+/* Forget a compiled group and free its device scratch. */
+int cinn_b200_release_group(const char* fn_name);
+
+/* What lower_func_ptr_g does, with a status result instead of the last-error side channel. */
+int cinn_b200_group_run(const char* fn_name, void* pod_args, int num_args, void* stream);
+
+/* Facts about a compiled group: matched kernel family, bytes of inputs+outputs, elements, launches per run,
+ * device scratch bytes.  Any out pointer may be NULL. */
+int cinn_b200_group_info(const char* fn_name, char* pattern, size_t pattern_len, long long* algorithmic_bytes,
+                         long long* elements, int* launches, long long* scratch_bytes);
+
+/* Name of the kernel of launch step `step` of a compiled group (for tests and profiles). */
+int cinn_b200_group_kernel(const char* fn_name, int step, char* name, size_t name_len);
+
+/* The matcher's canonical expression of a group description, e.g. "relu(elementwise_add(%0,%1))". */
+int cinn_b200_canonical_expr(const char* group_desc, char* out, size_t out_len);
+
+/*
+ * Run a compiled group on HOST buffers: every cinn_buffer_t in pod_args holds host memory (pinned for full
+ * copy speed); inputs are copied to `device`, the group runs, outputs are copied back, and the call returns
+ * after the outputs are complete.  This is the path Tensor::from_numpy -> Program::Execute -> Tensor::numpy
+ * takes in the reference (cinn/frontend/computation.cc:186-240, cinn/pybind/framework.cc:116-172).
+ * Device staging memory is kept per group and device and reused by later calls.
+ */
+int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, int device);
+
+/* Tuning knobs (integers) read by the matcher when a group is compiled; unknown keys give CINN_B200_ENOTFOUND.
+ * "sm_count": SM count assumed when no GPU is visible (default 148). */
+int cinn_b200_set_option(const char* key, long long value);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* CINN_B200_H_ */
