@@ -29,6 +29,26 @@ __device__ __forceinline__ float x86_tanh(float x) {
     return (e - 1.0f) / (e + 1.0f);
   }
 }
+// The same function for kernels whose OUTPUT is a 16-bit float (tolerance 1e-2 relative): one ex2.approx and
+// one rcp.approx instead of the full-accuracy expf and the IEEE division.  fp32 relative error of the quotient
+// is about 2^-21, far below the 2^-11 spacing of fp16 / 2^-8 of bf16; close to zero, where 1-e cancels, the
+// odd series a - a^3/3 is used instead (relative error < 2e-8 for |a| < 0.02).
+__device__ __forceinline__ float x86_tanh_for_16bit_out(float x) {
+  const float a = fabsf(x);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * -2.885390082f));  // exp(-2a) = 2^(-2a*log2(e))
+  float r       = __fdividef(1.0f - e, 1.0f + e);
+  const float s = a * fmaf(a * a, -0.33333334f, 1.0f);
+  r             = a < 0.02f ? s : r;
+  return x < 0.0f ? -r : r;
+}
+// exp for kernels whose output is a 16-bit float: ex2.approx of x*log2(e).  The product's rounding error is
+// |x|*2^-24 in the exponent, i.e. a relative error of about |x|*4e-8 in the result, plus 2 ulp of ex2.approx.
+__device__ __forceinline__ float exp_for_16bit_out(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 1.4426950408889634f));
+  return e;
+}
 // cinn/backends/llvm/llvm_intrin_rule.h:105-113.
 __device__ __forceinline__ float x86_rsqrt(float x) { return 1.0f / sqrtf(x); }
 // cinn/lang/builtin.h:79-82.

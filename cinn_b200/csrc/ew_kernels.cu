@@ -63,6 +63,16 @@ __device__ __forceinline__ void store8<float>(float* p, const float (&f)[8]) {
               make_uint4(__float_as_uint(f[4]), __float_as_uint(f[5]), __float_as_uint(f[6]), __float_as_uint(f[7])));
 }
 
+// 16-bit outputs use the reduced-cost tanh (accuracy matched to the output type), fp32 outputs the exact x86 form.
+template <typename OutT>
+__device__ __forceinline__ float tanh_for(float t) {
+  return x86_tanh_for_16bit_out(t);
+}
+template <>
+__device__ __forceinline__ float tanh_for<float>(float t) {
+  return x86_tanh(t);
+}
+
 template <typename OutT>
 __global__ void __launch_bounds__(256)
     k_bias_scale_tanh_cast(const float* __restrict__ x, const float* __restrict__ bias, OutT* __restrict__ y,
@@ -88,14 +98,14 @@ __global__ void __launch_bounds__(256)
       unpack4(ld_keep16(bias + c0), *reinterpret_cast<float(*)[4]>(&fb[0]));
       unpack4(ld_keep16(bias + c0 + 4), *reinterpret_cast<float(*)[4]>(&fb[4]));
 #pragma unroll
-      for (int i = 0; i < 8; ++i) fy[i] = x86_tanh(fmaf(scale, fx[i] + fb[i], shift));
+      for (int i = 0; i < 8; ++i) fy[i] = tanh_for<OutT>(fmaf(scale, fx[i] + fb[i], shift));
       store8<OutT>(y + 8 * v, fy);
       unpack4(r2, *reinterpret_cast<float(*)[4]>(&fx[0]));
       unpack4(r3, *reinterpret_cast<float(*)[4]>(&fx[4]));
       unpack4(ld_keep16(bias + c1), *reinterpret_cast<float(*)[4]>(&fb[0]));
       unpack4(ld_keep16(bias + c1 + 4), *reinterpret_cast<float(*)[4]>(&fb[4]));
 #pragma unroll
-      for (int i = 0; i < 8; ++i) fy[i] = x86_tanh(fmaf(scale, fx[i] + fb[i], shift));
+      for (int i = 0; i < 8; ++i) fy[i] = tanh_for<OutT>(fmaf(scale, fx[i] + fb[i], shift));
       store8<OutT>(y + 8 * v1, fy);
     }
     for (; v < nvec; v += stride) {
@@ -106,13 +116,13 @@ __global__ void __launch_bounds__(256)
       unpack4(ld_keep16(bias + c0), *reinterpret_cast<float(*)[4]>(&fb[0]));
       unpack4(ld_keep16(bias + c0 + 4), *reinterpret_cast<float(*)[4]>(&fb[4]));
 #pragma unroll
-      for (int i = 0; i < 8; ++i) fy[i] = x86_tanh(fmaf(scale, fx[i] + fb[i], shift));
+      for (int i = 0; i < 8; ++i) fy[i] = tanh_for<OutT>(fmaf(scale, fx[i] + fb[i], shift));
       store8<OutT>(y + 8 * v, fy);
     }
     done = nvec << 3;
   }
   for (long long i = done + tid; i < n; i += stride) {
-    float t = x86_tanh(fmaf(scale, x[i] + bias[i % cols], shift));
+    float t = tanh_for<OutT>(fmaf(scale, x[i] + bias[i % cols], shift));
     Io<OutT>::store1(y + i, t);
   }
 }
@@ -140,6 +150,8 @@ __global__ void __launch_bounds__(256)
     const int c           = (int)(plane % channels);
     const float m = mean[c], s = scale[c], b = bias[c];
     const float d = sqrtf(var[c] + (float)eps_d);
+    // 16-bit storage: multiply by the reciprocal (one rounding more than the division, far inside 1e-2).
+    const float inv_d = 1.0f / d;
     const T* xp   = x + plane * hw;
     T* yp         = y + plane * hw;
     if (vec_ok) {
@@ -161,7 +173,7 @@ __global__ void __launch_bounds__(256)
             Io<T>::unpack(r[j], f);
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-              f[i] = ((f[i] - m) * s) / d + b;
+              f[i] = sizeof(T) == 2 ? ((f[i] - m) * s) * inv_d + b : ((f[i] - m) * s) / d + b;
               if (RELU) f[i] = x86_max(f[i], 0.0f);
             }
             st_stream16(yp + (long long)(v + j * B) * V, Io<T>::pack(f));
@@ -173,7 +185,8 @@ __global__ void __launch_bounds__(256)
       const long long begin = chunk * per;
       const long long end   = min(begin + per, hw);
       for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        float f = ((Io<T>::load1(xp + i) - m) * s) / d + b;
+        float f = Io<T>::load1(xp + i);
+        f       = sizeof(T) == 2 ? ((f - m) * s) * inv_d + b : ((f - m) * s) / d + b;
         if (RELU) f = x86_max(f, 0.0f);
         Io<T>::store1(yp + i, f);
       }

@@ -162,10 +162,11 @@ __global__ void __launch_bounds__(256) k_col_reduce(const float* __restrict__ x,
   const long long split  = blockIdx.z;
   const long long k0     = split * rows_per_split;
   const long long k1     = min(k0 + rows_per_split, r);
-  const long long col    = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long col0   = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long cstep  = (long long)gridDim.x * blockDim.x;  // the grid is sized for the vector path
   if (vec_ok) {
     const long long inner_v = inner >> 2;
-    if (col >= inner_v) return;
+    for (long long col = col0; col < inner_v; col += cstep)
     for (long long o = blockIdx.y; o < outer; o += gridDim.y) {
       const uint4* p = reinterpret_cast<const uint4*>(x + o * r * inner) + col;
       float a0 = Op::identity(), a1 = a0, a2 = a0, a3 = a0;
@@ -193,7 +194,7 @@ __global__ void __launch_bounds__(256) k_col_reduce(const float* __restrict__ x,
       reinterpret_cast<uint4*>(y + (split * outer + o) * inner)[col] = out;
     }
   } else {
-    if (col >= inner) return;
+    for (long long col = col0; col < inner; col += cstep)
     for (long long o = blockIdx.y; o < outer; o += gridDim.y) {
       const float* p = x + o * r * inner + col;
       float acc      = Op::identity();
