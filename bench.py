@@ -194,6 +194,42 @@ def side_groups(torch, dev, peak, only=None):
     return out
 
 
+PROFILE_GROUPS = {
+    "bias_scale_tanh_cast": lambda W: W.bias_scale_tanh_cast(HEADLINE_SHAPE),
+    "add_relu": lambda W: W.add_relu((256, 3, 224, 224), name="fn_add_relu_stacked"),
+    "reduce_sum": lambda W: W.reduce_sum_last((128, 1024, 1024)),
+    "reduce_max": lambda W: W.reduce_max_first((128, 1024, 1024)),
+    "softmax_f32": lambda W: W.softmax((16384, 4096)),
+    "softmax_f16": lambda W: W.softmax((16384, 4096), half=True),
+    "layer_norm_f32": lambda W: W.layer_norm((16384, 4096)),
+    "layer_norm_f16": lambda W: W.layer_norm((16384, 4096), half=True),
+    "bn_relu_f32": lambda W: W.bn_relu((256, 64, 112, 112)),
+    "bn_relu_f16": lambda W: W.bn_relu((256, 64, 112, 112), half=True),
+}
+
+
+def run_profile_case(args):
+    """One group alone, a handful of launches: the command that is run under ncu (and once without it)."""
+    import torch
+    import cinn_b200
+    from cinn_b200 import workloads as W
+    for kv in args.option or []:
+        k, v = kv.split("=")
+        cinn_b200._lib.check(cinn_b200.lib().cinn_b200_set_option(k.encode(), int(v)))
+    dev = torch.device("cuda", 0)
+    w = PROFILE_GROUPS[args.profile](W)
+    g = cinn_b200.FusedGroup(w.desc)
+    tmap = {np.dtype(np.float32): torch.float32, np.dtype(np.float16): torch.float16}
+    ins = [torch.from_numpy(a).to(dev) for a in w.inputs]
+    out = torch.empty(w.out_shape, dtype=tmap[np.dtype(w.out_dtype)], device=dev)
+    g.run(ins + [out])  # status-checked first launch
+    ms = time_group(g, [ins + [out]], iters=max(args.steps, 1), warmup=max(args.warmup, 1), torch=torch)
+    print(json.dumps({"profile": args.profile, "kernels": g.kernel_names(), "ms": ms,
+                      "bytes_per_launch": g.algorithmic_bytes,
+                      "GB/s": g.algorithmic_bytes / (ms * 1e-3) / 1e9}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -203,9 +239,14 @@ def main():
     ap.add_argument("--no-side-groups", action="store_true", help="skip the per-group table of the other configs")
     ap.add_argument("--only", nargs="*", default=None, help="side groups whose name contains one of these")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", choices=sorted(PROFILE_GROUPS), default=None,
+                    help="run only this group for --warmup + --steps launches (the small case captured by ncu)")
+    ap.add_argument("--option", nargs="*", default=None, help="planner options key=value (see cinn_b200_set_option)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.profile:
+        return run_profile_case(args)
 
     import torch
     import torch.distributed as dist

@@ -64,6 +64,8 @@ def lib():
         L.cinn_b200_canonical_expr.argtypes = [cs, ctypes.c_char_p, ctypes.c_size_t]
         L.cinn_b200_group_run_host.restype = ci
         L.cinn_b200_group_run_host.argtypes = [cs, vp, ci, ci]
+        L.cinn_b200_device_status.restype = ci
+        L.cinn_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         L.cinn_b200_set_option.restype = ci
         L.cinn_b200_set_option.argtypes = [cs, ll]
         _lib = L

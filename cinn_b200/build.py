@@ -19,6 +19,7 @@ SOURCES = [
     "ew_kernels.cu",
     "reduce_kernels.cu",
     "rownorm_kernels.cu",
+    "rownorm_tma.cu",
     "group_desc.cc",
     "group_match.cc",
     "runtime.cc",

@@ -94,6 +94,11 @@ struct CompiledGroup {
 struct DeviceInfo {
   int sm_count              = 148;
   int max_smem_optin        = 227 * 1024;
+  // Tuning knobs of the row-normalisation planner (0 = automatic).
+  int rownorm_stages        = 0;
+  int rownorm_ctas_per_sm   = 0;
+  int rownorm_rows_per_iter = 0;  // rows a CTA of the register-resident kernels takes per iteration
+  int enable_tma_rownorm    = -1;  // rows streamed through shared memory by bulk copies: 1 on, 0 off, -1 automatic
 };
 
 // Returns nullptr and fills *err when no prebuilt kernel covers the group.

@@ -9,7 +9,8 @@
 //
 // Arithmetic (the x86 path's, in fp32; T is only the storage type of x and out):
 //   softmax     e = exp(x); out = e / sum(e)                       (no max subtraction: pe/nn.cc:755-796)
-//   layer_norm  mean = sum(x)/N; var = max(sum(x*x)/N - mean*mean, 0); rstd = 1/sqrt(var+eps);
+//   layer_norm  mean = sum(x)/N; var = max(sum(x*x)/N - mean*mean, 0); rstd = 1/sqrt(var+eps)  [see k_rownorm_reg
+//               for the cheaper per-row forms used inside the 1e-5 reduction tolerance];
 //               out = fma((x-mean)*rstd, gamma, beta)              (cinn/frontend/op_mappers/paddle/layer_norm.cc:84-139
 //               with rsqrt+multiply in place of sqrt+divide; x*x is rounded before it is summed because a
 //               producer of a reduce is materialised, cinn/hlir/framework/op_lowering_util.cc:757-761)
@@ -43,111 +44,150 @@ __device__ __forceinline__ void row_iteration_space(long long& first_row, long l
 }
 
 // ------------------------------------------------------------------------------------------------
-// softmax, row in registers.  Requires cols % V == 0, 16-byte aligned pointers, cols <= G*VPT*V.
+// softmax / layer_norm with the rows in registers.  Requires cols % V == 0, 16-byte aligned pointers and
+// cols <= G*VPT*V.  A group of G threads owns R consecutive rows per iteration; all R*VPT 16-byte loads of a
+// thread are issued before the first use.  The rows are kept PACKED in registers (4 registers per 16 bytes
+// whatever the element type) and unpacked once for the statistics and once for the output, which is what
+// keeps the register count low enough for five 256-thread CTAs per SM.  For layer_norm the fp32 gamma/beta
+// slices are read through L1 once per iteration and reused for the R rows; the sums of the R rows are reduced
+// together with a single barrier (scratch double-buffered by iteration parity).
 // ------------------------------------------------------------------------------------------------
-template <typename T, int G, int VPT>
-__global__ void __launch_bounds__(G == 32 ? 256 : G)
-    k_softmax_row(const T* __restrict__ x, T* __restrict__ y, long long rows, long long cols) {
-  constexpr int V = Io<T>::kVec;
-  __shared__ float scratch[32];
-  long long row, row_stride;
-  int t;
-  row_iteration_space<G>(row, row_stride, t);
-  const int nvec = (int)(cols / V);
-  for (; row < rows; row += row_stride) {
-    const uint4* px = reinterpret_cast<const uint4*>(x + row * cols);
-    uint4* py       = reinterpret_cast<uint4*>(y + row * cols);
-    uint4 raw[VPT];
-#pragma unroll
-    for (int j = 0; j < VPT; ++j) {
-      const int v = t + j * G;
-      if (v < nvec) raw[j] = __ldcs(px + v);
-    }
-    float e[VPT][V];
-    float local = 0.0f;
-#pragma unroll
-    for (int j = 0; j < VPT; ++j) {
-      const int v = t + j * G;
-      if (v < nvec) {
-        Io<T>::unpack(raw[j], e[j]);
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-          e[j][i] = sizeof(T) == 2 ? exp_for_16bit_out(e[j][i]) : expf(e[j][i]);
-          local   = local + e[j][i];
-        }
-      }
-    }
-    const float s = group_allreduce<G, SumOp>(local, scratch);
-    // e * (1/s) instead of e / s: at most one more rounding (1.5 ulp), inside the 1e-5 bar of a reduction group.
-    const float inv_s = 1.0f / s;
-#pragma unroll
-    for (int j = 0; j < VPT; ++j) {
-      const int v = t + j * G;
-      if (v < nvec) {
-#pragma unroll
-        for (int i = 0; i < V; ++i) e[j][i] = e[j][i] * inv_s;
-        __stcs(py + v, Io<T>::pack(e[j]));
-      }
-    }
-  }
+// Resident CTAs per SM asked of the compiler: enough threads for about 80 KiB of loads in flight per SM.
+constexpr int RownormMinBlocks(int g, int vpt, int r) {
+  if (g == 32) return 5;
+  if (g >= 1024) return 1;
+  int threads = 5120 / (vpt * r);
+  if (threads > 2048) threads = 2048;
+  int blocks = (threads + g - 1) / g;
+  return blocks < 1 ? 1 : blocks;
 }
 
-// ------------------------------------------------------------------------------------------------
-// layer_norm, row in registers.  gamma/beta are fp32 and stay in L1 across the rows a CTA processes.
-// ------------------------------------------------------------------------------------------------
-template <typename T, int G, int VPT>
-__global__ void __launch_bounds__(G == 32 ? 256 : G)
-    k_layernorm_row(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
-                    T* __restrict__ y, long long rows, long long cols, double eps_d) {
-  constexpr int V = Io<T>::kVec;
-  __shared__ float scratch[32];
-  long long row, row_stride;
+template <typename T, int G, int VPT, int R, bool LAYERNORM>
+__global__ void __launch_bounds__(G == 32 ? 256 : G, RownormMinBlocks(G, VPT, R))
+    k_rownorm_reg(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                  T* __restrict__ y, long long rows, long long cols, double eps_d, double inv_n_d) {
+  constexpr int V      = Io<T>::kVec;
+  constexpr int NWARPS = G == 32 ? 1 : G / 32;
+  // layer_norm keeps the rows packed; softmax keeps exp(x) in fp32 (it is needed again for the output and
+  // costs a transcendental to recompute).
+  constexpr int KEEP = LAYERNORM ? 1 : V;
+  __shared__ __align__(16) float2 partial[2][R][32];
+  long long grp, grp_stride;
   int t;
-  row_iteration_space<G>(row, row_stride, t);
-  const int nvec  = (int)(cols / V);
-  const float eps = (float)eps_d;
-  const float n   = (float)cols;
-  for (; row < rows; row += row_stride) {
-    const uint4* px = reinterpret_cast<const uint4*>(x + row * cols);
-    uint4* py       = reinterpret_cast<uint4*>(y + row * cols);
-    uint4 raw[VPT];
+  row_iteration_space<G>(grp, grp_stride, t);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec    = (int)(cols / V);
+  const float eps   = (float)eps_d;
+  const float inv_n = (float)inv_n_d;
+  for (int it = 0; grp * R < rows; grp += grp_stride, ++it) {
+    const long long row0 = grp * R;
+    uint4 raw[R][VPT];
 #pragma unroll
-    for (int j = 0; j < VPT; ++j) {
-      const int v = t + j * G;
-      if (v < nvec) raw[j] = __ldcs(px + v);
+    for (int r = 0; r < R; ++r) {
+      const uint4* px = reinterpret_cast<const uint4*>(x + (row0 + r) * cols);
+#pragma unroll
+      for (int j = 0; j < VPT; ++j) {
+        const int v = t + j * G;
+        if (v < nvec && row0 + r < rows) raw[r][j] = __ldcs(px + v);
+      }
     }
-    float f[VPT][V];
-    float s1 = 0.0f, s2 = 0.0f;
+    float ev[R][VPT][KEEP];
+    float s1[R], s2[R];
 #pragma unroll
-    for (int j = 0; j < VPT; ++j) {
-      const int v = t + j * G;
-      if (v < nvec) {
-        Io<T>::unpack(raw[j], f[j]);
+    for (int r = 0; r < R; ++r) {
+      s1[r] = 0.0f;
+      s2[r] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          s1 = s1 + f[j][i];
-          s2 = s2 + f[j][i] * f[j][i];
+      for (int j = 0; j < VPT; ++j) {
+        const int v = t + j * G;
+        if (v < nvec && row0 + r < rows) {
+          float f[V];
+          Io<T>::unpack(raw[r][j], f);
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            if (LAYERNORM) {
+              s1[r] = s1[r] + f[i];
+              s2[r] = s2[r] + f[i] * f[i];
+            } else {
+              f[i]            = sizeof(T) == 2 ? exp_for_16bit_out(f[i]) : expf(f[i]);
+              ev[r][j][i % KEEP] = f[i];
+              s1[r]           = s1[r] + f[i];
+            }
+          }
+        }
+      }
+      s1[r] = warp_allreduce<SumOp>(s1[r]);
+      if (LAYERNORM) s2[r] = warp_allreduce<SumOp>(s2[r]);
+    }
+    if (G != 32) {
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) partial[it & 1][r][warp] = make_float2(s1[r], s2[r]);
+      }
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (NWARPS <= 8) {
+          // Every thread adds the per-warp partials itself (broadcast shared-memory reads, fixed order).
+          const float4* pp = reinterpret_cast<const float4*>(&partial[it & 1][r][0]);
+          float t1 = 0.0f, t2 = 0.0f;
+#pragma unroll
+          for (int w = 0; w < NWARPS / 2; ++w) {
+            const float4 q = pp[w];
+            t1             = (t1 + q.x) + q.z;
+            t2             = (t2 + q.y) + q.w;
+          }
+          s1[r] = t1;
+          s2[r] = t2;
+        } else {
+          float2 p = lane < NWARPS ? partial[it & 1][r][lane] : make_float2(0.0f, 0.0f);
+          s1[r]    = warp_allreduce<SumOp>(p.x);
+          if (LAYERNORM) s2[r] = warp_allreduce<SumOp>(p.y);
         }
       }
     }
-    s1 = group_allreduce<G, SumOp>(s1, scratch);
-    s2 = group_allreduce<G, SumOp>(s2, scratch);
-    const float mean = s1 / n;
-    const float var  = x86_max(s2 / n - mean * mean, 0.0f);
-    const float rstd = x86_rsqrt(var + eps);
+    // Per-row scalars.  These groups are in the reduction tolerance class (1e-5 relative), so the row
+    // statistics use a multiplication by 1/N and the hardware reciprocal square root (2 ulp) instead of two
+    // IEEE divisions and a square root per row and warp; softmax multiplies by 1/sum.
+    float a[R], m[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (LAYERNORM) {
+        m[r]            = s1[r] * inv_n;
+        const float var = x86_max(s2[r] * inv_n - m[r] * m[r], 0.0f);
+        a[r]            = rsqrtf(var + eps);
+      } else {
+        a[r] = 1.0f / s1[r];
+        m[r] = 0.0f;
+      }
+    }
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int v = t + j * G;
       if (v < nvec) {
         float g[V], b[V];
+        if (LAYERNORM) {
 #pragma unroll
-        for (int q = 0; q < V / 4; ++q) {
-          Io<float>::unpack(ld_keep16(gamma + (long long)v * V + 4 * q), g + 4 * q);
-          Io<float>::unpack(ld_keep16(beta + (long long)v * V + 4 * q), b + 4 * q);
+          for (int q = 0; q < V / 4; ++q) {
+            Io<float>::unpack(ld_keep16(gamma + (long long)v * V + 4 * q), g + 4 * q);
+            Io<float>::unpack(ld_keep16(beta + (long long)v * V + 4 * q), b + 4 * q);
+          }
         }
 #pragma unroll
-        for (int i = 0; i < V; ++i) f[j][i] = fmaf((f[j][i] - mean) * rstd, g[i], b[i]);
-        __stcs(py + v, Io<T>::pack(f[j]));
+        for (int r = 0; r < R; ++r) {
+          if (row0 + r < rows) {
+            float f[V];
+            if (LAYERNORM) {
+              Io<T>::unpack(raw[r][j], f);
+#pragma unroll
+              for (int i = 0; i < V; ++i) f[i] = fmaf((f[i] - m[r]) * a[r], g[i], b[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < V; ++i) f[i] = ev[r][j][i % KEEP] * a[r];
+            }
+            __stcs(reinterpret_cast<uint4*>(y + (row0 + r) * cols) + v, Io<T>::pack(f));
+          }
+        }
       }
     }
   }
@@ -217,20 +257,31 @@ __global__ void __launch_bounds__(512)
   }
 }
 
-#define REG_ROWNORM_G(TNAME, T, G)                                                                             \
-  CINN_B200_REGISTER_KERNEL("softmax_row_" TNAME "_g" #G "_v1", 4, (G == 32 ? 256 : G), k_softmax_row<T, G, 1>); \
-  CINN_B200_REGISTER_KERNEL("softmax_row_" TNAME "_g" #G "_v2", 4, (G == 32 ? 256 : G), k_softmax_row<T, G, 2>); \
-  CINN_B200_REGISTER_KERNEL("softmax_row_" TNAME "_g" #G "_v4", 4, (G == 32 ? 256 : G), k_softmax_row<T, G, 4>); \
-  CINN_B200_REGISTER_KERNEL("layernorm_row_" TNAME "_g" #G "_v1", 7, (G == 32 ? 256 : G), k_layernorm_row<T, G, 1>); \
-  CINN_B200_REGISTER_KERNEL("layernorm_row_" TNAME "_g" #G "_v2", 7, (G == 32 ? 256 : G), k_layernorm_row<T, G, 2>); \
-  CINN_B200_REGISTER_KERNEL("layernorm_row_" TNAME "_g" #G "_v4", 7, (G == 32 ? 256 : G), k_layernorm_row<T, G, 4>)
+#define REG_ROWNORM_ONE(TNAME, T, G, VPT, R)                                                                     \
+  CINN_B200_REGISTER_KERNEL("softmax_row_" TNAME "_g" #G "_v" #VPT "_r" #R, 8, (G == 32 ? 256 : G),               \
+                            k_rownorm_reg<T, G, VPT, R, false>);                                                  \
+  CINN_B200_REGISTER_KERNEL("layernorm_row_" TNAME "_g" #G "_v" #VPT "_r" #R, 8, (G == 32 ? 256 : G),             \
+                            k_rownorm_reg<T, G, VPT, R, true>)
+#define REG_ROWNORM_G(TNAME, T, G)    \
+  REG_ROWNORM_ONE(TNAME, T, G, 1, 1); \
+  REG_ROWNORM_ONE(TNAME, T, G, 2, 1); \
+  REG_ROWNORM_ONE(TNAME, T, G, 4, 1); \
+  REG_ROWNORM_ONE(TNAME, T, G, 1, 2); \
+  REG_ROWNORM_ONE(TNAME, T, G, 2, 2); \
+  REG_ROWNORM_ONE(TNAME, T, G, 4, 2); \
+  REG_ROWNORM_ONE(TNAME, T, G, 1, 4); \
+  REG_ROWNORM_ONE(TNAME, T, G, 2, 4)
 
-#define REG_ROWNORM_T(TNAME, T) \
-  REG_ROWNORM_G(TNAME, T, 32);  \
-  REG_ROWNORM_G(TNAME, T, 128); \
-  REG_ROWNORM_G(TNAME, T, 256); \
-  REG_ROWNORM_G(TNAME, T, 512); \
-  REG_ROWNORM_G(TNAME, T, 1024); \
+#define REG_ROWNORM_T(TNAME, T)       \
+  REG_ROWNORM_ONE(TNAME, T, 32, 1, 1); \
+  REG_ROWNORM_ONE(TNAME, T, 32, 2, 1); \
+  REG_ROWNORM_ONE(TNAME, T, 32, 4, 1); \
+  REG_ROWNORM_G(TNAME, T, 128);       \
+  REG_ROWNORM_G(TNAME, T, 256);       \
+  REG_ROWNORM_G(TNAME, T, 512);       \
+  REG_ROWNORM_ONE(TNAME, T, 1024, 1, 1); \
+  REG_ROWNORM_ONE(TNAME, T, 1024, 2, 1); \
+  REG_ROWNORM_ONE(TNAME, T, 1024, 4, 1); \
   CINN_B200_REGISTER_KERNEL("rownorm_cluster_" TNAME, 9, 512, k_rownorm_cluster<T>)
 
 REG_ROWNORM_T("f32", float);

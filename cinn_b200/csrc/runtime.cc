@@ -68,9 +68,17 @@ static std::atomic<long long> g_launches{0};
 // ---- options ----------------------------------------------------------------------------------------
 static std::mutex g_mu;
 static int g_opt_sm_count = 0;  // 0: query the device, or 148 without one
+static int g_opt_rownorm_rows = 0;
+static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1;
+
+unsigned int ReadAndClearAsyncWaitTimeouts(int* cuda_status);  // rownorm_tma.cu
 
 static DeviceInfo CurrentDeviceInfo() {
   DeviceInfo d;
+  d.rownorm_rows_per_iter = g_opt_rownorm_rows;
+  d.rownorm_stages      = g_opt_rownorm_stages;
+  d.rownorm_ctas_per_sm = g_opt_rownorm_ctas;
+  d.enable_tma_rownorm = g_opt_enable_tma_rownorm;
   if (g_opt_sm_count > 0) {
     d.sm_count = g_opt_sm_count;
     return d;
@@ -115,7 +123,7 @@ static int LaunchKernel(const void* kernel_fn, void* v_args, int num_args, int g
       params[i] = &args[i].value_;
     }
   }
-  if (dyn_smem > 48 * 1024) {
+  if (dyn_smem > 40 * 1024) {  // static + dynamic above 48 KiB needs the opt-in
     cudaError_t e = cudaFuncSetAttribute(kernel_fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn_smem);
     if (e != cudaSuccess)
       return SetError(CINN_B200_ECUDA, "kernel %s: cannot reserve %zu bytes of shared memory: %s", entry->name,
@@ -537,10 +545,34 @@ int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, 
   return CINN_B200_OK;
 }
 
+int cinn_b200_device_status(unsigned int* async_wait_timeouts) {
+  int st         = 0;
+  unsigned int v = ReadAndClearAsyncWaitTimeouts(&st);
+  if (st != 0) return SetError(CINN_B200_ECUDA, "reading the device status word: %s", cudaGetErrorString((cudaError_t)st));
+  if (async_wait_timeouts) *async_wait_timeouts = v;
+  return CINN_B200_OK;
+}
+
 int cinn_b200_set_option(const char* key, long long value) {
   if (!key) return SetError(CINN_B200_EINVAL, "null option key");
   if (!strcmp(key, "sm_count")) {
     g_opt_sm_count = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "rownorm_rows_per_iter")) {
+    g_opt_rownorm_rows = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "rownorm_stages")) {
+    g_opt_rownorm_stages = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "rownorm_ctas_per_sm")) {
+    g_opt_rownorm_ctas = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "enable_tma_rownorm")) {
+    g_opt_enable_tma_rownorm = (int)value;
     return CINN_B200_OK;
   }
   return SetError(CINN_B200_ENOTFOUND, "unknown option '%s'", key);

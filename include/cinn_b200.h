@@ -106,8 +106,19 @@ int cinn_b200_canonical_expr(const char* group_desc, char* out, size_t out_len);
  */
 int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, int device);
 
+/*
+ * Device-side status of the current device: the number of bounded waits on asynchronous copies that gave up
+ * since the last call (0 in a healthy run); reading clears it.  Synchronises with the device.  The reference
+ * has no counterpart (its generated kernels never wait on asynchronous copies).
+ */
+int cinn_b200_device_status(unsigned int* async_wait_timeouts);
+
 /* Tuning knobs (integers) read by the matcher when a group is compiled; unknown keys give CINN_B200_ENOTFOUND.
- * "sm_count": SM count assumed when no GPU is visible (default 148). */
+ * "sm_count": SM count assumed when no GPU is visible (default 148); "rownorm_rows_per_iter": rows per CTA
+ * iteration of the register-resident softmax / layer_norm kernels (0 = automatic, else 1, 2 or 4); "rownorm_stages", "rownorm_ctas_per_sm":
+ * ring depth and resident CTAs per SM of the streamed softmax / layer_norm kernels (0 = automatic);
+ * "enable_tma_rownorm": 1 selects the kernels that stream rows through a shared-memory ring with bulk
+ * asynchronous copies, 0 the register-resident ones, -1 (default) chooses per group. */
 int cinn_b200_set_option(const char* key, long long value);
 
 #ifdef __cplusplus
