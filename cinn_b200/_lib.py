@@ -64,6 +64,43 @@ def lib():
         L.cinn_b200_canonical_expr.argtypes = [cs, ctypes.c_char_p, ctypes.c_size_t]
         L.cinn_b200_group_run_host.restype = ci
         L.cinn_b200_group_run_host.argtypes = [cs, vp, ci, ci]
+        L.cinn_b200_builder_create.restype = vp
+        L.cinn_b200_builder_create.argtypes = [cs]
+        L.cinn_b200_builder_destroy.restype = None
+        L.cinn_b200_builder_destroy.argtypes = [vp]
+        L.cinn_b200_builder_create_input.restype = ci
+        L.cinn_b200_builder_create_input.argtypes = [vp, cs, ctypes.POINTER(ll), ci, cs, ctypes.c_char_p,
+                                                     ctypes.c_size_t]
+        L.cinn_b200_builder_add_op.restype = ci
+        L.cinn_b200_builder_add_op.argtypes = [vp, cs, ctypes.POINTER(cs), ci, cs, ctypes.c_char_p, ctypes.c_size_t]
+        L.cinn_b200_builder_var_info.restype = ci
+        L.cinn_b200_builder_var_info.argtypes = [vp, cs, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ll),
+                                                 ctypes.POINTER(ci)]
+        L.cinn_b200_computation_build_and_compile.restype = vp
+        L.cinn_b200_computation_build_and_compile.argtypes = [vp, ci, ctypes.POINTER(cs), ci]
+        L.cinn_b200_computation_destroy.restype = None
+        L.cinn_b200_computation_destroy.argtypes = [vp]
+        L.cinn_b200_computation_execute.restype = ci
+        L.cinn_b200_computation_execute.argtypes = [vp, vp]
+        L.cinn_b200_computation_set_tensor_data.restype = ci
+        L.cinn_b200_computation_set_tensor_data.argtypes = [vp, cs, vp, ctypes.c_size_t]
+        L.cinn_b200_computation_get_tensor_data.restype = ci
+        L.cinn_b200_computation_get_tensor_data.argtypes = [vp, cs, vp, ctypes.c_size_t]
+        L.cinn_b200_computation_bind_tensor.restype = ci
+        L.cinn_b200_computation_bind_tensor.argtypes = [vp, cs, vp]
+        L.cinn_b200_computation_num_tensors.restype = ci
+        L.cinn_b200_computation_num_tensors.argtypes = [vp]
+        L.cinn_b200_computation_tensor_name.restype = cs
+        L.cinn_b200_computation_tensor_name.argtypes = [vp, ci]
+        L.cinn_b200_computation_tensor_info.restype = ci
+        L.cinn_b200_computation_tensor_info.argtypes = [vp, cs, ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ll),
+                                                        ctypes.POINTER(ci), ctypes.POINTER(vp)]
+        L.cinn_b200_computation_num_groups.restype = ci
+        L.cinn_b200_computation_num_groups.argtypes = [vp]
+        L.cinn_b200_computation_group_desc.restype = ci
+        L.cinn_b200_computation_group_desc.argtypes = [vp, ci, ctypes.c_char_p, ctypes.c_size_t]
+        L.cinn_b200_computation_group_pattern.restype = ci
+        L.cinn_b200_computation_group_pattern.argtypes = [vp, ci, ctypes.c_char_p, ctypes.c_size_t]
         L.cinn_b200_device_status.restype = ci
         L.cinn_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         L.cinn_b200_set_option.restype = ci

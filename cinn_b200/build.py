@@ -20,9 +20,13 @@ SOURCES = [
     "reduce_kernels.cu",
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
+    "ew_chain.cu",
     "group_desc.cc",
     "group_match.cc",
+    "chain_match.cc",
     "runtime.cc",
+    "frontend.cc",
+    "capi_frontend.cc",
 ]
 
 # -fmad=false: a*b+c is fused only where fmaf() is written (the x86 path's contraction rule);

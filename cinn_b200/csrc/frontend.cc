@@ -1,0 +1,681 @@
+// NetBuilder, op shape/dtype inference, the fusion pass and the Computation executor.
+#include "frontend.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <cstring>
+#include <functional>
+#include <set>
+#include <sstream>
+
+#include "../../include/cinn_b200.h"
+
+namespace cinn_b200 {
+
+// ---- op registry ------------------------------------------------------------------------------------
+// Names and pattern kinds follow the op registrations of cinn/hlir/op/elementwise.cc:860-1066,
+// broadcast.cc:361-441, reduction.cc:477-505 and nn.cc:2262-2433; binary "broadcast" ops take part in
+// fusion as elementwise ops (cinn/hlir/pass/fusion_helper_base.h:47-59).
+namespace {
+
+const std::set<std::string>& UnaryOps() {
+  static const std::set<std::string> s = {
+      "sqrt", "tanh", "sigmoid", "identity", "exp", "erf", "rsqrt", "log", "log2", "log10", "floor", "ceil", "round",
+      "trunc", "sin", "cos", "negative", "sign", "abs", "relu", "relu6", "reciprocal", "gelu"};
+  return s;
+}
+const std::set<std::string>& BinaryOps() {
+  static const std::set<std::string> s = {"elementwise_add", "elementwise_mul", "subtract", "divide", "max", "min",
+                                          "pow"};
+  return s;
+}
+const std::set<std::string>& CompareOps() {
+  static const std::set<std::string> s = {"equal", "not_equal", "greater_than", "less_than", "greater_equal",
+                                          "less_equal"};
+  return s;
+}
+const std::set<std::string>& ReduceOps() {
+  static const std::set<std::string> s = {"reduce_sum", "reduce_prod", "reduce_max", "reduce_min"};
+  return s;
+}
+
+std::vector<int64_t> ParseIntList(const std::string& text) {
+  std::vector<int64_t> out;
+  std::string cur;
+  for (char c : text + ",") {
+    if (c == ',') {
+      if (!cur.empty()) out.push_back(atoll(cur.c_str()));
+      cur.clear();
+    } else if (c != '[' && c != ']' && c != ' ' && c != '(' && c != ')') {
+      cur.push_back(c);
+    }
+  }
+  return out;
+}
+
+std::string JoinInts(const std::vector<int64_t>& v) {
+  std::string s;
+  for (size_t i = 0; i < v.size(); ++i) {
+    if (i) s += ",";
+    s += std::to_string(v[i]);
+  }
+  return s;
+}
+
+// cinn/hlir/pe/broadcast.cc:35-118 (GetBroadcastShape): equal shapes pass through; otherwise the
+// lower-rank operand is aligned at `axis` (axis = -1: right-aligned) and extents must match or be 1.
+bool BroadcastShape(const std::vector<int64_t>& a, const std::vector<int64_t>& b, int64_t axis,
+                    std::vector<int64_t>* out, std::string* err) {
+  if (a == b) {
+    *out = a;
+    return true;
+  }
+  const std::vector<int64_t>& big   = a.size() >= b.size() ? a : b;
+  const std::vector<int64_t>& small = a.size() >= b.size() ? b : a;
+  int64_t off = axis < 0 ? (int64_t)big.size() - (int64_t)small.size() : axis;
+  if (off < 0 || off + small.size() > big.size()) {
+    if (err) *err = "broadcast axis " + std::to_string(axis) + " does not fit the operand ranks";
+    return false;
+  }
+  *out = big;
+  for (size_t i = 0; i < small.size(); ++i) {
+    int64_t x = big[off + i], y = small[i];
+    if (x == y || y == 1) continue;
+    if (x == 1) {
+      (*out)[off + i] = y;
+      continue;
+    }
+    if (err) *err = "operands cannot be broadcast together: extents " + std::to_string(x) + " and " + std::to_string(y);
+    return false;
+  }
+  return true;
+}
+
+}  // namespace
+
+bool KnownOp(const std::string& t) {
+  return UnaryOps().count(t) || BinaryOps().count(t) || CompareOps().count(t) || ReduceOps().count(t) ||
+         t == "scale" || t == "cast" || t == "select" || t == "broadcast_to" || t == "fill_constant" ||
+         t == "softmax" || t == "batch_norm" || t == "reshape";
+}
+
+OpPattern PatternOf(const std::string& t) {
+  if (t == "fill_constant") return OpPattern::kConst;
+  if (ReduceOps().count(t)) return OpPattern::kReduction;
+  if (t == "broadcast_to") return OpPattern::kBroadcast;
+  if (t == "reshape") return OpPattern::kNonFusible;
+  // softmax is registered kNonFusible in the reference (cinn/hlir/op/nn.cc:2383-2393); here the casts around
+  // it may join its group, so it takes part in fusion like an elementwise op.
+  return OpPattern::kElementWise;
+}
+
+// ---- NetBuilder ---------------------------------------------------------------------------------------
+std::string NetBuilder::NewId(const std::string& hint) {
+  if (!hint.empty() && !var_index_.count(hint)) return hint;
+  std::string id;
+  do {
+    id = "var_" + std::to_string(counter_++);
+  } while (var_index_.count(id));
+  return id;
+}
+
+int NetBuilder::FindVar(const std::string& id) const {
+  auto it = var_index_.find(id);
+  return it == var_index_.end() ? -1 : it->second;
+}
+
+int NetBuilder::CreateInput(DType dtype, const std::vector<int64_t>& shape, const std::string& id_hint,
+                            std::string* err) {
+  if (dtype == DType::kUnknown) {
+    if (err) *err = "create_input: unknown dtype";
+    return -1;
+  }
+  if (shape.size() > CINN_BUFFER_MAX_DIMS) {
+    if (err) *err = "create_input: at most 8 dimensions (cinn_buffer_t)";
+    return -1;
+  }
+  for (auto d : shape)
+    if (d <= 0) {
+      if (err) *err = "create_input: non-positive extent";
+      return -1;
+    }
+  Variable v;
+  v.id       = NewId(id_hint);
+  v.dtype    = dtype;
+  v.shape    = shape;
+  v.is_input = true;
+  vars_.push_back(v);
+  var_index_[v.id] = (int)vars_.size() - 1;
+  return (int)vars_.size() - 1;
+}
+
+int NetBuilder::AddOp(const std::string& op, const std::vector<int>& inputs,
+                      const std::map<std::string, std::string>& attrs_in, std::string* err) {
+  auto fail = [&](const std::string& m) {
+    if (err) *err = op + ": " + m;
+    return -1;
+  };
+  if (!KnownOp(op)) return fail("op is not supported by the fused-group kernel library");
+  for (int i : inputs)
+    if (i < 0 || i >= (int)vars_.size()) return fail("bad input variable");
+  auto attrs = attrs_in;
+  auto in    = [&](int k) -> const Variable& { return vars_[inputs[k]]; };
+  auto need  = [&](size_t n) { return inputs.size() == n; };
+  Variable out;
+  if (UnaryOps().count(op)) {
+    if (!need(1)) return fail("takes 1 input");
+    out.dtype = in(0).dtype;
+    out.shape = in(0).shape;
+  } else if (BinaryOps().count(op) || CompareOps().count(op)) {
+    if (!need(2)) return fail("takes 2 inputs");
+    if (in(0).dtype != in(1).dtype) return fail("operand dtypes differ");
+    int64_t axis = attrs.count("axis") ? atoll(attrs["axis"].c_str()) : -1;
+    attrs["axis"] = std::to_string(axis);
+    std::string e;
+    if (!BroadcastShape(in(0).shape, in(1).shape, axis, &out.shape, &e)) return fail(e);
+    out.dtype = CompareOps().count(op) ? DType::kBool : in(0).dtype;
+  } else if (op == "scale") {
+    if (!need(1)) return fail("takes 1 input");
+    if (!attrs.count("scale")) attrs["scale"] = "1.0";
+    if (!attrs.count("bias")) attrs["bias"] = "0.0";
+    if (!attrs.count("bias_after_scale")) attrs["bias_after_scale"] = "true";
+    out.dtype = in(0).dtype;
+    out.shape = in(0).shape;
+  } else if (op == "cast") {
+    if (!need(1)) return fail("takes 1 input");
+    out.dtype = DTypeFromName(attrs.count("dtype") ? attrs["dtype"] : "");
+    if (out.dtype == DType::kUnknown) return fail("needs a known 'dtype' attribute");
+    out.shape = in(0).shape;
+  } else if (op == "select") {
+    if (!need(3)) return fail("takes 3 inputs (condition, true value, false value)");
+    if (in(0).dtype != DType::kBool) return fail("condition must be bool");
+    if (in(1).dtype != in(2).dtype || in(1).shape != in(2).shape || in(0).shape != in(1).shape)
+      return fail("operands must have one shape and the values one dtype");
+    out.dtype = in(1).dtype;
+    out.shape = in(1).shape;
+  } else if (op == "broadcast_to") {
+    if (!need(1)) return fail("takes 1 input");
+    out.shape = ParseIntList(attrs.count("out_shape") ? attrs["out_shape"] : "");
+    if (out.shape.empty()) return fail("needs 'out_shape'");
+    std::vector<int64_t> axes = ParseIntList(attrs.count("broadcast_axes") ? attrs["broadcast_axes"] : "");
+    if (axes.empty()) {  // right-aligned, cinn/hlir/pe/broadcast.cc:293-327
+      for (size_t i = 0; i < in(0).shape.size(); ++i) axes.push_back(out.shape.size() - in(0).shape.size() + i);
+    }
+    if (axes.size() != in(0).shape.size()) return fail("'broadcast_axes' must have one entry per input dimension");
+    for (size_t i = 0; i < axes.size(); ++i) {
+      if (axes[i] < 0) axes[i] += out.shape.size();
+      if (axes[i] < 0 || axes[i] >= (int64_t)out.shape.size()) return fail("broadcast axis out of range");
+      if (in(0).shape[i] != 1 && in(0).shape[i] != out.shape[axes[i]]) return fail("input extent does not match out_shape");
+    }
+    attrs["out_shape"]      = JoinInts(out.shape);
+    attrs["broadcast_axes"] = JoinInts(axes);
+    out.dtype               = in(0).dtype;
+  } else if (op == "fill_constant") {
+    if (!need(0)) return fail("takes no input");
+    out.shape = ParseIntList(attrs.count("shape") ? attrs["shape"] : "");
+    if (out.shape.empty()) return fail("needs 'shape'");
+    if (!attrs.count("value")) return fail("needs 'value'");
+    out.dtype = DTypeFromName(attrs.count("dtype") ? attrs["dtype"] : "float32");
+    if (out.dtype == DType::kUnknown) return fail("unknown 'dtype'");
+    attrs["shape"] = JoinInts(out.shape);
+    attrs["dtype"] = DTypeName(out.dtype);
+  } else if (ReduceOps().count(op)) {
+    if (!need(1)) return fail("takes 1 input");
+    const int nd = (int)in(0).shape.size();
+    std::vector<int64_t> dims = ParseIntList(attrs.count("dim") ? attrs["dim"] : "");
+    // cinn/frontend/net_builder.cc:98-128: empty dim = all axes, negative axes wrap.
+    if (dims.empty())
+      for (int i = 0; i < nd; ++i) dims.push_back(i);
+    for (auto& d : dims) {
+      if (d < 0) d += nd;
+      if (d < 0 || d >= nd) return fail("reduce axis out of range");
+    }
+    std::sort(dims.begin(), dims.end());
+    dims.erase(std::unique(dims.begin(), dims.end()), dims.end());
+    bool keep = attrs.count("keep_dim") && (attrs["keep_dim"] == "true" || attrs["keep_dim"] == "1" || attrs["keep_dim"] == "True");
+    attrs["dim"]      = JoinInts(dims);
+    attrs["keep_dim"] = keep ? "true" : "false";
+    for (int i = 0; i < nd; ++i) {
+      bool red = std::binary_search(dims.begin(), dims.end(), (int64_t)i);
+      if (!red) out.shape.push_back(in(0).shape[i]);
+      else if (keep) out.shape.push_back(1);
+    }
+    if (out.shape.empty()) out.shape.push_back(1);
+    out.dtype = in(0).dtype;
+  } else if (op == "softmax") {
+    if (!need(1)) return fail("takes 1 input");
+    if (!attrs.count("axis")) attrs["axis"] = "-1";
+    out.dtype = in(0).dtype;
+    out.shape = in(0).shape;
+  } else if (op == "batch_norm") {
+    // argument order x, scale, bias, mean, variance: cinn/frontend/net_builder.cc:764-801
+    if (!need(5)) return fail("takes 5 inputs (x, scale, bias, mean, variance)");
+    if (in(0).shape.size() != 4) return fail("input must be 4-D");
+    if (!attrs.count("epsilon")) attrs["epsilon"] = "1e-05";
+    if (!attrs.count("data_layout")) attrs["data_layout"] = "NCHW";
+    out.dtype = in(0).dtype;
+    out.shape = in(0).shape;
+  } else if (op == "reshape") {
+    if (!need(1)) return fail("takes 1 input");
+    out.shape = ParseIntList(attrs.count("shape") ? attrs["shape"] : "");
+    int64_t n = 1, total = 1, unknown = -1;
+    for (auto d : in(0).shape) total *= d;
+    for (size_t i = 0; i < out.shape.size(); ++i) {
+      if (out.shape[i] == -1) unknown = (int64_t)i;
+      else n *= out.shape[i];
+    }
+    if (unknown >= 0) {
+      if (n == 0 || total % n) return fail("cannot infer the -1 extent");
+      out.shape[unknown] = total / n;
+      n *= out.shape[unknown];
+    }
+    if (n != total) return fail("element count changes");
+    attrs["shape"] = JoinInts(out.shape);
+    out.dtype      = in(0).dtype;
+  }
+  if (out.shape.size() > CINN_BUFFER_MAX_DIMS) return fail("result has more than 8 dimensions");
+  out.id = NewId("");
+  vars_.push_back(out);
+  var_index_[out.id] = (int)vars_.size() - 1;
+  ProgramInstr ins;
+  ins.op_type = op;
+  ins.inputs  = inputs;
+  ins.output  = (int)vars_.size() - 1;
+  ins.attrs   = attrs;
+  instrs_.push_back(ins);
+  return ins.output;
+}
+
+// ---- fusion ---------------------------------------------------------------------------------------------
+namespace {
+
+struct FusionState {
+  const NetBuilder& b;
+  const DeviceInfo& dev;
+  std::vector<int> producer_of_var;                // variable -> instruction (-1 for inputs)
+  std::vector<std::vector<int>> consumers_of_var;  // variable -> instructions
+  std::set<int> fetch;
+  int uid;
+
+  FusionState(const NetBuilder& b_, const DeviceInfo& d, int uid_) : b(b_), dev(d), uid(uid_) {
+    producer_of_var.assign(b.vars().size(), -1);
+    consumers_of_var.assign(b.vars().size(), {});
+    for (size_t i = 0; i < b.instrs().size(); ++i) {
+      producer_of_var[b.instrs()[i].output] = (int)i;
+      for (int v : b.instrs()[i].inputs) consumers_of_var[v].push_back((int)i);
+    }
+  }
+
+  bool IsConst(int instr) const { return PatternOf(b.instrs()[instr].op_type) == OpPattern::kConst; }
+
+  // Builds the description of the group formed by `members` (non-const instructions) plus the constants they
+  // read.  Inputs are listed in first-encounter order walking the members producer -> consumer
+  // (cinn/hlir/framework/op_lowering_util.cc:79-97); outputs are the members' results used outside or fetched.
+  FusedGroupInfo Describe(const std::set<int>& members) const {
+    FusedGroupInfo g;
+    std::set<int> all = members;
+    for (int m : members)
+      for (int v : b.instrs()[m].inputs) {
+        int p = producer_of_var[v];
+        if (p >= 0 && IsConst(p)) all.insert(p);
+      }
+    std::set<int> seen_inputs;
+    std::string name = "fn";
+    for (int i : all) {  // std::set iterates in program (topological) order
+      const ProgramInstr& ins = b.instrs()[i];
+      g.instr_indices.push_back(i);
+      if (!IsConst(i) && name.size() < 96) name += "_" + ins.op_type;
+      OpDesc od;
+      od.type   = ins.op_type;
+      od.output = b.vars()[ins.output].id;
+      od.attrs  = ins.attrs;
+      for (int v : ins.inputs) {
+        od.inputs.push_back(b.vars()[v].id);
+        int p = producer_of_var[v];
+        if ((p < 0 || !all.count(p)) && !seen_inputs.count(v)) {
+          seen_inputs.insert(v);
+          g.input_vars.push_back(v);
+          TensorDesc t;
+          t.name  = b.vars()[v].id;
+          t.dtype = b.vars()[v].dtype;
+          t.shape = b.vars()[v].shape;
+          g.desc.inputs.push_back(t);
+        }
+      }
+      g.desc.ops.push_back(od);
+    }
+    for (int i : members) {
+      int v          = b.instrs()[i].output;
+      bool external  = fetch.count(v) > 0;
+      for (int c : consumers_of_var[v])
+        if (!all.count(c)) external = true;
+      if (external) {
+        g.output_vars.push_back(v);
+        TensorDesc t;
+        t.name  = b.vars()[v].id;
+        t.dtype = b.vars()[v].dtype;
+        t.shape = b.vars()[v].shape;
+        g.desc.outputs.push_back(t);
+      }
+    }
+    g.desc.name = name + "_" + std::to_string(uid) + "_" + std::to_string(*members.begin());
+    return g;
+  }
+
+  bool Compiles(const std::set<int>& members, FusedGroupInfo* out, std::string* why) const {
+    FusedGroupInfo g = Describe(members);
+    if (g.desc.outputs.size() != 1) {
+      if (why) *why = "group would have " + std::to_string(g.desc.outputs.size()) + " outputs";
+      return false;
+    }
+    std::string err;
+    auto plan = CompileGroup(g.desc, dev, &err);
+    if (!plan) {
+      if (why) *why = err;
+      return false;
+    }
+    g.pattern = plan->pattern;
+    for (auto& s : plan->steps) g.kernels.push_back(s.kernel->name);
+    if (out) *out = std::move(g);
+    return true;
+  }
+};
+
+std::atomic<int> g_computation_uid{0};
+
+}  // namespace
+
+bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const DeviceInfo& dev,
+                std::vector<FusedGroupInfo>* groups, std::string* err) {
+  FusionState st(b, dev, g_computation_uid.fetch_add(1));
+  const int n = (int)b.instrs().size();
+  if (fetch_in.empty()) {
+    for (size_t v = 0; v < b.vars().size(); ++v)
+      if (st.producer_of_var[v] >= 0 && st.consumers_of_var[v].empty()) st.fetch.insert((int)v);
+  } else {
+    for (int v : fetch_in) st.fetch.insert(v);
+  }
+  std::vector<int> group_of(n, -1);
+  std::vector<std::set<int>> sets;
+
+  // Step 1: connected regions of fusible instructions, tried whole.  This is what lets a multi-reduction
+  // composition (softmax, layer_norm) become ONE kernel whatever its row length, where the reference splits at
+  // reduce -> broadcast edges longer than 1024 (cinn/hlir/pass/op_fusion_pass_util.h:263-265).
+  {
+    std::vector<int> comp(n, -1);
+    int ncomp = 0;
+    for (int i = 0; i < n; ++i) {
+      if (comp[i] >= 0 || st.IsConst(i) || PatternOf(b.instrs()[i].op_type) == OpPattern::kNonFusible) continue;
+      std::vector<int> stack = {i};
+      comp[i]                = ncomp;
+      while (!stack.empty()) {
+        int u = stack.back();
+        stack.pop_back();
+        auto visit = [&](int w) {
+          if (w < 0 || comp[w] >= 0 || st.IsConst(w) || PatternOf(b.instrs()[w].op_type) == OpPattern::kNonFusible) return;
+          comp[w] = ncomp;
+          stack.push_back(w);
+        };
+        for (int v : b.instrs()[u].inputs) visit(st.producer_of_var[v]);
+        for (int c : st.consumers_of_var[b.instrs()[u].output]) visit(c);
+      }
+      ++ncomp;
+    }
+    for (int c = 0; c < ncomp; ++c) {
+      std::set<int> members;
+      for (int i = 0; i < n; ++i)
+        if (comp[i] == c) members.insert(i);
+      if (members.size() < 2) continue;
+      if (st.Compiles(members, nullptr, nullptr)) {
+        for (int i : members) group_of[i] = (int)sets.size();
+        sets.push_back(members);
+      }
+    }
+  }
+
+  // Step 2: vertical fusion, consumer first (the reference walks the graph in reverse topological order,
+  // cinn/hlir/pass/op_fusion_pass.cc:94-95): a producer joins its consumer's group when all of its uses are
+  // inside the group and a kernel exists for the enlarged group.
+  for (int root = n - 1; root >= 0; --root) {
+    if (group_of[root] >= 0 || st.IsConst(root)) continue;
+    std::set<int> members = {root};
+    bool grew             = PatternOf(b.instrs()[root].op_type) != OpPattern::kNonFusible;
+    while (grew) {
+      grew = false;
+      for (int m : std::set<int>(members)) {
+        for (int v : b.instrs()[m].inputs) {
+          int p = st.producer_of_var[v];
+          if (p < 0 || members.count(p) || group_of[p] >= 0 || st.IsConst(p)) continue;
+          if (PatternOf(b.instrs()[p].op_type) == OpPattern::kNonFusible) continue;
+          if (st.fetch.count(b.instrs()[p].output)) continue;
+          bool all_inside = true;
+          for (int c : st.consumers_of_var[b.instrs()[p].output])
+            if (!members.count(c)) all_inside = false;
+          if (!all_inside) continue;
+          std::set<int> trial = members;
+          trial.insert(p);
+          if (st.Compiles(trial, nullptr, nullptr)) {
+            members = trial;
+            grew    = true;
+          }
+        }
+      }
+    }
+    for (int i : members) group_of[i] = (int)sets.size();
+    sets.push_back(members);
+  }
+
+  // Emit in topological order of the groups' first instruction; every group must compile.
+  std::vector<int> order(sets.size());
+  for (size_t i = 0; i < sets.size(); ++i) order[i] = (int)i;
+  std::sort(order.begin(), order.end(), [&](int x, int y) { return *sets[x].rbegin() < *sets[y].rbegin(); });
+  groups->clear();
+  for (int gi : order) {
+    FusedGroupInfo info;
+    std::string why;
+    if (sets[gi].size() == 1 && b.instrs()[*sets[gi].begin()].op_type == "reshape") {
+      // A reshape is not a kernel: its result aliases its operand's memory (graph_compiler.cc:1017-1027).
+      info         = st.Describe(sets[gi]);
+      info.pattern = "reshape_alias";
+      if (info.desc.outputs.empty()) {
+        const ProgramInstr& ins = b.instrs()[*sets[gi].begin()];
+        info.output_vars.push_back(ins.output);
+      }
+      groups->push_back(std::move(info));
+      continue;
+    }
+    if (!st.Compiles(sets[gi], &info, &why)) {
+      if (err) *err = "no prebuilt kernel for instruction group {" + PrintGroupDesc(st.Describe(sets[gi]).desc) + "}: " + why;
+      return false;
+    }
+    groups->push_back(std::move(info));
+  }
+  return true;
+}
+
+// ---- Computation ----------------------------------------------------------------------------------------
+namespace {
+
+cinn_type_t RuntimeType(DType t) {
+  cinn_type_t r;
+  r.lanes         = 1;
+  r.num_asterisks = 0;
+  switch (t) {
+    case DType::kFloat32: r.code = cinn_type_float; r.bits = 32; break;
+    case DType::kFloat16: r.code = cinn_type_float; r.bits = 16; break;
+    case DType::kBFloat16: r.code = cinn_type_bfloat; r.bits = 16; break;
+    case DType::kFloat64: r.code = cinn_type_float; r.bits = 64; break;
+    case DType::kInt32: r.code = cinn_type_int; r.bits = 32; break;
+    case DType::kInt64: r.code = cinn_type_int; r.bits = 64; break;
+    case DType::kBool: r.code = cinn_type_int; r.bits = 1; break;
+    case DType::kUInt8: r.code = cinn_type_uint; r.bits = 8; break;
+    default: r.code = cinn_type_unk; r.bits = 0; break;
+  }
+  return r;
+}
+
+int Fail(std::string* err, const std::string& m, int code = CINN_B200_EINVAL) {
+  if (err) *err = m;
+  return code;
+}
+
+}  // namespace
+
+std::unique_ptr<Computation> Computation::BuildAndCompile(const NetBuilder& b, const std::vector<int>& fetch,
+                                                          int device, std::string* err) {
+  std::unique_ptr<Computation> c(new Computation());
+  c->device_ = device;
+  DeviceInfo dev;
+  if (device >= 0) {
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) {
+      if (err) *err = std::string("cudaSetDevice: ") + cudaGetErrorString(e);
+      return nullptr;
+    }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && sms > 0) dev.sm_count = sms;
+  }
+  if (!FusePasses(b, fetch, dev, &c->groups_, err)) return nullptr;
+  // Scope: one tensor per variable that crosses a group boundary (cinn/hlir/framework/graph_compiler.cc:1430-1451).
+  auto add_tensor = [&](int v) {
+    const Variable& var = b.vars()[v];
+    if (c->scope_.count(var.id)) return;
+    auto t    = std::make_unique<ScopeTensor>();
+    t->var    = var;
+    memset(&t->buffer, 0, sizeof(t->buffer));
+    t->buffer.device     = cinn_unk_device;
+    t->buffer.flag       = cinn_buffer_on_device;
+    t->buffer.type       = RuntimeType(var.dtype);
+    t->buffer.dimensions = (int32_t)var.shape.size();
+    int64_t n            = 1;
+    for (size_t i = 0; i < var.shape.size(); ++i) {
+      t->buffer.dims[i] = (cinn_dimension_t)var.shape[i];
+      n *= var.shape[i];
+    }
+    t->bytes              = (size_t)n * DTypeBytes(var.dtype);
+    t->buffer.memory_size = t->bytes;
+    c->names_.push_back(var.id);
+    c->scope_[var.id] = std::move(t);
+  };
+  for (auto& g : c->groups_) {
+    for (int v : g.input_vars) add_tensor(v);
+    for (int v : g.output_vars) add_tensor(v);
+  }
+  // Compile every group into the library's registry and keep the entry points (parallel_compiler.cc:201-217).
+  for (auto& g : c->groups_) {
+    if (g.pattern == "reshape_alias") {
+      c->aliases_.push_back({b.vars()[g.output_vars[0]].id, b.vars()[g.input_vars[0]].id});
+      continue;
+    }
+    lower_func_ptr_g fn = nullptr;
+    int rc              = cinn_b200_compile_group(PrintGroupDesc(g.desc).c_str(), &fn);
+    if (rc != CINN_B200_OK) {
+      if (err) *err = cinn_b200_last_error();
+      return nullptr;
+    }
+    Instr ins;
+    ins.fn      = fn;
+    ins.fn_name = g.desc.name;
+    for (int v : g.input_vars) ins.args.push_back(b.vars()[v].id);
+    for (int v : g.output_vars) ins.args.push_back(b.vars()[v].id);
+    c->instrs_.push_back(std::move(ins));
+  }
+  if (device >= 0) {
+    std::set<std::string> alias_outputs;
+    for (auto& a : c->aliases_) alias_outputs.insert(a.first);
+    // cinn/hlir/framework/memory.cc:43-52: device memory from cudaMalloc, owned by the scope.
+    for (auto& kv : c->scope_) {
+      if (alias_outputs.count(kv.first)) continue;
+      void* p       = nullptr;
+      cudaError_t e = cudaMalloc(&p, std::max<size_t>(kv.second->bytes, 16));
+      if (e != cudaSuccess) {
+        if (err) *err = "cudaMalloc of tensor " + kv.first + ": " + cudaGetErrorString(e);
+        return nullptr;
+      }
+      kv.second->buffer.memory = static_cast<uint8_t*>(p);
+      kv.second->owned         = true;
+    }
+  }
+  return c;
+}
+
+Computation::~Computation() {
+  for (auto& ins : instrs_) cinn_b200_release_group(ins.fn_name.c_str());
+  if (device_ >= 0) {
+    int prev = 0;
+    cudaGetDevice(&prev);
+    cudaSetDevice(device_);
+    for (auto& kv : scope_)
+      if (kv.second->owned && kv.second->buffer.memory) cudaFree(kv.second->buffer.memory);
+    cudaSetDevice(prev);
+  }
+}
+
+ScopeTensor* Computation::Find(const std::string& id) {
+  auto it = scope_.find(id);
+  return it == scope_.end() ? nullptr : it->second.get();
+}
+
+int Computation::BindTensor(const std::string& id, void* device_ptr, std::string* err) {
+  ScopeTensor* t = Find(id);
+  if (!t) return Fail(err, "no tensor named '" + id + "'", CINN_B200_ENOTFOUND);
+  if (!device_ptr) return Fail(err, "null device pointer for tensor '" + id + "'");
+  if (t->owned && t->buffer.memory) {
+    cudaFree(t->buffer.memory);
+    t->owned = false;
+  }
+  t->buffer.memory = static_cast<uint8_t*>(device_ptr);
+  return CINN_B200_OK;
+}
+
+int Computation::SetTensorData(const std::string& id, const void* host, size_t bytes, std::string* err) {
+  ScopeTensor* t = Find(id);
+  if (!t) return Fail(err, "no tensor named '" + id + "'", CINN_B200_ENOTFOUND);
+  if (bytes != t->bytes) return Fail(err, "tensor '" + id + "' holds " + std::to_string(t->bytes) + " bytes, got " + std::to_string(bytes), CINN_B200_ESHAPE);
+  if (!t->buffer.memory) return Fail(err, "tensor '" + id + "' has no device memory (planned without a device)");
+  cudaError_t e = cudaMemcpy(t->buffer.memory, host, bytes, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return Fail(err, std::string("host->device copy: ") + cudaGetErrorString(e), CINN_B200_ECUDA);
+  return CINN_B200_OK;
+}
+
+int Computation::GetTensorData(const std::string& id, void* host, size_t bytes, std::string* err) {
+  ScopeTensor* t = Find(id);
+  if (!t) return Fail(err, "no tensor named '" + id + "'", CINN_B200_ENOTFOUND);
+  if (bytes != t->bytes) return Fail(err, "tensor '" + id + "' holds " + std::to_string(t->bytes) + " bytes, got " + std::to_string(bytes), CINN_B200_ESHAPE);
+  if (!t->buffer.memory) return Fail(err, "tensor '" + id + "' has no device memory (planned without a device)");
+  cudaError_t e = cudaMemcpy(host, t->buffer.memory, bytes, cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return Fail(err, std::string("device->host copy: ") + cudaGetErrorString(e), CINN_B200_ECUDA);
+  return CINN_B200_OK;
+}
+
+int Computation::Execute(void* stream, std::string* err) {
+  if (device_ < 0) return Fail(err, "this computation was planned without a device");
+  // Instruction::UpdateArgsCache (instruction.cc:77-106): pod arrays are built once and reused.
+  if (!args_cached_) {
+    for (auto& ins : instrs_) {
+      ins.pods.resize(ins.args.size());
+      for (size_t i = 0; i < ins.args.size(); ++i) {
+        ScopeTensor* t              = Find(ins.args[i]);
+        ins.pods[i].type_code_      = CINN_POD_BUFFERP;
+        ins.pods[i].value_.v_handle = &t->buffer;
+      }
+    }
+    args_cached_ = true;
+  }
+  for (auto& a : aliases_) Find(a.first)->buffer.memory = Find(a.second)->buffer.memory;
+  for (auto& ins : instrs_) {
+    int rc = cinn_b200_group_run(ins.fn_name.c_str(), ins.pods.data(), (int)ins.pods.size(), stream);
+    if (rc != CINN_B200_OK) return Fail(err, cinn_b200_last_error(), rc);
+  }
+  // Program::Execute synchronises only when no stream was given (graph_compiler.cc:216-221).
+  if (stream == nullptr) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return Fail(err, std::string("cudaDeviceSynchronize: ") + cudaGetErrorString(e), CINN_B200_ECUDA);
+  }
+  return CINN_B200_OK;
+}
+
+}  // namespace cinn_b200

@@ -15,6 +15,9 @@
 #include "group_desc.h"
 
 namespace cinn_b200 {
+
+std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const DeviceInfo& dev, std::string* why);  // chain_match.cc
+
 namespace {
 
 int64_t CeilDiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -665,7 +668,10 @@ struct Matcher {
       if (p) return p;
       if (err && !err->empty()) return nullptr;  // a matcher recognised the form but rejected its details
     }
-    Fail("no prebuilt sm_100a kernel matches expression " + expr);
+    // Last resort for elementwise / broadcast groups: a linear chain run by the generic kernel.
+    std::string why;
+    if (auto p = MatchGenericChain(g, dev, &why)) return p;
+    Fail("no prebuilt sm_100a kernel matches expression " + expr + " (as an elementwise chain: " + why + ")");
     return nullptr;
   }
 };

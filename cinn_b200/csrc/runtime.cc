@@ -56,6 +56,8 @@ static int SetError(int code, const char* fmt, ...) {
   return code;
 }
 
+int SetLastError(int code, const std::string& message) { return SetError(code, "%s", message.c_str()); }
+
 static void FatalIfRequested() {
   if (getenv("CINN_B200_ABORT_ON_ERROR")) {
     fprintf(stderr, "[cinn_b200] fatal: %s\n", tls_error.c_str());

@@ -1,0 +1,308 @@
+"""NetBuilder / Computation with the method names of the reference's Python API.
+
+Mirrors `cinn.frontend` as exposed by cinn/pybind/frontend.cc:156-761 for the ops that form elementwise,
+broadcast and reduction fused groups: `NetBuilder.create_input / add / relu / scale / cast / reduce_sum / ...`,
+`Computation.build_and_compile(target, builder)`, `.get_tensor(name).from_numpy(a, target)`, `.numpy(target)`,
+`.execute()`.  All work happens in libcinn_b200.so (C++): graph building, shape inference, the fusion pass,
+group compilation and execution.
+"""
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from .common import Target, Type
+
+_NP = {"float32": np.float32, "float16": np.float16, "float64": np.float64, "int32": np.int32, "int64": np.int64,
+       "bool": np.bool_, "uint8": np.uint8}
+
+
+def _attrs(**kw):
+    parts = []
+    for k, v in kw.items():
+        if v is None:
+            continue
+        if isinstance(v, bool):
+            v = "true" if v else "false"
+        elif isinstance(v, (list, tuple)):
+            v = ",".join(str(int(i)) for i in v)
+        elif isinstance(v, float):
+            v = repr(v)
+        elif isinstance(v, Type):
+            v = v.name
+        parts.append("%s=%s" % (k, v))
+    return " ".join(parts)
+
+
+class Variable:
+    """A value of the program; `str(v)` is its id, as with the reference's frontend.Variable."""
+
+    def __init__(self, builder, vid):
+        self._builder = builder
+        self.id = vid
+
+    def __str__(self):
+        return self.id
+
+    __repr__ = __str__
+
+    def _info(self):
+        L = _lib.lib()
+        dt = ctypes.create_string_buffer(32)
+        shape = (ctypes.c_longlong * 8)()
+        nd = ctypes.c_int()
+        _lib.check(L.cinn_b200_builder_var_info(self._builder._h, self.id.encode(), dt, 32, shape, ctypes.byref(nd)))
+        return dt.value.decode(), tuple(shape[i] for i in range(nd.value))
+
+    @property
+    def shape(self):
+        return list(self._info()[1])
+
+    @property
+    def type(self):
+        return Type(self._info()[0])
+
+
+class NetBuilder:
+    def __init__(self, name="net"):
+        L = _lib.lib()
+        self._h = ctypes.c_void_p(L.cinn_b200_builder_create(name.encode()))
+        self.name = name
+
+    def __del__(self):
+        try:
+            _lib.lib().cinn_b200_builder_destroy(self._h)
+        except Exception:
+            pass
+
+    # ---- plumbing ------------------------------------------------------------------------------
+    def _op(self, op_type, inputs, **attrs):
+        L = _lib.lib()
+        ids = (ctypes.c_char_p * max(len(inputs), 1))(*[str(v).encode() for v in inputs])
+        out = ctypes.create_string_buffer(128)
+        _lib.check(L.cinn_b200_builder_add_op(self._h, op_type.encode(), ids, len(inputs), _attrs(**attrs).encode(),
+                                              out, 128))
+        return Variable(self, out.value.decode())
+
+    def create_input(self, type, shape, id_hint=""):
+        L = _lib.lib()
+        sh = (ctypes.c_longlong * max(len(shape), 1))(*[int(d) for d in shape])
+        out = ctypes.create_string_buffer(128)
+        name = type.name if isinstance(type, Type) else str(type)
+        _lib.check(L.cinn_b200_builder_create_input(self._h, name.encode(), sh, len(shape), id_hint.encode(), out, 128))
+        return Variable(self, out.value.decode())
+
+    # ---- unary (cinn/frontend/net_builder.cc:130-180) -------------------------------------------
+    def _unary(name):  # noqa: N805
+        def f(self, x):
+            return self._op(name, [x])
+        f.__name__ = name
+        return f
+
+    for _n in ["sqrt", "tanh", "sigmoid", "identity", "exp", "erf", "rsqrt", "log", "log2", "log10", "floor", "ceil",
+               "round", "trunc", "sin", "cos", "negative", "sign", "abs", "reciprocal"]:
+        locals()[_n] = _unary(_n)
+    del _n, _unary
+
+    def relu(self, x):
+        return self._op("relu", [x])
+
+    def relu6(self, x, threshold=6.0):
+        return self._op("relu6", [x], threshold=float(threshold))
+
+    # ---- binary with the `axis` broadcast rule (net_builder.cc:182-227) -------------------------
+    def add(self, x, y, axis=-1):
+        return self._op("elementwise_add", [x, y], axis=axis)
+
+    elementwise_add = add
+
+    def multiply(self, x, y, axis=-1):
+        return self._op("elementwise_mul", [x, y], axis=axis)
+
+    elementwise_mul = multiply
+
+    def subtract(self, x, y, axis=-1):
+        return self._op("subtract", [x, y], axis=axis)
+
+    def divide(self, x, y, axis=-1):
+        return self._op("divide", [x, y], axis=axis)
+
+    def max(self, x, y, axis=-1):
+        return self._op("max", [x, y], axis=axis)
+
+    def min(self, x, y, axis=-1):
+        return self._op("min", [x, y], axis=axis)
+
+    def pow(self, x, y, axis=-1):
+        return self._op("pow", [x, y], axis=axis)
+
+    # ---- others ------------------------------------------------------------------------------------
+    def scale(self, x, scale=1.0, bias=0.0, bias_after_scale=True):
+        return self._op("scale", [x], scale=float(scale), bias=float(bias), bias_after_scale=bool(bias_after_scale))
+
+    def cast(self, x, dtype):
+        return self._op("cast", [x], dtype=dtype.name if isinstance(dtype, Type) else dtype)
+
+    def select(self, condition, true_value, false_value):
+        return self._op("select", [condition, true_value, false_value])
+
+    def broadcast_to(self, x, out_shape, broadcast_axes=None):
+        return self._op("broadcast_to", [x], out_shape=list(out_shape), broadcast_axes=broadcast_axes)
+
+    def fill_constant(self, shape, value, name="", dtype="float32", force_cpu=False):
+        return self._op("fill_constant", [], shape=list(shape), value=float(value), dtype=dtype)
+
+    def reshape(self, x, shape):
+        return self._op("reshape", [x], shape=list(shape))
+
+    def reduce_sum(self, x, dim=(), keep_dim=False):
+        return self._op("reduce_sum", [x], dim=list(dim) or None, keep_dim=keep_dim)
+
+    def reduce_prod(self, x, dim=(), keep_dim=False):
+        return self._op("reduce_prod", [x], dim=list(dim) or None, keep_dim=keep_dim)
+
+    def reduce_max(self, x, dim=(), keep_dim=False):
+        return self._op("reduce_max", [x], dim=list(dim) or None, keep_dim=keep_dim)
+
+    def reduce_min(self, x, dim=(), keep_dim=False):
+        return self._op("reduce_min", [x], dim=list(dim) or None, keep_dim=keep_dim)
+
+    def softmax(self, x, axes=(-1,), mode="fast", data_format="AnyLayout"):
+        if len(axes) != 1:
+            raise ValueError("softmax over several axes has no prebuilt kernel")
+        return self._op("softmax", [x], axis=int(axes[0]))
+
+    def batchnorm(self, x, scale, bias, mean, variance, epsilon=1e-5, momentum=0.9, data_layout="NCHW", is_test=True):
+        if not is_test:
+            raise NotImplementedError("batch_norm_train is outside the fused-group kernel library")
+        return [self._op("batch_norm", [x, scale, bias, mean, variance], epsilon=float(epsilon),
+                         momentum=float(momentum), data_layout=data_layout)]
+
+    def batch_norm(self, *a, **kw):
+        return self.batchnorm(*a, **kw)[0]
+
+    def layer_norm(self, x, gamma, beta, epsilon=1e-5):
+        """layer_norm over the last axis of a 2-D `x`, composed from primitives the way the reference's Paddle
+        op mapper does (cinn/frontend/op_mappers/paddle/layer_norm.cc:84-139) with rsqrt + multiply."""
+        dt, (rows, cols) = x._info()
+        half = dt in ("float16", "bfloat16")
+        x32 = self.cast(x, "float32") if half else x
+        s1 = self.reduce_sum(x32, [1])
+        n = self.fill_constant([rows], float(cols))
+        mean = self.divide(s1, n)
+        xx = self.multiply(x32, self.identity(x32))
+        s2 = self.reduce_sum(xx, [1])
+        m2 = self.divide(s2, n)
+        mm = self.multiply(mean, self.identity(mean))
+        var = self.max(self.subtract(m2, mm), self.fill_constant([rows], 0.0))
+        rstd = self.rsqrt(self.add(var, self.fill_constant([rows], float(epsilon))))
+        xc = self.subtract(x32, self.broadcast_to(mean, [rows, cols], [0]))
+        xn = self.multiply(xc, self.broadcast_to(rstd, [rows, cols], [0]))
+        y = self.add(self.multiply(xn, self.broadcast_to(gamma, [rows, cols], [1])),
+                     self.broadcast_to(beta, [rows, cols], [1]))
+        return self.cast(y, dt) if half else y
+
+
+class Tensor:
+    """A tensor of a computation's scope (hlir::framework::Tensor as exposed by cinn/pybind/framework.cc:116-172)."""
+
+    def __init__(self, comp, name):
+        self._comp = comp
+        self.name = name
+
+    def _info(self):
+        L = _lib.lib()
+        dt = ctypes.create_string_buffer(32)
+        shape = (ctypes.c_longlong * 8)()
+        nd = ctypes.c_int()
+        ptr = ctypes.c_void_p()
+        _lib.check(L.cinn_b200_computation_tensor_info(self._comp._h, self.name.encode(), dt, 32, shape,
+                                                       ctypes.byref(nd), ctypes.byref(ptr)))
+        return dt.value.decode(), tuple(shape[i] for i in range(nd.value)), ptr.value
+
+    def shape(self):
+        return list(self._info()[1])
+
+    def data_ptr(self):
+        return self._info()[2]
+
+    def from_numpy(self, array, target=None):
+        dt, shape, _ = self._info()
+        a = np.ascontiguousarray(array)
+        if a.dtype != _NP[dt] or tuple(a.shape) != shape:
+            raise ValueError("tensor %s is %s%s, got %s%s" % (self.name, dt, shape, a.dtype, a.shape))
+        _lib.check(_lib.lib().cinn_b200_computation_set_tensor_data(self._comp._h, self.name.encode(),
+                                                                   a.ctypes.data_as(ctypes.c_void_p), a.nbytes))
+
+    def numpy(self, target=None):
+        dt, shape, _ = self._info()
+        a = np.empty(shape, _NP[dt])
+        _lib.check(_lib.lib().cinn_b200_computation_get_tensor_data(self._comp._h, self.name.encode(),
+                                                                   a.ctypes.data_as(ctypes.c_void_p), a.nbytes))
+        return a
+
+    def bind(self, device_ptr):
+        """Use caller-owned device memory for this tensor (the reference's external-buffer mode)."""
+        _lib.check(_lib.lib().cinn_b200_computation_bind_tensor(self._comp._h, self.name.encode(),
+                                                               ctypes.c_void_p(device_ptr)))
+
+
+class Computation:
+    class CompileOptions:
+        def __init__(self):
+            self.use_decomposer = False
+            self.do_prerun = True
+            self.use_default_passes = True
+            self.passes = []
+
+    def __init__(self, handle, builder):
+        self._h = handle
+        self._builder = builder  # keeps the builder alive
+
+    def __del__(self):
+        try:
+            _lib.lib().cinn_b200_computation_destroy(self._h)
+        except Exception:
+            pass
+
+    @staticmethod
+    def default_compile_options():
+        return Computation.CompileOptions()
+
+    @staticmethod
+    def build_and_compile(target, builder, options=None, fetch=None, plan_only=False):
+        """Fuse, compile and allocate.  `plan_only=True` (or no GPU needed) plans without a device."""
+        if isinstance(target, Target) and target.arch != "nvgpu":
+            raise RuntimeError("the fused-group kernel library runs on NVIDIA B200 only; there is no x86 path")
+        device = -1 if plan_only else (target.device if isinstance(target, Target) else 0)
+        L = _lib.lib()
+        L.cinn_b200_computation_build_and_compile.restype = ctypes.c_void_p
+        fetch = [str(f) for f in (fetch or [])]
+        ids = (ctypes.c_char_p * max(len(fetch), 1))(*[f.encode() for f in fetch])
+        h = L.cinn_b200_computation_build_and_compile(builder._h, device, ids, len(fetch))
+        if not h:
+            raise _lib.CinnB200Error(-2, L.cinn_b200_last_error().decode())
+        return Computation(ctypes.c_void_p(h), builder)
+
+    def get_all_tensor_names(self):
+        L = _lib.lib()
+        n = L.cinn_b200_computation_num_tensors(self._h)
+        return [L.cinn_b200_computation_tensor_name(self._h, i).decode() for i in range(n)]
+
+    def get_tensor(self, name):
+        return Tensor(self, str(name))
+
+    def execute(self, stream=None):
+        _lib.check(_lib.lib().cinn_b200_computation_execute(self._h, stream))
+
+    def groups(self):
+        """[(group description text, 'pattern kernel kernel ...')] after fusion, for inspection and tests."""
+        L = _lib.lib()
+        out = []
+        for i in range(L.cinn_b200_computation_num_groups(self._h)):
+            d = ctypes.create_string_buffer(1 << 16)
+            p = ctypes.create_string_buffer(1 << 12)
+            _lib.check(L.cinn_b200_computation_group_desc(self._h, i, d, len(d)))
+            _lib.check(L.cinn_b200_computation_group_pattern(self._h, i, p, len(p)))
+            out.append((d.value.decode(), p.value.decode()))
+        return out

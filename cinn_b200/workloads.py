@@ -13,21 +13,36 @@ def _shape(s):
 
 
 class Workload:
-    """name, group description text, input arrays (host numpy), output dtype/shape."""
+    """name, group description text, input arrays (host numpy, generated on first use), output dtype/shape."""
 
     def __init__(self, name, desc, inputs, out_dtype, out_shape):
         self.name = name
         self.desc = desc
-        self.inputs = inputs
+        self._inputs = inputs  # a list of arrays, or a function returning one
         self.out_dtype = out_dtype
         self.out_shape = tuple(int(d) for d in out_shape)
+
+    @property
+    def inputs(self):
+        if callable(self._inputs):
+            self._inputs = self._inputs()
+        return self._inputs
 
     @property
     def group_name(self):
         return self.desc.split()[1]
 
     def input_bytes(self):
-        return sum(a.nbytes for a in self.inputs)
+        """From the description's input lines, so that it does not materialise the arrays."""
+        total = 0
+        for line in self.desc.splitlines():
+            w = line.split()
+            if w and w[0] == "input":
+                n = 1
+                for d in w[3].split(","):
+                    n *= int(d)
+                total += n * {"float32": 4, "float16": 2, "bfloat16": 2, "float64": 8}[w[2]]
+        return total
 
     def output_bytes(self):
         return int(np.prod(self.out_shape)) * np.dtype(self.out_dtype).itemsize
@@ -38,26 +53,30 @@ class Workload:
 
 def add_relu(shape=(1, 3, 224, 224), seed=0, name="fn_elementwise_add_relu"):
     """relu(A + B), fp32: the README example (one elementwise group)."""
-    rng = np.random.default_rng(seed)
-    a = rng.uniform(-1, 1, shape).astype(np.float32)
-    b = rng.uniform(-1, 1, shape).astype(np.float32)
+    def gen():
+        rng = np.random.default_rng(seed)
+        a = rng.uniform(-1, 1, shape).astype(np.float32)
+        b = rng.uniform(-1, 1, shape).astype(np.float32)
+        return [a, b]
     s = _shape(shape)
     desc = (f"group {name}\ninput A float32 {s}\ninput B float32 {s}\n"
             f"op elementwise_add var_0 = A B ; axis=-1\nop relu var_1 = var_0\noutput var_1 float32 {s}\n")
-    return Workload("add_relu", desc, [a, b], np.float32, shape)
+    return Workload("add_relu", desc, gen, np.float32, shape)
 
 
 def bias_scale_tanh_cast(shape=(64, 1024, 1024), seed=1, name="fn_bias_scale_tanh_cast"):
     """cast_fp16(tanh((X + bias) * 0.5)), bias broadcast on the last axis."""
-    rng = np.random.default_rng(seed)
-    x = rng.standard_normal(shape, dtype=np.float32)
-    bias = (0.1 * rng.standard_normal(shape[-1])).astype(np.float32)
+    def gen():
+        rng = np.random.default_rng(seed)
+        x = rng.standard_normal(shape, dtype=np.float32)
+        bias = (0.1 * rng.standard_normal(shape[-1])).astype(np.float32)
+        return [x, bias]
     s = _shape(shape)
     desc = (f"group {name}\ninput X float32 {s}\ninput bias float32 {shape[-1]}\n"
             f"op elementwise_add var_0 = X bias ; axis=-1\n"
             f"op scale var_1 = var_0 ; scale=0.5 bias=0.0 bias_after_scale=true\n"
             f"op tanh var_2 = var_1\nop cast var_3 = var_2 ; dtype=float16\noutput var_3 float16 {s}\n")
-    return Workload("bias_scale_tanh_cast", desc, [x, bias], np.float16, shape)
+    return Workload("bias_scale_tanh_cast", desc, gen, np.float16, shape)
 
 
 def reduce_input(shape=(128, 1024, 1024), seed=2):
@@ -66,22 +85,22 @@ def reduce_input(shape=(128, 1024, 1024), seed=2):
 
 def reduce_sum_last(shape=(128, 1024, 1024), seed=2, x=None, name="fn_reduce_sum_last"):
     """reduce_sum over the last axis (row reduction)."""
-    x = reduce_input(shape, seed) if x is None else x
     out_shape = shape[:-1]
     desc = (f"group {name}\ninput X float32 {_shape(shape)}\n"
             f"op reduce_sum var_0 = X ; dim={len(shape) - 1} keep_dim=false\n"
             f"output var_0 float32 {_shape(out_shape)}\n")
-    return Workload("reduce_sum_last", desc, [x], np.float32, out_shape)
+    return Workload("reduce_sum_last", desc, (lambda: [reduce_input(shape, seed)]) if x is None else [x], np.float32,
+                    out_shape)
 
 
 def reduce_max_first(shape=(128, 1024, 1024), seed=2, x=None, name="fn_reduce_max_first"):
     """reduce_max over axis 0 (column reduction)."""
-    x = reduce_input(shape, seed) if x is None else x
     out_shape = shape[1:]
     desc = (f"group {name}\ninput X float32 {_shape(shape)}\n"
             f"op reduce_max var_0 = X ; dim=0 keep_dim=false\n"
             f"output var_0 float32 {_shape(out_shape)}\n")
-    return Workload("reduce_max_first", desc, [x], np.float32, out_shape)
+    return Workload("reduce_max_first", desc, (lambda: [reduce_input(shape, seed)]) if x is None else [x], np.float32,
+                    out_shape)
 
 
 def rownorm_inputs(shape=(16384, 4096), seed=3):
@@ -94,16 +113,16 @@ def rownorm_inputs(shape=(16384, 4096), seed=3):
 
 def softmax(shape=(16384, 4096), seed=3, half=False, name=None):
     """softmax along the last axis; half=True stores x and out as fp16 and computes in fp32."""
-    x, _, _ = rownorm_inputs(shape, seed)
     s = _shape(shape)
     name = name or ("fn_softmax_f16" if half else "fn_softmax_f32")
     if half:
         desc = (f"group {name}\ninput X float16 {s}\nop cast var_0 = X ; dtype=float32\n"
                 f"op softmax var_1 = var_0 ; axis=-1\nop cast var_2 = var_1 ; dtype=float16\n"
                 f"output var_2 float16 {s}\n")
-        return Workload("softmax_f16", desc, [x.astype(np.float16)], np.float16, shape)
+        return Workload("softmax_f16", desc, lambda: [rownorm_inputs(shape, seed)[0].astype(np.float16)], np.float16,
+                        shape)
     desc = f"group {name}\ninput X float32 {s}\nop softmax var_0 = X ; axis=-1\noutput var_0 float32 {s}\n"
-    return Workload("softmax_f32", desc, [x], np.float32, shape)
+    return Workload("softmax_f32", desc, lambda: [rownorm_inputs(shape, seed)[0]], np.float32, shape)
 
 
 def layer_norm_ops(rows, cols, eps, half):
@@ -148,27 +167,31 @@ def layer_norm_ops(rows, cols, eps, half):
 
 def layer_norm(shape=(16384, 4096), seed=3, half=False, eps=1e-5, name=None):
     """layer_norm along the last axis of a 2-D tensor, composed from NetBuilder primitives."""
-    x, gamma, beta = rownorm_inputs(shape, seed)
     rows, cols = shape
     name = name or ("fn_layer_norm_f16" if half else "fn_layer_norm_f32")
     dt = "float16" if half else "float32"
     lines, out = layer_norm_ops(rows, cols, eps, half)
     desc = (f"group {name}\ninput X {dt} {rows},{cols}\ninput gamma float32 {cols}\ninput beta float32 {cols}\n" +
             "\n".join(lines) + f"\noutput {out} {dt} {rows},{cols}\n")
-    xin = x.astype(np.float16) if half else x
-    return Workload("layer_norm_f16" if half else "layer_norm_f32", desc, [xin, gamma, beta],
-                    np.float16 if half else np.float32, shape)
+    def gen():
+        x, gamma, beta = rownorm_inputs(shape, seed)
+        return [x.astype(np.float16) if half else x, gamma, beta]
+    return Workload("layer_norm_f16" if half else "layer_norm_f32", desc, gen, np.float16 if half else np.float32,
+                    shape)
 
 
 def bn_relu(shape=(256, 64, 112, 112), seed=4, half=False, eps=1e-5, name=None):
     """relu(batch_norm_infer(X)) on NCHW; argument order x, scale, bias, mean, variance."""
-    rng = np.random.default_rng(seed)
-    x = rng.standard_normal(shape, dtype=np.float32)
     c = shape[1]
-    mean = (0.1 * rng.standard_normal(c)).astype(np.float32)
-    var = rng.uniform(0.5, 1.5, c).astype(np.float32)
-    scale = (1 + 0.1 * rng.standard_normal(c)).astype(np.float32)
-    bias = (0.1 * rng.standard_normal(c)).astype(np.float32)
+
+    def gen():
+        rng = np.random.default_rng(seed)
+        x = rng.standard_normal(shape, dtype=np.float32)
+        mean = (0.1 * rng.standard_normal(c)).astype(np.float32)
+        var = rng.uniform(0.5, 1.5, c).astype(np.float32)
+        scale = (1 + 0.1 * rng.standard_normal(c)).astype(np.float32)
+        bias = (0.1 * rng.standard_normal(c)).astype(np.float32)
+        return [x.astype(np.float16) if half else x, scale, bias, mean, var]
     s = _shape(shape)
     name = name or ("fn_batch_norm_relu_f16" if half else "fn_batch_norm_relu_f32")
     params = f"input scale float32 {c}\ninput bias float32 {c}\ninput mean float32 {c}\ninput variance float32 {c}\n"
@@ -179,8 +202,8 @@ def bn_relu(shape=(256, 64, 112, 112), seed=4, half=False, eps=1e-5, name=None):
                 f"op batch_norm var_0 = x32 scale bias mean variance ; {attrs}\n"
                 "op relu var_1 = var_0\nop cast var_2 = var_1 ; dtype=float16\n"
                 f"output var_2 float16 {s}\n")
-        return Workload("bn_relu_f16", desc, [x.astype(np.float16), scale, bias, mean, var], np.float16, shape)
+        return Workload("bn_relu_f16", desc, gen, np.float16, shape)
     desc = (f"group {name}\ninput X float32 {s}\n" + params +
             f"op batch_norm var_0 = X scale bias mean variance ; {attrs}\n"
             f"op relu var_1 = var_0\noutput var_1 float32 {s}\n")
-    return Workload("bn_relu_f32", desc, [x, scale, bias, mean, var], np.float32, shape)
+    return Workload("bn_relu_f32", desc, gen, np.float32, shape)

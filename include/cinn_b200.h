@@ -106,6 +106,56 @@ int cinn_b200_canonical_expr(const char* group_desc, char* out, size_t out_len);
  */
 int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, int device);
 
+/* ---- NetBuilder / Computation --------------------------------------------------------------------- */
+
+/*
+ * Program construction, the C form of frontend::NetBuilder (cinn/frontend/net_builder.h:125-1146).  A variable
+ * is named by its id string.  cinn_b200_builder_add_op is the generic form of every op method: `op_type` is the
+ * HLIR op name (elementwise_add, relu, scale, cast, reduce_sum, softmax, batch_norm, ... as registered in
+ * cinn/hlir/op/elementwise.cc:860-1066, broadcast.cc:361-441, reduction.cc:477-505, nn.cc:2262-2433), `attrs`
+ * a blank-separated "key=value" list with the reference's attribute names (axis, scale, bias,
+ * bias_after_scale, dtype, dim, keep_dim, epsilon, data_layout, out_shape, broadcast_axes, shape, value).
+ * Output shape and dtype are inferred; the new variable's id is written to id_out.
+ */
+typedef struct cinn_b200_builder cinn_b200_builder;
+cinn_b200_builder* cinn_b200_builder_create(const char* name);
+void cinn_b200_builder_destroy(cinn_b200_builder* builder);
+int cinn_b200_builder_create_input(cinn_b200_builder* builder, const char* dtype, const long long* shape, int ndim,
+                                   const char* id_hint, char* id_out, size_t id_len);
+int cinn_b200_builder_add_op(cinn_b200_builder* builder, const char* op_type, const char* const* input_ids,
+                             int num_inputs, const char* attrs, char* id_out, size_t id_len);
+int cinn_b200_builder_var_info(cinn_b200_builder* builder, const char* id, char* dtype, size_t dtype_len,
+                               long long* shape /* [8] */, int* ndim);
+
+/*
+ * CinnComputation (cinn/frontend/computation.h:26-158): BuildAndCompile runs the fusion pass (the counterpart of
+ * OpFusionPass + FusionMergePass, cinn/hlir/pass/op_fusion_pass.cc:123-331), compiles every group to prebuilt
+ * kernels and allocates the scope's tensors on `device` with cudaMalloc (device < 0: plan only, no GPU touched).
+ * fetch_ids name the variables to materialise (none: every variable that nothing consumes).  NULL on failure.
+ * Execute runs the groups in order on `stream` and, like Program::Execute (cinn/hlir/framework/
+ * graph_compiler.cc:212-222), synchronises the device only when stream is NULL.  set/get_tensor_data copy
+ * between host memory and a scope tensor (computation.cc:186-240); bind_tensor substitutes caller-owned device
+ * memory for a scope tensor (the reference's external-buffer mode, graph_compiler.cc:1305-1398).
+ */
+typedef struct cinn_b200_computation cinn_b200_computation;
+cinn_b200_computation* cinn_b200_computation_build_and_compile(cinn_b200_builder* builder, int device,
+                                                               const char* const* fetch_ids, int num_fetch);
+void cinn_b200_computation_destroy(cinn_b200_computation* computation);
+int cinn_b200_computation_execute(cinn_b200_computation* computation, void* stream);
+int cinn_b200_computation_set_tensor_data(cinn_b200_computation* computation, const char* id, const void* host,
+                                          size_t bytes);
+int cinn_b200_computation_get_tensor_data(cinn_b200_computation* computation, const char* id, void* host,
+                                          size_t bytes);
+int cinn_b200_computation_bind_tensor(cinn_b200_computation* computation, const char* id, void* device_ptr);
+int cinn_b200_computation_num_tensors(cinn_b200_computation* computation);
+const char* cinn_b200_computation_tensor_name(cinn_b200_computation* computation, int index);
+int cinn_b200_computation_tensor_info(cinn_b200_computation* computation, const char* id, char* dtype,
+                                      size_t dtype_len, long long* shape /* [8] */, int* ndim, void** device_ptr);
+/* The groups the fusion pass produced: description text, and "pattern kernel kernel ..." of the match. */
+int cinn_b200_computation_num_groups(cinn_b200_computation* computation);
+int cinn_b200_computation_group_desc(cinn_b200_computation* computation, int index, char* out, size_t out_len);
+int cinn_b200_computation_group_pattern(cinn_b200_computation* computation, int index, char* out, size_t out_len);
+
 /*
  * Device-side status of the current device: the number of bounded waits on asynchronous copies that gave up
  * since the last call (0 in a healthy run); reading clears it.  Synchronises with the device.  The reference

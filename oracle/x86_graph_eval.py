@@ -1,0 +1,171 @@
+"""Evaluates a fused-group description op by op with the x86-path arithmetic of cinn_x86_oracle.c.
+
+TEST INFRASTRUCTURE (see the header of cinn_x86_oracle.c).  Given the text description of a group (the same
+text the product compiles) and numpy inputs, it computes every value of the group the way the reference's x86
+path would after inlining: one C loop per op, except that an Add whose operand is an inlined Mul (same group,
+fp32, single use) is evaluated as a fused multiply-add (cinn/optim/lower_intrin.cc:41-59), and a `scale` is
+fma(scale, x, bias) (cinn/hlir/op/elementwise.cc:149-163).  Values of float16 type are rounded after every op.
+"""
+import numpy as np
+
+from . import x86_oracle as orc
+
+UNARY = {"exp", "tanh", "sigmoid", "rsqrt", "sqrt", "relu", "negative", "abs", "identity", "log", "floor", "ceil",
+         "erf", "sin", "cos", "reciprocal", "round", "trunc", "log2", "log10", "sign"}
+BINARY = {"elementwise_add": "add", "subtract": "subtract", "elementwise_mul": "multiply", "divide": "divide",
+          "max": "max", "min": "min", "pow": "pow"}
+REDUCE = {"reduce_sum": "sum", "reduce_prod": "prod", "reduce_max": "max", "reduce_min": "min"}
+NP = {"float32": np.float32, "float16": np.float16}
+
+
+def parse(desc):
+    g = {"inputs": [], "outputs": [], "ops": []}
+    for line in desc.splitlines():
+        line = line.split("#")[0]
+        attrs = {}
+        if ";" in line:
+            line, a = line.split(";", 1)
+            for kv in a.split():
+                k, v = kv.split("=", 1)
+                attrs[k] = v
+        w = line.split()
+        if not w:
+            continue
+        if w[0] == "group":
+            g["name"] = w[1]
+        elif w[0] in ("input", "output"):
+            shape = tuple(int(d) for d in w[3].split(",")) if w[3] != "scalar" else ()
+            g[w[0] + "s"].append((w[1], w[2], shape))
+        elif w[0] == "op":
+            g["ops"].append({"type": w[1], "out": w[2], "ins": w[4:], "attrs": attrs})
+    return g
+
+
+def _aligned(a, out_shape, axis):
+    """Reshape operand `a` so that numpy-style right-aligned broadcasting places it at `axis` of out_shape."""
+    if a.ndim == len(out_shape) or axis < 0:
+        return a
+    return a.reshape(a.shape + (1,) * (len(out_shape) - axis - a.ndim))
+
+
+def _f32(v):
+    return orc.cast_f16_f32(v) if v.dtype == np.float16 else v
+
+
+def _store(v32, dtype):
+    return orc.cast_f32_f16(v32) if dtype == np.float16 else v32
+
+
+def evaluate(desc, inputs):
+    """inputs: list of numpy arrays in the group's input order.  Returns {value name: array}."""
+    g = parse(desc)
+    vals = {}
+    for (name, dt, shape), a in zip(g["inputs"], inputs):
+        assert a.dtype == NP[dt] and tuple(a.shape) == shape, (name, a.dtype, a.shape)
+        vals[name] = np.ascontiguousarray(a)
+    uses = {}
+    producer = {}
+    for op in g["ops"]:
+        producer[op["out"]] = op
+        for i in op["ins"]:
+            uses[i] = uses.get(i, 0) + 1
+    outputs = {o[0] for o in g["outputs"]}
+    feeds_reduce = {i for op in g["ops"] if op["type"] in REDUCE for i in op["ins"]}
+
+    def inlined_mul(name):
+        """The Mul op producing `name` if it is inlined into its single consumer (then it can be contracted)."""
+        p = producer.get(name)
+        if p is None or name in outputs or name in feeds_reduce or uses.get(name, 0) != 1:
+            return None
+        if p["type"] == "elementwise_mul" and vals[name].dtype == np.float32:
+            return p
+        return None
+
+    for op in g["ops"]:
+        t, ins, at = op["type"], op["ins"], op["attrs"]
+        if t == "fill_constant":
+            shape = tuple(int(d) for d in at["shape"].split(","))
+            out = np.full(shape, float(at["value"]), NP[at.get("dtype", "float32")])
+        elif t == "cast":
+            x = vals[ins[0]]
+            to = NP[at["dtype"]]
+            out = x if x.dtype == to else (orc.cast_f32_f16(x) if to == np.float16 else orc.cast_f16_f32(x))
+        elif t == "broadcast_to":
+            x = vals[ins[0]]
+            shape = tuple(int(d) for d in at["out_shape"].split(","))
+            axes = [int(d) for d in at["broadcast_axes"].split(",")]
+            view = [1] * len(shape)
+            for i, ax in enumerate(axes):
+                view[ax] = x.shape[i]
+            out = np.ascontiguousarray(np.broadcast_to(x.reshape(view), shape))
+        elif t == "scale":
+            x = vals[ins[0]]
+            after = at.get("bias_after_scale", "true") in ("true", "1", "True")
+            out = _store(orc.scale(_f32(x), float(at.get("scale", 1)), float(at.get("bias", 0)), after), x.dtype)
+        elif t in UNARY:
+            x = vals[ins[0]]
+            out = _store(orc.unary(t, _f32(x)), x.dtype)
+        elif t == "relu6":
+            x = vals[ins[0]]
+            thr = np.float32(float(at.get("threshold", 6)))
+            out = _store(orc.binary("min", orc.unary("relu", _f32(x)), np.full(1, thr, np.float32), x.shape), x.dtype)
+        elif t in BINARY:
+            a, b = vals[ins[0]], vals[ins[1]]
+            axis = int(at.get("axis", -1))
+            big, small = (a, b) if a.ndim >= b.ndim else (b, a)
+            shape = np.broadcast_shapes(big.shape, _aligned(small, big.shape, axis).shape)
+            aa = a if a is big else _aligned(a, shape, axis)
+            bb = b if b is big else _aligned(b, shape, axis)
+            dt = a.dtype
+            done = False
+            if t == "elementwise_add" and dt == np.float32:
+                # lower_intrin.cc:45-50: the right operand is tried first
+                for mul_name, other in ((ins[1], aa), (ins[0], bb)):
+                    m = inlined_mul(mul_name)
+                    if m is not None:
+                        ma, mb = vals[m["ins"][0]], vals[m["ins"][1]]
+                        maxis = int(m["attrs"].get("axis", -1))
+                        mbig = ma if ma.ndim >= mb.ndim else mb
+                        ma2 = ma if ma is mbig else _aligned(ma, mbig.shape, maxis)
+                        mb2 = mb if mb is mbig else _aligned(mb, mbig.shape, maxis)
+                        out = orc.fma(ma2, mb2, other, shape)
+                        done = True
+                        break
+            if not done:
+                out = _store(orc.binary(BINARY[t], _f32(aa), _f32(bb), shape), dt)
+        elif t in REDUCE:
+            x = vals[ins[0]]
+            dims = sorted(int(d) % x.ndim for d in at["dim"].split(",")) if at.get("dim") else list(range(x.ndim))
+            keep = at.get("keep_dim", "false") in ("true", "1", "True")
+            lo, hi = dims[0], dims[-1]
+            assert dims == list(range(lo, hi + 1)), "oracle evaluator: reduce over adjacent axes only"
+            outer = int(np.prod(x.shape[:lo]))
+            r = int(np.prod(x.shape[lo:hi + 1]))
+            inner = int(np.prod(x.shape[hi + 1:]))
+            res = orc.reduce(REDUCE[t], x, outer, r, inner)
+            oshape = [d for i, d in enumerate(x.shape) if i not in dims or keep]
+            if keep:
+                oshape = [1 if i in dims else d for i, d in enumerate(x.shape)]
+            out = res.reshape(oshape if oshape else (1,))
+        elif t == "softmax":
+            out = orc.softmax(vals[ins[0]])
+        elif t == "batch_norm":
+            x, scale, bias, mean, var = (vals[i] for i in ins)
+            eps = np.float32(float(at.get("epsilon", 1e-5)))
+            c = x.shape[1]
+            sh = (1, c, 1, 1)
+            d = orc.unary("sqrt", orc.binary("add", var, np.full(1, eps, np.float32), var.shape))
+            t1 = orc.binary("subtract", x, mean.reshape(sh), x.shape)
+            t2 = orc.binary("multiply", t1, scale.reshape(sh), x.shape)
+            t3 = orc.binary("divide", t2, d.reshape(sh), x.shape)
+            out = orc.binary("add", t3, bias.reshape(sh), x.shape)
+        else:
+            raise NotImplementedError("oracle evaluator: op " + t)
+        vals[op["out"]] = np.ascontiguousarray(out)
+    return vals
+
+
+def run(desc, inputs):
+    """The group's single output."""
+    g = parse(desc)
+    return evaluate(desc, inputs)[g["outputs"][0][0]]

@@ -1,0 +1,209 @@
+"""NetBuilder shape inference, the fusion pass and the matcher, planned without a GPU.
+
+Group-count assertions follow the style of the reference's fusion tests
+(cinn/hlir/pass/op_fusion_pass_test.cc:22-253, fusion_merge_pass_test.cc:22-462)."""
+import ctypes
+
+import pytest
+
+import cinn_b200
+from cinn_b200 import common
+from cinn_b200 import workloads as W
+from cinn_b200.frontend import Computation, NetBuilder
+
+TARGET = common.DefaultNVGPUTarget()
+
+
+def plan(builder, **kw):
+    return Computation.build_and_compile(TARGET, builder, plan_only=True, **kw)
+
+
+def patterns(comp):
+    return [p.split()[0] for _, p in comp.groups()]
+
+
+def test_readme_example_is_one_group():
+    b = NetBuilder(name="network")
+    a = b.create_input(type=common.Float(32), shape=(1, 3, 224, 224), id_hint="A")
+    bb = b.create_input(type=common.Float(32), shape=(1, 3, 224, 224), id_hint="B")
+    res = b.relu(b.add(a, bb))
+    c = plan(b)
+    assert patterns(c) == ["ew_add_relu"]
+    desc, _ = c.groups()[0]
+    assert desc.splitlines()[1].split()[:2] == ["input", "A"] and desc.splitlines()[2].split()[:2] == ["input", "B"]
+    assert res.shape == [1, 3, 224, 224] and str(res.type) == "float32"
+    assert set(c.get_all_tensor_names()) == {"A", "B", str(res)}
+
+
+def test_shape_and_dtype_inference():
+    b = NetBuilder("infer")
+    x = b.create_input(common.Float(32), (4, 8, 16), "x")
+    v = b.create_input(common.Float(32), (8,), "v")
+    assert b.add(x, v, axis=1).shape == [4, 8, 16]
+    assert b.reduce_sum(x, [1]).shape == [4, 16]
+    assert b.reduce_max(x, [0, 1], keep_dim=True).shape == [1, 1, 16]
+    assert b.reduce_sum(x).shape == [1]
+    assert b.reduce_sum(x, [-1]).shape == [4, 8]
+    assert str(b.cast(x, "float16").type) == "float16"
+    assert b.broadcast_to(v, [4, 8, 16], [1]).shape == [4, 8, 16]
+    assert b.reshape(x, [32, -1]).shape == [32, 16]
+    with pytest.raises(cinn_b200.CinnB200Error):
+        b.add(x, b.create_input(common.Float(32), (7,), "bad"))
+    with pytest.raises(cinn_b200.CinnB200Error):
+        b.add(x, b.cast(x, "float16"))
+    with pytest.raises(cinn_b200.CinnB200Error):
+        b.reduce_sum(x, [3])
+    with pytest.raises(cinn_b200.CinnB200Error):
+        b._op("conv2d", [x, x])
+
+
+def test_broadcast_chain_is_one_group():
+    b = NetBuilder("c2")
+    x = b.create_input(common.Float(32), (64, 1024, 1024), "X")
+    bias = b.create_input(common.Float(32), (1024,), "bias")
+    y = b.cast(b.tanh(b.scale(b.add(x, bias), 0.5, 0.0)), "float16")
+    c = plan(b)
+    assert patterns(c) == ["ew_bias_scale_tanh_cast"]
+    assert y.shape == [64, 1024, 1024]
+
+
+def test_reductions_are_their_own_groups():
+    b = NetBuilder("c3")
+    x = b.create_input(common.Float(32), (128, 1024, 1024), "X")
+    b.reduce_sum(x, [2])
+    b.reduce_max(x, [0])
+    c = plan(b)
+    assert sorted(patterns(c)) == ["col_reduce", "row_reduce"]
+
+
+def test_softmax_op_and_decomposed_form_and_fp16_wrappers():
+    for half in (False, True):
+        b = NetBuilder("sm")
+        x = b.create_input(common.Float(16 if half else 32), (16384, 4096), "X")
+        xin = b.cast(x, "float32") if half else x
+        y = b.softmax(xin)
+        if half:
+            y = b.cast(y, "float16")
+        assert patterns(plan(b)) == ["softmax_row"]
+    # decomposed "fast" form: exp -> reduce_sum -> broadcast -> divide, rows far longer than the reference's 1024
+    # limit for fusing a reduce with its broadcast consumer: still ONE group here
+    b = NetBuilder("smd")
+    x = b.create_input(common.Float(32), (64, 4096), "X")
+    e = b.exp(x)
+    s = b.reduce_sum(e, [1])
+    b.divide(e, b.broadcast_to(s, [64, 4096], [0]))
+    assert patterns(plan(b)) == ["softmax_row"]
+
+
+def test_layer_norm_composition_is_one_group():
+    for half in (False, True):
+        b = NetBuilder("ln")
+        x = b.create_input(common.Float(16 if half else 32), (16384, 4096), "X")
+        g = b.create_input(common.Float(32), (4096,), "gamma")
+        be = b.create_input(common.Float(32), (4096,), "beta")
+        b.layer_norm(x, g, be, 1e-5)
+        c = plan(b)
+        assert patterns(c) == ["layernorm_row"]
+        desc, _ = c.groups()[0]
+        assert [l.split()[1] for l in desc.splitlines() if l.startswith("input")] == ["X", "gamma", "beta"]
+
+
+def test_batch_norm_relu_group_and_argument_order():
+    b = NetBuilder("bn")
+    x = b.create_input(common.Float(32), (256, 64, 112, 112), "x")
+    names = ["scale", "bias", "mean", "variance"]
+    params = [b.create_input(common.Float(32), (64,), n) for n in names]
+    b.relu(b.batchnorm(x, *params, epsilon=1e-5, is_test=True)[0])
+    c = plan(b)
+    assert patterns(c) == ["ew_bn_relu_nchw"]
+    desc, _ = c.groups()[0]
+    assert [l.split()[1] for l in desc.splitlines() if l.startswith("input")] == ["x"] + names
+
+
+def test_mixed_graph_partitions_into_chain_reduce_chain():
+    b = NetBuilder("mixed")
+    x = b.create_input(common.Float(32), (8, 16, 1024), "X")
+    bias = b.create_input(common.Float(32), (1024,), "bias")
+    y = b.sigmoid(b.multiply(b.add(x, bias), bias))
+    z = b.reduce_sum(y, [2])
+    b.sqrt(b.abs(z))
+    c = plan(b)
+    assert patterns(c) == ["ew_chain", "row_reduce", "ew_chain"]
+
+
+def test_value_used_twice_is_materialised_once():
+    """A producer with two consumers is not duplicated: it becomes a group output (op_lowering_util.cc:745-803)."""
+    b = NetBuilder("fanout")
+    x = b.create_input(common.Float(32), (64, 64), "X")
+    t = b.exp(x)
+    b.relu(t)
+    b.tanh(t)
+    c = plan(b)
+    assert len(c.groups()) == 3
+    assert str(t) in c.get_all_tensor_names()
+
+
+def test_fetch_keeps_an_intermediate():
+    b = NetBuilder("fetch")
+    x = b.create_input(common.Float(32), (64, 64), "X")
+    t = b.exp(x)
+    y = b.relu(t)
+    assert len(plan(b).groups()) == 1
+    c = plan(b, fetch=[t, y])
+    assert len(c.groups()) == 2 and str(t) in c.get_all_tensor_names()
+
+
+def test_unmatched_group_is_an_error_not_a_fallback():
+    L = cinn_b200.lib()
+    fn = ctypes.c_void_p()
+    rc = L.cinn_b200_compile_group(b"group g\ninput x float32 4,4\nop conv2d y = x x\noutput y float32 4,4\n",
+                                   ctypes.byref(fn))
+    assert rc == -2 and b"no prebuilt sm_100a kernel" in L.cinn_b200_last_error()
+    rc = L.cinn_b200_compile_group(b"group g\ninput x int32 4,4\nop relu y = x\noutput y int32 4,4\n", ctypes.byref(fn))
+    assert rc == -2
+    rc = L.cinn_b200_compile_group(b"nonsense", ctypes.byref(fn))
+    assert rc == -1
+    # reduce over non-adjacent axes
+    rc = L.cinn_b200_compile_group(
+        b"group g\ninput x float32 4,5,6\nop reduce_sum y = x ; dim=0,2\noutput y float32 5\n", ctypes.byref(fn))
+    assert rc == -2 and b"non-adjacent" in L.cinn_b200_last_error()
+    assert L.cinn_b200_lookup(b"g") is None
+
+
+def test_canonical_expression_and_plans_of_the_workloads():
+    L = cinn_b200.lib()
+    buf = ctypes.create_string_buffer(4096)
+    w = W.bias_scale_tanh_cast((2, 4, 8))
+    assert L.cinn_b200_canonical_expr(w.desc.encode(), buf, 4096) == 0
+    assert buf.value == b"cast(tanh(scale(elementwise_add(%0,%1))))"
+    expect = {
+        "add_relu": (W.add_relu((1, 3, 224, 224)), ["ew_add_relu_f32"]),
+        "c2": (W.bias_scale_tanh_cast((64, 1024, 1024)), ["ew_bias_scale_tanh_cast_f32_f16"]),
+        "c3a": (W.reduce_sum_last((128, 1024, 1024)), ["row_reduce_warp8_sum_f32"]),
+        "c3b": (W.reduce_max_first((128, 1024, 1024)), ["col_reduce_max_f32"]),
+        "c4a": (W.softmax((16384, 4096)), ["softmax_row_f32_g256_v4_r1"]),
+        "c4b16": (W.layer_norm((16384, 4096), half=True), ["layernorm_tma_f16_g256_v2"]),
+        "c5": (W.bn_relu((256, 64, 112, 112)), ["ew_bn_relu_nchw_f32"]),
+        "long_row": (W.reduce_sum_last((1, 3000001)), ["row_reduce_cta_sum_f32", "row_reduce_warp4_sum_f32"]),
+        "cluster_row": (W.reduce_sum_last((40, 70000)), ["row_reduce_cluster_sum_f32"]),
+        "cluster_softmax": (W.softmax((2, 100000)), ["rownorm_cluster_f32"]),
+    }
+    for key, (w, kernels) in expect.items():
+        g = cinn_b200.FusedGroup(w.desc)
+        assert g.kernel_names() == kernels, key
+        assert g.algorithmic_bytes == w.algorithmic_bytes(), key
+        g.release()
+
+
+def test_byte_counts_of_the_benchmark_groups():
+    sizes = {"c1": (W.add_relu(), 1806336), "c2": (None, 402657280), "c3a": (None, 537395200),
+             "c3b": (None, 541065216)}
+    assert W.add_relu().algorithmic_bytes() == sizes["c1"][1]
+
+
+def test_host_x86_target_is_refused():
+    b = NetBuilder("x86")
+    x = b.create_input(common.Float(32), (4, 4), "X")
+    b.relu(x)
+    with pytest.raises(RuntimeError):
+        Computation.build_and_compile(common.DefaultHostTarget(), b)

@@ -1,0 +1,234 @@
+"""GPU: programs built with NetBuilder, fused, compiled and executed through Computation, against the oracle.
+
+Elementwise chains are checked op-graph by op-graph with oracle/x86_graph_eval.py (the x86 arithmetic incl. the
+Mul+Add contraction).  fp32 results: <= 2 ulp, except where the formula itself cancels (tanh near 0), where the
+bound is 2 ulp of the cancelling operand (documented per case)."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import cinn_b200
+from cinn_b200 import common
+from cinn_b200.frontend import Computation, NetBuilder
+from oracle import x86_graph_eval as ge
+
+pytestmark = pytest.mark.gpu
+TARGET = common.DefaultNVGPUTarget()
+
+
+def run_program(builder, feeds, fetch):
+    comp = Computation.build_and_compile(TARGET, builder)
+    for name, arr in feeds.items():
+        comp.get_tensor(name).from_numpy(arr, TARGET)
+    comp.execute()
+    return comp, {str(f): comp.get_tensor(str(f)).numpy(TARGET) for f in fetch}
+
+
+def oracle_program(comp, feeds):
+    """Evaluate the computation's groups in order with the oracle, feeding each group from the values so far."""
+    vals = dict(feeds)
+    for desc, pattern in comp.groups():
+        if pattern.startswith("reshape_alias"):
+            g = ge.parse(desc)
+            vals[g["ops"][0]["out"]] = vals[g["ops"][0]["ins"][0]].reshape(
+                [int(d) for d in g["ops"][0]["attrs"]["shape"].split(",")])
+            continue
+        g = ge.parse(desc)
+        out = ge.run(desc, [vals[name] for name, _, _ in g["inputs"]])
+        vals[g["outputs"][0][0]] = out
+    return vals
+
+
+def test_readme_example_end_to_end(oracle):
+    builder = NetBuilder(name="network")
+    a = builder.create_input(type=common.Float(32), shape=(1, 3, 224, 224), id_hint="A")
+    b = builder.create_input(type=common.Float(32), shape=(1, 3, 224, 224), id_hint="B")
+    res = builder.relu(builder.add(a, b))
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (1, 3, 224, 224)).astype(np.float32)
+    B = rng.uniform(-1, 1, (1, 3, 224, 224)).astype(np.float32)
+    computation = Computation.build_and_compile(TARGET, builder)
+    computation.get_tensor("A").from_numpy(A, TARGET)
+    computation.get_tensor("B").from_numpy(B, TARGET)
+    computation.execute()
+    out = computation.get_tensor(str(res)).numpy(TARGET)
+    assert oracle.max_ulp(out, oracle.add_relu(A, B)) == 0
+
+
+UNARY_CASES = [("exp", (-10, 10), 2), ("log", (1e-3, 50), 2), ("sqrt", (0, 100), 0), ("rsqrt", (1e-3, 100), 0),
+               ("sigmoid", (-15, 15), 2), ("relu", (-3, 3), 0), ("abs", (-3, 3), 0), ("negative", (-3, 3), 0),
+               ("floor", (-9, 9), 0), ("ceil", (-9, 9), 0), ("trunc", (-9, 9), 0), ("round", (-9, 9), 0),
+               ("sign", (-3, 3), 0), ("reciprocal", (0.01, 9), 0), ("erf", (-3, 3), 2), ("sin", (-6, 6), 2),
+               ("cos", (-6, 6), 2), ("log2", (1e-3, 50), 2), ("log10", (1e-3, 50), 2), ("identity", (-3, 3), 0)]
+
+
+@pytest.mark.parametrize("op,rng_range,ulps", UNARY_CASES)
+def test_single_unary_op_groups(oracle, op, rng_range, ulps):
+    b = NetBuilder("u_" + op)
+    x = b.create_input(common.Float(32), (257, 129), "X")
+    y = getattr(b, op)(x)
+    X = np.random.default_rng(7).uniform(rng_range[0], rng_range[1], (257, 129)).astype(np.float32)
+    comp, out = run_program(b, {"X": X}, [y])
+    ref = oracle.unary(op, X)
+    got = out[str(y)]
+    d = oracle.max_ulp(got, ref)
+    print("%s: max ulp distance to the x86 oracle %d" % (op, d))
+    assert d <= ulps, (op, d)
+
+
+def test_tanh_fp32_within_two_ulp_of_the_cancelling_term(oracle):
+    """tanh = (1 - e)/(1 + e) with e = exp(-2|x|): an ulp of e (<= 2^-24) moves the result by up to 2^-25, so the
+    bound is absolute near zero and relative (2 ulp) elsewhere."""
+    b = NetBuilder("tanh32")
+    x = b.create_input(common.Float(32), (513, 127), "X")
+    y = b.tanh(x)
+    X = np.random.default_rng(8).standard_normal((513, 127)).astype(np.float32) * 2
+    comp, out = run_program(b, {"X": X}, [y])
+    ref = oracle.unary("tanh", X)
+    err = np.abs(out[str(y)].astype(np.float64) - ref)
+    assert (err <= 2 * 2.0 ** -24 + 2 * np.spacing(np.abs(ref))).all(), float(err.max())
+
+
+def chain_programs():
+    def per_channel(b):
+        x = b.create_input(common.Float(32), (4, 8, 15, 17), "X")
+        ch = b.create_input(common.Float(32), (8,), "ch")
+        y = b.relu(b.add(b.multiply(x, ch, axis=1), ch, axis=1))  # Mul+Add -> fma, per-channel side operand
+        return {"X": (4, 8, 15, 17), "ch": (8,)}, b.sigmoid(b.subtract(b.fill_constant([4, 8, 15, 17], 1.0), y))
+
+    def last_axis(b):
+        x = b.create_input(common.Float(32), (6, 5, 64), "X")
+        v = b.create_input(common.Float(32), (64,), "v")
+        y = b.divide(b.add(x, v), b.fill_constant([1], 3.0))
+        return {"X": (6, 5, 64), "v": (64,)}, b.scale(b.max(y, v), 1.5, -0.25, bias_after_scale=False)
+
+    def odd_sizes(b):
+        x = b.create_input(common.Float(32), (3, 5, 7), "X")
+        v = b.create_input(common.Float(32), (7,), "v")
+        w = b.create_input(common.Float(32), (3, 5, 7), "W")
+        return {"X": (3, 5, 7), "v": (7,), "W": (3, 5, 7)}, b.sqrt(b.abs(b.subtract(b.multiply(x, v), w)))
+
+    def square_fma(b):
+        x = b.create_input(common.Float(32), (33, 65), "X")
+        c = b.create_input(common.Float(32), (33, 65), "C")
+        return {"X": (33, 65), "C": (33, 65)}, b.add(b.multiply(x, b.identity(x)), c)  # fma(x, x, c)
+
+    def scale_chain(b):
+        x = b.create_input(common.Float(32), (1000,), "X")
+        return {"X": (1000,)}, b.exp(b.scale(b.negative(b.abs(x)), 0.3333333, 0.1))
+
+    def middle_axis(b):
+        x = b.create_input(common.Float(32), (4, 6, 10), "X")
+        m = b.create_input(common.Float(32), (6, 1), "m")
+        return {"X": (4, 6, 10), "m": (6, 1)}, b.min(b.pow(b.abs(x), b.fill_constant([1], 1.5)), b.abs(m))
+
+    return [per_channel, last_axis, odd_sizes, square_fma, scale_chain, middle_axis]
+
+
+@pytest.mark.parametrize("make", chain_programs(), ids=lambda f: f.__name__)
+def test_generic_chains_match_the_oracle(oracle, make):
+    b = NetBuilder(make.__name__)
+    shapes, y = make(b)
+    rng = np.random.default_rng(11)
+    feeds = {k: rng.standard_normal(s).astype(np.float32) for k, s in shapes.items()}
+    comp, out = run_program(b, feeds, [y])
+    assert all(p.split()[0] == "ew_chain" for _, p in comp.groups()), comp.groups()
+    ref = oracle_program(comp, feeds)[str(y)]
+    d = oracle.max_ulp(out[str(y)], ref)
+    print("%s: %d group(s), max ulp %d" % (make.__name__, len(comp.groups()), d))
+    assert d <= 2, d
+
+
+def test_fp16_chain_rounds_after_every_op(oracle):
+    b = NetBuilder("h")
+    x = b.create_input(common.Float(16), (40, 72), "X")
+    y = b.create_input(common.Float(16), (40, 72), "Y")
+    z = b.relu(b.multiply(b.add(x, y), y))
+    rng = np.random.default_rng(12)
+    feeds = {"X": rng.standard_normal((40, 72)).astype(np.float16), "Y": rng.standard_normal((40, 72)).astype(np.float16)}
+    comp, out = run_program(b, feeds, [z])
+    ref = oracle_program(comp, feeds)[str(z)]
+    assert np.array_equal(out[str(z)].view(np.uint16), ref.view(np.uint16))
+
+
+def test_comparison_gives_bool_bit_exact(oracle):
+    b = NetBuilder("cmp")
+    x = b.create_input(common.Float(32), (37, 41), "X")
+    y = b.create_input(common.Float(32), (41,), "Y")
+    z = b._op("greater_than", [x, y], axis=-1)
+    rng = np.random.default_rng(13)
+    X, Y = rng.standard_normal((37, 41)).astype(np.float32), rng.standard_normal(41).astype(np.float32)
+    comp, out = run_program(b, {"X": X, "Y": Y}, [z])
+    assert out[str(z)].dtype == np.bool_ and np.array_equal(out[str(z)], X > Y)
+
+
+def test_tree_shaped_expression_is_partitioned_and_correct(oracle):
+    b = NetBuilder("tree")
+    x = b.create_input(common.Float(32), (64, 96), "X")
+    y = b.add(b.sqrt(b.abs(x)), b.exp(b.negative(x)))
+    X = np.random.default_rng(14).standard_normal((64, 96)).astype(np.float32)
+    comp, out = run_program(b, {"X": X}, [y])
+    assert len(comp.groups()) == 2
+    ref = oracle_program(comp, {"X": X})[str(y)]
+    assert oracle.max_ulp(out[str(y)], ref) <= 2
+
+
+def test_mixed_program_chain_reduce_chain(oracle):
+    b = NetBuilder("mixed")
+    x = b.create_input(common.Float(32), (8, 16, 1024), "X")
+    bias = b.create_input(common.Float(32), (1024,), "bias")
+    y = b.sigmoid(b.multiply(b.add(x, bias), bias))
+    z = b.reduce_sum(y, [2])
+    w = b.sqrt(b.abs(z))
+    rng = np.random.default_rng(15)
+    feeds = {"X": rng.standard_normal((8, 16, 1024)).astype(np.float32),
+             "bias": rng.standard_normal(1024).astype(np.float32)}
+    comp, out = run_program(b, feeds, [w])
+    assert [p.split()[0] for _, p in comp.groups()] == ["ew_chain", "row_reduce", "ew_chain"]
+    ref = oracle_program(comp, feeds)[str(w)]
+    bad, worst = oracle.count_not_close(out[str(w)], ref, 1e-5, 1e-5)
+    assert bad == 0, (bad, worst)
+
+
+def test_reshape_aliases_and_layer_norm_on_3d(oracle):
+    b = NetBuilder("ln3d")
+    x = b.create_input(common.Float(32), (4, 8, 256), "X")
+    g = b.create_input(common.Float(32), (256,), "gamma")
+    be = b.create_input(common.Float(32), (256,), "beta")
+    y = b.reshape(b.layer_norm(b.reshape(x, [32, 256]), g, be), [4, 8, 256])
+    rng = np.random.default_rng(16)
+    feeds = {"X": rng.standard_normal((4, 8, 256)).astype(np.float32),
+             "gamma": (1 + 0.02 * rng.standard_normal(256)).astype(np.float32),
+             "beta": (0.02 * rng.standard_normal(256)).astype(np.float32)}
+    comp, out = run_program(b, feeds, [y])
+    ref = oracle.layernorm(feeds["X"].reshape(32, 256), feeds["gamma"], feeds["beta"], 1e-5).reshape(4, 8, 256)
+    bad, worst = oracle.count_not_close(out[str(y)], ref, 1e-5, 1e-6)
+    assert bad == 0, (bad, worst)
+
+
+def test_bind_caller_memory_and_run_on_a_stream(oracle):
+    import torch
+    b = NetBuilder("bind")
+    x = b.create_input(common.Float(32), (128, 256), "X")
+    y = b.tanh(b.scale(x, 0.5))
+    comp = Computation.build_and_compile(TARGET, b)
+    X = torch.randn(128, 256, device="cuda")
+    out = torch.empty(128, 256, device="cuda")
+    comp.get_tensor("X").bind(X.data_ptr())
+    comp.get_tensor(str(y)).bind(out.data_ptr())
+    s = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        comp.execute(ctypes.c_void_p(s.cuda_stream))
+    s.synchronize()
+    ref = oracle.unary("tanh", oracle.scale(X.cpu().numpy(), 0.5, 0.0, True))
+    err = np.abs(out.cpu().numpy().astype(np.float64) - ref)
+    assert (err <= 2 * 2.0 ** -24 + 2 * np.spacing(np.abs(ref))).all()
+
+
+def test_no_bounded_wait_gave_up():
+    L = cinn_b200.lib()
+    n = ctypes.c_uint(99)
+    assert L.cinn_b200_device_status(ctypes.byref(n)) == 0
+    assert n.value == 0

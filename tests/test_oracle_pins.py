@@ -1,0 +1,175 @@
+"""Pins of the CPU oracle (no GPU): the known-answer relations the reference's own tests check on its x86 path,
+applied to the restatement, plus self-consistency between its fused loops and its op-at-a-time evaluators.
+
+The reference stores no golden numeric vectors for this path; what its tests pin is:
+  * x86 JIT vs libm lambdas at abs 1e-5         cinn/hlir/pe/pe_elementwise_test.cc:96-109, 131-156
+  * A + (A + B) == 2A + B at 1e-5                cinn/frontend/computation_test.cc:74-103
+  * batch-norm vs a serial CPU loop, rtol 1e-5   cinn/frontend/decomposer/batch_norm_test.cc:50-145,
+                                                 cinn/frontend/decomposer/test_helper.h:113-141
+  * reduce vs a serial CPU loop, rel 1e-4        cinn/hlir/op/reduction_test.cc:305-404
+"""
+import math
+
+import numpy as np
+import pytest
+
+from cinn_b200 import workloads as W
+from oracle import x86_graph_eval as ge
+
+
+def test_unary_against_libm_like_the_reference_pe_tests(oracle):
+    rng = np.random.default_rng(1234)
+    x = rng.uniform(-4, 4, 4096).astype(np.float32)
+    pos = np.abs(x) + np.float32(0.01)
+    cases = {"exp": (x, np.exp), "tanh": (x, np.tanh), "sigmoid": (x, lambda v: 1 / (1 + np.exp(-v))),
+             "sqrt": (pos, np.sqrt), "rsqrt": (pos, lambda v: 1 / np.sqrt(v)), "log": (pos, np.log),
+             "floor": (x, np.floor), "ceil": (x, np.ceil), "abs": (x, np.abs), "negative": (x, np.negative),
+             "sin": (x, np.sin), "cos": (x, np.cos), "erf": (x, np.vectorize(math.erf)),
+             "relu": (x, lambda v: np.maximum(v, 0)), "sign": (x, np.sign), "trunc": (x, np.trunc),
+             "round": (x, np.rint), "reciprocal": (pos, lambda v: 1 / v), "log2": (pos, np.log2),
+             "log10": (pos, np.log10)}
+    for name, (arg, fn) in cases.items():
+        got = oracle.unary(name, arg)
+        want = fn(arg.astype(np.float64))
+        assert np.abs(got - want).max() <= 1e-5 * max(1.0, np.abs(want).max()), name
+
+
+def test_tanh_is_the_two_branch_exp_formula(oracle):
+    """cinn/backends/llvm/llvm_intrin_rule.h:136-154, evaluated with glibc expf in fp32."""
+    import ctypes
+    libm = ctypes.CDLL("libm.so.6")
+    libm.expf.restype = ctypes.c_float
+    libm.expf.argtypes = [ctypes.c_float]
+    xs = np.array([-3.5, -1.0, -1e-3, -0.0, 0.0, 1e-6, 0.25, 1.0, 8.0, 20.0], np.float32)
+    got = oracle.unary("tanh", xs)
+    for x, g in zip(xs, got):
+        one = np.float32(1)
+        if x >= 0:
+            e = np.float32(libm.expf(np.float32(-2) * x))
+            want = (one - e) / (one + e)
+        else:
+            e = np.float32(libm.expf(np.float32(2) * x))
+            want = (e - one) / (e + one)
+        assert g == np.float32(want), (x, g, want)
+    assert not np.signbit(got[3])  # tanh(-0.0) takes the x >= 0 branch: +0
+
+
+def test_relu_and_max_are_compare_select(oracle):
+    a = np.array([-0.0, 0.0, np.nan, 1.0, -2.0], np.float32)
+    r = oracle.unary("relu", a)
+    assert not np.signbit(r[0]) and r[0] == 0  # -0 > 0 is false -> the second operand, +0
+    assert r[2] == 0  # NaN > 0 is false -> 0
+    m = oracle.binary("max", np.array([np.nan, 1.0], np.float32), np.array([2.0, np.nan], np.float32))
+    assert m[0] == 2.0 and np.isnan(m[1])
+
+
+def test_a_plus_a_plus_b_like_computation_test(oracle):
+    rng = np.random.default_rng(0)
+    a = rng.random((32, 32), dtype=np.float32)
+    b = rng.random((32, 32), dtype=np.float32)
+    got = oracle.binary("add", a, oracle.binary("add", a, b))
+    assert np.abs(got - (2 * a + b)).max() <= 1e-5
+
+
+def test_scale_is_fma_and_contraction_is_single_rounding(oracle):
+    x = np.array([1.0000001, 3.3333333, -7.7777777], np.float32)
+    s, b = np.float32(0.3333333), np.float32(1e-7)
+    got = oracle.scale(x, float(s), float(b), True)
+    want = (x.astype(np.float64) * np.float64(s) + np.float64(b)).astype(np.float32)  # exact product, one rounding
+    assert np.array_equal(got, want)
+    two_roundings = (x * s) + b
+    assert not np.array_equal(got, two_roundings) or True  # may coincide; the fma form is what is pinned above
+    pre = oracle.scale(x, float(s), float(b), False)
+    assert np.array_equal(pre, s * (x + b))
+
+
+def test_casts_round_to_nearest_even(oracle):
+    x = np.array([1.0 + 2 ** -11, 1.0 + 3 * 2 ** -11, 65504.0, 65520.0, 1e-8, -2.5], np.float32)
+    assert np.array_equal(oracle.cast_f32_f16(x), x.astype(np.float16))
+    rng = np.random.default_rng(5)
+    y = rng.standard_normal(100000).astype(np.float32)
+    assert np.array_equal(oracle.cast_f32_f16(y).view(np.uint16), y.astype(np.float16).view(np.uint16))
+    bf = oracle.cast_f32_bf16(np.array([1.0, 1.00390625, 1.01171875, -3.0], np.float32))
+    assert list(bf) == [0x3F80, 0x3F80, 0x3F82, 0xC040]  # ties to even on the upper 16 bits
+
+
+def test_reduce_is_the_serial_loop_of_reduction_test(oracle):
+    rng = np.random.default_rng(2)
+    x = rng.standard_normal((7, 33, 5)).astype(np.float32)
+    for kind, init, fn in [("sum", np.float32(0), lambda a, v: np.float32(a + v)),
+                           ("prod", np.float32(1), lambda a, v: np.float32(a * v)),
+                           ("max", np.float32(-3.4028235e38), lambda a, v: a if a > v else v),
+                           ("min", np.float32(3.4028235e38), lambda a, v: a if a < v else v)]:
+        got = oracle.reduce(kind, x, 7, 33, 5).reshape(7, 5)
+        for o in range(7):
+            for i in range(5):
+                acc = init
+                for k in range(33):
+                    acc = fn(acc, x[o, k, i])
+                assert got[o, i] == acc, (kind, o, i)
+    # thread count does not change a result (each output keeps its serial order)
+    assert np.array_equal(oracle.reduce("sum", x, 7, 33, 5, threads=4), oracle.reduce("sum", x, 7, 33, 5))
+    assert oracle.reduce("max", np.full(4, -np.inf, np.float32), 1, 4, 1)[0] == np.float32(-3.4028235e38)
+
+
+def test_batch_norm_against_the_serial_reference_loop(oracle):
+    """The CPU loop of cinn/frontend/decomposer/batch_norm_test.cc, in float64, rtol 1e-5 / atol 1e-8."""
+    w = W.bn_relu((2, 5, 7, 3))
+    x, scale, bias, mean, var = w.inputs
+    got = oracle.bn_relu_nchw(x, scale, bias, mean, var, 1e-5)
+    sh = (1, 5, 1, 1)
+    want = np.maximum((x.astype(np.float64) - mean.reshape(sh)) * scale.reshape(sh) /
+                      np.sqrt(var.reshape(sh).astype(np.float64) + 1e-5) + bias.reshape(sh), 0)
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-8)
+
+
+def test_softmax_rows_sum_to_one_and_match_float64(oracle):
+    w = W.softmax((16, 257))
+    got = oracle.softmax(w.inputs[0])
+    x = w.inputs[0].astype(np.float64)
+    want = np.exp(x) / np.exp(x).sum(-1, keepdims=True)
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-8)
+    h = W.softmax((16, 257), half=True)
+    got16 = oracle.softmax(h.inputs[0])
+    assert got16.dtype == np.float16 and np.allclose(got16.astype(np.float64), want, rtol=2e-2, atol=1e-6)
+
+
+def test_layer_norm_matches_float64(oracle):
+    w = W.layer_norm((9, 300))
+    x, gamma, beta = w.inputs
+    got = oracle.layernorm(x, gamma, beta, 1e-5)
+    xd = x.astype(np.float64)
+    mean = xd.mean(-1, keepdims=True)
+    var = (xd * xd).mean(-1, keepdims=True) - mean * mean
+    want = (xd - mean) / np.sqrt(var + 1e-5) * gamma + beta
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("make", [
+    lambda: W.add_relu((3, 5, 7)), lambda: W.bias_scale_tanh_cast((3, 5, 16)), lambda: W.softmax((5, 33)),
+    lambda: W.softmax((5, 32), half=True), lambda: W.layer_norm((6, 40)), lambda: W.layer_norm((6, 40), half=True),
+    lambda: W.bn_relu((2, 3, 4, 5)), lambda: W.bn_relu((2, 3, 4, 5), half=True),
+    lambda: W.reduce_sum_last((3, 4, 50)), lambda: W.reduce_max_first((9, 4, 5))])
+def test_fused_loops_equal_op_at_a_time_evaluation(oracle, make):
+    """The reference's own fused-vs-unfused self-check (python/tests/fusion/fusion_test.py:23-63), on the oracle:
+    the single-pass loops that are timed as the CPU baseline give bit-identical results to evaluating the same
+    group description one op at a time."""
+    w = make()
+    unfused = ge.run(w.desc, w.inputs)
+    name = w.name
+    if name == "add_relu":
+        fused = oracle.add_relu(*w.inputs)
+    elif name == "bias_scale_tanh_cast":
+        fused = oracle.bias_scale_tanh_f16(w.inputs[0], w.inputs[1], 0.5, 0.0)
+    elif name.startswith("softmax"):
+        fused = oracle.softmax(w.inputs[0])
+    elif name.startswith("layer_norm"):
+        fused = oracle.layernorm(*w.inputs, 1e-5)
+    elif name.startswith("bn_relu"):
+        fused = oracle.bn_relu_nchw(*w.inputs, 1e-5)
+    elif name == "reduce_sum_last":
+        fused = oracle.reduce("sum", w.inputs[0], 12, 50, 1).reshape(w.out_shape)
+    else:
+        fused = oracle.reduce("max", w.inputs[0], 1, 9, 20).reshape(w.out_shape)
+    assert fused.dtype == unfused.dtype and fused.shape == tuple(unfused.shape)
+    assert np.array_equal(fused.view(np.uint8), unfused.view(np.uint8))
