@@ -101,6 +101,8 @@ def lib():
         L.cinn_b200_computation_group_desc.argtypes = [vp, ci, ctypes.c_char_p, ctypes.c_size_t]
         L.cinn_b200_computation_group_pattern.restype = ci
         L.cinn_b200_computation_group_pattern.argtypes = [vp, ci, ctypes.c_char_p, ctypes.c_size_t]
+        L.cinn_b200_col_reduce_f32_static_scratch.restype = ci
+        L.cinn_b200_col_reduce_f32_static_scratch.argtypes = [ci, vp, vp, ll, ll, ll, vp]
         L.cinn_b200_device_status.restype = ci
         L.cinn_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         L.cinn_b200_set_option.restype = ci

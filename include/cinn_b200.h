@@ -157,6 +157,27 @@ int cinn_b200_computation_group_desc(cinn_b200_computation* computation, int ind
 int cinn_b200_computation_group_pattern(cinn_b200_computation* computation, int index, char* out, size_t out_len);
 
 /*
+ * Column reduction without any allocation.  No counterpart in the reference (its kernels never need scratch
+ * memory: it reduces such shapes with one serial loop per output element).
+ *
+ * y[o, i] = reduce over k of x[o, k, i], x viewed as [outer, r, inner] fp32, kind 0 sum / 1 prod / 2 max / 3 min:
+ * the same kernels and the same two-step split over r as a compiled reduce group uses, but the partials go to a
+ * fixed 4 MiB array inside the library instead of scratch obtained with cudaMalloc.  It exists for callers that
+ * must not have this library allocate device memory: a host framework that owns the whole device pool and passes
+ * in only buffers of its choosing, or a serving loop where the device-wide synchronisation of a cudaMalloc is
+ * not acceptable.  x and y are device pointers supplied by the caller; the call issues one or two launches on
+ * `stream` and returns without synchronising.
+ *
+ * Limits and rules: the partials must fit the static array -- roughly 2 * outer * inner <= 1,048,576 floats;
+ * larger outputs are refused with CINN_B200_ENOSPACE and a message (use a compiled group instead).  The first call
+ * on each device looks up the array's device address (cudaGetSymbolAddress); make that first call outside any
+ * stream capture.  All calls share the array, so calls that can overlap on the GPU (different streams or threads)
+ * must be serialised by the caller.  Nothing needs to be cleared between calls.
+ */
+int cinn_b200_col_reduce_f32_static_scratch(int kind, const float* x, float* y, long long outer, long long r,
+                                            long long inner, void* stream);
+
+/*
  * Device-side status of the current device: the number of bounded waits on asynchronous copies that gave up
  * since the last call (0 in a healthy run); reading clears it.  Synchronises with the device.  The reference
  * has no counterpart (its generated kernels never wait on asynchronous copies).
