@@ -230,6 +230,41 @@ def run_profile_case(args):
     return 0
 
 
+def sharded_reduce_max(torch, dist, dev, world, rank, peak):
+    """reduce_max over axis 0 of [128,1024,1024] with axis 0 sharded over the ranks (strong scaling): the local
+    column reduction alone, and with the NCCL all-reduce(MAX) of the 4 MiB partials that finishes it."""
+    from cinn_b200 import sharding
+    full = (128, 1024, 1024)
+    op = sharding.ShardedReduceAxis0.from_library("max", full, world, rank)
+    x = torch.randn(op.local_shape, device=dev)
+    out = torch.empty(op.out_shape, device=dev)
+    stream = torch.cuda.current_stream()
+
+    def timed(fn, iters=30, warm=5):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_local = timed(lambda: op.local_reduce(x, out))
+    ms_total = timed(lambda: op(x, out))
+    total_bytes = 4 * (full[0] * full[1] * full[2]) + 4 * full[1] * full[2]
+    return {"ms_local_kernel": round(ms_local, 5), "ms_with_allreduce": round(ms_total, 5),
+            "GB/s_whole_job_local": round(total_bytes / (ms_local * 1e-3) / 1e9, 1),
+            "GB/s_whole_job_with_allreduce": round(total_bytes / (ms_total * 1e-3) / 1e9, 1),
+            "frac_of_peak_per_gpu_with_allreduce": round(total_bytes / (ms_total * 1e-3) / 1e9 / world / peak, 4),
+            "scaling": "strong", "collective": "nccl all_reduce(MAX) of 4 MiB per rank"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -354,6 +389,10 @@ def main():
                                 "sample": "full headline group, 3 passes, OpenMP over rows, %d threads" % threads}
     if rank == 0 and world == 1 and not args.no_side_groups:
         line["groups"] = side_groups(torch, dev, peak, args.only)
+    if world > 1 and not args.no_side_groups:
+        sharded = sharded_reduce_max(torch, dist, dev, world, rank, peak)
+        if rank == 0:
+            line["groups"] = {"reduce_max_axis0_128x1024x1024_sharded_on_axis0": sharded}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

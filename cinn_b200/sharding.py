@@ -1,0 +1,92 @@
+"""Outer-axis sharding of fused groups over the GPUs of one node (one process per GPU, torch.distributed).
+
+Every group of this library is independent along its outermost axis, so a rank simply compiles the group for its
+own slice of that axis and runs it on its own buffers: no communication.  The one exception is a reduction over
+the sharded axis itself (reduce over axis 0 of a tensor sharded on axis 0): each rank reduces its slice to a
+full-size partial in its own HBM and a single all-reduce with the matching operator combines the partials
+(NCCL over NVLink on GPUs, gloo in the CPU tests).  Kernels never read another GPU's memory.
+
+The reference has no multi-GPU execution at all (its only per-device state is one CUmodule per card,
+cinn/runtime/cuda/cuda_module.h:67); this module is new functionality behind the same group interface.
+"""
+import torch
+import torch.distributed as dist
+
+_REDUCE_OPS = {"sum": dist.ReduceOp.SUM, "prod": dist.ReduceOp.PRODUCT, "max": dist.ReduceOp.MAX,
+               "min": dist.ReduceOp.MIN}
+
+
+def shard_range(extent, world, rank):
+    """(start, count) of rank's contiguous slice of an axis of `extent` elements; earlier ranks take the remainder."""
+    if not 0 <= rank < world:
+        raise ValueError("rank %d outside world of %d" % (rank, world))
+    base, rem = divmod(extent, world)
+    start = rank * base + min(rank, rem)
+    return start, base + (1 if rank < rem else 0)
+
+
+def sharded_shape(shape, world, rank):
+    """Shape of rank's slice when axis 0 is sharded."""
+    _, count = shard_range(shape[0], world, rank)
+    return (count,) + tuple(shape[1:])
+
+
+def finish_reduce_over_sharded_axis(partial, kind, group=None):
+    """All-reduce the per-rank partial of a reduction over the sharded axis, in place, on the current stream.
+
+    `partial` holds this rank's reduce_<kind> over its slice (identity elements if the slice is empty)."""
+    if kind not in _REDUCE_OPS:
+        raise ValueError("unknown reduce kind %r" % (kind,))
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(partial, op=_REDUCE_OPS[kind], group=group)
+    return partial
+
+
+def identity_of(kind):
+    """Initial value of the reduction (cinn/lang/builtin.cc:123-143: lowest()/max(), not infinities)."""
+    return {"sum": 0.0, "prod": 1.0, "max": -3.4028234663852886e38, "min": 3.4028234663852886e38}[kind]
+
+
+class ShardedReduceAxis0:
+    """reduce_<kind> over axis 0 of a [R, ...] fp32 tensor whose axis 0 is sharded over the ranks.
+
+    `local_reduce(x_slice, out)` computes the reduction of this rank's slice into `out`; on GPUs it is the
+    compiled group's entry point (see `from_library`), in CPU tests a stand-in."""
+
+    def __init__(self, kind, full_shape, world, rank, local_reduce, group=None):
+        self.kind, self.full_shape, self.world, self.rank = kind, tuple(full_shape), world, rank
+        self.local_shape = sharded_shape(full_shape, world, rank)
+        self.out_shape = tuple(full_shape[1:])
+        self.local_reduce = local_reduce
+        self.group = group
+
+    @classmethod
+    def from_library(cls, kind, full_shape, world, rank, group=None):
+        import cinn_b200
+        local = sharded_shape(full_shape, world, rank)
+        fused = None
+        if local[0] > 0:
+            s_in = ",".join(str(d) for d in local)
+            s_out = ",".join(str(d) for d in full_shape[1:])
+            fused = cinn_b200.FusedGroup(
+                "group fn_reduce_%s_axis0_rank%d\ninput X float32 %s\nop reduce_%s var_0 = X ; dim=0 keep_dim=false\n"
+                "output var_0 float32 %s\n" % (kind, rank, s_in, kind, s_out))
+
+        def local_reduce(x, out):
+            stream = torch.cuda.current_stream().cuda_stream
+            import ctypes
+            fused.run([x, out], ctypes.c_void_p(stream))
+
+        obj = cls(kind, full_shape, world, rank, local_reduce, group)
+        obj.fused = fused
+        return obj
+
+    def __call__(self, x_slice, out):
+        if tuple(x_slice.shape) != self.local_shape:
+            raise ValueError("rank %d expects a slice of shape %s, got %s" % (self.rank, self.local_shape,
+                                                                           tuple(x_slice.shape)))
+        if self.local_shape[0] > 0:
+            self.local_reduce(x_slice, out)
+        else:
+            out.fill_(identity_of(self.kind))
+        return finish_reduce_over_sharded_axis(out, self.kind, self.group)

@@ -239,3 +239,16 @@ def test_errors_do_not_launch():
     with pytest.raises(cinn_b200.CinnB200Error):
         g.run([a, a.half(), a])  # wrong dtype
     torch.cuda.synchronize()
+
+
+def test_sharded_reduce_single_rank_matches_plain_group(oracle):
+    """World size 1: the sharded reduction is the plain group (the cross-rank finish is a no-op)."""
+    import torch
+    from cinn_b200 import sharding
+    shape = (64, 32, 128)
+    op = sharding.ShardedReduceAxis0.from_library("max", shape, 1, 0)
+    x = W.reduce_input(shape, seed=9)
+    out = torch.empty(shape[1:], device="cuda")
+    op(torch.from_numpy(x).cuda(), out)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().reshape(-1), oracle.reduce("max", x, 1, 64, 32 * 128))
