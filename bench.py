@@ -95,7 +95,8 @@ def cpu_reference_run(steps, warmup):
     """Times the CPU restatement of the reference's x86 path on the headline group, all host threads."""
     from oracle import x86_oracle
     from cinn_b200 import workloads as W
-    threads = x86_oracle.num_threads()
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every core this process may run on instead.
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else x86_oracle.num_threads()
     w = W.bias_scale_tanh_cast(HEADLINE_SHAPE)
     x, bias = w.inputs
     for _ in range(max(warmup, 1)):

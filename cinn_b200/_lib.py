@@ -105,6 +105,8 @@ def lib():
         L.cinn_b200_col_reduce_f32_static_scratch.argtypes = [ci, vp, vp, ll, ll, ll, vp]
         L.cinn_b200_device_status.restype = ci
         L.cinn_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        L.cinn_b200_group_host_chunks.restype = ci
+        L.cinn_b200_group_host_chunks.argtypes = [cs]
         L.cinn_b200_set_option.restype = ci
         L.cinn_b200_set_option.argtypes = [cs, ll]
         _lib = L

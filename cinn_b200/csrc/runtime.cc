@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <unordered_map>
 #include <utility>
@@ -157,14 +158,23 @@ static int LaunchKernel(const void* kernel_fn, void* v_args, int num_args, int g
 // ---- group registry ---------------------------------------------------------------------------------
 constexpr int kMaxGroups = 1024;
 
+constexpr int kHostStreams = 3;
+
 struct HostStaging {
   void* dev        = nullptr;
   size_t bytes     = 0;
-  cudaStream_t s   = nullptr;
+  cudaStream_t s[kHostStreams] = {nullptr, nullptr, nullptr};
+  cudaEvent_t replicated_ready = nullptr;
 };
 
 struct GroupSlot {
   std::unique_ptr<CompiledGroup> plan;
+  GroupDesc desc;                                // what the plan was compiled from
+  // run_host pipelines copies and kernels over chunks of the outer axis when the group allows it.
+  bool chunk_tried = false;
+  int chunk_count  = 0;                          // 0: not chunkable
+  std::vector<bool> chunk_sharded;               // per argument (inputs then outputs): sliced on axis 0
+  std::unique_ptr<CompiledGroup> chunk_plan;     // the group compiled for one chunk
   std::unordered_map<int, void*> scratch;        // device ordinal -> scratch buffer
   std::unordered_map<int, HostStaging> staging;  // device ordinal -> staging for run_host
 };
@@ -237,8 +247,7 @@ static int CheckArgs(const CompiledGroup& plan, void* pod_args, int num_args, st
   return CINN_B200_OK;
 }
 
-static int RunPlan(GroupSlot& slot, const std::vector<cinn_buffer_t*>& bufs, void* stream) {
-  const CompiledGroup& plan = *slot.plan;
+static int RunPlan(const CompiledGroup& plan, GroupSlot& slot, const std::vector<cinn_buffer_t*>& bufs, void* stream) {
   const int n_in            = (int)plan.inputs.size();
   // Device scratch (split reductions only), one buffer per device, allocated on first use.
   uint8_t* scratch = nullptr;
@@ -320,7 +329,7 @@ static int RunSlot(int slot_index, void* pod_args, int num_args, void* stream) {
   std::vector<cinn_buffer_t*> bufs;
   int rc = CheckArgs(*slot.plan, pod_args, num_args, &bufs);
   if (rc != CINN_B200_OK) return rc;
-  return RunPlan(slot, bufs, stream);
+  return RunPlan(*slot.plan, slot, bufs, stream);
 }
 
 static int SlotOf(const char* fn_name) {
@@ -343,12 +352,17 @@ static void FreeSlotResources(GroupSlot& s) {
     cudaGetDevice(&prev);
     cudaSetDevice(kv.first);
     if (kv.second.dev) cudaFree(kv.second.dev);
-    if (kv.second.s) cudaStreamDestroy(kv.second.s);
+    for (int k = 0; k < kHostStreams; ++k)
+      if (kv.second.s[k]) cudaStreamDestroy(kv.second.s[k]);
+    if (kv.second.replicated_ready) cudaEventDestroy(kv.second.replicated_ready);
     cudaSetDevice(prev);
   }
   s.scratch.clear();
   s.staging.clear();
   s.plan.reset();
+  s.chunk_plan.reset();
+  s.chunk_tried = false;
+  s.chunk_count = 0;
 }
 
 }  // namespace cinn_b200
@@ -421,6 +435,7 @@ int cinn_b200_compile_group(const char* group_desc, lower_func_ptr_g* fn_out) {
     g_slot_of_name[g.name] = slot;
   }
   g_slots[slot].plan = std::move(plan);
+  g_slots[slot].desc = g;
   if (fn_out) *fn_out = g_trampolines[slot];
   return CINN_B200_OK;
 }
@@ -486,6 +501,85 @@ int cinn_b200_canonical_expr(const char* group_desc, char* out, size_t out_len) 
   return CopyOut(e, out, out_len);
 }
 
+// Decides once per group whether run_host may pipeline over chunks of the outer axis, and compiles the group for
+// one chunk.  A group qualifies when its output and at least one input carry the outer extent D0 as their first
+// dimension, no operand is indexed by that axis other than through its own first dimension, no reduction runs over
+// it, and the chunk-sized group compiles to the same kernel family without scratch memory.
+static void PrepareChunking(GroupSlot& slot) {
+  slot.chunk_tried = true;
+  const GroupDesc& g = slot.desc;
+  const CompiledGroup& plan = *slot.plan;
+  if (plan.scratch_bytes != 0 || g.outputs.size() != 1 || g.outputs[0].shape.empty()) return;
+  const int64_t d0 = g.outputs[0].shape[0];
+  if (d0 < 2) return;
+  const size_t out_rank = g.outputs[0].shape.size();
+  size_t max_rank       = out_rank;
+  for (auto& t : g.inputs) max_rank = std::max(max_rank, t.shape.size());
+  std::vector<bool> sharded;
+  bool any = false;
+  std::map<std::string, bool> sharded_input;
+  for (auto& t : g.inputs) {
+    bool sh = !t.shape.empty() && t.shape[0] == d0 && t.shape.size() == max_rank;
+    sharded.push_back(sh);
+    sharded_input[t.name] = sh;
+    any = any || sh;
+  }
+  sharded.push_back(true);
+  if (!any) return;
+  auto attr = [](const OpDesc& op, const char* k) {
+    auto it = op.attrs.find(k);
+    return it == op.attrs.end() ? std::string() : it->second;
+  };
+  auto first_int = [](const std::string& text) { return text.empty() ? (int64_t)-1 : (int64_t)atoll(text.c_str()); };
+  for (auto& op : g.ops) {
+    if (op.type.rfind("reduce_", 0) == 0) {
+      std::string dims = "," + attr(op, "dim") + ",";
+      if (dims == ",," || dims.find(",0,") != std::string::npos) return;  // reduces the outer axis
+    }
+    for (auto& in : op.inputs) {
+      auto it = sharded_input.find(in);
+      if (it == sharded_input.end() || it->second) continue;
+      // a replicated input: it must not be aligned to axis 0
+      if (attr(op, "axis") == "0") return;
+      if (op.type == "broadcast_to") {
+        std::string axes = "," + attr(op, "broadcast_axes") + ",";
+        if (axes.find(",0,") != std::string::npos) return;
+      }
+    }
+  }
+  size_t total = 0;
+  for (auto& t : g.inputs) total += (size_t)t.numel() * DTypeBytes(t.dtype);
+  total += (size_t)g.outputs[0].numel() * DTypeBytes(g.outputs[0].dtype);
+  int chunks = 0;
+  for (int c : {16, 8, 4, 2})
+    if (d0 % c == 0 && total / c >= (4u << 20)) {
+      chunks = c;
+      break;
+    }
+  if (!chunks) return;
+  const int64_t part = d0 / chunks;
+  GroupDesc sub      = g;
+  sub.name           = g.name + "__chunk";
+  for (size_t i = 0; i < sub.inputs.size(); ++i)
+    if (sharded[i]) sub.inputs[i].shape[0] = part;
+  sub.outputs[0].shape[0] = part;
+  for (auto& op : sub.ops) {
+    for (const char* key : {"shape", "out_shape"}) {
+      auto it = op.attrs.find(key);
+      if (it != op.attrs.end() && first_int(it->second) == d0) {
+        auto comma = it->second.find(',');
+        it->second = std::to_string(part) + (comma == std::string::npos ? "" : it->second.substr(comma));
+      }
+    }
+  }
+  std::string err;
+  auto sub_plan = CompileGroup(sub, CurrentDeviceInfo(), &err);
+  if (!sub_plan || sub_plan->pattern != plan.pattern || sub_plan->scratch_bytes != 0) return;
+  slot.chunk_plan    = std::move(sub_plan);
+  slot.chunk_sharded = sharded;
+  slot.chunk_count   = chunks;
+}
+
 int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, int device) {
   int slot_index = SlotOf(fn_name);
   if (slot_index < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
@@ -510,6 +604,7 @@ int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, 
   {
     std::lock_guard<std::mutex> lk(g_mu);
     st = &slot.staging[device];
+    if (!slot.chunk_tried) PrepareChunking(slot);
   }
   if (st->bytes < total) {
     if (st->dev) cudaFree(st->dev);
@@ -518,33 +613,89 @@ int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, 
     if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaMalloc of %zu staging bytes: %s", total, cudaGetErrorString(e));
     st->bytes = total;
   }
-  if (!st->s) {
-    e = cudaStreamCreateWithFlags(&st->s, cudaStreamNonBlocking);
+  for (int k = 0; k < kHostStreams; ++k) {
+    if (st->s[k]) continue;
+    e = cudaStreamCreateWithFlags(&st->s[k], cudaStreamNonBlocking);
     if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaStreamCreate: %s", cudaGetErrorString(e));
   }
-  std::vector<cinn_buffer_t> dev_bufs(num_args);
-  std::vector<cinn_pod_value_t> dev_pods(num_args);
-  for (int i = 0; i < num_args; ++i) {
-    dev_bufs[i]                  = *host[i];
-    dev_bufs[i].memory           = static_cast<uint8_t*>(st->dev) + offs[i];
-    dev_bufs[i].external_malloc  = nullptr;
-    dev_bufs[i].external_free    = nullptr;
-    dev_pods[i].type_code_       = CINN_POD_BUFFERP;
-    dev_pods[i].value_.v_handle  = &dev_bufs[i];
+  if (!st->replicated_ready) {
+    e = cudaEventCreateWithFlags(&st->replicated_ready, cudaEventDisableTiming);
+    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaEventCreate: %s", cudaGetErrorString(e));
   }
+  uint8_t* base = static_cast<uint8_t*>(st->dev);
+  auto fail_copy = [&](const char* what, const std::string& name, cudaError_t err) {
+    return SetError(CINN_B200_ECUDA, "%s copy of %s: %s", what, name.c_str(), cudaGetErrorString(err));
+  };
+  const int chunks = slot.chunk_count > 0 ? slot.chunk_count : 1;
+  // Replicated (small) inputs go first on stream 0; the other streams wait for them.
   for (int i = 0; i < n_in; ++i) {
-    e = cudaMemcpyAsync(dev_bufs[i].memory, host[i]->memory, sizes[i], cudaMemcpyHostToDevice, st->s);
-    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "host->device copy of %s: %s", plan.inputs[i].name.c_str(), cudaGetErrorString(e));
+    if (chunks > 1 && slot.chunk_sharded[i]) continue;
+    e = cudaMemcpyAsync(base + offs[i], host[i]->memory, sizes[i], cudaMemcpyHostToDevice, st->s[0]);
+    if (e != cudaSuccess) return fail_copy("host->device", plan.inputs[i].name, e);
   }
-  rc = RunSlot(slot_index, dev_pods.data(), num_args, st->s);
-  if (rc != CINN_B200_OK) return rc;
-  for (int i = n_in; i < num_args; ++i) {
-    e = cudaMemcpyAsync(host[i]->memory, dev_bufs[i].memory, sizes[i], cudaMemcpyDeviceToHost, st->s);
-    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "device->host copy of %s: %s", plan.outputs[i - n_in].name.c_str(), cudaGetErrorString(e));
+  if (chunks == 1) {
+    std::vector<cinn_buffer_t> dev_bufs(num_args);
+    std::vector<cinn_buffer_t*> ptrs(num_args);
+    for (int i = 0; i < num_args; ++i) {
+      dev_bufs[i]        = *host[i];
+      dev_bufs[i].memory = base + offs[i];
+      ptrs[i]            = &dev_bufs[i];
+    }
+    rc = RunPlan(plan, slot, ptrs, st->s[0]);
+    if (rc != CINN_B200_OK) return rc;
+    for (int i = n_in; i < num_args; ++i) {
+      e = cudaMemcpyAsync(host[i]->memory, base + offs[i], sizes[i], cudaMemcpyDeviceToHost, st->s[0]);
+      if (e != cudaSuccess) return fail_copy("device->host", plan.outputs[i - n_in].name, e);
+    }
+    e = cudaStreamSynchronize(st->s[0]);
+    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "group %s: %s", plan.name.c_str(), cudaGetErrorString(e));
+    return CINN_B200_OK;
   }
-  e = cudaStreamSynchronize(st->s);
-  if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "group %s: %s", plan.name.c_str(), cudaGetErrorString(e));
+  // Pipelined: chunk c uses stream c % 3: copy its slices in, run the chunk-sized group, copy its slice out.  With
+  // three streams the host->device copy of one chunk, the kernel of another and the device->host copy of a third
+  // overlap (the two copy directions use different DMA engines).
+  e = cudaEventRecord(st->replicated_ready, st->s[0]);
+  if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaEventRecord: %s", cudaGetErrorString(e));
+  for (int k = 1; k < kHostStreams; ++k) cudaStreamWaitEvent(st->s[k], st->replicated_ready, 0);
+  const CompiledGroup& sub = *slot.chunk_plan;
+  std::vector<cinn_buffer_t> dev_bufs(num_args);
+  std::vector<cinn_buffer_t*> ptrs(num_args);
+  for (int c = 0; c < chunks; ++c) {
+    cudaStream_t stream = st->s[c % kHostStreams];
+    for (int i = 0; i < num_args; ++i) {
+      const bool sh       = slot.chunk_sharded[i];
+      const size_t part   = sh ? sizes[i] / chunks : sizes[i];
+      const size_t off    = sh ? part * c : 0;
+      dev_bufs[i]         = *host[i];
+      dev_bufs[i].memory  = base + offs[i] + off;
+      if (sh) dev_bufs[i].dims[0] = host[i]->dims[0] / chunks;
+      ptrs[i]             = &dev_bufs[i];
+      if (i < n_in && sh) {
+        e = cudaMemcpyAsync(dev_bufs[i].memory, host[i]->memory + off, part, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) return fail_copy("host->device", plan.inputs[i].name, e);
+      }
+    }
+    rc = RunPlan(sub, slot, ptrs, stream);
+    if (rc != CINN_B200_OK) return rc;
+    const int o        = n_in;
+    const size_t part  = sizes[o] / chunks;
+    e = cudaMemcpyAsync(host[o]->memory + part * c, base + offs[o] + part * c, part, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return fail_copy("device->host", plan.outputs[0].name, e);
+  }
+  for (int k = 0; k < kHostStreams; ++k) {
+    e = cudaStreamSynchronize(st->s[k]);
+    if (e != cudaSuccess) return SetError(CINN_B200_ECUDA, "group %s: %s", plan.name.c_str(), cudaGetErrorString(e));
+  }
   return CINN_B200_OK;
+}
+
+int cinn_b200_group_host_chunks(const char* fn_name) {
+  int slot_index = SlotOf(fn_name);
+  if (slot_index < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  std::lock_guard<std::mutex> lk(g_mu);
+  GroupSlot& slot = g_slots[slot_index];
+  if (!slot.chunk_tried) PrepareChunking(slot);
+  return slot.chunk_count > 0 ? slot.chunk_count : 1;
 }
 
 int cinn_b200_device_status(unsigned int* async_wait_timeouts) {

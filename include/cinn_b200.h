@@ -66,8 +66,13 @@ long long cinn_b200_launch_count(void);
 /* ---- fused groups ------------------------------------------------------------------------------- */
 
 /*
- * Compile one fused group, given in the text form documented in INTEGRATION.md ("group/input/op/output"
- * lines), to a launch plan over the prebuilt kernels and bind it to an entry point of the reference's
+ * Compile one fused group to a launch plan over the prebuilt kernels and bind it to an entry point of the
+ * reference's type.  The group is given as text, one item per line:
+ *     group <function name>
+ *     input <id> <dtype> <d0,d1,...>                       (one per input, in argument order)
+ *     op <HLIR op name> <out id> = <in id> ... ; key=value ...   (topological order, the reference's attributes)
+ *     output <id> <dtype> <d0,d1,...>
+ * The result is bound to an entry point of the reference's
  * type lower_func_ptr_g (cinn/runtime/cinn_runtime.h:497-499).  Replaces, for the groups it covers,
  * ParallelCompiler::Task::Lowering + CodegenAndJit (cinn/hlir/framework/parallel_compiler.cc:123-199).
  * The entry point takes cinn_pod_value_t[num_args] = the group's inputs then outputs, each a
@@ -102,9 +107,15 @@ int cinn_b200_canonical_expr(const char* group_desc, char* out, size_t out_len);
  * copy speed); inputs are copied to `device`, the group runs, outputs are copied back, and the call returns
  * after the outputs are complete.  This is the path Tensor::from_numpy -> Program::Execute -> Tensor::numpy
  * takes in the reference (cinn/frontend/computation.cc:186-240, cinn/pybind/framework.cc:116-172).
- * Device staging memory is kept per group and device and reused by later calls.
+ * Device staging memory is kept per group and device and reused by later calls.  Groups that are independent
+ * along their outer axis are pipelined over chunks of it (see cinn_b200_group_host_chunks).
  */
 int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, int device);
+
+/* In how many chunks of the outer axis cinn_b200_group_run_host pipelines this group (host->device copy of one
+ * chunk, kernel of another, device->host copy of a third overlap on three streams); 1 when the group's outer
+ * axis cannot be sliced (a reduction over it, an operand aligned to it, scratch memory) or it is too small. */
+int cinn_b200_group_host_chunks(const char* fn_name);
 
 /* ---- NetBuilder / Computation --------------------------------------------------------------------- */
 
