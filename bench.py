@@ -25,6 +25,10 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 HEADLINE_SHAPE = (64, 1024, 1024)
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel at full size, from the ncu
+# capture summarised in profiles/ncu_bias_scale_tanh_cast.md (268.5 MB read + 103.0 MB written; the write-back L2
+# still holds part of the 134 MB output when the kernel ends).
+HEADLINE_DRAM_TRAFFIC_BYTES = 371520000
 METRIC = "fused-group HBM throughput"
 UNIT = "GB/s"
 
@@ -372,7 +376,9 @@ def main():
                    "sharding": "axis 0, no collective; each rank runs the full-size group (weak scaling)"},
         "elements_per_s": g.elements * world / (ms_per_step * 1e-3),
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
-                     "frac": round(per_gpu / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "frac": round(per_gpu / peak, 4), "traffic": HEADLINE_DRAM_TRAFFIC_BYTES,
+                     "traffic_unit": "bytes per launch (dram read + write, one ncu --set full capture)",
+                     "algorithmic_bytes": bytes_per_launch, "peak_source": peak_src,
                      "kernel": g.kernel_names()[0]},
         "e2e": {"value": round(e2e_value, 3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": int(x_host.numel() * 4 + bias_host.numel() * 4),
