@@ -21,6 +21,7 @@ SOURCES = [
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
     "ew_chain.cu",
+    "ew_stream.cu",
     "reduce_static_scratch.cu",
     "group_desc.cc",
     "group_match.cc",

@@ -97,6 +97,9 @@ struct DeviceInfo {
   // Tuning knobs of the row-normalisation planner (0 = automatic).
   int rownorm_stages        = 0;
   int rownorm_ctas_per_sm   = 0;
+  int enable_ew_stream      = 1;   // elementwise groups streamed through shared-memory rings (0 = register kernels)
+  int ew_stream_stages      = 0;
+  int ew_stream_ctas_per_sm = 0;
   int rownorm_rows_per_iter = 0;  // rows a CTA of the register-resident kernels takes per iteration
   int enable_tma_rownorm    = -1;  // rows streamed through shared memory by bulk copies: 1 on, 0 off, -1 automatic
 };

@@ -166,7 +166,8 @@ __global__ void __launch_bounds__(256) k_col_reduce(const float* __restrict__ x,
   const long long cstep  = (long long)gridDim.x * blockDim.x;  // the grid is sized for the vector path
   if (vec_ok) {
     const long long inner_v = inner >> 2;
-    for (long long col = col0; col < inner_v; col += cstep)
+    const long long col = col0;  // the grid covers every column group of the vector path
+    if (col >= inner_v) return;
     for (long long o = blockIdx.y; o < outer; o += gridDim.y) {
       const uint4* p = reinterpret_cast<const uint4*>(x + o * r * inner) + col;
       float a0 = Op::identity(), a1 = a0, a2 = a0, a3 = a0;

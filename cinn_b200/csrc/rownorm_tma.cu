@@ -13,57 +13,13 @@
 // through cinn_b200_device_status), drains the other armed buffers with bounded waits and leaves the kernel.
 #include "device_math.cuh"
 #include "kernel_registry.h"
+#include "tma_utils.cuh"
 
 namespace cinn_b200 {
 
-__device__ unsigned int g_async_wait_timeouts = 0;
-
-unsigned int ReadAndClearAsyncWaitTimeouts(int* cuda_status) {
-  unsigned int v = 0, zero = 0;
-  cudaError_t e = cudaMemcpyFromSymbol(&v, g_async_wait_timeouts, sizeof(v));
-  if (e == cudaSuccess && v != 0) e = cudaMemcpyToSymbol(g_async_wait_timeouts, &zero, sizeof(zero));
-  if (cuda_status) *cuda_status = (int)e;
-  return v;
-}
+CINN_B200_DEFINE_ASYNC_TIMEOUT_COUNTER(g_rownorm_wait_timeouts);
 
 namespace {
-
-constexpr int kMaxStages      = 8;
-constexpr unsigned kWaitLimit = 1u << 22;  // try_wait calls before a wait is abandoned
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_addr(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (unsigned i = 0; i < kWaitLimit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-// Global -> this CTA's shared memory, `bytes` a multiple of 16, both addresses 16-byte aligned; completion is
-// signalled on `bar` as transferred bytes.  (A CTA launched without a cluster is its own cluster of one, so the
-// shared::cluster destination window is this CTA's shared memory.)
-__device__ __forceinline__ void bulk_load_row(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_addr(smem_dst)),
-               "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar))
-               : "memory");
-}
 
 template <typename T, int G, int VPT, bool LAYERNORM>
 __global__ void __launch_bounds__(G)
@@ -206,7 +162,7 @@ __global__ void __launch_bounds__(G)
     }
   }
   if (gave_up) {
-    if (t == 0) atomicAdd(&g_async_wait_timeouts, 1u);
+    if (t == 0) atomicAdd(&g_rownorm_wait_timeouts, 1u);
     // Copies already issued for later rows still target this CTA's shared memory: wait for them (bounded)
     // before the CTA exits.  Rows k+1 .. k+stages-1 (if they exist) are armed.
     for (long long kk = k + 1; kk < my_rows && kk < k + stages; ++kk)

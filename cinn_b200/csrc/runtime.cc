@@ -72,13 +72,35 @@ static std::atomic<long long> g_launches{0};
 static std::mutex g_mu;
 static int g_opt_sm_count = 0;  // 0: query the device, or 148 without one
 static int g_opt_rownorm_rows = 0;
+static int g_opt_ew_stream = 1, g_opt_ew_stream_stages = 0, g_opt_ew_stream_ctas = 0;
 static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1;
 
-unsigned int ReadAndClearAsyncWaitTimeouts(int* cuda_status);  // rownorm_tma.cu
+typedef unsigned int (*AsyncTimeoutReader)(int* cuda_status);
+static std::vector<AsyncTimeoutReader>& TimeoutReaders() {
+  static std::vector<AsyncTimeoutReader> v;
+  return v;
+}
+int RegisterAsyncTimeoutReader(AsyncTimeoutReader reader) {
+  TimeoutReaders().push_back(reader);
+  return (int)TimeoutReaders().size();
+}
+static unsigned int ReadAndClearAsyncWaitTimeouts(int* cuda_status) {
+  unsigned int total = 0;
+  if (cuda_status) *cuda_status = 0;
+  for (AsyncTimeoutReader r : TimeoutReaders()) {
+    int st = 0;
+    total += r(&st);
+    if (st != 0 && cuda_status) *cuda_status = st;
+  }
+  return total;
+}
 
 static DeviceInfo CurrentDeviceInfo() {
   DeviceInfo d;
   d.rownorm_rows_per_iter = g_opt_rownorm_rows;
+  d.enable_ew_stream      = g_opt_ew_stream;
+  d.ew_stream_stages      = g_opt_ew_stream_stages;
+  d.ew_stream_ctas_per_sm = g_opt_ew_stream_ctas;
   d.rownorm_stages      = g_opt_rownorm_stages;
   d.rownorm_ctas_per_sm = g_opt_rownorm_ctas;
   d.enable_tma_rownorm = g_opt_enable_tma_rownorm;
@@ -710,6 +732,18 @@ int cinn_b200_set_option(const char* key, long long value) {
   if (!key) return SetError(CINN_B200_EINVAL, "null option key");
   if (!strcmp(key, "sm_count")) {
     g_opt_sm_count = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "enable_ew_stream")) {
+    g_opt_ew_stream = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "ew_stream_stages")) {
+    g_opt_ew_stream_stages = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "ew_stream_ctas_per_sm")) {
+    g_opt_ew_stream_ctas = (int)value;
     return CINN_B200_OK;
   }
   if (!strcmp(key, "rownorm_rows_per_iter")) {

@@ -196,7 +196,9 @@ int cinn_b200_col_reduce_f32_static_scratch(int kind, const float* x, float* y, 
 int cinn_b200_device_status(unsigned int* async_wait_timeouts);
 
 /* Tuning knobs (integers) read by the matcher when a group is compiled; unknown keys give CINN_B200_ENOTFOUND.
- * "sm_count": SM count assumed when no GPU is visible (default 148); "rownorm_rows_per_iter": rows per CTA
+ * "sm_count": SM count assumed when no GPU is visible (default 148); "enable_ew_stream" (default 1),
+ * "ew_stream_stages", "ew_stream_ctas_per_sm": whether large elementwise groups with 16-bit outputs stream their
+ * input through shared-memory rings filled by bulk copies, the ring depth and the resident CTAs per SM; "rownorm_rows_per_iter": rows per CTA
  * iteration of the register-resident softmax / layer_norm kernels (0 = automatic, else 1, 2 or 4); "rownorm_stages", "rownorm_ctas_per_sm":
  * ring depth and resident CTAs per SM of the streamed softmax / layer_norm kernels (0 = automatic);
  * "enable_tma_rownorm": 1 selects the kernels that stream rows through a shared-memory ring with bulk

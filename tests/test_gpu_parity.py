@@ -30,7 +30,8 @@ def test_add_relu_bit_exact(oracle, shape, misalign):
 
 
 # ---- config 2: cast_fp16(tanh((X+bias)*0.5)) -----------------------------------------------------
-@pytest.mark.parametrize("shape", [(2, 8, 1024), (3, 5, 7), (1, 1, 8), (6, 1000), (64, 1024, 1024)])
+@pytest.mark.parametrize("shape", [(2, 8, 1024), (3, 5, 7), (1, 1, 8), (6, 1000), (512, 100, 120), (5000, 1001),
+                                   (64, 1024, 1024)])
 @pytest.mark.parametrize("misalign", [0, 1])
 def test_bias_scale_tanh_cast(oracle, shape, misalign):
     if misalign and int(np.prod(shape)) > 1 << 24:
