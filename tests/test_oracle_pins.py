@@ -173,3 +173,22 @@ def test_fused_loops_equal_op_at_a_time_evaluation(oracle, make):
         fused = oracle.reduce("max", w.inputs[0], 1, 9, 20).reshape(w.out_shape)
     assert fused.dtype == unfused.dtype and fused.shape == tuple(unfused.shape)
     assert np.array_equal(fused.view(np.uint8), unfused.view(np.uint8))
+
+
+def test_oracle_reproduces_llvm_compiled_loops_bit_for_bit(oracle):
+    """tests/golden/llvm_x86_vectors.npz holds the outputs of LLVM-20 -O3 (loop + SLP vectorised, no fast-math)
+    builds of the IR constructs CINN's x86 path emits for these groups (llvm.fmuladd / llvm.exp / llvm.sqrt
+    intrinsics, fcmp + select, fptrunc to half, serial fadd reductions); tests/golden/make_llvm_x86_vectors.py
+    generated it.  The C oracle must give exactly those bits."""
+    import os
+    d = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llvm_x86_vectors.npz"))
+
+    def same(got, want):
+        return got.dtype == want.dtype and got.shape == want.shape and np.array_equal(got.view(np.uint8),
+                                                                                      want.view(np.uint8))
+    assert same(oracle.add_relu(d["add_relu_a"], d["add_relu_b"]), d["add_relu_y"])
+    assert same(oracle.bias_scale_tanh_f16(d["tanh_x"], d["tanh_bias"], 0.5, 0.0), d["tanh_y"])
+    assert same(oracle.reduce("sum", d["sum_x"], 29, 1031, 1), d["sum_y"])
+    assert same(oracle.softmax(d["softmax_x"]), d["softmax_y"])
+    assert same(oracle.layernorm(d["ln_x"], d["ln_gamma"], d["ln_beta"], 1e-5), d["ln_y"])
+    assert same(oracle.bn_relu_nchw(d["bn_x"], d["bn_scale"], d["bn_bias"], d["bn_mean"], d["bn_var"], 1e-5), d["bn_y"])
