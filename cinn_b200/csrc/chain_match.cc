@@ -450,7 +450,7 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
     return nullptr;
   }
   st.block[0] = 256;
-  st.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(CeilDiv(cb.n, 4), 256), (int64_t)dev.sm_count * 32));
+  st.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(CeilDiv(cb.n, 8), 256), (int64_t)dev.sm_count * 16));
   auto in_arg = [](int i) { ArgSpec a; a.kind = ArgSpec::kInput; a.index = i; return a; };
   auto int_arg = [](int64_t v) { ArgSpec a; a.kind = ArgSpec::kInt; a.ivalue = v; return a; };
   st.args.push_back(in_arg(in0));

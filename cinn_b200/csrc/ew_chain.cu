@@ -17,67 +17,88 @@
 namespace cinn_b200 {
 namespace {
 
+// Rarely used, code-heavy functions stay out of line so that the interpreter's unrolled body stays small enough
+// for the instruction cache (each inlined copy of erff / sinf / powf is hundreds of instructions).
+__device__ __noinline__ float heavy_unary(int op, float x) {
+  switch (op) {
+    case EW_ERF: return erff(x);
+    case EW_SIN: return sinf(x);
+    case EW_COS: return cosf(x);
+    case EW_LOG2: return log2f(x);
+    case EW_LOG10: return log10f(x);
+    default: return x;
+  }
+}
+__device__ __noinline__ float heavy_pow(float l, float r) { return powf(l, r); }
+
 template <int VEC>
 __device__ __forceinline__ void apply_unary(int op, float imm, float (&a)[VEC]) {
+#define EW_UNARY_CASE(code, expr) \
+  case code:                      \
+    _Pragma("unroll") for (int i = 0; i < VEC; ++i) { const float x = a[i]; a[i] = (expr); } \
+    break;
+  switch (op) {
+    EW_UNARY_CASE(EW_EXP, expf(x))
+    EW_UNARY_CASE(EW_TANH, x86_tanh(x))
+    EW_UNARY_CASE(EW_SIGMOID, x86_sigmoid(x))
+    EW_UNARY_CASE(EW_RSQRT, x86_rsqrt(x))
+    EW_UNARY_CASE(EW_SQRT, sqrtf(x))
+    EW_UNARY_CASE(EW_RELU, x86_max(x, 0.0f))
+    EW_UNARY_CASE(EW_NEG, -x)
+    EW_UNARY_CASE(EW_ABS, fabsf(x))
+    EW_UNARY_CASE(EW_LOG, logf(x))
+    EW_UNARY_CASE(EW_FLOOR, floorf(x))
+    EW_UNARY_CASE(EW_CEIL, ceilf(x))
+    EW_UNARY_CASE(EW_RECIP, 1.0f / x)
+    EW_UNARY_CASE(EW_ROUND, nearbyintf(x))
+    EW_UNARY_CASE(EW_TRUNC, truncf(x))
+    EW_UNARY_CASE(EW_SIGN, x < 0.0f ? -1.0f : (x > 0.0f ? 1.0f : (x == 0.0f ? 0.0f : x)))
+    EW_UNARY_CASE(EW_RELU6, x86_min(x86_max(x, 0.0f), imm))
+    EW_UNARY_CASE(EW_ROUND_F16, __half2float(__float2half_rn(x)))
+    EW_UNARY_CASE(EW_ROUND_BF16, __bfloat162float(__float2bfloat16_rn(x)))
+    case EW_ERF:
+    case EW_SIN:
+    case EW_COS:
+    case EW_LOG2:
+    case EW_LOG10:
 #pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    float x = a[i];
-    switch (op) {
-      case EW_EXP: x = expf(x); break;
-      case EW_TANH: x = x86_tanh(x); break;
-      case EW_SIGMOID: x = x86_sigmoid(x); break;
-      case EW_RSQRT: x = x86_rsqrt(x); break;
-      case EW_SQRT: x = sqrtf(x); break;
-      case EW_RELU: x = x86_max(x, 0.0f); break;
-      case EW_NEG: x = -x; break;
-      case EW_ABS: x = fabsf(x); break;
-      case EW_LOG: x = logf(x); break;
-      case EW_FLOOR: x = floorf(x); break;
-      case EW_CEIL: x = ceilf(x); break;
-      case EW_ERF: x = erff(x); break;
-      case EW_SIN: x = sinf(x); break;
-      case EW_COS: x = cosf(x); break;
-      case EW_RECIP: x = 1.0f / x; break;
-      case EW_ROUND: x = nearbyintf(x); break;
-      case EW_TRUNC: x = truncf(x); break;
-      case EW_SIGN: x = x < 0.0f ? -1.0f : (x > 0.0f ? 1.0f : (x == 0.0f ? 0.0f : x)); break;
-      case EW_RELU6: x = x86_min(x86_max(x, 0.0f), imm); break;
-      case EW_LOG2: x = log2f(x); break;
-      case EW_LOG10: x = log10f(x); break;
-      case EW_ROUND_F16: x = __half2float(__float2half_rn(x)); break;
-      case EW_ROUND_BF16: x = __bfloat162float(__float2bfloat16_rn(x)); break;
-      default: break;
-    }
-    a[i] = x;
+      for (int i = 0; i < VEC; ++i) a[i] = heavy_unary(op, a[i]);
+      break;
+    default:
+      break;
   }
+#undef EW_UNARY_CASE
 }
 
 // acc (op) o, or o (op) acc when swapped: the operand order of the reference expression is kept because
 // max/min/sub/div/pow and the comparisons are not symmetric (max(a,b) = a > b ? a : b).
 template <int VEC>
 __device__ __forceinline__ void apply_binary(int op, bool swap, const float (&o)[VEC], float (&a)[VEC]) {
-#pragma unroll
-  for (int i = 0; i < VEC; ++i) {
-    const float l = swap ? o[i] : a[i], r = swap ? a[i] : o[i];
-    float x;
-    switch (op) {
-      case EW_ADD: x = l + r; break;
-      case EW_SUB: x = l - r; break;
-      case EW_MUL: x = l * r; break;
-      case EW_DIV: x = l / r; break;
-      case EW_MAX: x = x86_max(l, r); break;
-      case EW_MIN: x = x86_min(l, r); break;
-      case EW_POW: x = powf(l, r); break;
-      case EW_EQ: x = l == r ? 1.0f : 0.0f; break;
-      case EW_NE: x = l != r ? 1.0f : 0.0f; break;
-      case EW_GT: x = l > r ? 1.0f : 0.0f; break;
-      case EW_LT: x = l < r ? 1.0f : 0.0f; break;
-      case EW_GE: x = l >= r ? 1.0f : 0.0f; break;
-      case EW_LE: x = l <= r ? 1.0f : 0.0f; break;
-      default: x = a[i]; break;
-    }
-    a[i] = x;
+#define EW_BINARY_CASE(code, expr)                                 \
+  case code:                                                       \
+    _Pragma("unroll") for (int i = 0; i < VEC; ++i) {              \
+      const float l = swap ? o[i] : a[i], r = swap ? a[i] : o[i];  \
+      a[i] = (expr);                                               \
+    }                                                              \
+    break;
+  switch (op) {
+    EW_BINARY_CASE(EW_ADD, l + r)
+    EW_BINARY_CASE(EW_SUB, l - r)
+    EW_BINARY_CASE(EW_MUL, l * r)
+    EW_BINARY_CASE(EW_DIV, l / r)
+    EW_BINARY_CASE(EW_MAX, x86_max(l, r))
+    EW_BINARY_CASE(EW_MIN, x86_min(l, r))
+    EW_BINARY_CASE(EW_POW, heavy_pow(l, r))
+    EW_BINARY_CASE(EW_EQ, l == r ? 1.0f : 0.0f)
+    EW_BINARY_CASE(EW_NE, l != r ? 1.0f : 0.0f)
+    EW_BINARY_CASE(EW_GT, l > r ? 1.0f : 0.0f)
+    EW_BINARY_CASE(EW_LT, l < r ? 1.0f : 0.0f)
+    EW_BINARY_CASE(EW_GE, l >= r ? 1.0f : 0.0f)
+    EW_BINARY_CASE(EW_LE, l <= r ? 1.0f : 0.0f)
+    default:
+      break;
   }
+#undef EW_BINARY_CASE
 }
 
 __device__ __forceinline__ float load_scalar(const void* p, int dtype, long long idx) {
@@ -139,19 +160,25 @@ struct SideSpec {
   long long mid, inner;
 };
 
+// (i / inner) % mid, in 32-bit arithmetic whenever the operands allow it (64-bit division is several times dearer).
+__device__ __forceinline__ long long side_index(long long i, long long inner, long long mid) {
+  if (((i | inner | mid) >> 31) == 0) return (long long)(((unsigned)i / (unsigned)inner) % (unsigned)mid);
+  return (i / inner) % mid;
+}
+
 template <int VEC>
 __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, float (&f)[VEC]) {
   if (VEC == 4 && s.mode == EW_SIDE_FULL) {
     load_vec4(s.ptr, s.dtype, i0, true, *reinterpret_cast<float(*)[4]>(&f[0]));
   } else if (VEC == 4 && s.mode == EW_SIDE_PERIODIC_VEC) {
-    load_vec4(s.ptr, s.dtype, i0 % s.mid, false, *reinterpret_cast<float(*)[4]>(&f[0]));
+    load_vec4(s.ptr, s.dtype, side_index(i0, 1, s.mid), false, *reinterpret_cast<float(*)[4]>(&f[0]));
   } else if (s.mode == EW_SIDE_ONE_PER_VEC || s.mode == EW_SIDE_SCALAR) {
-    const float v = load_scalar(s.ptr, s.dtype, s.mode == EW_SIDE_SCALAR ? 0 : (i0 / s.inner) % s.mid);
+    const float v = load_scalar(s.ptr, s.dtype, s.mode == EW_SIDE_SCALAR ? 0 : side_index(i0, s.inner, s.mid));
 #pragma unroll
     for (int i = 0; i < VEC; ++i) f[i] = v;
   } else {
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) f[i] = load_scalar(s.ptr, s.dtype, ((i0 + i) / s.inner) % s.mid);
+    for (int i = 0; i < VEC; ++i) f[i] = load_scalar(s.ptr, s.dtype, side_index(i0 + i, s.inner, s.mid));
   }
 }
 
@@ -165,14 +192,34 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
     const int bsel     = (int)((st >> 16) & 0xff);
     const bool swap    = ((st >> 24) & 1) != 0;
     const float imm    = __uint_as_float((uint32_t)(st >> 32));
+    if (op == EW_NOP) continue;
     if (op >= EW_FIRST_UNARY) {
       apply_unary<VEC>(op, imm, acc);
       continue;
     }
     float o[VEC];
+    switch (asel) {  // one uniform branch per step instead of a select chain per element
+      case 1:
 #pragma unroll
-    for (int i = 0; i < VEC; ++i)
-      o[i] = asel == 1 ? s1[i] : (asel == 2 ? s2[i] : (asel == 3 ? s3[i] : (asel == 4 ? acc[i] : imm)));
+        for (int i = 0; i < VEC; ++i) o[i] = s1[i];
+        break;
+      case 2:
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = s2[i];
+        break;
+      case 3:
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = s3[i];
+        break;
+      case 4:
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = acc[i];
+        break;
+      default:
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = imm;
+        break;
+    }
     if (op == EW_FMA) {
       // acc = fma(acc, A, B); B is a side operand or the immediate of the next program slot.
       const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
@@ -228,7 +275,27 @@ __global__ void __launch_bounds__(256)
   long long done         = 0;
   if (vec_ok) {
     const long long nvec = n >> 2;
-    for (long long v = tid; v < nvec; v += stride) {
+    // Two vectors (8 elements) per thread iteration: all of their loads are issued before the program runs,
+    // and one pass of the interpreter serves the eight elements.
+    long long v = tid;
+    for (; v + stride < nvec; v += 2 * stride) {
+      float acc[8], s1[8], s2[8], s3[8];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        load_vec4(in0, DTypeCode<InT>::v, (v + j * stride) << 2, true, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const long long i0 = (v + j * stride) << 2;
+        if (sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, *reinterpret_cast<float(*)[4]>(&s1[4 * j]));
+        if (sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, *reinterpret_cast<float(*)[4]>(&s2[4 * j]));
+        if (sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, *reinterpret_cast<float(*)[4]>(&s3[4 * j]));
+      }
+      run_chain<8>(steps, nsteps, s1, s2, s3, acc);
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        store_vec4<OutT>(out, (v + j * stride) << 2, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
+    }
+    for (; v < nvec; v += stride) {
       const long long i0 = v << 2;
       float acc[4], s1[4], s2[4], s3[4];
       load_vec4(in0, DTypeCode<InT>::v, i0, true, acc);
