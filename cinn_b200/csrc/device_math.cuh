@@ -151,22 +151,42 @@ struct Io<__nv_bfloat16> {
 };
 
 // ---- warp / CTA reductions ---------------------------------------------------------------------
+// A reduction op has two faces: accum(acc, x) folds one INPUT element into an accumulator, apply(a, b) combines two
+// partial results.  For the plain ops they coincide; the composite ops below apply an elementwise producer to the
+// element first (the producer of a reduce is materialised in the reference, cinn/hlir/framework/
+// op_lowering_util.cc:757-761, so its result is rounded to fp32 before it is accumulated: x*x then +, no fma).
 struct SumOp {
   __device__ static __forceinline__ float identity() { return 0.0f; }
   __device__ static __forceinline__ float apply(float a, float b) { return a + b; }
+  __device__ static __forceinline__ float accum(float a, float x) { return a + x; }
 };
 struct ProdOp {
   __device__ static __forceinline__ float identity() { return 1.0f; }
   __device__ static __forceinline__ float apply(float a, float b) { return a * b; }
+  __device__ static __forceinline__ float accum(float a, float x) { return a * x; }
 };
 // cinn/lang/builtin.cc:123-143: the initial value of max is lowest() (= -FLT_MAX), not -inf.
 struct MaxOp {
   __device__ static __forceinline__ float identity() { return -3.402823466e+38f; }
   __device__ static __forceinline__ float apply(float a, float b) { return x86_max(a, b); }
+  __device__ static __forceinline__ float accum(float a, float x) { return x86_max(a, x); }
 };
 struct MinOp {
   __device__ static __forceinline__ float identity() { return 3.402823466e+38f; }
   __device__ static __forceinline__ float apply(float a, float b) { return x86_min(a, b); }
+  __device__ static __forceinline__ float accum(float a, float x) { return x86_min(a, x); }
+};
+struct SumSquareOp : SumOp {  // reduce_sum(x * x)
+  __device__ static __forceinline__ float accum(float a, float x) { return a + x * x; }
+};
+struct SumAbsOp : SumOp {  // reduce_sum(abs(x))
+  __device__ static __forceinline__ float accum(float a, float x) { return a + fabsf(x); }
+};
+struct SumExpOp : SumOp {  // reduce_sum(exp(x))
+  __device__ static __forceinline__ float accum(float a, float x) { return a + expf(x); }
+};
+struct MaxAbsOp : MaxOp {  // reduce_max(abs(x))
+  __device__ static __forceinline__ float accum(float a, float x) { return x86_max(a, fabsf(x)); }
 };
 
 template <class Op>

@@ -460,6 +460,33 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
           if (st.Compiles(trial, nullptr, nullptr)) {
             members = trial;
             grew    = true;
+            continue;
+          }
+          // The producer alone does not give a known group; try it together with the producers that feed only
+          // it (e.g. multiply(x, identity(x)) under a reduce_sum needs the identity as well).
+          std::set<int> closure = trial;
+          bool added            = true;
+          while (added && closure.size() < trial.size() + 8) {
+            added = false;
+            for (int m2 : std::set<int>(closure)) {
+              if (members.count(m2)) continue;
+              for (int v2 : b.instrs()[m2].inputs) {
+                int q = st.producer_of_var[v2];
+                if (q < 0 || closure.count(q) || group_of[q] >= 0 || st.IsConst(q)) continue;
+                if (PatternOf(b.instrs()[q].op_type) == OpPattern::kNonFusible) continue;
+                if (st.fetch.count(b.instrs()[q].output)) continue;
+                bool inside = true;
+                for (int c : st.consumers_of_var[b.instrs()[q].output])
+                  if (!closure.count(c)) inside = false;
+                if (!inside) continue;
+                closure.insert(q);
+                added = true;
+              }
+            }
+          }
+          if (closure.size() > trial.size() && st.Compiles(closure, nullptr, nullptr)) {
+            members = closure;
+            grew    = true;
           }
         }
       }

@@ -393,7 +393,7 @@ struct Matcher {
       s1.args = {src, Scratch(scratch_off), I(rows), I(r), I(splits), I(seg), Aligned(vec, src_in_for_align, {})};
       p->steps.push_back(s1);
       // The partials of a sum are summed; of max/min/prod combined with the same op.
-      return PlanReduceFinishRows(p, opname, rows, splits, Scratch(scratch_off), dst);
+      return PlanReduceFinishRows(p, BaseReduceOp(opname), rows, splits, Scratch(scratch_off), dst);
     }
     // inner > 1: column reduction.
     const bool vec       = inner % 4 == 0;
@@ -429,7 +429,7 @@ struct Matcher {
               Aligned(vec, src_in_for_align, {})};
     p->steps.push_back(s);
     const int64_t oi = outer * inner;
-    return PlanReduce(p, opname, 1, splits, oi, Scratch(scratch_off), dst, {});
+    return PlanReduce(p, BaseReduceOp(opname), 1, splits, oi, Scratch(scratch_off), dst, {});
   }
 
   bool PlanReduceFinishRows(CompiledGroup* p, const char* opname, int64_t rows, int64_t splits, ArgSpec src,
@@ -437,9 +437,23 @@ struct Matcher {
     return PlanReduce(p, opname, rows, splits, 1, src, dst, {});
   }
 
+  // Second passes over partial results use the plain op of a reduction that has a producer folded in.
+  static const char* BaseReduceOp(const char* opname) {
+    const std::string s = opname;
+    if (s == "sumsq" || s == "sumabs" || s == "sumexp") return "sum";
+    if (s == "maxabs") return "max";
+    return opname;
+  }
+
+  // reduce_{sum,prod,max,min}(%0), and the forms with one elementwise producer folded into the reduction's first
+  // pass: sum of squares, of absolute values, of exponentials, and max of absolute values.  (The reference keeps a
+  // reduce's producer as a separate, materialised stage of the same kernel; here it costs no extra pass over HBM.)
   std::unique_ptr<CompiledGroup> MatchReduce(const std::string& expr) {
     static const std::map<std::string, const char*> kinds = {
-        {"reduce_sum(%0)", "sum"}, {"reduce_prod(%0)", "prod"}, {"reduce_max(%0)", "max"}, {"reduce_min(%0)", "min"}};
+        {"reduce_sum(%0)", "sum"}, {"reduce_prod(%0)", "prod"}, {"reduce_max(%0)", "max"}, {"reduce_min(%0)", "min"},
+        {"reduce_sum(elementwise_mul(%0,%0))", "sumsq"}, {"reduce_sum(elementwise_mul(%0,identity(%0)))", "sumsq"},
+        {"reduce_sum(elementwise_mul(identity(%0),%0))", "sumsq"}, {"reduce_sum(abs(%0))", "sumabs"},
+        {"reduce_sum(exp(%0))", "sumexp"}, {"reduce_max(abs(%0))", "maxabs"}};
     auto it = kinds.find(expr);
     if (it == kinds.end()) return nullptr;
     const auto &x = g.inputs[0], &o = g.outputs[0];

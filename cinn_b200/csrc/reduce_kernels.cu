@@ -21,10 +21,10 @@ namespace cinn_b200 {
 
 template <class Op>
 __device__ __forceinline__ float combine4(float acc, uint4 u) {
-  acc = Op::apply(acc, __uint_as_float(u.x));
-  acc = Op::apply(acc, __uint_as_float(u.y));
-  acc = Op::apply(acc, __uint_as_float(u.z));
-  acc = Op::apply(acc, __uint_as_float(u.w));
+  acc = Op::accum(acc, __uint_as_float(u.x));
+  acc = Op::accum(acc, __uint_as_float(u.y));
+  acc = Op::accum(acc, __uint_as_float(u.z));
+  acc = Op::accum(acc, __uint_as_float(u.w));
   return acc;
 }
 
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(256) k_row_reduce_warp(const float* __restrict
       }
     } else {
       const float* p = x + row * r;
-      for (long long c = lane; c < r; c += 32) acc = Op::apply(acc, p[c]);
+      for (long long c = lane; c < r; c += 32) acc = Op::accum(acc, p[c]);
     }
     acc = warp_allreduce<Op>(acc);
     if (lane == 0) y[row] = acc;
@@ -82,9 +82,9 @@ __device__ __forceinline__ float segment_partial(const float* __restrict__ p, lo
       for (int j = 0; j < 4; ++j)
         if (v + j * B < nvec) acc = combine4<Op>(acc, u[j]);
     }
-    for (long long c = begin + (nvec << 2) + threadIdx.x; c < end; c += blockDim.x) acc = Op::apply(acc, p[c]);
+    for (long long c = begin + (nvec << 2) + threadIdx.x; c < end; c += blockDim.x) acc = Op::accum(acc, p[c]);
   } else {
-    for (long long c = begin + threadIdx.x; c < end; c += blockDim.x) acc = Op::apply(acc, p[c]);
+    for (long long c = begin + threadIdx.x; c < end; c += blockDim.x) acc = Op::accum(acc, p[c]);
   }
   return acc;
 }
@@ -178,18 +178,18 @@ __global__ void __launch_bounds__(256) k_col_reduce(const float* __restrict__ x,
         for (int j = 0; j < 8; ++j) u[j] = __ldcs(p + (k + j) * inner_v);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          a0 = Op::apply(a0, __uint_as_float(u[j].x));
-          a1 = Op::apply(a1, __uint_as_float(u[j].y));
-          a2 = Op::apply(a2, __uint_as_float(u[j].z));
-          a3 = Op::apply(a3, __uint_as_float(u[j].w));
+          a0 = Op::accum(a0, __uint_as_float(u[j].x));
+          a1 = Op::accum(a1, __uint_as_float(u[j].y));
+          a2 = Op::accum(a2, __uint_as_float(u[j].z));
+          a3 = Op::accum(a3, __uint_as_float(u[j].w));
         }
       }
       for (; k < k1; ++k) {
         uint4 u = __ldcs(p + k * inner_v);
-        a0      = Op::apply(a0, __uint_as_float(u.x));
-        a1      = Op::apply(a1, __uint_as_float(u.y));
-        a2      = Op::apply(a2, __uint_as_float(u.z));
-        a3      = Op::apply(a3, __uint_as_float(u.w));
+        a0      = Op::accum(a0, __uint_as_float(u.x));
+        a1      = Op::accum(a1, __uint_as_float(u.y));
+        a2      = Op::accum(a2, __uint_as_float(u.z));
+        a3      = Op::accum(a3, __uint_as_float(u.w));
       }
       uint4 out = make_uint4(__float_as_uint(a0), __float_as_uint(a1), __float_as_uint(a2), __float_as_uint(a3));
       reinterpret_cast<uint4*>(y + (split * outer + o) * inner)[col] = out;
@@ -202,9 +202,9 @@ __global__ void __launch_bounds__(256) k_col_reduce(const float* __restrict__ x,
       long long k    = k0;
       for (; k + 4 <= k1; k += 4) {
         float f0 = p[k * inner], f1 = p[(k + 1) * inner], f2 = p[(k + 2) * inner], f3 = p[(k + 3) * inner];
-        acc = Op::apply(Op::apply(Op::apply(Op::apply(acc, f0), f1), f2), f3);
+        acc = Op::accum(Op::accum(Op::accum(Op::accum(acc, f0), f1), f2), f3);
       }
-      for (; k < k1; ++k) acc = Op::apply(acc, p[k * inner]);
+      for (; k < k1; ++k) acc = Op::accum(acc, p[k * inner]);
       y[(split * outer + o) * inner + col] = acc;
     }
   }
@@ -224,5 +224,10 @@ REG_REDUCE_FAMILY("sum", SumOp);
 REG_REDUCE_FAMILY("prod", ProdOp);
 REG_REDUCE_FAMILY("max", MaxOp);
 REG_REDUCE_FAMILY("min", MinOp);
+// Reductions with an elementwise producer folded into the first pass (second passes over partials use the plain op).
+REG_REDUCE_FAMILY("sumsq", SumSquareOp);
+REG_REDUCE_FAMILY("sumabs", SumAbsOp);
+REG_REDUCE_FAMILY("sumexp", SumExpOp);
+REG_REDUCE_FAMILY("maxabs", MaxAbsOp);
 
 }  // namespace cinn_b200

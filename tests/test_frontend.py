@@ -131,6 +131,14 @@ def test_mixed_graph_partitions_into_chain_reduce_chain():
     assert patterns(c) == ["ew_chain", "row_reduce", "ew_chain"]
 
 
+def test_elementwise_producer_folds_into_reduction():
+    b = NetBuilder("fold")
+    x = b.create_input(common.Float(32), (64, 4096), "X")
+    b.sqrt(b.divide(b.reduce_sum(b.multiply(x, b.identity(x)), [1]), b.fill_constant([64], 4096.0)))
+    c = plan(b)
+    assert [p for _, p in c.groups()] == ["row_reduce row_reduce_cta_sumsq_f32", "ew_chain ew_chain_f32_f32"]
+
+
 def test_value_used_twice_is_materialised_once():
     """A producer with two consumers is not duplicated: it becomes a group output (op_lowering_util.cc:745-803)."""
     b = NetBuilder("fanout")
@@ -178,7 +186,7 @@ def test_canonical_expression_and_plans_of_the_workloads():
     assert buf.value == b"cast(tanh(scale(elementwise_add(%0,%1))))"
     expect = {
         "add_relu": (W.add_relu((1, 3, 224, 224)), ["ew_add_relu_f32"]),
-        "c2": (W.bias_scale_tanh_cast((64, 1024, 1024)), ["ew_bias_scale_tanh_cast_f32_f16"]),
+        "c2": (W.bias_scale_tanh_cast((64, 1024, 1024)), ["ew_bias_scale_tanh_cast_stream_f32_f16"]),
         "c3a": (W.reduce_sum_last((128, 1024, 1024)), ["row_reduce_warp8_sum_f32"]),
         "c3b": (W.reduce_max_first((128, 1024, 1024)), ["col_reduce_max_f32"]),
         "c4a": (W.softmax((16384, 4096)), ["softmax_row_f32_g256_v4_r1"]),

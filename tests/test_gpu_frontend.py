@@ -232,3 +232,26 @@ def test_no_bounded_wait_gave_up():
     n = ctypes.c_uint(99)
     assert L.cinn_b200_device_status(ctypes.byref(n)) == 0
     assert n.value == 0
+
+
+@pytest.mark.parametrize("shape,axis", [((64, 4096), 1), ((300, 1000), 1), ((128, 64, 32), 0), ((5, 70000), 1)])
+def test_reductions_with_a_folded_producer(oracle, shape, axis):
+    """reduce_sum(x*x), reduce_sum(|x|), reduce_sum(exp(x)), reduce_max(|x|): one kernel each, no materialised
+    intermediate; against the oracle's materialise-then-reduce evaluation."""
+    b = NetBuilder("fold")
+    x = b.create_input(common.Float(32), shape, "X")
+    outs = {"sumsq": b.reduce_sum(b.multiply(x, b.identity(x)), [axis]), "sumabs": b.reduce_sum(b.abs(x), [axis]),
+            "sumexp": b.reduce_sum(b.exp(x), [axis]), "maxabs": b.reduce_max(b.abs(x), [axis])}
+    X = np.random.default_rng(17).standard_normal(shape).astype(np.float32)
+    comp, got = run_program(b, {"X": X}, list(outs.values()))
+    kernels = " ".join(p for _, p in comp.groups())
+    assert len(comp.groups()) == 4 and all(k in kernels for k in ("sumsq", "sumabs", "sumexp", "maxabs")), kernels
+    ref = oracle_program(comp, {"X": X})
+    r = shape[axis]
+    for name, var in outs.items():
+        g, w = got[str(var)], ref[str(var)]
+        if name == "maxabs":
+            assert np.array_equal(g, w)
+        else:
+            scale = float(np.abs(w).max())
+            assert np.allclose(g, w, rtol=1e-5, atol=2e-7 * r * scale / max(np.sqrt(r), 1)), name
