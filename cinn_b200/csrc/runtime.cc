@@ -123,6 +123,10 @@ static DeviceInfo CurrentDeviceInfo() {
 }
 
 // ---- launch primitive -------------------------------------------------------------------------------
+static int LaunchEntry(const KernelEntry* entry, void* v_args, int num_args, int gx, int gy, int gz, int bx, int by,
+                       int bz, unsigned cluster_x, size_t dyn_smem, void* stream);
+
+// The public launch primitive: resolves the handle in the kernel table, then launches.
 static int LaunchKernel(const void* kernel_fn, void* v_args, int num_args, int gx, int gy, int gz, int bx, int by,
                         int bz, unsigned cluster_x, size_t dyn_smem, void* stream) {
   if (!kernel_fn || (!v_args && num_args > 0) || num_args < 0 || num_args > 64)
@@ -130,6 +134,13 @@ static int LaunchKernel(const void* kernel_fn, void* v_args, int num_args, int g
                     num_args);
   const KernelEntry* entry = FindKernelByFn(kernel_fn);
   if (!entry) return SetError(CINN_B200_ENOTFOUND, "cinn_call_cuda_kernel: %p is not a kernel of this library", kernel_fn);
+  return LaunchEntry(entry, v_args, num_args, gx, gy, gz, bx, by, bz, cluster_x, dyn_smem, stream);
+}
+
+// Group entry points already hold the table entry and come straight here.
+static int LaunchEntry(const KernelEntry* entry, void* v_args, int num_args, int gx, int gy, int gz, int bx, int by,
+                       int bz, unsigned cluster_x, size_t dyn_smem, void* stream) {
+  const void* kernel_fn = entry->fn;
   if (num_args != entry->num_params)
     return SetError(CINN_B200_EINVAL, "kernel %s takes %d parameters, got %d", entry->name, entry->num_params, num_args);
   if (gx <= 0 || gy <= 0 || gz <= 0 || bx <= 0 || by <= 0 || bz <= 0 ||
@@ -338,8 +349,8 @@ static int RunPlan(const CompiledGroup& plan, GroupSlot& slot, const std::vector
         }
       }
     }
-    int rc = LaunchKernel(s.kernel->fn, pods, n, s.grid[0], s.grid[1], s.grid[2], s.block[0], s.block[1], s.block[2],
-                          s.cluster, s.dyn_smem, stream);
+    int rc = LaunchEntry(s.kernel, pods, n, s.grid[0], s.grid[1], s.grid[2], s.block[0], s.block[1], s.block[2],
+                         s.cluster, s.dyn_smem, stream);
     if (rc != CINN_B200_OK) return rc;
   }
   return CINN_B200_OK;
