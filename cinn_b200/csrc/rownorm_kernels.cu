@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(G == 32 ? 256 : G, RownormMinBlocks(G, VPT, R)
           for (int i = 0; i < V; ++i) {
             if (LAYERNORM) {
               s1[r] = s1[r] + f[i];
-              s2[r] = s2[r] + f[i] * f[i];
+              // 16-bit storage (1e-2 tolerance): the square is accumulated with one fused multiply-add.
+              s2[r] = sizeof(T) == 2 ? fmaf(f[i], f[i], s2[r]) : s2[r] + f[i] * f[i];
             } else {
               f[i]            = sizeof(T) == 2 ? exp_for_16bit_out(f[i]) : expf(f[i]);
               ev[r][j][i % KEEP] = f[i];
@@ -180,7 +181,9 @@ __global__ void __launch_bounds__(G == 32 ? 256 : G, RownormMinBlocks(G, VPT, R)
             if (LAYERNORM) {
               Io<T>::unpack(raw[r][j], f);
 #pragma unroll
-              for (int i = 0; i < V; ++i) f[i] = fmaf((f[i] - m[r]) * a[r], g[i], b[i]);
+              for (int i = 0; i < V; ++i)
+                f[i] = sizeof(T) == 2 ? fmaf(fmaf(f[i], a[r], -m[r] * a[r]), g[i], b[i])
+                                      : fmaf((f[i] - m[r]) * a[r], g[i], b[i]);
             } else {
 #pragma unroll
               for (int i = 0; i < V; ++i) f[i] = ev[r][j][i % KEEP] * a[r];

@@ -98,7 +98,8 @@ __global__ void __launch_bounds__(G)
         for (int i = 0; i < V; ++i) {
           if (LAYERNORM) {
             s1 = s1 + f[j][i];
-            s2 = s2 + f[j][i] * f[j][i];
+            // 16-bit storage (1e-2 tolerance): the square is accumulated with one fused multiply-add.
+            s2 = sizeof(T) == 2 ? fmaf(f[j][i], f[j][i], s2) : s2 + f[j][i] * f[j][i];
           } else {
             f[j][i] = sizeof(T) == 2 ? exp_for_16bit_out(f[j][i]) : expf(f[j][i]);
             s1      = s1 + f[j][i];
@@ -139,12 +140,15 @@ __global__ void __launch_bounds__(G)
       const float mean = s1 * inv_n;
       const float var  = x86_max(s2 * inv_n - mean * mean, 0.0f);
       const float rstd = rsqrtf(var + eps);
+      const float nmr  = -mean * rstd;  // 16-bit storage: (x - mean) * rstd as one fma(x, rstd, -mean * rstd)
 #pragma unroll
       for (int j = 0; j < VPT; ++j) {
         const int v = t + j * G;
         if (v < nvec) {
 #pragma unroll
-          for (int i = 0; i < V; ++i) f[j][i] = fmaf((f[j][i] - mean) * rstd, g[j][i], b[j][i]);
+          for (int i = 0; i < V; ++i)
+            f[j][i] = sizeof(T) == 2 ? fmaf(fmaf(f[j][i], rstd, nmr), g[j][i], b[j][i])
+                                     : fmaf((f[j][i] - mean) * rstd, g[j][i], b[j][i]);
           __stcs(dst + v, Io<T>::pack(f[j]));
         }
       }
