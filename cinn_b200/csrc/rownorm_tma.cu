@@ -176,6 +176,21 @@ __global__ void __launch_bounds__(G)
 
 }  // namespace
 
+// Self-test of the bounded-wait path: waits on an mbarrier that nothing will ever complete, with a small poll
+// limit, records the give-up in this file's counter exactly as the streaming kernels do, and returns.  It lets a
+// host test check that a wait that runs out surfaces through cinn_b200_device_status without any kernel hanging.
+__global__ void __launch_bounds__(32) k_selftest_bounded_wait(long long polls) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    bool done = false;
+    for (long long i = 0; i < polls && !done; ++i) done = mbar_try_wait(&bar, 0);
+    if (!done) atomicAdd(&g_rownorm_wait_timeouts, 1u);
+  }
+}
+CINN_B200_REGISTER_KERNEL("selftest_bounded_wait", 1, 32, k_selftest_bounded_wait);
+
 #define REG_TMA_ONE(TNAME, T, G, VPT)                                                               \
   CINN_B200_REGISTER_KERNEL("softmax_tma_" TNAME "_g" #G "_v" #VPT, 8, G, k_rownorm_tma<T, G, VPT, false>); \
   CINN_B200_REGISTER_KERNEL("layernorm_tma_" TNAME "_g" #G "_v" #VPT, 8, G, k_rownorm_tma<T, G, VPT, true>)

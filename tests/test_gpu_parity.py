@@ -273,3 +273,52 @@ def test_run_host_pipelined_equals_device_run(make, min_chunks):
     assert chunks >= min_chunks and (min_chunks > 1 or chunks == 1), chunks
     assert np.array_equal(out.view(np.uint8), dev_out.view(np.uint8))
     g.release()
+
+
+def test_bounded_wait_that_runs_out_is_reported_not_hung():
+    """A wait on a barrier that nothing completes gives up after its poll limit and shows up in the device status
+    word; the kernel returns normally and the context stays usable."""
+    import ctypes
+    import torch
+    import cinn_b200
+    from cinn_b200 import runtime as rt
+    L = cinn_b200.lib()
+    n = ctypes.c_uint(0)
+    assert L.cinn_b200_device_status(ctypes.byref(n)) == 0  # clear
+    k = L.cinn_b200_get_kernel(b"selftest_bounded_wait")
+    pods = (rt.cinn_pod_value_t * 1)()
+    pods[0].type_code_ = rt.POD_INT64
+    pods[0].value_.v_int64 = 2000
+    assert L.cinn_b200_call_cuda_kernel_ex(k, pods, 1, 1, 1, 1, 32, 1, 1, 0, 0, None) == 0, L.cinn_b200_last_error()
+    torch.cuda.synchronize()
+    assert L.cinn_b200_device_status(ctypes.byref(n)) == 0 and n.value == 1
+    assert L.cinn_b200_device_status(ctypes.byref(n)) == 0 and n.value == 0
+    # the context is healthy: a normal group still runs
+    w = W.add_relu((4, 4))
+    got, _ = run_group(w)
+    assert np.array_equal(got, np.maximum(w.inputs[0] + w.inputs[1], 0))
+
+
+def test_more_than_two_to_the_31_elements():
+    """64-bit indexing: relu(A+B) over 2^31 + 4096 fp32 elements (26 GB on the device), bit-exact against the same
+    arithmetic done by torch on the device (the host oracle is not needed for an add and a max)."""
+    import torch
+    import cinn_b200
+    free, _ = torch.cuda.mem_get_info()
+    n0, n1 = 2, (1 << 30) + 2048
+    if free < 3 * n0 * n1 * 4 + (4 << 30):
+        pytest.skip("not enough free device memory")
+    a = torch.empty(n0, n1, device="cuda").uniform_(-1, 1)
+    b = torch.empty(n0, n1, device="cuda").uniform_(-1, 1)
+    y = torch.empty(n0, n1, device="cuda")
+    s = "%d,%d" % (n0, n1)
+    g = cinn_b200.FusedGroup(f"group fn_big_add_relu\ninput A float32 {s}\ninput B float32 {s}\n"
+                             f"op elementwise_add t0 = A B ; axis=-1\nop relu t1 = t0\noutput t1 float32 {s}\n")
+    g.run([a, b, y])
+    torch.cuda.synchronize()
+    a.add_(b).clamp_(min=0)  # reference in place to save memory
+    assert torch.equal(y, a)
+    assert float(y[1, -1]) == float(a[1, -1])
+    g.release()
+    del a, b, y
+    torch.cuda.empty_cache()
