@@ -103,6 +103,14 @@ def lib():
         L.cinn_b200_computation_group_pattern.argtypes = [vp, ci, ctypes.c_char_p, ctypes.c_size_t]
         L.cinn_b200_col_reduce_f32_static_scratch.restype = ci
         L.cinn_b200_col_reduce_f32_static_scratch.argtypes = [ci, vp, vp, ll, ll, ll, vp]
+        L.cinn_b200_peer_create.restype = ci
+        L.cinn_b200_peer_create.argtypes = [ci, ci, ll, ctypes.c_char_p, ctypes.POINTER(vp)]
+        L.cinn_b200_peer_connect.restype = ci
+        L.cinn_b200_peer_connect.argtypes = [vp, ctypes.c_char_p]
+        L.cinn_b200_peer_destroy.restype = ci
+        L.cinn_b200_peer_destroy.argtypes = [vp]
+        L.cinn_b200_col_reduce_sharded_f32.restype = ci
+        L.cinn_b200_col_reduce_sharded_f32.argtypes = [vp, ci, vp, ll, ll, vp, ci, vp]
         L.cinn_b200_device_status.restype = ci
         L.cinn_b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         L.cinn_b200_group_host_chunks.restype = ci

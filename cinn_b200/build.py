@@ -23,6 +23,7 @@ SOURCES = [
     "ew_chain.cu",
     "ew_stream.cu",
     "reduce_static_scratch.cu",
+    "peer_reduce.cu",
     "group_desc.cc",
     "group_match.cc",
     "chain_match.cc",

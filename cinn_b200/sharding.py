@@ -90,3 +90,59 @@ class ShardedReduceAxis0:
         else:
             out.fill_(identity_of(self.kind))
         return finish_reduce_over_sharded_axis(out, self.kind, self.group)
+
+
+class FusedShardedReduceAxis0:
+    """reduce_<kind> over axis 0 of a [R, inner...] fp32 tensor sharded on axis 0, local reduction and cross-GPU
+    exchange in ONE kernel per rank over NVLink peer memory (see cinn_b200_col_reduce_sharded_f32).
+
+    `all_gather=True` leaves the full result on every rank (what an all-reduce gives); `False` leaves on each rank
+    the band of columns it owns (what a reduce-scatter gives).  Needs an initialised process group with one rank per
+    GPU of the node; the exchange buffers are mapped across processes with CUDA IPC at construction."""
+
+    KINDS = {"sum": 0, "prod": 1, "max": 2, "min": 3}
+
+    def __init__(self, kind, full_shape, world, rank, all_gather=True, group=None):
+        import ctypes
+        from . import _lib
+        self.kind, self.full_shape, self.world, self.rank = kind, tuple(full_shape), world, rank
+        self.all_gather = all_gather
+        self.local_shape = sharded_shape(full_shape, world, rank)
+        self.inner = 1
+        for d in full_shape[1:]:
+            self.inner *= int(d)
+        if self.inner % (4 * world):
+            raise ValueError("the reduced tensor's inner size must be a multiple of 4 * world")
+        self.out_shape = tuple(full_shape[1:]) if all_gather else (self.inner // world,)
+        L = _lib.lib()
+        handle = ctypes.create_string_buffer(64)
+        ctx = ctypes.c_void_p()
+        _lib.check(L.cinn_b200_peer_create(rank, world, self.inner, handle, ctypes.byref(ctx)))
+        self._ctx = ctx
+        handles = [None] * world
+        if world > 1:
+            dist.all_gather_object(handles, handle.raw, group=group)
+        else:
+            handles[0] = handle.raw
+        _lib.check(L.cinn_b200_peer_connect(ctx, b"".join(handles)))
+        if world > 1:
+            dist.barrier(group=group)  # every rank has mapped every buffer before anyone stores into them
+
+    def __call__(self, x_slice, out):
+        import ctypes
+        from . import _lib
+        if tuple(x_slice.shape) != self.local_shape or self.local_shape[0] == 0:
+            raise ValueError("rank %d expects a non-empty slice of shape %s" % (self.rank, self.local_shape))
+        if out.numel() != (self.inner if self.all_gather else self.inner // self.world):
+            raise ValueError("output has the wrong number of elements")
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib().cinn_b200_col_reduce_sharded_f32(
+            self._ctx, self.KINDS[self.kind], ctypes.c_void_p(x_slice.data_ptr()), self.local_shape[0], self.inner,
+            ctypes.c_void_p(out.data_ptr()), 1 if self.all_gather else 0, ctypes.c_void_p(stream)))
+        return out
+
+    def close(self):
+        from . import _lib
+        if self._ctx is not None:
+            _lib.lib().cinn_b200_peer_destroy(self._ctx)
+            self._ctx = None

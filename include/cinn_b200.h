@@ -188,6 +188,30 @@ int cinn_b200_computation_group_pattern(cinn_b200_computation* computation, int 
 int cinn_b200_col_reduce_f32_static_scratch(int kind, const float* x, float* y, long long outer, long long r,
                                             long long inner, void* stream);
 
+/* ---- reductions over an axis sharded across GPUs --------------------------------------------------- */
+
+/*
+ * No counterpart in the reference (it has no multi-GPU execution).  x is [R, inner] fp32 with the R axis split over
+ * `world` ranks, one process per GPU of one node; every rank holds rows_local rows.  One kernel per rank reduces the
+ * local rows and exchanges the partials over NVLink peer memory (plain peer stores, mapped with CUDA IPC; no
+ * multicast): each rank ends up with the final result of the band of columns it owns (all_gather == 0: `out` holds
+ * inner / world elements, band `rank`) or with the full result (all_gather != 0: `out` holds inner elements).
+ * Requirements: inner % (4 * world) == 0, 16-byte aligned x_local / out, every rank calls with the same kind /
+ * inner / all_gather, in the same order.  Waits on peers are bounded (about a second); a wait that runs out is
+ * reported by cinn_b200_device_status and leaves `out` undefined.
+ *
+ * peer_create allocates this rank's exchange buffer for results of up to max_inner elements and writes its 64-byte
+ * IPC handle; the caller gathers the handles of all ranks (rank order) and passes them to peer_connect.
+ */
+typedef struct cinn_b200_peer_ctx cinn_b200_peer_ctx;
+int cinn_b200_peer_create(int rank, int world, long long max_inner, unsigned char* handle_out /* 64 bytes */,
+                          cinn_b200_peer_ctx** ctx_out);
+int cinn_b200_peer_connect(cinn_b200_peer_ctx* ctx, const unsigned char* all_handles /* world * 64 bytes */);
+int cinn_b200_peer_destroy(cinn_b200_peer_ctx* ctx);
+int cinn_b200_col_reduce_sharded_f32(cinn_b200_peer_ctx* ctx, int kind /* 0 sum, 1 prod, 2 max, 3 min */,
+                                     const float* x_local, long long rows_local, long long inner, float* out,
+                                     int all_gather, void* stream);
+
 /*
  * Device-side status of the current device: the number of bounded waits on asynchronous copies that gave up
  * since the last call (0 in a healthy run); reading clears it.  Synchronises with the device.  The reference

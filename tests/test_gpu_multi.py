@@ -51,6 +51,26 @@ def _worker(rank, world, port, out_dir):
         g.run([torch.from_numpy(np.ascontiguousarray(xs[s0:s0 + c0])).to(dev), torch.from_numpy(bias).to(dev), y])
         torch.cuda.synchronize()
         np.save(os.path.join(out_dir, "c2_rank%d.npy" % rank), y.cpu().numpy())
+        # (3) the fused reduction + exchange over NVLink peer memory: full result and owned band, several calls in a row
+        import ctypes
+        full2 = (48, 64, 256)
+        inner = 64 * 256
+        st, cnt = sharding.shard_range(full2[0], world, rank)
+        for kind in ("max", "sum"):
+            for gather in (True, False):
+                fused = sharding.FusedShardedReduceAxis0(kind, full2, world, rank, all_gather=gather)
+                for call in range(3):
+                    xf = W.reduce_input(full2, seed=40 + call)
+                    xl = torch.from_numpy(np.ascontiguousarray(xf[st:st + cnt])).to(dev)
+                    o = torch.full(fused.out_shape, float("nan"), device=dev)
+                    fused(xl, o)
+                    torch.cuda.synchronize()
+                    np.save(os.path.join(out_dir, "fused_%s_%d_%d_rank%d.npy" % (kind, int(gather), call, rank)),
+                            o.cpu().numpy())
+                dist.barrier()
+                fused.close()
+        n = ctypes.c_uint(0)
+        assert cinn_b200.lib().cinn_b200_device_status(ctypes.byref(n)) == 0 and n.value == 0, n.value
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -75,3 +95,19 @@ def test_two_ranks_sharded_groups(tmp_path, oracle):
     got = np.concatenate([np.load(tmp_path / ("c2_rank%d.npy" % r)) for r in range(world)], axis=0)
     bad, worst = oracle.count_not_close(got, ref, 1e-2, 1.2e-7)
     assert bad == 0, (bad, worst)
+    # fused reduce + exchange
+    full2, inner = (48, 64, 256), 64 * 256
+    for kind in ("max", "sum"):
+        for call in range(3):
+            xf = W.reduce_input(full2, seed=40 + call)
+            want = oracle.reduce(kind, xf, 1, 48, inner)
+            for r in range(world):
+                full_res = np.load(tmp_path / ("fused_%s_1_%d_rank%d.npy" % (kind, call, r))).reshape(-1)
+                band_res = np.load(tmp_path / ("fused_%s_0_%d_rank%d.npy" % (kind, call, r))).reshape(-1)
+                band = inner // world
+                if kind == "max":
+                    assert np.array_equal(full_res, want), (kind, call, r)
+                    assert np.array_equal(band_res, want[r * band:(r + 1) * band]), (kind, call, r)
+                else:
+                    assert np.allclose(full_res, want, rtol=1e-5, atol=1e-4), (kind, call, r)
+                    assert np.allclose(band_res, want[r * band:(r + 1) * band], rtol=1e-5, atol=1e-4), (kind, call, r)
