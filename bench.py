@@ -288,11 +288,43 @@ def sharded_reduce_max(torch, dist, dev, world, rank, peak):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed_in_graph(fn, iters=20, replays=5):
+        """The same calls replayed from one CUDA graph: no per-launch host work, so the device time shows even where
+        a launch from Python (some 15-20 us) is longer than the kernel."""
+        try:
+            fn()
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(iters):
+                        fn()
+            graph.replay()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(replays):
+                graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / (iters * replays)], device=dev, dtype=torch.float64)
+        except Exception as exc:  # reported, not hidden: the eager numbers stand on their own
+            sys.stderr.write("graph timing failed on rank %d: %r\n" % (rank, exc))
+            t = torch.tensor([float("nan")], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        v = float(t.item())
+        return None if v != v else round(v, 5)
+
     ms_local = timed(lambda: op.local_reduce(x, out))
     ms_total = timed(lambda: op(x, out))
+    g_local = timed_in_graph(lambda: op.local_reduce(x, out))
+    g_total = timed_in_graph(lambda: op(x, out))
     # The same reduction with the exchange fused into the kernel (peer stores over NVLink, no NCCL call).
     fused_full = sharding.FusedShardedReduceAxis0("max", full, world, rank, all_gather=True)
     ms_fused_full = timed(lambda: fused_full(x, out))
+    g_fused_full = timed_in_graph(lambda: fused_full(x, out))
     check = out.clone()
     op(x, out)
     torch.cuda.synchronize()
@@ -300,6 +332,7 @@ def sharded_reduce_max(torch, dist, dev, world, rank, peak):
     fused_band = sharding.FusedShardedReduceAxis0("max", full, world, rank, all_gather=False)
     band_out = torch.empty(fused_band.out_shape, device=dev)
     ms_fused_band = timed(lambda: fused_band(x, band_out))
+    g_fused_band = timed_in_graph(lambda: fused_band(x, band_out))
     dist.barrier()
     fused_full.close()
     fused_band.close()
@@ -309,6 +342,8 @@ def sharded_reduce_max(torch, dist, dev, world, rank, peak):
             "ms_fused_kernel_full_result": round(ms_fused_full, 5),
             "ms_fused_kernel_owned_band": round(ms_fused_band, 5),
             "fused_equals_nccl_result": same,
+            "ms_in_cuda_graph": {"local_kernel": g_local, "with_nccl_allreduce": g_total,
+                                 "fused_kernel_full_result": g_fused_full, "fused_kernel_owned_band": g_fused_band},
             "GB/s_whole_job_local": gbs(ms_local), "GB/s_whole_job_with_nccl_allreduce": gbs(ms_total),
             "GB/s_whole_job_fused_full_result": gbs(ms_fused_full),
             "GB/s_whole_job_fused_owned_band": gbs(ms_fused_band),

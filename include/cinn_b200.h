@@ -197,8 +197,10 @@ int cinn_b200_col_reduce_f32_static_scratch(int kind, const float* x, float* y, 
  * multicast): each rank ends up with the final result of the band of columns it owns (all_gather == 0: `out` holds
  * inner / world elements, band `rank`) or with the full result (all_gather != 0: `out` holds inner elements).
  * Requirements: inner % (4 * world) == 0, 16-byte aligned x_local / out, every rank calls with the same kind /
- * inner / all_gather, in the same order.  Waits on peers are bounded (about a second); a wait that runs out is
- * reported by cinn_b200_device_status and leaves `out` undefined.
+ * inner / all_gather, in the same order, and a context serves ONE inner size and ONE result mode (fixed by its first
+ * call).  A result whose bits are 0xFFFFFFFF (a NaN pattern used inside as "not arrived") is delivered as the default
+ * NaN 0x7FFFFFFF.  Waits on peers are bounded (about half a second); a wait that runs out is reported by
+ * cinn_b200_device_status, leaves `out` undefined and the context unusable (destroy it).
  *
  * peer_create allocates this rank's exchange buffer for results of up to max_inner elements and writes its 64-byte
  * IPC handle; the caller gathers the handles of all ranks (rank order) and passes them to peer_connect.

@@ -11,6 +11,10 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+# calls per context of the fused reduction: more than the three exchange areas it rotates through
+N_FUSED_CALLS = 7
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -59,7 +63,7 @@ def _worker(rank, world, port, out_dir):
         for kind in ("max", "sum"):
             for gather in (True, False):
                 fused = sharding.FusedShardedReduceAxis0(kind, full2, world, rank, all_gather=gather)
-                for call in range(3):
+                for call in range(N_FUSED_CALLS):
                     xf = W.reduce_input(full2, seed=40 + call)
                     xl = torch.from_numpy(np.ascontiguousarray(xf[st:st + cnt])).to(dev)
                     o = torch.full(fused.out_shape, float("nan"), device=dev)
@@ -67,6 +71,21 @@ def _worker(rank, world, port, out_dir):
                     torch.cuda.synchronize()
                     np.save(os.path.join(out_dir, "fused_%s_%d_%d_rank%d.npy" % (kind, int(gather), call, rank)),
                             o.cpu().numpy())
+                if kind == "max" and gather:
+                    # the same context replayed from a CUDA graph (the call counter lives on the device)
+                    xf = W.reduce_input(full2, seed=77)
+                    xl = torch.from_numpy(np.ascontiguousarray(xf[st:st + cnt])).to(dev)
+                    o = torch.full(fused.out_shape, float("nan"), device=dev)
+                    side = torch.cuda.Stream()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.stream(side):
+                        with torch.cuda.graph(graph, stream=side):
+                            for _ in range(4):
+                                fused(xl, o)
+                    for _ in range(2):
+                        graph.replay()
+                    torch.cuda.synchronize()
+                    np.save(os.path.join(out_dir, "fused_graph_rank%d.npy" % rank), o.cpu().numpy())
                 dist.barrier()
                 fused.close()
         n = ctypes.c_uint(0)
@@ -97,8 +116,11 @@ def test_two_ranks_sharded_groups(tmp_path, oracle):
     assert bad == 0, (bad, worst)
     # fused reduce + exchange
     full2, inner = (48, 64, 256), 64 * 256
+    want = oracle.reduce("max", W.reduce_input(full2, seed=77), 1, 48, inner)
+    for r in range(world):
+        assert np.array_equal(np.load(tmp_path / ("fused_graph_rank%d.npy" % r)).reshape(-1), want), r
     for kind in ("max", "sum"):
-        for call in range(3):
+        for call in range(N_FUSED_CALLS):
             xf = W.reduce_input(full2, seed=40 + call)
             want = oracle.reduce(kind, xf, 1, 48, inner)
             for r in range(world):
