@@ -51,7 +51,10 @@ const std::map<std::string, int>& UnaryCodes() {
       {"relu", EW_RELU},   {"negative", EW_NEG}, {"abs", EW_ABS},        {"log", EW_LOG},     {"floor", EW_FLOOR},
       {"ceil", EW_CEIL},   {"erf", EW_ERF},     {"sin", EW_SIN},         {"cos", EW_COS},     {"reciprocal", EW_RECIP},
       {"round", EW_ROUND}, {"trunc", EW_TRUNC}, {"sign", EW_SIGN},       {"relu6", EW_RELU6}, {"log2", EW_LOG2},
-      {"log10", EW_LOG10}, {"identity", EW_IDENTITY}};
+      {"log10", EW_LOG10}, {"identity", EW_IDENTITY}, {"tan", EW_TAN},       {"sinh", EW_SINH},   {"cosh", EW_COSH},
+      {"asin", EW_ASIN},   {"acos", EW_ACOS},   {"atan", EW_ATAN},       {"asinh", EW_ASINH}, {"acosh", EW_ACOSH},
+      {"atanh", EW_ATANH}, {"cbrt", EW_CBRT},   {"isnan", EW_ISNAN},     {"isinf", EW_ISINF}, {"isfinite", EW_ISFINITE},
+      {"logical_not", EW_LNOT}};
   return m;
 }
 const std::map<std::string, int>& BinaryCodes() {
@@ -59,15 +62,25 @@ const std::map<std::string, int>& BinaryCodes() {
       {"elementwise_add", EW_ADD}, {"subtract", EW_SUB},   {"elementwise_mul", EW_MUL}, {"divide", EW_DIV},
       {"max", EW_MAX},             {"min", EW_MIN},        {"pow", EW_POW},             {"equal", EW_EQ},
       {"not_equal", EW_NE},        {"greater_than", EW_GT}, {"less_than", EW_LT},       {"greater_equal", EW_GE},
-      {"less_equal", EW_LE}};
+      {"less_equal", EW_LE},       {"mod", EW_MOD},        {"remainder", EW_MOD},       {"floor_divide", EW_FLOOR_DIV},
+      {"atan2", EW_ATAN2},         {"logical_and", EW_LAND}, {"logical_or", EW_LOR},    {"logical_xor", EW_LXOR}};
   return m;
 }
 
-uint64_t Word(int op, int asel, int bsel, bool swap, float imm) {
+uint64_t Word(int op, int asel, int bsel, int role, float imm) {
   uint32_t bits;
   memcpy(&bits, &imm, 4);
   return (uint64_t)(op & 0xff) | ((uint64_t)(asel & 0xff) << 8) | ((uint64_t)(bsel & 0xff) << 16) |
-         ((uint64_t)(swap ? 1 : 0) << 24) | ((uint64_t)bits << 32);
+         ((uint64_t)(role & 3) << 24) | ((uint64_t)bits << 32);
+}
+
+bool IsFloatType(DType t) { return t == DType::kFloat32 || t == DType::kFloat16 || t == DType::kBFloat16; }
+bool IsIntType(DType t) { return t == DType::kInt32 || t == DType::kInt64; }
+// Types whose values the kernel carries exactly in an fp32 register.
+bool IsChainType(DType t) { return IsFloatType(t) || t == DType::kBool; }
+bool YieldsBool(int code) {
+  return (code >= EW_EQ && code <= EW_LE) || code == EW_LAND || code == EW_LOR || code == EW_LXOR || code == EW_ISNAN ||
+         code == EW_ISINF || code == EW_ISFINITE || code == EW_LNOT;
 }
 
 struct Side {
@@ -84,6 +97,10 @@ struct Step {
   bool swap  = false;
   float imm  = 0.0f;
   bool f32   = true;   // result type is float32 (contraction only applies to fp32 arithmetic)
+  // EW_SELECT only: second operand and the role of the chain value (see ew_chain.h)
+  int bsel   = 0;
+  float imm2 = 0.0f;
+  int role   = 0;
 };
 
 struct ChainBuilder {
@@ -137,10 +154,16 @@ struct ChainBuilder {
         const Value &a = values[op.inputs[0]], &b = values[op.inputs[1]];
         v       = a.numel() >= b.numel() ? a : b;
         if (a.shape.size() != b.shape.size() && a.numel() == b.numel()) v = a.shape.size() >= b.shape.size() ? a : b;
-        v.dtype = BinaryCodes().at(op.type) >= EW_EQ && BinaryCodes().at(op.type) <= EW_LE ? DType::kBool : a.dtype;
+        v.dtype = YieldsBool(BinaryCodes().at(op.type)) ? DType::kBool : a.dtype;
       } else if (UnaryCodes().count(op.type) || op.type == "scale") {
         if (op.inputs.size() != 1) return Fail(op.type + " needs one operand");
         v = values[op.inputs[0]];
+        if (UnaryCodes().count(op.type) && YieldsBool(UnaryCodes().at(op.type))) v.dtype = DType::kBool;
+      } else if (op.type == "select") {
+        if (op.inputs.size() != 3) return Fail("select needs three operands");
+        v = values[op.inputs[1]];
+        for (int k = 0; k < 3; ++k)
+          if (values[op.inputs[k]].numel() > v.numel()) v.shape = values[op.inputs[k]].shape;
       } else {
         return Fail("op '" + op.type + "' is not an elementwise op");
       }
@@ -210,7 +233,14 @@ struct ChainBuilder {
     std::string src = name;
     std::vector<int64_t> axes;
     const Value* sv = &values[name];
-    if (p && p->type == "broadcast_to") {
+    if (p && IsLoadCast(*p)) {
+      // cast(group input): the conversion happens in the load
+      src = p->inputs[0];
+      sv  = &values[src];
+      int64_t axis = atoll(Attr(op, "axis", "-1").c_str());
+      int64_t off  = (axis < 0 || sv->shape.size() == out_shape.size()) ? (int64_t)out_shape.size() - (int64_t)sv->shape.size() : axis;
+      for (size_t i = 0; i < sv->shape.size(); ++i) axes.push_back(off + (int64_t)i);
+    } else if (p && p->type == "broadcast_to") {
       src = p->inputs[0];
       if (!input_index.count(src)) return false;
       axes = IntList(Attr(*p, "broadcast_axes", ""));
@@ -228,13 +258,24 @@ struct ChainBuilder {
       int64_t off  = (axis < 0 || sv->shape.size() == out_shape.size()) ? (int64_t)out_shape.size() - (int64_t)sv->shape.size() : axis;
       for (size_t i = 0; i < sv->shape.size(); ++i) axes.push_back(off + (int64_t)i);
     }
-    if (sv->dtype != DType::kFloat32 && sv->dtype != DType::kFloat16 && sv->dtype != DType::kBFloat16) return false;
+    if (!IsChainType(sv->dtype) && !(IsIntType(sv->dtype) && src != name)) return false;
     Side s;
     if (!SideSpec(sv->shape, axes, input_index[src], &s)) return false;
     int sel = AddSide(s);
     if (sel < 0) return false;
     *asel = sel;
     return true;
+  }
+
+  // A cast whose source is a group input and whose conversion the kernel's load performs exactly as the cast op
+  // would: integer -> float32 (one rounding to nearest even), bool -> any float, float16/bfloat16 -> float32.
+  bool IsLoadCast(const OpDesc& p) {
+    if (p.type != "cast" || !input_index.count(p.inputs[0])) return false;
+    const DType from = values[p.inputs[0]].dtype, to = values[p.output].dtype;
+    if (IsIntType(from)) return to == DType::kFloat32;
+    if (from == DType::kBool) return IsFloatType(to);
+    if (from == DType::kFloat16 || from == DType::kBFloat16) return to == DType::kFloat32;
+    return false;
   }
 
   // True if `name` is the chain value `chain` possibly through identity ops.
@@ -252,17 +293,30 @@ struct ChainBuilder {
     if (!p) return false;
     if (p->type == "fill_constant") return false;
     if (p->type == "broadcast_to" && input_index.count(p->inputs[0])) return false;
+    if (IsLoadCast(*p)) return false;
     return true;
   }
 };
 
-int DTypeKernelCode(DType t) { return t == DType::kFloat32 ? 0 : (t == DType::kFloat16 ? 1 : (t == DType::kBFloat16 ? 2 : -1)); }
+int DTypeKernelCode(DType t) {
+  switch (t) {
+    case DType::kFloat32: return EW_F32;
+    case DType::kFloat16: return EW_F16;
+    case DType::kBFloat16: return EW_BF16;
+    case DType::kBool: return EW_BOOL;
+    case DType::kInt32: return EW_I32;
+    case DType::kInt64: return EW_I64;
+    default: return -1;
+  }
+}
 const char* DTypeKernelName(DType t) {
   switch (t) {
     case DType::kFloat32: return "f32";
     case DType::kFloat16: return "f16";
     case DType::kBFloat16: return "bf16";
     case DType::kBool: return "bool";
+    case DType::kInt32: return "i32";
+    case DType::kInt64: return "i64";
     default: return nullptr;
   }
 }
@@ -310,13 +364,27 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
     const bool f32 = ov.dtype == DType::kFloat32;
     if (op.type == "cast") {
       const Value& iv = cb.values[op.inputs[0]];
-      const bool in_float  = iv.dtype == DType::kFloat32 || iv.dtype == DType::kFloat16 || iv.dtype == DType::kBFloat16;
-      const bool out_float = ov.dtype == DType::kFloat32 || ov.dtype == DType::kFloat16 || ov.dtype == DType::kBFloat16;
-      if (!in_float || !out_float) {
-        cb.Fail("cast between " + std::string(DTypeName(iv.dtype)) + " and " + DTypeName(ov.dtype) + " is not supported in a chain");
+      bool ok = false;
+      if (IsFloatType(iv.dtype) && IsFloatType(ov.dtype)) {
+        ok = true;
+        round_after();  // widening casts are exact and need no step
+      } else if (iv.dtype == DType::kBool && (IsFloatType(ov.dtype) || ov.dtype == DType::kBool)) {
+        ok = true;      // 0 / 1 are exact in every float type
+      } else if (IsChainType(iv.dtype) && ov.dtype == DType::kBool) {
+        ok = true;
+        Step r;
+        r.op = EW_TO_BOOL;
+        r.f32 = false;
+        rev.push_back(r);
+      } else if (IsChainType(iv.dtype) && IsIntType(ov.dtype)) {
+        ok = cur == out.name;  // float -> integer only as the last op: the store converts (toward zero)
+      } else if (IsIntType(iv.dtype) && ov.dtype == DType::kFloat32) {
+        ok = cb.input_index.count(op.inputs[0]) != 0;  // integer -> float32 only on the chain's input: the load converts
+      }
+      if (!ok) {
+        cb.Fail("cast from " + std::string(DTypeName(iv.dtype)) + " to " + DTypeName(ov.dtype) + " is not supported at this place of a chain");
         return nullptr;
       }
-      round_after();  // widening casts are exact and need no step
       cur = op.inputs[0];
     } else if (op.type == "scale") {
       const float s = (float)atof(ChainBuilder::Attr(op, "scale", "1").c_str());
@@ -332,6 +400,10 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
       else { rev.push_back(mul); rev.push_back(add); }
       cur = op.inputs[0];
     } else if (UnaryCodes().count(op.type)) {
+      if (!IsChainType(cb.values[op.inputs[0]].dtype)) {
+        cb.Fail("op '" + op.type + "' on a " + DTypeName(cb.values[op.inputs[0]].dtype) + " value is not a float chain");
+        return nullptr;
+      }
       round_after();
       if (op.type != "identity") {
         Step s;
@@ -380,13 +452,53 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
         }
         s.swap = !chain_is_a;  // the side operand is the LEFT operand
       }
-      if (s.op >= EW_EQ && s.op <= EW_LE && cur != out.name) {
-        cb.Fail("a comparison must be the last op of a chain");
+      if (!IsChainType(cb.values[a].dtype) || !IsChainType(cb.values[b].dtype)) {
+        cb.Fail("op '" + op.type + "' on " + DTypeName(cb.values[a].dtype) + " operands is not a float chain");
         return nullptr;
       }
       round_after();
       rev.push_back(s);
       cur = next;
+    } else if (op.type == "select") {
+      // One of the three operands continues the chain; the other two are inputs, constants or the chain value.
+      int chain_pos = -1;
+      for (int k = 0; k < 3 && chain_pos < 0; ++k)
+        if (cb.InGroupComputed(op.inputs[k])) chain_pos = k;
+      for (int k = 0; k < 3; ++k)
+        if (cb.InGroupComputed(op.inputs[k]) && k != chain_pos && !cb.IsSameAs(op.inputs[k], op.inputs[chain_pos])) {
+          cb.Fail("select combines two values computed in the group (a tree, not a chain)");
+          return nullptr;
+        }
+      if (chain_pos < 0) {
+        for (int k : {1, 2, 0})
+          if (chain_pos < 0 && cb.input_index.count(op.inputs[k]) && cb.values[op.inputs[k]].numel() == cb.n &&
+              IsChainType(cb.values[op.inputs[k]].dtype))
+            chain_pos = k;
+        if (chain_pos < 0) {
+          cb.Fail("select has no full-size operand to start the chain from");
+          return nullptr;
+        }
+      }
+      Step s;
+      s.op   = EW_SELECT;
+      s.role = chain_pos;
+      s.f32  = false;
+      // operand A / B by role: role 0 -> (true, false); role 1 -> (cond, false); role 2 -> (cond, true)
+      const int a_pos = chain_pos == 0 ? 1 : 0, b_pos = chain_pos == 2 ? 1 : 2;
+      const std::string& chain = op.inputs[chain_pos];
+      auto resolve = [&](int pos, int* sel, float* imm) {
+        const std::string& nm = op.inputs[pos];
+        if (!IsChainType(cb.values[nm].dtype)) return false;
+        if (cb.IsSameAs(nm, chain)) { *sel = 4; return true; }
+        return cb.ResolveOperand(nm, op, sel, imm);
+      };
+      if (!IsChainType(cb.values[chain].dtype) || !resolve(a_pos, &s.asel, &s.imm) || !resolve(b_pos, &s.bsel, &s.imm2)) {
+        cb.Fail("an operand of select is neither a broadcastable group input nor a constant");
+        return nullptr;
+      }
+      round_after();
+      rev.push_back(s);
+      cur = chain;
     } else {
       cb.Fail("op '" + op.type + "' cannot be part of an elementwise chain");
       return nullptr;
@@ -420,15 +532,19 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
     if (s.op == EW_MUL && s.f32 && i + 1 < steps.size() && steps[i + 1].op == EW_ADD && steps[i + 1].f32 &&
         steps[i + 1].asel != 4) {
       const Step& a = steps[i + 1];
-      words.push_back(Word(EW_FMA, s.asel, a.asel, false, s.imm));
-      if (a.asel == 0) words.push_back(Word(EW_NOP, 0, 0, false, a.imm));
+      words.push_back(Word(EW_FMA, s.asel, a.asel, 0, s.imm));
+      if (a.asel == 0) words.push_back(Word(EW_NOP, 0, 0, 0, a.imm));
       ++i;
       continue;
     }
-    if (s.op >= EW_FIRST_UNARY)
-      words.push_back(Word(s.op, 0, 0, false, s.imm));
-    else
-      words.push_back(Word(s.op, s.asel, 0, s.swap, s.imm));
+    if (s.op >= EW_FIRST_UNARY) {
+      words.push_back(Word(s.op, 0, 0, 0, s.imm));
+    } else if (s.op == EW_SELECT) {
+      words.push_back(Word(EW_SELECT, s.asel, s.bsel, s.role, s.imm));
+      if (s.bsel == 0) words.push_back(Word(EW_NOP, 0, 0, 0, s.imm2));
+    } else {
+      words.push_back(Word(s.op, s.asel, 0, s.swap ? 1 : 0, s.imm));
+    }
   }
   if (words.size() > (size_t)EW_MAX_STEPS) {
     cb.Fail("chain of " + std::to_string(words.size()) + " steps exceeds the limit of " + std::to_string(EW_MAX_STEPS));
@@ -444,7 +560,7 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
   for (auto& t : g.inputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
   p->algorithmic_bytes += out.numel() * DTypeBytes(out.dtype);
   LaunchStep st;
-  st.kernel = FindKernel(std::string("ew_chain_") + DTypeKernelName(in_type) + "_" + DTypeKernelName(out.dtype));
+  st.kernel = FindKernel(std::string("ew_chain_") + DTypeKernelName(out.dtype));
   if (!st.kernel) {
     cb.Fail("chain kernel for these dtypes is not in the library");
     return nullptr;
@@ -454,7 +570,7 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
   auto in_arg = [](int i) { ArgSpec a; a.kind = ArgSpec::kInput; a.index = i; return a; };
   auto int_arg = [](int64_t v) { ArgSpec a; a.kind = ArgSpec::kInt; a.ivalue = v; return a; };
   st.args.push_back(in_arg(in0));
-  int64_t meta = 0;
+  int64_t meta = (int64_t)DTypeKernelCode(in_type) << 24;
   ArgSpec aligned;
   aligned.kind   = ArgSpec::kAligned;
   aligned.ivalue = 1;

@@ -26,10 +26,38 @@ __device__ __noinline__ float heavy_unary(int op, float x) {
     case EW_COS: return cosf(x);
     case EW_LOG2: return log2f(x);
     case EW_LOG10: return log10f(x);
+    // The functions below are evaluated in double precision and rounded once: the host library the x86 path calls
+    // is within an ulp of the correctly rounded result, which CUDA's single-precision versions (2-4 ulp) are not.
+    // cinn/backends/llvm/llvm_intrin_rule.h:126-175: tan = sin / cos, sinh / cosh from two exps
+    case EW_TAN: return (float)sin((double)x) / (float)cos((double)x);
+    case EW_SINH: return ((float)exp((double)x) - (float)exp((double)(x * -1.0f))) / 2.0f;
+    case EW_COSH: return ((float)exp((double)x) + (float)exp((double)(x * -1.0f))) / 2.0f;
+    // cinn/optim/map_extern_call.cc:42-74: the host's asinf ... atanhf
+    case EW_ASIN: return (float)asin((double)x);
+    case EW_ACOS: return (float)acos((double)x);
+    case EW_ATAN: return (float)atan((double)x);
+    case EW_ASINH: return (float)asinh((double)x);
+    case EW_ACOSH: return (float)acosh((double)x);
+    case EW_ATANH: return (float)atanh((double)x);
+    // cinn/runtime/cpu/host_intrinsics.cc:216: the double-precision cbrt of the promoted argument
+    case EW_CBRT: return (float)cbrt((double)x);
     default: return x;
   }
 }
 __device__ __noinline__ float heavy_pow(float l, float r) { return powf(l, r); }
+// cinn/runtime/cuda/cinn_cuda_runtime_source.cuh:84-88: the result takes the sign of the divisor
+__device__ __noinline__ float heavy_mod(float l, float r) {
+  float res = fmodf(l, r);
+  if ((res != 0.0f) && ((res < 0.0f) != (r < 0.0f))) res += r;
+  return res;
+}
+// cinn/hlir/pe/broadcast.cc:275-291
+__device__ __noinline__ float heavy_atan2(float a, float b) {
+  const float at = (float)atan((double)(a / b));
+  const float pi = (float)3.14159265358979323846, half_pi = (float)(3.14159265358979323846 / 2);
+  if (b == 0.0f) return a == 0.0f ? 0.0f : (a > 0.0f ? half_pi : -half_pi);
+  return b > 0.0f ? at : (a >= 0.0f ? at + pi : at - pi);
+}
 
 template <int VEC>
 __device__ __forceinline__ void apply_unary(int op, float imm, float (&a)[VEC]) {
@@ -56,15 +84,17 @@ __device__ __forceinline__ void apply_unary(int op, float imm, float (&a)[VEC]) 
     EW_UNARY_CASE(EW_RELU6, x86_min(x86_max(x, 0.0f), imm))
     EW_UNARY_CASE(EW_ROUND_F16, __half2float(__float2half_rn(x)))
     EW_UNARY_CASE(EW_ROUND_BF16, __bfloat162float(__float2bfloat16_rn(x)))
-    case EW_ERF:
-    case EW_SIN:
-    case EW_COS:
-    case EW_LOG2:
-    case EW_LOG10:
+    // cinn/backends/llvm/llvm_intrin_rule.h:78-104 and cinn/lang/builtin.cc:212-259
+    EW_UNARY_CASE(EW_ISNAN, x != x ? 1.0f : 0.0f)
+    EW_UNARY_CASE(EW_ISINF, (fabsf(x) == __int_as_float(0x7f800000) && !(x != x)) ? 1.0f : 0.0f)
+    EW_UNARY_CASE(EW_ISFINITE, (fabsf(x) == __int_as_float(0x7f800000) || x != x) ? 0.0f : 1.0f)
+    EW_UNARY_CASE(EW_LNOT, x == 0.0f ? 1.0f : 0.0f)
+    EW_UNARY_CASE(EW_TO_BOOL, x != 0.0f ? 1.0f : 0.0f)
+    case EW_IDENTITY:
+      break;
+    default:  // the code-heavy functions
 #pragma unroll
       for (int i = 0; i < VEC; ++i) a[i] = heavy_unary(op, a[i]);
-      break;
-    default:
       break;
   }
 #undef EW_UNARY_CASE
@@ -95,6 +125,12 @@ __device__ __forceinline__ void apply_binary(int op, bool swap, const float (&o)
     EW_BINARY_CASE(EW_LT, l < r ? 1.0f : 0.0f)
     EW_BINARY_CASE(EW_GE, l >= r ? 1.0f : 0.0f)
     EW_BINARY_CASE(EW_LE, l <= r ? 1.0f : 0.0f)
+    EW_BINARY_CASE(EW_MOD, heavy_mod(l, r))
+    EW_BINARY_CASE(EW_FLOOR_DIV, floorf(l / r))
+    EW_BINARY_CASE(EW_ATAN2, heavy_atan2(l, r))
+    EW_BINARY_CASE(EW_LAND, (l != 0.0f && r != 0.0f) ? 1.0f : 0.0f)
+    EW_BINARY_CASE(EW_LOR, (l != 0.0f || r != 0.0f) ? 1.0f : 0.0f)
+    EW_BINARY_CASE(EW_LXOR, ((l != 0.0f) != (r != 0.0f)) ? 1.0f : 0.0f)
     default:
       break;
   }
@@ -102,27 +138,55 @@ __device__ __forceinline__ void apply_binary(int op, bool swap, const float (&o)
 }
 
 __device__ __forceinline__ float load_scalar(const void* p, int dtype, long long idx) {
-  if (dtype == 0) return static_cast<const float*>(p)[idx];
-  if (dtype == 1) return __half2float(static_cast<const __half*>(p)[idx]);
-  return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+  switch (dtype) {
+    case EW_F32: return static_cast<const float*>(p)[idx];
+    case EW_F16: return __half2float(static_cast<const __half*>(p)[idx]);
+    case EW_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
+    case EW_BOOL: return static_cast<const uint8_t*>(p)[idx] != 0 ? 1.0f : 0.0f;
+    case EW_I32: return (float)static_cast<const int32_t*>(p)[idx];  // the cast op's own rounding (to nearest even)
+    default: return (float)static_cast<const long long*>(p)[idx];
+  }
 }
 
-// Four consecutive elements starting at idx (idx % 4 == 0, pointer 16-byte aligned for fp32 / 8 for 16-bit).
+// Four consecutive elements starting at idx (idx % 4 == 0, pointer 16-byte aligned).
 __device__ __forceinline__ void load_vec4(const void* p, int dtype, long long idx, bool stream, float (&f)[4]) {
-  if (dtype == 0) {
+  if (dtype == EW_F32) {
     const uint4* q = reinterpret_cast<const uint4*>(static_cast<const float*>(p) + idx);
     unpack4(stream ? __ldcs(q) : __ldg(q), f);
-  } else {
+  } else if (dtype == EW_F16 || dtype == EW_BF16) {
     const uint2* q = reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(p) + idx);
     uint2 u        = stream ? __ldcs(q) : __ldg(q);
-    if (dtype == 1) {
+    if (dtype == EW_F16) {
       unpack_h2(u.x, f[0], f[1]);
       unpack_h2(u.y, f[2], f[3]);
     } else {
       unpack_bf2(u.x, f[0], f[1]);
       unpack_bf2(u.y, f[2], f[3]);
     }
+  } else if (dtype == EW_BOOL) {
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p) + idx);
+    const uint32_t u  = stream ? __ldcs(q) : __ldg(q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = ((u >> (8 * i)) & 0xffu) != 0 ? 1.0f : 0.0f;
+  } else if (dtype == EW_I32) {
+    const int4* q = reinterpret_cast<const int4*>(static_cast<const int32_t*>(p) + idx);
+    const int4 u  = stream ? __ldcs(q) : __ldg(q);
+    f[0] = (float)u.x; f[1] = (float)u.y; f[2] = (float)u.z; f[3] = (float)u.w;
+  } else {
+    const longlong2* q = reinterpret_cast<const longlong2*>(static_cast<const long long*>(p) + idx);
+    const longlong2 u0 = stream ? __ldcs(q) : __ldg(q);
+    const longlong2 u1 = stream ? __ldcs(q + 1) : __ldg(q + 1);
+    f[0] = (float)u0.x; f[1] = (float)u0.y; f[2] = (float)u1.x; f[3] = (float)u1.y;
   }
+}
+
+// float -> integer as the x86 conversion instruction does it (cvttss2si): toward zero; NaN and values out of
+// range give the most negative integer.
+__device__ __forceinline__ int32_t x86_f2i32(float x) {
+  return (x >= -2147483648.0f && x < 2147483648.0f) ? (int32_t)x : (int32_t)0x80000000;
+}
+__device__ __forceinline__ long long x86_f2i64(float x) {
+  return (x >= -9223372036854775808.0f && x < 9223372036854775808.0f) ? (long long)x : (long long)0x8000000000000000ull;
 }
 
 template <typename OutT>
@@ -145,6 +209,15 @@ __device__ __forceinline__ void store_vec4<uint8_t>(uint8_t* p, long long idx, c
                (f[3] != 0.0f ? 1u << 24 : 0u);
   *reinterpret_cast<uint32_t*>(p + idx) = u;
 }
+template <>
+__device__ __forceinline__ void store_vec4<int32_t>(int32_t* p, long long idx, const float (&f)[4]) {
+  __stcs(reinterpret_cast<int4*>(p + idx), make_int4(x86_f2i32(f[0]), x86_f2i32(f[1]), x86_f2i32(f[2]), x86_f2i32(f[3])));
+}
+template <>
+__device__ __forceinline__ void store_vec4<long long>(long long* p, long long idx, const float (&f)[4]) {
+  __stcs(reinterpret_cast<longlong2*>(p + idx), make_longlong2(x86_f2i64(f[0]), x86_f2i64(f[1])));
+  __stcs(reinterpret_cast<longlong2*>(p + idx) + 1, make_longlong2(x86_f2i64(f[2]), x86_f2i64(f[3])));
+}
 template <typename OutT>
 __device__ __forceinline__ void store_one(OutT* p, long long idx, float v) {
   Io<OutT>::store1(p + idx, v);
@@ -152,6 +225,14 @@ __device__ __forceinline__ void store_one(OutT* p, long long idx, float v) {
 template <>
 __device__ __forceinline__ void store_one<uint8_t>(uint8_t* p, long long idx, float v) {
   p[idx] = v != 0.0f ? 1 : 0;
+}
+template <>
+__device__ __forceinline__ void store_one<int32_t>(int32_t* p, long long idx, float v) {
+  p[idx] = x86_f2i32(v);
+}
+template <>
+__device__ __forceinline__ void store_one<long long>(long long* p, long long idx, float v) {
+  p[idx] = x86_f2i64(v);
 }
 
 struct SideSpec {
@@ -190,7 +271,8 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
     const int op       = (int)(st & 0xff);
     const int asel     = (int)((st >> 8) & 0xff);
     const int bsel     = (int)((st >> 16) & 0xff);
-    const bool swap    = ((st >> 24) & 1) != 0;
+    const int role     = (int)((st >> 24) & 3);
+    const bool swap    = role != 0;
     const float imm    = __uint_as_float((uint32_t)(st >> 32));
     if (op == EW_NOP) continue;
     if (op >= EW_FIRST_UNARY) {
@@ -229,6 +311,18 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
         acc[i]        = fmaf(acc[i], o[i], b);
       }
       if (bsel == 0) ++k;
+    } else if (op == EW_SELECT) {
+      // cinn/hlir/pe/elementwise.cc Select: cond ? true_value : false_value; the chain value is one of the three.
+      const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float b = bsel == 1 ? s1[i] : (bsel == 2 ? s2[i] : (bsel == 3 ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        const float c = role == 0 ? acc[i] : o[i];
+        const float t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
+        const float f = role == 2 ? acc[i] : b;
+        acc[i]        = c != 0.0f ? t : f;
+      }
+      if (bsel == 0) ++k;
     } else if (op == EW_SCALE_PRE) {
       // imm * (acc + imm2): scale with bias_after_scale = false
       const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
@@ -241,25 +335,10 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
   }
 }
 
-template <typename InT>
-struct DTypeCode;
-template <>
-struct DTypeCode<float> {
-  static constexpr int v = 0;
-};
-template <>
-struct DTypeCode<__half> {
-  static constexpr int v = 1;
-};
-template <>
-struct DTypeCode<__nv_bfloat16> {
-  static constexpr int v = 2;
-};
-
-// meta: bits 0-3 dtype of side 1, 4-7 mode of side 1, 8-11 / 12-15 side 2, 16-19 / 20-23 side 3.
-template <typename InT, typename OutT>
+// meta: bits 0-3 dtype of side 1, 4-7 mode of side 1, 8-11 / 12-15 side 2, 16-19 / 20-23 side 3, 24-27 dtype of in0.
+template <typename OutT>
 __global__ void __launch_bounds__(256)
-    k_ew_chain(const InT* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
+    k_ew_chain(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
                const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
                long long mid1, long long inner1, long long mid2, long long inner2, long long mid3, long long inner3,
                long long nsteps_ll, long long t0, long long t1, long long t2, long long t3, long long t4,
@@ -267,6 +346,7 @@ __global__ void __launch_bounds__(256)
                long long t12, long long t13, long long t14, long long t15) {
   const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
   const int nsteps = (int)nsteps_ll;
+  const int in_type = (int)((meta >> 24) & 15);
   const SideSpec sd1 = {p1, (int)(meta & 15), (int)((meta >> 4) & 15), mid1, inner1};
   const SideSpec sd2 = {p2, (int)((meta >> 8) & 15), (int)((meta >> 12) & 15), mid2, inner2};
   const SideSpec sd3 = {p3, (int)((meta >> 16) & 15), (int)((meta >> 20) & 15), mid3, inner3};
@@ -282,7 +362,7 @@ __global__ void __launch_bounds__(256)
       float acc[8], s1[8], s2[8], s3[8];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
-        load_vec4(in0, DTypeCode<InT>::v, (v + j * stride) << 2, true, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
+        load_vec4(in0, in_type, (v + j * stride) << 2, true, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const long long i0 = (v + j * stride) << 2;
@@ -298,7 +378,7 @@ __global__ void __launch_bounds__(256)
     for (; v < nvec; v += stride) {
       const long long i0 = v << 2;
       float acc[4], s1[4], s2[4], s3[4];
-      load_vec4(in0, DTypeCode<InT>::v, i0, true, acc);
+      load_vec4(in0, in_type, i0, true, acc);
       if (sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
       if (sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
       if (sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
@@ -309,7 +389,7 @@ __global__ void __launch_bounds__(256)
   }
   for (long long i = done + tid; i < n; i += stride) {
     float acc[1], s1[1], s2[1], s3[1];
-    acc[0] = load_scalar(in0, DTypeCode<InT>::v, i);
+    acc[0] = load_scalar(in0, in_type, i);
     if (sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
     if (sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
     if (sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
@@ -320,16 +400,12 @@ __global__ void __launch_bounds__(256)
 
 }  // namespace
 
-#define REG_CHAIN(INNAME, InT, OUTNAME, OutT) \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" INNAME "_" OUTNAME, 31, 256, k_ew_chain<InT, OutT>)
-#define REG_CHAIN_IN(INNAME, InT)            \
-  REG_CHAIN(INNAME, InT, "f32", float);      \
-  REG_CHAIN(INNAME, InT, "f16", __half);     \
-  REG_CHAIN(INNAME, InT, "bf16", __nv_bfloat16); \
-  REG_CHAIN(INNAME, InT, "bool", uint8_t)
-
-REG_CHAIN_IN("f32", float);
-REG_CHAIN_IN("f16", __half);
-REG_CHAIN_IN("bf16", __nv_bfloat16);
+#define REG_CHAIN(OUTNAME, OutT) CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME, 31, 256, k_ew_chain<OutT>)
+REG_CHAIN("f32", float);
+REG_CHAIN("f16", __half);
+REG_CHAIN("bf16", __nv_bfloat16);
+REG_CHAIN("bool", uint8_t);
+REG_CHAIN("i32", int32_t);
+REG_CHAIN("i64", long long);
 
 }  // namespace cinn_b200

@@ -2,8 +2,11 @@
 //
 // A step is one 64-bit word: bits 0-7 opcode, 8-15 operand A selector (0 = the immediate, 1..3 = side input,
 // 4 = the chain value itself),
-// 16-23 operand B selector (EW_FMA only: 0 = the immediate of the NEXT word, which is then skipped),
-// bit 24 "swap" (the side operand is the LEFT operand of a binary op), bits 32-63 an fp32 immediate.
+// 16-23 operand B selector (EW_FMA and EW_SELECT only: 0 = the immediate of the NEXT word, which is then skipped),
+// bits 24-25 "swap" for a binary op (1: the side operand is the LEFT operand) or, for EW_SELECT, the role of the
+// chain value (0: the condition, A = value if true, B = value if false; 1: the value if true, A = condition,
+// B = value if false; 2: the value if false, A = condition, B = value if true), bits 32-63 an fp32 immediate.
+// Values of type bool travel as 0.0f / 1.0f.
 #pragma once
 
 namespace cinn_b200 {
@@ -15,14 +18,22 @@ enum EwOp {
   // binary: acc = acc (op) operand, or operand (op) acc when swapped
   EW_ADD = 1, EW_SUB, EW_MUL, EW_DIV, EW_MAX, EW_MIN, EW_POW,
   EW_EQ, EW_NE, EW_GT, EW_LT, EW_GE, EW_LE,
+  EW_MOD = 14, EW_FLOOR_DIV, EW_ATAN2, EW_LAND, EW_LOR, EW_LXOR,
   EW_FMA = 20,        // acc = fma(acc, A, B)
   EW_SCALE_PRE = 21,  // acc = imm * (acc + imm_next)
+  EW_SELECT = 22,     // acc = cond ? t : f, see the role bits above
   // unary
   EW_FIRST_UNARY = 32,
   EW_EXP = 32, EW_TANH, EW_SIGMOID, EW_RSQRT, EW_SQRT, EW_RELU, EW_NEG, EW_ABS, EW_LOG, EW_FLOOR, EW_CEIL, EW_ERF,
   EW_SIN, EW_COS, EW_RECIP, EW_ROUND, EW_TRUNC, EW_SIGN, EW_RELU6, EW_LOG2, EW_LOG10,
-  EW_ROUND_F16, EW_ROUND_BF16, EW_IDENTITY
+  EW_ROUND_F16, EW_ROUND_BF16, EW_IDENTITY,
+  EW_TAN, EW_SINH, EW_COSH, EW_ASIN, EW_ACOS, EW_ATAN, EW_ASINH, EW_ACOSH, EW_ATANH, EW_CBRT,
+  EW_ISNAN, EW_ISINF, EW_ISFINITE, EW_LNOT,
+  EW_TO_BOOL  // x != 0 ? 1 : 0 (cast to bool in the middle of a chain)
 };
+
+// Storage types of the chain kernel's operands (runtime codes; the output type is a template parameter).
+enum EwDType { EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5 };
 
 // How a side input is addressed for the flat output index i: value = side[(i / inner) % mid].
 enum EwSideMode {

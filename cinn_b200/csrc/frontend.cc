@@ -24,12 +24,22 @@ namespace {
 const std::set<std::string>& UnaryOps() {
   static const std::set<std::string> s = {
       "sqrt", "tanh", "sigmoid", "identity", "exp", "erf", "rsqrt", "log", "log2", "log10", "floor", "ceil", "round",
-      "trunc", "sin", "cos", "negative", "sign", "abs", "relu", "relu6", "reciprocal", "gelu"};
+      "trunc", "sin", "cos", "negative", "sign", "abs", "relu", "relu6", "reciprocal", "gelu",
+      "tan", "sinh", "cosh", "asin", "acos", "atan", "asinh", "acosh", "atanh", "cbrt",
+      "isnan", "isinf", "isfinite", "logical_not", "bitwise_not", "clz", "popc"};
+  return s;
+}
+// Unary ops whose result is bool whatever the operand type (cinn/hlir/op/elementwise.cc: isnan, isfinite, isinf,
+// logical_not).
+const std::set<std::string>& PredicateOps() {
+  static const std::set<std::string> s = {"isnan", "isinf", "isfinite", "logical_not"};
   return s;
 }
 const std::set<std::string>& BinaryOps() {
   static const std::set<std::string> s = {"elementwise_add", "elementwise_mul", "subtract", "divide", "max", "min",
-                                          "pow"};
+                                          "pow", "mod", "remainder", "floor_divide", "atan2", "logical_and",
+                                          "logical_or", "logical_xor", "bitwise_and", "bitwise_or", "bitwise_xor",
+                                          "left_shift", "right_shift", "logical_right_shift"};
   return s;
 }
 const std::set<std::string>& CompareOps() {
@@ -167,8 +177,12 @@ int NetBuilder::AddOp(const std::string& op, const std::vector<int>& inputs,
   Variable out;
   if (UnaryOps().count(op)) {
     if (!need(1)) return fail("takes 1 input");
-    out.dtype = in(0).dtype;
+    out.dtype = PredicateOps().count(op) ? DType::kBool : in(0).dtype;
     out.shape = in(0).shape;
+    if (op == "logical_not" && in(0).dtype != DType::kBool) return fail("operand must be bool");
+    if ((op == "bitwise_not" || op == "clz" || op == "popc") && in(0).dtype != DType::kInt32 && in(0).dtype != DType::kInt64 &&
+        !(op == "bitwise_not" && in(0).dtype == DType::kBool))
+      return fail("operand must be an integer");
   } else if (BinaryOps().count(op) || CompareOps().count(op)) {
     if (!need(2)) return fail("takes 2 inputs");
     if (in(0).dtype != in(1).dtype) return fail("operand dtypes differ");
@@ -177,6 +191,8 @@ int NetBuilder::AddOp(const std::string& op, const std::vector<int>& inputs,
     std::string e;
     if (!BroadcastShape(in(0).shape, in(1).shape, axis, &out.shape, &e)) return fail(e);
     out.dtype = CompareOps().count(op) ? DType::kBool : in(0).dtype;
+    if (op.rfind("logical_", 0) == 0 && op != "logical_right_shift" && in(0).dtype != DType::kBool)
+      return fail("operands must be bool");
   } else if (op == "scale") {
     if (!need(1)) return fail("takes 1 input");
     if (!attrs.count("scale")) attrs["scale"] = "1.0";

@@ -100,7 +100,9 @@ class NetBuilder:
         return f
 
     for _n in ["sqrt", "tanh", "sigmoid", "identity", "exp", "erf", "rsqrt", "log", "log2", "log10", "floor", "ceil",
-               "round", "trunc", "sin", "cos", "negative", "sign", "abs", "reciprocal"]:
+               "round", "trunc", "sin", "cos", "negative", "sign", "abs", "reciprocal", "tan", "sinh", "cosh", "asin",
+               "acos", "atan", "asinh", "acosh", "atanh", "cbrt", "isnan", "isinf", "isfinite", "logical_not",
+               "bitwise_not", "clz", "popc"]:
         locals()[_n] = _unary(_n)
     del _n, _unary
 
@@ -135,6 +137,18 @@ class NetBuilder:
 
     def pow(self, x, y, axis=-1):
         return self._op("pow", [x, y], axis=axis)
+
+    def _binary(name):  # noqa: N805
+        def f(self, x, y, axis=-1):
+            return self._op(name, [x, y], axis=axis)
+        f.__name__ = name
+        return f
+
+    for _n in ["mod", "remainder", "floor_divide", "atan2", "logical_and", "logical_or", "logical_xor", "bitwise_and",
+               "bitwise_or", "bitwise_xor", "left_shift", "right_shift", "logical_right_shift", "equal", "not_equal",
+               "greater_than", "less_than", "greater_equal", "less_equal"]:
+        locals()[_n] = _binary(_n)
+    del _n, _binary
 
     # ---- others ------------------------------------------------------------------------------------
     def scale(self, x, scale=1.0, bias=0.0, bias_after_scale=True):

@@ -11,11 +11,18 @@ import numpy as np
 from . import x86_oracle as orc
 
 UNARY = {"exp", "tanh", "sigmoid", "rsqrt", "sqrt", "relu", "negative", "abs", "identity", "log", "floor", "ceil",
-         "erf", "sin", "cos", "reciprocal", "round", "trunc", "log2", "log10", "sign"}
+         "erf", "sin", "cos", "reciprocal", "round", "trunc", "log2", "log10", "sign", "tan", "sinh", "cosh", "asin",
+         "acos", "atan", "asinh", "acosh", "atanh", "cbrt", "isnan", "isinf", "isfinite", "logical_not"}
+PREDICATES = {"isnan", "isinf", "isfinite", "logical_not"}
 BINARY = {"elementwise_add": "add", "subtract": "subtract", "elementwise_mul": "multiply", "divide": "divide",
-          "max": "max", "min": "min", "pow": "pow"}
+          "max": "max", "min": "min", "pow": "pow", "equal": "equal", "not_equal": "not_equal",
+          "greater_than": "greater_than", "less_than": "less_than", "greater_equal": "greater_equal",
+          "less_equal": "less_equal", "mod": "mod", "remainder": "mod", "floor_divide": "floor_divide",
+          "atan2": "atan2", "logical_and": "logical_and", "logical_or": "logical_or", "logical_xor": "logical_xor"}
+BOOL_RESULT = {"equal", "not_equal", "greater_than", "less_than", "greater_equal", "less_equal", "logical_and",
+               "logical_or", "logical_xor"}
 REDUCE = {"reduce_sum": "sum", "reduce_prod": "prod", "reduce_max": "max", "reduce_min": "min"}
-NP = {"float32": np.float32, "float16": np.float16}
+NP = {"float32": np.float32, "float16": np.float16, "bool": np.bool_, "int32": np.int32, "int64": np.int64}
 
 
 def parse(desc):
@@ -49,11 +56,24 @@ def _aligned(a, out_shape, axis):
 
 
 def _f32(v):
-    return orc.cast_f16_f32(v) if v.dtype == np.float16 else v
+    """The value as the fp32 numbers the arithmetic sees: float16 widened, bool as 0/1, integers converted the way
+    the cast op does (round to nearest even)."""
+    if v.dtype == np.float16:
+        return orc.cast_f16_f32(v)
+    if v.dtype == np.float32:
+        return v
+    return np.ascontiguousarray(v.astype(np.float32))
 
 
 def _store(v32, dtype):
-    return orc.cast_f32_f16(v32) if dtype == np.float16 else v32
+    dtype = np.dtype(dtype)
+    if dtype == np.float16:
+        return orc.cast_f32_f16(v32)
+    if dtype == np.bool_:
+        return v32 != 0
+    if dtype in (np.dtype(np.int32), np.dtype(np.int64)):
+        return orc.cast_f32_int(v32, dtype)
+    return v32
 
 
 def evaluate(desc, inputs):
@@ -89,7 +109,7 @@ def evaluate(desc, inputs):
         elif t == "cast":
             x = vals[ins[0]]
             to = NP[at["dtype"]]
-            out = x if x.dtype == to else (orc.cast_f32_f16(x) if to == np.float16 else orc.cast_f16_f32(x))
+            out = x if x.dtype == to else _store(_f32(x), to)
         elif t == "broadcast_to":
             x = vals[ins[0]]
             shape = tuple(int(d) for d in at["out_shape"].split(","))
@@ -104,7 +124,10 @@ def evaluate(desc, inputs):
             out = _store(orc.scale(_f32(x), float(at.get("scale", 1)), float(at.get("bias", 0)), after), x.dtype)
         elif t in UNARY:
             x = vals[ins[0]]
-            out = _store(orc.unary(t, _f32(x)), x.dtype)
+            out = _store(orc.unary(t, _f32(x)), np.bool_ if t in PREDICATES else x.dtype)
+        elif t == "select":
+            c, tv, fv = (vals[i] for i in ins)
+            out = np.where(c, tv, fv)
         elif t == "relu6":
             x = vals[ins[0]]
             thr = np.float32(float(at.get("threshold", 6)))
@@ -116,7 +139,7 @@ def evaluate(desc, inputs):
             shape = np.broadcast_shapes(big.shape, _aligned(small, big.shape, axis).shape)
             aa = a if a is big else _aligned(a, shape, axis)
             bb = b if b is big else _aligned(b, shape, axis)
-            dt = a.dtype
+            dt = np.dtype(np.bool_) if t in BOOL_RESULT else a.dtype
             done = False
             if t == "elementwise_add" and dt == np.float32:
                 # lower_intrin.cc:45-50: the right operand is tried first

@@ -14,8 +14,11 @@ LIB_PATH = os.path.join(HERE, "libcinn_x86_oracle.so")
 
 UNARY = {name: i for i, name in enumerate(
     ["exp", "tanh", "sigmoid", "rsqrt", "sqrt", "relu", "negative", "abs", "identity", "log", "floor", "ceil",
-     "erf", "sin", "cos", "reciprocal", "round", "trunc", "log2", "log10", "sign"])}
-BINARY = {name: i for i, name in enumerate(["add", "subtract", "multiply", "divide", "max", "min", "pow"])}
+     "erf", "sin", "cos", "reciprocal", "round", "trunc", "log2", "log10", "sign", "tan", "sinh", "cosh", "asin",
+     "acos", "atan", "asinh", "acosh", "atanh", "cbrt", "isnan", "isinf", "isfinite", "logical_not"])}
+BINARY = {name: i for i, name in enumerate(
+    ["add", "subtract", "multiply", "divide", "max", "min", "pow", "equal", "not_equal", "greater_than", "less_than",
+     "greater_equal", "less_equal", "mod", "floor_divide", "atan2", "logical_and", "logical_or", "logical_xor"])}
 REDUCE = {"sum": 0, "prod": 1, "max": 2, "min": 3}
 
 _lib = None
@@ -113,6 +116,15 @@ def scale(x, s, b, bias_after_scale=True):
     y = np.empty_like(x)
     lib().orc_scale_f32(_p(x), ctypes.c_float(s), ctypes.c_float(b), ctypes.c_int(int(bias_after_scale)), _p(y),
                         _i64(x.size))
+    return y
+
+
+def cast_f32_int(x, dtype):
+    """float32 -> int32 / int64 the way the x86 conversion instruction does it (toward zero)."""
+    x = _f32(x)
+    y = np.empty(x.shape, dtype)
+    fn = lib().orc_cast_f32_i32 if np.dtype(dtype) == np.int32 else lib().orc_cast_f32_i64
+    fn(_p(x), _p(y), _i64(x.size))
     return y
 
 

@@ -136,7 +136,7 @@ def test_elementwise_producer_folds_into_reduction():
     x = b.create_input(common.Float(32), (64, 4096), "X")
     b.sqrt(b.divide(b.reduce_sum(b.multiply(x, b.identity(x)), [1]), b.fill_constant([64], 4096.0)))
     c = plan(b)
-    assert [p for _, p in c.groups()] == ["row_reduce row_reduce_cta_sumsq_f32", "ew_chain ew_chain_f32_f32"]
+    assert [p for _, p in c.groups()] == ["row_reduce row_reduce_cta_sumsq_f32", "ew_chain ew_chain_f32"]
 
 
 def test_value_used_twice_is_materialised_once():

@@ -255,3 +255,124 @@ def test_reductions_with_a_folded_producer(oracle, shape, axis):
         else:
             scale = float(np.abs(w).max())
             assert np.allclose(g, w, rtol=1e-5, atol=2e-7 * r * scale / max(np.sqrt(r), 1)), name
+
+
+# ---- the remaining elementwise ops of the registry: trigonometric / hyperbolic, predicates, logical, select, casts ----
+
+MORE_UNARY_CASES = [("tan", (-1.4, 1.4), 2), ("sinh", (1.0, 8.0), 2), ("cosh", (-8.0, 8.0), 2), ("asin", (-1, 1), 2),
+                    ("acos", (-1, 1), 2), ("atan", (-20, 20), 2), ("asinh", (-50, 50), 2), ("acosh", (1, 50), 2),
+                    ("atanh", (-0.99, 0.99), 2), ("cbrt", (-50, 50), 1)]
+
+
+@pytest.mark.parametrize("op,rng_range,ulps", MORE_UNARY_CASES)
+def test_more_unary_op_groups(oracle, op, rng_range, ulps):
+    b = NetBuilder("u_" + op)
+    x = b.create_input(common.Float(32), (257, 129), "X")
+    y = getattr(b, op)(x)
+    X = np.random.default_rng(21).uniform(rng_range[0], rng_range[1], (257, 129)).astype(np.float32)
+    comp, out = run_program(b, {"X": X}, [y])
+    d = oracle.max_ulp(out[str(y)], oracle.unary(op, X))
+    print("%s: max ulp distance to the x86 oracle %d" % (op, d))
+    assert d <= ulps, (op, d)
+
+
+def test_predicates_on_special_values(oracle):
+    X = np.random.default_rng(22).standard_normal((33, 64)).astype(np.float32)
+    X[::3, 1] = np.nan
+    X[1::5, 2] = np.inf
+    X[2::7, 3] = -np.inf
+    for op, want in (("isnan", np.isnan(X)), ("isinf", np.isinf(X)), ("isfinite", np.isfinite(X))):
+        b = NetBuilder("p_" + op)
+        x = b.create_input(common.Float(32), X.shape, "X")
+        y = getattr(b, op)(x)
+        comp, out = run_program(b, {"X": X}, [y])
+        assert out[str(y)].dtype == np.bool_ and np.array_equal(out[str(y)], want), op
+        assert np.array_equal(oracle_program(comp, {"X": X})[str(y)], want), op
+
+
+@pytest.mark.parametrize("op", ["mod", "remainder", "floor_divide", "atan2"])
+def test_more_binary_ops(oracle, op):
+    b = NetBuilder("b_" + op)
+    x = b.create_input(common.Float(32), (65, 48), "X")
+    y = b.create_input(common.Float(32), (48,), "Y")
+    z = getattr(b, op)(x, y)
+    rng = np.random.default_rng(23)
+    X = (rng.standard_normal((65, 48)) * 5).astype(np.float32)
+    Y = (rng.standard_normal(48) * 2).astype(np.float32)
+    Y[3] = 0.0
+    X[:, 5] = 0.0
+    comp, out = run_program(b, {"X": X, "Y": Y}, [z])
+    ref = oracle_program(comp, {"X": X, "Y": Y})[str(z)]
+    got = out[str(z)]
+    both_nan = np.isnan(got) & np.isnan(ref)
+    d = oracle.max_ulp(np.where(both_nan, 0, got).astype(np.float32), np.where(both_nan, 0, ref).astype(np.float32))
+    print("%s: max ulp %d" % (op, d))
+    assert d <= (2 if op == "atan2" else 0), (op, d)
+
+
+def test_logical_ops_and_not(oracle):
+    rng = np.random.default_rng(24)
+    P, Q = rng.random((40, 36)) > 0.5, rng.random((40, 36)) > 0.5
+    for op, want in (("logical_and", P & Q), ("logical_or", P | Q), ("logical_xor", P ^ Q)):
+        b = NetBuilder(op)
+        p = b.create_input(common.Bool(), P.shape, "P")
+        q = b.create_input(common.Bool(), Q.shape, "Q")
+        y = b.logical_not(getattr(b, op)(p, q))
+        comp, out = run_program(b, {"P": P, "Q": Q}, [y])
+        assert out[str(y)].dtype == np.bool_ and np.array_equal(out[str(y)], ~want), op
+
+
+def test_select_with_mask_input_and_with_computed_condition(oracle):
+    rng = np.random.default_rng(25)
+    X = rng.standard_normal((31, 100)).astype(np.float32)
+    Y = rng.standard_normal((31, 100)).astype(np.float32)
+    M = rng.random((31, 100)) > 0.3
+    # (1) mask as an input, both values computed from inputs: where(M, exp(X), Y)
+    b = NetBuilder("sel1")
+    x = b.create_input(common.Float(32), X.shape, "X")
+    y = b.create_input(common.Float(32), Y.shape, "Y")
+    m = b.create_input(common.Bool(), M.shape, "M")
+    z = b.select(m, b.exp(x), y)
+    comp, out = run_program(b, {"X": X, "Y": Y, "M": M}, [z])
+    assert len(comp.groups()) == 1, comp.groups()
+    ref = oracle_program(comp, {"X": X, "Y": Y, "M": M})[str(z)]
+    assert oracle.max_ulp(out[str(z)], ref) <= 2
+    # (2) leaky relu written with a comparison: where(X > 0, X, 0.1 * X) (a tree: cut into groups, same values)
+    b = NetBuilder("sel2")
+    x = b.create_input(common.Float(32), X.shape, "X")
+    z = b.select(b.greater_than(x, b.fill_constant(list(X.shape), 0.0)), x, b.scale(x, 0.1))
+    comp, out = run_program(b, {"X": X}, [z])
+    ref = oracle_program(comp, {"X": X})[str(z)]
+    assert np.array_equal(out[str(z)], ref)
+    assert np.array_equal(ref, np.where(X > 0, X, np.float32(0.1) * X))
+    # (3) the comparison feeds arithmetic: relu as x * cast(x > 0)
+    b = NetBuilder("sel3")
+    x = b.create_input(common.Float(32), X.shape, "X")
+    z = b.multiply(b.cast(b.greater_than(x, b.fill_constant(list(X.shape), 0.0)), "float32"), x)
+    comp, out = run_program(b, {"X": X}, [z])
+    assert np.array_equal(out[str(z)], np.where(X > 0, X, X * 0).astype(np.float32))
+
+
+def test_casts_to_and_from_integers_and_bool(oracle):
+    rng = np.random.default_rng(26)
+    X = (rng.standard_normal((29, 52)) * 1000).astype(np.float32)
+    X[0, :6] = [np.nan, np.inf, -np.inf, 3e9, -3e9, 2147483520.0]
+    for to, npt in (("int32", np.int32), ("int64", np.int64)):
+        b = NetBuilder("f2" + to)
+        x = b.create_input(common.Float(32), X.shape, "X")
+        y = b.cast(b.scale(x, 1.5, 0.25), to)
+        comp, out = run_program(b, {"X": X}, [y])
+        ref = oracle_program(comp, {"X": X})[str(y)]
+        assert out[str(y)].dtype == npt and np.array_equal(out[str(y)], ref), to
+    I = rng.integers(-2 ** 31, 2 ** 31 - 1, (29, 52), dtype=np.int64)
+    for frm, arr in (("int32", I.astype(np.int32)), ("int64", I * 1025)):
+        b = NetBuilder(frm + "2f")
+        x = b.create_input(common.Int(int(frm[3:])), arr.shape, "X")
+        y = b.abs(b.cast(x, "float32"))
+        comp, out = run_program(b, {"X": arr}, [y])
+        assert np.array_equal(out[str(y)], np.abs(arr.astype(np.float32))), frm
+    b = NetBuilder("f2b")
+    x = b.create_input(common.Float(32), X.shape, "X")
+    y = b.cast(b.relu(x), "bool")
+    comp, out = run_program(b, {"X": X}, [y])
+    assert out[str(y)].dtype == np.bool_ and np.array_equal(out[str(y)], np.where(X > 0, X, 0) != 0)
