@@ -18,6 +18,7 @@ LIB_PATH = os.path.join(HERE, "libcinn_b200.so")
 SOURCES = [
     "ew_kernels.cu",
     "reduce_kernels.cu",
+    "reduce_generic.cu",
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
     "ew_chain.cu",

@@ -48,7 +48,8 @@ const std::set<std::string>& CompareOps() {
   return s;
 }
 const std::set<std::string>& ReduceOps() {
-  static const std::set<std::string> s = {"reduce_sum", "reduce_prod", "reduce_max", "reduce_min"};
+  static const std::set<std::string> s = {"reduce_sum", "reduce_prod", "reduce_max", "reduce_min", "reduce_all",
+                                          "reduce_any"};
   return s;
 }
 
@@ -261,6 +262,7 @@ int NetBuilder::AddOp(const std::string& op, const std::vector<int>& inputs,
     }
     if (out.shape.empty()) out.shape.push_back(1);
     out.dtype = in(0).dtype;
+    if ((op == "reduce_all" || op == "reduce_any") && in(0).dtype != DType::kBool) return fail("operand must be bool");
   } else if (op == "softmax") {
     if (!need(1)) return fail("takes 1 input");
     if (!attrs.count("axis")) attrs["axis"] = "-1";

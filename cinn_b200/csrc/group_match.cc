@@ -455,12 +455,10 @@ struct Matcher {
         {"reduce_sum(elementwise_mul(identity(%0),%0))", "sumsq"}, {"reduce_sum(abs(%0))", "sumabs"},
         {"reduce_sum(exp(%0))", "sumexp"}, {"reduce_max(abs(%0))", "maxabs"}};
     auto it = kinds.find(expr);
-    if (it == kinds.end()) return nullptr;
+    const bool all_any = expr == "reduce_all(%0)" || expr == "reduce_any(%0)";
+    if (it == kinds.end() && !all_any) return nullptr;
     const auto &x = g.inputs[0], &o = g.outputs[0];
-    if (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32) {
-      Fail("reductions are prebuilt for float32 only");
-      return nullptr;
-    }
+    if (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32 || all_any) return MatchGenericReduce(expr);
     const OpDesc* op = Producer(o.name);
     int64_t outer, r, inner;
     if (!ReduceView(x.shape, AttrList(*op, "dim"), &outer, &r, &inner)) {
@@ -474,6 +472,89 @@ struct Matcher {
     auto p      = NewPlan(inner == 1 ? "row_reduce" : "col_reduce");
     p->elements = x.numel();
     if (!PlanReduce(p.get(), it->second, outer, r, inner, In(0), Out(0), {0})) return nullptr;
+    return p;
+  }
+
+  // Reductions of the other element types (reduce_generic.cu): float16 / bfloat16 / float64 / int32 / int64 with
+  // sum, prod, max, min; bool with all, any (cinn/hlir/op/reduction.cc:477-505).
+  std::unique_ptr<CompiledGroup> MatchGenericReduce(const std::string& expr) {
+    static const std::map<std::string, const char*> kinds = {
+        {"reduce_sum(%0)", "sum"}, {"reduce_prod(%0)", "prod"}, {"reduce_max(%0)", "max"},
+        {"reduce_min(%0)", "min"}, {"reduce_all(%0)", "all"},   {"reduce_any(%0)", "any"}};
+    auto it = kinds.find(expr);
+    const auto &x = g.inputs[0], &o = g.outputs[0];
+    if (it == kinds.end()) {
+      Fail("reductions with a folded producer are prebuilt for float32 only");
+      return nullptr;
+    }
+    const char* tname = nullptr;
+    switch (x.dtype) {
+      case DType::kFloat16: tname = "f16"; break;
+      case DType::kBFloat16: tname = "bf16"; break;
+      case DType::kFloat64: tname = "f64"; break;
+      case DType::kInt32: tname = "i32"; break;
+      case DType::kInt64: tname = "i64"; break;
+      case DType::kBool: tname = "bool"; break;
+      default: break;
+    }
+    const bool logical = std::string(it->second) == "all" || std::string(it->second) == "any";
+    if (!tname || o.dtype != x.dtype || logical != (x.dtype == DType::kBool)) {
+      Fail(std::string("no prebuilt ") + it->second + " reduction from " + DTypeName(x.dtype) + " to " + DTypeName(o.dtype));
+      return nullptr;
+    }
+    const OpDesc* op = Producer(o.name);
+    int64_t outer, r, inner;
+    if (!ReduceView(x.shape, AttrList(*op, "dim"), &outer, &r, &inner)) {
+      Fail("reduce over non-adjacent axes has no prebuilt kernel");
+      return nullptr;
+    }
+    if (o.numel() != outer * inner) {
+      Fail("reduce output has " + std::to_string(o.numel()) + " elements, expected " + std::to_string(outer * inner));
+      return nullptr;
+    }
+    const int64_t esize = DTypeBytes(x.dtype), V = 16 / esize;
+    const int sms       = dev.sm_count;
+    const std::string suffix = std::string(it->second) + "_" + tname;
+    auto p      = NewPlan(inner == 1 ? "row_reduce" : "col_reduce");
+    p->elements = x.numel();
+    auto row_step = [&](ArgSpec src, ArgSpec dst, int64_t rows, int64_t len, std::vector<int> align_in) -> bool {
+      LaunchStep s;
+      if (!Kernel(&s, "reduce_generic_row_" + suffix)) return false;
+      const int64_t group = len * esize > 8192 ? 256 : 32;
+      s.block[0] = 256;
+      s.grid[0]  = (unsigned)std::max<int64_t>(
+          1, group == 32 ? std::min<int64_t>(CeilDiv(rows, 8), (int64_t)sms * 32) : std::min<int64_t>(rows, (int64_t)sms * 16));
+      ArgSpec al = Aligned(len % V == 0, align_in, {});
+      s.args     = {src, dst, I(rows), I(len), I(group), al};
+      p->steps.push_back(s);
+      return true;
+    };
+    if (inner == 1) {
+      // Few very long rows: cut each row into S equal segments (partials in scratch), then fold the S partials.
+      int64_t S = 1;
+      if (outer < (int64_t)sms * 2 && r >= 65536) {
+        while (S < 1024 && r % (S * 2) == 0 && r / (S * 2) >= 4096 && outer * S < (int64_t)sms * 8) S *= 2;
+      }
+      if (S > 1) {
+        const int64_t off = p->scratch_bytes;
+        p->scratch_bytes += (size_t)RoundUp(outer * S * esize, 256);
+        if (!row_step(In(0), Scratch(off), outer * S, r / S, {0})) return nullptr;
+        if (!row_step(Scratch(off), Out(0), outer, S, {})) return nullptr;
+      } else if (!row_step(In(0), Out(0), outer, r, {0})) {
+        return nullptr;
+      }
+      return p;
+    }
+    LaunchStep s;
+    if (!Kernel(&s, "reduce_generic_col_" + suffix)) return nullptr;
+    const bool vec     = inner % V == 0;
+    const int64_t cols = vec ? inner / V : inner;
+    s.block[0] = cols >= 256 ? 256 : (cols >= 128 ? 128 : 64);
+    s.grid[0]  = (unsigned)std::max<int64_t>(1, vec ? CeilDiv(cols, s.block[0]) : std::min<int64_t>(CeilDiv(cols, s.block[0]), (int64_t)sms * 8));
+    s.grid[1]  = (unsigned)std::min<int64_t>(outer, 65535);
+    ArgSpec al = Aligned(vec, {0}, {0});
+    s.args     = {In(0), Out(0), I(outer), I(r), I(inner), al};
+    p->steps.push_back(s);
     return p;
   }
 

@@ -181,6 +181,12 @@ class NetBuilder:
     def reduce_min(self, x, dim=(), keep_dim=False):
         return self._op("reduce_min", [x], dim=list(dim) or None, keep_dim=keep_dim)
 
+    def reduce_all(self, x, dim=(), keep_dim=False):
+        return self._op("reduce_all", [x], dim=list(dim) or None, keep_dim=keep_dim)
+
+    def reduce_any(self, x, dim=(), keep_dim=False):
+        return self._op("reduce_any", [x], dim=list(dim) or None, keep_dim=keep_dim)
+
     def softmax(self, x, axes=(-1,), mode="fast", data_format="AnyLayout"):
         if len(axes) != 1:
             raise ValueError("softmax over several axes has no prebuilt kernel")

@@ -21,8 +21,10 @@ BINARY = {"elementwise_add": "add", "subtract": "subtract", "elementwise_mul": "
           "atan2": "atan2", "logical_and": "logical_and", "logical_or": "logical_or", "logical_xor": "logical_xor"}
 BOOL_RESULT = {"equal", "not_equal", "greater_than", "less_than", "greater_equal", "less_equal", "logical_and",
                "logical_or", "logical_xor"}
-REDUCE = {"reduce_sum": "sum", "reduce_prod": "prod", "reduce_max": "max", "reduce_min": "min"}
-NP = {"float32": np.float32, "float16": np.float16, "bool": np.bool_, "int32": np.int32, "int64": np.int64}
+REDUCE = {"reduce_sum": "sum", "reduce_prod": "prod", "reduce_max": "max", "reduce_min": "min", "reduce_all": "all",
+          "reduce_any": "any"}
+NP = {"float32": np.float32, "float16": np.float16, "bool": np.bool_, "int32": np.int32, "int64": np.int64,
+      "float64": np.float64}
 
 
 def parse(desc):

@@ -151,7 +151,24 @@ def cast_f32_bf16(x):
     return y
 
 
+_TYPED = {np.dtype(np.float16): 1, np.dtype(np.float64): 3, np.dtype(np.int32): 4, np.dtype(np.int64): 5,
+          np.dtype(np.bool_): 6}
+
+
+def reduce_typed(kind, x, outer, r, inner):
+    """Serial reduction with the accumulator in the tensor's own type (float16, float64, int32, int64, bool)."""
+    x = np.ascontiguousarray(x)
+    assert x.size == outer * r * inner
+    y = np.empty(outer * inner, x.dtype)
+    code = {"sum": 0, "prod": 1, "max": 2, "min": 3, "all": 4, "any": 5}[kind]
+    rc = lib().orc_reduce_typed(code, _TYPED[x.dtype], _p(x), _i64(outer), _i64(r), _i64(inner), _p(y))
+    assert rc == 0, (kind, x.dtype)
+    return y
+
+
 def reduce(kind, x, outer, r, inner, threads=1):
+    if np.asarray(x).dtype != np.float32:
+        return reduce_typed(kind, x, outer, r, inner)
     x = _f32(x)
     assert x.size == outer * r * inner
     y = np.empty(outer * inner, np.float32)

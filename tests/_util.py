@@ -4,7 +4,9 @@ import torch
 
 import cinn_b200
 
-NP2TORCH = {np.dtype(np.float32): torch.float32, np.dtype(np.float16): torch.float16}
+NP2TORCH = {np.dtype(np.float32): torch.float32, np.dtype(np.float16): torch.float16,
+            np.dtype(np.float64): torch.float64, np.dtype(np.int32): torch.int32, np.dtype(np.int64): torch.int64,
+            np.dtype(np.bool_): torch.bool}
 
 
 def run_group(workload, misalign=0, check_canary=True):
@@ -24,14 +26,15 @@ def run_group(workload, misalign=0, check_canary=True):
     n_out = int(np.prod(workload.out_shape))
     pad = 64
     out_t = NP2TORCH[np.dtype(workload.out_dtype)]
-    raw = torch.full((n_out + 2 * pad + misalign,), 777.0, dtype=out_t, device=dev)
+    canary = True if out_t == torch.bool else 77
+    raw = torch.full((n_out + 2 * pad + misalign,), canary, dtype=out_t, device=dev)
     out = raw[pad + misalign: pad + misalign + n_out].view(workload.out_shape)
     g.run(ins + [out])
     torch.cuda.synchronize()
     if check_canary:
         head = raw[: pad + misalign].float().cpu().numpy()
         tail = raw[pad + misalign + n_out:].float().cpu().numpy()
-        assert (head == 777.0).all() and (tail == 777.0).all(), "kernel wrote outside its output buffer"
+        assert (head == float(canary)).all() and (tail == float(canary)).all(), "kernel wrote outside its output buffer"
     res = out.cpu().numpy()
     g.release()
     return res, g
