@@ -22,6 +22,7 @@ SOURCES = [
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
     "ew_chain.cu",
+    "ew_chain_int.cu",
     "ew_stream.cu",
     "reduce_static_scratch.cu",
     "peer_reduce.cu",

@@ -57,6 +57,22 @@ const std::map<std::string, int>& UnaryCodes() {
       {"logical_not", EW_LNOT}};
   return m;
 }
+const std::map<std::string, int>& IntUnaryCodes() {
+  static const std::map<std::string, int> m = {
+      {"negative", EW_NEG}, {"abs", EW_ABS}, {"identity", EW_IDENTITY}, {"relu", EW_RELU}, {"logical_not", EW_LNOT},
+      {"bitwise_not", EW_BNOT}, {"clz", EW_CLZ}, {"popc", EW_POPC}};
+  return m;
+}
+const std::map<std::string, int>& IntBinaryCodes() {
+  static const std::map<std::string, int> m = {
+      {"elementwise_add", EW_ADD}, {"subtract", EW_SUB}, {"elementwise_mul", EW_MUL}, {"divide", EW_DIV},
+      {"max", EW_MAX}, {"min", EW_MIN}, {"equal", EW_EQ}, {"not_equal", EW_NE}, {"greater_than", EW_GT},
+      {"less_than", EW_LT}, {"greater_equal", EW_GE}, {"less_equal", EW_LE}, {"mod", EW_MOD}, {"remainder", EW_MOD},
+      {"floor_divide", EW_FLOOR_DIV}, {"logical_and", EW_LAND}, {"logical_or", EW_LOR}, {"logical_xor", EW_LXOR},
+      {"bitwise_and", EW_BAND}, {"bitwise_or", EW_BOR}, {"bitwise_xor", EW_BXOR}, {"left_shift", EW_SHL},
+      {"right_shift", EW_SHR}, {"logical_right_shift", EW_LSHR}};
+  return m;
+}
 const std::map<std::string, int>& BinaryCodes() {
   static const std::map<std::string, int> m = {
       {"elementwise_add", EW_ADD}, {"subtract", EW_SUB},   {"elementwise_mul", EW_MUL}, {"divide", EW_DIV},
@@ -76,8 +92,9 @@ uint64_t Word(int op, int asel, int bsel, int role, float imm) {
 
 bool IsFloatType(DType t) { return t == DType::kFloat32 || t == DType::kFloat16 || t == DType::kBFloat16; }
 bool IsIntType(DType t) { return t == DType::kInt32 || t == DType::kInt64; }
-// Types whose values the kernel carries exactly in an fp32 register.
-bool IsChainType(DType t) { return IsFloatType(t) || t == DType::kBool; }
+bool IsAnyOp(const std::string& t) {
+  return UnaryCodes().count(t) || BinaryCodes().count(t) || IntUnaryCodes().count(t) || IntBinaryCodes().count(t);
+}
 bool YieldsBool(int code) {
   return (code >= EW_EQ && code <= EW_LE) || code == EW_LAND || code == EW_LOR || code == EW_LXOR || code == EW_ISNAN ||
          code == EW_ISINF || code == EW_ISFINITE || code == EW_LNOT;
@@ -112,8 +129,31 @@ struct ChainBuilder {
   std::vector<Side> sides;
   int64_t n = 0;
   std::vector<int64_t> out_shape;
+  // The float form carries float32 / float16 / bfloat16 / bool values in fp32 registers; the integer form carries
+  // values of ONE integer type (`compute`) and bool in registers of that type.
+  bool int_class = false;
+  DType compute  = DType::kFloat32;
 
   ChainBuilder(const GroupDesc& g_, std::string* w) : g(g_), why(w) {}
+
+  bool Ok(DType t) const {
+    if (t == DType::kBool) return true;
+    return int_class ? t == compute : IsFloatType(t);
+  }
+  const std::map<std::string, int>& Unary() const { return int_class ? IntUnaryCodes() : UnaryCodes(); }
+  const std::map<std::string, int>& Binary() const { return int_class ? IntBinaryCodes() : BinaryCodes(); }
+  // A constant as the immediate field of a program word: an fp32 value, or (integer form) the bits of an int32.
+  bool Imm(const std::string& text, float* out) {
+    if (!int_class) {
+      *out = (float)atof(text.c_str());
+      return true;
+    }
+    const double d = atof(text.c_str());
+    if (d != std::floor(d) || d < -2147483648.0 || d > 2147483647.0) return false;
+    const int32_t v = (int32_t)d;
+    memcpy(out, &v, 4);
+    return true;
+  }
 
   bool Fail(const std::string& m) {
     if (why) *why = m;
@@ -149,13 +189,14 @@ struct ChainBuilder {
       } else if (op.type == "broadcast_to") {
         v.dtype = values[op.inputs[0]].dtype;
         v.shape = IntList(Attr(op, "out_shape", ""));
-      } else if (BinaryCodes().count(op.type)) {
+      } else if (BinaryCodes().count(op.type) || IntBinaryCodes().count(op.type)) {
         if (op.inputs.size() != 2) return Fail(op.type + " needs two operands");
         const Value &a = values[op.inputs[0]], &b = values[op.inputs[1]];
         v       = a.numel() >= b.numel() ? a : b;
         if (a.shape.size() != b.shape.size() && a.numel() == b.numel()) v = a.shape.size() >= b.shape.size() ? a : b;
-        v.dtype = YieldsBool(BinaryCodes().at(op.type)) ? DType::kBool : a.dtype;
-      } else if (UnaryCodes().count(op.type) || op.type == "scale") {
+        const int code = BinaryCodes().count(op.type) ? BinaryCodes().at(op.type) : IntBinaryCodes().at(op.type);
+        v.dtype        = YieldsBool(code) ? DType::kBool : a.dtype;
+      } else if (UnaryCodes().count(op.type) || IntUnaryCodes().count(op.type) || op.type == "scale") {
         if (op.inputs.size() != 1) return Fail(op.type + " needs one operand");
         v = values[op.inputs[0]];
         if (UnaryCodes().count(op.type) && YieldsBool(UnaryCodes().at(op.type))) v.dtype = DType::kBool;
@@ -227,8 +268,7 @@ struct ChainBuilder {
     const OpDesc* p = producer.count(name) ? producer[name] : nullptr;
     if (p && p->type == "fill_constant") {
       *asel = 0;
-      *imm  = (float)atof(Attr(*p, "value", "0").c_str());
-      return true;
+      return Imm(Attr(*p, "value", "0"), imm);
     }
     std::string src = name;
     std::vector<int64_t> axes;
@@ -258,7 +298,7 @@ struct ChainBuilder {
       int64_t off  = (axis < 0 || sv->shape.size() == out_shape.size()) ? (int64_t)out_shape.size() - (int64_t)sv->shape.size() : axis;
       for (size_t i = 0; i < sv->shape.size(); ++i) axes.push_back(off + (int64_t)i);
     }
-    if (!IsChainType(sv->dtype) && !(IsIntType(sv->dtype) && src != name)) return false;
+    if (!Ok(sv->dtype) && !(IsIntType(sv->dtype) && src != name)) return false;
     Side s;
     if (!SideSpec(sv->shape, axes, input_index[src], &s)) return false;
     int sel = AddSide(s);
@@ -272,6 +312,7 @@ struct ChainBuilder {
   bool IsLoadCast(const OpDesc& p) {
     if (p.type != "cast" || !input_index.count(p.inputs[0])) return false;
     const DType from = values[p.inputs[0]].dtype, to = values[p.output].dtype;
+    if (int_class) return (IsIntType(from) || from == DType::kBool) && to == compute;  // widen / truncate / 0-1
     if (IsIntType(from)) return to == DType::kFloat32;
     if (from == DType::kBool) return IsFloatType(to);
     if (from == DType::kFloat16 || from == DType::kBFloat16) return to == DType::kFloat32;
@@ -323,8 +364,10 @@ const char* DTypeKernelName(DType t) {
 
 }  // namespace
 
-std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const DeviceInfo& dev, std::string* why) {
+std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const DeviceInfo& dev, bool int_class,
+                                                 std::string* why) {
   ChainBuilder cb(g, why);
+  cb.int_class = int_class;
   if (g.outputs.size() != 1) {
     cb.Fail("a chain has exactly one output");
     return nullptr;
@@ -340,6 +383,27 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
   if (!DTypeKernelName(out.dtype)) {
     cb.Fail(std::string("output dtype ") + DTypeName(out.dtype) + " is not supported by the chain kernel");
     return nullptr;
+  }
+  if (int_class) {
+    // The integer type the chain computes in: that of the last value that is not a cast or a bool, walking back
+    // from the output.
+    std::string v = out.name;
+    cb.compute    = DType::kUnknown;
+    for (int guard = 0; guard < 64 && cb.compute == DType::kUnknown; ++guard) {
+      const DType t   = cb.values[v].dtype;
+      const OpDesc* p = cb.producer.count(v) ? cb.producer[v] : nullptr;
+      if (IsIntType(t) && !(p && p->type == "cast")) cb.compute = t;
+      else if (p && !p->inputs.empty()) v = p->inputs[p->type == "select" ? 1 : 0];
+      else break;
+    }
+    if (cb.compute == DType::kUnknown) {
+      cb.Fail("no integer arithmetic in the group");
+      return nullptr;
+    }
+    if (out.dtype != DType::kInt32 && out.dtype != DType::kInt64 && out.dtype != DType::kBool && out.dtype != DType::kFloat32) {
+      cb.Fail(std::string("an integer chain cannot store ") + DTypeName(out.dtype));
+      return nullptr;
+    }
   }
 
   // Walk back from the output collecting primitive steps in reverse order.
@@ -365,18 +429,31 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
     if (op.type == "cast") {
       const Value& iv = cb.values[op.inputs[0]];
       bool ok = false;
-      if (IsFloatType(iv.dtype) && IsFloatType(ov.dtype)) {
+      if (int_class) {
+        if (cb.Ok(iv.dtype) && ov.dtype == DType::kBool && iv.dtype != DType::kBool) {
+          ok = true;
+          Step r;
+          r.op = EW_TO_BOOL;
+          rev.push_back(r);
+        } else if (cb.Ok(iv.dtype) && cb.Ok(ov.dtype)) {
+          ok = true;  // bool -> integer (0 / 1) or the same type
+        } else if (cb.Ok(iv.dtype) && cur == out.name && (IsIntType(ov.dtype) || ov.dtype == DType::kFloat32)) {
+          ok = true;  // the store converts: other integer width, or float32 (to nearest even)
+        } else if ((IsIntType(iv.dtype) || iv.dtype == DType::kBool) && ov.dtype == cb.compute) {
+          ok = cb.input_index.count(op.inputs[0]) != 0;  // the load of the chain's input converts
+        }
+      } else if (IsFloatType(iv.dtype) && IsFloatType(ov.dtype)) {
         ok = true;
         round_after();  // widening casts are exact and need no step
       } else if (iv.dtype == DType::kBool && (IsFloatType(ov.dtype) || ov.dtype == DType::kBool)) {
         ok = true;      // 0 / 1 are exact in every float type
-      } else if (IsChainType(iv.dtype) && ov.dtype == DType::kBool) {
+      } else if (cb.Ok(iv.dtype) && ov.dtype == DType::kBool) {
         ok = true;
         Step r;
         r.op = EW_TO_BOOL;
         r.f32 = false;
         rev.push_back(r);
-      } else if (IsChainType(iv.dtype) && IsIntType(ov.dtype)) {
+      } else if (cb.Ok(iv.dtype) && IsIntType(ov.dtype)) {
         ok = cur == out.name;  // float -> integer only as the last op: the store converts (toward zero)
       } else if (IsIntType(iv.dtype) && ov.dtype == DType::kFloat32) {
         ok = cb.input_index.count(op.inputs[0]) != 0;  // integer -> float32 only on the chain's input: the load converts
@@ -386,6 +463,9 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
         return nullptr;
       }
       cur = op.inputs[0];
+    } else if (op.type == "scale" && int_class) {
+      cb.Fail("scale on integers has no prebuilt kernel");
+      return nullptr;
     } else if (op.type == "scale") {
       const float s = (float)atof(ChainBuilder::Attr(op, "scale", "1").c_str());
       const float b = (float)atof(ChainBuilder::Attr(op, "bias", "0").c_str());
@@ -399,25 +479,29 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
       if (after) { rev.push_back(add); rev.push_back(mul); }
       else { rev.push_back(mul); rev.push_back(add); }
       cur = op.inputs[0];
-    } else if (UnaryCodes().count(op.type)) {
-      if (!IsChainType(cb.values[op.inputs[0]].dtype)) {
-        cb.Fail("op '" + op.type + "' on a " + DTypeName(cb.values[op.inputs[0]].dtype) + " value is not a float chain");
+    } else if (cb.Unary().count(op.type)) {
+      if (!cb.Ok(cb.values[op.inputs[0]].dtype)) {
+        cb.Fail("op '" + op.type + "' on a " + DTypeName(cb.values[op.inputs[0]].dtype) + " value does not fit this form of chain");
         return nullptr;
       }
       round_after();
       if (op.type != "identity") {
         Step s;
-        s.op  = UnaryCodes().at(op.type);
+        s.op  = cb.Unary().at(op.type);
         s.f32 = f32;
         if (op.type == "relu6") s.imm = (float)atof(ChainBuilder::Attr(op, "threshold", "6").c_str());
+        if (s.op == EW_RELU && int_class) {  // max(x, 0) with an integer zero
+          s.op = EW_MAX;
+          cb.Imm("0", &s.imm);
+        }
         rev.push_back(s);
       }
       cur = op.inputs[0];
-    } else if (BinaryCodes().count(op.type)) {
+    } else if (cb.Binary().count(op.type)) {
       const std::string &a = op.inputs[0], &b = op.inputs[1];
       const bool ca = cb.InGroupComputed(a), cbb = cb.InGroupComputed(b);
       Step s;
-      s.op  = BinaryCodes().at(op.type);
+      s.op  = cb.Binary().at(op.type);
       s.f32 = cb.values[a].dtype == DType::kFloat32;
       std::string next;
       if (ca && cbb) {
@@ -452,8 +536,8 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
         }
         s.swap = !chain_is_a;  // the side operand is the LEFT operand
       }
-      if (!IsChainType(cb.values[a].dtype) || !IsChainType(cb.values[b].dtype)) {
-        cb.Fail("op '" + op.type + "' on " + DTypeName(cb.values[a].dtype) + " operands is not a float chain");
+      if (!cb.Ok(cb.values[a].dtype) || !cb.Ok(cb.values[b].dtype)) {
+        cb.Fail("op '" + op.type + "' on " + DTypeName(cb.values[a].dtype) + " operands does not fit this form of chain");
         return nullptr;
       }
       round_after();
@@ -472,7 +556,7 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
       if (chain_pos < 0) {
         for (int k : {1, 2, 0})
           if (chain_pos < 0 && cb.input_index.count(op.inputs[k]) && cb.values[op.inputs[k]].numel() == cb.n &&
-              IsChainType(cb.values[op.inputs[k]].dtype))
+              cb.Ok(cb.values[op.inputs[k]].dtype))
             chain_pos = k;
         if (chain_pos < 0) {
           cb.Fail("select has no full-size operand to start the chain from");
@@ -488,11 +572,11 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
       const std::string& chain = op.inputs[chain_pos];
       auto resolve = [&](int pos, int* sel, float* imm) {
         const std::string& nm = op.inputs[pos];
-        if (!IsChainType(cb.values[nm].dtype)) return false;
+        if (!cb.Ok(cb.values[nm].dtype)) return false;
         if (cb.IsSameAs(nm, chain)) { *sel = 4; return true; }
         return cb.ResolveOperand(nm, op, sel, imm);
       };
-      if (!IsChainType(cb.values[chain].dtype) || !resolve(a_pos, &s.asel, &s.imm) || !resolve(b_pos, &s.bsel, &s.imm2)) {
+      if (!cb.Ok(cb.values[chain].dtype) || !resolve(a_pos, &s.asel, &s.imm) || !resolve(b_pos, &s.bsel, &s.imm2)) {
         cb.Fail("an operand of select is neither a broadcastable group input nor a constant");
         return nullptr;
       }
@@ -510,6 +594,10 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
   }
   const int in0       = cb.input_index[cur];
   const DType in_type = g.inputs[in0].dtype;
+  if (int_class && !IsIntType(in_type) && in_type != DType::kBool) {
+    cb.Fail("an integer chain starts at an integer or bool input");
+    return nullptr;
+  }
   if (DTypeKernelCode(in_type) < 0) {
     cb.Fail(std::string("input dtype ") + DTypeName(in_type) + " is not supported by the chain kernel");
     return nullptr;
@@ -529,7 +617,7 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
   std::vector<uint64_t> words;
   for (size_t i = 0; i < steps.size(); ++i) {
     const Step& s = steps[i];
-    if (s.op == EW_MUL && s.f32 && i + 1 < steps.size() && steps[i + 1].op == EW_ADD && steps[i + 1].f32 &&
+    if (!int_class && s.op == EW_MUL && s.f32 && i + 1 < steps.size() && steps[i + 1].op == EW_ADD && steps[i + 1].f32 &&
         steps[i + 1].asel != 4) {
       const Step& a = steps[i + 1];
       words.push_back(Word(EW_FMA, s.asel, a.asel, 0, s.imm));
@@ -560,7 +648,8 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
   for (auto& t : g.inputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
   p->algorithmic_bytes += out.numel() * DTypeBytes(out.dtype);
   LaunchStep st;
-  st.kernel = FindKernel(std::string("ew_chain_") + DTypeKernelName(out.dtype));
+  st.kernel = FindKernel(int_class ? std::string("ew_chain_int_") + DTypeKernelName(cb.compute) + "_" + DTypeKernelName(out.dtype)
+                                   : std::string("ew_chain_") + DTypeKernelName(out.dtype));
   if (!st.kernel) {
     cb.Fail("chain kernel for these dtypes is not in the library");
     return nullptr;
@@ -601,6 +690,21 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
   for (int k = 0; k < EW_MAX_STEPS; ++k) st.args.push_back(int_arg(k < (int)words.size() ? (int64_t)words[k] : 0));
   p->steps.push_back(st);
   return p;
+}
+
+std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const DeviceInfo& dev, std::string* why) {
+  std::string why_float, why_int;
+  if (auto p = MatchChainOfClass(g, dev, false, &why_float)) return p;
+  bool has_int = false;
+  for (auto& t : g.inputs) has_int = has_int || IsIntType(t.dtype);
+  for (auto& t : g.outputs) has_int = has_int || IsIntType(t.dtype);
+  if (has_int) {
+    if (auto p = MatchChainOfClass(g, dev, true, &why_int)) return p;
+    if (why) *why = why_float + "; as an integer chain: " + why_int;
+  } else if (why) {
+    *why = why_float;
+  }
+  return nullptr;
 }
 
 }  // namespace cinn_b200

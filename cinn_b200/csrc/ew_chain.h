@@ -6,7 +6,8 @@
 // bits 24-25 "swap" for a binary op (1: the side operand is the LEFT operand) or, for EW_SELECT, the role of the
 // chain value (0: the condition, A = value if true, B = value if false; 1: the value if true, A = condition,
 // B = value if false; 2: the value if false, A = condition, B = value if true), bits 32-63 an fp32 immediate.
-// Values of type bool travel as 0.0f / 1.0f.
+// Values of type bool travel as 0.0f / 1.0f.  The integer form of the kernel (ew_chain_int.cu) uses the same words
+// with a signed 32-bit integer in bits 32-63; bool travels as 0 / 1.
 #pragma once
 
 namespace cinn_b200 {
@@ -19,6 +20,8 @@ enum EwOp {
   EW_ADD = 1, EW_SUB, EW_MUL, EW_DIV, EW_MAX, EW_MIN, EW_POW,
   EW_EQ, EW_NE, EW_GT, EW_LT, EW_GE, EW_LE,
   EW_MOD = 14, EW_FLOOR_DIV, EW_ATAN2, EW_LAND, EW_LOR, EW_LXOR,
+  // integer chains only
+  EW_BAND = 23, EW_BOR, EW_BXOR, EW_SHL, EW_SHR, EW_LSHR,
   EW_FMA = 20,        // acc = fma(acc, A, B)
   EW_SCALE_PRE = 21,  // acc = imm * (acc + imm_next)
   EW_SELECT = 22,     // acc = cond ? t : f, see the role bits above
@@ -29,7 +32,8 @@ enum EwOp {
   EW_ROUND_F16, EW_ROUND_BF16, EW_IDENTITY,
   EW_TAN, EW_SINH, EW_COSH, EW_ASIN, EW_ACOS, EW_ATAN, EW_ASINH, EW_ACOSH, EW_ATANH, EW_CBRT,
   EW_ISNAN, EW_ISINF, EW_ISFINITE, EW_LNOT,
-  EW_TO_BOOL  // x != 0 ? 1 : 0 (cast to bool in the middle of a chain)
+  EW_TO_BOOL,  // x != 0 ? 1 : 0 (cast to bool in the middle of a chain)
+  EW_BNOT, EW_CLZ, EW_POPC  // integer chains only
 };
 
 // Storage types of the chain kernel's operands (runtime codes; the output type is a template parameter).

@@ -1,0 +1,262 @@
+// Integer form of the generic elementwise chain (see ew_chain.cu for the float form and ew_chain.h for the program
+// encoding): the chain value and its side operands are int32 or int64 values, bool travels as 0 / 1, immediates are
+// signed 32-bit integers.  Arithmetic is what the reference generates for integer tensors:
+// + - * wrap, `divide` truncates toward zero (ir::Div), max / min are compare + select, mod takes the sign of the
+// divisor and floor_divide rounds toward minus infinity (cinn/lang/builtin.cc:108-121,
+// cinn/runtime/cuda/cinn_cuda_runtime_source.cuh:160-183), shifts and bitwise ops are the C operators
+// (cinn/hlir/pe/broadcast.cc:256-266), logical_right_shift shifts the unsigned value, clz / popc count bits
+// (cinn/runtime/cpu/host_intrinsics.cc:240-262).  A divisor of zero gives 0 (the reference's x86 code would trap).
+#include <cstdint>
+
+#include "device_math.cuh"
+#include "ew_chain.h"
+#include "kernel_registry.h"
+
+namespace cinn_b200 {
+namespace {
+
+template <typename T>
+struct UnsignedOf;
+template <>
+struct UnsignedOf<int32_t> {
+  using type = uint32_t;
+};
+template <>
+struct UnsignedOf<long long> {
+  using type = unsigned long long;
+};
+
+template <typename T>
+__device__ __forceinline__ T int_unary(int op, T x) {
+  using U = typename UnsignedOf<T>::type;
+  switch (op) {
+    case EW_NEG: return (T)(U(0) - (U)x);
+    case EW_ABS: return x > 0 ? x : (T)(U(0) - (U)x);
+    case EW_LNOT: return x == 0 ? 1 : 0;
+    case EW_TO_BOOL: return x != 0 ? 1 : 0;
+    case EW_BNOT: return ~x;
+    case EW_CLZ: return sizeof(T) == 4 ? (T)__clz((int)x) : (T)__clzll((long long)x);
+    case EW_POPC: return sizeof(T) == 4 ? (T)__popc((unsigned)x) : (T)__popcll((unsigned long long)x);
+    default: return x;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ T int_binary(int op, T l, T r) {
+  using U = typename UnsignedOf<T>::type;
+  constexpr int kBits = sizeof(T) * 8;
+  switch (op) {
+    case EW_ADD: return (T)((U)l + (U)r);
+    case EW_SUB: return (T)((U)l - (U)r);
+    case EW_MUL: return (T)((U)l * (U)r);
+    case EW_DIV: return r == 0 ? 0 : ((r == -1) ? (T)(U(0) - (U)l) : l / r);
+    case EW_MAX: return l > r ? l : r;
+    case EW_MIN: return l < r ? l : r;
+    case EW_EQ: return l == r;
+    case EW_NE: return l != r;
+    case EW_GT: return l > r;
+    case EW_LT: return l < r;
+    case EW_GE: return l >= r;
+    case EW_LE: return l <= r;
+    case EW_MOD: {
+      if (r == 0 || r == -1) return 0;
+      T res = l % r;
+      if (res != 0 && ((r ^ res) < 0)) res += r;
+      return res;
+    }
+    case EW_FLOOR_DIV: {
+      if (r == 0) return 0;
+      if (r == -1) return (T)(U(0) - (U)l);
+      const T div = l / r, mod = l % r;
+      return ((l > 0 && r > 0) || (l < 0 && r < 0)) ? div : (mod == 0 ? div : div - 1);
+    }
+    case EW_LAND: return (l != 0 && r != 0) ? 1 : 0;
+    case EW_LOR: return (l != 0 || r != 0) ? 1 : 0;
+    case EW_LXOR: return ((l != 0) != (r != 0)) ? 1 : 0;
+    case EW_BAND: return l & r;
+    case EW_BOR: return l | r;
+    case EW_BXOR: return l ^ r;
+    // shift counts are taken modulo the width, as the x86 shift instructions do
+    case EW_SHL: return (T)((U)l << ((int)r & (kBits - 1)));
+    case EW_SHR: return l >> ((int)r & (kBits - 1));
+    case EW_LSHR: return (T)((U)l >> ((int)r & (kBits - 1)));
+    default: return l;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ T load_int(const void* p, int dtype, long long idx) {
+  switch (dtype) {
+    case EW_BOOL: return static_cast<const uint8_t*>(p)[idx] != 0 ? 1 : 0;
+    case EW_I32: return (T) static_cast<const int32_t*>(p)[idx];
+    default: return (T) static_cast<const long long*>(p)[idx];
+  }
+}
+
+// Four consecutive elements starting at idx (idx % 4 == 0, pointer 16-byte aligned).
+template <typename T>
+__device__ __forceinline__ void load_int4(const void* p, int dtype, long long idx, bool stream, T (&v)[4]) {
+  if (dtype == EW_BOOL) {
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p) + idx);
+    const uint32_t u  = stream ? __ldcs(q) : __ldg(q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = ((u >> (8 * i)) & 0xffu) != 0 ? 1 : 0;
+  } else if (dtype == EW_I32) {
+    const int4* q = reinterpret_cast<const int4*>(static_cast<const int32_t*>(p) + idx);
+    const int4 u  = stream ? __ldcs(q) : __ldg(q);
+    v[0] = (T)u.x; v[1] = (T)u.y; v[2] = (T)u.z; v[3] = (T)u.w;
+  } else {
+    const longlong2* q = reinterpret_cast<const longlong2*>(static_cast<const long long*>(p) + idx);
+    const longlong2 u0 = stream ? __ldcs(q) : __ldg(q);
+    const longlong2 u1 = stream ? __ldcs(q + 1) : __ldg(q + 1);
+    v[0] = (T)u0.x; v[1] = (T)u0.y; v[2] = (T)u1.x; v[3] = (T)u1.y;
+  }
+}
+
+template <typename T, typename OutT>
+__device__ __forceinline__ OutT convert_out(T v);
+template <> __device__ __forceinline__ int32_t convert_out<int32_t, int32_t>(int32_t v) { return v; }
+template <> __device__ __forceinline__ long long convert_out<int32_t, long long>(int32_t v) { return v; }
+template <> __device__ __forceinline__ uint8_t convert_out<int32_t, uint8_t>(int32_t v) { return v != 0; }
+template <> __device__ __forceinline__ float convert_out<int32_t, float>(int32_t v) { return (float)v; }
+template <> __device__ __forceinline__ int32_t convert_out<long long, int32_t>(long long v) { return (int32_t)v; }
+template <> __device__ __forceinline__ long long convert_out<long long, long long>(long long v) { return v; }
+template <> __device__ __forceinline__ uint8_t convert_out<long long, uint8_t>(long long v) { return v != 0; }
+template <> __device__ __forceinline__ float convert_out<long long, float>(long long v) { return (float)v; }
+
+template <typename T, typename OutT>
+__device__ __forceinline__ void store_int4(OutT* p, long long idx, const T (&v)[4]) {
+  // one store of 4 / 16 bytes, or two of 16 for 8-byte elements (the buffers are only known to be 16-byte aligned)
+  constexpr int kHalf = sizeof(OutT) == 8 ? 2 : 4;
+  struct alignas(sizeof(OutT) * kHalf) Pack {
+    OutT e[kHalf];
+  };
+#pragma unroll
+  for (int h = 0; h < 4 / kHalf; ++h) {
+    Pack pk;
+#pragma unroll
+    for (int i = 0; i < kHalf; ++i) pk.e[i] = convert_out<T, OutT>(v[h * kHalf + i]);
+    *reinterpret_cast<Pack*>(p + idx + h * kHalf) = pk;
+  }
+}
+
+struct SideSpec {
+  const void* ptr;
+  int dtype, mode;
+  long long mid, inner;
+};
+
+__device__ __forceinline__ long long side_index(long long i, long long inner, long long mid) {
+  if (((i | inner | mid) >> 31) == 0) return (long long)(((unsigned)i / (unsigned)inner) % (unsigned)mid);
+  return (i / inner) % mid;
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void load_side(const SideSpec& s, long long i0, T (&f)[VEC]) {
+  if (VEC == 4 && s.mode == EW_SIDE_FULL) {
+    load_int4<T>(s.ptr, s.dtype, i0, true, *reinterpret_cast<T(*)[4]>(&f[0]));
+  } else if (VEC == 4 && s.mode == EW_SIDE_PERIODIC_VEC) {
+    load_int4<T>(s.ptr, s.dtype, side_index(i0, 1, s.mid), false, *reinterpret_cast<T(*)[4]>(&f[0]));
+  } else if (s.mode == EW_SIDE_ONE_PER_VEC || s.mode == EW_SIDE_SCALAR) {
+    const T v = load_int<T>(s.ptr, s.dtype, s.mode == EW_SIDE_SCALAR ? 0 : side_index(i0, s.inner, s.mid));
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) f[i] = v;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) f[i] = load_int<T>(s.ptr, s.dtype, side_index(i0 + i, s.inner, s.mid));
+  }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const T (&s1)[VEC], const T (&s2)[VEC],
+                                          const T (&s3)[VEC], T (&acc)[VEC]) {
+  for (int k = 0; k < nsteps; ++k) {
+    const long long st = steps[k];
+    const int op       = (int)(st & 0xff);
+    const int asel     = (int)((st >> 8) & 0xff);
+    const int bsel     = (int)((st >> 16) & 0xff);
+    const int role     = (int)((st >> 24) & 3);
+    const T imm        = (T)(int32_t)(st >> 32);
+    if (op == EW_NOP) continue;
+    if (op >= EW_FIRST_UNARY) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = int_unary<T>(op, acc[i]);
+      continue;
+    }
+    T o[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) o[i] = asel == 1 ? s1[i] : (asel == 2 ? s2[i] : (asel == 3 ? s3[i] : (asel == 4 ? acc[i] : imm)));
+    if (op == EW_SELECT) {
+      const T imm2 = (T)(int32_t)(steps[k + 1] >> 32);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const T b = bsel == 1 ? s1[i] : (bsel == 2 ? s2[i] : (bsel == 3 ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        const T c = role == 0 ? acc[i] : o[i];
+        const T t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
+        const T f = role == 2 ? acc[i] : b;
+        acc[i]    = c != 0 ? t : f;
+      }
+      if (bsel == 0) ++k;
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = role != 0 ? int_binary<T>(op, o[i], acc[i]) : int_binary<T>(op, acc[i], o[i]);
+    }
+  }
+}
+
+// Same parameter list as the float form (k_ew_chain): meta bits 0-3 / 4-7 dtype / mode of side 1, 8-15 side 2,
+// 16-23 side 3, 24-27 dtype of in0.
+template <typename T, typename OutT>
+__global__ void __launch_bounds__(256)
+    k_ew_chain_int(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
+                   const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
+                   long long mid1, long long inner1, long long mid2, long long inner2, long long mid3,
+                   long long inner3, long long nsteps_ll, long long t0, long long t1, long long t2, long long t3,
+                   long long t4, long long t5, long long t6, long long t7, long long t8, long long t9, long long t10,
+                   long long t11, long long t12, long long t13, long long t14, long long t15) {
+  const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
+  const int nsteps  = (int)nsteps_ll;
+  const int in_type = (int)((meta >> 24) & 15);
+  const SideSpec sd1 = {p1, (int)(meta & 15), (int)((meta >> 4) & 15), mid1, inner1};
+  const SideSpec sd2 = {p2, (int)((meta >> 8) & 15), (int)((meta >> 12) & 15), mid2, inner2};
+  const SideSpec sd3 = {p3, (int)((meta >> 16) & 15), (int)((meta >> 20) & 15), mid3, inner3};
+  const long long tid    = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long done         = 0;
+  if (vec_ok) {
+    const long long nvec = n >> 2;
+    for (long long v = tid; v < nvec; v += stride) {
+      const long long i0 = v << 2;
+      T acc[4], s1[4], s2[4], s3[4];
+      load_int4<T>(in0, in_type, i0, true, acc);
+      if (sd1.mode != EW_SIDE_NONE) load_side<T, 4>(sd1, i0, s1);
+      if (sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, s2);
+      if (sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, s3);
+      run_chain<T, 4>(steps, nsteps, s1, s2, s3, acc);
+      store_int4<T, OutT>(out, i0, acc);
+    }
+    done = nvec << 2;
+  }
+  for (long long i = done + tid; i < n; i += stride) {
+    T acc[1], s1[1], s2[1], s3[1];
+    acc[0] = load_int<T>(in0, in_type, i);
+    if (sd1.mode != EW_SIDE_NONE) load_side<T, 1>(sd1, i, s1);
+    if (sd2.mode != EW_SIDE_NONE) load_side<T, 1>(sd2, i, s2);
+    if (sd3.mode != EW_SIDE_NONE) load_side<T, 1>(sd3, i, s3);
+    run_chain<T, 1>(steps, nsteps, s1, s2, s3, acc);
+    out[i] = convert_out<T, OutT>(acc[0]);
+  }
+}
+
+}  // namespace
+
+#define REG_INT_CHAIN(TNAME, T)                                                                            \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i32", 31, 256, k_ew_chain_int<T, int32_t>);          \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i64", 31, 256, k_ew_chain_int<T, long long>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_bool", 31, 256, k_ew_chain_int<T, uint8_t>);         \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_f32", 31, 256, k_ew_chain_int<T, float>)
+
+REG_INT_CHAIN("i32", int32_t);
+REG_INT_CHAIN("i64", long long);
+
+}  // namespace cinn_b200

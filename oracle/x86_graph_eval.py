@@ -78,6 +78,92 @@ def _store(v32, dtype):
     return v32
 
 
+INT_UNARY = {"negative", "abs", "identity", "relu", "logical_not", "bitwise_not", "clz", "popc"}
+
+
+def _int_unary(t, x):
+    """Integer tensors: plain two's-complement arithmetic (numpy wraps like the C operators)."""
+    bits = x.dtype.itemsize * 8
+    u = x.view(np.uint32 if bits == 32 else np.uint64)
+    with np.errstate(over="ignore"):
+        if t == "negative":
+            return (0 - x).astype(x.dtype)
+        if t == "abs":
+            return np.where(x > 0, x, (0 - x).astype(x.dtype))
+        if t == "relu":
+            return np.maximum(x, 0).astype(x.dtype)
+        if t == "logical_not":
+            return x == 0
+        if t == "bitwise_not":
+            return ~x
+        if t in ("clz", "popc"):
+            ones = np.zeros(x.shape, np.int64)
+            lead = np.full(x.shape, bits, np.int64)
+            for b in range(bits):
+                bit = ((u >> np.array(b, u.dtype)) & np.array(1, u.dtype)).astype(np.int64)
+                ones += bit
+                lead = np.where(bit == 1, bits - 1 - b, lead)
+            return (ones if t == "popc" else lead).astype(x.dtype)
+    return x
+
+
+def _int_binary(t, a, b):
+    """a, b broadcast-compatible integer arrays of one dtype (or bool for the logical ops)."""
+    dt = a.dtype
+    bits = dt.itemsize * 8
+    with np.errstate(over="ignore", divide="ignore"):
+        if t == "elementwise_add":
+            return (a + b).astype(dt)
+        if t == "subtract":
+            return (a - b).astype(dt)
+        if t == "elementwise_mul":
+            return (a * b).astype(dt)
+        if t in ("divide", "floor_divide", "mod", "remainder"):
+            safe = np.where((b == 0) | (b == -1), 1, b).astype(dt)
+            fl = np.floor_divide(a, safe)
+            md = (a - fl * safe).astype(dt)                       # sign of the divisor
+            tr = np.where((md != 0) & ((a < 0) != (safe < 0)), fl + 1, fl).astype(dt)   # toward zero
+            neg = (0 - a).astype(dt)
+            if t == "divide":
+                return np.where(b == 0, 0, np.where(b == -1, neg, tr)).astype(dt)
+            if t == "floor_divide":
+                return np.where(b == 0, 0, np.where(b == -1, neg, fl)).astype(dt)
+            return np.where((b == 0) | (b == -1), 0, md).astype(dt)
+        if t == "max":
+            return np.where(a > b, a, b).astype(dt)
+        if t == "min":
+            return np.where(a < b, a, b).astype(dt)
+        if t in ("equal", "not_equal", "greater_than", "less_than", "greater_equal", "less_equal"):
+            return {"equal": a == b, "not_equal": a != b, "greater_than": a > b, "less_than": a < b,
+                    "greater_equal": a >= b, "less_equal": a <= b}[t]
+        if t in ("logical_and", "logical_or", "logical_xor"):
+            p, q = a != 0, b != 0
+            return {"logical_and": p & q, "logical_or": p | q, "logical_xor": p ^ q}[t]
+        if t == "bitwise_and":
+            return a & b
+        if t == "bitwise_or":
+            return a | b
+        if t == "bitwise_xor":
+            return a ^ b
+        cnt = (b & (bits - 1)).astype(dt)
+        if t == "left_shift":
+            ut = np.uint32 if bits == 32 else np.uint64
+            return (a.astype(dt).view(ut) << cnt.view(ut)).view(dt)
+        if t == "right_shift":
+            return (a >> cnt).astype(dt)
+        if t == "logical_right_shift":
+            ut = np.uint32 if bits == 32 else np.uint64
+            return (np.ascontiguousarray(np.broadcast_to(a, np.broadcast_shapes(a.shape, b.shape))).view(ut)
+                    >> np.ascontiguousarray(np.broadcast_to(cnt, np.broadcast_shapes(a.shape, b.shape))).view(ut)).view(dt)
+    raise NotImplementedError(t)
+
+
+INT_BINARY = {"elementwise_add", "subtract", "elementwise_mul", "divide", "max", "min", "equal", "not_equal",
+              "greater_than", "less_than", "greater_equal", "less_equal", "mod", "remainder", "floor_divide",
+              "logical_and", "logical_or", "logical_xor", "bitwise_and", "bitwise_or", "bitwise_xor", "left_shift",
+              "right_shift", "logical_right_shift"}
+
+
 def evaluate(desc, inputs):
     """inputs: list of numpy arrays in the group's input order.  Returns {value name: array}."""
     g = parse(desc)
@@ -111,7 +197,22 @@ def evaluate(desc, inputs):
         elif t == "cast":
             x = vals[ins[0]]
             to = NP[at["dtype"]]
-            out = x if x.dtype == to else _store(_f32(x), to)
+            if x.dtype == to:
+                out = x
+            elif x.dtype.kind in "ib" and np.dtype(to).kind in "ib":
+                out = (x != 0) if to == np.bool_ else x.astype(to)   # widen / truncate / 0-1
+            else:
+                out = _store(_f32(x), to)
+        elif t in INT_UNARY and vals[ins[0]].dtype.kind == "i":
+            out = _int_unary(t, vals[ins[0]])
+        elif t in INT_BINARY and vals[ins[0]].dtype.kind == "i":
+            a, b = vals[ins[0]], vals[ins[1]]
+            axis = int(at.get("axis", -1))
+            big, small = (a, b) if a.ndim >= b.ndim else (b, a)
+            shape = np.broadcast_shapes(big.shape, _aligned(small, big.shape, axis).shape)
+            aa = a if a is big else _aligned(a, shape, axis)
+            bb = b if b is big else _aligned(b, shape, axis)
+            out = np.broadcast_to(_int_binary(t, aa, bb), shape)
         elif t == "broadcast_to":
             x = vals[ins[0]]
             shape = tuple(int(d) for d in at["out_shape"].split(","))

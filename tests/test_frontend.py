@@ -167,7 +167,7 @@ def test_unmatched_group_is_an_error_not_a_fallback():
     rc = L.cinn_b200_compile_group(b"group g\ninput x float32 4,4\nop conv2d y = x x\noutput y float32 4,4\n",
                                    ctypes.byref(fn))
     assert rc == -2 and b"no prebuilt sm_100a kernel" in L.cinn_b200_last_error()
-    rc = L.cinn_b200_compile_group(b"group g\ninput x int32 4,4\nop relu y = x\noutput y int32 4,4\n", ctypes.byref(fn))
+    rc = L.cinn_b200_compile_group(b"group g\ninput x uint8 4,4\nop exp y = x\noutput y uint8 4,4\n", ctypes.byref(fn))
     assert rc == -2
     rc = L.cinn_b200_compile_group(b"nonsense", ctypes.byref(fn))
     assert rc == -1

@@ -376,3 +376,74 @@ def test_casts_to_and_from_integers_and_bool(oracle):
     y = b.cast(b.relu(x), "bool")
     comp, out = run_program(b, {"X": X}, [y])
     assert out[str(y)].dtype == np.bool_ and np.array_equal(out[str(y)], np.where(X > 0, X, 0) != 0)
+
+
+# ---- integer chains (int32 / int64 arithmetic, bit operations, comparisons, select, casts at the ends) -------------
+
+def int_programs(bits):
+    T = common.Int(bits)
+    shape = (37, 52)
+
+    def arith(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, (52,), "Y")
+        return b.subtract(b.multiply(b.add(x, y), b.fill_constant([1], 3, dtype=T.name)), b.fill_constant([1], -7, dtype=T.name))
+
+    def divisions(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        return b.mod(b.floor_divide(b.divide(x, b.fill_constant([1], 3, dtype=T.name)), y), y)
+
+    def bit_ops(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        z = b.bitwise_xor(b.bitwise_not(b.bitwise_or(b.bitwise_and(x, y), b.fill_constant([1], 0x0f0f, dtype=T.name))), y)
+        return b.right_shift(b.logical_right_shift(b.left_shift(z, b.fill_constant([1], 3, dtype=T.name)),
+                                                   b.fill_constant([1], 5, dtype=T.name)),
+                             b.fill_constant([1], 1, dtype=T.name))
+
+    def counts(b):
+        x = b.create_input(T, shape, "X")
+        return b.add(b.popc(x), b.clz(b.abs(x)))
+
+    def compare(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, (52,), "Y")
+        return b.logical_not(b.greater_equal(b.max(b.negative(x), y), b.fill_constant([1], 100, dtype=T.name)))
+
+    def choose(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        m = b.create_input(common.Bool(), shape, "M")
+        return b.select(m, b.min(x, y), b.relu(y))
+
+    def to_float(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        return b.cast(b.add(x, y), "float32")
+
+    def other_width(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        other = "int64" if bits == 32 else "int32"
+        return b.cast(b.multiply(x, y), other)
+
+    return [arith, divisions, bit_ops, counts, compare, choose, to_float, other_width]
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("index", range(8))
+def test_integer_chains_bit_exact(oracle, bits, index):
+    make = int_programs(bits)[index]
+    b = NetBuilder("int_%s_%d" % (make.__name__, bits))
+    y = make(b)
+    rng = np.random.default_rng(40 + index)
+    npt = np.int32 if bits == 32 else np.int64
+    lo, hi = (-2 ** 31, 2 ** 31 - 1) if bits == 32 else (-2 ** 63, 2 ** 63 - 1)
+    X = rng.integers(lo, hi, (37, 52), dtype=npt)
+    Y = rng.integers(-50, 50, (37, 52), dtype=npt) if make.__name__ == "divisions" else rng.integers(lo, hi, (37, 52), dtype=npt)
+    X[0, :4] = [lo, hi, 0, -1]
+    feeds = {"X": X, "Y": Y, "M": rng.random((37, 52)) > 0.5}
+    names = {n for d, _ in Computation.build_and_compile(TARGET, b, plan_only=True).groups() for n in
+             [l.split()[1] for l in d.splitlines() if l.startswith("input")]}
+    if make.__name__ in ("arith", "compare"):
+        feeds["Y"] = Y[0].copy()
+    feeds = {k: v for k, v in feeds.items() if k in names}
+    comp, out = run_program(b, feeds, [y])
+    assert all(p.split()[1].startswith("ew_chain_int_") for _, p in comp.groups()), comp.groups()
+    ref = oracle_program(comp, feeds)[str(y)]
+    got = out[str(y)]
+    assert got.dtype == ref.dtype and np.array_equal(got, ref), (make.__name__, comp.groups())
