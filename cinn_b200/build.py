@@ -23,6 +23,7 @@ SOURCES = [
     "rownorm_tma.cu",
     "ew_chain.cu",
     "ew_chain_int.cu",
+    "ew_chain_f64.cu",
     "ew_stream.cu",
     "reduce_static_scratch.cu",
     "peer_reduce.cu",

@@ -132,18 +132,36 @@ struct ChainBuilder {
   // The float form carries float32 / float16 / bfloat16 / bool values in fp32 registers; the integer form carries
   // values of ONE integer type (`compute`) and bool in registers of that type.
   bool int_class = false;
+  bool dbl_class = false;  // float64 values and bool in double registers; immediates through a table of doubles
   DType compute  = DType::kFloat32;
+  std::vector<double> dimms;
 
   ChainBuilder(const GroupDesc& g_, std::string* w) : g(g_), why(w) {}
 
   bool Ok(DType t) const {
     if (t == DType::kBool) return true;
+    if (dbl_class) return t == DType::kFloat64;
     return int_class ? t == compute : IsFloatType(t);
   }
+  // The type whose Mul + Add pairs contract into a fused multiply-add.
+  bool Arith(DType t) const { return dbl_class ? t == DType::kFloat64 : (!int_class && t == DType::kFloat32); }
   const std::map<std::string, int>& Unary() const { return int_class ? IntUnaryCodes() : UnaryCodes(); }
   const std::map<std::string, int>& Binary() const { return int_class ? IntBinaryCodes() : BinaryCodes(); }
   // A constant as the immediate field of a program word: an fp32 value, or (integer form) the bits of an int32.
   bool Imm(const std::string& text, float* out) {
+    if (dbl_class) {
+      const double d = atof(text.c_str());
+      int32_t idx    = -1;
+      for (size_t i = 0; i < dimms.size(); ++i)
+        if (memcmp(&dimms[i], &d, 8) == 0) idx = (int32_t)i;
+      if (idx < 0) {
+        if (dimms.size() >= 8) return false;
+        dimms.push_back(d);
+        idx = (int32_t)dimms.size() - 1;
+      }
+      memcpy(out, &idx, 4);
+      return true;
+    }
     if (!int_class) {
       *out = (float)atof(text.c_str());
       return true;
@@ -298,7 +316,7 @@ struct ChainBuilder {
       int64_t off  = (axis < 0 || sv->shape.size() == out_shape.size()) ? (int64_t)out_shape.size() - (int64_t)sv->shape.size() : axis;
       for (size_t i = 0; i < sv->shape.size(); ++i) axes.push_back(off + (int64_t)i);
     }
-    if (!Ok(sv->dtype) && !(IsIntType(sv->dtype) && src != name)) return false;
+    if (!Ok(sv->dtype) && !((IsIntType(sv->dtype) || (dbl_class && sv->dtype == DType::kFloat32)) && src != name)) return false;
     Side s;
     if (!SideSpec(sv->shape, axes, input_index[src], &s)) return false;
     int sel = AddSide(s);
@@ -313,6 +331,7 @@ struct ChainBuilder {
     if (p.type != "cast" || !input_index.count(p.inputs[0])) return false;
     const DType from = values[p.inputs[0]].dtype, to = values[p.output].dtype;
     if (int_class) return (IsIntType(from) || from == DType::kBool) && to == compute;  // widen / truncate / 0-1
+    if (dbl_class) return (from == DType::kFloat32 || IsIntType(from) || from == DType::kBool) && to == DType::kFloat64;
     if (IsIntType(from)) return to == DType::kFloat32;
     if (from == DType::kBool) return IsFloatType(to);
     if (from == DType::kFloat16 || from == DType::kBFloat16) return to == DType::kFloat32;
@@ -347,6 +366,7 @@ int DTypeKernelCode(DType t) {
     case DType::kBool: return EW_BOOL;
     case DType::kInt32: return EW_I32;
     case DType::kInt64: return EW_I64;
+    case DType::kFloat64: return EW_F64;
     default: return -1;
   }
 }
@@ -358,16 +378,22 @@ const char* DTypeKernelName(DType t) {
     case DType::kBool: return "bool";
     case DType::kInt32: return "i32";
     case DType::kInt64: return "i64";
+    case DType::kFloat64: return "f64";
     default: return nullptr;
   }
 }
 
 }  // namespace
 
-std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const DeviceInfo& dev, bool int_class,
+enum ChainClass { kFloatChain, kIntChain, kDoubleChain };
+
+std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const DeviceInfo& dev, ChainClass klass,
                                                  std::string* why) {
   ChainBuilder cb(g, why);
+  const bool int_class = klass == kIntChain, dbl_class = klass == kDoubleChain;
   cb.int_class = int_class;
+  cb.dbl_class = dbl_class;
+  if (dbl_class) cb.compute = DType::kFloat64;
   if (g.outputs.size() != 1) {
     cb.Fail("a chain has exactly one output");
     return nullptr;
@@ -382,6 +408,10 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   cb.out_shape = out.shape;
   if (!DTypeKernelName(out.dtype)) {
     cb.Fail(std::string("output dtype ") + DTypeName(out.dtype) + " is not supported by the chain kernel");
+    return nullptr;
+  }
+  if (dbl_class && out.dtype != DType::kFloat64 && out.dtype != DType::kFloat32 && out.dtype != DType::kBool) {
+    cb.Fail(std::string("a float64 chain cannot store ") + DTypeName(out.dtype));
     return nullptr;
   }
   if (int_class) {
@@ -425,11 +455,25 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
         rev.push_back(r);
       }
     };
-    const bool f32 = ov.dtype == DType::kFloat32;
+    const bool f32 = cb.Arith(ov.dtype);
     if (op.type == "cast") {
       const Value& iv = cb.values[op.inputs[0]];
       bool ok = false;
-      if (int_class) {
+      if (dbl_class) {
+        if (iv.dtype == DType::kFloat64 && ov.dtype == DType::kBool) {
+          ok = true;
+          Step r;
+          r.op  = EW_TO_BOOL;
+          r.f32 = false;
+          rev.push_back(r);
+        } else if (cb.Ok(iv.dtype) && cb.Ok(ov.dtype)) {
+          ok = true;  // bool -> float64 (0 / 1) or the same type
+        } else if (iv.dtype == DType::kFloat64 && ov.dtype == DType::kFloat32) {
+          ok = cur == out.name;  // the store rounds to float32
+        } else if ((iv.dtype == DType::kFloat32 || IsIntType(iv.dtype)) && ov.dtype == DType::kFloat64) {
+          ok = cb.input_index.count(op.inputs[0]) != 0;  // the load of the chain's input converts
+        }
+      } else if (int_class) {
         if (cb.Ok(iv.dtype) && ov.dtype == DType::kBool && iv.dtype != DType::kBool) {
           ok = true;
           Step r;
@@ -467,8 +511,11 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
       cb.Fail("scale on integers has no prebuilt kernel");
       return nullptr;
     } else if (op.type == "scale") {
-      const float s = (float)atof(ChainBuilder::Attr(op, "scale", "1").c_str());
-      const float b = (float)atof(ChainBuilder::Attr(op, "bias", "0").c_str());
+      float s = 0.0f, b = 0.0f;
+      if (!cb.Imm(ChainBuilder::Attr(op, "scale", "1"), &s) || !cb.Imm(ChainBuilder::Attr(op, "bias", "0"), &b)) {
+        cb.Fail("too many distinct constants for one chain");
+        return nullptr;
+      }
       const std::string bas = ChainBuilder::Attr(op, "bias_after_scale", "true");
       const bool after      = bas == "true" || bas == "1" || bas == "True";
       round_after();
@@ -489,7 +536,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
         Step s;
         s.op  = cb.Unary().at(op.type);
         s.f32 = f32;
-        if (op.type == "relu6") s.imm = (float)atof(ChainBuilder::Attr(op, "threshold", "6").c_str());
+        if (op.type == "relu6") cb.Imm(ChainBuilder::Attr(op, "threshold", "6"), &s.imm);
         if (s.op == EW_RELU && int_class) {  // max(x, 0) with an integer zero
           s.op = EW_MAX;
           cb.Imm("0", &s.imm);
@@ -502,7 +549,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
       const bool ca = cb.InGroupComputed(a), cbb = cb.InGroupComputed(b);
       Step s;
       s.op  = cb.Binary().at(op.type);
-      s.f32 = cb.values[a].dtype == DType::kFloat32;
+      s.f32 = cb.Arith(cb.values[a].dtype);
       std::string next;
       if (ca && cbb) {
         // Both computed in the group: only the "value with itself" form is a chain.
@@ -598,6 +645,10 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
     cb.Fail("an integer chain starts at an integer or bool input");
     return nullptr;
   }
+  if (!dbl_class && !int_class && in_type == DType::kFloat64) {
+    cb.Fail("float64 input");
+    return nullptr;
+  }
   if (DTypeKernelCode(in_type) < 0) {
     cb.Fail(std::string("input dtype ") + DTypeName(in_type) + " is not supported by the chain kernel");
     return nullptr;
@@ -649,7 +700,8 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   p->algorithmic_bytes += out.numel() * DTypeBytes(out.dtype);
   LaunchStep st;
   st.kernel = FindKernel(int_class ? std::string("ew_chain_int_") + DTypeKernelName(cb.compute) + "_" + DTypeKernelName(out.dtype)
-                                   : std::string("ew_chain_") + DTypeKernelName(out.dtype));
+                         : dbl_class ? std::string("ew_chain_f64_") + DTypeKernelName(out.dtype)
+                                     : std::string("ew_chain_") + DTypeKernelName(out.dtype));
   if (!st.kernel) {
     cb.Fail("chain kernel for these dtypes is not in the library");
     return nullptr;
@@ -688,21 +740,32 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   }
   st.args.push_back(int_arg((int64_t)words.size()));
   for (int k = 0; k < EW_MAX_STEPS; ++k) st.args.push_back(int_arg(k < (int)words.size() ? (int64_t)words[k] : 0));
+  if (dbl_class) {
+    for (int k = 0; k < 8; ++k) {
+      ArgSpec a;
+      a.kind   = ArgSpec::kFloat;
+      a.fvalue = k < (int)cb.dimms.size() ? cb.dimms[k] : 0.0;
+      st.args.push_back(a);
+    }
+  }
   p->steps.push_back(st);
   return p;
 }
 
 std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const DeviceInfo& dev, std::string* why) {
-  std::string why_float, why_int;
-  if (auto p = MatchChainOfClass(g, dev, false, &why_float)) return p;
-  bool has_int = false;
-  for (auto& t : g.inputs) has_int = has_int || IsIntType(t.dtype);
-  for (auto& t : g.outputs) has_int = has_int || IsIntType(t.dtype);
+  std::string why_float, why_other;
+  if (auto p = MatchChainOfClass(g, dev, kFloatChain, &why_float)) return p;
+  bool has_int = false, has_f64 = false;
+  for (auto& t : g.inputs) has_int = has_int || IsIntType(t.dtype), has_f64 = has_f64 || t.dtype == DType::kFloat64;
+  for (auto& t : g.outputs) has_int = has_int || IsIntType(t.dtype), has_f64 = has_f64 || t.dtype == DType::kFloat64;
+  if (why) *why = why_float;
+  if (has_f64) {
+    if (auto p = MatchChainOfClass(g, dev, kDoubleChain, &why_other)) return p;
+    if (why) *why += "; as a float64 chain: " + why_other;
+  }
   if (has_int) {
-    if (auto p = MatchChainOfClass(g, dev, true, &why_int)) return p;
-    if (why) *why = why_float + "; as an integer chain: " + why_int;
-  } else if (why) {
-    *why = why_float;
+    if (auto p = MatchChainOfClass(g, dev, kIntChain, &why_other)) return p;
+    if (why) *why += "; as an integer chain: " + why_other;
   }
   return nullptr;
 }

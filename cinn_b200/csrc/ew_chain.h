@@ -7,7 +7,8 @@
 // chain value (0: the condition, A = value if true, B = value if false; 1: the value if true, A = condition,
 // B = value if false; 2: the value if false, A = condition, B = value if true), bits 32-63 an fp32 immediate.
 // Values of type bool travel as 0.0f / 1.0f.  The integer form of the kernel (ew_chain_int.cu) uses the same words
-// with a signed 32-bit integer in bits 32-63; bool travels as 0 / 1.
+// with a signed 32-bit integer in bits 32-63; bool travels as 0 / 1.  The float64 form (ew_chain_f64.cu) keeps in
+// bits 32-63 an index into a table of eight double immediates.
 #pragma once
 
 namespace cinn_b200 {
@@ -37,7 +38,7 @@ enum EwOp {
 };
 
 // Storage types of the chain kernel's operands (runtime codes; the output type is a template parameter).
-enum EwDType { EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5 };
+enum EwDType { EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5, EW_F64 = 6 };
 
 // How a side input is addressed for the flat output index i: value = side[(i / inner) % mid].
 enum EwSideMode {

@@ -185,7 +185,7 @@ def evaluate(desc, inputs):
         p = producer.get(name)
         if p is None or name in outputs or name in feeds_reduce or uses.get(name, 0) != 1:
             return None
-        if p["type"] == "elementwise_mul" and vals[name].dtype == np.float32:
+        if p["type"] == "elementwise_mul" and vals[name].dtype in (np.float32, np.float64):
             return p
         return None
 
@@ -199,6 +199,9 @@ def evaluate(desc, inputs):
             to = NP[at["dtype"]]
             if x.dtype == to:
                 out = x
+            elif x.dtype == np.float64 or to == np.float64:
+                # float64 <-> float32 / integers / bool: one IEEE conversion (numpy rounds to nearest even)
+                out = (x != 0) if to == np.bool_ else x.astype(to)
             elif x.dtype.kind in "ib" and np.dtype(to).kind in "ib":
                 out = (x != 0) if to == np.bool_ else x.astype(to)   # widen / truncate / 0-1
             else:
@@ -221,10 +224,21 @@ def evaluate(desc, inputs):
             for i, ax in enumerate(axes):
                 view[ax] = x.shape[i]
             out = np.ascontiguousarray(np.broadcast_to(x.reshape(view), shape))
+        elif t == "scale" and vals[ins[0]].dtype == np.float64:
+            x = vals[ins[0]]
+            after = at.get("bias_after_scale", "true") in ("true", "1", "True")
+            sc, bi = np.full(1, float(at.get("scale", 1))), np.full(1, float(at.get("bias", 0)))
+            out = orc.fma_f64(sc, x, bi, x.shape) if after else orc.binary_f64("multiply", sc, orc.binary_f64("add", x, bi, x.shape), x.shape)
         elif t == "scale":
             x = vals[ins[0]]
             after = at.get("bias_after_scale", "true") in ("true", "1", "True")
             out = _store(orc.scale(_f32(x), float(at.get("scale", 1)), float(at.get("bias", 0)), after), x.dtype)
+        elif t in UNARY and vals[ins[0]].dtype == np.float64:
+            out = orc.unary_f64(t, vals[ins[0]])
+            out = (out != 0) if t in PREDICATES else out
+        elif t == "relu6" and vals[ins[0]].dtype == np.float64:
+            x = vals[ins[0]]
+            out = orc.binary_f64("min", orc.unary_f64("relu", x), np.full(1, float(at.get("threshold", 6))), x.shape)
         elif t in UNARY:
             x = vals[ins[0]]
             out = _store(orc.unary(t, _f32(x)), np.bool_ if t in PREDICATES else x.dtype)
@@ -244,7 +258,10 @@ def evaluate(desc, inputs):
             bb = b if b is big else _aligned(b, shape, axis)
             dt = np.dtype(np.bool_) if t in BOOL_RESULT else a.dtype
             done = False
-            if t == "elementwise_add" and dt == np.float32:
+            dbl = a.dtype == np.float64 or b.dtype == np.float64
+            if dbl:
+                aa, bb = np.ascontiguousarray(aa.astype(np.float64)), np.ascontiguousarray(bb.astype(np.float64))
+            if t == "elementwise_add" and dt in (np.float32, np.float64):
                 # lower_intrin.cc:45-50: the right operand is tried first
                 for mul_name, other in ((ins[1], aa), (ins[0], bb)):
                     m = inlined_mul(mul_name)
@@ -254,10 +271,13 @@ def evaluate(desc, inputs):
                         mbig = ma if ma.ndim >= mb.ndim else mb
                         ma2 = ma if ma is mbig else _aligned(ma, mbig.shape, maxis)
                         mb2 = mb if mb is mbig else _aligned(mb, mbig.shape, maxis)
-                        out = orc.fma(ma2, mb2, other, shape)
+                        out = orc.fma_f64(ma2, mb2, other, shape) if dbl else orc.fma(ma2, mb2, other, shape)
                         done = True
                         break
-            if not done:
+            if not done and dbl:
+                out = orc.binary_f64(BINARY[t], aa, bb, shape)
+                out = (out != 0) if t in BOOL_RESULT else out
+            elif not done:
                 out = _store(orc.binary(BINARY[t], _f32(aa), _f32(bb), shape), dt)
         elif t in REDUCE:
             x = vals[ins[0]]

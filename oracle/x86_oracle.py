@@ -82,7 +82,44 @@ def _spec(a, out_shape):
     return mid, inner
 
 
+def _f64(a):
+    a = np.ascontiguousarray(a)
+    assert a.dtype == np.float64, a.dtype
+    return a
+
+
+def unary_f64(op, x):
+    x = _f64(x)
+    y = np.empty_like(x)
+    lib().orc_unary_f64(UNARY[op], _p(x), _p(y), _i64(x.size))
+    return y
+
+
+def binary_f64(op, a, b, out_shape=None):
+    a, b = _f64(a), _f64(b)
+    if out_shape is None:
+        out_shape = np.broadcast_shapes(a.shape, b.shape)
+    y = np.empty(out_shape, np.float64)
+    am, ai = _spec(a, out_shape)
+    bm, bi = _spec(b, out_shape)
+    lib().orc_binary_f64(BINARY[op], _p(a), _i64(am), _i64(ai), _p(b), _i64(bm), _i64(bi), _p(y), _i64(y.size))
+    return y
+
+
+def fma_f64(a, b, c, out_shape=None):
+    a, b, c = _f64(a), _f64(b), _f64(c)
+    if out_shape is None:
+        out_shape = np.broadcast_shapes(a.shape, b.shape, c.shape)
+    y = np.empty(out_shape, np.float64)
+    sp = [_spec(t, out_shape) for t in (a, b, c)]
+    lib().orc_fma_f64(_p(a), _i64(sp[0][0]), _i64(sp[0][1]), _p(b), _i64(sp[1][0]), _i64(sp[1][1]), _p(c),
+                      _i64(sp[2][0]), _i64(sp[2][1]), _p(y), _i64(y.size))
+    return y
+
+
 def unary(op, x):
+    if np.asarray(x).dtype == np.float64:
+        return unary_f64(op, x)
     x = _f32(x)
     y = np.empty_like(x)
     lib().orc_unary_f32(UNARY[op], _p(x), _p(y), _i64(x.size))

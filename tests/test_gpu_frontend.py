@@ -447,3 +447,72 @@ def test_integer_chains_bit_exact(oracle, bits, index):
     ref = oracle_program(comp, feeds)[str(y)]
     got = out[str(y)]
     assert got.dtype == ref.dtype and np.array_equal(got, ref), (make.__name__, comp.groups())
+
+
+# ---- float64 chains ---------------------------------------------------------------------------------------------
+
+def f64_programs():
+    T = common.Float(64)
+    shape = (33, 76)
+
+    def affine(b):
+        x, v = b.create_input(T, shape, "X"), b.create_input(T, (76,), "V")
+        return b.add(b.multiply(b.scale(x, 0.1, 1e-5), v), v)       # fma(scale(x), v, v), constants not exact in fp32
+
+    def transcendental(b):
+        x = b.create_input(T, shape, "X")
+        return b.tanh(b.log(b.add(b.exp(b.negative(b.abs(x))), b.fill_constant([1], 1.0, dtype="float64"))))
+
+    def trig(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        return b.atan2(b.sin(x), b.cosh(y))
+
+    def compare_select(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        m = b.create_input(common.Bool(), shape, "M")
+        return b.select(m, b.sqrt(b.abs(x)), b.floor_divide(y, b.fill_constant([1], 0.3, dtype="float64")))
+
+    def to_float32(b):
+        x = b.create_input(T, shape, "X")
+        return b.cast(b.sigmoid(x), "float32")
+
+    def from_float32(b):
+        x = b.create_input(common.Float(32), shape, "X32")
+        y = b.create_input(T, shape, "Y")
+        return b.divide(b.cast(x, "float64"), b.relu6(y))
+
+    def predicate(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        return b.logical_not(b.less_equal(b.rsqrt(b.abs(x)), y))
+
+    return [affine, transcendental, trig, compare_select, to_float32, from_float32, predicate]
+
+
+@pytest.mark.parametrize("index", range(7))
+def test_float64_chains(oracle, index):
+    make = f64_programs()[index]
+    b = NetBuilder("f64_" + make.__name__)
+    y = make(b)
+    rng = np.random.default_rng(60 + index)
+    feeds = {"X": rng.standard_normal((33, 76)), "Y": rng.standard_normal((33, 76)) * 3, "V": rng.standard_normal(76),
+             "M": rng.random((33, 76)) > 0.5, "X32": rng.standard_normal((33, 76)).astype(np.float32)}
+    names = {n for d, _ in Computation.build_and_compile(TARGET, b, plan_only=True).groups() for n in
+             [l.split()[1] for l in d.splitlines() if l.startswith("input")]}
+    feeds = {k: v for k, v in feeds.items() if k in names}
+    comp, out = run_program(b, feeds, [y])
+    assert all(p.split()[1].startswith("ew_chain_f64_") for _, p in comp.groups()), comp.groups()
+    ref = oracle_program(comp, feeds)[str(y)]
+    got = out[str(y)]
+    assert got.dtype == ref.dtype
+    if got.dtype == np.bool_:
+        assert np.array_equal(got, ref)
+    else:
+        fin = np.isfinite(ref)
+        assert np.array_equal(np.isfinite(got), fin)
+        # 4 ulp, plus 4 ulp of 1.0 where the x86 tanh formula (1 - e) / (1 + e) cancels (as in the fp32 test above)
+        eps = 2.0 ** -52 if got.dtype == np.float64 else 2.0 ** -23
+        err = np.abs(got[fin].astype(np.float64) - ref[fin])
+        ulp = err / np.spacing(np.abs(ref[fin]).astype(got.dtype)).astype(np.float64)
+        print("%s: max distance %.2f ulp" % (make.__name__, ulp.max()))
+        slack = 4 * eps if make.__name__ == "transcendental" else 0.0
+        assert (err <= 4 * np.spacing(np.abs(ref[fin]).astype(got.dtype)).astype(np.float64) + slack).all(), float(ulp.max())
