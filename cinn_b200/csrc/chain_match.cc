@@ -701,7 +701,8 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   LaunchStep st;
   st.kernel = FindKernel(int_class ? std::string("ew_chain_int_") + DTypeKernelName(cb.compute) + "_" + DTypeKernelName(out.dtype)
                          : dbl_class ? std::string("ew_chain_f64_") + DTypeKernelName(out.dtype)
-                                     : std::string("ew_chain_") + DTypeKernelName(out.dtype));
+                                     : std::string("ew_chain_") + DTypeKernelName(out.dtype) + "_s" +
+                                           (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3")));
   if (!st.kernel) {
     cb.Fail("chain kernel for these dtypes is not in the library");
     return nullptr;

@@ -263,7 +263,8 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, float
   }
 }
 
-template <int VEC>
+// NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
+template <int VEC, int NS>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const float (&s1)[VEC],
                                           const float (&s2)[VEC], const float (&s3)[VEC], float (&acc)[VEC]) {
   for (int k = 0; k < nsteps; ++k) {
@@ -283,15 +284,15 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
     switch (asel) {  // one uniform branch per step instead of a select chain per element
       case 1:
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = s1[i];
+        for (int i = 0; i < VEC; ++i) o[i] = NS >= 1 ? s1[i] : imm;
         break;
       case 2:
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = s2[i];
+        for (int i = 0; i < VEC; ++i) o[i] = NS >= 2 ? s2[i] : imm;
         break;
       case 3:
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = s3[i];
+        for (int i = 0; i < VEC; ++i) o[i] = NS >= 3 ? s3[i] : imm;
         break;
       case 4:
 #pragma unroll
@@ -307,7 +308,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const float b = bsel == 1 ? s1[i] : (bsel == 2 ? s2[i] : (bsel == 3 ? s3[i] : imm2));
+        const float b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
         acc[i]        = fmaf(acc[i], o[i], b);
       }
       if (bsel == 0) ++k;
@@ -316,7 +317,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const float b = bsel == 1 ? s1[i] : (bsel == 2 ? s2[i] : (bsel == 3 ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        const float b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
         const float c = role == 0 ? acc[i] : o[i];
         const float t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
         const float f = role == 2 ? acc[i] : b;
@@ -336,8 +337,8 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
 }
 
 // meta: bits 0-3 dtype of side 1, 4-7 mode of side 1, 8-11 / 12-15 side 2, 16-19 / 20-23 side 3, 24-27 dtype of in0.
-template <typename OutT>
-__global__ void __launch_bounds__(256)
+template <typename OutT, int NS>
+__global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
     k_ew_chain(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
                const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
                long long mid1, long long inner1, long long mid2, long long inner2, long long mid3, long long inner3,
@@ -366,11 +367,11 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const long long i0 = (v + j * stride) << 2;
-        if (sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, *reinterpret_cast<float(*)[4]>(&s1[4 * j]));
-        if (sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, *reinterpret_cast<float(*)[4]>(&s2[4 * j]));
-        if (sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, *reinterpret_cast<float(*)[4]>(&s3[4 * j]));
+        if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, *reinterpret_cast<float(*)[4]>(&s1[4 * j]));
+        if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, *reinterpret_cast<float(*)[4]>(&s2[4 * j]));
+        if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, *reinterpret_cast<float(*)[4]>(&s3[4 * j]));
       }
-      run_chain<8>(steps, nsteps, s1, s2, s3, acc);
+      run_chain<8, NS>(steps, nsteps, s1, s2, s3, acc);
 #pragma unroll
       for (int j = 0; j < 2; ++j)
         store_vec4<OutT>(out, (v + j * stride) << 2, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
@@ -379,10 +380,10 @@ __global__ void __launch_bounds__(256)
       const long long i0 = v << 2;
       float acc[4], s1[4], s2[4], s3[4];
       load_vec4(in0, in_type, i0, true, acc);
-      if (sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
-      if (sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
-      if (sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
-      run_chain<4>(steps, nsteps, s1, s2, s3, acc);
+      if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
+      if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
+      if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
+      run_chain<4, NS>(steps, nsteps, s1, s2, s3, acc);
       store_vec4<OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -390,17 +391,20 @@ __global__ void __launch_bounds__(256)
   for (long long i = done + tid; i < n; i += stride) {
     float acc[1], s1[1], s2[1], s3[1];
     acc[0] = load_scalar(in0, in_type, i);
-    if (sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
-    if (sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
-    if (sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
-    run_chain<1>(steps, nsteps, s1, s2, s3, acc);
+    if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
+    if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
+    if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
+    run_chain<1, NS>(steps, nsteps, s1, s2, s3, acc);
     store_one<OutT>(out, i, acc[0]);
   }
 }
 
 }  // namespace
 
-#define REG_CHAIN(OUTNAME, OutT) CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME, 31, 256, k_ew_chain<OutT>)
+#define REG_CHAIN(OUTNAME, OutT)                                                               \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s0", 31, 256, k_ew_chain<OutT, 0>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s1", 31, 256, k_ew_chain<OutT, 1>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3", 31, 256, k_ew_chain<OutT, 3>)
 REG_CHAIN("f32", float);
 REG_CHAIN("f16", __half);
 REG_CHAIN("bf16", __nv_bfloat16);

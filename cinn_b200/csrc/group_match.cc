@@ -545,16 +545,40 @@ struct Matcher {
       }
       return p;
     }
-    LaunchStep s;
-    if (!Kernel(&s, "reduce_generic_col_" + suffix)) return nullptr;
+    // Columns: a thread per 16 bytes of columns.  With few columns the reduced axis is split over blockIdx.z into
+    // partial results in scratch, which a second launch of the same kernel folds.
+    auto col_step = [&](ArgSpec src, ArgSpec dst, int64_t o, int64_t len, int64_t in, int64_t splits,
+                        std::vector<int> align_in, bool dst_is_out) -> bool {
+      LaunchStep s;
+      if (!Kernel(&s, "reduce_generic_col_" + suffix)) return false;
+      const bool vec     = in % V == 0;
+      const int64_t cols = vec ? in / V : in;
+      s.block[0] = cols >= 256 ? 256 : (cols >= 128 ? 128 : 64);
+      s.grid[0]  = (unsigned)std::max<int64_t>(1, vec ? CeilDiv(cols, s.block[0]) : std::min<int64_t>(CeilDiv(cols, s.block[0]), (int64_t)sms * 8));
+      s.grid[1]  = (unsigned)std::min<int64_t>(o, 65535);
+      s.grid[2]  = (unsigned)splits;
+      ArgSpec al = Aligned(vec, align_in, dst_is_out ? std::vector<int>{0} : std::vector<int>{});
+      s.args     = {src, dst, I(o), I(len), I(in), I(CeilDiv(len, splits)), al};
+      p->steps.push_back(s);
+      return true;
+    };
     const bool vec     = inner % V == 0;
-    const int64_t cols = vec ? inner / V : inner;
-    s.block[0] = cols >= 256 ? 256 : (cols >= 128 ? 128 : 64);
-    s.grid[0]  = (unsigned)std::max<int64_t>(1, vec ? CeilDiv(cols, s.block[0]) : std::min<int64_t>(CeilDiv(cols, s.block[0]), (int64_t)sms * 8));
-    s.grid[1]  = (unsigned)std::min<int64_t>(outer, 65535);
-    ArgSpec al = Aligned(vec, {0}, {0});
-    s.args     = {In(0), Out(0), I(outer), I(r), I(inner), al};
-    p->steps.push_back(s);
+    const int64_t thr  = (vec ? inner / V : inner) * outer;
+    int64_t splits     = 1;
+    if (thr < (int64_t)sms * 512 && r >= 64 && x.numel() * esize >= (4 << 20)) {  // a second launch only pays on large inputs
+      splits = std::min<int64_t>(r / 16, CeilDiv((int64_t)sms * 1024, thr));
+      splits = std::max<int64_t>(1, std::min<int64_t>(splits, 512));
+    }
+    const int64_t rps = CeilDiv(r, splits);
+    splits            = CeilDiv(r, rps);
+    if (splits == 1) {
+      if (!col_step(In(0), Out(0), outer, r, inner, 1, {0}, true)) return nullptr;
+      return p;
+    }
+    const int64_t off = p->scratch_bytes;
+    p->scratch_bytes += (size_t)RoundUp(splits * outer * inner * esize, 256);
+    if (!col_step(In(0), Scratch(off), outer, r, inner, splits, {0}, false)) return nullptr;
+    if (!col_step(Scratch(off), Out(0), 1, splits, outer * inner, 1, {}, true)) return nullptr;
     return p;
   }
 

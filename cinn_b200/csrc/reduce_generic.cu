@@ -168,13 +168,16 @@ __global__ void __launch_bounds__(256)
 // ---- columns: y[o, c] = fold over x[o, 0..r, c] --------------------------------------------------------------------
 template <typename T, class Op>
 __global__ void __launch_bounds__(256)
-    k_reduce_generic_col(const T* __restrict__ x, T* __restrict__ y, long long outer, long long r, long long inner,
-                         long long vec_ok) {
+    k_reduce_generic_col(const T* __restrict__ x, T* __restrict__ y, long long outer, long long r_total,
+                         long long inner, long long rows_per_split, long long vec_ok) {
   using A         = typename Elem<T>::Acc;
   constexpr int V = 16 / sizeof(T);
+  // blockIdx.z = split of the reduced axis: rows [k0, k0 + r) go to partial result z (y holds [splits][outer][inner])
+  const long long k0 = (long long)blockIdx.z * rows_per_split;
+  const long long r  = min(rows_per_split, r_total - k0);
   for (long long o = blockIdx.y; o < outer; o += gridDim.y) {
-    const T* px = x + o * r * inner;
-    T* py       = y + o * inner;
+    const T* px = x + (o * r_total + k0) * inner;
+    T* py       = y + ((long long)blockIdx.z * outer + o) * inner;
     if (vec_ok) {  // inner % V == 0, 16-byte aligned bases
       const long long nv = inner / V;
       const long long c  = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -228,7 +231,7 @@ __global__ void __launch_bounds__(256)
 
 #define REG_GENERIC(OPNAME, OP, TNAME, T)                                                                       \
   CINN_B200_REGISTER_KERNEL("reduce_generic_row_" OPNAME "_" TNAME, 6, 256, k_reduce_generic_row<T, OP>);      \
-  CINN_B200_REGISTER_KERNEL("reduce_generic_col_" OPNAME "_" TNAME, 6, 256, k_reduce_generic_col<T, OP>)
+  CINN_B200_REGISTER_KERNEL("reduce_generic_col_" OPNAME "_" TNAME, 7, 256, k_reduce_generic_col<T, OP>)
 #define REG_GENERIC_ARITH(TNAME, T)   \
   REG_GENERIC("sum", GSum, TNAME, T);  \
   REG_GENERIC("prod", GProd, TNAME, T); \

@@ -94,7 +94,7 @@ def test_kernel_table_is_populated():
     names = {L.cinn_b200_kernel_name(i).decode() for i in range(n)}
     for k in ["ew_add_relu_f32", "ew_bias_scale_tanh_cast_f32_f16", "ew_bn_relu_nchw_f32", "row_reduce_warp8_sum_f32",
               "col_reduce_max_f32", "row_reduce_cluster_sum_f32", "softmax_row_f32_g256_v4_r1",
-              "layernorm_tma_f16_g256_v2", "rownorm_cluster_f32", "ew_chain_f16"]:
+              "layernorm_tma_f16_g256_v2", "rownorm_cluster_f32", "ew_chain_f16_s1"]:
         assert k in names, k
     assert L.cinn_b200_get_kernel(b"no_such_kernel") is None
     assert b"no_such_kernel" in L.cinn_b200_last_error()

@@ -136,7 +136,7 @@ def test_elementwise_producer_folds_into_reduction():
     x = b.create_input(common.Float(32), (64, 4096), "X")
     b.sqrt(b.divide(b.reduce_sum(b.multiply(x, b.identity(x)), [1]), b.fill_constant([64], 4096.0)))
     c = plan(b)
-    assert [p for _, p in c.groups()] == ["row_reduce row_reduce_cta_sumsq_f32", "ew_chain ew_chain_f32"]
+    assert [p for _, p in c.groups()] == ["row_reduce row_reduce_cta_sumsq_f32", "ew_chain ew_chain_f32_s0"]
 
 
 def test_value_used_twice_is_materialised_once():
@@ -215,3 +215,43 @@ def test_host_x86_target_is_refused():
     b.relu(x)
     with pytest.raises(RuntimeError):
         Computation.build_and_compile(common.DefaultHostTarget(), b)
+
+
+def test_other_dtypes_pick_their_kernel_families():
+    """float64 / integer / bool groups are planned onto the double, integer and typed-reduction kernels."""
+    def one(make):
+        b = NetBuilder("p")
+        make(b)
+        return [p for _, p in plan(b).groups()]
+
+    i32, i64, f64, f16 = common.Int(32), common.Int(64), common.Float(64), common.Float(16)
+    assert one(lambda b: b.abs(b.add(b.create_input(i32, (8, 64), "X"), b.create_input(i32, (64,), "Y")))) == \
+        ["ew_chain ew_chain_int_i32_i32"]
+    assert one(lambda b: b.cast(b.bitwise_and(b.create_input(i64, (8, 64), "X"), b.create_input(i64, (8, 64), "Y")),
+                                "int32")) == ["ew_chain ew_chain_int_i64_i32"]
+    assert one(lambda b: b.less_than(b.create_input(i32, (8, 64), "X"), b.create_input(i32, (8, 64), "Y"))) == \
+        ["ew_chain ew_chain_int_i32_bool"]
+    assert one(lambda b: b.tanh(b.create_input(f64, (8, 64), "X"))) == ["ew_chain ew_chain_f64_f64"]
+    assert one(lambda b: b.cast(b.floor(b.create_input(common.Float(32), (8, 64), "X")), "int64")) == \
+        ["ew_chain ew_chain_i64_s0"]
+    assert one(lambda b: b.select(b.create_input(common.Bool(), (8, 64), "M"), b.create_input(f16, (8, 64), "X"),
+                                  b.create_input(f16, (8, 64), "Y"))) == ["ew_chain ew_chain_f16_s3"]
+    assert one(lambda b: b.reduce_sum(b.create_input(i32, (8, 64), "X"), [1])) == \
+        ["row_reduce reduce_generic_row_sum_i32"]
+    assert one(lambda b: b.reduce_max(b.create_input(f16, (8, 64, 32), "X"), [1])) == \
+        ["col_reduce reduce_generic_col_max_f16"]
+    assert one(lambda b: b.reduce_all(b.create_input(common.Bool(), (8, 64), "X"), [1])) == \
+        ["row_reduce reduce_generic_row_all_bool"]
+    assert one(lambda b: b.reduce_any(b.create_input(common.Bool(), (8, 64), "X"), [0])) == \
+        ["col_reduce reduce_generic_col_any_bool"]
+
+
+def test_operand_type_rules_of_the_new_ops():
+    b = NetBuilder("bad")
+    x = b.create_input(common.Float(32), (4, 4), "X")
+    m = b.create_input(common.Bool(), (4, 4), "M")
+    for make in (lambda: b.logical_and(x, x), lambda: b.logical_not(x), lambda: b.reduce_all(x, [0]),
+                 lambda: b.popc(x), lambda: b.select(x, x, x)):
+        with pytest.raises(Exception):
+            make()
+    assert b.isnan(x)._info()[0] == "bool" and b.logical_xor(m, m)._info()[0] == "bool"
