@@ -177,6 +177,12 @@ def graph_launch_us(group, tensors, torch, launches=100, replays=20):
     return e0.elapsed_time(e1) * 1e3 / (launches * replays)
 
 
+def TORCH_OF_NUMPY(torch):
+    return {np.dtype(np.float32): torch.float32, np.dtype(np.float16): torch.float16,
+            np.dtype(np.float64): torch.float64, np.dtype(np.int32): torch.int32, np.dtype(np.int64): torch.int64,
+            np.dtype(np.bool_): torch.bool}
+
+
 def side_groups(torch, dev, peak, only=None):
     """Per-group throughput of the other fused groups (device-resident inputs, kernel time only)."""
     import cinn_b200
@@ -187,8 +193,7 @@ def side_groups(torch, dev, peak, only=None):
         sets = []
         for _ in range(reps):
             ins = [torch.from_numpy(a).to(dev) for a in w.inputs]
-            o = torch.empty(w.out_shape, dtype={np.dtype(np.float32): torch.float32,
-                                                np.dtype(np.float16): torch.float16}[np.dtype(w.out_dtype)], device=dev)
+            o = torch.empty(w.out_shape, dtype=TORCH_OF_NUMPY(torch)[np.dtype(w.out_dtype)], device=dev)
             sets.append(ins + [o])
         return sets
 
@@ -204,6 +209,17 @@ def side_groups(torch, dev, peak, only=None):
         ("layer_norm_f16_16384x4096", lambda: W.layer_norm((16384, 4096), half=True), 2, ""),
         ("bn_relu_f32_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112)), 1, ""),
         ("bn_relu_f16_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112), half=True), 1, ""),
+        # the generic families: any other elementwise chain / element type (interpreted program, not a dedicated kernel)
+        ("generic_chain_abs_add_f32_8192x8192", lambda: W.generic_chain("abs_add_f32"), 1, "generic chain kernel"),
+        ("generic_chain_select_f32_8192x8192", lambda: W.generic_chain("select_f32"), 1, "generic chain kernel"),
+        ("generic_chain_greater_than_f32_8192x8192", lambda: W.generic_chain("greater_than_f32"), 1, "generic chain kernel"),
+        ("generic_chain_abs_add_i32_8192x8192", lambda: W.generic_chain("abs_add_i32"), 1, "generic integer chain kernel"),
+        ("generic_chain_affine_f64_8192x8192", lambda: W.generic_chain("affine_f64"), 1, "generic float64 chain kernel"),
+        ("generic_reduce_sum_f16_rows_16384x8192", lambda: W.generic_reduce("sum", "float16", axis=1), 2, ""),
+        ("generic_reduce_sum_f16_cols_16384x8192", lambda: W.generic_reduce("sum", "float16", axis=0), 2, ""),
+        ("generic_reduce_max_i32_rows_16384x8192", lambda: W.generic_reduce("max", "int32", axis=1), 1, ""),
+        ("generic_reduce_sum_i32_cols_16384x8192", lambda: W.generic_reduce("sum", "int32", axis=0), 1, ""),
+        ("generic_reduce_all_bool_rows_16384x8192", lambda: W.generic_reduce("all", "bool", axis=1), 4, ""),
     ]
     for name, make, reps, note in plan:
         if only and not any(o in name for o in only):
@@ -238,6 +254,11 @@ PROFILE_GROUPS = {
     "layer_norm_f16": lambda W: W.layer_norm((16384, 4096), half=True),
     "bn_relu_f32": lambda W: W.bn_relu((256, 64, 112, 112)),
     "bn_relu_f16": lambda W: W.bn_relu((256, 64, 112, 112), half=True),
+    "chain_abs_add_f32": lambda W: W.generic_chain("abs_add_f32"),
+    "chain_select_f32": lambda W: W.generic_chain("select_f32"),
+    "chain_abs_add_i32": lambda W: W.generic_chain("abs_add_i32"),
+    "reduce_sum_f16_rows": lambda W: W.generic_reduce("sum", "float16", axis=1),
+    "reduce_sum_i32_cols": lambda W: W.generic_reduce("sum", "int32", axis=0),
 }
 
 
@@ -252,9 +273,8 @@ def run_profile_case(args):
     dev = torch.device("cuda", 0)
     w = PROFILE_GROUPS[args.profile](W)
     g = cinn_b200.FusedGroup(w.desc)
-    tmap = {np.dtype(np.float32): torch.float32, np.dtype(np.float16): torch.float16}
     ins = [torch.from_numpy(a).to(dev) for a in w.inputs]
-    out = torch.empty(w.out_shape, dtype=tmap[np.dtype(w.out_dtype)], device=dev)
+    out = torch.empty(w.out_shape, dtype=TORCH_OF_NUMPY(torch)[np.dtype(w.out_dtype)], device=dev)
     g.run(ins + [out])  # status-checked first launch
     ms = time_group(g, [ins + [out]], iters=max(args.steps, 1), warmup=max(args.warmup, 1), torch=torch)
     print(json.dumps({"profile": args.profile, "kernels": g.kernel_names(), "ms": ms,

@@ -207,3 +207,47 @@ def bn_relu(shape=(256, 64, 112, 112), seed=4, half=False, eps=1e-5, name=None):
             f"op batch_norm var_0 = X scale bias mean variance ; {attrs}\n"
             f"op relu var_1 = var_0\noutput var_1 float32 {s}\n")
     return Workload("bn_relu_f32", desc, gen, np.float32, shape)
+
+
+# ---- groups of the generic kernel families (elementwise chains of any op / type, typed reductions) ----------------
+
+_NP = {"float32": np.float32, "float16": np.float16, "float64": np.float64, "int32": np.int32, "int64": np.int64,
+       "bool": np.bool_}
+
+
+def _draw(rng, shape, dtype):
+    if dtype in ("int32", "int64"):
+        return rng.integers(-1000, 1000, shape).astype(_NP[dtype])
+    if dtype == "bool":
+        return rng.random(shape) > 0.5
+    return rng.standard_normal(shape, dtype=np.float32).astype(_NP[dtype])
+
+
+def generic_chain(kind, shape=(8192, 8192), seed=5):
+    """Elementwise groups that only the generic chain kernels cover.  kind: leaky_relu_f32 (select on a mask
+    input), abs_add_f32, greater_than_f32 (bool output), abs_add_i32, affine_f64."""
+    s = _shape(shape)
+    table = {
+        "abs_add_f32": (["A float32", "B float32"], ["op elementwise_add t0 = A B", "op abs t1 = t0"], "t1", "float32"),
+        "select_f32": (["M bool", "A float32", "B float32"], ["op select t0 = M A B"], "t0", "float32"),
+        "greater_than_f32": (["A float32", "B float32"], ["op greater_than t0 = A B"], "t0", "bool"),
+        "abs_add_i32": (["A int32", "B int32"], ["op elementwise_add t0 = A B", "op abs t1 = t0"], "t1", "int32"),
+        "affine_f64": (["A float64"], ["op scale t0 = A ; scale=0.1 bias=1e-05", "op abs t1 = t0"], "t1", "float64"),
+    }
+    ins, ops, out, out_dtype = table[kind]
+    desc = "group fn_chain_%s\n%s\n%s\noutput %s %s %s\n" % (
+        kind, "\n".join("input %s %s" % (i, s) for i in ins), "\n".join(ops), out, out_dtype, s)
+
+    def gen():
+        rng = np.random.default_rng(seed)
+        return [_draw(rng, shape, i.split()[1]) for i in ins]
+    return Workload("chain_" + kind, desc, gen, _NP[out_dtype], shape)
+
+
+def generic_reduce(kind, dtype, shape=(16384, 8192), axis=1, seed=6):
+    """reduce_<kind> of a tensor of one of the other element types over one axis of a 2-D shape."""
+    out_shape = tuple(d for i, d in enumerate(shape) if i != axis)
+    desc = ("group fn_reduce_%s_%s_axis%d\ninput X %s %s\nop reduce_%s var_0 = X ; dim=%d keep_dim=false\n"
+            "output var_0 %s %s\n" % (kind, dtype, axis, dtype, _shape(shape), kind, axis, dtype, _shape(out_shape)))
+    return Workload("reduce_%s_%s" % (kind, dtype), desc, lambda: [_draw(np.random.default_rng(seed), shape, dtype)],
+                    _NP[dtype], out_shape)
