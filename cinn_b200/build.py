@@ -19,6 +19,7 @@ SOURCES = [
     "ew_kernels.cu",
     "reduce_kernels.cu",
     "reduce_generic.cu",
+    "channel_reduce.cu",
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
     "ew_chain.cu",

@@ -137,7 +137,10 @@ CINN_B200_REGISTER_KERNEL("ew_bias_scale_tanh_cast_f32_f32", 8, 256, k_bias_scal
 // the parameters are fp32.  A CTA owns one chunk of one (n, c) plane, so the channel index and the four
 // parameters are computed once per CTA.  vec_ok != 0: x and out are 16-byte aligned and hw % (16/sizeof(T)) == 0.
 // ------------------------------------------------------------------------------------------------
-template <typename T, bool RELU>
+// TRAIN: the normalisation step of the decomposed batch_norm_train (cinn/frontend/decomposer/batch_norm.cc:160-166),
+// y = ((x - mean) * rsqrt(var + eps)) * scale + bias with mean / var the batch statistics: rsqrt is 1 / sqrt, the last
+// multiply and add contract to one fused multiply-add (cinn/optim/lower_intrin.cc:41-59).
+template <typename T, bool RELU, bool TRAIN = false>
 __global__ void __launch_bounds__(256)
     k_bn_nchw(const T* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ bias,
               const float* __restrict__ mean, const float* __restrict__ var, T* __restrict__ y, long long planes,
@@ -173,7 +176,8 @@ __global__ void __launch_bounds__(256)
             Io<T>::unpack(r[j], f);
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-              f[i] = sizeof(T) == 2 ? ((f[i] - m) * s) * inv_d + b : ((f[i] - m) * s) / d + b;
+              if (TRAIN) f[i] = fmaf((f[i] - m) * inv_d, s, b);
+              else f[i] = sizeof(T) == 2 ? ((f[i] - m) * s) * inv_d + b : ((f[i] - m) * s) / d + b;
               if (RELU) f[i] = x86_max(f[i], 0.0f);
             }
             st_stream16(yp + (long long)(v + j * B) * V, Io<T>::pack(f));
@@ -186,7 +190,8 @@ __global__ void __launch_bounds__(256)
       const long long end   = min(begin + per, hw);
       for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
         float f = Io<T>::load1(xp + i);
-        f       = sizeof(T) == 2 ? ((f - m) * s) * inv_d + b : ((f - m) * s) / d + b;
+        if (TRAIN) f = fmaf((f - m) * inv_d, s, b);
+        else f = sizeof(T) == 2 ? ((f - m) * s) * inv_d + b : ((f - m) * s) / d + b;
         if (RELU) f = x86_max(f, 0.0f);
         Io<T>::store1(yp + i, f);
       }
@@ -197,5 +202,7 @@ CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f32", 12, 256, k_bn_nchw<float, true>
 CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true>);
 CINN_B200_REGISTER_KERNEL("ew_bn_nchw_f32", 12, 256, k_bn_nchw<float, false>);
 CINN_B200_REGISTER_KERNEL("ew_bn_nchw_f16", 12, 256, k_bn_nchw<__half, false>);
+CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_nchw_f32", 12, 256, k_bn_nchw<float, false, true>);
+CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_relu_nchw_f32", 12, 256, k_bn_nchw<float, true, true>);
 
 }  // namespace cinn_b200

@@ -385,8 +385,8 @@ struct FusionState {
 
   bool Compiles(const std::set<int>& members, FusedGroupInfo* out, std::string* why) const {
     FusedGroupInfo g = Describe(members);
-    if (g.desc.outputs.size() != 1) {
-      if (why) *why = "group would have " + std::to_string(g.desc.outputs.size()) + " outputs";
+    if (g.desc.outputs.empty()) {
+      if (why) *why = "group would have no output";
       return false;
     }
     std::string err;
@@ -505,6 +505,33 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
           if (closure.size() > trial.size() && st.Compiles(closure, nullptr, nullptr)) {
             members = closure;
             grew    = true;
+            continue;
+          }
+          // Last attempt: everything upstream of the whole group that is used only inside it, at once.  Some
+          // compositions only have a kernel as a whole (the normalisation of batch_norm_train needs x - mean and
+          // rsqrt(var + eps) together; either alone leaves too many full-size operands).
+          std::set<int> big = trial;
+          added             = true;
+          while (added && big.size() < trial.size() + 32) {
+            added = false;
+            for (int m2 : std::set<int>(big)) {
+              for (int v2 : b.instrs()[m2].inputs) {
+                int q = st.producer_of_var[v2];
+                if (q < 0 || big.count(q) || group_of[q] >= 0 || st.IsConst(q)) continue;
+                if (PatternOf(b.instrs()[q].op_type) == OpPattern::kNonFusible) continue;
+                if (st.fetch.count(b.instrs()[q].output)) continue;
+                bool inside = true;
+                for (int c : st.consumers_of_var[b.instrs()[q].output])
+                  if (!big.count(c)) inside = false;
+                if (!inside) continue;
+                big.insert(q);
+                added = true;
+              }
+            }
+          }
+          if (big.size() > closure.size() && st.Compiles(big, nullptr, nullptr)) {
+            members = big;
+            grew    = true;
           }
         }
       }
@@ -513,10 +540,66 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
     sets.push_back(members);
   }
 
-  // Emit in topological order of the groups' first instruction; every group must compile.
-  std::vector<int> order(sets.size());
-  for (size_t i = 0; i < sets.size(); ++i) order[i] = (int)i;
-  std::sort(order.begin(), order.end(), [&](int x, int y) { return *sets[x].rbegin() < *sets[y].rbegin(); });
+  // Step 3: horizontal fusion of reduction groups that read the same tensor and do not depend on one another
+  // (cinn/hlir/pass/fusion_merge_pass.cc:85-460), kept when a kernel exists for the merged, multi-output group:
+  // the two channel reductions of batch_norm_train become one pass over x.
+  {
+    auto is_reduce_group = [&](const std::set<int>& m) {
+      for (int i : m)
+        if (PatternOf(b.instrs()[i].op_type) == OpPattern::kReduction) return true;
+      return false;
+    };
+    for (size_t i = 0; i < sets.size(); ++i) {
+      if (sets[i].empty() || !is_reduce_group(sets[i])) continue;
+      const FusedGroupInfo gi = st.Describe(sets[i]);
+      if (gi.input_vars.size() != 1) continue;
+      for (size_t j = i + 1; j < sets.size(); ++j) {
+        if (sets[j].empty() || !is_reduce_group(sets[j])) continue;
+        const FusedGroupInfo gj = st.Describe(sets[j]);
+        if (gj.input_vars != gi.input_vars) continue;
+        std::set<int> merged = sets[i];
+        merged.insert(sets[j].begin(), sets[j].end());
+        if (!st.Compiles(merged, nullptr, nullptr)) continue;
+        for (int k : sets[j]) group_of[k] = (int)i;
+        sets[i] = merged;
+        sets[j].clear();
+        break;
+      }
+    }
+  }
+
+  // Emit in a topological order of the groups (a group after the groups that produce its inputs), ties by program
+  // order; every group must compile.
+  std::vector<int> order;
+  {
+    const int ng = (int)sets.size();
+    std::vector<std::set<int>> deps(ng);
+    for (int gidx = 0; gidx < ng; ++gidx)
+      for (int i : sets[gidx])
+        for (int v : b.instrs()[i].inputs) {
+          const int p = st.producer_of_var[v];
+          if (p >= 0 && group_of[p] >= 0 && group_of[p] != gidx) deps[gidx].insert(group_of[p]);
+        }
+    std::vector<bool> done(ng, false);
+    for (int emitted = 0; emitted < ng;) {
+      int pick = -1;
+      for (int gidx = 0; gidx < ng; ++gidx) {
+        if (done[gidx]) continue;
+        if (sets[gidx].empty()) {
+          done[gidx] = true;
+          ++emitted;
+          continue;
+        }
+        bool ready = true;
+        for (int d : deps[gidx]) ready = ready && done[d];
+        if (ready && (pick < 0 || *sets[gidx].begin() < *sets[pick].begin())) pick = gidx;
+      }
+      if (pick < 0) break;  // only empty sets were left
+      done[pick] = true;
+      ++emitted;
+      order.push_back(pick);
+    }
+  }
   groups->clear();
   for (int gi : order) {
     FusedGroupInfo info;

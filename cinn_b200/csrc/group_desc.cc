@@ -162,8 +162,8 @@ std::string CanonicalExpr(const GroupDesc& g, std::string* err) {
   for (size_t i = 0; i < g.inputs.size(); ++i) input_index[g.inputs[i].name] = (int)i;
   std::map<std::string, const OpDesc*> producer;
   for (auto& op : g.ops) producer[op.output] = &op;
-  if (g.outputs.size() != 1) {
-    if (err) *err = "canonical expression needs exactly one output, group has " + std::to_string(g.outputs.size());
+  if (g.outputs.empty()) {
+    if (err) *err = "group has no output";
     return "";
   }
   bool ok = true;
@@ -188,7 +188,9 @@ std::string CanonicalExpr(const GroupDesc& g, std::string* err) {
     }
     return s + ")";
   };
-  std::string s = print(g.outputs[0].name, 0);
+  // Several outputs: their expressions in output order, separated by ';'.
+  std::string s;
+  for (size_t i = 0; i < g.outputs.size(); ++i) s += (i ? ";" : "") + print(g.outputs[i].name, 0);
   return ok ? s : "";
 }
 

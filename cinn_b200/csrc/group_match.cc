@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <functional>
+#include <regex>
 #include <set>
 #include <sstream>
 
@@ -303,6 +304,60 @@ struct Matcher {
     return p;
   }
 
+  // The normalisation group of the decomposed batch_norm_train (cinn/frontend/decomposer/batch_norm.cc:155-166):
+  // add(mul(mul(sub(x, bc(mean)), rsqrt(add(bc(var), eps))), bc(scale)), bc(bias)), optionally under a relu.
+  // Whatever the numbering of the inputs, the five operands are picked out of the expression.
+  std::unique_ptr<CompiledGroup> MatchBnTrainApply(const std::string& expr) {
+    static const std::regex form(
+        R"(^(relu\()?elementwise_add\(elementwise_mul\(elementwise_mul\(subtract\(%(\d),broadcast_to\(%(\d)\)\),)"
+        R"(rsqrt\(elementwise_add\(broadcast_to\(%(\d)\),fill_constant\(\)\)\)\),broadcast_to\(%(\d)\)\),broadcast_to\(%(\d)\)\)(\))?$)");
+    std::smatch m;
+    if (!std::regex_match(expr, m, form) || g.inputs.size() != 5) return nullptr;
+    const bool relu = m[1].matched;
+    if (relu != m[7].matched) return nullptr;
+    const int ix = atoi(m[2].str().c_str()), im = atoi(m[3].str().c_str()), iv = atoi(m[4].str().c_str()),
+              is = atoi(m[5].str().c_str()), ib = atoi(m[6].str().c_str());
+    const std::set<int> distinct = {ix, im, iv, is, ib};
+    if (distinct.size() != 5 || *distinct.rbegin() > 4) return nullptr;
+    const auto &x = g.inputs[ix], &o = g.outputs[0];
+    if (x.shape.size() != 4 || o.shape != x.shape || x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32) return nullptr;
+    const int64_t N = x.shape[0], C = x.shape[1], HW = x.shape[2] * x.shape[3];
+    for (int i : {im, iv, is, ib})
+      if (g.inputs[i].dtype != DType::kFloat32 || g.inputs[i].numel() != C) return nullptr;
+    double eps = 0.0;
+    bool have_eps = false;
+    for (auto& op : g.ops) {
+      if (op.type == "broadcast_to") {
+        const std::vector<int64_t> axes = AttrList(op, "broadcast_axes");
+        if (axes != std::vector<int64_t>{1}) {
+          Fail("batch_norm_train parameters must be broadcast along axis 1 (NCHW)");
+          return nullptr;
+        }
+      } else if (op.type == "rsqrt") {
+        const OpDesc* add = Producer(op.inputs[0]);
+        for (auto& in : add->inputs)
+          if (const OpDesc* fc = ProducerOfType(in, "fill_constant")) {
+            eps      = (float)AttrF(*fc, "value", 1e-5);
+            have_eps = true;
+          }
+      }
+    }
+    if (!have_eps) return nullptr;
+    auto p = NewPlan(relu ? "ew_bn_train_apply_relu_nchw" : "ew_bn_train_apply_nchw");
+    const int64_t planes = N * C;
+    const int64_t units  = HW % 4 == 0 ? HW / 4 : HW;
+    int64_t chunks       = std::max<int64_t>(1, (units + 512) / 1024);
+    while (planes * chunks < (int64_t)dev.sm_count * 4 && units / (chunks * 2) >= 256) chunks *= 2;
+    LaunchStep s;
+    if (!Kernel(&s, std::string(relu ? "ew_bn_train_apply_relu_nchw_f32" : "ew_bn_train_apply_nchw_f32"))) return nullptr;
+    s.block[0] = 256;
+    s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(planes * chunks, (int64_t)dev.sm_count * 64));
+    s.args     = {In(ix), In(is), In(ib), In(im), In(iv), Out(0), I(planes), I(C), I(HW), I(chunks),
+                  Aligned(HW % 4 == 0, {ix}, {0}), F(eps)};
+    p->steps.push_back(s);
+    return p;
+  }
+
   // ---- reduce_{sum,prod,max,min}(%0) -----------------------------------------------------------
   // cinn/hlir/op/reduction.cc:49-158 (dim normalisation: negative dims wrap, empty = all), cinn/hlir/pe/reduction.cc.
   static bool ReduceView(const std::vector<int64_t>& shape, std::vector<int64_t> dims, int64_t* outer, int64_t* r,
@@ -337,6 +392,54 @@ struct Matcher {
         else *inner *= ext[i];
       }
     }
+    return true;
+  }
+
+  // x viewed as [A, B, I] with the axes of A and I reduced and those of B kept (extent-1 axes ignored): the
+  // reduced axes form a leading and a trailing block, e.g. dims {0, 2, 3} of an NCHW tensor.
+  static bool MidKeepView(const std::vector<int64_t>& shape, std::vector<int64_t> dims, int64_t* A, int64_t* B,
+                          int64_t* I) {
+    const int nd = (int)shape.size();
+    for (auto& d : dims)
+      if (d < 0) d += nd;
+    std::sort(dims.begin(), dims.end());
+    *A = *B = *I = 1;
+    int state    = 0;  // 0 leading reduced block, 1 kept block, 2 trailing reduced block
+    for (int i = 0; i < nd; ++i) {
+      if (shape[i] == 1) continue;
+      const bool red = std::binary_search(dims.begin(), dims.end(), (int64_t)i);
+      if (state == 0 && !red) state = 1;
+      else if (state == 1 && red) state = 2;
+      else if (state == 2 && !red) return false;
+      (state == 0 ? *A : (state == 1 ? *B : *I)) *= shape[i];
+    }
+    return state == 2 && *A > 1;
+  }
+
+  // First pass of a middle-axis-keeping reduction into scratch partials [splits][B] (per accumulation), then a
+  // column reduction over the splits.  opname2 != nullptr: the dual kernel (sum and sum of squares).
+  bool PlanMidKeep(CompiledGroup* p, const char* opname, bool dual, int64_t A, int64_t B, int64_t I, ArgSpec dst,
+                   ArgSpec dst2) {
+    const int sms        = dev.sm_count;
+    const bool vec       = I % 4 == 0;
+    const int64_t units  = vec ? I / 4 : I;
+    const int64_t chunks = std::max<int64_t>(1, (units + 2048) / 4096);  // about 4096 vectors per work item
+    const int64_t items  = A * chunks;
+    int64_t splits       = std::max<int64_t>(1, std::min<int64_t>(items, CeilDiv((int64_t)sms * 8, B)));
+    const int64_t off1   = p->scratch_bytes;
+    p->scratch_bytes += (size_t)RoundUp(splits * B * 4, 256);
+    const int64_t off2 = p->scratch_bytes;
+    if (dual) p->scratch_bytes += (size_t)RoundUp(splits * B * 4, 256);
+    LaunchStep s;
+    if (!Kernel(&s, dual ? std::string("mid_keep_reduce_sum_sumsq_f32") : std::string("mid_keep_reduce_") + opname + "_f32"))
+      return false;
+    s.block[0] = 256;
+    s.grid[0]  = (unsigned)(B * splits);
+    s.args     = {In(0), Scratch(off1), Scratch(dual ? off2 : off1), this->I(A), this->I(B), this->I(I), this->I(chunks), this->I(splits),
+                  Aligned(vec, {0}, {})};
+    p->steps.push_back(s);
+    if (!PlanReduce(p, BaseReduceOp(opname), 1, splits, B, Scratch(off1), dst, {})) return false;
+    if (dual && !PlanReduce(p, "sum", 1, splits, B, Scratch(off2), dst2, {})) return false;
     return true;
   }
 
@@ -462,7 +565,15 @@ struct Matcher {
     const OpDesc* op = Producer(o.name);
     int64_t outer, r, inner;
     if (!ReduceView(x.shape, AttrList(*op, "dim"), &outer, &r, &inner)) {
-      Fail("reduce over non-adjacent axes has no prebuilt kernel");
+      int64_t A, B, I;
+      if (MidKeepView(x.shape, AttrList(*op, "dim"), &A, &B, &I) && o.numel() == B &&
+          FindKernel(std::string("mid_keep_reduce_") + it->second + "_f32")) {
+        auto p      = NewPlan("mid_keep_reduce");
+        p->elements = x.numel();
+        if (!PlanMidKeep(p.get(), it->second, false, A, B, I, Out(0), Out(0))) return nullptr;
+        return p;
+      }
+      Fail("reduce over these non-adjacent axes has no prebuilt kernel");
       return nullptr;
     }
     if (o.numel() != outer * inner) {
@@ -472,6 +583,31 @@ struct Matcher {
     auto p      = NewPlan(inner == 1 ? "row_reduce" : "col_reduce");
     p->elements = x.numel();
     if (!PlanReduce(p.get(), it->second, outer, r, inner, In(0), Out(0), {0})) return nullptr;
+    return p;
+  }
+
+  // The two-output group {reduce_sum(x), reduce_sum(x * x)} over the same leading + trailing axes: the statistics
+  // pass of batch_norm_train (cinn/frontend/decomposer/batch_norm.cc:60-92), one read of x.
+  std::unique_ptr<CompiledGroup> MatchChannelStats(const std::string& expr) {
+    static const std::set<std::string> forms = {
+        "reduce_sum(%0);reduce_sum(elementwise_mul(%0,identity(%0)))", "reduce_sum(%0);reduce_sum(elementwise_mul(%0,%0))",
+        "reduce_sum(%0);reduce_sum(elementwise_mul(identity(%0),%0))"};
+    if (!forms.count(expr) || g.inputs.size() != 1 || g.outputs.size() != 2) return nullptr;
+    const auto& x = g.inputs[0];
+    if (x.dtype != DType::kFloat32 || g.outputs[0].dtype != DType::kFloat32 || g.outputs[1].dtype != DType::kFloat32) {
+      Fail("channel statistics are prebuilt for float32 only");
+      return nullptr;
+    }
+    const OpDesc *r0 = Producer(g.outputs[0].name), *r1 = Producer(g.outputs[1].name);
+    int64_t A, B, I, A2, B2, I2;
+    if (!MidKeepView(x.shape, AttrList(*r0, "dim"), &A, &B, &I) || !MidKeepView(x.shape, AttrList(*r1, "dim"), &A2, &B2, &I2) ||
+        A != A2 || B != B2 || I != I2 || g.outputs[0].numel() != B || g.outputs[1].numel() != B) {
+      Fail("the two reductions must keep the same middle axes");
+      return nullptr;
+    }
+    auto p      = NewPlan("channel_stats");
+    p->elements = x.numel();
+    if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Out(0), Out(1))) return nullptr;
     return p;
   }
 
@@ -804,10 +940,6 @@ struct Matcher {
   }
 
   std::unique_ptr<CompiledGroup> Run() {
-    if (g.outputs.size() != 1) {
-      Fail("groups with " + std::to_string(g.outputs.size()) + " outputs have no prebuilt kernel");
-      return nullptr;
-    }
     std::string e;
     std::string expr = CanonicalExpr(g, &e);
     if (expr.empty()) {
@@ -815,9 +947,17 @@ struct Matcher {
       return nullptr;
     }
     if (err) err->clear();
+    if (g.outputs.size() != 1) {
+      // The only multi-output family: the fused channel statistics.
+      if (auto p = MatchChannelStats(expr)) return p;
+      if (err && err->empty())
+        Fail("groups with " + std::to_string(g.outputs.size()) + " outputs have no prebuilt kernel (" + expr + ")");
+      return nullptr;
+    }
     typedef std::unique_ptr<CompiledGroup> (Matcher::*Fn)(const std::string&);
     const Fn fns[] = {&Matcher::MatchAddRelu, &Matcher::MatchBiasScaleTanhCast, &Matcher::MatchBatchNorm,
-                      &Matcher::MatchReduce,  &Matcher::MatchSoftmax,           &Matcher::MatchLayerNorm};
+                      &Matcher::MatchBnTrainApply, &Matcher::MatchReduce,       &Matcher::MatchSoftmax,
+                      &Matcher::MatchLayerNorm};
     for (Fn f : fns) {
       auto p = (this->*f)(expr);
       if (p) return p;

@@ -194,12 +194,41 @@ class NetBuilder:
 
     def batchnorm(self, x, scale, bias, mean, variance, epsilon=1e-5, momentum=0.9, data_layout="NCHW", is_test=True):
         if not is_test:
-            raise NotImplementedError("batch_norm_train is outside the fused-group kernel library")
+            return self.batch_norm_train(x, scale, bias, mean, variance, epsilon, momentum, data_layout)
         return [self._op("batch_norm", [x, scale, bias, mean, variance], epsilon=float(epsilon),
                          momentum=float(momentum), data_layout=data_layout)]
 
     def batch_norm(self, *a, **kw):
         return self.batchnorm(*a, **kw)[0]
+
+    def batch_norm_train(self, x, scale, bias, moving_mean, moving_variance, epsilon=1e-5, momentum=0.9,
+                         data_layout="NCHW"):
+        """Training-mode batch norm, composed from primitives exactly as the reference's decomposer does
+        (cinn/frontend/decomposer/batch_norm.cc:60-177).  Returns [y, saved_mean, saved_variance, new_moving_mean,
+        new_moving_variance]."""
+        if data_layout != "NCHW":
+            raise NotImplementedError("batch_norm_train: only NCHW has prebuilt kernels")
+        dt, shape = x._info()
+        n, c, h, w = shape
+        count = float(n * h * w)
+        red = [0, 2, 3]
+        full = list(shape)
+        # mean = reduce_sum(x) / nhw ; variance = reduce_sum(x * x) / nhw - mean * mean
+        mean = self.divide(self.reduce_sum(x, red), self.fill_constant([c], count, dtype=dt))
+        sq_mean = self.divide(self.reduce_sum(self.multiply(x, self.identity(x)), red),
+                              self.fill_constant([c], count, dtype=dt))
+        variance = self.subtract(sq_mean, self.multiply(mean, self.identity(mean)))
+        mean_4d = self.broadcast_to(mean, full, [1])
+        var_4d = self.broadcast_to(variance, full, [1])
+        std_inv_4d = self.rsqrt(self.add(var_4d, self.fill_constant(full, float(epsilon), dtype=dt)))
+        # y = scale * (x - mean) * std_variance_inv + bias
+        normalized = self.multiply(self.subtract(x, mean_4d), std_inv_4d)
+        y = self.add(self.multiply(normalized, self.broadcast_to(scale, full, [1])), self.broadcast_to(bias, full, [1]))
+
+        def update(moving, saved):
+            return self.add(self.multiply(moving, self.fill_constant([c], float(momentum), dtype=dt)),
+                            self.multiply(saved, self.fill_constant([c], 1.0 - float(momentum), dtype=dt)))
+        return [y, mean, variance, update(moving_mean, mean), update(moving_variance, variance)]
 
     def layer_norm(self, x, gamma, beta, epsilon=1e-5):
         """layer_norm over the last axis of a 2-D `x`, composed from primitives the way the reference's Paddle

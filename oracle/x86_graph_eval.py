@@ -284,11 +284,18 @@ def evaluate(desc, inputs):
             dims = sorted(int(d) % x.ndim for d in at["dim"].split(",")) if at.get("dim") else list(range(x.ndim))
             keep = at.get("keep_dim", "false") in ("true", "1", "True")
             lo, hi = dims[0], dims[-1]
-            assert dims == list(range(lo, hi + 1)), "oracle evaluator: reduce over adjacent axes only"
-            outer = int(np.prod(x.shape[:lo]))
-            r = int(np.prod(x.shape[lo:hi + 1]))
-            inner = int(np.prod(x.shape[hi + 1:]))
-            res = orc.reduce(REDUCE[t], x, outer, r, inner)
+            if dims == list(range(lo, hi + 1)):
+                outer = int(np.prod(x.shape[:lo]))
+                r = int(np.prod(x.shape[lo:hi + 1]))
+                inner = int(np.prod(x.shape[hi + 1:]))
+                res = orc.reduce(REDUCE[t], x, outer, r, inner)
+            else:
+                # non-adjacent axes: the serial loop nest visits the reduced axes in increasing order, innermost
+                # fastest (cinn/hlir/pe/reduction.cc:139-227) -- the same as reducing a copy with the kept axes first
+                kept = [i for i in range(x.ndim) if i not in dims]
+                xt = np.ascontiguousarray(np.transpose(x, kept + dims))
+                res = orc.reduce(REDUCE[t], xt, int(np.prod([x.shape[i] for i in kept])),
+                                 int(np.prod([x.shape[i] for i in dims])), 1)
             oshape = [d for i, d in enumerate(x.shape) if i not in dims or keep]
             if keep:
                 oshape = [1 if i in dims else d for i, d in enumerate(x.shape)]
@@ -315,3 +322,10 @@ def run(desc, inputs):
     """The group's single output."""
     g = parse(desc)
     return evaluate(desc, inputs)[g["outputs"][0][0]]
+
+
+def run_all(desc, inputs):
+    """{name: array} of all outputs of the group."""
+    g = parse(desc)
+    vals = evaluate(desc, inputs)
+    return {o[0]: vals[o[0]] for o in g["outputs"]}

@@ -173,7 +173,7 @@ def test_unmatched_group_is_an_error_not_a_fallback():
     assert rc == -1
     # reduce over non-adjacent axes
     rc = L.cinn_b200_compile_group(
-        b"group g\ninput x float32 4,5,6\nop reduce_sum y = x ; dim=0,2\noutput y float32 5\n", ctypes.byref(fn))
+        b"group g\ninput x float32 4,5,6,7\nop reduce_sum y = x ; dim=1,3\noutput y float32 4,6\n", ctypes.byref(fn))
     assert rc == -2 and b"non-adjacent" in L.cinn_b200_last_error()
     assert L.cinn_b200_lookup(b"g") is None
 
@@ -255,3 +255,19 @@ def test_operand_type_rules_of_the_new_ops():
         with pytest.raises(Exception):
             make()
     assert b.isnan(x)._info()[0] == "bool" and b.logical_xor(m, m)._info()[0] == "bool"
+
+
+def test_batch_norm_train_plans_one_statistics_pass_and_one_normalisation_pass():
+    b = NetBuilder("bnt")
+    x = b.create_input(common.Float(32), (256, 64, 112, 112), "x")
+    ps = [b.create_input(common.Float(32), (64,), n) for n in ["scale", "bias", "mm", "mv"]]
+    b.batchnorm(x, *ps, is_test=False)
+    c = plan(b)
+    pats = patterns(c)
+    assert pats.count("channel_stats") == 1 and pats.count("ew_bn_train_apply_nchw") == 1
+    # everything else works on [64]-element vectors
+    for desc, p in c.groups():
+        if p.split()[0] == "ew_chain":
+            assert all(l.split()[3] == "64" for l in desc.splitlines() if l.startswith(("input", "output"))), desc
+    stats = [d for d, p in c.groups() if p.startswith("channel_stats")][0]
+    assert len([l for l in stats.splitlines() if l.startswith("output")]) == 2

@@ -35,8 +35,7 @@ def oracle_program(comp, feeds):
                 [int(d) for d in g["ops"][0]["attrs"]["shape"].split(",")])
             continue
         g = ge.parse(desc)
-        out = ge.run(desc, [vals[name] for name, _, _ in g["inputs"]])
-        vals[g["outputs"][0][0]] = out
+        vals.update(ge.run_all(desc, [vals[name] for name, _, _ in g["inputs"]]))
     return vals
 
 
@@ -516,3 +515,86 @@ def test_float64_chains(oracle, index):
         print("%s: max distance %.2f ulp" % (make.__name__, ulp.max()))
         slack = 4 * eps if make.__name__ == "transcendental" else 0.0
         assert (err <= 4 * np.spacing(np.abs(ref[fin]).astype(got.dtype)).astype(np.float64) + slack).all(), float(ulp.max())
+
+
+# ---- batch_norm_train (decomposed): fused channel statistics + normalisation kernel ---------------------------------
+
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (3, 5, 7, 9), (32, 64, 56, 56), (2, 3, 1, 5)])
+def test_batch_norm_train_decomposed(oracle, shape):
+    n, c, h, w = shape
+    b = NetBuilder("bn_train")
+    x = b.create_input(common.Float(32), shape, "x")
+    ps = [b.create_input(common.Float(32), (c,), nm) for nm in ("scale", "bias", "moving_mean", "moving_variance")]
+    outs = b.batchnorm(x, *ps, epsilon=1e-5, momentum=0.9, is_test=False)
+    rng = np.random.default_rng(70)
+    feeds = {"x": (rng.standard_normal(shape) * 2 + 0.5).astype(np.float32),
+             "scale": (1 + 0.1 * rng.standard_normal(c)).astype(np.float32),
+             "bias": (0.1 * rng.standard_normal(c)).astype(np.float32),
+             "moving_mean": (0.1 * rng.standard_normal(c)).astype(np.float32),
+             "moving_variance": rng.uniform(0.5, 1.5, c).astype(np.float32)}
+    comp, out = run_program(b, feeds, outs)
+    pats = [p.split()[0] for _, p in comp.groups()]
+    assert pats.count("channel_stats") == 1 and pats.count("ew_bn_train_apply_nchw") == 1, pats
+    ref = oracle_program(comp, feeds)
+    y, mean, var, new_mean, new_var = (str(o) for o in outs)
+    # statistics: reduction class (tree order on the GPU, serial in the oracle), checked against float64 as well
+    x64 = feeds["x"].astype(np.float64)
+    m64 = x64.mean(axis=(0, 2, 3))
+    v64 = (x64 * x64).mean(axis=(0, 2, 3)) - m64 * m64
+    cnt = n * h * w
+    assert np.allclose(out[mean], m64, rtol=1e-5, atol=1e-6)
+    assert (np.abs(out[mean] - ref[mean]) <= np.abs(ref[mean] - m64) + 1e-5 * np.abs(m64) + 1e-6).all()
+    assert np.allclose(out[var], v64, rtol=1e-4, atol=1e-5), np.abs(out[var] - v64).max()
+    assert np.allclose(out[new_mean], ref[new_mean], rtol=1e-5, atol=1e-6)
+    assert np.allclose(out[new_var], ref[new_var], rtol=1e-4, atol=1e-5)
+    # normalisation: the kernel given the oracle's statistics would be exact; with its own statistics the difference
+    # is that of the statistics, amplified by |x - mean| / std <= a few units
+    assert np.allclose(out[y], ref[y], rtol=1e-4, atol=1e-4), np.abs(out[y] - ref[y]).max()
+
+
+def test_bn_train_apply_kernel_is_bit_exact_given_the_statistics(oracle):
+    """The normalisation group alone (statistics as inputs): same bits as the x86 arithmetic (1 / sqrt, one fma)."""
+    shape, c = (6, 10, 9, 11), 10
+    b = NetBuilder("bn_apply")
+    F = common.Float(32)
+    x = b.create_input(F, shape, "x")
+    mean, var, scale, bias = [b.create_input(F, (c,), nm) for nm in ("mean", "var", "scale", "bias")]
+    full = list(shape)
+    std = b.rsqrt(b.add(b.broadcast_to(var, full, [1]), b.fill_constant(full, 1e-5)))
+    norm = b.multiply(b.subtract(x, b.broadcast_to(mean, full, [1])), std)
+    y = b.relu(b.add(b.multiply(norm, b.broadcast_to(scale, full, [1])), b.broadcast_to(bias, full, [1])))
+    rng = np.random.default_rng(71)
+    feeds = {"x": rng.standard_normal(shape).astype(np.float32), "mean": (0.1 * rng.standard_normal(c)).astype(np.float32),
+             "var": rng.uniform(0.5, 1.5, c).astype(np.float32), "scale": (1 + 0.1 * rng.standard_normal(c)).astype(np.float32),
+             "bias": (0.1 * rng.standard_normal(c)).astype(np.float32)}
+    comp, out = run_program(b, feeds, [y])
+    assert [p.split()[0] for _, p in comp.groups()] == ["ew_bn_train_apply_relu_nchw"], comp.groups()
+    m, v, s_, b_ = (feeds[k].reshape(1, c, 1, 1) for k in ("mean", "var", "scale", "bias"))
+    inv = oracle.unary("rsqrt", (v + np.float32(1e-5)).astype(np.float32))
+    normalized = ((feeds["x"] - m).astype(np.float32) * inv).astype(np.float32)
+    want = np.maximum(oracle.fma(normalized, np.broadcast_to(s_, shape).copy(), np.broadcast_to(b_, shape).copy(), shape), 0)
+    assert oracle.max_ulp(out[str(y)], want.astype(np.float32)) == 0
+
+
+@pytest.mark.parametrize("kind", ["sum", "max", "min"])
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (5, 3, 7), (64, 32, 50, 20), (2, 7, 1, 1030)])
+def test_reduce_over_leading_and_trailing_axes(oracle, kind, shape):
+    b = NetBuilder("midkeep")
+    x = b.create_input(common.Float(32), shape, "X")
+    dims = [0] + list(range(2, len(shape)))
+    y = getattr(b, "reduce_" + kind)(x, dims)
+    X = np.random.default_rng(72).standard_normal(shape).astype(np.float32)
+    comp, out = run_program(b, {"X": X}, [y])
+    assert [p.split()[0] for _, p in comp.groups()] == ["mid_keep_reduce"], comp.groups()
+    ref = oracle_program(comp, {"X": X})[str(y)]
+    if kind == "sum":
+        cnt = X.size // shape[1]
+        # the serial fp32 sum of the oracle is itself off by up to ~sqrt(cnt) * 2^-24 * |partial sums|; the float64
+        # sum arbitrates: the kernel (tree order) must be at least as close to it as the tolerance, and no farther
+        # from the oracle than the oracle is from the exact sum plus that tolerance
+        exact = X.astype(np.float64).sum(axis=tuple(dims))
+        tol = 1e-5 * np.abs(exact) + 1e-6 * np.sqrt(cnt)
+        assert (np.abs(out[str(y)] - exact) <= tol).all()
+        assert (np.abs(out[str(y)] - ref) <= np.abs(ref - exact) + tol).all()
+    else:
+        assert np.array_equal(out[str(y)], ref)
