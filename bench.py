@@ -194,7 +194,8 @@ def side_groups(torch, dev, peak, only=None):
         for _ in range(reps):
             ins = [torch.from_numpy(a).to(dev) for a in w.inputs]
             o = torch.empty(w.out_shape, dtype=TORCH_OF_NUMPY(torch)[np.dtype(w.out_dtype)], device=dev)
-            sets.append(ins + [o])
+            more = [torch.empty(sh, dtype=TORCH_OF_NUMPY(torch)[np.dtype(dt)], device=dev) for dt, sh in w.more_outputs]
+            sets.append(ins + [o] + more)
         return sets
 
     plan = [
@@ -209,6 +210,10 @@ def side_groups(torch, dev, peak, only=None):
         ("layer_norm_f16_16384x4096", lambda: W.layer_norm((16384, 4096), half=True), 2, ""),
         ("bn_relu_f32_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112)), 1, ""),
         ("bn_relu_f16_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112), half=True), 1, ""),
+        # batch_norm_train as the reference decomposes it: one statistics pass (two outputs) + one normalisation pass
+        ("bn_train_stats_256x64x112x112", lambda: W.bn_train_stats((256, 64, 112, 112)), 1,
+         "sum and sum of squares per channel in one read of x"),
+        ("bn_train_apply_256x64x112x112", lambda: W.bn_train_apply((256, 64, 112, 112)), 1, ""),
         # the generic families: any other elementwise chain / element type (interpreted program, not a dedicated kernel)
         ("generic_chain_abs_add_f32_8192x8192", lambda: W.generic_chain("abs_add_f32"), 1, "generic chain kernel"),
         ("generic_chain_select_f32_8192x8192", lambda: W.generic_chain("select_f32"), 1, "generic chain kernel"),
@@ -254,6 +259,8 @@ PROFILE_GROUPS = {
     "layer_norm_f16": lambda W: W.layer_norm((16384, 4096), half=True),
     "bn_relu_f32": lambda W: W.bn_relu((256, 64, 112, 112)),
     "bn_relu_f16": lambda W: W.bn_relu((256, 64, 112, 112), half=True),
+    "bn_train_stats": lambda W: W.bn_train_stats((256, 64, 112, 112)),
+    "bn_train_apply": lambda W: W.bn_train_apply((256, 64, 112, 112)),
     "chain_abs_add_f32": lambda W: W.generic_chain("abs_add_f32"),
     "chain_select_f32": lambda W: W.generic_chain("select_f32"),
     "chain_abs_add_i32": lambda W: W.generic_chain("abs_add_i32"),
@@ -274,9 +281,10 @@ def run_profile_case(args):
     w = PROFILE_GROUPS[args.profile](W)
     g = cinn_b200.FusedGroup(w.desc)
     ins = [torch.from_numpy(a).to(dev) for a in w.inputs]
-    out = torch.empty(w.out_shape, dtype=TORCH_OF_NUMPY(torch)[np.dtype(w.out_dtype)], device=dev)
-    g.run(ins + [out])  # status-checked first launch
-    ms = time_group(g, [ins + [out]], iters=max(args.steps, 1), warmup=max(args.warmup, 1), torch=torch)
+    out = [torch.empty(w.out_shape, dtype=TORCH_OF_NUMPY(torch)[np.dtype(w.out_dtype)], device=dev)]
+    out += [torch.empty(sh, dtype=TORCH_OF_NUMPY(torch)[np.dtype(dt)], device=dev) for dt, sh in w.more_outputs]
+    g.run(ins + out)  # status-checked first launch
+    ms = time_group(g, [ins + out], iters=max(args.steps, 1), warmup=max(args.warmup, 1), torch=torch)
     print(json.dumps({"profile": args.profile, "kernels": g.kernel_names(), "ms": ms,
                       "bytes_per_launch": g.algorithmic_bytes,
                       "GB/s": g.algorithmic_bytes / (ms * 1e-3) / 1e9}))

@@ -5,11 +5,13 @@
 // (cinn/hlir/pe/reduction.cc:139-227, serial per output element); two such reduces of the same tensor are fused
 // horizontally into one kernel there (cinn/hlir/pass/fusion_merge_pass.cc:85-460).
 //
-// Here one launch streams x once: CTA (b, s) walks the work items (a, chunk of I) s, s + splits, ... of channel b
-// with four 16-byte loads in flight per thread and writes one partial per accumulation to scratch [splits][B];
-// a column reduction over the splits finishes.  The DUAL form keeps two accumulations, sum and sum of squares, for
-// the two-output group {reduce_sum(x), reduce_sum(x * x)}.  Squares are rounded products added without fma, as a
-// materialised producer would be.
+// Here one launch streams x once: CTA (b, s) walks the work items (a, chunk of I) s, s + splits, ... of channel b as
+// one flat list of 16-byte vectors with four loads in flight per thread, and writes one partial per accumulation
+// to scratch [splits][B].  The last CTA of a channel to finish (a ticket counter per channel in scratch, zero
+// between launches) folds the channel's partials in a fixed order and writes the result, so there is no second
+// launch and the result does not depend on which CTA came last.  The DUAL form keeps two accumulations, sum and sum
+// of squares, for the two-output group {reduce_sum(x), reduce_sum(x * x)}.  Squares are rounded products added
+// without fma, as a materialised producer would be.
 #include "device_math.cuh"
 #include "kernel_registry.h"
 
@@ -18,36 +20,59 @@ namespace {
 
 template <class OpA, class OpB, bool DUAL>
 __global__ void __launch_bounds__(256)
-    k_mid_keep_reduce(const float* __restrict__ x, float* __restrict__ pa, float* __restrict__ pb, long long A,
+    k_mid_keep_reduce(const float* __restrict__ x, float* __restrict__ pa, float* __restrict__ pb,
+                      unsigned int* __restrict__ tickets, float* __restrict__ ya, float* __restrict__ yb, long long A,
                       long long B, long long I, long long chunks, long long splits, long long vec_ok) {
   __shared__ float scratch[32];
+  __shared__ unsigned int ticket;
   const long long b = blockIdx.x % B, s = blockIdx.x / B;
-  const long long items = A * chunks;
+  const long long items    = A * chunks;
+  const long long my_items = s < items ? (items - s + splits - 1) / splits : 0;
   float a0 = OpA::identity(), a1 = OpB::identity();
+  const int T = blockDim.x;
   if (vec_ok) {
-    const int nvec = (int)(I >> 2);
-    const int per  = (int)((nvec + chunks - 1) / chunks);
-    for (long long it = s; it < items; it += splits) {
-      const long long a = it / chunks;
-      const int chunk   = (int)(it - a * chunks);
-      const int begin = chunk * per, end = min(begin + per, nvec);
-      const uint4* px = reinterpret_cast<const uint4*>(x + (a * B + b) * I);
-      const int T     = blockDim.x;
-      for (int v = begin + threadIdx.x; v < end; v += 4 * T) {
-        uint4 r[4];
+    const long long nvec  = I >> 2;
+    const long long per   = (nvec + chunks - 1) / chunks;
+    const long long total = my_items * per;
+    const uint4* px       = reinterpret_cast<const uint4*>(x);
+    // (k, v) = (item, vector inside the item) of flat index id, advanced incrementally: no division per load.
+    long long k = threadIdx.x / per, v = threadIdx.x - k * per;
+    const long long step_k = T / per, step_v = T - step_k * per;  // one stride of T vectors
+    for (long long idx = threadIdx.x; idx < total; idx += 4 * T) {
+      uint4 r[4];
+      bool ok[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (v + j * T < end) r[j] = __ldcs(px + v + j * T);
+      for (int j = 0; j < 4; ++j) {
+        ok[j] = false;
+        if (idx + (long long)j * T < total) {
+          const long long it = s + k * splits;
+          long long a = it, chunk = 0;
+          if (chunks != 1) {
+            a     = (unsigned)it / (unsigned)chunks;  // items < 2^31 (checked by the planner)
+            chunk = it - a * chunks;
+          }
+          const long long vv = chunk * per + v;
+          if (vv < nvec) {
+            r[j]  = __ldcs(px + (a * B + b) * nvec + vv);
+            ok[j] = true;
+          }
+        }
+        k += step_k;
+        v += step_v;
+        if (v >= per) {
+          v -= per;
+          ++k;
+        }
+      }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (v + j * T < end) {
-            float f[4];
-            unpack4(r[j], f);
+      for (int j = 0; j < 4; ++j) {
+        if (ok[j]) {
+          float f[4];
+          unpack4(r[j], f);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              a0 = OpA::accum(a0, f[i]);
-              if (DUAL) a1 = OpB::accum(a1, f[i]);
-            }
+          for (int i = 0; i < 4; ++i) {
+            a0 = OpA::accum(a0, f[i]);
+            if (DUAL) a1 = OpB::accum(a1, f[i]);
           }
         }
       }
@@ -58,7 +83,7 @@ __global__ void __launch_bounds__(256)
       const long long a = it / chunks, chunk = it - a * chunks;
       const long long begin = chunk * per, end = min(begin + per, I);
       const float* px = x + (a * B + b) * I;
-      for (long long i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      for (long long i = begin + threadIdx.x; i < end; i += T) {
         const float f = px[i];
         a0            = OpA::accum(a0, f);
         if (DUAL) a1 = OpB::accum(a1, f);
@@ -70,13 +95,31 @@ __global__ void __launch_bounds__(256)
   if (threadIdx.x == 0) {
     pa[s * B + b] = a0;
     if (DUAL) pb[s * B + b] = a1;
+    __threadfence();
+    ticket = atomicAdd(&tickets[b], 1u);
+  }
+  __syncthreads();
+  if (ticket != (unsigned)(splits - 1)) return;
+  // Last CTA of channel b: every partial of the channel is visible (fence + ticket); fold them in split order.
+  __threadfence();
+  float t0 = OpA::identity(), t1 = OpB::identity();
+  for (long long k = threadIdx.x; k < splits; k += T) {
+    t0 = OpA::apply(t0, __ldcg(pa + k * B + b));
+    if (DUAL) t1 = OpB::apply(t1, __ldcg(pb + k * B + b));
+  }
+  t0 = cta_allreduce<OpA>(t0, scratch);
+  if (DUAL) t1 = cta_allreduce<OpB>(t1, scratch);
+  if (threadIdx.x == 0) {
+    ya[b] = t0;
+    if (DUAL) yb[b] = t1;
+    tickets[b] = 0;  // ready for the next launch
   }
 }
 
 }  // namespace
 
 #define REG_MID(OPNAME, OP) \
-  CINN_B200_REGISTER_KERNEL("mid_keep_reduce_" OPNAME "_f32", 9, 256, k_mid_keep_reduce<OP, OP, false>)
+  CINN_B200_REGISTER_KERNEL("mid_keep_reduce_" OPNAME "_f32", 12, 256, k_mid_keep_reduce<OP, OP, false>)
 REG_MID("sum", SumOp);
 REG_MID("prod", ProdOp);
 REG_MID("max", MaxOp);
@@ -84,6 +127,6 @@ REG_MID("min", MinOp);
 REG_MID("sumsq", SumSquareOp);
 REG_MID("sumabs", SumAbsOp);
 REG_MID("maxabs", MaxAbsOp);
-CINN_B200_REGISTER_KERNEL("mid_keep_reduce_sum_sumsq_f32", 9, 256, k_mid_keep_reduce<SumOp, SumSquareOp, true>);
+CINN_B200_REGISTER_KERNEL("mid_keep_reduce_sum_sumsq_f32", 12, 256, k_mid_keep_reduce<SumOp, SumSquareOp, true>);
 
 }  // namespace cinn_b200

@@ -425,21 +425,23 @@ struct Matcher {
     const int64_t units  = vec ? I / 4 : I;
     const int64_t chunks = std::max<int64_t>(1, (units + 2048) / 4096);  // about 4096 vectors per work item
     const int64_t items  = A * chunks;
-    int64_t splits       = std::max<int64_t>(1, std::min<int64_t>(items, CeilDiv((int64_t)sms * 8, B)));
+    if (items >= (int64_t)1 << 31) return Fail("reduction with more than 2^31 work items");
+    // Several waves of small CTAs (5 are resident per SM) balance better than one wave of large ones (measured).
+    int64_t splits       = std::max<int64_t>(1, std::min<int64_t>(items, CeilDiv((int64_t)sms * 32, B)));
     const int64_t off1   = p->scratch_bytes;
     p->scratch_bytes += (size_t)RoundUp(splits * B * 4, 256);
     const int64_t off2 = p->scratch_bytes;
     if (dual) p->scratch_bytes += (size_t)RoundUp(splits * B * 4, 256);
+    const int64_t off_tickets = p->scratch_bytes;  // one counter per kept element; scratch starts zeroed
+    p->scratch_bytes += (size_t)RoundUp(B * 4, 256);
     LaunchStep s;
     if (!Kernel(&s, dual ? std::string("mid_keep_reduce_sum_sumsq_f32") : std::string("mid_keep_reduce_") + opname + "_f32"))
       return false;
     s.block[0] = 256;
     s.grid[0]  = (unsigned)(B * splits);
-    s.args     = {In(0), Scratch(off1), Scratch(dual ? off2 : off1), this->I(A), this->I(B), this->I(I), this->I(chunks), this->I(splits),
-                  Aligned(vec, {0}, {})};
+    s.args     = {In(0), Scratch(off1), Scratch(dual ? off2 : off1), Scratch(off_tickets), dst, dual ? dst2 : dst,
+                  this->I(A), this->I(B), this->I(I), this->I(chunks), this->I(splits), Aligned(vec, {0}, {})};
     p->steps.push_back(s);
-    if (!PlanReduce(p, BaseReduceOp(opname), 1, splits, B, Scratch(off1), dst, {})) return false;
-    if (dual && !PlanReduce(p, "sum", 1, splits, B, Scratch(off2), dst2, {})) return false;
     return true;
   }
 

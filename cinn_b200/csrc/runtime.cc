@@ -295,6 +295,8 @@ static int RunPlan(const CompiledGroup& plan, GroupSlot& slot, const std::vector
       if (e != cudaSuccess)
         return SetError(CINN_B200_ECUDA, "group %s: cudaMalloc of %zu scratch bytes failed: %s", plan.name.c_str(),
                         plan.scratch_bytes, cudaGetErrorString(e));
+      // Zeroed once: kernels that keep counters in scratch (ticket counters) return them to zero themselves.
+      cudaMemsetAsync(p, 0, plan.scratch_bytes, static_cast<cudaStream_t>(stream));
       it = slot.scratch.emplace(dev, p).first;
     }
     scratch = static_cast<uint8_t*>(it->second);

@@ -15,12 +15,13 @@ def _shape(s):
 class Workload:
     """name, group description text, input arrays (host numpy, generated on first use), output dtype/shape."""
 
-    def __init__(self, name, desc, inputs, out_dtype, out_shape):
+    def __init__(self, name, desc, inputs, out_dtype, out_shape, more_outputs=()):
         self.name = name
         self.desc = desc
         self._inputs = inputs  # a list of arrays, or a function returning one
         self.out_dtype = out_dtype
         self.out_shape = tuple(int(d) for d in out_shape)
+        self.more_outputs = tuple(more_outputs)  # (dtype, shape) of the outputs after the first
 
     @property
     def inputs(self):
@@ -251,3 +252,42 @@ def generic_reduce(kind, dtype, shape=(16384, 8192), axis=1, seed=6):
             "output var_0 %s %s\n" % (kind, dtype, axis, dtype, _shape(shape), kind, axis, dtype, _shape(out_shape)))
     return Workload("reduce_%s_%s" % (kind, dtype), desc, lambda: [_draw(np.random.default_rng(seed), shape, dtype)],
                     _NP[dtype], out_shape)
+
+
+def bn_train_inputs(shape=(256, 64, 112, 112), seed=4):
+    rng = np.random.default_rng(seed)
+    c = shape[1]
+    x = rng.standard_normal(shape, dtype=np.float32)
+    mean = (0.1 * rng.standard_normal(c)).astype(np.float32)
+    var = rng.uniform(0.5, 1.5, c).astype(np.float32)
+    scale = (1 + 0.1 * rng.standard_normal(c)).astype(np.float32)
+    bias = (0.1 * rng.standard_normal(c)).astype(np.float32)
+    return x, mean, var, scale, bias
+
+
+def bn_train_stats(shape=(256, 64, 112, 112), seed=4):
+    """The statistics pass of the decomposed batch_norm_train: {reduce_sum(x), reduce_sum(x * x)} over N, H, W."""
+    s, c = _shape(shape), shape[1]
+    desc = (f"group fn_bn_train_stats\ninput x float32 {s}\nop reduce_sum s1 = x ; dim=0,2,3 keep_dim=false\n"
+            f"op identity xi = x\nop elementwise_mul xx = x xi ; axis=-1\n"
+            f"op reduce_sum s2 = xx ; dim=0,2,3 keep_dim=false\noutput s1 float32 {c}\noutput s2 float32 {c}\n")
+    return Workload("bn_train_stats", desc, lambda: [bn_train_inputs(shape, seed)[0]], np.float32, (c,),
+                    more_outputs=[(np.float32, (c,))])
+
+
+def bn_train_apply(shape=(256, 64, 112, 112), seed=4):
+    """The normalisation pass: ((x - mean) * rsqrt(var + eps)) * scale + bias with per-channel operands."""
+    s, c = _shape(shape), shape[1]
+    bc = f"broadcast_axes=1 out_shape={s}"
+    desc = (f"group fn_bn_train_apply\ninput mean float32 {c}\ninput var float32 {c}\ninput x float32 {s}\n"
+            f"input scale float32 {c}\ninput bias float32 {c}\n"
+            f"op broadcast_to m4 = mean ; {bc}\nop broadcast_to v4 = var ; {bc}\n"
+            f"op fill_constant e = ; shape={s} value=1e-05 dtype=float32\nop elementwise_add ve = v4 e ; axis=-1\n"
+            f"op rsqrt r = ve\nop subtract d = x m4 ; axis=-1\nop elementwise_mul n = d r ; axis=-1\n"
+            f"op broadcast_to s4 = scale ; {bc}\nop elementwise_mul sn = n s4 ; axis=-1\n"
+            f"op broadcast_to b4 = bias ; {bc}\nop elementwise_add y = sn b4 ; axis=-1\noutput y float32 {s}\n")
+
+    def gen():
+        x, mean, var, scale, bias = bn_train_inputs(shape, seed)
+        return [mean, var, x, scale, bias]
+    return Workload("bn_train_apply", desc, gen, np.float32, shape)
