@@ -210,6 +210,8 @@ def side_groups(torch, dev, peak, only=None):
         ("layer_norm_f16_16384x4096", lambda: W.layer_norm((16384, 4096), half=True), 2, ""),
         ("bn_relu_f32_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112)), 1, ""),
         ("bn_relu_f16_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112), half=True), 1, ""),
+        ("softmax_max_subtracted_f32_16384x4096", lambda: W.softmax_safe((16384, 4096)), 2, "decomposed softmax, mode != fast"),
+        ("softmax_max_subtracted_f16_16384x4096", lambda: W.softmax_safe((16384, 4096), half=True), 2, ""),
         # batch_norm_train as the reference decomposes it: one statistics pass (two outputs) + one normalisation pass
         ("bn_train_stats_256x64x112x112", lambda: W.bn_train_stats((256, 64, 112, 112)), 1,
          "sum and sum of squares per channel in one read of x"),
@@ -259,6 +261,7 @@ PROFILE_GROUPS = {
     "layer_norm_f16": lambda W: W.layer_norm((16384, 4096), half=True),
     "bn_relu_f32": lambda W: W.bn_relu((256, 64, 112, 112)),
     "bn_relu_f16": lambda W: W.bn_relu((256, 64, 112, 112), half=True),
+    "softmax_safe_f32": lambda W: W.softmax_safe((16384, 4096)),
     "bn_train_stats": lambda W: W.bn_train_stats((256, 64, 112, 112)),
     "bn_train_apply": lambda W: W.bn_train_apply((256, 64, 112, 112)),
     "chain_abs_add_f32": lambda W: W.generic_chain("abs_add_f32"),

@@ -22,6 +22,7 @@ SOURCES = [
     "channel_reduce.cu",
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
+    "softmax_safe.cu",
     "ew_chain.cu",
     "ew_chain_int.cu",
     "ew_chain_f64.cu",

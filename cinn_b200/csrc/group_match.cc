@@ -834,11 +834,20 @@ struct Matcher {
   // cast(softmax(cast(%0))).  Also the decomposed "fast" form of cinn/frontend/decomposer/activation.cc:70-118:
   // divide(exp(x), broadcast_to(reduce_sum(exp(x)))).
   std::unique_ptr<CompiledGroup> MatchSoftmax(const std::string& expr) {
-    bool half = false;
+    bool half = false, safe = false;
+    // The decomposed form with the row maximum subtracted (cinn/frontend/decomposer/activation.cc:104-116).
+    auto safe_form = [](const std::string& x) {
+      const std::string d = "exp(subtract(" + x + ",broadcast_to(reduce_max(" + x + "))))";
+      return "divide(" + d + ",broadcast_to(reduce_sum(" + d + ")))";
+    };
     if (expr == "softmax(%0)" || expr == "divide(exp(%0),broadcast_to(reduce_sum(exp(%0))))") {
     } else if (expr == "cast(softmax(cast(%0)))" ||
                expr == "cast(divide(exp(cast(%0)),broadcast_to(reduce_sum(exp(cast(%0))))))") {
       half = true;
+    } else if (expr == safe_form("%0")) {
+      safe = true;
+    } else if (expr == "cast(" + safe_form("cast(%0)") + ")") {
+      safe = half = true;
     } else {
       return nullptr;
     }
@@ -857,7 +866,7 @@ struct Matcher {
           Fail("softmax is prebuilt for the last axis only");
           return nullptr;
         }
-      } else if (op.type == "reduce_sum") {
+      } else if (op.type == "reduce_sum" || op.type == "reduce_max") {
         auto dims = AttrList(op, "dim");
         if (dims.size() != 1 || !(dims[0] == -1 || dims[0] == nd - 1)) {
           Fail("decomposed softmax must reduce the last axis");
@@ -866,6 +875,29 @@ struct Matcher {
       }
     }
     const int64_t cols = x.shape.back(), rows = x.numel() / std::max<int64_t>(cols, 1);
+    if (safe) {
+      // One CTA per row, the row in registers: at most 512 threads x 8 vectors.
+      const int V        = half ? 8 : 4;
+      const int64_t nvec = CeilDiv(cols, V);
+      if (nvec > 4096) {
+        Fail("max-subtracted softmax is prebuilt for rows of up to " + std::to_string(4096 * V) + " elements");
+        return nullptr;
+      }
+      // 4 vectors per thread for fp32, 2 for 16-bit storage (16 values each way), between 128 and 512 threads.
+      const int target = half ? 2 : 4;
+      int G            = 128;
+      while (G < 512 && G * target < nvec) G *= 2;
+      int vpt = 1;
+      while (G * vpt < nvec) vpt *= 2;
+      auto p = NewPlan("softmax_safe_row");
+      LaunchStep s;
+      if (!Kernel(&s, std::string("softmax_safe_") + (half ? "f16" : "f32") + "_v" + std::to_string(vpt))) return nullptr;
+      s.block[0] = G;
+      s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(rows, (int64_t)dev.sm_count * (2048 / G) * 4));
+      s.args     = {In(0), Out(0), I(rows), I(cols), Aligned(cols % V == 0, {0}, {0})};
+      p->steps.push_back(s);
+      return p;
+    }
     auto p = NewPlan("softmax_row");
     if (!PlanRowNorm(p.get(), false, half, rows, cols, 0.0, 0, 0, 0)) return nullptr;
     return p;

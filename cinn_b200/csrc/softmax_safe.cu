@@ -1,0 +1,103 @@
+// Row softmax with the row maximum subtracted first: the decomposed form of the softmax op in every mode other than
+// "fast" (cinn/frontend/decomposer/activation.cc:104-116):
+//     x_max = reduce_max(x); x_exp = exp(x - x_max); out = exp(x - x_max) / reduce_sum(x_exp)
+// The reference runs it as several kernels (two reductions, each refusing to fuse with its broadcast consumer above
+// 1024 columns); here one CTA keeps the row in registers and makes the three passes (maximum, exponentials and their
+// sum, output) over registers: x is read once and the result written once.  The maximum is compare + select
+// starting from the lowest finite value (cinn/lang/builtin.cc:123-143); this group is in the reduction tolerance
+// class, so the quotient is a multiplication by 1 / sum and 16-bit outputs use the fast exponential.
+#include "device_math.cuh"
+#include "kernel_registry.h"
+
+namespace cinn_b200 {
+namespace {
+
+// One CTA of blockDim.x threads per row; thread t holds vectors t, t + blockDim.x, ... (VPT of them at most).
+// vec_ok != 0: 16-byte aligned buffers and cols % V == 0 (16-byte accesses); otherwise the same register layout is
+// filled and drained element by element, positions at or beyond `cols` masked out.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(512)
+    k_softmax_safe(const T* __restrict__ x, T* __restrict__ y, long long rows, long long cols, long long vec_ok) {
+  constexpr int V = Io<T>::kVec;
+  __shared__ float scratch[32];
+  const int nvec = (int)((cols + V - 1) / V);
+  const int G    = blockDim.x;
+  // The vectors of the NEXT row of this CTA are requested before the current row is reduced, so that the two
+  // barriers of a row do not leave the memory pipe idle.
+  uint4 raw[VPT];
+  if (vec_ok && blockIdx.x < rows) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j)
+      if ((int)threadIdx.x + j * G < nvec) raw[j] = __ldcs(reinterpret_cast<const uint4*>(x + (long long)blockIdx.x * cols) + threadIdx.x + j * G);
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + row * cols;
+    T* yr       = y + row * cols;
+    float f[VPT][V];
+    float mx = MaxOp::identity();
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int v = (int)threadIdx.x + j * G;
+      if (v < nvec) {
+        if (vec_ok) {
+          Io<T>::unpack(raw[j], f[j]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) f[j][i] = (long long)v * V + i < cols ? Io<T>::load1(xr + (long long)v * V + i) : MaxOp::identity();
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) mx = x86_max(mx, f[j][i]);
+      }
+    }
+    if (vec_ok && row + gridDim.x < rows) {
+      const uint4* pn = reinterpret_cast<const uint4*>(xr + (long long)gridDim.x * cols);
+#pragma unroll
+      for (int j = 0; j < VPT; ++j)
+        if ((int)threadIdx.x + j * G < nvec) raw[j] = __ldcs(pn + threadIdx.x + j * G);
+    }
+    mx = cta_allreduce<MaxOp>(mx, scratch);
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int v = (int)threadIdx.x + j * G;
+      if (v < nvec) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          const float d = f[j][i] - mx;
+          const float e = sizeof(T) == 2 ? exp_for_16bit_out(d) : expf(d);
+          f[j][i]       = (vec_ok || (long long)v * V + i < cols) ? e : 0.0f;
+          sum           = sum + f[j][i];
+        }
+      }
+    }
+    sum             = cta_allreduce<SumOp>(sum, scratch);
+    const float inv = 1.0f / sum;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      const int v = (int)threadIdx.x + j * G;
+      if (v < nvec) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) f[j][i] = f[j][i] * inv;
+        if (vec_ok) {
+          __stcs(reinterpret_cast<uint4*>(yr) + v, Io<T>::pack(f[j]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i)
+            if ((long long)v * V + i < cols) Io<T>::store1(yr + (long long)v * V + i, f[j][i]);
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+#define REG_SAFE(TNAME, T)                                                                      \
+  CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v1", 5, 512, k_softmax_safe<T, 1>);        \
+  CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v2", 5, 512, k_softmax_safe<T, 2>);        \
+  CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v4", 5, 512, k_softmax_safe<T, 4>);        \
+  CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v8", 5, 512, k_softmax_safe<T, 8>)
+REG_SAFE("f32", float);
+REG_SAFE("f16", __half);
+
+}  // namespace cinn_b200

@@ -188,9 +188,35 @@ class NetBuilder:
         return self._op("reduce_any", [x], dim=list(dim) or None, keep_dim=keep_dim)
 
     def softmax(self, x, axes=(-1,), mode="fast", data_format="AnyLayout"):
+        """mode "fast": exp(x) / sum(exp(x)) (the op's own definition, cinn/hlir/pe/nn.cc:755-796); any other mode
+        subtracts the row maximum first and is composed from primitives as the reference's decomposer does
+        (cinn/frontend/decomposer/activation.cc:104-116)."""
         if len(axes) != 1:
             raise ValueError("softmax over several axes has no prebuilt kernel")
-        return self._op("softmax", [x], axis=int(axes[0]))
+        if mode == "fast":
+            return self._op("softmax", [x], axis=int(axes[0]))
+        _, shape = x._info()
+        nd = len(shape)
+        axis = int(axes[0]) % nd
+        b_axes = [i for i in range(nd) if i != axis] or [-1]
+        x_max = self.broadcast_to(self.reduce_max(x, [axis]), list(shape), b_axes)
+        x_exp = self.exp(self.subtract(x, x_max))
+        x_sum = self.broadcast_to(self.reduce_sum(x_exp, [axis]), list(shape), b_axes)
+        return self.divide(self.exp(self.subtract(x, x_max)), x_sum)
+
+    def gelu(self, x):
+        """x * (0.5 + 0.5 * erf(sqrt(0.5) * x)), cinn/frontend/decomposer/activation.cc:54-69."""
+        dt, shape = x._info()
+        p_5 = self.fill_constant(list(shape), 0.5, dtype=dt)
+        p_7 = self.fill_constant(list(shape), float(np.sqrt(0.5)), dtype=dt)
+        cdf = self.add(p_5, self.multiply(p_5, self.erf(self.multiply(x, p_7))))
+        return self.multiply(x, cdf)
+
+    def relu_grad(self, dout, out):
+        """select(out > 0, dout, 0), cinn/frontend/decomposer/activation.cc:36-51."""
+        dt, shape = out._info()
+        zero = self.fill_constant(list(shape), 0.0, dtype=dt)
+        return self.select(self.greater_than(out, zero), dout, zero)
 
     def batchnorm(self, x, scale, bias, mean, variance, epsilon=1e-5, momentum=0.9, data_layout="NCHW", is_test=True):
         if not is_test:

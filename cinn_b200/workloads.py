@@ -291,3 +291,27 @@ def bn_train_apply(shape=(256, 64, 112, 112), seed=4):
         x, mean, var, scale, bias = bn_train_inputs(shape, seed)
         return [mean, var, x, scale, bias]
     return Workload("bn_train_apply", desc, gen, np.float32, shape)
+
+
+def softmax_safe(shape=(16384, 4096), seed=3, half=False):
+    """softmax along the last axis of a 2-D tensor with the row maximum subtracted (the decomposed form of every
+    softmax mode but "fast"); half=True stores x and out as fp16 and computes in fp32."""
+    rows, cols = shape
+    s, r = _shape(shape), str(rows)
+    x = "x32" if half else "X"
+    lines = ["op cast x32 = X ; dtype=float32"] if half else []
+    lines += [
+        f"op reduce_max m = {x} ; dim=1 keep_dim=false",
+        f"op broadcast_to m2 = m ; broadcast_axes=0 out_shape={s}",
+        f"op subtract d = {x} m2 ; axis=-1", "op exp e = d",
+        "op reduce_sum sm = e ; dim=1 keep_dim=false",
+        f"op broadcast_to s2 = sm ; broadcast_axes=0 out_shape={s}",
+        f"op subtract d2 = {x} m2 ; axis=-1", "op exp e2 = d2", "op divide y = e2 s2 ; axis=-1"]
+    out = "y"
+    if half:
+        lines.append("op cast y16 = y ; dtype=float16")
+        out = "y16"
+    dt = "float16" if half else "float32"
+    desc = "group fn_softmax_safe_%s\ninput X %s %s\n%s\noutput %s %s %s\n" % (dt, dt, s, "\n".join(lines), out, dt, s)
+    npdt = np.float16 if half else np.float32
+    return Workload("softmax_safe_" + dt, desc, lambda: [(3 * rownorm_inputs(shape, seed)[0]).astype(npdt)], npdt, shape)

@@ -598,3 +598,28 @@ def test_reduce_over_leading_and_trailing_axes(oracle, kind, shape):
         assert (np.abs(out[str(y)] - ref) <= np.abs(ref - exact) + tol).all()
     else:
         assert np.array_equal(out[str(y)], ref)
+
+
+def test_gelu_relu_grad_and_safe_softmax_compositions(oracle):
+    rng = np.random.default_rng(80)
+    X = (rng.standard_normal((48, 200)) * 2).astype(np.float32)
+    D = rng.standard_normal((48, 200)).astype(np.float32)
+    b = NetBuilder("gelu")
+    y = b.gelu(b.create_input(common.Float(32), X.shape, "X"))
+    comp, out = run_program(b, {"X": X}, [y])
+    assert len(comp.groups()) == 1
+    # 0.5 + 0.5 * erf(..) cancels for negative x: an ulp of erf (2^-24 near -1) is an absolute error of the factor
+    ref = oracle_program(comp, {"X": X})[str(y)]
+    err = np.abs(out[str(y)].astype(np.float64) - ref)
+    assert (err <= 2 * np.spacing(np.abs(ref)) + 2.0 ** -23 * np.abs(X)).all(), float(err.max())
+    b = NetBuilder("relu_grad")
+    o, d = b.create_input(common.Float(32), X.shape, "O"), b.create_input(common.Float(32), X.shape, "D")
+    y = b.relu_grad(d, o)
+    comp, out = run_program(b, {"O": X, "D": D}, [y])
+    assert np.array_equal(out[str(y)], np.where(X > 0, D, np.float32(0)))
+    b = NetBuilder("softmax_safe")
+    y = b.softmax(b.create_input(common.Float(32), X.shape, "X"), mode="safe")
+    comp, out = run_program(b, {"X": X * 30}, [y])
+    assert [p.split()[0] for _, p in comp.groups()] == ["softmax_safe_row"]
+    ref = oracle_program(comp, {"X": X * 30})[str(y)]
+    assert oracle.count_not_close(out[str(y)], ref, 1e-5, 1e-30)[0] == 0

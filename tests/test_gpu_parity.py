@@ -134,6 +134,48 @@ def test_softmax(oracle, shape, half):
     print("softmax %s half=%s worst/limit %.3g" % (shape, half, worst))
 
 
+@pytest.mark.parametrize("shape", [(4, 4096), (3, 7), (5, 128), (9, 1000), (2, 8192), (3, 16384), (16384, 4096)])
+@pytest.mark.parametrize("half", [False, True])
+@pytest.mark.parametrize("misalign", [0, 1])
+def test_softmax_with_row_maximum_subtracted(oracle, shape, half, misalign):
+    """The decomposed form of softmax in every mode but "fast": reduce_max, exp(x - max), reduce_sum, divide."""
+    from oracle import x86_graph_eval as ge
+    if misalign and shape[0] > 100:
+        pytest.skip("misaligned path is covered at small sizes")
+    w = W.softmax_safe(shape, half=half)
+    got, g = run_group(w, misalign)
+    assert g.pattern == "softmax_safe_row"
+    x = w.inputs[0]
+    if shape[0] > 100:   # the op-by-op evaluator is slow at full size: check a band of rows and the row sums
+        rows = np.r_[0:16, shape[0] // 2:shape[0] // 2 + 16, shape[0] - 16:shape[0]]
+        sub = W.softmax_safe((len(rows), shape[1]), half=half)
+        ref = ge.run(sub.desc, [np.ascontiguousarray(x[rows])])
+        part = got[rows]
+        assert np.allclose(got.astype(np.float64).sum(axis=1), 1.0, atol=2e-3 if half else 1e-5)
+    else:
+        ref, part = ge.run(w.desc, [x]), got
+    # The oracle's serial fp32 row sum drifts by more than 1e-5 on long rows; the float64 softmax arbitrates: the
+    # kernel must be within tolerance of it, and no farther from the oracle than the oracle is from it (+ tolerance).
+    xs = (x[rows] if shape[0] > 100 else x).astype(np.float64)
+    e = np.exp(xs - xs.max(axis=1, keepdims=True))
+    exact = e / e.sum(axis=1, keepdims=True)
+    tol = (1e-2 * exact + 1e-7) if half else (1e-5 * exact + 1e-12)
+    assert (np.abs(part.astype(np.float64) - exact) <= tol).all()
+    assert (np.abs(part.astype(np.float64) - ref) <= np.abs(ref.astype(np.float64) - exact) + tol).all()
+    assert np.isfinite(got.astype(np.float32)).all()
+
+
+def test_softmax_with_maximum_survives_large_inputs(oracle):
+    """What the maximum is subtracted for: inputs whose exponentials overflow in the plain form."""
+    from oracle import x86_graph_eval as ge
+    w = W.softmax_safe((6, 512))
+    x = (w.inputs[0] * 40 + 100).astype(np.float32)
+    w2 = W.Workload("big", w.desc, [x], np.float32, (6, 512))
+    got, _ = run_group(w2)
+    ref = ge.run(w.desc, [x])
+    assert np.isfinite(got).all() and oracle.count_not_close(got, ref, 2e-5, 1e-30)[0] == 0
+
+
 def test_softmax_misaligned(oracle):
     w = W.softmax((5, 4096))
     got, g = run_group(w, misalign=1)
