@@ -386,6 +386,7 @@ const char* DTypeKernelName(DType t) {
 }  // namespace
 
 enum ChainClass { kFloatChain, kIntChain, kDoubleChain };
+bool Ok2(const ChainBuilder& cb, DType t) { return cb.Ok(t); }
 
 std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const DeviceInfo& dev, ChainClass klass,
                                                  std::string* why) {
@@ -437,6 +438,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   }
 
   // Walk back from the output collecting primitive steps in reverse order.
+  bool starts_from_operand = false;
   std::vector<Step> rev;
   std::string cur = out.name;
   while (cb.producer.count(cur)) {
@@ -630,16 +632,40 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
       round_after();
       rev.push_back(s);
       cur = chain;
+    } else if (op.type == "broadcast_to" && cb.input_index.count(op.inputs[0])) {
+      // No operand has the output's size: the chain starts from this broadcast operand (EW_COPY).
+      Step s;
+      s.op  = EW_COPY;
+      s.f32 = false;
+      if (!cb.ResolveOperand(cur, op, &s.asel, &s.imm)) {
+        cb.Fail("the broadcast of '" + op.inputs[0] + "' cannot be addressed as a chain operand");
+        return nullptr;
+      }
+      rev.push_back(s);
+      starts_from_operand = true;
+      break;
     } else {
       cb.Fail("op '" + op.type + "' cannot be part of an elementwise chain");
       return nullptr;
     }
   }
-  if (!cb.input_index.count(cur) || cb.values[cur].numel() != cb.n) {
+  if (!starts_from_operand && cb.input_index.count(cur) && cb.values[cur].numel() != cb.n && Ok2(cb, cb.values[cur].dtype)) {
+    // A group input smaller than the output that broadcasts by the binary ops' own rule (e.g. bias + scalar).
+    Step s;
+    s.op  = EW_COPY;
+    s.f32 = false;
+    OpDesc fake;
+    fake.type = "elementwise_add";
+    if (cb.ResolveOperand(cur, fake, &s.asel, &s.imm)) {
+      rev.push_back(s);
+      starts_from_operand = true;
+    }
+  }
+  if (!starts_from_operand && (!cb.input_index.count(cur) || cb.values[cur].numel() != cb.n)) {
     cb.Fail("the chain does not start at a full-size group input");
     return nullptr;
   }
-  const int in0       = cb.input_index[cur];
+  const int in0       = starts_from_operand ? cb.sides[0].input : cb.input_index[cur];
   const DType in_type = g.inputs[in0].dtype;
   if (int_class && !IsIntType(in_type) && in_type != DType::kBool) {
     cb.Fail("an integer chain starts at an integer or bool input");
@@ -655,7 +681,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   }
   // Every group input must be used (as the chain start or as a side operand).
   for (size_t i = 0; i < g.inputs.size(); ++i) {
-    bool used = (int)i == in0;
+    bool used = !starts_from_operand && (int)i == in0;
     for (auto& s : cb.sides) used = used || s.input == (int)i;
     if (!used) {
       cb.Fail("group input '" + g.inputs[i].name + "' is not reachable as a chain operand");
@@ -712,7 +738,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   auto in_arg = [](int i) { ArgSpec a; a.kind = ArgSpec::kInput; a.index = i; return a; };
   auto int_arg = [](int64_t v) { ArgSpec a; a.kind = ArgSpec::kInt; a.ivalue = v; return a; };
   st.args.push_back(in_arg(in0));
-  int64_t meta = (int64_t)DTypeKernelCode(in_type) << 24;
+  int64_t meta = (int64_t)(starts_from_operand ? (int)EW_NO_INPUT : DTypeKernelCode(in_type)) << 24;
   ArgSpec aligned;
   aligned.kind   = ArgSpec::kAligned;
   aligned.ivalue = 1;

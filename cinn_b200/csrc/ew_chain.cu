@@ -131,6 +131,10 @@ __device__ __forceinline__ void apply_binary(int op, bool swap, const float (&o)
     EW_BINARY_CASE(EW_LAND, (l != 0.0f && r != 0.0f) ? 1.0f : 0.0f)
     EW_BINARY_CASE(EW_LOR, (l != 0.0f || r != 0.0f) ? 1.0f : 0.0f)
     EW_BINARY_CASE(EW_LXOR, ((l != 0.0f) != (r != 0.0f)) ? 1.0f : 0.0f)
+    case EW_COPY:
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) a[i] = o[i];
+      break;
     default:
       break;
   }
@@ -363,7 +367,8 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
       float acc[8], s1[8], s2[8], s3[8];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
-        load_vec4(in0, in_type, (v + j * stride) << 2, true, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
+        if (in_type != EW_NO_INPUT)
+          load_vec4(in0, in_type, (v + j * stride) << 2, true, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const long long i0 = (v + j * stride) << 2;
@@ -379,7 +384,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
     for (; v < nvec; v += stride) {
       const long long i0 = v << 2;
       float acc[4], s1[4], s2[4], s3[4];
-      load_vec4(in0, in_type, i0, true, acc);
+      if (in_type != EW_NO_INPUT) load_vec4(in0, in_type, i0, true, acc);
       if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
       if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
       if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
@@ -390,7 +395,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
   }
   for (long long i = done + tid; i < n; i += stride) {
     float acc[1], s1[1], s2[1], s3[1];
-    acc[0] = load_scalar(in0, in_type, i);
+    acc[0] = in_type != EW_NO_INPUT ? load_scalar(in0, in_type, i) : 0.0f;
     if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
     if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
     if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);

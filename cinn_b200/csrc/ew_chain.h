@@ -23,6 +23,7 @@ enum EwOp {
   EW_MOD = 14, EW_FLOOR_DIV, EW_ATAN2, EW_LAND, EW_LOR, EW_LXOR,
   // integer chains only
   EW_BAND = 23, EW_BOR, EW_BXOR, EW_SHL, EW_SHR, EW_LSHR,
+  EW_COPY = 29,  // acc = operand: how a chain starts from a broadcast operand when no input has the output's size
   EW_FMA = 20,        // acc = fma(acc, A, B)
   EW_SCALE_PRE = 21,  // acc = imm * (acc + imm_next)
   EW_SELECT = 22,     // acc = cond ? t : f, see the role bits above
@@ -38,7 +39,8 @@ enum EwOp {
 };
 
 // Storage types of the chain kernel's operands (runtime codes; the output type is a template parameter).
-enum EwDType { EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5, EW_F64 = 6 };
+// EW_NO_INPUT as the type of the chain input: there is none, the program starts with EW_COPY.
+enum EwDType { EW_NO_INPUT = 15, EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5, EW_F64 = 6 };
 
 // How a side input is addressed for the flat output index i: value = side[(i / inner) % mid].
 enum EwSideMode {

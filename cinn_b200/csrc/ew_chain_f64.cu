@@ -109,6 +109,7 @@ __device__ __forceinline__ double d_binary(int op, double l, double r) {
     case EW_LAND: return (l != 0.0 && r != 0.0) ? 1.0 : 0.0;
     case EW_LOR: return (l != 0.0 || r != 0.0) ? 1.0 : 0.0;
     case EW_LXOR: return ((l != 0.0) != (r != 0.0)) ? 1.0 : 0.0;
+    case EW_COPY: return r;
     default: return d_binary_heavy(op, l, r);
   }
 }
@@ -232,7 +233,8 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       if (bsel == 0) ++k;
     } else {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] = role != 0 ? d_binary(op, o[i], acc[i]) : d_binary(op, acc[i], o[i]);
+      for (int i = 0; i < VEC; ++i)
+        acc[i] = (role != 0 && op != EW_COPY) ? d_binary(op, o[i], acc[i]) : d_binary(op, acc[i], o[i]);
     }
   }
 }
@@ -262,7 +264,7 @@ __global__ void __launch_bounds__(256)
     for (long long v = tid; v < nvec; v += stride) {
       const long long i0 = v << 2;
       double acc[4], s1[4], s2[4], s3[4];
-      load_d4(in0, in_type, i0, true, acc);
+      if (in_type != EW_NO_INPUT) load_d4(in0, in_type, i0, true, acc);
       if (sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
       if (sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
       if (sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
@@ -273,7 +275,7 @@ __global__ void __launch_bounds__(256)
   }
   for (long long i = done + tid; i < n; i += stride) {
     double acc[1], s1[1], s2[1], s3[1];
-    acc[0] = load_d(in0, in_type, i);
+    acc[0] = in_type != EW_NO_INPUT ? load_d(in0, in_type, i) : 0.0;
     if (sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
     if (sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
     if (sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);

@@ -80,6 +80,7 @@ __device__ __forceinline__ T int_binary(int op, T l, T r) {
     case EW_SHL: return (T)((U)l << ((int)r & (kBits - 1)));
     case EW_SHR: return l >> ((int)r & (kBits - 1));
     case EW_LSHR: return (T)((U)l >> ((int)r & (kBits - 1)));
+    case EW_COPY: return r;
     default: return l;
   }
 }
@@ -199,7 +200,8 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       if (bsel == 0) ++k;
     } else {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] = role != 0 ? int_binary<T>(op, o[i], acc[i]) : int_binary<T>(op, acc[i], o[i]);
+      for (int i = 0; i < VEC; ++i)
+        acc[i] = (role != 0 && op != EW_COPY) ? int_binary<T>(op, o[i], acc[i]) : int_binary<T>(op, acc[i], o[i]);
     }
   }
 }
@@ -228,7 +230,7 @@ __global__ void __launch_bounds__(256)
     for (long long v = tid; v < nvec; v += stride) {
       const long long i0 = v << 2;
       T acc[4], s1[4], s2[4], s3[4];
-      load_int4<T>(in0, in_type, i0, true, acc);
+      if (in_type != EW_NO_INPUT) load_int4<T>(in0, in_type, i0, true, acc);
       if (sd1.mode != EW_SIDE_NONE) load_side<T, 4>(sd1, i0, s1);
       if (sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, s2);
       if (sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, s3);
@@ -239,7 +241,7 @@ __global__ void __launch_bounds__(256)
   }
   for (long long i = done + tid; i < n; i += stride) {
     T acc[1], s1[1], s2[1], s3[1];
-    acc[0] = load_int<T>(in0, in_type, i);
+    acc[0] = in_type != EW_NO_INPUT ? load_int<T>(in0, in_type, i) : 0;
     if (sd1.mode != EW_SIDE_NONE) load_side<T, 1>(sd1, i, s1);
     if (sd2.mode != EW_SIDE_NONE) load_side<T, 1>(sd2, i, s2);
     if (sd3.mode != EW_SIDE_NONE) load_side<T, 1>(sd3, i, s3);

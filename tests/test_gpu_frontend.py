@@ -623,3 +623,24 @@ def test_gelu_relu_grad_and_safe_softmax_compositions(oracle):
     assert [p.split()[0] for _, p in comp.groups()] == ["softmax_safe_row"]
     ref = oracle_program(comp, {"X": X * 30})[str(y)]
     assert oracle.count_not_close(out[str(y)], ref, 1e-5, 1e-30)[0] == 0
+
+
+def test_chain_that_starts_from_a_broadcast_operand(oracle):
+    """No operand has the output's size: broadcast_to alone, and a broadcast followed by arithmetic."""
+    rng = np.random.default_rng(81)
+    V = rng.standard_normal(24).astype(np.float32)
+    b = NetBuilder("bc")
+    v = b.create_input(common.Float(32), (24,), "V")
+    y = b.broadcast_to(v, [5, 24, 7], [1])
+    z = b.exp(b.scale(b.broadcast_to(v, [3, 24], [1]), 0.5, 1.0))
+    comp, out = run_program(b, {"V": V}, [y, z])
+    assert all(p.split()[0] == "ew_chain" for _, p in comp.groups())
+    assert np.array_equal(out[str(y)], np.broadcast_to(V.reshape(1, 24, 1), (5, 24, 7)))
+    ref = oracle_program(comp, {"V": V})[str(z)]
+    assert oracle.max_ulp(out[str(z)], ref) <= 2
+    I = rng.integers(-100, 100, (6,), dtype=np.int32)
+    b = NetBuilder("bci")
+    i = b.create_input(common.Int(32), (6,), "I")
+    y = b.negative(b.broadcast_to(i, [6, 10], [0]))
+    comp, out = run_program(b, {"I": I}, [y])
+    assert np.array_equal(out[str(y)], -np.broadcast_to(I.reshape(6, 1), (6, 10)))
