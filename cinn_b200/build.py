@@ -20,6 +20,7 @@ SOURCES = [
     "reduce_kernels.cu",
     "reduce_generic.cu",
     "channel_reduce.cu",
+    "transform_kernels.cu",
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
     "softmax_safe.cu",

@@ -110,7 +110,8 @@ bool BroadcastShape(const std::vector<int64_t>& a, const std::vector<int64_t>& b
 bool KnownOp(const std::string& t) {
   return UnaryOps().count(t) || BinaryOps().count(t) || CompareOps().count(t) || ReduceOps().count(t) ||
          t == "scale" || t == "cast" || t == "select" || t == "broadcast_to" || t == "fill_constant" ||
-         t == "softmax" || t == "batch_norm" || t == "reshape";
+         t == "softmax" || t == "batch_norm" || t == "reshape" || t == "squeeze" || t == "expand_dims" ||
+         t == "transpose" || t == "slice" || t == "concat";
 }
 
 OpPattern PatternOf(const std::string& t) {
@@ -118,6 +119,8 @@ OpPattern PatternOf(const std::string& t) {
   if (ReduceOps().count(t)) return OpPattern::kReduction;
   if (t == "broadcast_to") return OpPattern::kBroadcast;
   if (t == "reshape") return OpPattern::kNonFusible;
+  // Data movement (registered kInjective in the reference, cinn/hlir/op/transform.cc): a kernel of its own here.
+  if (t == "transpose" || t == "slice" || t == "concat") return OpPattern::kNonFusible;
   // softmax is registered kNonFusible in the reference (cinn/hlir/op/nn.cc:2383-2393); here the casts around
   // it may join its group, so it takes part in fusion like an elementwise op.
   return OpPattern::kElementWise;
@@ -175,6 +178,35 @@ int NetBuilder::AddOp(const std::string& op, const std::vector<int>& inputs,
   auto attrs = attrs_in;
   auto in    = [&](int k) -> const Variable& { return vars_[inputs[k]]; };
   auto need  = [&](size_t n) { return inputs.size() == n; };
+  if (op == "squeeze" || op == "expand_dims") {
+    // Both only change the shape: they become a reshape, which aliases its operand's memory.
+    if (!need(1)) return fail("takes 1 input");
+    std::vector<int64_t> axes = ParseIntList(attrs.count("axes") ? attrs["axes"] : "");
+    std::vector<int64_t> shape;
+    const int nd = (int)in(0).shape.size();
+    if (op == "squeeze") {
+      for (auto& a : axes)
+        if (a < 0) a += nd;
+      for (int i = 0; i < nd; ++i) {
+        const bool listed = std::find(axes.begin(), axes.end(), (int64_t)i) != axes.end();
+        if (listed && in(0).shape[i] != 1) return fail("squeezed axis has extent " + std::to_string(in(0).shape[i]));
+        if (!(in(0).shape[i] == 1 && (axes.empty() || listed))) shape.push_back(in(0).shape[i]);
+      }
+      if (shape.empty()) shape.push_back(1);
+    } else {
+      // cinn/hlir/op/transform.cc expand_dims: each listed position of the RESULT gets an extent-1 axis
+      const int out_nd = nd + (int)axes.size();
+      std::vector<bool> is_new(out_nd, false);
+      for (auto a : axes) {
+        if (a < 0) a += out_nd;
+        if (a < 0 || a >= out_nd) return fail("axis out of range");
+        is_new[a] = true;
+      }
+      int k = 0;
+      for (int i = 0; i < out_nd; ++i) shape.push_back(is_new[i] ? 1 : in(0).shape[k++]);
+    }
+    return AddOp("reshape", inputs, {{"shape", JoinInts(shape)}}, err);
+  }
   Variable out;
   if (UnaryOps().count(op)) {
     if (!need(1)) return fail("takes 1 input");
@@ -293,6 +325,73 @@ int NetBuilder::AddOp(const std::string& op, const std::vector<int>& inputs,
     if (n != total) return fail("element count changes");
     attrs["shape"] = JoinInts(out.shape);
     out.dtype      = in(0).dtype;
+  } else if (op == "transpose") {
+    if (!need(1)) return fail("takes 1 input");
+    const int nd = (int)in(0).shape.size();
+    std::vector<int64_t> perm = ParseIntList(attrs.count("axis") ? attrs["axis"] : "");
+    if ((int)perm.size() != nd) return fail("'axis' must list every axis once");
+    std::vector<bool> seen(nd, false);
+    for (auto& a : perm) {
+      if (a < 0) a += nd;
+      if (a < 0 || a >= nd || seen[a]) return fail("'axis' must be a permutation");
+      seen[a] = true;
+      out.shape.push_back(in(0).shape[a]);
+    }
+    attrs["axis"] = JoinInts(perm);
+    out.dtype     = in(0).dtype;
+  } else if (op == "concat") {
+    if (inputs.empty()) return fail("takes at least 1 input");
+    const int nd = (int)in(0).shape.size();
+    int64_t axis = attrs.count("axis") ? atoll(attrs["axis"].c_str()) : 0;
+    if (axis < 0) axis += nd;
+    if (axis < 0 || axis >= nd) return fail("axis out of range");
+    out.shape = in(0).shape;
+    out.dtype = in(0).dtype;
+    for (size_t k = 1; k < inputs.size(); ++k) {
+      if (in(k).dtype != out.dtype || (int)in(k).shape.size() != nd) return fail("operands differ in type or rank");
+      for (int i = 0; i < nd; ++i)
+        if (i != axis && in(k).shape[i] != out.shape[i]) return fail("operands differ outside the concat axis");
+      out.shape[axis] += in(k).shape[axis];
+      for (size_t q = 0; q < k; ++q)
+        if (inputs[q] == inputs[k]) return fail("the same variable twice has no prebuilt kernel");
+    }
+    attrs["axis"] = std::to_string(axis);
+  } else if (op == "slice") {
+    if (!need(1)) return fail("takes 1 input");
+    const int nd = (int)in(0).shape.size();
+    std::vector<int64_t> axes = ParseIntList(attrs.count("axes") ? attrs["axes"] : ""),
+                         starts = ParseIntList(attrs.count("starts") ? attrs["starts"] : ""),
+                         ends = ParseIntList(attrs.count("ends") ? attrs["ends"] : ""),
+                         strides = ParseIntList(attrs.count("strides") ? attrs["strides"] : ""),
+                         decrease = ParseIntList(attrs.count("decrease_axis") ? attrs["decrease_axis"] : "");
+    if (starts.size() != axes.size() || ends.size() != axes.size()) return fail("axes / starts / ends differ in length");
+    std::vector<int64_t> shape = in(0).shape;
+    for (size_t k = 0; k < axes.size(); ++k) {
+      int64_t a = axes[k] < 0 ? axes[k] + nd : axes[k];
+      if (a < 0 || a >= nd) return fail("axis out of range");
+      const int64_t dim = in(0).shape[a], st = k < strides.size() ? strides[k] : 1;
+      int64_t b = starts[k] < 0 ? starts[k] + dim : starts[k], e = ends[k] < 0 ? ends[k] + dim : ends[k];
+      if (st > 0) {
+        b = std::min(std::max<int64_t>(b, 0), dim);
+        e = std::min(std::max<int64_t>(e, 0), dim);
+        shape[a] = e > b ? (e - b + st - 1) / st : 0;
+      } else if (st < 0) {
+        b = std::min(std::max<int64_t>(b, -1), dim - 1);
+        e = std::min(std::max<int64_t>(e, -1), dim - 1);
+        shape[a] = b > e ? (b - e + (-st) - 1) / (-st) : 0;
+      } else {
+        return fail("zero stride");
+      }
+      if (shape[a] <= 0) return fail("empty slice");
+    }
+    for (int i = 0; i < nd; ++i) {
+      bool drop = false;
+      for (auto d : decrease) drop = drop || (d < 0 ? d + nd : d) == i;
+      if (drop && shape[i] != 1) return fail("decrease_axis on an axis of extent " + std::to_string(shape[i]));
+      if (!drop) out.shape.push_back(shape[i]);
+    }
+    if (out.shape.empty()) out.shape.push_back(1);
+    out.dtype = in(0).dtype;
   }
   if (out.shape.size() > CINN_BUFFER_MAX_DIMS) return fail("result has more than 8 dimensions");
   out.id = NewId("");

@@ -358,6 +358,202 @@ struct Matcher {
     return p;
   }
 
+  // ---- transpose / slice / concat (cinn/hlir/op/transform.cc): data movement, typed by element size ----------
+  static std::vector<int64_t> StridesOf(const std::vector<int64_t>& shape) {
+    std::vector<int64_t> st(shape.size(), 1);
+    for (int i = (int)shape.size() - 2; i >= 0; --i) st[i] = st[i + 1] * shape[i + 1];
+    return st;
+  }
+
+  bool GatherStep(CompiledGroup* p, int es, const std::vector<int64_t>& ext, const std::vector<int64_t>& str, int64_t base,
+                  int64_t n) {
+    if (ext.size() > 6) return Fail("more than six axes after merging have no prebuilt kernel");
+    LaunchStep s;
+    if (!Kernel(&s, "strided_gather_b" + std::to_string(es))) return false;
+    s.block[0] = 256;
+    s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(n, 256), (int64_t)dev.sm_count * 32));
+    s.args     = {In(0), Out(0), I(n), I(base), I((int64_t)ext.size())};
+    for (int d = 0; d < 6; ++d) s.args.push_back(I(d < (int)ext.size() ? ext[d] : 1));
+    for (int d = 0; d < 6; ++d) s.args.push_back(I(d < (int)str.size() ? str[d] : 0));
+    p->steps.push_back(s);
+    return true;
+  }
+
+  std::unique_ptr<CompiledGroup> MatchTransform(const std::string& expr) {
+    static const std::regex concat_form(R"(^concat\((%\d+)(,%\d+)*\)$)");
+    const bool is_concat = std::regex_match(expr, concat_form);
+    if (expr != "transpose(%0)" && expr != "slice(%0)" && !is_concat) return nullptr;
+    const auto& o     = g.outputs[0];
+    const OpDesc& op  = g.ops.back();
+    const int es      = DTypeBytes(o.dtype);
+    for (auto& t : g.inputs)
+      if (t.dtype != o.dtype) {
+        Fail("operands and result must have one element type");
+        return nullptr;
+      }
+    if (es != 1 && es != 2 && es != 4 && es != 8) return nullptr;
+    if (is_concat) {
+      const int nd = (int)o.shape.size();
+      int64_t axis = AttrI(op, "axis", 0);
+      if (axis < 0) axis += nd;
+      if (axis < 0 || axis >= nd || g.inputs.size() != op.inputs.size()) {
+        Fail("concat: bad axis or repeated operand");
+        return nullptr;
+      }
+      int64_t outer = 1, inner = 1, total = 0;
+      for (int i = 0; i < axis; ++i) outer *= o.shape[i];
+      for (int i = axis + 1; i < nd; ++i) inner *= o.shape[i];
+      for (auto& t : g.inputs) total += t.shape[axis];
+      if (total != o.shape[axis]) {
+        Fail("concat: operand extents do not add up to the output extent");
+        return nullptr;
+      }
+      auto p      = NewPlan("concat_rows");
+      p->elements = o.numel();
+      for (int pass = 0; pass < 2; ++pass) {  // 0: widest unit (needs 16-byte aligned buffers), 1: element-sized units
+        int ub = pass == 0 ? 16 : es;
+        if (pass == 0) {
+          int64_t all = o.shape[axis] * inner * es;
+          int64_t off = 0;
+          for (auto& t : g.inputs) {
+            all |= t.shape[axis] * inner * es | off;
+            off += t.shape[axis] * inner * es;
+          }
+          while (ub > es && all % ub != 0) ub /= 2;
+        }
+        std::vector<LaunchStep>& dst = pass == 0 ? p->steps : p->steps_unaligned;
+        int64_t off_elems            = 0;
+        for (size_t k = 0; k < g.inputs.size(); ++k) {
+          // operands are bound in the order the op lists them
+          int idx = -1;
+          for (size_t q = 0; q < g.inputs.size(); ++q)
+            if (g.inputs[q].name == op.inputs[k]) idx = (int)q;
+          const int64_t w = g.inputs[idx].shape[axis] * inner;
+          LaunchStep s;
+          if (!Kernel(&s, "copy_rows_b" + std::to_string(ub))) return nullptr;
+          const int64_t units = outer * w * es / ub;
+          s.block[0] = 256;
+          s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(units, 256), (int64_t)dev.sm_count * 32));
+          s.args     = {In(idx), Out(0), I(outer), I(w * es / ub), I(o.shape[axis] * inner * es / ub), I(off_elems * es / ub)};
+          if (units > 0) dst.push_back(s);
+          off_elems += w;
+        }
+      }
+      for (size_t q = 0; q < g.inputs.size(); ++q) p->aligned_inputs.push_back((int)q);
+      p->aligned_outputs = {0};
+      return p;
+    }
+    const auto& x = g.inputs[0];
+    const int nd  = (int)x.shape.size();
+    const std::vector<int64_t> in_str = StridesOf(x.shape);
+    if (expr == "slice(%0)") {
+      std::vector<int64_t> axes = AttrList(op, "axes"), starts = AttrList(op, "starts"), ends = AttrList(op, "ends"),
+                           strides = AttrList(op, "strides");
+      std::vector<int64_t> start(nd, 0), step(nd, 1), ext = x.shape;
+      if (starts.size() != axes.size() || ends.size() != axes.size()) {
+        Fail("slice: axes / starts / ends differ in length");
+        return nullptr;
+      }
+      for (size_t k = 0; k < axes.size(); ++k) {
+        int64_t a = axes[k] < 0 ? axes[k] + nd : axes[k];
+        if (a < 0 || a >= nd) {
+          Fail("slice: axis out of range");
+          return nullptr;
+        }
+        // cinn/hlir/pe/transform.cc Slice: negative positions count from the end, positions are clamped
+        const int64_t dim = x.shape[a], st = k < strides.size() ? strides[k] : 1;
+        int64_t b = starts[k] < 0 ? starts[k] + dim : starts[k], e = ends[k] < 0 ? ends[k] + dim : ends[k];
+        if (st > 0) {
+          b = std::min(std::max<int64_t>(b, 0), dim);
+          e = std::min(std::max<int64_t>(e, 0), dim);
+          ext[a] = e > b ? CeilDiv(e - b, st) : 0;
+        } else if (st < 0) {
+          b = std::min(std::max<int64_t>(b, -1), dim - 1);
+          e = std::min(std::max<int64_t>(e, -1), dim - 1);
+          ext[a] = b > e ? CeilDiv(b - e, -st) : 0;
+        } else {
+          Fail("slice: zero stride");
+          return nullptr;
+        }
+        start[a] = b;
+        step[a]  = st;
+      }
+      int64_t n = 1, base = 0;
+      std::vector<int64_t> e2, s2;
+      for (int a = 0; a < nd; ++a) {
+        n *= ext[a];
+        base += start[a] * in_str[a];
+        if (ext[a] != 1) {
+          e2.push_back(ext[a]);
+          s2.push_back(step[a] * in_str[a]);
+        }
+      }
+      if (n != o.numel() || n == 0) {
+        Fail("slice: the output has " + std::to_string(o.numel()) + " elements, the slice " + std::to_string(n));
+        return nullptr;
+      }
+      auto p      = NewPlan("slice_gather");
+      p->elements = n;
+      if (!GatherStep(p.get(), es, e2, s2, base, n)) return nullptr;
+      return p;
+    }
+    // transpose: out axis k is in axis perm[k]
+    std::vector<int64_t> perm = AttrList(op, "axis");
+    if ((int)perm.size() != nd) {
+      Fail("transpose: 'axis' must list every axis");
+      return nullptr;
+    }
+    std::vector<int64_t> ext, str, first;  // merged output axes: extent, input stride, first input axis of the run
+    int64_t prev = -2;
+    for (int k = 0; k < nd; ++k) {
+      int64_t a = perm[k] < 0 ? perm[k] + nd : perm[k];
+      if (a < 0 || a >= nd) {
+        Fail("transpose: axis out of range");
+        return nullptr;
+      }
+      if (x.shape[a] == 1) continue;
+      // the next non-unit input axis after `prev`?
+      int64_t nxt = prev + 1;
+      while (prev >= 0 && nxt < nd && x.shape[nxt] == 1) ++nxt;
+      if (prev >= 0 && a == nxt) {
+        ext.back() *= x.shape[a];
+        str.back() = in_str[a];
+      } else {
+        ext.push_back(x.shape[a]);
+        str.push_back(in_str[a]);
+        first.push_back(a);
+      }
+      prev = a;
+    }
+    const int m = (int)ext.size();
+    const int64_t n = x.numel();
+    if (n != o.numel()) {
+      Fail("transpose: element counts differ");
+      return nullptr;
+    }
+    bool tiled = m >= 2 && str[m - 2] == 1;  // the input's innermost run becomes the output's second-to-last
+    for (int d = 0; tiled && d + 1 < m - 2; ++d) tiled = first[d] < first[d + 1];
+    if (tiled && m >= 3) tiled = first[m - 3] < first[m - 1];
+    if (tiled) tiled = first[m - 1] < first[m - 2];
+    auto p      = NewPlan(tiled ? "transpose_tiled" : "transpose_gather");
+    p->elements = n;
+    if (tiled) {
+      int64_t B = 1;
+      for (int d = 0; d < m - 2; ++d) B *= ext[d];
+      const int64_t C = ext[m - 2], R = ext[m - 1];
+      LaunchStep s;
+      if (!Kernel(&s, "transpose_tiled_b" + std::to_string(es))) return nullptr;
+      s.block[0] = 256;
+      const int64_t tiles = B * CeilDiv(R, 64) * CeilDiv(C, 64);
+      s.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>(tiles, (int64_t)dev.sm_count * 64));
+      s.args    = {In(0), Out(0), I(B), I(R), I(C)};
+      p->steps.push_back(s);
+      return p;
+    }
+    if (!GatherStep(p.get(), es, ext, str, 0, n)) return nullptr;
+    return p;
+  }
+
   // ---- reduce_{sum,prod,max,min}(%0) -----------------------------------------------------------
   // cinn/hlir/op/reduction.cc:49-158 (dim normalisation: negative dims wrap, empty = all), cinn/hlir/pe/reduction.cc.
   static bool ReduceView(const std::vector<int64_t>& shape, std::vector<int64_t> dims, int64_t* outer, int64_t* r,
@@ -990,8 +1186,8 @@ struct Matcher {
     }
     typedef std::unique_ptr<CompiledGroup> (Matcher::*Fn)(const std::string&);
     const Fn fns[] = {&Matcher::MatchAddRelu, &Matcher::MatchBiasScaleTanhCast, &Matcher::MatchBatchNorm,
-                      &Matcher::MatchBnTrainApply, &Matcher::MatchReduce,       &Matcher::MatchSoftmax,
-                      &Matcher::MatchLayerNorm};
+                      &Matcher::MatchBnTrainApply, &Matcher::MatchTransform,    &Matcher::MatchReduce,
+                      &Matcher::MatchSoftmax,      &Matcher::MatchLayerNorm};
     for (Fn f : fns) {
       auto p = (this->*f)(expr);
       if (p) return p;

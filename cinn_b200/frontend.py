@@ -169,6 +169,22 @@ class NetBuilder:
     def reshape(self, x, shape):
         return self._op("reshape", [x], shape=list(shape))
 
+    def squeeze(self, x, axes=()):
+        return self._op("squeeze", [x], axes=list(axes) or None)
+
+    def expand_dims(self, x, axes):
+        return self._op("expand_dims", [x], axes=list(axes))
+
+    def transpose(self, x, axis):
+        return self._op("transpose", [x], axis=list(axis))
+
+    def concat(self, inputs, axis=0):
+        return self._op("concat", list(inputs), axis=int(axis))
+
+    def slice(self, x, axes, starts, ends, infer_flags=(), strides=(), decrease_axis=()):
+        return self._op("slice", [x], axes=list(axes), starts=list(starts), ends=list(ends),
+                        strides=list(strides) or None, decrease_axis=list(decrease_axis) or None)
+
     def reduce_sum(self, x, dim=(), keep_dim=False):
         return self._op("reduce_sum", [x], dim=list(dim) or None, keep_dim=keep_dim)
 

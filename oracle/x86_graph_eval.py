@@ -300,6 +300,33 @@ def evaluate(desc, inputs):
             if keep:
                 oshape = [1 if i in dims else d for i, d in enumerate(x.shape)]
             out = res.reshape(oshape if oshape else (1,))
+        elif t == "transpose":
+            out = np.transpose(vals[ins[0]], [int(d) for d in at["axis"].split(",")])
+        elif t == "concat":
+            out = np.concatenate([vals[i] for i in ins], axis=int(at.get("axis", 0)))
+        elif t == "reshape":
+            out = vals[ins[0]].reshape([int(d) for d in at["shape"].split(",")])
+        elif t == "slice":
+            x = vals[ins[0]]
+            ints = lambda k: [int(d) for d in at[k].split(",")] if at.get(k) else []  # noqa: E731
+            sl = [slice(None)] * x.ndim
+            strides = ints("strides")
+            for k, a in enumerate(ints("axes")):
+                a %= x.ndim
+                st = strides[k] if k < len(strides) else 1
+                b, e = ints("starts")[k], ints("ends")[k]
+                dim = x.shape[a]
+                b = b + dim if b < 0 else b
+                e = e + dim if e < 0 else e
+                if st > 0:
+                    sl[a] = slice(min(max(b, 0), dim), min(max(e, 0), dim), st)
+                else:   # positions clamped to [-1, dim - 1]; -1 means "before the first element"
+                    b, e = min(max(b, -1), dim - 1), min(max(e, -1), dim - 1)
+                    sl[a] = slice(b, e if e >= 0 else None, st)
+            out = x[tuple(sl)]
+            drop = [d % x.ndim for d in ints("decrease_axis")]
+            if drop:
+                out = out.reshape([d for i, d in enumerate(out.shape) if i not in drop] or [1])
         elif t == "softmax":
             out = orc.softmax(vals[ins[0]])
         elif t == "batch_norm":
