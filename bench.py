@@ -212,6 +212,11 @@ def side_groups(torch, dev, peak, only=None):
         ("bn_relu_f16_256x64x112x112", lambda: W.bn_relu((256, 64, 112, 112), half=True), 1, ""),
         ("softmax_max_subtracted_f32_16384x4096", lambda: W.softmax_safe((16384, 4096)), 2, "decomposed softmax, mode != fast"),
         ("softmax_max_subtracted_f16_16384x4096", lambda: W.softmax_safe((16384, 4096), half=True), 2, ""),
+        # data movement either side of the groups
+        ("transpose_nchw_to_nhwc_f32_256x64x112x112", lambda: W.transpose((256, 64, 112, 112), (0, 2, 3, 1)), 1, ""),
+        ("transpose_nhwc_to_nchw_f16_256x112x112x64", lambda: W.transpose((256, 112, 112, 64), (0, 3, 1, 2), "float16"), 1, ""),
+        ("transpose_matrix_f32_8192x8192", lambda: W.transpose((8192, 8192), (1, 0)), 1, ""),
+        ("concat_axis1_f32_2x(4096x8192)", lambda: W.concat([(4096, 8192), (4096, 8192)], 1), 1, ""),
         # batch_norm_train as the reference decomposes it: one statistics pass (two outputs) + one normalisation pass
         ("bn_train_stats_256x64x112x112", lambda: W.bn_train_stats((256, 64, 112, 112)), 1,
          "sum and sum of squares per channel in one read of x"),
@@ -261,6 +266,7 @@ PROFILE_GROUPS = {
     "layer_norm_f16": lambda W: W.layer_norm((16384, 4096), half=True),
     "bn_relu_f32": lambda W: W.bn_relu((256, 64, 112, 112)),
     "bn_relu_f16": lambda W: W.bn_relu((256, 64, 112, 112), half=True),
+    "transpose_nchw_to_nhwc": lambda W: W.transpose((256, 64, 112, 112), (0, 2, 3, 1)),
     "softmax_safe_f32": lambda W: W.softmax_safe((16384, 4096)),
     "bn_train_stats": lambda W: W.bn_train_stats((256, 64, 112, 112)),
     "bn_train_apply": lambda W: W.bn_train_apply((256, 64, 112, 112)),

@@ -547,7 +547,18 @@ struct Matcher {
       const int64_t tiles = B * CeilDiv(R, 64) * CeilDiv(C, 64);
       s.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>(tiles, (int64_t)dev.sm_count * 64));
       s.args    = {In(0), Out(0), I(B), I(R), I(C)};
-      p->steps.push_back(s);
+      const int ve = 16 / es;
+      if (R % ve == 0 && C % ve == 0) {
+        // 16-byte accesses on both sides when the buffers are aligned; the element-wise tiles otherwise.
+        LaunchStep v = s;
+        if (!Kernel(&v, "transpose_vec_b" + std::to_string(es))) return nullptr;
+        p->steps.push_back(v);
+        p->steps_unaligned.push_back(s);
+        p->aligned_inputs  = {0};
+        p->aligned_outputs = {0};
+      } else {
+        p->steps.push_back(s);
+      }
       return p;
     }
     if (!GatherStep(p.get(), es, ext, str, 0, n)) return nullptr;

@@ -3,8 +3,9 @@
 // are aliases of their operand's memory and launch nothing).  They move bits, so the kernels are typed by element
 // SIZE only (1, 2, 4 or 8 bytes) and every element type shares them.
 //
-//   k_transpose_tiled   a permutation that collapses to [B, R, C] -> [B, C, R]: 64 x 64 tiles through padded shared
-//                       memory, coalesced on both sides (NCHW <-> NHWC, matrix transposes, ...)
+//   k_transpose_vec     a permutation that collapses to [B, R, C] -> [B, C, R] (NCHW <-> NHWC, matrix transposes):
+//                       64 x 64 tiles through padded shared memory, 16-byte global accesses on both sides
+//   k_transpose_tiled   the same with element-sized accesses, for odd extents or unaligned buffers
 //   k_strided_gather    any other permutation and every slice: out[i] = in[base + sum_d coord_d(i) * stride_d]
 //   k_copy_rows         concat: each operand's rows are copied to their column offset of the output rows
 #include <cstdint>
@@ -52,6 +53,62 @@ __global__ void __launch_bounds__(256)
     for (int k = 0; k < kTile / 4; ++k) {
       const int c = ty + 4 * k;
       if (c0 + c < C && r0 + tx < R) pout[(c0 + c) * R + r0 + tx] = tile[tx][c];
+    }
+    __syncthreads();
+  }
+}
+
+// The same transposition with 16-byte global accesses on both sides (R and C multiples of 16 / ES elements, 16-byte
+// aligned buffers): a thread loads a vector of a tile row, scatters its elements into the padded tile, and after the
+// barrier gathers a vector of a tile COLUMN and stores it.  Consecutive lanes take consecutive vectors of a row, so
+// every warp access is a run of 256 contiguous bytes (or the whole tile row).
+template <int ES>
+__global__ void __launch_bounds__(256)
+    k_transpose_vec(const void* __restrict__ in_v, void* __restrict__ out_v, long long B, long long R, long long C) {
+  using U          = typename UnitOf<ES>::type;
+  constexpr int VE = 16 / ES;                       // elements per 16-byte vector
+  constexpr int VR = kTile / VE;                    // vectors per tile row
+  constexpr int RP = 256 / VR;                      // tile rows handled per pass of the CTA
+  constexpr int STRIDE = kTile + (ES >= 4 ? 1 : 4 / ES);  // row stride: an odd number of 32-bit words
+  __shared__ U tile[kTile][STRIDE];
+  const U* in = static_cast<const U*>(in_v);
+  U* out      = static_cast<U*>(out_v);
+  const int vq = threadIdx.x % VR, rq = threadIdx.x / VR;
+  const long long tiles_c = (C + kTile - 1) / kTile, tiles_r = (R + kTile - 1) / kTile;
+  const long long total   = B * tiles_r * tiles_c;
+  for (long long t = blockIdx.x; t < total; t += gridDim.x) {
+    const long long b  = t / (tiles_r * tiles_c);
+    const long long rc = t - b * tiles_r * tiles_c;
+    const long long tr = rc / tiles_c, tc = rc - tr * tiles_c;
+    const long long r0 = tr * kTile, c0 = tc * kTile;
+    const U* pin = in + b * R * C;
+    U* pout      = out + b * R * C;
+    uint4 v[kTile / RP];
+#pragma unroll
+    for (int k = 0; k < kTile / RP; ++k) {
+      const int r = rq + RP * k;
+      if (r0 + r < R && c0 + vq * VE < C) v[k] = __ldcs(reinterpret_cast<const uint4*>(pin + (r0 + r) * C + c0 + vq * VE));
+    }
+#pragma unroll
+    for (int k = 0; k < kTile / RP; ++k) {
+      const int r = rq + RP * k;
+      if (r0 + r < R && c0 + vq * VE < C) {
+        const U* e = reinterpret_cast<const U*>(&v[k]);
+#pragma unroll
+        for (int i = 0; i < VE; ++i) tile[r][vq * VE + i] = e[i];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < kTile / RP; ++k) {
+      const int c = rq + RP * k;
+      if (c0 + c < C && r0 + vq * VE < R) {
+        uint4 w;
+        U* e = reinterpret_cast<U*>(&w);
+#pragma unroll
+        for (int i = 0; i < VE; ++i) e[i] = tile[vq * VE + i][c];
+        __stcs(reinterpret_cast<uint4*>(pout + (c0 + c) * R + r0 + vq * VE), w);
+      }
     }
     __syncthreads();
   }
@@ -122,6 +179,7 @@ __global__ void __launch_bounds__(256)
 
 #define REG_TRANSFORM(ES)                                                                          \
   CINN_B200_REGISTER_KERNEL("transpose_tiled_b" #ES, 5, 256, k_transpose_tiled<ES>);             \
+  CINN_B200_REGISTER_KERNEL("transpose_vec_b" #ES, 5, 256, k_transpose_vec<ES>);                 \
   CINN_B200_REGISTER_KERNEL("strided_gather_b" #ES, 17, 256, k_strided_gather<ES>)
 REG_TRANSFORM(1);
 REG_TRANSFORM(2);

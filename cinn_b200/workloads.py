@@ -315,3 +315,23 @@ def softmax_safe(shape=(16384, 4096), seed=3, half=False):
     desc = "group fn_softmax_safe_%s\ninput X %s %s\n%s\noutput %s %s %s\n" % (dt, dt, s, "\n".join(lines), out, dt, s)
     npdt = np.float16 if half else np.float32
     return Workload("softmax_safe_" + dt, desc, lambda: [(3 * rownorm_inputs(shape, seed)[0]).astype(npdt)], npdt, shape)
+
+
+def transpose(shape, perm, dtype="float32", seed=7):
+    out_shape = tuple(shape[p] for p in perm)
+    desc = ("group fn_transpose\ninput X %s %s\nop transpose y = X ; axis=%s\noutput y %s %s\n"
+            % (dtype, _shape(shape), ",".join(map(str, perm)), dtype, _shape(out_shape)))
+    return Workload("transpose", desc, lambda: [_draw(np.random.default_rng(seed), shape, dtype)], _NP[dtype], out_shape)
+
+
+def concat(shapes, axis, dtype="float32", seed=8):
+    out_shape = list(shapes[0])
+    out_shape[axis] = sum(s[axis] for s in shapes)
+    ins = "\n".join("input X%d %s %s" % (i, dtype, _shape(s)) for i, s in enumerate(shapes))
+    desc = ("group fn_concat\n%s\nop concat y = %s ; axis=%d\noutput y %s %s\n"
+            % (ins, " ".join("X%d" % i for i in range(len(shapes))), axis, dtype, _shape(out_shape)))
+
+    def gen():
+        rng = np.random.default_rng(seed)
+        return [_draw(rng, s, dtype) for s in shapes]
+    return Workload("concat", desc, gen, _NP[dtype], out_shape)
