@@ -108,6 +108,33 @@ cinn_b200_computation* cinn_b200_computation_build_and_compile(cinn_b200_builder
 
 void cinn_b200_computation_destroy(cinn_b200_computation* c) { delete c; }
 
+long long cinn_b200_computation_export(cinn_b200_computation* c, char* out, size_t out_len) {
+  if (!c) return SetLastError(CINN_B200_EINVAL, "export: null computation");
+  const std::string text = c->impl->Export();
+  if (out && out_len > 0) {
+    const size_t n = std::min(out_len - 1, text.size());
+    memcpy(out, text.data(), n);
+    out[n] = 0;
+  }
+  return (long long)text.size() + 1;
+}
+
+cinn_b200_computation* cinn_b200_program_load(const char* text, int device) {
+  if (!text) {
+    SetLastError(CINN_B200_EINVAL, "program_load: null text");
+    return nullptr;
+  }
+  std::string err;
+  auto impl = Computation::Load(text, device, &err);
+  if (!impl) {
+    SetLastError(CINN_B200_ENOMATCH, err);
+    return nullptr;
+  }
+  auto* c = new cinn_b200_computation();
+  c->impl = std::move(impl);
+  return c;
+}
+
 int cinn_b200_computation_execute(cinn_b200_computation* c, void* stream) {
   if (!c) return SetLastError(CINN_B200_EINVAL, "execute: null computation");
   std::string err;

@@ -767,26 +767,7 @@ std::unique_ptr<Computation> Computation::BuildAndCompile(const NetBuilder& b, c
   }
   if (!FusePasses(b, fetch, dev, &c->groups_, err)) return nullptr;
   // Scope: one tensor per variable that crosses a group boundary (cinn/hlir/framework/graph_compiler.cc:1430-1451).
-  auto add_tensor = [&](int v) {
-    const Variable& var = b.vars()[v];
-    if (c->scope_.count(var.id)) return;
-    auto t    = std::make_unique<ScopeTensor>();
-    t->var    = var;
-    memset(&t->buffer, 0, sizeof(t->buffer));
-    t->buffer.device     = cinn_unk_device;
-    t->buffer.flag       = cinn_buffer_on_device;
-    t->buffer.type       = RuntimeType(var.dtype);
-    t->buffer.dimensions = (int32_t)var.shape.size();
-    int64_t n            = 1;
-    for (size_t i = 0; i < var.shape.size(); ++i) {
-      t->buffer.dims[i] = (cinn_dimension_t)var.shape[i];
-      n *= var.shape[i];
-    }
-    t->bytes              = (size_t)n * DTypeBytes(var.dtype);
-    t->buffer.memory_size = t->bytes;
-    c->names_.push_back(var.id);
-    c->scope_[var.id] = std::move(t);
-  };
+  auto add_tensor = [&](int v) { c->AddScopeTensor(b.vars()[v]); };
   for (auto& g : c->groups_) {
     for (int v : g.input_vars) add_tensor(v);
     for (int v : g.output_vars) add_tensor(v);
@@ -810,22 +791,141 @@ std::unique_ptr<Computation> Computation::BuildAndCompile(const NetBuilder& b, c
     for (int v : g.output_vars) ins.args.push_back(b.vars()[v].id);
     c->instrs_.push_back(std::move(ins));
   }
+  if (device >= 0 && !c->AllocateScope(err)) return nullptr;
+  return c;
+}
+
+void Computation::AddScopeTensor(const Variable& var) {
+  if (scope_.count(var.id)) return;
+  auto t    = std::make_unique<ScopeTensor>();
+  t->var    = var;
+  memset(&t->buffer, 0, sizeof(t->buffer));
+  t->buffer.device     = cinn_unk_device;
+  t->buffer.flag       = cinn_buffer_on_device;
+  t->buffer.type       = RuntimeType(var.dtype);
+  t->buffer.dimensions = (int32_t)var.shape.size();
+  int64_t n            = 1;
+  for (size_t i = 0; i < var.shape.size(); ++i) {
+    t->buffer.dims[i] = (cinn_dimension_t)var.shape[i];
+    n *= var.shape[i];
+  }
+  t->bytes              = (size_t)n * DTypeBytes(var.dtype);
+  t->buffer.memory_size = t->bytes;
+  names_.push_back(var.id);
+  scope_[var.id] = std::move(t);
+}
+
+// cinn/hlir/framework/memory.cc:43-52: device memory from cudaMalloc, owned by the scope (alias results own none).
+bool Computation::AllocateScope(std::string* err) {
+  std::set<std::string> alias_outputs;
+  for (auto& a : aliases_) alias_outputs.insert(a.first);
+  for (auto& kv : scope_) {
+    if (alias_outputs.count(kv.first)) continue;
+    void* p       = nullptr;
+    cudaError_t e = cudaMalloc(&p, std::max<size_t>(kv.second->bytes, 16));
+    if (e != cudaSuccess) {
+      if (err) *err = "cudaMalloc of tensor " + kv.first + ": " + cudaGetErrorString(e);
+      return false;
+    }
+    kv.second->buffer.memory = static_cast<uint8_t*>(p);
+    kv.second->owned         = true;
+  }
+  return true;
+}
+
+std::string Computation::Export() const {
+  std::ostringstream os;
+  os << "cinn_b200_program 1\n";
+  for (auto& name : names_) {
+    const Variable& v = scope_.at(name)->var;
+    os << "tensor " << v.id << " " << DTypeName(v.dtype) << " ";
+    for (size_t i = 0; i < v.shape.size(); ++i) os << (i ? "," : "") << v.shape[i];
+    os << "\n";
+  }
+  for (auto& g : groups_) {
+    if (g.pattern == "reshape_alias") continue;
+    os << "begin_group\n" << PrintGroupDesc(g.desc) << "end_group\n";
+  }
+  for (auto& a : aliases_) os << "alias " << a.first << " " << a.second << "\n";
+  return os.str();
+}
+
+std::unique_ptr<Computation> Computation::Load(const std::string& text, int device, std::string* err) {
+  auto fail = [&](const std::string& m) {
+    if (err) *err = "load: " + m;
+    return nullptr;
+  };
+  std::unique_ptr<Computation> c(new Computation());
+  c->device_ = device;
   if (device >= 0) {
-    std::set<std::string> alias_outputs;
-    for (auto& a : c->aliases_) alias_outputs.insert(a.first);
-    // cinn/hlir/framework/memory.cc:43-52: device memory from cudaMalloc, owned by the scope.
-    for (auto& kv : c->scope_) {
-      if (alias_outputs.count(kv.first)) continue;
-      void* p       = nullptr;
-      cudaError_t e = cudaMalloc(&p, std::max<size_t>(kv.second->bytes, 16));
-      if (e != cudaSuccess) {
-        if (err) *err = "cudaMalloc of tensor " + kv.first + ": " + cudaGetErrorString(e);
-        return nullptr;
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return fail(std::string("cudaSetDevice: ") + cudaGetErrorString(e));
+  }
+  std::istringstream is(text);
+  std::string line;
+  if (!std::getline(is, line) || line != "cinn_b200_program 1") return fail("not a program of this library (bad first line)");
+  while (std::getline(is, line)) {
+    if (line.empty()) continue;
+    std::istringstream ls(line);
+    std::string word;
+    ls >> word;
+    if (word == "tensor") {
+      Variable v;
+      std::string dt, shape;
+      ls >> v.id >> dt >> shape;
+      v.dtype = DTypeFromName(dt);
+      if (v.id.empty() || v.dtype == DType::kUnknown) return fail("bad tensor line: " + line);
+      v.shape = ParseIntList(shape);
+      c->AddScopeTensor(v);
+    } else if (word == "alias") {
+      std::string a, b2;
+      ls >> a >> b2;
+      if (!c->scope_.count(a) || !c->scope_.count(b2)) return fail("alias of an unknown tensor: " + line);
+      c->aliases_.push_back({a, b2});
+    } else if (word == "begin_group") {
+      std::string body;
+      bool closed = false;
+      while (std::getline(is, line)) {
+        if (line == "end_group") {
+          closed = true;
+          break;
+        }
+        body += line + "\n";
       }
-      kv.second->buffer.memory = static_cast<uint8_t*>(p);
-      kv.second->owned         = true;
+      if (!closed) return fail("group without end_group");
+      FusedGroupInfo g;
+      std::string e;
+      if (!ParseGroupDesc(body, &g.desc, &e)) return fail(e);
+      for (auto& t : g.desc.inputs)
+        if (!c->scope_.count(t.name)) return fail("group " + g.desc.name + " reads the unknown tensor " + t.name);
+      for (auto& t : g.desc.outputs)
+        if (!c->scope_.count(t.name)) return fail("group " + g.desc.name + " writes the unknown tensor " + t.name);
+      // A name of its own: the computation that exported the program may still be alive in this process, and the
+      // entry-point registry is keyed by name.
+      g.desc.name += "_ld" + std::to_string(g_computation_uid.fetch_add(1));
+      lower_func_ptr_g fn = nullptr;
+      if (cinn_b200_compile_group(PrintGroupDesc(g.desc).c_str(), &fn) != CINN_B200_OK) return fail(cinn_b200_last_error());
+      char pattern[128] = {0};
+      long long bytes = 0, elements = 0, scratch = 0;
+      int launches = 0;
+      cinn_b200_group_info(g.desc.name.c_str(), pattern, sizeof(pattern), &bytes, &elements, &launches, &scratch);
+      g.pattern = pattern;
+      for (int k = 0; k < launches; ++k) {
+        char kn[128] = {0};
+        if (cinn_b200_group_kernel(g.desc.name.c_str(), k, kn, sizeof(kn)) == CINN_B200_OK) g.kernels.push_back(kn);
+      }
+      Instr ins;
+      ins.fn      = fn;
+      ins.fn_name = g.desc.name;
+      for (auto& t : g.desc.inputs) ins.args.push_back(t.name);
+      for (auto& t : g.desc.outputs) ins.args.push_back(t.name);
+      c->instrs_.push_back(std::move(ins));
+      c->groups_.push_back(std::move(g));
+    } else {
+      return fail("unknown line: " + line);
     }
   }
+  if (device >= 0 && !c->AllocateScope(err)) return nullptr;
   return c;
 }
 

@@ -95,6 +95,13 @@ class Computation {
   // device.  device < 0 plans without touching a GPU.
   static std::unique_ptr<Computation> BuildAndCompile(const NetBuilder& b, const std::vector<int>& fetch,
                                                       int device, std::string* err);
+  // The compiled program as text: its tensors, its groups (descriptions, in execution order) and its aliases.  What
+  // the reference's Program::Export writes into a "CINN" file for its tiny runtime
+  // (cinn/hlir/framework/graph_compiler.cc:89-210, cinn/runtime/tiny_runtime.cc:40-136), re-targeted to the prebuilt
+  // kernel library: instruction -> group description -> prebuilt launcher, no builder, no fusion pass, no JIT.
+  std::string Export() const;
+  // Rebuilds a computation from Export()'s text: every group is matched to its prebuilt kernels again.
+  static std::unique_ptr<Computation> Load(const std::string& text, int device, std::string* err);
   ~Computation();
   int Execute(void* stream, std::string* err);                       // Program::Execute
   int SetTensorData(const std::string& id, const void* host, size_t bytes, std::string* err);
@@ -107,6 +114,8 @@ class Computation {
 
  private:
   Computation() = default;
+  bool AllocateScope(std::string* err);
+  void AddScopeTensor(const Variable& var);
   struct Instr {
     lower_func_ptr_g fn = nullptr;
     std::string fn_name;

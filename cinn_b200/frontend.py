@@ -375,6 +375,38 @@ class Computation:
             raise _lib.CinnB200Error(-2, L.cinn_b200_last_error().decode())
         return Computation(ctypes.c_void_p(h), builder)
 
+    def export(self, path=None):
+        """The compiled program as text (tensors, group descriptions in execution order, aliases): the ahead-of-time
+        format that `Computation.load` runs without a builder or a fusion pass (what Program::Export and the tiny
+        runtime are in the reference).  Written to `path` when given; returned either way."""
+        L = _lib.lib()
+        L.cinn_b200_computation_export.restype = ctypes.c_longlong
+        L.cinn_b200_computation_export.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+        need = L.cinn_b200_computation_export(self._h, None, 0)
+        if need < 0:
+            raise _lib.CinnB200Error(int(need), L.cinn_b200_last_error().decode())
+        buf = ctypes.create_string_buffer(int(need))
+        L.cinn_b200_computation_export(self._h, buf, len(buf))
+        text = buf.value.decode()
+        if path is not None:
+            with open(path, "w") as f:
+                f.write(text)
+        return text
+
+    @staticmethod
+    def load(program, target=None, plan_only=False):
+        """A computation from an exported program (its text, or the path of a file holding it)."""
+        import os
+        text = open(program).read() if os.path.exists(program) else program
+        device = -1 if plan_only else (target.device if isinstance(target, Target) else 0)
+        L = _lib.lib()
+        L.cinn_b200_program_load.restype = ctypes.c_void_p
+        L.cinn_b200_program_load.argtypes = [ctypes.c_char_p, ctypes.c_int]
+        h = L.cinn_b200_program_load(text.encode(), device)
+        if not h:
+            raise _lib.CinnB200Error(-2, L.cinn_b200_last_error().decode())
+        return Computation(ctypes.c_void_p(h), None)
+
     def get_all_tensor_names(self):
         L = _lib.lib()
         n = L.cinn_b200_computation_num_tensors(self._h)

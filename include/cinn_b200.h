@@ -152,6 +152,15 @@ typedef struct cinn_b200_computation cinn_b200_computation;
 cinn_b200_computation* cinn_b200_computation_build_and_compile(cinn_b200_builder* builder, int device,
                                                                const char* const* fetch_ids, int num_fetch);
 void cinn_b200_computation_destroy(cinn_b200_computation* computation);
+/*
+ * Ahead-of-time program: replaces Program::Export and the tiny runtime's loader
+ * (cinn/hlir/framework/graph_compiler.cc:89-210, cinn/runtime/tiny_runtime.cc:40-136).  export writes the compiled
+ * program as text (tensors, group descriptions in execution order, aliases) into `out` (truncated to out_len) and
+ * returns the size needed including the terminator; program_load rebuilds a computation from that text with no
+ * builder and no fusion pass (device < 0: plan only), NULL + last_error on failure.
+ */
+long long cinn_b200_computation_export(cinn_b200_computation* computation, char* out, size_t out_len);
+cinn_b200_computation* cinn_b200_program_load(const char* text, int device);
 int cinn_b200_computation_execute(cinn_b200_computation* computation, void* stream);
 int cinn_b200_computation_set_tensor_data(cinn_b200_computation* computation, const char* id, const void* host,
                                           size_t bytes);

@@ -271,3 +271,23 @@ def test_batch_norm_train_plans_one_statistics_pass_and_one_normalisation_pass()
             assert all(l.split()[3] == "64" for l in desc.splitlines() if l.startswith(("input", "output"))), desc
     stats = [d for d, p in c.groups() if p.startswith("channel_stats")][0]
     assert len([l for l in stats.splitlines() if l.startswith("output")]) == 2
+
+
+def test_exported_program_loads_without_builder_and_plans_the_same_kernels(tmp_path):
+    b = NetBuilder("exp")
+    x = b.create_input(common.Float(32), (8, 16, 1024), "X")
+    bias = b.create_input(common.Float(32), (1024,), "bias")
+    y = b.sigmoid(b.multiply(b.add(x, bias), bias))
+    z = b.reduce_sum(y, [2])
+    b.sqrt(b.abs(b.reshape(z, [128])))
+    c = plan(b)
+    text = c.export(str(tmp_path / "prog.txt"))
+    assert text.startswith("cinn_b200_program 1\n") and "begin_group" in text and "alias " in text
+    c2 = Computation.load(str(tmp_path / "prog.txt"), plan_only=True)
+    kernels = lambda comp: [p.split()[1:] for _, p in comp.groups() if not p.startswith("reshape_alias")]  # noqa: E731
+    assert kernels(c2) == kernels(c)
+    assert sorted(c2.get_all_tensor_names()) == sorted(c.get_all_tensor_names())
+    with pytest.raises(Exception):
+        Computation.load("not a program", plan_only=True)
+    with pytest.raises(Exception):
+        Computation.load(text.replace("op sigmoid", "op conv2d"), plan_only=True)

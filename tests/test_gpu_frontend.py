@@ -644,3 +644,27 @@ def test_chain_that_starts_from_a_broadcast_operand(oracle):
     y = b.negative(b.broadcast_to(i, [6, 10], [0]))
     comp, out = run_program(b, {"I": I}, [y])
     assert np.array_equal(out[str(y)], -np.broadcast_to(I.reshape(6, 1), (6, 10)))
+
+
+def test_exported_program_runs_the_same_bits(oracle, tmp_path):
+    """Export -> load (no builder, no fusion pass) -> execute: same results as the computation it came from."""
+    rng = np.random.default_rng(95)
+    b = NetBuilder("exp")
+    x = b.create_input(common.Float(32), (4, 8, 6, 10), "x")
+    ps = [b.create_input(common.Float(32), (8,), nm) for nm in ("scale", "bias", "mm", "mv")]
+    outs = b.batchnorm(x, *ps, is_test=False)
+    t = b.transpose(b.relu(outs[0]), [0, 2, 3, 1])
+    final = b.reshape(b.softmax(b.reshape(t, [4 * 6 * 10, 8]), mode="safe"), [4, 6, 10, 8])
+    feeds = {"x": rng.standard_normal((4, 8, 6, 10)).astype(np.float32), "scale": np.ones(8, np.float32),
+             "bias": np.zeros(8, np.float32), "mm": np.zeros(8, np.float32), "mv": np.ones(8, np.float32)}
+    fetch = [final, outs[3], outs[4]]
+    comp, out = run_program(b, feeds, fetch)
+    path = str(tmp_path / "program.txt")
+    comp.export(path)
+    loaded = Computation.load(path, TARGET)
+    for k, v in feeds.items():
+        loaded.get_tensor(k).from_numpy(v, TARGET)
+    loaded.execute()
+    for f in fetch:
+        assert np.array_equal(loaded.get_tensor(str(f)).numpy(TARGET), out[str(f)]), str(f)
+    assert np.allclose(out[str(final)].sum(axis=-1), 1.0, atol=1e-5)
