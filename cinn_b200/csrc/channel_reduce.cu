@@ -18,14 +18,19 @@
 namespace cinn_b200 {
 namespace {
 
-template <class OpA, class OpB, bool DUAL>
+// GRAD: the statistics pass of the decomposed batch_norm_grad (cinn/frontend/decomposer/batch_norm.cc:62-72): x is
+// y_grad, x2 the forward input, `mean` the saved per-channel mean; the two accumulations are
+// reduce_sum(y_grad) and reduce_sum(y_grad * (x2 - mean)), difference and product rounded, no fma.
+template <class OpA, class OpB, bool DUAL, bool GRAD = false>
 __global__ void __launch_bounds__(256)
-    k_mid_keep_reduce(const float* __restrict__ x, float* __restrict__ pa, float* __restrict__ pb,
-                      unsigned int* __restrict__ tickets, float* __restrict__ ya, float* __restrict__ yb, long long A,
-                      long long B, long long I, long long chunks, long long splits, long long vec_ok) {
+    k_mid_keep_reduce(const float* __restrict__ x, const float* __restrict__ x2, const float* __restrict__ mean,
+                      float* __restrict__ pa, float* __restrict__ pb, unsigned int* __restrict__ tickets,
+                      float* __restrict__ ya, float* __restrict__ yb, long long A, long long B, long long I,
+                      long long chunks, long long splits, long long vec_ok) {
   __shared__ float scratch[32];
   __shared__ unsigned int ticket;
   const long long b = blockIdx.x % B, s = blockIdx.x / B;
+  const float mu    = GRAD ? mean[b] : 0.0f;
   const long long items    = A * chunks;
   const long long my_items = s < items ? (items - s + splits - 1) / splits : 0;
   float a0 = OpA::identity(), a1 = OpB::identity();
@@ -35,11 +40,12 @@ __global__ void __launch_bounds__(256)
     const long long per   = (nvec + chunks - 1) / chunks;
     const long long total = my_items * per;
     const uint4* px       = reinterpret_cast<const uint4*>(x);
+    const uint4* px2      = reinterpret_cast<const uint4*>(x2);
     // (k, v) = (item, vector inside the item) of flat index id, advanced incrementally: no division per load.
     long long k = threadIdx.x / per, v = threadIdx.x - k * per;
     const long long step_k = T / per, step_v = T - step_k * per;  // one stride of T vectors
     for (long long idx = threadIdx.x; idx < total; idx += 4 * T) {
-      uint4 r[4];
+      uint4 r[4], r2[4];
       bool ok[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -54,6 +60,7 @@ __global__ void __launch_bounds__(256)
           const long long vv = chunk * per + v;
           if (vv < nvec) {
             r[j]  = __ldcs(px + (a * B + b) * nvec + vv);
+            if (GRAD) r2[j] = __ldcs(px2 + (a * B + b) * nvec + vv);
             ok[j] = true;
           }
         }
@@ -67,12 +74,14 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (ok[j]) {
-          float f[4];
+          float f[4], f2[4];
           unpack4(r[j], f);
+          if (GRAD) unpack4(r2[j], f2);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             a0 = OpA::accum(a0, f[i]);
-            if (DUAL) a1 = OpB::accum(a1, f[i]);
+            if (GRAD) a1 = a1 + f[i] * (f2[i] - mu);
+            else if (DUAL) a1 = OpB::accum(a1, f[i]);
           }
         }
       }
@@ -86,7 +95,8 @@ __global__ void __launch_bounds__(256)
       for (long long i = begin + threadIdx.x; i < end; i += T) {
         const float f = px[i];
         a0            = OpA::accum(a0, f);
-        if (DUAL) a1 = OpB::accum(a1, f);
+        if (GRAD) a1 = a1 + f * (x2[(a * B + b) * I + i] - mu);
+        else if (DUAL) a1 = OpB::accum(a1, f);
       }
     }
   }
@@ -119,7 +129,7 @@ __global__ void __launch_bounds__(256)
 }  // namespace
 
 #define REG_MID(OPNAME, OP) \
-  CINN_B200_REGISTER_KERNEL("mid_keep_reduce_" OPNAME "_f32", 12, 256, k_mid_keep_reduce<OP, OP, false>)
+  CINN_B200_REGISTER_KERNEL("mid_keep_reduce_" OPNAME "_f32", 14, 256, k_mid_keep_reduce<OP, OP, false>)
 REG_MID("sum", SumOp);
 REG_MID("prod", ProdOp);
 REG_MID("max", MaxOp);
@@ -127,6 +137,7 @@ REG_MID("min", MinOp);
 REG_MID("sumsq", SumSquareOp);
 REG_MID("sumabs", SumAbsOp);
 REG_MID("maxabs", MaxAbsOp);
-CINN_B200_REGISTER_KERNEL("mid_keep_reduce_sum_sumsq_f32", 12, 256, k_mid_keep_reduce<SumOp, SumSquareOp, true>);
+CINN_B200_REGISTER_KERNEL("mid_keep_reduce_sum_sumsq_f32", 14, 256, k_mid_keep_reduce<SumOp, SumSquareOp, true>);
+CINN_B200_REGISTER_KERNEL("bn_grad_stats_f32", 14, 256, k_mid_keep_reduce<SumOp, SumOp, true, true>);
 
 }  // namespace cinn_b200

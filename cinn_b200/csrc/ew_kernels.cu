@@ -198,6 +198,69 @@ __global__ void __launch_bounds__(256)
     }
   }
 }
+// ------------------------------------------------------------------------------------------------
+// x_grad of the decomposed batch_norm_grad (cinn/frontend/decomposer/batch_norm.cc:212-238), NCHW fp32:
+//     x_grad = tmp0 * ((dy * nhw - bias_grad) - ((x - mean) * S) / (var + eps))
+// with per-channel tmp0 = (scale * rsqrt(var + eps)) / nhw, bias_grad = sum(dy), S = sum(dy * (x - mean)).
+// Two streamed inputs, one output; the per-channel values are formed once per CTA, in the reference's operation
+// order (rsqrt = 1 / sqrt; subtractions and the division are not contracted).  t0_form / vae_form = 1: tmp0 / var+eps
+// are computed here from scale and var; 0: they are given as per-channel inputs.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+    k_bn_grad_apply(const float* __restrict__ x, const float* __restrict__ dy, const float* __restrict__ mean,
+                    const float* __restrict__ sum_s, const float* __restrict__ bias_grad, const float* __restrict__ vae_in,
+                    const float* __restrict__ t0_in, const float* __restrict__ var0, float* __restrict__ y,
+                    long long planes, long long channels, long long hw, long long chunks, long long vec_ok,
+                    long long t0_form, long long vae_form, double count_d, double eps_d) {
+  const long long n_ctas = planes * chunks;
+  const float count = (float)count_d, eps = (float)eps_d;
+  for (long long cta = blockIdx.x; cta < n_ctas; cta += gridDim.x) {
+    const long long plane = cta / chunks;
+    const int chunk       = (int)(cta - plane * chunks);
+    const int c           = (int)(plane % channels);
+    const float m = mean[c], S = sum_s[c], db = bias_grad[c];
+    const float vae = vae_form ? vae_in[c] + eps : vae_in[c];
+    const float t0  = t0_form ? (t0_in[c] * (1.0f / sqrtf(var0[c] + eps))) / count : t0_in[c];
+    const float* xp  = x + plane * hw;
+    const float* dp  = dy + plane * hw;
+    float* yp        = y + plane * hw;
+    if (vec_ok) {
+      const int nvec  = (int)(hw / 4);
+      const int per   = (int)((nvec + chunks - 1) / chunks);
+      const int begin = chunk * per;
+      const int end   = min(begin + per, nvec);
+      const int B     = blockDim.x;
+      for (int v = begin + threadIdx.x; v < end; v += 2 * B) {
+        uint4 rx[2], rd[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          if (v + j * B < end) {
+            rx[j] = ld_stream16(xp + (long long)(v + j * B) * 4);
+            rd[j] = ld_stream16(dp + (long long)(v + j * B) * 4);
+          }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          if (v + j * B < end) {
+            float fx[4], fd[4];
+            unpack4(rx[j], fx);
+            unpack4(rd[j], fd);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) fx[i] = t0 * (((fd[i] * count) - db) - (((fx[i] - m) * S) / vae));
+            st_stream16(yp + (long long)(v + j * B) * 4, pack4(fx));
+          }
+        }
+      }
+    } else {
+      const long long per   = (hw + chunks - 1) / chunks;
+      const long long begin = chunk * per;
+      const long long end   = min(begin + per, hw);
+      for (long long i = begin + threadIdx.x; i < end; i += blockDim.x)
+        yp[i] = t0 * (((dp[i] * count) - db) - (((xp[i] - m) * S) / vae));
+    }
+  }
+}
+CINN_B200_REGISTER_KERNEL("ew_bn_grad_apply_nchw_f32", 18, 256, k_bn_grad_apply);
+
 CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f32", 12, 256, k_bn_nchw<float, true>);
 CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true>);
 CINN_B200_REGISTER_KERNEL("ew_bn_nchw_f32", 12, 256, k_bn_nchw<float, false>);

@@ -651,11 +651,17 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
     for (size_t i = 0; i < sets.size(); ++i) {
       if (sets[i].empty() || !is_reduce_group(sets[i])) continue;
       const FusedGroupInfo gi = st.Describe(sets[i]);
-      if (gi.input_vars.size() != 1) continue;
       for (size_t j = i + 1; j < sets.size(); ++j) {
         if (sets[j].empty() || !is_reduce_group(sets[j])) continue;
         const FusedGroupInfo gj = st.Describe(sets[j]);
-        if (gj.input_vars != gi.input_vars) continue;
+        bool shared = false, dependent = false;
+        for (int v : gj.input_vars) {
+          shared = shared || std::find(gi.input_vars.begin(), gi.input_vars.end(), v) != gi.input_vars.end();
+          dependent = dependent || std::find(gi.output_vars.begin(), gi.output_vars.end(), v) != gi.output_vars.end();
+        }
+        for (int v : gi.input_vars)
+          dependent = dependent || std::find(gj.output_vars.begin(), gj.output_vars.end(), v) != gj.output_vars.end();
+        if (!shared || dependent) continue;
         std::set<int> merged = sets[i];
         merged.insert(sets[j].begin(), sets[j].end());
         if (!st.Compiles(merged, nullptr, nullptr)) continue;

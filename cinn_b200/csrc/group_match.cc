@@ -358,6 +358,65 @@ struct Matcher {
     return p;
   }
 
+  // x_grad of the decomposed batch_norm_grad (cinn/frontend/decomposer/batch_norm.cc:212-238):
+  //   mul(tmp0, sub(sub(mul(dy, nhw), bc(bias_grad)), div(mul(sub(x, bc(mean)), bc(S)), bc(var + eps))))
+  // tmp0 is broadcast(%t) or broadcast((scale * rsqrt(var + eps)) / nhw); var + eps is broadcast(%v) or computed.
+  std::unique_ptr<CompiledGroup> MatchBnGradApply(const std::string& expr) {
+    static const std::string t0 =
+        R"(broadcast_to\((?:%(\d)|divide\(elementwise_mul\(%(\d),rsqrt\(elementwise_add\(%(\d),fill_constant\(\)\)\)\),fill_constant\(\)\))\))";
+    static const std::string vae = R"(broadcast_to\((?:%(\d)|elementwise_add\(%(\d),fill_constant\(\)\))\))";
+    static const std::regex form("^elementwise_mul\\(" + t0 +
+                                 R"(,subtract\(subtract\(elementwise_mul\(%(\d),fill_constant\(\)\),broadcast_to\(%(\d)\)\),)"
+                                 R"(divide\(elementwise_mul\(subtract\(%(\d),broadcast_to\(%(\d)\)\),broadcast_to\(%(\d)\)\),)" +
+                                 vae + R"(\)\)\)$)");
+    std::smatch m;
+    if (!std::regex_match(expr, m, form)) return nullptr;
+    auto idx = [&](int k) { return m[k].matched ? atoi(m[k].str().c_str()) : -1; };
+    const int t0_in = idx(1), scale = idx(2), var0 = idx(3), dy = idx(4), db = idx(5), x = idx(6), mean = idx(7),
+              S = idx(8), vae_in = idx(9), var1 = idx(10);
+    const bool t0_form = t0_in < 0, vae_form = vae_in < 0;
+    const auto& xt = g.inputs[x];
+    const auto& o  = g.outputs[0];
+    if (xt.shape.size() != 4 || g.inputs[dy].shape != xt.shape || o.shape != xt.shape || xt.dtype != DType::kFloat32 ||
+        g.inputs[dy].dtype != DType::kFloat32 || o.dtype != DType::kFloat32 || x == dy)
+      return nullptr;
+    const int64_t N = xt.shape[0], C = xt.shape[1], HW = xt.shape[2] * xt.shape[3];
+    for (int i : {t0_form ? scale : t0_in, t0_form ? var0 : mean, db, mean, S, vae_form ? var1 : vae_in})
+      if (i < 0 || i >= (int)g.inputs.size() || g.inputs[i].dtype != DType::kFloat32 || g.inputs[i].numel() != C) return nullptr;
+    double count = 0.0, eps = 0.0;
+    for (auto& op : g.ops) {
+      if (op.type == "broadcast_to" && AttrList(op, "broadcast_axes") != std::vector<int64_t>{1}) {
+        Fail("batch_norm_grad operands must be broadcast along axis 1 (NCHW)");
+        return nullptr;
+      }
+      const OpDesc* fc = nullptr;
+      for (auto& in : op.inputs)
+        if (const OpDesc* q = ProducerOfType(in, "fill_constant")) fc = q;
+      if (!fc) continue;
+      const double v = (float)AttrF(*fc, "value", 0.0);
+      if (op.type == "elementwise_add") eps = v;
+      else if (op.type == "elementwise_mul" || op.type == "divide") count = v;
+    }
+    if (count != (double)(N * HW)) {
+      Fail("batch_norm_grad: the element count constant does not match the tensor");
+      return nullptr;
+    }
+    auto p               = NewPlan("ew_bn_grad_apply_nchw");
+    const int64_t planes = N * C;
+    const int64_t units  = HW % 4 == 0 ? HW / 4 : HW;
+    int64_t chunks       = std::max<int64_t>(1, (units + 256) / 512);
+    while (planes * chunks < (int64_t)dev.sm_count * 4 && units / (chunks * 2) >= 256) chunks *= 2;
+    LaunchStep s;
+    if (!Kernel(&s, "ew_bn_grad_apply_nchw_f32")) return nullptr;
+    s.block[0] = 256;
+    s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(planes * chunks, (int64_t)dev.sm_count * 64));
+    s.args     = {In(x), In(dy), In(mean), In(S), In(db), In(vae_form ? var1 : vae_in), In(t0_form ? scale : t0_in),
+                  In(t0_form ? var0 : mean), Out(0), I(planes), I(C), I(HW), I(chunks), Aligned(HW % 4 == 0, {x, dy}, {0}),
+                  I(t0_form ? 1 : 0), I(vae_form ? 1 : 0), F(count), F(eps)};
+    p->steps.push_back(s);
+    return p;
+  }
+
   // ---- transpose / slice / concat (cinn/hlir/op/transform.cc): data movement, typed by element size ----------
   static std::vector<int64_t> StridesOf(const std::vector<int64_t>& shape) {
     std::vector<int64_t> st(shape.size(), 1);
@@ -626,7 +685,7 @@ struct Matcher {
   // First pass of a middle-axis-keeping reduction into scratch partials [splits][B] (per accumulation), then a
   // column reduction over the splits.  opname2 != nullptr: the dual kernel (sum and sum of squares).
   bool PlanMidKeep(CompiledGroup* p, const char* opname, bool dual, int64_t A, int64_t B, int64_t I, ArgSpec dst,
-                   ArgSpec dst2) {
+                   ArgSpec dst2, int x_in = 0, int x2_in = -1, int mean_in = -1) {
     const int sms        = dev.sm_count;
     const bool vec       = I % 4 == 0;
     const int64_t units  = vec ? I / 4 : I;
@@ -642,12 +701,17 @@ struct Matcher {
     const int64_t off_tickets = p->scratch_bytes;  // one counter per kept element; scratch starts zeroed
     p->scratch_bytes += (size_t)RoundUp(B * 4, 256);
     LaunchStep s;
-    if (!Kernel(&s, dual ? std::string("mid_keep_reduce_sum_sumsq_f32") : std::string("mid_keep_reduce_") + opname + "_f32"))
+    const bool grad = x2_in >= 0;
+    if (!Kernel(&s, grad ? std::string("bn_grad_stats_f32")
+                         : (dual ? std::string("mid_keep_reduce_sum_sumsq_f32") : std::string("mid_keep_reduce_") + opname + "_f32")))
       return false;
     s.block[0] = 256;
     s.grid[0]  = (unsigned)(B * splits);
-    s.args     = {In(0), Scratch(off1), Scratch(dual ? off2 : off1), Scratch(off_tickets), dst, dual ? dst2 : dst,
-                  this->I(A), this->I(B), this->I(I), this->I(chunks), this->I(splits), Aligned(vec, {0}, {})};
+    std::vector<int> aligned_in = {x_in};
+    if (grad) aligned_in.push_back(x2_in);
+    s.args = {In(x_in), In(grad ? x2_in : x_in), In(grad ? mean_in : x_in), Scratch(off1), Scratch(dual ? off2 : off1),
+              Scratch(off_tickets), dst, dual ? dst2 : dst, this->I(A), this->I(B), this->I(I), this->I(chunks),
+              this->I(splits), Aligned(vec, aligned_in, {})};
     p->steps.push_back(s);
     return true;
   }
@@ -797,6 +861,57 @@ struct Matcher {
 
   // The two-output group {reduce_sum(x), reduce_sum(x * x)} over the same leading + trailing axes: the statistics
   // pass of batch_norm_train (cinn/frontend/decomposer/batch_norm.cc:60-92), one read of x.
+  // The statistics of the decomposed batch_norm_grad (cinn/frontend/decomposer/batch_norm.cc:62-72):
+  // {reduce_sum(dy), reduce_sum(dy * (x - broadcast(mean)))} over N, H, W, or the second one alone.
+  std::unique_ptr<CompiledGroup> MatchBnGradStats(const std::string& expr) {
+    static const std::regex both(R"(^reduce_sum\(%(\d)\);reduce_sum\(elementwise_mul\(%(\d),subtract\(%(\d),broadcast_to\(%(\d)\)\)\)\)$)");
+    static const std::regex one(R"(^reduce_sum\(elementwise_mul\(%(\d),subtract\(%(\d),broadcast_to\(%(\d)\)\)\)\)$)");
+    std::smatch m;
+    int idy, ix, im;
+    bool dual;
+    if (std::regex_match(expr, m, both) && g.outputs.size() == 2) {
+      if (m[1].str() != m[2].str()) return nullptr;
+      idy = atoi(m[2].str().c_str()), ix = atoi(m[3].str().c_str()), im = atoi(m[4].str().c_str());
+      dual = true;
+    } else if (std::regex_match(expr, m, one) && g.outputs.size() == 1) {
+      idy = atoi(m[1].str().c_str()), ix = atoi(m[2].str().c_str()), im = atoi(m[3].str().c_str());
+      dual = false;
+    } else {
+      return nullptr;
+    }
+    if (g.inputs.size() != 3 || idy == ix || idy == im || ix == im) return nullptr;
+    const auto &dy = g.inputs[idy], &x = g.inputs[ix], &mean = g.inputs[im];
+    if (dy.dtype != DType::kFloat32 || x.dtype != DType::kFloat32 || mean.dtype != DType::kFloat32 || dy.shape != x.shape) {
+      Fail("batch_norm_grad statistics are prebuilt for float32 tensors of one shape");
+      return nullptr;
+    }
+    int64_t A = 0, B = 0, I = 0;
+    for (auto& op : g.ops) {
+      if (op.type == "reduce_sum") {
+        int64_t a2, b2, i2;
+        if (!MidKeepView(x.shape, AttrList(op, "dim"), &a2, &b2, &i2) || (A && (a2 != A || b2 != B || i2 != I))) {
+          Fail("the reductions must keep the same middle axes");
+          return nullptr;
+        }
+        A = a2, B = b2, I = i2;
+      }
+    }
+    if (!A || mean.numel() != B) return nullptr;
+    for (auto& o : g.outputs)
+      if (o.numel() != B || o.dtype != DType::kFloat32) return nullptr;
+    auto p      = NewPlan("bn_grad_stats");
+    p->elements = x.numel();
+    if (dual) {
+      if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Out(0), Out(1), idy, ix, im)) return nullptr;
+    } else {
+      // the kernel always keeps both sums; the first one lands in scratch
+      const int64_t off = p->scratch_bytes;
+      p->scratch_bytes += (size_t)RoundUp(B * 4, 256);
+      if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Scratch(off), Out(0), idy, ix, im)) return nullptr;
+    }
+    return p;
+  }
+
   std::unique_ptr<CompiledGroup> MatchChannelStats(const std::string& expr) {
     static const std::set<std::string> forms = {
         "reduce_sum(%0);reduce_sum(elementwise_mul(%0,identity(%0)))", "reduce_sum(%0);reduce_sum(elementwise_mul(%0,%0))",
@@ -1191,13 +1306,17 @@ struct Matcher {
     if (g.outputs.size() != 1) {
       // The only multi-output family: the fused channel statistics.
       if (auto p = MatchChannelStats(expr)) return p;
+      if (err && !err->empty()) return nullptr;
+      if (auto p = MatchBnGradStats(expr)) return p;
       if (err && err->empty())
         Fail("groups with " + std::to_string(g.outputs.size()) + " outputs have no prebuilt kernel (" + expr + ")");
       return nullptr;
     }
     typedef std::unique_ptr<CompiledGroup> (Matcher::*Fn)(const std::string&);
     const Fn fns[] = {&Matcher::MatchAddRelu, &Matcher::MatchBiasScaleTanhCast, &Matcher::MatchBatchNorm,
-                      &Matcher::MatchBnTrainApply, &Matcher::MatchTransform,    &Matcher::MatchReduce,
+                      &Matcher::MatchBnTrainApply, &Matcher::MatchBnGradApply,  &Matcher::MatchTransform,
+                      &Matcher::MatchBnGradStats,
+                      &Matcher::MatchReduce,
                       &Matcher::MatchSoftmax,      &Matcher::MatchLayerNorm};
     for (Fn f : fns) {
       auto p = (this->*f)(expr);

@@ -272,6 +272,33 @@ class NetBuilder:
                             self.multiply(saved, self.fill_constant([c], 1.0 - float(momentum), dtype=dt)))
         return [y, mean, variance, update(moving_mean, mean), update(moving_variance, variance)]
 
+    def batch_norm_grad(self, y_grad, x, scale, save_mean, save_variance, epsilon=1e-5, data_layout="NCHW"):
+        """Gradient of training-mode batch norm, composed as the reference's decomposer does
+        (cinn/frontend/decomposer/batch_norm.cc:179-243).  Returns [x_grad, scale_grad, bias_grad]."""
+        if data_layout != "NCHW":
+            raise NotImplementedError("batch_norm_grad: only NCHW has prebuilt kernels")
+        dt, shape = x._info()
+        n, c, h, w = shape
+        count = float(n * h * w)
+        red, full = [0, 2, 3], list(shape)
+
+        def std_inv_1d():
+            return self.rsqrt(self.add(save_variance, self.fill_constant([c], float(epsilon), dtype=dt)))
+        x_mean_diff = self.subtract(x, self.broadcast_to(save_mean, full, [1]))
+        bias_grad = self.reduce_sum(y_grad, red)
+        sum_dy_xmu = self.reduce_sum(self.multiply(y_grad, x_mean_diff), red)
+        scale_grad = self.multiply(sum_dy_xmu, std_inv_1d())
+        scaled_std_inv = self.multiply(scale, std_inv_1d())
+        tmp0 = self.broadcast_to(self.divide(scaled_std_inv, self.fill_constant([c], count, dtype=dt)), full, [1])
+        tmp1 = self.multiply(y_grad, self.fill_constant(full, count, dtype=dt))
+        tmp2 = self.broadcast_to(bias_grad, full, [1])
+        x_mean_diff2 = self.subtract(x, self.broadcast_to(save_mean, full, [1]))
+        tmp3_0 = self.multiply(x_mean_diff2, self.broadcast_to(sum_dy_xmu, full, [1]))
+        var_eps_4d = self.broadcast_to(self.add(save_variance, self.fill_constant([c], float(epsilon), dtype=dt)), full, [1])
+        tmp3 = self.divide(tmp3_0, var_eps_4d)
+        x_grad = self.multiply(tmp0, self.subtract(self.subtract(tmp1, tmp2), tmp3))
+        return [x_grad, scale_grad, bias_grad]
+
     def layer_norm(self, x, gamma, beta, epsilon=1e-5):
         """layer_norm over the last axis of a 2-D `x`, composed from primitives the way the reference's Paddle
         op mapper does (cinn/frontend/op_mappers/paddle/layer_norm.cc:84-139) with rsqrt + multiply."""

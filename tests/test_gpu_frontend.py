@@ -668,3 +668,64 @@ def test_exported_program_runs_the_same_bits(oracle, tmp_path):
     for f in fetch:
         assert np.array_equal(loaded.get_tensor(str(f)).numpy(TARGET), out[str(f)]), str(f)
     assert np.allclose(out[str(final)].sum(axis=-1), 1.0, atol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (3, 5, 7, 9), (16, 32, 28, 28)])
+def test_batch_norm_grad_decomposed(oracle, shape):
+    n, c, h, w = shape
+    rng = np.random.default_rng(96)
+    b = NetBuilder("bn_grad")
+    F = common.Float(32)
+    dy, x = b.create_input(F, shape, "dy"), b.create_input(F, shape, "x")
+    scale, mean, var = (b.create_input(F, (c,), nm) for nm in ("scale", "mean", "var"))
+    outs = b.batch_norm_grad(dy, x, scale, mean, var, epsilon=1e-5)
+    X = (rng.standard_normal(shape) * 1.5 + 0.3).astype(np.float32)
+    feeds = {"dy": rng.standard_normal(shape).astype(np.float32), "x": X,
+             "scale": (1 + 0.1 * rng.standard_normal(c)).astype(np.float32),
+             "mean": X.mean(axis=(0, 2, 3)).astype(np.float32), "var": X.var(axis=(0, 2, 3)).astype(np.float32)}
+    comp, out = run_program(b, feeds, outs)
+    pats = [p.split()[0] for _, p in comp.groups()]
+    assert pats.count("bn_grad_stats") == 1 and pats.count("ew_bn_grad_apply_nchw") == 1 and len(pats) == 3, pats
+    ref = oracle_program(comp, feeds)
+    x_grad, scale_grad, bias_grad = (str(o) for o in outs)
+    # float64 evaluation of the same formulas
+    d64 = {k: v.astype(np.float64) for k, v in feeds.items()}
+    m, v, s = (d64[k].reshape(1, c, 1, 1) for k in ("mean", "var", "scale"))
+    cnt = n * h * w
+    db = d64["dy"].sum(axis=(0, 2, 3))
+    S = (d64["dy"] * (d64["x"] - m)).sum(axis=(0, 2, 3))
+    inv = 1 / np.sqrt(v + 1e-5)
+    dx = (s * inv / cnt) * ((d64["dy"] * cnt - db.reshape(1, c, 1, 1)) - (d64["x"] - m) * S.reshape(1, c, 1, 1) / (v + 1e-5))
+    tol_sum = 1e-5 * np.abs(d64["dy"]).sum(axis=(0, 2, 3)) + 1e-6
+    assert (np.abs(out[bias_grad] - db) <= tol_sum).all()
+    assert (np.abs(out[scale_grad] - S * inv.reshape(-1)) <= 3e-5 * (np.abs(d64["dy"] * (d64["x"] - m)).sum(axis=(0, 2, 3)) * inv.reshape(-1)) + 1e-6).all()
+    scale_dx = np.abs(dx).max()
+    assert np.abs(out[x_grad] - dx).max() <= 2e-4 * scale_dx, np.abs(out[x_grad] - dx).max() / scale_dx
+    # and no farther from the oracle than the oracle is from the float64 result (+ the same tolerance)
+    assert np.abs(out[x_grad] - ref[x_grad]).max() <= np.abs(ref[x_grad] - dx).max() + 2e-4 * scale_dx
+
+
+def test_bn_grad_apply_kernel_is_bit_exact_given_the_statistics(oracle):
+    """The x_grad group alone with every per-channel operand as an input: the oracle's bits."""
+    shape, c = (4, 6, 5, 12), 6
+    rng = np.random.default_rng(97)
+    b = NetBuilder("bn_grad_apply")
+    F = common.Float(32)
+    dy, x = b.create_input(F, shape, "dy"), b.create_input(F, shape, "x")
+    t0, db, mean, S, vae = (b.create_input(F, (c,), nm) for nm in ("t0", "db", "mean", "S", "vae"))
+    full, cnt = list(shape), float(4 * 5 * 12)
+    tmp1 = b.multiply(dy, b.fill_constant(full, cnt))
+    tmp3 = b.divide(b.multiply(b.subtract(x, b.broadcast_to(mean, full, [1])), b.broadcast_to(S, full, [1])),
+                    b.broadcast_to(vae, full, [1]))
+    y = b.multiply(b.broadcast_to(t0, full, [1]), b.subtract(b.subtract(tmp1, b.broadcast_to(db, full, [1])), tmp3))
+    feeds = {"dy": rng.standard_normal(shape).astype(np.float32), "x": rng.standard_normal(shape).astype(np.float32),
+             "t0": rng.uniform(0.001, 0.01, c).astype(np.float32), "db": rng.standard_normal(c).astype(np.float32),
+             "mean": (0.1 * rng.standard_normal(c)).astype(np.float32), "S": rng.standard_normal(c).astype(np.float32),
+             "vae": rng.uniform(0.5, 1.5, c).astype(np.float32)}
+    comp, out = run_program(b, feeds, [y])
+    assert [p.split()[0] for _, p in comp.groups()] == ["ew_bn_grad_apply_nchw"], comp.groups()
+    r = lambda k: feeds[k].reshape(1, c, 1, 1)  # noqa: E731
+    f32 = np.float32
+    want = (r("t0") * (((feeds["dy"] * f32(cnt)).astype(f32) - r("db")).astype(f32)
+                        - (((feeds["x"] - r("mean")).astype(f32) * r("S")).astype(f32) / r("vae")).astype(f32)).astype(f32)).astype(f32)
+    assert oracle.max_ulp(out[str(y)], want) == 0
