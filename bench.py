@@ -221,6 +221,9 @@ def side_groups(torch, dev, peak, only=None):
         ("bn_train_stats_256x64x112x112", lambda: W.bn_train_stats((256, 64, 112, 112)), 1,
          "sum and sum of squares per channel in one read of x"),
         ("bn_train_apply_256x64x112x112", lambda: W.bn_train_apply((256, 64, 112, 112)), 1, ""),
+        ("bn_grad_stats_256x64x112x112", lambda: W.bn_grad_stats((256, 64, 112, 112)), 1,
+         "sum(dy) and sum(dy * (x - mean)) per channel in one read of dy and x"),
+        ("bn_grad_apply_256x64x112x112", lambda: W.bn_grad_apply((256, 64, 112, 112)), 1, ""),
         # the generic families: any other elementwise chain / element type (interpreted program, not a dedicated kernel)
         ("generic_chain_abs_add_f32_8192x8192", lambda: W.generic_chain("abs_add_f32"), 1, "generic chain kernel"),
         ("generic_chain_select_f32_8192x8192", lambda: W.generic_chain("select_f32"), 1, "generic chain kernel"),
@@ -270,6 +273,8 @@ PROFILE_GROUPS = {
     "softmax_safe_f32": lambda W: W.softmax_safe((16384, 4096)),
     "bn_train_stats": lambda W: W.bn_train_stats((256, 64, 112, 112)),
     "bn_train_apply": lambda W: W.bn_train_apply((256, 64, 112, 112)),
+    "bn_grad_stats": lambda W: W.bn_grad_stats((256, 64, 112, 112)),
+    "bn_grad_apply": lambda W: W.bn_grad_apply((256, 64, 112, 112)),
     "chain_abs_add_f32": lambda W: W.generic_chain("abs_add_f32"),
     "chain_select_f32": lambda W: W.generic_chain("select_f32"),
     "chain_abs_add_i32": lambda W: W.generic_chain("abs_add_i32"),

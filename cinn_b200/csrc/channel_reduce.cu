@@ -42,13 +42,15 @@ __global__ void __launch_bounds__(256)
     const uint4* px       = reinterpret_cast<const uint4*>(x);
     const uint4* px2      = reinterpret_cast<const uint4*>(x2);
     // (k, v) = (item, vector inside the item) of flat index id, advanced incrementally: no division per load.
+    // four 16-byte vectors in flight per thread and stream (eight were slower: fewer, longer iterations per CTA)
+    constexpr int U = 4;
     long long k = threadIdx.x / per, v = threadIdx.x - k * per;
     const long long step_k = T / per, step_v = T - step_k * per;  // one stride of T vectors
-    for (long long idx = threadIdx.x; idx < total; idx += 4 * T) {
-      uint4 r[4], r2[4];
-      bool ok[4];
+    for (long long idx = threadIdx.x; idx < total; idx += U * T) {
+      uint4 r[U], r2[GRAD ? U : 1];
+      bool ok[U];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < U; ++j) {
         ok[j] = false;
         if (idx + (long long)j * T < total) {
           const long long it = s + k * splits;
@@ -60,7 +62,7 @@ __global__ void __launch_bounds__(256)
           const long long vv = chunk * per + v;
           if (vv < nvec) {
             r[j]  = __ldcs(px + (a * B + b) * nvec + vv);
-            if (GRAD) r2[j] = __ldcs(px2 + (a * B + b) * nvec + vv);
+            if (GRAD) r2[GRAD ? j : 0] = __ldcs(px2 + (a * B + b) * nvec + vv);
             ok[j] = true;
           }
         }
@@ -72,11 +74,11 @@ __global__ void __launch_bounds__(256)
         }
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < U; ++j) {
         if (ok[j]) {
           float f[4], f2[4];
           unpack4(r[j], f);
-          if (GRAD) unpack4(r2[j], f2);
+          if (GRAD) unpack4(r2[GRAD ? j : 0], f2);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             a0 = OpA::accum(a0, f[i]);

@@ -335,3 +335,43 @@ def concat(shapes, axis, dtype="float32", seed=8):
         rng = np.random.default_rng(seed)
         return [_draw(rng, s, dtype) for s in shapes]
     return Workload("concat", desc, gen, _NP[dtype], out_shape)
+
+
+def bn_grad_stats(shape=(256, 64, 112, 112), seed=4):
+    """Statistics pass of the decomposed batch_norm_grad: {sum(dy), sum(dy * (x - mean))} over N, H, W."""
+    s, c = _shape(shape), shape[1]
+    desc = (f"group fn_bn_grad_stats\ninput mean float32 {c}\ninput x float32 {s}\ninput dy float32 {s}\n"
+            f"op broadcast_to m4 = mean ; broadcast_axes=1 out_shape={s}\nop subtract d = x m4 ; axis=-1\n"
+            f"op reduce_sum db = dy ; dim=0,2,3 keep_dim=false\nop elementwise_mul p = dy d ; axis=-1\n"
+            f"op reduce_sum sd = p ; dim=0,2,3 keep_dim=false\noutput db float32 {c}\noutput sd float32 {c}\n")
+
+    def gen():
+        x, mean, var, scale, bias = bn_train_inputs(shape, seed)
+        return [mean, x, np.random.default_rng(seed + 100).standard_normal(shape, dtype=np.float32)]
+    return Workload("bn_grad_stats", desc, gen, np.float32, (c,), more_outputs=[(np.float32, (c,))])
+
+
+def bn_grad_apply(shape=(256, 64, 112, 112), seed=4):
+    """x_grad of the decomposed batch_norm_grad with its per-channel prologue fused in."""
+    s, c = _shape(shape), shape[1]
+    cnt = float(shape[0] * shape[2] * shape[3])
+    bc = f"broadcast_axes=1 out_shape={s}"
+    desc = (f"group fn_bn_grad_apply\ninput scale float32 {c}\ninput var float32 {c}\ninput dy float32 {s}\n"
+            f"input db float32 {c}\ninput x float32 {s}\ninput mean float32 {c}\ninput sd float32 {c}\n"
+            f"op fill_constant e1 = ; shape={c} value=1e-05 dtype=float32\nop elementwise_add ve1 = var e1 ; axis=-1\n"
+            f"op rsqrt r = ve1\nop elementwise_mul sr = scale r ; axis=-1\n"
+            f"op fill_constant n1 = ; shape={c} value={cnt} dtype=float32\nop divide t0 = sr n1 ; axis=-1\n"
+            f"op broadcast_to t04 = t0 ; {bc}\nop fill_constant n4 = ; shape={s} value={cnt} dtype=float32\n"
+            f"op elementwise_mul t1 = dy n4 ; axis=-1\nop broadcast_to t2 = db ; {bc}\n"
+            f"op broadcast_to m4 = mean ; {bc}\nop subtract d = x m4 ; axis=-1\nop broadcast_to s4 = sd ; {bc}\n"
+            f"op elementwise_mul t30 = d s4 ; axis=-1\nop fill_constant e2 = ; shape={c} value=1e-05 dtype=float32\n"
+            f"op elementwise_add ve2 = var e2 ; axis=-1\nop broadcast_to v4 = ve2 ; {bc}\nop divide t3 = t30 v4 ; axis=-1\n"
+            f"op subtract a = t1 t2 ; axis=-1\nop subtract b = a t3 ; axis=-1\nop elementwise_mul y = t04 b ; axis=-1\n"
+            f"output y float32 {s}\n")
+
+    def gen():
+        x, mean, var, scale, bias = bn_train_inputs(shape, seed)
+        rng = np.random.default_rng(seed + 100)
+        dy = rng.standard_normal(shape, dtype=np.float32)
+        return [scale, var, dy, rng.standard_normal(c).astype(np.float32), x, mean, rng.standard_normal(c).astype(np.float32)]
+    return Workload("bn_grad_apply", desc, gen, np.float32, shape)
