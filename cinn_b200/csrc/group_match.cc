@@ -1205,7 +1205,8 @@ struct Matcher {
         Fail("max-subtracted softmax is prebuilt for rows of up to " + std::to_string(4096 * V) + " elements");
         return nullptr;
       }
-      // 4 vectors per thread for fp32, 2 for 16-bit storage (16 values each way), between 128 and 512 threads.
+      // 4 vectors per thread for fp32, 2 for 16-bit storage (measured: 128-thread CTAs with 4 are slower there),
+      // between 128 and 512 threads; as many again of the next row are on their way.
       const int target = half ? 2 : 4;
       int G            = 128;
       while (G < 512 && G * target < nvec) G *= 2;

@@ -12,6 +12,26 @@
 namespace cinn_b200 {
 namespace {
 
+// Reduction over the CTA with ONE barrier: every warp leaves its partial in shared memory, and after the barrier
+// every thread folds the (at most 16) partials itself, in a fixed order.  `slot` alternates between two buffers so
+// that the next reduction may start writing while slow warps still read this one.
+template <class Op>
+__device__ __forceinline__ float cta_fold(float v, float (*buf)[16], int slot) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  v = warp_allreduce<Op>(v);
+  if (lane == 0) buf[slot][warp] = v;
+  __syncthreads();
+  // 4, 8 or 16 warps: whole float4 reads (broadcast), folded pairwise
+  const float4* q = reinterpret_cast<const float4*>(&buf[slot][0]);
+  float4 a        = q[0];
+  float r         = Op::apply(Op::apply(a.x, a.y), Op::apply(a.z, a.w));
+  for (int w = 1; w < (nwarps >> 2); ++w) {
+    a = q[w];
+    r = Op::apply(r, Op::apply(Op::apply(a.x, a.y), Op::apply(a.z, a.w)));
+  }
+  return r;
+}
+
 // One CTA of blockDim.x threads per row; thread t holds vectors t, t + blockDim.x, ... (VPT of them at most).
 // vec_ok != 0: 16-byte aligned buffers and cols % V == 0 (16-byte accesses); otherwise the same register layout is
 // filled and drained element by element, positions at or beyond `cols` masked out.
@@ -19,7 +39,8 @@ template <typename T, int VPT>
 __global__ void __launch_bounds__(512)
     k_softmax_safe(const T* __restrict__ x, T* __restrict__ y, long long rows, long long cols, long long vec_ok) {
   constexpr int V = Io<T>::kVec;
-  __shared__ float scratch[32];
+  __shared__ __align__(16) float max_buf[2][16], sum_buf[2][16];
+  int parity     = 0;
   const int nvec = (int)((cols + V - 1) / V);
   const int G    = blockDim.x;
   // The vectors of the NEXT row of this CTA are requested before the current row is reduced, so that the two
@@ -55,7 +76,7 @@ __global__ void __launch_bounds__(512)
       for (int j = 0; j < VPT; ++j)
         if ((int)threadIdx.x + j * G < nvec) raw[j] = __ldcs(pn + threadIdx.x + j * G);
     }
-    mx = cta_allreduce<MaxOp>(mx, scratch);
+    mx = cta_fold<MaxOp>(mx, max_buf, parity);
     float sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
@@ -70,7 +91,8 @@ __global__ void __launch_bounds__(512)
         }
       }
     }
-    sum             = cta_allreduce<SumOp>(sum, scratch);
+    sum             = cta_fold<SumOp>(sum, sum_buf, parity);
+    parity ^= 1;
     const float inv = 1.0f / sum;
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
