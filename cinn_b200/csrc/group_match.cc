@@ -1197,7 +1197,8 @@ struct Matcher {
       }
     }
     const int64_t cols = x.shape.back(), rows = x.numel() / std::max<int64_t>(cols, 1);
-    if (safe) {
+    const bool simple  = !safe && dev.rownorm_simple > 0 && CeilDiv(cols, half ? 8 : 4) <= 4096;
+    if (safe || simple) {
       // One CTA per row, the row in registers: at most 512 threads x 8 vectors.
       const int V        = half ? 8 : 4;
       const int64_t nvec = CeilDiv(cols, V);
@@ -1212,9 +1213,10 @@ struct Matcher {
       while (G < 512 && G * target < nvec) G *= 2;
       int vpt = 1;
       while (G * vpt < nvec) vpt *= 2;
-      auto p = NewPlan("softmax_safe_row");
+      auto p = NewPlan(safe ? "softmax_safe_row" : "softmax_row");
       LaunchStep s;
-      if (!Kernel(&s, std::string("softmax_safe_") + (half ? "f16" : "f32") + "_v" + std::to_string(vpt))) return nullptr;
+      if (!Kernel(&s, std::string(safe ? "softmax_safe_" : "softmax_plain_") + (half ? "f16" : "f32") + "_v" + std::to_string(vpt)))
+        return nullptr;
       s.block[0] = G;
       s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(rows, (int64_t)dev.sm_count * (2048 / G) * 4));
       s.args     = {In(0), Out(0), I(rows), I(cols), Aligned(cols % V == 0, {0}, {0})};

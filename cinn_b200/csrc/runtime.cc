@@ -73,7 +73,7 @@ static std::mutex g_mu;
 static int g_opt_sm_count = 0;  // 0: query the device, or 148 without one
 static int g_opt_rownorm_rows = 0;
 static int g_opt_ew_stream = 1, g_opt_ew_stream_stages = 0, g_opt_ew_stream_ctas = 0;
-static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1;
+static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1, g_opt_rownorm_simple = -1;
 
 typedef unsigned int (*AsyncTimeoutReader)(int* cuda_status);
 static std::vector<AsyncTimeoutReader>& TimeoutReaders() {
@@ -104,6 +104,7 @@ static DeviceInfo CurrentDeviceInfo() {
   d.rownorm_stages      = g_opt_rownorm_stages;
   d.rownorm_ctas_per_sm = g_opt_rownorm_ctas;
   d.enable_tma_rownorm = g_opt_enable_tma_rownorm;
+  d.rownorm_simple     = g_opt_rownorm_simple;
   if (g_opt_sm_count > 0) {
     d.sm_count = g_opt_sm_count;
     return d;
@@ -769,6 +770,10 @@ int cinn_b200_set_option(const char* key, long long value) {
   }
   if (!strcmp(key, "rownorm_ctas_per_sm")) {
     g_opt_rownorm_ctas = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "rownorm_simple")) {
+    g_opt_rownorm_simple = (int)value;
     return CINN_B200_OK;
   }
   if (!strcmp(key, "enable_tma_rownorm")) {

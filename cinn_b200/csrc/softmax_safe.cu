@@ -35,7 +35,8 @@ __device__ __forceinline__ float cta_fold(float v, float (*buf)[16], int slot) {
 // One CTA of blockDim.x threads per row; thread t holds vectors t, t + blockDim.x, ... (VPT of them at most).
 // vec_ok != 0: 16-byte aligned buffers and cols % V == 0 (16-byte accesses); otherwise the same register layout is
 // filled and drained element by element, positions at or beyond `cols` masked out.
-template <typename T, int VPT>
+// SUBMAX = false: the plain form exp(x) / sum(exp(x)) of the softmax op itself (cinn/hlir/pe/nn.cc:755-796).
+template <typename T, int VPT, bool SUBMAX = true>
 __global__ void __launch_bounds__(512)
     k_softmax_safe(const T* __restrict__ x, T* __restrict__ y, long long rows, long long cols, long long vec_ok) {
   constexpr int V = Io<T>::kVec;
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(512)
       for (int j = 0; j < VPT; ++j)
         if ((int)threadIdx.x + j * G < nvec) raw[j] = __ldcs(pn + threadIdx.x + j * G);
     }
-    mx = cta_fold<MaxOp>(mx, max_buf, parity);
+    mx = SUBMAX ? cta_fold<MaxOp>(mx, max_buf, parity) : 0.0f;
     float sum = 0.0f;
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
@@ -84,7 +85,7 @@ __global__ void __launch_bounds__(512)
       if (v < nvec) {
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-          const float d = f[j][i] - mx;
+          const float d = SUBMAX ? f[j][i] - mx : f[j][i];
           const float e = sizeof(T) == 2 ? exp_for_16bit_out(d) : expf(d);
           f[j][i]       = (vec_ok || (long long)v * V + i < cols) ? e : 0.0f;
           sum           = sum + f[j][i];
@@ -119,6 +120,13 @@ __global__ void __launch_bounds__(512)
   CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v2", 5, 512, k_softmax_safe<T, 2>);        \
   CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v4", 5, 512, k_softmax_safe<T, 4>);        \
   CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v8", 5, 512, k_softmax_safe<T, 8>)
+#define REG_PLAIN(TNAME, T)                                                                        \
+  CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v1", 5, 512, k_softmax_safe<T, 1, false>);   \
+  CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v2", 5, 512, k_softmax_safe<T, 2, false>);   \
+  CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v4", 5, 512, k_softmax_safe<T, 4, false>);   \
+  CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v8", 5, 512, k_softmax_safe<T, 8, false>)
+REG_PLAIN("f32", float);
+REG_PLAIN("f16", __half);
 REG_SAFE("f32", float);
 REG_SAFE("f16", __half);
 

@@ -237,7 +237,8 @@ int cinn_b200_device_status(unsigned int* async_wait_timeouts);
  * iteration of the register-resident softmax / layer_norm kernels (0 = automatic, else 1, 2 or 4); "rownorm_stages", "rownorm_ctas_per_sm":
  * ring depth and resident CTAs per SM of the streamed softmax / layer_norm kernels (0 = automatic);
  * "enable_tma_rownorm": 1 selects the kernels that stream rows through a shared-memory ring with bulk
- * asynchronous copies, 0 the register-resident ones, -1 (default) chooses per group. */
+ * asynchronous copies, 0 the register-resident ones, -1 (default) chooses per group; "rownorm_simple": 1 runs the
+ * plain softmax through the one-CTA-per-row kernel written for the max-subtracted form (measured equal; default off). */
 int cinn_b200_set_option(const char* key, long long value);
 
 #ifdef __cplusplus
