@@ -632,6 +632,19 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
       round_after();
       rev.push_back(s);
       cur = chain;
+    } else if (op.type == "fill_constant") {
+      // The chain starts from a constant (EW_COPY of an immediate): no operand at all at this end.
+      Step s;
+      s.op   = EW_COPY;
+      s.asel = 0;
+      s.f32  = false;
+      if (!cb.Imm(ChainBuilder::Attr(op, "value", "0"), &s.imm)) {
+        cb.Fail("constant does not fit an immediate");
+        return nullptr;
+      }
+      rev.push_back(s);
+      starts_from_operand = true;
+      break;
     } else if (op.type == "broadcast_to" && cb.input_index.count(op.inputs[0])) {
       // No operand has the output's size: the chain starts from this broadcast operand (EW_COPY).
       Step s;
@@ -665,8 +678,10 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
     cb.Fail("the chain does not start at a full-size group input");
     return nullptr;
   }
-  const int in0       = starts_from_operand ? cb.sides[0].input : cb.input_index[cur];
-  const DType in_type = g.inputs[in0].dtype;
+  // in0 < 0: no pointer operand at all (a chain of constants); the output pointer fills the unused slots.
+  const int in0       = starts_from_operand ? (cb.sides.empty() ? -1 : cb.sides[0].input) : cb.input_index[cur];
+  const DType in_type = in0 >= 0 ? g.inputs[in0].dtype
+                                 : (int_class ? cb.compute : (dbl_class ? DType::kFloat64 : DType::kFloat32));
   if (int_class && !IsIntType(in_type) && in_type != DType::kBool) {
     cb.Fail("an integer chain starts at an integer or bool input");
     return nullptr;
@@ -735,14 +750,19 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   }
   st.block[0] = 256;
   st.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(CeilDiv(cb.n, 8), 256), (int64_t)dev.sm_count * 16));
-  auto in_arg = [](int i) { ArgSpec a; a.kind = ArgSpec::kInput; a.index = i; return a; };
+  auto in_arg = [](int i) {
+    ArgSpec a;
+    a.kind  = i >= 0 ? ArgSpec::kInput : ArgSpec::kOutput;
+    a.index = i >= 0 ? i : 0;
+    return a;
+  };
   auto int_arg = [](int64_t v) { ArgSpec a; a.kind = ArgSpec::kInt; a.ivalue = v; return a; };
   st.args.push_back(in_arg(in0));
   int64_t meta = (int64_t)(starts_from_operand ? (int)EW_NO_INPUT : DTypeKernelCode(in_type)) << 24;
   ArgSpec aligned;
   aligned.kind   = ArgSpec::kAligned;
   aligned.ivalue = 1;
-  aligned.aligned_inputs.push_back(in0);
+  if (in0 >= 0) aligned.aligned_inputs.push_back(in0);
   aligned.aligned_outputs.push_back(0);
   for (int k = 0; k < 3; ++k) {
     if (k < (int)cb.sides.size()) {

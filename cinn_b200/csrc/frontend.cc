@@ -517,6 +517,26 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
   }
   std::vector<int> group_of(n, -1);
   std::vector<std::set<int>> sets;
+  // Instructions that no fetched variable depends on are dropped (they would form groups without an output):
+  // the reference prunes them the same way when it builds the graph from the fetch list.
+  {
+    std::vector<bool> live(n, false);
+    std::vector<int> stack;
+    for (int v : st.fetch)
+      if (st.producer_of_var[v] >= 0) stack.push_back(st.producer_of_var[v]);
+    while (!stack.empty()) {
+      int i = stack.back();
+      stack.pop_back();
+      if (live[i]) continue;
+      live[i] = true;
+      for (int v : b.instrs()[i].inputs)
+        if (st.producer_of_var[v] >= 0) stack.push_back(st.producer_of_var[v]);
+    }
+    for (int i = 0; i < n; ++i)
+      if (!live[i]) group_of[i] = -2;  // neither grouped nor available
+    for (auto& cons : st.consumers_of_var)
+      cons.erase(std::remove_if(cons.begin(), cons.end(), [&](int c) { return !live[c]; }), cons.end());
+  }
 
   // Step 1: connected regions of fusible instructions, tried whole.  This is what lets a multi-reduction
   // composition (softmax, layer_norm) become ONE kernel whatever its row length, where the reference splits at
@@ -525,14 +545,14 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
     std::vector<int> comp(n, -1);
     int ncomp = 0;
     for (int i = 0; i < n; ++i) {
-      if (comp[i] >= 0 || st.IsConst(i) || PatternOf(b.instrs()[i].op_type) == OpPattern::kNonFusible) continue;
+      if (comp[i] >= 0 || group_of[i] == -2 || st.IsConst(i) || PatternOf(b.instrs()[i].op_type) == OpPattern::kNonFusible) continue;
       std::vector<int> stack = {i};
       comp[i]                = ncomp;
       while (!stack.empty()) {
         int u = stack.back();
         stack.pop_back();
         auto visit = [&](int w) {
-          if (w < 0 || comp[w] >= 0 || st.IsConst(w) || PatternOf(b.instrs()[w].op_type) == OpPattern::kNonFusible) return;
+          if (w < 0 || comp[w] >= 0 || group_of[w] == -2 || st.IsConst(w) || PatternOf(b.instrs()[w].op_type) == OpPattern::kNonFusible) return;
           comp[w] = ncomp;
           stack.push_back(w);
         };
@@ -557,7 +577,7 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
   // cinn/hlir/pass/op_fusion_pass.cc:94-95): a producer joins its consumer's group when all of its uses are
   // inside the group and a kernel exists for the enlarged group.
   for (int root = n - 1; root >= 0; --root) {
-    if (group_of[root] >= 0 || st.IsConst(root)) continue;
+    if (group_of[root] != -1 || st.IsConst(root)) continue;
     std::set<int> members = {root};
     bool grew             = PatternOf(b.instrs()[root].op_type) != OpPattern::kNonFusible;
     while (grew) {
