@@ -242,7 +242,7 @@ def side_groups(torch, dev, peak, only=None):
         w = make()
         g = cinn_b200.FusedGroup(w.desc)
         sets = dev_inputs(w, reps)
-        ms = time_group(g, sets, iters=30, warmup=5, torch=torch)
+        ms = time_group(g, sets, iters=50, warmup=10, torch=torch)
         gbs = g.algorithmic_bytes / (ms * 1e-3) / 1e9
         out[name] = {"ms": round(ms, 5), "GB/s": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
                      "elements_per_s": g.elements / (ms * 1e-3), "kernels": g.kernel_names(),
@@ -303,6 +303,37 @@ def run_profile_case(args):
                       "bytes_per_launch": g.algorithmic_bytes,
                       "GB/s": g.algorithmic_bytes / (ms * 1e-3) / 1e9}))
     return 0
+
+
+def strong_scaling_headline(torch, dist, dev, world, rank):
+    """The headline group with its TOTAL size fixed and axis 0 split over the ranks (no communication): every rank
+    runs its [64 / world, 1024, 1024] slice; argument sets rotate through more than 2 x L2 so that inputs come from
+    HBM.  Reported beside the weak-scaling headline; the speed-up over one GPU is total bytes / max-over-ranks time."""
+    import cinn_b200
+    from cinn_b200 import sharding
+    from cinn_b200 import workloads as W
+    start, count = sharding.shard_range(HEADLINE_SHAPE[0], world, rank)
+    if count == 0:
+        return None
+    shape = (count,) + tuple(HEADLINE_SHAPE[1:])
+    w = W.bias_scale_tanh_cast(shape, name="fn_bias_scale_tanh_cast_shard%d" % rank)
+    g = cinn_b200.FusedGroup(w.desc)
+    per_set = 6 * count * HEADLINE_SHAPE[1] * HEADLINE_SHAPE[2]
+    nsets = max(2, int(300e6 // per_set) + 1)
+    bias = torch.randn(HEADLINE_SHAPE[-1], device=dev) * 0.1
+    sets = [[torch.randn(shape, device=dev), bias, torch.empty(shape, dtype=torch.float16, device=dev)]
+            for _ in range(nsets)]
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = time_group(g, sets, iters=100, warmup=10, torch=torch)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    total = 6 * HEADLINE_SHAPE[0] * HEADLINE_SHAPE[1] * HEADLINE_SHAPE[2] + 4 * HEADLINE_SHAPE[2]
+    g.release()
+    return {"ms_per_step_max_over_ranks": round(ms, 5), "GB/s_whole_job": round(total / (ms * 1e-3) / 1e9, 1),
+            "slice_per_rank": list(shape), "argument_sets_rotated": nsets, "scaling": "strong",
+            "note": "no communication; speed-up over one GPU = this GB/s / the N=1 value"}
 
 
 def sharded_reduce_max(torch, dist, dev, world, rank, peak):
@@ -522,8 +553,10 @@ def main():
         line["groups"] = side_groups(torch, dev, peak, args.only)
     if world > 1 and not args.no_side_groups:
         sharded = sharded_reduce_max(torch, dist, dev, world, rank, peak)
+        strong = strong_scaling_headline(torch, dist, dev, world, rank)
         if rank == 0:
-            line["groups"] = {"reduce_max_axis0_128x1024x1024_sharded_on_axis0": sharded}
+            line["groups"] = {"reduce_max_axis0_128x1024x1024_sharded_on_axis0": sharded,
+                              "headline_group_total_size_fixed_sharded_on_axis0": strong}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
