@@ -106,3 +106,67 @@ def test_random_program_matches_the_oracle(oracle, seed, half):
         # (16-bit: a differently rounded transcendental may move a result by one float16 step per op)
         tol = (1e-2 if half else 1e-5) * np.maximum(np.abs(ref.astype(np.float64)), 1.0)
         assert (err <= tol).all(), (seed, str(f), float(err.max()), [p for _, p in comp.groups()])
+
+
+def build_random_int_program(rng, b, shape, bits):
+    T = common.Int(bits)
+    npt = np.int32 if bits == 32 else np.int64
+    feeds = {}
+
+    def new_input(shp, name, lo=-2 ** 20, hi=2 ** 20):
+        feeds[name] = rng.integers(lo, hi, shp).astype(npt)
+        return b.create_input(T, shp, name)
+
+    full = [new_input(shape, "A"), new_input(shape, "B", -2 ** (bits - 2), 2 ** (bits - 2))]
+    div = new_input(shape, "D", 1, 97)            # strictly positive divisors
+    last = new_input((shape[-1],), "v_last")
+    const = lambda v: b.fill_constant(list(shape), float(v), dtype=T.name)  # noqa: E731
+    fetch = []
+    for step in range(int(rng.integers(4, 10))):
+        x = full[int(rng.integers(0, len(full)))]
+        kind = str(rng.choice(["unary", "binary", "vec", "const", "shift", "divmod", "select", "reduce"]))
+        if kind == "unary":
+            y = getattr(b, str(rng.choice(["abs", "negative", "bitwise_not", "identity", "relu"])))(x)
+        elif kind == "binary":
+            op = str(rng.choice(["add", "subtract", "multiply", "max", "min", "bitwise_and", "bitwise_or", "bitwise_xor"]))
+            o = full[int(rng.integers(0, len(full)))]
+            y = getattr(b, op)(x, o) if rng.random() < 0.5 else getattr(b, op)(o, x)
+        elif kind == "vec":
+            y = getattr(b, str(rng.choice(["add", "subtract", "max", "bitwise_xor"])))(x, last)
+        elif kind == "const":
+            y = getattr(b, str(rng.choice(["add", "multiply", "min", "bitwise_and"])))(x, const(int(rng.integers(-1000, 1000))))
+        elif kind == "shift":
+            y = getattr(b, str(rng.choice(["left_shift", "right_shift", "logical_right_shift"])))(x, const(int(rng.integers(0, bits))))
+        elif kind == "divmod":
+            y = getattr(b, str(rng.choice(["floor_divide", "mod", "divide"])))(x, div)
+        elif kind == "select":
+            y = b.select(b.less_than(x, full[int(rng.integers(0, len(full)))]), x, full[int(rng.integers(0, len(full)))])
+        else:
+            fetch.append(getattr(b, str(rng.choice(["reduce_sum", "reduce_max", "reduce_min"])))(x, [int(rng.integers(0, len(shape)))]))
+            continue
+        full.append(y)
+    fetch.append(full[-1])
+    if rng.random() < 0.5:
+        fetch.append(b.cast(full[len(full) // 2], "float32"))
+    return feeds, fetch
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("seed", range(40))
+def test_random_integer_program_is_bit_exact(oracle, seed, bits):
+    rng = np.random.default_rng(5000 + seed)
+    shape = [(6, 40), (3, 5, 16), (33,), (4, 9, 28)][seed % 4]
+    b = NetBuilder("randint%d" % seed)
+    feeds, fetch = build_random_int_program(rng, b, shape, bits)
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(f) for f in fetch])
+    for k, v in feeds.items():
+        if k in comp.get_all_tensor_names():
+            comp.get_tensor(k).from_numpy(v, TARGET)
+    comp.execute()
+    vals = dict(feeds)
+    for desc, pattern in comp.groups():
+        g = ge.parse(desc)
+        vals.update(ge.run_all(desc, [vals[name] for name, _, _ in g["inputs"]]))
+    for f in fetch:
+        got, ref = comp.get_tensor(str(f)).numpy(TARGET), vals[str(f)]
+        assert got.dtype == ref.dtype and np.array_equal(got, ref), (seed, str(f), [p for _, p in comp.groups()])
