@@ -546,9 +546,9 @@ def main():
     torch.cuda.empty_cache()
 
     if rank == 0 and not args.no_cpu_baseline:
-        gbs, ms, threads = cpu_reference_run(steps=3, warmup=1)
+        gbs, ms, threads = cpu_reference_run(steps=20, warmup=2)
         line["cpu_baseline"] = {"value": round(gbs, 3), "unit": UNIT, "cores": threads, "kind": "port", "ms": ms,
-                                "sample": "full headline group, 3 passes, OpenMP over rows, %d threads" % threads}
+                                "sample": "full headline group, 20 passes after 2 warm-up passes, OpenMP over rows, %d threads" % threads}
     if rank == 0 and world == 1 and not args.no_side_groups:
         line["groups"] = side_groups(torch, dev, peak, args.only)
     if world > 1 and not args.no_side_groups:
