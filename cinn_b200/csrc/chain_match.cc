@@ -740,10 +740,10 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   for (auto& t : g.inputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
   p->algorithmic_bytes += out.numel() * DTypeBytes(out.dtype);
   LaunchStep st;
-  st.kernel = FindKernel(int_class ? std::string("ew_chain_int_") + DTypeKernelName(cb.compute) + "_" + DTypeKernelName(out.dtype)
-                         : dbl_class ? std::string("ew_chain_f64_") + DTypeKernelName(out.dtype)
-                                     : std::string("ew_chain_") + DTypeKernelName(out.dtype) + "_s" +
-                                           (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3")));
+  const std::string ns = std::string("_s") + (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3"));
+  st.kernel = FindKernel(int_class ? std::string("ew_chain_int_") + DTypeKernelName(cb.compute) + "_" + DTypeKernelName(out.dtype) + ns
+                         : dbl_class ? std::string("ew_chain_f64_") + DTypeKernelName(out.dtype) + ns
+                                     : std::string("ew_chain_") + DTypeKernelName(out.dtype) + ns);
   if (!st.kernel) {
     cb.Fail("chain kernel for these dtypes is not in the library");
     return nullptr;

@@ -189,7 +189,8 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, doubl
   }
 }
 
-template <int VEC>
+// NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
+template <int VEC, int NS>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const double* imms,
                                           const double (&s1)[VEC], const double (&s2)[VEC], const double (&s3)[VEC],
                                           double (&acc)[VEC]) {
@@ -208,12 +209,13 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
     }
     double o[VEC];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) o[i] = asel == 1 ? s1[i] : (asel == 2 ? s2[i] : (asel == 3 ? s3[i] : (asel == 4 ? acc[i] : imm)));
+    for (int i = 0; i < VEC; ++i)
+      o[i] = (NS >= 1 && asel == 1) ? s1[i] : ((NS >= 2 && asel == 2) ? s2[i] : ((NS >= 3 && asel == 3) ? s3[i] : (asel == 4 ? acc[i] : imm)));
     const double imm2 = imms[(int)(steps[k + 1] >> 32) & (kMaxImm - 1)];
     if (op == EW_FMA) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const double b = bsel == 1 ? s1[i] : (bsel == 2 ? s2[i] : (bsel == 3 ? s3[i] : imm2));
+        const double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
         acc[i]         = fma(acc[i], o[i], b);
       }
       if (bsel == 0) ++k;
@@ -224,7 +226,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
     } else if (op == EW_SELECT) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const double b = bsel == 1 ? s1[i] : (bsel == 2 ? s2[i] : (bsel == 3 ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        const double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
         const double c = role == 0 ? acc[i] : o[i];
         const double t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
         const double f = role == 2 ? acc[i] : b;
@@ -240,7 +242,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
 }
 
 // The fp32 form's parameter list followed by the table of double immediates.
-template <typename OutT>
+template <typename OutT, int NS>
 __global__ void __launch_bounds__(256)
     k_ew_chain_f64(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
                    const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
@@ -265,10 +267,10 @@ __global__ void __launch_bounds__(256)
       const long long i0 = v << 2;
       double acc[4], s1[4], s2[4], s3[4];
       if (in_type != EW_NO_INPUT) load_d4(in0, in_type, i0, true, acc);
-      if (sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
-      if (sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
-      if (sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
-      run_chain<4>(steps, nsteps, imms, s1, s2, s3, acc);
+      if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
+      if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
+      if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
+      run_chain<4, NS>(steps, nsteps, imms, s1, s2, s3, acc);
       store_d4<OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -276,18 +278,22 @@ __global__ void __launch_bounds__(256)
   for (long long i = done + tid; i < n; i += stride) {
     double acc[1], s1[1], s2[1], s3[1];
     acc[0] = in_type != EW_NO_INPUT ? load_d(in0, in_type, i) : 0.0;
-    if (sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
-    if (sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
-    if (sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
-    run_chain<1>(steps, nsteps, imms, s1, s2, s3, acc);
+    if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
+    if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
+    if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
+    run_chain<1, NS>(steps, nsteps, imms, s1, s2, s3, acc);
     out[i] = out_of<OutT>(acc[0]);
   }
 }
 
 }  // namespace
 
-CINN_B200_REGISTER_KERNEL("ew_chain_f64_f64", 39, 256, k_ew_chain_f64<double>);
-CINN_B200_REGISTER_KERNEL("ew_chain_f64_f32", 39, 256, k_ew_chain_f64<float>);
-CINN_B200_REGISTER_KERNEL("ew_chain_f64_bool", 39, 256, k_ew_chain_f64<uint8_t>);
+#define REG_F64_CHAIN(NSNAME, NS)                                                                  \
+  CINN_B200_REGISTER_KERNEL("ew_chain_f64_f64_" NSNAME, 39, 256, k_ew_chain_f64<double, NS>);     \
+  CINN_B200_REGISTER_KERNEL("ew_chain_f64_f32_" NSNAME, 39, 256, k_ew_chain_f64<float, NS>);      \
+  CINN_B200_REGISTER_KERNEL("ew_chain_f64_bool_" NSNAME, 39, 256, k_ew_chain_f64<uint8_t, NS>)
+REG_F64_CHAIN("s0", 0);
+REG_F64_CHAIN("s1", 1);
+REG_F64_CHAIN("s3", 3);
 
 }  // namespace cinn_b200

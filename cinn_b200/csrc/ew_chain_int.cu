@@ -168,7 +168,8 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, T (&f
   }
 }
 
-template <typename T, int VEC>
+// NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
+template <typename T, int VEC, int NS>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const T (&s1)[VEC], const T (&s2)[VEC],
                                           const T (&s3)[VEC], T (&acc)[VEC]) {
   for (int k = 0; k < nsteps; ++k) {
@@ -186,12 +187,13 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
     }
     T o[VEC];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) o[i] = asel == 1 ? s1[i] : (asel == 2 ? s2[i] : (asel == 3 ? s3[i] : (asel == 4 ? acc[i] : imm)));
+    for (int i = 0; i < VEC; ++i)
+      o[i] = (NS >= 1 && asel == 1) ? s1[i] : ((NS >= 2 && asel == 2) ? s2[i] : ((NS >= 3 && asel == 3) ? s3[i] : (asel == 4 ? acc[i] : imm)));
     if (op == EW_SELECT) {
       const T imm2 = (T)(int32_t)(steps[k + 1] >> 32);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const T b = bsel == 1 ? s1[i] : (bsel == 2 ? s2[i] : (bsel == 3 ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        const T b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
         const T c = role == 0 ? acc[i] : o[i];
         const T t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
         const T f = role == 2 ? acc[i] : b;
@@ -208,7 +210,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
 
 // Same parameter list as the float form (k_ew_chain): meta bits 0-3 / 4-7 dtype / mode of side 1, 8-15 side 2,
 // 16-23 side 3, 24-27 dtype of in0.
-template <typename T, typename OutT>
+template <typename T, typename OutT, int NS>
 __global__ void __launch_bounds__(256)
     k_ew_chain_int(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
                    const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
@@ -227,14 +229,33 @@ __global__ void __launch_bounds__(256)
   long long done         = 0;
   if (vec_ok) {
     const long long nvec = n >> 2;
-    for (long long v = tid; v < nvec; v += stride) {
+    // 32-bit values: two vectors (8 elements) per thread iteration, all loads issued before the program runs.
+    constexpr int NV = sizeof(T) == 4 ? 2 : 1;
+    long long v      = tid;
+    for (; v + (NV - 1) * stride < nvec; v += NV * stride) {
+      T acc[4 * NV], s1[4 * NV], s2[4 * NV], s3[4 * NV];
+#pragma unroll
+      for (int j = 0; j < NV; ++j)
+        if (in_type != EW_NO_INPUT) load_int4<T>(in0, in_type, (v + j * stride) << 2, true, *reinterpret_cast<T(*)[4]>(&acc[4 * j]));
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const long long i0 = (v + j * stride) << 2;
+        if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<T, 4>(sd1, i0, *reinterpret_cast<T(*)[4]>(&s1[4 * j]));
+        if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, *reinterpret_cast<T(*)[4]>(&s2[4 * j]));
+        if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, *reinterpret_cast<T(*)[4]>(&s3[4 * j]));
+      }
+      run_chain<T, 4 * NV, NS>(steps, nsteps, s1, s2, s3, acc);
+#pragma unroll
+      for (int j = 0; j < NV; ++j) store_int4<T, OutT>(out, (v + j * stride) << 2, *reinterpret_cast<T(*)[4]>(&acc[4 * j]));
+    }
+    for (; v < nvec; v += stride) {
       const long long i0 = v << 2;
       T acc[4], s1[4], s2[4], s3[4];
       if (in_type != EW_NO_INPUT) load_int4<T>(in0, in_type, i0, true, acc);
-      if (sd1.mode != EW_SIDE_NONE) load_side<T, 4>(sd1, i0, s1);
-      if (sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, s2);
-      if (sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, s3);
-      run_chain<T, 4>(steps, nsteps, s1, s2, s3, acc);
+      if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<T, 4>(sd1, i0, s1);
+      if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, s2);
+      if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, s3);
+      run_chain<T, 4, NS>(steps, nsteps, s1, s2, s3, acc);
       store_int4<T, OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -242,21 +263,25 @@ __global__ void __launch_bounds__(256)
   for (long long i = done + tid; i < n; i += stride) {
     T acc[1], s1[1], s2[1], s3[1];
     acc[0] = in_type != EW_NO_INPUT ? load_int<T>(in0, in_type, i) : 0;
-    if (sd1.mode != EW_SIDE_NONE) load_side<T, 1>(sd1, i, s1);
-    if (sd2.mode != EW_SIDE_NONE) load_side<T, 1>(sd2, i, s2);
-    if (sd3.mode != EW_SIDE_NONE) load_side<T, 1>(sd3, i, s3);
-    run_chain<T, 1>(steps, nsteps, s1, s2, s3, acc);
+    if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<T, 1>(sd1, i, s1);
+    if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 1>(sd2, i, s2);
+    if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 1>(sd3, i, s3);
+    run_chain<T, 1, NS>(steps, nsteps, s1, s2, s3, acc);
     out[i] = convert_out<T, OutT>(acc[0]);
   }
 }
 
 }  // namespace
 
-#define REG_INT_CHAIN(TNAME, T)                                                                            \
-  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i32", 31, 256, k_ew_chain_int<T, int32_t>);          \
-  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i64", 31, 256, k_ew_chain_int<T, long long>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_bool", 31, 256, k_ew_chain_int<T, uint8_t>);         \
-  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_f32", 31, 256, k_ew_chain_int<T, float>)
+#define REG_INT_CHAIN_NS(TNAME, T, NSNAME, NS)                                                                       \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i32_" NSNAME, 31, 256, k_ew_chain_int<T, int32_t, NS>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i64_" NSNAME, 31, 256, k_ew_chain_int<T, long long, NS>);      \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_bool_" NSNAME, 31, 256, k_ew_chain_int<T, uint8_t, NS>);       \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_f32_" NSNAME, 31, 256, k_ew_chain_int<T, float, NS>)
+#define REG_INT_CHAIN(TNAME, T)          \
+  REG_INT_CHAIN_NS(TNAME, T, "s0", 0);   \
+  REG_INT_CHAIN_NS(TNAME, T, "s1", 1);   \
+  REG_INT_CHAIN_NS(TNAME, T, "s3", 3)
 
 REG_INT_CHAIN("i32", int32_t);
 REG_INT_CHAIN("i64", long long);

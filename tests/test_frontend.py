@@ -226,12 +226,12 @@ def test_other_dtypes_pick_their_kernel_families():
 
     i32, i64, f64, f16 = common.Int(32), common.Int(64), common.Float(64), common.Float(16)
     assert one(lambda b: b.abs(b.add(b.create_input(i32, (8, 64), "X"), b.create_input(i32, (64,), "Y")))) == \
-        ["ew_chain ew_chain_int_i32_i32"]
+        ["ew_chain ew_chain_int_i32_i32_s1"]
     assert one(lambda b: b.cast(b.bitwise_and(b.create_input(i64, (8, 64), "X"), b.create_input(i64, (8, 64), "Y")),
-                                "int32")) == ["ew_chain ew_chain_int_i64_i32"]
+                                "int32")) == ["ew_chain ew_chain_int_i64_i32_s1"]
     assert one(lambda b: b.less_than(b.create_input(i32, (8, 64), "X"), b.create_input(i32, (8, 64), "Y"))) == \
-        ["ew_chain ew_chain_int_i32_bool"]
-    assert one(lambda b: b.tanh(b.create_input(f64, (8, 64), "X"))) == ["ew_chain ew_chain_f64_f64"]
+        ["ew_chain ew_chain_int_i32_bool_s1"]
+    assert one(lambda b: b.tanh(b.create_input(f64, (8, 64), "X"))) == ["ew_chain ew_chain_f64_f64_s0"]
     assert one(lambda b: b.cast(b.floor(b.create_input(common.Float(32), (8, 64), "X")), "int64")) == \
         ["ew_chain ew_chain_i64_s0"]
     assert one(lambda b: b.select(b.create_input(common.Bool(), (8, 64), "M"), b.create_input(f16, (8, 64), "X"),
