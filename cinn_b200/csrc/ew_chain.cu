@@ -318,14 +318,40 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       if (bsel == 0) ++k;
     } else if (op == EW_SELECT) {
       // cinn/hlir/pe/elementwise.cc Select: cond ? true_value : false_value; the chain value is one of the three.
+      // The operand and role decisions are uniform: they are taken once per step, outside the element loops.
       const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
+      float b[VEC];
+      switch (bsel) {
+        case 1:
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        const float b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
-        const float c = role == 0 ? acc[i] : o[i];
-        const float t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
-        const float f = role == 2 ? acc[i] : b;
-        acc[i]        = c != 0.0f ? t : f;
+          for (int i = 0; i < VEC; ++i) b[i] = NS >= 1 ? s1[i] : imm2;
+          break;
+        case 2:
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) b[i] = NS >= 2 ? s2[i] : imm2;
+          break;
+        case 3:
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) b[i] = NS >= 3 ? s3[i] : imm2;
+          break;
+        case 4:
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) b[i] = acc[i];
+          break;
+        default:
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) b[i] = imm2;
+          break;
+      }
+      if (role == 0) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = acc[i] != 0.0f ? o[i] : b[i];
+      } else if (role == 1) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = o[i] != 0.0f ? acc[i] : b[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = o[i] != 0.0f ? b[i] : acc[i];
       }
       if (bsel == 0) ++k;
     } else if (op == EW_SCALE_PRE) {
