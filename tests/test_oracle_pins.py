@@ -192,3 +192,52 @@ def test_oracle_reproduces_llvm_compiled_loops_bit_for_bit(oracle):
     assert same(oracle.softmax(d["softmax_x"]), d["softmax_y"])
     assert same(oracle.layernorm(d["ln_x"], d["ln_gamma"], d["ln_beta"], 1e-5), d["ln_y"])
     assert same(oracle.bn_relu_nchw(d["bn_x"], d["bn_scale"], d["bn_bias"], d["bn_mean"], d["bn_var"], 1e-5), d["bn_y"])
+
+
+def test_graph_evaluator_reproduces_llvm_builds_of_the_decomposed_groups(oracle):
+    """tests/golden/llvm_x86_vectors_decomposed.npz (made by make_llvm_x86_vectors_decomposed.py): LLVM -O3 builds of the
+    loops the decomposed batch_norm_train / batch_norm_grad / max-subtracted softmax / gelu groups lower to.  The
+    op-by-op evaluator (oracle/x86_graph_eval.py), fed the groups as text, must give exactly those bits: this pins its
+    contraction rule (only an Add fed by a Mul fuses), its 1 / sqrt, its compare + select maximum from the lowest finite
+    value, its serial sums and true divisions, and the host erff."""
+    import os
+    from oracle import x86_graph_eval as ge
+    from cinn_b200 import workloads as W
+    from cinn_b200 import common
+    from cinn_b200.frontend import Computation, NetBuilder
+    d = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llvm_x86_vectors_decomposed.npz"))
+
+    def same(got, want):
+        return got.dtype == want.dtype and got.shape == want.shape and np.array_equal(got.view(np.uint8), want.view(np.uint8))
+
+    shape = d["bnt_x"].shape
+    w = W.bn_train_apply(shape)   # inputs: mean, var, x, scale, bias
+    got = ge.run(w.desc, [d["bnt_mean"], d["bnt_var"], d["bnt_x"], d["bnt_scale"], d["bnt_bias"]])
+    assert same(got, d["bnt_y"])
+
+    # x_grad with every per-channel operand given (t0 and var + eps as inputs), built through the front end
+    b = NetBuilder("g")
+    F = common.Float(32)
+    c = shape[1]
+    dy, x = b.create_input(F, shape, "dy"), b.create_input(F, shape, "x")
+    t0, db, mean, S, vae = (b.create_input(F, (c,), nm) for nm in ("t0", "db", "mean", "S", "vae"))
+    full, cnt = list(shape), float(shape[0] * shape[2] * shape[3])
+    tmp1 = b.multiply(dy, b.fill_constant(full, cnt))
+    tmp3 = b.divide(b.multiply(b.subtract(x, b.broadcast_to(mean, full, [1])), b.broadcast_to(S, full, [1])),
+                    b.broadcast_to(vae, full, [1]))
+    y = b.multiply(b.broadcast_to(t0, full, [1]), b.subtract(b.subtract(tmp1, b.broadcast_to(db, full, [1])), tmp3))
+    comp = Computation.build_and_compile(common.DefaultNVGPUTarget(), b, plan_only=True)
+    (desc, pattern), = comp.groups()
+    feeds = {"dy": d["bng_dy"], "x": d["bng_x"], "t0": d["bng_t0"], "db": d["bng_db"], "mean": d["bng_mean"],
+             "S": d["bng_s"], "vae": d["bng_vae"]}
+    got = ge.run(desc, [feeds[name] for name, _, _ in ge.parse(desc)["inputs"]])
+    assert same(got, d["bng_y"])
+
+    w = W.softmax_safe(d["sms_x"].shape)
+    assert same(ge.run(w.desc, [d["sms_x"]]), d["sms_y"])
+
+    b = NetBuilder("gelu")
+    y = b.gelu(b.create_input(F, d["gelu_x"].shape, "X"))
+    comp = Computation.build_and_compile(common.DefaultNVGPUTarget(), b, plan_only=True)
+    (desc, pattern), = comp.groups()
+    assert same(ge.run(desc, [d["gelu_x"]]), d["gelu_y"])
