@@ -236,6 +236,19 @@ def side_groups(torch, dev, peak, only=None):
         ("generic_reduce_sum_i32_cols_16384x8192", lambda: W.generic_reduce("sum", "int32", axis=0), 1, ""),
         ("generic_reduce_all_bool_rows_16384x8192", lambda: W.generic_reduce("all", "bool", axis=1), 4, ""),
     ]
+    if not only or any(o in "add_relu_1x3x224x224" for o in only):
+        # config 1 through NetBuilder / Computation, timed by the library's own ExecuteTest loop (no Python per launch)
+        from cinn_b200 import common
+        from cinn_b200.frontend import Computation, NetBuilder
+        b = NetBuilder("c1")
+        a_ = b.create_input(common.Float(32), (1, 3, 224, 224), "A")
+        b_ = b.create_input(common.Float(32), (1, 3, 224, 224), "B")
+        b.relu(b.add(a_, b_))
+        comp = Computation.build_and_compile(common.DefaultNVGPUTarget(), b)
+        out["add_relu_1x3x224x224_execute_test"] = {
+            "us_per_run": round(comp.execute_test(5000) * 1e3, 3),
+            "note": "Program::ExecuteTest of the one-group program: host clock over 5000 back-to-back runs"}
+        del comp
     for name, make, reps, note in plan:
         if only and not any(o in name for o in only):
             continue

@@ -135,6 +135,14 @@ cinn_b200_computation* cinn_b200_program_load(const char* text, int device) {
   return c;
 }
 
+int cinn_b200_computation_execute_test(cinn_b200_computation* c, int repeat, double* avg_ms) {
+  if (!c) return SetLastError(CINN_B200_EINVAL, "execute_test: null computation");
+  std::string err;
+  int rc = c->impl->ExecuteTest(repeat, avg_ms, &err);
+  if (rc != CINN_B200_OK) return SetLastError(rc, err);
+  return CINN_B200_OK;
+}
+
 int cinn_b200_computation_execute(cinn_b200_computation* c, void* stream) {
   if (!c) return SetLastError(CINN_B200_EINVAL, "execute: null computation");
   std::string err;

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <chrono>
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -1028,6 +1029,25 @@ int Computation::Execute(void* stream, std::string* err) {
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return Fail(err, std::string("cudaDeviceSynchronize: ") + cudaGetErrorString(e), CINN_B200_ECUDA);
   }
+  return CINN_B200_OK;
+}
+
+// Program::ExecuteTest (cinn/hlir/framework/graph_compiler.cc:224-244): 100 untimed runs, then `repeat` runs timed on
+// the host clock up to a device synchronisation; the average per run in milliseconds.
+int Computation::ExecuteTest(int repeat, double* avg_ms, std::string* err) {
+  if (repeat <= 0) return Fail(err, "repeat must be positive");
+  cudaStream_t stream = nullptr;
+  if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) return Fail(err, "cudaStreamCreate failed", CINN_B200_ECUDA);
+  int rc = CINN_B200_OK;
+  for (int i = 0; i < 100 && rc == CINN_B200_OK; ++i) rc = Execute(stream, err);
+  cudaStreamSynchronize(stream);
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int i = 0; i < repeat && rc == CINN_B200_OK; ++i) rc = Execute(stream, err);
+  cudaStreamSynchronize(stream);
+  const auto t1 = std::chrono::steady_clock::now();
+  cudaStreamDestroy(stream);
+  if (rc != CINN_B200_OK) return rc;
+  if (avg_ms) *avg_ms = std::chrono::duration<double, std::milli>(t1 - t0).count() / repeat;
   return CINN_B200_OK;
 }
 

@@ -104,6 +104,7 @@ class Computation {
   static std::unique_ptr<Computation> Load(const std::string& text, int device, std::string* err);
   ~Computation();
   int Execute(void* stream, std::string* err);                       // Program::Execute
+  int ExecuteTest(int repeat, double* avg_ms, std::string* err);     // Program::ExecuteTest
   int SetTensorData(const std::string& id, const void* host, size_t bytes, std::string* err);
   int GetTensorData(const std::string& id, void* host, size_t bytes, std::string* err);
   int BindTensor(const std::string& id, void* device_ptr, std::string* err);  // caller-owned memory

@@ -445,6 +445,15 @@ class Computation:
     def execute(self, stream=None):
         _lib.check(_lib.lib().cinn_b200_computation_execute(self._h, stream))
 
+    def execute_test(self, repeat=1000):
+        """Program::ExecuteTest: 100 untimed runs, then `repeat` timed ones; average milliseconds per run (the whole
+        loop runs inside the library, so no Python call overhead is in the figure)."""
+        ms = ctypes.c_double(0.0)
+        L = _lib.lib()
+        L.cinn_b200_computation_execute_test.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+        _lib.check(L.cinn_b200_computation_execute_test(self._h, int(repeat), ctypes.byref(ms)))
+        return ms.value
+
     def groups(self):
         """[(group description text, 'pattern kernel kernel ...')] after fusion, for inspection and tests."""
         L = _lib.lib()
