@@ -135,10 +135,19 @@ cinn_b200_computation* cinn_b200_program_load(const char* text, int device) {
   return c;
 }
 
+int cinn_b200_computation_execute_graph(cinn_b200_computation* c, void* stream) {
+  if (!c) return SetLastError(CINN_B200_EINVAL, "execute_graph: null computation");
+  std::string err;
+  int rc = c->impl->ExecuteGraph(stream, &err);
+  if (rc != CINN_B200_OK) return SetLastError(rc, err);
+  return CINN_B200_OK;
+}
+
 int cinn_b200_computation_execute_test(cinn_b200_computation* c, int repeat, double* avg_ms) {
   if (!c) return SetLastError(CINN_B200_EINVAL, "execute_test: null computation");
   std::string err;
-  int rc = c->impl->ExecuteTest(repeat, avg_ms, &err);
+  // repeat < 0: the same measurement with the program replayed from its CUDA graph
+  int rc = c->impl->ExecuteTest(repeat < 0 ? -repeat : repeat, avg_ms, &err, repeat < 0);
   if (rc != CINN_B200_OK) return SetLastError(rc, err);
   return CINN_B200_OK;
 }

@@ -957,6 +957,7 @@ std::unique_ptr<Computation> Computation::Load(const std::string& text, int devi
 }
 
 Computation::~Computation() {
+  if (graph_exec_) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec_));
   for (auto& ins : instrs_) cinn_b200_release_group(ins.fn_name.c_str());
   if (device_ >= 0) {
     int prev = 0;
@@ -982,6 +983,10 @@ int Computation::BindTensor(const std::string& id, void* device_ptr, std::string
     t->owned = false;
   }
   t->buffer.memory = static_cast<uint8_t*>(device_ptr);
+  if (graph_exec_) {  // the captured graph holds the old address
+    cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(graph_exec_));
+    graph_exec_ = nullptr;
+  }
   return CINN_B200_OK;
 }
 
@@ -1034,15 +1039,43 @@ int Computation::Execute(void* stream, std::string* err) {
 
 // Program::ExecuteTest (cinn/hlir/framework/graph_compiler.cc:224-244): 100 untimed runs, then `repeat` runs timed on
 // the host clock up to a device synchronisation; the average per run in milliseconds.
-int Computation::ExecuteTest(int repeat, double* avg_ms, std::string* err) {
+int Computation::ExecuteGraph(void* stream_v, std::string* err) {
+  if (device_ < 0) return Fail(err, "this computation was planned without a device");
+  if (!stream_v) return Fail(err, "ExecuteGraph needs a stream (capture is not possible on the NULL stream)");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (!graph_exec_) {
+    int rc = Execute(stream, err);  // ordinary run first: allocations (scratch) must not happen inside a capture
+    if (rc != CINN_B200_OK) return rc;
+    cudaError_t e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return Fail(err, std::string("cudaStreamBeginCapture: ") + cudaGetErrorString(e), CINN_B200_ECUDA);
+    rc = Execute(stream, err);
+    cudaGraph_t graph = nullptr;
+    e                 = cudaStreamEndCapture(stream, &graph);
+    if (rc != CINN_B200_OK || e != cudaSuccess || !graph) {
+      if (graph) cudaGraphDestroy(graph);
+      return rc != CINN_B200_OK ? rc : Fail(err, std::string("cudaStreamEndCapture: ") + cudaGetErrorString(e), CINN_B200_ECUDA);
+    }
+    cudaGraphExec_t exec = nullptr;
+    e                    = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return Fail(err, std::string("cudaGraphInstantiate: ") + cudaGetErrorString(e), CINN_B200_ECUDA);
+    graph_exec_ = exec;
+    return CINN_B200_OK;  // the capture pass did not run the kernels; the ordinary run above produced this call's results
+  }
+  cudaError_t e = cudaGraphLaunch(static_cast<cudaGraphExec_t>(graph_exec_), stream);
+  if (e != cudaSuccess) return Fail(err, std::string("cudaGraphLaunch: ") + cudaGetErrorString(e), CINN_B200_ECUDA);
+  return CINN_B200_OK;
+}
+
+int Computation::ExecuteTest(int repeat, double* avg_ms, std::string* err, bool use_graph) {
   if (repeat <= 0) return Fail(err, "repeat must be positive");
   cudaStream_t stream = nullptr;
   if (cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking) != cudaSuccess) return Fail(err, "cudaStreamCreate failed", CINN_B200_ECUDA);
   int rc = CINN_B200_OK;
-  for (int i = 0; i < 100 && rc == CINN_B200_OK; ++i) rc = Execute(stream, err);
+  for (int i = 0; i < 100 && rc == CINN_B200_OK; ++i) rc = use_graph ? ExecuteGraph(stream, err) : Execute(stream, err);
   cudaStreamSynchronize(stream);
   const auto t0 = std::chrono::steady_clock::now();
-  for (int i = 0; i < repeat && rc == CINN_B200_OK; ++i) rc = Execute(stream, err);
+  for (int i = 0; i < repeat && rc == CINN_B200_OK; ++i) rc = use_graph ? ExecuteGraph(stream, err) : Execute(stream, err);
   cudaStreamSynchronize(stream);
   const auto t1 = std::chrono::steady_clock::now();
   cudaStreamDestroy(stream);

@@ -104,7 +104,11 @@ class Computation {
   static std::unique_ptr<Computation> Load(const std::string& text, int device, std::string* err);
   ~Computation();
   int Execute(void* stream, std::string* err);                       // Program::Execute
-  int ExecuteTest(int repeat, double* avg_ms, std::string* err);     // Program::ExecuteTest
+  int ExecuteTest(int repeat, double* avg_ms, std::string* err, bool use_graph = false);  // Program::ExecuteTest
+  // The whole program as ONE CUDA graph: captured on the first call (after one ordinary run, so that every group has
+  // its scratch), replayed afterwards; re-captured when a tensor is re-bound.  `stream` must not be NULL.  No
+  // counterpart in the reference (its host loop issues one launch per instruction every time).
+  int ExecuteGraph(void* stream, std::string* err);
   int SetTensorData(const std::string& id, const void* host, size_t bytes, std::string* err);
   int GetTensorData(const std::string& id, void* host, size_t bytes, std::string* err);
   int BindTensor(const std::string& id, void* device_ptr, std::string* err);  // caller-owned memory
@@ -130,6 +134,7 @@ class Computation {
   std::vector<std::string> names_;
   int device_ = -1;
   bool args_cached_ = false;
+  void* graph_exec_ = nullptr;  // cudaGraphExec_t
   std::string uid_;
 };
 

@@ -445,13 +445,20 @@ class Computation:
     def execute(self, stream=None):
         _lib.check(_lib.lib().cinn_b200_computation_execute(self._h, stream))
 
-    def execute_test(self, repeat=1000):
+    def execute_graph(self, stream):
+        """The whole program replayed as one CUDA graph (captured at the first call); `stream` is a raw stream handle."""
+        L = _lib.lib()
+        L.cinn_b200_computation_execute_graph.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        _lib.check(L.cinn_b200_computation_execute_graph(self._h, ctypes.c_void_p(stream)))
+
+    def execute_test(self, repeat=1000, use_graph=False):
         """Program::ExecuteTest: 100 untimed runs, then `repeat` timed ones; average milliseconds per run (the whole
-        loop runs inside the library, so no Python call overhead is in the figure)."""
+        loop runs inside the library, so no Python call overhead is in the figure).  use_graph=True replays the
+        program's CUDA graph instead of issuing the launches one by one."""
         ms = ctypes.c_double(0.0)
         L = _lib.lib()
         L.cinn_b200_computation_execute_test.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
-        _lib.check(L.cinn_b200_computation_execute_test(self._h, int(repeat), ctypes.byref(ms)))
+        _lib.check(L.cinn_b200_computation_execute_test(self._h, -int(repeat) if use_graph else int(repeat), ctypes.byref(ms)))
         return ms.value
 
     def groups(self):

@@ -162,8 +162,13 @@ void cinn_b200_computation_destroy(cinn_b200_computation* computation);
 long long cinn_b200_computation_export(cinn_b200_computation* computation, char* out, size_t out_len);
 cinn_b200_computation* cinn_b200_program_load(const char* text, int device);
 int cinn_b200_computation_execute(cinn_b200_computation* computation, void* stream);
+/* The whole program as one CUDA graph: captured at the first call (which also runs the program once the ordinary
+ * way), replayed by later calls, re-captured after bind_tensor.  `stream` must not be NULL.  The reference has no
+ * counterpart: its host loop issues one launch per instruction at every Execute. */
+int cinn_b200_computation_execute_graph(cinn_b200_computation* computation, void* stream);
 /* Program::ExecuteTest (cinn/hlir/framework/graph_compiler.cc:224-244): 100 untimed runs, then `repeat` runs timed on
- * the host clock up to a device synchronisation; writes the average milliseconds per run. */
+ * the host clock up to a device synchronisation; writes the average milliseconds per run.  repeat < 0 measures
+ * |repeat| replays of the program's CUDA graph instead. */
 int cinn_b200_computation_execute_test(cinn_b200_computation* computation, int repeat, double* avg_ms);
 int cinn_b200_computation_set_tensor_data(cinn_b200_computation* computation, const char* id, const void* host,
                                           size_t bytes);
