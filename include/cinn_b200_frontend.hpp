@@ -188,6 +188,14 @@ class CinnComputation {
   CinnComputation& operator=(const CinnComputation&) = delete;
 
   void Execute(void* stream = nullptr) { Check(cinn_b200_computation_execute(h_, stream)); }
+  // The whole program replayed as one CUDA graph (captured at the first call); `stream` must not be NULL.
+  void ExecuteGraph(void* stream) { Check(cinn_b200_computation_execute_graph(h_, stream)); }
+  // Program::ExecuteTest: average milliseconds per run over `repeat` runs (use_graph: replaying the CUDA graph).
+  double ExecuteTest(int repeat, bool use_graph = false) {
+    double ms = 0.0;
+    Check(cinn_b200_computation_execute_test(h_, use_graph ? -repeat : repeat, &ms));
+    return ms;
+  }
   void SetTensorData(const std::string& id, const void* host, size_t bytes) {
     Check(cinn_b200_computation_set_tensor_data(h_, id.c_str(), host, bytes));
   }
