@@ -199,6 +199,29 @@ int cinn_b200_computation_tensor_info(cinn_b200_computation* c, const char* id, 
   return CopyText(DTypeName(t->var.dtype), dtype, dtype_len);
 }
 
+int cinn_b200_computation_tensor_role(cinn_b200_computation* c, const char* id) {
+  if (!c || !id) return SetLastError(CINN_B200_EINVAL, "tensor_role: bad argument");
+  if (!c->impl->Find(id)) return SetLastError(CINN_B200_ENOTFOUND, std::string("no tensor named '") + id + "'");
+  bool written = false, read = false;
+  for (auto& g : c->impl->groups()) {
+    if (g.pattern == "reshape_alias") {
+      // an alias group reads its operand and defines its result
+      for (auto& op : g.desc.ops) {
+        written = written || op.output == id;
+        for (auto& in : op.inputs) read = read || in == id;
+      }
+      continue;
+    }
+    for (auto& t : g.desc.outputs) written = written || t.name == id;
+    for (auto& t : g.desc.inputs) read = read || t.name == id;
+  }
+  for (auto& a : c->impl->aliases()) {
+    written = written || a.first == id;
+    read    = read || a.second == id;
+  }
+  return !written ? 0 : (read ? 1 : 2);
+}
+
 int cinn_b200_computation_num_groups(cinn_b200_computation* c) { return c ? (int)c->impl->groups().size() : 0; }
 
 int cinn_b200_computation_group_desc(cinn_b200_computation* c, int index, char* out, size_t len) {

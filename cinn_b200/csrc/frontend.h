@@ -115,6 +115,7 @@ class Computation {
   ScopeTensor* Find(const std::string& id);
   const std::vector<FusedGroupInfo>& groups() const { return groups_; }
   const std::vector<std::string>& tensor_names() const { return names_; }
+  const std::vector<std::pair<std::string, std::string>>& aliases() const { return aliases_; }
   int device() const { return device_; }
 
  private:

@@ -442,6 +442,17 @@ class Computation:
     def get_tensor(self, name):
         return Tensor(self, str(name))
 
+    def _tensors_of_role(self, role):
+        L = _lib.lib()
+        return [Tensor(self, n) for n in self.get_all_tensor_names()
+                if L.cinn_b200_computation_tensor_role(self._h, n.encode()) == role]
+
+    def get_input_tensors(self):
+        return self._tensors_of_role(0)
+
+    def get_output_tensors(self):
+        return self._tensors_of_role(2)
+
     def execute(self, stream=None):
         _lib.check(_lib.lib().cinn_b200_computation_execute(self._h, stream))
 

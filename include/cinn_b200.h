@@ -179,6 +179,10 @@ int cinn_b200_computation_num_tensors(cinn_b200_computation* computation);
 const char* cinn_b200_computation_tensor_name(cinn_b200_computation* computation, int index);
 int cinn_b200_computation_tensor_info(cinn_b200_computation* computation, const char* id, char* dtype,
                                       size_t dtype_len, long long* shape /* [8] */, int* ndim, void** device_ptr);
+/* 0: an input of the program (nothing in it writes the tensor), 2: an output (written, read by nothing in it),
+ * 1: in between; negative on error.  What GetInputTensors / GetOutputTensors of frontend::CinnComputation
+ * (cinn/frontend/computation.h:120-140) enumerate. */
+int cinn_b200_computation_tensor_role(cinn_b200_computation* computation, const char* id);
 /* The groups the fusion pass produced: description text, and "pattern kernel kernel ..." of the match. */
 int cinn_b200_computation_num_groups(cinn_b200_computation* computation);
 int cinn_b200_computation_group_desc(cinn_b200_computation* computation, int index, char* out, size_t out_len);

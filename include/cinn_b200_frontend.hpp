@@ -164,9 +164,38 @@ class NetBuilder {
   cinn_b200_builder* h_;
 };
 
+// What CinnComputation::GetTensor returns: a description of a scope tensor (hlir::framework::Tensor in the reference).
+struct TensorInfo {
+  std::string id, dtype;
+  std::vector<int64_t> shape;
+  void* device_ptr = nullptr;
+  int64_t numel() const {
+    int64_t n = 1;
+    for (auto d : shape) n *= d;
+    return n;
+  }
+};
+
 // frontend::CinnComputation (cinn/frontend/computation.h:26-158).
 class CinnComputation {
  public:
+  // Compile is BuildAndCompile under the reference's other name (there it takes a Program already built).
+  static std::shared_ptr<CinnComputation> Compile(int device, const NetBuilder& builder, const std::vector<Variable>& outputs = {}) {
+    return BuildAndCompile(device, builder, outputs);
+  }
+  TensorInfo GetTensor(const std::string& id) const {
+    TensorInfo t;
+    char dt[32];
+    long long shape[8];
+    int nd = 0;
+    Check(cinn_b200_computation_tensor_info(h_, id.c_str(), dt, sizeof(dt), shape, &nd, &t.device_ptr));
+    t.id    = id;
+    t.dtype = dt;
+    t.shape.assign(shape, shape + nd);
+    return t;
+  }
+  std::vector<TensorInfo> GetInputTensors() const { return TensorsOfRole(0); }
+  std::vector<TensorInfo> GetOutputTensors() const { return TensorsOfRole(2); }
   // device < 0 plans without touching a GPU (fusion + kernel matching only).
   static std::shared_ptr<CinnComputation> BuildAndCompile(int device, const NetBuilder& builder,
                                                           const std::vector<Variable>& outputs = {}) {
@@ -232,6 +261,12 @@ class CinnComputation {
 
  private:
   explicit CinnComputation(cinn_b200_computation* h) : h_(h) {}
+  std::vector<TensorInfo> TensorsOfRole(int role) const {
+    std::vector<TensorInfo> out;
+    for (auto& name : GetAllTensorNames())
+      if (cinn_b200_computation_tensor_role(h_, name.c_str()) == role) out.push_back(GetTensor(name));
+    return out;
+  }
   static void Check(int rc) {
     if (rc != CINN_B200_OK) throw std::runtime_error(std::string("cinn_b200: ") + cinn_b200_last_error());
   }

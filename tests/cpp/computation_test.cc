@@ -33,6 +33,11 @@ int main(int argc, char** argv) {
       printf("FAILED: the loaded program has a different number of groups\n");
       return 1;
     }
+    if (computation->GetInputTensors().size() != 2 || computation->GetOutputTensors().size() != 3 ||
+        computation->GetTensor("A").shape != std::vector<int64_t>{M, N} || computation->GetTensor(cmp.id).dtype != "bool") {
+      printf("FAILED: inputs / outputs of the computation are not what the program declares\n");
+      return 1;
+    }
     if (!run) {
       printf("PLANNED\n");
       return 0;
