@@ -265,6 +265,8 @@ CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f32", 12, 256, k_bn_nchw<float, true>
 CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true>);
 CINN_B200_REGISTER_KERNEL("ew_bn_nchw_f32", 12, 256, k_bn_nchw<float, false>);
 CINN_B200_REGISTER_KERNEL("ew_bn_nchw_f16", 12, 256, k_bn_nchw<__half, false>);
+CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, true>);
+CINN_B200_REGISTER_KERNEL("ew_bn_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, false>);
 CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_nchw_f32", 12, 256, k_bn_nchw<float, false, true>);
 CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_relu_nchw_f32", 12, 256, k_bn_nchw<float, true, true>);
 

@@ -136,6 +136,13 @@ struct Matcher {
     a.fvalue = v;
     return a;
   }
+  // 16-bit storage of a group computed in fp32: float16 or bfloat16, the same on both sides.
+  const char* half_name_ = "f16";
+  bool SetHalfType(DType in, DType out) {
+    if (in != out || (in != DType::kFloat16 && in != DType::kBFloat16)) return false;
+    half_name_ = in == DType::kFloat16 ? "f16" : "bf16";
+    return true;
+  }
   static ArgSpec Aligned(bool static_ok, std::vector<int> ins, std::vector<int> outs) {
     ArgSpec a;
     a.kind            = ArgSpec::kAligned;
@@ -268,7 +275,7 @@ struct Matcher {
     if (g.inputs.size() != 5) return nullptr;
     const auto &x = g.inputs[0], &o = g.outputs[0];
     if (x.shape.size() != 4 || o.shape != x.shape) return nullptr;
-    if (half ? (x.dtype != DType::kFloat16 || o.dtype != DType::kFloat16)
+    if (half ? !SetHalfType(x.dtype, o.dtype)
              : (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32))
       return nullptr;
     const int64_t N = x.shape[0], C = x.shape[1], HW = x.shape[2] * x.shape[3];
@@ -295,7 +302,7 @@ struct Matcher {
     int64_t chunks      = std::max<int64_t>(1, (units + 512) / 1024);
     while (planes * chunks < (int64_t)dev.sm_count * 4 && units / (chunks * 2) >= 256) chunks *= 2;
     LaunchStep s;
-    if (!Kernel(&s, std::string(relu ? "ew_bn_relu_nchw_" : "ew_bn_nchw_") + (half ? "f16" : "f32"))) return nullptr;
+    if (!Kernel(&s, std::string(relu ? "ew_bn_relu_nchw_" : "ew_bn_nchw_") + (half ? half_name_ : "f32"))) return nullptr;
     s.block[0] = 256;
     s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(planes * chunks, (int64_t)dev.sm_count * 64));
     s.args     = {In(0), In(1), In(2), In(3), In(4), Out(0), I(planes), I(C), I(HW), I(chunks),
@@ -1046,7 +1053,7 @@ struct Matcher {
   bool PlanRowNorm(CompiledGroup* p, bool layernorm, bool half, int64_t rows, int64_t cols, double eps, int x_in,
                    int gamma_in, int beta_in) {
     const int V        = half ? 8 : 4;
-    const char* tname  = half ? "f16" : "f32";
+    const char* tname  = half ? half_name_ : "f32";
     const int sms      = dev.sm_count;
     const int64_t nvec = cols / V;
     auto cluster_step  = [&](LaunchStep* s) -> bool {
@@ -1175,7 +1182,7 @@ struct Matcher {
     }
     const auto &x = g.inputs[0], &o = g.outputs[0];
     if (x.shape.empty() || o.shape != x.shape) return nullptr;
-    if (half ? (x.dtype != DType::kFloat16 || o.dtype != DType::kFloat16)
+    if (half ? !SetHalfType(x.dtype, o.dtype)
              : (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32))
       return nullptr;
     const int nd = (int)x.shape.size();
@@ -1215,7 +1222,7 @@ struct Matcher {
       while (G * vpt < nvec) vpt *= 2;
       auto p = NewPlan(safe ? "softmax_safe_row" : "softmax_row");
       LaunchStep s;
-      if (!Kernel(&s, std::string(safe ? "softmax_safe_" : "softmax_plain_") + (half ? "f16" : "f32") + "_v" + std::to_string(vpt)))
+      if (!Kernel(&s, std::string(safe ? "softmax_safe_" : "softmax_plain_") + (half ? half_name_ : "f32") + "_v" + std::to_string(vpt)))
         return nullptr;
       s.block[0] = G;
       s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(rows, (int64_t)dev.sm_count * (2048 / G) * 4));
@@ -1254,7 +1261,7 @@ struct Matcher {
     if (g.inputs.size() != 3) return nullptr;
     const auto &x = g.inputs[0], &gamma = g.inputs[1], &beta = g.inputs[2], &o = g.outputs[0];
     if (x.shape.size() != 2 || o.shape != x.shape) return nullptr;
-    if (half ? (x.dtype != DType::kFloat16 || o.dtype != DType::kFloat16)
+    if (half ? !SetHalfType(x.dtype, o.dtype)
              : (x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32))
       return nullptr;
     const int64_t rows = x.shape[0], cols = x.shape[1];

@@ -289,5 +289,6 @@ __global__ void __launch_bounds__(512)
 
 REG_ROWNORM_T("f32", float);
 REG_ROWNORM_T("f16", __half);
+REG_ROWNORM_T("bf16", __nv_bfloat16);
 
 }  // namespace cinn_b200

@@ -205,5 +205,8 @@ REG_TMA_G("f32", float, 512);
 REG_TMA_G("f16", __half, 128);
 REG_TMA_G("f16", __half, 256);
 REG_TMA_G("f16", __half, 512);
+REG_TMA_G("bf16", __nv_bfloat16, 128);
+REG_TMA_G("bf16", __nv_bfloat16, 256);
+REG_TMA_G("bf16", __nv_bfloat16, 512);
 
 }  // namespace cinn_b200

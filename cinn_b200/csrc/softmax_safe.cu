@@ -127,7 +127,9 @@ __global__ void __launch_bounds__(512)
   CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v8", 5, 512, k_softmax_safe<T, 8, false>)
 REG_PLAIN("f32", float);
 REG_PLAIN("f16", __half);
+REG_PLAIN("bf16", __nv_bfloat16);
 REG_SAFE("f32", float);
 REG_SAFE("f16", __half);
+REG_SAFE("bf16", __nv_bfloat16);
 
 }  // namespace cinn_b200

@@ -291,3 +291,14 @@ def test_exported_program_loads_without_builder_and_plans_the_same_kernels(tmp_p
         Computation.load("not a program", plan_only=True)
     with pytest.raises(Exception):
         Computation.load(text.replace("op sigmoid", "op conv2d"), plan_only=True)
+
+
+def test_bfloat16_storage_picks_bf16_kernels():
+    """The dedicated batch_norm / softmax / layer_norm kernels exist for bfloat16 storage as for float16."""
+    from cinn_b200 import workloads as W
+    import cinn_b200
+    for w, want in ((W.softmax((64, 4096), half=True), "bf16"), (W.softmax_safe((64, 4096), half=True), "softmax_safe_bf16"),
+                    (W.layer_norm((64, 4096), half=True), "bf16"), (W.bn_relu((2, 8, 14, 14), half=True), "ew_bn_relu_nchw_bf16")):
+        g = cinn_b200.FusedGroup(w.desc.replace("float16", "bfloat16"))
+        assert want in g.kernel_names()[0], g.kernel_names()
+        g.release()

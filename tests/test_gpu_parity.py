@@ -364,3 +364,61 @@ def test_more_than_two_to_the_31_elements():
     g.release()
     del a, b, y
     torch.cuda.empty_cache()
+
+
+# ---- bfloat16 storage (numpy has no bfloat16: torch tensors in, float64 reference from the rounded inputs) -----------
+def _bf16_group(desc, ins, out_shape):
+    import torch
+    import cinn_b200
+    g = cinn_b200.FusedGroup(desc)
+    out = torch.empty(out_shape, dtype=torch.bfloat16, device="cuda:0")
+    g.run(list(ins) + [out])
+    torch.cuda.synchronize()
+    names = g.kernel_names()
+    g.release()
+    return out.double(), names
+
+
+@pytest.mark.parametrize("shape", [(64, 4096), (33, 1000), (16, 16384)])
+def test_bfloat16_softmax_and_layer_norm(shape):
+    import torch
+    torch.manual_seed(7)
+    rows, cols = shape
+    s = "%d,%d" % shape
+    x = (torch.randn(shape, device="cuda:0") * 2).to(torch.bfloat16)
+    x64 = x.double()
+    # plain softmax, cast wrappers as for float16
+    desc = ("group fn_sm_bf16\ninput X bfloat16 %s\nop cast a = X ; dtype=float32\nop softmax b = a ; axis=-1\n"
+            "op cast c = b ; dtype=bfloat16\noutput c bfloat16 %s\n" % (s, s))
+    got, names = _bf16_group(desc, [x], shape)
+    assert "bf16" in names[0], names
+    want = torch.softmax(x64, dim=1)
+    assert bool(((got - want).abs() <= 1e-2 * want + 1e-7).all())
+    # max-subtracted softmax
+    w = W.softmax_safe(shape, half=True)
+    got, names = _bf16_group(w.desc.replace("float16", "bfloat16"), [x], shape)
+    assert "softmax_safe_bf16" in names[0], names
+    assert bool(((got - want).abs() <= 1e-2 * want + 1e-7).all())
+    # layer_norm
+    gamma = 1 + 0.02 * torch.randn(cols, device="cuda:0")
+    beta = 0.02 * torch.randn(cols, device="cuda:0")
+    w = W.layer_norm(shape, half=True)
+    got, names = _bf16_group(w.desc.replace("float16", "bfloat16"), [x, gamma, beta], shape)
+    assert "bf16" in names[0], names
+    want = torch.nn.functional.layer_norm(x64, (cols,), gamma.double(), beta.double(), 1e-5)
+    assert bool(((got - want).abs() <= 1e-2 * want.abs() + 1e-2).all()), float((got - want).abs().max())
+
+
+def test_bfloat16_batch_norm_relu():
+    import torch
+    torch.manual_seed(8)
+    shape, c = (8, 16, 28, 28), 16
+    x = torch.randn(shape, device="cuda:0").to(torch.bfloat16)
+    mean, var = 0.1 * torch.randn(c, device="cuda:0"), torch.rand(c, device="cuda:0") + 0.5
+    scale, bias = 1 + 0.1 * torch.randn(c, device="cuda:0"), 0.1 * torch.randn(c, device="cuda:0")
+    w = W.bn_relu(shape, half=True)
+    got, names = _bf16_group(w.desc.replace("float16", "bfloat16"), [x, scale, bias, mean, var], shape)
+    assert names == ["ew_bn_relu_nchw_bf16"], names
+    r = lambda t: t.double().reshape(1, c, 1, 1)  # noqa: E731
+    want = torch.relu((x.double() - r(mean)) * r(scale) / torch.sqrt(r(var) + 1e-5) + r(bias))
+    assert bool(((got - want).abs() <= 1e-2 * want.abs() + 1e-2).all())
