@@ -34,7 +34,7 @@ SOURCES = [
     "group_match.cc",
     "chain_match.cc",
     "runtime.cc",
-    "frontend.cc",
+    "frontend.cc", "program_pass.cc",
     "capi_frontend.cc",
 ]
 

@@ -80,6 +80,37 @@ int cinn_b200_builder_var_info(cinn_b200_builder* b, const char* id, char* dtype
   return CopyText(DTypeName(var.dtype), dtype, dtype_len);
 }
 
+int cinn_b200_builder_apply_passes(cinn_b200_builder* b, const char* const* passes, int num_passes,
+                                   const char* const* fetch_ids, int num_fetch) {
+  if (!b || num_passes < 0 || num_fetch < 0 || (num_passes > 0 && !passes) || (num_fetch > 0 && !fetch_ids))
+    return SetLastError(CINN_B200_EINVAL, "apply_passes: bad argument");
+  std::vector<int> fetch;
+  for (int i = 0; i < num_fetch; ++i) {
+    int v = fetch_ids[i] ? b->builder.FindVar(fetch_ids[i]) : -1;
+    if (v < 0) return SetLastError(CINN_B200_ENOTFOUND, "apply_passes: unknown fetch variable");
+    fetch.push_back(v);
+  }
+  std::vector<std::string> names;
+  for (int i = 0; i < num_passes; ++i) names.push_back(passes[i] ? passes[i] : "");
+  if (names.empty()) names = DefaultProgramPasses();
+  for (auto& name : names) {
+    std::string err;
+    if (!ApplyProgramPass(&b->builder, name, fetch, &err)) return SetLastError(CINN_B200_EINVAL, err);
+  }
+  return CINN_B200_OK;
+}
+
+long long cinn_b200_builder_program_text(cinn_b200_builder* b, char* out, size_t out_len) {
+  if (!b) return SetLastError(CINN_B200_EINVAL, "program_text: null builder");
+  const std::string text = PrintProgram(b->builder);
+  if (out && out_len > 0) {
+    const size_t n = std::min(out_len - 1, text.size());
+    memcpy(out, text.data(), n);
+    out[n] = 0;
+  }
+  return (long long)text.size() + 1;
+}
+
 cinn_b200_computation* cinn_b200_computation_build_and_compile(cinn_b200_builder* b, int device,
                                                                const char* const* fetch_ids, int num_fetch) {
   if (!b) {

@@ -115,6 +115,8 @@ bool KnownOp(const std::string& t) {
          t == "transpose" || t == "slice" || t == "concat";
 }
 
+bool IsBinaryBroadcastOp(const std::string& t) { return BinaryOps().count(t) || CompareOps().count(t); }
+
 OpPattern PatternOf(const std::string& t) {
   if (t == "fill_constant") return OpPattern::kConst;
   if (ReduceOps().count(t)) return OpPattern::kReduction;

@@ -52,6 +52,10 @@ class NetBuilder {
   const std::string& name() const { return name_; }
   const std::vector<Variable>& vars() const { return vars_; }
   const std::vector<ProgramInstr>& instrs() const { return instrs_; }
+  // For the program passes, which rebuild the instruction list the way the reference's passes rebuild a Program
+  // through a fresh builder (cinn/frontend/pass/*.cc): variables are only ever appended, so indices stay valid.
+  std::vector<ProgramInstr> TakeInstrs() { return std::move(instrs_); }
+  void AppendInstr(const ProgramInstr& instr) { instrs_.push_back(instr); }
 
  private:
   std::string NewId(const std::string& hint);
@@ -64,6 +68,20 @@ class NetBuilder {
 
 OpPattern PatternOf(const std::string& op_type);
 bool KnownOp(const std::string& op_type);
+// Ops registered with the kBroadcast pattern that take two operands (cinn/hlir/op/broadcast.cc:361-441).
+bool IsBinaryBroadcastOp(const std::string& op_type);
+
+// Program passes (cinn/frontend/program_pass.h:36-105, cinn/frontend/pass/*.cc).  Known names: "AutoCast",
+// "AutoBroadcast", "CastCollapsing", "RemoveIdentity", "DeadCodeEliminate"; the remaining names of the reference's
+// default list are accepted and do nothing here ("ExpandZeroDim", "Decomposer", "TransposeCollapsing",
+// "FillConstantRewriter", "FillConstantFolding": decompositions happen in the builder's own methods, and the other
+// three only remove work that the fusion pass inlines anyway).  `fetch` lists variables that must survive.
+// An unknown name fails with *err set, as the reference's registry lookup does.
+bool ApplyProgramPass(NetBuilder* b, const std::string& pass, const std::vector<int>& fetch, std::string* err);
+// cinn/frontend/optimize.cc:44-82 (DefaultTrainingOptimizeOptions), in its order.
+const std::vector<std::string>& DefaultProgramPasses();
+// One line per instruction, "op out = in, in ; attr=value ...": what a pass left, for tests and logs.
+std::string PrintProgram(const NetBuilder& b);
 
 // One fused group after the fusion pass: which instructions it holds and its interface.
 struct FusedGroupInfo {

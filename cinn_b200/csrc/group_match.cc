@@ -180,10 +180,22 @@ struct Matcher {
   // cinn/hlir/pe/broadcast.cc:35-273 (axis = -1 or ndim-1), cinn/hlir/op/elementwise.cc:149-163,
   // cinn/backends/llvm/llvm_intrin_rule.h:136-154, cinn/hlir/pe/elementwise.cc:213-217.
   std::unique_ptr<CompiledGroup> MatchBiasScaleTanhCast(const std::string& expr) {
-    bool with_cast = expr == "cast(tanh(scale(elementwise_add(%0,%1))))";
-    if (!with_cast && expr != "tanh(scale(elementwise_add(%0,%1)))") return nullptr;
-    if (g.inputs.size() != 2) return nullptr;
-    const auto &x = g.inputs[0], &bias = g.inputs[1], &o = g.outputs[0];
+    // The bias arrives either through the add's `axis` rule or, after the AutoBroadcast program pass, through an
+    // explicit broadcast_to along the last axis (cinn/frontend/pass/auto_broadcast.cc:60-110), which then comes first
+    // in the group and makes the bias input 0.
+    int xi = 0, bi = 1;
+    bool explicit_bc = false, with_cast = false, found = false;
+    for (int form = 0; form < 3 && !found; ++form) {
+      const std::string operands = form == 0 ? "%0,%1" : form == 1 ? "%0,broadcast_to(%1)" : "%1,broadcast_to(%0)";
+      const std::string core     = "tanh(scale(elementwise_add(" + operands + ")))";
+      if (expr != core && expr != "cast(" + core + ")") continue;
+      found       = true;
+      with_cast   = expr != core;
+      explicit_bc = form > 0;
+      if (form == 2) xi = 1, bi = 0;
+    }
+    if (!found || g.inputs.size() != 2) return nullptr;
+    const auto &x = g.inputs[xi], &bias = g.inputs[bi], &o = g.outputs[0];
     if (x.dtype != DType::kFloat32 || bias.dtype != DType::kFloat32) return nullptr;
     if (x.shape.empty() || o.numel() != x.numel()) return nullptr;
     const int64_t cols = x.shape.back();
@@ -193,7 +205,12 @@ struct Matcher {
     const OpDesc* scale = Producer(tanh->inputs[0]);
     const OpDesc* add   = Producer(scale->inputs[0]);
     int64_t axis        = AttrI(*add, "axis", -1);
-    if (!(axis == -1 || axis == (int64_t)x.shape.size() - 1)) return nullptr;
+    if (explicit_bc) {
+      const OpDesc* bc = Producer(add->inputs[1]);
+      if (!bc || AttrList(*bc, "broadcast_axes") != std::vector<int64_t>{(int64_t)x.shape.size() - 1}) return nullptr;
+    } else if (!(axis == -1 || axis == (int64_t)x.shape.size() - 1)) {
+      return nullptr;
+    }
     if (!AttrB(*scale, "bias_after_scale", true)) return nullptr;
     const char* suffix = nullptr;
     if (with_cast) {
@@ -215,7 +232,7 @@ struct Matcher {
     if (!Kernel(&s, std::string("ew_bias_scale_tanh_cast_f32_") + suffix)) return nullptr;
     s.block[0] = 256;
     s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(CeilDiv(n, 8), 512), dev.sm_count * 32));
-    s.args     = {In(0), In(1), Out(0), I(n), I(cols), Aligned(cols % 8 == 0, {0, 1}, {0}),
+    s.args     = {In(xi), In(bi), Out(0), I(n), I(cols), Aligned(cols % 8 == 0, {0, 1}, {0}),
                   F((float)AttrF(*scale, "scale", 1.0)), F((float)AttrF(*scale, "bias", 0.0))};
     // Large 16-bit-output launches stream x through warp-private shared-memory rings filled by bulk copies
     // (ew_stream.cu); the register kernel above stays as the plan for unaligned buffers and small sizes.
@@ -245,7 +262,7 @@ struct Matcher {
       t.block[0] = 256;
       t.grid[0]  = (unsigned)grid;
       t.dyn_smem = (size_t)smem;
-      t.args     = {In(0), In(1), Out(0), I(n), I(cols), I(stages), F((float)AttrF(*scale, "scale", 1.0)),
+      t.args     = {In(xi), In(bi), Out(0), I(n), I(cols), I(stages), F((float)AttrF(*scale, "scale", 1.0)),
                     F((float)AttrF(*scale, "bias", 0.0))};
       p->steps.push_back(t);
       p->steps_unaligned.push_back(s);
@@ -837,6 +854,18 @@ struct Matcher {
         {"reduce_sum(elementwise_mul(%0,%0))", "sumsq"}, {"reduce_sum(elementwise_mul(%0,identity(%0)))", "sumsq"},
         {"reduce_sum(elementwise_mul(identity(%0),%0))", "sumsq"}, {"reduce_sum(abs(%0))", "sumabs"},
         {"reduce_sum(exp(%0))", "sumexp"}, {"reduce_max(abs(%0))", "maxabs"}};
+    // What the AutoCast program pass makes of a 16-bit reduction (cinn/frontend/pass/auto_cast.cc:50-76): widen, reduce
+    // in float32, narrow.  The 16-bit reduction kernels do exactly that in registers.
+    static const std::regex widened(R"(^cast\((reduce_(?:sum|prod|max|min))\(cast\(%0\)\)\)$)");
+    std::smatch wm;
+    if (std::regex_match(expr, wm, widened)) {
+      const auto &x = g.inputs[0], &o = g.outputs[0];
+      const OpDesc* red = Producer(Producer(o.name)->inputs[0]);
+      const OpDesc* in  = red ? Producer(red->inputs[0]) : nullptr;
+      const bool half   = x.dtype == DType::kFloat16 || x.dtype == DType::kBFloat16;
+      if (!half || o.dtype != x.dtype || !in || DTypeFromName(AttrS(*in, "dtype", "")) != DType::kFloat32) return nullptr;
+      return MatchGenericReduce(wm[1].str() + "(%0)");
+    }
     auto it = kinds.find(expr);
     const bool all_any = expr == "reduce_all(%0)" || expr == "reduce_any(%0)";
     if (it == kinds.end() && !all_any) return nullptr;
@@ -970,6 +999,7 @@ struct Matcher {
       return nullptr;
     }
     const OpDesc* op = Producer(o.name);
+    if (op->type == "cast") op = Producer(op->inputs[0]);  // the widened form, see MatchReduce
     int64_t outer, r, inner;
     if (!ReduceView(x.shape, AttrList(*op, "dim"), &outer, &r, &inner)) {
       Fail("reduce over non-adjacent axes has no prebuilt kernel");

@@ -1,0 +1,349 @@
+// Program passes: rewrites of the instruction list between the builder and the fusion pass.
+//
+// What the reference does in cinn/frontend/pass/*.cc behind ProgramPass::Apply (cinn/frontend/program_pass.h:36-105),
+// which frontend::Optimize runs with the list of DefaultTrainingOptimizeOptions (cinn/frontend/optimize.cc:44-82) for
+// Program.apply_pass / Program.build_and_get_output (cinn/pybind/frontend.cc:157-242):
+//   AutoCast          cinn/frontend/pass/auto_cast.cc:31-214     fp16 / bf16 operands of listed ops computed in fp32
+//   AutoBroadcast     cinn/frontend/pass/auto_broadcast.cc:32-125 explicit broadcast_to in front of binary ops
+//   CastCollapsing    cinn/frontend/pass/cast_collapsing.cc:50-301 chains of casts folded into one
+//   RemoveIdentity    cinn/frontend/pass/remove_identity.cc:23-262 ops that change nothing removed
+//   DeadCodeEliminate cinn/frontend/pass/dead_code_eliminate.cc   instructions no fetched variable depends on removed
+// Each pass here rebuilds the builder's instruction list in place; the variable table only grows, so variable indices
+// held by the caller (the fetch list, Python Variable objects) stay valid.
+#include <algorithm>
+#include <functional>
+#include <set>
+#include <sstream>
+
+#include "frontend.h"
+
+namespace cinn_b200 {
+namespace {
+
+bool IsHalf(DType t) { return t == DType::kFloat16 || t == DType::kBFloat16; }
+
+std::vector<int64_t> IntList(const std::string& text) {
+  std::vector<int64_t> out;
+  std::stringstream ss(text);
+  std::string item;
+  while (std::getline(ss, item, ','))
+    if (!item.empty()) out.push_back(atoll(item.c_str()));
+  return out;
+}
+
+std::string JoinList(const std::vector<int64_t>& v) {
+  std::string s;
+  for (size_t i = 0; i < v.size(); ++i) s += (i ? "," : "") + std::to_string(v[i]);
+  return s;
+}
+
+ProgramInstr CastInto(int from, int to, DType dtype) {
+  ProgramInstr c;
+  c.op_type = "cast";
+  c.inputs  = {from};
+  c.output  = to;
+  c.attrs   = {{"dtype", DTypeName(dtype)}};
+  return c;
+}
+
+// ---- AutoCast ----------------------------------------------------------------------------------------
+// The ops of the reference's need_cast_list that exist here (auto_cast.cc:78-108).  For batch_norm only x is cast:
+// its four parameter vectors must be float32 already (auto_cast.cc:109-137).
+const std::set<std::string>& NeedCastOps() {
+  static const std::set<std::string> s = {"sin", "cos", "exp", "log", "log2", "log10", "sqrt", "rsqrt", "cbrt", "erf",
+                                          "sinh", "cosh", "tanh", "asin", "acos", "atan", "asinh", "acosh", "atanh",
+                                          "remainder", "pow", "reduce_sum", "reduce_prod", "sigmoid", "softmax", "gelu",
+                                          "batch_norm"};
+  return s;
+}
+
+bool AutoCast(NetBuilder* b, std::string* err) {
+  const std::vector<ProgramInstr> old = b->TakeInstrs();
+  for (const ProgramInstr& ins : old) {
+    bool half_in = false;
+    for (int v : ins.inputs) half_in = half_in || IsHalf(b->vars()[v].dtype);
+    if (!NeedCastOps().count(ins.op_type) || !half_in) {
+      b->AppendInstr(ins);
+      continue;
+    }
+    std::vector<int> casted = ins.inputs;
+    if (ins.op_type == "batch_norm") {
+      for (size_t k = 1; k < ins.inputs.size(); ++k)
+        if (b->vars()[ins.inputs[k]].dtype != DType::kFloat32) {
+          if (err) *err = "AutoCast: batch_norm's scale, bias, mean and variance must be float32";
+          return false;
+        }
+    }
+    for (size_t k = 0; k < casted.size(); ++k) {
+      if (!IsHalf(b->vars()[casted[k]].dtype) || (ins.op_type == "batch_norm" && k > 0)) continue;
+      casted[k] = b->AddOp("cast", {casted[k]}, {{"dtype", "float32"}}, err);
+      if (casted[k] < 0) return false;
+    }
+    const int wide = b->AddOp(ins.op_type, casted, ins.attrs, err);
+    if (wide < 0) return false;
+    const DType narrow = b->vars()[ins.output].dtype;
+    if (b->vars()[wide].dtype == DType::kFloat32) {
+      b->AppendInstr(CastInto(wide, ins.output, narrow));
+    } else {
+      ProgramInstr keep;
+      keep.op_type = "identity";
+      keep.inputs  = {wide};
+      keep.output  = ins.output;
+      b->AppendInstr(keep);
+    }
+  }
+  return true;
+}
+
+// ---- AutoBroadcast -----------------------------------------------------------------------------------
+bool AutoBroadcast(NetBuilder* b, std::string* err) {
+  const std::vector<ProgramInstr> old = b->TakeInstrs();
+  for (ProgramInstr ins : old) {
+    if (!IsBinaryBroadcastOp(ins.op_type) || ins.inputs.size() <= 1) {
+      b->AppendInstr(ins);
+      continue;
+    }
+    const std::vector<int64_t> out_shape = b->vars()[ins.output].shape;
+    int64_t axis = ins.attrs.count("axis") ? atoll(ins.attrs.at("axis").c_str()) : -1;
+    bool inserted = false;
+    for (int& v : ins.inputs) {
+      const std::vector<int64_t> shape = b->vars()[v].shape;
+      if (shape == out_shape) continue;
+      // auto_broadcast.cc:37-58: same rank => every axis in place, otherwise `axis` (or right-aligned) onwards
+      std::vector<int64_t> axes;
+      if (shape.size() == out_shape.size()) {
+        for (size_t i = 0; i < shape.size(); ++i) axes.push_back((int64_t)i);
+      } else {
+        int64_t a = axis == -1 ? (int64_t)out_shape.size() - (int64_t)shape.size() : axis;
+        if (a < 0 || a + shape.size() > out_shape.size()) {
+          if (err) *err = "AutoBroadcast: cannot broadcast [" + JoinList(shape) + "] to [" + JoinList(out_shape) + "] with axis=" + std::to_string(axis);
+          return false;
+        }
+        for (size_t i = 0; i < shape.size(); ++i) axes.push_back(a++);
+      }
+      v = b->AddOp("broadcast_to", {v}, {{"out_shape", JoinList(out_shape)}, {"broadcast_axes", JoinList(axes)}}, err);
+      if (v < 0) return false;
+      inserted = true;
+    }
+    if (inserted) ins.attrs["axis"] = "-1";
+    b->AppendInstr(ins);
+  }
+  return true;
+}
+
+// ---- CastCollapsing ----------------------------------------------------------------------------------
+// cast_collapsing.cc:111-248: every chain of casts is walked from its first cast; a cast all of whose users are casts
+// hands its operand to them and disappears, a cast to its operand's own type disappears (or, when fetched, becomes an
+// identity), a cast nothing uses and nobody fetches disappears.  As in the reference a program with a single cast is
+// left alone, and the user lists are those of the program before the pass.
+struct CastCollapser {
+  NetBuilder* b;
+  std::vector<ProgramInstr> ins;
+  std::set<int> fetch;
+  std::vector<std::vector<int>> users;  // per variable: instructions reading it (before the pass)
+  std::vector<int> producer;            // per variable
+  std::set<int> removed, visited;
+
+  DType TypeOf(int v) const { return b->vars()[v].dtype; }
+
+  void Fuse(int i) {
+    visited.insert(i);
+    ProgramInstr& c      = ins[i];
+    const int in         = c.inputs[0], out = c.output;
+    const bool fetched   = fetch.count(out) > 0;
+    const bool same_type = TypeOf(in) == TypeOf(out);
+    const std::vector<int>& next = users[out];
+    if (next.empty()) {
+      if (!fetched) removed.insert(i);
+      else if (same_type) ToIdentity(&c);
+      return;
+    }
+    if (same_type) {
+      if (fetched) {
+        ToIdentity(&c);
+        return;
+      }
+      for (int u : next)
+        for (int& v : ins[u].inputs)
+          if (v == out) v = in;
+      removed.insert(i);
+      for (int u : next)
+        if (ins[u].op_type == "cast") Fuse(u);
+      return;
+    }
+    bool any_cast = false;
+    for (int u : next) any_cast = any_cast || ins[u].op_type == "cast";
+    if (!any_cast) return;
+    bool can_remove = !fetched;
+    std::vector<int> fused;
+    for (int u : next) {
+      if (ins[u].op_type != "cast") {
+        can_remove = false;
+        continue;
+      }
+      ins[u].inputs[0] = in;  // the second cast keeps its own target type
+      fused.push_back(u);
+    }
+    if (can_remove) removed.insert(i);
+    for (int u : fused) Fuse(u);
+  }
+
+  static void ToIdentity(ProgramInstr* c) {
+    c->op_type = "identity";
+    c->attrs.clear();
+  }
+
+  void Run() {
+    users.assign(b->vars().size(), {});
+    producer.assign(b->vars().size(), -1);
+    int casts = 0;
+    for (size_t i = 0; i < ins.size(); ++i) {
+      producer[ins[i].output] = (int)i;
+      std::set<int> seen;
+      for (int v : ins[i].inputs)
+        if (seen.insert(v).second) users[v].push_back((int)i);
+      casts += ins[i].op_type == "cast";
+    }
+    if (casts <= 1) return;
+    for (size_t i = 0; i < ins.size(); ++i) {
+      if (ins[i].op_type != "cast" || visited.count((int)i)) continue;
+      int first = (int)i;
+      for (int p = producer[ins[first].inputs[0]]; p >= 0 && ins[p].op_type == "cast"; p = producer[ins[p].inputs[0]]) first = p;
+      if (!visited.count(first)) Fuse(first);
+    }
+  }
+};
+
+bool CastCollapsing(NetBuilder* b, const std::vector<int>& fetch) {
+  CastCollapser c;
+  c.b   = b;
+  c.ins = b->TakeInstrs();
+  c.fetch.insert(fetch.begin(), fetch.end());
+  c.Run();
+  for (size_t i = 0; i < c.ins.size(); ++i)
+    if (!c.removed.count((int)i)) b->AppendInstr(c.ins[i]);
+  return true;
+}
+
+// ---- RemoveIdentity ----------------------------------------------------------------------------------
+// remove_identity.cc:36-75: which instructions change nothing.
+bool ChangesNothing(const NetBuilder& b, const ProgramInstr& ins) {
+  const std::string& t = ins.op_type;
+  auto attr = [&](const char* k, const char* d) { return ins.attrs.count(k) ? ins.attrs.at(k) : std::string(d); };
+  if (t == "identity") return true;
+  if (t == "scale") return atof(attr("scale", "1").c_str()) == 1.0 && atof(attr("bias", "0").c_str()) == 0.0;
+  if (t == "cast") return b.vars()[ins.inputs[0]].dtype == b.vars()[ins.output].dtype;
+  if (t == "transpose") {
+    std::vector<int64_t> perm = IntList(attr("axis", ""));
+    if (perm.size() != b.vars()[ins.inputs[0]].shape.size()) return false;
+    for (size_t i = 0; i < perm.size(); ++i)
+      if (perm[i] != (int64_t)i) return false;
+    return true;
+  }
+  if (t == "concat") return ins.inputs.size() == 1;
+  if (t == "broadcast_to" || t == "slice" || t == "reshape" || t.rfind("reduce_", 0) == 0)
+    return b.vars()[ins.inputs[0]].shape == b.vars()[ins.output].shape;
+  return false;
+}
+
+bool RemoveIdentity(NetBuilder* b, const std::vector<int>& fetch_list) {
+  std::vector<ProgramInstr> ins = b->TakeInstrs();
+  std::set<int> fetch(fetch_list.begin(), fetch_list.end());
+  const int nv = (int)b->vars().size();
+  std::vector<int> producer(nv, -1), repl(nv);
+  for (int v = 0; v < nv; ++v) repl[v] = v;
+  for (size_t i = 0; i < ins.size(); ++i) producer[ins[i].output] = (int)i;
+  std::function<int(int)> find = [&](int v) { return repl[v] == v ? v : repl[v] = find(repl[v]); };
+  std::vector<bool> gone(ins.size(), false);
+  for (size_t i = 0; i < ins.size(); ++i) {
+    if (!ChangesNothing(*b, ins[i])) continue;
+    const int in = find(ins[i].inputs[0]), out = ins[i].output;
+    if (!fetch.count(out)) {
+      repl[out] = in;  // users of the result read the operand
+      gone[i]   = true;
+    } else if (!b->vars()[in].is_input && !fetch.count(in) && producer[in] >= 0 &&
+               b->vars()[in].shape == b->vars()[out].shape && b->vars()[in].dtype == b->vars()[out].dtype) {
+      ins[producer[in]].output = out;  // the operand's producer writes the fetched result directly
+      producer[out]            = producer[in];
+      repl[in]                 = out;
+      gone[i]                  = true;
+    } else if (ins[i].op_type != "reshape") {
+      ins[i].op_type = "identity";  // both ends must survive (remove_identity.cc:222-224)
+      ins[i].attrs.clear();
+    }
+  }
+  for (size_t i = 0; i < ins.size(); ++i) {
+    if (gone[i]) continue;
+    for (int& v : ins[i].inputs) v = find(v);
+    b->AppendInstr(ins[i]);
+  }
+  return true;
+}
+
+// ---- DeadCodeEliminate -------------------------------------------------------------------------------
+bool DeadCodeEliminate(NetBuilder* b, const std::vector<int>& fetch) {
+  if (fetch.empty()) return true;  // nothing named: every unread result counts as an output
+  std::vector<ProgramInstr> ins = b->TakeInstrs();
+  std::vector<int> producer(b->vars().size(), -1);
+  for (size_t i = 0; i < ins.size(); ++i) producer[ins[i].output] = (int)i;
+  std::vector<bool> live(ins.size(), false);
+  std::vector<int> stack;
+  for (int v : fetch)
+    if (producer[v] >= 0) stack.push_back(producer[v]);
+  while (!stack.empty()) {
+    int i = stack.back();
+    stack.pop_back();
+    if (live[i]) continue;
+    live[i] = true;
+    for (int v : ins[i].inputs)
+      if (producer[v] >= 0) stack.push_back(producer[v]);
+  }
+  for (size_t i = 0; i < ins.size(); ++i)
+    if (live[i]) b->AppendInstr(ins[i]);
+  return true;
+}
+
+}  // namespace
+
+const std::vector<std::string>& DefaultProgramPasses() {
+  static const std::vector<std::string> s = {"ExpandZeroDim", "AutoCast", "Decomposer", "RemoveIdentity",
+                                             "CastCollapsing", "TransposeCollapsing", "RemoveIdentity",
+                                             "AutoBroadcast", "FillConstantRewriter", "FillConstantFolding",
+                                             "RemoveIdentity", "DeadCodeEliminate"};
+  return s;
+}
+
+bool ApplyProgramPass(NetBuilder* b, const std::string& pass, const std::vector<int>& fetch, std::string* err) {
+  if (!b) return false;
+  for (int v : fetch)
+    if (v < 0 || v >= (int)b->vars().size()) {
+      if (err) *err = "apply_pass: bad fetch variable";
+      return false;
+    }
+  if (pass == "AutoCast") return AutoCast(b, err);
+  if (pass == "AutoBroadcast") return AutoBroadcast(b, err);
+  if (pass == "CastCollapsing") return CastCollapsing(b, fetch);
+  if (pass == "RemoveIdentity") return RemoveIdentity(b, fetch);
+  if (pass == "DeadCodeEliminate") return DeadCodeEliminate(b, fetch);
+  if (pass == "ExpandZeroDim" || pass == "Decomposer" || pass == "TransposeCollapsing" || pass == "FillConstantRewriter" ||
+      pass == "FillConstantFolding")
+    return true;
+  if (err) *err = "apply_pass: no program pass named '" + pass + "'";
+  return false;
+}
+
+std::string PrintProgram(const NetBuilder& b) {
+  std::string s;
+  for (const ProgramInstr& ins : b.instrs()) {
+    s += ins.op_type + " " + b.vars()[ins.output].id + " =";
+    for (size_t k = 0; k < ins.inputs.size(); ++k) s += (k ? ", " : " ") + b.vars()[ins.inputs[k]].id;
+    if (!ins.attrs.empty()) {
+      s += " ;";
+      for (auto& kv : ins.attrs) s += " " + kv.first + "=" + kv.second;
+    }
+    s += "\n";
+  }
+  return s;
+}
+
+}  // namespace cinn_b200

@@ -84,6 +84,40 @@ class NetBuilder:
                                               out, 128))
         return Variable(self, out.value.decode())
 
+    # ---- program passes (Program.apply_pass / build_and_get_output, cinn/pybind/frontend.cc:157-242) ----------
+    def apply_pass(self, fetch_ids=(), target=None, passes=()):
+        """Rewrites the program by the named program passes, in order; an empty list applies the reference's
+        default list (cinn/frontend/optimize.cc:44-82).  `fetch_ids` are the variables that must survive.  Returns
+        the number of fused groups the rewritten program compiles into, as the reference's apply_pass does."""
+        L = _lib.lib()
+        fetch = [str(f).encode() for f in fetch_ids]
+        names = [str(p).encode() for p in passes]
+        f_arr = (ctypes.c_char_p * max(len(fetch), 1))(*fetch)
+        p_arr = (ctypes.c_char_p * max(len(names), 1))(*names)
+        _lib.check(L.cinn_b200_builder_apply_passes(self._h, p_arr, len(names), f_arr, len(fetch)))
+        comp = Computation.build_and_compile(None, self, fetch=[str(f) for f in fetch_ids], plan_only=True)
+        return len(comp.groups())
+
+    def program_text(self):
+        """One line per instruction, `op out = in, in ; attr=value ...`."""
+        L = _lib.lib()
+        L.cinn_b200_builder_program_text.restype = ctypes.c_longlong
+        L.cinn_b200_builder_program_text.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_size_t]
+        need = L.cinn_b200_builder_program_text(self._h, None, 0)
+        buf = ctypes.create_string_buffer(int(need))
+        L.cinn_b200_builder_program_text(self._h, buf, len(buf))
+        return buf.value.decode()
+
+    def build_and_get_output(self, target, tensor_inputs, input_data, tensor_outputs, passes=()):
+        """Applies the program passes (default list when empty), compiles, feeds `input_data` (numpy arrays, in the
+        order of `tensor_inputs`), runs once and returns the outputs as numpy arrays."""
+        self.apply_pass([str(v) for v in tensor_outputs], target, passes)
+        comp = Computation.build_and_compile(target, self, fetch=[str(v) for v in tensor_outputs])
+        for var, data in zip(tensor_inputs, input_data):
+            comp.get_tensor(str(var)).from_numpy(data, target)
+        comp.execute()
+        return [comp.get_tensor(str(v)).numpy(target) for v in tensor_outputs]
+
     def create_input(self, type, shape, id_hint=""):
         L = _lib.lib()
         sh = (ctypes.c_longlong * max(len(shape), 1))(*[int(d) for d in shape])

@@ -139,6 +139,21 @@ int cinn_b200_builder_var_info(cinn_b200_builder* builder, const char* id, char*
                                long long* shape /* [8] */, int* ndim);
 
 /*
+ * Program passes: replaces ProgramPass::Apply as reached from Program.apply_pass and Program.build_and_get_output
+ * (cinn/frontend/program_pass.h:36-105, cinn/pybind/frontend.cc:157-242).  Rewrites the builder's instruction list in
+ * place by the named passes, in order; num_passes == 0 applies the reference's default list
+ * (cinn/frontend/optimize.cc:44-82).  Built: "AutoCast" (auto_cast.cc), "AutoBroadcast" (auto_broadcast.cc),
+ * "CastCollapsing" (cast_collapsing.cc), "RemoveIdentity" (remove_identity.cc), "DeadCodeEliminate"; the other names of
+ * the default list are accepted and change nothing; any other name fails with CINN_B200_EINVAL.  `fetch_ids` are the
+ * variables that must survive.  Variable ids handed out earlier stay valid.  program_text writes one line per
+ * instruction ("op out = in, in ; attr=value ...") into `out` (truncated to out_len) and returns the size needed
+ * including the terminator.
+ */
+int cinn_b200_builder_apply_passes(cinn_b200_builder* builder, const char* const* passes, int num_passes,
+                                   const char* const* fetch_ids, int num_fetch);
+long long cinn_b200_builder_program_text(cinn_b200_builder* builder, char* out, size_t out_len);
+
+/*
  * CinnComputation (cinn/frontend/computation.h:26-158): BuildAndCompile runs the fusion pass (the counterpart of
  * OpFusionPass + FusionMergePass, cinn/hlir/pass/op_fusion_pass.cc:123-331), compiles every group to prebuilt
  * kernels and allocates the scope's tensors on `device` with cudaMalloc (device < 0: plan only, no GPU touched).

@@ -145,6 +145,23 @@ class NetBuilder {
                      float epsilon = 1e-5f, const std::string& data_layout = "NCHW") {
     return CustomInstr("batch_norm", {x, scale, bias, mean, variance}, "epsilon=" + Num(epsilon) + " data_layout=" + data_layout);
   }
+  // ProgramPass::Apply (cinn/frontend/program_pass.h:36-105): rewrites the program by the named passes, in order; an
+  // empty list applies the default list of cinn/frontend/optimize.cc:44-82.  `fetch` are the variables that must survive.
+  void ApplyPasses(const std::vector<Variable>& fetch, const std::vector<std::string>& passes = {}) {
+    std::vector<const char*> f, p;
+    for (auto& v : fetch) f.push_back(v.id.c_str());
+    for (auto& n : passes) p.push_back(n.c_str());
+    Check(cinn_b200_builder_apply_passes(h_, p.data(), (int)p.size(), f.data(), (int)f.size()));
+  }
+  // One line per instruction: "op out = in, in ; attr=value ...".
+  std::string ProgramText() const {
+    long long need = cinn_b200_builder_program_text(h_, nullptr, 0);
+    if (need <= 0) throw std::runtime_error(std::string("cinn_b200: ") + cinn_b200_last_error());
+    std::string text((size_t)need, '\0');
+    cinn_b200_builder_program_text(h_, &text[0], text.size());
+    text.resize((size_t)need - 1);
+    return text;
+  }
 
  private:
   static void Check(int rc) {

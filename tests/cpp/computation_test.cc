@@ -17,6 +17,18 @@ int main(int argc, char** argv) {
   const bool run = argc > 1 && !strcmp(argv[1], "run");
   const int M = 32, N = 24;
   try {
+    {
+      // program passes: cast(cast(cast(x, int32), int64), float32) collapses to x (cast_collapsing_test.cc:90-109)
+      NetBuilder pb("pass_builder");
+      auto x   = pb.CreateInput("float32", {4, 5, 3}, "X");
+      auto o   = pb.Cast(pb.Cast(pb.Cast(x, "int32"), "int64"), "float32");
+      auto sum = pb.Add(o, o);
+      pb.ApplyPasses({sum}, {"CastCollapsing"});
+      if (pb.ProgramText().find("cast") != std::string::npos || pb.ProgramText().find("= X, X") == std::string::npos) {
+        printf("FAILED: CastCollapsing left %s\n", pb.ProgramText().c_str());
+        return 1;
+      }
+    }
     NetBuilder builder("net_builder");
     auto a   = builder.CreateInput("float32", {M, N}, "A");
     auto b   = builder.CreateInput("float32", {M, N}, "B");

@@ -757,3 +757,66 @@ def test_program_replayed_as_one_cuda_graph(oracle):
     plain, graph = comp.execute_test(300), comp.execute_test(300, use_graph=True)
     print("batch_norm_train %s: %.1f us per run launch by launch, %.1f us replayed from one CUDA graph" % (shape, plain * 1e3, graph * 1e3))
     assert graph < plain
+
+
+# ---- program passes, run ---------------------------------------------------------------------------------------------
+def test_default_passes_on_a_float16_program(oracle):
+    """Default pass list on a 16-bit program: exp and reduce_sum computed in float32 (AutoCast), the bias
+    broadcast explicitly (AutoBroadcast), the dead branch gone; the result equals the oracle's evaluation of the
+    rewritten program and stays within 1e-2 of an exact evaluation."""
+    rng = np.random.default_rng(11)
+    X = rng.standard_normal((256, 2048)).astype(np.float16)
+    Bv = (0.1 * rng.standard_normal(2048)).astype(np.float16)
+    b = NetBuilder("net")
+    x = b.create_input(common.Float(16), X.shape, "X")
+    bias = b.create_input(common.Float(16), Bv.shape, "B")
+    out = b.reduce_sum(b.exp(b.identity(b.add(x, bias))), [1], False)
+    b.tanh(x)  # dead
+    got, = b.build_and_get_output(TARGET, [x, bias], [X, Bv], [out])
+    ops = [ln.split()[0] for ln in b.program_text().splitlines()]
+    # the float32 -> float16 -> float32 pair between exp and reduce_sum is collapsed away (CastCollapsing)
+    assert ops == ["broadcast_to", "elementwise_add", "cast", "exp", "reduce_sum", "cast"]
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(out)])
+    ref = oracle_program(comp, {"X": X, "B": Bv})[str(out)]
+    assert got.dtype == np.float16 and got.shape == (256,)
+    np.testing.assert_allclose(got.astype(np.float64), ref.astype(np.float64), rtol=1e-2)
+    exact = np.exp((X + Bv).astype(np.float64)).sum(axis=1)
+    np.testing.assert_allclose(got.astype(np.float64), exact, rtol=1e-2)
+
+
+def test_cast_collapsing_changes_the_result_like_the_reference():
+    """cast(cast(x, int32), float32) is x itself after CastCollapsing (cast_collapsing_test.cc:90-109): the truncation
+    disappears, exactly as in the reference."""
+    rng = np.random.default_rng(12)
+    X = rng.uniform(-9, 9, (64, 333)).astype(np.float32)
+
+    def build():
+        b = NetBuilder("net")
+        x = b.create_input(common.Float(32), X.shape, "X")
+        t = b.cast(b.cast(x, "int32"), "float32")
+        return b, x, b.add(t, t)
+    b, x, out = build()
+    plain = run_program(b, {"X": X}, [out])[1][str(out)]
+    assert np.array_equal(plain, 2 * np.trunc(X))
+    b, x, out = build()
+    got, = b.build_and_get_output(TARGET, [x], [X], [out], passes=["CastCollapsing"])
+    assert np.array_equal(got, X + X)
+
+
+def test_auto_broadcast_keeps_the_dedicated_kernel_and_its_bits(oracle):
+    from cinn_b200 import workloads as W
+    w = W.bias_scale_tanh_cast((6, 1000))
+    X, Bv = w.inputs
+
+    def build():
+        b = NetBuilder("net")
+        x = b.create_input(common.Float(32), X.shape, "X")
+        bias = b.create_input(common.Float(32), Bv.shape, "bias")
+        return b, x, bias, b.cast(b.tanh(b.scale(b.add(x, bias), 0.5, 0.0, True)), "float16")
+    b, x, bias, out = build()
+    plain = run_program(b, {"X": X, "bias": Bv}, [out])[1][str(out)]
+    b, x, bias, out = build()
+    got, = b.build_and_get_output(TARGET, [x, bias], [X, Bv], [out], passes=["AutoBroadcast"])
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(out)])
+    assert "ew_bias_scale_tanh_cast" in comp.groups()[0][1]
+    assert np.array_equal(got.view(np.uint16), plain.view(np.uint16))

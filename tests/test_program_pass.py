@@ -1,0 +1,209 @@
+"""Program passes (AutoCast, AutoBroadcast, CastCollapsing, RemoveIdentity, DeadCodeEliminate) on CPU.
+
+The expected instruction-count changes are the ones the reference's own pass tests assert
+(cinn/frontend/pass/cast_collapsing_test.cc:28-233, auto_cast_test.cc:29-71: the fourth argument of CompareResult /
+CompareProgramPassResult is `size before - size after`).
+"""
+import pytest
+
+from cinn_b200 import frontend as F
+
+
+def _count(b):
+    return len([ln for ln in b.program_text().splitlines() if ln.strip()])
+
+
+def _ops(b):
+    return [ln.split()[0] for ln in b.program_text().splitlines() if ln.strip()]
+
+
+def _x(b, dtype="float32", shape=(4, 5, 3)):
+    return b.create_input(F.Type(dtype), list(shape), "X")
+
+
+# ---- CastCollapsing: the reference's seven cases --------------------------------------------------------------------
+def test_cast_collapsing_two_casts():
+    b = F.NetBuilder("net")
+    out = b.cast(b.cast(_x(b), "float16"), "float32")
+    n = _count(b)
+    b.apply_pass([out], None, ["Decomposer", "CastCollapsing"])
+    assert n - _count(b) == 1
+    assert _ops(b) == ["identity"]  # x -> float32 is useless but fetched
+
+
+def test_cast_collapsing_three_casts():
+    b = F.NetBuilder("net")
+    out = b.cast(b.cast(b.cast(_x(b), "int32"), "int64"), "float32")
+    n = _count(b)
+    b.apply_pass([out], None, ["CastCollapsing"])
+    assert n - _count(b) == 2
+
+
+def test_cast_collapsing_single_useless_cast_is_left_alone():
+    b = F.NetBuilder("net")
+    out = b.cast(_x(b), "float32")
+    b.apply_pass([out], None, ["CastCollapsing"])
+    assert _ops(b) == ["cast"]
+
+
+def test_cast_collapsing_chain_becomes_useless():
+    b = F.NetBuilder("net")
+    t = b.cast(b.cast(b.cast(_x(b), "int32"), "int64"), "float32")
+    out = b.add(t, t)
+    n = _count(b)
+    b.apply_pass([out], None, ["CastCollapsing"])
+    assert n - _count(b) == 3
+    assert b.program_text().strip().startswith("elementwise_add") and "= X, X" in b.program_text()
+
+
+def test_cast_collapsing_with_other_users():
+    b = F.NetBuilder("net")
+    x = _x(b)
+    t1 = b.cast(x, "int32")
+    t2 = b.cast(t1, "float32")
+    t3 = b.cast(t2, "int32")
+    outs = [b.transpose(t, [0, 2, 1]) for t in (t1, t2, t3)]
+    n = _count(b)
+    b.apply_pass(outs, None, ["CastCollapsing"])
+    assert n - _count(b) == 1
+
+
+def test_cast_collapsing_two_chains():
+    b = F.NetBuilder("net")
+    x = _x(b)
+    t2 = b.cast(b.cast(x, "int32"), "float32")
+    out1 = b.reshape(t2, [5, 3, 4])
+    b.cast(b.cast(out1, "int32"), "float32")
+    out2 = b.transpose(t2, [0, 2, 1])
+    n = _count(b)
+    b.apply_pass([out1, out2], None, ["CastCollapsing"])
+    assert n - _count(b) == 4
+    assert sorted(_ops(b)) == ["reshape", "transpose"]
+
+
+def test_cast_collapsing_parallel_casts_stay():
+    b = F.NetBuilder("net")
+    x = _x(b)
+    out = b.add(b.cast(x, "int32"), b.cast(x, "int32"))
+    n = _count(b)
+    b.apply_pass([out], None, ["CastCollapsing"])
+    assert n - _count(b) == 0
+
+
+def test_cast_collapsing_vertical_and_parallel():
+    b = F.NetBuilder("net")
+    x = _x(b)
+    out = b.add(b.cast(b.cast(x, "int32"), "float32"), b.cast(x, "float32"))
+    n = _count(b)
+    b.apply_pass([out], None, ["CastCollapsing"])
+    assert n - _count(b) == 3
+
+
+# ---- AutoCast --------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_auto_cast_exp(dtype):
+    b = F.NetBuilder("net")
+    out = b.exp(_x(b, dtype))
+    n = _count(b)
+    b.apply_pass([out], None, ["AutoCast", "Decomposer"])
+    assert n - _count(b) == -2
+    assert _ops(b) == ["cast", "exp", "cast"]
+    assert out.type.name == dtype
+    lines = b.program_text().splitlines()
+    assert "dtype=float32" in lines[0] and ("dtype=" + dtype) in lines[2] and lines[2].split()[1] == str(out)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_auto_cast_batch_norm_casts_x_only(dtype):
+    b = F.NetBuilder("net")
+    x = _x(b, dtype, (8, 16, 14, 14))
+    params = [b.create_input(F.Type("float32"), [16], n) for n in ("scale", "bias", "mean", "variance")]
+    out = b.batch_norm(x, *params, epsilon=1e-5, is_test=True)
+    n = _count(b)
+    b.apply_pass([out], None, ["AutoCast", "Decomposer"])
+    assert n - _count(b) == -2
+    assert _ops(b).count("cast") == 2
+
+
+def test_auto_cast_leaves_float32_and_unlisted_ops():
+    b = F.NetBuilder("net")
+    out = b.exp(_x(b))
+    h = b.relu(b.create_input(F.Type("float16"), [4, 4], "H"))
+    before = b.program_text()
+    b.apply_pass([out, h], None, ["AutoCast"])
+    assert b.program_text() == before
+
+
+def test_auto_cast_then_fusion_picks_the_half_storage_reduction():
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float16"), [64, 4096], "X")
+    out = b.reduce_sum(x, [1], False)
+    assert b.apply_pass([out], None, ["AutoCast"]) == 1  # cast + reduce_sum + cast: one group
+
+
+# ---- AutoBroadcast ---------------------------------------------------------------------------------------------------
+def test_auto_broadcast_inserts_broadcast_to():
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float32"), [2, 8, 1024], "X")
+    bias = b.create_input(F.Type("float32"), [1024], "B")
+    out = b.cast(b.tanh(b.scale(b.add(x, bias), 0.5, 0.0, True)), "float16")
+    groups = b.apply_pass([out], None, ["AutoBroadcast"])
+    lines = b.program_text().splitlines()
+    assert lines[0].startswith("broadcast_to") and "broadcast_axes=2" in lines[0] and "out_shape=2,8,1024" in lines[0]
+    assert "axis=-1" in lines[1]
+    assert groups == 1
+    comp = F.Computation.build_and_compile(None, b, fetch=[str(out)], plan_only=True)
+    assert "ew_bias_scale_tanh_cast" in comp.groups()[0][1]  # still the dedicated kernel
+
+
+def test_auto_broadcast_with_axis_and_same_rank():
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float32"), [4, 6, 5], "X")
+    m = b.create_input(F.Type("float32"), [6], "M")
+    k = b.create_input(F.Type("float32"), [1, 1, 5], "K")
+    out = b.multiply(b.add(x, m, axis=1), k)
+    b.apply_pass([out], None, ["AutoBroadcast"])
+    lines = b.program_text().splitlines()
+    assert "broadcast_axes=1" in lines[0] and "broadcast_axes=0,1,2" in lines[2]
+    same = F.NetBuilder("net")
+    a = same.create_input(F.Type("float32"), [4, 4], "A")
+    c = same.create_input(F.Type("float32"), [4, 4], "C")
+    o = same.add(a, c)
+    before = same.program_text()
+    same.apply_pass([o], None, ["AutoBroadcast"])
+    assert same.program_text() == before
+
+
+# ---- RemoveIdentity / DeadCodeEliminate / the default list -----------------------------------------------------------
+def test_remove_identity():
+    b = F.NetBuilder("net")
+    x = _x(b)
+    t = b.identity(b.scale(b.exp(x), 1.0, 0.0, True))
+    out = b.relu(t)
+    kept = b.identity(b.tanh(x))  # fetched: its producer writes the fetched variable directly
+    same_in = b.identity(x)       # input and fetched: both ends survive
+    b.apply_pass([out, kept, same_in], None, ["RemoveIdentity"])
+    assert sorted(_ops(b)) == ["exp", "identity", "relu", "tanh"]
+    text = b.program_text()
+    assert ("tanh %s = X" % kept) in text and ("identity %s = X" % same_in) in text
+
+
+def test_dead_code_eliminate():
+    b = F.NetBuilder("net")
+    x = _x(b)
+    out = b.relu(x)
+    b.exp(b.tanh(x))
+    b.apply_pass([out], None, ["DeadCodeEliminate"])
+    assert _ops(b) == ["relu"]
+
+
+def test_default_pass_list_and_unknown_pass():
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float16"), [64, 1024], "X")
+    bias = b.create_input(F.Type("float16"), [1024], "B")
+    out = b.exp(b.identity(b.add(x, bias)))
+    b.tanh(x)  # dead
+    assert b.apply_pass([out]) == 1
+    assert _ops(b) == ["broadcast_to", "elementwise_add", "cast", "exp", "cast"]
+    with pytest.raises(Exception, match="no program pass named"):
+        b.apply_pass([out], None, ["NoSuchPass"])
