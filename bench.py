@@ -235,6 +235,11 @@ def side_groups(torch, dev, peak, only=None):
         ("generic_reduce_max_i32_rows_16384x8192", lambda: W.generic_reduce("max", "int32", axis=1), 1, ""),
         ("generic_reduce_sum_i32_cols_16384x8192", lambda: W.generic_reduce("sum", "int32", axis=0), 1, ""),
         ("generic_reduce_all_bool_rows_16384x8192", lambda: W.generic_reduce("all", "bool", axis=1), 4, ""),
+        # a reduction with an elementwise chain as its operand: the chain runs inside the reduction kernel
+        ("chain_reduce_sum_abs_diff_rows_8192x8192", lambda: W.chain_reduce("sum_abs_diff", axis=1), 1, "chain + reduce, one kernel"),
+        ("chain_reduce_sum_abs_diff_cols_8192x8192", lambda: W.chain_reduce("sum_abs_diff", axis=0), 1, "chain + reduce, one kernel"),
+        ("chain_reduce_sum_sigmoid_affine_rows_8192x8192", lambda: W.chain_reduce("sum_sigmoid_affine", axis=1), 1,
+         "chain + reduce, one kernel"),
     ]
     if not only or any(o in "add_relu_1x3x224x224" for o in only):
         # config 1 through NetBuilder / Computation, timed by the library's own ExecuteTest loop (no Python per launch)

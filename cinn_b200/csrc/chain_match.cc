@@ -12,6 +12,7 @@
 #include <cstring>
 #include <functional>
 #include <map>
+#include <sstream>
 
 #include "ew_chain.h"
 #include "group_desc.h"
@@ -796,6 +797,206 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
     }
   }
   p->steps.push_back(st);
+  return p;
+}
+
+namespace {
+
+// x of `shape` reduced over `dims` seen as [outer, r, inner] (extent-1 axes ignored): the reduced axes must be adjacent.
+bool AdjacentReduceView(const std::vector<int64_t>& shape, std::vector<int64_t> dims, int64_t* outer, int64_t* r, int64_t* inner) {
+  const int nd = (int)shape.size();
+  if (dims.empty())
+    for (int i = 0; i < nd; ++i) dims.push_back(i);
+  for (auto& d : dims) {
+    if (d < 0) d += nd;
+    if (d < 0 || d >= nd) return false;
+  }
+  *outer = *r = *inner = 1;
+  int state            = 0;  // 0 outer, 1 reduce, 2 inner
+  for (int i = 0; i < nd; ++i) {
+    if (shape[i] == 1) continue;
+    if (std::find(dims.begin(), dims.end(), (int64_t)i) != dims.end()) {
+      if (state == 2) return false;
+      state = 1;
+      *r *= shape[i];
+    } else {
+      if (state == 1) state = 2;
+      (state == 0 ? *outer : *inner) *= shape[i];
+    }
+  }
+  return true;
+}
+
+std::vector<int64_t> DimList(const std::string& text) {
+  std::vector<int64_t> v;
+  std::stringstream ss(text);
+  std::string item;
+  while (std::getline(ss, item, ','))
+    if (!item.empty()) v.push_back(atoll(item.c_str()));
+  return v;
+}
+
+}  // namespace
+
+// reduce_{sum,prod,max,min}(chain(inputs)) [-> cast to a 16-bit float]: the chain is matched as for the plain chain
+// kernel (float form), then run as the first stage of the reduction kernels of chain_reduce.cu.  Returns nullptr
+// without a reason when the group is not of this form at all.
+std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const DeviceInfo& dev, std::string* why) {
+  if (g.outputs.size() != 1 || g.ops.size() < 2) return nullptr;
+  const TensorDesc& out = g.outputs[0];
+  std::map<std::string, const OpDesc*> producer;
+  std::map<std::string, int> uses;
+  for (auto& op : g.ops) {
+    producer[op.output] = &op;
+    for (auto& in : op.inputs) ++uses[in];
+  }
+  if (!producer.count(out.name)) return nullptr;
+  const OpDesc* top = producer[out.name];
+  const OpDesc* red = top;
+  if (top->type == "cast") {
+    if (out.dtype != DType::kFloat16 && out.dtype != DType::kBFloat16) return nullptr;
+    if (top->inputs.empty() || !producer.count(top->inputs[0])) return nullptr;
+    red = producer[top->inputs[0]];
+    if (uses[red->output] != 1) return nullptr;
+  } else if (out.dtype != DType::kFloat32) {
+    return nullptr;
+  }
+  static const std::map<std::string, int> kinds = {{"reduce_sum", 0}, {"reduce_prod", 1}, {"reduce_max", 2}, {"reduce_min", 3}};
+  auto kind = kinds.find(red->type);
+  if (kind == kinds.end() || red->inputs.size() != 1) return nullptr;
+  const std::string t = red->inputs[0];
+  if (!producer.count(t) || uses[t] != 1) return nullptr;  // a bare input is the plain reductions' business
+  // The chain alone, as a group of its own whose output is the reduce's operand.
+  GroupDesc chain = g;
+  chain.ops.clear();
+  for (auto& op : g.ops)
+    if (&op != red && &op != top) chain.ops.push_back(op);
+  std::string w;
+  std::vector<int64_t> shape;
+  {
+    ChainBuilder probe(chain, &w);
+    if (!probe.Infer() || !probe.values.count(t)) return nullptr;
+    if (probe.values[t].dtype != DType::kFloat32) {
+      if (why) *why = "a reduction fused with its producers is prebuilt for a float32 operand only";
+      return nullptr;
+    }
+    shape = probe.values[t].shape;
+  }
+  chain.outputs.resize(1);
+  chain.outputs[0].name  = t;
+  chain.outputs[0].dtype = DType::kFloat32;
+  chain.outputs[0].shape = shape;
+  auto plan = MatchChainOfClass(chain, dev, kFloatChain, &w);
+  if (!plan) {
+    if (why) *why = "the reduce's operand is not an elementwise chain: " + w;
+    return nullptr;
+  }
+  int64_t outer, r, inner;
+  auto it_dim = red->attrs.find("dim");
+  if (!AdjacentReduceView(shape, DimList(it_dim == red->attrs.end() ? "" : it_dim->second), &outer, &r, &inner)) {
+    if (why) *why = "reduce over non-adjacent axes has no prebuilt kernel";
+    return nullptr;
+  }
+  if (out.numel() != outer * inner) {
+    if (why) *why = "reduce output has " + std::to_string(out.numel()) + " elements, expected " + std::to_string(outer * inner);
+    return nullptr;
+  }
+  // Re-target the chain's launch: same 31 parameters (the program, the side operands), reduce geometry appended.
+  LaunchStep st    = plan->steps[0];
+  const std::string ns = std::string(st.kernel->name).substr(std::string(st.kernel->name).size() - 3);  // "_s0" / "_s1" / "_s3"
+  auto int_arg = [](int64_t v) { ArgSpec a; a.kind = ArgSpec::kInt; a.ivalue = v; return a; };
+  const int kOut = 4, kAligned = 6, kMeta = 7;
+  const int64_t out_code = out.dtype == DType::kFloat16 ? EW_F16 : (out.dtype == DType::kBFloat16 ? EW_BF16 : EW_F32);
+  st.args[kMeta].ivalue |= ((int64_t)kind->second << 28) | (out_code << 32);
+  const int sms  = dev.sm_count;
+  const bool f32 = out.dtype == DType::kFloat32;
+  auto p         = std::make_unique<CompiledGroup>();
+  p->name        = g.name;
+  p->pattern     = inner == 1 ? "chain_row_reduce" : "chain_col_reduce";
+  p->inputs      = g.inputs;
+  p->outputs     = g.outputs;
+  p->elements    = outer * r * inner;
+  for (auto& x : g.inputs) p->algorithmic_bytes += x.numel() * DTypeBytes(x.dtype);
+  p->algorithmic_bytes += out.numel() * DTypeBytes(out.dtype);
+  // vectors of four: rows must start on a vector boundary / columns must come in fours; the chain's own side-operand
+  // modes were chosen for the flat index, which both layouts keep.
+  st.args[kAligned].ivalue = ((inner == 1 ? r : inner) % 4 == 0) ? 1 : 0;
+  st.args[kAligned].aligned_outputs.clear();
+  const char* opname = kind->second == 0 ? "sum" : (kind->second == 1 ? "prod" : (kind->second == 2 ? "max" : "min"));
+  auto scratch_arg = [&](int64_t off) { ArgSpec a; a.kind = ArgSpec::kScratch; a.ivalue = off; return a; };
+  ArgSpec out_arg;
+  out_arg.kind  = ArgSpec::kOutput;
+  out_arg.index = 0;
+  if (inner == 1) {
+    int64_t S = 1;  // few long rows: segments of a row, folded by a second launch
+    if (f32 && outer < (int64_t)sms * 2 && r >= 65536)
+      while (S < 1024 && r % (S * 2) == 0 && (r / (S * 2)) % 4 == 0 && r / (S * 2) >= 4096 && outer * S < (int64_t)sms * 8) S *= 2;
+    const int64_t rows = outer * S, len = r / S;
+    st.kernel = FindKernel("chain_reduce_row" + ns);
+    if (!st.kernel) return nullptr;
+    const int64_t group = len > 2048 ? 256 : 32;
+    st.block[0] = 256;
+    st.grid[0]  = (unsigned)std::max<int64_t>(
+        1, group == 32 ? std::min<int64_t>(CeilDiv(rows, 8), (int64_t)sms * 32) : std::min<int64_t>(rows, (int64_t)sms * 16));
+    if (S > 1) {
+      p->scratch_bytes = (size_t)(rows * 4 + 255) / 256 * 256;
+      st.args[kOut]    = scratch_arg(0);
+    }
+    st.args.push_back(int_arg(rows));
+    st.args.push_back(int_arg(len));
+    st.args.push_back(int_arg(group));
+    p->steps.push_back(st);
+    if (S > 1) {
+      LaunchStep f;
+      f.kernel = FindKernel(std::string("reduce_generic_row_") + opname + "_f32");
+      if (!f.kernel) return nullptr;
+      f.block[0] = 256;
+      f.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(outer, 8), (int64_t)sms * 32));
+      f.args     = {scratch_arg(0), out_arg, int_arg(outer), int_arg(S), int_arg(32), int_arg(S % 4 == 0 ? 1 : 0)};
+      p->steps.push_back(f);
+    }
+  } else {
+    const int64_t cols = st.args[kAligned].ivalue ? inner / 4 : inner;
+    const int64_t gx   = std::max<int64_t>(1, CeilDiv(cols, 256));
+    int64_t S = 1;  // few columns: the reduced axis in segments, folded by a second launch
+    if (f32 && outer * r * inner * 4 >= (4 << 20))
+      while (gx * outer * S < (int64_t)sms * 4 && r / (S * 2) >= 16 && S < 64) S *= 2;
+    const int64_t rows_per_split = CeilDiv(r, S);
+    S                            = CeilDiv(r, rows_per_split);
+    st.kernel = FindKernel("chain_reduce_col" + ns);
+    if (!st.kernel) return nullptr;
+    if (outer > 65535) {
+      if (why) *why = "more than 65535 outer slices in a column reduction";
+      return nullptr;
+    }
+    st.block[0] = 256;
+    st.grid[0]  = (unsigned)gx;
+    st.grid[1]  = (unsigned)outer;
+    st.grid[2]  = (unsigned)S;
+    if (S > 1) {
+      p->scratch_bytes = (size_t)(S * outer * inner * 4 + 255) / 256 * 256;
+      st.args[kOut]    = scratch_arg(0);
+    }
+    st.args.push_back(int_arg(outer));
+    st.args.push_back(int_arg(r));
+    st.args.push_back(int_arg(inner));
+    st.args.push_back(int_arg(rows_per_split));
+    p->steps.push_back(st);
+    if (S > 1) {
+      LaunchStep f;
+      f.kernel = FindKernel(std::string("reduce_generic_col_") + opname + "_f32");
+      if (!f.kernel) return nullptr;
+      const int64_t total = outer * inner;
+      ArgSpec al;
+      al.kind   = ArgSpec::kAligned;
+      al.ivalue = total % 4 == 0 ? 1 : 0;
+      al.aligned_outputs.push_back(0);
+      f.block[0] = 256;
+      f.grid[0]  = (unsigned)std::max<int64_t>(1, CeilDiv(total % 4 == 0 ? total / 4 : total, 256));
+      f.args     = {scratch_arg(0), out_arg, int_arg(1), int_arg(S), int_arg(total), int_arg(S), al};
+      p->steps.push_back(f);
+    }
+  }
   return p;
 }
 

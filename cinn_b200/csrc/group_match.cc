@@ -18,6 +18,7 @@
 namespace cinn_b200 {
 
 std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const DeviceInfo& dev, std::string* why);  // chain_match.cc
+std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const DeviceInfo& dev, std::string* why);   // chain_match.cc
 
 namespace {
 
@@ -1362,6 +1363,13 @@ struct Matcher {
       auto p = (this->*f)(expr);
       if (p) return p;
       if (err && !err->empty()) return nullptr;  // a matcher recognised the form but rejected its details
+    }
+    // A reduction whose operand is an elementwise chain: the chain runs inside the reduction kernel.
+    std::string why_reduce;
+    if (auto p = MatchChainReduce(g, dev, &why_reduce)) return p;
+    if (!why_reduce.empty()) {
+      Fail("no prebuilt sm_100a kernel matches expression " + expr + " (" + why_reduce + ")");
+      return nullptr;
     }
     // Last resort for elementwise / broadcast groups: a linear chain run by the generic kernel.
     std::string why;

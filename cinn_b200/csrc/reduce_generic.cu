@@ -35,6 +35,14 @@ struct Elem<__nv_bfloat16> {
   __device__ static Acc largest() { return __uint_as_float(0x7f7f0000u); }
 };
 template <>
+struct Elem<float> {  // second pass of the reductions that leave float32 partials (chain_reduce.cu)
+  using Acc = float;
+  __device__ static Acc load(float v) { return v; }
+  __device__ static float store(Acc v) { return v; }
+  __device__ static Acc lowest() { return -3.402823466e38f; }
+  __device__ static Acc largest() { return 3.402823466e38f; }
+};
+template <>
 struct Elem<double> {
   using Acc = double;
   __device__ static Acc load(double v) { return v; }
@@ -238,6 +246,7 @@ __global__ void __launch_bounds__(256)
   REG_GENERIC("max", GMax, TNAME, T);  \
   REG_GENERIC("min", GMin, TNAME, T)
 
+REG_GENERIC_ARITH("f32", float);
 REG_GENERIC_ARITH("f16", __half);
 REG_GENERIC_ARITH("bf16", __nv_bfloat16);
 REG_GENERIC_ARITH("f64", double);

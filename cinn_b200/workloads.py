@@ -254,6 +254,26 @@ def generic_reduce(kind, dtype, shape=(16384, 8192), axis=1, seed=6):
                     _NP[dtype], out_shape)
 
 
+def chain_reduce(kind="sum_abs_diff", shape=(8192, 8192), axis=1, seed=8):
+    """A reduction whose operand is an elementwise chain, one kernel: `sum_abs_diff` = reduce_sum(|x - y|) of two
+    tensors, `sum_sigmoid_affine` = reduce_sum(sigmoid((x + b) * b)) with a row vector b."""
+    out_shape = tuple(d for i, d in enumerate(shape) if i != axis)
+    s, o = _shape(shape), _shape(out_shape)
+    if kind == "sum_abs_diff":
+        desc = (f"group fn_sum_abs_diff_axis{axis}\ninput X float32 {s}\ninput Y float32 {s}\n"
+                f"op subtract d = X Y ; axis=-1\nop abs a = d\nop reduce_sum r = a ; dim={axis} keep_dim=false\n"
+                f"output r float32 {o}\n")
+        gen = lambda: [_draw(np.random.default_rng(seed), shape, "float32"),  # noqa: E731
+                       _draw(np.random.default_rng(seed + 1), shape, "float32")]
+    else:
+        desc = (f"group fn_sum_sigmoid_affine_axis{axis}\ninput X float32 {s}\ninput B float32 {shape[-1]}\n"
+                f"op elementwise_add t = X B ; axis=-1\nop elementwise_mul u = t B ; axis=-1\nop sigmoid v = u\n"
+                f"op reduce_sum r = v ; dim={axis} keep_dim=false\noutput r float32 {o}\n")
+        gen = lambda: [_draw(np.random.default_rng(seed), shape, "float32"),  # noqa: E731
+                       _draw(np.random.default_rng(seed + 1), (shape[-1],), "float32")]
+    return Workload("chain_reduce_" + kind, desc, gen, np.float32, out_shape)
+
+
 def bn_train_inputs(shape=(256, 64, 112, 112), seed=4):
     rng = np.random.default_rng(seed)
     c = shape[1]

@@ -120,7 +120,7 @@ def test_batch_norm_relu_group_and_argument_order():
     assert [l.split()[1] for l in desc.splitlines() if l.startswith("input")] == ["x"] + names
 
 
-def test_mixed_graph_partitions_into_chain_reduce_chain():
+def test_mixed_graph_partitions_into_fused_chain_reduce_and_chain():
     b = NetBuilder("mixed")
     x = b.create_input(common.Float(32), (8, 16, 1024), "X")
     bias = b.create_input(common.Float(32), (1024,), "bias")
@@ -128,7 +128,8 @@ def test_mixed_graph_partitions_into_chain_reduce_chain():
     z = b.reduce_sum(y, [2])
     b.sqrt(b.abs(z))
     c = plan(b)
-    assert patterns(c) == ["ew_chain", "row_reduce", "ew_chain"]
+    # the chain in front of the reduction runs inside the reduction kernel: no intermediate tensor
+    assert [p for _, p in c.groups()] == ["chain_row_reduce chain_reduce_row_s1", "ew_chain ew_chain_f32_s0"]
 
 
 def test_elementwise_producer_folds_into_reduction():
