@@ -184,7 +184,7 @@ def test_mixed_program_chain_reduce_chain(oracle):
     feeds = {"X": rng.standard_normal((8, 16, 1024)).astype(np.float32),
              "bias": rng.standard_normal(1024).astype(np.float32)}
     comp, out = run_program(b, feeds, [w])
-    assert [p.split()[0] for _, p in comp.groups()] == ["ew_chain", "row_reduce", "ew_chain"]
+    assert [p.split()[0] for _, p in comp.groups()] == ["chain_row_reduce", "ew_chain"]
     ref = oracle_program(comp, feeds)[str(w)]
     bad, worst = oracle.count_not_close(out[str(w)], ref, 1e-5, 1e-5)
     assert bad == 0, (bad, worst)
