@@ -115,6 +115,7 @@ struct Step {
   bool swap  = false;
   float imm  = 0.0f;
   bool f32   = true;   // result type is float32 (contraction only applies to fp32 arithmetic)
+  bool single_use = true;  // EW_MUL: the product has one user in the group (the reference inlines, hence contracts, only then)
   // EW_SELECT only: second operand and the role of the chain value (see ew_chain.h)
   int bsel   = 0;
   float imm2 = 0.0f;
@@ -438,247 +439,312 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
     }
   }
 
-  // Walk back from the output collecting primitive steps in reverse order.
-  bool starts_from_operand = false;
-  std::vector<Step> rev;
-  std::string cur = out.name;
-  while (cb.producer.count(cur)) {
-    const OpDesc& op = *cb.producer[cur];
-    const Value& ov  = cb.values[cur];
-    if (ov.numel() != cb.n) {
-      cb.Fail("value '" + cur + "' on the chain has " + std::to_string(ov.numel()) + " elements, the output " + std::to_string(cb.n));
-      return nullptr;
-    }
-    // 16-bit float results are rounded to their type after the op.
-    auto round_after = [&]() {
-      if (ov.dtype == DType::kFloat16 || ov.dtype == DType::kBFloat16) {
-        Step r;
-        r.op  = ov.dtype == DType::kFloat16 ? EW_ROUND_F16 : EW_ROUND_BF16;
-        r.f32 = false;
-        rev.push_back(r);
-      }
-    };
-    const bool f32 = cb.Arith(ov.dtype);
-    if (op.type == "cast") {
-      const Value& iv = cb.values[op.inputs[0]];
-      bool ok = false;
-      if (dbl_class) {
-        if (iv.dtype == DType::kFloat64 && ov.dtype == DType::kBool) {
-          ok = true;
-          Step r;
-          r.op  = EW_TO_BOOL;
-          r.f32 = false;
-          rev.push_back(r);
-        } else if (cb.Ok(iv.dtype) && cb.Ok(ov.dtype)) {
-          ok = true;  // bool -> float64 (0 / 1) or the same type
-        } else if (iv.dtype == DType::kFloat64 && ov.dtype == DType::kFloat32) {
-          ok = cur == out.name;  // the store rounds to float32
-        } else if ((iv.dtype == DType::kFloat32 || IsIntType(iv.dtype)) && ov.dtype == DType::kFloat64) {
-          ok = cb.input_index.count(op.inputs[0]) != 0;  // the load of the chain's input converts
-        }
-      } else if (int_class) {
-        if (cb.Ok(iv.dtype) && ov.dtype == DType::kBool && iv.dtype != DType::kBool) {
-          ok = true;
-          Step r;
-          r.op = EW_TO_BOOL;
-          rev.push_back(r);
-        } else if (cb.Ok(iv.dtype) && cb.Ok(ov.dtype)) {
-          ok = true;  // bool -> integer (0 / 1) or the same type
-        } else if (cb.Ok(iv.dtype) && cur == out.name && (IsIntType(ov.dtype) || ov.dtype == DType::kFloat32)) {
-          ok = true;  // the store converts: other integer width, or float32 (to nearest even)
-        } else if ((IsIntType(iv.dtype) || iv.dtype == DType::kBool) && ov.dtype == cb.compute) {
-          ok = cb.input_index.count(op.inputs[0]) != 0;  // the load of the chain's input converts
-        }
-      } else if (IsFloatType(iv.dtype) && IsFloatType(ov.dtype)) {
-        ok = true;
-        round_after();  // widening casts are exact and need no step
-      } else if (iv.dtype == DType::kBool && (IsFloatType(ov.dtype) || ov.dtype == DType::kBool)) {
-        ok = true;      // 0 / 1 are exact in every float type
-      } else if (cb.Ok(iv.dtype) && ov.dtype == DType::kBool) {
-        ok = true;
-        Step r;
-        r.op = EW_TO_BOOL;
-        r.f32 = false;
-        rev.push_back(r);
-      } else if (cb.Ok(iv.dtype) && IsIntType(ov.dtype)) {
-        ok = cur == out.name;  // float -> integer only as the last op: the store converts (toward zero)
-      } else if (IsIntType(iv.dtype) && ov.dtype == DType::kFloat32) {
-        ok = cb.input_index.count(op.inputs[0]) != 0;  // integer -> float32 only on the chain's input: the load converts
-      }
-      if (!ok) {
-        cb.Fail("cast from " + std::string(DTypeName(iv.dtype)) + " to " + DTypeName(ov.dtype) + " is not supported at this place of a chain");
-        return nullptr;
-      }
-      cur = op.inputs[0];
-    } else if (op.type == "scale" && int_class) {
-      cb.Fail("scale on integers has no prebuilt kernel");
-      return nullptr;
-    } else if (op.type == "scale") {
-      float s = 0.0f, b = 0.0f;
-      if (!cb.Imm(ChainBuilder::Attr(op, "scale", "1"), &s) || !cb.Imm(ChainBuilder::Attr(op, "bias", "0"), &b)) {
-        cb.Fail("too many distinct constants for one chain");
-        return nullptr;
-      }
-      const std::string bas = ChainBuilder::Attr(op, "bias_after_scale", "true");
-      const bool after      = bas == "true" || bas == "1" || bas == "True";
-      round_after();
-      Step mul, add;
-      mul.op = EW_MUL; mul.imm = s; mul.f32 = f32;
-      add.op = EW_ADD; add.imm = b; add.f32 = f32;
-      // reverse order: the step executed last is pushed first
-      if (after) { rev.push_back(add); rev.push_back(mul); }
-      else { rev.push_back(mul); rev.push_back(add); }
-      cur = op.inputs[0];
-    } else if (cb.Unary().count(op.type)) {
-      if (!cb.Ok(cb.values[op.inputs[0]].dtype)) {
-        cb.Fail("op '" + op.type + "' on a " + DTypeName(cb.values[op.inputs[0]].dtype) + " value does not fit this form of chain");
-        return nullptr;
-      }
-      round_after();
-      if (op.type != "identity") {
-        Step s;
-        s.op  = cb.Unary().at(op.type);
-        s.f32 = f32;
-        if (op.type == "relu6") cb.Imm(ChainBuilder::Attr(op, "threshold", "6"), &s.imm);
-        if (s.op == EW_RELU && int_class) {  // max(x, 0) with an integer zero
-          s.op = EW_MAX;
-          cb.Imm("0", &s.imm);
-        }
-        rev.push_back(s);
-      }
-      cur = op.inputs[0];
-    } else if (cb.Binary().count(op.type)) {
-      const std::string &a = op.inputs[0], &b = op.inputs[1];
-      const bool ca = cb.InGroupComputed(a), cbb = cb.InGroupComputed(b);
-      Step s;
-      s.op  = cb.Binary().at(op.type);
-      s.f32 = cb.Arith(cb.values[a].dtype);
-      std::string next;
-      if (ca && cbb) {
-        // Both computed in the group: only the "value with itself" form is a chain.
-        if (cb.IsSameAs(b, a)) { next = a; s.asel = 4; }
-        else if (cb.IsSameAs(a, b)) { next = b; s.asel = 4; s.swap = true; }
-        else {
-          cb.Fail("op '" + op.type + "' combines two values computed in the group (a tree, not a chain)");
-          return nullptr;
-        }
-      } else {
-        bool chain_is_a;
-        if (ca) chain_is_a = true;
-        else if (cbb) chain_is_a = false;
-        else {
-          // Neither operand is computed in the group: the chain starts at the full-size group input.
-          const bool a_full = cb.input_index.count(a) && cb.values[a].numel() == cb.n;
-          const bool b_full = cb.input_index.count(b) && cb.values[b].numel() == cb.n;
-          if (!a_full && !b_full) {
-            cb.Fail("op '" + op.type + "' has no full-size operand to start the chain from");
-            return nullptr;
-          }
-          chain_is_a = a_full;
-        }
-        next                     = chain_is_a ? a : b;
-        const std::string& other = chain_is_a ? b : a;
-        if (cb.IsSameAs(other, next)) {
-          s.asel = 4;
-        } else if (!cb.ResolveOperand(other, op, &s.asel, &s.imm)) {
-          cb.Fail("operand '" + other + "' of '" + op.type + "' is neither a broadcastable group input nor a constant");
-          return nullptr;
-        }
-        s.swap = !chain_is_a;  // the side operand is the LEFT operand
-      }
-      if (!cb.Ok(cb.values[a].dtype) || !cb.Ok(cb.values[b].dtype)) {
-        cb.Fail("op '" + op.type + "' on " + DTypeName(cb.values[a].dtype) + " operands does not fit this form of chain");
-        return nullptr;
-      }
-      round_after();
-      rev.push_back(s);
-      cur = next;
-    } else if (op.type == "select") {
-      // One of the three operands continues the chain; the other two are inputs, constants or the chain value.
-      int chain_pos = -1;
-      for (int k = 0; k < 3 && chain_pos < 0; ++k)
-        if (cb.InGroupComputed(op.inputs[k])) chain_pos = k;
-      for (int k = 0; k < 3; ++k)
-        if (cb.InGroupComputed(op.inputs[k]) && k != chain_pos && !cb.IsSameAs(op.inputs[k], op.inputs[chain_pos])) {
-          cb.Fail("select combines two values computed in the group (a tree, not a chain)");
-          return nullptr;
-        }
-      if (chain_pos < 0) {
-        for (int k : {1, 2, 0})
-          if (chain_pos < 0 && cb.input_index.count(op.inputs[k]) && cb.values[op.inputs[k]].numel() == cb.n &&
-              cb.Ok(cb.values[op.inputs[k]].dtype))
-            chain_pos = k;
-        if (chain_pos < 0) {
-          cb.Fail("select has no full-size operand to start the chain from");
-          return nullptr;
-        }
-      }
-      Step s;
-      s.op   = EW_SELECT;
-      s.role = chain_pos;
-      s.f32  = false;
-      // operand A / B by role: role 0 -> (true, false); role 1 -> (cond, false); role 2 -> (cond, true)
-      const int a_pos = chain_pos == 0 ? 1 : 0, b_pos = chain_pos == 2 ? 1 : 2;
-      const std::string& chain = op.inputs[chain_pos];
-      auto resolve = [&](int pos, int* sel, float* imm) {
-        const std::string& nm = op.inputs[pos];
-        if (!cb.Ok(cb.values[nm].dtype)) return false;
-        if (cb.IsSameAs(nm, chain)) { *sel = 4; return true; }
-        return cb.ResolveOperand(nm, op, sel, imm);
-      };
-      if (!cb.Ok(cb.values[chain].dtype) || !resolve(a_pos, &s.asel, &s.imm) || !resolve(b_pos, &s.bsel, &s.imm2)) {
-        cb.Fail("an operand of select is neither a broadcastable group input nor a constant");
-        return nullptr;
-      }
-      round_after();
-      rev.push_back(s);
-      cur = chain;
-    } else if (op.type == "fill_constant") {
-      // The chain starts from a constant (EW_COPY of an immediate): no operand at all at this end.
-      Step s;
-      s.op   = EW_COPY;
-      s.asel = 0;
-      s.f32  = false;
-      if (!cb.Imm(ChainBuilder::Attr(op, "value", "0"), &s.imm)) {
-        cb.Fail("constant does not fit an immediate");
-        return nullptr;
-      }
-      rev.push_back(s);
-      starts_from_operand = true;
-      break;
-    } else if (op.type == "broadcast_to" && cb.input_index.count(op.inputs[0])) {
-      // No operand has the output's size: the chain starts from this broadcast operand (EW_COPY).
+  // Walk back from a value collecting primitive steps in reverse order.  A segment is one such walk: the main one
+  // starts at the output; a binary op whose operands are BOTH computed in the group (a tree) makes the walk of one
+  // operand a segment of its own, which runs first and leaves its value in a temporary (float form only, at most
+  // two temporaries per group).
+  struct Segment {
+    std::vector<Step> rev;
+    bool starts_from_operand = false;
+    std::string end;  // the value the walk stopped at (a group input unless starts_from_operand)
+  };
+  std::vector<Segment> segments;  // finished sub-segments, in program order
+  int temps_used = 0;
+  std::map<std::string, int> uses;
+  for (auto& o : g.ops)
+    for (auto& in : o.inputs) ++uses[in];
+  auto single_use_mul = [&](const std::string& v) {
+    const OpDesc* q = cb.producer.count(v) ? cb.producer[v] : nullptr;
+    return q && q->type == "elementwise_mul" && uses[v] == 1 && cb.Arith(cb.values[v].dtype);
+  };
+  // Where a segment starts: a broadcast operand / constant (EW_COPY already pushed), a smaller group input that
+  // broadcasts by the binary ops' own rule, or a full-size group input.  Only the first segment of the program finds
+  // its full-size input preloaded in the chain value; the others copy it from a side operand.
+  auto finish_start = [&](Segment* seg, bool first) -> bool {
+    const std::string& cur = seg->end;
+    if (!seg->starts_from_operand && cb.input_index.count(cur) && (cb.values[cur].numel() != cb.n || !first) && Ok2(cb, cb.values[cur].dtype)) {
       Step s;
       s.op  = EW_COPY;
       s.f32 = false;
-      if (!cb.ResolveOperand(cur, op, &s.asel, &s.imm)) {
-        cb.Fail("the broadcast of '" + op.inputs[0] + "' cannot be addressed as a chain operand");
-        return nullptr;
+      OpDesc fake;
+      fake.type = "elementwise_add";
+      if (cb.ResolveOperand(cur, fake, &s.asel, &s.imm)) {
+        seg->rev.push_back(s);
+        seg->starts_from_operand = true;
       }
-      rev.push_back(s);
-      starts_from_operand = true;
-      break;
-    } else {
-      cb.Fail("op '" + op.type + "' cannot be part of an elementwise chain");
-      return nullptr;
     }
-  }
-  if (!starts_from_operand && cb.input_index.count(cur) && cb.values[cur].numel() != cb.n && Ok2(cb, cb.values[cur].dtype)) {
-    // A group input smaller than the output that broadcasts by the binary ops' own rule (e.g. bias + scalar).
-    Step s;
-    s.op  = EW_COPY;
-    s.f32 = false;
-    OpDesc fake;
-    fake.type = "elementwise_add";
-    if (cb.ResolveOperand(cur, fake, &s.asel, &s.imm)) {
-      rev.push_back(s);
-      starts_from_operand = true;
+    if (!seg->starts_from_operand && (!cb.input_index.count(cur) || cb.values[cur].numel() != cb.n)) {
+      cb.Fail("the chain does not start at a full-size group input");
+      return false;
     }
-  }
-  if (!starts_from_operand && (!cb.input_index.count(cur) || cb.values[cur].numel() != cb.n)) {
-    cb.Fail("the chain does not start at a full-size group input");
-    return nullptr;
-  }
+    if (!seg->starts_from_operand && !first) {
+      cb.Fail("too many operands for a second branch of the expression");
+      return false;
+    }
+    return true;
+  };
+  std::function<bool(std::string, Segment*)> walk = [&](std::string cur, Segment* seg) -> bool {
+    std::vector<Step>& rev    = seg->rev;
+    bool& starts_from_operand = seg->starts_from_operand;
+    while (cb.producer.count(cur)) {
+      const OpDesc& op = *cb.producer[cur];
+      const Value& ov  = cb.values[cur];
+      if (ov.numel() != cb.n) {
+        cb.Fail("value '" + cur + "' on the chain has " + std::to_string(ov.numel()) + " elements, the output " + std::to_string(cb.n));
+        return false;
+      }
+      // 16-bit float results are rounded to their type after the op.
+      auto round_after = [&]() {
+        if (ov.dtype == DType::kFloat16 || ov.dtype == DType::kBFloat16) {
+          Step r;
+          r.op  = ov.dtype == DType::kFloat16 ? EW_ROUND_F16 : EW_ROUND_BF16;
+          r.f32 = false;
+          rev.push_back(r);
+        }
+      };
+      const bool f32 = cb.Arith(ov.dtype);
+      if (op.type == "cast") {
+        const Value& iv = cb.values[op.inputs[0]];
+        bool ok = false;
+        if (dbl_class) {
+          if (iv.dtype == DType::kFloat64 && ov.dtype == DType::kBool) {
+            ok = true;
+            Step r;
+            r.op  = EW_TO_BOOL;
+            r.f32 = false;
+            rev.push_back(r);
+          } else if (cb.Ok(iv.dtype) && cb.Ok(ov.dtype)) {
+            ok = true;  // bool -> float64 (0 / 1) or the same type
+          } else if (iv.dtype == DType::kFloat64 && ov.dtype == DType::kFloat32) {
+            ok = cur == out.name;  // the store rounds to float32
+          } else if ((iv.dtype == DType::kFloat32 || IsIntType(iv.dtype)) && ov.dtype == DType::kFloat64) {
+            ok = cb.input_index.count(op.inputs[0]) != 0;  // the load of the chain's input converts
+          }
+        } else if (int_class) {
+          if (cb.Ok(iv.dtype) && ov.dtype == DType::kBool && iv.dtype != DType::kBool) {
+            ok = true;
+            Step r;
+            r.op = EW_TO_BOOL;
+            rev.push_back(r);
+          } else if (cb.Ok(iv.dtype) && cb.Ok(ov.dtype)) {
+            ok = true;  // bool -> integer (0 / 1) or the same type
+          } else if (cb.Ok(iv.dtype) && cur == out.name && (IsIntType(ov.dtype) || ov.dtype == DType::kFloat32)) {
+            ok = true;  // the store converts: other integer width, or float32 (to nearest even)
+          } else if ((IsIntType(iv.dtype) || iv.dtype == DType::kBool) && ov.dtype == cb.compute) {
+            ok = cb.input_index.count(op.inputs[0]) != 0;  // the load of the chain's input converts
+          }
+        } else if (IsFloatType(iv.dtype) && IsFloatType(ov.dtype)) {
+          ok = true;
+          round_after();  // widening casts are exact and need no step
+        } else if (iv.dtype == DType::kBool && (IsFloatType(ov.dtype) || ov.dtype == DType::kBool)) {
+          ok = true;      // 0 / 1 are exact in every float type
+        } else if (cb.Ok(iv.dtype) && ov.dtype == DType::kBool) {
+          ok = true;
+          Step r;
+          r.op = EW_TO_BOOL;
+          r.f32 = false;
+          rev.push_back(r);
+        } else if (cb.Ok(iv.dtype) && IsIntType(ov.dtype)) {
+          ok = cur == out.name;  // float -> integer only as the last op: the store converts (toward zero)
+        } else if (IsIntType(iv.dtype) && ov.dtype == DType::kFloat32) {
+          ok = cb.input_index.count(op.inputs[0]) != 0;  // integer -> float32 only on the chain's input: the load converts
+        }
+        if (!ok) {
+          cb.Fail("cast from " + std::string(DTypeName(iv.dtype)) + " to " + DTypeName(ov.dtype) + " is not supported at this place of a chain");
+          return false;
+        }
+        cur = op.inputs[0];
+      } else if (op.type == "scale" && int_class) {
+        cb.Fail("scale on integers has no prebuilt kernel");
+        return false;
+      } else if (op.type == "scale") {
+        float s = 0.0f, b = 0.0f;
+        if (!cb.Imm(ChainBuilder::Attr(op, "scale", "1"), &s) || !cb.Imm(ChainBuilder::Attr(op, "bias", "0"), &b)) {
+          cb.Fail("too many distinct constants for one chain");
+          return false;
+        }
+        const std::string bas = ChainBuilder::Attr(op, "bias_after_scale", "true");
+        const bool after      = bas == "true" || bas == "1" || bas == "True";
+        round_after();
+        Step mul, add;
+        mul.op = EW_MUL; mul.imm = s; mul.f32 = f32;
+        add.op = EW_ADD; add.imm = b; add.f32 = f32;
+        // reverse order: the step executed last is pushed first
+        if (after) { rev.push_back(add); rev.push_back(mul); }
+        else { rev.push_back(mul); rev.push_back(add); }
+        cur = op.inputs[0];
+      } else if (cb.Unary().count(op.type)) {
+        if (!cb.Ok(cb.values[op.inputs[0]].dtype)) {
+          cb.Fail("op '" + op.type + "' on a " + DTypeName(cb.values[op.inputs[0]].dtype) + " value does not fit this form of chain");
+          return false;
+        }
+        round_after();
+        if (op.type != "identity") {
+          Step s;
+          s.op  = cb.Unary().at(op.type);
+          s.f32 = f32;
+          if (op.type == "relu6") cb.Imm(ChainBuilder::Attr(op, "threshold", "6"), &s.imm);
+          if (s.op == EW_RELU && int_class) {  // max(x, 0) with an integer zero
+            s.op = EW_MAX;
+            cb.Imm("0", &s.imm);
+          }
+          rev.push_back(s);
+        }
+        cur = op.inputs[0];
+      } else if (cb.Binary().count(op.type)) {
+        const std::string &a = op.inputs[0], &b = op.inputs[1];
+        const bool ca = cb.InGroupComputed(a), cbb = cb.InGroupComputed(b);
+        Step s;
+        s.op  = cb.Binary().at(op.type);
+        s.f32 = cb.Arith(cb.values[a].dtype);
+        std::string next;
+        if (ca && cbb) {
+          // Both computed in the group: only the "value with itself" form is a chain.
+          if (cb.IsSameAs(b, a)) { next = a; s.asel = 4; }
+          else if (cb.IsSameAs(a, b)) { next = b; s.asel = 4; s.swap = true; }
+          else if (!int_class && !dbl_class && temps_used < 2 && cb.values[a].numel() == cb.n && cb.values[b].numel() == cb.n) {
+            // A tree: one operand is walked as a segment of its own, which runs first and is stashed in a temporary;
+            // the other continues this walk.  For a float32 add the operand that continues is the product the
+            // reference contracts into a fused multiply-add (the right one first, cinn/optim/lower_intrin.cc:45-50),
+            // so that the Mul and the Add end up adjacent.
+            bool chain_is_a = true;
+            if (s.op == EW_ADD && s.f32) {
+              if (single_use_mul(b)) chain_is_a = false;
+              else if (single_use_mul(a)) chain_is_a = true;
+            }
+            const std::string sub = chain_is_a ? b : a;
+            const int t           = temps_used++;
+            Segment sg;
+            if (!walk(sub, &sg)) return false;
+            if (!finish_start(&sg, segments.empty())) return false;
+            Step st;
+            st.op   = EW_STASH;
+            st.asel = 5 + t;
+            st.f32  = false;
+            sg.rev.insert(sg.rev.begin(), st);  // executed last in its segment
+            segments.push_back(sg);
+            next   = chain_is_a ? a : b;
+            s.asel = 5 + t;
+            s.swap = !chain_is_a;
+          } else {
+            cb.Fail("op '" + op.type + "' combines two values computed in the group (a tree, not a chain)");
+            return false;
+          }
+        } else {
+          bool chain_is_a;
+          if (ca) chain_is_a = true;
+          else if (cbb) chain_is_a = false;
+          else {
+            // Neither operand is computed in the group: the chain starts at the full-size group input.
+            const bool a_full = cb.input_index.count(a) && cb.values[a].numel() == cb.n;
+            const bool b_full = cb.input_index.count(b) && cb.values[b].numel() == cb.n;
+            if (!a_full && !b_full) {
+              cb.Fail("op '" + op.type + "' has no full-size operand to start the chain from");
+              return false;
+            }
+            chain_is_a = a_full;
+          }
+          next                     = chain_is_a ? a : b;
+          const std::string& other = chain_is_a ? b : a;
+          if (cb.IsSameAs(other, next)) {
+            s.asel = 4;
+          } else if (!cb.ResolveOperand(other, op, &s.asel, &s.imm)) {
+            cb.Fail("operand '" + other + "' of '" + op.type + "' is neither a broadcastable group input nor a constant");
+            return false;
+          }
+          s.swap = !chain_is_a;  // the side operand is the LEFT operand
+        }
+        if (!cb.Ok(cb.values[a].dtype) || !cb.Ok(cb.values[b].dtype)) {
+          cb.Fail("op '" + op.type + "' on " + DTypeName(cb.values[a].dtype) + " operands does not fit this form of chain");
+          return false;
+        }
+        s.single_use = uses[op.output] <= 1;
+        round_after();
+        rev.push_back(s);
+        cur = next;
+      } else if (op.type == "select") {
+        // One of the three operands continues the chain; the other two are inputs, constants or the chain value.
+        int chain_pos = -1;
+        for (int k = 0; k < 3 && chain_pos < 0; ++k)
+          if (cb.InGroupComputed(op.inputs[k])) chain_pos = k;
+        for (int k = 0; k < 3; ++k)
+          if (cb.InGroupComputed(op.inputs[k]) && k != chain_pos && !cb.IsSameAs(op.inputs[k], op.inputs[chain_pos])) {
+            cb.Fail("select combines two values computed in the group (a tree, not a chain)");
+            return false;
+          }
+        if (chain_pos < 0) {
+          for (int k : {1, 2, 0})
+            if (chain_pos < 0 && cb.input_index.count(op.inputs[k]) && cb.values[op.inputs[k]].numel() == cb.n &&
+                cb.Ok(cb.values[op.inputs[k]].dtype))
+              chain_pos = k;
+          if (chain_pos < 0) {
+            cb.Fail("select has no full-size operand to start the chain from");
+            return false;
+          }
+        }
+        Step s;
+        s.op   = EW_SELECT;
+        s.role = chain_pos;
+        s.f32  = false;
+        // operand A / B by role: role 0 -> (true, false); role 1 -> (cond, false); role 2 -> (cond, true)
+        const int a_pos = chain_pos == 0 ? 1 : 0, b_pos = chain_pos == 2 ? 1 : 2;
+        const std::string& chain = op.inputs[chain_pos];
+        auto resolve = [&](int pos, int* sel, float* imm) {
+          const std::string& nm = op.inputs[pos];
+          if (!cb.Ok(cb.values[nm].dtype)) return false;
+          if (cb.IsSameAs(nm, chain)) { *sel = 4; return true; }
+          return cb.ResolveOperand(nm, op, sel, imm);
+        };
+        if (!cb.Ok(cb.values[chain].dtype) || !resolve(a_pos, &s.asel, &s.imm) || !resolve(b_pos, &s.bsel, &s.imm2)) {
+          cb.Fail("an operand of select is neither a broadcastable group input nor a constant");
+          return false;
+        }
+        round_after();
+        rev.push_back(s);
+        cur = chain;
+      } else if (op.type == "fill_constant") {
+        // The chain starts from a constant (EW_COPY of an immediate): no operand at all at this end.
+        Step s;
+        s.op   = EW_COPY;
+        s.asel = 0;
+        s.f32  = false;
+        if (!cb.Imm(ChainBuilder::Attr(op, "value", "0"), &s.imm)) {
+          cb.Fail("constant does not fit an immediate");
+          return false;
+        }
+        rev.push_back(s);
+        starts_from_operand = true;
+        break;
+      } else if (op.type == "broadcast_to" && cb.input_index.count(op.inputs[0])) {
+        // No operand has the output's size: the chain starts from this broadcast operand (EW_COPY).
+        Step s;
+        s.op  = EW_COPY;
+        s.f32 = false;
+        if (!cb.ResolveOperand(cur, op, &s.asel, &s.imm)) {
+          cb.Fail("the broadcast of '" + op.inputs[0] + "' cannot be addressed as a chain operand");
+          return false;
+        }
+        rev.push_back(s);
+        starts_from_operand = true;
+        break;
+      } else {
+        cb.Fail("op '" + op.type + "' cannot be part of an elementwise chain");
+        return false;
+      }
+    }
+    seg->end = cur;
+    return true;
+  };
+  Segment main_seg;
+  if (!walk(out.name, &main_seg)) return nullptr;
+  if (!finish_start(&main_seg, segments.empty())) return nullptr;
+  // Program order: sub-segments (innermost first), then the main walk.
+  std::vector<Step> rev;  // the whole program, reversed
+  rev = main_seg.rev;
+  for (auto it = segments.rbegin(); it != segments.rend(); ++it) rev.insert(rev.end(), it->rev.begin(), it->rev.end());
+  const Segment& first_seg       = segments.empty() ? main_seg : segments.front();
+  const bool starts_from_operand = first_seg.starts_from_operand;
+  std::string cur                = first_seg.end;
   // in0 < 0: no pointer operand at all (a chain of constants); the output pointer fills the unused slots.
   const int in0       = starts_from_operand ? (cb.sides.empty() ? -1 : cb.sides[0].input) : cb.input_index[cur];
   const DType in_type = in0 >= 0 ? g.inputs[in0].dtype
@@ -710,7 +776,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   std::vector<uint64_t> words;
   for (size_t i = 0; i < steps.size(); ++i) {
     const Step& s = steps[i];
-    if (!int_class && s.op == EW_MUL && s.f32 && i + 1 < steps.size() && steps[i + 1].op == EW_ADD && steps[i + 1].f32 &&
+    if (!int_class && s.op == EW_MUL && s.f32 && s.single_use && i + 1 < steps.size() && steps[i + 1].op == EW_ADD && steps[i + 1].f32 &&
         steps[i + 1].asel != 4) {
       const Step& a = steps[i + 1];
       words.push_back(Word(EW_FMA, s.asel, a.asel, 0, s.imm));
@@ -741,7 +807,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   for (auto& t : g.inputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
   p->algorithmic_bytes += out.numel() * DTypeBytes(out.dtype);
   LaunchStep st;
-  const std::string ns = std::string("_s") + (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3"));
+  const std::string ns = temps_used > 0 ? "_s3t" : std::string("_s") + (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3"));
   st.kernel = FindKernel(int_class ? std::string("ew_chain_int_") + DTypeKernelName(cb.compute) + "_" + DTypeKernelName(out.dtype) + ns
                          : dbl_class ? std::string("ew_chain_f64_") + DTypeKernelName(out.dtype) + ns
                                      : std::string("ew_chain_") + DTypeKernelName(out.dtype) + ns);
@@ -903,7 +969,8 @@ std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const Device
   }
   // Re-target the chain's launch: same 31 parameters (the program, the side operands), reduce geometry appended.
   LaunchStep st    = plan->steps[0];
-  const std::string ns = std::string(st.kernel->name).substr(std::string(st.kernel->name).size() - 3);  // "_s0" / "_s1" / "_s3"
+  const std::string kname = st.kernel->name;
+  const std::string ns    = kname.substr(kname.rfind('_'));  // "_s0" / "_s1" / "_s3" / "_s3t"
   auto int_arg = [](int64_t v) { ArgSpec a; a.kind = ArgSpec::kInt; a.ivalue = v; return a; };
   const int kOut = 4, kAligned = 6, kMeta = 7;
   const int64_t out_code = out.dtype == DType::kFloat16 ? EW_F16 : (out.dtype == DType::kBFloat16 ? EW_BF16 : EW_F32);

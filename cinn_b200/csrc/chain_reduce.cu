@@ -57,7 +57,7 @@ __device__ __forceinline__ void cr_store(void* out, int out_type, long long idx,
   const SideSpec sd3 = {p3, (int)((meta >> 16) & 15), (int)((meta >> 20) & 15), mid3, inner3}
 
 // The chain's values of VEC consecutive elements starting at flat input index i0.
-template <int VEC, int NS>
+template <int VEC, int NS, int NT>
 __device__ __forceinline__ void chain_values(const void* in0, int in_type, const SideSpec& sd1, const SideSpec& sd2,
                                              const SideSpec& sd3, const long long* steps, int nsteps, long long i0,
                                              float (&acc)[VEC]) {
@@ -70,10 +70,11 @@ __device__ __forceinline__ void chain_values(const void* in0, int in_type, const
   if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<VEC>(sd1, i0, s1);
   if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<VEC>(sd2, i0, s2);
   if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<VEC>(sd3, i0, s3);
-  run_chain<VEC, NS>(steps, nsteps, s1, s2, s3, acc);
+  run_chain<VEC, NS, NT>(steps, nsteps, s1, s2, s3, acc);
 }
 
-// Two vectors whose loads are all issued before the program runs once over the eight values.
+// Two vectors whose loads are all issued before the program runs once over the eight values (kernels without
+// temporaries only).
 template <int NS>
 __device__ __forceinline__ void chain_values2(const void* in0, int in_type, const SideSpec& sd1, const SideSpec& sd2,
                                               const SideSpec& sd3, const long long* steps, int nsteps, long long ia,
@@ -98,7 +99,7 @@ __device__ __forceinline__ void chain_values2(const void* in0, int in_type, cons
 // cut (the matcher passes rows * S and r / S): a segment is just a shorter row of the same flat index space.
 // Occupancy, measured on B200 with sum(|x - y|) over 8192 x 8192 (one side operand): 4 CTAs per SM (64 registers, a
 // few spilled words) 0.70 of the HBM peak; 3 CTAs (80 registers, no spills) 0.61; 5 CTAs (48 registers) 0.57.
-template <int NS>
+template <int NS, int NT = 0>
 __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
     k_chain_reduce_row(CHAIN_PARAMS, long long rows, long long r, long long group) {
   CHAIN_PROLOGUE;
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
     if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary
       const long long nv = r >> 2;
       long long v        = t;
-      for (; v + nt < nv; v += 2 * nt) {
+      for (; NT == 0 && v + nt < nv; v += 2 * nt) {
         float acc[8];
         chain_values2<NS>(in0, in_type, sd1, sd2, sd3, steps, nsteps, base + (v << 2), base + ((v + nt) << 2), acc);
 #pragma unroll
@@ -124,7 +125,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
       }
       for (; v < nv; v += nt) {
         float acc[4];
-        chain_values<4, NS>(in0, in_type, sd1, sd2, sd3, steps, nsteps, base + (v << 2), acc);
+        chain_values<4, NS, NT>(in0, in_type, sd1, sd2, sd3, steps, nsteps, base + (v << 2), acc);
 #pragma unroll
         for (int i = 0; i < 4; ++i) a[i] = cr_apply(rop, a[i], acc[i]);
       }
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
     }
     for (long long j = done + t; j < r; j += nt) {
       float acc[1];
-      chain_values<1, NS>(in0, in_type, sd1, sd2, sd3, steps, nsteps, base + j, acc);
+      chain_values<1, NS, NT>(in0, in_type, sd1, sd2, sd3, steps, nsteps, base + j, acc);
       a[0] = cr_apply(rop, a[0], acc[0]);
     }
     float v = cr_apply(rop, cr_apply(rop, a[0], a[1]), cr_apply(rop, a[2], a[3]));
@@ -157,7 +158,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
 // ---- columns: y[o, c] = fold over k of f(x[(o * r + k) * inner + c]) -----------------------------------------------
 // blockIdx.y = o, blockIdx.z = segment of the reduced axis (rows_per_split rows each; segment s of o writes
 // out[(s * outer + o) * inner + c], so that a second launch folds the segments as rows of one matrix).
-template <int NS>
+template <int NS, int NT = 0>
 __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
     k_chain_reduce_col(CHAIN_PARAMS, long long outer, long long r, long long inner, long long rows_per_split) {
   CHAIN_PROLOGUE;
@@ -171,7 +172,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
     for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < nc; c += (long long)gridDim.x * blockDim.x) {
       float a[4] = {id, id, id, id};
       long long k = k0;
-      for (; k + 2 <= k1; k += 2) {
+      for (; NT == 0 && k + 2 <= k1; k += 2) {
         float acc[8];
         const long long ia = (o * r + k) * inner + (c << 2);
         chain_values2<NS>(in0, in_type, sd1, sd2, sd3, steps, nsteps, ia, ia + inner, acc);
@@ -180,7 +181,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
       }
       for (; k < k1; ++k) {
         float acc[4];
-        chain_values<4, NS>(in0, in_type, sd1, sd2, sd3, steps, nsteps, (o * r + k) * inner + (c << 2), acc);
+        chain_values<4, NS, NT>(in0, in_type, sd1, sd2, sd3, steps, nsteps, (o * r + k) * inner + (c << 2), acc);
 #pragma unroll
         for (int i = 0; i < 4; ++i) a[i] = cr_apply(rop, a[i], acc[i]);
       }
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
       float a = id;
       for (long long k = k0; k < k1; ++k) {
         float acc[1];
-        chain_values<1, NS>(in0, in_type, sd1, sd2, sd3, steps, nsteps, (o * r + k) * inner + c, acc);
+        chain_values<1, NS, NT>(in0, in_type, sd1, sd2, sd3, steps, nsteps, (o * r + k) * inner + c, acc);
         a = cr_apply(rop, a, acc[0]);
       }
       cr_store(out, out_type, ybase + c, a);
@@ -205,8 +206,10 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
 CINN_B200_REGISTER_KERNEL("chain_reduce_row_s0", 34, 256, k_chain_reduce_row<0>);
 CINN_B200_REGISTER_KERNEL("chain_reduce_row_s1", 34, 256, k_chain_reduce_row<1>);
 CINN_B200_REGISTER_KERNEL("chain_reduce_row_s3", 34, 256, k_chain_reduce_row<3>);
+CINN_B200_REGISTER_KERNEL("chain_reduce_row_s3t", 34, 256, k_chain_reduce_row<3, 2>);
 CINN_B200_REGISTER_KERNEL("chain_reduce_col_s0", 35, 256, k_chain_reduce_col<0>);
 CINN_B200_REGISTER_KERNEL("chain_reduce_col_s1", 35, 256, k_chain_reduce_col<1>);
 CINN_B200_REGISTER_KERNEL("chain_reduce_col_s3", 35, 256, k_chain_reduce_col<3>);
+CINN_B200_REGISTER_KERNEL("chain_reduce_col_s3t", 35, 256, k_chain_reduce_col<3, 2>);
 
 }  // namespace cinn_b200

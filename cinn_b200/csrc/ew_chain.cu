@@ -17,7 +17,9 @@ namespace cinn_b200 {
 namespace {
 
 // meta: bits 0-3 dtype of side 1, 4-7 mode of side 1, 8-11 / 12-15 side 2, 16-19 / 20-23 side 3, 24-27 dtype of in0.
-template <typename OutT, int NS>
+// NT = 2: the variant with two temporaries for expression trees; it takes one vector per iteration so that the
+// temporaries fit the same register budget.
+template <typename OutT, int NS, int NT = 0>
 __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
     k_ew_chain(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
                const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
@@ -39,7 +41,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
     // Two vectors (8 elements) per thread iteration: all of their loads are issued before the program runs,
     // and one pass of the interpreter serves the eight elements.
     long long v = tid;
-    for (; v + stride < nvec; v += 2 * stride) {
+    for (; NT == 0 && v + stride < nvec; v += 2 * stride) {
       float acc[8], s1[8], s2[8], s3[8];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
@@ -52,7 +54,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
         if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, *reinterpret_cast<float(*)[4]>(&s2[4 * j]));
         if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, *reinterpret_cast<float(*)[4]>(&s3[4 * j]));
       }
-      run_chain<8, NS>(steps, nsteps, s1, s2, s3, acc);
+      run_chain<8, NS, 0>(steps, nsteps, s1, s2, s3, acc);
 #pragma unroll
       for (int j = 0; j < 2; ++j)
         store_vec4<OutT>(out, (v + j * stride) << 2, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
       if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
       if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
       if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
-      run_chain<4, NS>(steps, nsteps, s1, s2, s3, acc);
+      run_chain<4, NS, NT>(steps, nsteps, s1, s2, s3, acc);
       store_vec4<OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -75,7 +77,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
     if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
     if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
     if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
-    run_chain<1, NS>(steps, nsteps, s1, s2, s3, acc);
+    run_chain<1, NS, NT>(steps, nsteps, s1, s2, s3, acc);
     store_one<OutT>(out, i, acc[0]);
   }
 }
@@ -85,7 +87,8 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
 #define REG_CHAIN(OUTNAME, OutT)                                                               \
   CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s0", 31, 256, k_ew_chain<OutT, 0>);        \
   CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s1", 31, 256, k_ew_chain<OutT, 1>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3", 31, 256, k_ew_chain<OutT, 3>)
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3", 31, 256, k_ew_chain<OutT, 3>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3t", 31, 256, k_ew_chain<OutT, 3, 2>)
 REG_CHAIN("f32", float);
 REG_CHAIN("f16", __half);
 REG_CHAIN("bf16", __nv_bfloat16);

@@ -6,6 +6,8 @@
 // bits 24-25 "swap" for a binary op (1: the side operand is the LEFT operand) or, for EW_SELECT, the role of the
 // chain value (0: the condition, A = value if true, B = value if false; 1: the value if true, A = condition,
 // B = value if false; 2: the value if false, A = condition, B = value if true), bits 32-63 an fp32 immediate.
+// Operand selectors 5 and 6 name two temporaries (float form only): EW_STASH copies the chain value into the
+// temporary its A selector names, so that an expression tree runs as: first branch, stash, second branch, join.
 // Values of type bool travel as 0.0f / 1.0f.  The integer form of the kernel (ew_chain_int.cu) uses the same words
 // with a signed 32-bit integer in bits 32-63; bool travels as 0 / 1.  The float64 form (ew_chain_f64.cu) keeps in
 // bits 32-63 an index into a table of eight double immediates.
@@ -24,6 +26,7 @@ enum EwOp {
   // integer chains only
   EW_BAND = 23, EW_BOR, EW_BXOR, EW_SHL, EW_SHR, EW_LSHR,
   EW_COPY = 29,  // acc = operand: how a chain starts from a broadcast operand when no input has the output's size
+  EW_STASH = 30, // temporary[A - 5] = acc (kernels with temporaries only)
   EW_FMA = 20,        // acc = fma(acc, A, B)
   EW_SCALE_PRE = 21,  // acc = imm * (acc + imm_next)
   EW_SELECT = 22,     // acc = cond ? t : f, see the role bits above

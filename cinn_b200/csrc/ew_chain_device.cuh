@@ -262,9 +262,15 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, float
 }
 
 // NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
-template <int VEC, int NS>
+// NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees.
+template <int VEC, int NS, int NT = 0>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const float (&s1)[VEC],
                                           const float (&s2)[VEC], const float (&s3)[VEC], float (&acc)[VEC]) {
+  float ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
+  if (NT > 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0.0f;
+  }
   for (int k = 0; k < nsteps; ++k) {
     const long long st = steps[k];
     const int op       = (int)(st & 0xff);
@@ -278,8 +284,26 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       apply_unary<VEC>(op, imm, acc);
       continue;
     }
+    if (NT > 0 && op == EW_STASH) {
+      if (asel == 5) {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) ta[NT > 0 ? i : 0] = acc[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) tb[NT > 0 ? i : 0] = acc[i];
+      }
+      continue;
+    }
     float o[VEC];
     switch (asel) {  // one uniform branch per step instead of a select chain per element
+      case 5:
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = NT > 0 ? ta[NT > 0 ? i : 0] : imm;
+        break;
+      case 6:
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = NT > 0 ? tb[NT > 0 ? i : 0] : imm;
+        break;
       case 1:
 #pragma unroll
         for (int i = 0; i < VEC; ++i) o[i] = NS >= 1 ? s1[i] : imm;
@@ -306,8 +330,9 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const float b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
-        acc[i]        = fmaf(acc[i], o[i], b);
+        float b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
+        if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
+        acc[i] = fmaf(acc[i], o[i], b);
       }
       if (bsel == 0) ++k;
     } else if (op == EW_SELECT) {
@@ -331,6 +356,14 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
         case 4:
 #pragma unroll
           for (int i = 0; i < VEC; ++i) b[i] = acc[i];
+          break;
+        case 5:
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) b[i] = NT > 0 ? ta[NT > 0 ? i : 0] : imm2;
+          break;
+        case 6:
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) b[i] = NT > 0 ? tb[NT > 0 ? i : 0] : imm2;
           break;
         default:
 #pragma unroll

@@ -303,3 +303,26 @@ def test_bfloat16_storage_picks_bf16_kernels():
         g = cinn_b200.FusedGroup(w.desc.replace("float16", "bfloat16"))
         assert want in g.kernel_names()[0], g.kernel_names()
         g.release()
+
+
+def test_expression_trees_compile_into_one_kernel_with_temporaries():
+    """A binary op whose operands are both computed in the group: one branch runs first and is stashed in a temporary
+    (two temporaries at most, three side operands at most); beyond that the fusion pass splits the group."""
+    def build(n_inputs=4):
+        b = NetBuilder("tree")
+        return b, [b.create_input(common.Float(32), (64, 1024), n) for n in "ABCD"[:n_inputs]]
+    b, (A, B, C, D) = build()
+    b.multiply(b.add(A, B), b.subtract(C, D))
+    assert [p for _, p in plan(b).groups()] == ["ew_chain ew_chain_f32_s3t"]
+    b, (A, B, C, D) = build()
+    b.reduce_max(b.add(b.multiply(A, B), b.multiply(C, D)), [0])
+    assert [p for _, p in plan(b).groups()] == ["chain_col_reduce chain_reduce_col_s3t"]
+    # integer and float64 trees have no kernel with temporaries: two chains and a join
+    b = NetBuilder("tree")
+    I = [b.create_input(common.Int(32), (64, 1024), n) for n in "ABCD"]
+    b.multiply(b.add(I[0], I[1]), b.subtract(I[2], I[3]))
+    assert len(plan(b).groups()) == 2
+    # three joins need three temporaries: split
+    b, (A, B, C, D) = build()
+    b.add(b.multiply(b.exp(A), b.tanh(B)), b.multiply(b.sqrt(b.abs(C)), b.sigmoid(D)))
+    assert len(plan(b).groups()) > 1

@@ -162,15 +162,100 @@ def test_comparison_gives_bool_bit_exact(oracle):
     assert out[str(z)].dtype == np.bool_ and np.array_equal(out[str(z)], X > Y)
 
 
-def test_tree_shaped_expression_is_partitioned_and_correct(oracle):
+def test_tree_shaped_expression_is_one_kernel_and_correct(oracle):
     b = NetBuilder("tree")
     x = b.create_input(common.Float(32), (64, 96), "X")
     y = b.add(b.sqrt(b.abs(x)), b.exp(b.negative(x)))
     X = np.random.default_rng(14).standard_normal((64, 96)).astype(np.float32)
     comp, out = run_program(b, {"X": X}, [y])
-    assert len(comp.groups()) == 2
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s3t"]  # one branch stashed in a temporary
     ref = oracle_program(comp, {"X": X})[str(y)]
     assert oracle.max_ulp(out[str(y)], ref) <= 2
+
+
+TREE_SHAPES = [(64, 1024), (33, 1001), (2048, 4096)]
+
+
+def _four_inputs(b, shape, dtype=32):
+    return [b.create_input(common.Float(dtype), shape, n) for n in "ABCD"]
+
+
+def _tree_cases():
+    def product_of_sum_and_difference(b, A, B, C, D):
+        return b.multiply(b.add(A, B), b.subtract(C, D))
+
+    def sum_of_products(b, A, B, C, D):       # fma(C, D, A * B): the right product is the contracted one
+        return b.add(b.multiply(A, B), b.multiply(C, D))
+
+    def product_plus_chain(b, A, B, C, D):    # fma(A, B, relu(C) - D): the only product is on the left
+        return b.add(b.multiply(A, B), b.subtract(b.relu(C), D))
+
+    def shared_product_is_not_contracted(b, A, B, C, D):
+        m = b.multiply(A, B)                  # two users: materialised by the reference, hence a plain add
+        return b.multiply(b.add(m, C), b.max(m, C))
+
+    def nested(b, A, B, C, D):
+        return b.subtract(b.multiply(b.add(A, B), b.min(A, C)), b.sqrt(b.abs(B)))   # two joins, two temporaries
+    return [product_of_sum_and_difference, sum_of_products, product_plus_chain, shared_product_is_not_contracted, nested]
+
+
+@pytest.mark.parametrize("shape", TREE_SHAPES)
+@pytest.mark.parametrize("case", _tree_cases(), ids=lambda f: f.__name__)
+def test_arithmetic_trees_are_one_kernel_and_bit_exact(oracle, shape, case):
+    rng = np.random.default_rng(16)
+    feeds = {n: rng.standard_normal(shape).astype(np.float32) for n in "ABCD"}
+    b = NetBuilder("tree")
+    out = case(b, *_four_inputs(b, shape))
+    if case.__name__ in ("nested", "shared_product_is_not_contracted"):
+        del feeds["D"]  # not used by this expression, hence not a tensor of the computation
+    comp, got = run_program(b, feeds, [out])
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s3t"], comp.groups()
+    ref = oracle_program(comp, feeds)[str(out)]
+    assert oracle.max_ulp(got[str(out)], ref) == 0
+
+
+def test_tree_with_broadcast_operands_and_a_reused_input(oracle):
+    rng = np.random.default_rng(17)
+    shape = (257, 1024)
+    feeds = {"X": rng.standard_normal(shape).astype(np.float32), "bias": rng.standard_normal(1024).astype(np.float32),
+             "mean": rng.standard_normal(1024).astype(np.float32)}
+    b = NetBuilder("tree")
+    x = b.create_input(common.Float(32), shape, "X")
+    bias = b.create_input(common.Float(32), (1024,), "bias")
+    mean = b.create_input(common.Float(32), (1024,), "mean")
+    out = b.multiply(b.add(x, bias), b.subtract(x, mean))   # X feeds both branches
+    comp, got = run_program(b, feeds, [out])
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s3t"], comp.groups()
+    ref = oracle_program(comp, feeds)[str(out)]
+    assert oracle.max_ulp(got[str(out)], ref) == 0
+
+
+def test_float16_tree_rounds_after_every_op(oracle):
+    rng = np.random.default_rng(18)
+    shape = (128, 1000)
+    feeds = {n: rng.standard_normal(shape).astype(np.float16) for n in "ABCD"}
+    b = NetBuilder("tree")
+    A, B, C, D = _four_inputs(b, shape, 16)
+    out = b.multiply(b.add(A, B), b.subtract(C, D))
+    comp, got = run_program(b, feeds, [out])
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f16_s3t"], comp.groups()
+    ref = oracle_program(comp, feeds)[str(out)]
+    assert np.array_equal(got[str(out)].view(np.uint16), ref.view(np.uint16))
+
+
+def test_sum_of_a_tree_is_one_reduction_kernel():
+    rng = np.random.default_rng(19)
+    shape = (512, 4096)
+    feeds = {n: rng.standard_normal(shape).astype(np.float32) for n in "ABCD"}
+    b = NetBuilder("tree")
+    A, B, C, D = _four_inputs(b, shape)
+    out = b.reduce_sum(b.multiply(b.add(A, B), b.subtract(C, D)), [1])
+    comp, got = run_program(b, feeds, [out])
+    assert [p for _, p in comp.groups()] == ["chain_row_reduce chain_reduce_row_s3t"], comp.groups()
+    f = {k: v.astype(np.float64) for k, v in feeds.items()}
+    terms = (f["A"] + f["B"]) * (f["C"] - f["D"])
+    exact = terms.sum(axis=1)
+    assert np.all(np.abs(got[str(out)] - exact) <= 1e-5 * np.abs(exact) + 1e-6 * np.abs(terms).sum(axis=1))
 
 
 def test_mixed_program_chain_reduce_chain(oracle):
