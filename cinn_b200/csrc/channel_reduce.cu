@@ -21,9 +21,11 @@ namespace {
 // GRAD: the statistics pass of the decomposed batch_norm_grad (cinn/frontend/decomposer/batch_norm.cc:62-72): x is
 // y_grad, x2 the forward input, `mean` the saved per-channel mean; the two accumulations are
 // reduce_sum(y_grad) and reduce_sum(y_grad * (x2 - mean)), difference and product rounded, no fma.
-template <class OpA, class OpB, bool DUAL, bool GRAD = false>
+// T: storage type of x (and x2): float, or a 16-bit float widened on load as the casts the AutoCast pass puts around
+// batch_norm_train / batch_norm_grad would (cinn/frontend/pass/auto_cast.cc:138-214); everything else is float32.
+template <class OpA, class OpB, bool DUAL, bool GRAD = false, typename T = float>
 __global__ void __launch_bounds__(256)
-    k_mid_keep_reduce(const float* __restrict__ x, const float* __restrict__ x2, const float* __restrict__ mean,
+    k_mid_keep_reduce(const T* __restrict__ x, const T* __restrict__ x2, const float* __restrict__ mean,
                       float* __restrict__ pa, float* __restrict__ pb, unsigned int* __restrict__ tickets,
                       float* __restrict__ ya, float* __restrict__ yb, long long A, long long B, long long I,
                       long long chunks, long long splits, long long vec_ok) {
@@ -34,9 +36,10 @@ __global__ void __launch_bounds__(256)
   const long long items    = A * chunks;
   const long long my_items = s < items ? (items - s + splits - 1) / splits : 0;
   float a0 = OpA::identity(), a1 = OpB::identity();
-  const int T = blockDim.x;
+  const int T_ = blockDim.x;
+  constexpr int V = 16 / sizeof(T);  // elements per 16-byte vector
   if (vec_ok) {
-    const long long nvec  = I >> 2;
+    const long long nvec  = I / V;
     const long long per   = (nvec + chunks - 1) / chunks;
     const long long total = my_items * per;
     const uint4* px       = reinterpret_cast<const uint4*>(x);
@@ -45,14 +48,14 @@ __global__ void __launch_bounds__(256)
     // four 16-byte vectors in flight per thread and stream (eight were slower: fewer, longer iterations per CTA)
     constexpr int U = 4;
     long long k = threadIdx.x / per, v = threadIdx.x - k * per;
-    const long long step_k = T / per, step_v = T - step_k * per;  // one stride of T vectors
-    for (long long idx = threadIdx.x; idx < total; idx += U * T) {
+    const long long step_k = T_ / per, step_v = T_ - step_k * per;  // one stride of T_ vectors
+    for (long long idx = threadIdx.x; idx < total; idx += U * T_) {
       uint4 r[U], r2[GRAD ? U : 1];
       bool ok[U];
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         ok[j] = false;
-        if (idx + (long long)j * T < total) {
+        if (idx + (long long)j * T_ < total) {
           const long long it = s + k * splits;
           long long a = it, chunk = 0;
           if (chunks != 1) {
@@ -76,11 +79,11 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         if (ok[j]) {
-          float f[4], f2[4];
-          unpack4(r[j], f);
-          if (GRAD) unpack4(r2[GRAD ? j : 0], f2);
+          float f[V], f2[V];
+          Io<T>::unpack(r[j], f);
+          if (GRAD) Io<T>::unpack(r2[GRAD ? j : 0], f2);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
+          for (int i = 0; i < V; ++i) {
             a0 = OpA::accum(a0, f[i]);
             if (GRAD) a1 = a1 + f[i] * (f2[i] - mu);
             else if (DUAL) a1 = OpB::accum(a1, f[i]);
@@ -93,11 +96,11 @@ __global__ void __launch_bounds__(256)
     for (long long it = s; it < items; it += splits) {
       const long long a = it / chunks, chunk = it - a * chunks;
       const long long begin = chunk * per, end = min(begin + per, I);
-      const float* px = x + (a * B + b) * I;
-      for (long long i = begin + threadIdx.x; i < end; i += T) {
-        const float f = px[i];
+      const T* px = x + (a * B + b) * I;
+      for (long long i = begin + threadIdx.x; i < end; i += T_) {
+        const float f = Io<T>::load1(px + i);
         a0            = OpA::accum(a0, f);
-        if (GRAD) a1 = a1 + f * (x2[(a * B + b) * I + i] - mu);
+        if (GRAD) a1 = a1 + f * (Io<T>::load1(x2 + (a * B + b) * I + i) - mu);
         else if (DUAL) a1 = OpB::accum(a1, f);
       }
     }
@@ -115,7 +118,7 @@ __global__ void __launch_bounds__(256)
   // Last CTA of channel b: every partial of the channel is visible (fence + ticket); fold them in split order.
   __threadfence();
   float t0 = OpA::identity(), t1 = OpB::identity();
-  for (long long k = threadIdx.x; k < splits; k += T) {
+  for (long long k = threadIdx.x; k < splits; k += T_) {
     t0 = OpA::apply(t0, __ldcg(pa + k * B + b));
     if (DUAL) t1 = OpB::apply(t1, __ldcg(pb + k * B + b));
   }
@@ -141,5 +144,9 @@ REG_MID("sumabs", SumAbsOp);
 REG_MID("maxabs", MaxAbsOp);
 CINN_B200_REGISTER_KERNEL("mid_keep_reduce_sum_sumsq_f32", 14, 256, k_mid_keep_reduce<SumOp, SumSquareOp, true>);
 CINN_B200_REGISTER_KERNEL("bn_grad_stats_f32", 14, 256, k_mid_keep_reduce<SumOp, SumOp, true, true>);
+CINN_B200_REGISTER_KERNEL("mid_keep_reduce_sum_sumsq_f16", 14, 256, k_mid_keep_reduce<SumOp, SumSquareOp, true, false, __half>);
+CINN_B200_REGISTER_KERNEL("mid_keep_reduce_sum_sumsq_bf16", 14, 256, k_mid_keep_reduce<SumOp, SumSquareOp, true, false, __nv_bfloat16>);
+CINN_B200_REGISTER_KERNEL("bn_grad_stats_f16", 14, 256, k_mid_keep_reduce<SumOp, SumOp, true, true, __half>);
+CINN_B200_REGISTER_KERNEL("bn_grad_stats_bf16", 14, 256, k_mid_keep_reduce<SumOp, SumOp, true, true, __nv_bfloat16>);
 
 }  // namespace cinn_b200

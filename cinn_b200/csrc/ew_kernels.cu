@@ -206,10 +206,12 @@ __global__ void __launch_bounds__(256)
 // order (rsqrt = 1 / sqrt; subtractions and the division are not contracted).  t0_form / vae_form = 1: tmp0 / var+eps
 // are computed here from scale and var; 0: they are given as per-channel inputs.
 // ------------------------------------------------------------------------------------------------
+// T: storage type of x, dy and the result (float, or a 16-bit float between the casts of the AutoCast pass).
+template <typename T>
 __global__ void __launch_bounds__(256)
-    k_bn_grad_apply(const float* __restrict__ x, const float* __restrict__ dy, const float* __restrict__ mean,
+    k_bn_grad_apply(const T* __restrict__ x, const T* __restrict__ dy, const float* __restrict__ mean,
                     const float* __restrict__ sum_s, const float* __restrict__ bias_grad, const float* __restrict__ vae_in,
-                    const float* __restrict__ t0_in, const float* __restrict__ var0, float* __restrict__ y,
+                    const float* __restrict__ t0_in, const float* __restrict__ var0, T* __restrict__ y,
                     long long planes, long long channels, long long hw, long long chunks, long long vec_ok,
                     long long t0_form, long long vae_form, double count_d, double eps_d) {
   const long long n_ctas = planes * chunks;
@@ -221,11 +223,12 @@ __global__ void __launch_bounds__(256)
     const float m = mean[c], S = sum_s[c], db = bias_grad[c];
     const float vae = vae_form ? vae_in[c] + eps : vae_in[c];
     const float t0  = t0_form ? (t0_in[c] * (1.0f / sqrtf(var0[c] + eps))) / count : t0_in[c];
-    const float* xp  = x + plane * hw;
-    const float* dp  = dy + plane * hw;
-    float* yp        = y + plane * hw;
+    const T* xp  = x + plane * hw;
+    const T* dp  = dy + plane * hw;
+    T* yp        = y + plane * hw;
+    constexpr int V = Io<T>::kVec;
     if (vec_ok) {
-      const int nvec  = (int)(hw / 4);
+      const int nvec  = (int)(hw / V);
       const int per   = (int)((nvec + chunks - 1) / chunks);
       const int begin = chunk * per;
       const int end   = min(begin + per, nvec);
@@ -235,18 +238,18 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
         for (int j = 0; j < 2; ++j)
           if (v + j * B < end) {
-            rx[j] = ld_stream16(xp + (long long)(v + j * B) * 4);
-            rd[j] = ld_stream16(dp + (long long)(v + j * B) * 4);
+            rx[j] = ld_stream16(xp + (long long)(v + j * B) * V);
+            rd[j] = ld_stream16(dp + (long long)(v + j * B) * V);
           }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           if (v + j * B < end) {
-            float fx[4], fd[4];
-            unpack4(rx[j], fx);
-            unpack4(rd[j], fd);
+            float fx[V], fd[V];
+            Io<T>::unpack(rx[j], fx);
+            Io<T>::unpack(rd[j], fd);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) fx[i] = t0 * (((fd[i] * count) - db) - (((fx[i] - m) * S) / vae));
-            st_stream16(yp + (long long)(v + j * B) * 4, pack4(fx));
+            for (int i = 0; i < V; ++i) fx[i] = t0 * (((fd[i] * count) - db) - (((fx[i] - m) * S) / vae));
+            st_stream16(yp + (long long)(v + j * B) * V, Io<T>::pack(fx));
           }
         }
       }
@@ -255,11 +258,13 @@ __global__ void __launch_bounds__(256)
       const long long begin = chunk * per;
       const long long end   = min(begin + per, hw);
       for (long long i = begin + threadIdx.x; i < end; i += blockDim.x)
-        yp[i] = t0 * (((dp[i] * count) - db) - (((xp[i] - m) * S) / vae));
+        Io<T>::store1(yp + i, t0 * (((Io<T>::load1(dp + i) * count) - db) - (((Io<T>::load1(xp + i) - m) * S) / vae)));
     }
   }
 }
-CINN_B200_REGISTER_KERNEL("ew_bn_grad_apply_nchw_f32", 18, 256, k_bn_grad_apply);
+CINN_B200_REGISTER_KERNEL("ew_bn_grad_apply_nchw_f32", 18, 256, k_bn_grad_apply<float>);
+CINN_B200_REGISTER_KERNEL("ew_bn_grad_apply_nchw_f16", 18, 256, k_bn_grad_apply<__half>);
+CINN_B200_REGISTER_KERNEL("ew_bn_grad_apply_nchw_bf16", 18, 256, k_bn_grad_apply<__nv_bfloat16>);
 
 CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f32", 12, 256, k_bn_nchw<float, true>);
 CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true>);
@@ -269,5 +274,9 @@ CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat
 CINN_B200_REGISTER_KERNEL("ew_bn_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, false>);
 CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_nchw_f32", 12, 256, k_bn_nchw<float, false, true>);
 CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_relu_nchw_f32", 12, 256, k_bn_nchw<float, true, true>);
+CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_nchw_f16", 12, 256, k_bn_nchw<__half, false, true>);
+CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true, true>);
+CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, false, true>);
+CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_relu_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, true, true>);
 
 }  // namespace cinn_b200

@@ -629,6 +629,22 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
             grew    = true;
             continue;
           }
+          // The same without the casts at its leaves: a cast that widens one 16-bit operand while another operand
+          // (widened by a cast with further users) is still float32 gives a mixed group no kernel takes; the casts
+          // join after the horizontal merge, when all of them can come in together.
+          {
+            std::set<int> inner = closure;
+            for (int q : closure) {
+              if (trial.count(q) || b.instrs()[q].op_type != "cast") continue;
+              const int src = st.producer_of_var[b.instrs()[q].inputs[0]];
+              if (src < 0 || !closure.count(src)) inner.erase(q);
+            }
+            if (inner.size() < closure.size() && inner.size() > trial.size() && st.Compiles(inner, nullptr, nullptr)) {
+              members = inner;
+              grew    = true;
+              continue;
+            }
+          }
           // Last attempt: everything upstream of the whole group that is used only inside it, at once.  Some
           // compositions only have a kernel as a whole (the normalisation of batch_norm_train needs x - mean and
           // rsqrt(var + eps) together; either alone leaves too many full-size operands).
@@ -691,6 +707,36 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
         for (int k : sets[j]) group_of[k] = (int)i;
         sets[i] = merged;
         sets[j].clear();
+        // The merged group may now hold every user of a producer that vertical fusion had to leave outside (the cast
+        // that widens a 16-bit x feeds both statistics): pull such single-instruction producers in.
+        {
+          std::vector<int> eligible;
+          for (int m : sets[i]) {
+            for (int v : b.instrs()[m].inputs) {
+              const int p = st.producer_of_var[v];
+              if (p < 0 || group_of[p] < 0 || group_of[p] == (int)i || sets[group_of[p]].size() != 1) continue;
+              if (st.IsConst(p) || PatternOf(b.instrs()[p].op_type) == OpPattern::kNonFusible) continue;
+              if (st.fetch.count(b.instrs()[p].output)) continue;
+              bool all_inside = true;
+              for (int c : st.consumers_of_var[b.instrs()[p].output])
+                if (!sets[i].count(c)) all_inside = false;
+              if (all_inside && std::find(eligible.begin(), eligible.end(), p) == eligible.end()) eligible.push_back(p);
+            }
+          }
+          auto take = [&](const std::vector<int>& ps) {
+            std::set<int> trial = sets[i];
+            trial.insert(ps.begin(), ps.end());
+            if (ps.empty() || !st.Compiles(trial, nullptr, nullptr)) return false;
+            for (int p : ps) {
+              sets[group_of[p]].clear();
+              group_of[p] = (int)i;
+            }
+            sets[i] = trial;
+            return true;
+          };
+          if (!take(eligible))  // all at once (two casts of one 16-bit type), else one by one
+            for (int p : eligible) take({p});
+        }
         break;
       }
     }

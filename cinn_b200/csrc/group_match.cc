@@ -144,6 +144,32 @@ struct Matcher {
     half_name_ = in == DType::kFloat16 ? "f16" : "bf16";
     return true;
   }
+  // What the AutoCast pass leaves around a 16-bit batch norm (cinn/frontend/pass/auto_cast.cc:109-214): 16-bit inputs
+  // widened to float32 by a cast at the load, the result narrowed by a cast at the end.  Returns the expression with
+  // those casts removed ("cast(%2)" -> "%2", an outer "cast(...)" dropped) and sets *wide to the 16-bit type
+  // (kFloat32 if there is none).  The kernels do the same conversions in their loads and stores.
+  std::string StripHalfCasts(const std::string& expr, DType* wide) {
+    *wide = DType::kFloat32;
+    auto is_half = [](DType t) { return t == DType::kFloat16 || t == DType::kBFloat16; };
+    std::string e = expr;
+    for (size_t i = 0; i < g.inputs.size(); ++i) {
+      if (!is_half(g.inputs[i].dtype)) continue;
+      if (*wide != DType::kFloat32 && *wide != g.inputs[i].dtype) return expr;  // two different 16-bit types
+      for (auto& op : g.ops)
+        if (op.type == "cast" && op.inputs[0] == g.inputs[i].name && DTypeFromName(AttrS(op, "dtype", "")) != DType::kFloat32) return expr;
+      *wide = g.inputs[i].dtype;
+      const std::string from = "cast(%" + std::to_string(i) + ")", to = "%" + std::to_string(i);
+      for (size_t pos = e.find(from); pos != std::string::npos; pos = e.find(from, pos + to.size())) e.replace(pos, from.size(), to);
+    }
+    if (*wide == DType::kFloat32) return expr;
+    if (g.outputs.size() == 1 && is_half(g.outputs[0].dtype)) {
+      const OpDesc* top = Producer(g.outputs[0].name);
+      if (!top || top->type != "cast" || g.outputs[0].dtype != *wide || e.rfind("cast(", 0) != 0 || e.back() != ')') return expr;
+      e = e.substr(5, e.size() - 6);
+    }
+    half_name_ = *wide == DType::kFloat16 ? "f16" : "bf16";
+    return e;
+  }
   static ArgSpec Aligned(bool static_ok, std::vector<int> ins, std::vector<int> outs) {
     ArgSpec a;
     a.kind            = ArgSpec::kAligned;
@@ -337,7 +363,9 @@ struct Matcher {
         R"(^(relu\()?elementwise_add\(elementwise_mul\(elementwise_mul\(subtract\(%(\d),broadcast_to\(%(\d)\)\),)"
         R"(rsqrt\(elementwise_add\(broadcast_to\(%(\d)\),fill_constant\(\)\)\)\),broadcast_to\(%(\d)\)\),broadcast_to\(%(\d)\)\)(\))?$)");
     std::smatch m;
-    if (!std::regex_match(expr, m, form) || g.inputs.size() != 5) return nullptr;
+    DType wide;
+    const std::string stripped = StripHalfCasts(expr, &wide);
+    if (!std::regex_match(stripped, m, form) || g.inputs.size() != 5) return nullptr;
     const bool relu = m[1].matched;
     if (relu != m[7].matched) return nullptr;
     const int ix = atoi(m[2].str().c_str()), im = atoi(m[3].str().c_str()), iv = atoi(m[4].str().c_str()),
@@ -345,7 +373,9 @@ struct Matcher {
     const std::set<int> distinct = {ix, im, iv, is, ib};
     if (distinct.size() != 5 || *distinct.rbegin() > 4) return nullptr;
     const auto &x = g.inputs[ix], &o = g.outputs[0];
-    if (x.shape.size() != 4 || o.shape != x.shape || x.dtype != DType::kFloat32 || o.dtype != DType::kFloat32) return nullptr;
+    if (x.shape.size() != 4 || o.shape != x.shape || x.dtype != wide || o.dtype != wide) return nullptr;
+    const int V = wide == DType::kFloat32 ? 4 : 8;
+    const std::string tname = wide == DType::kFloat32 ? "f32" : half_name_;
     const int64_t N = x.shape[0], C = x.shape[1], HW = x.shape[2] * x.shape[3];
     for (int i : {im, iv, is, ib})
       if (g.inputs[i].dtype != DType::kFloat32 || g.inputs[i].numel() != C) return nullptr;
@@ -370,15 +400,15 @@ struct Matcher {
     if (!have_eps) return nullptr;
     auto p = NewPlan(relu ? "ew_bn_train_apply_relu_nchw" : "ew_bn_train_apply_nchw");
     const int64_t planes = N * C;
-    const int64_t units  = HW % 4 == 0 ? HW / 4 : HW;
+    const int64_t units  = HW % V == 0 ? HW / V : HW;
     int64_t chunks       = std::max<int64_t>(1, (units + 512) / 1024);
     while (planes * chunks < (int64_t)dev.sm_count * 4 && units / (chunks * 2) >= 256) chunks *= 2;
     LaunchStep s;
-    if (!Kernel(&s, std::string(relu ? "ew_bn_train_apply_relu_nchw_f32" : "ew_bn_train_apply_nchw_f32"))) return nullptr;
+    if (!Kernel(&s, std::string(relu ? "ew_bn_train_apply_relu_nchw_" : "ew_bn_train_apply_nchw_") + tname)) return nullptr;
     s.block[0] = 256;
     s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(planes * chunks, (int64_t)dev.sm_count * 64));
     s.args     = {In(ix), In(is), In(ib), In(im), In(iv), Out(0), I(planes), I(C), I(HW), I(chunks),
-                  Aligned(HW % 4 == 0, {ix}, {0}), F(eps)};
+                  Aligned(HW % V == 0, {ix}, {0}), F(eps)};
     p->steps.push_back(s);
     return p;
   }
@@ -395,16 +425,19 @@ struct Matcher {
                                  R"(divide\(elementwise_mul\(subtract\(%(\d),broadcast_to\(%(\d)\)\),broadcast_to\(%(\d)\)\),)" +
                                  vae + R"(\)\)\)$)");
     std::smatch m;
-    if (!std::regex_match(expr, m, form)) return nullptr;
+    DType wide;
+    const std::string stripped = StripHalfCasts(expr, &wide);
+    if (!std::regex_match(stripped, m, form)) return nullptr;
     auto idx = [&](int k) { return m[k].matched ? atoi(m[k].str().c_str()) : -1; };
     const int t0_in = idx(1), scale = idx(2), var0 = idx(3), dy = idx(4), db = idx(5), x = idx(6), mean = idx(7),
               S = idx(8), vae_in = idx(9), var1 = idx(10);
     const bool t0_form = t0_in < 0, vae_form = vae_in < 0;
     const auto& xt = g.inputs[x];
     const auto& o  = g.outputs[0];
-    if (xt.shape.size() != 4 || g.inputs[dy].shape != xt.shape || o.shape != xt.shape || xt.dtype != DType::kFloat32 ||
-        g.inputs[dy].dtype != DType::kFloat32 || o.dtype != DType::kFloat32 || x == dy)
+    if (xt.shape.size() != 4 || g.inputs[dy].shape != xt.shape || o.shape != xt.shape || xt.dtype != wide ||
+        g.inputs[dy].dtype != wide || o.dtype != wide || x == dy)
       return nullptr;
+    const int V = wide == DType::kFloat32 ? 4 : 8;
     const int64_t N = xt.shape[0], C = xt.shape[1], HW = xt.shape[2] * xt.shape[3];
     for (int i : {t0_form ? scale : t0_in, t0_form ? var0 : mean, db, mean, S, vae_form ? var1 : vae_in})
       if (i < 0 || i >= (int)g.inputs.size() || g.inputs[i].dtype != DType::kFloat32 || g.inputs[i].numel() != C) return nullptr;
@@ -428,15 +461,15 @@ struct Matcher {
     }
     auto p               = NewPlan("ew_bn_grad_apply_nchw");
     const int64_t planes = N * C;
-    const int64_t units  = HW % 4 == 0 ? HW / 4 : HW;
+    const int64_t units  = HW % V == 0 ? HW / V : HW;
     int64_t chunks       = std::max<int64_t>(1, (units + 256) / 512);
     while (planes * chunks < (int64_t)dev.sm_count * 4 && units / (chunks * 2) >= 256) chunks *= 2;
     LaunchStep s;
-    if (!Kernel(&s, "ew_bn_grad_apply_nchw_f32")) return nullptr;
+    if (!Kernel(&s, std::string("ew_bn_grad_apply_nchw_") + (wide == DType::kFloat32 ? "f32" : half_name_))) return nullptr;
     s.block[0] = 256;
     s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(planes * chunks, (int64_t)dev.sm_count * 64));
     s.args     = {In(x), In(dy), In(mean), In(S), In(db), In(vae_form ? var1 : vae_in), In(t0_form ? scale : t0_in),
-                  In(t0_form ? var0 : mean), Out(0), I(planes), I(C), I(HW), I(chunks), Aligned(HW % 4 == 0, {x, dy}, {0}),
+                  In(t0_form ? var0 : mean), Out(0), I(planes), I(C), I(HW), I(chunks), Aligned(HW % V == 0, {x, dy}, {0}),
                   I(t0_form ? 1 : 0), I(vae_form ? 1 : 0), F(count), F(eps)};
     p->steps.push_back(s);
     return p;
@@ -710,10 +743,12 @@ struct Matcher {
   // First pass of a middle-axis-keeping reduction into scratch partials [splits][B] (per accumulation), then a
   // column reduction over the splits.  opname2 != nullptr: the dual kernel (sum and sum of squares).
   bool PlanMidKeep(CompiledGroup* p, const char* opname, bool dual, int64_t A, int64_t B, int64_t I, ArgSpec dst,
-                   ArgSpec dst2, int x_in = 0, int x2_in = -1, int mean_in = -1) {
+                   ArgSpec dst2, int x_in = 0, int x2_in = -1, int mean_in = -1, DType storage = DType::kFloat32) {
     const int sms        = dev.sm_count;
-    const bool vec       = I % 4 == 0;
-    const int64_t units  = vec ? I / 4 : I;
+    const int V          = storage == DType::kFloat32 ? 4 : 8;  // elements per 16-byte vector
+    const char* tname    = storage == DType::kFloat32 ? "f32" : (storage == DType::kFloat16 ? "f16" : "bf16");
+    const bool vec       = I % V == 0;
+    const int64_t units  = vec ? I / V : I;
     const int64_t chunks = std::max<int64_t>(1, (units + 2048) / 4096);  // about 4096 vectors per work item
     const int64_t items  = A * chunks;
     if (items >= (int64_t)1 << 31) return Fail("reduction with more than 2^31 work items");
@@ -727,8 +762,9 @@ struct Matcher {
     p->scratch_bytes += (size_t)RoundUp(B * 4, 256);
     LaunchStep s;
     const bool grad = x2_in >= 0;
-    if (!Kernel(&s, grad ? std::string("bn_grad_stats_f32")
-                         : (dual ? std::string("mid_keep_reduce_sum_sumsq_f32") : std::string("mid_keep_reduce_") + opname + "_f32")))
+    if (storage != DType::kFloat32 && !grad && !dual) return Fail("16-bit channel reductions are prebuilt for the statistics pair only");
+    if (!Kernel(&s, grad ? std::string("bn_grad_stats_") + tname
+                         : (dual ? std::string("mid_keep_reduce_sum_sumsq_") + tname : std::string("mid_keep_reduce_") + opname + "_f32")))
       return false;
     s.block[0] = 256;
     s.grid[0]  = (unsigned)(B * splits);
@@ -900,12 +936,15 @@ struct Matcher {
   // pass of batch_norm_train (cinn/frontend/decomposer/batch_norm.cc:60-92), one read of x.
   // The statistics of the decomposed batch_norm_grad (cinn/frontend/decomposer/batch_norm.cc:62-72):
   // {reduce_sum(dy), reduce_sum(dy * (x - broadcast(mean)))} over N, H, W, or the second one alone.
-  std::unique_ptr<CompiledGroup> MatchBnGradStats(const std::string& expr) {
+  std::unique_ptr<CompiledGroup> MatchBnGradStats(const std::string& expr_in) {
     static const std::regex both(R"(^reduce_sum\(%(\d)\);reduce_sum\(elementwise_mul\(%(\d),subtract\(%(\d),broadcast_to\(%(\d)\)\)\)\)$)");
     static const std::regex one(R"(^reduce_sum\(elementwise_mul\(%(\d),subtract\(%(\d),broadcast_to\(%(\d)\)\)\)\)$)");
     std::smatch m;
     int idy, ix, im;
     bool dual;
+    DType wide;
+    const std::string stripped = StripHalfCasts(expr_in, &wide);
+    const std::string& expr    = stripped;
     if (std::regex_match(expr, m, both) && g.outputs.size() == 2) {
       if (m[1].str() != m[2].str()) return nullptr;
       idy = atoi(m[2].str().c_str()), ix = atoi(m[3].str().c_str()), im = atoi(m[4].str().c_str());
@@ -918,8 +957,8 @@ struct Matcher {
     }
     if (g.inputs.size() != 3 || idy == ix || idy == im || ix == im) return nullptr;
     const auto &dy = g.inputs[idy], &x = g.inputs[ix], &mean = g.inputs[im];
-    if (dy.dtype != DType::kFloat32 || x.dtype != DType::kFloat32 || mean.dtype != DType::kFloat32 || dy.shape != x.shape) {
-      Fail("batch_norm_grad statistics are prebuilt for float32 tensors of one shape");
+    if (dy.dtype != wide || x.dtype != wide || mean.dtype != DType::kFloat32 || dy.shape != x.shape) {
+      Fail("batch_norm_grad statistics are prebuilt for float32 (or, between casts, 16-bit) tensors of one shape");
       return nullptr;
     }
     int64_t A = 0, B = 0, I = 0;
@@ -939,12 +978,12 @@ struct Matcher {
     auto p      = NewPlan("bn_grad_stats");
     p->elements = x.numel();
     if (dual) {
-      if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Out(0), Out(1), idy, ix, im)) return nullptr;
+      if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Out(0), Out(1), idy, ix, im, wide)) return nullptr;
     } else {
       // the kernel always keeps both sums; the first one lands in scratch
       const int64_t off = p->scratch_bytes;
       p->scratch_bytes += (size_t)RoundUp(B * 4, 256);
-      if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Scratch(off), Out(0), idy, ix, im)) return nullptr;
+      if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Scratch(off), Out(0), idy, ix, im, wide)) return nullptr;
     }
     return p;
   }
@@ -953,10 +992,12 @@ struct Matcher {
     static const std::set<std::string> forms = {
         "reduce_sum(%0);reduce_sum(elementwise_mul(%0,identity(%0)))", "reduce_sum(%0);reduce_sum(elementwise_mul(%0,%0))",
         "reduce_sum(%0);reduce_sum(elementwise_mul(identity(%0),%0))"};
-    if (!forms.count(expr) || g.inputs.size() != 1 || g.outputs.size() != 2) return nullptr;
+    DType wide;
+    const std::string stripped = StripHalfCasts(expr, &wide);
+    if (!forms.count(stripped) || g.inputs.size() != 1 || g.outputs.size() != 2) return nullptr;
     const auto& x = g.inputs[0];
-    if (x.dtype != DType::kFloat32 || g.outputs[0].dtype != DType::kFloat32 || g.outputs[1].dtype != DType::kFloat32) {
-      Fail("channel statistics are prebuilt for float32 only");
+    if (x.dtype != wide || g.outputs[0].dtype != DType::kFloat32 || g.outputs[1].dtype != DType::kFloat32) {
+      Fail("channel statistics are prebuilt for float32 results only");
       return nullptr;
     }
     const OpDesc *r0 = Producer(g.outputs[0].name), *r1 = Producer(g.outputs[1].name);
@@ -968,7 +1009,7 @@ struct Matcher {
     }
     auto p      = NewPlan("channel_stats");
     p->elements = x.numel();
-    if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Out(0), Out(1))) return nullptr;
+    if (!PlanMidKeep(p.get(), "sum", true, A, B, I, Out(0), Out(1), 0, -1, -1, wide)) return nullptr;
     return p;
   }
 

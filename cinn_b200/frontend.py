@@ -289,10 +289,20 @@ class NetBuilder:
         count = float(n * h * w)
         red = [0, 2, 3]
         full = list(shape)
+        # 16-bit x: computed in float32 between casts, as the AutoCast pass arranges it around the op
+        # (cinn/frontend/pass/auto_cast.cc:138-172); statistics and moving averages stay float32.  The statistics and
+        # the normalisation each widen x themselves, so that neither needs a float32 copy of it in memory.
+        half_dt = dt if dt in ("float16", "bfloat16") else None
+        x_in = x
+        if half_dt:
+            dt = "float32"
+            x = self.cast(x_in, "float32")
         # mean = reduce_sum(x) / nhw ; variance = reduce_sum(x * x) / nhw - mean * mean
         mean = self.divide(self.reduce_sum(x, red), self.fill_constant([c], count, dtype=dt))
         sq_mean = self.divide(self.reduce_sum(self.multiply(x, self.identity(x)), red),
                               self.fill_constant([c], count, dtype=dt))
+        if half_dt:
+            x = self.cast(x_in, "float32")
         variance = self.subtract(sq_mean, self.multiply(mean, self.identity(mean)))
         mean_4d = self.broadcast_to(mean, full, [1])
         var_4d = self.broadcast_to(variance, full, [1])
@@ -300,6 +310,8 @@ class NetBuilder:
         # y = scale * (x - mean) * std_variance_inv + bias
         normalized = self.multiply(self.subtract(x, mean_4d), std_inv_4d)
         y = self.add(self.multiply(normalized, self.broadcast_to(scale, full, [1])), self.broadcast_to(bias, full, [1]))
+        if half_dt:
+            y = self.cast(y, half_dt)
 
         def update(moving, saved):
             return self.add(self.multiply(moving, self.fill_constant([c], float(momentum), dtype=dt)),
@@ -315,6 +327,14 @@ class NetBuilder:
         n, c, h, w = shape
         count = float(n * h * w)
         red, full = [0, 2, 3], list(shape)
+        # 16-bit y_grad and x: computed in float32 between casts (cinn/frontend/pass/auto_cast.cc:173-214); x_grad goes
+        # back to the 16-bit type, scale_grad and bias_grad stay float32.  The statistics and the x_grad expression
+        # each widen their operands themselves, so that no float32 copy of them is written to memory.
+        half_dt = dt if dt in ("float16", "bfloat16") else None
+        y_grad_in, x_in = y_grad, x
+        if half_dt:
+            dt = "float32"
+            y_grad, x = self.cast(y_grad_in, "float32"), self.cast(x_in, "float32")
 
         def std_inv_1d():
             return self.rsqrt(self.add(save_variance, self.fill_constant([c], float(epsilon), dtype=dt)))
@@ -324,6 +344,8 @@ class NetBuilder:
         scale_grad = self.multiply(sum_dy_xmu, std_inv_1d())
         scaled_std_inv = self.multiply(scale, std_inv_1d())
         tmp0 = self.broadcast_to(self.divide(scaled_std_inv, self.fill_constant([c], count, dtype=dt)), full, [1])
+        if half_dt:
+            y_grad, x = self.cast(y_grad_in, "float32"), self.cast(x_in, "float32")
         tmp1 = self.multiply(y_grad, self.fill_constant(full, count, dtype=dt))
         tmp2 = self.broadcast_to(bias_grad, full, [1])
         x_mean_diff2 = self.subtract(x, self.broadcast_to(save_mean, full, [1]))
@@ -331,6 +353,8 @@ class NetBuilder:
         var_eps_4d = self.broadcast_to(self.add(save_variance, self.fill_constant([c], float(epsilon), dtype=dt)), full, [1])
         tmp3 = self.divide(tmp3_0, var_eps_4d)
         x_grad = self.multiply(tmp0, self.subtract(self.subtract(tmp1, tmp2), tmp3))
+        if half_dt:
+            x_grad = self.cast(x_grad, half_dt)
         return [x_grad, scale_grad, bias_grad]
 
     def layer_norm(self, x, gamma, beta, epsilon=1e-5):

@@ -905,3 +905,82 @@ def test_auto_broadcast_keeps_the_dedicated_kernel_and_its_bits(oracle):
     comp = Computation.build_and_compile(TARGET, b, fetch=[str(out)])
     assert "ew_bias_scale_tanh_cast" in comp.groups()[0][1]
     assert np.array_equal(got.view(np.uint16), plain.view(np.uint16))
+
+
+# ---- 16-bit batch_norm_train / batch_norm_grad: float32 arithmetic between casts, 16-bit storage -----------------------
+def _bind_run(comp, tensors):
+    import torch
+    for name, t in tensors.items():
+        comp.get_tensor(name).bind(t.data_ptr())
+    comp.execute()
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (3, 5, 7, 9), (32, 64, 56, 56)])
+def test_sixteen_bit_batch_norm_train(dtype, shape):
+    import torch
+    torch.manual_seed(71)
+    tdt = torch.float16 if dtype == "float16" else torch.bfloat16
+    n, c, h, w = shape
+    b = NetBuilder("bn_train16")
+    x = b.create_input(common.Type(dtype), shape, "x")
+    ps = [b.create_input(common.Float(32), (c,), nm) for nm in ("scale", "bias", "moving_mean", "moving_variance")]
+    outs = b.batch_norm_train(x, *ps, epsilon=1e-5, momentum=0.9)
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(o) for o in outs])
+    pats = [p for _, p in comp.groups()]
+    short = "f16" if dtype == "float16" else "bf16"
+    assert "channel_stats mid_keep_reduce_sum_sumsq_" + short in pats and "ew_bn_train_apply_nchw ew_bn_train_apply_nchw_" + short in pats, pats
+    dev = "cuda:0"
+    t = {"x": (torch.randn(shape, device=dev) * 2 + 0.5).to(tdt),
+         "scale": 1 + 0.1 * torch.randn(c, device=dev), "bias": 0.1 * torch.randn(c, device=dev),
+         "moving_mean": 0.1 * torch.randn(c, device=dev), "moving_variance": torch.rand(c, device=dev) + 0.5}
+    y = torch.empty(shape, dtype=tdt, device=dev)
+    stats = [torch.empty(c, dtype=torch.float32, device=dev) for _ in range(4)]
+    _bind_run(comp, {**t, str(outs[0]): y, **{str(o): s for o, s in zip(outs[1:], stats)}})
+    x64 = t["x"].double()
+    m = x64.mean(dim=(0, 2, 3))
+    v = (x64 * x64).mean(dim=(0, 2, 3)) - m * m
+    r = lambda a: a.double().reshape(1, c, 1, 1)  # noqa: E731
+    want = (x64 - r(m)) / torch.sqrt(r(v) + 1e-5) * r(t["scale"]) + r(t["bias"])
+    assert torch.allclose(stats[0].double(), m, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(stats[1].double(), v, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(stats[2].double(), 0.9 * t["moving_mean"].double() + 0.1 * m, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(stats[3].double(), 0.9 * t["moving_variance"].double() + 0.1 * v, rtol=1e-4, atol=1e-5)
+    assert bool(((y.double() - want).abs() <= 1e-2 * want.abs() + 1e-2).all()), float((y.double() - want).abs().max())
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(8, 16, 12, 12), (3, 5, 7, 9), (32, 64, 56, 56)])
+def test_sixteen_bit_batch_norm_grad(dtype, shape):
+    import torch
+    torch.manual_seed(72)
+    tdt = torch.float16 if dtype == "float16" else torch.bfloat16
+    n, c, h, w = shape
+    b = NetBuilder("bn_grad16")
+    dy, x = b.create_input(common.Type(dtype), shape, "dy"), b.create_input(common.Type(dtype), shape, "x")
+    scale, mean, var = (b.create_input(common.Float(32), (c,), nm) for nm in ("scale", "mean", "var"))
+    outs = b.batch_norm_grad(dy, x, scale, mean, var, epsilon=1e-5)
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(o) for o in outs])
+    pats = [p for _, p in comp.groups()]
+    short = "f16" if dtype == "float16" else "bf16"
+    assert pats == ["bn_grad_stats bn_grad_stats_" + short, "ew_chain ew_chain_f32_s1",
+                    "ew_bn_grad_apply_nchw ew_bn_grad_apply_nchw_" + short], pats
+    dev = "cuda:0"
+    X = (torch.randn(shape, device=dev) * 1.5 + 0.3).to(tdt)
+    t = {"dy": torch.randn(shape, device=dev).to(tdt), "x": X, "scale": 1 + 0.1 * torch.randn(c, device=dev),
+         "mean": X.float().mean(dim=(0, 2, 3)), "var": X.float().var(dim=(0, 2, 3), unbiased=False)}
+    dx = torch.empty(shape, dtype=tdt, device=dev)
+    dscale, dbias = (torch.empty(c, dtype=torch.float32, device=dev) for _ in range(2))
+    _bind_run(comp, {**t, str(outs[0]): dx, str(outs[1]): dscale, str(outs[2]): dbias})
+    d = {k: v_.double() for k, v_ in t.items()}
+    m, v, s = (d[k].reshape(1, c, 1, 1) for k in ("mean", "var", "scale"))
+    cnt = n * h * w
+    db = d["dy"].sum(dim=(0, 2, 3))
+    S = (d["dy"] * (d["x"] - m)).sum(dim=(0, 2, 3))
+    inv = 1 / torch.sqrt(v + 1e-5)
+    want = (s * inv / cnt) * ((d["dy"] * cnt - db.reshape(1, c, 1, 1)) - (d["x"] - m) * S.reshape(1, c, 1, 1) / (v + 1e-5))
+    assert bool(((dbias.double() - db).abs() <= 1e-5 * d["dy"].abs().sum(dim=(0, 2, 3)) + 1e-6).all())
+    assert bool(((dscale.double() - S * inv.reshape(-1)).abs()
+                 <= 3e-5 * (d["dy"] * (d["x"] - m)).abs().sum(dim=(0, 2, 3)) * inv.reshape(-1) + 1e-6).all())
+    assert bool(((dx.double() - want).abs() <= 1e-2 * want.abs() + 1e-2 * want.abs().max()).all())
