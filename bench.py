@@ -235,6 +235,10 @@ def side_groups(torch, dev, peak, only=None):
         ("generic_reduce_max_i32_rows_16384x8192", lambda: W.generic_reduce("max", "int32", axis=1), 1, ""),
         ("generic_reduce_sum_i32_cols_16384x8192", lambda: W.generic_reduce("sum", "int32", axis=0), 1, ""),
         ("generic_reduce_all_bool_rows_16384x8192", lambda: W.generic_reduce("all", "bool", axis=1), 4, ""),
+        ("generic_tree_f32_8192x8192", lambda: W.chain_tree(), 1, "(A+B)*(C-D): chain kernel with temporaries"),
+        ("bn_train_stats_f16_256x64x112x112", lambda: W.bn_train_stats((256, 64, 112, 112), half=True), 1,
+         "fp16 x widened in the load; sum and sum of squares per channel"),
+        ("bn_train_apply_f16_256x64x112x112", lambda: W.bn_train_apply((256, 64, 112, 112), half=True), 1, "fp16 storage"),
         # a reduction with an elementwise chain as its operand: the chain runs inside the reduction kernel
         ("chain_reduce_sum_abs_diff_rows_8192x8192", lambda: W.chain_reduce("sum_abs_diff", axis=1), 1, "chain + reduce, one kernel"),
         ("chain_reduce_sum_abs_diff_cols_8192x8192", lambda: W.chain_reduce("sum_abs_diff", axis=0), 1, "chain + reduce, one kernel"),

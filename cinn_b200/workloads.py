@@ -254,6 +254,16 @@ def generic_reduce(kind, dtype, shape=(16384, 8192), axis=1, seed=6):
                     _NP[dtype], out_shape)
 
 
+def chain_tree(shape=(8192, 8192), seed=9):
+    """(A + B) * (C - D): an expression tree, one kernel (one branch stashed in a temporary)."""
+    s = _shape(shape)
+    desc = (f"group fn_tree\ninput A float32 {s}\ninput B float32 {s}\ninput C float32 {s}\ninput D float32 {s}\n"
+            f"op elementwise_add t = A B ; axis=-1\nop subtract u = C D ; axis=-1\nop elementwise_mul y = t u ; axis=-1\n"
+            f"output y float32 {s}\n")
+    return Workload("chain_tree", desc, lambda: [_draw(np.random.default_rng(seed + k), shape, "float32") for k in range(4)],
+                    np.float32, shape)
+
+
 def chain_reduce(kind="sum_abs_diff", shape=(8192, 8192), axis=1, seed=8):
     """A reduction whose operand is an elementwise chain, one kernel: `sum_abs_diff` = reduce_sum(|x - y|) of two
     tensors, `sum_sigmoid_affine` = reduce_sum(sigmoid((x + b) * b)) with a row vector b."""
@@ -285,9 +295,17 @@ def bn_train_inputs(shape=(256, 64, 112, 112), seed=4):
     return x, mean, var, scale, bias
 
 
-def bn_train_stats(shape=(256, 64, 112, 112), seed=4):
-    """The statistics pass of the decomposed batch_norm_train: {reduce_sum(x), reduce_sum(x * x)} over N, H, W."""
+def bn_train_stats(shape=(256, 64, 112, 112), seed=4, half=False):
+    """The statistics pass of the decomposed batch_norm_train: {reduce_sum(x), reduce_sum(x * x)} over N, H, W.
+    half=True: x is stored as fp16 and widened by a cast inside the group."""
     s, c = _shape(shape), shape[1]
+    if half:
+        desc = (f"group fn_bn_train_stats_f16\ninput x16 float16 {s}\nop cast x = x16 ; dtype=float32\n"
+                f"op reduce_sum s1 = x ; dim=0,2,3 keep_dim=false\n"
+                f"op identity xi = x\nop elementwise_mul xx = x xi ; axis=-1\n"
+                f"op reduce_sum s2 = xx ; dim=0,2,3 keep_dim=false\noutput s1 float32 {c}\noutput s2 float32 {c}\n")
+        return Workload("bn_train_stats_f16", desc, lambda: [bn_train_inputs(shape, seed)[0].astype(np.float16)],
+                        np.float32, (c,), more_outputs=[(np.float32, (c,))])
     desc = (f"group fn_bn_train_stats\ninput x float32 {s}\nop reduce_sum s1 = x ; dim=0,2,3 keep_dim=false\n"
             f"op identity xi = x\nop elementwise_mul xx = x xi ; axis=-1\n"
             f"op reduce_sum s2 = xx ; dim=0,2,3 keep_dim=false\noutput s1 float32 {c}\noutput s2 float32 {c}\n")
@@ -295,7 +313,7 @@ def bn_train_stats(shape=(256, 64, 112, 112), seed=4):
                     more_outputs=[(np.float32, (c,))])
 
 
-def bn_train_apply(shape=(256, 64, 112, 112), seed=4):
+def bn_train_apply(shape=(256, 64, 112, 112), seed=4, half=False):
     """The normalisation pass: ((x - mean) * rsqrt(var + eps)) * scale + bias with per-channel operands."""
     s, c = _shape(shape), shape[1]
     bc = f"broadcast_axes=1 out_shape={s}"
@@ -307,10 +325,15 @@ def bn_train_apply(shape=(256, 64, 112, 112), seed=4):
             f"op broadcast_to s4 = scale ; {bc}\nop elementwise_mul sn = n s4 ; axis=-1\n"
             f"op broadcast_to b4 = bias ; {bc}\nop elementwise_add y = sn b4 ; axis=-1\noutput y float32 {s}\n")
 
+    if half:
+        desc = desc.replace("fn_bn_train_apply", "fn_bn_train_apply_f16").replace(f"input x float32 {s}", f"input x16 float16 {s}")
+        desc = desc.replace("op broadcast_to m4", "op cast x = x16 ; dtype=float32\nop broadcast_to m4", 1)
+        desc = desc.replace(f"output y float32 {s}", f"op cast y16 = y ; dtype=float16\noutput y16 float16 {s}")
+
     def gen():
         x, mean, var, scale, bias = bn_train_inputs(shape, seed)
-        return [mean, var, x, scale, bias]
-    return Workload("bn_train_apply", desc, gen, np.float32, shape)
+        return [mean, var, x.astype(np.float16) if half else x, scale, bias]
+    return Workload("bn_train_apply_f16" if half else "bn_train_apply", desc, gen, np.float16 if half else np.float32, shape)
 
 
 def softmax_safe(shape=(16384, 4096), seed=3, half=False):
