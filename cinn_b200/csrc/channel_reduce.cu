@@ -21,6 +21,69 @@ namespace {
 // GRAD: the statistics pass of the decomposed batch_norm_grad (cinn/frontend/decomposer/batch_norm.cc:62-72): x is
 // y_grad, x2 the forward input, `mean` the saved per-channel mean; the two accumulations are
 // reduce_sum(y_grad) and reduce_sum(y_grad * (x2 - mean)), difference and product rounded, no fma.
+// The vector walk of k_mid_keep_reduce: the work items s, s + splits, ... of channel b as one flat list of 16-byte
+// vectors.  (k, v) = (item, vector inside the item) of the flat index, advanced incrementally: no division per load.
+// Four vectors in flight per thread and stream (eight were slower: fewer, longer iterations per CTA).  IdxT: the type
+// of the index arithmetic.
+template <class OpA, class OpB, bool DUAL, bool GRAD, typename T, typename IdxT>
+__device__ __forceinline__ void walk_vectors(const uint4* __restrict__ px, const uint4* __restrict__ px2, float mu,
+                                             long long A_, long long B_, long long I_, long long chunks_,
+                                             long long splits_, long long b_, long long s_, long long my_items,
+                                             float& a0, float& a1) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int U = 4;
+  const IdxT B = (IdxT)B_, chunks = (IdxT)chunks_, splits = (IdxT)splits_, b = (IdxT)b_, s = (IdxT)s_;
+  const IdxT T_    = (IdxT)blockDim.x;
+  const IdxT nvec  = (IdxT)(I_ / V);
+  const IdxT per   = (nvec + chunks - 1) / chunks;
+  const IdxT total = (IdxT)my_items * per;
+  IdxT k = (IdxT)threadIdx.x / per, v = (IdxT)threadIdx.x - k * per;
+  const IdxT step_k = T_ / per, step_v = T_ - step_k * per;  // one stride of T_ vectors
+  for (IdxT idx = threadIdx.x; idx < total; idx += U * T_) {
+    uint4 r[U], r2[GRAD ? U : 1];
+    bool ok[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      ok[j] = false;
+      if (idx + (IdxT)j * T_ < total) {
+        const IdxT it = s + k * splits;
+        IdxT a = it, chunk = 0;
+        if (chunks != 1) {
+          a     = (unsigned)it / (unsigned)chunks;  // items < 2^31 (checked by the planner)
+          chunk = it - a * chunks;
+        }
+        const IdxT vv = chunk * per + v;
+        if (vv < nvec) {
+          const IdxT at = (a * B + b) * nvec + vv;
+          r[j]          = __ldcs(px + at);
+          if (GRAD) r2[GRAD ? j : 0] = __ldcs(px2 + at);
+          ok[j] = true;
+        }
+      }
+      k += step_k;
+      v += step_v;
+      if (v >= per) {
+        v -= per;
+        ++k;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      if (ok[j]) {
+        float f[V], f2[V];
+        Io<T>::unpack(r[j], f);
+        if (GRAD) Io<T>::unpack(r2[GRAD ? j : 0], f2);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          a0 = OpA::accum(a0, f[i]);
+          if (GRAD) a1 = a1 + f[i] * (f2[i] - mu);
+          else if (DUAL) a1 = OpB::accum(a1, f[i]);
+        }
+      }
+    }
+  }
+}
+
 // T: storage type of x (and x2): float, or a 16-bit float widened on load as the casts the AutoCast pass puts around
 // batch_norm_train / batch_norm_grad would (cinn/frontend/pass/auto_cast.cc:138-214); everything else is float32.
 template <class OpA, class OpB, bool DUAL, bool GRAD = false, typename T = float>
@@ -39,58 +102,14 @@ __global__ void __launch_bounds__(256)
   const int T_ = blockDim.x;
   constexpr int V = 16 / sizeof(T);  // elements per 16-byte vector
   if (vec_ok) {
-    const long long nvec  = I / V;
-    const long long per   = (nvec + chunks - 1) / chunks;
-    const long long total = my_items * per;
-    const uint4* px       = reinterpret_cast<const uint4*>(x);
-    const uint4* px2      = reinterpret_cast<const uint4*>(x2);
-    // (k, v) = (item, vector inside the item) of flat index id, advanced incrementally: no division per load.
-    // four 16-byte vectors in flight per thread and stream (eight were slower: fewer, longer iterations per CTA)
-    constexpr int U = 4;
-    long long k = threadIdx.x / per, v = threadIdx.x - k * per;
-    const long long step_k = T_ / per, step_v = T_ - step_k * per;  // one stride of T_ vectors
-    for (long long idx = threadIdx.x; idx < total; idx += U * T_) {
-      uint4 r[U], r2[GRAD ? U : 1];
-      bool ok[U];
-#pragma unroll
-      for (int j = 0; j < U; ++j) {
-        ok[j] = false;
-        if (idx + (long long)j * T_ < total) {
-          const long long it = s + k * splits;
-          long long a = it, chunk = 0;
-          if (chunks != 1) {
-            a     = (unsigned)it / (unsigned)chunks;  // items < 2^31 (checked by the planner)
-            chunk = it - a * chunks;
-          }
-          const long long vv = chunk * per + v;
-          if (vv < nvec) {
-            r[j]  = __ldcs(px + (a * B + b) * nvec + vv);
-            if (GRAD) r2[GRAD ? j : 0] = __ldcs(px2 + (a * B + b) * nvec + vv);
-            ok[j] = true;
-          }
-        }
-        k += step_k;
-        v += step_v;
-        if (v >= per) {
-          v -= per;
-          ++k;
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < U; ++j) {
-        if (ok[j]) {
-          float f[V], f2[V];
-          Io<T>::unpack(r[j], f);
-          if (GRAD) Io<T>::unpack(r2[GRAD ? j : 0], f2);
-#pragma unroll
-          for (int i = 0; i < V; ++i) {
-            a0 = OpA::accum(a0, f[i]);
-            if (GRAD) a1 = a1 + f[i] * (f2[i] - mu);
-            else if (DUAL) a1 = OpB::accum(a1, f[i]);
-          }
-        }
-      }
-    }
+    const uint4* px  = reinterpret_cast<const uint4*>(x);
+    const uint4* px2 = reinterpret_cast<const uint4*>(x2);
+    // Index arithmetic in 32 bits whenever the tensor has fewer than 2^31 vectors (64-bit multiplies per load cost
+    // as much as the arithmetic on the loaded values, and with 16-bit storage made the kernel issue-bound).
+    if (A * B * (I / V) < (1ll << 31))
+      walk_vectors<OpA, OpB, DUAL, GRAD, T, unsigned>(px, px2, mu, A, B, I, chunks, splits, b, s, my_items, a0, a1);
+    else
+      walk_vectors<OpA, OpB, DUAL, GRAD, T, long long>(px, px2, mu, A, B, I, chunks, splits, b, s, my_items, a0, a1);
   } else {
     const long long per = (I + chunks - 1) / chunks;
     for (long long it = s; it < items; it += splits) {
