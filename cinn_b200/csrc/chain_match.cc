@@ -390,19 +390,31 @@ const char* DTypeKernelName(DType t) {
 enum ChainClass { kFloatChain, kIntChain, kDoubleChain };
 bool Ok2(const ChainBuilder& cb, DType t) { return cb.Ok(t); }
 
+// `final_idx`: which output the chain ends at.  A second output (float form only) must be a value on the way to it:
+// it is stored by an EW_STORE2 step right after the op that produces it.
 std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const DeviceInfo& dev, ChainClass klass,
-                                                 std::string* why) {
+                                                 std::string* why, int final_idx = 0) {
   ChainBuilder cb(g, why);
   const bool int_class = klass == kIntChain, dbl_class = klass == kDoubleChain;
   cb.int_class = int_class;
   cb.dbl_class = dbl_class;
   if (dbl_class) cb.compute = DType::kFloat64;
-  if (g.outputs.size() != 1) {
-    cb.Fail("a chain has exactly one output");
+  if (g.outputs.size() != 1 && !(g.outputs.size() == 2 && klass == kFloatChain)) {
+    cb.Fail("a chain has one output (two in the float form)");
     return nullptr;
   }
   if (!cb.Infer()) return nullptr;
-  const TensorDesc& out = g.outputs[0];
+  const TensorDesc& out    = g.outputs[final_idx];
+  const TensorDesc* second = g.outputs.size() == 2 ? &g.outputs[1 - final_idx] : nullptr;
+  int second_stores        = 0;
+  if (second) {
+    const DType t = second->dtype;
+    if (!cb.values.count(second->name) || cb.values[second->name].dtype != t || second->numel() != out.numel() ||
+        !(t == DType::kFloat32 || t == DType::kFloat16 || t == DType::kBFloat16 || t == DType::kBool)) {
+      cb.Fail("the second output must be a float or bool value of the output's size");
+      return nullptr;
+    }
+  }
   if (!cb.values.count(out.name)) {
     cb.Fail("output is not produced by the group");
     return nullptr;
@@ -453,6 +465,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   std::map<std::string, int> uses;
   for (auto& o : g.ops)
     for (auto& in : o.inputs) ++uses[in];
+  if (second) ++uses[second->name];  // a group output is materialised: its product is not contracted into a later add
   auto single_use_mul = [&](const std::string& v) {
     const OpDesc* q = cb.producer.count(v) ? cb.producer[v] : nullptr;
     return q && q->type == "elementwise_mul" && uses[v] == 1 && cb.Arith(cb.values[v].dtype);
@@ -489,6 +502,13 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
     while (cb.producer.count(cur)) {
       const OpDesc& op = *cb.producer[cur];
       const Value& ov  = cb.values[cur];
+      if (second && cur == second->name) {
+        Step st;
+        st.op  = EW_STORE2;
+        st.f32 = false;
+        rev.push_back(st);  // runs right after the op (and the rounding) that produces this value
+        ++second_stores;
+      }
       if (ov.numel() != cb.n) {
         cb.Fail("value '" + cur + "' on the chain has " + std::to_string(ov.numel()) + " elements, the output " + std::to_string(cb.n));
         return false;
@@ -737,6 +757,10 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   };
   Segment main_seg;
   if (!walk(out.name, &main_seg)) return nullptr;
+  if (second && second_stores != 1) {
+    cb.Fail("output '" + second->name + "' is not a value on the way to output '" + out.name + "'");
+    return nullptr;
+  }
   if (!finish_start(&main_seg, segments.empty())) return nullptr;
   // Program order: sub-segments (innermost first), then the main walk.
   std::vector<Step> rev;  // the whole program, reversed
@@ -806,8 +830,9 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   p->elements = cb.n;
   for (auto& t : g.inputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
   p->algorithmic_bytes += out.numel() * DTypeBytes(out.dtype);
+  if (second) p->algorithmic_bytes += second->numel() * DTypeBytes(second->dtype);
   LaunchStep st;
-  const std::string ns = temps_used > 0 ? "_s3t" : std::string("_s") + (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3"));
+  const std::string ns = (temps_used > 0 || second) ? "_s3t" : std::string("_s") + (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3"));
   st.kernel = FindKernel(int_class ? std::string("ew_chain_int_") + DTypeKernelName(cb.compute) + "_" + DTypeKernelName(out.dtype) + ns
                          : dbl_class ? std::string("ew_chain_f64_") + DTypeKernelName(out.dtype) + ns
                                      : std::string("ew_chain_") + DTypeKernelName(out.dtype) + ns);
@@ -831,6 +856,8 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   aligned.ivalue = 1;
   if (in0 >= 0) aligned.aligned_inputs.push_back(in0);
   aligned.aligned_outputs.push_back(0);
+  if (second) aligned.aligned_outputs.push_back(1);
+  if (second) meta |= (int64_t)DTypeKernelCode(second->dtype) << 36;
   for (int k = 0; k < 3; ++k) {
     if (k < (int)cb.sides.size()) {
       const Side& s = cb.sides[k];
@@ -843,7 +870,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   }
   ArgSpec out_arg;
   out_arg.kind  = ArgSpec::kOutput;
-  out_arg.index = 0;
+  out_arg.index = final_idx;
   st.args.push_back(out_arg);
   st.args.push_back(int_arg(cb.n));
   st.args.push_back(aligned);
@@ -861,6 +888,12 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
       a.fvalue = k < (int)cb.dimms.size() ? cb.dimms[k] : 0.0;
       st.args.push_back(a);
     }
+  }
+  if (!int_class && !dbl_class) {  // the float kernels' last parameter: the second output (the first one when there is none)
+    ArgSpec o2;
+    o2.kind  = ArgSpec::kOutput;
+    o2.index = second ? 1 - final_idx : final_idx;
+    st.args.push_back(o2);
   }
   p->steps.push_back(st);
   return p;
@@ -969,6 +1002,7 @@ std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const Device
   }
   // Re-target the chain's launch: same 31 parameters (the program, the side operands), reduce geometry appended.
   LaunchStep st    = plan->steps[0];
+  st.args.resize(31);  // the chain kernel's own last parameter (its second output) is not one of these kernels'
   const std::string kname = st.kernel->name;
   const std::string ns    = kname.substr(kname.rfind('_'));  // "_s0" / "_s1" / "_s3" / "_s3t"
   auto int_arg = [](int64_t v) { ArgSpec a; a.kind = ArgSpec::kInt; a.ivalue = v; return a; };
@@ -1070,6 +1104,10 @@ std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const Device
 std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const DeviceInfo& dev, std::string* why) {
   std::string why_float, why_other;
   if (auto p = MatchChainOfClass(g, dev, kFloatChain, &why_float)) return p;
+  if (g.outputs.size() == 2) {
+    std::string why_swapped;
+    if (auto p = MatchChainOfClass(g, dev, kFloatChain, &why_swapped, 1)) return p;
+  }
   bool has_int = false, has_f64 = false;
   for (auto& t : g.inputs) has_int = has_int || IsIntType(t.dtype), has_f64 = has_f64 || t.dtype == DType::kFloat64;
   for (auto& t : g.outputs) has_int = has_int || IsIntType(t.dtype), has_f64 = has_f64 || t.dtype == DType::kFloat64;

@@ -16,7 +16,8 @@
 namespace cinn_b200 {
 namespace {
 
-// meta: bits 0-3 dtype of side 1, 4-7 mode of side 1, 8-11 / 12-15 side 2, 16-19 / 20-23 side 3, 24-27 dtype of in0.
+// meta: bits 0-3 dtype of side 1, 4-7 mode of side 1, 8-11 / 12-15 side 2, 16-19 / 20-23 side 3, 24-27 dtype of in0,
+// 36-39 storage type of the second output `out2` (written by EW_STORE2; kernels with temporaries only).
 // NT = 2: the variant with two temporaries for expression trees; it takes one vector per iteration so that the
 // temporaries fit the same register budget.
 template <typename OutT, int NS, int NT = 0>
@@ -26,10 +27,11 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
                long long mid1, long long inner1, long long mid2, long long inner2, long long mid3, long long inner3,
                long long nsteps_ll, long long t0, long long t1, long long t2, long long t3, long long t4,
                long long t5, long long t6, long long t7, long long t8, long long t9, long long t10, long long t11,
-               long long t12, long long t13, long long t14, long long t15) {
+               long long t12, long long t13, long long t14, long long t15, void* __restrict__ out2) {
   const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
   const int nsteps = (int)nsteps_ll;
   const int in_type = (int)((meta >> 24) & 15);
+  const int out2_type = (int)((meta >> 36) & 15);  // storage type of the second output (EW_STORE2)
   const SideSpec sd1 = {p1, (int)(meta & 15), (int)((meta >> 4) & 15), mid1, inner1};
   const SideSpec sd2 = {p2, (int)((meta >> 8) & 15), (int)((meta >> 12) & 15), mid2, inner2};
   const SideSpec sd3 = {p3, (int)((meta >> 16) & 15), (int)((meta >> 20) & 15), mid3, inner3};
@@ -66,7 +68,8 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
       if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
       if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
       if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
-      run_chain<4, NS, NT>(steps, nsteps, s1, s2, s3, acc);
+      const Store2 st2 = {out2, out2_type, i0};
+      run_chain<4, NS, NT>(steps, nsteps, s1, s2, s3, acc, NT > 0 ? &st2 : nullptr);
       store_vec4<OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -77,7 +80,8 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
     if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
     if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
     if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
-    run_chain<1, NS, NT>(steps, nsteps, s1, s2, s3, acc);
+    const Store2 st2 = {out2, out2_type, i};
+    run_chain<1, NS, NT>(steps, nsteps, s1, s2, s3, acc, NT > 0 ? &st2 : nullptr);
     store_one<OutT>(out, i, acc[0]);
   }
 }
@@ -85,10 +89,10 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
 }  // namespace
 
 #define REG_CHAIN(OUTNAME, OutT)                                                               \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s0", 31, 256, k_ew_chain<OutT, 0>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s1", 31, 256, k_ew_chain<OutT, 1>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3", 31, 256, k_ew_chain<OutT, 3>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3t", 31, 256, k_ew_chain<OutT, 3, 2>)
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s0", 32, 256, k_ew_chain<OutT, 0>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s1", 32, 256, k_ew_chain<OutT, 1>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3", 32, 256, k_ew_chain<OutT, 3>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3t", 32, 256, k_ew_chain<OutT, 3, 2>)
 REG_CHAIN("f32", float);
 REG_CHAIN("f16", __half);
 REG_CHAIN("bf16", __nv_bfloat16);

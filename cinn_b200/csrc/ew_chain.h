@@ -27,6 +27,7 @@ enum EwOp {
   EW_BAND = 23, EW_BOR, EW_BXOR, EW_SHL, EW_SHR, EW_LSHR,
   EW_COPY = 29,  // acc = operand: how a chain starts from a broadcast operand when no input has the output's size
   EW_STASH = 30, // temporary[A - 5] = acc (kernels with temporaries only)
+  EW_STORE2 = 31, // second output[i] = acc: a value on the way that is a group output too (same kernels)
   EW_FMA = 20,        // acc = fma(acc, A, B)
   EW_SCALE_PRE = 21,  // acc = imm * (acc + imm_next)
   EW_SELECT = 22,     // acc = cond ? t : f, see the role bits above

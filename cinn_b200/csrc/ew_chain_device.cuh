@@ -262,10 +262,37 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, float
 }
 
 // NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
-// NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees.
+// Where EW_STORE2 writes: the group's second output, its storage type (EwDType) and the flat index of acc[0].
+struct Store2 {
+  void* ptr;
+  int dtype;
+  long long i0;
+};
+
+template <int VEC>
+__device__ __forceinline__ void store_second(const Store2& st, const float (&a)[VEC]) {
+  if (VEC == 4 && st.dtype == EW_F32) {
+    __stcs(reinterpret_cast<uint4*>(static_cast<float*>(st.ptr) + st.i0), pack4(*reinterpret_cast<const float(*)[4]>(&a[0])));
+  } else if (VEC == 4 && st.dtype == EW_F16) {
+    __stcs(reinterpret_cast<uint2*>(static_cast<__half*>(st.ptr) + st.i0), make_uint2(pack_h2(a[0], a[1]), pack_h2(a[2], a[3])));
+  } else if (VEC == 4 && st.dtype == EW_BF16) {
+    __stcs(reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(st.ptr) + st.i0), make_uint2(pack_bf2(a[0], a[1]), pack_bf2(a[2], a[3])));
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      if (st.dtype == EW_F32) static_cast<float*>(st.ptr)[st.i0 + i] = a[i];
+      else if (st.dtype == EW_F16) static_cast<__half*>(st.ptr)[st.i0 + i] = __float2half_rn(a[i]);
+      else if (st.dtype == EW_BF16) static_cast<__nv_bfloat16*>(st.ptr)[st.i0 + i] = __float2bfloat16_rn(a[i]);
+      else static_cast<uint8_t*>(st.ptr)[st.i0 + i] = a[i] != 0.0f ? 1 : 0;
+    }
+  }
+}
+
+// NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees, and EW_STORE2.
 template <int VEC, int NS, int NT = 0>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const float (&s1)[VEC],
-                                          const float (&s2)[VEC], const float (&s3)[VEC], float (&acc)[VEC]) {
+                                          const float (&s2)[VEC], const float (&s3)[VEC], float (&acc)[VEC],
+                                          const Store2* st2 = nullptr) {
   float ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
   if (NT > 0) {
 #pragma unroll
@@ -282,6 +309,10 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
     if (op == EW_NOP) continue;
     if (op >= EW_FIRST_UNARY) {
       apply_unary<VEC>(op, imm, acc);
+      continue;
+    }
+    if (NT > 0 && op == EW_STORE2) {
+      if (st2) store_second<VEC>(*st2, acc);
       continue;
     }
     if (NT > 0 && op == EW_STASH) {

@@ -576,6 +576,36 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
     }
   }
 
+  // True if some path leaves `trial` and comes back into it, with every group formed so far taken as one node: the
+  // group of `trial` would then depend on a group that depends on it.
+  auto leaves_and_reenters = [&](const std::set<int>& trial) {
+    std::set<int> seen_instr, seen_group;
+    std::vector<int> stack;
+    auto push_consumers_of = [&](int i) {
+      for (int c : st.consumers_of_var[b.instrs()[i].output])
+        if (!trial.count(c)) stack.push_back(c);
+    };
+    for (int i : trial) push_consumers_of(i);
+    while (!stack.empty()) {
+      const int c = stack.back();
+      stack.pop_back();
+      if (group_of[c] == -2 || !seen_instr.insert(c).second) continue;
+      std::vector<int> node = {c};
+      if (group_of[c] >= 0) {
+        if (!seen_group.insert(group_of[c]).second) continue;
+        node.assign(sets[group_of[c]].begin(), sets[group_of[c]].end());
+      }
+      for (int i : node) {
+        seen_instr.insert(i);
+        for (int d : st.consumers_of_var[b.instrs()[i].output]) {
+          if (trial.count(d)) return true;
+          stack.push_back(d);
+        }
+      }
+    }
+    return false;
+  };
+
   // Step 2: vertical fusion, consumer first (the reference walks the graph in reverse topological order,
   // cinn/hlir/pass/op_fusion_pass.cc:94-95): a producer joins its consumer's group when all of its uses are
   // inside the group and a kernel exists for the enlarged group.
@@ -590,13 +620,22 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
           int p = st.producer_of_var[v];
           if (p < 0 || members.count(p) || group_of[p] >= 0 || st.IsConst(p)) continue;
           if (PatternOf(b.instrs()[p].op_type) == OpPattern::kNonFusible) continue;
-          if (st.fetch.count(b.instrs()[p].output)) continue;
-          bool all_inside = true;
+          bool all_inside = !st.fetch.count(b.instrs()[p].output);
           for (int c : st.consumers_of_var[b.instrs()[p].output])
             if (!members.count(c)) all_inside = false;
-          if (!all_inside) continue;
           std::set<int> trial = members;
           trial.insert(p);
+          if (!all_inside) {
+            // The producer's result is needed outside as well (fetched, or read by another group): it may still join
+            // as a second output of the group (the reference's groups keep such values as output nodes,
+            // cinn/hlir/framework/op_lowering.cc:121-151) when a kernel exists for the two-output group and no other
+            // group ends up both behind and in front of this one.
+            if (!leaves_and_reenters(trial) && st.Compiles(trial, nullptr, nullptr)) {
+              members = trial;
+              grew    = true;
+            }
+            continue;
+          }
           if (st.Compiles(trial, nullptr, nullptr)) {
             members = trial;
             grew    = true;
@@ -768,7 +807,14 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
         for (int d : deps[gidx]) ready = ready && done[d];
         if (ready && (pick < 0 || *sets[gidx].begin() < *sets[pick].begin())) pick = gidx;
       }
-      if (pick < 0) break;  // only empty sets were left
+      if (pick < 0) {
+        for (int gidx = 0; gidx < ng; ++gidx)
+          if (!done[gidx] && !sets[gidx].empty()) {
+            if (err) *err = "internal error: the fused groups depend on one another";
+            return false;
+          }
+        break;  // only empty sets were left
+      }
       done[pick] = true;
       ++emitted;
       order.push_back(pick);

@@ -1390,8 +1390,13 @@ struct Matcher {
       if (auto p = MatchChannelStats(expr)) return p;
       if (err && !err->empty()) return nullptr;
       if (auto p = MatchBnGradStats(expr)) return p;
-      if (err && err->empty())
-        Fail("groups with " + std::to_string(g.outputs.size()) + " outputs have no prebuilt kernel (" + expr + ")");
+      if (err && !err->empty()) return nullptr;
+      // An elementwise chain one of whose intermediate values is an output too.
+      std::string why2;
+      if (g.outputs.size() == 2)
+        if (auto p = MatchGenericChain(g, dev, &why2)) return p;
+      Fail("groups with " + std::to_string(g.outputs.size()) + " outputs have no prebuilt kernel (" + expr +
+           (why2.empty() ? std::string(")") : "; as a chain with a second output: " + why2 + ")"));
       return nullptr;
     }
     typedef std::unique_ptr<CompiledGroup> (Matcher::*Fn)(const std::string&);

@@ -25,6 +25,14 @@ def run_program(builder, feeds, fetch):
     return comp, {str(f): comp.get_tensor(str(f)).numpy(TARGET) for f in fetch}
 
 
+def run_program_fetch(builder, feeds, fetch):
+    comp = Computation.build_and_compile(TARGET, builder, fetch=[str(f) for f in fetch])
+    for name, arr in feeds.items():
+        comp.get_tensor(name).from_numpy(arr, TARGET)
+    comp.execute()
+    return comp, {str(f): comp.get_tensor(str(f)).numpy(TARGET) for f in fetch}
+
+
 def oracle_program(comp, feeds):
     """Evaluate the computation's groups in order with the oracle, feeding each group from the values so far."""
     vals = dict(feeds)
@@ -984,3 +992,64 @@ def test_sixteen_bit_batch_norm_grad(dtype, shape):
     assert bool(((dscale.double() - S * inv.reshape(-1)).abs()
                  <= 3e-5 * (d["dy"] * (d["x"] - m)).abs().sum(dim=(0, 2, 3)) * inv.reshape(-1) + 1e-6).all())
     assert bool(((dx.double() - want).abs() <= 1e-2 * want.abs() + 1e-2 * want.abs().max()).all())
+
+
+# ---- elementwise groups with two outputs: a value on the way is stored as well ------------------------------------
+@pytest.mark.parametrize("shape", [(64, 1024), (33, 1001), (1024, 4096)])
+def test_pre_activation_and_activation_from_one_kernel(oracle, shape):
+    rng = np.random.default_rng(81)
+    feeds = {"X": rng.standard_normal(shape).astype(np.float32), "B": rng.standard_normal(shape[-1]).astype(np.float32)}
+    b = NetBuilder("two_out")
+    x = b.create_input(common.Float(32), shape, "X")
+    bias = b.create_input(common.Float(32), (shape[-1],), "B")
+    pre = b.add(x, bias)
+    act = b.tanh(b.relu(pre))
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(pre), str(act)])
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s3t"], comp.groups()
+    for name, arr in feeds.items():
+        comp.get_tensor(name).from_numpy(arr, TARGET)
+    comp.execute()
+    ref = oracle_program(comp, feeds)
+    assert oracle.max_ulp(comp.get_tensor(str(pre)).numpy(TARGET), ref[str(pre)]) == 0
+    assert oracle.max_ulp(comp.get_tensor(str(act)).numpy(TARGET), ref[str(act)]) <= 2
+
+
+def test_second_output_of_another_type_and_no_contraction_across_it(oracle):
+    """A stored product is read back by the add in the reference (an output node is not inlined), so no fused
+    multiply-add there; the second output may be a bool or a 16-bit value."""
+    rng = np.random.default_rng(82)
+    shape = (128, 1000)
+    feeds = {n: rng.standard_normal(shape).astype(np.float32) for n in "ABC"}
+    b = NetBuilder("two_out")
+    A, B, C = (b.create_input(common.Float(32), shape, n) for n in "ABC")
+    prod = b.multiply(A, B)
+    total = b.add(prod, C)
+    comp, got = run_program_fetch(b, feeds, [prod, total])
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s3t"], comp.groups()
+    assert np.array_equal(got[str(prod)], feeds["A"] * feeds["B"])
+    assert np.array_equal(got[str(total)], feeds["A"] * feeds["B"] + feeds["C"])  # rounded product, then the add
+    b = NetBuilder("two_out")
+    A, B, C = (b.create_input(common.Float(32), shape, n) for n in "ABC")
+    mask = b.greater_than(A, B)
+    half = b.cast(b.select(mask, A, C), "float16")
+    comp, got = run_program_fetch(b, feeds, [mask, half])
+    assert len(comp.groups()) == 1 and "s3t" in comp.groups()[0][1], comp.groups()
+    assert np.array_equal(got[str(mask)], feeds["A"] > feeds["B"])
+    want = np.where(feeds["A"] > feeds["B"], feeds["A"], feeds["C"]).astype(np.float16)
+    assert np.array_equal(got[str(half)].view(np.uint16), want.view(np.uint16))
+
+
+def test_value_with_two_consumers_is_computed_once(oracle):
+    rng = np.random.default_rng(83)
+    X = rng.standard_normal((256, 2048)).astype(np.float32)
+    b = NetBuilder("fanout")
+    x = b.create_input(common.Float(32), X.shape, "X")
+    e = b.exp(x)
+    s = b.reduce_sum(e, [1])
+    y = b.tanh(b.scale(e, 2.0, 0.0, True))
+    comp, got = run_program_fetch(b, {"X": X}, [s, y])
+    assert len(comp.groups()) == 2, comp.groups()
+    ref = oracle_program(comp, {"X": X})
+    assert oracle.max_ulp(got[str(y)], ref[str(y)]) <= 2
+    exact = np.exp(X.astype(np.float64)).sum(axis=1)
+    assert np.allclose(got[str(s)], exact, rtol=1e-5)
