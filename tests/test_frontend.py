@@ -328,3 +328,46 @@ def test_expression_trees_compile_into_one_kernel_with_temporaries():
     b, (A, B, C, D) = build()
     b.add(b.multiply(b.exp(A), b.tanh(B)), b.multiply(b.sqrt(b.abs(C)), b.sigmoid(D)))
     assert len(plan(b).groups()) > 1
+
+
+def _assert_topological(c, program_inputs):
+    """Every group reads program inputs or results of earlier groups."""
+    known = set(program_inputs)
+    for desc, _ in c.groups():
+        lines = desc.splitlines()
+        for ln in lines:
+            if ln.startswith("input "):
+                assert ln.split()[1] in known, (ln, [p for _, p in c.groups()])
+        for ln in lines:
+            if ln.startswith("output "):
+                known.add(ln.split()[1])
+            if ln.startswith("op reshape"):
+                known.add(ln.split()[2])
+
+
+def test_two_output_groups_and_no_group_cycles():
+    # a fetched intermediate is stored on the way: one kernel
+    b = NetBuilder("two_out")
+    x = b.create_input(common.Float(32), (64, 1024), "X")
+    bias = b.create_input(common.Float(32), (1024,), "B")
+    pre = b.add(x, bias)
+    act = b.tanh(b.relu(pre))
+    c = plan(b, fetch=[pre, act])
+    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s3t"]
+    # siblings (neither is on the way to the other) stay two kernels
+    b = NetBuilder("siblings")
+    x = b.create_input(common.Float(32), (64, 1024), "X")
+    t = b.exp(x)
+    c = plan(b, fetch=[b.relu(t), b.tanh(t)])
+    assert len(c.groups()) == 2
+    _assert_topological(c, ["X"])
+    # exp may not join the subtract: its other user (the reduction) feeds the subtract as well, and the two groups
+    # would wait for each other
+    b = NetBuilder("no_cycle")
+    x = b.create_input(common.Float(32), (64, 1024), "X")
+    e = b.exp(x)
+    m = b.reduce_max(e, [1])
+    b.subtract(e, b.broadcast_to(m, [64, 1024], [0]))
+    c = plan(b)
+    _assert_topological(c, ["X"])
+    assert len(c.groups()) >= 2
