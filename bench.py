@@ -236,6 +236,8 @@ def side_groups(torch, dev, peak, only=None):
         ("generic_reduce_sum_i32_cols_16384x8192", lambda: W.generic_reduce("sum", "int32", axis=0), 1, ""),
         ("generic_reduce_all_bool_rows_16384x8192", lambda: W.generic_reduce("all", "bool", axis=1), 4, ""),
         ("generic_tree_f32_8192x8192", lambda: W.chain_tree(), 1, "(A+B)*(C-D): chain kernel with temporaries"),
+        ("generic_two_outputs_f32_8192x8192", lambda: W.chain_two_outputs(), 1,
+         "pre = X + bias and relu(pre) from one kernel: one read, two writes"),
         ("bn_train_stats_f16_256x64x112x112", lambda: W.bn_train_stats((256, 64, 112, 112), half=True), 1,
          "fp16 x widened in the load; sum and sum of squares per channel"),
         ("bn_train_apply_f16_256x64x112x112", lambda: W.bn_train_apply((256, 64, 112, 112), half=True), 1, "fp16 storage"),

@@ -832,7 +832,8 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   p->algorithmic_bytes += out.numel() * DTypeBytes(out.dtype);
   if (second) p->algorithmic_bytes += second->numel() * DTypeBytes(second->dtype);
   LaunchStep st;
-  const std::string ns = (temps_used > 0 || second) ? "_s3t" : std::string("_s") + (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3"));
+  // _s3t: temporaries (and a second output); _s1o / _s3o: a second output without temporaries; else by operand count
+  const std::string ns = temps_used > 0 ? "_s3t" : second ? (cb.sides.size() <= 1 ? "_s1o" : "_s3o") : std::string("_s") + (cb.sides.empty() ? "0" : (cb.sides.size() == 1 ? "1" : "3"));
   st.kernel = FindKernel(int_class ? std::string("ew_chain_int_") + DTypeKernelName(cb.compute) + "_" + DTypeKernelName(out.dtype) + ns
                          : dbl_class ? std::string("ew_chain_f64_") + DTypeKernelName(out.dtype) + ns
                                      : std::string("ew_chain_") + DTypeKernelName(out.dtype) + ns);

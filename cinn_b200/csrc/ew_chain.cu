@@ -20,7 +20,8 @@ namespace {
 // 36-39 storage type of the second output `out2` (written by EW_STORE2; kernels with temporaries only).
 // NT = 2: the variant with two temporaries for expression trees; it takes one vector per iteration so that the
 // temporaries fit the same register budget.
-template <typename OutT, int NS, int NT = 0>
+// ST2: the variant whose programs may store a second output (EW_STORE2) into `out2`.
+template <typename OutT, int NS, int NT = 0, bool ST2 = (NT > 0)>
 __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
     k_ew_chain(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
                const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
@@ -56,7 +57,8 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
         if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, *reinterpret_cast<float(*)[4]>(&s2[4 * j]));
         if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, *reinterpret_cast<float(*)[4]>(&s3[4 * j]));
       }
-      run_chain<8, NS, 0>(steps, nsteps, s1, s2, s3, acc);
+      const Store2 st2 = {out2, out2_type, v << 2, (v + stride) << 2};
+      run_chain<8, NS, 0, ST2>(steps, nsteps, s1, s2, s3, acc, ST2 ? &st2 : nullptr);
 #pragma unroll
       for (int j = 0; j < 2; ++j)
         store_vec4<OutT>(out, (v + j * stride) << 2, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
@@ -68,8 +70,8 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
       if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
       if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
       if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
-      const Store2 st2 = {out2, out2_type, i0};
-      run_chain<4, NS, NT>(steps, nsteps, s1, s2, s3, acc, NT > 0 ? &st2 : nullptr);
+      const Store2 st2 = {out2, out2_type, i0, 0};
+      run_chain<4, NS, NT, ST2>(steps, nsteps, s1, s2, s3, acc, ST2 ? &st2 : nullptr);
       store_vec4<OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -80,8 +82,8 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
     if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
     if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
     if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
-    const Store2 st2 = {out2, out2_type, i};
-    run_chain<1, NS, NT>(steps, nsteps, s1, s2, s3, acc, NT > 0 ? &st2 : nullptr);
+    const Store2 st2 = {out2, out2_type, i, 0};
+    run_chain<1, NS, NT, ST2>(steps, nsteps, s1, s2, s3, acc, ST2 ? &st2 : nullptr);
     store_one<OutT>(out, i, acc[0]);
   }
 }
@@ -92,7 +94,9 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
   CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s0", 32, 256, k_ew_chain<OutT, 0>);        \
   CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s1", 32, 256, k_ew_chain<OutT, 1>);        \
   CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3", 32, 256, k_ew_chain<OutT, 3>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3t", 32, 256, k_ew_chain<OutT, 3, 2>)
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3t", 32, 256, k_ew_chain<OutT, 3, 2>);    \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s1o", 32, 256, k_ew_chain<OutT, 1, 0, true>); \
+  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3o", 32, 256, k_ew_chain<OutT, 3, 0, true>)
 REG_CHAIN("f32", float);
 REG_CHAIN("f16", __half);
 REG_CHAIN("bf16", __nv_bfloat16);

@@ -267,10 +267,16 @@ struct Store2 {
   void* ptr;
   int dtype;
   long long i0;
+  long long i1;  // VEC = 8 only: the flat index of acc[4] (the second vector)
 };
 
 template <int VEC>
 __device__ __forceinline__ void store_second(const Store2& st, const float (&a)[VEC]) {
+  if constexpr (VEC == 8) {
+    store_second<4>(Store2{st.ptr, st.dtype, st.i0, 0}, *reinterpret_cast<const float(*)[4]>(&a[0]));
+    store_second<4>(Store2{st.ptr, st.dtype, st.i1, 0}, *reinterpret_cast<const float(*)[4]>(&a[4]));
+    return;
+  }
   if (VEC == 4 && st.dtype == EW_F32) {
     __stcs(reinterpret_cast<uint4*>(static_cast<float*>(st.ptr) + st.i0), pack4(*reinterpret_cast<const float(*)[4]>(&a[0])));
   } else if (VEC == 4 && st.dtype == EW_F16) {
@@ -289,7 +295,8 @@ __device__ __forceinline__ void store_second(const Store2& st, const float (&a)[
 }
 
 // NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees, and EW_STORE2.
-template <int VEC, int NS, int NT = 0>
+// ST2: the program may hold EW_STORE2 steps (st2 then says where they write).
+template <int VEC, int NS, int NT = 0, bool ST2 = (NT > 0)>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const float (&s1)[VEC],
                                           const float (&s2)[VEC], const float (&s3)[VEC], float (&acc)[VEC],
                                           const Store2* st2 = nullptr) {
@@ -311,7 +318,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       apply_unary<VEC>(op, imm, acc);
       continue;
     }
-    if (NT > 0 && op == EW_STORE2) {
+    if (ST2 && op == EW_STORE2) {
       if (st2) store_second<VEC>(*st2, acc);
       continue;
     }

@@ -264,6 +264,17 @@ def chain_tree(shape=(8192, 8192), seed=9):
                     np.float32, shape)
 
 
+def chain_two_outputs(shape=(8192, 8192), seed=10):
+    """pre = X + bias (kept for the backward pass) and act = relu(pre): one kernel, two outputs."""
+    s = _shape(shape)
+    desc = (f"group fn_pre_act\ninput X float32 {s}\ninput B float32 {shape[-1]}\n"
+            f"op elementwise_add pre = X B ; axis=-1\nop relu act = pre\noutput pre float32 {s}\noutput act float32 {s}\n")
+    return Workload("chain_two_outputs", desc,
+                    lambda: [_draw(np.random.default_rng(seed), shape, "float32"),
+                             _draw(np.random.default_rng(seed + 1), (shape[-1],), "float32")],
+                    np.float32, shape, more_outputs=[(np.float32, shape)])
+
+
 def chain_reduce(kind="sum_abs_diff", shape=(8192, 8192), axis=1, seed=8):
     """A reduction whose operand is an elementwise chain, one kernel: `sum_abs_diff` = reduce_sum(|x - y|) of two
     tensors, `sum_sigmoid_affine` = reduce_sum(sigmoid((x + b) * b)) with a row vector b."""

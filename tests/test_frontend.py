@@ -149,7 +149,7 @@ def test_value_used_twice_is_materialised_once():
     b.tanh(t)
     c = plan(b)
     # exp joins one of its consumers as a second output of that group; the other consumer reads the stored value
-    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s3t", "ew_chain ew_chain_f32_s0"]
+    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s1o", "ew_chain ew_chain_f32_s0"]
     assert str(t) in c.get_all_tensor_names()
 
 
@@ -161,7 +161,7 @@ def test_fetch_keeps_an_intermediate():
     assert len(plan(b).groups()) == 1
     c = plan(b, fetch=[t, y])
     # one kernel with two outputs: the fetched intermediate is stored on the way
-    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s3t"] and str(t) in c.get_all_tensor_names()
+    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s1o"] and str(t) in c.get_all_tensor_names()
 
 
 def test_unmatched_group_is_an_error_not_a_fallback():
@@ -353,7 +353,7 @@ def test_two_output_groups_and_no_group_cycles():
     pre = b.add(x, bias)
     act = b.tanh(b.relu(pre))
     c = plan(b, fetch=[pre, act])
-    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s3t"]
+    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s1o"]
     # siblings (neither is on the way to the other) stay two kernels
     b = NetBuilder("siblings")
     x = b.create_input(common.Float(32), (64, 1024), "X")

@@ -1005,7 +1005,7 @@ def test_pre_activation_and_activation_from_one_kernel(oracle, shape):
     pre = b.add(x, bias)
     act = b.sigmoid(b.relu(pre))
     comp = Computation.build_and_compile(TARGET, b, fetch=[str(pre), str(act)])
-    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s3t"], comp.groups()
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s1o"], comp.groups()
     for name, arr in feeds.items():
         comp.get_tensor(name).from_numpy(arr, TARGET)
     comp.execute()
@@ -1025,7 +1025,7 @@ def test_second_output_of_another_type_and_no_contraction_across_it(oracle):
     prod = b.multiply(A, B)
     total = b.add(prod, C)
     comp, got = run_program_fetch(b, feeds, [prod, total])
-    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s3t"], comp.groups()
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f32_s3o"], comp.groups()
     assert np.array_equal(got[str(prod)], feeds["A"] * feeds["B"])
     assert np.array_equal(got[str(total)], feeds["A"] * feeds["B"] + feeds["C"])  # rounded product, then the add
     b = NetBuilder("two_out")
@@ -1033,7 +1033,7 @@ def test_second_output_of_another_type_and_no_contraction_across_it(oracle):
     mask = b.greater_than(A, B)
     half = b.cast(b.select(mask, A, C), "float16")
     comp, got = run_program_fetch(b, feeds, [mask, half])
-    assert len(comp.groups()) == 1 and "s3t" in comp.groups()[0][1], comp.groups()
+    assert len(comp.groups()) == 1 and "s3o" in comp.groups()[0][1], comp.groups()
     assert np.array_equal(got[str(mask)], feeds["A"] > feeds["B"])
     want = np.where(feeds["A"] > feeds["B"], feeds["A"], feeds["C"]).astype(np.float16)
     assert np.array_equal(got[str(half)].view(np.uint16), want.view(np.uint16))
