@@ -393,7 +393,7 @@ bool Ok2(const ChainBuilder& cb, DType t) { return cb.Ok(t); }
 // `final_idx`: which output the chain ends at.  A second output (float form only) must be a value on the way to it:
 // it is stored by an EW_STORE2 step right after the op that produces it.
 std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const DeviceInfo& dev, ChainClass klass,
-                                                 std::string* why, int final_idx = 0) {
+                                                 std::string* why, int final_idx = 0, bool allow_sibling = false) {
   ChainBuilder cb(g, why);
   const bool int_class = klass == kIntChain, dbl_class = klass == kDoubleChain;
   cb.int_class = int_class;
@@ -757,8 +757,17 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
   };
   Segment main_seg;
   if (!walk(out.name, &main_seg)) return nullptr;
+  if (second && second_stores == 0 && allow_sibling) {
+    // The second output is not on the way to the first: a sibling (two expressions over shared inputs, the
+    // reference's horizontal fusion, cinn/hlir/pass/fusion_merge_pass.cc:85-460).  It is evaluated first as a segment
+    // of its own that ends in the store; the main walk then restarts from its own input.
+    Segment sg;
+    if (!walk(second->name, &sg)) return nullptr;
+    if (!finish_start(&sg, segments.empty())) return nullptr;
+    segments.push_back(sg);
+  }
   if (second && second_stores != 1) {
-    cb.Fail("output '" + second->name + "' is not a value on the way to output '" + out.name + "'");
+    cb.Fail("output '" + second->name + (second_stores ? "' would have to be stored more than once" : "' is not a value on the way to the other output"));
     return nullptr;
   }
   if (!finish_start(&main_seg, segments.empty())) return nullptr;
@@ -1106,8 +1115,11 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
   std::string why_float, why_other;
   if (auto p = MatchChainOfClass(g, dev, kFloatChain, &why_float)) return p;
   if (g.outputs.size() == 2) {
-    std::string why_swapped;
-    if (auto p = MatchChainOfClass(g, dev, kFloatChain, &why_swapped, 1)) return p;
+    // first the forms where one output lies on the way to the other (nothing is computed twice), then siblings
+    std::string w;
+    if (auto p = MatchChainOfClass(g, dev, kFloatChain, &w, 1)) return p;
+    if (auto p = MatchChainOfClass(g, dev, kFloatChain, &w, 0, true)) return p;
+    if (auto p = MatchChainOfClass(g, dev, kFloatChain, &w, 1, true)) return p;
   }
   bool has_int = false, has_f64 = false;
   for (auto& t : g.inputs) has_int = has_int || IsIntType(t.dtype), has_f64 = has_f64 || t.dtype == DType::kFloat64;

@@ -781,6 +781,39 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
     }
   }
 
+  // Step 4: horizontal fusion of elementwise groups that read the same tensor (the same pass of the reference): two
+  // groups become one two-output group when a kernel exists for it (the chain kernel evaluates one expression,
+  // stores it, and restarts for the other) and no other group ends up both behind and in front of the merged one.
+  {
+    auto plain_elementwise = [&](const std::set<int>& m) {
+      for (int i : m) {
+        const OpPattern p = PatternOf(b.instrs()[i].op_type);
+        if (p == OpPattern::kReduction || p == OpPattern::kNonFusible) return false;
+      }
+      return !m.empty();
+    };
+    for (size_t i = 0; i < sets.size(); ++i) {
+      if (!plain_elementwise(sets[i])) continue;
+      for (size_t j = i + 1; j < sets.size(); ++j) {
+        if (!plain_elementwise(sets[j])) continue;
+        const FusedGroupInfo gi = st.Describe(sets[i]), gj = st.Describe(sets[j]);
+        if (gi.output_vars.size() != 1 || gj.output_vars.size() != 1) continue;
+        if (b.vars()[gi.output_vars[0]].shape != b.vars()[gj.output_vars[0]].shape) continue;
+        bool shared = false;
+        for (int v : gj.input_vars)
+          shared = shared || std::find(gi.input_vars.begin(), gi.input_vars.end(), v) != gi.input_vars.end();
+        if (!shared) continue;
+        std::set<int> merged = sets[i];
+        merged.insert(sets[j].begin(), sets[j].end());
+        if (leaves_and_reenters(merged) || !st.Compiles(merged, nullptr, nullptr)) continue;
+        for (int k : sets[j]) group_of[k] = (int)i;
+        sets[i] = merged;
+        sets[j].clear();
+        break;  // a group has two outputs at most
+      }
+    }
+  }
+
   // Emit in a topological order of the groups (a group after the groups that produce its inputs), ties by program
   // order; every group must compile.
   std::vector<int> order;

@@ -140,17 +140,17 @@ def test_elementwise_producer_folds_into_reduction():
     assert [p for _, p in c.groups()] == ["row_reduce row_reduce_cta_sumsq_f32", "ew_chain ew_chain_f32_s0"]
 
 
-def test_value_used_twice_is_materialised_once():
-    """A producer with two consumers is not duplicated: it becomes a group output (op_lowering_util.cc:745-803)."""
+def test_value_used_twice_feeds_two_outputs_of_one_kernel():
+    """Two elementwise consumers of one value are fused horizontally (fusion_merge_pass.cc:85-460)."""
     b = NetBuilder("fanout")
     x = b.create_input(common.Float(32), (64, 64), "X")
     t = b.exp(x)
     b.relu(t)
     b.tanh(t)
     c = plan(b)
-    # exp joins one of its consumers as a second output of that group; the other consumer reads the stored value
-    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s1o", "ew_chain ew_chain_f32_s0"]
-    assert str(t) in c.get_all_tensor_names()
+    # the two consumers are siblings over one input: one kernel with two outputs, exp never reaches memory
+    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s1o"]
+    assert str(t) not in c.get_all_tensor_names()
 
 
 def test_fetch_keeps_an_intermediate():
@@ -354,11 +354,16 @@ def test_two_output_groups_and_no_group_cycles():
     act = b.tanh(b.relu(pre))
     c = plan(b, fetch=[pre, act])
     assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s1o"]
-    # siblings (neither is on the way to the other) stay two kernels
+    # siblings (neither is on the way to the other): one kernel that evaluates one, stores it and restarts
     b = NetBuilder("siblings")
     x = b.create_input(common.Float(32), (64, 1024), "X")
     t = b.exp(x)
     c = plan(b, fetch=[b.relu(t), b.tanh(t)])
+    assert [p for _, p in c.groups()] == ["ew_chain ew_chain_f32_s1o"]
+    # three siblings: two in one kernel, the third on its own
+    b = NetBuilder("siblings3")
+    x = b.create_input(common.Float(32), (64, 1024), "X")
+    c = plan(b, fetch=[b.relu(x), b.tanh(x), b.exp(x)])
     assert len(c.groups()) == 2
     _assert_topological(c, ["X"])
     # exp may not join the subtract: its other user (the reduction) feeds the subtract as well, and the two groups

@@ -1053,3 +1053,28 @@ def test_value_with_two_consumers_is_computed_once(oracle):
     assert oracle.max_ulp(got[str(y)], ref[str(y)]) <= 2
     exact = np.exp(X.astype(np.float64)).sum(axis=1)
     assert np.allclose(got[str(s)], exact, rtol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(64, 1024), (33, 1001), (1024, 4096)])
+def test_sibling_expressions_share_one_kernel(oracle, shape):
+    """Two expressions over the same inputs, neither on the way to the other: horizontal fusion."""
+    rng = np.random.default_rng(84)
+    feeds = {"X": rng.standard_normal(shape).astype(np.float32), "B": rng.standard_normal(shape[-1]).astype(np.float32)}
+    b = NetBuilder("siblings")
+    x = b.create_input(common.Float(32), shape, "X")
+    bias = b.create_input(common.Float(32), (shape[-1],), "B")
+    y1 = b.relu(b.add(x, bias))
+    y2 = b.multiply(b.subtract(x, bias), bias)
+    comp, got = run_program_fetch(b, feeds, [y1, y2])
+    assert len(comp.groups()) == 1 and "ew_chain_f32_s" in comp.groups()[0][1], comp.groups()
+    ref = oracle_program(comp, feeds)
+    assert oracle.max_ulp(got[str(y1)], ref[str(y1)]) == 0 and oracle.max_ulp(got[str(y2)], ref[str(y2)]) == 0
+    # a shared prefix is evaluated for each output; the results are the same bits
+    b = NetBuilder("siblings_prefix")
+    x = b.create_input(common.Float(32), shape, "X")
+    t = b.sqrt(b.abs(x))
+    z1, z2 = b.relu(b.negative(t)), b.scale(t, 3.0, 1.0, True)
+    comp, got = run_program_fetch(b, {"X": feeds["X"]}, [z1, z2])
+    assert len(comp.groups()) == 1, comp.groups()
+    ref = oracle_program(comp, {"X": feeds["X"]})
+    assert oracle.max_ulp(got[str(z1)], ref[str(z1)]) == 0 and oracle.max_ulp(got[str(z2)], ref[str(z2)]) == 0
