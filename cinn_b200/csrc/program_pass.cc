@@ -6,6 +6,7 @@
 //   AutoCast          cinn/frontend/pass/auto_cast.cc:31-214     fp16 / bf16 operands of listed ops computed in fp32
 //   AutoBroadcast     cinn/frontend/pass/auto_broadcast.cc:32-125 explicit broadcast_to in front of binary ops
 //   CastCollapsing    cinn/frontend/pass/cast_collapsing.cc:50-301 chains of casts folded into one
+//   TransposeCollapsing cinn/frontend/pass/transpose_collapsing.cc:60-340 chains of transposes folded into one
 //   RemoveIdentity    cinn/frontend/pass/remove_identity.cc:23-262 ops that change nothing removed
 //   DeadCodeEliminate cinn/frontend/pass/dead_code_eliminate.cc   instructions no fetched variable depends on removed
 // Each pass here rebuilds the builder's instruction list in place; the variable table only grows, so variable indices
@@ -131,34 +132,53 @@ bool AutoBroadcast(NetBuilder* b, std::string* err) {
   return true;
 }
 
-// ---- CastCollapsing ----------------------------------------------------------------------------------
-// cast_collapsing.cc:111-248: every chain of casts is walked from its first cast; a cast all of whose users are casts
-// hands its operand to them and disappears, a cast to its operand's own type disappears (or, when fetched, becomes an
-// identity), a cast nothing uses and nobody fetches disappears.  As in the reference a program with a single cast is
-// left alone, and the user lists are those of the program before the pass.
-struct CastCollapser {
+// ---- CastCollapsing / TransposeCollapsing -------------------------------------------------------------
+// cast_collapsing.cc:111-248 and transpose_collapsing.cc:119-290, which share one algorithm: every chain of casts
+// (transposes) is walked from its first one; an op all of whose users are of the same kind hands its operand to them
+// and disappears (a transpose composes its permutation into theirs), an op that changes nothing - a cast to its
+// operand's own type, an identity permutation - disappears (or, when fetched, becomes an identity), an op nothing
+// uses and nobody fetches disappears.  As in the reference a program with a single such op is left alone, and the
+// user lists are those of the program before the pass.
+struct Collapser {
   NetBuilder* b;
+  std::string kind;  // "cast" or "transpose"
   std::vector<ProgramInstr> ins;
   std::set<int> fetch;
   std::vector<std::vector<int>> users;  // per variable: instructions reading it (before the pass)
   std::vector<int> producer;            // per variable
   std::set<int> removed, visited;
 
-  DType TypeOf(int v) const { return b->vars()[v].dtype; }
+  bool ChangesNothing(const ProgramInstr& c) const {
+    if (kind == "cast") return b->vars()[c.inputs[0]].dtype == b->vars()[c.output].dtype;
+    const std::vector<int64_t> perm = IntList(c.attrs.count("axis") ? c.attrs.at("axis") : "");
+    for (size_t i = 0; i < perm.size(); ++i)
+      if (perm[i] != (int64_t)i) return false;
+    return true;
+  }
+
+  // `first` then `second`, as one op written into `second`.
+  void Compose(const ProgramInstr& first, ProgramInstr* second) const {
+    second->inputs[0] = first.inputs[0];
+    if (kind == "cast") return;  // the second cast keeps its own target type
+    const std::vector<int64_t> p1 = IntList(first.attrs.at("axis")), p2 = IntList(second->attrs.at("axis"));
+    std::vector<int64_t> fused(p2.size());
+    for (size_t i = 0; i < p2.size(); ++i) fused[i] = p1[p2[i]];  // out[i] = mid[p2[i]] and mid[j] = in[p1[j]]
+    second->attrs["axis"] = JoinList(fused);
+  }
 
   void Fuse(int i) {
     visited.insert(i);
-    ProgramInstr& c      = ins[i];
-    const int in         = c.inputs[0], out = c.output;
-    const bool fetched   = fetch.count(out) > 0;
-    const bool same_type = TypeOf(in) == TypeOf(out);
+    ProgramInstr& c    = ins[i];
+    const int in       = c.inputs[0], out = c.output;
+    const bool fetched = fetch.count(out) > 0;
+    const bool useless = ChangesNothing(c);
     const std::vector<int>& next = users[out];
     if (next.empty()) {
       if (!fetched) removed.insert(i);
-      else if (same_type) ToIdentity(&c);
+      else if (useless) ToIdentity(&c);
       return;
     }
-    if (same_type) {
+    if (useless) {
       if (fetched) {
         ToIdentity(&c);
         return;
@@ -168,20 +188,20 @@ struct CastCollapser {
           if (v == out) v = in;
       removed.insert(i);
       for (int u : next)
-        if (ins[u].op_type == "cast") Fuse(u);
+        if (ins[u].op_type == kind) Fuse(u);
       return;
     }
-    bool any_cast = false;
-    for (int u : next) any_cast = any_cast || ins[u].op_type == "cast";
-    if (!any_cast) return;
+    bool any_same = false;
+    for (int u : next) any_same = any_same || ins[u].op_type == kind;
+    if (!any_same) return;
     bool can_remove = !fetched;
     std::vector<int> fused;
     for (int u : next) {
-      if (ins[u].op_type != "cast") {
+      if (ins[u].op_type != kind) {
         can_remove = false;
         continue;
       }
-      ins[u].inputs[0] = in;  // the second cast keeps its own target type
+      Compose(c, &ins[u]);
       fused.push_back(u);
     }
     if (can_remove) removed.insert(i);
@@ -196,32 +216,35 @@ struct CastCollapser {
   void Run() {
     users.assign(b->vars().size(), {});
     producer.assign(b->vars().size(), -1);
-    int casts = 0;
+    int count = 0;
     for (size_t i = 0; i < ins.size(); ++i) {
       producer[ins[i].output] = (int)i;
       std::set<int> seen;
       for (int v : ins[i].inputs)
         if (seen.insert(v).second) users[v].push_back((int)i);
-      casts += ins[i].op_type == "cast";
+      count += ins[i].op_type == kind;
     }
-    if (casts <= 1) return;
+    if (count <= 1) return;
     for (size_t i = 0; i < ins.size(); ++i) {
-      if (ins[i].op_type != "cast" || visited.count((int)i)) continue;
+      if (ins[i].op_type != kind || visited.count((int)i)) continue;
       int first = (int)i;
-      for (int p = producer[ins[first].inputs[0]]; p >= 0 && ins[p].op_type == "cast"; p = producer[ins[p].inputs[0]]) first = p;
+      for (int p = producer[ins[first].inputs[0]]; p >= 0 && ins[p].op_type == kind; p = producer[ins[p].inputs[0]]) first = p;
       if (!visited.count(first)) Fuse(first);
     }
   }
 };
 
-bool CastCollapsing(NetBuilder* b, const std::vector<int>& fetch) {
-  CastCollapser c;
-  c.b   = b;
-  c.ins = b->TakeInstrs();
+bool Collapse(NetBuilder* b, const std::string& kind, const std::vector<int>& fetch) {
+  Collapser c;
+  c.b    = b;
+  c.kind = kind;
+  c.ins  = b->TakeInstrs();
   c.fetch.insert(fetch.begin(), fetch.end());
   c.Run();
-  for (size_t i = 0; i < c.ins.size(); ++i)
-    if (!c.removed.count((int)i)) b->AppendInstr(c.ins[i]);
+  for (size_t i = 0; i < c.ins.size(); ++i) {
+    if (c.removed.count((int)i)) continue;
+    b->AppendInstr(c.ins[i]);
+  }
   return true;
 }
 
@@ -322,11 +345,11 @@ bool ApplyProgramPass(NetBuilder* b, const std::string& pass, const std::vector<
     }
   if (pass == "AutoCast") return AutoCast(b, err);
   if (pass == "AutoBroadcast") return AutoBroadcast(b, err);
-  if (pass == "CastCollapsing") return CastCollapsing(b, fetch);
+  if (pass == "CastCollapsing") return Collapse(b, "cast", fetch);
+  if (pass == "TransposeCollapsing") return Collapse(b, "transpose", fetch);
   if (pass == "RemoveIdentity") return RemoveIdentity(b, fetch);
   if (pass == "DeadCodeEliminate") return DeadCodeEliminate(b, fetch);
-  if (pass == "ExpandZeroDim" || pass == "Decomposer" || pass == "TransposeCollapsing" || pass == "FillConstantRewriter" ||
-      pass == "FillConstantFolding")
+  if (pass == "ExpandZeroDim" || pass == "Decomposer" || pass == "FillConstantRewriter" || pass == "FillConstantFolding")
     return true;
   if (err) *err = "apply_pass: no program pass named '" + pass + "'";
   return false;

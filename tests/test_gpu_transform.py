@@ -111,3 +111,27 @@ def test_transforms_between_fused_groups(oracle):
     comp, (got,) = run(b, {"X": X, "bias": bias}, [out])
     want_act = np.maximum(np.transpose(X, (0, 2, 3, 1)) + bias, 0)
     assert np.array_equal(got, np.concatenate([want_act[..., :3], want_act], axis=3))
+
+
+def test_transpose_collapsing_keeps_the_values():
+    """A chain of transposes before and after the TransposeCollapsing pass: same bits, one kernel instead of three."""
+    from cinn_b200 import common
+    from cinn_b200.frontend import Computation, NetBuilder
+    target = common.DefaultNVGPUTarget()
+    rng = np.random.default_rng(55)
+    X = rng.standard_normal((48, 40, 36)).astype(np.float32)
+
+    def build():
+        b = NetBuilder("net")
+        x = b.create_input(common.Float(32), X.shape, "X")
+        t = b.transpose(b.transpose(b.transpose(x, [0, 2, 1]), [2, 1, 0]), [1, 2, 0])
+        return b, x, b.relu(t)
+    want = np.maximum(X.transpose(0, 2, 1).transpose(2, 1, 0).transpose(1, 2, 0), 0)
+    b, x, out = build()
+    comp = Computation.build_and_compile(target, b, fetch=[str(out)])
+    n_plain = len(comp.groups())
+    b, x, out = build()
+    got, = b.build_and_get_output(target, [x], [X], [out], passes=["TransposeCollapsing"])
+    comp = Computation.build_and_compile(target, b, fetch=[str(out)])
+    assert len(comp.groups()) < n_plain
+    assert np.array_equal(got, want)

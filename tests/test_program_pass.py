@@ -207,3 +207,63 @@ def test_default_pass_list_and_unknown_pass():
     assert _ops(b) == ["broadcast_to", "elementwise_add", "cast", "exp", "cast"]
     with pytest.raises(Exception, match="no program pass named"):
         b.apply_pass([out], None, ["NoSuchPass"])
+
+
+# ---- TransposeCollapsing: the reference's cases (transpose_collapsing_test.cc:77-450) ---------------------------------
+def _tc(build, fetch_of, expected_removed, expected_text=None):
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float32"), [4, 5, 3], "X")
+    outs = build(b, x)
+    n = _count(b)
+    b.apply_pass(fetch_of(outs), None, ["TransposeCollapsing"])
+    assert n - _count(b) == expected_removed, b.program_text()
+    if expected_text:
+        assert expected_text in b.program_text(), b.program_text()
+    return b
+
+
+def test_transpose_collapsing_chains():
+    # two transposes become one with the composed permutation [1,2,0]
+    _tc(lambda b, x: [b.transpose(b.transpose(x, [0, 2, 1]), [2, 1, 0])], lambda o: o, 1, "axis=1,2,0")
+    # three: [0,2,1] then [2,1,0] then [1,2,0]
+    _tc(lambda b, x: [b.transpose(b.transpose(b.transpose(x, [0, 2, 1]), [2, 1, 0]), [1, 2, 0])], lambda o: o, 2)
+    # a single useless transpose is left alone when fetched ...
+    _tc(lambda b, x: [b.transpose(x, [0, 1, 2])], lambda o: o, 0)
+    # ... three [0,2,1] in a row collapse into one
+    def three(b, x):
+        t = b.transpose(b.transpose(b.transpose(x, [0, 2, 1]), [0, 2, 1]), [0, 2, 1])
+        return [b.add(t, t)]
+    _tc(three, lambda o: o, 2, "axis=0,2,1")
+
+
+def test_transpose_collapsing_with_other_users_and_two_chains():
+    def multi(b, x):
+        t1 = b.transpose(x, [0, 2, 1])
+        t2 = b.transpose(t1, [2, 0, 1])
+        t3 = b.transpose(t2, [2, 1, 0])
+        return [b.sqrt(t1), b.sqrt(t2), b.sqrt(t3)]
+    b = _tc(multi, lambda o: o, 0)
+    # every transpose now reads X directly
+    assert all("= X" in ln for ln in b.program_text().splitlines() if ln.startswith("transpose"))
+
+    def two_sections(b, x):
+        out1 = b.reshape(b.transpose(b.transpose(x, [0, 2, 1]), [2, 1, 0]), [5, 3, 4])
+        out2 = b.sqrt(b.transpose(b.transpose(out1, [0, 2, 1]), [2, 1, 0]))
+        return [out1, out2]
+    _tc(two_sections, lambda o: o, 2)
+    # parallel transposes of one input are not merged (the horizontal step is off in the reference too)
+    _tc(lambda b, x: [b.add(b.transpose(x, [0, 2, 1]), b.transpose(x, [0, 2, 1]))], lambda o: o, 0)
+    # a chain that composes to what a parallel transpose already computes: the chain still folds
+    def ver_and_hor(b, x):
+        return [b.add(b.transpose(b.transpose(x, [0, 2, 1]), [2, 1, 0]), b.transpose(x, [1, 2, 0]))]
+    _tc(ver_and_hor, lambda o: o, 1)
+
+
+def test_transpose_collapsing_shapes_stay_consistent():
+    """The composed permutation applied to X gives the shape the last transpose of the chain had."""
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float32"), [4, 5, 3], "X")
+    out = b.transpose(b.transpose(x, [0, 2, 1]), [2, 1, 0])   # [4,3,5] -> [5,3,4]
+    b.apply_pass([out], None, ["TransposeCollapsing"])
+    comp = F.Computation.build_and_compile(None, b, fetch=[str(out)], plan_only=True)
+    assert len(comp.groups()) == 1 and out.shape == [5, 3, 4]
