@@ -658,11 +658,16 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
             // Neither operand is computed in the group: the chain starts at the full-size group input.
             const bool a_full = cb.input_index.count(a) && cb.values[a].numel() == cb.n;
             const bool b_full = cb.input_index.count(b) && cb.values[b].numel() == cb.n;
-            if (!a_full && !b_full) {
+            // two constants (or a constant and a broadcast operand): the chain starts from a full-size constant
+            auto full_constant = [&](const std::string& v) {
+              const OpDesc* q = cb.producer.count(v) ? cb.producer[v] : nullptr;
+              return q && q->type == "fill_constant" && cb.values[v].numel() == cb.n;
+            };
+            if (!a_full && !b_full && !full_constant(a) && !full_constant(b)) {
               cb.Fail("op '" + op.type + "' has no full-size operand to start the chain from");
               return false;
             }
-            chain_is_a = a_full;
+            chain_is_a = a_full || (!b_full && full_constant(a));
           }
           next                     = chain_is_a ? a : b;
           const std::string& other = chain_is_a ? b : a;

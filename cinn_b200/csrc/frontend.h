@@ -72,10 +72,10 @@ bool KnownOp(const std::string& op_type);
 bool IsBinaryBroadcastOp(const std::string& op_type);
 
 // Program passes (cinn/frontend/program_pass.h:36-105, cinn/frontend/pass/*.cc).  Known names: "AutoCast",
-// "AutoBroadcast", "CastCollapsing", "TransposeCollapsing", "RemoveIdentity", "DeadCodeEliminate"; the remaining names
-// of the reference's default list are accepted and do nothing here ("ExpandZeroDim", "Decomposer",
-// "FillConstantRewriter", "FillConstantFolding": decompositions happen in the builder's own methods, and the constant
-// passes only remove work that the fusion pass inlines anyway).  `fetch` lists variables that must survive.
+// "AutoBroadcast", "CastCollapsing", "TransposeCollapsing", "FillConstantRewriter", "FillConstantFolding",
+// "RemoveIdentity", "DeadCodeEliminate"; the two remaining names of the reference's default list are accepted and do
+// nothing here ("ExpandZeroDim": tensors here have at least one dimension; "Decomposer": decompositions happen in the
+// builder's own methods).  `fetch` lists variables that must survive.
 // An unknown name fails with *err set, as the reference's registry lookup does.
 bool ApplyProgramPass(NetBuilder* b, const std::string& pass, const std::vector<int>& fetch, std::string* err);
 // cinn/frontend/optimize.cc:44-82 (DefaultTrainingOptimizeOptions), in its order.

@@ -8,10 +8,14 @@
 //   CastCollapsing    cinn/frontend/pass/cast_collapsing.cc:50-301 chains of casts folded into one
 //   TransposeCollapsing cinn/frontend/pass/transpose_collapsing.cc:60-340 chains of transposes folded into one
 //   RemoveIdentity    cinn/frontend/pass/remove_identity.cc:23-262 ops that change nothing removed
+//   FillConstantRewriter / FillConstantFolding  cinn/frontend/pass/fill_constant_rewriter.cc, fill_constant_folding.cc
 //   DeadCodeEliminate cinn/frontend/pass/dead_code_eliminate.cc   instructions no fetched variable depends on removed
 // Each pass here rebuilds the builder's instruction list in place; the variable table only grows, so variable indices
 // held by the caller (the fetch list, Python Variable objects) stay valid.
 #include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <map>
 #include <functional>
 #include <set>
 #include <sstream>
@@ -303,6 +307,122 @@ bool RemoveIdentity(NetBuilder* b, const std::vector<int>& fetch_list) {
   return true;
 }
 
+// ---- FillConstantRewriter / FillConstantFolding ----------------------------------------------------------
+std::string FormatConstant(double v, DType t) {
+  char buf[64];
+  if (t == DType::kInt32 || t == DType::kInt64 || t == DType::kBool) snprintf(buf, sizeof(buf), "%lld", (long long)v);
+  else if (t == DType::kFloat64) snprintf(buf, sizeof(buf), "%.17g", v);
+  else snprintf(buf, sizeof(buf), "%.9g", (double)(float)v);
+  return buf;
+}
+
+// fill_constant_rewriter.cc:54-142: an op that reads a constant and whose result is a constant again becomes a
+// fill_constant itself (reshape, scale, cast, broadcast_to, slice, abs, log, log2, log10, tanh); a constant all of
+// whose users were rewritten, and that nobody fetches, disappears.  float32 constants are computed in float, as the
+// reference's variant holding a `float` does.
+bool FillConstantRewriter(NetBuilder* b, const std::vector<int>& fetch_list) {
+  std::vector<ProgramInstr> ins = b->TakeInstrs();
+  const std::set<int> fetch(fetch_list.begin(), fetch_list.end());
+  std::vector<std::vector<int>> users(b->vars().size());
+  for (size_t i = 0; i < ins.size(); ++i) {
+    std::set<int> seen;
+    for (int v : ins[i].inputs)
+      if (seen.insert(v).second) users[v].push_back((int)i);
+  }
+  std::set<int> removed;
+  static const std::set<std::string> math = {"abs", "log", "log2", "log10", "tanh"};
+  std::function<void(int)> rewrite = [&](int ci) {
+    const ProgramInstr constant = ins[ci];  // a copy: users are rewritten in place
+    const int out               = constant.output;
+    if (users[out].empty()) return;
+    bool can_remove = true;
+    for (int u : users[out]) {
+      ProgramInstr& op     = ins[u];
+      const std::string t  = op.op_type;
+      const DType out_type = b->vars()[op.output].dtype;
+      const DType in_type  = b->vars()[out].dtype;
+      const bool is_float  = in_type == DType::kFloat32 || in_type == DType::kFloat16 || in_type == DType::kBFloat16;
+      auto attr = [&](const char* k, const char* d) { return op.attrs.count(k) ? op.attrs.at(k) : std::string(d); };
+      std::map<std::string, std::string> attrs = constant.attrs;
+      const double v = atof(constant.attrs.count("value") ? constant.attrs.at("value").c_str() : "0");
+      if (t == "reshape" || t == "broadcast_to" || t == "slice") {
+        attrs["shape"] = JoinList(b->vars()[op.output].shape);
+      } else if (t == "scale") {
+        const std::string bas = attr("bias_after_scale", "true");
+        const bool after      = bas == "true" || bas == "1" || bas == "True";
+        double r;
+        if (is_float) {
+          const float x = (float)v, sc = (float)atof(attr("scale", "1").c_str()), bi = (float)atof(attr("bias", "0").c_str());
+          volatile float prod = after ? x * sc : x + bi;  // two roundings, as two float operations
+          r                   = after ? (float)(prod + bi) : (float)(prod * sc);
+        } else {
+          const double sc = atof(attr("scale", "1").c_str()), bi = atof(attr("bias", "0").c_str());
+          r = after ? v * sc + bi : (v + bi) * sc;
+          if (in_type == DType::kInt32 || in_type == DType::kInt64) r = (double)(long long)r;
+        }
+        attrs["value"] = FormatConstant(r, in_type);
+      } else if (t == "cast") {
+        attrs["dtype"] = DTypeName(out_type);
+        double r = v;
+        if (out_type == DType::kInt32 || out_type == DType::kInt64) r = (double)(long long)v;  // toward zero
+        if (out_type == DType::kBool) r = v != 0.0;
+        attrs["value"] = FormatConstant(r, out_type);
+      } else if (math.count(t) && (is_float || in_type == DType::kFloat64)) {
+        double r;
+        if (is_float) {
+          const float x = (float)v;
+          r = t == "abs" ? fabsf(x) : t == "log" ? logf(x) : t == "log2" ? log2f(x) : t == "log10" ? log10f(x) : tanhf(x);
+        } else {
+          r = t == "abs" ? fabs(v) : t == "log" ? log(v) : t == "log2" ? log2(v) : t == "log10" ? log10(v) : tanh(v);
+        }
+        attrs["value"] = FormatConstant(r, in_type);
+      } else {
+        can_remove = false;
+        continue;
+      }
+      op.op_type = "fill_constant";
+      op.inputs.clear();
+      op.attrs = attrs;
+      if (!op.attrs.count("dtype")) op.attrs["dtype"] = DTypeName(out_type);
+      rewrite(u);
+    }
+    if (can_remove && !fetch.count(out)) removed.insert(ci);
+  };
+  for (size_t i = 0; i < ins.size(); ++i)
+    if (ins[i].op_type == "fill_constant" && !removed.count((int)i)) rewrite((int)i);
+  for (size_t i = 0; i < ins.size(); ++i)
+    if (!removed.count((int)i)) b->AppendInstr(ins[i]);
+  return true;
+}
+
+// fill_constant_folding.cc: constants with the same shape, value and type are one constant; the later ones, unless
+// fetched, disappear and their users read the first.
+bool FillConstantFolding(NetBuilder* b, const std::vector<int>& fetch_list) {
+  std::vector<ProgramInstr> ins = b->TakeInstrs();
+  const std::set<int> fetch(fetch_list.begin(), fetch_list.end());
+  std::map<std::string, int> first;  // key -> variable
+  std::map<int, int> repl;
+  for (size_t i = 0; i < ins.size(); ++i) {
+    ProgramInstr& op = ins[i];
+    for (int& v : op.inputs)
+      if (repl.count(v)) v = repl[v];
+    if (op.op_type != "fill_constant") {
+      b->AppendInstr(op);
+      continue;
+    }
+    std::string key;
+    for (auto& kv : op.attrs) key += kv.first + "=" + kv.second + ";";
+    auto it = first.find(key);
+    if (it == first.end() || fetch.count(op.output)) {
+      if (it == first.end()) first[key] = op.output;
+      b->AppendInstr(op);
+    } else {
+      repl[op.output] = it->second;
+    }
+  }
+  return true;
+}
+
 // ---- DeadCodeEliminate -------------------------------------------------------------------------------
 bool DeadCodeEliminate(NetBuilder* b, const std::vector<int>& fetch) {
   if (fetch.empty()) return true;  // nothing named: every unread result counts as an output
@@ -349,7 +469,9 @@ bool ApplyProgramPass(NetBuilder* b, const std::string& pass, const std::vector<
   if (pass == "TransposeCollapsing") return Collapse(b, "transpose", fetch);
   if (pass == "RemoveIdentity") return RemoveIdentity(b, fetch);
   if (pass == "DeadCodeEliminate") return DeadCodeEliminate(b, fetch);
-  if (pass == "ExpandZeroDim" || pass == "Decomposer" || pass == "FillConstantRewriter" || pass == "FillConstantFolding")
+  if (pass == "FillConstantRewriter") return FillConstantRewriter(b, fetch);
+  if (pass == "FillConstantFolding") return FillConstantFolding(b, fetch);
+  if (pass == "ExpandZeroDim" || pass == "Decomposer")
     return true;
   if (err) *err = "apply_pass: no program pass named '" + pass + "'";
   return false;

@@ -267,3 +267,68 @@ def test_transpose_collapsing_shapes_stay_consistent():
     b.apply_pass([out], None, ["TransposeCollapsing"])
     comp = F.Computation.build_and_compile(None, b, fetch=[str(out)], plan_only=True)
     assert len(comp.groups()) == 1 and out.shape == [5, 3, 4]
+
+
+# ---- FillConstantRewriter / FillConstantFolding (fill_constant_rewriter_test.cc, fill_constant_folding_test.cc) -----
+def test_fill_constant_rewriter_cases_of_the_reference():
+    # reshape of a constant becomes a constant; the reshape of x to its own shape goes with RemoveIdentity: 2 removed
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float32"), [32, 16], "x")
+    c1 = b.fill_constant([16, 32], 1.0, "constant_1")
+    out = b.add(b.reshape(c1, [32, 16]), b.reshape(x, [32, 16]))
+    n = _count(b)
+    b.apply_pass([out], None, ["FillConstantRewriter", "RemoveIdentity"])
+    assert n - _count(b) == 2
+    assert "fill_constant" in b.program_text() and "shape=32,16" in b.program_text() and "reshape" not in b.program_text()
+    # scale(128, -1) = -128
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float32"), [32, 16], "x")
+    out = b.add(b.scale(b.fill_constant([32, 16], 128.0, "c"), -1.0), b.scale(x, 1.0))
+    n = _count(b)
+    b.apply_pass([out], None, ["FillConstantRewriter", "RemoveIdentity"])
+    assert n - _count(b) == 2 and "value=-128" in b.program_text()
+    # three scales in a row: ((128 * -1) * 2 + 10 + 1) * 3 = -735
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float32"), [32, 16], "x")
+    s3 = b.scale(b.scale(b.scale(b.fill_constant([32, 16], 128.0, "c"), -1.0), 2.0, 10.0), 3.0, 1.0, False)
+    out = b.add(s3, b.scale(x, 1.0))
+    n = _count(b)
+    b.apply_pass([out], None, ["FillConstantRewriter", "RemoveIdentity"])
+    assert n - _count(b) == 4 and "value=-735" in b.program_text()
+    # cast and the math functions; a constant with another kind of user stays
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float32"), [4, 4], "x")
+    c = b.fill_constant([4, 4], -2.5, "c")
+    out = b.add(b.add(x, b.abs(c)), b.cast(b.cast(c, "int32"), "float32"))
+    keep = b.multiply(x, c)
+    b.apply_pass([out, keep], None, ["FillConstantRewriter"])
+    assert set(_ops(b)) == {"fill_constant", "elementwise_add", "elementwise_mul"}
+    values = sorted(ln.split("value=")[1].split()[0] for ln in b.program_text().splitlines() if "value=" in ln)
+    assert values == ["-2", "-2.5", "2.5"]  # float32(int32(c)) (the int32 constant in between is gone), c itself, |c|
+
+
+def test_fill_constant_folding_cases_of_the_reference():
+    def build(values, use):
+        b = F.NetBuilder("net")
+        cs = [b.fill_constant([32, 32], v, "") for v in values]
+        outs = use(b, cs)
+        n = _count(b)
+        b.apply_pass(outs, None, ["FillConstantFolding"])
+        return n - _count(b), b
+    # (the reference's cases put a transpose on the constants; a transposed constant has no kernel here, relu stands in)
+    assert build([1.0, 1.0], lambda b, c: [b.add(b.relu(c[0]), b.relu(c[1]))])[0] == 1
+    assert build([1.0, 1.0], lambda b, c: [b.relu(c[0]), b.add(c[1], c[1])])[0] == 1
+    assert build([1.0, 1.0, 1.0], lambda b, c: [b.relu(c[0]), b.add(c[1], c[2])])[0] == 2
+    removed, b = build([1.0, 1.0, 0.0], lambda b, c: [b.relu(c[0]), b.add(c[1], c[2])])
+    assert removed == 1 and b.program_text().count("fill_constant") == 2
+
+
+def test_default_pass_list_is_fully_built():
+    b = F.NetBuilder("net")
+    x = b.create_input(F.Type("float16"), [64, 1024], "X")
+    c = b.scale(b.fill_constant([64, 1024], 2.0, "", "float16"), 0.5, 0.25)
+    t = b.transpose(b.transpose(b.add(x, c), [1, 0]), [1, 0])
+    out = b.exp(t)
+    assert b.apply_pass([out]) == 1
+    assert _ops(b) == ["fill_constant", "elementwise_add", "cast", "exp", "cast"]
+    assert "value=1.25" in b.program_text()
