@@ -82,10 +82,25 @@ def build_random_program(rng, b, shape, half=False):
 @pytest.mark.parametrize("half", [False, True])
 @pytest.mark.parametrize("seed", range(100))
 def test_random_program_matches_the_oracle(oracle, seed, half):
+    _random_program_case(seed, half, passes=False)
+
+
+@pytest.mark.parametrize("half", [False, True])
+@pytest.mark.parametrize("seed", range(0, 100, 3))
+def test_random_program_after_the_default_passes(oracle, seed, half):
+    """The same programs rewritten by the default program passes first (AutoCast, the collapsing passes,
+    AutoBroadcast, the constant passes, RemoveIdentity, DeadCodeEliminate): whatever groups come out are checked
+    against the oracle's evaluation of those groups."""
+    _random_program_case(seed, half, passes=True)
+
+
+def _random_program_case(seed, half, passes):
     rng = np.random.default_rng(1000 + seed)
     shape = [(6, 40), (3, 5, 16), (2, 7, 3, 12), (33,), (4, 9, 28)][seed % 5]
     b = NetBuilder("rand%d" % seed)
     feeds, fetch = build_random_program(rng, b, shape, half)
+    if passes:
+        b.apply_pass([str(f) for f in fetch])
     comp = Computation.build_and_compile(TARGET, b, fetch=[str(f) for f in fetch])
     for k, v in feeds.items():
         if k in comp.get_all_tensor_names():
