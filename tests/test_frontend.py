@@ -376,3 +376,21 @@ def test_two_output_groups_and_no_group_cycles():
     c = plan(b)
     _assert_topological(c, ["X"])
     assert len(c.groups()) >= 2
+
+
+def test_export_and_load_keep_two_output_and_tree_groups():
+    b = NetBuilder("aot")
+    x = b.create_input(common.Float(32), (64, 1024), "X")
+    y = b.create_input(common.Float(32), (64, 1024), "Y")
+    bias = b.create_input(common.Float(32), (1024,), "B")
+    pre = b.add(x, bias)
+    act = b.relu(pre)                                             # two outputs, one on the way to the other
+    tree = b.multiply(b.add(x, y), b.subtract(x, bias))           # a tree
+    norm = b.reduce_sum(b.abs(b.subtract(x, y)), [1])             # chain + reduce
+    c = plan(b, fetch=[pre, act, tree, norm])
+    text = c.export()
+    loaded = Computation.load(text, plan_only=True)
+    assert [p for _, p in loaded.groups()] == [p for _, p in c.groups()]
+    assert sorted(loaded.get_all_tensor_names()) == sorted(c.get_all_tensor_names())
+    kinds = " ".join(p for _, p in c.groups())
+    assert "chain_row_reduce" in kinds and "_s1o" in kinds and "_s3t" in kinds
