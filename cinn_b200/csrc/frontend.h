@@ -73,9 +73,9 @@ bool IsBinaryBroadcastOp(const std::string& op_type);
 
 // Program passes (cinn/frontend/program_pass.h:36-105, cinn/frontend/pass/*.cc).  Known names: "AutoCast",
 // "AutoBroadcast", "CastCollapsing", "TransposeCollapsing", "FillConstantRewriter", "FillConstantFolding",
-// "RemoveIdentity", "DeadCodeEliminate"; the two remaining names of the reference's default list are accepted and do
-// nothing here ("ExpandZeroDim": tensors here have at least one dimension; "Decomposer": decompositions happen in the
-// builder's own methods).  `fetch` lists variables that must survive.
+// "Decomposer" (gelu, softmax of any mode but "fast", inference batch_norm), "RemoveIdentity", "DeadCodeEliminate";
+// "ExpandZeroDim", the one remaining name of the reference's default list, is accepted and does nothing (tensors here
+// have at least one dimension).  `fetch` lists variables that must survive.
 // An unknown name fails with *err set, as the reference's registry lookup does.
 bool ApplyProgramPass(NetBuilder* b, const std::string& pass, const std::vector<int>& fetch, std::string* err);
 // cinn/frontend/optimize.cc:44-82 (DefaultTrainingOptimizeOptions), in its order.

@@ -8,6 +8,7 @@
 //   CastCollapsing    cinn/frontend/pass/cast_collapsing.cc:50-301 chains of casts folded into one
 //   TransposeCollapsing cinn/frontend/pass/transpose_collapsing.cc:60-340 chains of transposes folded into one
 //   RemoveIdentity    cinn/frontend/pass/remove_identity.cc:23-262 ops that change nothing removed
+//   Decomposer        cinn/frontend/pass/decomposer.cc + cinn/frontend/decomposer/*.cc  gelu, softmax, batch_norm into primitives
 //   FillConstantRewriter / FillConstantFolding  cinn/frontend/pass/fill_constant_rewriter.cc, fill_constant_folding.cc
 //   DeadCodeEliminate cinn/frontend/pass/dead_code_eliminate.cc   instructions no fetched variable depends on removed
 // Each pass here rebuilds the builder's instruction list in place; the variable table only grows, so variable indices
@@ -423,6 +424,71 @@ bool FillConstantFolding(NetBuilder* b, const std::vector<int>& fetch_list) {
   return true;
 }
 
+// ---- Decomposer -------------------------------------------------------------------------------------------
+// cinn/frontend/pass/decomposer.cc with the decomposers of cinn/frontend/decomposer/activation.cc:54-118 (gelu,
+// softmax) and batch_norm.cc:246-280 (inference batch_norm): the instruction is replaced by the primitives that
+// compute it, the last of which writes the original result variable.  relu is left alone: its decomposed form
+// max(x, 0) is what the kernels compute for it anyway.  The training-mode batch norms are decomposed by the
+// builder's own methods (they have several results).
+bool Decomposer(NetBuilder* b, std::string* err) {
+  const std::vector<ProgramInstr> old = b->TakeInstrs();
+  bool ok = true;
+  auto op = [&](const std::string& type, const std::vector<int>& ins, const std::map<std::string, std::string>& attrs) {
+    const int v = ok ? b->AddOp(type, ins, attrs, err) : -1;
+    ok = ok && v >= 0;
+    return v;
+  };
+  // the instruction that produced `v` (the last one appended) writes `into` instead
+  auto retarget = [&](int v, int into) {
+    if (!ok) return;
+    std::vector<ProgramInstr> all = b->TakeInstrs();
+    if (!all.empty() && all.back().output == v) all.back().output = into;
+    for (auto& i : all) b->AppendInstr(i);
+  };
+  for (const ProgramInstr& ins : old) {
+    const Variable x = ins.inputs.empty() ? Variable() : b->vars()[ins.inputs[0]];
+    const std::string shape = JoinList(x.shape), dt = DTypeName(x.dtype);
+    auto attr = [&](const char* k, const char* d) { return ins.attrs.count(k) ? ins.attrs.at(k) : std::string(d); };
+    auto constant = [&](const std::string& value) { return op("fill_constant", {}, {{"shape", shape}, {"value", value}, {"dtype", dt}}); };
+    if (ins.op_type == "gelu") {
+      // x * (0.5 + 0.5 * erf(sqrt(0.5) * x))
+      const int p5 = constant("0.5"), p7 = constant("0.7071067811865476");
+      const int e  = op("erf", {op("elementwise_mul", {ins.inputs[0], p7}, {})}, {});
+      const int cdf = op("elementwise_add", {p5, op("elementwise_mul", {p5, e}, {})}, {});
+      retarget(op("elementwise_mul", {ins.inputs[0], cdf}, {}), ins.output);
+    } else if (ins.op_type == "softmax" && attr("mode", "fast") != "fast") {
+      // exp(x - max) / sum(exp(x - max)) along the axis
+      const int nd = (int)x.shape.size();
+      int axis     = atoi(attr("axis", "-1").c_str());
+      if (axis < 0) axis += nd;
+      std::vector<int64_t> kept;
+      for (int i = 0; i < nd; ++i)
+        if (i != axis) kept.push_back(i);
+      if (kept.empty()) kept.push_back(-1);
+      const std::map<std::string, std::string> red = {{"dim", std::to_string(axis)}, {"keep_dim", "false"}};
+      const std::map<std::string, std::string> bc  = {{"out_shape", shape}, {"broadcast_axes", JoinList(kept)}};
+      const int m4 = op("broadcast_to", {op("reduce_max", {ins.inputs[0]}, red)}, bc);
+      const int e1 = op("exp", {op("subtract", {ins.inputs[0], m4}, {})}, {});
+      const int s4 = op("broadcast_to", {op("reduce_sum", {e1}, red)}, bc);
+      const int e2 = op("exp", {op("subtract", {ins.inputs[0], m4}, {})}, {});
+      retarget(op("divide", {e2, s4}, {}), ins.output);
+    } else if (ins.op_type == "batch_norm" && ins.inputs.size() == 5 && x.shape.size() == 4 && attr("data_layout", "NCHW") == "NCHW") {
+      // ((x - mean) * rsqrt(variance + epsilon)) * scale + bias with the per-channel operands broadcast along axis 1
+      const std::map<std::string, std::string> bc = {{"out_shape", shape}, {"broadcast_axes", "1"}};
+      const int mean4 = op("broadcast_to", {ins.inputs[3]}, bc);
+      const int var4  = op("broadcast_to", {ins.inputs[4]}, bc);
+      const int inv   = op("rsqrt", {op("elementwise_add", {var4, constant(attr("epsilon", "1e-05"))}, {})}, {});
+      const int sc4 = op("broadcast_to", {ins.inputs[1]}, bc), bi4 = op("broadcast_to", {ins.inputs[2]}, bc);
+      const int normalized = op("elementwise_mul", {op("subtract", {ins.inputs[0], mean4}, {}), inv}, {});
+      retarget(op("elementwise_add", {op("elementwise_mul", {normalized, sc4}, {}), bi4}, {}), ins.output);
+    } else {
+      b->AppendInstr(ins);
+    }
+    if (!ok) return false;
+  }
+  return true;
+}
+
 // ---- DeadCodeEliminate -------------------------------------------------------------------------------
 bool DeadCodeEliminate(NetBuilder* b, const std::vector<int>& fetch) {
   if (fetch.empty()) return true;  // nothing named: every unread result counts as an output
@@ -471,7 +537,8 @@ bool ApplyProgramPass(NetBuilder* b, const std::string& pass, const std::vector<
   if (pass == "DeadCodeEliminate") return DeadCodeEliminate(b, fetch);
   if (pass == "FillConstantRewriter") return FillConstantRewriter(b, fetch);
   if (pass == "FillConstantFolding") return FillConstantFolding(b, fetch);
-  if (pass == "ExpandZeroDim" || pass == "Decomposer")
+  if (pass == "Decomposer") return Decomposer(b, err);
+  if (pass == "ExpandZeroDim")
     return true;
   if (err) *err = "apply_pass: no program pass named '" + pass + "'";
   return false;

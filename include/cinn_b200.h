@@ -144,7 +144,8 @@ int cinn_b200_builder_var_info(cinn_b200_builder* builder, const char* id, char*
  * place by the named passes, in order; num_passes == 0 applies the reference's default list
  * (cinn/frontend/optimize.cc:44-82).  Built: "AutoCast" (auto_cast.cc), "AutoBroadcast" (auto_broadcast.cc),
  * "CastCollapsing" (cast_collapsing.cc), "TransposeCollapsing" (transpose_collapsing.cc), "FillConstantRewriter",
- * "FillConstantFolding", "RemoveIdentity" (remove_identity.cc), "DeadCodeEliminate"; the other names of
+ * "FillConstantFolding", "Decomposer" (gelu, softmax modes, inference batch_norm), "RemoveIdentity"
+ * (remove_identity.cc), "DeadCodeEliminate"; the other names of
  * the default list are accepted and change nothing; any other name fails with CINN_B200_EINVAL.  `fetch_ids` are the
  * variables that must survive.  Variable ids handed out earlier stay valid.  program_text writes one line per
  * instruction ("op out = in, in ; attr=value ...") into `out` (truncated to out_len) and returns the size needed

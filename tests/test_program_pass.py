@@ -120,9 +120,14 @@ def test_auto_cast_batch_norm_casts_x_only(dtype):
     params = [b.create_input(F.Type("float32"), [16], n) for n in ("scale", "bias", "mean", "variance")]
     out = b.batch_norm(x, *params, epsilon=1e-5, is_test=True)
     n = _count(b)
-    b.apply_pass([out], None, ["AutoCast", "Decomposer"])
+    b.apply_pass([out], None, ["AutoCast"])
     assert n - _count(b) == -2
     assert _ops(b).count("cast") == 2
+    b.apply_pass([out], None, ["Decomposer"])   # then the float32 batch_norm goes into primitives between the casts
+    assert "batch_norm" not in _ops(b) and _ops(b)[0] == "cast" and _ops(b)[-1] == "cast"
+    comp = F.Computation.build_and_compile(None, b, fetch=[str(out)], plan_only=True)
+    short = "f16" if dtype == "float16" else "bf16"
+    assert [p for _, p in comp.groups()] == ["ew_bn_train_apply_nchw ew_bn_train_apply_nchw_" + short]
 
 
 def test_auto_cast_leaves_float32_and_unlisted_ops():
@@ -332,3 +337,56 @@ def test_default_pass_list_is_fully_built():
     assert b.apply_pass([out]) == 1
     assert _ops(b) == ["fill_constant", "elementwise_add", "cast", "exp", "cast"]
     assert "value=1.25" in b.program_text()
+
+
+# ---- Decomposer --------------------------------------------------------------------------------------------------------
+def _group_text_without_names(comp):
+    import re
+    out = []
+    for desc, pattern in comp.groups():
+        out.append((re.sub(r"var_[0-9]+|fn_[^ \n]+", "_", desc), pattern))
+    return out
+
+
+def test_decomposer_emits_what_the_builder_methods_compose():
+    """gelu, the max-subtracted softmax and inference batch_norm as instructions, decomposed by the pass: the same
+    groups (up to variable names), hence the same kernels and arguments, as the builder's own compositions."""
+    def plan(b, out):
+        return F.Computation.build_and_compile(None, b, fetch=[str(out)], plan_only=True)
+    # gelu
+    b1 = F.NetBuilder("net")
+    y1 = b1.gelu(b1.create_input(F.Type("float32"), [64, 4096], "X"))
+    b2 = F.NetBuilder("net")
+    y2 = b2._op("gelu", [b2.create_input(F.Type("float32"), [64, 4096], "X")])
+    b2.apply_pass([y2], None, ["Decomposer"])
+    assert "gelu" not in b2.program_text()
+    assert _group_text_without_names(plan(b1, y1)) == _group_text_without_names(plan(b2, y2))
+    # softmax, any mode but "fast"
+    b1 = F.NetBuilder("net")
+    y1 = b1.softmax(b1.create_input(F.Type("float32"), [64, 4096], "X"), (-1,), "safe")
+    b2 = F.NetBuilder("net")
+    y2 = b2._op("softmax", [b2.create_input(F.Type("float32"), [64, 4096], "X")], axis=-1, mode="safe")
+    b2.apply_pass([y2], None, ["Decomposer"])
+    g1, g2 = _group_text_without_names(plan(b1, y1)), _group_text_without_names(plan(b2, y2))
+    assert g1 == g2 and g2[0][1].startswith("softmax_safe_row")
+    # the fast mode stays the op
+    b3 = F.NetBuilder("net")
+    y3 = b3._op("softmax", [b3.create_input(F.Type("float32"), [64, 4096], "X")], axis=-1, mode="fast")
+    b3.apply_pass([y3], None, ["Decomposer"])
+    assert _ops(b3) == ["softmax"]
+    # inference batch_norm: the decomposed arithmetic ((x - mean) * rsqrt(var + eps)) * scale + bias
+    b4 = F.NetBuilder("net")
+    x = b4.create_input(F.Type("float32"), [8, 16, 14, 14], "x")
+    ps = [b4.create_input(F.Type("float32"), [16], n) for n in ("scale", "bias", "mean", "variance")]
+    y4 = b4.batch_norm(x, *ps, epsilon=1e-5, is_test=True)
+    b4.apply_pass([y4], None, ["Decomposer"])
+    assert "batch_norm" not in b4.program_text() and "rsqrt" in b4.program_text()
+    comp = plan(b4, y4)
+    assert [p for _, p in comp.groups()] == ["ew_bn_train_apply_nchw ew_bn_train_apply_nchw_f32"]
+
+
+def test_default_passes_decompose_a_sixteen_bit_gelu():
+    b = F.NetBuilder("net")
+    y = b._op("gelu", [b.create_input(F.Type("float16"), [64, 4096], "X")])
+    assert b.apply_pass([y]) == 1           # cast, the float32 gelu primitives, cast: one chain kernel
+    assert "gelu" not in b.program_text() and _ops(b).count("cast") == 2
