@@ -164,8 +164,15 @@ struct Matcher {
     if (*wide == DType::kFloat32) return expr;
     if (g.outputs.size() == 1 && is_half(g.outputs[0].dtype)) {
       const OpDesc* top = Producer(g.outputs[0].name);
-      if (!top || top->type != "cast" || g.outputs[0].dtype != *wide || e.rfind("cast(", 0) != 0 || e.back() != ')') return expr;
-      e = e.substr(5, e.size() - 6);
+      if (top && top->type == "relu" && g.outputs[0].dtype == *wide && e.rfind("relu(cast(", 0) == 0 && e.size() > 12 &&
+          e.compare(e.size() - 2, 2, "))") == 0) {
+        // relu after the narrowing cast (what AutoCast leaves of relu(batch_norm(x)) on 16-bit storage): rounding is
+        // monotonic and keeps zero, so relu(cast(v)) and cast(relu(v)) are the same bits
+        e = "relu(" + e.substr(10, e.size() - 12) + ")";
+      } else {
+        if (!top || top->type != "cast" || g.outputs[0].dtype != *wide || e.rfind("cast(", 0) != 0 || e.back() != ')') return expr;
+        e = e.substr(5, e.size() - 6);
+      }
     }
     half_name_ = *wide == DType::kFloat16 ? "f16" : "bf16";
     return e;

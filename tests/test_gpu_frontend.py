@@ -1078,3 +1078,32 @@ def test_sibling_expressions_share_one_kernel(oracle, shape):
     assert len(comp.groups()) == 1, comp.groups()
     ref = oracle_program(comp, {"X": feeds["X"]})
     assert oracle.max_ulp(got[str(z1)], ref[str(z1)]) == 0 and oracle.max_ulp(got[str(z2)], ref[str(z2)]) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16", "float32"])
+def test_batch_norm_relu_after_the_default_passes(dtype):
+    """relu(batch_norm(x)) rewritten by AutoCast + Decomposer (+ the rest of the default list): the decomposed
+    arithmetic ((x - mean) * rsqrt(var + eps)) * scale + bias between casts, relu after the narrowing cast; still one
+    dedicated kernel."""
+    import torch
+    torch.manual_seed(73)
+    tdt = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
+    shape, c = (8, 16, 28, 28), 16
+    b = NetBuilder("bn_relu_passes")
+    x = b.create_input(common.Type(dtype), shape, "x")
+    ps = [b.create_input(common.Float(32), (c,), nm) for nm in ("scale", "bias", "mean", "variance")]
+    y = b.relu(b.batch_norm(x, *ps, epsilon=1e-5, is_test=True))
+    assert b.apply_pass([y]) == 1
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(y)])
+    short = {"float16": "f16", "bfloat16": "bf16", "float32": "f32"}[dtype]
+    assert [p for _, p in comp.groups()] == ["ew_bn_train_apply_relu_nchw ew_bn_train_apply_relu_nchw_" + short]
+    dev = "cuda:0"
+    t = {"x": torch.randn(shape, device=dev).to(tdt), "scale": 1 + 0.1 * torch.randn(c, device=dev),
+         "bias": 0.1 * torch.randn(c, device=dev), "mean": 0.1 * torch.randn(c, device=dev),
+         "variance": torch.rand(c, device=dev) + 0.5}
+    out = torch.empty(shape, dtype=tdt, device=dev)
+    _bind_run(comp, {**t, str(y): out})
+    r = lambda a: a.double().reshape(1, c, 1, 1)  # noqa: E731
+    want = torch.relu((t["x"].double() - r(t["mean"])) / torch.sqrt(r(t["variance"]) + 1e-5) * r(t["scale"]) + r(t["bias"]))
+    tol = 1e-5 if dtype == "float32" else 1e-2
+    assert bool(((out.double() - want).abs() <= tol * want.abs() + tol).all())
