@@ -572,6 +572,85 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
       if (st.Compiles(members, nullptr, nullptr)) {
         for (int i : members) group_of[i] = (int)sets.size();
         sets.push_back(members);
+        continue;
+      }
+      // The region as a whole has no kernel, but everything downstream of one of its values may be a composition
+      // that has one (a max-subtracted softmax or a layer_norm applied to a computed tensor): such a set is closed
+      // under consumers, so it can be a group of its own with that value as an input.
+      std::vector<int> fork_vars;  // every value the region reads, program inputs included, in order of first use
+      for (int m : members)
+        for (int w : b.instrs()[m].inputs)
+          if (std::find(fork_vars.begin(), fork_vars.end(), w) == fork_vars.end()) fork_vars.push_back(w);
+      for (int v : fork_vars) {
+        const int i = st.producer_of_var[v];  // -1: a program input
+        if (i >= 0 && (st.IsConst(i) || group_of[i] == -2)) continue;
+        int inside  = 0;
+        for (int cns : st.consumers_of_var[v]) inside += members.count(cns) ? 1 : 0;
+        if (inside < 2) continue;
+        std::set<int> down;
+        std::vector<int> stack(st.consumers_of_var[v].begin(), st.consumers_of_var[v].end());
+        bool clean = true;
+        while (!stack.empty() && clean) {
+          const int d = stack.back();
+          stack.pop_back();
+          if (down.count(d)) continue;
+          if (!members.count(d) || group_of[d] != -1) {
+            clean = false;  // leaves the region, or runs into a group already formed
+            break;
+          }
+          down.insert(d);
+          for (int cns : st.consumers_of_var[b.instrs()[d].output]) stack.push_back(cns);
+        }
+        if (!clean || down.size() < 3) continue;
+        // Candidates: everything downstream of v, or - when more follows the composition - the part of it that leads
+        // to one instruction z and escapes nowhere else (largest first).
+        std::vector<int> ends(down.rbegin(), down.rend());
+        for (int z : ends) {
+          std::set<int> part;
+          std::vector<int> up = {z};
+          while (!up.empty()) {
+            const int d = up.back();
+            up.pop_back();
+            if (!down.count(d) || !part.insert(d).second) continue;
+            for (int w : b.instrs()[d].inputs) {
+              const int pw = st.producer_of_var[w];
+              if (pw >= 0) up.push_back(pw);
+            }
+          }
+          bool closed = part.size() >= 3;
+          for (int d : part) {
+            if (d == z || !closed) continue;
+            closed = closed && !st.fetch.count(b.instrs()[d].output);
+            for (int cns : st.consumers_of_var[b.instrs()[d].output]) closed = closed && part.count(cns);
+          }
+          if (!closed) continue;
+          // plus what only feeds this set and hangs on nothing computed outside it (the broadcasts of gamma and beta)
+          for (bool added = true; added;) {
+            added = false;
+            for (int q : members) {
+              if (part.count(q) || group_of[q] != -1 || q == i) continue;
+              bool feeds_only_part = !st.consumers_of_var[b.instrs()[q].output].empty() && !st.fetch.count(b.instrs()[q].output);
+              for (int cns : st.consumers_of_var[b.instrs()[q].output]) feeds_only_part = feeds_only_part && part.count(cns);
+              bool free_inputs = true;
+              for (int w : b.instrs()[q].inputs) {
+                const int pw = st.producer_of_var[w];
+                free_inputs  = free_inputs && (pw < 0 || st.IsConst(pw) || part.count(pw));
+              }
+              if (feeds_only_part && free_inputs) {
+                part.insert(q);
+                added = true;
+              }
+            }
+          }
+          // Only the row compositions are taken here (several reductions and their consumers in one kernel); a part
+          // that merely is some chain is left to the steps below, which know better where chains should end.
+          FusedGroupInfo info;
+          if (!st.Compiles(part, &info, nullptr)) continue;
+          if (info.pattern != "softmax_row" && info.pattern != "softmax_safe_row" && info.pattern != "layernorm_row") continue;
+          for (int d : part) group_of[d] = (int)sets.size();
+          sets.push_back(part);
+          break;
+        }
       }
     }
   }

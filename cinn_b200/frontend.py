@@ -454,6 +454,13 @@ class Computation:
         L = _lib.lib()
         L.cinn_b200_computation_build_and_compile.restype = ctypes.c_void_p
         fetch = [str(f) for f in (fetch or [])]
+        if options is not None and (options.use_decomposer or options.passes):
+            # CinnComputation::CompileOptions (cinn/frontend/computation.h:30-44): the Decomposer first when asked
+            # for (computation.cc:53-55), then the named passes (there graph passes; here program passes by name)
+            names = (["Decomposer"] if options.use_decomposer else []) + [str(p) for p in options.passes]
+            f_arr = (ctypes.c_char_p * max(len(fetch), 1))(*[f.encode() for f in fetch])
+            p_arr = (ctypes.c_char_p * len(names))(*[n.encode() for n in names])
+            _lib.check(L.cinn_b200_builder_apply_passes(builder._h, p_arr, len(names), f_arr, len(fetch)))
         ids = (ctypes.c_char_p * max(len(fetch), 1))(*[f.encode() for f in fetch])
         h = L.cinn_b200_computation_build_and_compile(builder._h, device, ids, len(fetch))
         if not h:

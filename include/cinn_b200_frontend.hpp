@@ -140,6 +140,13 @@ class NetBuilder {
   Variable Softmax(const Variable& x, const std::vector<int>& axes = {-1}) {
     return CustomInstr("softmax", {x}, "axis=" + std::to_string(axes.empty() ? -1 : axes[0]));
   }
+  // gelu as an instruction (cinn/frontend/net_builder.h Gelu): no kernel takes it as such; compile with
+  // CompileOptions::use_decomposer (or apply the "Decomposer" pass) to turn it into its primitives.
+  Variable Gelu(const Variable& x) { return CustomInstr("gelu", {x}); }
+  // Softmax with a mode: "fast" is the op above; any other mode subtracts the row maximum and needs the Decomposer.
+  Variable Softmax(const Variable& x, const std::vector<int>& axes, const std::string& mode) {
+    return CustomInstr("softmax", {x}, "axis=" + std::to_string(axes.empty() ? -1 : axes[0]) + " mode=" + mode);
+  }
   // Inference batch norm (is_test = true), argument order of cinn/frontend/net_builder.cc:764-801.
   Variable BatchNorm(const Variable& x, const Variable& scale, const Variable& bias, const Variable& mean, const Variable& variance,
                      float epsilon = 1e-5f, const std::string& data_layout = "NCHW") {
@@ -214,6 +221,22 @@ class CinnComputation {
   std::vector<TensorInfo> GetInputTensors() const { return TensorsOfRole(0); }
   std::vector<TensorInfo> GetOutputTensors() const { return TensorsOfRole(2); }
   // device < 0 plans without touching a GPU (fusion + kernel matching only).
+  // CinnComputation::CompileOptions (cinn/frontend/computation.h:30-44).  use_decomposer runs the Decomposer program
+  // pass first, as cinn/frontend/computation.cc:53-55 does; `passes` names further program passes to run after it.
+  struct CompileOptions {
+    bool use_decomposer = false;
+    bool do_prerun = true;           // kept for source compatibility: kernels are prebuilt, there is nothing to pre-run
+    bool use_default_passes = true;  // the fusion pass always runs
+    std::vector<std::string> passes;
+  };
+  static CompileOptions DefaultCompileOptions() { return CompileOptions(); }
+  static std::shared_ptr<CinnComputation> BuildAndCompile(int device, NetBuilder& builder, const CompileOptions& options,
+                                                          const std::vector<Variable>& outputs = {}) {
+    std::vector<std::string> names = options.passes;
+    if (options.use_decomposer) names.insert(names.begin(), "Decomposer");
+    if (!names.empty()) builder.ApplyPasses(outputs, names);
+    return BuildAndCompile(device, builder, outputs);
+  }
   static std::shared_ptr<CinnComputation> BuildAndCompile(int device, const NetBuilder& builder,
                                                           const std::vector<Variable>& outputs = {}) {
     std::vector<const char*> ids;

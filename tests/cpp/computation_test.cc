@@ -29,6 +29,21 @@ int main(int argc, char** argv) {
         return 1;
       }
     }
+    {
+      // CompileOptions::use_decomposer: gelu and the max-subtracted softmax as instructions, decomposed at compile time
+      NetBuilder db("decomposed");
+      auto x = db.CreateInput("float32", {64, 4096}, "X");
+      auto g = db.Softmax(db.Gelu(x), {-1}, "safe");
+      CinnComputation::CompileOptions options = CinnComputation::DefaultCompileOptions();
+      options.use_decomposer = true;
+      auto comp = CinnComputation::BuildAndCompile(-1, db, options, {g});
+      bool safe = false;
+      for (auto& p : comp->GroupPatterns()) safe = safe || p.find("softmax_safe_row") != std::string::npos;
+      if (!safe || db.ProgramText().find("gelu") != std::string::npos) {
+        printf("FAILED: the decomposer left %s\n", db.ProgramText().c_str());
+        return 1;
+      }
+    }
     NetBuilder builder("net_builder");
     auto a   = builder.CreateInput("float32", {M, N}, "A");
     auto b   = builder.CreateInput("float32", {M, N}, "B");

@@ -394,3 +394,21 @@ def test_export_and_load_keep_two_output_and_tree_groups():
     assert sorted(loaded.get_all_tensor_names()) == sorted(c.get_all_tensor_names())
     kinds = " ".join(p for _, p in c.groups())
     assert "chain_row_reduce" in kinds and "_s1o" in kinds and "_s3t" in kinds
+
+
+def test_compositions_between_other_ops_are_still_one_kernel():
+    """A decomposed softmax / layer_norm whose operand is computed in the program and whose result feeds more ops: the
+    part of the region between the fork and the point where its branches meet again is a group of its own."""
+    b = NetBuilder("mid")
+    x = b.create_input(common.Float(32), (64, 4096), "X")
+    g, be = b.create_input(common.Float(32), (4096,), "G"), b.create_input(common.Float(32), (4096,), "Bt")
+    b.tanh(b.layer_norm(b.relu(b.scale(x, 2.0, 1.0)), g, be))
+    assert patterns(plan(b)) == ["ew_chain", "layernorm_row", "ew_chain"]
+    b = NetBuilder("mid2")
+    x = b.create_input(common.Float(32), (64, 4096), "X")
+    b.relu(b.softmax(b.gelu(x), (-1,), "safe"))
+    assert patterns(plan(b)) == ["ew_chain", "softmax_safe_row", "ew_chain"]
+    b = NetBuilder("mid3")
+    x = b.create_input(common.Float(32), (64, 4096), "X")
+    b.softmax(b.softmax(x, (-1,), "safe"), (-1,), "safe")
+    assert patterns(plan(b)) == ["softmax_safe_row", "softmax_safe_row"]

@@ -1107,3 +1107,31 @@ def test_batch_norm_relu_after_the_default_passes(dtype):
     want = torch.relu((t["x"].double() - r(t["mean"])) / torch.sqrt(r(t["variance"]) + 1e-5) * r(t["scale"]) + r(t["bias"]))
     tol = 1e-5 if dtype == "float32" else 1e-2
     assert bool(((out.double() - want).abs() <= tol * want.abs() + tol).all())
+
+
+def test_compositions_between_other_ops(oracle):
+    """op -> layer_norm -> op and gelu -> max-subtracted softmax -> relu: three kernels each, results as the oracle's
+    evaluation of those groups."""
+    rng = np.random.default_rng(85)
+    X = rng.standard_normal((128, 2048)).astype(np.float32)
+    G = (1 + 0.02 * rng.standard_normal(2048)).astype(np.float32)
+    Bt = (0.02 * rng.standard_normal(2048)).astype(np.float32)
+    b = NetBuilder("mid")
+    x = b.create_input(common.Float(32), X.shape, "X")
+    g, be = b.create_input(common.Float(32), (2048,), "G"), b.create_input(common.Float(32), (2048,), "Bt")
+    y = b.tanh(b.layer_norm(b.relu(b.scale(x, 2.0, 1.0)), g, be))
+    feeds = {"X": X, "G": G, "Bt": Bt}
+    comp, out = run_program(b, feeds, [y])
+    assert [p.split()[0] for _, p in comp.groups()] == ["ew_chain", "layernorm_row", "ew_chain"]
+    ref = oracle_program(comp, feeds)[str(y)]
+    bad, worst = oracle.count_not_close(out[str(y)], ref, 1e-4, 1e-5)
+    assert bad == 0, (bad, worst)
+    b = NetBuilder("mid2")
+    x = b.create_input(common.Float(32), X.shape, "X")
+    y = b.relu(b.softmax(b.gelu(x), (-1,), "safe"))
+    comp, out = run_program(b, {"X": X}, [y])
+    assert [p.split()[0] for _, p in comp.groups()] == ["ew_chain", "softmax_safe_row", "ew_chain"]
+    ref = oracle_program(comp, {"X": X})[str(y)]
+    bad, worst = oracle.count_not_close(out[str(y)], ref, 1e-5, 1e-9)
+    assert bad == 0, (bad, worst)
+    assert np.allclose(out[str(y)].sum(axis=1), 1.0, rtol=1e-5)
