@@ -245,22 +245,30 @@ class NetBuilder:
             raise ValueError("softmax over several axes has no prebuilt kernel")
         if mode == "fast":
             return self._op("softmax", [x], axis=int(axes[0]))
-        _, shape = x._info()
+        dt, shape = x._info()
+        half_dt = dt if dt in ("float16", "bfloat16") else None
+        if half_dt:  # computed in float32 between casts, as AutoCast arranges it around the op (auto_cast.cc:100-104)
+            x = self.cast(x, "float32")
         nd = len(shape)
         axis = int(axes[0]) % nd
         b_axes = [i for i in range(nd) if i != axis] or [-1]
         x_max = self.broadcast_to(self.reduce_max(x, [axis]), list(shape), b_axes)
         x_exp = self.exp(self.subtract(x, x_max))
         x_sum = self.broadcast_to(self.reduce_sum(x_exp, [axis]), list(shape), b_axes)
-        return self.divide(self.exp(self.subtract(x, x_max)), x_sum)
+        y = self.divide(self.exp(self.subtract(x, x_max)), x_sum)
+        return self.cast(y, half_dt) if half_dt else y
 
     def gelu(self, x):
         """x * (0.5 + 0.5 * erf(sqrt(0.5) * x)), cinn/frontend/decomposer/activation.cc:54-69."""
         dt, shape = x._info()
+        half_dt = dt if dt in ("float16", "bfloat16") else None
+        if half_dt:  # computed in float32 between casts, as AutoCast arranges it around the op (auto_cast.cc:100-104)
+            x, dt = self.cast(x, "float32"), "float32"
         p_5 = self.fill_constant(list(shape), 0.5, dtype=dt)
         p_7 = self.fill_constant(list(shape), float(np.sqrt(0.5)), dtype=dt)
         cdf = self.add(p_5, self.multiply(p_5, self.erf(self.multiply(x, p_7))))
-        return self.multiply(x, cdf)
+        y = self.multiply(x, cdf)
+        return self.cast(y, half_dt) if half_dt else y
 
     def relu_grad(self, dout, out):
         """select(out > 0, dout, 0), cinn/frontend/decomposer/activation.cc:36-51."""

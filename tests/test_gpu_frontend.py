@@ -1135,3 +1135,26 @@ def test_compositions_between_other_ops(oracle):
     bad, worst = oracle.count_not_close(out[str(y)], ref, 1e-5, 1e-9)
     assert bad == 0, (bad, worst)
     assert np.allclose(out[str(y)].sum(axis=1), 1.0, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+def test_sixteen_bit_gelu_and_max_subtracted_softmax(dtype):
+    """The builder's gelu and softmax(mode != "fast") on 16-bit tensors: float32 arithmetic between casts."""
+    import torch
+    torch.manual_seed(74)
+    tdt = torch.float16 if dtype == "float16" else torch.bfloat16
+    shape = (96, 2048)
+    b = NetBuilder("half_acts")
+    x = b.create_input(common.Type(dtype), shape, "X")
+    y, z = b.gelu(x), b.softmax(x, (-1,), "safe")
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(y), str(z)])
+    short = "f16" if dtype == "float16" else "bf16"
+    assert sorted(p.split()[1].rsplit("_", 1)[0] for _, p in comp.groups()) == ["ew_chain_" + short, "softmax_safe_" + short]
+    xt = (torch.randn(shape, device="cuda:0") * 1.5).to(tdt)
+    yt, zt = (torch.empty(shape, dtype=tdt, device="cuda:0") for _ in range(2))
+    _bind_run(comp, {"X": xt, str(y): yt, str(z): zt})
+    x64 = xt.double()
+    want_y = x64 * 0.5 * (1 + torch.erf(x64 * (0.5 ** 0.5)))
+    want_z = torch.softmax(x64, dim=1)
+    assert bool(((yt.double() - want_y).abs() <= 1e-2 * want_y.abs() + 1e-3).all())
+    assert bool(((zt.double() - want_z).abs() <= 1e-2 * want_z + 1e-7).all())
