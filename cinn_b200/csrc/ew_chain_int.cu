@@ -169,9 +169,15 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, T (&f
 }
 
 // NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
-template <typename T, int VEC, int NS>
+// NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees, as in the float form.
+template <typename T, int VEC, int NS, int NT = 0>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const T (&s1)[VEC], const T (&s2)[VEC],
                                           const T (&s3)[VEC], T (&acc)[VEC]) {
+  T ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
+  if (NT > 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0;
+  }
   for (int k = 0; k < nsteps; ++k) {
     const long long st = steps[k];
     const int op       = (int)(st & 0xff);
@@ -185,15 +191,23 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       for (int i = 0; i < VEC; ++i) acc[i] = int_unary<T>(op, acc[i]);
       continue;
     }
+    if (NT > 0 && op == EW_STASH) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) (asel == 5 ? ta : tb)[NT > 0 ? i : 0] = acc[i];
+      continue;
+    }
     T o[VEC];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i)
+    for (int i = 0; i < VEC; ++i) {
       o[i] = (NS >= 1 && asel == 1) ? s1[i] : ((NS >= 2 && asel == 2) ? s2[i] : ((NS >= 3 && asel == 3) ? s3[i] : (asel == 4 ? acc[i] : imm)));
+      if (NT > 0) o[i] = asel == 5 ? ta[NT > 0 ? i : 0] : (asel == 6 ? tb[NT > 0 ? i : 0] : o[i]);
+    }
     if (op == EW_SELECT) {
       const T imm2 = (T)(int32_t)(steps[k + 1] >> 32);
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const T b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        T b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
         const T c = role == 0 ? acc[i] : o[i];
         const T t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
         const T f = role == 2 ? acc[i] : b;
@@ -210,7 +224,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
 
 // Same parameter list as the float form (k_ew_chain): meta bits 0-3 / 4-7 dtype / mode of side 1, 8-15 side 2,
 // 16-23 side 3, 24-27 dtype of in0.
-template <typename T, typename OutT, int NS>
+template <typename T, typename OutT, int NS, int NT = 0>
 __global__ void __launch_bounds__(256)
     k_ew_chain_int(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
                    const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
@@ -230,7 +244,7 @@ __global__ void __launch_bounds__(256)
   if (vec_ok) {
     const long long nvec = n >> 2;
     // 32-bit values: two vectors (8 elements) per thread iteration, all loads issued before the program runs.
-    constexpr int NV = sizeof(T) == 4 ? 2 : 1;
+    constexpr int NV = (sizeof(T) == 4 && NT == 0) ? 2 : 1;  // one vector with temporaries: they cost registers
     long long v      = tid;
     for (; v + (NV - 1) * stride < nvec; v += NV * stride) {
       T acc[4 * NV], s1[4 * NV], s2[4 * NV], s3[4 * NV];
@@ -244,7 +258,7 @@ __global__ void __launch_bounds__(256)
         if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, *reinterpret_cast<T(*)[4]>(&s2[4 * j]));
         if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, *reinterpret_cast<T(*)[4]>(&s3[4 * j]));
       }
-      run_chain<T, 4 * NV, NS>(steps, nsteps, s1, s2, s3, acc);
+      run_chain<T, 4 * NV, NS, NT>(steps, nsteps, s1, s2, s3, acc);
 #pragma unroll
       for (int j = 0; j < NV; ++j) store_int4<T, OutT>(out, (v + j * stride) << 2, *reinterpret_cast<T(*)[4]>(&acc[4 * j]));
     }
@@ -255,7 +269,7 @@ __global__ void __launch_bounds__(256)
       if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<T, 4>(sd1, i0, s1);
       if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, s2);
       if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, s3);
-      run_chain<T, 4, NS>(steps, nsteps, s1, s2, s3, acc);
+      run_chain<T, 4, NS, NT>(steps, nsteps, s1, s2, s3, acc);
       store_int4<T, OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -266,7 +280,7 @@ __global__ void __launch_bounds__(256)
     if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<T, 1>(sd1, i, s1);
     if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 1>(sd2, i, s2);
     if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 1>(sd3, i, s3);
-    run_chain<T, 1, NS>(steps, nsteps, s1, s2, s3, acc);
+    run_chain<T, 1, NS, NT>(steps, nsteps, s1, s2, s3, acc);
     out[i] = convert_out<T, OutT>(acc[0]);
   }
 }
@@ -278,10 +292,14 @@ __global__ void __launch_bounds__(256)
   CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i64_" NSNAME, 31, 256, k_ew_chain_int<T, long long, NS>);      \
   CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_bool_" NSNAME, 31, 256, k_ew_chain_int<T, uint8_t, NS>);       \
   CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_f32_" NSNAME, 31, 256, k_ew_chain_int<T, float, NS>)
-#define REG_INT_CHAIN(TNAME, T)          \
-  REG_INT_CHAIN_NS(TNAME, T, "s0", 0);   \
-  REG_INT_CHAIN_NS(TNAME, T, "s1", 1);   \
-  REG_INT_CHAIN_NS(TNAME, T, "s3", 3)
+#define REG_INT_CHAIN(TNAME, T)                                                                                     \
+  REG_INT_CHAIN_NS(TNAME, T, "s0", 0);                                                                              \
+  REG_INT_CHAIN_NS(TNAME, T, "s1", 1);                                                                              \
+  REG_INT_CHAIN_NS(TNAME, T, "s3", 3);                                                                              \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i32_s3t", 31, 256, k_ew_chain_int<T, int32_t, 3, 2>);          \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_i64_s3t", 31, 256, k_ew_chain_int<T, long long, 3, 2>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_bool_s3t", 31, 256, k_ew_chain_int<T, uint8_t, 3, 2>);         \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_f32_s3t", 31, 256, k_ew_chain_int<T, float, 3, 2>)
 
 REG_INT_CHAIN("i32", int32_t);
 REG_INT_CHAIN("i64", long long);

@@ -1158,3 +1158,19 @@ def test_sixteen_bit_gelu_and_max_subtracted_softmax(dtype):
     want_z = torch.softmax(x64, dim=1)
     assert bool(((yt.double() - want_y).abs() <= 1e-2 * want_y.abs() + 1e-3).all())
     assert bool(((zt.double() - want_z).abs() <= 1e-2 * want_z + 1e-7).all())
+
+
+@pytest.mark.parametrize("bits", [32, 64])
+def test_integer_trees_are_one_kernel_and_bit_exact(bits):
+    rng = np.random.default_rng(86)
+    npt = np.int32 if bits == 32 else np.int64
+    shape = (129, 1000)
+    feeds = {n: rng.integers(-1000, 1000, shape).astype(npt) for n in "ABC"}
+    b = NetBuilder("int_tree")
+    A, B, C = (b.create_input(common.Int(bits), shape, n) for n in "ABC")
+    out = b.subtract(b.multiply(b.add(A, B), b.max(A, C)), b.bitwise_and(B, C))   # two joins, three tensors
+    comp, got = run_program_fetch(b, feeds, [out])
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_int_i%d_i%d_s3t" % (bits, bits)], comp.groups()
+    f = feeds
+    want = ((f["A"] + f["B"]) * np.maximum(f["A"], f["C"]) - (f["B"] & f["C"])).astype(npt)
+    assert np.array_equal(got[str(out)], want)
