@@ -390,3 +390,23 @@ def test_default_passes_decompose_a_sixteen_bit_gelu():
     y = b._op("gelu", [b.create_input(F.Type("float16"), [64, 4096], "X")])
     assert b.apply_pass([y]) == 1           # cast, the float32 gelu primitives, cast: one chain kernel
     assert "gelu" not in b.program_text() and _ops(b).count("cast") == 2
+
+
+def test_default_passes_are_idempotent_and_keep_the_fetched_variables():
+    """Seeded random programs (the generator of the GPU tests): the default pass list applied twice changes nothing
+    the second time, the fetched variables keep their shapes and types, and the rewritten program still plans."""
+    import importlib
+    import numpy as np
+    gen = importlib.import_module("tests.test_gpu_random_programs")
+    for half in (False, True):
+        for seed in range(0, 100, 4):
+            rng = np.random.default_rng(1000 + seed)
+            shape = [(6, 40), (3, 5, 16), (2, 7, 3, 12), (33,), (4, 9, 28)][seed % 5]
+            b = F.NetBuilder("rand%d" % seed)
+            _, fetch = gen.build_random_program(rng, b, shape, half)
+            ids = [str(f) for f in fetch]
+            before = [(f.shape, f.type.name) for f in fetch]
+            groups = b.apply_pass(ids)
+            text = b.program_text()
+            assert b.apply_pass(ids) == groups and b.program_text() == text, (seed, half)
+            assert [(f.shape, f.type.name) for f in fetch] == before
