@@ -416,3 +416,17 @@ def test_compositions_between_other_ops_are_still_one_kernel():
     x = b.create_input(common.Float(32), (64, 4096), "X")
     b.softmax(b.softmax(x, (-1,), "safe"), (-1,), "safe")
     assert patterns(plan(b)) == ["softmax_safe_row", "softmax_safe_row"]
+
+
+def test_compile_options_use_decomposer_and_passes():
+    """CinnComputation::CompileOptions (cinn/frontend/computation.h:30-44): the Decomposer first, then named passes."""
+    b = NetBuilder("opts")
+    x = b.create_input(common.Float(32), (64, 4096), "X")
+    y = b._op("softmax", [b._op("gelu", [x])], axis=-1, mode="safe")
+    with pytest.raises(Exception, match="no prebuilt"):
+        Computation.build_and_compile(None, b, fetch=[str(y)], plan_only=True)   # gelu as such has no kernel
+    opts = Computation.default_compile_options()
+    opts.use_decomposer = True
+    opts.passes = ["RemoveIdentity"]
+    c = Computation.build_and_compile(None, b, options=opts, fetch=[str(y)], plan_only=True)
+    assert patterns(c) == ["ew_chain", "softmax_safe_row"]
