@@ -622,7 +622,7 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
           // Both computed in the group: only the "value with itself" form is a chain.
           if (cb.IsSameAs(b, a)) { next = a; s.asel = 4; }
           else if (cb.IsSameAs(a, b)) { next = b; s.asel = 4; s.swap = true; }
-          else if (!dbl_class && temps_used < 2 && cb.values[a].numel() == cb.n && cb.values[b].numel() == cb.n) {
+          else if (temps_used < 2 && cb.values[a].numel() == cb.n && cb.values[b].numel() == cb.n) {
             // A tree: one operand is walked as a segment of its own, which runs first and is stashed in a temporary;
             // the other continues this walk.  For a float32 add the operand that continues is the product the
             // reference contracts into a fused multiply-add (the right one first, cinn/optim/lower_intrin.cc:45-50),

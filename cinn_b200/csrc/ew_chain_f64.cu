@@ -190,10 +190,16 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, doubl
 }
 
 // NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
-template <int VEC, int NS>
+// NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees, as in the float form.
+template <int VEC, int NS, int NT = 0>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const double* imms,
                                           const double (&s1)[VEC], const double (&s2)[VEC], const double (&s3)[VEC],
                                           double (&acc)[VEC]) {
+  double ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
+  if (NT > 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0.0;
+  }
   for (int k = 0; k < nsteps; ++k) {
     const long long st = steps[k];
     const int op       = (int)(st & 0xff);
@@ -207,16 +213,24 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
       for (int i = 0; i < VEC; ++i) acc[i] = d_unary(op, imm, acc[i]);
       continue;
     }
+    if (NT > 0 && op == EW_STASH) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) (asel == 5 ? ta : tb)[NT > 0 ? i : 0] = acc[i];
+      continue;
+    }
     double o[VEC];
 #pragma unroll
-    for (int i = 0; i < VEC; ++i)
+    for (int i = 0; i < VEC; ++i) {
       o[i] = (NS >= 1 && asel == 1) ? s1[i] : ((NS >= 2 && asel == 2) ? s2[i] : ((NS >= 3 && asel == 3) ? s3[i] : (asel == 4 ? acc[i] : imm)));
+      if (NT > 0) o[i] = asel == 5 ? ta[NT > 0 ? i : 0] : (asel == 6 ? tb[NT > 0 ? i : 0] : o[i]);
+    }
     const double imm2 = imms[(int)(steps[k + 1] >> 32) & (kMaxImm - 1)];
     if (op == EW_FMA) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
-        acc[i]         = fma(acc[i], o[i], b);
+        double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
+        if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
+        acc[i] = fma(acc[i], o[i], b);
       }
       if (bsel == 0) ++k;
     } else if (op == EW_SCALE_PRE) {
@@ -226,7 +240,8 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
     } else if (op == EW_SELECT) {
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+        if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
         const double c = role == 0 ? acc[i] : o[i];
         const double t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
         const double f = role == 2 ? acc[i] : b;
@@ -242,7 +257,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
 }
 
 // The fp32 form's parameter list followed by the table of double immediates.
-template <typename OutT, int NS>
+template <typename OutT, int NS, int NT = 0>
 __global__ void __launch_bounds__(256)
     k_ew_chain_f64(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
                    const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
@@ -270,7 +285,7 @@ __global__ void __launch_bounds__(256)
       if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
       if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
       if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
-      run_chain<4, NS>(steps, nsteps, imms, s1, s2, s3, acc);
+      run_chain<4, NS, NT>(steps, nsteps, imms, s1, s2, s3, acc);
       store_d4<OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -281,7 +296,7 @@ __global__ void __launch_bounds__(256)
     if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
     if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
     if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
-    run_chain<1, NS>(steps, nsteps, imms, s1, s2, s3, acc);
+    run_chain<1, NS, NT>(steps, nsteps, imms, s1, s2, s3, acc);
     out[i] = out_of<OutT>(acc[0]);
   }
 }
@@ -295,5 +310,8 @@ __global__ void __launch_bounds__(256)
 REG_F64_CHAIN("s0", 0);
 REG_F64_CHAIN("s1", 1);
 REG_F64_CHAIN("s3", 3);
+CINN_B200_REGISTER_KERNEL("ew_chain_f64_f64_s3t", 39, 256, k_ew_chain_f64<double, 3, 2>);
+CINN_B200_REGISTER_KERNEL("ew_chain_f64_f32_s3t", 39, 256, k_ew_chain_f64<float, 3, 2>);
+CINN_B200_REGISTER_KERNEL("ew_chain_f64_bool_s3t", 39, 256, k_ew_chain_f64<uint8_t, 3, 2>);
 
 }  // namespace cinn_b200

@@ -1174,3 +1174,23 @@ def test_integer_trees_are_one_kernel_and_bit_exact(bits):
     f = feeds
     want = ((f["A"] + f["B"]) * np.maximum(f["A"], f["C"]) - (f["B"] & f["C"])).astype(npt)
     assert np.array_equal(got[str(out)], want)
+
+
+def test_float64_trees_are_one_kernel(oracle):
+    rng = np.random.default_rng(87)
+    shape = (129, 1000)
+    feeds = {n: rng.standard_normal(shape) for n in "ABCD"}
+    b = NetBuilder("f64_tree")
+    A, B, C, D = (b.create_input(common.Float(64), shape, n) for n in "ABCD")
+    out = b.add(b.multiply(A, B), b.multiply(C, D))        # fma(C, D, A * B) in double
+    comp, got = run_program_fetch(b, feeds, [out])
+    assert [p for _, p in comp.groups()] == ["ew_chain ew_chain_f64_f64_s3t"], comp.groups()
+    ref = oracle_program(comp, feeds)[str(out)]
+    assert np.array_equal(got[str(out)], ref)
+    b = NetBuilder("f64_tree2")
+    A, B, C, D = (b.create_input(common.Float(64), shape, n) for n in "ABCD")
+    out = b.divide(b.subtract(A, B), b.add(b.abs(C), b.abs(D)))
+    comp, got = run_program_fetch(b, feeds, [out])
+    assert len(comp.groups()) == 1 and "s3t" in comp.groups()[0][1], comp.groups()
+    f = feeds
+    assert np.array_equal(got[str(out)], (f["A"] - f["B"]) / (np.abs(f["C"]) + np.abs(f["D"])))
