@@ -1,8 +1,9 @@
-"""Program passes (AutoCast, AutoBroadcast, CastCollapsing, RemoveIdentity, DeadCodeEliminate) on CPU.
+"""Program passes (AutoCast, Decomposer, AutoBroadcast, CastCollapsing, TransposeCollapsing, FillConstantRewriter,
+FillConstantFolding, RemoveIdentity, DeadCodeEliminate) on CPU.
 
 The expected instruction-count changes are the ones the reference's own pass tests assert
-(cinn/frontend/pass/cast_collapsing_test.cc:28-233, auto_cast_test.cc:29-71: the fourth argument of CompareResult /
-CompareProgramPassResult is `size before - size after`).
+(cinn/frontend/pass/cast_collapsing_test.cc:28-233, transpose_collapsing_test.cc:77-450, auto_cast_test.cc:29-71,
+fill_constant_rewriter_test.cc:20-145, fill_constant_folding_test.cc:40-205: `size before - size after`).
 """
 import pytest
 
