@@ -25,10 +25,12 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 HEADLINE_SHAPE = (64, 1024, 1024)
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel at full size, from the ncu
-# capture summarised in profiles/ncu_bias_scale_tanh_cast.md (268.5 MB read + 95.0 MB written; the write-back L2
-# still holds part of the 134 MB output when the kernel ends).
+HEADLINE_WORKLOAD = "bias_scale_tanh_cast X f32[64,1024,1024] + bias[1024] -> f16"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel at full size: a figure RECORDED
+# from one ncu --set full capture of this kernel (268.5 MB read + 95.0 MB written; the write-back L2 still holds
+# part of the 134 MB output when the kernel ends), not measured by this program.
 HEADLINE_DRAM_TRAFFIC_BYTES = 363450000
+DATASHEET_HBM_GBS = 8000.0
 METRIC = "fused-group HBM throughput"
 UNIT = "GB/s"
 
@@ -95,8 +97,21 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.samples)}
 
 
-def cpu_reference_run(steps, warmup):
-    """Times the CPU restatement of the reference's x86 path on the headline group, all host threads."""
+def cpu_model():
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
+def cpu_reference_run(steps, warmup, one_thread_sample=True):
+    """Times the CPU restatement of the reference's x86 path on the headline group: all host threads on the full
+    group (OpenMP over rows), and one thread on an eighth of it (the reference's x86 schedule is serial; a slice
+    keeps the run short, throughput per byte is the same)."""
     from oracle import x86_oracle
     from cinn_b200 import workloads as W
     # torchrun exports OMP_NUM_THREADS=1; the CPU arm uses every core this process may run on instead.
@@ -109,23 +124,44 @@ def cpu_reference_run(steps, warmup):
     for _ in range(steps):
         x86_oracle.bias_scale_tanh_f16(x, bias, 0.5, 0.0, threads=threads)
     dt = (time.perf_counter() - t0) / steps
-    return w.algorithmic_bytes() / dt / 1e9, dt * 1e3, threads
+    out = {"gbs": w.algorithmic_bytes() / dt / 1e9, "ms": dt * 1e3, "threads": threads, "cpu_model": cpu_model()}
+    if one_thread_sample:
+        xs = x[:HEADLINE_SHAPE[0] // 8]
+        x86_oracle.bias_scale_tanh_f16(xs, bias, 0.5, 0.0, threads=1)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            x86_oracle.bias_scale_tanh_f16(xs, bias, 0.5, 0.0, threads=1)
+        dt1 = (time.perf_counter() - t0) / 3
+        out["gbs_one_thread"] = (xs.size * 6 + bias.size * 4) / dt1 / 1e9
+        out["one_thread_sample"] = "X[8,1024,1024] slice of the headline group, 3 passes after 1 warm-up, 1 thread"
+    return out
+
+
+def cpu_baseline_dict(r, sample):
+    d = {"value": round(r["gbs"], 3), "unit": UNIT, "cores": r["threads"], "kind": "port", "ms": r["ms"],
+         "cpu_model": r["cpu_model"], "sample": sample}
+    if "gbs_one_thread" in r:
+        d["one_thread"] = {"value": round(r["gbs_one_thread"], 3), "unit": UNIT, "cores": 1,
+                           "sample": r["one_thread_sample"],
+                           "note": "the reference's x86 schedule for this group is serial (no Parallel in its IR schedule)"}
+    return d
 
 
 def run_reference_arm(args):
+    """The reference arm: the CPU restatement of the reference's x86 path on the headline group, all host threads,
+    exactly --warmup untimed and --steps timed passes over the full group (about 40 ms each on 16 threads)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    steps = min(args.steps, 10)
-    warm = min(args.warmup, 2)
-    gbs, ms, threads = cpu_reference_run(steps, warm)
+    steps, warm = max(args.steps, 1), max(args.warmup, 0)
+    r = cpu_reference_run(steps, warm)
+    gbs, ms, threads = r["gbs"], r["ms"], r["threads"]
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "bias_scale_tanh_cast X f32[64,1024,1024] + bias[1024] -> f16", "elements": 67108864},
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": "full headline group per step, OpenMP over rows, %d threads" % threads},
+        "config": {"workload": HEADLINE_WORKLOAD, "elements": 67108864},
+        "cpu_baseline": cpu_baseline_dict(r, "full headline group per step, OpenMP over rows, %d threads" % threads),
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "elements_per_s": 67108864 / (ms * 1e-3),
     }
@@ -332,124 +368,328 @@ def run_profile_case(args):
     return 0
 
 
-def strong_scaling_headline(torch, dist, dev, world, rank):
-    """The headline group with its TOTAL size fixed and axis 0 split over the ranks (no communication): every rank
-    runs its [64 / world, 1024, 1024] slice; argument sets rotate through more than 2 x L2 so that inputs come from
-    HBM.  Reported beside the weak-scaling headline; the speed-up over one GPU is total bytes / max-over-ranks time."""
+L2_BYTES = 126 * 1024 * 1024
+
+
+def device_args_from_desc(desc, torch, dev):
+    """Device tensors for a group description's arguments (inputs then outputs), filled on the device: standard
+    normal values for floating-point inputs (a `variance` operand uniform in [0.5, 1.5)), as the configs prescribe;
+    timing does not depend on the seed, so nothing is generated on the host."""
+    tmap = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16,
+            "float64": torch.float64, "int32": torch.int32, "int64": torch.int64, "bool": torch.bool}
+    args, nbytes = [], 0
+    for line in desc.splitlines():
+        w = line.split()
+        if not w or w[0] not in ("input", "output"):
+            continue
+        shape = tuple(int(d) for d in w[3].split(","))
+        dt = tmap[w[2]]
+        if w[0] == "output":
+            t = torch.empty(shape, dtype=dt, device=dev)
+        elif dt in (torch.int32, torch.int64):
+            t = torch.randint(-1000, 1000, shape, dtype=dt, device=dev)
+        elif dt == torch.bool:
+            t = torch.rand(shape, device=dev) > 0.5
+        elif w[1] == "variance":
+            t = (torch.rand(shape, device=dev) + 0.5).to(dt)
+        else:
+            t = torch.randn(shape, device=dev, dtype=torch.float32).to(dt)
+        args.append(t)
+        nbytes += t.numel() * t.element_size()
+    return args, nbytes
+
+
+def rotating_sets(desc, torch, dev, min_sets=2):
+    """Enough argument sets that consecutive launches walk through more than 2 x L2 of distinct memory."""
+    first, nbytes = device_args_from_desc(desc, torch, dev)
+    nsets = max(min_sets, int(2 * L2_BYTES // max(nbytes, 1)) + 2)
+    nsets = min(nsets, 160)  # config 1 (1.8 MB) stays L2-resident whatever the rotation: it is latency-bound
+    return [first] + [device_args_from_desc(desc, torch, dev)[0] for _ in range(nsets - 1)], nbytes
+
+
+def time_calls_in_graph(calls, torch, batches=10, min_launches=50):
+    """Median over `batches` replays of one CUDA graph that holds every call of `calls` once (repeated until the
+    graph has at least `min_launches / batches` launches): device microseconds per call, no host work per launch.
+    `calls` are functions of a stream pointer."""
+    reps = max(1, -(-max(20, -(-min_launches // batches)) // len(calls)))  # at least 20 launches per replay
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        sp = ctypes.c_void_p(side.cuda_stream)
+        for c in calls:
+            c(sp)  # warm-up outside the capture (first-use allocations, module load)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            sp = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            for _ in range(reps):
+                for c in calls:
+                    c(sp)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(batches):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / (reps * len(calls)))
+    del graph
+    return float(np.median(times))
+
+
+def time_calls_eager(calls, torch, iters=50, warmup=10):
+    """Device microseconds per call with one launch call from Python per step (host-bound for short kernels)."""
+    stream = torch.cuda.current_stream()
+    sp = ctypes.c_void_p(stream.cuda_stream)
+    for i in range(warmup):
+        calls[i % len(calls)](sp)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(iters):
+        calls[i % len(calls)](sp)
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
+def group_calls(group, sets):
+    bound = [group.bind(ts) for ts in sets]
+    n = len(sets[0])
+    return [(lambda sp, pods=pods: group.run_entry(pods, n, sp)) for pods, _ in bound], bound
+
+
+def sharded_configs(W, world, rank, sharding):
+    """(key, full-size workload, this rank's shard of it) for the configs that shard on their outer axis with no
+    communication.  Config 1 has batch 1: its flat element range is split instead."""
+    def part(n):
+        return sharding.shard_range(n, world, rank)[1]
+    tag = "_shard%dof%d" % (rank, world)
+    return [
+        ("c1_add_relu_f32", W.add_relu((150528,), name="fn_c1_full"), W.add_relu((part(150528),), name="fn_c1" + tag)),
+        ("c2_bias_scale_tanh_cast", W.bias_scale_tanh_cast((64, 1024, 1024), name="fn_c2_full"),
+         W.bias_scale_tanh_cast((part(64), 1024, 1024), name="fn_c2" + tag)),
+        ("c3a_reduce_sum_axis2", W.reduce_sum_last((128, 1024, 1024), name="fn_c3a_full"),
+         W.reduce_sum_last((part(128), 1024, 1024), name="fn_c3a" + tag)),
+        ("c4a_softmax_f32", W.softmax((16384, 4096), name="fn_c4a32_full"),
+         W.softmax((part(16384), 4096), name="fn_c4a32" + tag)),
+        ("c4a_softmax_f16", W.softmax((16384, 4096), half=True, name="fn_c4a16_full"),
+         W.softmax((part(16384), 4096), half=True, name="fn_c4a16" + tag)),
+        ("c4b_layer_norm_f32", W.layer_norm((16384, 4096), name="fn_c4b32_full"),
+         W.layer_norm((part(16384), 4096), name="fn_c4b32" + tag)),
+        ("c4b_layer_norm_f16", W.layer_norm((16384, 4096), half=True, name="fn_c4b16_full"),
+         W.layer_norm((part(16384), 4096), half=True, name="fn_c4b16" + tag)),
+        ("c5_bn_relu_f32", W.bn_relu((256, 64, 112, 112), name="fn_c5_32_full"),
+         W.bn_relu((part(256), 64, 112, 112), name="fn_c5_32" + tag)),
+        ("c5_bn_relu_f16", W.bn_relu((256, 64, 112, 112), half=True, name="fn_c5_16_full"),
+         W.bn_relu((part(256), 64, 112, 112), half=True, name="fn_c5_16" + tag)),
+    ]
+
+
+def strong_scaling_table(torch, dist, dev, world, rank, peak, only=None):
+    """Every config with its TOTAL size fixed and the outer axis split over `world` ranks (strong scaling).
+
+    t1 is the full-size group on one GPU, tN a rank's shard (max over ranks), both as the median device time per
+    launch of CUDA-graph replays whose launches rotate through more than 2 x L2 of argument sets; `eager` is the
+    same with one launch call per step from Python.  speedup = t1 / tN.  No config but 3b communicates; 3b (the
+    reduction over the sharded axis) is timed as local kernel only, local kernel + NCCL all-reduce, and the fused
+    kernel that exchanges partials over NVLink peer memory."""
     import cinn_b200
     from cinn_b200 import sharding
     from cinn_b200 import workloads as W
-    start, count = sharding.shard_range(HEADLINE_SHAPE[0], world, rank)
-    if count == 0:
-        return None
-    shape = (count,) + tuple(HEADLINE_SHAPE[1:])
-    w = W.bias_scale_tanh_cast(shape, name="fn_bias_scale_tanh_cast_shard%d" % rank)
-    g = cinn_b200.FusedGroup(w.desc)
-    per_set = 6 * count * HEADLINE_SHAPE[1] * HEADLINE_SHAPE[2]
-    nsets = max(2, int(300e6 // per_set) + 1)
-    bias = torch.randn(HEADLINE_SHAPE[-1], device=dev) * 0.1
-    sets = [[torch.randn(shape, device=dev), bias, torch.empty(shape, dtype=torch.float16, device=dev)]
-            for _ in range(nsets)]
-    torch.cuda.synchronize()
-    dist.barrier()
-    ms = time_group(g, sets, iters=100, warmup=10, torch=torch)
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    total = 6 * HEADLINE_SHAPE[0] * HEADLINE_SHAPE[1] * HEADLINE_SHAPE[2] + 4 * HEADLINE_SHAPE[2]
-    g.release()
-    return {"ms_per_step_max_over_ranks": round(ms, 5), "GB/s_whole_job": round(total / (ms * 1e-3) / 1e9, 1),
-            "slice_per_rank": list(shape), "argument_sets_rotated": nsets, "scaling": "strong",
-            "note": "no communication; speed-up over one GPU = this GB/s / the N=1 value"}
+
+    def reduce_max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def reduce_mean_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item()) / world
+
+    table = {}
+    for key, full, shard in sharded_configs(W, world, rank, sharding):
+        if only and not any(o in key for o in only):
+            continue
+        row = {}
+        for label, w in (("t1", full), ("tN", shard)):
+            if label == "tN" and world == 1:
+                row["tN_us"], row["tN_eager_us"] = row["t1_us"], row["t1_eager_us"]
+                continue
+            g = cinn_b200.FusedGroup(w.desc)
+            sets, nbytes = rotating_sets(w.desc, torch, dev)
+            calls, keep = group_calls(g, sets)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            us_graph = time_calls_in_graph(calls, torch)
+            us_eager = time_calls_eager(calls, torch)
+            red = reduce_mean_over_ranks if label == "t1" else reduce_max_over_ranks
+            row[label + "_us"] = round(red(us_graph), 3)
+            row[label + "_eager_us"] = round(red(us_eager), 3)
+            if label == "t1":
+                row["bytes"] = g.algorithmic_bytes
+                row["kernel"] = g.kernel_names()[0]
+                row["frac_of_peak_n1"] = round(g.algorithmic_bytes / (row["t1_us"] * 1e-6) / 1e9 / peak, 4)
+            else:
+                row["shard_kernel"] = g.kernel_names()[0]
+                row["argument_sets_rotated"] = len(sets)
+            g.release()
+            del calls, keep, sets
+            torch.cuda.empty_cache()
+        row["speedup"] = round(row["t1_us"] / row["tN_us"], 3)
+        row["speedup_eager"] = round(row["t1_eager_us"] / row["tN_eager_us"], 3)
+        table[key] = row
+    if not only or any(o in "c3b_reduce_max_axis0" for o in only):
+        if world > 1:
+            table["c3b_reduce_max_axis0"] = sharded_reduce_max(torch, dist, dev, world, rank, peak)
+        else:
+            w = W.reduce_max_first((128, 1024, 1024), name="fn_c3b_full")
+            g = cinn_b200.FusedGroup(w.desc)
+            sets, _ = rotating_sets(w.desc, torch, dev)
+            calls, keep = group_calls(g, sets)
+            t1, t1e = time_calls_in_graph(calls, torch), time_calls_eager(calls, torch)
+            table["c3b_reduce_max_axis0"] = {
+                "t1_us": round(t1, 3), "t1_eager_us": round(t1e, 3), "tN_us": round(t1, 3), "speedup": 1.0,
+                "bytes": g.algorithmic_bytes, "kernel": g.kernel_names()[0],
+                "frac_of_peak_n1": round(g.algorithmic_bytes / (t1 * 1e-6) / 1e9 / peak, 4)}
+            g.release()
+            del calls, keep, sets
+            torch.cuda.empty_cache()
+    return table
 
 
 def sharded_reduce_max(torch, dist, dev, world, rank, peak):
     """reduce_max over axis 0 of [128,1024,1024] with axis 0 sharded over the ranks (strong scaling): the local
-    column reduction alone, and with the NCCL all-reduce(MAX) of the 4 MiB partials that finishes it."""
+    column reduction alone, with the NCCL all-reduce(MAX) of the 4 MiB partials that finishes it, and with the
+    exchange fused into the kernel.  Input slices rotate through more than 2 x L2, so every launch reads HBM."""
+    import cinn_b200
     from cinn_b200 import sharding
+    from cinn_b200 import workloads as W
     full = (128, 1024, 1024)
-    op = sharding.ShardedReduceAxis0.from_library("max", full, world, rank)
-    x = torch.randn(op.local_shape, device=dev)
-    out = torch.empty(op.out_shape, device=dev)
-    stream = torch.cuda.current_stream()
 
-    def timed(fn, iters=30, warm=5):
-        for _ in range(warm):
-            fn()
+    def max_over_ranks(v):
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return round(float(t.item()), 3)
+
+    # t1: the whole reduction on one GPU
+    w = W.reduce_max_first(full, name="fn_c3b_full")
+    g = cinn_b200.FusedGroup(w.desc)
+    sets, _ = rotating_sets(w.desc, torch, dev)
+    calls, keep = group_calls(g, sets)
+    t1 = time_calls_in_graph(calls, torch)
+    t1_eager = time_calls_eager(calls, torch)
+    kernel = g.kernel_names()[0]
+    bytes_total = g.algorithmic_bytes
+    g.release()
+    del calls, keep, sets
+    torch.cuda.empty_cache()
+
+    op = sharding.ShardedReduceAxis0.from_library("max", full, world, rank)
+    slice_bytes = 4 * op.local_shape[0] * full[1] * full[2]
+    nsets = int(2 * L2_BYTES // slice_bytes) + 2
+    xs = [torch.randn(op.local_shape, device=dev) for _ in range(nsets)]
+    out = torch.empty(op.out_shape, device=dev)
+
+    def on_stream(fn):
+        # these wrappers launch on torch's current stream, which is the stream the timers pass
+        return lambda sp: fn()
+
+    def measure(make_call):
+        calls = [make_call(x) for x in xs]
         torch.cuda.synchronize()
         dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(iters):
-            fn()
-        e1.record(stream)
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def timed_in_graph(fn, iters=20, replays=5):
-        """The same calls replayed from one CUDA graph: no per-launch host work, so the device time shows even where
-        a launch from Python (some 15-20 us) is longer than the kernel."""
         try:
-            fn()
-            torch.cuda.synchronize()
-            side = torch.cuda.Stream()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(side):
-                with torch.cuda.graph(graph, stream=side):
-                    for _ in range(iters):
-                        fn()
-            graph.replay()
-            torch.cuda.synchronize()
-            dist.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(stream)
-            for _ in range(replays):
-                graph.replay()
-            e1.record(stream)
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1) / (iters * replays)], device=dev, dtype=torch.float64)
-        except Exception as exc:  # reported, not hidden: the eager numbers stand on their own
+            us_graph = time_calls_in_graph(calls, torch)
+        except Exception as exc:  # reported, not hidden: the eager number stands on its own
             sys.stderr.write("graph timing failed on rank %d: %r\n" % (rank, exc))
-            t = torch.tensor([float("nan")], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        v = float(t.item())
-        return None if v != v else round(v, 5)
+            us_graph = float("nan")
+        dist.barrier()
+        us_eager = time_calls_eager(calls, torch)
+        g_, e_ = max_over_ranks(us_graph), max_over_ranks(us_eager)
+        return (None if g_ != g_ else g_), e_
 
-    ms_local = timed(lambda: op.local_reduce(x, out))
-    ms_total = timed(lambda: op(x, out))
-    g_local = timed_in_graph(lambda: op.local_reduce(x, out))
-    g_total = timed_in_graph(lambda: op(x, out))
-    # The same reduction with the exchange fused into the kernel (peer stores over NVLink, no NCCL call).
+    res = {"t1_us": round(t1, 3), "t1_eager_us": round(t1_eager, 3), "kernel": kernel, "bytes": bytes_total,
+           "frac_of_peak_n1": round(bytes_total / (t1 * 1e-6) / 1e9 / peak, 4), "argument_sets_rotated": nsets}
+    res["local_kernel_us"], res["local_kernel_eager_us"] = measure(
+        lambda x: on_stream(lambda: op.local_reduce(x, out)))
+    res["local_plus_nccl_allreduce_us"], res["local_plus_nccl_allreduce_eager_us"] = measure(
+        lambda x: on_stream(lambda: op(x, out)))
     fused_full = sharding.FusedShardedReduceAxis0("max", full, world, rank, all_gather=True)
-    ms_fused_full = timed(lambda: fused_full(x, out))
-    g_fused_full = timed_in_graph(lambda: fused_full(x, out))
+    res["fused_full_result_us"], res["fused_full_result_eager_us"] = measure(
+        lambda x: on_stream(lambda: fused_full(x, out)))
+    fused_full(xs[0], out)
     check = out.clone()
-    op(x, out)
+    op(xs[0], out)
     torch.cuda.synchronize()
-    same = bool(torch.equal(check, out))
+    same = torch.tensor([1.0 if torch.equal(check, out) else 0.0], device=dev)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    res["fused_equals_nccl_result"] = bool(same.item() == 1.0)
     fused_band = sharding.FusedShardedReduceAxis0("max", full, world, rank, all_gather=False)
     band_out = torch.empty(fused_band.out_shape, device=dev)
-    ms_fused_band = timed(lambda: fused_band(x, band_out))
-    g_fused_band = timed_in_graph(lambda: fused_band(x, band_out))
+    res["fused_owned_band_us"], res["fused_owned_band_eager_us"] = measure(
+        lambda x: on_stream(lambda: fused_band(x, band_out)))
+    st = fused_full.status() + fused_band.status()
     dist.barrier()
     fused_full.close()
     fused_band.close()
-    total_bytes = 4 * (full[0] * full[1] * full[2]) + 4 * full[1] * full[2]
-    gbs = lambda ms: round(total_bytes / (ms * 1e-3) / 1e9, 1)  # noqa: E731
-    return {"ms_local_kernel": round(ms_local, 5), "ms_with_nccl_allreduce": round(ms_total, 5),
-            "ms_fused_kernel_full_result": round(ms_fused_full, 5),
-            "ms_fused_kernel_owned_band": round(ms_fused_band, 5),
-            "fused_equals_nccl_result": same,
-            "ms_in_cuda_graph": {"local_kernel": g_local, "with_nccl_allreduce": g_total,
-                                 "fused_kernel_full_result": g_fused_full, "fused_kernel_owned_band": g_fused_band},
-            "GB/s_whole_job_local": gbs(ms_local), "GB/s_whole_job_with_nccl_allreduce": gbs(ms_total),
-            "GB/s_whole_job_fused_full_result": gbs(ms_fused_full),
-            "GB/s_whole_job_fused_owned_band": gbs(ms_fused_band),
-            "frac_of_peak_per_gpu_fused_full_result": round(total_bytes / (ms_fused_full * 1e-3) / 1e9 / world / peak, 4),
-            "scaling": "strong",
-            "collective": "nccl all_reduce(MAX) of 4 MiB per rank, vs one kernel per rank exchanging over NVLink peer memory"}
+    res["bounded_wait_give_ups"] = int(st)
+    tn = res["fused_full_result_us"] or res["fused_full_result_eager_us"]
+    res["tN_us"] = tn
+    res["speedup"] = round(t1 / tn, 3)
+    res["speedup_local_kernel_only"] = round(t1 / (res["local_kernel_us"] or res["local_kernel_eager_us"]), 3)
+    res["speedup_with_nccl_allreduce"] = round(
+        t1 / (res["local_plus_nccl_allreduce_us"] or res["local_plus_nccl_allreduce_eager_us"]), 3)
+    res["speedup_owned_band"] = round(t1 / (res["fused_owned_band_us"] or res["fused_owned_band_eager_us"]), 3)
+    res["collective"] = ("tN = ONE kernel per rank: local reduction + exchange of the partials over NVLink peer "
+                         "memory (full result on every rank); beside it kernel + nccl all_reduce(MAX) of 4 MiB")
+    return res
+
+
+def pinned_copy_ceiling(torch, dev, h2d_bytes, d2h_bytes, reps=5):
+    """What plain pinned copies of the end-to-end step's sizes reach on this rank: one cudaMemcpyAsync per copy, each
+    direction alone and both at once on two streams (GB/s of the bytes moved).  The ceiling the e2e number is read
+    against; under N ranks all ranks copy at the same time, so the host side is shared."""
+    hin = torch.empty(h2d_bytes, dtype=torch.uint8).pin_memory()
+    hout = torch.empty(d2h_bytes, dtype=torch.uint8).pin_memory()
+    din = torch.empty(h2d_bytes, dtype=torch.uint8, device=dev)
+    dout = torch.empty(d2h_bytes, dtype=torch.uint8, device=dev)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps
+
+    def h2d():
+        with torch.cuda.stream(s1):
+            din.copy_(hin, non_blocking=True)
+
+    def d2h():
+        with torch.cuda.stream(s2):
+            hout.copy_(dout, non_blocking=True)
+
+    def both():
+        h2d()
+        d2h()
+    t_in, t_out, t_both = timed(h2d), timed(d2h), timed(both)
+    return {"h2d_only_GB/s": round(h2d_bytes / t_in / 1e9, 2), "d2h_only_GB/s": round(d2h_bytes / t_out / 1e9, 2),
+            "both_directions_ms": round(t_both * 1e3, 3),
+            "both_directions_GB/s": round((h2d_bytes + d2h_bytes) / t_both / 1e9, 2)}
 
 
 def main():
@@ -458,9 +698,13 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-side-groups", action="store_true", help="skip the per-group table of the other configs")
-    ap.add_argument("--only", nargs="*", default=None, help="side groups whose name contains one of these")
+    ap.add_argument("--no-side-groups", action="store_true", help="skip the per-group table of the other kernels")
+    ap.add_argument("--no-strong-table", action="store_true", help="skip the per-config strong-scaling table")
+    ap.add_argument("--only", nargs="*", default=None, help="side groups / configs whose name contains one of these")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="N=1 only: time the shards a rank of a world of this size would run (no communication), "
+                         "for tuning the small-slice launches on one GPU; printed under config.strong_scaling_emulated")
     ap.add_argument("--profile", choices=sorted(PROFILE_GROUPS), default=None,
                     help="run only this group for --warmup + --steps launches (the small case captured by ncu)")
     ap.add_argument("--option", nargs="*", default=None, help="planner options key=value (see cinn_b200_set_option)")
@@ -484,6 +728,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    for kv in args.option or []:
+        k, v = kv.split("=")
+        cinn_b200._lib.check(cinn_b200.lib().cinn_b200_set_option(k.encode(), int(v)))
     warmup = max(args.warmup, 3)
     peak, peak_src = measured_peak_gbs()
 
@@ -508,7 +755,7 @@ def main():
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, period_s=0.0005)
     sampler.start()
     launches0 = cinn_b200.lib().cinn_b200_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -519,8 +766,18 @@ def main():
     e1.record(stream)
     torch.cuda.synchronize()
     launches = cinn_b200.lib().cinn_b200_launch_count() - launches0
-    clocks = sampler.stop()
     total_ms = e0.elapsed_time(e1)
+    # The same launches timed one by one: the median of 50 (the sampler keeps running: same kernel, same load).
+    singles = []
+    for i in range(50):
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(stream)
+        g.run_entry(bound[i % 2][0], 3, sp)
+        a1.record(stream)
+        singles.append((a0, a1))
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    median_single_ms = float(np.median([a.elapsed_time(b) for a, b in singles]))
     if world > 1:
         t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -547,24 +804,47 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_value = bytes_per_launch * world / (e2e_ms * 1e-3) / 1e9
+    h2d_bytes = int(x_host.numel() * 4 + bias_host.numel() * 4)
+    d2h_bytes = int(out_host.numel() * 2)
+    if world > 1:
+        dist.barrier()
+    ceiling = pinned_copy_ceiling(torch, dev, h2d_bytes, d2h_bytes)
+    if world > 1:
+        # all ranks copied at the same time; report the slowest rank's figures
+        t = torch.tensor([ceiling["h2d_only_GB/s"], ceiling["d2h_only_GB/s"], -ceiling["both_directions_ms"]],
+                         device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ceiling = {"h2d_only_GB/s": round(float(t[0]), 2), "d2h_only_GB/s": round(float(t[1]), 2),
+                   "both_directions_ms": round(-float(t[2]), 3),
+                   "both_directions_GB/s": round((h2d_bytes + d2h_bytes) / (-float(t[2]) * 1e-3) / 1e9, 2)}
+    ceiling["note"] = ("plain pinned cudaMemcpyAsync of the step's sizes, all %d ranks at once, slowest rank; "
+                       "e2e ms_per_step / both_directions_ms says how close the step is to it" % world)
 
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "bias_scale_tanh_cast X f32[64,1024,1024] + bias[1024] -> f16 (per GPU)",
+        "config": {"workload": HEADLINE_WORKLOAD,
                    "elements": g.elements, "bytes_per_launch": bytes_per_launch,
                    "l2": "inputs (268 MB) larger than L2; two argument sets alternated",
-                   "sharding": "axis 0, no collective; each rank runs the full-size group (weak scaling)"},
+                   "sharding": "axis 0, no collective; value = every rank runs the full-size group on its own "
+                               "data (weak scaling, per GPU); config.strong_scaling holds every config with the "
+                               "total size fixed and the outer axis split"},
         "elements_per_s": g.elements * world / (ms_per_step * 1e-3),
         "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
-                     "frac": round(per_gpu / peak, 4), "traffic": HEADLINE_DRAM_TRAFFIC_BYTES,
-                     "traffic_unit": "bytes per launch (dram read + write, one ncu --set full capture)",
+                     "frac": round(per_gpu / peak, 4),
+                     "frac_of_datasheet": round(per_gpu / DATASHEET_HBM_GBS, 4), "datasheet_peak": DATASHEET_HBM_GBS,
+                     "traffic": HEADLINE_DRAM_TRAFFIC_BYTES, "traffic_recorded": True,
+                     "traffic_unit": "bytes per launch (dram read + write; recorded from one ncu --set full "
+                                     "capture of this kernel at this size, not measured in this run)",
                      "algorithmic_bytes": bytes_per_launch, "peak_source": peak_src,
-                     "kernel": g.kernel_names()[0]},
+                     "kernel": g.kernel_names()[0],
+                     "median_of_50_single_launches_ms": round(median_single_ms, 5),
+                     "frac_at_median_single_launch": round(bytes_per_launch / (median_single_ms * 1e-3) / 1e9 / peak, 4)},
         "e2e": {"value": round(e2e_value, 3), "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": int(x_host.numel() * 4 + bias_host.numel() * 4),
-                "d2h_bytes_per_step": int(out_host.numel() * 2), "steps": e2e_steps},
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps,
+                "host_chunks": cinn_b200.lib().cinn_b200_group_host_chunks(g.name.encode()),
+                "pinned_copy_ceiling": ceiling},
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
@@ -573,17 +853,47 @@ def main():
     torch.cuda.empty_cache()
 
     if rank == 0 and not args.no_cpu_baseline:
-        gbs, ms, threads = cpu_reference_run(steps=20, warmup=2)
-        line["cpu_baseline"] = {"value": round(gbs, 3), "unit": UNIT, "cores": threads, "kind": "port", "ms": ms,
-                                "sample": "full headline group, 20 passes after 2 warm-up passes, OpenMP over rows, %d threads" % threads}
+        r = cpu_reference_run(steps=20, warmup=2)
+        line["cpu_baseline"] = cpu_baseline_dict(
+            r, "full headline group, 20 passes after 2 warm-up passes, OpenMP over rows, %d threads" % r["threads"])
+    if not args.no_strong_table:
+        if world > 1:
+            dist.barrier()
+        table = strong_scaling_table(torch, dist, dev, world, rank, peak, args.only)
+        sp_keys = [k for k in table if not k.startswith("c1_")]
+        summary = {"world": world,
+                   "method": "t1 = full-size group on one GPU, tN = one rank's shard (max over ranks); median device "
+                             "time per launch over 10 replays of a CUDA graph of >= 20 launches rotating through "
+                             "> 2 x L2 of argument sets; speedup = t1 / tN",
+                   "speedup": {k: table[k]["speedup"] for k in table},
+                   "tN_us": {k: table[k]["tN_us"] for k in table},
+                   "t1_us": {k: table[k]["t1_us"] for k in table},
+                   "min_speedup_configs_2_to_5": min(table[k]["speedup"] for k in sp_keys) if sp_keys else None,
+                   "c1_note": "config 1 is 1.8 MB in total: launch-latency-bound at every N, listed but not in the minimum"}
+        if "c3b_reduce_max_axis0" in table and world > 1:
+            c3b = table["c3b_reduce_max_axis0"]
+            summary["c3b"] = {k: c3b[k] for k in c3b if k.endswith("_us") or k.startswith("speedup") or
+                              k in ("fused_equals_nccl_result", "bounded_wait_give_ups")}
+        line["config"]["strong_scaling"] = summary
+        fr = {k: table[k]["frac_of_peak_n1"] for k in table if "frac_of_peak_n1" in table[k]}
+        line["config"]["frac_of_peak_per_config"] = fr
+        rest = [v for k, v in fr.items() if not k.startswith("c1_")]
+        line["config"]["min_frac_of_peak_configs_2_to_5"] = min(rest) if rest else None
+        if rank == 0:
+            line["strong_scaling_detail"] = table
+    if args.emulate_world > 1 and world == 1:
+        emu = {}
+        for r in sorted({0, args.emulate_world - 1}):
+            emu["rank%d" % r] = strong_scaling_table(torch, dist, dev, args.emulate_world, r, peak,
+                                                     args.only or ["c1", "c2", "c3a", "c4", "c5"])
+        line["config"]["strong_scaling_emulated"] = {
+            "world": args.emulate_world,
+            "speedup": {k: v["speedup"] for k, v in emu["rank0"].items()},
+            "tN_us": {k: v["tN_us"] for k, v in emu["rank0"].items()},
+            "note": "one GPU timing the shard a rank of this world would run; no communication in these configs"}
+        line["strong_scaling_emulated_detail"] = emu
     if rank == 0 and world == 1 and not args.no_side_groups:
         line["groups"] = side_groups(torch, dev, peak, args.only)
-    if world > 1 and not args.no_side_groups:
-        sharded = sharded_reduce_max(torch, dist, dev, world, rank, peak)
-        strong = strong_scaling_headline(torch, dist, dev, world, rank)
-        if rank == 0:
-            line["groups"] = {"reduce_max_axis0_128x1024x1024_sharded_on_axis0": sharded,
-                              "headline_group_total_size_fixed_sharded_on_axis0": strong}
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

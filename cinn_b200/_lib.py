@@ -109,6 +109,15 @@ def lib():
         L.cinn_b200_peer_connect.argtypes = [vp, ctypes.c_char_p]
         L.cinn_b200_peer_destroy.restype = ci
         L.cinn_b200_peer_destroy.argtypes = [vp]
+        L.cinn_b200_peer_close_imports.restype = ci
+        L.cinn_b200_peer_close_imports.argtypes = [vp]
+        L.cinn_b200_peer_status.restype = ci
+        L.cinn_b200_peer_status.argtypes = [vp, ctypes.POINTER(ci)]
+        L.cinn_b200_peer_create_emulated.restype = ci
+        L.cinn_b200_peer_create_emulated.argtypes = [ci, ll, ctypes.POINTER(vp)]
+        L.cinn_b200_col_reduce_sharded_f32_emulated.restype = ci
+        L.cinn_b200_col_reduce_sharded_f32_emulated.argtypes = [vp, ci, ctypes.POINTER(vp), ll, ll,
+                                                                ctypes.POINTER(vp), ci, vp]
         L.cinn_b200_col_reduce_sharded_f32.restype = ci
         L.cinn_b200_col_reduce_sharded_f32.argtypes = [vp, ci, vp, ll, ll, vp, ci, vp]
         L.cinn_b200_device_status.restype = ci

@@ -89,6 +89,17 @@ extern "C" int cinn_b200_col_reduce_f32_static_scratch(int kind, const float* x,
   if (!x || !y || outer <= 0 || r <= 0 || inner <= 0) return SetLastError(CINN_B200_EINVAL, "null buffer or non-positive extent");
   const KernelEntry* k = KernelByCName(kNames[kind]);
   if (!k) return SetLastError(CINN_B200_ENOTFOUND, "column-reduction kernel missing from the library");
+  // One rule, whatever plan the shape would get: two partials of the output must fit the static array.  Larger
+  // outputs are refused even where this device would not split the reduced axis at all, so that the limit does not
+  // depend on the SM count or on the split heuristic.
+  if (outer > kStaticScratchFloats || inner > kStaticScratchFloats || 2 * outer * inner > kStaticScratchFloats) {
+    char msg[256];
+    snprintf(msg, sizeof(msg),
+             "reduction with %lld output elements exceeds the limit of %lld: the static scratch holds %lld floats and "
+             "two partials must fit (use the regular group entry point)",
+             outer * inner, kStaticScratchFloats / 2, kStaticScratchFloats);
+    return SetLastError(CINN_B200_ENOSPACE, msg);
+  }
   float* scratch = nullptr;
   int rc         = ScratchAddress(&scratch);
   if (rc != CINN_B200_OK) return rc;
@@ -111,18 +122,7 @@ extern "C" int cinn_b200_col_reduce_f32_static_scratch(int kind, const float* x,
     if (splits > 1024) splits = 1024;
     if (splits < 1) splits = 1;
   }
-  if (splits > 1 && splits * out_elems > kStaticScratchFloats) {
-    // Fewer splits would still be correct; refuse only what cannot fit even with two.
-    splits = kStaticScratchFloats / out_elems;
-    if (splits < 2) {
-      char msg[256];
-      snprintf(msg, sizeof(msg),
-               "reduction with %lld output elements needs at least %lld scratch floats; the static scratch holds %lld "
-               "(use the regular group entry point, which allocates)",
-               out_elems, 2 * out_elems, kStaticScratchFloats);
-      return SetLastError(CINN_B200_ENOSPACE, msg);
-    }
-  }
+  if (splits * out_elems > kStaticScratchFloats) splits = kStaticScratchFloats / out_elems;  // >= 2, checked above
   long long rows_per_split = (r + splits - 1) / splits;
   splits                   = (r + rows_per_split - 1) / rows_per_split;
   const unsigned block     = cols >= 256 ? 256 : (cols >= 128 ? 128 : 64);

@@ -30,6 +30,7 @@ __global__ void __launch_bounds__(G)
   extern __shared__ __align__(128) unsigned char ring[];
   __shared__ __align__(8) uint64_t full[kMaxStages];
   __shared__ __align__(16) float2 partial[2][32];
+  __shared__ volatile int abort_flag;  // set by a warp whose bounded wait ran out
 
   const int t              = threadIdx.x;
   const int lane           = t & 31, warp = t >> 5;
@@ -42,6 +43,7 @@ __global__ void __launch_bounds__(G)
   const long long my_rows = rows > (long long)blockIdx.x ? (rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
 
   if (t == 0) {
+    abort_flag = 0;
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -76,15 +78,15 @@ __global__ void __launch_bounds__(G)
   for (; k < my_rows; ++k) {
     const int s           = (int)(k % stages);
     const uint32_t parity = (uint32_t)((k / stages) & 1);
-    // One lane per warp polls the barrier (bounded); the warp then re-converges, which also orders the other
-    // lanes' reads of the buffer after the completion that lane 0 observed.
+    // One lane per warp polls the barrier (bounded).  The warp barrier after the broadcast orders the other lanes'
+    // reads of the buffer after the completion that lane 0 observed (a shuffle alone orders nothing).  A warp whose
+    // wait ran out raises the CTA's abort flag and still goes through this row's CTA barrier (with zero partials),
+    // after which every warp sees the flag and leaves the loop together: no warp continues on unwritten partials.
     int ok = 1;
     if (lane == 0) ok = mbar_wait_bounded(&full[s], parity) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
-    if (!ok) {
-      gave_up = true;
-      break;
-    }
+    __syncwarp();
+    if (!ok && lane == 0) abort_flag = 1;
     const long long row = (long long)blockIdx.x + k * gridDim.x;
     const uint4* src    = reinterpret_cast<const uint4*>(ring + (size_t)s * row_bytes);
     float f[VPT][V];
@@ -92,7 +94,7 @@ __global__ void __launch_bounds__(G)
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int v = t + j * G;
-      if (v < nvec) {
+      if (v < nvec && ok) {
         Io<T>::unpack(src[v], f[j]);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
@@ -113,6 +115,10 @@ __global__ void __launch_bounds__(G)
     float2* scratch = partial[k & 1];
     if (lane == 0) scratch[warp] = make_float2(s1, s2);
     __syncthreads();  // also: every thread has finished reading ring buffer s
+    if (abort_flag) {
+      gave_up = true;
+      break;
+    }
     if (t == 0 && k + stages < my_rows) {
       // Order the generic-proxy reads of buffer s before the async-proxy write that refills it.
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

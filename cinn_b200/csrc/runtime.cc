@@ -211,10 +211,21 @@ struct GroupSlot {
   std::unique_ptr<CompiledGroup> chunk_plan;     // the group compiled for one chunk
   std::unordered_map<int, void*> scratch;        // device ordinal -> scratch buffer
   std::unordered_map<int, HostStaging> staging;  // device ordinal -> staging for run_host
+  std::mutex mu;                                 // guards scratch / staging / chunk_* of this group
+  ~GroupSlot();
 };
 
-static GroupSlot g_slots[kMaxGroups];
+// A slot holds its group through a shared_ptr: a run takes its own reference under g_mu, so compiling the same
+// name again or releasing the group while another thread is inside a run cannot free the plan under it; the
+// group's device memory is freed when the last reference goes.
+static std::shared_ptr<GroupSlot> g_slots[kMaxGroups];
 static std::unordered_map<std::string, int> g_slot_of_name;
+
+static std::shared_ptr<GroupSlot> SlotRef(int index) {
+  if (index < 0 || index >= kMaxGroups) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  return g_slots[index];
+}
 
 static int RunSlot(int slot, void* pod_args, int num_args, void* stream);
 
@@ -288,16 +299,29 @@ static int RunPlan(const CompiledGroup& plan, GroupSlot& slot, const std::vector
   if (plan.scratch_bytes) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return SetError(CINN_B200_ECUDA, "cudaGetDevice failed");
-    std::lock_guard<std::mutex> lk(g_mu);
+    std::lock_guard<std::mutex> lk(slot.mu);
     auto it = slot.scratch.find(dev);
     if (it == slot.scratch.end()) {
+      // First run on this device.  The buffer is zeroed (kernels that keep ticket counters in it return them to
+      // zero themselves) and the zeroing is COMPLETE before this call goes on, so that a later run on any other
+      // stream is ordered after it as well.  That needs a synchronisation, hence no stream capture here.
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+        return SetError(CINN_B200_EINVAL,
+                        "group %s needs scratch memory: run it once outside stream capture before capturing it",
+                        plan.name.c_str());
       void* p       = nullptr;
       cudaError_t e = cudaMalloc(&p, plan.scratch_bytes);
       if (e != cudaSuccess)
         return SetError(CINN_B200_ECUDA, "group %s: cudaMalloc of %zu scratch bytes failed: %s", plan.name.c_str(),
                         plan.scratch_bytes, cudaGetErrorString(e));
-      // Zeroed once: kernels that keep counters in scratch (ticket counters) return them to zero themselves.
-      cudaMemsetAsync(p, 0, plan.scratch_bytes, static_cast<cudaStream_t>(stream));
+      e = cudaMemsetAsync(p, 0, plan.scratch_bytes, static_cast<cudaStream_t>(stream));
+      if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) {
+        cudaFree(p);
+        return SetError(CINN_B200_ECUDA, "group %s: zeroing the scratch buffer failed: %s", plan.name.c_str(),
+                        cudaGetErrorString(e));
+      }
       it = slot.scratch.emplace(dev, p).first;
     }
     scratch = static_cast<uint8_t*>(it->second);
@@ -360,12 +384,12 @@ static int RunPlan(const CompiledGroup& plan, GroupSlot& slot, const std::vector
 }
 
 static int RunSlot(int slot_index, void* pod_args, int num_args, void* stream) {
-  GroupSlot& slot = g_slots[slot_index];
-  if (!slot.plan) return SetError(CINN_B200_ENOTFOUND, "entry point %d is not bound to a compiled group", slot_index);
+  std::shared_ptr<GroupSlot> slot = SlotRef(slot_index);
+  if (!slot || !slot->plan) return SetError(CINN_B200_ENOTFOUND, "entry point %d is not bound to a compiled group", slot_index);
   std::vector<cinn_buffer_t*> bufs;
-  int rc = CheckArgs(*slot.plan, pod_args, num_args, &bufs);
+  int rc = CheckArgs(*slot->plan, pod_args, num_args, &bufs);
   if (rc != CINN_B200_OK) return rc;
-  return RunPlan(*slot.plan, slot, bufs, stream);
+  return RunPlan(*slot->plan, *slot, bufs, stream);
 }
 
 static int SlotOf(const char* fn_name) {
@@ -375,15 +399,15 @@ static int SlotOf(const char* fn_name) {
   return it == g_slot_of_name.end() ? -1 : it->second;
 }
 
-static void FreeSlotResources(GroupSlot& s) {
-  for (auto& kv : s.scratch) {
+GroupSlot::~GroupSlot() {
+  for (auto& kv : scratch) {
     int prev = 0;
     cudaGetDevice(&prev);
     cudaSetDevice(kv.first);
     cudaFree(kv.second);
     cudaSetDevice(prev);
   }
-  for (auto& kv : s.staging) {
+  for (auto& kv : staging) {
     int prev = 0;
     cudaGetDevice(&prev);
     cudaSetDevice(kv.first);
@@ -393,13 +417,9 @@ static void FreeSlotResources(GroupSlot& s) {
     if (kv.second.replicated_ready) cudaEventDestroy(kv.second.replicated_ready);
     cudaSetDevice(prev);
   }
-  s.scratch.clear();
-  s.staging.clear();
-  s.plan.reset();
-  s.chunk_plan.reset();
-  s.chunk_tried = false;
-  s.chunk_count = 0;
 }
+
+static std::shared_ptr<GroupSlot> SlotByName(const char* fn_name) { return SlotRef(SlotOf(fn_name)); }
 
 }  // namespace cinn_b200
 
@@ -455,24 +475,29 @@ int cinn_b200_compile_group(const char* group_desc, lower_func_ptr_g* fn_out) {
   DeviceInfo dev = CurrentDeviceInfo();
   auto plan      = CompileGroup(g, dev, &err);
   if (!plan) return SetError(CINN_B200_ENOMATCH, "%s", err.c_str());
-  std::lock_guard<std::mutex> lk(g_mu);
-  int slot = -1;
-  auto it  = g_slot_of_name.find(g.name);
-  if (it != g_slot_of_name.end()) {
-    slot = it->second;
-    FreeSlotResources(g_slots[slot]);
-  } else {
-    for (int i = 0; i < kMaxGroups; ++i)
-      if (!g_slots[i].plan) {
-        slot = i;
-        break;
-      }
-    if (slot < 0) return SetError(CINN_B200_ENOSPACE, "all %d entry points are in use; release some groups", kMaxGroups);
-    g_slot_of_name[g.name] = slot;
+  auto fresh   = std::make_shared<GroupSlot>();
+  fresh->plan  = std::move(plan);
+  fresh->desc  = g;
+  std::shared_ptr<GroupSlot> old;  // dropped after the lock is released (its destructor frees device memory)
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int slot = -1;
+    auto it  = g_slot_of_name.find(g.name);
+    if (it != g_slot_of_name.end()) {
+      slot = it->second;
+    } else {
+      for (int i = 0; i < kMaxGroups; ++i)
+        if (!g_slots[i]) {
+          slot = i;
+          break;
+        }
+      if (slot < 0) return SetError(CINN_B200_ENOSPACE, "all %d entry points are in use; release some groups", kMaxGroups);
+      g_slot_of_name[g.name] = slot;
+    }
+    old           = std::move(g_slots[slot]);
+    g_slots[slot] = std::move(fresh);
+    if (fn_out) *fn_out = g_trampolines[slot];
   }
-  g_slots[slot].plan = std::move(plan);
-  g_slots[slot].desc = g;
-  if (fn_out) *fn_out = g_trampolines[slot];
   return CINN_B200_OK;
 }
 
@@ -486,12 +511,17 @@ lower_func_ptr_g cinn_b200_lookup(const char* fn_name) {
 }
 
 int cinn_b200_release_group(const char* fn_name) {
-  int slot = SlotOf(fn_name);
-  if (slot < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
-  std::lock_guard<std::mutex> lk(g_mu);
-  FreeSlotResources(g_slots[slot]);
-  g_slot_of_name.erase(fn_name);
-  return CINN_B200_OK;
+  if (!fn_name) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '(null)'");
+  std::shared_ptr<GroupSlot> old;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_slot_of_name.find(fn_name);
+    if (it == g_slot_of_name.end()) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name);
+    old = std::move(g_slots[it->second]);
+    g_slots[it->second].reset();
+    g_slot_of_name.erase(it);
+  }
+  return CINN_B200_OK;  // `old` goes here, or when the last run that still holds it returns
 }
 
 int cinn_b200_group_run(const char* fn_name, void* pod_args, int num_args, void* stream) {
@@ -509,9 +539,9 @@ static int CopyOut(const std::string& s, char* out, size_t len) {
 
 int cinn_b200_group_info(const char* fn_name, char* pattern, size_t pattern_len, long long* algorithmic_bytes,
                          long long* elements, int* launches, long long* scratch_bytes) {
-  int slot = SlotOf(fn_name);
-  if (slot < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
-  const CompiledGroup& p = *g_slots[slot].plan;
+  std::shared_ptr<GroupSlot> ref = SlotByName(fn_name);
+  if (!ref) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  const CompiledGroup& p = *ref->plan;
   if (algorithmic_bytes) *algorithmic_bytes = p.algorithmic_bytes;
   if (elements) *elements = p.elements;
   if (launches) *launches = (int)p.steps.size();
@@ -520,9 +550,9 @@ int cinn_b200_group_info(const char* fn_name, char* pattern, size_t pattern_len,
 }
 
 int cinn_b200_group_kernel(const char* fn_name, int step, char* name, size_t name_len) {
-  int slot = SlotOf(fn_name);
-  if (slot < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
-  const CompiledGroup& p = *g_slots[slot].plan;
+  std::shared_ptr<GroupSlot> ref = SlotByName(fn_name);
+  if (!ref) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  const CompiledGroup& p = *ref->plan;
   if (step < 0 || step >= (int)p.steps.size()) return SetError(CINN_B200_EINVAL, "group %s has %zu launch steps", fn_name, p.steps.size());
   return CopyOut(p.steps[step].kernel->name, name, name_len);
 }
@@ -617,9 +647,9 @@ static void PrepareChunking(GroupSlot& slot) {
 }
 
 int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, int device) {
-  int slot_index = SlotOf(fn_name);
-  if (slot_index < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
-  GroupSlot& slot           = g_slots[slot_index];
+  std::shared_ptr<GroupSlot> ref = SlotByName(fn_name);
+  if (!ref) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  GroupSlot& slot           = *ref;
   const CompiledGroup& plan = *slot.plan;
   std::vector<cinn_buffer_t*> host;
   int rc = CheckArgs(plan, pod_args, num_args, &host);
@@ -638,7 +668,7 @@ int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, 
   }
   HostStaging* st = nullptr;
   {
-    std::lock_guard<std::mutex> lk(g_mu);
+    std::lock_guard<std::mutex> lk(slot.mu);
     st = &slot.staging[device];
     if (!slot.chunk_tried) PrepareChunking(slot);
   }
@@ -726,10 +756,10 @@ int cinn_b200_group_run_host(const char* fn_name, void* pod_args, int num_args, 
 }
 
 int cinn_b200_group_host_chunks(const char* fn_name) {
-  int slot_index = SlotOf(fn_name);
-  if (slot_index < 0) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
-  std::lock_guard<std::mutex> lk(g_mu);
-  GroupSlot& slot = g_slots[slot_index];
+  std::shared_ptr<GroupSlot> ref = SlotByName(fn_name);
+  if (!ref) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  GroupSlot& slot = *ref;
+  std::lock_guard<std::mutex> lk(slot.mu);
   if (!slot.chunk_tried) PrepareChunking(slot);
   return slot.chunk_count > 0 ? slot.chunk_count : 1;
 }

@@ -4,7 +4,8 @@ Every group of this library is independent along its outermost axis, so a rank s
 own slice of that axis and runs it on its own buffers: no communication.  The one exception is a reduction over
 the sharded axis itself (reduce over axis 0 of a tensor sharded on axis 0): each rank reduces its slice to a
 full-size partial in its own HBM and a single all-reduce with the matching operator combines the partials
-(NCCL over NVLink on GPUs, gloo in the CPU tests).  Kernels never read another GPU's memory.
+(NCCL over NVLink on GPUs, gloo in the CPU tests) -- or, in the fused form, the reduction kernel itself stores its
+partials into the owner ranks' memory over NVLink and no collective library is called (FusedShardedReduceAxis0).
 
 The reference has no multi-GPU execution at all (its only per-device state is one CUmodule per card,
 cinn/runtime/cuda/cuda_module.h:67); this module is new functionality behind the same group interface.
@@ -119,6 +120,7 @@ class FusedShardedReduceAxis0:
         ctx = ctypes.c_void_p()
         _lib.check(L.cinn_b200_peer_create(rank, world, self.inner, handle, ctypes.byref(ctx)))
         self._ctx = ctx
+        self._group = group
         handles = [None] * world
         if world > 1:
             dist.all_gather_object(handles, handle.raw, group=group)
@@ -140,6 +142,64 @@ class FusedShardedReduceAxis0:
             self._ctx, self.KINDS[self.kind], ctypes.c_void_p(x_slice.data_ptr()), self.local_shape[0], self.inner,
             ctypes.c_void_p(out.data_ptr()), 1 if self.all_gather else 0, ctypes.c_void_p(stream)))
         return out
+
+    def status(self):
+        """1 if a bounded wait of an earlier call gave up (the context is then unusable), else 0.  Synchronises."""
+        import ctypes
+        from . import _lib
+        failed = ctypes.c_int(0)
+        _lib.check(_lib.lib().cinn_b200_peer_status(self._ctx, ctypes.byref(failed)))
+        return failed.value
+
+    def close(self):
+        """Every rank must call this, with none of its calls in flight.  The peers' buffers are unmapped on every
+        rank before any rank frees its own (freeing an allocation that another process still has open is undefined)."""
+        from . import _lib
+        if self._ctx is not None:
+            _lib.lib().cinn_b200_peer_close_imports(self._ctx)
+            if self.world > 1:
+                dist.barrier(group=self._group)
+            _lib.lib().cinn_b200_peer_destroy(self._ctx)
+            self._ctx = None
+
+
+class EmulatedFusedShardedReduceAxis0:
+    """FusedShardedReduceAxis0 with all `world` ranks on ONE GPU and in one launch (the library's emulated form):
+    the exchange protocol without NVLink, for machines with a single GPU.  Called with the list of every rank's
+    slice and the list of every rank's output tensor."""
+
+    def __init__(self, kind, full_shape, world, all_gather=True):
+        import ctypes
+        from . import _lib
+        self.kind, self.full_shape, self.world, self.all_gather = kind, tuple(full_shape), world, all_gather
+        if full_shape[0] % world:
+            raise ValueError("the emulated form needs equal slices")
+        self.rows_local = full_shape[0] // world
+        self.inner = 1
+        for d in full_shape[1:]:
+            self.inner *= int(d)
+        self.out_shape = tuple(full_shape[1:]) if all_gather else (self.inner // world,)
+        ctx = ctypes.c_void_p()
+        _lib.check(_lib.lib().cinn_b200_peer_create_emulated(world, self.inner, ctypes.byref(ctx)))
+        self._ctx = ctx
+
+    def __call__(self, x_slices, outs):
+        import ctypes
+        from . import _lib
+        xs = (ctypes.c_void_p * self.world)(*[x.data_ptr() for x in x_slices])
+        os_ = (ctypes.c_void_p * self.world)(*[o.data_ptr() for o in outs])
+        stream = torch.cuda.current_stream().cuda_stream
+        _lib.check(_lib.lib().cinn_b200_col_reduce_sharded_f32_emulated(
+            self._ctx, FusedShardedReduceAxis0.KINDS[self.kind], xs, self.rows_local, self.inner, os_,
+            1 if self.all_gather else 0, ctypes.c_void_p(stream)))
+        return outs
+
+    def status(self):
+        import ctypes
+        from . import _lib
+        failed = ctypes.c_int(0)
+        _lib.check(_lib.lib().cinn_b200_peer_status(self._ctx, ctypes.byref(failed)))
+        return failed.value
 
     def close(self):
         from . import _lib

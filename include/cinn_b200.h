@@ -217,8 +217,10 @@ int cinn_b200_computation_group_pattern(cinn_b200_computation* computation, int 
  * not acceptable.  x and y are device pointers supplied by the caller; the call issues one or two launches on
  * `stream` and returns without synchronising.
  *
- * Limits and rules: the partials must fit the static array -- roughly 2 * outer * inner <= 1,048,576 floats;
- * larger outputs are refused with CINN_B200_ENOSPACE and a message (use a compiled group instead).  The first call
+ * Limits and rules: two partials of the output must fit the static array: 2 * outer * inner <= 1,048,576 floats.
+ * Any larger output is refused with CINN_B200_ENOSPACE and a message, whether or not this device would split the
+ * reduced axis for it (so the limit does not depend on the SM count); such reductions run through a compiled
+ * group, which needs no scratch when it does not split.  The first call
  * on each device looks up the array's device address (cudaGetSymbolAddress); make that first call outside any
  * stream capture.  All calls share the array, so calls that can overlap on the GPU (different streams or threads)
  * must be serialised by the caller.  Nothing needs to be cleared between calls.
@@ -237,20 +239,45 @@ int cinn_b200_col_reduce_f32_static_scratch(int kind, const float* x, float* y, 
  * Requirements: inner % (4 * world) == 0, 16-byte aligned x_local / out, every rank calls with the same kind /
  * inner / all_gather, in the same order, and a context serves ONE inner size and ONE result mode (fixed by its first
  * call).  A result whose bits are 0xFFFFFFFF (a NaN pattern used inside as "not arrived") is delivered as the default
- * NaN 0x7FFFFFFF.  Waits on peers are bounded (about half a second); a wait that runs out is reported by
- * cinn_b200_device_status, leaves `out` undefined and the context unusable (destroy it).
+ * NaN 0x7FFFFFFF.  Waits on peers are bounded (about a quarter of a second); a wait that runs out is reported by
+ * cinn_b200_device_status and cinn_b200_peer_status, leaves `out` undefined and the context unusable (destroy it).
  *
  * peer_create allocates this rank's exchange buffer for results of up to max_inner elements and writes its 64-byte
  * IPC handle; the caller gathers the handles of all ranks (rank order) and passes them to peer_connect.
+ *
+ * Teardown has two steps with a barrier between them, because CUDA leaves freeing an exported allocation while
+ * another process still has it open undefined: every rank calls peer_close_imports (which first waits for this
+ * rank's device to go idle), the caller runs a barrier over all ranks, then every rank calls peer_destroy.
+ * peer_destroy alone closes the imports too, for a world of one or when the caller has synchronised the ranks itself.
+ *
+ * The ranks' launches of one call must start within the wait budget of each other (about a quarter of a second);
+ * a first call delayed by a module load or a stalled host on one rank can exhaust it on all.  After a wait has run
+ * out the context stays failed: later launches on it return at once without touching `out`, peer_status writes 1.
  */
 typedef struct cinn_b200_peer_ctx cinn_b200_peer_ctx;
 int cinn_b200_peer_create(int rank, int world, long long max_inner, unsigned char* handle_out /* 64 bytes */,
                           cinn_b200_peer_ctx** ctx_out);
 int cinn_b200_peer_connect(cinn_b200_peer_ctx* ctx, const unsigned char* all_handles /* world * 64 bytes */);
+int cinn_b200_peer_close_imports(cinn_b200_peer_ctx* ctx);
 int cinn_b200_peer_destroy(cinn_b200_peer_ctx* ctx);
+/* 1 in *failed_out when a bounded wait of an earlier call on this context gave up (synchronises with the device). */
+int cinn_b200_peer_status(cinn_b200_peer_ctx* ctx, int* failed_out);
 int cinn_b200_col_reduce_sharded_f32(cinn_b200_peer_ctx* ctx, int kind /* 0 sum, 1 prod, 2 max, 3 min */,
                                      const float* x_local, long long rows_local, long long inner, float* out,
                                      int all_gather, void* stream);
+
+/*
+ * The same kernel with every rank of the world on ONE GPU: peer_create_emulated allocates `world` exchange buffers
+ * on the current device, and one launch (gridDim.y = world) runs all ranks at once, rank r reading x_per_rank[r]
+ * ([rows_local, inner]) and writing out_per_rank[r].  It exists so that the exchange protocol -- arrival by
+ * sentinel, rank-order combination, the three rotating areas -- can be verified on a machine with a single GPU; the
+ * stores that cross NVLink in the real form are local stores here.  Destroy with peer_destroy.  No counterpart in
+ * the reference.
+ */
+int cinn_b200_peer_create_emulated(int world, long long max_inner, cinn_b200_peer_ctx** ctx_out);
+int cinn_b200_col_reduce_sharded_f32_emulated(cinn_b200_peer_ctx* ctx, int kind, const float* const* x_per_rank,
+                                              long long rows_local, long long inner, float* const* out_per_rank,
+                                              int all_gather, void* stream);
 
 /*
  * Device-side status of the current device: the number of bounded waits on asynchronous copies that gave up

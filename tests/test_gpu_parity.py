@@ -43,10 +43,12 @@ def test_bias_scale_tanh_cast(oracle, shape, misalign):
     ref = oracle.bias_scale_tanh_f16(x, bias, 0.5, 0.0, threads=oracle.num_threads())
     bad, worst = oracle.count_not_close(got, ref, 1e-2, F16_ATOL)
     assert bad == 0, (bad, worst)
-    # how often the fp16 results are identical (information for the log, not a bar)
-    same = float((got.view(np.uint16) == ref.view(np.uint16)).mean())
-    print("bias_scale_tanh_cast %s: identical fp16 results %.6f, worst/limit %.3g" % (shape, same, worst))
-    assert same > 0.99
+    # The approximate exp / reciprocal of the 16-bit-output tanh may move a result by one fp16 step where the exact
+    # value sits on a rounding boundary: observed on fewer than 1 in 1000 elements, and that is the bar (one
+    # element is allowed at the tiny shapes), next to the 1e-2 relative bar above that every element meets.
+    differ = int((got.view(np.uint16) != ref.view(np.uint16)).sum())
+    print("bias_scale_tanh_cast %s: %d of %d fp16 results differ, worst/limit %.3g" % (shape, differ, got.size, worst))
+    assert differ <= max(1, got.size // 1000)
 
 
 # ---- config 3a: reduce_sum over the last axis -----------------------------------------------------

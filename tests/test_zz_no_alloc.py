@@ -71,11 +71,25 @@ def test_static_scratch_rejects_what_does_not_fit():
     import torch
     import cinn_b200
     L = cinn_b200.lib()
-    x = torch.zeros(1, device="cuda")
-    # 600000 columns x 65536 rows: the plan wants to split the rows, but even two partials of 600000 floats exceed
-    # the 1 Mi-float array, so the call must be refused before anything is launched (the pointers are never used).
-    rc = L.cinn_b200_col_reduce_f32_static_scratch(0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(x.data_ptr()),
-                                                   1, 1 << 16, 600000, None)
+    # 600000 output columns: two partials of the output (1.2 M floats) exceed the 1 Mi-float array, so the call is
+    # refused whatever plan the shape would get.  The buffers are real and large enough for the shape all the same:
+    # an entry point that may launch is never handed pointers it could overrun.
+    r, inner = 64, 600000
+    x = torch.zeros(r, inner, device="cuda")
+    y = torch.full((inner,), 7.0, device="cuda")
+    rc = L.cinn_b200_col_reduce_f32_static_scratch(0, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()),
+                                                   1, r, inner, None)
     assert rc == -6 and b"static scratch holds" in L.cinn_b200_last_error()
+    torch.cuda.synchronize()
+    assert bool((y == 7.0).all()), "a refused call must not launch anything"
+    # the largest output that is accepted: exactly half the array
+    inner = 524288
+    x = torch.randn(64, inner, device="cuda")
+    y = torch.empty(inner, device="cuda")
+    rc = L.cinn_b200_col_reduce_f32_static_scratch(2, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()),
+                                                   1, 64, inner, None)
+    assert rc == 0, L.cinn_b200_last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(y, x.max(dim=0).values)
     assert L.cinn_b200_col_reduce_f32_static_scratch(7, None, None, 1, 1, 1, None) == -1
     torch.cuda.synchronize()
