@@ -60,6 +60,10 @@ def lib():
                                            ctypes.POINTER(ll), ctypes.POINTER(ci), ctypes.POINTER(ll)]
         L.cinn_b200_group_kernel.restype = ci
         L.cinn_b200_group_kernel.argtypes = [cs, ci, ctypes.c_char_p, ctypes.c_size_t]
+        L.cinn_b200_group_launch_text.restype = ll
+        L.cinn_b200_group_launch_text.argtypes = [cs, ctypes.c_char_p, ctypes.c_size_t]
+        L.cinn_b200_num_static_chains.restype = ci
+        L.cinn_b200_num_static_chains.argtypes = []
         L.cinn_b200_canonical_expr.restype = ci
         L.cinn_b200_canonical_expr.argtypes = [cs, ctypes.c_char_p, ctypes.c_size_t]
         L.cinn_b200_group_run_host.restype = ci

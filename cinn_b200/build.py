@@ -24,7 +24,7 @@ SOURCES = [
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
     "softmax_safe.cu",
-    "ew_chain.cu", "chain_reduce.cu",
+    "ew_chain.cu", "chain_reduce.cu", "ew_static.cu",
     "ew_chain_int.cu",
     "ew_chain_f64.cu",
     "ew_stream.cu",
@@ -66,7 +66,7 @@ def build_library(force=False, verbose=False):
     """Compile csrc/ into libcinn_b200.so; returns the library path.  Up-to-date objects are reused."""
     nvcc = _nvcc()
     os.makedirs(OBJ_DIR, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     headers += [os.path.join(HERE, "..", "include", f) for f in os.listdir(os.path.join(HERE, "..", "include"))]
     headers.append(os.path.abspath(__file__))
     jobs = []

@@ -910,6 +910,13 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
     o2.index = second ? 1 - final_idx : final_idx;
     st.args.push_back(o2);
   }
+  if (dev.enable_static_chains) {
+    // A kernel specialised at build time for exactly this program (same operand types and addressing modes, same
+    // ops and operand selectors; the immediates stay parameters) takes the interpreter's place: same parameters.
+    uint32_t sig[EW_MAX_STEPS] = {0};
+    for (size_t k = 0; k < words.size(); ++k) sig[k] = (uint32_t)(words[k] & 0xffffffffu);
+    if (const KernelEntry* fixed = FindStaticChain(st.kernel->name, meta, (int)words.size(), sig)) st.kernel = fixed;
+  }
   p->steps.push_back(st);
   return p;
 }

@@ -10,7 +10,7 @@
 // (cinn/hlir/pe/elementwise.cc:213-217) and the Mul+Add -> fma contraction of cinn/optim/lower_intrin.cc:41-59.
 // The program is interpreted per 4-element vector; every thread of a warp takes the same branch, so the cost
 // of the dispatch is shared by the vector.
-#include "ew_chain_device.cuh"
+#include "ew_chain_body.cuh"
 #include "kernel_registry.h"
 
 namespace cinn_b200 {
@@ -30,62 +30,11 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
                long long t5, long long t6, long long t7, long long t8, long long t9, long long t10, long long t11,
                long long t12, long long t13, long long t14, long long t15, void* __restrict__ out2) {
   const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
-  const int nsteps = (int)nsteps_ll;
-  const int in_type = (int)((meta >> 24) & 15);
-  const int out2_type = (int)((meta >> 36) & 15);  // storage type of the second output (EW_STORE2)
-  const SideSpec sd1 = {p1, (int)(meta & 15), (int)((meta >> 4) & 15), mid1, inner1};
-  const SideSpec sd2 = {p2, (int)((meta >> 8) & 15), (int)((meta >> 12) & 15), mid2, inner2};
-  const SideSpec sd3 = {p3, (int)((meta >> 16) & 15), (int)((meta >> 20) & 15), mid3, inner3};
-  const long long tid    = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  long long done         = 0;
-  if (vec_ok) {
-    const long long nvec = n >> 2;
-    // Two vectors (8 elements) per thread iteration: all of their loads are issued before the program runs,
-    // and one pass of the interpreter serves the eight elements.
-    long long v = tid;
-    for (; NT == 0 && v + stride < nvec; v += 2 * stride) {
-      float acc[8], s1[8], s2[8], s3[8];
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-        if (in_type != EW_NO_INPUT)
-          load_vec4(in0, in_type, (v + j * stride) << 2, true, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const long long i0 = (v + j * stride) << 2;
-        if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, *reinterpret_cast<float(*)[4]>(&s1[4 * j]));
-        if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, *reinterpret_cast<float(*)[4]>(&s2[4 * j]));
-        if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, *reinterpret_cast<float(*)[4]>(&s3[4 * j]));
-      }
-      const Store2 st2 = {out2, out2_type, v << 2, (v + stride) << 2};
-      run_chain<8, NS, 0, ST2>(steps, nsteps, s1, s2, s3, acc, ST2 ? &st2 : nullptr);
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-        store_vec4<OutT>(out, (v + j * stride) << 2, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
-    }
-    for (; v < nvec; v += stride) {
-      const long long i0 = v << 2;
-      float acc[4], s1[4], s2[4], s3[4];
-      if (in_type != EW_NO_INPUT) load_vec4(in0, in_type, i0, true, acc);
-      if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
-      if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
-      if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
-      const Store2 st2 = {out2, out2_type, i0, 0};
-      run_chain<4, NS, NT, ST2>(steps, nsteps, s1, s2, s3, acc, ST2 ? &st2 : nullptr);
-      store_vec4<OutT>(out, i0, acc);
-    }
-    done = nvec << 2;
-  }
-  for (long long i = done + tid; i < n; i += stride) {
-    float acc[1], s1[1], s2[1], s3[1];
-    acc[0] = in_type != EW_NO_INPUT ? load_scalar(in0, in_type, i) : 0.0f;
-    if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
-    if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
-    if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
-    const Store2 st2 = {out2, out2_type, i, 0};
-    run_chain<1, NS, NT, ST2>(steps, nsteps, s1, s2, s3, acc, ST2 ? &st2 : nullptr);
-    store_one<OutT>(out, i, acc[0]);
-  }
+  const DynProgram prog    = {steps, (int)nsteps_ll, meta};
+  const ChainGeometry geo  = {n, vec_ok, mid1, inner1, mid2, inner2, mid3, inner3};
+  // Two vectors (8 elements) per thread iteration: all of their loads are issued before the program runs, and one
+  // pass of the interpreter serves the eight elements.
+  ew_chain_body<OutT, NS, NT, ST2, 2>(prog, in0, p1, p2, p3, out, geo, out2);
 }
 
 }  // namespace

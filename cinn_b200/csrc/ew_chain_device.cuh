@@ -294,8 +294,112 @@ __device__ __forceinline__ void store_second(const Store2& st, const float (&a)[
   }
 }
 
-// NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees, and EW_STORE2.
+// Operand of a step by its selector: 0 the immediate, 1..3 a side input, 4 the chain value, 5 / 6 a temporary.
+template <int VEC, int NS, int NT>
+__device__ __forceinline__ void pick_operand(int sel, float imm, const float (&s1)[VEC], const float (&s2)[VEC],
+                                             const float (&s3)[VEC], const float (&acc)[VEC],
+                                             const float (&ta)[NT > 0 ? VEC : 1], const float (&tb)[NT > 0 ? VEC : 1],
+                                             float (&o)[VEC]) {
+  switch (sel) {  // one uniform branch per step instead of a select chain per element
+    case 1:
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = NS >= 1 ? s1[i] : imm;
+      break;
+    case 2:
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = NS >= 2 ? s2[i] : imm;
+      break;
+    case 3:
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = NS >= 3 ? s3[i] : imm;
+      break;
+    case 4:
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = acc[i];
+      break;
+    case 5:
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = NT > 0 ? ta[NT > 0 ? i : 0] : imm;
+      break;
+    case 6:
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = NT > 0 ? tb[NT > 0 ? i : 0] : imm;
+      break;
+    default:
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) o[i] = imm;
+      break;
+  }
+}
+
+// ONE step of a chain program on VEC values.  op / asel / bsel / role are the fields of the step's word, imm its
+// immediate and imm2 the immediate of the next word.  Returns true when the step used the next word as its second
+// immediate (the caller then skips it).  The interpreter calls this with values decoded at run time; the kernels
+// specialised at build time call it with constants, so that both execute the same arithmetic by construction.
+// NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees.
 // ST2: the program may hold EW_STORE2 steps (st2 then says where they write).
+template <int VEC, int NS, int NT, bool ST2>
+__device__ __forceinline__ bool chain_step(int op, int asel, int bsel, int role, float imm, float imm2,
+                                           const float (&s1)[VEC], const float (&s2)[VEC], const float (&s3)[VEC],
+                                           float (&acc)[VEC], float (&ta)[NT > 0 ? VEC : 1],
+                                           float (&tb)[NT > 0 ? VEC : 1], const Store2* st2) {
+  if (op == EW_NOP) return false;
+  if (op >= EW_FIRST_UNARY) {
+    apply_unary<VEC>(op, imm, acc);
+    return false;
+  }
+  if (ST2 && op == EW_STORE2) {
+    if (st2) store_second<VEC>(*st2, acc);
+    return false;
+  }
+  if (NT > 0 && op == EW_STASH) {
+    if (asel == 5) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) ta[NT > 0 ? i : 0] = acc[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) tb[NT > 0 ? i : 0] = acc[i];
+    }
+    return false;
+  }
+  float o[VEC];
+  pick_operand<VEC, NS, NT>(asel, imm, s1, s2, s3, acc, ta, tb, o);
+  if (op == EW_FMA) {
+    // acc = fma(acc, A, B); B is a side operand, a temporary or the immediate of the next program slot.
+    float b[VEC];
+    pick_operand<VEC, NS, NT>(bsel == 4 ? 0 : bsel, imm2, s1, s2, s3, acc, ta, tb, b);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(acc[i], o[i], b[i]);
+    return bsel == 0;
+  }
+  if (op == EW_SELECT) {
+    // cinn/hlir/pe/elementwise.cc Select: cond ? true_value : false_value; the chain value is one of the three.
+    // The operand and role decisions are uniform: they are taken once per step, outside the element loops.
+    float b[VEC];
+    pick_operand<VEC, NS, NT>(bsel, imm2, s1, s2, s3, acc, ta, tb, b);
+    if (role == 0) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = acc[i] != 0.0f ? o[i] : b[i];
+    } else if (role == 1) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = o[i] != 0.0f ? acc[i] : b[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = o[i] != 0.0f ? b[i] : acc[i];
+    }
+    return bsel == 0;
+  }
+  if (op == EW_SCALE_PRE) {
+    // imm * (acc + imm2): scale with bias_after_scale = false
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = imm * (acc[i] + imm2);
+    return true;
+  }
+  apply_binary<VEC>(op, role != 0, o, acc);
+  return false;
+}
+
+// The interpreter: decodes the program's words at run time.
 template <int VEC, int NS, int NT = 0, bool ST2 = (NT > 0)>
 __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const float (&s1)[VEC],
                                           const float (&s2)[VEC], const float (&s3)[VEC], float (&acc)[VEC],
@@ -307,128 +411,45 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
   }
   for (int k = 0; k < nsteps; ++k) {
     const long long st = steps[k];
-    const int op       = (int)(st & 0xff);
-    const int asel     = (int)((st >> 8) & 0xff);
-    const int bsel     = (int)((st >> 16) & 0xff);
-    const int role     = (int)((st >> 24) & 3);
-    const bool swap    = role != 0;
     const float imm    = __uint_as_float((uint32_t)(st >> 32));
-    if (op == EW_NOP) continue;
-    if (op >= EW_FIRST_UNARY) {
-      apply_unary<VEC>(op, imm, acc);
-      continue;
-    }
-    if (ST2 && op == EW_STORE2) {
-      if (st2) store_second<VEC>(*st2, acc);
-      continue;
-    }
-    if (NT > 0 && op == EW_STASH) {
-      if (asel == 5) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) ta[NT > 0 ? i : 0] = acc[i];
-      } else {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) tb[NT > 0 ? i : 0] = acc[i];
-      }
-      continue;
-    }
-    float o[VEC];
-    switch (asel) {  // one uniform branch per step instead of a select chain per element
-      case 5:
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = NT > 0 ? ta[NT > 0 ? i : 0] : imm;
-        break;
-      case 6:
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = NT > 0 ? tb[NT > 0 ? i : 0] : imm;
-        break;
-      case 1:
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = NS >= 1 ? s1[i] : imm;
-        break;
-      case 2:
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = NS >= 2 ? s2[i] : imm;
-        break;
-      case 3:
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = NS >= 3 ? s3[i] : imm;
-        break;
-      case 4:
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = acc[i];
-        break;
-      default:
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = imm;
-        break;
-    }
-    if (op == EW_FMA) {
-      // acc = fma(acc, A, B); B is a side operand or the immediate of the next program slot.
-      const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        float b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
-        if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
-        acc[i] = fmaf(acc[i], o[i], b);
-      }
-      if (bsel == 0) ++k;
-    } else if (op == EW_SELECT) {
-      // cinn/hlir/pe/elementwise.cc Select: cond ? true_value : false_value; the chain value is one of the three.
-      // The operand and role decisions are uniform: they are taken once per step, outside the element loops.
-      const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
-      float b[VEC];
-      switch (bsel) {
-        case 1:
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) b[i] = NS >= 1 ? s1[i] : imm2;
-          break;
-        case 2:
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) b[i] = NS >= 2 ? s2[i] : imm2;
-          break;
-        case 3:
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) b[i] = NS >= 3 ? s3[i] : imm2;
-          break;
-        case 4:
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) b[i] = acc[i];
-          break;
-        case 5:
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) b[i] = NT > 0 ? ta[NT > 0 ? i : 0] : imm2;
-          break;
-        case 6:
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) b[i] = NT > 0 ? tb[NT > 0 ? i : 0] : imm2;
-          break;
-        default:
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) b[i] = imm2;
-          break;
-      }
-      if (role == 0) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] = acc[i] != 0.0f ? o[i] : b[i];
-      } else if (role == 1) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] = o[i] != 0.0f ? acc[i] : b[i];
-      } else {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] = o[i] != 0.0f ? b[i] : acc[i];
-      }
-      if (bsel == 0) ++k;
-    } else if (op == EW_SCALE_PRE) {
-      // imm * (acc + imm2): scale with bias_after_scale = false
-      const float imm2 = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] = imm * (acc[i] + imm2);
+    const float imm2   = __uint_as_float((uint32_t)(steps[k + 1] >> 32));
+    if (chain_step<VEC, NS, NT, ST2>((int)(st & 0xff), (int)((st >> 8) & 0xff), (int)((st >> 16) & 0xff),
+                                     (int)((st >> 24) & 3), imm, imm2, s1, s2, s3, acc, ta, tb, st2))
       ++k;
-    } else {
-      apply_binary<VEC>(op, swap, o, acc);
-    }
   }
+}
+
+// The same program with its words' low halves (op, selectors, role) known at build time: SIG... are those 32-bit
+// halves, the immediates still come from the kernel's parameters.  Every branch of chain_step folds away.
+template <int VEC, int NS, int NT, bool ST2, int K, uint32_t... SIG>
+__device__ __forceinline__ void run_chain_static_from(const long long* steps, const float (&s1)[VEC],
+                                                      const float (&s2)[VEC], const float (&s3)[VEC],
+                                                      float (&acc)[VEC], float (&ta)[NT > 0 ? VEC : 1],
+                                                      float (&tb)[NT > 0 ? VEC : 1], const Store2* st2) {
+  constexpr int N = (int)sizeof...(SIG);
+  if constexpr (K < N) {
+    constexpr uint32_t sig[N] = {SIG...};
+    constexpr uint32_t w      = sig[K];
+    constexpr int op = (int)(w & 0xff), asel = (int)((w >> 8) & 0xff), bsel = (int)((w >> 16) & 0xff),
+                  role = (int)((w >> 24) & 3);
+    // what chain_step would return, as a constant: the step reads the next word's immediate
+    constexpr bool two = ((op == EW_FMA || op == EW_SELECT) && bsel == 0) || op == EW_SCALE_PRE;
+    const float imm  = __uint_as_float((uint32_t)(steps[K] >> 32));
+    const float imm2 = __uint_as_float((uint32_t)(steps[K + 1 < EW_MAX_STEPS ? K + 1 : K] >> 32));
+    (void)chain_step<VEC, NS, NT, ST2>(op, asel, bsel, role, imm, imm2, s1, s2, s3, acc, ta, tb, st2);
+    run_chain_static_from<VEC, NS, NT, ST2, K + (two ? 2 : 1), SIG...>(steps, s1, s2, s3, acc, ta, tb, st2);
+  }
+}
+template <int VEC, int NS, int NT, bool ST2, uint32_t... SIG>
+__device__ __forceinline__ void run_chain_static(const long long* steps, const float (&s1)[VEC],
+                                                 const float (&s2)[VEC], const float (&s3)[VEC], float (&acc)[VEC],
+                                                 const Store2* st2 = nullptr) {
+  float ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
+  if (NT > 0) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0.0f;
+  }
+  run_chain_static_from<VEC, NS, NT, ST2, 0, SIG...>(steps, s1, s2, s3, acc, ta, tb, st2);
 }
 }  // namespace
 }  // namespace cinn_b200

@@ -89,6 +89,7 @@ __global__ void __launch_bounds__(256)
     int ok = 1;
     if (lane == 0) ok = mbar_wait_bounded(&full[warp][s], parity) ? 1 : 0;
     ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();  // orders every lane's reads of the buffer after the completion lane 0 observed
     if (!ok) {
       gave_up = true;
       break;

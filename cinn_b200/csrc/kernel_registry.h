@@ -31,6 +31,21 @@ struct KernelRegistrar {
   }
 };
 
+// Chain kernels specialised at build time (ew_static.cu): each is registered under the interpreted kernel it
+// replaces (`base`, e.g. "ew_chain_f32_s1"), the `meta` word (operand types and addressing modes) and the low
+// halves of the program's step words (op, operand selectors, role).  The matcher compiles a group to the interpreted
+// kernel's plan as always and then swaps in the specialised kernel when one with the same key exists: the two take
+// the same parameters, immediates included.
+struct StaticChainKey {
+  const char* base;
+  long long meta;
+  int nsteps;
+  uint32_t sig[16];
+};
+int RegisterStaticChain(const StaticChainKey& key, const char* kernel_name);
+const KernelEntry* FindStaticChain(const char* base, long long meta, int nsteps, const uint32_t* sig);
+int NumStaticChains();
+
 #define CINN_B200_CAT_(a, b) a##b
 #define CINN_B200_CAT(a, b) CINN_B200_CAT_(a, b)
 // `fn` may contain commas (template arguments), hence the variadic tail.

@@ -6,6 +6,7 @@
 // build Instructions (cinn/backends/llvm/execution_engine.cc:221-230).
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <array>
 #include <atomic>
 #include <cstdarg>
@@ -43,6 +44,30 @@ const KernelEntry* FindKernelByFn(const void* fn) {
 }
 const std::vector<KernelEntry>& AllKernels() { return Table(); }
 
+// ---- chain kernels specialised at build time -----------------------------------------------------------
+struct StaticChainRecord {
+  StaticChainKey key;
+  std::string kernel_name;
+};
+static std::vector<StaticChainRecord>& StaticChains() {
+  static std::vector<StaticChainRecord> t;
+  return t;
+}
+int RegisterStaticChain(const StaticChainKey& key, const char* kernel_name) {
+  StaticChains().push_back(StaticChainRecord{key, kernel_name});
+  return (int)StaticChains().size();
+}
+const KernelEntry* FindStaticChain(const char* base, long long meta, int nsteps, const uint32_t* sig) {
+  for (auto& r : StaticChains()) {
+    if (r.key.meta != meta || r.key.nsteps != nsteps || strcmp(r.key.base, base) != 0) continue;
+    bool same = true;
+    for (int i = 0; i < nsteps && same; ++i) same = r.key.sig[i] == sig[i];
+    if (same) return FindKernel(r.kernel_name);
+  }
+  return nullptr;
+}
+int NumStaticChains() { return (int)StaticChains().size(); }
+
 // ---- errors ---------------------------------------------------------------------------------------
 static thread_local std::string tls_error;
 
@@ -73,6 +98,7 @@ static std::mutex g_mu;
 static int g_opt_sm_count = 0;  // 0: query the device, or 148 without one
 static int g_opt_rownorm_rows = 0;
 static int g_opt_ew_stream = 1, g_opt_ew_stream_stages = 0, g_opt_ew_stream_ctas = 0;
+static int g_opt_static_chains = 1;
 static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1, g_opt_rownorm_simple = -1;
 
 typedef unsigned int (*AsyncTimeoutReader)(int* cuda_status);
@@ -105,6 +131,7 @@ static DeviceInfo CurrentDeviceInfo() {
   d.rownorm_ctas_per_sm = g_opt_rownorm_ctas;
   d.enable_tma_rownorm = g_opt_enable_tma_rownorm;
   d.rownorm_simple     = g_opt_rownorm_simple;
+  d.enable_static_chains = g_opt_static_chains;
   if (g_opt_sm_count > 0) {
     d.sm_count = g_opt_sm_count;
     return d;
@@ -557,6 +584,40 @@ int cinn_b200_group_kernel(const char* fn_name, int step, char* name, size_t nam
   return CopyOut(p.steps[step].kernel->name, name, name_len);
 }
 
+long long cinn_b200_group_launch_text(const char* fn_name, char* out, size_t out_len) {
+  std::shared_ptr<GroupSlot> ref = SlotByName(fn_name);
+  if (!ref) return SetError(CINN_B200_ENOTFOUND, "no compiled group named '%s'", fn_name ? fn_name : "(null)");
+  std::string text;
+  char buf[256];
+  int index = 0;
+  for (const LaunchStep& s : ref->plan->steps) {
+    snprintf(buf, sizeof(buf), "launch %d %s grid=%u,%u,%u block=%u,%u,%u cluster=%u smem=%zu\n", index++, s.kernel->name,
+             s.grid[0], s.grid[1], s.grid[2], s.block[0], s.block[1], s.block[2], s.cluster, s.dyn_smem);
+    text += buf;
+    int k = 0;
+    for (const ArgSpec& a : s.args) {
+      switch (a.kind) {
+        case ArgSpec::kInput: snprintf(buf, sizeof(buf), "arg %d input %d\n", k, a.index); break;
+        case ArgSpec::kOutput: snprintf(buf, sizeof(buf), "arg %d output %d\n", k, a.index); break;
+        case ArgSpec::kScratch: snprintf(buf, sizeof(buf), "arg %d scratch %lld\n", k, (long long)a.ivalue); break;
+        case ArgSpec::kInt: snprintf(buf, sizeof(buf), "arg %d int %lld\n", k, (long long)a.ivalue); break;
+        case ArgSpec::kFloat: snprintf(buf, sizeof(buf), "arg %d float %.17g\n", k, a.fvalue); break;
+        default: snprintf(buf, sizeof(buf), "arg %d aligned %lld\n", k, (long long)a.ivalue); break;
+      }
+      text += buf;
+      ++k;
+    }
+  }
+  if (out && out_len > 0) {
+    const size_t n = std::min(text.size(), out_len - 1);
+    memcpy(out, text.data(), n);
+    out[n] = 0;
+  }
+  return (long long)text.size() + 1;
+}
+
+int cinn_b200_num_static_chains(void) { return NumStaticChains(); }
+
 int cinn_b200_canonical_expr(const char* group_desc, char* out, size_t out_len) {
   if (!group_desc) return SetError(CINN_B200_EINVAL, "null group description");
   GroupDesc g;
@@ -776,6 +837,10 @@ int cinn_b200_set_option(const char* key, long long value) {
   if (!key) return SetError(CINN_B200_EINVAL, "null option key");
   if (!strcmp(key, "sm_count")) {
     g_opt_sm_count = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "enable_static_chains")) {
+    g_opt_static_chains = (int)value;
     return CINN_B200_OK;
   }
   if (!strcmp(key, "enable_ew_stream")) {

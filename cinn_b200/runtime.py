@@ -138,6 +138,16 @@ class FusedGroup:
             out.append(buf.value.decode())
         return out
 
+    def launch_text(self):
+        """The launch plan as text (kernel, grid, block and every kernel parameter of each launch)."""
+        L = _lib.lib()
+        need = L.cinn_b200_group_launch_text(self.name.encode(), None, 0)
+        if need < 0:
+            _lib.check(int(need))
+        buf = ctypes.create_string_buffer(int(need))
+        L.cinn_b200_group_launch_text(self.name.encode(), buf, int(need))
+        return buf.value.decode()
+
     def bind(self, tensors):
         """Pod array for device tensors (inputs then outputs).  Keep the returned tuple alive while it is used."""
         bufs = [make_buffer(t.data_ptr(), torch_dtype_name(t), tuple(t.shape)) for t in tensors]

@@ -99,6 +99,17 @@ int cinn_b200_group_info(const char* fn_name, char* pattern, size_t pattern_len,
 /* Name of the kernel of launch step `step` of a compiled group (for tests and profiles). */
 int cinn_b200_group_kernel(const char* fn_name, int step, char* name, size_t name_len);
 
+/* The launch plan of a compiled group as text, for tests, profiles and the generator of the build-time chain
+ * kernels: one "launch <i> <kernel> grid=x,y,z block=x,y,z cluster=c smem=bytes" line per launch, each followed by
+ * one "arg <k> input|output <index>" / "arg <k> int <value>" / "arg <k> float <value>" / "arg <k> scratch <offset>" /
+ * "arg <k> aligned <0|1>" line per kernel parameter.  Written to `out` (truncated to out_len); returns the size
+ * needed including the terminator, negative on error.  The reference's counterpart is the generated host stub
+ * itself (cinn/backends/codegen_cuda_host.cc:35-170), which can only be read as LLVM IR. */
+long long cinn_b200_group_launch_text(const char* fn_name, char* out, size_t out_len);
+
+/* How many chain programs have a kernel specialised at build time in this library. */
+int cinn_b200_num_static_chains(void);
+
 /* The matcher's canonical expression of a group description, e.g. "relu(elementwise_add(%0,%1))". */
 int cinn_b200_canonical_expr(const char* group_desc, char* out, size_t out_len);
 
@@ -287,7 +298,9 @@ int cinn_b200_col_reduce_sharded_f32_emulated(cinn_b200_peer_ctx* ctx, int kind,
 int cinn_b200_device_status(unsigned int* async_wait_timeouts);
 
 /* Tuning knobs (integers) read by the matcher when a group is compiled; unknown keys give CINN_B200_ENOTFOUND.
- * "sm_count": SM count assumed when no GPU is visible (default 148); "enable_ew_stream" (default 1),
+ * "sm_count": SM count assumed when no GPU is visible (default 148); "enable_static_chains" (default 1): elementwise
+ * chains whose program has a kernel specialised at build time use it instead of the interpreting kernel;
+ * "enable_ew_stream" (default 1),
  * "ew_stream_stages", "ew_stream_ctas_per_sm": whether large elementwise groups with 16-bit outputs stream their
  * input through shared-memory rings filled by bulk copies, the ring depth and the resident CTAs per SM; "rownorm_rows_per_iter": rows per CTA
  * iteration of the register-resident softmax / layer_norm kernels (0 = automatic, else 1, 2 or 4); "rownorm_stages", "rownorm_ctas_per_sm":
