@@ -656,8 +656,14 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
           else if (cbb) chain_is_a = false;
           else {
             // Neither operand is computed in the group: the chain starts at the full-size group input.
-            const bool a_full = cb.input_index.count(a) && cb.values[a].numel() == cb.n;
-            const bool b_full = cb.input_index.count(b) && cb.values[b].numel() == cb.n;
+            // (a group input itself, or a cast of one that the load performs: the walk continues through that cast)
+            auto full_input = [&](const std::string& v) {
+              if (cb.values[v].numel() != cb.n) return false;
+              if (cb.input_index.count(v)) return true;
+              const OpDesc* q = cb.producer.count(v) ? cb.producer[v] : nullptr;
+              return q && cb.IsLoadCast(*q);
+            };
+            const bool a_full = full_input(a), b_full = full_input(b);
             // two constants (or a constant and a broadcast operand): the chain starts from a full-size constant
             auto full_constant = [&](const std::string& v) {
               const OpDesc* q = cb.producer.count(v) ? cb.producer[v] : nullptr;

@@ -102,6 +102,7 @@ __device__ __forceinline__ void chain_values2(const void* in0, int in_type, cons
 template <int NS, int NT = 0>
 __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
     k_chain_reduce_row(CHAIN_PARAMS, long long rows, long long r, long long group) {
+  grid_dependency_sync();
   CHAIN_PROLOGUE;
   __shared__ float part[8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -161,6 +162,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
 template <int NS, int NT = 0>
 __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
     k_chain_reduce_col(CHAIN_PARAMS, long long outer, long long r, long long inner, long long rows_per_split) {
+  grid_dependency_sync();
   CHAIN_PROLOGUE;
   const float id     = cr_identity(rop);
   const long long o  = blockIdx.y;
@@ -203,13 +205,13 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
 
 }  // namespace
 
-CINN_B200_REGISTER_KERNEL("chain_reduce_row_s0", 34, 256, k_chain_reduce_row<0>);
-CINN_B200_REGISTER_KERNEL("chain_reduce_row_s1", 34, 256, k_chain_reduce_row<1>);
-CINN_B200_REGISTER_KERNEL("chain_reduce_row_s3", 34, 256, k_chain_reduce_row<3>);
-CINN_B200_REGISTER_KERNEL("chain_reduce_row_s3t", 34, 256, k_chain_reduce_row<3, 2>);
-CINN_B200_REGISTER_KERNEL("chain_reduce_col_s0", 35, 256, k_chain_reduce_col<0>);
-CINN_B200_REGISTER_KERNEL("chain_reduce_col_s1", 35, 256, k_chain_reduce_col<1>);
-CINN_B200_REGISTER_KERNEL("chain_reduce_col_s3", 35, 256, k_chain_reduce_col<3>);
-CINN_B200_REGISTER_KERNEL("chain_reduce_col_s3t", 35, 256, k_chain_reduce_col<3, 2>);
+CINN_B200_REGISTER_KERNEL_PDL("chain_reduce_row_s0", 34, 256, k_chain_reduce_row<0>);
+CINN_B200_REGISTER_KERNEL_PDL("chain_reduce_row_s1", 34, 256, k_chain_reduce_row<1>);
+CINN_B200_REGISTER_KERNEL_PDL("chain_reduce_row_s3", 34, 256, k_chain_reduce_row<3>);
+CINN_B200_REGISTER_KERNEL_PDL("chain_reduce_row_s3t", 34, 256, k_chain_reduce_row<3, 2>);
+CINN_B200_REGISTER_KERNEL_PDL("chain_reduce_col_s0", 35, 256, k_chain_reduce_col<0>);
+CINN_B200_REGISTER_KERNEL_PDL("chain_reduce_col_s1", 35, 256, k_chain_reduce_col<1>);
+CINN_B200_REGISTER_KERNEL_PDL("chain_reduce_col_s3", 35, 256, k_chain_reduce_col<3>);
+CINN_B200_REGISTER_KERNEL_PDL("chain_reduce_col_s3t", 35, 256, k_chain_reduce_col<3, 2>);
 
 }  // namespace cinn_b200

@@ -14,6 +14,16 @@
 
 namespace cinn_b200 {
 
+// First statement of the kernels that may be launched with programmatic stream serialisation: wait until the
+// kernel launched before this one on the stream has completed and its writes are visible (a no-op for an ordinary
+// launch), then allow the NEXT kernel of the stream to be scheduled early in turn.  The dependents are released only
+// after this wait, so at most one kernel ever sits waiting behind a running one.
+__device__ __forceinline__ void grid_dependency_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+
 // cinn/backends/llvm/codegen_llvm.cc:310-340: fcmp ogt/olt + select.
 __device__ __forceinline__ float x86_max(float a, float b) { return a > b ? a : b; }
 __device__ __forceinline__ float x86_min(float a, float b) { return a < b ? a : b; }

@@ -29,6 +29,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
                long long nsteps_ll, long long t0, long long t1, long long t2, long long t3, long long t4,
                long long t5, long long t6, long long t7, long long t8, long long t9, long long t10, long long t11,
                long long t12, long long t13, long long t14, long long t15, void* __restrict__ out2) {
+  grid_dependency_sync();
   const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
   const DynProgram prog    = {steps, (int)nsteps_ll, meta};
   const ChainGeometry geo  = {n, vec_ok, mid1, inner1, mid2, inner2, mid3, inner3};
@@ -40,12 +41,12 @@ __global__ void __launch_bounds__(256, NS == 0 ? 6 : (NS == 1 ? 5 : 4))
 }  // namespace
 
 #define REG_CHAIN(OUTNAME, OutT)                                                               \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s0", 32, 256, k_ew_chain<OutT, 0>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s1", 32, 256, k_ew_chain<OutT, 1>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3", 32, 256, k_ew_chain<OutT, 3>);        \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3t", 32, 256, k_ew_chain<OutT, 3, 2>);    \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s1o", 32, 256, k_ew_chain<OutT, 1, 0, true>); \
-  CINN_B200_REGISTER_KERNEL("ew_chain_" OUTNAME "_s3o", 32, 256, k_ew_chain<OutT, 3, 0, true>)
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_" OUTNAME "_s0", 32, 256, k_ew_chain<OutT, 0>);        \
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_" OUTNAME "_s1", 32, 256, k_ew_chain<OutT, 1>);        \
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_" OUTNAME "_s3", 32, 256, k_ew_chain<OutT, 3>);        \
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_" OUTNAME "_s3t", 32, 256, k_ew_chain<OutT, 3, 2>);    \
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_" OUTNAME "_s1o", 32, 256, k_ew_chain<OutT, 1, 0, true>); \
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_" OUTNAME "_s3o", 32, 256, k_ew_chain<OutT, 3, 0, true>)
 REG_CHAIN("f32", float);
 REG_CHAIN("f16", __half);
 REG_CHAIN("bf16", __nv_bfloat16);

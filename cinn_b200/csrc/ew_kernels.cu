@@ -20,6 +20,7 @@ namespace cinn_b200 {
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) k_add_relu_f32(const float* __restrict__ a, const float* __restrict__ b,
                                                       float* __restrict__ y, long long n, long long vec_ok) {
+  grid_dependency_sync();
   const long long tid    = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   long long done         = 0;
@@ -37,7 +38,7 @@ __global__ void __launch_bounds__(256) k_add_relu_f32(const float* __restrict__ 
   }
   for (long long i = done + tid; i < n; i += stride) y[i] = x86_max(a[i] + b[i], 0.0f);
 }
-CINN_B200_REGISTER_KERNEL("ew_add_relu_f32", 5, 256, k_add_relu_f32);
+CINN_B200_REGISTER_KERNEL_PDL("ew_add_relu_f32", 5, 256, k_add_relu_f32);
 
 // ------------------------------------------------------------------------------------------------
 // out = cast<OutT>(tanh(scale * (x + bias[col]) + shift)), bias broadcast along the last axis.
@@ -77,6 +78,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
     k_bias_scale_tanh_cast(const float* __restrict__ x, const float* __restrict__ bias, OutT* __restrict__ y,
                            long long n, long long cols, long long vec_ok, double scale_d, double shift_d) {
+  grid_dependency_sync();
   const float scale      = (float)scale_d;
   const float shift      = (float)shift_d;
   const long long tid    = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -126,9 +128,9 @@ __global__ void __launch_bounds__(256)
     Io<OutT>::store1(y + i, t);
   }
 }
-CINN_B200_REGISTER_KERNEL("ew_bias_scale_tanh_cast_f32_f16", 8, 256, k_bias_scale_tanh_cast<__half>);
-CINN_B200_REGISTER_KERNEL("ew_bias_scale_tanh_cast_f32_bf16", 8, 256, k_bias_scale_tanh_cast<__nv_bfloat16>);
-CINN_B200_REGISTER_KERNEL("ew_bias_scale_tanh_cast_f32_f32", 8, 256, k_bias_scale_tanh_cast<float>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bias_scale_tanh_cast_f32_f16", 8, 256, k_bias_scale_tanh_cast<__half>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bias_scale_tanh_cast_f32_bf16", 8, 256, k_bias_scale_tanh_cast<__nv_bfloat16>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bias_scale_tanh_cast_f32_f32", 8, 256, k_bias_scale_tanh_cast<float>);
 
 // ------------------------------------------------------------------------------------------------
 // out = [relu](batch_norm_infer(x)) on NCHW: max(((x - mean[c]) * scale[c]) / sqrt(var[c] + eps) + bias[c], 0).
@@ -145,6 +147,7 @@ __global__ void __launch_bounds__(256)
     k_bn_nchw(const T* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ bias,
               const float* __restrict__ mean, const float* __restrict__ var, T* __restrict__ y, long long planes,
               long long channels, long long hw, long long chunks, long long vec_ok, double eps_d) {
+  grid_dependency_sync();
   constexpr int V        = Io<T>::kVec;
   const long long n_ctas = planes * chunks;
   for (long long cta = blockIdx.x; cta < n_ctas; cta += gridDim.x) {
@@ -214,6 +217,7 @@ __global__ void __launch_bounds__(256)
                     const float* __restrict__ t0_in, const float* __restrict__ var0, T* __restrict__ y,
                     long long planes, long long channels, long long hw, long long chunks, long long vec_ok,
                     long long t0_form, long long vae_form, double count_d, double eps_d) {
+  grid_dependency_sync();
   const long long n_ctas = planes * chunks;
   const float count = (float)count_d, eps = (float)eps_d;
   for (long long cta = blockIdx.x; cta < n_ctas; cta += gridDim.x) {
@@ -262,21 +266,21 @@ __global__ void __launch_bounds__(256)
     }
   }
 }
-CINN_B200_REGISTER_KERNEL("ew_bn_grad_apply_nchw_f32", 18, 256, k_bn_grad_apply<float>);
-CINN_B200_REGISTER_KERNEL("ew_bn_grad_apply_nchw_f16", 18, 256, k_bn_grad_apply<__half>);
-CINN_B200_REGISTER_KERNEL("ew_bn_grad_apply_nchw_bf16", 18, 256, k_bn_grad_apply<__nv_bfloat16>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_grad_apply_nchw_f32", 18, 256, k_bn_grad_apply<float>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_grad_apply_nchw_f16", 18, 256, k_bn_grad_apply<__half>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_grad_apply_nchw_bf16", 18, 256, k_bn_grad_apply<__nv_bfloat16>);
 
-CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f32", 12, 256, k_bn_nchw<float, true>);
-CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true>);
-CINN_B200_REGISTER_KERNEL("ew_bn_nchw_f32", 12, 256, k_bn_nchw<float, false>);
-CINN_B200_REGISTER_KERNEL("ew_bn_nchw_f16", 12, 256, k_bn_nchw<__half, false>);
-CINN_B200_REGISTER_KERNEL("ew_bn_relu_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, true>);
-CINN_B200_REGISTER_KERNEL("ew_bn_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, false>);
-CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_nchw_f32", 12, 256, k_bn_nchw<float, false, true>);
-CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_relu_nchw_f32", 12, 256, k_bn_nchw<float, true, true>);
-CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_nchw_f16", 12, 256, k_bn_nchw<__half, false, true>);
-CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true, true>);
-CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, false, true>);
-CINN_B200_REGISTER_KERNEL("ew_bn_train_apply_relu_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, true, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_relu_nchw_f32", 12, 256, k_bn_nchw<float, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_nchw_f32", 12, 256, k_bn_nchw<float, false>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_nchw_f16", 12, 256, k_bn_nchw<__half, false>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_relu_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, false>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_train_apply_nchw_f32", 12, 256, k_bn_nchw<float, false, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_train_apply_relu_nchw_f32", 12, 256, k_bn_nchw<float, true, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_train_apply_nchw_f16", 12, 256, k_bn_nchw<__half, false, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_train_apply_relu_nchw_f16", 12, 256, k_bn_nchw<__half, true, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_train_apply_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, false, true>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bn_train_apply_relu_nchw_bf16", 12, 256, k_bn_nchw<__nv_bfloat16, true, true>);
 
 }  // namespace cinn_b200

@@ -42,6 +42,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
     k_bias_scale_tanh_cast_stream(const float* __restrict__ x, const float* __restrict__ bias, OutT* __restrict__ y,
                                   long long n, long long cols, long long stages_ll, double scale_d, double shift_d) {
+  grid_dependency_sync();
   extern __shared__ __align__(128) unsigned char ring_all[];
   __shared__ __align__(8) uint64_t full[kWarps][kMaxStages];
   const int lane           = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -139,8 +140,8 @@ __global__ void __launch_bounds__(256)
 
 }  // namespace
 
-CINN_B200_REGISTER_KERNEL("ew_bias_scale_tanh_cast_stream_f32_f16", 8, 256, k_bias_scale_tanh_cast_stream<__half>);
-CINN_B200_REGISTER_KERNEL("ew_bias_scale_tanh_cast_stream_f32_bf16", 8, 256,
+CINN_B200_REGISTER_KERNEL_PDL("ew_bias_scale_tanh_cast_stream_f32_f16", 8, 256, k_bias_scale_tanh_cast_stream<__half>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_bias_scale_tanh_cast_stream_f32_bf16", 8, 256,
                           k_bias_scale_tanh_cast_stream<__nv_bfloat16>);
 
 }  // namespace cinn_b200

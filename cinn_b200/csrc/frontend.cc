@@ -988,7 +988,7 @@ std::unique_ptr<Computation> Computation::BuildAndCompile(const NetBuilder& b, c
                                                           int device, std::string* err) {
   std::unique_ptr<Computation> c(new Computation());
   c->device_ = device;
-  DeviceInfo dev;
+  DeviceInfo dev = CurrentDeviceInfo();  // the planner options apply to the fusion pass's trial compilations too
   if (device >= 0) {
     cudaError_t e = cudaSetDevice(device);
     if (e != cudaSuccess) {

@@ -1,0 +1,225 @@
+"""Generates ew_static_table.inc: one STATIC_CHAIN line per elementwise program that gets a kernel specialised at
+build time (see ew_static.cu).
+
+    python cinn_b200/csrc/gen_static_chains.py            # rewrite the table, then rebuild the library
+    python cinn_b200/csrc/gen_static_chains.py --check    # exit 1 if the committed table is out of date
+
+Each entry of GROUPS is a fused group as the fusion pass would emit it.  The script compiles it with the library's
+own matcher (interpreter forced, no GPU needed), reads the plan back as text and turns the interpreted kernel's name,
+its `meta` word (operand types and addressing modes) and the low halves of its step words into the template
+arguments of one kernel.  Shapes only matter through the addressing mode they give each operand: a full-size operand,
+a vector along the last axis, a per-channel vector of NCHW, a single element.  Sizes and immediates stay run-time
+parameters of the generated kernel, so an entry serves every shape with the same modes and every constant.
+
+The list holds what elementwise groups of real networks mostly are (bias + activation, residual add, affine,
+clamp, masks and compares, casts, gelu / swish) and the groups the benchmark times.
+"""
+import os
+import re
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FULL = "64,1024"        # a full-size operand
+ROWVEC = "1024"         # broadcast along the last axis
+NCHW = "8,16,32,32"     # with a per-channel operand [16] on axis 1
+CHAN = "16"
+
+
+def group(name, inputs, ops, out, out_dtype, shape=FULL):
+    lines = ["group fn_static_" + name]
+    lines += ["input %s" % i for i in inputs]
+    lines += ["op %s" % o for o in ops]
+    lines.append("output %s %s %s" % (out, out_dtype, shape))
+    return name, "\n".join(lines) + "\n"
+
+
+def unary(op, dt="float32"):
+    return group("%s_%s" % (op, dt), ["x %s %s" % (dt, FULL)], ["%s y = x" % op], "y", dt)
+
+
+def binary(op, dt="float32", out_dt=None, tag=None):
+    return group("%s_%s" % (tag or op, dt), ["a %s %s" % (dt, FULL), "b %s %s" % (dt, FULL)],
+                 ["%s y = a b ; axis=-1" % op], "y", out_dt or dt)
+
+
+def bias_act(act, dt="float32"):
+    """act(x + bias) with bias along the last axis; 16-bit storage widened by casts as AutoCast leaves it."""
+    if dt == "float32":
+        ops = ["elementwise_add t = x b ; axis=-1"] + (["%s y = t" % act] if act else [])
+        return group("bias_%s_f32" % (act or "add"), ["x float32 " + FULL, "b float32 " + ROWVEC], ops,
+                     "y" if act else "t", "float32")
+    ops = ["cast x32 = x ; dtype=float32", "elementwise_add t = x32 b ; axis=-1"]
+    ops += ["%s u = t" % act] if act else ["identity u = t"]
+    ops += ["cast y = u ; dtype=%s" % dt]
+    return group("bias_%s_%s" % (act or "add", dt), ["x %s %s" % (dt, FULL), "b float32 " + ROWVEC], ops, "y", dt)
+
+
+GROUPS = []
+# unary math
+for op in ("relu", "sigmoid", "tanh", "exp", "log", "sqrt", "rsqrt", "abs", "negative", "reciprocal", "erf"):
+    GROUPS.append(unary(op))
+for op in ("relu", "sigmoid", "tanh", "exp"):
+    GROUPS.append(group("%s_f16" % op, ["x float16 " + FULL], ["cast a = x ; dtype=float32", "%s b = a" % op,
+                                                                  "cast y = b ; dtype=float16"], "y", "float16"))
+# binary, both operands full size
+for op, tag in (("elementwise_add", "add"), ("subtract", "sub"), ("elementwise_mul", "mul"), ("divide", "div"),
+                ("max", "max"), ("min", "min")):
+    GROUPS.append(binary(op, tag=tag))
+for op in ("greater_than", "less_than", "equal", "greater_equal"):
+    GROUPS.append(binary(op, out_dt="bool"))
+GROUPS.append(binary("logical_and", dt="bool"))
+GROUPS.append(binary("logical_or", dt="bool"))
+for op, tag in (("elementwise_add", "add"), ("elementwise_mul", "mul")):
+    GROUPS.append(group("%s_f16" % tag, ["a float16 " + FULL, "b float16 " + FULL],
+                        ["cast a32 = a ; dtype=float32", "cast b32 = b ; dtype=float32",
+                         "%s t = a32 b32 ; axis=-1" % op, "cast y = t ; dtype=float16"], "y", "float16"))
+# the benchmark's generic groups
+GROUPS.append(group("abs_add_f32", ["A float32 " + FULL, "B float32 " + FULL],
+                    ["elementwise_add t0 = A B", "abs t1 = t0"], "t1", "float32"))
+GROUPS.append(group("select_f32", ["M bool " + FULL, "A float32 " + FULL, "B float32 " + FULL],
+                    ["select t0 = M A B"], "t0", "float32"))
+GROUPS.append(group("tree_add_mul_sub_f32", ["A float32 " + FULL, "B float32 " + FULL, "C float32 " + FULL,
+                                             "D float32 " + FULL],
+                    ["elementwise_add s = A B ; axis=-1", "subtract d = C D ; axis=-1",
+                     "elementwise_mul y = s d ; axis=-1"], "y", "float32"))
+# bias (last axis) + activation
+for act in (None, "relu", "sigmoid", "tanh", "gelu"):
+    if act == "gelu":
+        continue
+    GROUPS.append(bias_act(act))
+for act in (None, "relu", "sigmoid"):
+    GROUPS.append(bias_act(act, "float16"))
+# residual: relu(a + b) exists as a dedicated kernel; three-operand sum and add + activation variants
+GROUPS.append(group("add3_f32", ["a float32 " + FULL, "b float32 " + FULL, "c float32 " + FULL],
+                    ["elementwise_add t = a b ; axis=-1", "elementwise_add y = t c ; axis=-1"], "y", "float32"))
+GROUPS.append(group("add_sigmoid_f32", ["a float32 " + FULL, "b float32 " + FULL],
+                    ["elementwise_add t = a b ; axis=-1", "sigmoid y = t"], "y", "float32"))
+GROUPS.append(group("add_tanh_f32", ["a float32 " + FULL, "b float32 " + FULL],
+                    ["elementwise_add t = a b ; axis=-1", "tanh y = t"], "y", "float32"))
+# affine forms
+GROUPS.append(group("scale_f32", ["x float32 " + FULL], ["scale y = x ; scale=2.0 bias=1.0 bias_after_scale=true"],
+                    "y", "float32"))
+GROUPS.append(group("scale_relu_f32", ["x float32 " + FULL],
+                    ["scale t = x ; scale=2.0 bias=1.0 bias_after_scale=true", "relu y = t"], "y", "float32"))
+GROUPS.append(group("mul_add_f32", ["x float32 " + FULL, "a float32 " + FULL, "b float32 " + FULL],
+                    ["elementwise_mul t = x a ; axis=-1", "elementwise_add y = t b ; axis=-1"], "y", "float32"))
+GROUPS.append(group("rowvec_mul_add_f32", ["x float32 " + FULL, "g float32 " + ROWVEC, "b float32 " + ROWVEC],
+                    ["elementwise_mul t = x g ; axis=-1", "elementwise_add y = t b ; axis=-1"], "y", "float32"))
+GROUPS.append(group("channel_mul_add_f32", ["x float32 " + NCHW, "g float32 " + CHAN, "b float32 " + CHAN],
+                    ["elementwise_mul t = x g ; axis=1", "elementwise_add y = t b ; axis=1"], "y", "float32", NCHW))
+GROUPS.append(group("channel_mul_add_relu_f32", ["x float32 " + NCHW, "g float32 " + CHAN, "b float32 " + CHAN],
+                    ["elementwise_mul t = x g ; axis=1", "elementwise_add u = t b ; axis=1", "relu y = u"], "y",
+                    "float32", NCHW))
+# clamp, masks, casts
+GROUPS.append(group("clip_f32", ["x float32 " + FULL],
+                    ["fill_constant lo = ; shape=%s value=-1.0 dtype=float32" % FULL, "max t = x lo ; axis=-1",
+                     "fill_constant hi = ; shape=%s value=1.0 dtype=float32" % FULL, "min y = t hi ; axis=-1"],
+                    "y", "float32"))
+GROUPS.append(unary("relu6"))
+GROUPS.append(group("dropout_apply_f32", ["x float32 " + FULL, "m float32 " + FULL],
+                    ["elementwise_mul t = x m ; axis=-1", "scale y = t ; scale=1.25 bias=0.0 bias_after_scale=true"],
+                    "y", "float32"))
+GROUPS.append(group("cast_f32_f16", ["x float32 " + FULL], ["cast y = x ; dtype=float16"], "y", "float16"))
+GROUPS.append(group("cast_f16_f32", ["x float16 " + FULL], ["cast y = x ; dtype=float32"], "y", "float32"))
+GROUPS.append(group("cast_f32_bf16", ["x float32 " + FULL], ["cast y = x ; dtype=bfloat16"], "y", "bfloat16"))
+# squared difference, swish, gelu (as the decomposer writes it)
+GROUPS.append(group("sq_diff_f32", ["a float32 " + FULL, "b float32 " + FULL],
+                    ["subtract d = a b ; axis=-1", "identity di = d", "elementwise_mul y = d di ; axis=-1"], "y",
+                    "float32"))
+GROUPS.append(group("swish_f32", ["x float32 " + FULL], ["sigmoid s = x", "elementwise_mul y = x s ; axis=-1"], "y",
+                    "float32"))
+# two outputs: the pre-activation kept beside the activation
+GROUPS.append(("bias_pre_and_relu_f32",
+               "group fn_static_bias_pre_and_relu_f32\ninput X float32 %s\ninput bias float32 %s\n"
+               "op elementwise_add pre = X bias ; axis=-1\nop relu act = pre\n"
+               "output pre float32 %s\noutput act float32 %s\n" % (FULL, ROWVEC, FULL, FULL)))
+
+VARIANT = {"_s0": (0, 0, "false"), "_s1": (1, 0, "false"), "_s3": (3, 0, "false"), "_s3t": (3, 2, "true"),
+           "_s1o": (1, 0, "true"), "_s3o": (3, 0, "true")}
+OUT_T = {"f32": "float", "f16": "__half", "bf16": "__nv_bfloat16", "bool": "uint8_t", "i32": "int32_t",
+         "i64": "long long"}
+
+
+def plan_of(desc):
+    """(kernel name, [int args]) of the interpreted plan of one group, or None when it is not a float chain."""
+    import cinn_b200
+    g = cinn_b200.FusedGroup(desc)
+    try:
+        text = g.launch_text()
+    finally:
+        g.release()
+    launches = [l for l in text.splitlines() if l.startswith("launch ")]
+    if len(launches) != 1:
+        return None
+    kernel = launches[0].split()[2]
+    if not re.match(r"ew_chain_(f32|f16|bf16|bool|i32|i64)_s", kernel):
+        return None
+    args = {}
+    for l in text.splitlines():
+        w = l.split()
+        if w[0] == "arg" and w[2] == "int":
+            args[int(w[1])] = int(w[3])
+    return kernel, args
+
+
+def table_lines():
+    import cinn_b200
+    L = cinn_b200.lib()
+    cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
+    try:
+        seen, lines, skipped = {}, [], []
+        for name, desc in GROUPS:
+            try:
+                got = plan_of(desc)
+            except cinn_b200.CinnB200Error as e:
+                skipped.append("%s: %s" % (name, e))
+                continue
+            if got is None:
+                skipped.append("%s: not a single interpreted float chain" % name)
+                continue
+            kernel, args = got
+            m = re.match(r"ew_chain_(\w+?)(_s\w+)$", kernel)
+            out_t, (ns, nt, st2) = OUT_T[m.group(1)], VARIANT[m.group(2)]
+            meta, nsteps = args[7], args[14]
+            sig = [args[15 + k] & 0xffffffff for k in range(nsteps)]
+            if nsteps == 0:
+                skipped.append("%s: empty program" % name)
+                continue
+            key = (kernel, meta, tuple(sig))
+            if key in seen:
+                skipped.append("%s: same program as %s" % (name, seen[key]))
+                continue
+            seen[key] = name
+            lines.append('STATIC_CHAIN(%s, "%s", %s, %d, %d, %s, %d, %s);' % (
+                name, kernel, out_t, ns, nt, st2, meta, ", ".join("0x%08xu" % s for s in sig)))
+        return lines, skipped
+    finally:
+        L.cinn_b200_set_option(b"enable_static_chains", 1)
+
+
+HEADER = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_CHAIN(id, interpreted kernel, output type, side\n"
+          "// inputs, temporaries, second output, meta word, low halves of the step words...).\n")
+
+
+def main():
+    lines, skipped = table_lines()
+    text = HEADER + "\n".join(lines) + "\n"
+    path = os.path.join(HERE, "ew_static_table.inc")
+    if "--check" in sys.argv:
+        ok = open(path).read() == text
+        print("ew_static_table.inc is %s" % ("up to date" if ok else "OUT OF DATE"))
+        return 0 if ok else 1
+    with open(path, "w") as f:
+        f.write(text)
+    print("%d static chains written" % len(lines))
+    for s in skipped:
+        print("skipped", s)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -106,6 +106,10 @@ struct DeviceInfo {
   int enable_tma_rownorm    = -1;  // rows streamed through shared memory by bulk copies: 1 on, 0 off, -1 automatic
 };
 
+// The planner's view of the current device with the options of cinn_b200_set_option applied (runtime.cc); without
+// a GPU, the B200 defaults.
+DeviceInfo CurrentDeviceInfo();
+
 // Returns nullptr and fills *err when no prebuilt kernel covers the group.
 std::unique_ptr<CompiledGroup> CompileGroup(const GroupDesc& g, const DeviceInfo& dev, std::string* err);
 

@@ -17,17 +17,19 @@ struct KernelEntry {
   const void* fn;     // host stub address, what cinn_call_cuda_kernel receives as kernel_fn
   int num_params;     // number of kernel parameters (pointers first, then scalars)
   int max_threads;    // __launch_bounds__ of the kernel
+  bool pdl;           // the kernel calls grid_dependency_sync() before it touches global memory, so it may be
+                      // launched with programmatic stream serialisation (see LaunchEntry in runtime.cc)
 };
 
 // Adds an entry at static-initialisation time; returns its index.
-int RegisterKernel(const char* name, const void* fn, int num_params, int max_threads);
+int RegisterKernel(const char* name, const void* fn, int num_params, int max_threads, bool pdl = false);
 const KernelEntry* FindKernel(const std::string& name);
 const KernelEntry* FindKernelByFn(const void* fn);
 const std::vector<KernelEntry>& AllKernels();
 
 struct KernelRegistrar {
-  KernelRegistrar(const char* name, const void* fn, int num_params, int max_threads) {
-    RegisterKernel(name, fn, num_params, max_threads);
+  KernelRegistrar(const char* name, const void* fn, int num_params, int max_threads, bool pdl = false) {
+    RegisterKernel(name, fn, num_params, max_threads, pdl);
   }
 };
 
@@ -52,5 +54,10 @@ int NumStaticChains();
 #define CINN_B200_REGISTER_KERNEL(name, num_params, max_threads, ...)                                  \
   static ::cinn_b200::KernelRegistrar CINN_B200_CAT(cinn_b200_kernel_registrar_, __COUNTER__)(        \
       name, reinterpret_cast<const void*>(&__VA_ARGS__), num_params, max_threads)
+
+// The same for a kernel whose first statement is grid_dependency_sync().
+#define CINN_B200_REGISTER_KERNEL_PDL(name, num_params, max_threads, ...)                              \
+  static ::cinn_b200::KernelRegistrar CINN_B200_CAT(cinn_b200_kernel_registrar_, __COUNTER__)(        \
+      name, reinterpret_cast<const void*>(&__VA_ARGS__), num_params, max_threads, true)
 
 }  // namespace cinn_b200

@@ -36,6 +36,7 @@ __device__ __forceinline__ float combine4(float acc, uint4 u) {
 template <class Op, int ITERS>
 __global__ void __launch_bounds__(256) k_row_reduce_warp(const float* __restrict__ x, float* __restrict__ y,
                                                          long long rows, long long r, long long vec_ok) {
+  grid_dependency_sync();
   const int lane         = threadIdx.x & 31;
   const long long warp   = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -98,6 +99,7 @@ template <class Op>
 __global__ void __launch_bounds__(512) k_row_reduce_cta(const float* __restrict__ x, float* __restrict__ y,
                                                         long long rows, long long r, long long splits,
                                                         long long seg, long long vec_ok) {
+  grid_dependency_sync();
   __shared__ float scratch[32];
   const long long n_ctas = rows * splits;
   for (long long cta = blockIdx.x; cta < n_ctas; cta += gridDim.x) {
@@ -121,6 +123,7 @@ template <class Op>
 __global__ void __launch_bounds__(512) k_row_reduce_cluster(const float* __restrict__ x, float* __restrict__ y,
                                                             long long rows, long long r, long long seg,
                                                             long long vec_ok) {
+  grid_dependency_sync();
   __shared__ float scratch[32];
   __shared__ float partials[16];
   cg::cluster_group cluster  = cg::this_cluster();
@@ -159,6 +162,7 @@ template <class Op>
 __global__ void __launch_bounds__(256) k_col_reduce(const float* __restrict__ x, float* __restrict__ y,
                                                     long long outer, long long r, long long inner,
                                                     long long rows_per_split, long long vec_ok) {
+  grid_dependency_sync();
   const long long split  = blockIdx.z;
   const long long k0     = split * rows_per_split;
   const long long k1     = min(k0 + rows_per_split, r);
@@ -211,14 +215,14 @@ __global__ void __launch_bounds__(256) k_col_reduce(const float* __restrict__ x,
 }
 
 #define REG_REDUCE_FAMILY(OPNAME, OP)                                                                       \
-  CINN_B200_REGISTER_KERNEL("row_reduce_warp1_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 1>);           \
-  CINN_B200_REGISTER_KERNEL("row_reduce_warp2_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 2>);           \
-  CINN_B200_REGISTER_KERNEL("row_reduce_warp4_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 4>);           \
-  CINN_B200_REGISTER_KERNEL("row_reduce_warp8_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 8>);           \
-  CINN_B200_REGISTER_KERNEL("row_reduce_warp16_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 16>);         \
-  CINN_B200_REGISTER_KERNEL("row_reduce_cta_" OPNAME "_f32", 7, 512, k_row_reduce_cta<OP>);                 \
-  CINN_B200_REGISTER_KERNEL("row_reduce_cluster_" OPNAME "_f32", 6, 512, k_row_reduce_cluster<OP>);         \
-  CINN_B200_REGISTER_KERNEL("col_reduce_" OPNAME "_f32", 7, 256, k_col_reduce<OP>)
+  CINN_B200_REGISTER_KERNEL_PDL("row_reduce_warp1_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 1>);           \
+  CINN_B200_REGISTER_KERNEL_PDL("row_reduce_warp2_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 2>);           \
+  CINN_B200_REGISTER_KERNEL_PDL("row_reduce_warp4_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 4>);           \
+  CINN_B200_REGISTER_KERNEL_PDL("row_reduce_warp8_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 8>);           \
+  CINN_B200_REGISTER_KERNEL_PDL("row_reduce_warp16_" OPNAME "_f32", 5, 256, k_row_reduce_warp<OP, 16>);         \
+  CINN_B200_REGISTER_KERNEL_PDL("row_reduce_cta_" OPNAME "_f32", 7, 512, k_row_reduce_cta<OP>);                 \
+  CINN_B200_REGISTER_KERNEL_PDL("row_reduce_cluster_" OPNAME "_f32", 6, 512, k_row_reduce_cluster<OP>);         \
+  CINN_B200_REGISTER_KERNEL_PDL("col_reduce_" OPNAME "_f32", 7, 256, k_col_reduce<OP>)
 
 REG_REDUCE_FAMILY("sum", SumOp);
 REG_REDUCE_FAMILY("prod", ProdOp);

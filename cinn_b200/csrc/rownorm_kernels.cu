@@ -66,6 +66,7 @@ template <typename T, int G, int VPT, int R, bool LAYERNORM>
 __global__ void __launch_bounds__(G == 32 ? 256 : G, RownormMinBlocks(G, VPT, R))
     k_rownorm_reg(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                   T* __restrict__ y, long long rows, long long cols, double eps_d, double inv_n_d) {
+  grid_dependency_sync();
   constexpr int V      = Io<T>::kVec;
   constexpr int NWARPS = G == 32 ? 1 : G / 32;
   // layer_norm keeps the rows packed; softmax keeps exp(x) in fp32 (it is needed again for the output and
@@ -208,6 +209,7 @@ __global__ void __launch_bounds__(512)
     k_rownorm_cluster(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                       T* __restrict__ y, long long rows, long long cols, long long seg, long long mode,
                       double eps_d) {
+  grid_dependency_sync();
   extern __shared__ __align__(16) float row_smem[];
   __shared__ float scratch[32];
   __shared__ float part1[16], part2[16];
@@ -261,9 +263,9 @@ __global__ void __launch_bounds__(512)
 }
 
 #define REG_ROWNORM_ONE(TNAME, T, G, VPT, R)                                                                     \
-  CINN_B200_REGISTER_KERNEL("softmax_row_" TNAME "_g" #G "_v" #VPT "_r" #R, 8, (G == 32 ? 256 : G),               \
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_row_" TNAME "_g" #G "_v" #VPT "_r" #R, 8, (G == 32 ? 256 : G),               \
                             k_rownorm_reg<T, G, VPT, R, false>);                                                  \
-  CINN_B200_REGISTER_KERNEL("layernorm_row_" TNAME "_g" #G "_v" #VPT "_r" #R, 8, (G == 32 ? 256 : G),             \
+  CINN_B200_REGISTER_KERNEL_PDL("layernorm_row_" TNAME "_g" #G "_v" #VPT "_r" #R, 8, (G == 32 ? 256 : G),             \
                             k_rownorm_reg<T, G, VPT, R, true>)
 #define REG_ROWNORM_G(TNAME, T, G)    \
   REG_ROWNORM_ONE(TNAME, T, G, 1, 1); \
@@ -285,7 +287,7 @@ __global__ void __launch_bounds__(512)
   REG_ROWNORM_ONE(TNAME, T, 1024, 1, 1); \
   REG_ROWNORM_ONE(TNAME, T, 1024, 2, 1); \
   REG_ROWNORM_ONE(TNAME, T, 1024, 4, 1); \
-  CINN_B200_REGISTER_KERNEL("rownorm_cluster_" TNAME, 9, 512, k_rownorm_cluster<T>)
+  CINN_B200_REGISTER_KERNEL_PDL("rownorm_cluster_" TNAME, 9, 512, k_rownorm_cluster<T>)
 
 REG_ROWNORM_T("f32", float);
 REG_ROWNORM_T("f16", __half);

@@ -25,6 +25,7 @@ template <typename T, int G, int VPT, bool LAYERNORM>
 __global__ void __launch_bounds__(G)
     k_rownorm_tma(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
                   T* __restrict__ y, long long rows, long long cols, long long stages_ll, double eps_d) {
+  grid_dependency_sync();
   constexpr int V      = Io<T>::kVec;
   constexpr int NWARPS = G / 32;
   extern __shared__ __align__(128) unsigned char ring[];
@@ -186,6 +187,7 @@ __global__ void __launch_bounds__(G)
 // limit, records the give-up in this file's counter exactly as the streaming kernels do, and returns.  It lets a
 // host test check that a wait that runs out surfaces through cinn_b200_device_status without any kernel hanging.
 __global__ void __launch_bounds__(32) k_selftest_bounded_wait(long long polls) {
+  grid_dependency_sync();
   __shared__ __align__(8) uint64_t bar;
   if (threadIdx.x == 0) {
     mbar_init(&bar, 1);
@@ -195,11 +197,11 @@ __global__ void __launch_bounds__(32) k_selftest_bounded_wait(long long polls) {
     if (!done) atomicAdd(&g_rownorm_wait_timeouts, 1u);
   }
 }
-CINN_B200_REGISTER_KERNEL("selftest_bounded_wait", 1, 32, k_selftest_bounded_wait);
+CINN_B200_REGISTER_KERNEL_PDL("selftest_bounded_wait", 1, 32, k_selftest_bounded_wait);
 
 #define REG_TMA_ONE(TNAME, T, G, VPT)                                                               \
-  CINN_B200_REGISTER_KERNEL("softmax_tma_" TNAME "_g" #G "_v" #VPT, 8, G, k_rownorm_tma<T, G, VPT, false>); \
-  CINN_B200_REGISTER_KERNEL("layernorm_tma_" TNAME "_g" #G "_v" #VPT, 8, G, k_rownorm_tma<T, G, VPT, true>)
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_tma_" TNAME "_g" #G "_v" #VPT, 8, G, k_rownorm_tma<T, G, VPT, false>); \
+  CINN_B200_REGISTER_KERNEL_PDL("layernorm_tma_" TNAME "_g" #G "_v" #VPT, 8, G, k_rownorm_tma<T, G, VPT, true>)
 #define REG_TMA_G(TNAME, T, G) \
   REG_TMA_ONE(TNAME, T, G, 1); \
   REG_TMA_ONE(TNAME, T, G, 2); \

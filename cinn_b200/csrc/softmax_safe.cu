@@ -39,6 +39,7 @@ __device__ __forceinline__ float cta_fold(float v, float (*buf)[16], int slot) {
 template <typename T, int VPT, bool SUBMAX = true>
 __global__ void __launch_bounds__(512)
     k_softmax_safe(const T* __restrict__ x, T* __restrict__ y, long long rows, long long cols, long long vec_ok) {
+  grid_dependency_sync();
   constexpr int V = Io<T>::kVec;
   __shared__ __align__(16) float max_buf[2][16], sum_buf[2][16];
   int parity     = 0;
@@ -116,15 +117,15 @@ __global__ void __launch_bounds__(512)
 }  // namespace
 
 #define REG_SAFE(TNAME, T)                                                                      \
-  CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v1", 5, 512, k_softmax_safe<T, 1>);        \
-  CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v2", 5, 512, k_softmax_safe<T, 2>);        \
-  CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v4", 5, 512, k_softmax_safe<T, 4>);        \
-  CINN_B200_REGISTER_KERNEL("softmax_safe_" TNAME "_v8", 5, 512, k_softmax_safe<T, 8>)
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_safe_" TNAME "_v1", 5, 512, k_softmax_safe<T, 1>);        \
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_safe_" TNAME "_v2", 5, 512, k_softmax_safe<T, 2>);        \
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_safe_" TNAME "_v4", 5, 512, k_softmax_safe<T, 4>);        \
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_safe_" TNAME "_v8", 5, 512, k_softmax_safe<T, 8>)
 #define REG_PLAIN(TNAME, T)                                                                        \
-  CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v1", 5, 512, k_softmax_safe<T, 1, false>);   \
-  CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v2", 5, 512, k_softmax_safe<T, 2, false>);   \
-  CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v4", 5, 512, k_softmax_safe<T, 4, false>);   \
-  CINN_B200_REGISTER_KERNEL("softmax_plain_" TNAME "_v8", 5, 512, k_softmax_safe<T, 8, false>)
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_plain_" TNAME "_v1", 5, 512, k_softmax_safe<T, 1, false>);   \
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_plain_" TNAME "_v2", 5, 512, k_softmax_safe<T, 2, false>);   \
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_plain_" TNAME "_v4", 5, 512, k_softmax_safe<T, 4, false>);   \
+  CINN_B200_REGISTER_KERNEL_PDL("softmax_plain_" TNAME "_v8", 5, 512, k_softmax_safe<T, 8, false>)
 REG_PLAIN("f32", float);
 REG_PLAIN("f16", __half);
 REG_PLAIN("bf16", __nv_bfloat16);

@@ -298,7 +298,9 @@ int cinn_b200_col_reduce_sharded_f32_emulated(cinn_b200_peer_ctx* ctx, int kind,
 int cinn_b200_device_status(unsigned int* async_wait_timeouts);
 
 /* Tuning knobs (integers) read by the matcher when a group is compiled; unknown keys give CINN_B200_ENOTFOUND.
- * "sm_count": SM count assumed when no GPU is visible (default 148); "enable_static_chains" (default 1): elementwise
+ * "sm_count": SM count assumed when no GPU is visible (default 148); "enable_pdl" (default 1; read at every launch):
+ * kernels that wait for their predecessor on the device are launched with programmatic stream serialisation, which
+ * hides the launch latency between consecutive kernels of a stream; "enable_static_chains" (default 1): elementwise
  * chains whose program has a kernel specialised at build time use it instead of the interpreting kernel;
  * "enable_ew_stream" (default 1),
  * "ew_stream_stages", "ew_stream_ctas_per_sm": whether large elementwise groups with 16-bit outputs stream their

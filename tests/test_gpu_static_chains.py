@@ -1,0 +1,82 @@
+"""Every chain kernel specialised at build time against the interpreting kernel it replaces: the same group, the
+same inputs, once with the substitution on and once with it off, bit for bit -- both run chain_step(), so any
+difference would be a miscompiled specialisation.  Sizes that leave a ragged tail, and a misaligned case that takes
+the scalar path, are included; a few entries are also checked against the CPU oracle through the usual parity
+helpers elsewhere (abs_add, select, trees, bias + relu with a second output)."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cinn_b200
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+_spec = importlib.util.spec_from_file_location(
+    "gen_static_chains", os.path.join(ROOT, "cinn_b200", "csrc", "gen_static_chains.py"))
+GEN = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(GEN)
+
+TORCH_T = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16, "bool": torch.bool}
+
+
+def _tensors(desc, seed, misalign):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    ins, outs = [], []
+    for line in desc.splitlines():
+        w = line.split()
+        if not w or w[0] not in ("input", "output"):
+            continue
+        shape = tuple(int(d) for d in w[3].split(","))
+        n = int(np.prod(shape))
+        dt = TORCH_T[w[2]]
+        raw = torch.empty(n + misalign, dtype=dt, device="cuda")
+        view = raw[misalign:].view(shape)
+        if w[0] == "input":
+            if dt == torch.bool:
+                view.copy_(torch.rand(shape, device="cuda", generator=gen) > 0.5)
+            else:
+                # positive and negative values, magnitudes around one, a few exact zeros
+                v = torch.randn(shape, device="cuda", generator=gen) * 1.5
+                v[torch.rand(shape, device="cuda", generator=gen) < 0.01] = 0.0
+                view.copy_(v.to(dt))
+            ins.append(view)
+        else:
+            outs.append(view)
+    return ins, outs
+
+
+def _run(desc, name, static, seed, misalign):
+    L = cinn_b200.lib()
+    L.cinn_b200_set_option(b"enable_static_chains", 1 if static else 0)
+    try:
+        g = cinn_b200.FusedGroup(desc.replace("fn_static_", "fn_%s_" % name))
+    finally:
+        L.cinn_b200_set_option(b"enable_static_chains", 1)
+    ins, outs = _tensors(desc, seed, misalign)
+    for o in outs:
+        o.view(torch.uint8).fill_(0x5A)
+    g.run(ins + outs)
+    torch.cuda.synchronize()
+    kernels = g.kernel_names()
+    g.release()
+    return [o.view(torch.uint8).cpu().numpy().copy() for o in outs], kernels
+
+
+@pytest.mark.parametrize("name,desc", GEN.GROUPS, ids=[n for n, _ in GEN.GROUPS])
+@pytest.mark.parametrize("variant", ["table_shape", "ragged", "misaligned"])
+def test_static_kernel_equals_interpreter(name, desc, variant):
+    if variant == "ragged":
+        # 61 x 1028 / 3 x 16 x 9 x 28: vector path plus a tail, a last extent that keeps the addressing modes
+        desc = desc.replace("64,1024", "61,1028").replace(" 1024\n", " 1028\n").replace("8,16,32,32", "3,16,9,28")
+    misalign = 1 if variant == "misaligned" else 0
+    got_s, k_s = _run(desc, "s_" + variant, True, seed=11, misalign=misalign)
+    got_i, k_i = _run(desc, "i_" + variant, False, seed=11, misalign=misalign)
+    assert all(k.startswith("ew_chain_") for k in k_i), k_i
+    if not k_s[0].startswith("ew_static_"):
+        pytest.skip("no specialised kernel for this entry (%s)" % k_s[0])
+    for a, b in zip(got_s, got_i):
+        assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))

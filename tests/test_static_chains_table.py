@@ -1,0 +1,65 @@
+"""The table of chain programs compiled into kernels at build time (cinn_b200/csrc/ew_static_table.inc) is what the
+generator beside it produces from today's matcher, and the library holds one kernel per line (no GPU needed)."""
+import importlib.util
+import os
+import re
+
+import cinn_b200
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GEN = os.path.join(ROOT, "cinn_b200", "csrc", "gen_static_chains.py")
+
+
+def load_generator():
+    spec = importlib.util.spec_from_file_location("gen_static_chains", GEN)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_committed_table_is_up_to_date_and_registered():
+    gen = load_generator()
+    lines, _ = gen.table_lines()
+    text = gen.HEADER + "\n".join(lines) + "\n"
+    committed = open(os.path.join(ROOT, "cinn_b200", "csrc", "ew_static_table.inc")).read()
+    assert committed == text, "run python cinn_b200/csrc/gen_static_chains.py and rebuild the library"
+    L = cinn_b200.lib()
+    assert L.cinn_b200_num_static_chains() == len(lines) >= 40
+    for l in lines:
+        name = "ew_static_" + re.match(r"STATIC_CHAIN\((\w+),", l).group(1)
+        assert L.cinn_b200_get_kernel(name.encode()), name
+
+
+def test_listed_groups_plan_to_their_static_kernel_and_others_to_the_interpreter():
+    gen = load_generator()
+    by_name = dict(gen.GROUPS)
+    g = cinn_b200.FusedGroup(by_name["abs_add_f32"])
+    assert g.kernel_names() == ["ew_static_abs_add_f32"]
+    interpreted_plan = None
+    L = cinn_b200.lib()
+    L.cinn_b200_set_option(b"enable_static_chains", 0)
+    try:
+        g2 = cinn_b200.FusedGroup(by_name["abs_add_f32"].replace("fn_static_abs_add_f32", "fn_interp_abs_add_f32"))
+        assert g2.kernel_names() == ["ew_chain_f32_s1"]
+        interpreted_plan = g2.launch_text()
+        g2.release()
+    finally:
+        L.cinn_b200_set_option(b"enable_static_chains", 1)
+    # same launch shape and the same parameters: only the kernel differs
+    strip = lambda t: re.sub(r"^launch 0 \S+", "launch 0 K", t)  # noqa: E731
+    assert strip(g.launch_text()) == strip(interpreted_plan)
+    g.release()
+    # a different constant is the same program (immediates are parameters) ...
+    d = by_name["scale_relu_f32"].replace("scale=2.0 bias=1.0", "scale=-0.75 bias=3.5").replace("fn_static", "fn_other")
+    g = cinn_b200.FusedGroup(d)
+    assert g.kernel_names() == ["ew_static_scale_relu_f32"]
+    g.release()
+    # ... another shape with the same addressing modes too, but another op sequence is not
+    d = by_name["abs_add_f32"].replace("64,1024", "7,12,20").replace("fn_static", "fn_shape")
+    g = cinn_b200.FusedGroup(d)
+    assert g.kernel_names() == ["ew_static_abs_add_f32"]
+    g.release()
+    d = by_name["abs_add_f32"].replace("op abs t1 = t0", "op ceil t1 = t0").replace("fn_static", "fn_ceil")
+    g = cinn_b200.FusedGroup(d)
+    assert g.kernel_names() == ["ew_chain_f32_s1"]
+    g.release()
