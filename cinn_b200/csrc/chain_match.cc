@@ -1013,7 +1013,9 @@ std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const Device
   chain.outputs[0].name  = t;
   chain.outputs[0].dtype = DType::kFloat32;
   chain.outputs[0].shape = shape;
-  auto plan = MatchChainOfClass(chain, dev, kFloatChain, &w);
+  DeviceInfo interp = dev;
+  interp.enable_static_chains = 0;  // the plan is re-targeted below; the reductions have their own static table
+  auto plan = MatchChainOfClass(chain, interp, kFloatChain, &w);
   if (!plan) {
     if (why) *why = "the reduce's operand is not an elementwise chain: " + w;
     return nullptr;
@@ -1053,6 +1055,15 @@ std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const Device
   st.args[kAligned].aligned_outputs.clear();
   const char* opname = kind->second == 0 ? "sum" : (kind->second == 1 ? "prod" : (kind->second == 2 ? "max" : "min"));
   auto scratch_arg = [&](int64_t off) { ArgSpec a; a.kind = ArgSpec::kScratch; a.ivalue = off; return a; };
+  // The kernel specialised at build time for this program and reduce op, when the library has one.
+  auto specialised = [&](const KernelEntry* base) {
+    if (!dev.enable_static_chains || !base) return base;
+    const int nsteps = (int)st.args[14].ivalue;
+    uint32_t sig[EW_MAX_STEPS] = {0};
+    for (int k = 0; k < nsteps && k < EW_MAX_STEPS; ++k) sig[k] = (uint32_t)(st.args[15 + k].ivalue & 0xffffffff);
+    const KernelEntry* fixed = FindStaticChain(base->name, st.args[kMeta].ivalue, nsteps, sig);
+    return fixed ? fixed : base;
+  };
   ArgSpec out_arg;
   out_arg.kind  = ArgSpec::kOutput;
   out_arg.index = 0;
@@ -1061,7 +1072,7 @@ std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const Device
     if (f32 && outer < (int64_t)sms * 2 && r >= 65536)
       while (S < 1024 && r % (S * 2) == 0 && (r / (S * 2)) % 4 == 0 && r / (S * 2) >= 4096 && outer * S < (int64_t)sms * 8) S *= 2;
     const int64_t rows = outer * S, len = r / S;
-    st.kernel = FindKernel("chain_reduce_row" + ns);
+    st.kernel = specialised(FindKernel("chain_reduce_row" + ns));
     if (!st.kernel) return nullptr;
     const int64_t group = len > 2048 ? 256 : 32;
     st.block[0] = 256;
@@ -1092,7 +1103,7 @@ std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const Device
       while (gx * outer * S < (int64_t)sms * 4 && r / (S * 2) >= 16 && S < 64) S *= 2;
     const int64_t rows_per_split = CeilDiv(r, S);
     S                            = CeilDiv(r, rows_per_split);
-    st.kernel = FindKernel("chain_reduce_col" + ns);
+    st.kernel = specialised(FindKernel("chain_reduce_col" + ns));
     if (!st.kernel) return nullptr;
     if (outer > 65535) {
       if (why) *why = "more than 65535 outer slices in a column reduction";

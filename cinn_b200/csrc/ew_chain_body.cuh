@@ -113,6 +113,9 @@ struct DynProgram {
   long long meta;
   __device__ __forceinline__ int in_type() const { return (int)((meta >> 24) & 15); }
   __device__ __forceinline__ int out2_type() const { return (int)((meta >> 36) & 15); }
+  // the reductions with a chain as operand (chain_reduce.cu): reduce op and storage type of the result
+  __device__ __forceinline__ int reduce_op() const { return (int)((meta >> 28) & 3); }
+  __device__ __forceinline__ int result_type() const { return (int)((meta >> 32) & 15); }
   __device__ __forceinline__ int side_dtype(int k) const { return (int)((meta >> (8 * (k - 1))) & 15); }
   __device__ __forceinline__ int side_mode(int k) const { return (int)((meta >> (8 * (k - 1) + 4)) & 15); }
   template <int VEC, int NS, int NT, bool ST2>
@@ -129,6 +132,8 @@ struct StaticProgram {
   const long long* steps;
   __device__ __forceinline__ constexpr int in_type() const { return (int)((META >> 24) & 15); }
   __device__ __forceinline__ constexpr int out2_type() const { return (int)((META >> 36) & 15); }
+  __device__ __forceinline__ constexpr int reduce_op() const { return (int)((META >> 28) & 3); }
+  __device__ __forceinline__ constexpr int result_type() const { return (int)((META >> 32) & 15); }
   __device__ __forceinline__ constexpr int side_dtype(int k) const { return (int)((META >> (8 * (k - 1))) & 15); }
   __device__ __forceinline__ constexpr int side_mode(int k) const { return (int)((META >> (8 * (k - 1) + 4)) & 15); }
   template <int VEC, int NS, int NT, bool ST2>

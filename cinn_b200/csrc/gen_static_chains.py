@@ -138,6 +138,38 @@ GROUPS.append(("bias_pre_and_relu_f32",
                "op elementwise_add pre = X bias ; axis=-1\nop relu act = pre\n"
                "output pre float32 %s\noutput act float32 %s\n" % (FULL, ROWVEC, FULL, FULL)))
 
+
+
+def reduce_group(name, inputs, ops, red, operand, axis, shape=FULL):
+    """reduce_<red>(chain) over one axis of a 2-D shape: rows (axis 1) or columns (axis 0)."""
+    dims = [int(d) for d in shape.split(",")]
+    out_shape = ",".join(str(d) for i, d in enumerate(dims) if i != axis)
+    lines = ["group fn_static_" + name] + ["input %s" % i for i in inputs] + ["op %s" % o for o in ops]
+    lines.append("op reduce_%s y = %s ; dim=%d keep_dim=false" % (red, operand, axis))
+    lines.append("output y float32 " + out_shape)
+    return name, "\n".join(lines) + "\n"
+
+
+REDUCE_GROUPS = []
+for axis, tag in ((1, "rows"), (0, "cols")):
+    two = ["x float32 " + FULL, "y0 float32 " + FULL]
+    REDUCE_GROUPS.append(reduce_group("sum_abs_diff_" + tag, two, ["subtract d = x y0 ; axis=-1", "abs a = d"], "sum",
+                                      "a", axis))
+    REDUCE_GROUPS.append(reduce_group("sum_sq_diff_" + tag, two, ["subtract d = x y0 ; axis=-1", "identity di = d",
+                                                                   "elementwise_mul a = d di ; axis=-1"], "sum", "a",
+                                      axis))
+    REDUCE_GROUPS.append(reduce_group("sum_mul_" + tag, two, ["elementwise_mul a = x y0 ; axis=-1"], "sum", "a", axis))
+    REDUCE_GROUPS.append(reduce_group("max_abs_diff_" + tag, two, ["subtract d = x y0 ; axis=-1", "abs a = d"], "max",
+                                      "a", axis))
+    REDUCE_GROUPS.append(reduce_group("sum_sigmoid_affine_" + tag, ["x float32 " + FULL, "b float32 " + ROWVEC],
+                                      ["elementwise_add t = x b ; axis=-1", "elementwise_mul u = t b ; axis=-1",
+                                       "sigmoid a = u"], "sum", "a", axis))
+    REDUCE_GROUPS.append(reduce_group("sum_log_" + tag, ["x float32 " + FULL], ["log a = x"], "sum", "a", axis))
+    REDUCE_GROUPS.append(reduce_group("sum_relu_bias_" + tag, ["x float32 " + FULL, "b float32 " + ROWVEC],
+                                      ["elementwise_add t = x b ; axis=-1", "relu a = t"], "sum", "a", axis))
+    REDUCE_GROUPS.append(reduce_group("max_scale_" + tag, ["x float32 " + FULL],
+                                      ["scale a = x ; scale=0.5 bias=1.0 bias_after_scale=true"], "max", "a", axis))
+
 VARIANT = {"_s0": (0, 0, "false"), "_s1": (1, 0, "false"), "_s3": (3, 0, "false"), "_s3t": (3, 2, "true"),
            "_s1o": (1, 0, "true"), "_s3o": (3, 0, "true")}
 OUT_T = {"f32": "float", "f16": "__half", "bf16": "__nv_bfloat16", "bool": "uint8_t", "i32": "int32_t",
@@ -153,26 +185,28 @@ def plan_of(desc):
     finally:
         g.release()
     launches = [l for l in text.splitlines() if l.startswith("launch ")]
-    if len(launches) != 1:
-        return None
     kernel = launches[0].split()[2]
-    if not re.match(r"ew_chain_(f32|f16|bf16|bool|i32|i64)_s", kernel):
+    if not re.match(r"(ew_chain_(f32|f16|bf16|bool|i32|i64)|chain_reduce_(row|col))_s", kernel):
+        return None
+    if kernel.startswith("ew_chain_") and len(launches) != 1:
         return None
     args = {}
     for l in text.splitlines():
         w = l.split()
+        if w[0] == "launch" and w[1] != "0":
+            break  # a second launch folds partials; the program lives in the first
         if w[0] == "arg" and w[2] == "int":
             args[int(w[1])] = int(w[3])
     return kernel, args
 
 
-def table_lines():
+def table_lines(groups=None, reduce_table=False):
     import cinn_b200
     L = cinn_b200.lib()
     cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
     try:
         seen, lines, skipped = {}, [], []
-        for name, desc in GROUPS:
+        for name, desc in (GROUPS if groups is None else groups):
             try:
                 got = plan_of(desc)
             except cinn_b200.CinnB200Error as e:
@@ -182,9 +216,19 @@ def table_lines():
                 skipped.append("%s: not a single interpreted float chain" % name)
                 continue
             kernel, args = got
-            m = re.match(r"ew_chain_(\w+?)(_s\w+)$", kernel)
-            out_t, (ns, nt, st2) = OUT_T[m.group(1)], VARIANT[m.group(2)]
             meta, nsteps = args[7], args[14]
+            if reduce_table:
+                m = re.match(r"chain_reduce_(row|col)(_s\w+)$", kernel)
+                if not m:
+                    skipped.append("%s: not a chain reduction (%s)" % (name, kernel))
+                    continue
+                ns, nt, _ = VARIANT[m.group(2)]
+            else:
+                m = re.match(r"ew_chain_(\w+?)(_s\w+)$", kernel)
+                if not m:
+                    skipped.append("%s: not an elementwise chain (%s)" % (name, kernel))
+                    continue
+                out_t, (ns, nt, st2) = OUT_T[m.group(1)], VARIANT[m.group(2)]
             sig = [args[15 + k] & 0xffffffff for k in range(nsteps)]
             if nsteps == 0:
                 skipped.append("%s: empty program" % name)
@@ -194,8 +238,13 @@ def table_lines():
                 skipped.append("%s: same program as %s" % (name, seen[key]))
                 continue
             seen[key] = name
-            lines.append('STATIC_CHAIN(%s, "%s", %s, %d, %d, %s, %d, %s);' % (
-                name, kernel, out_t, ns, nt, st2, meta, ", ".join("0x%08xu" % s for s in sig)))
+            sigs = ", ".join("0x%08xu" % s for s in sig)
+            if reduce_table:
+                lines.append('STATIC_CHAIN_REDUCE_%s(%s, "%s", %d, %d, %d, %s);' % (
+                    m.group(1).upper(), name, kernel, ns, nt, meta, sigs))
+            else:
+                lines.append('STATIC_CHAIN(%s, "%s", %s, %d, %d, %s, %d, %s);' % (
+                    name, kernel, out_t, ns, nt, st2, meta, sigs))
         return lines, skipped
     finally:
         L.cinn_b200_set_option(b"enable_static_chains", 1)
@@ -205,20 +254,33 @@ HEADER = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_CHAIN(id
           "// inputs, temporaries, second output, meta word, low halves of the step words...).\n")
 
 
-def main():
+REDUCE_HEADER = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_CHAIN_REDUCE_ROW / _COL(id, interpreted\n"
+                 "// kernel, side inputs, temporaries, meta word (with the reduce op and result type), step words...).\n")
+
+
+def tables():
+    """[(file name, text, skipped notes)] of both generated tables."""
     lines, skipped = table_lines()
-    text = HEADER + "\n".join(lines) + "\n"
-    path = os.path.join(HERE, "ew_static_table.inc")
-    if "--check" in sys.argv:
-        ok = open(path).read() == text
-        print("ew_static_table.inc is %s" % ("up to date" if ok else "OUT OF DATE"))
-        return 0 if ok else 1
-    with open(path, "w") as f:
-        f.write(text)
-    print("%d static chains written" % len(lines))
-    for s in skipped:
-        print("skipped", s)
-    return 0
+    rlines, rskipped = table_lines(REDUCE_GROUPS, reduce_table=True)
+    return [("ew_static_table.inc", HEADER + "\n".join(lines) + "\n", skipped, len(lines)),
+            ("chain_reduce_static_table.inc", REDUCE_HEADER + "\n".join(rlines) + "\n", rskipped, len(rlines))]
+
+
+def main():
+    rc = 0
+    for fname, text, skipped, count in tables():
+        path = os.path.join(HERE, fname)
+        if "--check" in sys.argv:
+            ok = open(path).read() == text
+            print("%s is %s" % (fname, "up to date" if ok else "OUT OF DATE"))
+            rc = rc or (0 if ok else 1)
+            continue
+        with open(path, "w") as f:
+            f.write(text)
+        print("%s: %d kernels" % (fname, count))
+        for s in skipped:
+            print("  skipped", s)
+    return rc
 
 
 if __name__ == "__main__":

@@ -80,3 +80,30 @@ def test_static_kernel_equals_interpreter(name, desc, variant):
         pytest.skip("no specialised kernel for this entry (%s)" % k_s[0])
     for a, b in zip(got_s, got_i):
         assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))
+
+
+@pytest.mark.parametrize("name,desc", GEN.REDUCE_GROUPS, ids=[n for n, _ in GEN.REDUCE_GROUPS])
+@pytest.mark.parametrize("shape", ["64,1024", "61,1028", "4,65536", "4096,8"])
+def test_static_chain_reduction_equals_interpreter(name, desc, shape):
+    """The reductions with a chain as operand: the specialised kernel folds the same values in the same order."""
+    rows, cols = (int(d) for d in shape.split(","))
+    axis = 1 if name.endswith("_rows") else 0
+    out = str(rows if axis == 1 else cols)
+    lines = []
+    for l in desc.splitlines():
+        w = l.split()
+        if w[0] in ("input", "output") and w[3] == "64,1024":
+            l = " ".join(w[:3] + [shape])
+        elif w[0] == "input" and w[3] == "1024":
+            l = " ".join(w[:3] + [str(cols)])
+        elif w[0] == "output":
+            l = " ".join(w[:3] + [out])
+        lines.append(l)
+    desc = "\n".join(lines) + "\n"
+    got_s, k_s = _run(desc, "rs", True, seed=5, misalign=0)
+    got_i, k_i = _run(desc, "ri", False, seed=5, misalign=0)
+    assert k_i[0].startswith("chain_reduce_"), k_i
+    if not k_s[0].startswith("chain_reduce_static_"):
+        pytest.skip("no specialised kernel at this shape (%s)" % k_s[0])
+    for a, b in zip(got_s, got_i):
+        assert np.array_equal(a, b), (name, shape, k_s, int((a != b).sum()))

@@ -19,15 +19,16 @@ def load_generator():
 
 def test_committed_table_is_up_to_date_and_registered():
     gen = load_generator()
-    lines, _ = gen.table_lines()
-    text = gen.HEADER + "\n".join(lines) + "\n"
-    committed = open(os.path.join(ROOT, "cinn_b200", "csrc", "ew_static_table.inc")).read()
-    assert committed == text, "run python cinn_b200/csrc/gen_static_chains.py and rebuild the library"
     L = cinn_b200.lib()
-    assert L.cinn_b200_num_static_chains() == len(lines) >= 40
-    for l in lines:
-        name = "ew_static_" + re.match(r"STATIC_CHAIN\((\w+),", l).group(1)
-        assert L.cinn_b200_get_kernel(name.encode()), name
+    total = 0
+    for fname, text, _, count in gen.tables():
+        committed = open(os.path.join(ROOT, "cinn_b200", "csrc", fname)).read()
+        assert committed == text, "run python cinn_b200/csrc/gen_static_chains.py and rebuild the library"
+        total += count
+        for m in re.finditer(r"^STATIC_CHAIN(_REDUCE_ROW|_REDUCE_COL)?\((\w+),", text, flags=re.M):
+            name = ("chain_reduce_static_" if m.group(1) else "ew_static_") + m.group(2)
+            assert L.cinn_b200_get_kernel(name.encode()), name
+    assert L.cinn_b200_num_static_chains() == total >= 60
 
 
 def test_listed_groups_plan_to_their_static_kernel_and_others_to_the_interpreter():
@@ -62,4 +63,9 @@ def test_listed_groups_plan_to_their_static_kernel_and_others_to_the_interpreter
     d = by_name["abs_add_f32"].replace("op abs t1 = t0", "op ceil t1 = t0").replace("fn_static", "fn_ceil")
     g = cinn_b200.FusedGroup(d)
     assert g.kernel_names() == ["ew_chain_f32_s1"]
+    g.release()
+    # a reduction whose operand is a listed chain: its own specialised kernel, at any size
+    red = dict(gen.REDUCE_GROUPS)
+    g = cinn_b200.FusedGroup(red["sum_abs_diff_rows"].replace("64,1024", "8192,8192").replace("float32 64\n", "float32 8192\n"))
+    assert g.kernel_names()[0] == "chain_reduce_static_sum_abs_diff_rows", g.kernel_names()
     g.release()
