@@ -86,8 +86,9 @@ def _worker(rank, world, port, out_dir):
                         graph.replay()
                     torch.cuda.synchronize()
                     np.save(os.path.join(out_dir, "fused_graph_rank%d.npy" % rank), o.cpu().numpy())
+                assert fused.status() == 0
                 dist.barrier()
-                fused.close()
+                fused.close()  # unmaps the peers' buffers on every rank before any rank frees its own
         n = ctypes.c_uint(0)
         assert cinn_b200.lib().cinn_b200_device_status(ctypes.byref(n)) == 0 and n.value == 0, n.value
         dist.barrier()
