@@ -42,6 +42,19 @@ enum EwOp {
   EW_BNOT, EW_CLZ, EW_POPC  // integer chains only
 };
 
+// ---- register programs (ew_dag.cu) --------------------------------------------------------------------------------
+// An elementwise group that is not a chain (a value used twice, several outputs, more operands) runs as a register
+// program: up to DAG_MAX_IN inputs, DAG_MAX_OUT outputs of one shape, DAG_REGS vector registers.  A step word holds
+// bits 0-7 the op (an EwOp, or DAG_LOAD / DAG_STORE), 8-11 the destination register (DAG_STORE: the output index),
+// 12-16 / 17-21 / 22-26 operands A / B / C (0-7 a register, DAG_IMM the word's immediate, DAG_IMM2 the immediate of the
+// NEXT word, which is then skipped; DAG_LOAD: A is the input index), bits 32-63 an fp32 immediate.
+// Unary ops: dst = op(A).  Binary ops: dst = A op B.  EW_FMA: dst = fma(A, B, C).  EW_SELECT: dst = A != 0 ? B : C.
+// EW_SCALE_PRE: dst = imm * (A + imm2).  The kernel's meta word packs, per input k, bits 6k..6k+2 the storage type
+// and 6k+3..6k+5 the addressing mode, and per output j bits 48+3j..50+3j the storage type.
+constexpr int DAG_MAX_IN = 8, DAG_MAX_OUT = 4, DAG_MAX_STEPS = 30, DAG_REGS = 8;
+constexpr int DAG_LOAD = 200, DAG_STORE = 201;
+constexpr int DAG_IMM = 8, DAG_IMM2 = 9;
+
 // Storage types of the chain kernel's operands (runtime codes; the output type is a template parameter).
 // EW_NO_INPUT as the type of the chain input: there is none, the program starts with EW_COPY.
 enum EwDType { EW_NO_INPUT = 15, EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5, EW_F64 = 6 };

@@ -418,6 +418,9 @@ struct FusionState {
   std::vector<int> producer_of_var;                // variable -> instruction (-1 for inputs)
   std::vector<std::vector<int>> consumers_of_var;  // variable -> instructions
   std::set<int> fetch;
+  // Instructions that are evaluated again inside every group that reads their result (cheap elementwise producers
+  // with several consumers): their result is not a group output and is never materialised.
+  std::set<int> recomputed;
   int uid;
 
   FusionState(const NetBuilder& b_, const DeviceInfo& d, int uid_) : b(b_), dev(d), uid(uid_) {
@@ -471,7 +474,7 @@ struct FusionState {
       int v          = b.instrs()[i].output;
       bool external  = fetch.count(v) > 0;
       for (int c : consumers_of_var[v])
-        if (!all.count(c)) external = true;
+        if (!all.count(c) && !recomputed.count(i)) external = true;
       if (external) {
         g.output_vars.push_back(v);
         TensorDesc t;
@@ -891,6 +894,68 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
         break;  // a group has two outputs at most
       }
     }
+  }
+
+  // Step 5: recomputation.  A small elementwise group whose result several other groups read (bias + bias feeding
+  // two sums of different shapes, x + y feeding a row and a column reduction) is evaluated again inside each of
+  // them instead of being written to memory and read back, when every reader has a kernel for the enlarged group:
+  // the reference's merge pass fuses such a producer into all of its consumers the same way
+  // (cinn/hlir/pass/fusion_merge_pass.cc:605-700, vertical fusion with recompute).  Only producers that read nothing
+  // but program inputs and constants are moved, so no ordering between groups changes.
+  for (size_t si = 0; si < sets.size(); ++si) {
+    const std::set<int>& S = sets[si];
+    if (S.empty() || S.size() > 4) continue;
+    bool movable = true;
+    for (int i : S) {
+      const OpPattern pat = PatternOf(b.instrs()[i].op_type);
+      movable = movable && pat != OpPattern::kReduction && pat != OpPattern::kNonFusible && b.instrs()[i].op_type != "reshape";
+      for (int v : b.instrs()[i].inputs) {
+        const int pv = st.producer_of_var[v];
+        movable      = movable && (pv < 0 || st.IsConst(pv) || S.count(pv));
+      }
+    }
+    if (!movable) continue;
+    const FusedGroupInfo gs = st.Describe(S);
+    if (gs.output_vars.size() != 1 || st.fetch.count(gs.output_vars[0])) continue;
+    const int v = gs.output_vars[0];
+    int64_t v_numel = 1;
+    for (auto d : b.vars()[v].shape) v_numel *= d;
+    std::set<int> readers;
+    bool ok = true;
+    for (int c : st.consumers_of_var[v]) {
+      if (S.count(c)) continue;
+      if (group_of[c] < 0 || sets[group_of[c]].empty()) ok = false;
+      else readers.insert(group_of[c]);
+    }
+    if (!ok || readers.size() < 2) continue;
+    // tentatively: the producer's instructions count as present in every reader
+    for (int i : S) st.recomputed.insert(i);
+    std::vector<std::set<int>> enlarged;
+    for (int r : readers) {
+      std::set<int> trial = sets[r];
+      trial.insert(S.begin(), S.end());
+      FusedGroupInfo info;
+      bool fits = st.Compiles(trial, &info, nullptr);
+      // never recompute a larger tensor than the reader produces
+      for (int ov : info.output_vars) {
+        int64_t n_out = 1;
+        for (auto d : b.vars()[ov].shape) n_out *= d;
+        fits = fits && (v_numel <= n_out || PatternOf(b.instrs()[st.producer_of_var[ov]].op_type) == OpPattern::kReduction);
+      }
+      if (!fits) {
+        ok = false;
+        break;
+      }
+      enlarged.push_back(trial);
+    }
+    if (!ok) {
+      for (int i : S) st.recomputed.erase(i);
+      continue;
+    }
+    size_t k = 0;
+    for (int r : readers) sets[r] = enlarged[k++];
+    for (int i : S) group_of[i] = -3;  // lives in several groups
+    sets[si].clear();
   }
 
   // Emit in a topological order of the groups (a group after the groups that produce its inputs), ties by program

@@ -170,6 +170,48 @@ for axis, tag in ((1, "rows"), (0, "cols")):
     REDUCE_GROUPS.append(reduce_group("max_scale_" + tag, ["x float32 " + FULL],
                                       ["scale a = x ; scale=0.5 bias=1.0 bias_after_scale=true"], "max", "a", axis))
 
+def multi(name, inputs, ops, outputs, shape=FULL, dt="float32"):
+    lines = ["group fn_static_" + name] + ["input %s" % i for i in inputs] + ["op %s" % o for o in ops]
+    lines += ["output %s %s %s" % (o, dt, shape) for o in outputs]
+    return name, "\n".join(lines) + "\n"
+
+
+def _f(names, shape=FULL):
+    return ["%s float32 %s" % (n, shape) for n in names]
+
+
+# Elementwise groups that are not chains (register programs, ew_dag.cu): a value used several times, several outputs.
+DAG_GROUPS = [
+    # a shared sum feeding two, three and four consumers (the shapes of the reference's merge-pass tests)
+    multi("shared_sum_2out", _f("ABCD"), ["elementwise_add e = A B ; axis=-1", "elementwise_add f = e C ; axis=-1",
+                                          "elementwise_add g = e D ; axis=-1"], ["f", "g"]),
+    multi("shared_sum_joined", _f("ABCD"), ["elementwise_add e = A B ; axis=-1", "elementwise_add f = e C ; axis=-1",
+                                            "elementwise_add g = e D ; axis=-1", "elementwise_add h = f g ; axis=-1"],
+          ["h"]),
+    multi("two_sums_3out", _f("ABCDEF"), ["elementwise_add g = A B ; axis=-1", "elementwise_add h = C D ; axis=-1",
+                                          "elementwise_add i = E g ; axis=-1", "elementwise_add j = g h ; axis=-1",
+                                          "elementwise_add k = h F ; axis=-1"], ["i", "j", "k"]),
+    multi("shared_sum_4out", _f("ABCDEF"), ["elementwise_add g = A B ; axis=-1", "elementwise_add h = g C ; axis=-1",
+                                            "elementwise_add i = g D ; axis=-1", "elementwise_add j = g E ; axis=-1",
+                                            "elementwise_add k = g F ; axis=-1"], ["h", "i", "j", "k"]),
+    # bias vectors summed first, then broadcast into two full-size sums
+    multi("bias_sum_2out", _f("AB", ROWVEC) + _f("CD"), ["elementwise_add e = A B ; axis=-1",
+                                                        "elementwise_add f = C e ; axis=-1",
+                                                        "elementwise_add g = D e ; axis=-1"], ["f", "g"]),
+    # what training graphs keep: the pre-activation, the activation and its mask
+    multi("bias_relu_mask_3out", ["x float32 " + FULL, "b float32 " + ROWVEC],
+          ["elementwise_add pre = x b ; axis=-1", "relu act = pre",
+           "fill_constant z = ; shape=%s value=0.0 dtype=float32" % FULL, "greater_than m = pre z ; axis=-1",
+           "cast mf = m ; dtype=float32"], ["pre", "act", "mf"]),
+    # swish and its derivative factor from one read of x
+    multi("swish_and_sigmoid", ["x float32 " + FULL], ["sigmoid s = x", "elementwise_mul y = x s ; axis=-1"], ["s", "y"]),
+    # momentum update: two states from one gradient
+    multi("momentum_update", _f("WGV"), ["scale v1 = V ; scale=0.9 bias=0.0 bias_after_scale=true",
+                                         "elementwise_add v2 = v1 G ; axis=-1",
+                                         "scale st = v2 ; scale=-0.01 bias=0.0 bias_after_scale=true",
+                                         "elementwise_add w2 = W st ; axis=-1"], ["v2", "w2"]),
+]
+
 VARIANT = {"_s0": (0, 0, "false"), "_s1": (1, 0, "false"), "_s3": (3, 0, "false"), "_s3t": (3, 2, "true"),
            "_s1o": (1, 0, "true"), "_s3o": (3, 0, "true")}
 OUT_T = {"f32": "float", "f16": "__half", "bf16": "__nv_bfloat16", "bool": "uint8_t", "i32": "int32_t",
@@ -198,6 +240,37 @@ def plan_of(desc):
         if w[0] == "arg" and w[2] == "int":
             args[int(w[1])] = int(w[3])
     return kernel, args
+
+
+def dag_table_lines():
+    import cinn_b200
+    L = cinn_b200.lib()
+    cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
+    try:
+        seen, lines, skipped = {}, [], []
+        for name, desc in DAG_GROUPS:
+            try:
+                g = cinn_b200.FusedGroup(desc)
+            except cinn_b200.CinnB200Error as e:
+                skipped.append("%s: %s" % (name, e))
+                continue
+            text = g.launch_text()
+            g.release()
+            launches = [l for l in text.splitlines() if l.startswith("launch ")]
+            if len(launches) != 1 or launches[0].split()[2] != "ew_dag":
+                skipped.append("%s: not a register program (%s)" % (name, launches[0].split()[2]))
+                continue
+            args = {int(l.split()[1]): int(l.split()[3]) for l in text.splitlines() if l.startswith("arg ") and l.split()[2] == "int"}
+            meta, nsteps = args[14], args[31]
+            sig = tuple(args[32 + k] & 0xffffffff for k in range(nsteps))
+            if (meta, sig) in seen:
+                skipped.append("%s: same program as %s" % (name, seen[(meta, sig)]))
+                continue
+            seen[(meta, sig)] = name
+            lines.append("STATIC_DAG(%s, %d, %s);" % (name, meta, ", ".join("0x%08xu" % w for w in sig)))
+        return lines, skipped
+    finally:
+        L.cinn_b200_set_option(b"enable_static_chains", 1)
 
 
 def table_lines(groups=None, reduce_table=False):
@@ -262,8 +335,11 @@ def tables():
     """[(file name, text, skipped notes)] of both generated tables."""
     lines, skipped = table_lines()
     rlines, rskipped = table_lines(REDUCE_GROUPS, reduce_table=True)
+    dlines, dskipped = dag_table_lines()
+    dag_header = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_DAG(id, meta word, step words...).\n")
     return [("ew_static_table.inc", HEADER + "\n".join(lines) + "\n", skipped, len(lines)),
-            ("chain_reduce_static_table.inc", REDUCE_HEADER + "\n".join(rlines) + "\n", rskipped, len(rlines))]
+            ("chain_reduce_static_table.inc", REDUCE_HEADER + "\n".join(rlines) + "\n", rskipped, len(rlines)),
+            ("ew_dag_static_table.inc", dag_header + "\n".join(dlines) + "\n", dskipped, len(dlines))]
 
 
 def main():

@@ -19,6 +19,7 @@ namespace cinn_b200 {
 
 std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const DeviceInfo& dev, std::string* why);  // chain_match.cc
 std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const DeviceInfo& dev, std::string* why);   // chain_match.cc
+std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& dev, std::string* why);           // chain_match.cc
 
 namespace {
 
@@ -1410,8 +1411,12 @@ struct Matcher {
       std::string why2;
       if (g.outputs.size() == 2)
         if (auto p = MatchGenericChain(g, dev, &why2)) return p;
+      // Any other elementwise group with up to four outputs of one shape: a register program.
+      std::string why3;
+      if (auto p = MatchDag(g, dev, &why3)) return p;
       Fail("groups with " + std::to_string(g.outputs.size()) + " outputs have no prebuilt kernel (" + expr +
-           (why2.empty() ? std::string(")") : "; as a chain with a second output: " + why2 + ")"));
+           (why2.empty() ? std::string("") : "; as a chain with a second output: " + why2) +
+           "; as a register program: " + why3 + ")");
       return nullptr;
     }
     typedef std::unique_ptr<CompiledGroup> (Matcher::*Fn)(const std::string&);
@@ -1435,7 +1440,11 @@ struct Matcher {
     // Last resort for elementwise / broadcast groups: a linear chain run by the generic kernel.
     std::string why;
     if (auto p = MatchGenericChain(g, dev, &why)) return p;
-    Fail("no prebuilt sm_100a kernel matches expression " + expr + " (as an elementwise chain: " + why + ")");
+    // An elementwise group that is not a chain (a value used twice, more operands): a register program.
+    std::string why_dag;
+    if (auto p = MatchDag(g, dev, &why_dag)) return p;
+    Fail("no prebuilt sm_100a kernel matches expression " + expr + " (as an elementwise chain: " + why +
+         "; as a register program: " + why_dag + ")");
     return nullptr;
   }
 };

@@ -76,7 +76,7 @@ def op_reduce_0(b):  # :143-166
     return [b.add(e, b.reduce_sum(f, [0]))]
 
 
-@case(1)
+@case(1, 3, "two column reductions of different tensors plus their elementwise consumers: reductions of different inputs are not merged horizontally and the epilogue is a kernel of its own")
 def op_reduce_1(b):  # :168-192
     v = inputs(b, A=(W,), B=(W,), C=(H, W), D=(H, W))
     e = b.add(v["A"], v["B"])
@@ -84,20 +84,20 @@ def op_reduce_1(b):  # :168-192
     return [b.add(g, b.add(e, f))]
 
 
-@case(2)
+@case(2, 3, "the two reductions run over different axes and each keeps its elementwise consumer outside: an epilogue after a reduce is a kernel of its own here")
 def op_reduce_2(b):  # :194-218
     v = inputs(b, A=(W,), B=(W,), C=(H, W), D=(H, W))
     e, f = b.reduce_sum(v["C"], [0]), b.reduce_sum(v["D"], [1])
     return [b.add(b.add(v["A"], e), b.add(v["B"], f))]
 
 
-@case(1)
+@case(1, 3, "concat is a data-movement kernel of its own (copy_rows), not an operand of the elementwise kernels")
 def op_injective_0(b):  # :220-243
     v = inputs(b, A=(H, W), B=(H, W), C=(H, W), D=(2 * H, W))
     return [b.add(v["D"], b.concat([v["C"], b.add(v["A"], v["B"])], 0))]
 
 
-@case(1)
+@case(1, 2, "transpose is a tiled data-movement kernel of its own; expand_dims / broadcast_to fold into the add")
 def op_injective_1(b):  # :245-262
     v = inputs(b, A=(1, 19), B=(1, 19, 204))
     d = b.broadcast_to(b.expand_dims(v["A"], [1]), [1, 204, 19], [0, 1, 2])
@@ -196,7 +196,7 @@ def merge_broadcast_5(b):  # :309-334
     return [b.add(v["C"], f), b.add(v["D"], f), b.add(v["E"], f)]
 
 
-@case(4)
+@case(4, 3, "fewer: the shared sum is recomputed inside each of the three reductions instead of being written once (the reference leaves its final count for this case commented out)")
 def merge_reduce_0(b):  # :336-358 (final count commented out in the reference: the OpFusionPass count stands)
     v = inputs(b, A=(H, W), B=(H, W))
     c = b.add(v["A"], v["B"])
@@ -210,28 +210,28 @@ def merge_reduce_1(b):  # :360-381
     return [b.reduce_sum(c, [0]), b.reduce_sum(c, [1])]
 
 
-@case(2)
+@case(2, 3, "the shared sum is recomputed inside both reductions (as in the reference), but the two elementwise consumers of the reduced vectors run as one more, two-output kernel instead of inside the reduction kernels")
 def merge_reduce_2(b):  # :383-407
     v = inputs(b, A=(H, W), B=(H, W), C=(W,))
     d = b.add(v["A"], v["B"])
     return [b.add(v["C"], b.reduce_sum(d, [0])), b.add(v["C"], b.reduce_sum(d, [1]))]
 
 
-@case(4)
+@case(4, 3, "fewer: the sum runs inside the reduction kernel")
 def merge_reduce_3(b):  # :409-433 (final count commented out in the reference)
     v = inputs(b, A=(H, W), B=(H, W), C=(W,), D=(H, W))
     f = b.reduce_sum(b.add(v["A"], v["B"]), [0])
     return [b.add(v["C"], f), b.add(v["D"], f)]
 
 
-@case(5)
+@case(5, 3, "fewer: the sum runs inside the reduction kernel and the two identical consumers share a two-output kernel")
 def merge_reduce_4(b):  # :435-460 (final count commented out in the reference)
     v = inputs(b, A=(H, W), B=(H, W), C=(W,), D=(H, W))
     f = b.reduce_sum(b.add(v["A"], v["B"]), [0])
     return [b.add(v["C"], f), b.add(v["D"], f), b.add(v["D"], f)]
 
 
-@case(1)
+@case(1, 3, "row reductions of three different tensors are three launches: horizontal fusion here is for reductions that read the same tensor")
 def merge_reduce_5(b):  # :462-485
     v = inputs(b, A=(128, 128), B=(128, 128))
     c = b.add(v["A"], v["B"])
