@@ -339,9 +339,16 @@ def test_expression_trees_compile_into_one_kernel_with_temporaries():
     D = [b.create_input(common.Float(64), (64, 1024), n) for n in "ABCD"]
     b.multiply(b.add(D[0], D[1]), b.subtract(D[2], D[3]))
     assert [p for _, p in plan(b).groups()] == ["ew_chain ew_chain_f64_f64_s3t"]
-    # three joins need three temporaries: split
+    # three joins need three temporaries: no chain any more, but still one kernel, as a register program
     b, (A, B, C, D) = build()
     b.add(b.multiply(b.exp(A), b.tanh(B)), b.multiply(b.sqrt(b.abs(C)), b.sigmoid(D)))
+    assert [p for _, p in plan(b).groups()] == ["ew_dag ew_dag"]
+    # what no elementwise kernel takes is still split: nine tensors read at once
+    b = NetBuilder("wide")
+    xs = [b.create_input(common.Float(32), (64, 1024), "X%d" % i) for i in range(9)]
+    acc = xs[0]
+    for x in xs[1:]:
+        acc = b.add(acc, x)
     assert len(plan(b).groups()) > 1
 
 
