@@ -55,6 +55,21 @@ constexpr int DAG_MAX_IN = 8, DAG_MAX_OUT = 4, DAG_MAX_STEPS = 30, DAG_REGS = 8;
 constexpr int DAG_LOAD = 200, DAG_STORE = 201;
 constexpr int DAG_IMM = 8, DAG_IMM2 = 9;
 
+// ---- row programs (row_prog.cu) ------------------------------------------------------------------------------------
+// A group with reductions over the trailing axes and elementwise ops either side of them runs as a row program over
+// x viewed as [rows, r]: up to ROWP_MAX_PASSES passes over a row, each an element program (register-program steps
+// run on every vector of the row, with ROWP_ACC steps that fold a register into a row accumulator) followed, after
+// the accumulators have been combined across the row's threads, by a scalar program run once per row on the row's
+// ROWP_SREGS scalar registers.  Step words are those of the register programs with three additions: operand selectors
+// 16-23 name scalar register 0-7 (its value for every element); ROWP_ACC: scalar register `dst` receives the fold,
+// by reduce kind C (0 sum, 1 prod, 2 max, 3 min), of register A over the row; in a scalar program the registers ARE
+// the scalar registers, DAG_LOAD reads an input at the row index and DAG_STORE writes a per-row output.
+// counts word: bits 8p..8p+7 = element steps of pass p, bits 32+8p.. = scalar steps of pass p (steps are laid out
+// pass by pass, element program then scalar program).
+constexpr int ROWP_MAX_PASSES = 3, ROWP_MAX_STEPS = 36, ROWP_SREGS = 8, ROWP_MAX_ACC = 4;
+constexpr int ROWP_ACC = 202;
+constexpr int ROWP_SREG0 = 16;
+
 // Storage types of the chain kernel's operands (runtime codes; the output type is a template parameter).
 // EW_NO_INPUT as the type of the chain input: there is none, the program starts with EW_COPY.
 enum EwDType { EW_NO_INPUT = 15, EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5, EW_F64 = 6 };

@@ -301,6 +301,10 @@ int PlanLaunch(cinn_b200_peer_ctx* c, int kind, long long rows_local, long long 
   long long gath = gather ? std::min<long long>(tiles * (c->world - 1), std::max<long long>(1, std::min<long long>(c->sms, cap / 4))) : 0;
   long long red  = std::min<long long>(tiles * c->world, cap - comb - gath);
   if (red < 1) return SetLastError(CINN_B200_ECUDA, "col_reduce_sharded: the GPU cannot hold one CTA per role");
+  // Every reducer gets the same number of items (1024 items on 316 CTAs would leave most of them idle during the
+  // fourth round; 256 CTAs with four items each finish together).
+  const long long rounds = (tiles * c->world + red - 1) / red;
+  red                    = (tiles * c->world + rounds - 1) / rounds;
   *fn_out = fn;
   *n_red  = (int)red;
   *n_comb = (int)comb;

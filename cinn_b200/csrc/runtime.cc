@@ -152,13 +152,14 @@ DeviceInfo CurrentDeviceInfo() {
 }
 
 // ---- launch primitive -------------------------------------------------------------------------------
+constexpr int kMaxKernelParams = 80;  // the row-program kernels take 70
 static int LaunchEntry(const KernelEntry* entry, void* v_args, int num_args, int gx, int gy, int gz, int bx, int by,
                        int bz, unsigned cluster_x, size_t dyn_smem, void* stream);
 
 // The public launch primitive: resolves the handle in the kernel table, then launches.
 static int LaunchKernel(const void* kernel_fn, void* v_args, int num_args, int gx, int gy, int gz, int bx, int by,
                         int bz, unsigned cluster_x, size_t dyn_smem, void* stream) {
-  if (!kernel_fn || (!v_args && num_args > 0) || num_args < 0 || num_args > 64)
+  if (!kernel_fn || (!v_args && num_args > 0) || num_args < 0 || num_args > kMaxKernelParams)
     return SetError(CINN_B200_EINVAL, "cinn_call_cuda_kernel: bad kernel handle or argument array (num_args=%d)",
                     num_args);
   const KernelEntry* entry = FindKernelByFn(kernel_fn);
@@ -177,7 +178,7 @@ static int LaunchEntry(const KernelEntry* entry, void* v_args, int num_args, int
     return SetError(CINN_B200_EINVAL, "kernel %s: bad launch shape grid=(%d,%d,%d) block=(%d,%d,%d), max %d threads",
                     entry->name, gx, gy, gz, bx, by, bz, entry->max_threads);
   // cuda_util.cc:94-104: a buffer passes the address of its `memory` field, anything else its payload address.
-  void* params[64];
+  void* params[kMaxKernelParams];
   cinn_pod_value_t* args = static_cast<cinn_pod_value_t*>(v_args);
   for (int i = 0; i < num_args; ++i) {
     if (args[i].type_code_ == CINN_POD_BUFFERP) {
@@ -371,7 +372,7 @@ static int RunPlan(const CompiledGroup& plan, GroupSlot& slot, const std::vector
     if (!ok) steps = &plan.steps_unaligned;
   }
   for (const LaunchStep& s : *steps) {
-    cinn_pod_value_t pods[64];
+    cinn_pod_value_t pods[kMaxKernelParams];
     cinn_buffer_t scratch_bufs[8];
     int n_scratch = 0;
     const int n   = (int)s.args.size();
