@@ -12,6 +12,7 @@
 #include <cstring>
 #include <functional>
 #include <map>
+#include <set>
 #include <sstream>
 
 #include "ew_chain.h"
@@ -135,6 +136,7 @@ struct ChainBuilder {
   // values of ONE integer type (`compute`) and bool in registers of that type.
   bool int_class = false;
   bool dbl_class = false;  // float64 values and bool in double registers; immediates through a table of doubles
+  bool allow_reduce = false;  // Infer() also accepts reduce ops (the row programs)
   DType compute  = DType::kFloat32;
   std::vector<double> dimms;
 
@@ -225,6 +227,27 @@ struct ChainBuilder {
         v = values[op.inputs[1]];
         for (int k = 0; k < 3; ++k)
           if (values[op.inputs[k]].numel() > v.numel()) v.shape = values[op.inputs[k]].shape;
+      } else if (allow_reduce && op.type.rfind("reduce_", 0) == 0 && op.inputs.size() == 1) {
+        // cinn/hlir/op/reduction.cc:49-158: `dim` (empty: all axes), `keep_dim`
+        const Value& x = values[op.inputs[0]];
+        std::vector<int64_t> dims = IntList(Attr(op, "dim", ""));
+        const int nd = (int)x.shape.size();
+        if (dims.empty())
+          for (int i = 0; i < nd; ++i) dims.push_back(i);
+        std::vector<bool> red(nd, false);
+        for (auto d : dims) {
+          if (d < 0) d += nd;
+          if (d < 0 || d >= nd) return Fail("reduce dim out of range");
+          red[d] = true;
+        }
+        const std::string keep = Attr(op, "keep_dim", "false");
+        const bool keep_dim    = keep == "true" || keep == "1" || keep == "True";
+        v.dtype = x.dtype;
+        for (int i = 0; i < nd; ++i) {
+          if (!red[i]) v.shape.push_back(x.shape[i]);
+          else if (keep_dim) v.shape.push_back(1);
+        }
+        if (v.shape.empty()) v.shape.push_back(1);
       } else {
         return Fail("op '" + op.type + "' is not an elementwise op");
       }
@@ -1167,9 +1190,11 @@ std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const Devic
 
 }  // namespace cinn_b200
 
-// ---- register programs: elementwise groups that are not chains ------------------------------------------------------
-// (ew_dag.cu).  Every value of the group is evaluated at the flat index of the (common) output shape; the group's ops
-// are taken in their topological order, each live value holds one of DAG_REGS registers until its last use.
+// ---- register programs ------------------------------------------------------------------------------------------------
+// Elementwise groups that are not chains (ew_dag.cu) and groups with reductions over the trailing axes (row_prog.cu)
+// are compiled into register programs: the ops are taken in their topological order and each live value holds one of
+// DAG_REGS registers until its last use.  RegProgramBuilder emits one program segment at a time: the whole program of
+// an elementwise group, or one element / scalar program of a row program.
 namespace cinn_b200 {
 namespace {
 
@@ -1180,66 +1205,344 @@ uint64_t DagWord(int op, int dst, int a, int b, int c, float imm) {
          ((uint64_t)(c & 31) << 22) | ((uint64_t)bits << 32);
 }
 
-struct DagOperand {
+struct RegOperand {
   enum Kind { kReg, kImm } kind = kReg;
-  int reg   = -1;
+  int sel   = -1;  // register 0-7, or ROWP_SREG0 + k for a row scalar seen from an element program
   float imm = 0.0f;
 };
 
-}  // namespace
+// What happens to a value once its op has been emitted.
+struct ValueAction {
+  enum Kind { kNone, kStore, kAccumulate } kind = kNone;
+  int index = 0;      // kStore: output index; kAccumulate: scalar register that receives the row's total
+  int fold  = 0;      // kAccumulate: 0 sum, 1 prod, 2 max, 3 min
+};
 
-std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& dev, std::string* why) {
-  ChainBuilder cb(g, why);
-  if (g.outputs.empty() || g.outputs.size() > (size_t)DAG_MAX_OUT) {
-    cb.Fail("a register program has one to four outputs");
-    return nullptr;
-  }
-  if (g.inputs.size() > (size_t)DAG_MAX_IN) {
-    cb.Fail("a register program reads at most eight tensors");
-    return nullptr;
-  }
-  if (!cb.Infer()) return nullptr;
-  cb.out_shape = g.outputs[0].shape;
-  cb.n         = g.outputs[0].numel();
-  std::map<std::string, int> output_index;
-  for (size_t k = 0; k < g.outputs.size(); ++k) {
-    if (g.outputs[k].shape != cb.out_shape) {
-      cb.Fail("the outputs of a register program have one shape");
-      return nullptr;
-    }
-    if (!cb.values.count(g.outputs[k].name) || cb.values[g.outputs[k].name].dtype != g.outputs[k].dtype ||
-        cb.values[g.outputs[k].name].shape != cb.out_shape) {
-      cb.Fail("output '" + g.outputs[k].name + "' does not have the type and shape the ops give it");
-      return nullptr;
-    }
-    output_index[g.outputs[k].name] = (int)k;
-  }
-  auto storable = [](DType t) { return IsFloatType(t) || t == DType::kBool; };
-  for (auto& kv : cb.values)
-    if (!storable(kv.second.dtype)) {
-      cb.Fail(std::string("value of type ") + DTypeName(kv.second.dtype) + " in a float register program");
-      return nullptr;
-    }
+struct RegProgramBuilder {
+  ChainBuilder& cb;
+  const GroupDesc& g;
+  // Set by the caller -------------------------------------------------------------------------------------------
+  std::map<std::string, std::string> alias;           // value -> the value it merely renames (no-op ops)
+  std::map<std::string, int> uses;                    // uses of every value inside the whole group
+  std::set<std::string> group_outputs;
+  // Addressing of group input k in the index space of the segment being emitted (fills *side), false if impossible.
+  std::function<bool(const std::string&, int, Side*)> address_input;
+  // Selector of a value that lives outside the segment's register file (a row scalar seen from an element program),
+  // or -1.
+  std::function<int(const std::string&)> outside_selector = [](const std::string&) { return -1; };
+  // State ---------------------------------------------------------------------------------------------------------
+  std::vector<uint64_t> words;
+  std::vector<bool> reg_busy = std::vector<bool>(DAG_REGS, false);
+  std::map<std::string, int> reg_of;     // root value -> register
+  std::map<std::string, int> remaining;  // root value -> uses still to come in this segment
+  std::vector<Side> in_side;
+  std::vector<bool> in_used;
+  bool failed = false;
 
-  // ---- which output axis every dimension of every value sits on (walked from the outputs back) ----
-  std::map<std::string, std::vector<int64_t>> axes;
+  RegProgramBuilder(ChainBuilder& c) : cb(c), g(c.g), in_side(c.g.inputs.size()), in_used(c.g.inputs.size(), false) {}
+
+  void Fail(const std::string& m) {
+    if (!failed) cb.Fail(m);
+    failed = true;
+  }
+  std::string Root(const std::string& v) const {
+    auto it = alias.find(v);
+    return it == alias.end() ? v : Root(it->second);
+  }
+  bool ExactCast(const OpDesc& op) const {
+    const DType from = cb.values.at(op.inputs[0]).dtype, to = cb.values.at(op.output).dtype;
+    if (from == to) return true;
+    if (to == DType::kFloat32) return from == DType::kFloat16 || from == DType::kBFloat16 || from == DType::kBool;
+    if (from == DType::kBool) return IsFloatType(to);  // 0 / 1 are exact in every float type
+    return false;
+  }
+  // Values that are only another value seen through a no-op (broadcast_to, identity, exact casts) are aliases, unless
+  // they are group outputs (those need a register of their own to be stored from).
+  void FindAliases(const std::function<bool(const OpDesc&)>& live) {
+    for (auto& op : g.ops) {
+      if (!live(op)) continue;
+      const bool noop = op.type == "broadcast_to" || op.type == "identity" || (op.type == "cast" && ExactCast(op));
+      if (noop && !group_outputs.count(op.output)) alias[op.output] = op.inputs[0];
+    }
+  }
+  int Alloc() {
+    for (int r = 0; r < DAG_REGS; ++r)
+      if (!reg_busy[r]) {
+        reg_busy[r] = true;
+        return r;
+      }
+    Fail("more than eight values are live at once");
+    return -1;
+  }
+  bool ConstantOf(const std::string& v, float* imm) const {
+    const std::string r = Root(v);
+    auto p = cb.producer.find(r);
+    if (p == cb.producer.end() || p->second->type != "fill_constant") return false;
+    *imm = (float)atof(ChainBuilder::Attr(*p->second, "value", "0").c_str());
+    return true;
+  }
+  // The register, outside selector or immediate holding `v`; a group input is loaded on its first use.
+  RegOperand Operand(const std::string& v) {
+    RegOperand o;
+    if (ConstantOf(v, &o.imm)) {
+      o.kind = RegOperand::kImm;
+      return o;
+    }
+    const std::string r = Root(v);
+    const int outside   = outside_selector(r);
+    if (outside >= 0) {
+      o.sel = outside;
+      return o;
+    }
+    auto it = reg_of.find(r);
+    if (it != reg_of.end()) {
+      o.sel = it->second;
+      return o;
+    }
+    auto in = cb.input_index.find(r);
+    if (in == cb.input_index.end()) {
+      Fail("value '" + v + "' is used before it is computed");
+      return o;
+    }
+    const int k = in->second;
+    Side side;
+    if (!address_input(r, k, &side)) {
+      Fail("input '" + r + "' cannot be addressed from the index this part of the group runs over");
+      return o;
+    }
+    if (in_used[k] && !(in_side[k] == side)) {
+      Fail("input '" + r + "' is read at two different alignments");
+      return o;
+    }
+    in_side[k] = side;
+    in_used[k] = true;
+    const int reg = Alloc();
+    if (reg < 0) return o;
+    words.push_back(DagWord(DAG_LOAD, reg, k, 0, 0, 0.0f));
+    reg_of[r] = reg;
+    o.sel     = reg;
+    return o;
+  }
+  // One use of `v` has been emitted: its register is free after the last one.
+  void Release(const std::string& v) {
+    const std::string r = Root(v);
+    auto it = remaining.find(r);
+    if (it == remaining.end()) return;
+    if (--it->second <= 0) {
+      auto rg = reg_of.find(r);
+      if (rg != reg_of.end()) {
+        reg_busy[rg->second] = false;
+        reg_of.erase(rg);
+      }
+    }
+  }
+  // A Mul whose single consumer, a float32 Add, absorbs it as a fused multiply-add (cinn/optim/lower_intrin.cc:41-59).
+  const OpDesc* ContractibleMul(const std::string& v, const std::set<std::string>& never) const {
+    if (alias.count(v) || never.count(v)) return nullptr;  // the reference contracts the Mul node itself
+    auto p = cb.producer.find(v);
+    if (p == cb.producer.end() || p->second->type != "elementwise_mul") return nullptr;
+    auto u = uses.find(v);
+    if (u == uses.end() || u->second != 1 || group_outputs.count(v) || cb.values.at(v).dtype != DType::kFloat32) return nullptr;
+    return p->second;
+  }
+
+  int Emit(int opc, const std::string& out, const std::vector<RegOperand>& ops, float imm_for_op, bool has_op_imm) {
+    // immediates: at most two per step (the word's own and the next word's)
+    float imms[2] = {0.0f, 0.0f};
+    int n_imm     = 0;
+    if (has_op_imm) imms[n_imm++] = imm_for_op;
+    int sel[3] = {0, 0, 0};
+    for (size_t i = 0; i < ops.size(); ++i) {
+      if (ops[i].kind == RegOperand::kReg) {
+        sel[i] = ops[i].sel;
+        continue;
+      }
+      int found = -1;
+      for (int q = has_op_imm ? 1 : 0; q < n_imm; ++q)
+        if (memcmp(&imms[q], &ops[i].imm, 4) == 0) found = q;
+      if (found < 0) {
+        if (n_imm >= 2) {
+          Fail("an op needs more than two constants");
+          return -1;
+        }
+        imms[n_imm] = ops[i].imm;
+        found       = n_imm++;
+      }
+      sel[i] = found == 0 ? DAG_IMM : DAG_IMM2;
+    }
+    const int dst = Alloc();
+    if (dst < 0) return -1;
+    words.push_back(DagWord(opc, dst, sel[0], sel[1], sel[2], imms[0]));
+    if (n_imm == 2 || opc == EW_SCALE_PRE) words.push_back(DagWord(EW_NOP, 0, 0, 0, 0, imms[1]));
+    reg_of[out] = dst;
+    return dst;
+  }
+
+  // Emits `ops` (a topologically ordered subset of the group's ops, all of one index space).  `actions` says which
+  // values are stored or accumulated once computed; `extra_uses` are uses of values outside this segment that must
+  // keep their registers (scalar programs: values a later pass reads).  Values in `keep_mul` are never contracted
+  // (they are reduce operands: materialised in the reference).
+  bool EmitSegment(const std::vector<const OpDesc*>& ops, const std::map<std::string, ValueAction>& actions,
+                   const std::map<std::string, int>& extra_uses, const std::set<std::string>& keep_mul) {
+    std::set<const OpDesc*> in_segment(ops.begin(), ops.end());
+    for (const OpDesc* op : ops) {
+      if (alias.count(op->output)) continue;
+      for (auto& in : op->inputs) ++remaining[Root(in)];
+    }
+    for (auto& kv : actions) ++remaining[Root(kv.first)];
+    for (auto& kv : extra_uses) remaining[Root(kv.first)] += kv.second;
+    std::map<const OpDesc*, const OpDesc*> absorbed_by;  // mul -> add
+    for (const OpDesc* op : ops) {
+      if (op->type != "elementwise_add" || cb.values.at(op->output).dtype != DType::kFloat32) continue;
+      for (int k : {1, 0}) {  // the right operand is tried first
+        const OpDesc* m = ContractibleMul(op->inputs[k], keep_mul);
+        if (m && in_segment.count(m)) {
+          absorbed_by[m] = op;
+          break;
+        }
+      }
+    }
+    for (const OpDesc* opp : ops) {
+      const OpDesc& op = *opp;
+      if (failed) return false;
+      if (op.type == "fill_constant" || alias.count(op.output) || absorbed_by.count(opp)) continue;
+      const DType out_t = cb.values.at(op.output).dtype;
+      int dst = -1;
+      const OpDesc* mul = nullptr;
+      int mul_side      = -1;
+      if (op.type == "elementwise_add" && out_t == DType::kFloat32)
+        for (int k : {1, 0}) {
+          const OpDesc* m = ContractibleMul(op.inputs[k], keep_mul);
+          if (m && absorbed_by.count(m) && absorbed_by[m] == opp) {
+            mul      = m;
+            mul_side = k;
+            break;
+          }
+        }
+      if (mul) {
+        std::vector<RegOperand> o = {Operand(mul->inputs[0]), Operand(mul->inputs[1]), Operand(op.inputs[1 - mul_side])};
+        if (failed) return false;
+        Release(mul->inputs[0]);
+        Release(mul->inputs[1]);
+        Release(op.inputs[1 - mul_side]);
+        // the absorbed Mul's own result was counted as a use of the Add: it never gets a register
+        remaining.erase(Root(op.inputs[mul_side]));
+        dst = Emit(EW_FMA, op.output, o, 0.0f, false);
+      } else if (op.type == "scale") {
+        const float sc = (float)atof(ChainBuilder::Attr(op, "scale", "1").c_str());
+        const float bi = (float)atof(ChainBuilder::Attr(op, "bias", "0").c_str());
+        const std::string after = ChainBuilder::Attr(op, "bias_after_scale", "true");
+        RegOperand x = Operand(op.inputs[0]);
+        if (failed) return false;
+        if (x.kind != RegOperand::kReg) {
+          Fail("scale of a constant");
+          return false;
+        }
+        Release(op.inputs[0]);
+        if (after == "true" || after == "1" || after == "True") {
+          RegOperand s2, b2;
+          s2.kind = b2.kind = RegOperand::kImm;
+          s2.imm  = sc;
+          b2.imm  = bi;
+          dst = Emit(EW_FMA, op.output, {x, s2, b2}, 0.0f, false);  // fma(x, scale, bias)
+        } else {
+          dst = Alloc();
+          if (dst < 0) return false;
+          words.push_back(DagWord(EW_SCALE_PRE, dst, x.sel, 0, 0, sc));  // scale * (x + bias)
+          words.push_back(DagWord(EW_NOP, 0, 0, 0, 0, bi));
+          reg_of[op.output] = dst;
+        }
+      } else if (op.type == "cast") {
+        RegOperand x = Operand(op.inputs[0]);
+        if (failed) return false;
+        Release(op.inputs[0]);
+        const int code = out_t == DType::kBool ? EW_TO_BOOL
+                                               : (out_t == DType::kFloat16 ? EW_ROUND_F16
+                                                                           : (out_t == DType::kBFloat16 ? EW_ROUND_BF16 : EW_IDENTITY));
+        dst = Emit(code, op.output, {x}, 0.0f, false);
+      } else if (op.type == "identity" || op.type == "broadcast_to") {  // a no-op that is a group output: a copy
+        RegOperand x = Operand(op.inputs[0]);
+        if (failed) return false;
+        Release(op.inputs[0]);
+        dst = Emit(EW_IDENTITY, op.output, {x}, 0.0f, false);
+      } else if (op.type == "select") {
+        std::vector<RegOperand> o = {Operand(op.inputs[0]), Operand(op.inputs[1]), Operand(op.inputs[2])};
+        if (failed) return false;
+        for (auto& in : op.inputs) Release(in);
+        dst = Emit(EW_SELECT, op.output, o, 0.0f, false);
+      } else if (UnaryCodes().count(op.type)) {
+        RegOperand x = Operand(op.inputs[0]);
+        if (failed) return false;
+        Release(op.inputs[0]);
+        if (op.type == "relu6")
+          dst = Emit(EW_RELU6, op.output, {x}, (float)atof(ChainBuilder::Attr(op, "threshold", "6").c_str()), true);
+        else
+          dst = Emit(UnaryCodes().at(op.type), op.output, {x}, 0.0f, false);
+      } else if (BinaryCodes().count(op.type)) {
+        std::vector<RegOperand> o = {Operand(op.inputs[0]), Operand(op.inputs[1])};
+        if (failed) return false;
+        Release(op.inputs[0]);
+        Release(op.inputs[1]);
+        dst = Emit(BinaryCodes().at(op.type), op.output, o, 0.0f, false);
+      } else {
+        Fail("op '" + op.type + "' is not an elementwise op");
+        return false;
+      }
+      if (failed || dst < 0) return false;
+      // 16-bit values are rounded to their type after every op (a cast to that type IS the rounding)
+      if (op.type != "cast" && (out_t == DType::kFloat16 || out_t == DType::kBFloat16))
+        words.push_back(DagWord(out_t == DType::kFloat16 ? EW_ROUND_F16 : EW_ROUND_BF16, dst, dst, 0, 0, 0.0f));
+      auto act = actions.find(op.output);
+      if (act != actions.end()) {
+        if (act->second.kind == ValueAction::kStore) words.push_back(DagWord(DAG_STORE, act->second.index, dst, 0, 0, 0.0f));
+        if (act->second.kind == ValueAction::kAccumulate)
+          words.push_back(DagWord(ROWP_ACC, act->second.index, dst, 0, act->second.fold, 0.0f));
+        Release(op.output);
+      }
+      if (remaining.count(op.output) == 0 || remaining[op.output] <= 0) {  // nothing else reads it
+        auto rg = reg_of.find(op.output);
+        if (rg != reg_of.end()) {
+          reg_busy[rg->second] = false;
+          reg_of.erase(rg);
+        }
+      }
+    }
+    // targets that are not computed by an op of this segment: a group input (or a value held elsewhere) taken as is
+    for (auto& kv : actions) {
+      const std::string r = Root(kv.first);
+      auto p = cb.producer.find(kv.first);
+      const bool computed_here = p != cb.producer.end() && in_segment.count(p->second) && !alias.count(kv.first);
+      if (computed_here) continue;
+      RegOperand x = Operand(kv.first);
+      if (failed) return false;
+      if (x.kind != RegOperand::kReg || x.sel >= DAG_REGS) {
+        Fail("value '" + kv.first + "' cannot be stored or reduced as it is");
+        return false;
+      }
+      if (kv.second.kind == ValueAction::kStore) words.push_back(DagWord(DAG_STORE, kv.second.index, x.sel, 0, 0, 0.0f));
+      if (kv.second.kind == ValueAction::kAccumulate) words.push_back(DagWord(ROWP_ACC, kv.second.index, x.sel, 0, kv.second.fold, 0.0f));
+      Release(kv.first);
+      (void)r;
+    }
+    return !failed;
+  }
+};
+
+// Which output axis every dimension of every value sits on, walked back from `seeds` (value -> axes) through the ops
+// `take` accepts.  Returns false (with the reason set) on an impossible or contradictory placement.
+bool PlaceAxes(ChainBuilder& cb, const std::function<bool(const OpDesc&)>& take,
+               std::map<std::string, std::vector<int64_t>>* axes) {
   bool conflict = false;
   auto place    = [&](const std::string& name, const std::vector<int64_t>& ax) {
-    auto it = axes.find(name);
-    if (it == axes.end()) axes[name] = ax;
+    auto it = axes->find(name);
+    if (it == axes->end()) (*axes)[name] = ax;
     else if (it->second != ax) conflict = true;
   };
-  for (auto& o : g.outputs) {
-    std::vector<int64_t> id;
-    for (size_t i = 0; i < cb.out_shape.size(); ++i) id.push_back((int64_t)i);
-    place(o.name, id);
-  }
-  for (auto it = g.ops.rbegin(); it != g.ops.rend(); ++it) {
+  for (auto it = cb.g.ops.rbegin(); it != cb.g.ops.rend(); ++it) {
     const OpDesc& op = *it;
-    if (!axes.count(op.output)) continue;  // nothing uses it
-    const std::vector<int64_t> oa = axes[op.output];
+    if (!axes->count(op.output) || !take(op) || op.type == "fill_constant") continue;
+    const std::vector<int64_t> oa = (*axes)[op.output];
     const Value& ov               = cb.values[op.output];
-    if (op.type == "fill_constant") continue;
     if (op.type == "broadcast_to") {
       const Value& sv = cb.values[op.inputs[0]];
       std::vector<int64_t> bax = IntList(ChainBuilder::Attr(op, "broadcast_axes", ""));
@@ -1249,10 +1552,7 @@ std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& de
       }
       std::vector<int64_t> ax;
       for (auto d : bax) {
-        if (d < 0 || d >= (int64_t)oa.size()) {
-          cb.Fail("broadcast_axes out of range");
-          return nullptr;
-        }
+        if (d < 0 || d >= (int64_t)oa.size()) return cb.Fail("broadcast_axes out of range");
         ax.push_back(oa[d]);
       }
       place(op.inputs[0], ax);
@@ -1268,302 +1568,115 @@ std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& de
         const int64_t off = axis < 0 ? (int64_t)ov.shape.size() - (int64_t)sv.shape.size() : axis;
         std::vector<int64_t> ax;
         for (size_t i = 0; i < sv.shape.size(); ++i) {
-          if (off + (int64_t)i >= (int64_t)oa.size()) {
-            cb.Fail("operand of '" + op.type + "' does not fit at axis " + std::to_string(axis));
-            return nullptr;
-          }
+          if (off + (int64_t)i >= (int64_t)oa.size()) return cb.Fail("operand of '" + op.type + "' does not fit at axis " + std::to_string(axis));
           ax.push_back(oa[off + i]);
         }
         place(in, ax);
       } else {
-        cb.Fail("operand of '" + op.type + "' has a higher rank than its result");
-        return nullptr;
+        return cb.Fail("operand of '" + op.type + "' has a higher rank than its result");
       }
     }
   }
-  if (conflict) {
-    cb.Fail("a value is used at two different alignments");
+  if (conflict) return cb.Fail("a value is used at two different alignments");
+  return true;
+}
+
+bool StorableInFloatRegisters(ChainBuilder& cb) {
+  for (auto& kv : cb.values)
+    if (!IsFloatType(kv.second.dtype) && kv.second.dtype != DType::kBool)
+      return cb.Fail(std::string("value of type ") + DTypeName(kv.second.dtype) + " in a float register program");
+  return true;
+}
+
+ArgSpec IntArg(int64_t v) {
+  ArgSpec a;
+  a.kind   = ArgSpec::kInt;
+  a.ivalue = v;
+  return a;
+}
+
+// The pointer parameters (eight inputs, four outputs; unused slots repeat the first) and the meta word shared by the
+// register-program kernels; `aligned` collects the buffers the vector path needs 16-byte aligned.
+int64_t PushPointerArgs(const GroupDesc& g, const std::vector<Side>& in_side, LaunchStep* st, ArgSpec* aligned) {
+  int64_t meta = 0;
+  for (int k = 0; k < DAG_MAX_IN; ++k) {
+    ArgSpec a;
+    a.kind  = ArgSpec::kInput;
+    a.index = k < (int)g.inputs.size() ? k : 0;
+    st->args.push_back(a);
+    if (k < (int)g.inputs.size()) {
+      meta |= (int64_t)(DTypeKernelCode(g.inputs[k].dtype) | (in_side[k].mode << 3)) << (6 * k);
+      if (in_side[k].mode == EW_SIDE_FULL || in_side[k].mode == EW_SIDE_PERIODIC_VEC) aligned->aligned_inputs.push_back(k);
+    }
+  }
+  for (int k = 0; k < DAG_MAX_OUT; ++k) {
+    ArgSpec a;
+    a.kind  = ArgSpec::kOutput;
+    a.index = k < (int)g.outputs.size() ? k : 0;
+    st->args.push_back(a);
+    if (k < (int)g.outputs.size()) meta |= (int64_t)DTypeKernelCode(g.outputs[k].dtype) << (48 + 3 * k);
+  }
+  return meta;
+}
+
+}  // namespace
+
+std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& dev, std::string* why) {
+  ChainBuilder cb(g, why);
+  if (g.outputs.empty() || g.outputs.size() > (size_t)DAG_MAX_OUT) {
+    cb.Fail("a register program has one to four outputs");
     return nullptr;
   }
-
-  // ---- use counts, aliases ----
-  std::map<std::string, int> uses;  // uses inside the group
-  for (auto& op : g.ops)
-    if (axes.count(op.output))
-      for (auto& in : op.inputs) ++uses[in];
-  // A value that is only another value seen through a no-op: broadcast_to, identity, exact widening casts.
-  std::map<std::string, std::string> alias;
-  std::function<std::string(const std::string&)> root = [&](const std::string& v) {
-    auto it = alias.find(v);
-    return it == alias.end() ? v : root(it->second);
-  };
-  auto is_exact_cast = [&](const OpDesc& op) {
-    const DType from = cb.values[op.inputs[0]].dtype, to = cb.values[op.output].dtype;
-    if (from == to) return true;
-    if (to == DType::kFloat32) return from == DType::kFloat16 || from == DType::kBFloat16 || from == DType::kBool;
-    if (from == DType::kBool) return IsFloatType(to);  // 0 / 1 are exact in every float type
-    return false;
-  };
-
-  // ---- emission ----
-  std::vector<uint64_t> words;
-  std::map<std::string, int> reg_of;       // root value -> register
-  std::map<std::string, int> remaining;    // root value -> uses not yet emitted (group outputs count once more)
-  std::vector<bool> reg_busy(DAG_REGS, false);
-  std::vector<Side> in_side(g.inputs.size());
-  std::vector<bool> in_used(g.inputs.size(), false);
-  auto alloc = [&]() {
-    for (int r = 0; r < DAG_REGS; ++r)
-      if (!reg_busy[r]) {
-        reg_busy[r] = true;
-        return r;
-      }
-    return -1;
-  };
-  auto constant_of = [&](const std::string& v, float* imm) {
-    const std::string r = root(v);
-    auto p = cb.producer.find(r);
-    if (p == cb.producer.end() || p->second->type != "fill_constant") return false;
-    *imm = (float)atof(ChainBuilder::Attr(*p->second, "value", "0").c_str());
-    return true;
-  };
-  bool failed = false;
-  auto fail   = [&](const std::string& m) {
-    if (!failed) cb.Fail(m);
-    failed = true;
-  };
-  // The register (or immediate) holding `v`; loads a group input on its first use.
-  auto operand = [&](const std::string& v) {
-    DagOperand o;
-    if (constant_of(v, &o.imm)) {
-      o.kind = DagOperand::kImm;
-      return o;
-    }
-    const std::string r = root(v);
-    auto it = reg_of.find(r);
-    if (it != reg_of.end()) {
-      o.reg = it->second;
-      return o;
-    }
-    auto in = cb.input_index.find(r);
-    if (in == cb.input_index.end()) {
-      fail("value '" + v + "' is used before it is computed");
-      return o;
-    }
-    const int k = in->second;
-    if (!in_used[k]) {
-      auto ax = axes.find(r);
-      if (ax == axes.end() || !cb.SideSpec(cb.values[r].shape, ax->second, k, &in_side[k])) {
-        fail("input '" + r + "' cannot be addressed from the output's index");
-        return o;
-      }
-      in_used[k] = true;
-    }
-    const int reg = alloc();
-    if (reg < 0) {
-      fail("more than eight values are live at once");
-      return o;
-    }
-    words.push_back(DagWord(DAG_LOAD, reg, k, 0, 0, 0.0f));
-    reg_of[r] = reg;
-    o.reg     = reg;
-    return o;
-  };
-  // One use of `v` has been emitted: free its register after the last one.
-  auto release = [&](const std::string& v) {
-    const std::string r = root(v);
-    auto it = remaining.find(r);
-    if (it == remaining.end()) return;
-    if (--it->second <= 0) {
-      auto rg = reg_of.find(r);
-      if (rg != reg_of.end()) {
-        reg_busy[rg->second] = false;
-        reg_of.erase(rg);
-      }
-    }
-  };
-  // uses per ROOT value (aliases forward their uses), group outputs once more for their store
-  for (auto& op : g.ops) {
-    if (!axes.count(op.output)) continue;
-    const bool noop = op.type == "broadcast_to" || op.type == "identity" || (op.type == "cast" && is_exact_cast(op));
-    if (noop && !output_index.count(op.output)) alias[op.output] = op.inputs[0];
+  if (g.inputs.size() > (size_t)DAG_MAX_IN) {
+    cb.Fail("a register program reads at most eight tensors");
+    return nullptr;
   }
-  for (auto& op : g.ops) {
-    if (!axes.count(op.output) || alias.count(op.output)) continue;
-    for (auto& in : op.inputs) ++remaining[root(in)];
-  }
-  for (auto& o : g.outputs) ++remaining[root(o.name)];
-
-  // Mul ops that their single consumer, a float32 Add, absorbs as a fused multiply-add
-  // (cinn/optim/lower_intrin.cc:41-59; the right operand is tried first).
-  auto contractible_mul = [&](const std::string& v) -> const OpDesc* {
-    if (alias.count(v)) return nullptr;  // the reference contracts the Mul node itself, not a copy of it
-    auto p = cb.producer.find(v);
-    if (p == cb.producer.end() || p->second->type != "elementwise_mul") return nullptr;
-    if (uses[v] != 1 || output_index.count(v) || cb.values[v].dtype != DType::kFloat32) return nullptr;
-    return p->second;
-  };
-  std::map<const OpDesc*, const OpDesc*> absorbed_by;  // mul -> add
-  for (auto& op : g.ops) {
-    if (!axes.count(op.output) || op.type != "elementwise_add" || cb.values[op.output].dtype != DType::kFloat32) continue;
-    for (int k : {1, 0}) {
-      const OpDesc* m = contractible_mul(op.inputs[k]);
-      if (m) {
-        absorbed_by[m] = &op;
-        break;
-      }
-    }
-  }
-
-  auto emit = [&](int opc, const std::string& out, const std::vector<DagOperand>& ops, float imm_for_op, bool has_op_imm) {
-    // immediates: at most two per step (the word's own and the next word's)
-    float imms[2] = {0.0f, 0.0f};
-    int n_imm     = 0;
-    if (has_op_imm) imms[n_imm++] = imm_for_op;
-    int sel[3] = {0, 0, 0};
-    for (size_t i = 0; i < ops.size(); ++i) {
-      if (ops[i].kind == DagOperand::kReg) {
-        sel[i] = ops[i].reg;
-      } else {
-        int found = -1;
-        for (int q = has_op_imm ? 1 : 0; q < n_imm; ++q)
-          if (memcmp(&imms[q], &ops[i].imm, 4) == 0) found = q;
-        if (found < 0) {
-          if (n_imm >= 2) {
-            fail("op '" + std::string(out) + "' needs more than two constants");
-            return -1;
-          }
-          imms[n_imm] = ops[i].imm;
-          found       = n_imm++;
-        }
-        sel[i] = found == 0 ? DAG_IMM : DAG_IMM2;
-      }
-    }
-    const int dst = alloc();
-    if (dst < 0) {
-      fail("more than eight values are live at once");
-      return -1;
-    }
-    words.push_back(DagWord(opc, dst, sel[0], sel[1], sel[2], imms[0]));
-    if (n_imm == 2 || opc == EW_SCALE_PRE) words.push_back(DagWord(EW_NOP, 0, 0, 0, 0, imms[1]));
-    reg_of[out] = dst;
-    return dst;
-  };
-
-  for (auto& op : g.ops) {
-    if (failed) return nullptr;
-    if (!axes.count(op.output) || op.type == "fill_constant" || alias.count(op.output)) continue;
-    if (absorbed_by.count(&op)) continue;  // emitted with its Add
-    const DType out_t = cb.values[op.output].dtype;
-    std::vector<std::string> consumed;
-    int dst = -1;
-    if (op.type == "elementwise_add" && out_t == DType::kFloat32 &&
-        (absorbed_by.count(contractible_mul(op.inputs[1])) ? absorbed_by[contractible_mul(op.inputs[1])] == &op
-                                                            : (contractible_mul(op.inputs[0]) && absorbed_by.count(contractible_mul(op.inputs[0])) &&
-                                                               absorbed_by[contractible_mul(op.inputs[0])] == &op))) {
-      const int k       = (contractible_mul(op.inputs[1]) && absorbed_by[contractible_mul(op.inputs[1])] == &op) ? 1 : 0;
-      const OpDesc* mul = contractible_mul(op.inputs[k]);
-      std::vector<DagOperand> o = {operand(mul->inputs[0]), operand(mul->inputs[1]), operand(op.inputs[1 - k])};
-      if (failed) return nullptr;
-      consumed = {mul->inputs[0], mul->inputs[1], op.inputs[1 - k]};
-      for (auto& c : consumed) release(c);
-      dst = emit(EW_FMA, op.output, o, 0.0f, false);
-    } else if (op.type == "scale") {
-      const float sc = (float)atof(ChainBuilder::Attr(op, "scale", "1").c_str());
-      const float bi = (float)atof(ChainBuilder::Attr(op, "bias", "0").c_str());
-      const std::string after = ChainBuilder::Attr(op, "bias_after_scale", "true");
-      DagOperand x = operand(op.inputs[0]);
-      if (failed) return nullptr;
-      release(op.inputs[0]);
-      if (after == "true" || after == "1" || after == "True") {
-        DagOperand s, b2;
-        s.kind = b2.kind = DagOperand::kImm;
-        s.imm  = sc;
-        b2.imm = bi;
-        dst = emit(EW_FMA, op.output, {x, s, b2}, 0.0f, false);
-        if (dst >= 0 && words.size() >= 1 && sc == bi) {
-          // both constants equal: emit() folded them into one immediate; nothing else to do
-        }
-      } else {
-        // imm * (x + imm2)
-        const int d = alloc();
-        if (d < 0) {
-          cb.Fail("more than eight values are live at once");
-          return nullptr;
-        }
-        words.push_back(DagWord(EW_SCALE_PRE, d, x.kind == DagOperand::kReg ? x.reg : DAG_IMM, 0, 0, sc));
-        words.push_back(DagWord(EW_NOP, 0, 0, 0, 0, bi));
-        reg_of[op.output] = d;
-        dst               = d;
-        if (x.kind != DagOperand::kReg) {
-          cb.Fail("scale of a constant");
-          return nullptr;
-        }
-      }
-    } else if (op.type == "cast") {
-      DagOperand x = operand(op.inputs[0]);
-      if (failed) return nullptr;
-      release(op.inputs[0]);
-      const int code = out_t == DType::kBool ? EW_TO_BOOL
-                                             : (out_t == DType::kFloat16 ? EW_ROUND_F16
-                                                                         : (out_t == DType::kBFloat16 ? EW_ROUND_BF16 : EW_IDENTITY));
-      dst = emit(code, op.output, {x}, 0.0f, false);
-    } else if (op.type == "identity" || op.type == "broadcast_to") {  // a no-op that is a group output: a copy
-      DagOperand x = operand(op.inputs[0]);
-      if (failed) return nullptr;
-      release(op.inputs[0]);
-      dst = emit(EW_IDENTITY, op.output, {x}, 0.0f, false);
-    } else if (op.type == "select") {
-      std::vector<DagOperand> o = {operand(op.inputs[0]), operand(op.inputs[1]), operand(op.inputs[2])};
-      if (failed) return nullptr;
-      for (auto& in : op.inputs) release(in);
-      dst = emit(EW_SELECT, op.output, o, 0.0f, false);
-    } else if (UnaryCodes().count(op.type)) {
-      DagOperand x = operand(op.inputs[0]);
-      if (failed) return nullptr;
-      release(op.inputs[0]);
-      if (op.type == "relu6") {
-        dst = emit(EW_RELU6, op.output, {x}, (float)atof(ChainBuilder::Attr(op, "threshold", "6").c_str()), true);
-      } else {
-        dst = emit(UnaryCodes().at(op.type), op.output, {x}, 0.0f, false);
-      }
-    } else if (BinaryCodes().count(op.type)) {
-      std::vector<DagOperand> o = {operand(op.inputs[0]), operand(op.inputs[1])};
-      if (failed) return nullptr;
-      release(op.inputs[0]);
-      release(op.inputs[1]);
-      dst = emit(BinaryCodes().at(op.type), op.output, o, 0.0f, false);
-    } else {
-      cb.Fail("op '" + op.type + "' is not an elementwise op");
+  if (!cb.Infer() || !StorableInFloatRegisters(cb)) return nullptr;
+  cb.out_shape = g.outputs[0].shape;
+  cb.n         = g.outputs[0].numel();
+  std::map<std::string, std::vector<int64_t>> axes;
+  std::map<std::string, ValueAction> actions;
+  RegProgramBuilder rb(cb);
+  for (size_t k = 0; k < g.outputs.size(); ++k) {
+    const TensorDesc& o = g.outputs[k];
+    if (o.shape != cb.out_shape) {
+      cb.Fail("the outputs of a register program have one shape");
       return nullptr;
     }
-    if (failed || dst < 0) return nullptr;
-    // 16-bit values are rounded to their type after every op (a cast to that type IS the rounding)
-    if (op.type != "cast" && (out_t == DType::kFloat16 || out_t == DType::kBFloat16))
-      words.push_back(DagWord(out_t == DType::kFloat16 ? EW_ROUND_F16 : EW_ROUND_BF16, dst, dst, 0, 0, 0.0f));
-    if (remaining[op.output] <= 0) {  // computed but never read: cannot happen for a value with axes
-      reg_busy[dst] = false;
-      reg_of.erase(op.output);
+    if (!cb.values.count(o.name) || cb.values[o.name].dtype != o.dtype || cb.values[o.name].shape != cb.out_shape ||
+        !cb.producer.count(o.name) || cb.producer[o.name]->type == "fill_constant") {
+      cb.Fail("output '" + o.name + "' is not a value of that type and shape computed in the group");
+      return nullptr;
     }
-    auto oi = output_index.find(op.output);
-    if (oi != output_index.end()) {
-      words.push_back(DagWord(DAG_STORE, oi->second, dst, 0, 0, 0.0f));
-      release(op.output);
+    std::vector<int64_t> id;
+    for (size_t i = 0; i < cb.out_shape.size(); ++i) id.push_back((int64_t)i);
+    axes[o.name] = id;
+    ValueAction act;
+    act.kind  = ValueAction::kStore;
+    act.index = (int)k;
+    actions[o.name] = act;
+    rb.group_outputs.insert(o.name);
+  }
+  if (!PlaceAxes(cb, [](const OpDesc&) { return true; }, &axes)) return nullptr;
+  auto live = [&](const OpDesc& op) { return axes.count(op.output) > 0; };
+  std::vector<const OpDesc*> ops;
+  for (auto& op : g.ops)
+    if (live(op)) {
+      ops.push_back(&op);
+      for (auto& in : op.inputs) ++rb.uses[in];
     }
-  }
-  if (failed) return nullptr;
-  // outputs that are a group input or a constant seen through no-ops
-  for (auto& o : g.outputs) {
-    if (cb.producer.count(o.name) && !alias.count(o.name) && cb.producer[o.name]->type != "fill_constant") continue;
-    cb.Fail("output '" + o.name + "' is not computed by an op of the group");
-    return nullptr;
-  }
-  if (words.size() > (size_t)DAG_MAX_STEPS) {
-    cb.Fail("register program of " + std::to_string(words.size()) + " steps exceeds the limit of " + std::to_string(DAG_MAX_STEPS));
+  rb.FindAliases(live);
+  rb.address_input = [&](const std::string& name, int k, Side* side) {
+    auto ax = axes.find(name);
+    return ax != axes.end() && cb.SideSpec(cb.values[name].shape, ax->second, k, side);
+  };
+  if (!rb.EmitSegment(ops, actions, {}, {})) return nullptr;
+  if (rb.words.size() > (size_t)DAG_MAX_STEPS) {
+    cb.Fail("register program of " + std::to_string(rb.words.size()) + " steps exceeds the limit of " + std::to_string(DAG_MAX_STEPS));
     return nullptr;
   }
   for (size_t i = 0; i < g.inputs.size(); ++i)
-    if (!in_used[i]) {
+    if (!rb.in_used[i]) {
       cb.Fail("group input '" + g.inputs[i].name + "' is not used");
       return nullptr;
     }
@@ -1584,44 +1697,24 @@ std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& de
   }
   st.block[0] = 256;
   st.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(CeilDiv(cb.n, 8), 256), (int64_t)dev.sm_count * 16));
-  auto int_arg = [](int64_t v) { ArgSpec a; a.kind = ArgSpec::kInt; a.ivalue = v; return a; };
-  int64_t meta = 0;
   ArgSpec aligned;
   aligned.kind   = ArgSpec::kAligned;
   aligned.ivalue = 1;
-  for (int k = 0; k < DAG_MAX_IN; ++k) {
-    ArgSpec a;
-    a.kind  = ArgSpec::kInput;
-    a.index = k < (int)g.inputs.size() ? k : 0;
-    st.args.push_back(a);
-    if (k < (int)g.inputs.size()) {
-      meta |= (int64_t)(DTypeKernelCode(g.inputs[k].dtype) | (in_side[k].mode << 3)) << (6 * k);
-      if (in_side[k].mode == EW_SIDE_FULL || in_side[k].mode == EW_SIDE_PERIODIC_VEC) aligned.aligned_inputs.push_back(k);
-    }
-  }
-  for (int k = 0; k < DAG_MAX_OUT; ++k) {
-    ArgSpec a;
-    a.kind  = ArgSpec::kOutput;
-    a.index = k < (int)g.outputs.size() ? k : 0;
-    st.args.push_back(a);
-    if (k < (int)g.outputs.size()) {
-      meta |= (int64_t)DTypeKernelCode(g.outputs[k].dtype) << (48 + 3 * k);
-      aligned.aligned_outputs.push_back(k);
-    }
-  }
-  st.args.push_back(int_arg(cb.n));
+  const int64_t meta = PushPointerArgs(g, rb.in_side, &st, &aligned);
+  for (size_t k = 0; k < g.outputs.size(); ++k) aligned.aligned_outputs.push_back((int)k);
+  st.args.push_back(IntArg(cb.n));
   st.args.push_back(aligned);
-  st.args.push_back(int_arg(meta));
+  st.args.push_back(IntArg(meta));
   for (int k = 0; k < DAG_MAX_IN; ++k) {
-    st.args.push_back(int_arg(k < (int)g.inputs.size() ? in_side[k].mid : 1));
-    st.args.push_back(int_arg(k < (int)g.inputs.size() ? in_side[k].inner : 1));
+    st.args.push_back(IntArg(k < (int)g.inputs.size() ? rb.in_side[k].mid : 1));
+    st.args.push_back(IntArg(k < (int)g.inputs.size() ? rb.in_side[k].inner : 1));
   }
-  st.args.push_back(int_arg((int64_t)words.size()));
-  for (int k = 0; k < DAG_MAX_STEPS; ++k) st.args.push_back(int_arg(k < (int)words.size() ? (int64_t)words[k] : 0));
+  st.args.push_back(IntArg((int64_t)rb.words.size()));
+  for (int k = 0; k < DAG_MAX_STEPS; ++k) st.args.push_back(IntArg(k < (int)rb.words.size() ? (int64_t)rb.words[k] : 0));
   if (dev.enable_static_chains) {
     uint32_t sig[32] = {0};
-    for (size_t k = 0; k < words.size(); ++k) sig[k] = (uint32_t)(words[k] & 0xffffffffu);
-    if (const KernelEntry* fixed = FindStaticChain("ew_dag", meta, (int)words.size(), sig)) st.kernel = fixed;
+    for (size_t k = 0; k < rb.words.size(); ++k) sig[k] = (uint32_t)(rb.words[k] & 0xffffffffu);
+    if (const KernelEntry* fixed = FindStaticChain("ew_dag", meta, (int)rb.words.size(), sig)) st.kernel = fixed;
   }
   p->steps.push_back(st);
   return p;

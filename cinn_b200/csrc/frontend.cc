@@ -484,7 +484,14 @@ struct FusionState {
         g.desc.outputs.push_back(t);
       }
     }
-    g.desc.name = name + "_" + std::to_string(uid) + "_" + std::to_string(*members.begin());
+    // The first instruction that belongs to this group alone names it (a recomputed producer sits in several groups).
+    int first_own = *members.begin();
+    for (int i : members)
+      if (!recomputed.count(i)) {
+        first_own = i;
+        break;
+      }
+    g.desc.name = name + "_" + std::to_string(uid) + "_" + std::to_string(first_own);
     return g;
   }
 

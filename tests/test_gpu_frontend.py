@@ -154,7 +154,8 @@ def test_generic_chains_match_the_oracle(oracle, make):
     rng = np.random.default_rng(11)
     feeds = {k: rng.standard_normal(s).astype(np.float32) for k, s in shapes.items()}
     comp, out = run_program(b, feeds, [y])
-    assert all(p.split()[0] == "ew_chain" for _, p in comp.groups()), comp.groups()
+    # chains, or (an operand computed from a small input: abs(m) of shape [6, 1]) one register program
+    assert all(p.split()[0] in ("ew_chain", "ew_dag") for _, p in comp.groups()), comp.groups()
     ref = oracle_program(comp, feeds)[str(y)]
     d = oracle.max_ulp(out[str(y)], ref)
     print("%s: %d group(s), max ulp %d" % (make.__name__, len(comp.groups()), d))

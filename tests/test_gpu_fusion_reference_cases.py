@@ -15,7 +15,7 @@ pytestmark = pytest.mark.gpu
 TARGET = common.DefaultNVGPUTarget()
 
 
-def run_and_check(b, fetch, seed, exact=True):
+def run_and_check(b, fetch, seed, exact=True, rtol=1e-5, atol=1e-4):
     comp = Computation.build_and_compile(TARGET, b, fetch=[str(f) for f in fetch])
     rng = np.random.default_rng(seed)
     feeds = {}
@@ -34,7 +34,7 @@ def run_and_check(b, fetch, seed, exact=True):
             assert np.array_equal(got.view(np.uint8), np.ascontiguousarray(ref).view(np.uint8)), \
                 (str(f), [p for _, p in comp.groups()], float(np.abs(got.astype(np.float64) - ref).max()))
         else:
-            assert np.allclose(got, ref, rtol=1e-5, atol=1e-4), (str(f), [p for _, p in comp.groups()])
+            assert np.allclose(got, ref, rtol=rtol, atol=atol), (str(f), [p for _, p in comp.groups()])
     return comp
 
 
@@ -84,6 +84,9 @@ def _dag_programs():
 def test_register_programs_match_the_oracle(make):
     b = NetBuilder(make.__name__)
     fetch = make(b)
-    comp = run_and_check(b, fetch, seed=3)
+    # sigmoid / tanh go through the device's expf, within 2 ulp of the host library's: those programs are compared
+    # at a few ulp, everything else bit for bit
+    approx = make.__name__ in ("shared_value_four_outputs", "odd_size_takes_the_scalar_tail")
+    comp = run_and_check(b, fetch, seed=3, exact=not approx, rtol=5e-7, atol=2e-7)
     # one kernel either way: a register program, or (add of two products, squared) a chain with temporaries
     assert [p.split()[0] for _, p in comp.groups()] in (["ew_dag"], ["ew_chain"]), [p for _, p in comp.groups()]
