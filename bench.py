@@ -282,6 +282,15 @@ def side_groups(torch, dev, peak, only=None):
         ("chain_reduce_sum_abs_diff_cols_8192x8192", lambda: W.chain_reduce("sum_abs_diff", axis=0), 1, "chain + reduce, one kernel"),
         ("chain_reduce_sum_sigmoid_affine_rows_8192x8192", lambda: W.chain_reduce("sum_sigmoid_affine", axis=1), 1,
          "chain + reduce, one kernel"),
+        # reductions with elementwise ops around them (row programs) and elementwise groups with several outputs
+        ("row_program_l2_normalise_16384x4096", lambda: W.row_program("l2_normalise"), 2, "x / sqrt(sum(x^2)), one kernel"),
+        ("row_program_centre_16384x4096", lambda: W.row_program("centre"), 2, "x - mean(x), one kernel"),
+        ("row_program_affine_relu_16384x4096", lambda: W.row_program("affine_relu"), 2, "relu(sum(x) * a + c), one kernel"),
+        ("row_program_three_sums_16384x4096", lambda: W.row_program("three_sums"), 2, "sum(A), sum(B), sum(A + B), one kernel"),
+        ("dag_shared_sum_4out_4096x8192", lambda: W.dag_program("shared_sum_4out", (4096, 8192)), 1,
+         "g = A + B feeding four sums: six reads, four writes, one kernel"),
+        ("dag_bias_relu_mask_3out_8192x8192", lambda: W.dag_program("bias_relu_mask_3out"), 1,
+         "x + bias, its relu and its mask: one read, three writes"),
     ]
     if not only or any(o in "add_relu_1x3x224x224" for o in only):
         # config 1 through NetBuilder / Computation, timed by the library's own ExecuteTest loop (no Python per launch)
@@ -343,6 +352,12 @@ PROFILE_GROUPS = {
     "chain_reduce_rows": lambda W: W.chain_reduce("sum_abs_diff", axis=1),
     "chain_tree": lambda W: W.chain_tree(),
     "bn_train_stats_f16": lambda W: W.bn_train_stats((256, 64, 112, 112), half=True),
+    "chain_reduce_cols": lambda W: W.chain_reduce("sum_abs_diff", axis=0),
+    "chain_reduce_sigmoid_rows": lambda W: W.chain_reduce("sum_sigmoid_affine", axis=1),
+    "row_l2_normalise": lambda W: W.row_program("l2_normalise"),
+    "row_centre": lambda W: W.row_program("centre"),
+    "row_affine_relu": lambda W: W.row_program("affine_relu"),
+    "dag_shared_sum_4out": lambda W: W.dag_program("shared_sum_4out", (4096, 8192)),
 }
 
 

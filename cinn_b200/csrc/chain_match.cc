@@ -1336,6 +1336,16 @@ struct RegProgramBuilder {
       }
     }
   }
+  // The value will not be read again (by any segment): its register is free.
+  void ForceFree(const std::string& v) {
+    const std::string r = Root(v);
+    remaining.erase(r);
+    auto rg = reg_of.find(r);
+    if (rg != reg_of.end()) {
+      reg_busy[rg->second] = false;
+      reg_of.erase(rg);
+    }
+  }
   // A Mul whose single consumer, a float32 Add, absorbs it as a fused multiply-add (cinn/optim/lower_intrin.cc:41-59).
   const OpDesc* ContractibleMul(const std::string& v, const std::set<std::string>& never) const {
     if (alias.count(v) || never.count(v)) return nullptr;  // the reference contracts the Mul node itself
@@ -1712,9 +1722,399 @@ std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& de
   st.args.push_back(IntArg((int64_t)rb.words.size()));
   for (int k = 0; k < DAG_MAX_STEPS; ++k) st.args.push_back(IntArg(k < (int)rb.words.size() ? (int64_t)rb.words[k] : 0));
   if (dev.enable_static_chains) {
-    uint32_t sig[32] = {0};
+    uint32_t sig[40] = {0};
     for (size_t k = 0; k < rb.words.size(); ++k) sig[k] = (uint32_t)(rb.words[k] & 0xffffffffu);
     if (const KernelEntry* fixed = FindStaticChain("ew_dag", meta, (int)rb.words.size(), sig)) st.kernel = fixed;
+  }
+  p->steps.push_back(st);
+  return p;
+}
+
+}  // namespace cinn_b200
+
+// ---- row programs: reductions over the trailing axes with elementwise ops either side (row_prog.cu) -------------------
+namespace cinn_b200 {
+
+std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceInfo& dev, std::string* why) {
+  ChainBuilder cb(g, why);
+  cb.allow_reduce = true;
+  if (g.outputs.empty() || g.outputs.size() > (size_t)DAG_MAX_OUT || g.inputs.size() > (size_t)DAG_MAX_IN) {
+    cb.Fail("a row program has one to four outputs and reads at most eight tensors");
+    return nullptr;
+  }
+  if (!cb.Infer() || !StorableInFloatRegisters(cb)) return nullptr;
+  static const std::map<std::string, int> folds = {{"reduce_sum", 0}, {"reduce_prod", 1}, {"reduce_max", 2}, {"reduce_min", 3}};
+  // ---- geometry: every reduce folds the same trailing axes of one full shape ----
+  std::vector<int64_t> full;
+  int lead = -1;
+  std::vector<const OpDesc*> reduces;
+  for (auto& op : g.ops) {
+    if (op.type.rfind("reduce_", 0) != 0) continue;
+    if (!folds.count(op.type)) {
+      cb.Fail("'" + op.type + "' has no row-program form");
+      return nullptr;
+    }
+    const Value& x = cb.values[op.inputs[0]];
+    if (x.dtype != DType::kFloat32) {
+      cb.Fail("a row program reduces float32 values");
+      return nullptr;
+    }
+    std::vector<int64_t> dims = IntList(ChainBuilder::Attr(op, "dim", ""));
+    const int nd = (int)x.shape.size();
+    if (dims.empty())
+      for (int i = 0; i < nd; ++i) dims.push_back(i);
+    std::vector<bool> red(nd, false);
+    for (auto d : dims) red[(d % nd + nd) % nd] = true;
+    int first_red = nd;
+    for (int i = nd - 1; i >= 0 && red[i]; --i) first_red = i;
+    int count = 0;
+    for (bool b2 : red) count += b2 ? 1 : 0;
+    if (count != nd - first_red) {
+      cb.Fail("a row program reduces trailing axes");
+      return nullptr;
+    }
+    if (reduces.empty()) {
+      full = x.shape;
+      lead = first_red;
+    } else if (x.shape != full || first_red != lead) {
+      cb.Fail("the reductions of a row program fold the same axes of one shape");
+      return nullptr;
+    }
+    reduces.push_back(&op);
+  }
+  if (reduces.empty()) {
+    cb.Fail("no reduction in the group");
+    return nullptr;
+  }
+  int64_t rows = 1, r = 1;
+  for (int i = 0; i < (int)full.size(); ++i) (i < lead ? rows : r) *= full[i];
+  const int64_t n = rows * r;
+  if (r < 2 || r > 16384) {
+    cb.Fail("a row program keeps rows of 2 to 16384 elements");
+    return nullptr;
+  }
+  std::vector<int64_t> row_shape(full.begin(), full.begin() + lead);
+  if (row_shape.empty()) row_shape.push_back(1);
+
+  // ---- which values depend on a reduction, and where they live ----
+  std::map<std::string, bool> dep_red;
+  for (auto& t : g.inputs) dep_red[t.name] = false;
+  for (auto& op : g.ops) {
+    bool d = op.type.rfind("reduce_", 0) == 0;
+    for (auto& in : op.inputs) d = d || dep_red[in];
+    dep_red[op.output] = d;
+  }
+  auto is_row  = [&](const std::string& v) { return dep_red[v] && cb.values[v].numel() == rows; };
+  auto is_full = [&](const std::string& v) { return cb.values[v].numel() == n && cb.values[v].shape.size() == full.size() && !is_row(v); };
+  for (auto& op : g.ops)
+    if (dep_red[op.output] && !is_row(op.output) && cb.values[op.output].numel() != n) {
+      cb.Fail("value '" + op.output + "' is neither one per row nor one per element");
+      return nullptr;
+    }
+  // avail: the pass after whose reduction a per-row value exists; need: the first pass that can evaluate a
+  // per-element value (one after the last per-row value it reads)
+  std::map<std::string, int> avail, need, pass_of_reduce;
+  for (auto& t : g.inputs) need[t.name] = 0;
+  for (auto& op : g.ops) {
+    const std::string& o = op.output;
+    if (!dep_red[o]) {
+      need[o] = 0;
+    } else if (op.type.rfind("reduce_", 0) == 0) {
+      pass_of_reduce[o] = need[op.inputs[0]];
+      avail[o]          = pass_of_reduce[o];
+    } else if (is_row(o)) {
+      int a = 0;
+      for (auto& in : op.inputs)
+        if (dep_red[in]) {
+          if (!is_row(in)) {
+            cb.Fail("a per-row value computed from a per-element one without a reduction");
+            return nullptr;
+          }
+          a = std::max(a, avail[in]);
+        }
+      avail[o] = a;
+    } else {
+      int q = 0;
+      for (auto& in : op.inputs) q = std::max(q, dep_red[in] && is_row(in) ? avail[in] + 1 : need[in]);
+      need[o] = q;
+    }
+  }
+  int npass = 0;
+  for (auto& kv : pass_of_reduce) npass = std::max(npass, kv.second + 1);
+  std::map<std::string, int> output_index;
+  for (size_t k = 0; k < g.outputs.size(); ++k) {
+    const TensorDesc& o = g.outputs[k];
+    if (!cb.producer.count(o.name) || cb.values[o.name].dtype != o.dtype || cb.values[o.name].shape != o.shape) {
+      cb.Fail("output '" + o.name + "' is not a value of that type and shape computed in the group");
+      return nullptr;
+    }
+    if (is_row(o.name)) {
+    } else if (is_full(o.name) && o.shape == full) {
+      npass = std::max(npass, need[o.name] + 1);
+    } else {
+      cb.Fail("output '" + o.name + "' is neither one value per row nor a tensor of the reduced shape");
+      return nullptr;
+    }
+    output_index[o.name] = (int)k;
+  }
+  if (npass > ROWP_MAX_PASSES) {
+    cb.Fail("the reductions depend on one another more than three deep");
+    return nullptr;
+  }
+
+  // ---- axes: per-element values against the full shape, per-row values against the row shape ----
+  auto identity_axes = [](size_t rank) {
+    std::vector<int64_t> id;
+    for (size_t i = 0; i < rank; ++i) id.push_back((int64_t)i);
+    return id;
+  };
+  std::map<std::string, std::vector<int64_t>> full_axes, row_axes;
+  for (const OpDesc* red : reduces) full_axes[red->inputs[0]] = identity_axes(full.size());
+  for (auto& o : g.outputs)
+    if (!is_row(o.name)) full_axes[o.name] = identity_axes(full.size());
+  auto element_op = [&](const OpDesc& op) { return op.type.rfind("reduce_", 0) != 0 && !is_row(op.output); };
+  if (!PlaceAxes(cb, element_op, &full_axes)) return nullptr;
+  // a per-row value read by a per-element op must lie along the leading axes
+  for (auto& kv : full_axes) {
+    if (!dep_red[kv.first] || !is_row(kv.first)) continue;
+    const auto& shape = cb.values[kv.first].shape;
+    int next = 0;
+    for (size_t i = 0; i < shape.size(); ++i) {
+      if (shape[i] == 1) continue;
+      while (next < lead && full[next] == 1) ++next;
+      if (next >= lead || kv.second[i] != next) {
+        cb.Fail("per-row value '" + kv.first + "' is broadcast along an axis that is not reduced");
+        return nullptr;
+      }
+      ++next;
+    }
+  }
+  auto row_value_axes = [&](const std::string& v) {
+    const auto& shape = cb.values[v].shape;
+    std::vector<int64_t> ax;
+    int next = 0;
+    for (size_t i = 0; i < shape.size(); ++i) {
+      if (shape[i] == 1 && !(next < lead && full[next] == 1)) {
+        ax.push_back(0);  // an extent-1 axis kept by keep_dim: addressing ignores it
+        continue;
+      }
+      ax.push_back(std::min<int64_t>(next, (int64_t)row_shape.size() - 1));
+      ++next;
+    }
+    return ax;
+  };
+  for (auto& op : g.ops)
+    if (dep_red[op.output] && is_row(op.output)) row_axes[op.output] = row_value_axes(op.output);
+  auto scalar_op = [&](const OpDesc& op) { return op.type.rfind("reduce_", 0) != 0 && (is_row(op.output) || !dep_red[op.output]); };
+  {
+    // placements in the row space only matter below per-row values: walk from them
+    ChainBuilder& c2 = cb;
+    c2.out_shape     = row_shape;
+    c2.n             = rows;
+    if (!PlaceAxes(cb, scalar_op, &row_axes)) return nullptr;
+  }
+
+  // ---- uses and last uses ----
+  std::map<std::string, int> uses;
+  for (auto& op : g.ops)
+    for (auto& in : op.inputs) ++uses[in];
+  // what a set of targets needs, within one index space: ops in program order
+  auto needed_ops = [&](const std::vector<std::string>& targets, bool scalar_space, int pass) {
+    std::set<const OpDesc*> take;
+    std::vector<std::string> stack = targets;
+    while (!stack.empty()) {
+      const std::string v = stack.back();
+      stack.pop_back();
+      auto p = cb.producer.find(v);
+      if (p == cb.producer.end()) continue;  // a group input
+      const OpDesc* op = p->second;
+      if (op->type.rfind("reduce_", 0) == 0) continue;       // its total sits in a scalar register
+      if (!scalar_space && dep_red[v] && is_row(v)) continue;  // a per-row value: read from its scalar register
+      if (scalar_space && dep_red[v] && avail[v] < pass) continue;  // computed by an earlier scalar program
+      if (!take.insert(op).second) continue;
+      for (auto& in : op->inputs) stack.push_back(in);
+    }
+    std::vector<const OpDesc*> ordered;
+    for (auto& op : g.ops)
+      if (take.count(&op)) ordered.push_back(&op);
+    return ordered;
+  };
+  // segment index 2p (element program of pass p) / 2p + 1 (scalar program) of the last read of every per-row value
+  std::map<std::string, int> last_read;
+  std::vector<std::vector<const OpDesc*>> seg_ops(2 * npass);
+  std::vector<std::map<std::string, ValueAction>> seg_actions(2 * npass);
+  for (int p = 0; p < npass; ++p) {
+    std::vector<std::string> et, st2;
+    for (const OpDesc* red : reduces)
+      if (pass_of_reduce[red->output] == p) et.push_back(red->inputs[0]);
+    for (auto& o : g.outputs) {
+      if (!is_row(o.name) && need[o.name] == p) {
+        et.push_back(o.name);
+        ValueAction a;
+        a.kind  = ValueAction::kStore;
+        a.index = output_index[o.name];
+        seg_actions[2 * p][o.name] = a;
+      }
+      if (is_row(o.name) && avail[o.name] == p) {
+        ValueAction a;
+        a.kind  = ValueAction::kStore;
+        a.index = output_index[o.name];
+        seg_actions[2 * p + 1][o.name] = a;
+      }
+    }
+    for (auto& op : g.ops)
+      if (dep_red[op.output] && is_row(op.output) && op.type.rfind("reduce_", 0) != 0 && avail[op.output] == p) st2.push_back(op.output);
+    seg_ops[2 * p]     = needed_ops(et, false, p);
+    seg_ops[2 * p + 1] = needed_ops(st2, true, p);
+    for (int s2 = 2 * p; s2 <= 2 * p + 1; ++s2)
+      for (const OpDesc* op : seg_ops[s2])
+        for (auto& in : op->inputs)
+          if (dep_red[in] && is_row(in)) last_read[in] = s2;
+    for (auto& kv : seg_actions[2 * p + 1]) last_read[kv.first] = std::max(last_read[kv.first], 2 * p + 1);
+  }
+
+  // ---- emission ----
+  std::vector<Side> in_side(g.inputs.size());
+  std::vector<int> in_space(g.inputs.size(), -1);  // 0 element space, 1 row space
+  auto merge_sides = [&](const RegProgramBuilder& b2, int space) {
+    for (size_t k = 0; k < g.inputs.size(); ++k) {
+      if (!b2.in_used[k]) continue;
+      if (in_space[k] >= 0 && (in_space[k] != space || !(in_side[k] == b2.in_side[k]))) {
+        cb.Fail("input '" + g.inputs[k].name + "' is read both per element and per row");
+        return false;
+      }
+      in_space[k] = space;
+      in_side[k]  = b2.in_side[k];
+    }
+    return true;
+  };
+  std::set<std::string> reduce_operands;
+  for (const OpDesc* red : reduces) reduce_operands.insert(red->inputs[0]);
+  RegProgramBuilder sb(cb);  // the scalar registers persist over the passes
+  sb.uses = uses;
+  for (auto& o : g.outputs) sb.group_outputs.insert(o.name);
+  auto live_all = [](const OpDesc&) { return true; };
+  sb.FindAliases(live_all);
+  // a broadcast of a per-row value to the full shape is the value itself, seen from an element program; every other
+  // alias must stay inside one index space
+  sb.address_input = [&](const std::string& name, int k, Side* side) {
+    auto ax = row_axes.find(name);
+    cb.out_shape = row_shape;
+    cb.n         = rows;
+    return ax != row_axes.end() && cb.SideSpec(cb.values[name].shape, ax->second, k, side);
+  };
+  std::vector<uint64_t> words;
+  unsigned long long counts = 0;
+  for (int p = 0; p < npass; ++p) {
+    // element program
+    RegProgramBuilder eb(cb);
+    eb.uses          = uses;
+    eb.group_outputs = sb.group_outputs;
+    eb.alias         = sb.alias;
+    eb.address_input = [&](const std::string& name, int k, Side* side) {
+      auto ax = full_axes.find(name);
+      cb.out_shape = full;
+      cb.n         = n;
+      return ax != full_axes.end() && cb.SideSpec(cb.values[name].shape, ax->second, k, side);
+    };
+    eb.outside_selector = [&](const std::string& root) {
+      if (!(dep_red[root] && is_row(root))) return -1;
+      auto it = sb.reg_of.find(root);
+      return it == sb.reg_of.end() ? -1 : ROWP_SREG0 + it->second;
+    };
+    std::map<std::string, ValueAction> actions = seg_actions[2 * p];
+    for (const OpDesc* red : reduces) {
+      if (pass_of_reduce[red->output] != p) continue;
+      const int sreg = sb.Alloc();
+      if (sreg < 0) return nullptr;
+      sb.reg_of[red->output]    = sreg;
+      sb.remaining[red->output] = 1;  // held until its last read (freed below)
+      if (actions.count(red->inputs[0])) {
+        cb.Fail("a value is reduced twice, or reduced and stored, in one pass");
+        return nullptr;
+      }
+      ValueAction a;
+      a.kind  = ValueAction::kAccumulate;
+      a.index = sreg;
+      a.fold  = folds.at(red->type);
+      actions[red->inputs[0]] = a;
+    }
+    if (!eb.EmitSegment(seg_ops[2 * p], actions, {}, reduce_operands) || !merge_sides(eb, 0)) return nullptr;
+    counts |= (unsigned long long)eb.words.size() << (8 * p);
+    words.insert(words.end(), eb.words.begin(), eb.words.end());
+    for (auto& kv : last_read)
+      if (kv.second == 2 * p) sb.ForceFree(kv.first);
+    // scalar program
+    std::map<std::string, int> later;
+    for (auto& kv : last_read)
+      if (kv.second > 2 * p + 1) later[kv.first] = 1;
+    const size_t before = sb.words.size();
+    if (!sb.EmitSegment(seg_ops[2 * p + 1], seg_actions[2 * p + 1], later, {})) return nullptr;
+    counts |= (unsigned long long)(sb.words.size() - before) << (32 + 8 * p);
+    words.insert(words.end(), sb.words.begin() + before, sb.words.end());
+    for (auto& kv : last_read)
+      if (kv.second == 2 * p + 1) sb.ForceFree(kv.first);
+    // values the scalar program loaded or computed for itself only are dead now
+    for (auto it = sb.reg_of.begin(); it != sb.reg_of.end();) {
+      if (!last_read.count(it->first) || last_read[it->first] <= 2 * p + 1) {
+        sb.reg_busy[it->second] = false;
+        sb.remaining.erase(it->first);
+        it = sb.reg_of.erase(it);
+      } else {
+        ++it;
+      }
+    }
+  }
+  if (!merge_sides(sb, 1)) return nullptr;
+  if (words.size() > (size_t)ROWP_MAX_STEPS) {
+    cb.Fail("row program of " + std::to_string(words.size()) + " steps exceeds the limit of " + std::to_string(ROWP_MAX_STEPS));
+    return nullptr;
+  }
+  for (size_t k = 0; k < g.inputs.size(); ++k)
+    if (in_space[k] < 0) {
+      cb.Fail("group input '" + g.inputs[k].name + "' is not used");
+      return nullptr;
+    }
+
+  auto p      = std::make_unique<CompiledGroup>();
+  p->name     = g.name;
+  p->pattern  = "row_program";
+  p->inputs   = g.inputs;
+  p->outputs  = g.outputs;
+  p->elements = n;
+  for (auto& t : g.inputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
+  for (auto& t : g.outputs) p->algorithmic_bytes += t.numel() * DTypeBytes(t.dtype);
+  LaunchStep st;
+  st.kernel = FindKernel("row_program");
+  if (!st.kernel) {
+    cb.Fail("the row-program kernel is not in the library");
+    return nullptr;
+  }
+  const int64_t group = r > 1024 ? 256 : 32;
+  st.block[0] = 256;
+  st.grid[0]  = (unsigned)std::max<int64_t>(1, group == 32 ? std::min<int64_t>(CeilDiv(rows, 8), (int64_t)dev.sm_count * 16)
+                                                            : std::min<int64_t>(rows, (int64_t)dev.sm_count * 8));
+  ArgSpec aligned;
+  aligned.kind   = ArgSpec::kAligned;
+  aligned.ivalue = r % 4 == 0 ? 1 : 0;
+  const int64_t meta = PushPointerArgs(g, in_side, &st, &aligned);
+  for (size_t k = 0; k < g.outputs.size(); ++k)
+    if (!is_row(g.outputs[k].name)) aligned.aligned_outputs.push_back((int)k);
+  st.args.push_back(IntArg(rows));
+  st.args.push_back(IntArg(r));
+  st.args.push_back(IntArg(group));
+  st.args.push_back(aligned);
+  st.args.push_back(IntArg(meta));
+  st.args.push_back(IntArg((int64_t)counts));
+  for (int k = 0; k < DAG_MAX_IN; ++k) {
+    st.args.push_back(IntArg(k < (int)g.inputs.size() ? in_side[k].mid : 1));
+    st.args.push_back(IntArg(k < (int)g.inputs.size() ? in_side[k].inner : 1));
+  }
+  for (int k = 0; k < ROWP_MAX_STEPS; ++k) st.args.push_back(IntArg(k < (int)words.size() ? (int64_t)words[k] : 0));
+  if (dev.enable_static_chains) {
+    uint32_t sig[40] = {(uint32_t)(counts & 0xffffffffu), (uint32_t)(counts >> 32)};
+    for (size_t k = 0; k < words.size(); ++k) sig[k + 2] = (uint32_t)(words[k] & 0xffffffffu);
+    if (const KernelEntry* fixed = FindStaticChain("row_program", meta, (int)words.size() + 2, sig)) st.kernel = fixed;
   }
   p->steps.push_back(st);
   return p;

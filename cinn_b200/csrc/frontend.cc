@@ -509,6 +509,28 @@ struct FusionState {
     }
     g.pattern = plan->pattern;
     for (auto& s : plan->steps) g.kernels.push_back(s.kernel->name);
+    if (g.pattern == "row_program" && g.kernels[0] == "row_program") {
+      // The interpreting row-program kernel is worth a group of its own only where it saves a pass over a full-size
+      // tensor or a launch per reduction: a per-element result that depends on a reduction (x / ||x||), or several
+      // reductions.  One reduction with a per-row epilogue is better served by the dedicated reduction kernels plus
+      // a tiny elementwise kernel, unless the library holds a kernel specialised for exactly this program.
+      int n_reduce = 0;
+      std::set<std::string> after_reduce;  // values computed from a reduction's result
+      for (auto& op : g.desc.ops) {
+        bool dep = op.type.rfind("reduce_", 0) == 0;
+        n_reduce += dep ? 1 : 0;
+        for (auto& in : op.inputs) dep = dep || after_reduce.count(in);
+        if (dep) after_reduce.insert(op.output);
+      }
+      int64_t largest_in = 0;
+      for (auto& t : g.desc.inputs) largest_in = std::max<int64_t>(largest_in, t.numel());
+      bool full_result = false;
+      for (auto& t : g.desc.outputs) full_result = full_result || (t.numel() == largest_in && after_reduce.count(t.name));
+      if (n_reduce < 2 && !full_result) {
+        if (why) *why = "one reduction with a per-row epilogue: left to the reduction kernels";
+        return false;
+      }
+    }
     if (out) *out = std::move(g);
     return true;
   }
@@ -579,11 +601,18 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
       for (int i = 0; i < n; ++i)
         if (comp[i] == c) members.insert(i);
       if (members.size() < 2) continue;
-      if (st.Compiles(members, nullptr, nullptr)) {
+      FusedGroupInfo whole;
+      const bool whole_compiles = st.Compiles(members, &whole, nullptr);
+      // A region that only the interpreting row-program kernel takes as a whole is first searched for a softmax or
+      // layer_norm composition inside it (below): those have dedicated kernels several times faster, and the ops
+      // around them then run as chains.
+      const bool interpreted_rows = whole_compiles && whole.pattern == "row_program" && whole.kernels[0] == "row_program";
+      if (whole_compiles && !interpreted_rows) {
         for (int i : members) group_of[i] = (int)sets.size();
         sets.push_back(members);
         continue;
       }
+      const size_t sets_before = sets.size();
       // The region as a whole has no kernel, but everything downstream of one of its values may be a composition
       // that has one (a max-subtracted softmax or a layer_norm applied to a computed tensor): such a set is closed
       // under consumers, so it can be a group of its own with that value as an input.
@@ -661,6 +690,10 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
           sets.push_back(part);
           break;
         }
+      }
+      if (interpreted_rows && sets.size() == sets_before) {  // no dedicated composition inside: the row program it is
+        for (int i : members) group_of[i] = (int)sets.size();
+        sets.push_back(members);
       }
     }
   }
@@ -817,7 +850,7 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
     };
     for (size_t i = 0; i < sets.size(); ++i) {
       if (sets[i].empty() || !is_reduce_group(sets[i])) continue;
-      const FusedGroupInfo gi = st.Describe(sets[i]);
+      FusedGroupInfo gi = st.Describe(sets[i]);
       for (size_t j = i + 1; j < sets.size(); ++j) {
         if (sets[j].empty() || !is_reduce_group(sets[j])) continue;
         const FusedGroupInfo gj = st.Describe(sets[j]);
@@ -865,7 +898,7 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
           if (!take(eligible))  // all at once (two casts of one 16-bit type), else one by one
             for (int p : eligible) take({p});
         }
-        break;
+        gi = st.Describe(sets[i]);  // further reductions over the same tensors may join as well
       }
     }
   }

@@ -212,6 +212,40 @@ DAG_GROUPS = [
                                          "elementwise_add w2 = W st ; axis=-1"], ["v2", "w2"]),
 ]
 
+# Row programs (row_prog.cu): reductions over the last axis with elementwise ops around them.  Two row lengths per
+# program: one that a warp takes (1024) and one that a CTA takes (4096) plan to the same program, so one entry each.
+ROWS = "64,4096"
+
+
+def row_group(name, inputs, ops, outputs):
+    lines = ["group fn_static_" + name] + ["input %s" % i for i in inputs] + ["op %s" % o for o in ops]
+    lines += ["output %s" % o for o in outputs]
+    return name, "\n".join(lines) + "\n"
+
+
+ROW_GROUPS = [
+    row_group("l2_normalise", ["X float32 " + ROWS],
+              ["identity xi = X", "elementwise_mul xx = X xi ; axis=-1", "reduce_sum s = xx ; dim=1 keep_dim=true",
+               "sqrt n = s", "broadcast_to nb = n ; out_shape=%s broadcast_axes=0,1" % ROWS, "divide y = X nb ; axis=-1"],
+              ["y float32 " + ROWS]),
+    row_group("centre", ["X float32 " + ROWS],
+              ["reduce_sum s = X ; dim=1 keep_dim=false", "fill_constant c = ; shape=64 value=4096.0 dtype=float32",
+               "divide m = s c ; axis=-1", "broadcast_to mb = m ; out_shape=%s broadcast_axes=0" % ROWS,
+               "subtract y = X mb ; axis=-1"], ["y float32 " + ROWS]),
+    row_group("row_affine_relu", ["X float32 " + ROWS, "a float32 64", "c float32 64"],
+              ["reduce_sum s = X ; dim=1 keep_dim=false", "elementwise_mul t = s a ; axis=-1",
+               "elementwise_add u = t c ; axis=-1", "relu y = u"], ["y float32 64"]),
+    row_group("shifted_exp_normalised", ["X float32 " + ROWS],
+              ["reduce_max mx = X ; dim=1 keep_dim=false", "broadcast_to mb = mx ; out_shape=%s broadcast_axes=0" % ROWS,
+               "subtract d = X mb ; axis=-1", "exp e = d", "reduce_sum s = e ; dim=1 keep_dim=false",
+               "broadcast_to sb = s ; out_shape=%s broadcast_axes=0" % ROWS, "divide p = e sb ; axis=-1",
+               "scale y = p ; scale=2.0 bias=0.0 bias_after_scale=true"], ["y float32 " + ROWS]),
+    row_group("three_sums", ["A float32 " + ROWS, "B float32 " + ROWS],
+              ["reduce_sum sa = A ; dim=1 keep_dim=false", "reduce_sum sb = B ; dim=1 keep_dim=false",
+               "elementwise_add c = A B ; axis=-1", "reduce_sum sc = c ; dim=1 keep_dim=false"],
+              ["sa float32 64", "sb float32 64", "sc float32 64"]),
+]
+
 VARIANT = {"_s0": (0, 0, "false"), "_s1": (1, 0, "false"), "_s3": (3, 0, "false"), "_s3t": (3, 2, "true"),
            "_s1o": (1, 0, "true"), "_s3o": (3, 0, "true")}
 OUT_T = {"f32": "float", "f16": "__half", "bf16": "__nv_bfloat16", "bool": "uint8_t", "i32": "int32_t",
@@ -268,6 +302,38 @@ def dag_table_lines():
                 continue
             seen[(meta, sig)] = name
             lines.append("STATIC_DAG(%s, %d, %s);" % (name, meta, ", ".join("0x%08xu" % w for w in sig)))
+        return lines, skipped
+    finally:
+        L.cinn_b200_set_option(b"enable_static_chains", 1)
+
+
+def row_table_lines():
+    import cinn_b200
+    L = cinn_b200.lib()
+    cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
+    try:
+        seen, lines, skipped = {}, [], []
+        for name, desc in ROW_GROUPS:
+            try:
+                g = cinn_b200.FusedGroup(desc)
+            except cinn_b200.CinnB200Error as e:
+                skipped.append("%s: %s" % (name, e))
+                continue
+            text = g.launch_text()
+            g.release()
+            launches = [l for l in text.splitlines() if l.startswith("launch ")]
+            if len(launches) != 1 or launches[0].split()[2] != "row_program":
+                skipped.append("%s: not a row program (%s)" % (name, launches[0].split()[2]))
+                continue
+            args = {int(l.split()[1]): int(l.split()[3]) for l in text.splitlines() if l.startswith("arg ") and l.split()[2] == "int"}
+            meta, counts = args[16], args[17]
+            nsteps = sum((counts >> (8 * k)) & 0xff for k in (0, 1, 2, 4, 5, 6))
+            sig = tuple(args[34 + k] & 0xffffffff for k in range(nsteps))
+            if (meta, counts, sig) in seen:
+                skipped.append("%s: same program as %s" % (name, seen[(meta, counts, sig)]))
+                continue
+            seen[(meta, counts, sig)] = name
+            lines.append("STATIC_ROW_PROGRAM(%s, %d, %d, %s);" % (name, meta, counts, ", ".join("0x%08xu" % w for w in sig)))
         return lines, skipped
     finally:
         L.cinn_b200_set_option(b"enable_static_chains", 1)
@@ -339,7 +405,15 @@ def tables():
     dag_header = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_DAG(id, meta word, step words...).\n")
     return [("ew_static_table.inc", HEADER + "\n".join(lines) + "\n", skipped, len(lines)),
             ("chain_reduce_static_table.inc", REDUCE_HEADER + "\n".join(rlines) + "\n", rskipped, len(rlines)),
-            ("ew_dag_static_table.inc", dag_header + "\n".join(dlines) + "\n", dskipped, len(dlines))]
+            ("ew_dag_static_table.inc", dag_header + "\n".join(dlines) + "\n", dskipped, len(dlines)),
+            row_table()]
+
+
+def row_table():
+    lines, skipped = row_table_lines()
+    header = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_ROW_PROGRAM(id, meta word, counts word, step\n"
+              "// words...).\n")
+    return ("row_prog_static_table.inc", header + "\n".join(lines) + "\n", skipped, len(lines))
 
 
 def main():

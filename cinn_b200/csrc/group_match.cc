@@ -20,6 +20,7 @@ namespace cinn_b200 {
 std::unique_ptr<CompiledGroup> MatchGenericChain(const GroupDesc& g, const DeviceInfo& dev, std::string* why);  // chain_match.cc
 std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const DeviceInfo& dev, std::string* why);   // chain_match.cc
 std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& dev, std::string* why);           // chain_match.cc
+std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceInfo& dev, std::string* why);    // chain_match.cc
 
 namespace {
 
@@ -1393,6 +1394,12 @@ struct Matcher {
     return p;
   }
 
+  bool HasReduce() const {
+    for (auto& op : g.ops)
+      if (op.type.rfind("reduce_", 0) == 0) return true;
+    return false;
+  }
+
   std::unique_ptr<CompiledGroup> Run() {
     std::string e;
     std::string expr = CanonicalExpr(g, &e);
@@ -1414,6 +1421,11 @@ struct Matcher {
       // Any other elementwise group with up to four outputs of one shape: a register program.
       std::string why3;
       if (auto p = MatchDag(g, dev, &why3)) return p;
+      // Reductions over the trailing axes with elementwise ops around them, several results: a row program.
+      std::string why4;
+      if (HasReduce())
+        if (auto p = MatchRowProgram(g, dev, &why4)) return p;
+      if (!why4.empty()) why3 += "; as a row program: " + why4;
       Fail("groups with " + std::to_string(g.outputs.size()) + " outputs have no prebuilt kernel (" + expr +
            (why2.empty() ? std::string("") : "; as a chain with a second output: " + why2) +
            "; as a register program: " + why3 + ")");
@@ -1433,6 +1445,17 @@ struct Matcher {
     // A reduction whose operand is an elementwise chain: the chain runs inside the reduction kernel.
     std::string why_reduce;
     if (auto p = MatchChainReduce(g, dev, &why_reduce)) return p;
+    if (HasReduce()) {
+      // Anything else with reductions over the trailing axes: a row program (elementwise ops before, between and
+      // after the reductions, one kernel).
+      std::string why_row;
+      if (auto p = MatchRowProgram(g, dev, &why_row)) return p;
+      if (!why_reduce.empty() || !why_row.empty()) {
+        Fail("no prebuilt sm_100a kernel matches expression " + expr + " (" + why_reduce +
+             (why_row.empty() ? std::string("") : "; as a row program: " + why_row) + ")");
+        return nullptr;
+      }
+    }
     if (!why_reduce.empty()) {
       Fail("no prebuilt sm_100a kernel matches expression " + expr + " (" + why_reduce + ")");
       return nullptr;

@@ -42,7 +42,7 @@ struct StaticChainKey {
   const char* base;
   long long meta;
   int nsteps;
-  uint32_t sig[32];
+  uint32_t sig[40];
 };
 int RegisterStaticChain(const StaticChainKey& key, const char* kernel_name);
 const KernelEntry* FindStaticChain(const char* base, long long meta, int nsteps, const uint32_t* sig);

@@ -205,8 +205,8 @@ template <unsigned long long META, unsigned long long COUNTS, uint32_t... SIG>
 struct StaticRowProgram {
   const long long* steps;
   static constexpr int kN = (int)sizeof...(SIG);
-  static constexpr int count(int pass, bool scalar) { return (int)((COUNTS >> ((scalar ? 32 : 0) + 8 * pass)) & 0xff); }
-  static constexpr int first(int pass, bool scalar) {
+  __host__ __device__ static constexpr int count(int pass, bool scalar) { return (int)((COUNTS >> ((scalar ? 32 : 0) + 8 * pass)) & 0xff); }
+  __host__ __device__ static constexpr int first(int pass, bool scalar) {
     int at = 0;
     for (int k = 0; k < pass; ++k) at += count(k, false) + count(k, true);
     return at + (scalar ? count(pass, false) : 0);
@@ -217,7 +217,7 @@ struct StaticRowProgram {
       if (count(k, false) || count(k, true)) p = k + 1;
     return p;
   }
-  static constexpr uint32_t word(int k) {
+  __host__ __device__ static constexpr uint32_t word(int k) {
     constexpr uint32_t sig[kN > 0 ? kN : 1] = {SIG...};
     return sig[k];
   }

@@ -429,3 +429,64 @@ def bn_grad_apply(shape=(256, 64, 112, 112), seed=4):
         dy = rng.standard_normal(shape, dtype=np.float32)
         return [scale, var, dy, rng.standard_normal(c).astype(np.float32), x, mean, rng.standard_normal(c).astype(np.float32)]
     return Workload("bn_grad_apply", desc, gen, np.float32, shape)
+
+
+# ---- groups that are neither a chain nor a single reduction ---------------------------------------------------------
+
+def row_program(kind, shape=(16384, 4096), seed=12):
+    """Reductions over the last axis with elementwise ops around them, one group (row_prog.cu).  kind: l2_normalise
+    (x / sqrt(sum(x^2))), centre (x - mean(x)), affine_relu (relu(sum(x) * a + c), one value per row), three_sums
+    (sum(A), sum(B), sum(A + B))."""
+    rows, r = shape
+    s = _shape(shape)
+    if kind == "l2_normalise":
+        ins, outs = [f"X float32 {s}"], [("y", "float32", shape)]
+        ops = ["identity xi = X", "elementwise_mul xx = X xi ; axis=-1", "reduce_sum s = xx ; dim=1 keep_dim=true",
+               "sqrt n = s", f"broadcast_to nb = n ; out_shape={s} broadcast_axes=0,1", "divide y = X nb ; axis=-1"]
+    elif kind == "centre":
+        ins, outs = [f"X float32 {s}"], [("y", "float32", shape)]
+        ops = ["reduce_sum s = X ; dim=1 keep_dim=false", f"fill_constant c = ; shape={rows} value={float(r)} dtype=float32",
+               "divide m = s c ; axis=-1", f"broadcast_to mb = m ; out_shape={s} broadcast_axes=0", "subtract y = X mb ; axis=-1"]
+    elif kind == "affine_relu":
+        ins, outs = [f"X float32 {s}", f"a float32 {rows}", f"c float32 {rows}"], [("y", "float32", (rows,))]
+        ops = ["reduce_sum s = X ; dim=1 keep_dim=false", "elementwise_mul t = s a ; axis=-1",
+               "elementwise_add u = t c ; axis=-1", "relu y = u"]
+    elif kind == "three_sums":
+        ins = [f"A float32 {s}", f"B float32 {s}"]
+        outs = [("sa", "float32", (rows,)), ("sb", "float32", (rows,)), ("sc", "float32", (rows,))]
+        ops = ["reduce_sum sa = A ; dim=1 keep_dim=false", "reduce_sum sb = B ; dim=1 keep_dim=false",
+               "elementwise_add c = A B ; axis=-1", "reduce_sum sc = c ; dim=1 keep_dim=false"]
+    else:
+        raise ValueError(kind)
+    desc = (f"group fn_row_{kind}\n" + "".join(f"input {i}\n" for i in ins) + "".join(f"op {o}\n" for o in ops) +
+            "".join(f"output {n} {d} {_shape(sh)}\n" for n, d, sh in outs))
+
+    def gen():
+        rng = np.random.default_rng(seed)
+        return [rng.standard_normal([int(d) for d in i.split()[2].split(",")], dtype=np.float32) for i in ins]
+    return Workload("row_" + kind, desc, gen, np.float32, outs[0][2],
+                    more_outputs=[(np.float32, sh) for _, _, sh in outs[1:]])
+
+
+def dag_program(kind="shared_sum_4out", shape=(8192, 8192), seed=13):
+    """Elementwise groups that are not chains (ew_dag.cu).  shared_sum_4out: g = A + B feeding four sums with C..F (six
+    reads, four writes); bias_relu_mask_3out: x + bias, its relu and the mask of its positive part."""
+    s = _shape(shape)
+    if kind == "shared_sum_4out":
+        ins = [f"{n} float32 {s}" for n in "ABCDEF"]
+        ops = ["elementwise_add g = A B ; axis=-1"] + [f"elementwise_add {o} = g {i} ; axis=-1" for o, i in zip("hijk", "CDEF")]
+        outs = list("hijk")
+    elif kind == "bias_relu_mask_3out":
+        ins = [f"x float32 {s}", f"b float32 {shape[-1]}"]
+        ops = ["elementwise_add pre = x b ; axis=-1", "relu act = pre", f"fill_constant z = ; shape={s} value=0.0 dtype=float32",
+               "greater_than m = pre z ; axis=-1", "cast mf = m ; dtype=float32"]
+        outs = ["pre", "act", "mf"]
+    else:
+        raise ValueError(kind)
+    desc = (f"group fn_dag_{kind}\n" + "".join(f"input {i}\n" for i in ins) + "".join(f"op {o}\n" for o in ops) +
+            "".join(f"output {o} float32 {s}\n" for o in outs))
+
+    def gen():
+        rng = np.random.default_rng(seed)
+        return [rng.standard_normal([int(d) for d in i.split()[2].split(",")], dtype=np.float32) for i in ins]
+    return Workload("dag_" + kind, desc, gen, np.float32, shape, more_outputs=[(np.float32, shape)] * (len(outs) - 1))

@@ -84,7 +84,7 @@ def op_reduce_1(b):  # :168-192
     return [b.add(g, b.add(e, f))]
 
 
-@case(2, 3, "the two reductions run over different axes and each keeps its elementwise consumer outside: an epilogue after a reduce is a kernel of its own here")
+@case(2, 3, "the two reductions run over different axes; each keeps its one elementwise consumer outside (a single reduction with a per-row epilogue stays with the dedicated reduction kernels)")
 def op_reduce_2(b):  # :194-218
     v = inputs(b, A=(W,), B=(W,), C=(H, W), D=(H, W))
     e, f = b.reduce_sum(v["C"], [0]), b.reduce_sum(v["D"], [1])
@@ -231,7 +231,7 @@ def merge_reduce_4(b):  # :435-460 (final count commented out in the reference)
     return [b.add(v["C"], f), b.add(v["D"], f), b.add(v["D"], f)]
 
 
-@case(1, 3, "row reductions of three different tensors are three launches: horizontal fusion here is for reductions that read the same tensor")
+@case(1)
 def merge_reduce_5(b):  # :462-485
     v = inputs(b, A=(128, 128), B=(128, 128))
     c = b.add(v["A"], v["B"])

@@ -1,0 +1,107 @@
+"""Row programs (row_prog.cu): reductions over the trailing axes with elementwise ops before, between and after them,
+one kernel per group, against the op-by-op CPU oracle.  Sums are compared at the reduction tolerance (the kernel folds
+per-thread partials in a tree, the oracle serially); values computed from them inherit it."""
+import numpy as np
+import pytest
+
+import cinn_b200
+from cinn_b200 import common
+from cinn_b200.frontend import Computation, NetBuilder
+from oracle import x86_graph_eval as ge
+from tests.test_gpu_frontend import oracle_program
+
+pytestmark = pytest.mark.gpu
+TARGET = common.DefaultNVGPUTarget()
+F32 = common.Float(32)
+
+
+def l2_normalise(b, rows, r):
+    x = b.create_input(F32, (rows, r), "X")
+    s = b.reduce_sum(b.multiply(x, b.identity(x)), [1], keep_dim=True)
+    return [b.divide(x, b.broadcast_to(b.sqrt(s), [rows, r], [0, 1]))]
+
+
+def centre(b, rows, r):
+    x = b.create_input(F32, (rows, r), "X")
+    m = b.divide(b.reduce_sum(x, [1]), b.fill_constant([rows], float(r)))
+    return [b.subtract(x, b.broadcast_to(m, [rows, r], [0]))]
+
+
+def shifted_exponentials_with_bias(b, rows, r):
+    # three passes: the maximum, the sum of exp(x - max), the result
+    x = b.create_input(F32, (rows, r), "X")
+    g = b.create_input(F32, (r,), "G")
+    mx = b.broadcast_to(b.reduce_max(x, [1]), [rows, r], [0])
+    e = b.exp(b.scale(b.subtract(x, mx), 0.5, 0.0))  # (not the softmax composition, which has its own kernel)
+    s = b.broadcast_to(b.reduce_sum(e, [1]), [rows, r], [0])
+    return [b.add(b.divide(e, s), g)]
+
+
+def three_sums(b, rows, r):
+    a, c = b.create_input(F32, (rows, r), "A"), b.create_input(F32, (rows, r), "B")
+    return [b.reduce_sum(a, [1]), b.reduce_sum(c, [1]), b.reduce_sum(b.add(a, c), [1])]
+
+
+def centred_and_its_variance(b, rows, r):
+    x = b.create_input(F32, (rows, r), "X")
+    n = b.fill_constant([rows], float(r))
+    m = b.divide(b.reduce_sum(x, [1]), n)
+    xc = b.subtract(x, b.broadcast_to(m, [rows, r], [0]))
+    var = b.divide(b.reduce_sum(b.multiply(xc, b.identity(xc)), [1]), n)
+    return [xc, var]
+
+
+def exp_minus_its_maximum(b, rows, r):
+    x = b.create_input(F32, (rows, r), "X")
+    e = b.exp(x)
+    return [b.subtract(e, b.broadcast_to(b.reduce_max(e, [1]), [rows, r], [0]))]
+
+
+PROGRAMS = [l2_normalise, centre, shifted_exponentials_with_bias, three_sums, centred_and_its_variance,
+            exp_minus_its_maximum]
+SHAPES = [(70, 1024), (9, 4096), (33, 1001), (5, 2050), (128, 64)]  # warp / CTA per row, ragged rows, short rows
+
+
+@pytest.mark.parametrize("make", PROGRAMS, ids=lambda f: f.__name__)
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "%dx%d" % s)
+def test_row_program_matches_the_oracle(make, shape):
+    rows, r = shape
+    b = NetBuilder(make.__name__)
+    fetch = make(b, rows, r)
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(f) for f in fetch])
+    assert [p.split()[0] for _, p in comp.groups()] == ["row_program"], [p for _, p in comp.groups()]
+    rng = np.random.default_rng(rows * 7 + r)
+    feeds = {}
+    for t in comp.get_input_tensors():
+        _, shp, _ = t._info()
+        feeds[t.name] = rng.standard_normal(shp).astype(np.float32)
+        t.from_numpy(feeds[t.name], TARGET)
+    comp.execute()
+    want = oracle_program(comp, feeds)
+    for f in fetch:
+        got, ref = comp.get_tensor(str(f)).numpy(TARGET), np.asarray(want[str(f)])
+        assert got.shape == ref.shape
+        scale = max(1.0, float(np.abs(ref).max()))
+        assert np.allclose(got, ref, rtol=2e-5, atol=2e-6 * np.sqrt(r) * scale), \
+            (str(f), float(np.abs(got - ref).max()), [p for _, p in comp.groups()])
+
+
+def test_reduction_with_a_per_row_epilogue_as_one_group():
+    """relu(reduce_sum(x) * a + c): given as ONE group it is one row-program launch (the fusion pass itself leaves such
+    a group to the dedicated reduction kernels unless a specialised row program exists)."""
+    import torch
+    rows, r = 300, 1536
+    desc = ("group fn_row_affine_relu\ninput X float32 %d,%d\ninput a float32 %d\ninput c float32 %d\n"
+            "op reduce_sum s = X ; dim=1 keep_dim=false\nop elementwise_mul t = s a ; axis=-1\n"
+            "op elementwise_add u = t c ; axis=-1\nop relu y = u\noutput y float32 %d\n" % (rows, r, rows, rows, rows))
+    g = cinn_b200.FusedGroup(desc)
+    assert g.pattern == "row_program" and g.launches == 1
+    rng = np.random.default_rng(5)
+    ins = [rng.standard_normal((rows, r)).astype(np.float32), rng.standard_normal(rows).astype(np.float32),
+           rng.standard_normal(rows).astype(np.float32)]
+    out = torch.empty(rows, device="cuda")
+    g.run([torch.from_numpy(a).cuda() for a in ins] + [out])
+    torch.cuda.synchronize()
+    g.release()
+    want = ge.run_all(desc, ins)["y"]
+    assert np.allclose(out.cpu().numpy(), want, rtol=2e-5, atol=1e-4)

@@ -107,3 +107,21 @@ def test_static_chain_reduction_equals_interpreter(name, desc, shape):
         pytest.skip("no specialised kernel at this shape (%s)" % k_s[0])
     for a, b in zip(got_s, got_i):
         assert np.array_equal(a, b), (name, shape, k_s, int((a != b).sum()))
+
+
+@pytest.mark.parametrize("name,desc", GEN.DAG_GROUPS + GEN.ROW_GROUPS, ids=[n for n, _ in GEN.DAG_GROUPS + GEN.ROW_GROUPS])
+@pytest.mark.parametrize("variant", ["table_shape", "other_size"])
+def test_static_register_and_row_programs_equal_their_interpreters(name, desc, variant):
+    """Register programs (several outputs, shared values) and row programs (reductions with elementwise ops around
+    them): the kernel with the program as template arguments against the interpreting kernel, bit for bit (same steps,
+    same accumulation order)."""
+    if variant == "other_size":
+        desc = (desc.replace("64,4096", "37,1028").replace("shape=64 ", "shape=37 ").replace(" 64\n", " 37\n")
+                .replace("value=4096.0", "value=1028.0").replace("64,1024", "61,1028").replace(" 1024\n", " 1028\n"))
+    got_s, k_s = _run(desc, "ps_" + variant, True, seed=17, misalign=0)
+    got_i, k_i = _run(desc, "pi_" + variant, False, seed=17, misalign=0)
+    assert k_i[0] in ("ew_dag", "row_program"), k_i
+    if "_static_" not in k_s[0]:
+        pytest.skip("no specialised kernel for this entry (%s)" % k_s[0])
+    for a, b in zip(got_s, got_i):
+        assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))
