@@ -2090,7 +2090,9 @@ std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceI
     cb.Fail("the row-program kernel is not in the library");
     return nullptr;
   }
-  const int64_t group = r > 1024 ? 256 : 32;
+  // A warp per row while a row's re-reads fit L1 with every warp of the SM on a row of its own (one pass: rows of
+  // up to 16 KiB, read once; more passes: 4 KiB); else a CTA per row.
+  const int64_t group = r > (npass > 1 ? 1024 : 4096) ? 256 : 32;
   st.block[0] = 256;
   st.grid[0]  = (unsigned)std::max<int64_t>(1, group == 32 ? std::min<int64_t>(CeilDiv(rows, 8), (int64_t)dev.sm_count * 16)
                                                             : std::min<int64_t>(rows, (int64_t)dev.sm_count * 8));

@@ -242,13 +242,15 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
 }
 
 // The same with the program fixed at build time (see ew_static.cu for the scheme; the table of these kernels,
-// chain_reduce_static_table.inc, comes from the same generator).
+// chain_reduce_static_table.inc, comes from the same generator).  These kernels evaluate exp / tanh / sigmoid through
+// the hardware's approximate exponential and reciprocal (relative error about 1e-6 per term): a reduction's result is
+// judged at 1e-5 relative, and with the full-precision forms sum(sigmoid(..)) is issue-bound at 0.46 of the HBM peak.
 template <int NS, int NT, unsigned long long META, uint32_t... SIG>
 __global__ void __launch_bounds__(256)
     k_chain_reduce_row_static(CHAIN_PARAMS, long long rows, long long r, long long group) {
   grid_dependency_sync();
   CHAIN_STEPS;
-  const StaticProgram<META, SIG...> prog = {steps};
+  const StaticProgramT<META, true, SIG...> prog = {steps};
   chain_reduce_row_body<NS, NT>(prog, in0, make_sides(prog, p1, p2, p3, mid1, inner1, mid2, inner2, mid3, inner3), out,
                                 vec_ok, rows, r, group);
 }
@@ -257,7 +259,7 @@ __global__ void __launch_bounds__(256)
     k_chain_reduce_col_static(CHAIN_PARAMS, long long outer, long long r, long long inner, long long rows_per_split) {
   grid_dependency_sync();
   CHAIN_STEPS;
-  const StaticProgram<META, SIG...> prog = {steps};
+  const StaticProgramT<META, true, SIG...> prog = {steps};
   chain_reduce_col_body<NS, NT, 4>(prog, in0, make_sides(prog, p1, p2, p3, mid1, inner1, mid2, inner2, mid3, inner3),
                                    out, vec_ok, outer, r, inner, rows_per_split);
 }

@@ -127,8 +127,9 @@ struct DynProgram {
 
 // A program whose structure was fixed when the library was built: META is the kernel's `meta` word, SIG... the low
 // halves of its step words.  Only the immediates (the high halves) are read from the parameters.
-template <unsigned long long META, uint32_t... SIG>
-struct StaticProgram {
+// FAST: see apply_unary (the specialised reductions only).
+template <unsigned long long META, bool FAST, uint32_t... SIG>
+struct StaticProgramT {
   const long long* steps;
   __device__ __forceinline__ constexpr int in_type() const { return (int)((META >> 24) & 15); }
   __device__ __forceinline__ constexpr int out2_type() const { return (int)((META >> 36) & 15); }
@@ -139,9 +140,11 @@ struct StaticProgram {
   template <int VEC, int NS, int NT, bool ST2>
   __device__ __forceinline__ void run(const float (&s1)[VEC], const float (&s2)[VEC], const float (&s3)[VEC],
                                       float (&acc)[VEC], const Store2* st2) const {
-    run_chain_static<VEC, NS, NT, ST2, SIG...>(steps, s1, s2, s3, acc, st2);
+    run_chain_static<VEC, NS, NT, ST2, FAST, SIG...>(steps, s1, s2, s3, acc, st2);
   }
 };
+template <unsigned long long META, uint32_t... SIG>
+using StaticProgram = StaticProgramT<META, false, SIG...>;
 
 }  // namespace
 }  // namespace cinn_b200

@@ -53,16 +53,19 @@ __device__ __noinline__ float heavy_atan2(float a, float b) {
   return b > 0.0f ? at : (a >= 0.0f ? at + pi : at - pi);
 }
 
-template <int VEC>
+// FAST: exp / tanh / sigmoid through the hardware's approximate exponential and reciprocal (relative error about
+// 1e-6).  Only the specialised reductions use it: their result is judged at the reduction tolerance (1e-5 relative),
+// which a sum of such terms keeps with a wide margin, and the full-precision forms make those kernels issue-bound.
+template <int VEC, bool FAST = false>
 __device__ __forceinline__ void apply_unary(int op, float imm, float (&a)[VEC]) {
 #define EW_UNARY_CASE(code, expr) \
   case code:                      \
     _Pragma("unroll") for (int i = 0; i < VEC; ++i) { const float x = a[i]; a[i] = (expr); } \
     break;
   switch (op) {
-    EW_UNARY_CASE(EW_EXP, expf(x))
-    EW_UNARY_CASE(EW_TANH, x86_tanh(x))
-    EW_UNARY_CASE(EW_SIGMOID, x86_sigmoid(x))
+    EW_UNARY_CASE(EW_EXP, FAST ? exp_for_16bit_out(x) : expf(x))
+    EW_UNARY_CASE(EW_TANH, FAST ? x86_tanh_for_16bit_out(x) : x86_tanh(x))
+    EW_UNARY_CASE(EW_SIGMOID, FAST ? __fdividef(1.0f, 1.0f + exp_for_16bit_out(-x)) : x86_sigmoid(x))
     EW_UNARY_CASE(EW_RSQRT, x86_rsqrt(x))
     EW_UNARY_CASE(EW_SQRT, sqrtf(x))
     EW_UNARY_CASE(EW_RELU, x86_max(x, 0.0f))
@@ -245,10 +248,12 @@ __device__ __forceinline__ long long side_index(long long i, long long inner, lo
   return (i / inner) % mid;
 }
 
+// stream: a full-size operand is read once (evict-first); false when the same threads read it again shortly after
+// (the later passes of a row program), so that it stays in L1.
 template <int VEC>
-__device__ __forceinline__ void load_side(const SideSpec& s, long long i0, float (&f)[VEC]) {
+__device__ __forceinline__ void load_side(const SideSpec& s, long long i0, float (&f)[VEC], bool stream = true) {
   if (VEC == 4 && s.mode == EW_SIDE_FULL) {
-    load_vec4(s.ptr, s.dtype, i0, true, *reinterpret_cast<float(*)[4]>(&f[0]));
+    load_vec4(s.ptr, s.dtype, i0, stream, *reinterpret_cast<float(*)[4]>(&f[0]));
   } else if (VEC == 4 && s.mode == EW_SIDE_PERIODIC_VEC) {
     load_vec4(s.ptr, s.dtype, side_index(i0, 1, s.mid), false, *reinterpret_cast<float(*)[4]>(&f[0]));
   } else if (s.mode == EW_SIDE_ONE_PER_VEC || s.mode == EW_SIDE_SCALAR) {
@@ -338,14 +343,14 @@ __device__ __forceinline__ void pick_operand(int sel, float imm, const float (&s
 // specialised at build time call it with constants, so that both execute the same arithmetic by construction.
 // NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees.
 // ST2: the program may hold EW_STORE2 steps (st2 then says where they write).
-template <int VEC, int NS, int NT, bool ST2>
+template <int VEC, int NS, int NT, bool ST2, bool FAST = false>
 __device__ __forceinline__ bool chain_step(int op, int asel, int bsel, int role, float imm, float imm2,
                                            const float (&s1)[VEC], const float (&s2)[VEC], const float (&s3)[VEC],
                                            float (&acc)[VEC], float (&ta)[NT > 0 ? VEC : 1],
                                            float (&tb)[NT > 0 ? VEC : 1], const Store2* st2) {
   if (op == EW_NOP) return false;
   if (op >= EW_FIRST_UNARY) {
-    apply_unary<VEC>(op, imm, acc);
+    apply_unary<VEC, FAST>(op, imm, acc);
     return false;
   }
   if (ST2 && op == EW_STORE2) {
@@ -421,7 +426,7 @@ __device__ __forceinline__ void run_chain(const long long* steps, int nsteps, co
 
 // The same program with its words' low halves (op, selectors, role) known at build time: SIG... are those 32-bit
 // halves, the immediates still come from the kernel's parameters.  Every branch of chain_step folds away.
-template <int VEC, int NS, int NT, bool ST2, int K, uint32_t... SIG>
+template <int VEC, int NS, int NT, bool ST2, bool FAST, int K, uint32_t... SIG>
 __device__ __forceinline__ void run_chain_static_from(const long long* steps, const float (&s1)[VEC],
                                                       const float (&s2)[VEC], const float (&s3)[VEC],
                                                       float (&acc)[VEC], float (&ta)[NT > 0 ? VEC : 1],
@@ -436,11 +441,11 @@ __device__ __forceinline__ void run_chain_static_from(const long long* steps, co
     constexpr bool two = ((op == EW_FMA || op == EW_SELECT) && bsel == 0) || op == EW_SCALE_PRE;
     const float imm  = __uint_as_float((uint32_t)(steps[K] >> 32));
     const float imm2 = __uint_as_float((uint32_t)(steps[K + 1 < EW_MAX_STEPS ? K + 1 : K] >> 32));
-    (void)chain_step<VEC, NS, NT, ST2>(op, asel, bsel, role, imm, imm2, s1, s2, s3, acc, ta, tb, st2);
-    run_chain_static_from<VEC, NS, NT, ST2, K + (two ? 2 : 1), SIG...>(steps, s1, s2, s3, acc, ta, tb, st2);
+    (void)chain_step<VEC, NS, NT, ST2, FAST>(op, asel, bsel, role, imm, imm2, s1, s2, s3, acc, ta, tb, st2);
+    run_chain_static_from<VEC, NS, NT, ST2, FAST, K + (two ? 2 : 1), SIG...>(steps, s1, s2, s3, acc, ta, tb, st2);
   }
 }
-template <int VEC, int NS, int NT, bool ST2, uint32_t... SIG>
+template <int VEC, int NS, int NT, bool ST2, bool FAST, uint32_t... SIG>
 __device__ __forceinline__ void run_chain_static(const long long* steps, const float (&s1)[VEC],
                                                  const float (&s2)[VEC], const float (&s3)[VEC], float (&acc)[VEC],
                                                  const Store2* st2 = nullptr) {
@@ -449,7 +454,7 @@ __device__ __forceinline__ void run_chain_static(const long long* steps, const f
 #pragma unroll
     for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0.0f;
   }
-  run_chain_static_from<VEC, NS, NT, ST2, 0, SIG...>(steps, s1, s2, s3, acc, ta, tb, st2);
+  run_chain_static_from<VEC, NS, NT, ST2, FAST, 0, SIG...>(steps, s1, s2, s3, acc, ta, tb, st2);
 }
 }  // namespace
 }  // namespace cinn_b200

@@ -509,6 +509,15 @@ struct FusionState {
     }
     g.pattern = plan->pattern;
     for (auto& s : plan->steps) g.kernels.push_back(s.kernel->name);
+    if ((g.pattern == "row_program" && g.kernels[0] == "row_program") || (g.pattern == "ew_dag" && g.kernels[0] == "ew_dag")) {
+      // Measured on B200: the interpreting register-program kernel runs at 0.3 of the HBM peak and the interpreting
+      // row-program kernel at 0.1, their specialised forms at 0.9 and 0.55-0.87.  A region that only an interpreter
+      // takes is therefore split into groups for the chain and reduction kernels unless the caller asks otherwise.
+      if (!dev.fuse_interpreted_programs) {
+        if (why) *why = "only the interpreting program kernel takes this group";
+        return false;
+      }
+    }
     if (g.pattern == "row_program" && g.kernels[0] == "row_program") {
       // The interpreting row-program kernel is worth a group of its own only where it saves a pass over a full-size
       // tensor or a launch per reduction: a per-element result that depends on a reduction (x / ||x||), or several
@@ -851,6 +860,35 @@ bool FusePasses(const NetBuilder& b, const std::vector<int>& fetch_in, const Dev
     for (size_t i = 0; i < sets.size(); ++i) {
       if (sets[i].empty() || !is_reduce_group(sets[i])) continue;
       FusedGroupInfo gi = st.Describe(sets[i]);
+      // All the reduction groups that share an input with this one and are independent of it, at once (the merged
+      // group may have a kernel where a pair on the way to it has none), then one by one.
+      {
+        std::vector<size_t> cands;
+        for (size_t j = i + 1; j < sets.size(); ++j) {
+          if (sets[j].empty() || !is_reduce_group(sets[j])) continue;
+          const FusedGroupInfo gj = st.Describe(sets[j]);
+          bool shared = false, dependent = false;
+          for (int v : gj.input_vars) {
+            shared = shared || std::find(gi.input_vars.begin(), gi.input_vars.end(), v) != gi.input_vars.end();
+            dependent = dependent || std::find(gi.output_vars.begin(), gi.output_vars.end(), v) != gi.output_vars.end();
+          }
+          for (int v : gi.input_vars)
+            dependent = dependent || std::find(gj.output_vars.begin(), gj.output_vars.end(), v) != gj.output_vars.end();
+          if (shared && !dependent) cands.push_back(j);
+        }
+        if (cands.size() >= 2) {
+          std::set<int> merged = sets[i];
+          for (size_t j : cands) merged.insert(sets[j].begin(), sets[j].end());
+          if (st.Compiles(merged, nullptr, nullptr)) {
+            for (size_t j : cands) {
+              for (int k : sets[j]) group_of[k] = (int)i;
+              sets[j].clear();
+            }
+            sets[i] = merged;
+            gi      = st.Describe(sets[i]);
+          }
+        }
+      }
       for (size_t j = i + 1; j < sets.size(); ++j) {
         if (sets[j].empty() || !is_reduce_group(sets[j])) continue;
         const FusedGroupInfo gj = st.Describe(sets[j]);

@@ -241,10 +241,77 @@ ROW_GROUPS = [
                "broadcast_to sb = s ; out_shape=%s broadcast_axes=0" % ROWS, "divide p = e sb ; axis=-1",
                "scale y = p ; scale=2.0 bias=0.0 bias_after_scale=true"], ["y float32 " + ROWS]),
     row_group("three_sums", ["A float32 " + ROWS, "B float32 " + ROWS],
-              ["reduce_sum sa = A ; dim=1 keep_dim=false", "reduce_sum sb = B ; dim=1 keep_dim=false",
-               "elementwise_add c = A B ; axis=-1", "reduce_sum sc = c ; dim=1 keep_dim=false"],
+              ["elementwise_add c = A B ; axis=-1", "reduce_sum sa = A ; dim=1 keep_dim=false",
+               "reduce_sum sb = B ; dim=1 keep_dim=false", "reduce_sum sc = c ; dim=1 keep_dim=false"],
               ["sa float32 64", "sb float32 64", "sc float32 64"]),
 ]
+
+def builder_programs():
+    """Small NetBuilder programs whose register-program groups get kernels too: the shared-value graphs of the
+    reference's fusion tests (cinn/hlir/pass/fusion_merge_pass_test.cc:47-71, 131-158, 182-205;
+    op_fusion_pass_test.cc:95-119) that no entry above already equals.  The group descriptions are the fusion pass's
+    own, so the programs match what a user's graph of that form compiles to."""
+    from cinn_b200 import common
+    from cinn_b200.frontend import NetBuilder
+
+    def ins(b, **shapes):
+        return {k: b.create_input(common.Float(32), v, k) for k, v in shapes.items()}
+    H, W = 32, 32
+
+    def twice_the_same_sum(b):
+        v = ins(b, A=(H, W), B=(H, W), C=(H, W), D=(H, W))
+        e, f = b.add(v["A"], v["B"]), b.add(v["C"], v["D"])
+        return [b.add(e, f), b.add(e, f)]
+
+    def two_levels_of_sharing(b):
+        v = ins(b, A=(H, W), B=(H, W), C=(H, W), D=(H, W), E=(H, W), F=(H, W))
+        g = b.add(v["A"], v["B"])
+        i = b.add(g, v["D"])
+        return [b.add(g, v["C"]), b.add(i, v["E"]), b.add(i, v["F"])]
+
+    def vector_sum_into_matrix_sum(b):
+        v = ins(b, A=(W,), B=(W,), C=(H, W), D=(H, W))
+        return [b.add(b.add(v["C"], v["D"]), b.add(v["A"], v["B"]))]
+
+    def column_vector_sum_then_two_more(b):
+        v = ins(b, A=(W,), B=(W,), C=(H, W), D=(H, W))
+        e, f = b.add(v["A"], v["B"]), b.add(v["C"], v["D"])
+        return [b.add(b.add(b.add(f, e, axis=0), v["C"]), v["D"])]
+
+    def vector_sum_recomputed_in_two_shapes(b):  # fusion_merge_pass_test.cc:257-280: E = A + B joins both consumers
+        v = ins(b, A=(W,), B=(W,), C=(H * W, W), D=(H, W))
+        e = b.add(v["A"], v["B"])
+        return [b.add(v["C"], e), b.add(v["D"], e)]
+
+    return [twice_the_same_sum, two_levels_of_sharing, vector_sum_into_matrix_sum, column_vector_sum_then_two_more,
+            vector_sum_recomputed_in_two_shapes]
+
+
+def builder_dag_groups():
+    import cinn_b200
+    from cinn_b200.frontend import Computation, NetBuilder
+    L = cinn_b200.lib()
+    L.cinn_b200_set_option(b"fuse_interpreted_programs", 1)
+    L.cinn_b200_set_option(b"enable_static_chains", 0)
+    out = []
+    try:
+        for make in builder_programs():
+            b = NetBuilder(make.__name__)
+            fetch = make(b)
+            comp = Computation.build_and_compile(None, b, fetch=[str(f) for f in fetch], plan_only=True)
+            k = 0
+            for desc, pattern in comp.groups():
+                if pattern.split()[0] == "ew_dag":
+                    lines = desc.splitlines()
+                    name = make.__name__ + ("_%d" % k if k else "")
+                    k += 1
+                    lines[0] = "group fn_static_" + name
+                    out.append((name, "\n".join(lines) + "\n"))
+    finally:
+        L.cinn_b200_set_option(b"fuse_interpreted_programs", 0)
+        L.cinn_b200_set_option(b"enable_static_chains", 1)
+    return out
+
 
 VARIANT = {"_s0": (0, 0, "false"), "_s1": (1, 0, "false"), "_s3": (3, 0, "false"), "_s3t": (3, 2, "true"),
            "_s1o": (1, 0, "true"), "_s3o": (3, 0, "true")}
@@ -282,7 +349,8 @@ def dag_table_lines():
     cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
     try:
         seen, lines, skipped = {}, [], []
-        for name, desc in DAG_GROUPS:
+        for name, desc in DAG_GROUPS + builder_dag_groups():
+            cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
             try:
                 g = cinn_b200.FusedGroup(desc)
             except cinn_b200.CinnB200Error as e:

@@ -102,6 +102,9 @@ struct DeviceInfo {
   int ew_stream_ctas_per_sm = 0;
   int rownorm_rows_per_iter = 0;  // rows a CTA of the register-resident kernels takes per iteration
   int rownorm_simple        = -1;  // plain softmax by the one-CTA-per-row kernel of softmax_safe.cu: 1 on, 0 off, -1 automatic
+  int fuse_interpreted_programs = 0;  // the fusion pass also forms groups that only the INTERPRETING register / row
+                                      // program kernels take (several times slower than the specialised kernels; off:
+                                      // such regions are split into groups the chain and reduction kernels take)
   int enable_static_chains  = 1;   // chain programs with a kernel specialised at build time use it (0: always interpret)
   int enable_tma_rownorm    = -1;  // rows streamed through shared memory by bulk copies: 1 on, 0 off, -1 automatic
 };

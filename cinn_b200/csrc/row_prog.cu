@@ -65,13 +65,13 @@ template <int VEC>
 __device__ __forceinline__ bool rp_element_step(unsigned w, float imm, float imm2, unsigned long long meta,
                                                 const RowInputs& in, const RowOutputs& out, long long i0,
                                                 float (&regs)[DAG_REGS][VEC], const float (&sregs)[ROWP_SREGS],
-                                                float (&acc)[ROWP_SREGS]) {
+                                                float (&acc)[ROWP_SREGS], bool reread) {
   const int op = (int)(w & 0xff), dst = (int)((w >> 8) & 15), a = (int)((w >> 12) & 31), b = (int)((w >> 17) & 31),
             c = (int)((w >> 22) & 31);
   if (op == EW_NOP) return false;
   if (op == DAG_LOAD) {
     const SideSpec s = {in.ptr[a], (int)((meta >> (6 * a)) & 7), (int)((meta >> (6 * a + 3)) & 7), in.mid[a], in.inner[a]};
-    load_side<VEC>(s, i0, regs[dst]);
+    load_side<VEC>(s, i0, regs[dst], !reread);  // a row that a later pass reads again stays in L1
     return false;
   }
   if (op == DAG_STORE) {
@@ -191,7 +191,7 @@ struct DynRowProgram {
     float regs[DAG_REGS][VEC];
     const int b = first_step(pass, false), e = b + (int)((counts >> (8 * pass)) & 0xff);
     for (int k = b; k < e; ++k)
-      if (rp_element_step<VEC>((unsigned)steps[k], rp_imm(steps[k]), rp_imm(steps[k + 1]), meta, in, out, i0, regs, sregs, acc)) ++k;
+      if (rp_element_step<VEC>((unsigned)steps[k], rp_imm(steps[k]), rp_imm(steps[k + 1]), meta, in, out, i0, regs, sregs, acc, pass + 1 < passes())) ++k;
   }
   __device__ __forceinline__ void run_scalar(int pass, const RowInputs& in, const RowOutputs& out, long long row,
                                              bool writer, float (&sregs)[ROWP_SREGS]) const {
@@ -211,7 +211,7 @@ struct StaticRowProgram {
     for (int k = 0; k < pass; ++k) at += count(k, false) + count(k, true);
     return at + (scalar ? count(pass, false) : 0);
   }
-  __device__ __forceinline__ constexpr int passes() const {
+  __host__ __device__ constexpr int passes() const {
     int p = 0;
     for (int k = 0; k < ROWP_MAX_PASSES; ++k)
       if (count(k, false) || count(k, true)) p = k + 1;
@@ -236,7 +236,7 @@ struct StaticRowProgram {
       }
     }
   }
-  template <int VEC, int K, int END>
+  template <int VEC, int K, int END, bool REREAD>
   __device__ __forceinline__ void element_from(const RowInputs& in, const RowOutputs& out, long long i0,
                                                float (&regs)[DAG_REGS][VEC], const float (&sregs)[ROWP_SREGS],
                                                float (&acc)[ROWP_SREGS]) const {
@@ -246,8 +246,8 @@ struct StaticRowProgram {
       constexpr bool two = op != EW_NOP && op != DAG_LOAD && op != DAG_STORE && op != ROWP_ACC &&
                            (a == DAG_IMM2 || b == DAG_IMM2 || c == DAG_IMM2 || op == EW_SCALE_PRE);
       (void)rp_element_step<VEC>(w, rp_imm(steps[K]), rp_imm(steps[K + 1 < ROWP_MAX_STEPS ? K + 1 : K]), META, in, out, i0,
-                                 regs, sregs, acc);
-      element_from<VEC, K + (two ? 2 : 1), END>(in, out, i0, regs, sregs, acc);
+                                 regs, sregs, acc, REREAD);
+      element_from<VEC, K + (two ? 2 : 1), END, REREAD>(in, out, i0, regs, sregs, acc);
     }
   }
   template <int K, int END>
@@ -266,9 +266,10 @@ struct StaticRowProgram {
   __device__ __forceinline__ void run_element(int pass, const RowInputs& in, const RowOutputs& out, long long i0,
                                               const float (&sregs)[ROWP_SREGS], float (&acc)[ROWP_SREGS]) const {
     float regs[DAG_REGS][VEC];
-    if (pass == 0) element_from<VEC, first(0, false), first(0, false) + count(0, false)>(in, out, i0, regs, sregs, acc);
-    else if (pass == 1) element_from<VEC, first(1, false), first(1, false) + count(1, false)>(in, out, i0, regs, sregs, acc);
-    else element_from<VEC, first(2, false), first(2, false) + count(2, false)>(in, out, i0, regs, sregs, acc);
+    constexpr int np = StaticRowProgram().passes();
+    if (pass == 0) element_from<VEC, first(0, false), first(0, false) + count(0, false), (np > 1)>(in, out, i0, regs, sregs, acc);
+    else if (pass == 1) element_from<VEC, first(1, false), first(1, false) + count(1, false), (np > 2)>(in, out, i0, regs, sregs, acc);
+    else element_from<VEC, first(2, false), first(2, false) + count(2, false), false>(in, out, i0, regs, sregs, acc);
   }
   __device__ __forceinline__ void run_scalar(int pass, const RowInputs& in, const RowOutputs& out, long long row,
                                              bool writer, float (&sregs)[ROWP_SREGS]) const {
@@ -304,6 +305,7 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
       long long done = 0;
       if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary
         const long long nv = r >> 2;
+#pragma unroll 2
         for (long long v = t; v < nv; v += nt) prog.template run_element<4>(pass, in, out, base + (v << 2), sregs, acc);
         done = nv << 2;
       }

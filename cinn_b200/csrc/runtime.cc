@@ -99,6 +99,7 @@ static int g_opt_sm_count = 0;  // 0: query the device, or 148 without one
 static int g_opt_rownorm_rows = 0;
 static int g_opt_ew_stream = 1, g_opt_ew_stream_stages = 0, g_opt_ew_stream_ctas = 0;
 static int g_opt_static_chains = 1;
+static int g_opt_fuse_interpreted = 0;
 static int g_opt_pdl = 1;  // programmatic dependent launch for the kernels that support it
 static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1, g_opt_rownorm_simple = -1;
 
@@ -133,6 +134,7 @@ DeviceInfo CurrentDeviceInfo() {
   d.enable_tma_rownorm = g_opt_enable_tma_rownorm;
   d.rownorm_simple     = g_opt_rownorm_simple;
   d.enable_static_chains = g_opt_static_chains;
+  d.fuse_interpreted_programs = g_opt_fuse_interpreted;
   if (g_opt_sm_count > 0) {
     d.sm_count = g_opt_sm_count;
     return d;
@@ -852,6 +854,10 @@ int cinn_b200_set_option(const char* key, long long value) {
   }
   if (!strcmp(key, "enable_pdl")) {
     g_opt_pdl = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "fuse_interpreted_programs")) {
+    g_opt_fuse_interpreted = (int)value;
     return CINN_B200_OK;
   }
   if (!strcmp(key, "enable_static_chains")) {

@@ -454,8 +454,8 @@ def row_program(kind, shape=(16384, 4096), seed=12):
     elif kind == "three_sums":
         ins = [f"A float32 {s}", f"B float32 {s}"]
         outs = [("sa", "float32", (rows,)), ("sb", "float32", (rows,)), ("sc", "float32", (rows,))]
-        ops = ["reduce_sum sa = A ; dim=1 keep_dim=false", "reduce_sum sb = B ; dim=1 keep_dim=false",
-               "elementwise_add c = A B ; axis=-1", "reduce_sum sc = c ; dim=1 keep_dim=false"]
+        ops = ["elementwise_add c = A B ; axis=-1", "reduce_sum sa = A ; dim=1 keep_dim=false",
+               "reduce_sum sb = B ; dim=1 keep_dim=false", "reduce_sum sc = c ; dim=1 keep_dim=false"]
     else:
         raise ValueError(kind)
     desc = (f"group fn_row_{kind}\n" + "".join(f"input {i}\n" for i in ins) + "".join(f"op {o}\n" for o in ops) +

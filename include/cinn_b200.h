@@ -302,6 +302,10 @@ int cinn_b200_device_status(unsigned int* async_wait_timeouts);
  * kernels that wait for their predecessor on the device are launched with programmatic stream serialisation, which
  * hides the launch latency between consecutive kernels of a stream; "enable_static_chains" (default 1): elementwise
  * chains whose program has a kernel specialised at build time use it instead of the interpreting kernel;
+ * "fuse_interpreted_programs" (default 0): the fusion pass also forms groups that only the interpreting register-program
+ * or row-program kernel takes (one launch, but several times slower per byte than the specialised kernels; off, such
+ * regions are split into groups the chain and reduction kernels take; a group handed to cinn_b200_compile_group
+ * directly is always accepted);
  * "enable_ew_stream" (default 1),
  * "ew_stream_stages", "ew_stream_ctas_per_sm": whether large elementwise groups with 16-bit outputs stream their
  * input through shared-memory rings filled by bulk copies, the ring depth and the resident CTAs per SM; "rownorm_rows_per_iter": rows per CTA

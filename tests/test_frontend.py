@@ -339,10 +339,16 @@ def test_expression_trees_compile_into_one_kernel_with_temporaries():
     D = [b.create_input(common.Float(64), (64, 1024), n) for n in "ABCD"]
     b.multiply(b.add(D[0], D[1]), b.subtract(D[2], D[3]))
     assert [p for _, p in plan(b).groups()] == ["ew_chain ew_chain_f64_f64_s3t"]
-    # three joins need three temporaries: no chain any more, but still one kernel, as a register program
+    # three joins need three temporaries: no chain any more.  The fusion pass splits the region (only the
+    # interpreting register-program kernel would take it whole); asked to, it keeps it as one register program
     b, (A, B, C, D) = build()
     b.add(b.multiply(b.exp(A), b.tanh(B)), b.multiply(b.sqrt(b.abs(C)), b.sigmoid(D)))
-    assert [p for _, p in plan(b).groups()] == ["ew_dag ew_dag"]
+    assert len(plan(b).groups()) > 1
+    cinn_b200.lib().cinn_b200_set_option(b"fuse_interpreted_programs", 1)
+    try:
+        assert [p for _, p in plan(b).groups()] == ["ew_dag ew_dag"]
+    finally:
+        cinn_b200.lib().cinn_b200_set_option(b"fuse_interpreted_programs", 0)
     # what no elementwise kernel takes is still split: nine tensors read at once
     b = NetBuilder("wide")
     xs = [b.create_input(common.Float(32), (64, 1024), "X%d" % i) for i in range(9)]
@@ -397,8 +403,14 @@ def test_two_output_groups_and_no_group_cycles():
     b.subtract(e, b.broadcast_to(m, [64, 1024], [0]))
     c = plan(b)
     _assert_topological(c, ["X"])
-    # so the three instructions are one group: a row program (exp is evaluated again in the pass after the maximum)
-    assert [p for _, p in c.groups()] == ["row_program row_program"]
+    assert len(c.groups()) >= 2
+    # ... unless the three instructions are one group: a row program (exp is evaluated again in the pass after the
+    # maximum), which the fusion pass forms when asked to use the interpreting kernel
+    cinn_b200.lib().cinn_b200_set_option(b"fuse_interpreted_programs", 1)
+    try:
+        assert [p for _, p in plan(b).groups()] == ["row_program row_program"]
+    finally:
+        cinn_b200.lib().cinn_b200_set_option(b"fuse_interpreted_programs", 0)
 
 
 def test_export_and_load_keep_two_output_and_tree_groups():

@@ -12,6 +12,17 @@ from tests.test_fusion_reference_cases import CASES, build, inputs
 from tests.test_gpu_frontend import oracle_program
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True, scope="module")
+def fuse_interpreted_programs():
+    """These tests are about the register-program and row-program kernels themselves, interpreting forms included, so
+    the fusion pass is asked to form their groups even where only the interpreting kernel takes them."""
+    import cinn_b200
+    L = cinn_b200.lib()
+    L.cinn_b200_set_option(b"fuse_interpreted_programs", 1)
+    yield
+    L.cinn_b200_set_option(b"fuse_interpreted_programs", 0)
 TARGET = common.DefaultNVGPUTarget()
 
 

@@ -241,3 +241,40 @@ def test_graph_evaluator_reproduces_llvm_builds_of_the_decomposed_groups(oracle)
     comp = Computation.build_and_compile(common.DefaultNVGPUTarget(), b, plan_only=True)
     (desc, pattern), = comp.groups()
     assert same(ge.run(desc, [d["gelu_x"]]), d["gelu_y"])
+
+
+def test_every_op_of_the_registry_reproduces_its_llvm_build(oracle):
+    """tests/golden/llvm_x86_vectors_ops.npz (made by make_llvm_x86_vectors_ops.py): every unary and binary elementwise
+    op, float32 and float64, as LLVM -O3 compiles the IR the reference's x86 path emits for it (intrinsics, libm calls,
+    compare + select, the two-branch tanh, 1 / sqrt, ...), on inputs that include signed zeros, infinities, NaN,
+    denormals and domain edges; plus the integer ops of the int32 chains.  The C oracle (and, for int32, the graph
+    evaluator) must give exactly those bits, NaN payloads aside (a NaN must be a NaN)."""
+    import os
+    from oracle import x86_graph_eval as ge
+    d = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "llvm_x86_vectors_ops.npz"))
+
+    def same(got, want, what):
+        assert got.dtype == want.dtype and got.shape == want.shape, what
+        nan_g, nan_w = np.isnan(got), np.isnan(want)
+        assert np.array_equal(nan_g, nan_w), (what, "NaN positions differ")
+        ok = np.array_equal(got[~nan_g].view(np.uint8), want[~nan_w].view(np.uint8))
+        if not ok:
+            bad = np.flatnonzero((got != want) & ~nan_g)
+            raise AssertionError((what, int(bad.size), got[bad[:4]], want[bad[:4]]))
+
+    unary_names = sorted(k[2:-4] for k in d.files if k.startswith("u_") and k.endswith("_f32"))
+    binary_names = sorted(k[2:-4] for k in d.files if k.startswith("b_") and k.endswith("_f32"))
+    assert len(unary_names) >= 34 and len(binary_names) >= 18
+    with np.errstate(all="ignore"):
+        for op in unary_names:
+            same(oracle.unary(op, d["x_f32"]), d["u_%s_f32" % op], op + " f32")
+            same(oracle.unary_f64(op, d["x_f64"]), d["u_%s_f64" % op], op + " f64")
+        for op in binary_names:
+            same(oracle.binary(op, d["x_f32"], d["w_f32"]), d["b_%s_f32" % op], op + " f32")
+            same(oracle.binary_f64(op, d["x_f64"], d["w_f64"]), d["b_%s_f64" % op], op + " f64")
+    n = d["x_i32"].size
+    for key in [k for k in d.files if k.startswith("i_")]:
+        op = key[2:-4]
+        desc = ("group fn_i\ninput a int32 %d\ninput b int32 %d\nop %s y = a b ; axis=-1\noutput y int32 %d\n" % (n, n, op, n))
+        got = ge.run(desc, [d["x_i32"], d["w_i32"]])
+        assert got.dtype == np.int32 and np.array_equal(got, d[key]), op
