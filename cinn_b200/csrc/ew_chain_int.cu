@@ -168,76 +168,122 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, T (&f
   }
 }
 
+// ONE step of an integer chain program on VEC values (the fields of the step's word decoded by the caller: at run
+// time by the interpreter, as constants by the kernels specialised at build time).  Returns true when the step used
+// the next word's immediate.
 // NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
 // NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees, as in the float form.
-template <typename T, int VEC, int NS, int NT = 0>
-__device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const T (&s1)[VEC], const T (&s2)[VEC],
-                                          const T (&s3)[VEC], T (&acc)[VEC]) {
-  T ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
-  if (NT > 0) {
+template <typename T, int VEC, int NS, int NT>
+__device__ __forceinline__ bool int_chain_step(int op, int asel, int bsel, int role, T imm, T imm2, const T (&s1)[VEC],
+                                               const T (&s2)[VEC], const T (&s3)[VEC], T (&acc)[VEC],
+                                               T (&ta)[NT > 0 ? VEC : 1], T (&tb)[NT > 0 ? VEC : 1]) {
+  if (op == EW_NOP) return false;
+  if (op >= EW_FIRST_UNARY) {
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0;
+    for (int i = 0; i < VEC; ++i) acc[i] = int_unary<T>(op, acc[i]);
+    return false;
   }
-  for (int k = 0; k < nsteps; ++k) {
-    const long long st = steps[k];
-    const int op       = (int)(st & 0xff);
-    const int asel     = (int)((st >> 8) & 0xff);
-    const int bsel     = (int)((st >> 16) & 0xff);
-    const int role     = (int)((st >> 24) & 3);
-    const T imm        = (T)(int32_t)(st >> 32);
-    if (op == EW_NOP) continue;
-    if (op >= EW_FIRST_UNARY) {
+  if (NT > 0 && op == EW_STASH) {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] = int_unary<T>(op, acc[i]);
-      continue;
-    }
-    if (NT > 0 && op == EW_STASH) {
+    for (int i = 0; i < VEC; ++i) (asel == 5 ? ta : tb)[NT > 0 ? i : 0] = acc[i];
+    return false;
+  }
+  T o[VEC];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) (asel == 5 ? ta : tb)[NT > 0 ? i : 0] = acc[i];
-      continue;
-    }
-    T o[VEC];
+  for (int i = 0; i < VEC; ++i) {
+    o[i] = (NS >= 1 && asel == 1) ? s1[i] : ((NS >= 2 && asel == 2) ? s2[i] : ((NS >= 3 && asel == 3) ? s3[i] : (asel == 4 ? acc[i] : imm)));
+    if (NT > 0) o[i] = asel == 5 ? ta[NT > 0 ? i : 0] : (asel == 6 ? tb[NT > 0 ? i : 0] : o[i]);
+  }
+  if (op == EW_SELECT) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
-      o[i] = (NS >= 1 && asel == 1) ? s1[i] : ((NS >= 2 && asel == 2) ? s2[i] : ((NS >= 3 && asel == 3) ? s3[i] : (asel == 4 ? acc[i] : imm)));
-      if (NT > 0) o[i] = asel == 5 ? ta[NT > 0 ? i : 0] : (asel == 6 ? tb[NT > 0 ? i : 0] : o[i]);
+      T b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+      if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
+      const T c = role == 0 ? acc[i] : o[i];
+      const T t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
+      const T f = role == 2 ? acc[i] : b;
+      acc[i]    = c != 0 ? t : f;
     }
-    if (op == EW_SELECT) {
-      const T imm2 = (T)(int32_t)(steps[k + 1] >> 32);
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        T b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
-        if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
-        const T c = role == 0 ? acc[i] : o[i];
-        const T t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
-        const T f = role == 2 ? acc[i] : b;
-        acc[i]    = c != 0 ? t : f;
-      }
-      if (bsel == 0) ++k;
-    } else {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i)
-        acc[i] = (role != 0 && op != EW_COPY) ? int_binary<T>(op, o[i], acc[i]) : int_binary<T>(op, acc[i], o[i]);
-    }
+    return bsel == 0;
   }
+#pragma unroll
+  for (int i = 0; i < VEC; ++i)
+    acc[i] = (role != 0 && op != EW_COPY) ? int_binary<T>(op, o[i], acc[i]) : int_binary<T>(op, acc[i], o[i]);
+  return false;
 }
 
-// Same parameter list as the float form (k_ew_chain): meta bits 0-3 / 4-7 dtype / mode of side 1, 8-15 side 2,
-// 16-23 side 3, 24-27 dtype of in0.
-template <typename T, typename OutT, int NS, int NT = 0>
-__global__ void __launch_bounds__(256)
-    k_ew_chain_int(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
-                   const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
-                   long long mid1, long long inner1, long long mid2, long long inner2, long long mid3,
-                   long long inner3, long long nsteps_ll, long long t0, long long t1, long long t2, long long t3,
-                   long long t4, long long t5, long long t6, long long t7, long long t8, long long t9, long long t10,
-                   long long t11, long long t12, long long t13, long long t14, long long t15) {
-  const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
-  const int nsteps  = (int)nsteps_ll;
-  const int in_type = (int)((meta >> 24) & 15);
-  const SideSpec sd1 = {p1, (int)(meta & 15), (int)((meta >> 4) & 15), mid1, inner1};
-  const SideSpec sd2 = {p2, (int)((meta >> 8) & 15), (int)((meta >> 12) & 15), mid2, inner2};
-  const SideSpec sd3 = {p3, (int)((meta >> 16) & 15), (int)((meta >> 20) & 15), mid3, inner3};
+template <typename T>
+__device__ __forceinline__ T int_imm(long long word) { return (T)(int32_t)(word >> 32); }
+
+// The interpreter's program: everything comes from kernel parameters.
+template <typename T>
+struct DynIntProgram {
+  const long long* steps;
+  int nsteps;
+  long long meta;
+  __device__ __forceinline__ int in_type() const { return (int)((meta >> 24) & 15); }
+  __device__ __forceinline__ int side_dtype(int k) const { return (int)((meta >> (8 * (k - 1))) & 15); }
+  __device__ __forceinline__ int side_mode(int k) const { return (int)((meta >> (8 * (k - 1) + 4)) & 15); }
+  template <int VEC, int NS, int NT>
+  __device__ __forceinline__ void run(const T (&s1)[VEC], const T (&s2)[VEC], const T (&s3)[VEC], T (&acc)[VEC]) const {
+    T ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
+    if (NT > 0) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0;
+    }
+    for (int k = 0; k < nsteps; ++k) {
+      const long long st = steps[k];
+      if (int_chain_step<T, VEC, NS, NT>((int)(st & 0xff), (int)((st >> 8) & 0xff), (int)((st >> 16) & 0xff),
+                                         (int)((st >> 24) & 3), int_imm<T>(st), int_imm<T>(steps[k + 1]), s1, s2, s3,
+                                         acc, ta, tb))
+        ++k;
+    }
+  }
+};
+
+// A program whose structure was fixed when the library was built (see ew_static.cu for the scheme).
+template <typename T, unsigned long long META, uint32_t... SIG>
+struct StaticIntProgram {
+  const long long* steps;
+  __device__ __forceinline__ constexpr int in_type() const { return (int)((META >> 24) & 15); }
+  __device__ __forceinline__ constexpr int side_dtype(int k) const { return (int)((META >> (8 * (k - 1))) & 15); }
+  __device__ __forceinline__ constexpr int side_mode(int k) const { return (int)((META >> (8 * (k - 1) + 4)) & 15); }
+  template <int VEC, int NS, int NT, int K>
+  __device__ __forceinline__ void from(const T (&s1)[VEC], const T (&s2)[VEC], const T (&s3)[VEC], T (&acc)[VEC],
+                                       T (&ta)[NT > 0 ? VEC : 1], T (&tb)[NT > 0 ? VEC : 1]) const {
+    constexpr int N = (int)sizeof...(SIG);
+    if constexpr (K < N) {
+      constexpr uint32_t sig[N] = {SIG...};
+      constexpr uint32_t w      = sig[K];
+      constexpr int op = (int)(w & 0xff), asel = (int)((w >> 8) & 0xff), bsel = (int)((w >> 16) & 0xff),
+                    role = (int)((w >> 24) & 3);
+      constexpr bool two = op == EW_SELECT && bsel == 0;
+      (void)int_chain_step<T, VEC, NS, NT>(op, asel, bsel, role, int_imm<T>(steps[K]),
+                                           int_imm<T>(steps[K + 1 < EW_MAX_STEPS ? K + 1 : K]), s1, s2, s3, acc, ta, tb);
+      from<VEC, NS, NT, K + (two ? 2 : 1)>(s1, s2, s3, acc, ta, tb);
+    }
+  }
+  template <int VEC, int NS, int NT>
+  __device__ __forceinline__ void run(const T (&s1)[VEC], const T (&s2)[VEC], const T (&s3)[VEC], T (&acc)[VEC]) const {
+    T ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
+    if (NT > 0) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0;
+    }
+    from<VEC, NS, NT, 0>(s1, s2, s3, acc, ta, tb);
+  }
+};
+
+template <typename T, typename OutT, int NS, int NT, class Prog>
+__device__ __forceinline__ void int_chain_body(const Prog& prog, const void* __restrict__ in0,
+                                               const void* __restrict__ p1, const void* __restrict__ p2,
+                                               const void* __restrict__ p3, OutT* __restrict__ out, long long n,
+                                               long long vec_ok, long long mid1, long long inner1, long long mid2,
+                                               long long inner2, long long mid3, long long inner3) {
+  const int in_type  = prog.in_type();
+  const SideSpec sd1 = {p1, prog.side_dtype(1), prog.side_mode(1), mid1, inner1};
+  const SideSpec sd2 = {p2, prog.side_dtype(2), prog.side_mode(2), mid2, inner2};
+  const SideSpec sd3 = {p3, prog.side_dtype(3), prog.side_mode(3), mid3, inner3};
   const long long tid    = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   long long done         = 0;
@@ -258,7 +304,7 @@ __global__ void __launch_bounds__(256)
         if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, *reinterpret_cast<T(*)[4]>(&s2[4 * j]));
         if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, *reinterpret_cast<T(*)[4]>(&s3[4 * j]));
       }
-      run_chain<T, 4 * NV, NS, NT>(steps, nsteps, s1, s2, s3, acc);
+      prog.template run<4 * NV, NS, NT>(s1, s2, s3, acc);
 #pragma unroll
       for (int j = 0; j < NV; ++j) store_int4<T, OutT>(out, (v + j * stride) << 2, *reinterpret_cast<T(*)[4]>(&acc[4 * j]));
     }
@@ -269,7 +315,7 @@ __global__ void __launch_bounds__(256)
       if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<T, 4>(sd1, i0, s1);
       if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 4>(sd2, i0, s2);
       if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 4>(sd3, i0, s3);
-      run_chain<T, 4, NS, NT>(steps, nsteps, s1, s2, s3, acc);
+      prog.template run<4, NS, NT>(s1, s2, s3, acc);
       store_int4<T, OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -280,9 +326,38 @@ __global__ void __launch_bounds__(256)
     if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<T, 1>(sd1, i, s1);
     if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<T, 1>(sd2, i, s2);
     if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<T, 1>(sd3, i, s3);
-    run_chain<T, 1, NS, NT>(steps, nsteps, s1, s2, s3, acc);
+    prog.template run<1, NS, NT>(s1, s2, s3, acc);
     out[i] = convert_out<T, OutT>(acc[0]);
   }
+}
+
+#define INT_CHAIN_PARAMS                                                                                              \
+  const void *__restrict__ in0, const void *__restrict__ p1, const void *__restrict__ p2, const void *__restrict__ p3, \
+      OutT *__restrict__ out, long long n, long long vec_ok, long long meta, long long mid1, long long inner1,        \
+      long long mid2, long long inner2, long long mid3, long long inner3, long long nsteps_ll, long long t0,         \
+      long long t1, long long t2, long long t3, long long t4, long long t5, long long t6, long long t7, long long t8, \
+      long long t9, long long t10, long long t11, long long t12, long long t13, long long t14, long long t15
+
+// Same parameter list as the float form (k_ew_chain): meta bits 0-3 / 4-7 dtype / mode of side 1, 8-15 side 2,
+// 16-23 side 3, 24-27 dtype of in0.
+template <typename T, typename OutT, int NS, int NT = 0>
+__global__ void __launch_bounds__(256) k_ew_chain_int(INT_CHAIN_PARAMS) {
+  const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
+  const DynIntProgram<T> prog = {steps, (int)nsteps_ll, meta};
+  int_chain_body<T, OutT, NS, NT>(prog, in0, p1, p2, p3, out, n, vec_ok, mid1, inner1, mid2, inner2, mid3, inner3);
+}
+
+template <typename T, typename OutT, int NS, int NT, unsigned long long META, uint32_t... SIG>
+__global__ void __launch_bounds__(256) k_ew_chain_int_static(INT_CHAIN_PARAMS) {
+  const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
+  const StaticIntProgram<T, META, SIG...> prog = {steps};
+  int_chain_body<T, OutT, NS, NT>(prog, in0, p1, p2, p3, out, n, vec_ok, mid1, inner1, mid2, inner2, mid3, inner3);
+}
+
+template <uint32_t... SIG>
+StaticChainKey MakeKey(const char* base, long long meta) {
+  StaticChainKey k = {base, meta, (int)sizeof...(SIG), {SIG...}};
+  return k;
 }
 
 }  // namespace
@@ -304,4 +379,11 @@ __global__ void __launch_bounds__(256)
 REG_INT_CHAIN("i32", int32_t);
 REG_INT_CHAIN("i64", long long);
 
+}  // namespace cinn_b200
+
+namespace cinn_b200 {
+#define STATIC_INT_CHAIN(ID, BASE, T, OutT, NS, NT, META, ...)                                                      \
+  CINN_B200_REGISTER_KERNEL("ew_int_static_" #ID, 31, 256, k_ew_chain_int_static<T, OutT, NS, NT, META##ull, __VA_ARGS__>); \
+  static int cinn_b200_static_int_chain_##ID = RegisterStaticChain(MakeKey<__VA_ARGS__>(BASE, META##ll), "ew_int_static_" #ID)
+#include "ew_int_static_table.inc"
 }  // namespace cinn_b200

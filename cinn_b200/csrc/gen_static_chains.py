@@ -246,6 +246,60 @@ ROW_GROUPS = [
               ["sa float32 64", "sb float32 64", "sc float32 64"]),
 ]
 
+# Integer chains (ew_chain_int.cu): index arithmetic, masks and counters.
+def _i(names, dt="int32"):
+    return ["%s %s %s" % (n, dt, FULL) for n in names]
+
+
+INT_GROUPS = [
+    group("abs_add_i32", _i("AB"), ["elementwise_add t0 = A B", "abs t1 = t0"], "t1", "int32"),
+    group("add_i32", _i("AB"), ["elementwise_add y = A B ; axis=-1"], "y", "int32"),
+    group("sub_i32", _i("AB"), ["subtract y = A B ; axis=-1"], "y", "int32"),
+    group("mul_i32", _i("AB"), ["elementwise_mul y = A B ; axis=-1"], "y", "int32"),
+    group("max_i32", _i("AB"), ["max y = A B ; axis=-1"], "y", "int32"),
+    group("equal_i32", _i("AB"), ["equal y = A B ; axis=-1"], "y", "bool"),
+    group("less_than_i32", _i("AB"), ["less_than y = A B ; axis=-1"], "y", "bool"),
+    group("bitwise_and_i32", _i("AB"), ["bitwise_and y = A B ; axis=-1"], "y", "int32"),
+    group("add_i64", _i("AB", "int64"), ["elementwise_add y = A B ; axis=-1"], "y", "int64"),
+    group("mul_add_i32", _i("ABC"), ["elementwise_mul t = A B ; axis=-1", "elementwise_add y = t C ; axis=-1"], "y", "int32"),
+]
+INT_T = {"i32": "int32_t", "i64": "long long", "bool": "uint8_t", "f32": "float"}
+
+
+def int_table_lines():
+    import cinn_b200
+    L = cinn_b200.lib()
+    cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
+    try:
+        seen, lines, skipped = {}, [], []
+        for name, desc in INT_GROUPS:
+            try:
+                g = cinn_b200.FusedGroup(desc)
+            except cinn_b200.CinnB200Error as e:
+                skipped.append("%s: %s" % (name, e))
+                continue
+            text = g.launch_text()
+            g.release()
+            kernel = [l for l in text.splitlines() if l.startswith("launch ")][0].split()[2]
+            m = re.match(r"ew_chain_int_(i32|i64)_(i32|i64|bool|f32)(_s\w+)$", kernel)
+            if not m:
+                skipped.append("%s: not an integer chain (%s)" % (name, kernel))
+                continue
+            args = {int(l.split()[1]): int(l.split()[3]) for l in text.splitlines() if l.startswith("arg ") and l.split()[2] == "int"}
+            meta, nsteps = args[7], args[14]
+            sig = tuple(args[15 + k] & 0xffffffff for k in range(nsteps))
+            ns, nt, _ = VARIANT[m.group(3)]
+            if nsteps == 0 or (kernel, meta, sig) in seen:
+                skipped.append("%s: empty or repeated program" % name)
+                continue
+            seen[(kernel, meta, sig)] = name
+            lines.append('STATIC_INT_CHAIN(%s, "%s", %s, %s, %d, %d, %d, %s);' % (
+                name, kernel, INT_T[m.group(1)], INT_T[m.group(2)], ns, nt, meta, ", ".join("0x%08xu" % w for w in sig)))
+        return lines, skipped
+    finally:
+        L.cinn_b200_set_option(b"enable_static_chains", 1)
+
+
 def builder_programs():
     """Small NetBuilder programs whose register-program groups get kernels too: the shared-value graphs of the
     reference's fusion tests (cinn/hlir/pass/fusion_merge_pass_test.cc:47-71, 131-158, 182-205;
@@ -474,7 +528,14 @@ def tables():
     return [("ew_static_table.inc", HEADER + "\n".join(lines) + "\n", skipped, len(lines)),
             ("chain_reduce_static_table.inc", REDUCE_HEADER + "\n".join(rlines) + "\n", rskipped, len(rlines)),
             ("ew_dag_static_table.inc", dag_header + "\n".join(dlines) + "\n", dskipped, len(dlines)),
-            row_table()]
+            row_table(), int_table()]
+
+
+def int_table():
+    lines, skipped = int_table_lines()
+    header = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_INT_CHAIN(id, interpreted kernel, value type,\n"
+              "// output type, side inputs, temporaries, meta word, step words...).\n")
+    return ("ew_int_static_table.inc", header + "\n".join(lines) + "\n", skipped, len(lines))
 
 
 def row_table():

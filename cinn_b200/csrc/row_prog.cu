@@ -305,7 +305,9 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
       long long done = 0;
       if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary
         const long long nv = r >> 2;
-#pragma unroll 2
+        // four vectors per thread in flight (a 4096-element row is exactly that for a CTA): the loads of an unrolled
+        // group are independent and are issued together
+#pragma unroll 4
         for (long long v = t; v < nv; v += nt) prog.template run_element<4>(pass, in, out, base + (v << 2), sregs, acc);
         done = nv << 2;
       }

@@ -1212,3 +1212,21 @@ def test_float64_trees_are_one_kernel(oracle):
     assert len(comp.groups()) == 1 and "s3t" in comp.groups()[0][1], comp.groups()
     f = feeds
     assert np.array_equal(got[str(out)], (f["A"] - f["B"]) / (np.abs(f["C"]) + np.abs(f["D"])))
+
+
+def test_cast_and_squeeze_relations_of_the_reference_api_tests():
+    """cinn/frontend/net_builder_test.cc:441-491 (cast int32 -> float32: out == (float)in) and :493-783 (squeeze over
+    {1}, {-3}, {1, 3}, {1, -1}, {}: out == in with the extent-1 axes dropped), run on the GPU."""
+    rng = np.random.default_rng(10)
+    b = NetBuilder("net_builder")
+    x = b.create_input(common.Int(32), (4, 7), "In")
+    y = b.cast(x, "float32")
+    X = rng.integers(-2**31, 2**31 - 1, (4, 7), dtype=np.int64).astype(np.int32)
+    comp, got = run_program(b, {"In": X}, [y])
+    assert got[str(y)].dtype == np.float32 and np.array_equal(got[str(y)], X.astype(np.float32))
+    X = rng.standard_normal((4, 1, 7, 1)).astype(np.float32)
+    for axes, want in (([1], (4, 7, 1)), ([-3], (4, 7, 1)), ([1, 3], (4, 7)), ([1, -1], (4, 7)), ([], (4, 7))):
+        b = NetBuilder("net_builder")
+        out = b.squeeze(b.create_input(common.Float(32), (4, 1, 7, 1), "In"), axes)
+        comp, got = run_program_fetch(b, {"In": X}, [out])
+        assert got[str(out)].shape == want and np.array_equal(got[str(out)].reshape(-1), X.reshape(-1)), axes

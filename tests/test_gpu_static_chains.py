@@ -20,7 +20,8 @@ _spec = importlib.util.spec_from_file_location(
 GEN = importlib.util.module_from_spec(_spec)
 _spec.loader.exec_module(GEN)
 
-TORCH_T = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16, "bool": torch.bool}
+TORCH_T = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16, "bool": torch.bool,
+           "int32": torch.int32, "int64": torch.int64}
 
 
 def _tensors(desc, seed, misalign):
@@ -38,6 +39,8 @@ def _tensors(desc, seed, misalign):
         if w[0] == "input":
             if dt == torch.bool:
                 view.copy_(torch.rand(shape, device="cuda", generator=gen) > 0.5)
+            elif dt in (torch.int32, torch.int64):
+                view.copy_(torch.randint(-40000, 40000, shape, device="cuda", generator=gen, dtype=dt))
             else:
                 # positive and negative values, magnitudes around one, a few exact zeros
                 v = torch.randn(shape, device="cuda", generator=gen) * 1.5
@@ -66,7 +69,7 @@ def _run(desc, name, static, seed, misalign):
     return [o.view(torch.uint8).cpu().numpy().copy() for o in outs], kernels
 
 
-@pytest.mark.parametrize("name,desc", GEN.GROUPS, ids=[n for n, _ in GEN.GROUPS])
+@pytest.mark.parametrize("name,desc", GEN.GROUPS + GEN.INT_GROUPS, ids=[n for n, _ in GEN.GROUPS + GEN.INT_GROUPS])
 @pytest.mark.parametrize("variant", ["table_shape", "ragged", "misaligned"])
 def test_static_kernel_equals_interpreter(name, desc, variant):
     if variant == "ragged":
@@ -76,7 +79,7 @@ def test_static_kernel_equals_interpreter(name, desc, variant):
     got_s, k_s = _run(desc, "s_" + variant, True, seed=11, misalign=misalign)
     got_i, k_i = _run(desc, "i_" + variant, False, seed=11, misalign=misalign)
     assert all(k.startswith("ew_chain_") for k in k_i), k_i
-    if not k_s[0].startswith("ew_static_"):
+    if "_static_" not in k_s[0]:
         pytest.skip("no specialised kernel for this entry (%s)" % k_s[0])
     for a, b in zip(got_s, got_i):
         assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))

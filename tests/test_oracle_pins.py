@@ -278,3 +278,22 @@ def test_every_op_of_the_registry_reproduces_its_llvm_build(oracle):
         desc = ("group fn_i\ninput a int32 %d\ninput b int32 %d\nop %s y = a b ; axis=-1\noutput y int32 %d\n" % (n, n, op, n))
         got = ge.run(desc, [d["x_i32"], d["w_i32"]])
         assert got.dtype == np.int32 and np.array_equal(got, d[key]), op
+
+
+def test_cast_and_squeeze_relations_of_the_reference_api_tests():
+    """cinn/frontend/net_builder_test.cc:441-491: cast(int32 -> float32) gives exactly (float)in;
+    :493-783: squeeze over axes {1}, {-3}, {1, 3}, {1, -1} and {} keeps the data and drops the extent-1 axes.
+    Here through the graph evaluator and the front end's shape inference (tests/test_gpu_frontend.py runs the same
+    relations on the GPU)."""
+    from oracle import x86_graph_eval as ge
+    from cinn_b200 import common
+    from cinn_b200.frontend import NetBuilder
+    rng = np.random.default_rng(9)
+    x = rng.integers(-2**31, 2**31 - 1, (4, 7), dtype=np.int64).astype(np.int32)
+    desc = "group fn_c\ninput In int32 4,7\nop cast y = In ; dtype=float32\noutput y float32 4,7\n"
+    got = ge.run(desc, [x])
+    assert got.dtype == np.float32 and np.array_equal(got, x.astype(np.float32))
+    for axes, want in (([1], [4, 7, 1]), ([-3], [4, 7, 1]), ([1, 3], [4, 7]), ([1, -1], [4, 7]), ([], [4, 7])):
+        b = NetBuilder("sq")
+        out = b.squeeze(b.create_input(common.Float(32), (4, 1, 7, 1), "In"), axes)
+        assert out.shape == want, (axes, out.shape)
