@@ -589,8 +589,13 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
           rev.push_back(r);
         } else if (cb.Ok(iv.dtype) && IsIntType(ov.dtype)) {
           ok = cur == out.name;  // float -> integer only as the last op: the store converts (toward zero)
-        } else if (IsIntType(iv.dtype) && ov.dtype == DType::kFloat32) {
-          ok = cb.input_index.count(op.inputs[0]) != 0;  // integer -> float32 only on the chain's input: the load converts
+        } else if (IsIntType(iv.dtype) && IsFloatType(ov.dtype)) {
+          // integer -> float only on the chain's input: the load converts to float32 (to nearest even).  A 16-bit
+          // target is then rounded from that float32, which is what the reference's 16-bit classes do (they are
+          // constructed from float: cinn/common/float16.h:95-122, bfloat16.h); for float16 the result equals the direct
+          // conversion (every integer the first rounding touches overflows float16 anyway).
+          ok = cb.input_index.count(op.inputs[0]) != 0;
+          if (ok) round_after();
         }
         if (!ok) {
           cb.Fail("cast from " + std::string(DTypeName(iv.dtype)) + " to " + DTypeName(ov.dtype) + " is not supported at this place of a chain");

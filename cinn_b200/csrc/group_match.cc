@@ -932,8 +932,64 @@ struct Matcher {
         if (!PlanMidKeep(p.get(), it->second, false, A, B, I, Out(0), Out(0))) return nullptr;
         return p;
       }
-      Fail("reduce over these non-adjacent axes has no prebuilt kernel");
-      return nullptr;
+      // Any other set of axes (cinn/hlir/pe/reduction.cc:139-227 takes every set): the runs of adjacent reduced axes
+      // are folded one at a time, the last run first, each as an [outer, r, inner] reduction of what the previous
+      // step left in scratch memory.  Every step shrinks the data by its run's extent, so the first step carries
+      // nearly all of the traffic; the result differs from the serial order by rounding only (sum, prod) or not at
+      // all (max, min).
+      std::vector<int64_t> dims = AttrList(*op, "dim");
+      const int nd = (int)x.shape.size();
+      std::vector<bool> red(nd, false);
+      for (auto d : dims) {
+        if (d < 0) d += nd;
+        if (d < 0 || d >= nd) return nullptr;
+        red[d] = true;
+      }
+      std::vector<int64_t> ext;   // non-unit extents, and whether each is reduced
+      std::vector<bool> is_red;
+      for (int i = 0; i < nd; ++i)
+        if (x.shape[i] != 1) {
+          ext.push_back(x.shape[i]);
+          is_red.push_back(red[i]);
+        }
+      int64_t kept = 1;
+      for (size_t i = 0; i < ext.size(); ++i) kept *= is_red[i] ? 1 : ext[i];
+      if (o.numel() != kept) {
+        Fail("reduce output has " + std::to_string(o.numel()) + " elements, expected " + std::to_string(kept));
+        return nullptr;
+      }
+      auto p      = NewPlan("multi_axis_reduce");
+      p->elements = x.numel();
+      ArgSpec src = In(0);
+      std::vector<int> align = {0};
+      const char* kind = it->second;
+      while (true) {
+        int hi = (int)ext.size() - 1;
+        while (hi >= 0 && !is_red[hi]) --hi;
+        if (hi < 0) break;
+        int lo = hi;
+        while (lo > 0 && is_red[lo - 1]) --lo;
+        int64_t so = 1, sr = 1, si = 1;
+        for (int i = 0; i < lo; ++i) so *= ext[i];
+        for (int i = lo; i <= hi; ++i) sr *= ext[i];
+        for (int i = hi + 1; i < (int)ext.size(); ++i) si *= ext[i];
+        bool last = true;
+        for (int i = 0; i < lo; ++i) last = last && !is_red[i];
+        ArgSpec dst = Out(0);
+        if (!last) {
+          const int64_t off = p->scratch_bytes;
+          p->scratch_bytes += (size_t)RoundUp(so * si * 4, 256);
+          dst = Scratch(off);
+        }
+        if (!PlanReduce(p.get(), kind, so, sr, si, src, dst, align)) return nullptr;
+        ext.erase(ext.begin() + lo, ext.begin() + hi + 1);
+        is_red.erase(is_red.begin() + lo, is_red.begin() + hi + 1);
+        src  = dst;
+        align.clear();
+        kind = BaseReduceOp(kind);  // a folded producer (x * x, |x|, exp x) belongs to the first step only
+        if (last) break;
+      }
+      return p;
     }
     if (o.numel() != outer * inner) {
       Fail("reduce output has " + std::to_string(o.numel()) + " elements, expected " + std::to_string(outer * inner));

@@ -185,9 +185,14 @@ def test_unmatched_group_is_an_error_not_a_fallback():
     assert rc == -2
     rc = L.cinn_b200_compile_group(b"nonsense", ctypes.byref(fn))
     assert rc == -1
-    # reduce over non-adjacent axes
+    # a float32 reduce over non-adjacent axes is planned as one launch per run of adjacent axes ...
     rc = L.cinn_b200_compile_group(
-        b"group g\ninput x float32 4,5,6,7\nop reduce_sum y = x ; dim=1,3\noutput y float32 4,6\n", ctypes.byref(fn))
+        b"group g_multi\ninput x float32 4,5,6,7\nop reduce_sum y = x ; dim=1,3\noutput y float32 4,6\n", ctypes.byref(fn))
+    assert rc == 0
+    assert L.cinn_b200_release_group(b"g_multi") == 0
+    # ... the other element types have no such plan
+    rc = L.cinn_b200_compile_group(
+        b"group g\ninput x int32 4,5,6,7\nop reduce_sum y = x ; dim=1,3\noutput y int32 4,6\n", ctypes.byref(fn))
     assert rc == -2 and b"non-adjacent" in L.cinn_b200_last_error()
     assert L.cinn_b200_lookup(b"g") is None
 

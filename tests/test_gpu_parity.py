@@ -424,3 +424,35 @@ def test_bfloat16_batch_norm_relu():
     r = lambda t: t.double().reshape(1, c, 1, 1)  # noqa: E731
     want = torch.relu((x.double() - r(mean)) * r(scale) / torch.sqrt(r(var) + 1e-5) + r(bias))
     assert bool(((got - want).abs() <= 1e-2 * want.abs() + 1e-2).all())
+
+
+# ---- reductions over any set of axes (cinn/hlir/pe/reduction.cc:139-227) ----------------------------------------------
+@pytest.mark.parametrize("shape,dims", [((8, 16, 32, 4), (0, 2)), ((8, 16, 32, 4), (1, 3)), ((6, 5, 7, 3, 9), (0, 2, 4)),
+                                        ((64, 3, 128, 8), (0, 2)), ((4, 1, 9, 10, 2), (0, 3))])
+@pytest.mark.parametrize("kind", ["sum", "max", "min", "prod"])
+@pytest.mark.parametrize("keep", [False, True])
+def test_reduce_over_non_adjacent_axes(oracle, shape, dims, kind, keep):
+    """The runs of adjacent reduced axes are folded one launch at a time through scratch memory; against the oracle's
+    serial loop nest (max / min bit-exact, sum / prod at the reduction tolerance)."""
+    import torch
+    import cinn_b200
+    from oracle import x86_graph_eval as ge
+    rng = np.random.default_rng(3)
+    x = (rng.uniform(0.9, 1.1, shape) if kind == "prod" else rng.standard_normal(shape)).astype(np.float32)
+    out_shape = [1 if i in dims else d for i, d in enumerate(shape)] if keep else [d for i, d in enumerate(shape) if i not in dims]
+    s = lambda sh: ",".join(str(d) for d in sh)  # noqa: E731
+    desc = ("group fn_multi_axis_%s\ninput X float32 %s\nop reduce_%s y = X ; dim=%s keep_dim=%s\noutput y float32 %s\n"
+            % (kind, s(shape), kind, s(dims), "true" if keep else "false", s(out_shape)))
+    g = cinn_b200.FusedGroup(desc)
+    assert g.pattern == "multi_axis_reduce" and g.launches >= 2
+    out = torch.empty(out_shape, device="cuda")
+    g.run([torch.from_numpy(x).cuda(), out])
+    torch.cuda.synchronize()
+    g.release()
+    want = ge.run(desc, [x])
+    got = out.cpu().numpy()
+    if kind in ("max", "min"):
+        assert np.array_equal(got, want)
+    else:
+        r = int(np.prod([shape[d] for d in dims]))
+        assert np.allclose(got, want, rtol=1e-5, atol=2e-6 * np.sqrt(r))

@@ -64,8 +64,12 @@ def build_random_program(rng, b, shape, half=False):
         elif kind == "reduce":
             if half:
                 continue   # 16-bit reductions accumulate differently by design (fp32 tree vs fp16 serial)
-            axis = int(rng.integers(0, len(shape)))
-            r = getattr(b, str(rng.choice(["reduce_sum", "reduce_max", "reduce_min"])))(x, [axis])
+            # one axis, or (half of the time, from rank 3) any subset of axes, non-adjacent ones included
+            if len(shape) >= 3 and rng.random() < 0.5:
+                axes = sorted(int(a) for a in rng.choice(len(shape), size=int(rng.integers(2, len(shape))), replace=False))
+            else:
+                axes = [int(rng.integers(0, len(shape)))]
+            r = getattr(b, str(rng.choice(["reduce_sum", "reduce_max", "reduce_min"])))(x, axes)
             fetch.append(r)
             continue
         else:
