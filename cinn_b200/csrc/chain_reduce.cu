@@ -106,8 +106,10 @@ __device__ __forceinline__ void chain_values2(const Prog& prog, const void* in0,
 // per SM (64 registers, a few spilled words) 0.70 of the HBM peak; 3 CTAs (80 registers, no spills) 0.61; 5 CTAs (48
 // registers) 0.57.
 template <int NS, int NT, class Prog>
-__device__ __forceinline__ void chain_reduce_row_body(const Prog& prog, const void* in0, const Sides& sd, void* out,
+__device__ __forceinline__ void chain_reduce_row_body(const Prog& prog, const void* in0, const Sides& sides, void* out,
                                                       long long vec_ok, long long rows, long long r, long long group) {
+  Sides sd = sides;
+  sd.sd1.row_len = sd.sd2.row_len = sd.sd3.row_len = r;
   const int rop = prog.reduce_op(), out_type = prog.result_type();
   __shared__ float part[8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -118,6 +120,7 @@ __device__ __forceinline__ void chain_reduce_row_body(const Prog& prog, const vo
   const float id = cr_identity(rop);
   for (long long row = first; row < rows; row += step) {  // uniform per CTA in the CTA-per-row form
     const long long base = row * r;
+    sd.sd1.row_base = sd.sd2.row_base = sd.sd3.row_base = base;
     float a[4] = {id, id, id, id};
     long long done = 0;
     if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary

@@ -240,6 +240,9 @@ struct SideSpec {
   const void* ptr;
   int dtype, mode;
   long long mid, inner;
+  // Set by kernels that walk rows: the flat index at which the current row starts and the row's length.  A vector
+  // operand whose period is the row length is then indexed by the offset within the row, without a division.
+  long long row_base, row_len;
 };
 
 // (i / inner) % mid, in 32-bit arithmetic whenever the operands allow it (64-bit division is several times dearer).
@@ -255,7 +258,8 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, float
   if (VEC == 4 && s.mode == EW_SIDE_FULL) {
     load_vec4(s.ptr, s.dtype, i0, stream, *reinterpret_cast<float(*)[4]>(&f[0]));
   } else if (VEC == 4 && s.mode == EW_SIDE_PERIODIC_VEC) {
-    load_vec4(s.ptr, s.dtype, side_index(i0, 1, s.mid), false, *reinterpret_cast<float(*)[4]>(&f[0]));
+    const long long idx = s.mid == s.row_len ? i0 - s.row_base : side_index(i0, 1, s.mid);
+    load_vec4(s.ptr, s.dtype, idx, false, *reinterpret_cast<float(*)[4]>(&f[0]));
   } else if (s.mode == EW_SIDE_ONE_PER_VEC || s.mode == EW_SIDE_SCALAR) {
     const float v = load_scalar(s.ptr, s.dtype, s.mode == EW_SIDE_SCALAR ? 0 : side_index(i0, s.inner, s.mid));
 #pragma unroll

@@ -29,6 +29,7 @@ namespace {
 struct RowInputs {
   const void* ptr[DAG_MAX_IN];
   long long mid[DAG_MAX_IN], inner[DAG_MAX_IN];
+  long long row_base, row_len;  // the flat index at which the current row starts; the row's length
 };
 struct RowOutputs {
   void* ptr[DAG_MAX_OUT];
@@ -65,12 +66,19 @@ template <int VEC>
 __device__ __forceinline__ bool rp_element_step(unsigned w, float imm, float imm2, unsigned long long meta,
                                                 const RowInputs& in, const RowOutputs& out, long long i0,
                                                 float (&regs)[DAG_REGS][VEC], const float (&sregs)[ROWP_SREGS],
-                                                float (&acc)[ROWP_SREGS], bool reread) {
+                                                float (&acc)[ROWP_SREGS], bool reread, float (*cache)[4] = nullptr,
+                                                int cache_mode = 0) {
   const int op = (int)(w & 0xff), dst = (int)((w >> 8) & 15), a = (int)((w >> 12) & 31), b = (int)((w >> 17) & 31),
             c = (int)((w >> 22) & 31);
   if (op == EW_NOP) return false;
   if (op == DAG_LOAD) {
-    const SideSpec s = {in.ptr[a], (int)((meta >> (6 * a)) & 7), (int)((meta >> (6 * a + 3)) & 7), in.mid[a], in.inner[a]};
+    const SideSpec s = {in.ptr[a], (int)((meta >> (6 * a)) & 7), (int)((meta >> (6 * a + 3)) & 7), in.mid[a], in.inner[a], in.row_base, in.row_len};
+    // cache_mode 2: this full-size input of the row is already in this thread's registers
+    if (VEC == 4 && cache_mode == 2 && s.mode == EW_SIDE_FULL) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) regs[dst][i] = cache[a][i & 3];
+      return false;
+    }
     load_side<VEC>(s, i0, regs[dst], !reread);  // a row that a later pass reads again stays in L1
     return false;
   }
@@ -104,6 +112,13 @@ __device__ __forceinline__ bool rp_element_step(unsigned w, float imm, float imm
   } else if (op == EW_SCALE_PRE) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) x[i] = imm * (x[i] + imm2);
+  } else if (op == EW_DIV && b >= ROWP_SREG0) {
+    // Division by a per-row value (always a function of a reduction here): one reciprocal per row, a multiplication
+    // per element, as the dedicated row kernels do.  Within 1.5 ulp of the true quotient; a result that depends on
+    // a reduction is compared at 1e-5 relative.
+    const float rcp = 1.0f / sregs[(b - ROWP_SREG0) & 7];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) x[i] = x[i] * rcp;
   } else {
     float y[VEC];
     rp_operand<VEC>(b, imm, imm2, regs, sregs, y);
@@ -122,7 +137,7 @@ __device__ __forceinline__ bool rp_scalar_step(unsigned w, float imm, float imm2
             c = (int)((w >> 22) & 31);
   if (op == EW_NOP) return false;
   if (op == DAG_LOAD) {
-    const SideSpec s = {in.ptr[a], (int)((meta >> (6 * a)) & 7), (int)((meta >> (6 * a + 3)) & 7), in.mid[a], in.inner[a]};
+    const SideSpec s = {in.ptr[a], (int)((meta >> (6 * a)) & 7), (int)((meta >> (6 * a + 3)) & 7), in.mid[a], in.inner[a], in.row_base, in.row_len};
     float v[1];
     load_side<1>(s, row, v);
     sregs[dst & 7] = v[0];
@@ -159,8 +174,13 @@ __device__ __forceinline__ float rp_imm(long long w) { return __uint_as_float((u
 
 // ---- the two ways a program is known ---------------------------------------------------------------------------------
 struct DynRowProgram {
+  static constexpr bool kStatic = false;
   const long long* steps;
   unsigned long long counts, meta;
+  __device__ __forceinline__ void run_element_cached(int, const RowInputs&, const RowOutputs&, long long,
+                                                     const float (&)[ROWP_SREGS], float (&)[ROWP_SREGS], float (*)[4]) const {}
+  __device__ __forceinline__ void preload(const RowInputs&, long long, float (*)[4]) const {}
+  __device__ __forceinline__ void prefetch(const RowInputs&, long long) const {}
   __device__ __forceinline__ int passes() const {
     int p = 0;
     for (int k = 0; k < ROWP_MAX_PASSES; ++k)
@@ -262,6 +282,80 @@ struct StaticRowProgram {
       scalar_from<K + (two ? 2 : 1), END>(in, out, row, writer, sregs);
     }
   }
+  static constexpr bool kStatic = true;
+  // bit k: pass 0 loads input k (so a later pass may take it from the register cache)
+  __host__ __device__ static constexpr unsigned loaded_by_pass0() {
+    unsigned m = 0;
+    for (int k = first(0, false); k < first(0, false) + count(0, false); ++k)
+      if ((word(k) & 0xff) == (unsigned)DAG_LOAD) m |= 1u << ((word(k) >> 12) & 7);
+    return m;
+  }
+  __host__ __device__ static constexpr int step_words(int k) {
+    const uint32_t w = word(k);
+    const int op = (int)(w & 0xff), a = (int)((w >> 12) & 31), b = (int)((w >> 17) & 31), c = (int)((w >> 22) & 31);
+    const bool two = op != EW_NOP && op != DAG_LOAD && op != DAG_STORE && op != ROWP_ACC &&
+                     (a == DAG_IMM2 || b == DAG_IMM2 || c == DAG_IMM2 || op == EW_SCALE_PRE);
+    return two ? 2 : 1;
+  }
+  // The loads of pass 0's full-size inputs for one vector, into its cache slot; nothing uses the values here, so the
+  // loads of all of a thread's vectors are in flight together.
+  template <int K, int END>
+  __device__ __forceinline__ void preload_from(const RowInputs& in, long long i0, float (*cache)[4]) const {
+    if constexpr (K < END) {
+      constexpr uint32_t w = word(K);
+      if constexpr ((w & 0xff) == (unsigned)DAG_LOAD) {
+        constexpr int a = (int)((w >> 12) & 7);
+        if constexpr (((META >> (6 * a + 3)) & 7) == (unsigned)EW_SIDE_FULL)
+          load_vec4(in.ptr[a], (int)((META >> (6 * a)) & 7), i0, true, *reinterpret_cast<float(*)[4]>(&cache[a][0]));
+      }
+      preload_from<K + step_words(K), END>(in, i0, cache);
+    }
+  }
+  template <int K, int END>
+  __device__ __forceinline__ void prefetch_from(const RowInputs& in, long long i0) const {
+    if constexpr (K < END) {
+      constexpr uint32_t w = word(K);
+      if constexpr ((w & 0xff) == (unsigned)DAG_LOAD) {
+        constexpr int a = (int)((w >> 12) & 7);
+        if constexpr (((META >> (6 * a + 3)) & 7) == (unsigned)EW_SIDE_FULL) {
+          constexpr int dt = (int)((META >> (6 * a)) & 7);
+          const char* p = static_cast<const char*>(in.ptr[a]) + i0 * (dt == EW_F32 ? 4 : (dt == EW_BOOL ? 1 : 2));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+        }
+      }
+      prefetch_from<K + step_words(K), END>(in, i0);
+    }
+  }
+  // Asks the lines of pass 0's full-size inputs at flat index i0 into L2.
+  __device__ __forceinline__ void prefetch(const RowInputs& in, long long i0) const {
+    prefetch_from<first(0, false), first(0, false) + count(0, false)>(in, i0);
+  }
+  __device__ __forceinline__ void preload(const RowInputs& in, long long i0, float (*cache)[4]) const {
+    preload_from<first(0, false), first(0, false) + count(0, false)>(in, i0, cache);
+  }
+  template <int K, int END>
+  __device__ __forceinline__ void cached_from(const RowInputs& in, const RowOutputs& out, long long i0,
+                                              float (&regs)[DAG_REGS][4], const float (&sregs)[ROWP_SREGS],
+                                              float (&acc)[ROWP_SREGS], float (*cache)[4]) const {
+    if constexpr (K < END) {
+      constexpr uint32_t w = word(K);
+      // only what pass 0 loaded is in the cache
+      constexpr int mode = ((w & 0xff) == (unsigned)DAG_LOAD && ((loaded_by_pass0() >> ((w >> 12) & 7)) & 1u)) ? 2 : 0;
+      (void)rp_element_step<4>(w, rp_imm(steps[K]), rp_imm(steps[K + 1 < ROWP_MAX_STEPS ? K + 1 : K]), META, in, out, i0,
+                               regs, sregs, acc, false, cache, mode);
+      cached_from<K + step_words(K), END>(in, out, i0, regs, sregs, acc, cache);
+    }
+  }
+  // One vector of a row whose vectors stay in this thread's registers between the passes (`cache` is the slot of
+  // this vector: [input][lane of the vector]).
+  __device__ __forceinline__ void run_element_cached(int pass, const RowInputs& in, const RowOutputs& out, long long i0,
+                                                     const float (&sregs)[ROWP_SREGS], float (&acc)[ROWP_SREGS],
+                                                     float (*cache)[4]) const {
+    float regs[DAG_REGS][4];
+    if (pass == 0) cached_from<first(0, false), first(0, false) + count(0, false)>(in, out, i0, regs, sregs, acc, cache);
+    else if (pass == 1) cached_from<first(1, false), first(1, false) + count(1, false)>(in, out, i0, regs, sregs, acc, cache);
+    else cached_from<first(2, false), first(2, false) + count(2, false)>(in, out, i0, regs, sregs, acc, cache);
+  }
   template <int VEC>
   __device__ __forceinline__ void run_element(int pass, const RowInputs& in, const RowOutputs& out, long long i0,
                                               const float (&sregs)[ROWP_SREGS], float (&acc)[ROWP_SREGS]) const {
@@ -281,8 +375,10 @@ struct StaticRowProgram {
 
 // ---- the kernel body --------------------------------------------------------------------------------------------------
 template <class Prog>
-__device__ __forceinline__ void row_program_body(const Prog& prog, const RowInputs& in, const RowOutputs& out,
+__device__ __forceinline__ void row_program_body(const Prog& prog, const RowInputs& inputs, const RowOutputs& out,
                                                  long long rows, long long r, long long group, long long vec_ok) {
+  RowInputs in = inputs;
+  in.row_len   = r;
   __shared__ float part[8][ROWP_SREGS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool per_warp   = group == 32;
@@ -290,9 +386,31 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
   const long long step  = per_warp ? (long long)gridDim.x * 8 : gridDim.x;
   const int t = per_warp ? lane : (int)threadIdx.x, nt = per_warp ? 32 : 256;
   const int npass = prog.passes();
+  // A specialised program of several passes over a row that a CTA holds in at most four vectors per thread keeps the
+  // row in registers between the passes instead of reading it again.
+  constexpr int kCacheVecs = 4;
+  const bool use_cache = Prog::kStatic && !per_warp && vec_ok && npass > 1 && (r >> 2) <= (long long)kCacheVecs * 256;
+  float cache[kCacheVecs][DAG_MAX_IN][4];
   // CTA-per-row: every thread of the CTA walks the same rows, so the barriers below are uniform.
   for (long long row = first; per_warp ? row < rows : row < rows; row += step) {
     const long long base = row * r;
+    in.row_base          = base;
+    if (use_cache) {
+      // this row's loads, all in flight together; the next row is asked into L2 meanwhile (no registers held for it),
+      // so that the CTA's next wait is an L2 latency, not a DRAM one
+#pragma unroll
+      for (int j = 0; j < kCacheVecs; ++j) {
+        const long long v = t + (long long)j * 256;
+        if (v < (r >> 2)) prog.preload(in, base + (v << 2), cache[j]);
+      }
+      if (row + step < rows) {
+#pragma unroll
+        for (int j = 0; j < kCacheVecs; ++j) {
+          const long long v = t + (long long)j * 256;
+          if (v < (r >> 2)) prog.prefetch(in, base + step * r + (v << 2));
+        }
+      }
+    }
     float sregs[ROWP_SREGS];
 #pragma unroll
     for (int k = 0; k < ROWP_SREGS; ++k) sregs[k] = 0.0f;
@@ -303,7 +421,15 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
 #pragma unroll
       for (int k = 0; k < ROWP_SREGS; ++k) acc[k] = rp_identity((kinds >> (2 * k)) & 3);
       long long done = 0;
-      if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary
+      if (use_cache) {
+        // every thread's (at most four) vectors of the row were loaded once, all the loads in flight together
+#pragma unroll
+        for (int j = 0; j < kCacheVecs; ++j) {
+          const long long v = t + (long long)j * 256;
+          if (v < (r >> 2)) prog.run_element_cached(pass, in, out, base + (v << 2), sregs, acc, cache[j]);
+        }
+        done = r;
+      } else if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary
         const long long nv = r >> 2;
         // four vectors per thread in flight (a 4096-element row is exactly that for a CTA): the loads of an unrolled
         // group are independent and are issued together
