@@ -260,12 +260,14 @@ def side_groups(torch, dev, peak, only=None):
         ("bn_grad_stats_256x64x112x112", lambda: W.bn_grad_stats((256, 64, 112, 112)), 1,
          "sum(dy) and sum(dy * (x - mean)) per channel in one read of dy and x"),
         ("bn_grad_apply_256x64x112x112", lambda: W.bn_grad_apply((256, 64, 112, 112)), 1, ""),
-        # the generic families: any other elementwise chain / element type (interpreted program, not a dedicated kernel)
-        ("generic_chain_abs_add_f32_8192x8192", lambda: W.generic_chain("abs_add_f32"), 1, "generic chain kernel"),
-        ("generic_chain_select_f32_8192x8192", lambda: W.generic_chain("select_f32"), 1, "generic chain kernel"),
-        ("generic_chain_greater_than_f32_8192x8192", lambda: W.generic_chain("greater_than_f32"), 1, "generic chain kernel"),
-        ("generic_chain_abs_add_i32_8192x8192", lambda: W.generic_chain("abs_add_i32"), 1, "generic integer chain kernel"),
-        ("generic_chain_affine_f64_8192x8192", lambda: W.generic_chain("affine_f64"), 1, "generic float64 chain kernel"),
+        # the generic families: any other elementwise chain / element type (the chain kernels: specialised at build time
+        # for the programs of their table, interpreted otherwise; `kernels` in the result says which ran)
+        ("generic_chain_abs_add_f32_8192x8192", lambda: W.generic_chain("abs_add_f32"), 1, "chain kernel"),
+        ("generic_chain_select_f32_8192x8192", lambda: W.generic_chain("select_f32"), 1, "chain kernel"),
+        ("generic_chain_greater_than_f32_8192x8192", lambda: W.generic_chain("greater_than_f32"), 1, "chain kernel"),
+        ("generic_chain_abs_add_i32_8192x8192", lambda: W.generic_chain("abs_add_i32"), 1, "integer chain kernel"),
+        ("generic_chain_affine_f64_8192x8192", lambda: W.generic_chain("affine_f64"), 1, "float64 chain kernel"),
+        ("generic_chain_abs_add_f64_8192x8192", lambda: W.generic_chain("abs_add_f64"), 1, "float64 chain kernel"),
         ("generic_reduce_sum_f16_rows_16384x8192", lambda: W.generic_reduce("sum", "float16", axis=1), 2, ""),
         ("generic_reduce_sum_f16_cols_16384x8192", lambda: W.generic_reduce("sum", "float16", axis=0), 2, ""),
         ("generic_reduce_max_i32_rows_16384x8192", lambda: W.generic_reduce("max", "int32", axis=1), 1, ""),

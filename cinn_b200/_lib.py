@@ -122,6 +122,9 @@ def lib():
         L.cinn_b200_col_reduce_sharded_f32_emulated.restype = ci
         L.cinn_b200_col_reduce_sharded_f32_emulated.argtypes = [vp, ci, ctypes.POINTER(vp), ll, ll,
                                                                 ctypes.POINTER(vp), ci, vp]
+        L.cinn_b200_col_reduce_sharded_f32_emulated_ranks.restype = ci
+        L.cinn_b200_col_reduce_sharded_f32_emulated_ranks.argtypes = [vp, ci, ctypes.POINTER(vp), ll, ll,
+                                                                      ctypes.POINTER(vp), ci, ci, ci, vp]
         L.cinn_b200_col_reduce_sharded_f32.restype = ci
         L.cinn_b200_col_reduce_sharded_f32.argtypes = [vp, ci, vp, ll, ll, vp, ci, vp]
         L.cinn_b200_device_status.restype = ci

@@ -68,7 +68,7 @@ const std::map<std::string, int>& IntUnaryCodes() {
 const std::map<std::string, int>& IntBinaryCodes() {
   static const std::map<std::string, int> m = {
       {"elementwise_add", EW_ADD}, {"subtract", EW_SUB}, {"elementwise_mul", EW_MUL}, {"divide", EW_DIV},
-      {"max", EW_MAX}, {"min", EW_MIN}, {"equal", EW_EQ}, {"not_equal", EW_NE}, {"greater_than", EW_GT},
+      {"max", EW_MAX}, {"min", EW_MIN}, {"pow", EW_POW}, {"equal", EW_EQ}, {"not_equal", EW_NE}, {"greater_than", EW_GT},
       {"less_than", EW_LT}, {"greater_equal", EW_GE}, {"less_equal", EW_LE}, {"mod", EW_MOD}, {"remainder", EW_MOD},
       {"floor_divide", EW_FLOOR_DIV}, {"logical_and", EW_LAND}, {"logical_or", EW_LOR}, {"logical_xor", EW_LXOR},
       {"bitwise_and", EW_BAND}, {"bitwise_or", EW_BOR}, {"bitwise_xor", EW_BXOR}, {"left_shift", EW_SHL},

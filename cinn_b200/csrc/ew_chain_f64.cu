@@ -191,92 +191,170 @@ __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, doubl
 
 // NS = how many side inputs the kernel variant carries (0, 1 or 3): the registers of absent sides are never touched.
 // NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees, as in the float form.
-template <int VEC, int NS, int NT = 0>
-__device__ __forceinline__ void run_chain(const long long* steps, int nsteps, const double* imms,
-                                          const double (&s1)[VEC], const double (&s2)[VEC], const double (&s3)[VEC],
-                                          double (&acc)[VEC]) {
-  double ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
-  if (NT > 0) {
+// One step of the program; returns true when the step also used the next word's immediate.
+template <int VEC, int NS, int NT>
+__device__ __forceinline__ bool d_chain_step(int op, int asel, int bsel, int role, double imm, double imm2,
+                                             const double (&s1)[VEC], const double (&s2)[VEC], const double (&s3)[VEC],
+                                             double (&acc)[VEC], double (&ta)[NT > 0 ? VEC : 1],
+                                             double (&tb)[NT > 0 ? VEC : 1]) {
+  if (op == EW_NOP) return false;
+  if (op >= EW_FIRST_UNARY) {
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0.0;
+    for (int i = 0; i < VEC; ++i) acc[i] = d_unary(op, imm, acc[i]);
+    return false;
   }
-  for (int k = 0; k < nsteps; ++k) {
-    const long long st = steps[k];
-    const int op       = (int)(st & 0xff);
-    const int asel     = (int)((st >> 8) & 0xff);
-    const int bsel     = (int)((st >> 16) & 0xff);
-    const int role     = (int)((st >> 24) & 3);
-    const double imm   = imms[(int)(st >> 32) & (kMaxImm - 1)];
-    if (op == EW_NOP) continue;
-    if (op >= EW_FIRST_UNARY) {
+  if (NT > 0 && op == EW_STASH) {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] = d_unary(op, imm, acc[i]);
-      continue;
-    }
-    if (NT > 0 && op == EW_STASH) {
+    for (int i = 0; i < VEC; ++i) (asel == 5 ? ta : tb)[NT > 0 ? i : 0] = acc[i];
+    return false;
+  }
+  double o[VEC];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) (asel == 5 ? ta : tb)[NT > 0 ? i : 0] = acc[i];
-      continue;
-    }
-    double o[VEC];
+  for (int i = 0; i < VEC; ++i) {
+    o[i] = (NS >= 1 && asel == 1) ? s1[i] : ((NS >= 2 && asel == 2) ? s2[i] : ((NS >= 3 && asel == 3) ? s3[i] : (asel == 4 ? acc[i] : imm)));
+    if (NT > 0) o[i] = asel == 5 ? ta[NT > 0 ? i : 0] : (asel == 6 ? tb[NT > 0 ? i : 0] : o[i]);
+  }
+  if (op == EW_FMA) {
 #pragma unroll
     for (int i = 0; i < VEC; ++i) {
-      o[i] = (NS >= 1 && asel == 1) ? s1[i] : ((NS >= 2 && asel == 2) ? s2[i] : ((NS >= 3 && asel == 3) ? s3[i] : (asel == 4 ? acc[i] : imm)));
-      if (NT > 0) o[i] = asel == 5 ? ta[NT > 0 ? i : 0] : (asel == 6 ? tb[NT > 0 ? i : 0] : o[i]);
+      double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
+      if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
+      acc[i] = fma(acc[i], o[i], b);
     }
-    const double imm2 = imms[(int)(steps[k + 1] >> 32) & (kMaxImm - 1)];
-    if (op == EW_FMA) {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : imm2));
-        if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
-        acc[i] = fma(acc[i], o[i], b);
-      }
-      if (bsel == 0) ++k;
-    } else if (op == EW_SCALE_PRE) {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] = imm * (acc[i] + imm2);
-      ++k;
-    } else if (op == EW_SELECT) {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
-        if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
-        const double c = role == 0 ? acc[i] : o[i];
-        const double t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
-        const double f = role == 2 ? acc[i] : b;
-        acc[i]         = c != 0.0 ? t : f;
-      }
-      if (bsel == 0) ++k;
-    } else {
-#pragma unroll
-      for (int i = 0; i < VEC; ++i)
-        acc[i] = (role != 0 && op != EW_COPY) ? d_binary(op, o[i], acc[i]) : d_binary(op, acc[i], o[i]);
-    }
+    return bsel == 0;
   }
+  if (op == EW_SCALE_PRE) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = imm * (acc[i] + imm2);
+    return true;
+  }
+  if (op == EW_SELECT) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      double b = (NS >= 1 && bsel == 1) ? s1[i] : ((NS >= 2 && bsel == 2) ? s2[i] : ((NS >= 3 && bsel == 3) ? s3[i] : (bsel == 4 ? acc[i] : imm2)));
+      if (NT > 0) b = bsel == 5 ? ta[NT > 0 ? i : 0] : (bsel == 6 ? tb[NT > 0 ? i : 0] : b);
+      const double c = role == 0 ? acc[i] : o[i];
+      const double t = role == 0 ? o[i] : (role == 1 ? acc[i] : b);
+      const double f = role == 2 ? acc[i] : b;
+      acc[i]         = c != 0.0 ? t : f;
+    }
+    return bsel == 0;
+  }
+#pragma unroll
+  for (int i = 0; i < VEC; ++i)
+    acc[i] = (role != 0 && op != EW_COPY) ? d_binary(op, o[i], acc[i]) : d_binary(op, acc[i], o[i]);
+  return false;
 }
 
+// The program read from the kernel's parameters at run time.
+struct DynF64Program {
+  const long long* steps;
+  int nsteps;
+  long long meta_;
+  const double* imms;
+  __device__ __forceinline__ long long meta() const { return meta_; }
+  template <int VEC, int NS, int NT>
+  __device__ __forceinline__ void run(const double (&s1)[VEC], const double (&s2)[VEC], const double (&s3)[VEC],
+                                      double (&acc)[VEC]) const {
+    double ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
+    if (NT > 0) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0.0;
+    }
+    for (int k = 0; k < nsteps; ++k) {
+      const long long st = steps[k];
+      const double imm   = imms[(int)(st >> 32) & (kMaxImm - 1)];
+      const double imm2  = imms[(int)(steps[k + 1] >> 32) & (kMaxImm - 1)];
+      if (d_chain_step<VEC, NS, NT>((int)(st & 0xff), (int)((st >> 8) & 0xff), (int)((st >> 16) & 0xff),
+                                    (int)((st >> 24) & 3), imm, imm2, s1, s2, s3, acc, ta, tb))
+        ++k;
+    }
+  }
+};
+
+// Entry `idx` of the immediates without indexing the array at run time (which would move it to local memory).
+__device__ __forceinline__ double pick_imm(const double* imms, int idx) {
+  const double a = (idx & 1) ? imms[1] : imms[0], b = (idx & 1) ? imms[3] : imms[2];
+  const double c = (idx & 1) ? imms[5] : imms[4], d = (idx & 1) ? imms[7] : imms[6];
+  const double ab = (idx & 2) ? b : a, cd = (idx & 2) ? d : c;
+  return (idx & 4) ? cd : ab;
+}
+
+// The program fixed at build time: META and the low halves of the step words (op, selectors, role) are template
+// constants; which immediate a step takes still comes from the parameters.
+template <unsigned long long META, uint32_t... SIG>
+struct StaticF64Program {
+  const long long* steps;
+  const double* imms;
+  static constexpr int kSteps = (int)sizeof...(SIG);
+  __host__ __device__ static constexpr uint32_t word(int k) {
+    constexpr uint32_t w[kSteps + 1] = {SIG..., 0u};
+    return w[k < kSteps ? k : kSteps];
+  }
+  __host__ __device__ static constexpr bool uses_imm(int k) {
+    const uint32_t w = word(k);
+    const int op = (int)(w & 0xff), asel = (int)((w >> 8) & 0xff);
+    return op >= EW_FIRST_UNARY || op == EW_SCALE_PRE || asel == 0;
+  }
+  __host__ __device__ static constexpr bool uses_next(int k) {
+    const uint32_t w = word(k);
+    const int op = (int)(w & 0xff), bsel = (int)((w >> 16) & 0xff);
+    return op == EW_SCALE_PRE || ((op == EW_FMA || op == EW_SELECT) && bsel == 0);
+  }
+  __device__ __forceinline__ long long meta() const { return (long long)META; }
+  template <int VEC, int NS, int NT, int K>
+  __device__ __forceinline__ void from(const double (&s1)[VEC], const double (&s2)[VEC], const double (&s3)[VEC],
+                                       double (&acc)[VEC], double (&ta)[NT > 0 ? VEC : 1],
+                                       double (&tb)[NT > 0 ? VEC : 1]) const {
+    if constexpr (K < kSteps) {
+      constexpr uint32_t w = word(K);
+      const double imm  = uses_imm(K) ? pick_imm(imms, (int)(steps[K] >> 32)) : 0.0;
+      const double imm2 = uses_next(K) ? pick_imm(imms, (int)(steps[K + 1 < EW_MAX_STEPS ? K + 1 : K] >> 32)) : 0.0;
+      (void)d_chain_step<VEC, NS, NT>((int)(w & 0xff), (int)((w >> 8) & 0xff), (int)((w >> 16) & 0xff),
+                                      (int)((w >> 24) & 3), imm, imm2, s1, s2, s3, acc, ta, tb);
+      from<VEC, NS, NT, K + (uses_next(K) ? 2 : 1)>(s1, s2, s3, acc, ta, tb);
+    }
+  }
+  template <int VEC, int NS, int NT>
+  __device__ __forceinline__ void run(const double (&s1)[VEC], const double (&s2)[VEC], const double (&s3)[VEC],
+                                      double (&acc)[VEC]) const {
+    double ta[NT > 0 ? VEC : 1], tb[NT > 0 ? VEC : 1];
+    if (NT > 0) {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) ta[i] = tb[i] = 0.0;
+    }
+    from<VEC, NS, NT, 0>(s1, s2, s3, acc, ta, tb);
+  }
+};
+
 // The fp32 form's parameter list followed by the table of double immediates.
-template <typename OutT, int NS, int NT = 0>
-__global__ void __launch_bounds__(256)
-    k_ew_chain_f64(const void* __restrict__ in0, const void* __restrict__ p1, const void* __restrict__ p2,
-                   const void* __restrict__ p3, OutT* __restrict__ out, long long n, long long vec_ok, long long meta,
-                   long long mid1, long long inner1, long long mid2, long long inner2, long long mid3,
-                   long long inner3, long long nsteps_ll, long long t0, long long t1, long long t2, long long t3,
-                   long long t4, long long t5, long long t6, long long t7, long long t8, long long t9, long long t10,
-                   long long t11, long long t12, long long t13, long long t14, long long t15, double d0, double d1,
-                   double d2, double d3, double d4, double d5, double d6, double d7) {
-  const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0};
-  const double imms[kMaxImm]              = {d0, d1, d2, d3, d4, d5, d6, d7};
-  const int nsteps  = (int)nsteps_ll;
+#define F64_CHAIN_PARAMS                                                                                              \
+  const void *__restrict__ in0, const void *__restrict__ p1, const void *__restrict__ p2, const void *__restrict__ p3, \
+      OutT *__restrict__ out, long long n, long long vec_ok, long long meta_ll, long long mid1, long long inner1,    \
+      long long mid2, long long inner2, long long mid3, long long inner3, long long nsteps_ll, long long t0,         \
+      long long t1, long long t2, long long t3, long long t4, long long t5, long long t6, long long t7, long long t8, \
+      long long t9, long long t10, long long t11, long long t12, long long t13, long long t14, long long t15,        \
+      double d0, double d1, double d2, double d3, double d4, double d5, double d6, double d7
+#define F64_CHAIN_TABLES                                                                                              \
+  const long long steps[EW_MAX_STEPS + 1] = {t0, t1, t2, t3, t4, t5, t6, t7, t8, t9, t10, t11, t12, t13, t14, t15, 0}; \
+  const double imms[kMaxImm]              = {d0, d1, d2, d3, d4, d5, d6, d7}
+
+struct F64Geometry {
+  long long n, vec_ok, mid1, inner1, mid2, inner2, mid3, inner3;
+};
+
+template <typename OutT, int NS, int NT, class Prog>
+__device__ __forceinline__ void f64_chain_body(const Prog& prog, const void* in0, const void* p1, const void* p2,
+                                               const void* p3, OutT* out, const F64Geometry& geo) {
+  const long long meta = prog.meta(), n = geo.n;
   const int in_type = (int)((meta >> 24) & 15);
-  const SideSpec sd1 = {p1, (int)(meta & 15), (int)((meta >> 4) & 15), mid1, inner1};
-  const SideSpec sd2 = {p2, (int)((meta >> 8) & 15), (int)((meta >> 12) & 15), mid2, inner2};
-  const SideSpec sd3 = {p3, (int)((meta >> 16) & 15), (int)((meta >> 20) & 15), mid3, inner3};
+  const SideSpec sd1 = {p1, (int)(meta & 15), (int)((meta >> 4) & 15), geo.mid1, geo.inner1};
+  const SideSpec sd2 = {p2, (int)((meta >> 8) & 15), (int)((meta >> 12) & 15), geo.mid2, geo.inner2};
+  const SideSpec sd3 = {p3, (int)((meta >> 16) & 15), (int)((meta >> 20) & 15), geo.mid3, geo.inner3};
   const long long tid    = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long stride = (long long)gridDim.x * blockDim.x;
   long long done         = 0;
-  if (vec_ok) {
+  if (geo.vec_ok) {
     const long long nvec = n >> 2;
     for (long long v = tid; v < nvec; v += stride) {
       const long long i0 = v << 2;
@@ -285,7 +363,7 @@ __global__ void __launch_bounds__(256)
       if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<4>(sd1, i0, s1);
       if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<4>(sd2, i0, s2);
       if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<4>(sd3, i0, s3);
-      run_chain<4, NS, NT>(steps, nsteps, imms, s1, s2, s3, acc);
+      prog.template run<4, NS, NT>(s1, s2, s3, acc);
       store_d4<OutT>(out, i0, acc);
     }
     done = nvec << 2;
@@ -296,22 +374,51 @@ __global__ void __launch_bounds__(256)
     if (NS >= 1 && sd1.mode != EW_SIDE_NONE) load_side<1>(sd1, i, s1);
     if (NS >= 2 && sd2.mode != EW_SIDE_NONE) load_side<1>(sd2, i, s2);
     if (NS >= 3 && sd3.mode != EW_SIDE_NONE) load_side<1>(sd3, i, s3);
-    run_chain<1, NS, NT>(steps, nsteps, imms, s1, s2, s3, acc);
+    prog.template run<1, NS, NT>(s1, s2, s3, acc);
     out[i] = out_of<OutT>(acc[0]);
   }
+}
+
+template <typename OutT, int NS, int NT = 0>
+__global__ void __launch_bounds__(256) k_ew_chain_f64(F64_CHAIN_PARAMS) {
+  grid_dependency_sync();
+  F64_CHAIN_TABLES;
+  const DynF64Program prog = {steps, (int)nsteps_ll, meta_ll, imms};
+  f64_chain_body<OutT, NS, NT>(prog, in0, p1, p2, p3, out, F64Geometry{n, vec_ok, mid1, inner1, mid2, inner2, mid3, inner3});
+}
+
+// The same with the program fixed at build time (see ew_static.cu for the scheme).
+template <typename OutT, int NS, int NT, unsigned long long META, uint32_t... SIG>
+__global__ void __launch_bounds__(256) k_ew_chain_f64_static(F64_CHAIN_PARAMS) {
+  grid_dependency_sync();
+  F64_CHAIN_TABLES;
+  const StaticF64Program<META, SIG...> prog = {steps, imms};
+  f64_chain_body<OutT, NS, NT>(prog, in0, p1, p2, p3, out, F64Geometry{n, vec_ok, mid1, inner1, mid2, inner2, mid3, inner3});
+}
+
+template <uint32_t... SIG>
+StaticChainKey MakeF64Key(const char* base, long long meta) {
+  StaticChainKey k = {base, meta, (int)sizeof...(SIG), {SIG...}};
+  return k;
 }
 
 }  // namespace
 
 #define REG_F64_CHAIN(NSNAME, NS)                                                                  \
-  CINN_B200_REGISTER_KERNEL("ew_chain_f64_f64_" NSNAME, 39, 256, k_ew_chain_f64<double, NS>);     \
-  CINN_B200_REGISTER_KERNEL("ew_chain_f64_f32_" NSNAME, 39, 256, k_ew_chain_f64<float, NS>);      \
-  CINN_B200_REGISTER_KERNEL("ew_chain_f64_bool_" NSNAME, 39, 256, k_ew_chain_f64<uint8_t, NS>)
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_f64_f64_" NSNAME, 39, 256, k_ew_chain_f64<double, NS>);     \
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_f64_f32_" NSNAME, 39, 256, k_ew_chain_f64<float, NS>);      \
+  CINN_B200_REGISTER_KERNEL_PDL("ew_chain_f64_bool_" NSNAME, 39, 256, k_ew_chain_f64<uint8_t, NS>)
 REG_F64_CHAIN("s0", 0);
 REG_F64_CHAIN("s1", 1);
 REG_F64_CHAIN("s3", 3);
-CINN_B200_REGISTER_KERNEL("ew_chain_f64_f64_s3t", 39, 256, k_ew_chain_f64<double, 3, 2>);
-CINN_B200_REGISTER_KERNEL("ew_chain_f64_f32_s3t", 39, 256, k_ew_chain_f64<float, 3, 2>);
-CINN_B200_REGISTER_KERNEL("ew_chain_f64_bool_s3t", 39, 256, k_ew_chain_f64<uint8_t, 3, 2>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_chain_f64_f64_s3t", 39, 256, k_ew_chain_f64<double, 3, 2>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_chain_f64_f32_s3t", 39, 256, k_ew_chain_f64<float, 3, 2>);
+CINN_B200_REGISTER_KERNEL_PDL("ew_chain_f64_bool_s3t", 39, 256, k_ew_chain_f64<uint8_t, 3, 2>);
+
+
+#define STATIC_F64_CHAIN(ID, BASE, OutT, NS, NT, META, ...)                                                        \
+  CINN_B200_REGISTER_KERNEL_PDL("ew_f64_static_" #ID, 39, 256, k_ew_chain_f64_static<OutT, NS, NT, META##ull, __VA_ARGS__>); \
+  static int cinn_b200_static_f64_chain_##ID = RegisterStaticChain(MakeF64Key<__VA_ARGS__>(BASE, META##ll), "ew_f64_static_" #ID)
+#include "ew_f64_static_table.inc"
 
 }  // namespace cinn_b200

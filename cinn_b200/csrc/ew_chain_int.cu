@@ -41,6 +41,52 @@ __device__ __forceinline__ T int_unary(int op, T x) {
   }
 }
 
+// Integer pow as the reference's host intrinsics define it (cinn/runtime/cpu/host_intrinsics.cc:234-239, 255):
+// (T)pow((double)x, (double)y) with the truncating x86 conversion, which yields the most negative value for
+// anything out of range; int32 alone returns -1 for 0 to a negative power.  Computed exactly in integers: the
+// magnitude by repeated squaring in 64 bits with overflow detection, then rounded once to double (to nearest even)
+// and converted back.  Everything a double holds exactly -- every int32 result, int64 results up to 2^53 -- equals
+// the host function; beyond 2^53 the host returns glibc's pow, which is within one ulp of the true power but not
+// always the nearest double (9^17 lies exactly between two doubles and glibc returns the upper one), so results
+// there may differ by one step of the double grid.
+template <typename T>
+__device__ __noinline__ T int_pow(T x, T y) {
+  constexpr bool k32 = sizeof(T) == 4;
+  const T kMin       = k32 ? (T)INT32_MIN : (T)INT64_MIN;
+  // the exponent as double: beyond 2^53 every double is an even integer
+  const unsigned long long ymag = y < 0 ? 0ull - (unsigned long long)y : (unsigned long long)y;
+  const bool odd                = ymag <= (1ull << 53) && (ymag & 1);
+  if (y < 0) {
+    if (x == 0) return k32 ? (T)-1 : kMin;  // int64: pow(0, -n) is infinite
+    if (x == 1) return 1;
+    if (x == -1) return odd ? (T)-1 : (T)1;
+    return 0;  // |x| >= 2: a magnitude below one truncates to zero
+  }
+  unsigned long long base = x < 0 ? 0ull - (unsigned long long)(long long)x : (unsigned long long)x;
+  unsigned long long mag = 1, e = ymag;
+  bool over = false;
+  while (e) {
+    if (e & 1) {
+      over |= __umul64hi(mag, base) != 0;
+      mag *= base;
+    }
+    e >>= 1;
+    if (e) {
+      over |= __umul64hi(base, base) != 0;
+      base *= base;
+    }
+  }
+  const bool neg = x < 0 && odd;
+  if (k32) {
+    if (over || mag > 0x80000000ull || (!neg && mag == 0x80000000ull)) return kMin;
+    return (T)(neg ? 0ll - (long long)mag : (long long)mag);
+  }
+  const double d = __ull2double_rn(mag);
+  if (over || d >= 9223372036854775808.0) return kMin;
+  const long long v = __double2ll_rz(d);
+  return (T)(neg ? -v : v);
+}
+
 template <typename T>
 __device__ __forceinline__ T int_binary(int op, T l, T r) {
   using U = typename UnsignedOf<T>::type;
@@ -52,6 +98,7 @@ __device__ __forceinline__ T int_binary(int op, T l, T r) {
     case EW_DIV: return r == 0 ? 0 : ((r == -1) ? (T)(U(0) - (U)l) : l / r);
     case EW_MAX: return l > r ? l : r;
     case EW_MIN: return l < r ? l : r;
+    case EW_POW: return int_pow<T>(l, r);
     case EW_EQ: return l == r;
     case EW_NE: return l != r;
     case EW_GT: return l > r;

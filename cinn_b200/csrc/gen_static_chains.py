@@ -266,13 +266,32 @@ INT_GROUPS = [
 INT_T = {"i32": "int32_t", "i64": "long long", "bool": "uint8_t", "f32": "float"}
 
 
-def int_table_lines():
+F64_GROUPS = [
+    group("affine_abs_f64", _i("A", "float64"), ["scale t0 = A ; scale=0.1 bias=1e-05", "abs t1 = t0"], "t1", "float64"),
+    group("abs_add_f64", _i("AB", "float64"), ["elementwise_add t0 = A B", "abs t1 = t0"], "t1", "float64"),
+    group("add_f64", _i("AB", "float64"), ["elementwise_add y = A B ; axis=-1"], "y", "float64"),
+    group("sub_f64", _i("AB", "float64"), ["subtract y = A B ; axis=-1"], "y", "float64"),
+    group("mul_f64", _i("AB", "float64"), ["elementwise_mul y = A B ; axis=-1"], "y", "float64"),
+    group("div_f64", _i("AB", "float64"), ["divide y = A B ; axis=-1"], "y", "float64"),
+    group("max_f64", _i("AB", "float64"), ["max y = A B ; axis=-1"], "y", "float64"),
+    group("less_than_f64", _i("AB", "float64"), ["less_than y = A B ; axis=-1"], "y", "bool"),
+    group("mul_add_f64", _i("ABC", "float64"), ["elementwise_mul t = A B ; axis=-1", "elementwise_add y = t C ; axis=-1"], "y", "float64"),
+    group("scale_f64", _i("A", "float64"), ["scale y = A ; scale=2.0 bias=1.0"], "y", "float64"),
+    group("relu_f64", _i("A", "float64"), ["relu y = A"], "y", "float64"),
+    group("cast_f64_f32", _i("A", "float64"), ["cast y = A ; dtype=float32"], "y", "float32"),
+]
+F64_T = {"f64": "double", "f32": "float", "bool": "uint8_t"}
+
+
+def typed_table_lines(groups, kernel_re, line_of):
+    """One table line per distinct program among `groups` whose interpreted kernel's name matches `kernel_re`;
+    line_of(name, kernel, match, ns, nt, meta, sig) formats it."""
     import cinn_b200
     L = cinn_b200.lib()
     cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
     try:
         seen, lines, skipped = {}, [], []
-        for name, desc in INT_GROUPS:
+        for name, desc in groups:
             try:
                 g = cinn_b200.FusedGroup(desc)
             except cinn_b200.CinnB200Error as e:
@@ -281,23 +300,36 @@ def int_table_lines():
             text = g.launch_text()
             g.release()
             kernel = [l for l in text.splitlines() if l.startswith("launch ")][0].split()[2]
-            m = re.match(r"ew_chain_int_(i32|i64)_(i32|i64|bool|f32)(_s\w+)$", kernel)
+            m = re.match(kernel_re, kernel)
             if not m:
-                skipped.append("%s: not an integer chain (%s)" % (name, kernel))
+                skipped.append("%s: not a chain of this form (%s)" % (name, kernel))
                 continue
             args = {int(l.split()[1]): int(l.split()[3]) for l in text.splitlines() if l.startswith("arg ") and l.split()[2] == "int"}
             meta, nsteps = args[7], args[14]
             sig = tuple(args[15 + k] & 0xffffffff for k in range(nsteps))
-            ns, nt, _ = VARIANT[m.group(3)]
+            ns, nt, _ = VARIANT[m.groups()[-1]]
             if nsteps == 0 or (kernel, meta, sig) in seen:
                 skipped.append("%s: empty or repeated program" % name)
                 continue
             seen[(kernel, meta, sig)] = name
-            lines.append('STATIC_INT_CHAIN(%s, "%s", %s, %s, %d, %d, %d, %s);' % (
-                name, kernel, INT_T[m.group(1)], INT_T[m.group(2)], ns, nt, meta, ", ".join("0x%08xu" % w for w in sig)))
+            lines.append(line_of(name, kernel, m, ns, nt, meta, ", ".join("0x%08xu" % w for w in sig)))
         return lines, skipped
     finally:
         L.cinn_b200_set_option(b"enable_static_chains", 1)
+
+
+def int_table_lines():
+    return typed_table_lines(
+        INT_GROUPS, r"ew_chain_int_(i32|i64)_(i32|i64|bool|f32)(_s\w+)$",
+        lambda name, kernel, m, ns, nt, meta, sig: 'STATIC_INT_CHAIN(%s, "%s", %s, %s, %d, %d, %d, %s);' % (
+            name, kernel, INT_T[m.group(1)], INT_T[m.group(2)], ns, nt, meta, sig))
+
+
+def f64_table_lines():
+    return typed_table_lines(
+        F64_GROUPS, r"ew_chain_f64_(f64|f32|bool)(_s\w+)$",
+        lambda name, kernel, m, ns, nt, meta, sig: 'STATIC_F64_CHAIN(%s, "%s", %s, %d, %d, %d, %s);' % (
+            name, kernel, F64_T[m.group(1)], ns, nt, meta, sig))
 
 
 def builder_programs():
@@ -528,7 +560,7 @@ def tables():
     return [("ew_static_table.inc", HEADER + "\n".join(lines) + "\n", skipped, len(lines)),
             ("chain_reduce_static_table.inc", REDUCE_HEADER + "\n".join(rlines) + "\n", rskipped, len(rlines)),
             ("ew_dag_static_table.inc", dag_header + "\n".join(dlines) + "\n", dskipped, len(dlines)),
-            row_table(), int_table()]
+            row_table(), int_table(), f64_table()]
 
 
 def int_table():
@@ -536,6 +568,13 @@ def int_table():
     header = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_INT_CHAIN(id, interpreted kernel, value type,\n"
               "// output type, side inputs, temporaries, meta word, step words...).\n")
     return ("ew_int_static_table.inc", header + "\n".join(lines) + "\n", skipped, len(lines))
+
+
+def f64_table():
+    lines, skipped = f64_table_lines()
+    header = ("// Generated by gen_static_chains.py -- do not edit.  STATIC_F64_CHAIN(id, interpreted kernel, output type,\n"
+              "// side inputs, temporaries, meta word, step words...).\n")
+    return ("ew_f64_static_table.inc", header + "\n".join(lines) + "\n", skipped, len(lines))
 
 
 def row_table():

@@ -457,12 +457,12 @@ int cinn_b200_col_reduce_sharded_f32(cinn_b200_peer_ctx* c, int kind, const floa
   return Launch(c, fn, c->rank, 1, rows_local, inner, n_red, n_comb, n_gath, all_gather, stream);
 }
 
-int cinn_b200_col_reduce_sharded_f32_emulated(cinn_b200_peer_ctx* c, int kind, const float* const* x_per_rank,
-                                              long long rows_local, long long inner, float* const* out_per_rank,
-                                              int all_gather, void* stream) {
-  if (!c || !c->emulated || !x_per_rank || !out_per_rank)
+int cinn_b200_col_reduce_sharded_f32_emulated_ranks(cinn_b200_peer_ctx* c, int kind, const float* const* x_per_rank,
+                                                    long long rows_local, long long inner, float* const* out_per_rank,
+                                                    int all_gather, int rank0, int nranks, void* stream) {
+  if (!c || !c->emulated || !x_per_rank || !out_per_rank || rank0 < 0 || nranks < 1 || rank0 + nranks > c->world)
     return SetLastError(CINN_B200_EINVAL, "col_reduce_sharded_emulated: bad argument");
-  for (int r = 0; r < c->world; ++r) {
+  for (int r = rank0; r < rank0 + nranks; ++r) {
     if (!x_per_rank[r] || !out_per_rank[r] ||
         ((reinterpret_cast<uintptr_t>(x_per_rank[r]) | reinterpret_cast<uintptr_t>(out_per_rank[r])) & 15u))
       return SetLastError(CINN_B200_EINVAL, "col_reduce_sharded_emulated: buffers must be non-null and 16-byte aligned");
@@ -471,9 +471,17 @@ int cinn_b200_col_reduce_sharded_f32_emulated(cinn_b200_peer_ctx* c, int kind, c
   }
   const void* fn = nullptr;
   int n_red = 0, n_comb = 0, n_gath = 0;
-  int rc = PlanLaunch(c, kind, rows_local, inner, all_gather, c->world, &fn, &n_red, &n_comb, &n_gath);
+  int rc = PlanLaunch(c, kind, rows_local, inner, all_gather, nranks, &fn, &n_red, &n_comb, &n_gath);
   if (rc != CINN_B200_OK) return rc;
-  return Launch(c, fn, 0, c->world, rows_local, inner, n_red, n_comb, n_gath, all_gather, stream);
+  return Launch(c, fn, rank0, nranks, rows_local, inner, n_red, n_comb, n_gath, all_gather, stream);
+}
+
+int cinn_b200_col_reduce_sharded_f32_emulated(cinn_b200_peer_ctx* c, int kind, const float* const* x_per_rank,
+                                              long long rows_local, long long inner, float* const* out_per_rank,
+                                              int all_gather, void* stream) {
+  if (!c) return SetLastError(CINN_B200_EINVAL, "col_reduce_sharded_emulated: bad argument");
+  return cinn_b200_col_reduce_sharded_f32_emulated_ranks(c, kind, x_per_rank, rows_local, inner, out_per_rank, all_gather,
+                                                         0, c->world, stream);
 }
 
 }  // extern "C"

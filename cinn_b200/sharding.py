@@ -183,15 +183,18 @@ class EmulatedFusedShardedReduceAxis0:
         _lib.check(_lib.lib().cinn_b200_peer_create_emulated(world, self.inner, ctypes.byref(ctx)))
         self._ctx = ctx
 
-    def __call__(self, x_slices, outs):
+    def __call__(self, x_slices, outs, ranks=None):
+        """ranks = (first, count) launches only those ranks: with fewer than the world their bounded waits run out
+        (about a quarter of a second) and the context turns failed -- the give-up path, exercised without a peer."""
         import ctypes
         from . import _lib
         xs = (ctypes.c_void_p * self.world)(*[x.data_ptr() for x in x_slices])
         os_ = (ctypes.c_void_p * self.world)(*[o.data_ptr() for o in outs])
         stream = torch.cuda.current_stream().cuda_stream
-        _lib.check(_lib.lib().cinn_b200_col_reduce_sharded_f32_emulated(
+        first, count = ranks if ranks is not None else (0, self.world)
+        _lib.check(_lib.lib().cinn_b200_col_reduce_sharded_f32_emulated_ranks(
             self._ctx, FusedShardedReduceAxis0.KINDS[self.kind], xs, self.rows_local, self.inner, os_,
-            1 if self.all_gather else 0, ctypes.c_void_p(stream)))
+            1 if self.all_gather else 0, first, count, ctypes.c_void_p(stream)))
         return outs
 
     def status(self):

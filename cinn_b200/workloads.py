@@ -226,13 +226,14 @@ def _draw(rng, shape, dtype):
 
 def generic_chain(kind, shape=(8192, 8192), seed=5):
     """Elementwise groups that only the generic chain kernels cover.  kind: leaky_relu_f32 (select on a mask
-    input), abs_add_f32, greater_than_f32 (bool output), abs_add_i32, affine_f64."""
+    input), abs_add_f32, greater_than_f32 (bool output), abs_add_i32, abs_add_f64, affine_f64."""
     s = _shape(shape)
     table = {
         "abs_add_f32": (["A float32", "B float32"], ["op elementwise_add t0 = A B", "op abs t1 = t0"], "t1", "float32"),
         "select_f32": (["M bool", "A float32", "B float32"], ["op select t0 = M A B"], "t0", "float32"),
         "greater_than_f32": (["A float32", "B float32"], ["op greater_than t0 = A B"], "t0", "bool"),
         "abs_add_i32": (["A int32", "B int32"], ["op elementwise_add t0 = A B", "op abs t1 = t0"], "t1", "int32"),
+        "abs_add_f64": (["A float64", "B float64"], ["op elementwise_add t0 = A B", "op abs t1 = t0"], "t1", "float64"),
         "affine_f64": (["A float64"], ["op scale t0 = A ; scale=0.1 bias=1e-05", "op abs t1 = t0"], "t1", "float64"),
     }
     ins, ops, out, out_dtype = table[kind]

@@ -289,6 +289,16 @@ int cinn_b200_peer_create_emulated(int world, long long max_inner, cinn_b200_pee
 int cinn_b200_col_reduce_sharded_f32_emulated(cinn_b200_peer_ctx* ctx, int kind, const float* const* x_per_rank,
                                               long long rows_local, long long inner, float* const* out_per_rank,
                                               int all_gather, void* stream);
+/*
+ * The emulated launch restricted to ranks rank0 .. rank0 + nranks - 1 (the arrays are still indexed by rank; only
+ * those entries are read).  With fewer ranks than the world, the launched ranks wait for partials that never come:
+ * their bounded waits run out after about a quarter of a second, the call counts as failed
+ * (cinn_b200_device_status, cinn_b200_peer_status) and later calls on the context return without touching `out`.
+ * This is how the give-up path is exercised without a second GPU or a process that dies.
+ */
+int cinn_b200_col_reduce_sharded_f32_emulated_ranks(cinn_b200_peer_ctx* ctx, int kind, const float* const* x_per_rank,
+                                                    long long rows_local, long long inner, float* const* out_per_rank,
+                                                    int all_gather, int rank0, int nranks, void* stream);
 
 /*
  * Device-side status of the current device: the number of bounded waits on asynchronous copies that gave up

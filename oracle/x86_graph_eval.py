@@ -129,6 +129,9 @@ def _int_binary(t, a, b):
             if t == "floor_divide":
                 return np.where(b == 0, 0, np.where(b == -1, neg, fl)).astype(dt)
             return np.where((b == 0) | (b == -1), 0, md).astype(dt)
+        if t == "pow":
+            shape = np.broadcast_shapes(a.shape, b.shape)
+            return orc.pow_int(np.broadcast_to(a, shape), np.broadcast_to(b, shape))
         if t == "max":
             return np.where(a > b, a, b).astype(dt)
         if t == "min":
@@ -158,7 +161,7 @@ def _int_binary(t, a, b):
     raise NotImplementedError(t)
 
 
-INT_BINARY = {"elementwise_add", "subtract", "elementwise_mul", "divide", "max", "min", "equal", "not_equal",
+INT_BINARY = {"elementwise_add", "subtract", "elementwise_mul", "divide", "max", "min", "pow", "equal", "not_equal",
               "greater_than", "less_than", "greater_equal", "less_equal", "mod", "remainder", "floor_divide",
               "logical_and", "logical_or", "logical_xor", "bitwise_and", "bitwise_or", "bitwise_xor", "left_shift",
               "right_shift", "logical_right_shift"}

@@ -165,6 +165,16 @@ def cast_f32_int(x, dtype):
     return y
 
 
+def pow_int(a, b):
+    """Integer pow (int32 or int64 arrays of one shape) as the host intrinsic computes it."""
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    assert a.dtype == b.dtype and a.dtype in (np.int32, np.int64) and a.shape == b.shape
+    y = np.empty(a.shape, a.dtype)
+    fn = lib().orc_pow_i32 if a.dtype == np.int32 else lib().orc_pow_i64
+    fn(_p(a), _p(b), _p(y), _i64(a.size))
+    return y
+
+
 def cast_f32_f16(x):
     x = _f32(x)
     y = np.empty(x.shape, np.float16)

@@ -556,6 +556,48 @@ def test_integer_chains_bit_exact(oracle, bits, index):
     assert got.dtype == ref.dtype and np.array_equal(got, ref), (make.__name__, comp.groups())
 
 
+@pytest.mark.parametrize("bits", [32, 64])
+def test_integer_pow_bit_exact(oracle, bits):
+    """pow on integers follows the host intrinsic (cinn/runtime/cpu/host_intrinsics.cc:234-239, 255): through double
+    pow and the truncating conversion -- zero to a negative power, negative exponents, overflow and results beyond
+    2^53 included."""
+    T = common.Int(bits)
+    npt = np.int32 if bits == 32 else np.int64
+    lo, hi = (-2 ** 31, 2 ** 31 - 1) if bits == 32 else (-2 ** 63, 2 ** 63 - 1)
+    rng = np.random.default_rng(77 + bits)
+    shape = (41, 64)
+    X = rng.integers(-12, 13, shape).astype(npt)
+    Y = rng.integers(-3, 24, shape).astype(npt)
+    X[0, :12] = [lo, hi, 0, 0, 1, -1, -1, 2, -2, 46341, -46341, 3]
+    Y[0, :12] = [1, 1, -1, 0, hi, hi, lo, 62, 63, 2, 2, 39]
+    X[1, :8] = [2, 2, -2, 3037000500, -3037000499 if bits == 64 else -3, 7, lo, hi][:8] if bits == 64 else [2, 2, -2, 1290, -1291, 7, lo, hi]
+    Y[1, :8] = [31, 30, 31, 2, 2, 22 if bits == 64 else 11, 2, 2]
+    X[2] = rng.integers(lo, hi, shape[1], dtype=npt)   # any base, exponent 0..2
+    Y[2] = rng.integers(0, 3, shape[1]).astype(npt)
+    X[3] = rng.integers(-3, 4, shape[1]).astype(npt)   # small bases, any exponent
+    Y[3] = rng.integers(lo, hi, shape[1], dtype=npt)
+    b = NetBuilder("int_pow_%d" % bits)
+    x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+    z = b.pow(x, y)
+    comp, out = run_program(b, {"X": X, "Y": Y}, [z])
+    assert all(p.split()[1].startswith("ew_chain_int_") for _, p in comp.groups()), comp.groups()
+    ref = oracle_program(comp, {"X": X, "Y": Y})[str(z)]
+    got = out[str(z)]
+    assert got.dtype == ref.dtype
+    # Beyond 2^53 the host function returns whatever double pow returns for a power that no double holds exactly;
+    # glibc's pow is within one ulp of it but not always the nearest double (9^17 sits exactly between two doubles and
+    # glibc returns the upper one), while the kernel rounds the exact integer power to nearest-even.  There the two
+    # may differ by one step of the double grid; everything a double holds exactly must be equal.
+    mag = np.abs(ref.astype(np.float64))
+    step = np.where(mag > 2.0 ** 53, 2.0 ** (np.floor(np.log2(np.maximum(mag, 1.0))) - 52), 0.0)
+    diff = np.abs(got.astype(np.float64) - ref.astype(np.float64))
+    lowest = np.iinfo(npt).min
+    bad = np.argwhere((diff > step) | ((got == lowest) != (ref == lowest)))
+    assert bad.size == 0, [(int(X[i, j]), int(Y[i, j]), int(got[i, j]), int(ref[i, j])) for i, j in bad[:8]]
+    if bits == 32:
+        assert np.array_equal(got, ref)
+
+
 # ---- float64 chains ---------------------------------------------------------------------------------------------
 
 def f64_programs():

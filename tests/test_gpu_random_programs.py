@@ -127,7 +127,9 @@ def _random_program_case(seed, half, passes):
         assert (err <= tol).all(), (seed, str(f), float(err.max()), [p for _, p in comp.groups()])
 
 
-def build_random_int_program(rng, b, shape, bits):
+def build_random_int_program(rng, b, shape, bits, extended=False):
+    """extended: also draws integer pow (small bases, exponents from -2 to 6) and fetches a value cast to a 16-bit
+    float."""
     T = common.Int(bits)
     npt = np.int32 if bits == 32 else np.int64
     feeds = {}
@@ -143,9 +145,14 @@ def build_random_int_program(rng, b, shape, bits):
     fetch = []
     for step in range(int(rng.integers(4, 10))):
         x = full[int(rng.integers(0, len(full)))]
-        kind = str(rng.choice(["unary", "binary", "vec", "const", "shift", "divmod", "select", "reduce"]))
+        kinds = ["unary", "binary", "vec", "const", "shift", "divmod", "select", "reduce"] + (["pow", "pow"] if extended else [])
+        kind = str(rng.choice(kinds))
         if kind == "unary":
             y = getattr(b, str(rng.choice(["abs", "negative", "bitwise_not", "identity", "relu"])))(x)
+        elif kind == "pow":
+            o = full[int(rng.integers(0, len(full)))]
+            base = b.subtract(b.mod(x, const(int(rng.integers(5, 40)))), const(int(rng.integers(0, 6))))
+            y = b.pow(base, b.subtract(b.mod(o, const(9)), const(2)))
         elif kind == "binary":
             op = str(rng.choice(["add", "subtract", "multiply", "max", "min", "bitwise_and", "bitwise_or", "bitwise_xor"]))
             o = full[int(rng.integers(0, len(full)))]
@@ -167,16 +174,18 @@ def build_random_int_program(rng, b, shape, bits):
     fetch.append(full[-1])
     if rng.random() < 0.5:
         fetch.append(b.cast(full[len(full) // 2], "float32"))
+    if extended:
+        fetch.append(b.cast(full[int(rng.integers(0, len(full)))], "float16"))
     return feeds, fetch
 
 
 @pytest.mark.parametrize("bits", [32, 64])
-@pytest.mark.parametrize("seed", range(40))
+@pytest.mark.parametrize("seed", range(60))
 def test_random_integer_program_is_bit_exact(oracle, seed, bits):
     rng = np.random.default_rng(5000 + seed)
     shape = [(6, 40), (3, 5, 16), (33,), (4, 9, 28)][seed % 4]
     b = NetBuilder("randint%d" % seed)
-    feeds, fetch = build_random_int_program(rng, b, shape, bits)
+    feeds, fetch = build_random_int_program(rng, b, shape, bits, extended=seed >= 40)
     comp = Computation.build_and_compile(TARGET, b, fetch=[str(f) for f in fetch])
     for k, v in feeds.items():
         if k in comp.get_all_tensor_names():

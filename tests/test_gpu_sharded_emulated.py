@@ -103,3 +103,43 @@ def test_sentinel_valued_result_is_delivered_as_default_nan():
             assert not bits.any()
     finally:
         op.close()
+
+
+def test_missing_rank_runs_the_waits_out_and_the_context_turns_failed():
+    """Three of four ranks launched: the partials of the fourth never arrive, every wait gives up within its budget
+    (no fault, no hang), the give-up is counted, the context reports failed and a later call leaves its outputs
+    alone."""
+    import ctypes
+    import cinn_b200
+    from cinn_b200 import sharding
+    world, full = 4, (8, 16, 64)
+    dev = torch.device("cuda:0")
+    L = cinn_b200.lib()
+    cleared = ctypes.c_uint(0)
+    L.cinn_b200_device_status(ctypes.byref(cleared))  # start from a clean counter
+    op = sharding.EmulatedFusedShardedReduceAxis0("sum", full, world, all_gather=True)
+    try:
+        xs = [torch.ones((2,) + full[1:], device=dev) for _ in range(world)]
+        outs = [torch.full(op.out_shape, -5.0, device=dev) for _ in range(world)]
+        op(xs, outs, ranks=(0, 3))
+        torch.cuda.synchronize()
+        gave_up = ctypes.c_uint(0)
+        assert L.cinn_b200_device_status(ctypes.byref(gave_up)) == 0 and gave_up.value >= 1
+        assert op.status() == 1
+        # the context stays answerable; a complete launch now returns at once without writing results
+        outs2 = [torch.full(op.out_shape, -7.0, device=dev) for _ in range(world)]
+        op(xs, outs2)
+        torch.cuda.synchronize()
+        assert all(bool((o == -7.0).all()) for o in outs2)
+        assert op.status() == 1
+    finally:
+        op.close()
+    # a fresh context on the same device works
+    op = sharding.EmulatedFusedShardedReduceAxis0("sum", full, world, all_gather=True)
+    try:
+        outs = [torch.zeros(op.out_shape, device=dev) for _ in range(world)]
+        op(xs, outs)
+        torch.cuda.synchronize()
+        assert op.status() == 0 and all(bool((o == 8.0).all()) for o in outs)
+    finally:
+        op.close()

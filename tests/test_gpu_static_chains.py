@@ -21,7 +21,7 @@ GEN = importlib.util.module_from_spec(_spec)
 _spec.loader.exec_module(GEN)
 
 TORCH_T = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16, "bool": torch.bool,
-           "int32": torch.int32, "int64": torch.int64}
+           "int32": torch.int32, "int64": torch.int64, "float64": torch.float64}
 
 
 def _tensors(desc, seed, misalign):
@@ -69,7 +69,10 @@ def _run(desc, name, static, seed, misalign):
     return [o.view(torch.uint8).cpu().numpy().copy() for o in outs], kernels
 
 
-@pytest.mark.parametrize("name,desc", GEN.GROUPS + GEN.INT_GROUPS, ids=[n for n, _ in GEN.GROUPS + GEN.INT_GROUPS])
+ALL_CHAINS = GEN.GROUPS + GEN.INT_GROUPS + GEN.F64_GROUPS
+
+
+@pytest.mark.parametrize("name,desc", ALL_CHAINS, ids=[n for n, _ in ALL_CHAINS])
 @pytest.mark.parametrize("variant", ["table_shape", "ragged", "misaligned"])
 def test_static_kernel_equals_interpreter(name, desc, variant):
     if variant == "ragged":

@@ -297,3 +297,21 @@ def test_cast_and_squeeze_relations_of_the_reference_api_tests():
         b = NetBuilder("sq")
         out = b.squeeze(b.create_input(common.Float(32), (4, 1, 7, 1), "In"), axes)
         assert out.shape == want, (axes, out.shape)
+
+
+def test_integer_pow_known_answers():
+    """The host intrinsics' integer pow (cinn/runtime/cpu/host_intrinsics.cc:234-239, 255): double pow, truncating
+    conversion with the most negative value for anything out of range, -1 for int32 zero to a negative power."""
+    from oracle import x86_oracle as orc
+    i32 = lambda v: np.array(v, np.int32)  # noqa: E731
+    i64 = lambda v: np.array(v, np.int64)  # noqa: E731
+    lo32, lo64 = -2 ** 31, -2 ** 63
+    cases32 = [(0, -1, -1), (2, 10, 1024), (-3, 3, -27), (2, 31, lo32), (-2, 31, lo32), (2, -1, 0), (-1, -3, -1),
+               (-1, -4, 1), (46341, 2, lo32), (46340, 2, 2147395600), (7, 0, 1), (0, 0, 1), (1, 2 ** 31 - 1, 1)]
+    a, b, want = zip(*cases32)
+    assert orc.pow_int(i32(a), i32(b)).tolist() == list(want)
+    cases64 = [(0, -1, lo64), (2, 62, 2 ** 62), (2, 63, lo64), (-2, 63, lo64), (3, 39, int(float(3 ** 39))),
+               (-3, 39, -int(float(3 ** 39))), (10, 18, 10 ** 18), (3037000500, 2, lo64),
+               (3037000499, 2, int(float(3037000499 ** 2))), (5, -2, 0), (-1, 2 ** 62 + 1, 1), (2 ** 53 + 1, 1, 2 ** 53)]
+    a, b, want = zip(*cases64)
+    assert orc.pow_int(i64(a), i64(b)).tolist() == list(want)

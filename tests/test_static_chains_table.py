@@ -25,8 +25,8 @@ def test_committed_table_is_up_to_date_and_registered():
         committed = open(os.path.join(ROOT, "cinn_b200", "csrc", fname)).read()
         assert committed == text, "run python cinn_b200/csrc/gen_static_chains.py and rebuild the library"
         total += count
-        for m in re.finditer(r"^STATIC_(CHAIN_REDUCE_ROW|CHAIN_REDUCE_COL|CHAIN|DAG|ROW_PROGRAM|INT_CHAIN)\((\w+),", text, flags=re.M):
-            prefix = {"CHAIN": "ew_static_", "DAG": "ew_dag_static_", "ROW_PROGRAM": "row_program_static_", "INT_CHAIN": "ew_int_static_"}.get(m.group(1), "chain_reduce_static_")
+        for m in re.finditer(r"^STATIC_(CHAIN_REDUCE_ROW|CHAIN_REDUCE_COL|CHAIN|DAG|ROW_PROGRAM|INT_CHAIN|F64_CHAIN)\((\w+),", text, flags=re.M):
+            prefix = {"CHAIN": "ew_static_", "DAG": "ew_dag_static_", "ROW_PROGRAM": "row_program_static_", "INT_CHAIN": "ew_int_static_", "F64_CHAIN": "ew_f64_static_"}.get(m.group(1), "chain_reduce_static_")
             assert L.cinn_b200_get_kernel((prefix + m.group(2)).encode()), prefix + m.group(2)
     assert L.cinn_b200_num_static_chains() == total >= 60
 
