@@ -349,6 +349,7 @@ PROFILE_GROUPS = {
     "chain_abs_add_f32": lambda W: W.generic_chain("abs_add_f32"),
     "chain_select_f32": lambda W: W.generic_chain("select_f32"),
     "chain_abs_add_i32": lambda W: W.generic_chain("abs_add_i32"),
+    "chain_abs_add_f64": lambda W: W.generic_chain("abs_add_f64", (8192, 4096)),
     "reduce_sum_f16_rows": lambda W: W.generic_reduce("sum", "float16", axis=1),
     "reduce_sum_i32_cols": lambda W: W.generic_reduce("sum", "int32", axis=0),
     "chain_reduce_rows": lambda W: W.chain_reduce("sum_abs_diff", axis=1),

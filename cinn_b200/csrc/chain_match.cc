@@ -93,7 +93,7 @@ uint64_t Word(int op, int asel, int bsel, int role, float imm) {
 }
 
 bool IsFloatType(DType t) { return t == DType::kFloat32 || t == DType::kFloat16 || t == DType::kBFloat16; }
-bool IsIntType(DType t) { return t == DType::kInt32 || t == DType::kInt64; }
+bool IsIntType(DType t) { return t == DType::kInt32 || t == DType::kInt64 || t == DType::kUInt8; }
 bool IsAnyOp(const std::string& t) {
   return UnaryCodes().count(t) || BinaryCodes().count(t) || IntUnaryCodes().count(t) || IntBinaryCodes().count(t);
 }
@@ -392,6 +392,7 @@ int DTypeKernelCode(DType t) {
     case DType::kInt32: return EW_I32;
     case DType::kInt64: return EW_I64;
     case DType::kFloat64: return EW_F64;
+    case DType::kUInt8: return EW_U8;
     default: return -1;
   }
 }
@@ -404,6 +405,7 @@ const char* DTypeKernelName(DType t) {
     case DType::kInt32: return "i32";
     case DType::kInt64: return "i64";
     case DType::kFloat64: return "f64";
+    case DType::kUInt8: return "u8";
     default: return nullptr;
   }
 }
@@ -468,10 +470,16 @@ std::unique_ptr<CompiledGroup> MatchChainOfClass(const GroupDesc& g, const Devic
       cb.Fail("no integer arithmetic in the group");
       return nullptr;
     }
-    if (out.dtype != DType::kInt32 && out.dtype != DType::kInt64 && out.dtype != DType::kBool && out.dtype != DType::kFloat32) {
+    if (!IsIntType(out.dtype) && out.dtype != DType::kBool && out.dtype != DType::kFloat32) {
       cb.Fail(std::string("an integer chain cannot store ") + DTypeName(out.dtype));
       return nullptr;
     }
+    if (cb.compute == DType::kUInt8)
+      for (auto& op : g.ops)
+        if (op.type == "pow" || op.type == "clz") {
+          cb.Fail("'" + op.type + "' is not offered for uint8 (the reference's host intrinsics define it for int32 / int64 only)");
+          return nullptr;
+        }
   }
 
   // Walk back from a value collecting primitive steps in reverse order.  A segment is one such walk: the main one

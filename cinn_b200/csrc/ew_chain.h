@@ -72,7 +72,7 @@ constexpr int ROWP_SREG0 = 16;
 
 // Storage types of the chain kernel's operands (runtime codes; the output type is a template parameter).
 // EW_NO_INPUT as the type of the chain input: there is none, the program starts with EW_COPY.
-enum EwDType { EW_NO_INPUT = 15, EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5, EW_F64 = 6 };
+enum EwDType { EW_NO_INPUT = 15, EW_F32 = 0, EW_F16 = 1, EW_BF16 = 2, EW_BOOL = 3, EW_I32 = 4, EW_I64 = 5, EW_F64 = 6, EW_U8 = 7 };
 
 // How a side input is addressed for the flat output index i: value = side[(i / inner) % mid].
 enum EwSideMode {

@@ -145,6 +145,7 @@ __device__ __forceinline__ float load_scalar(const void* p, int dtype, long long
     case EW_BF16: return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[idx]);
     case EW_BOOL: return static_cast<const uint8_t*>(p)[idx] != 0 ? 1.0f : 0.0f;
     case EW_I32: return (float)static_cast<const int32_t*>(p)[idx];  // the cast op's own rounding (to nearest even)
+    case EW_U8: return (float)static_cast<const uint8_t*>(p)[idx];
     default: return (float)static_cast<const long long*>(p)[idx];
   }
 }
@@ -169,6 +170,11 @@ __device__ __forceinline__ void load_vec4(const void* p, int dtype, long long id
     const uint32_t u  = stream ? __ldcs(q) : __ldg(q);
 #pragma unroll
     for (int i = 0; i < 4; ++i) f[i] = ((u >> (8 * i)) & 0xffu) != 0 ? 1.0f : 0.0f;
+  } else if (dtype == EW_U8) {
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p) + idx);
+    const uint32_t u  = stream ? __ldcs(q) : __ldg(q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) f[i] = (float)((u >> (8 * i)) & 0xffu);
   } else if (dtype == EW_I32) {
     const int4* q = reinterpret_cast<const int4*>(static_cast<const int32_t*>(p) + idx);
     const int4 u  = stream ? __ldcs(q) : __ldg(q);

@@ -120,6 +120,7 @@ __device__ __forceinline__ double load_d(const void* p, int dtype, long long idx
     case EW_F32: return (double)static_cast<const float*>(p)[idx];
     case EW_BOOL: return static_cast<const uint8_t*>(p)[idx] != 0 ? 1.0 : 0.0;
     case EW_I32: return (double)static_cast<const int32_t*>(p)[idx];
+    case EW_U8: return (double)static_cast<const uint8_t*>(p)[idx];
     default: return (double)static_cast<const long long*>(p)[idx];
   }
 }

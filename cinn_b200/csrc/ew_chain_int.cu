@@ -1,12 +1,15 @@
 // Integer form of the generic elementwise chain (see ew_chain.cu for the float form and ew_chain.h for the program
-// encoding): the chain value and its side operands are int32 or int64 values, bool travels as 0 / 1, immediates are
-// signed 32-bit integers.  Arithmetic is what the reference generates for integer tensors:
+// encoding): the chain value and its side operands are int32, int64 or uint8 values, bool travels as 0 / 1,
+// immediates are signed 32-bit integers (truncated to the value type).  uint8 follows the unsigned instructions the
+// reference's LLVM code generator picks for `uint` types (cinn/backends/llvm/codegen_llvm.cc:205-216, 280-340,
+// 1449-1457: UDiv / URem, unsigned compares, logical right shift, zero-extending casts); + - * wrap modulo 256.  Arithmetic is what the reference generates for integer tensors:
 // + - * wrap, `divide` truncates toward zero (ir::Div), max / min are compare + select, mod takes the sign of the
 // divisor and floor_divide rounds toward minus infinity (cinn/lang/builtin.cc:108-121,
 // cinn/runtime/cuda/cinn_cuda_runtime_source.cuh:160-183), shifts and bitwise ops are the C operators
 // (cinn/hlir/pe/broadcast.cc:256-266), logical_right_shift shifts the unsigned value, clz / popc count bits
 // (cinn/runtime/cpu/host_intrinsics.cc:240-262).  A divisor of zero gives 0 (the reference's x86 code would trap).
 #include <cstdint>
+#include <type_traits>
 
 #include "device_math.cuh"
 #include "ew_chain.h"
@@ -25,6 +28,14 @@ template <>
 struct UnsignedOf<long long> {
   using type = unsigned long long;
 };
+template <>
+struct UnsignedOf<uint8_t> {
+  using type = uint8_t;
+};
+// The storage type of a uint8 OUTPUT (uint8_t itself names the one-byte bool output of these kernels).
+struct u8_out {
+  uint8_t v;
+};
 
 template <typename T>
 __device__ __forceinline__ T int_unary(int op, T x) {
@@ -34,7 +45,7 @@ __device__ __forceinline__ T int_unary(int op, T x) {
     case EW_ABS: return x > 0 ? x : (T)(U(0) - (U)x);
     case EW_LNOT: return x == 0 ? 1 : 0;
     case EW_TO_BOOL: return x != 0 ? 1 : 0;
-    case EW_BNOT: return ~x;
+    case EW_BNOT: return (T)~x;
     case EW_CLZ: return sizeof(T) == 4 ? (T)__clz((int)x) : (T)__clzll((long long)x);
     case EW_POPC: return sizeof(T) == 4 ? (T)__popc((unsigned)x) : (T)__popcll((unsigned long long)x);
     default: return x;
@@ -88,6 +99,17 @@ __device__ __noinline__ T int_pow(T x, T y) {
 }
 
 template <typename T>
+__device__ __forceinline__ bool is_minus_one(T v) {
+  if constexpr (std::is_signed<T>::value) return v == (T)-1;
+  return false;
+}
+template <typename T>
+__device__ __forceinline__ bool is_negative(T v) {
+  if constexpr (std::is_signed<T>::value) return v < 0;
+  return false;
+}
+
+template <typename T>
 __device__ __forceinline__ T int_binary(int op, T l, T r) {
   using U = typename UnsignedOf<T>::type;
   constexpr int kBits = sizeof(T) * 8;
@@ -95,10 +117,10 @@ __device__ __forceinline__ T int_binary(int op, T l, T r) {
     case EW_ADD: return (T)((U)l + (U)r);
     case EW_SUB: return (T)((U)l - (U)r);
     case EW_MUL: return (T)((U)l * (U)r);
-    case EW_DIV: return r == 0 ? 0 : ((r == -1) ? (T)(U(0) - (U)l) : l / r);
+    case EW_DIV: return r == 0 ? (T)0 : (is_minus_one(r) ? (T)(U(0) - (U)l) : (T)(l / r));
     case EW_MAX: return l > r ? l : r;
     case EW_MIN: return l < r ? l : r;
-    case EW_POW: return int_pow<T>(l, r);
+    case EW_POW: return sizeof(T) == 1 ? l : int_pow<typename std::conditional<sizeof(T) == 1, int32_t, T>::type>(l, r);
     case EW_EQ: return l == r;
     case EW_NE: return l != r;
     case EW_GT: return l > r;
@@ -106,26 +128,26 @@ __device__ __forceinline__ T int_binary(int op, T l, T r) {
     case EW_GE: return l >= r;
     case EW_LE: return l <= r;
     case EW_MOD: {
-      if (r == 0 || r == -1) return 0;
-      T res = l % r;
-      if (res != 0 && ((r ^ res) < 0)) res += r;
+      if (r == 0 || is_minus_one(r)) return 0;
+      T res = (T)(l % r);
+      if (res != 0 && is_negative((T)(r ^ res))) res = (T)(res + r);
       return res;
     }
     case EW_FLOOR_DIV: {
       if (r == 0) return 0;
-      if (r == -1) return (T)(U(0) - (U)l);
-      const T div = l / r, mod = l % r;
-      return ((l > 0 && r > 0) || (l < 0 && r < 0)) ? div : (mod == 0 ? div : div - 1);
+      if (is_minus_one(r)) return (T)(U(0) - (U)l);
+      const T div = (T)(l / r), mod = (T)(l % r);
+      return ((l > 0 && r > 0) || (is_negative(l) && is_negative(r))) ? div : (mod == 0 ? div : (T)(div - 1));
     }
     case EW_LAND: return (l != 0 && r != 0) ? 1 : 0;
     case EW_LOR: return (l != 0 || r != 0) ? 1 : 0;
     case EW_LXOR: return ((l != 0) != (r != 0)) ? 1 : 0;
-    case EW_BAND: return l & r;
-    case EW_BOR: return l | r;
-    case EW_BXOR: return l ^ r;
+    case EW_BAND: return (T)(l & r);
+    case EW_BOR: return (T)(l | r);
+    case EW_BXOR: return (T)(l ^ r);
     // shift counts are taken modulo the width, as the x86 shift instructions do
     case EW_SHL: return (T)((U)l << ((int)r & (kBits - 1)));
-    case EW_SHR: return l >> ((int)r & (kBits - 1));
+    case EW_SHR: return (T)(l >> ((int)r & (kBits - 1)));
     case EW_LSHR: return (T)((U)l >> ((int)r & (kBits - 1)));
     case EW_COPY: return r;
     default: return l;
@@ -137,6 +159,7 @@ __device__ __forceinline__ T load_int(const void* p, int dtype, long long idx) {
   switch (dtype) {
     case EW_BOOL: return static_cast<const uint8_t*>(p)[idx] != 0 ? 1 : 0;
     case EW_I32: return (T) static_cast<const int32_t*>(p)[idx];
+    case EW_U8: return (T) static_cast<const uint8_t*>(p)[idx];
     default: return (T) static_cast<const long long*>(p)[idx];
   }
 }
@@ -149,6 +172,11 @@ __device__ __forceinline__ void load_int4(const void* p, int dtype, long long id
     const uint32_t u  = stream ? __ldcs(q) : __ldg(q);
 #pragma unroll
     for (int i = 0; i < 4; ++i) v[i] = ((u >> (8 * i)) & 0xffu) != 0 ? 1 : 0;
+  } else if (dtype == EW_U8) {
+    const uint32_t* q = reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(p) + idx);
+    const uint32_t u  = stream ? __ldcs(q) : __ldg(q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = (T)((u >> (8 * i)) & 0xffu);
   } else if (dtype == EW_I32) {
     const int4* q = reinterpret_cast<const int4*>(static_cast<const int32_t*>(p) + idx);
     const int4 u  = stream ? __ldcs(q) : __ldg(q);
@@ -171,6 +199,13 @@ template <> __device__ __forceinline__ int32_t convert_out<long long, int32_t>(l
 template <> __device__ __forceinline__ long long convert_out<long long, long long>(long long v) { return v; }
 template <> __device__ __forceinline__ uint8_t convert_out<long long, uint8_t>(long long v) { return v != 0; }
 template <> __device__ __forceinline__ float convert_out<long long, float>(long long v) { return (float)v; }
+template <> __device__ __forceinline__ u8_out convert_out<uint8_t, u8_out>(uint8_t v) { return u8_out{v}; }
+template <> __device__ __forceinline__ uint8_t convert_out<uint8_t, uint8_t>(uint8_t v) { return v != 0; }
+template <> __device__ __forceinline__ int32_t convert_out<uint8_t, int32_t>(uint8_t v) { return v; }
+template <> __device__ __forceinline__ long long convert_out<uint8_t, long long>(uint8_t v) { return v; }
+template <> __device__ __forceinline__ float convert_out<uint8_t, float>(uint8_t v) { return (float)v; }
+template <> __device__ __forceinline__ u8_out convert_out<int32_t, u8_out>(int32_t v) { return u8_out{(uint8_t)v}; }
+template <> __device__ __forceinline__ u8_out convert_out<long long, u8_out>(long long v) { return u8_out{(uint8_t)v}; }
 
 template <typename T, typename OutT>
 __device__ __forceinline__ void store_int4(OutT* p, long long idx, const T (&v)[4]) {
@@ -423,8 +458,18 @@ StaticChainKey MakeKey(const char* base, long long meta) {
   CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_bool_s3t", 31, 256, k_ew_chain_int<T, uint8_t, 3, 2>);         \
   CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_f32_s3t", 31, 256, k_ew_chain_int<T, float, 3, 2>)
 
+#define REG_U8_OUT(TNAME, T)                                                                                \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_u8_s0", 31, 256, k_ew_chain_int<T, u8_out, 0>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_u8_s1", 31, 256, k_ew_chain_int<T, u8_out, 1>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_u8_s3", 31, 256, k_ew_chain_int<T, u8_out, 3>);        \
+  CINN_B200_REGISTER_KERNEL("ew_chain_int_" TNAME "_u8_s3t", 31, 256, k_ew_chain_int<T, u8_out, 3, 2>)
+
 REG_INT_CHAIN("i32", int32_t);
 REG_INT_CHAIN("i64", long long);
+REG_INT_CHAIN("u8", uint8_t);
+REG_U8_OUT("u8", uint8_t);
+REG_U8_OUT("i32", int32_t);
+REG_U8_OUT("i64", long long);
 
 }  // namespace cinn_b200
 

@@ -217,7 +217,7 @@ int NetBuilder::AddOp(const std::string& op, const std::vector<int>& inputs,
     out.shape = in(0).shape;
     if (op == "logical_not" && in(0).dtype != DType::kBool) return fail("operand must be bool");
     if ((op == "bitwise_not" || op == "clz" || op == "popc") && in(0).dtype != DType::kInt32 && in(0).dtype != DType::kInt64 &&
-        !(op == "bitwise_not" && in(0).dtype == DType::kBool))
+        in(0).dtype != DType::kUInt8 && !(op == "bitwise_not" && in(0).dtype == DType::kBool))
       return fail("operand must be an integer");
   } else if (BinaryOps().count(op) || CompareOps().count(op)) {
     if (!need(2)) return fail("takes 2 inputs");

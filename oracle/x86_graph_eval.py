@@ -24,7 +24,8 @@ BOOL_RESULT = {"equal", "not_equal", "greater_than", "less_than", "greater_equal
 REDUCE = {"reduce_sum": "sum", "reduce_prod": "prod", "reduce_max": "max", "reduce_min": "min", "reduce_all": "all",
           "reduce_any": "any"}
 NP = {"float32": np.float32, "float16": np.float16, "bool": np.bool_, "int32": np.int32, "int64": np.int64,
-      "float64": np.float64}
+      "float64": np.float64, "uint8": np.uint8}
+UNSIGNED_OF = {8: np.uint8, 32: np.uint32, 64: np.uint64}
 
 
 def parse(desc):
@@ -84,12 +85,12 @@ INT_UNARY = {"negative", "abs", "identity", "relu", "logical_not", "bitwise_not"
 def _int_unary(t, x):
     """Integer tensors: plain two's-complement arithmetic (numpy wraps like the C operators)."""
     bits = x.dtype.itemsize * 8
-    u = x.view(np.uint32 if bits == 32 else np.uint64)
+    u = x.view(UNSIGNED_OF[bits])
     with np.errstate(over="ignore"):
         if t == "negative":
-            return (0 - x).astype(x.dtype)
+            return (np.zeros((), x.dtype) - x).astype(x.dtype)
         if t == "abs":
-            return np.where(x > 0, x, (0 - x).astype(x.dtype))
+            return np.where(x > 0, x, (np.zeros((), x.dtype) - x).astype(x.dtype)).astype(x.dtype)
         if t == "relu":
             return np.maximum(x, 0).astype(x.dtype)
         if t == "logical_not":
@@ -119,16 +120,17 @@ def _int_binary(t, a, b):
         if t == "elementwise_mul":
             return (a * b).astype(dt)
         if t in ("divide", "floor_divide", "mod", "remainder"):
-            safe = np.where((b == 0) | (b == -1), 1, b).astype(dt)
+            m1 = (b == -1) if dt.kind == "i" else np.zeros(np.shape(b), bool)   # unsigned: UDiv / URem, no -1
+            safe = np.where((b == 0) | m1, 1, b).astype(dt)
             fl = np.floor_divide(a, safe)
             md = (a - fl * safe).astype(dt)                       # sign of the divisor
             tr = np.where((md != 0) & ((a < 0) != (safe < 0)), fl + 1, fl).astype(dt)   # toward zero
-            neg = (0 - a).astype(dt)
+            neg = (np.zeros((), dt) - a).astype(dt)
             if t == "divide":
-                return np.where(b == 0, 0, np.where(b == -1, neg, tr)).astype(dt)
+                return np.where(b == 0, 0, np.where(m1, neg, tr)).astype(dt)
             if t == "floor_divide":
-                return np.where(b == 0, 0, np.where(b == -1, neg, fl)).astype(dt)
-            return np.where((b == 0) | (b == -1), 0, md).astype(dt)
+                return np.where(b == 0, 0, np.where(m1, neg, fl)).astype(dt)
+            return np.where((b == 0) | m1, 0, md).astype(dt)
         if t == "pow":
             shape = np.broadcast_shapes(a.shape, b.shape)
             return orc.pow_int(np.broadcast_to(a, shape), np.broadcast_to(b, shape))
@@ -150,12 +152,12 @@ def _int_binary(t, a, b):
             return a ^ b
         cnt = (b & (bits - 1)).astype(dt)
         if t == "left_shift":
-            ut = np.uint32 if bits == 32 else np.uint64
+            ut = UNSIGNED_OF[bits]
             return (a.astype(dt).view(ut) << cnt.view(ut)).view(dt)
         if t == "right_shift":
             return (a >> cnt).astype(dt)
         if t == "logical_right_shift":
-            ut = np.uint32 if bits == 32 else np.uint64
+            ut = UNSIGNED_OF[bits]
             return (np.ascontiguousarray(np.broadcast_to(a, np.broadcast_shapes(a.shape, b.shape))).view(ut)
                     >> np.ascontiguousarray(np.broadcast_to(cnt, np.broadcast_shapes(a.shape, b.shape))).view(ut)).view(dt)
     raise NotImplementedError(t)
@@ -205,13 +207,13 @@ def evaluate(desc, inputs):
             elif x.dtype == np.float64 or to == np.float64:
                 # float64 <-> float32 / integers / bool: one IEEE conversion (numpy rounds to nearest even)
                 out = (x != 0) if to == np.bool_ else x.astype(to)
-            elif x.dtype.kind in "ib" and np.dtype(to).kind in "ib":
+            elif x.dtype.kind in "iub" and np.dtype(to).kind in "iub":
                 out = (x != 0) if to == np.bool_ else x.astype(to)   # widen / truncate / 0-1
             else:
                 out = _store(_f32(x), to)
-        elif t in INT_UNARY and vals[ins[0]].dtype.kind == "i":
+        elif t in INT_UNARY and vals[ins[0]].dtype.kind in "iu":
             out = _int_unary(t, vals[ins[0]])
-        elif t in INT_BINARY and vals[ins[0]].dtype.kind == "i":
+        elif t in INT_BINARY and vals[ins[0]].dtype.kind in "iu":
             a, b = vals[ins[0]], vals[ins[1]]
             axis = int(at.get("axis", -1))
             big, small = (a, b) if a.ndim >= b.ndim else (b, a)

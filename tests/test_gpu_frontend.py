@@ -598,6 +598,82 @@ def test_integer_pow_bit_exact(oracle, bits):
         assert np.array_equal(got, ref)
 
 
+# ---- uint8 chains: the unsigned instructions of cinn/backends/llvm/codegen_llvm.cc:205-216, 280-340, 1449-1457 -------
+
+def uint8_programs():
+    T = common.UInt(8)
+    shape = (37, 52)
+    c = lambda b, v: b.fill_constant([1], v, dtype="uint8")  # noqa: E731
+
+    def wrap(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, (52,), "Y")
+        return b.subtract(b.multiply(b.add(x, y), c(b, 3)), c(b, 7))
+
+    def divisions(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        return b.mod(b.floor_divide(b.divide(b.add(x, c(b, 100)), c(b, 3)), y), b.max(y, c(b, 2)))
+
+    def bit_ops(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        z = b.bitwise_xor(b.bitwise_not(b.bitwise_or(b.bitwise_and(x, y), c(b, 0x0f))), y)
+        return b.right_shift(b.logical_right_shift(b.left_shift(z, c(b, 3)), c(b, 2)), c(b, 1))
+
+    def compare(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, (52,), "Y")
+        return b.logical_not(b.greater_equal(b.max(b.negative(x), y), c(b, 100)))
+
+    def choose(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        m = b.create_input(common.Bool(), shape, "M")
+        return b.select(m, b.min(x, y), b.abs(y))
+
+    def to_float(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        return b.cast(b.add(x, y), "float32")
+
+    def to_int32(b):
+        x, y = b.create_input(T, shape, "X"), b.create_input(T, shape, "Y")
+        return b.cast(b.multiply(x, y), "int32")
+
+    def image_normalise(b):  # uint8 pixels -> float: the cast runs in the load of the float chain
+        x = b.create_input(T, shape, "X")
+        return b.scale(b.cast(x, "float32"), 1.0 / 255.0, -0.5)
+
+    return [wrap, divisions, bit_ops, compare, choose, to_float, to_int32, image_normalise]
+
+
+@pytest.mark.parametrize("index", range(8))
+def test_uint8_chains_bit_exact(oracle, index):
+    make = uint8_programs()[index]
+    b = NetBuilder("u8_%s" % make.__name__)
+    y = make(b)
+    rng = np.random.default_rng(60 + index)
+    X = rng.integers(0, 256, (37, 52)).astype(np.uint8)
+    Y = rng.integers(0, 256, (37, 52)).astype(np.uint8)
+    X[0, :4] = [0, 255, 1, 128]
+    Y[0, :4] = [0, 255, 0, 1]
+    feeds = {"X": X, "Y": Y, "M": rng.random((37, 52)) > 0.5}
+    names = {n for d, _ in Computation.build_and_compile(TARGET, b, plan_only=True).groups() for n in
+             [l.split()[1] for l in d.splitlines() if l.startswith("input")]}
+    if make.__name__ in ("wrap", "compare"):
+        feeds["Y"] = Y[0].copy()
+    feeds = {k: v for k, v in feeds.items() if k in names}
+    comp, out = run_program(b, feeds, [y])
+    ref = oracle_program(comp, feeds)[str(y)]
+    got = out[str(y)]
+    assert got.dtype == ref.dtype and np.array_equal(got, ref), (make.__name__, comp.groups())
+
+
+def test_uint8_pow_and_clz_are_refused_with_a_message():
+    for op in ("pow", "clz"):
+        b = NetBuilder("u8_" + op)
+        x = b.create_input(common.UInt(8), (8, 16), "X")
+        y = b.pow(x, x) if op == "pow" else b.clz(x)
+        with pytest.raises(Exception) as e:
+            Computation.build_and_compile(TARGET, b, fetch=[str(y)], plan_only=True)
+        assert "is not offered for uint8" in str(e.value)
+
+
 # ---- float64 chains ---------------------------------------------------------------------------------------------
 
 def f64_programs():

