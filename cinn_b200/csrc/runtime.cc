@@ -101,6 +101,7 @@ static int g_opt_ew_stream = 1, g_opt_ew_stream_stages = 0, g_opt_ew_stream_ctas
 static int g_opt_static_chains = 1;
 static int g_opt_fuse_interpreted = 0;
 static int g_opt_pdl = 1;  // programmatic dependent launch for the kernels that support it
+static int g_opt_host_chunks = 0;  // upper limit of the chunks group_run_host cuts a group into (0: up to 16)
 static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1, g_opt_rownorm_simple = -1;
 
 typedef unsigned int (*AsyncTimeoutReader)(int* cuda_status);
@@ -691,8 +692,9 @@ static void PrepareChunking(GroupSlot& slot) {
   for (auto& t : g.inputs) total += (size_t)t.numel() * DTypeBytes(t.dtype);
   total += (size_t)g.outputs[0].numel() * DTypeBytes(g.outputs[0].dtype);
   int chunks = 0;
+  const int most = g_opt_host_chunks > 0 ? g_opt_host_chunks : 16;
   for (int c : {16, 8, 4, 2})
-    if (d0 % c == 0 && total / c >= (4u << 20)) {
+    if (c <= most && d0 % c == 0 && total / c >= (4u << 20)) {
       chunks = c;
       break;
     }
@@ -850,6 +852,10 @@ int cinn_b200_set_option(const char* key, long long value) {
   if (!key) return SetError(CINN_B200_EINVAL, "null option key");
   if (!strcmp(key, "sm_count")) {
     g_opt_sm_count = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "host_chunks")) {
+    g_opt_host_chunks = (int)value;
     return CINN_B200_OK;
   }
   if (!strcmp(key, "enable_pdl")) {

@@ -316,6 +316,8 @@ int cinn_b200_device_status(unsigned int* async_wait_timeouts);
  * or row-program kernel takes (one launch, but several times slower per byte than the specialised kernels; off, such
  * regions are split into groups the chain and reduction kernels take; a group handed to cinn_b200_compile_group
  * directly is always accepted);
+ * "host_chunks" (default 0 = up to 16): the most chunks cinn_b200_group_run_host pipelines a group over (read at the
+ * group's first host run);
  * "enable_ew_stream" (default 1),
  * "ew_stream_stages", "ew_stream_ctas_per_sm": whether large elementwise groups with 16-bit outputs stream their
  * input through shared-memory rings filled by bulk copies, the ring depth and the resident CTAs per SM; "rownorm_rows_per_iter": rows per CTA
