@@ -289,6 +289,10 @@ def side_groups(torch, dev, peak, only=None):
         ("row_program_centre_16384x4096", lambda: W.row_program("centre"), 2, "x - mean(x), one kernel"),
         ("row_program_affine_relu_16384x4096", lambda: W.row_program("affine_relu"), 2, "relu(sum(x) * a + c), one kernel"),
         ("row_program_three_sums_16384x4096", lambda: W.row_program("three_sums"), 2, "sum(A), sum(B), sum(A + B), one kernel"),
+        ("row_program_rms_norm_16384x4096", lambda: W.row_program("rms_norm"), 2, "x * rsqrt(mean(x^2) + eps) * gamma, one kernel"),
+        ("row_program_standardise_16384x4096", lambda: W.row_program("standardise"), 2, "(x - mean) * rsqrt(var + eps), three passes over a row in registers, one kernel"),
+        ("row_program_log_softmax_16384x4096", lambda: W.row_program("log_softmax"), 2, "x - max - log(sum(exp(x - max))), one kernel"),
+        ("row_program_moments_16384x4096", lambda: W.row_program("moments"), 2, "mean and variance per row from one read"),
         ("dag_shared_sum_4out_4096x8192", lambda: W.dag_program("shared_sum_4out", (4096, 8192)), 1,
          "g = A + B feeding four sums: six reads, four writes, one kernel"),
         ("dag_bias_relu_mask_3out_8192x8192", lambda: W.dag_program("bias_relu_mask_3out"), 1,

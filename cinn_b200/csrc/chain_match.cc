@@ -1231,6 +1231,10 @@ struct ValueAction {
   int fold  = 0;      // kAccumulate: 0 sum, 1 prod, 2 max, 3 min
 };
 
+// What happens to values once computed: a value may be stored and folded into several accumulators (reduce_min and
+// reduce_max of the same operand).
+using ActionMap = std::multimap<std::string, ValueAction>;
+
 struct RegProgramBuilder {
   ChainBuilder& cb;
   const GroupDesc& g;
@@ -1405,7 +1409,7 @@ struct RegProgramBuilder {
   // values are stored or accumulated once computed; `extra_uses` are uses of values outside this segment that must
   // keep their registers (scalar programs: values a later pass reads).  Values in `keep_mul` are never contracted
   // (they are reduce operands: materialised in the reference).
-  bool EmitSegment(const std::vector<const OpDesc*>& ops, const std::map<std::string, ValueAction>& actions,
+  bool EmitSegment(const std::vector<const OpDesc*>& ops, const ActionMap& actions,
                    const std::map<std::string, int>& extra_uses, const std::set<std::string>& keep_mul) {
     std::set<const OpDesc*> in_segment(ops.begin(), ops.end());
     for (const OpDesc* op : ops) {
@@ -1515,8 +1519,8 @@ struct RegProgramBuilder {
       // 16-bit values are rounded to their type after every op (a cast to that type IS the rounding)
       if (op.type != "cast" && (out_t == DType::kFloat16 || out_t == DType::kBFloat16))
         words.push_back(DagWord(out_t == DType::kFloat16 ? EW_ROUND_F16 : EW_ROUND_BF16, dst, dst, 0, 0, 0.0f));
-      auto act = actions.find(op.output);
-      if (act != actions.end()) {
+      auto acts = actions.equal_range(op.output);
+      for (auto act = acts.first; act != acts.second; ++act) {
         if (act->second.kind == ValueAction::kStore) words.push_back(DagWord(DAG_STORE, act->second.index, dst, 0, 0, 0.0f));
         if (act->second.kind == ValueAction::kAccumulate)
           words.push_back(DagWord(ROWP_ACC, act->second.index, dst, 0, act->second.fold, 0.0f));
@@ -1658,7 +1662,7 @@ std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& de
   cb.out_shape = g.outputs[0].shape;
   cb.n         = g.outputs[0].numel();
   std::map<std::string, std::vector<int64_t>> axes;
-  std::map<std::string, ValueAction> actions;
+  ActionMap actions;
   RegProgramBuilder rb(cb);
   for (size_t k = 0; k < g.outputs.size(); ++k) {
     const TensorDesc& o = g.outputs[k];
@@ -1677,7 +1681,7 @@ std::unique_ptr<CompiledGroup> MatchDag(const GroupDesc& g, const DeviceInfo& de
     ValueAction act;
     act.kind  = ValueAction::kStore;
     act.index = (int)k;
-    actions[o.name] = act;
+    actions.insert({o.name, act});
     rb.group_outputs.insert(o.name);
   }
   if (!PlaceAxes(cb, [](const OpDesc&) { return true; }, &axes)) return nullptr;
@@ -1955,7 +1959,7 @@ std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceI
   // segment index 2p (element program of pass p) / 2p + 1 (scalar program) of the last read of every per-row value
   std::map<std::string, int> last_read;
   std::vector<std::vector<const OpDesc*>> seg_ops(2 * npass);
-  std::vector<std::map<std::string, ValueAction>> seg_actions(2 * npass);
+  std::vector<ActionMap> seg_actions(2 * npass);
   for (int p = 0; p < npass; ++p) {
     std::vector<std::string> et, st2;
     for (const OpDesc* red : reduces)
@@ -1966,13 +1970,13 @@ std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceI
         ValueAction a;
         a.kind  = ValueAction::kStore;
         a.index = output_index[o.name];
-        seg_actions[2 * p][o.name] = a;
+        seg_actions[2 * p].insert({o.name, a});
       }
       if (is_row(o.name) && avail[o.name] == p) {
         ValueAction a;
         a.kind  = ValueAction::kStore;
         a.index = output_index[o.name];
-        seg_actions[2 * p + 1][o.name] = a;
+        seg_actions[2 * p + 1].insert({o.name, a});
       }
     }
     for (auto& op : g.ops)
@@ -2035,22 +2039,18 @@ std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceI
       auto it = sb.reg_of.find(root);
       return it == sb.reg_of.end() ? -1 : ROWP_SREG0 + it->second;
     };
-    std::map<std::string, ValueAction> actions = seg_actions[2 * p];
+    ActionMap actions = seg_actions[2 * p];
     for (const OpDesc* red : reduces) {
       if (pass_of_reduce[red->output] != p) continue;
       const int sreg = sb.Alloc();
       if (sreg < 0) return nullptr;
       sb.reg_of[red->output]    = sreg;
       sb.remaining[red->output] = 1;  // held until its last read (freed below)
-      if (actions.count(red->inputs[0])) {
-        cb.Fail("a value is reduced twice, or reduced and stored, in one pass");
-        return nullptr;
-      }
       ValueAction a;
       a.kind  = ValueAction::kAccumulate;
       a.index = sreg;
       a.fold  = folds.at(red->type);
-      actions[red->inputs[0]] = a;
+      actions.insert({red->inputs[0], a});
     }
     if (!eb.EmitSegment(seg_ops[2 * p], actions, {}, reduce_operands) || !merge_sides(eb, 0)) return nullptr;
     counts |= (unsigned long long)eb.words.size() << (8 * p);

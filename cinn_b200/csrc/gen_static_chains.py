@@ -373,7 +373,51 @@ def builder_programs():
             vector_sum_recomputed_in_two_shapes]
 
 
-def builder_dag_groups():
+def builder_row_programs(R=64, C=4096):
+    """Row compositions written with the NetBuilder, as a user's program would: the fusion pass's own description of
+    their row-program group goes into the table, so that such programs run as ONE specialised kernel (the constants
+    and the shape are parameters of that kernel, not part of its key)."""
+    from cinn_b200 import common
+    F32 = common.Float(32)
+
+    def rms_norm(b):  # x * rsqrt(mean(x^2) + eps) * gamma
+        x, g = b.create_input(F32, (R, C), "X"), b.create_input(F32, (C,), "G")
+        inv = b.rsqrt(b.scale(b.reduce_sum(b.multiply(x, x), [1]), 1.0 / C, 1e-6))
+        return [b.multiply(b.multiply(x, b.broadcast_to(inv, [R, C], [0])), g)]
+
+    def standardise(b):  # (x - mean) * rsqrt(var + eps): three passes over a row held in registers
+        x = b.create_input(F32, (R, C), "X")
+        n = b.fill_constant([R], float(C))
+        xc = b.subtract(x, b.broadcast_to(b.divide(b.reduce_sum(x, [1]), n), [R, C], [0]))
+        var = b.divide(b.reduce_sum(b.multiply(xc, xc), [1]), n)
+        return [b.multiply(xc, b.broadcast_to(b.rsqrt(b.scale(var, 1.0, 1e-5)), [R, C], [0]))]
+
+    def log_softmax(b):
+        x = b.create_input(F32, (R, C), "X")
+        d = b.subtract(x, b.broadcast_to(b.reduce_max(x, [1]), [R, C], [0]))
+        return [b.subtract(d, b.broadcast_to(b.log(b.reduce_sum(b.exp(d), [1])), [R, C], [0]))]
+
+    def l1_normalise(b):
+        x = b.create_input(F32, (R, C), "X")
+        return [b.divide(x, b.broadcast_to(b.reduce_sum(b.abs(x), [1]), [R, C], [0]))]
+
+    def moments(b):  # mean and variance per row from one read
+        x = b.create_input(F32, (R, C), "X")
+        n = b.fill_constant([R], float(C))
+        m = b.divide(b.reduce_sum(x, [1]), n)
+        return [m, b.subtract(b.divide(b.reduce_sum(b.multiply(x, x), [1]), n), b.multiply(m, m))]
+
+    def min_max_normalise(b):  # (x - min) / (max - min): two reductions of the same operand in one pass
+        x = b.create_input(F32, (R, C), "X")
+        mn, mx = b.reduce_min(x, [1]), b.reduce_max(x, [1])
+        return [b.divide(b.subtract(x, b.broadcast_to(mn, [R, C], [0])), b.broadcast_to(b.subtract(mx, mn), [R, C], [0]))]
+
+    return [rms_norm, standardise, log_softmax, l1_normalise, moments, min_max_normalise]
+
+
+def builder_groups(programs, pattern):
+    """(name, description) of the groups of `pattern` that the fusion pass forms from the given builder programs when
+    it may form interpreted program groups."""
     import cinn_b200
     from cinn_b200.frontend import Computation, NetBuilder
     L = cinn_b200.lib()
@@ -381,13 +425,13 @@ def builder_dag_groups():
     L.cinn_b200_set_option(b"enable_static_chains", 0)
     out = []
     try:
-        for make in builder_programs():
+        for make in programs:
             b = NetBuilder(make.__name__)
             fetch = make(b)
             comp = Computation.build_and_compile(None, b, fetch=[str(f) for f in fetch], plan_only=True)
             k = 0
-            for desc, pattern in comp.groups():
-                if pattern.split()[0] == "ew_dag":
+            for desc, pat in comp.groups():
+                if pat.split()[0] == pattern:
                     lines = desc.splitlines()
                     name = make.__name__ + ("_%d" % k if k else "")
                     k += 1
@@ -397,6 +441,10 @@ def builder_dag_groups():
         L.cinn_b200_set_option(b"fuse_interpreted_programs", 0)
         L.cinn_b200_set_option(b"enable_static_chains", 1)
     return out
+
+
+def builder_dag_groups():
+    return builder_groups(builder_programs(), "ew_dag")
 
 
 VARIANT = {"_s0": (0, 0, "false"), "_s1": (1, 0, "false"), "_s3": (3, 0, "false"), "_s3t": (3, 2, "true"),
@@ -467,7 +515,8 @@ def row_table_lines():
     cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
     try:
         seen, lines, skipped = {}, [], []
-        for name, desc in ROW_GROUPS:
+        for name, desc in ROW_GROUPS + builder_groups(builder_row_programs(), "row_program"):
+            cinn_b200._lib.check(L.cinn_b200_set_option(b"enable_static_chains", 0))
             try:
                 g = cinn_b200.FusedGroup(desc)
             except cinn_b200.CinnB200Error as e:

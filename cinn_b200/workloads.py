@@ -457,6 +457,8 @@ def row_program(kind, shape=(16384, 4096), seed=12):
         outs = [("sa", "float32", (rows,)), ("sb", "float32", (rows,)), ("sc", "float32", (rows,))]
         ops = ["elementwise_add c = A B ; axis=-1", "reduce_sum sa = A ; dim=1 keep_dim=false",
                "reduce_sum sb = B ; dim=1 keep_dim=false", "reduce_sum sc = c ; dim=1 keep_dim=false"]
+    elif kind in ("rms_norm", "standardise", "log_softmax", "l1_normalise", "moments", "min_max_normalise"):
+        return _row_program_from_builder(kind, shape, seed)
     else:
         raise ValueError(kind)
     desc = (f"group fn_row_{kind}\n" + "".join(f"input {i}\n" for i in ins) + "".join(f"op {o}\n" for o in ops) +
@@ -467,6 +469,36 @@ def row_program(kind, shape=(16384, 4096), seed=12):
         return [rng.standard_normal([int(d) for d in i.split()[2].split(",")], dtype=np.float32) for i in ins]
     return Workload("row_" + kind, desc, gen, np.float32, outs[0][2],
                     more_outputs=[(np.float32, sh) for _, _, sh in outs[1:]])
+
+
+def _row_program_from_builder(kind, shape, seed):
+    """The row compositions that the table of specialised kernels lists as NetBuilder programs
+    (csrc/gen_static_chains.py: rms_norm, standardise, log_softmax, l1_normalise, moments), at `shape`: the group is
+    the one the fusion pass forms from the program."""
+    import importlib.util
+    import os
+    from .frontend import Computation, NetBuilder
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "gen_static_chains.py")
+    spec = importlib.util.spec_from_file_location("cinn_b200_gen_static_chains", path)
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    make = [m for m in gen.builder_row_programs(*shape) if m.__name__ == kind][0]
+    b = NetBuilder("row_" + kind)
+    fetch = make(b)
+    comp = Computation.build_and_compile(None, b, fetch=[str(f) for f in fetch], plan_only=True)
+    groups = comp.groups()
+    if len(groups) != 1:
+        raise RuntimeError("%s at %s is not one group: %s" % (kind, shape, [p for _, p in groups]))
+    desc = groups[0][0]
+    ins = [l.split() for l in desc.splitlines() if l.startswith("input ")]
+    outs = [l.split() for l in desc.splitlines() if l.startswith("output ")]
+    dims = lambda w: tuple(int(d) for d in w[3].split(","))  # noqa: E731
+
+    def gen_inputs():
+        rng = np.random.default_rng(seed)
+        return [rng.standard_normal(dims(w), dtype=np.float32) for w in ins]
+    return Workload("row_" + kind, desc, gen_inputs, np.float32, dims(outs[0]),
+                    more_outputs=[(np.float32, dims(w)) for w in outs[1:]])
 
 
 def dag_program(kind="shared_sum_4out", shape=(8192, 8192), seed=13):

@@ -68,8 +68,24 @@ def exp_minus_its_maximum(b, rows, r):
     return [b.subtract(e, b.broadcast_to(b.reduce_max(e, [1]), [rows, r], [0]))]
 
 
+def _tabled(index):
+    """The builder programs of the specialised-kernel table (cinn_b200/csrc/gen_static_chains.py), at any shape."""
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "cinn_b200", "csrc", "gen_static_chains.py")
+    spec = importlib.util.spec_from_file_location("gen_static_chains", path)
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    name = gen.builder_row_programs()[index].__name__
+
+    def make(b, rows, r):
+        return gen.builder_row_programs(rows, r)[index](b)
+    make.__name__ = name
+    return make
+
+
 PROGRAMS = [l2_normalise, centre, shifted_exponentials_with_bias, three_sums, centred_and_its_variance,
-            exp_minus_its_maximum]
+            exp_minus_its_maximum] + [_tabled(i) for i in range(6)]
 SHAPES = [(70, 1024), (9, 4096), (33, 1001), (5, 2050), (128, 64)]  # warp / CTA per row, ragged rows, short rows
 
 
