@@ -99,6 +99,26 @@ __device__ __forceinline__ void chain_values2(const Prog& prog, const void* in0,
   prog.template run<8, NS, 0, false>(s1, s2, s3, acc, nullptr);
 }
 
+// Four vectors: the specialised kernels' inner step for rows (sixteen values per thread and iteration: 64 bytes of
+// every full-size operand in flight per thread).
+template <int NS, class Prog>
+__device__ __forceinline__ void chain_values4(const Prog& prog, const void* in0, const Sides& sd, const long long (&idx)[4],
+                                              float (&acc)[16]) {
+  const int in_type = prog.in_type();
+  float s1[16], s2[16], s3[16];
+  if (in_type != EW_NO_INPUT) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) load_vec4(in0, in_type, idx[j], true, *reinterpret_cast<float(*)[4]>(&acc[4 * j]));
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (NS >= 1 && sd.sd1.mode != EW_SIDE_NONE) load_side<4>(sd.sd1, idx[j], *reinterpret_cast<float(*)[4]>(&s1[4 * j]));
+    if (NS >= 2 && sd.sd2.mode != EW_SIDE_NONE) load_side<4>(sd.sd2, idx[j], *reinterpret_cast<float(*)[4]>(&s2[4 * j]));
+    if (NS >= 3 && sd.sd3.mode != EW_SIDE_NONE) load_side<4>(sd.sd3, idx[j], *reinterpret_cast<float(*)[4]>(&s3[4 * j]));
+  }
+  prog.template run<16, NS, 0, false>(s1, s2, s3, acc, nullptr);
+}
+
 // ---- rows: y[row] = fold over j of f(x[row * r + j]) -----------------------------------------------------------------
 // `group` = 32: a warp per row (8 rows per CTA); `group` = 256: a CTA per row.  `rows` counts segments when a row is
 // cut (the matcher passes rows * S and r / S): a segment is just a shorter row of the same flat index space.
@@ -126,6 +146,15 @@ __device__ __forceinline__ void chain_reduce_row_body(const Prog& prog, const vo
     if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary
       const long long nv = r >> 2;
       long long v        = t;
+      if constexpr (Prog::kStatic && NT == 0 && NS <= 1) {
+        for (; v + 3 * nt < nv; v += 4 * nt) {
+          float acc[16];
+          const long long idx[4] = {base + (v << 2), base + ((v + nt) << 2), base + ((v + 2 * nt) << 2), base + ((v + 3 * nt) << 2)};
+          chain_values4<NS>(prog, in0, sd, idx, acc);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) a[i & 3] = cr_apply(rop, a[i & 3], acc[i]);
+        }
+      }
       for (; NT == 0 && v + nt < nv; v += 2 * nt) {
         float acc[8];
         chain_values2<NS>(prog, in0, sd, base + (v << 2), base + ((v + nt) << 2), acc);
@@ -249,7 +278,7 @@ __global__ void __launch_bounds__(256, NS == 0 ? 5 : 4)
 // the hardware's approximate exponential and reciprocal (relative error about 1e-6 per term): a reduction's result is
 // judged at 1e-5 relative, and with the full-precision forms sum(sigmoid(..)) is issue-bound at 0.46 of the HBM peak.
 template <int NS, int NT, unsigned long long META, uint32_t... SIG>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
     k_chain_reduce_row_static(CHAIN_PARAMS, long long rows, long long r, long long group) {
   grid_dependency_sync();
   CHAIN_STEPS;

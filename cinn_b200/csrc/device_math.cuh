@@ -43,11 +43,18 @@ __device__ __forceinline__ float x86_tanh(float x) {
 // one rcp.approx instead of the full-accuracy expf and the IEEE division.  fp32 relative error of the quotient
 // is about 2^-21, far below the 2^-11 spacing of fp16 / 2^-8 of bf16; close to zero, where 1-e cancels, the
 // odd series a - a^3/3 is used instead (relative error < 2e-8 for |a| < 0.02).
+// 1 / y by the hardware's approximate reciprocal alone (1 ulp; no range fix-ups: for y in [1, 2], or where an
+// infinite y may give 0).
+__device__ __forceinline__ float rcp_approx(float y) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(y));
+  return r;
+}
 __device__ __forceinline__ float x86_tanh_for_16bit_out(float x) {
   const float a = fabsf(x);
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * -2.885390082f));  // exp(-2a) = 2^(-2a*log2(e))
-  float r       = __fdividef(1.0f - e, 1.0f + e);
+  float r       = (1.0f - e) * rcp_approx(1.0f + e);  // 1 + e is in [1, 2]
   const float s = a * fmaf(a * a, -0.33333334f, 1.0f);
   r             = a < 0.02f ? s : r;
   return x < 0.0f ? -r : r;

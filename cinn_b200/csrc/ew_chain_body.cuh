@@ -108,6 +108,7 @@ __device__ __forceinline__ void ew_chain_body(const Prog& prog, const void* __re
 
 // The interpreter's program: everything comes from kernel parameters.
 struct DynProgram {
+  static constexpr bool kStatic = false;
   const long long* steps;
   int nsteps;
   long long meta;
@@ -130,6 +131,7 @@ struct DynProgram {
 // FAST: see apply_unary (the specialised reductions only).
 template <unsigned long long META, bool FAST, uint32_t... SIG>
 struct StaticProgramT {
+  static constexpr bool kStatic = true;
   const long long* steps;
   __device__ __forceinline__ constexpr int in_type() const { return (int)((META >> 24) & 15); }
   __device__ __forceinline__ constexpr int out2_type() const { return (int)((META >> 36) & 15); }

@@ -65,7 +65,7 @@ __device__ __forceinline__ void apply_unary(int op, float imm, float (&a)[VEC]) 
   switch (op) {
     EW_UNARY_CASE(EW_EXP, FAST ? exp_for_16bit_out(x) : expf(x))
     EW_UNARY_CASE(EW_TANH, FAST ? x86_tanh_for_16bit_out(x) : x86_tanh(x))
-    EW_UNARY_CASE(EW_SIGMOID, FAST ? __fdividef(1.0f, 1.0f + exp_for_16bit_out(-x)) : x86_sigmoid(x))
+    EW_UNARY_CASE(EW_SIGMOID, FAST ? rcp_approx(1.0f + exp_for_16bit_out(-x)) : x86_sigmoid(x))
     EW_UNARY_CASE(EW_RSQRT, x86_rsqrt(x))
     EW_UNARY_CASE(EW_SQRT, sqrtf(x))
     EW_UNARY_CASE(EW_RELU, x86_max(x, 0.0f))

@@ -1177,7 +1177,9 @@ struct Matcher {
       splits = std::min<int64_t>(r / 16, CeilDiv((int64_t)sms * 1024, thr));
       splits = std::max<int64_t>(1, std::min<int64_t>(splits, 512));
     }
-    const int64_t rps = CeilDiv(r, splits);
+    // whole groups of eight rows per split: the kernel keeps eight row loads in flight and takes a remainder one
+    // row (one DRAM latency) at a time
+    const int64_t rps = splits > 1 ? RoundUp(CeilDiv(r, splits), 8) : r;
     splits            = CeilDiv(r, rps);
     if (splits == 1) {
       if (!col_step(In(0), Out(0), outer, r, inner, 1, {0}, true)) return nullptr;

@@ -62,7 +62,10 @@ __device__ __forceinline__ void rp_operand(int sel, float imm, float imm2, const
 
 // One element-program step on VEC elements at flat index i0.  acc[k] is the accumulator whose total goes to scalar
 // register k.  Returns true when the step used the next word's immediate.
-template <int VEC>
+// FAST: exp / tanh / sigmoid through the hardware's approximate exponential and reciprocal (about 1e-6 relative):
+// every result of a row program depends on a row reduction and is judged at 1e-5 relative; the specialised kernels
+// use it, the interpreting kernel computes the full-precision forms.
+template <int VEC, bool FAST = false>
 __device__ __forceinline__ bool rp_element_step(unsigned w, float imm, float imm2, unsigned long long meta,
                                                 const RowInputs& in, const RowOutputs& out, long long i0,
                                                 float (&regs)[DAG_REGS][VEC], const float (&sregs)[ROWP_SREGS],
@@ -96,7 +99,7 @@ __device__ __forceinline__ bool rp_element_step(unsigned w, float imm, float imm
   float x[VEC];
   rp_operand<VEC>(a, imm, imm2, regs, sregs, x);
   if (op >= EW_FIRST_UNARY) {
-    apply_unary<VEC>(op, imm, x);
+    apply_unary<VEC, FAST>(op, imm, x);
   } else if (op == EW_FMA) {
     float y[VEC], z[VEC];
     rp_operand<VEC>(b, imm, imm2, regs, sregs, y);
@@ -265,7 +268,7 @@ struct StaticRowProgram {
       constexpr int op = (int)(w & 0xff), a = (int)((w >> 12) & 31), b = (int)((w >> 17) & 31), c = (int)((w >> 22) & 31);
       constexpr bool two = op != EW_NOP && op != DAG_LOAD && op != DAG_STORE && op != ROWP_ACC &&
                            (a == DAG_IMM2 || b == DAG_IMM2 || c == DAG_IMM2 || op == EW_SCALE_PRE);
-      (void)rp_element_step<VEC>(w, rp_imm(steps[K]), rp_imm(steps[K + 1 < ROWP_MAX_STEPS ? K + 1 : K]), META, in, out, i0,
+      (void)rp_element_step<VEC, true>(w, rp_imm(steps[K]), rp_imm(steps[K + 1 < ROWP_MAX_STEPS ? K + 1 : K]), META, in, out, i0,
                                  regs, sregs, acc, REREAD);
       element_from<VEC, K + (two ? 2 : 1), END, REREAD>(in, out, i0, regs, sregs, acc);
     }
@@ -341,7 +344,7 @@ struct StaticRowProgram {
       constexpr uint32_t w = word(K);
       // only what pass 0 loaded is in the cache
       constexpr int mode = ((w & 0xff) == (unsigned)DAG_LOAD && ((loaded_by_pass0() >> ((w >> 12) & 7)) & 1u)) ? 2 : 0;
-      (void)rp_element_step<4>(w, rp_imm(steps[K]), rp_imm(steps[K + 1 < ROWP_MAX_STEPS ? K + 1 : K]), META, in, out, i0,
+      (void)rp_element_step<4, true>(w, rp_imm(steps[K]), rp_imm(steps[K + 1 < ROWP_MAX_STEPS ? K + 1 : K]), META, in, out, i0,
                                regs, sregs, acc, false, cache, mode);
       cached_from<K + step_words(K), END>(in, out, i0, regs, sregs, acc, cache);
     }

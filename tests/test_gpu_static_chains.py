@@ -84,8 +84,15 @@ def test_static_kernel_equals_interpreter(name, desc, variant):
     assert all(k.startswith("ew_chain_") for k in k_i), k_i
     if "_static_" not in k_s[0]:
         pytest.skip("no specialised kernel for this entry (%s)" % k_s[0])
+    # A specialised ROW program evaluates exp / tanh / sigmoid through the approximate exponential and reciprocal
+    # (its results are of the reduction class); every other program is the interpreter's bit for bit.
+    approximate = k_i[0] == "row_program" and any(" %s " % t in desc for t in ("exp", "tanh", "sigmoid"))
     for a, b in zip(got_s, got_i):
-        assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))
+        if approximate:
+            fa, fb = a.view(np.float32), b.view(np.float32)
+            assert np.allclose(fa, fb, rtol=2e-5, atol=2e-6 * float(np.abs(fb).max())), (name, variant, k_s)
+        else:
+            assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))
 
 
 @pytest.mark.parametrize("name,desc", GEN.REDUCE_GROUPS, ids=[n for n, _ in GEN.REDUCE_GROUPS])
@@ -125,7 +132,7 @@ def test_static_chain_reduction_equals_interpreter(name, desc, shape):
 def test_static_register_and_row_programs_equal_their_interpreters(name, desc, variant):
     """Register programs (several outputs, shared values) and row programs (reductions with elementwise ops around
     them): the kernel with the program as template arguments against the interpreting kernel, bit for bit (same steps,
-    same accumulation order)."""
+    same accumulation order) except where the specialised form uses the approximate transcendental functions."""
     if variant == "other_size":
         desc = (desc.replace("64,4096", "37,1028").replace("shape=64 ", "shape=37 ").replace(" 64\n", " 37\n")
                 .replace("value=4096.0", "value=1028.0").replace("64,1024", "61,1028").replace(" 1024\n", " 1028\n"))
@@ -135,5 +142,12 @@ def test_static_register_and_row_programs_equal_their_interpreters(name, desc, v
         pytest.skip("this entry is a chain (%s): covered by the chain table" % k_i[0])
     if "_static_" not in k_s[0]:
         pytest.skip("no specialised kernel for this entry (%s)" % k_s[0])
+    # A specialised ROW program evaluates exp / tanh / sigmoid through the approximate exponential and reciprocal
+    # (its results are of the reduction class); every other program is the interpreter's bit for bit.
+    approximate = k_i[0] == "row_program" and any(" %s " % t in desc for t in ("exp", "tanh", "sigmoid"))
     for a, b in zip(got_s, got_i):
-        assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))
+        if approximate:
+            fa, fb = a.view(np.float32), b.view(np.float32)
+            assert np.allclose(fa, fb, rtol=2e-5, atol=2e-6 * float(np.abs(fb).max())), (name, variant, k_s)
+        else:
+            assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))
