@@ -54,7 +54,9 @@ __device__ __forceinline__ float x86_tanh_for_16bit_out(float x) {
   const float a = fabsf(x);
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(a * -2.885390082f));  // exp(-2a) = 2^(-2a*log2(e))
-  float r       = (1.0f - e) * rcp_approx(1.0f + e);  // 1 + e is in [1, 2]
+  // (the approximate division, not a bare rcp.approx through inline assembly: measured on the streamed headline
+  // kernel, 6525 GB/s against 6115 GB/s)
+  float r       = __fdividef(1.0f - e, 1.0f + e);
   const float s = a * fmaf(a * a, -0.33333334f, 1.0f);
   r             = a < 0.02f ? s : r;
   return x < 0.0f ? -r : r;
