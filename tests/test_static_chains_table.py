@@ -69,3 +69,19 @@ def test_listed_groups_plan_to_their_static_kernel_and_others_to_the_interpreter
     g = cinn_b200.FusedGroup(red["sum_abs_diff_rows"].replace("64,1024", "8192,8192").replace("float32 64\n", "float32 8192\n"))
     assert g.kernel_names()[0] == "chain_reduce_static_sum_abs_diff_rows", g.kernel_names()
     g.release()
+
+
+def test_builder_row_compositions_fuse_into_one_specialised_kernel():
+    """The row compositions the table lists as NetBuilder programs (rms_norm, standardise, log_softmax, l1_normalise,
+    moments, min_max_normalise): with the default options the fusion pass forms ONE group for each and the matcher
+    gives it its specialised row-program kernel, at the table's shape and at others (the shape and the constants are
+    kernel parameters); min_max_normalise folds the same operand twice in one pass."""
+    from cinn_b200.frontend import Computation, NetBuilder
+    gen = load_generator()
+    for shape in [(64, 4096), (16384, 4096), (70, 1024), (5, 2052)]:
+        for make in gen.builder_row_programs(*shape):
+            b = NetBuilder(make.__name__)
+            fetch = make(b)
+            comp = Computation.build_and_compile(None, b, fetch=[str(f) for f in fetch], plan_only=True)
+            kernels = [p.split()[1] for _, p in comp.groups()]
+            assert kernels == ["row_program_static_" + make.__name__], (shape, make.__name__, kernels)
