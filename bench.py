@@ -749,7 +749,20 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # NCCL announces its version on standard output when its communicator comes up; this program's standard
+        # output carries the one JSON line and nothing else, so the file descriptor points at standard error meanwhile.
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev)
+            first = torch.zeros(1, device=dev)
+            dist.all_reduce(first)
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
     for kv in args.option or []:
         k, v = kv.split("=")
         cinn_b200._lib.check(cinn_b200.lib().cinn_b200_set_option(k.encode(), int(v)))
