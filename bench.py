@@ -293,6 +293,8 @@ def side_groups(torch, dev, peak, only=None):
         ("row_program_standardise_16384x4096", lambda: W.row_program("standardise"), 2, "(x - mean) * rsqrt(var + eps), three passes over a row in registers, one kernel"),
         ("row_program_log_softmax_16384x4096", lambda: W.row_program("log_softmax"), 2, "x - max - log(sum(exp(x - max))), one kernel"),
         ("row_program_moments_16384x4096", lambda: W.row_program("moments"), 2, "mean and variance per row from one read"),
+        ("row_program_rms_norm_65536x1024", lambda: W.row_program("rms_norm", (65536, 1024)), 2, "short rows: a warp per row"),
+        ("row_program_standardise_65536x1024", lambda: W.row_program("standardise", (65536, 1024)), 2, "short rows: a warp per row"),
         ("dag_shared_sum_4out_4096x8192", lambda: W.dag_program("shared_sum_4out", (4096, 8192)), 1,
          "g = A + B feeding four sums: six reads, four writes, one kernel"),
         ("dag_bias_relu_mask_3out_8192x8192", lambda: W.dag_program("bias_relu_mask_3out"), 1,
@@ -364,6 +366,7 @@ PROFILE_GROUPS = {
     "row_l2_normalise": lambda W: W.row_program("l2_normalise"),
     "row_centre": lambda W: W.row_program("centre"),
     "row_affine_relu": lambda W: W.row_program("affine_relu"),
+    "row_rms_norm": lambda W: W.row_program("rms_norm"),
     "dag_shared_sum_4out": lambda W: W.dag_program("shared_sum_4out", (4096, 8192)),
 }
 
