@@ -2129,7 +2129,8 @@ std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceI
   if (dev.enable_static_chains) {
     uint32_t sig[40] = {(uint32_t)(counts & 0xffffffffu), (uint32_t)(counts >> 32)};
     for (size_t k = 0; k < words.size(); ++k) sig[k + 2] = (uint32_t)(words[k] & 0xffffffffu);
-    if (const KernelEntry* fixed = FindStaticChain("row_program", meta, (int)words.size() + 2, sig)) st.kernel = fixed;
+    if (const KernelEntry* fixed = FindStaticChain(group == 32 ? "row_program_w" : "row_program", meta, (int)words.size() + 2, sig))
+      st.kernel = fixed;
   }
   p->steps.push_back(st);
   return p;

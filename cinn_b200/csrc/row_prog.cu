@@ -377,39 +377,43 @@ struct StaticRowProgram {
 };
 
 // ---- the kernel body --------------------------------------------------------------------------------------------------
-template <class Prog>
+// FORM 0: warp or CTA per row by `group` at run time (the interpreting kernel); 1: a warp per row; 2: a CTA per row
+// (the specialised kernels: one instantiation each, so that the register cache below is sized for its form).
+template <class Prog, int FORM>
 __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInputs& inputs, const RowOutputs& out,
                                                  long long rows, long long r, long long group, long long vec_ok) {
   RowInputs in = inputs;
   in.row_len   = r;
   __shared__ float part[8][ROWP_SREGS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool per_warp   = group == 32;
+  const bool per_warp   = FORM == 1 ? true : (FORM == 2 ? false : group == 32);
   const long long first = per_warp ? (long long)blockIdx.x * 8 + warp : blockIdx.x;
   const long long step  = per_warp ? (long long)gridDim.x * 8 : gridDim.x;
   const int t = per_warp ? lane : (int)threadIdx.x, nt = per_warp ? 32 : 256;
   const int npass = prog.passes();
-  // A specialised program of several passes over a row that a CTA holds in at most four vectors per thread keeps the
-  // row in registers between the passes instead of reading it again.
-  constexpr int kCacheVecs = 4;
-  const bool use_cache = Prog::kStatic && !per_warp && vec_ok && npass > 1 && (r >> 2) <= (long long)kCacheVecs * 256;
+  // A specialised program of several passes keeps the row in registers between the passes instead of reading it
+  // again: a CTA holds a row of up to 4096 elements in four vectors per thread, a warp one of up to 1024 in eight
+  // vectors per lane.
+  constexpr int kCacheVecs = FORM == 1 ? 8 : 4;
+  constexpr int kStride    = FORM == 1 ? 32 : 256;
+  const bool use_cache = Prog::kStatic && FORM != 0 && vec_ok && npass > 1 && (r >> 2) <= (long long)kCacheVecs * kStride;
   float cache[kCacheVecs][DAG_MAX_IN][4];
   // CTA-per-row: every thread of the CTA walks the same rows, so the barriers below are uniform.
-  for (long long row = first; per_warp ? row < rows : row < rows; row += step) {
+  for (long long row = first; row < rows; row += step) {
     const long long base = row * r;
     in.row_base          = base;
     if (use_cache) {
       // this row's loads, all in flight together; the next row is asked into L2 meanwhile (no registers held for it),
-      // so that the CTA's next wait is an L2 latency, not a DRAM one
+      // so that the next wait is an L2 latency, not a DRAM one
 #pragma unroll
       for (int j = 0; j < kCacheVecs; ++j) {
-        const long long v = t + (long long)j * 256;
+        const long long v = t + (long long)j * kStride;
         if (v < (r >> 2)) prog.preload(in, base + (v << 2), cache[j]);
       }
       if (row + step < rows) {
 #pragma unroll
         for (int j = 0; j < kCacheVecs; ++j) {
-          const long long v = t + (long long)j * 256;
+          const long long v = t + (long long)j * kStride;
           if (v < (r >> 2)) prog.prefetch(in, base + step * r + (v << 2));
         }
       }
@@ -425,10 +429,10 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
       for (int k = 0; k < ROWP_SREGS; ++k) acc[k] = rp_identity((kinds >> (2 * k)) & 3);
       long long done = 0;
       if (use_cache) {
-        // every thread's (at most four) vectors of the row were loaded once, all the loads in flight together
+        // every thread's vectors of the row were loaded once, all the loads in flight together
 #pragma unroll
         for (int j = 0; j < kCacheVecs; ++j) {
-          const long long v = t + (long long)j * 256;
+          const long long v = t + (long long)j * kStride;
           if (v < (r >> 2)) prog.run_element_cached(pass, in, out, base + (v << 2), sregs, acc, cache[j]);
         }
         done = r;
@@ -502,15 +506,15 @@ __global__ void __launch_bounds__(256) k_row_program(ROWP_PARAMS) {
   grid_dependency_sync();
   ROWP_UNPACK;
   const DynRowProgram prog = {steps, (unsigned long long)counts, (unsigned long long)meta};
-  row_program_body(prog, in, out, rows, r, group, vec_ok);
+  row_program_body<DynRowProgram, 0>(prog, in, out, rows, r, group, vec_ok);
 }
 
-template <unsigned long long META, unsigned long long COUNTS, uint32_t... SIG>
-__global__ void __launch_bounds__(256) k_row_program_static(ROWP_PARAMS) {
+template <int FORM, unsigned long long META, unsigned long long COUNTS, uint32_t... SIG>
+__global__ void __launch_bounds__(256, FORM == 1 ? 3 : 1) k_row_program_static(ROWP_PARAMS) {
   grid_dependency_sync();
   ROWP_UNPACK;
   const StaticRowProgram<META, COUNTS, SIG...> prog = {steps};
-  row_program_body(prog, in, out, rows, r, group, vec_ok);
+  row_program_body<StaticRowProgram<META, COUNTS, SIG...>, FORM>(prog, in, out, rows, r, group, vec_ok);
 }
 
 template <uint32_t... SIG>
@@ -524,10 +528,13 @@ StaticChainKey MakeRowKey(const char* base, long long meta, long long counts) {
 
 CINN_B200_REGISTER_KERNEL_PDL("row_program", 70, 256, k_row_program);
 
+// Two kernels per program: a CTA per row (key "row_program") and a warp per row (key "row_program_w").
 #define STATIC_ROW_PROGRAM(ID, META, COUNTS, ...)                                                                  \
-  CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID, 70, 256, k_row_program_static<META##ull, COUNTS##ull, __VA_ARGS__>); \
+  CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID, 70, 256, k_row_program_static<2, META##ull, COUNTS##ull, __VA_ARGS__>); \
+  CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID "_w", 70, 256, k_row_program_static<1, META##ull, COUNTS##ull, __VA_ARGS__>); \
   static int cinn_b200_static_row_program_##ID =                                                                     \
-      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program", META##ll, COUNTS##ll), "row_program_static_" #ID)
+      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program", META##ll, COUNTS##ll), "row_program_static_" #ID) + \
+      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program_w", META##ll, COUNTS##ll), "row_program_static_" #ID "_w")
 
 #include "row_prog_static_table.inc"
 
