@@ -1111,20 +1111,10 @@ struct Matcher {
     }
     const OpDesc* op = Producer(o.name);
     if (op->type == "cast") op = Producer(op->inputs[0]);  // the widened form, see MatchReduce
-    int64_t outer, r, inner;
-    if (!ReduceView(x.shape, AttrList(*op, "dim"), &outer, &r, &inner)) {
-      Fail("reduce over non-adjacent axes has no prebuilt kernel");
-      return nullptr;
-    }
-    if (o.numel() != outer * inner) {
-      Fail("reduce output has " + std::to_string(o.numel()) + " elements, expected " + std::to_string(outer * inner));
-      return nullptr;
-    }
     const int64_t esize = DTypeBytes(x.dtype), V = 16 / esize;
     const int sms       = dev.sm_count;
     const std::string suffix = std::string(it->second) + "_" + tname;
-    auto p      = NewPlan(inner == 1 ? "row_reduce" : "col_reduce");
-    p->elements = x.numel();
+    std::unique_ptr<CompiledGroup> p;
     auto row_step = [&](ArgSpec src, ArgSpec dst, int64_t rows, int64_t len, std::vector<int> align_in) -> bool {
       LaunchStep s;
       if (!Kernel(&s, "reduce_generic_row_" + suffix)) return false;
@@ -1137,25 +1127,9 @@ struct Matcher {
       p->steps.push_back(s);
       return true;
     };
-    if (inner == 1) {
-      // Few very long rows: cut each row into S equal segments (partials in scratch), then fold the S partials.
-      int64_t S = 1;
-      if (outer < (int64_t)sms * 2 && r >= 65536) {
-        while (S < 1024 && r % (S * 2) == 0 && r / (S * 2) >= 4096 && outer * S < (int64_t)sms * 8) S *= 2;
-      }
-      if (S > 1) {
-        const int64_t off = p->scratch_bytes;
-        p->scratch_bytes += (size_t)RoundUp(outer * S * esize, 256);
-        if (!row_step(In(0), Scratch(off), outer * S, r / S, {0})) return nullptr;
-        if (!row_step(Scratch(off), Out(0), outer, S, {})) return nullptr;
-      } else if (!row_step(In(0), Out(0), outer, r, {0})) {
-        return nullptr;
-      }
-      return p;
-    }
     // Columns: a thread per 16 bytes of columns.  With few columns the reduced axis is split over blockIdx.z into
     // partial results in scratch, which a second launch of the same kernel folds.
-    auto col_step = [&](ArgSpec src, ArgSpec dst, int64_t o, int64_t len, int64_t in, int64_t splits,
+    auto col_step = [&](ArgSpec src, ArgSpec dst, int64_t o2, int64_t len, int64_t in, int64_t splits,
                         std::vector<int> align_in, bool dst_is_out) -> bool {
       LaunchStep s;
       if (!Kernel(&s, "reduce_generic_col_" + suffix)) return false;
@@ -1163,32 +1137,111 @@ struct Matcher {
       const int64_t cols = vec ? in / V : in;
       s.block[0] = cols >= 256 ? 256 : (cols >= 128 ? 128 : 64);
       s.grid[0]  = (unsigned)std::max<int64_t>(1, vec ? CeilDiv(cols, s.block[0]) : std::min<int64_t>(CeilDiv(cols, s.block[0]), (int64_t)sms * 8));
-      s.grid[1]  = (unsigned)std::min<int64_t>(o, 65535);
+      s.grid[1]  = (unsigned)std::min<int64_t>(o2, 65535);
       s.grid[2]  = (unsigned)splits;
       ArgSpec al = Aligned(vec, align_in, dst_is_out ? std::vector<int>{0} : std::vector<int>{});
-      s.args     = {src, dst, I(o), I(len), I(in), I(CeilDiv(len, splits)), al};
+      s.args     = {src, dst, I(o2), I(len), I(in), I(CeilDiv(len, splits)), al};
       p->steps.push_back(s);
       return true;
     };
-    const bool vec     = inner % V == 0;
-    const int64_t thr  = (vec ? inner / V : inner) * outer;
-    int64_t splits     = 1;
-    if (thr < (int64_t)sms * 512 && r >= 64 && x.numel() * esize >= (4 << 20)) {  // a second launch only pays on large inputs
-      splits = std::min<int64_t>(r / 16, CeilDiv((int64_t)sms * 1024, thr));
-      splits = std::max<int64_t>(1, std::min<int64_t>(splits, 512));
-    }
-    // whole groups of eight rows per split: the kernel keeps eight row loads in flight and takes a remainder one
-    // row (one DRAM latency) at a time
-    const int64_t rps = splits > 1 ? RoundUp(CeilDiv(r, splits), 8) : r;
-    splits            = CeilDiv(r, rps);
-    if (splits == 1) {
-      if (!col_step(In(0), Out(0), outer, r, inner, 1, {0}, true)) return nullptr;
+    // One [outer, r, inner] reduction from `src` to `dst` (either may be scratch memory of an earlier / for a later step).
+    auto plan_one = [&](ArgSpec src, ArgSpec dst, int64_t outer, int64_t r, int64_t inner, std::vector<int> align_in,
+                        bool dst_is_out) -> bool {
+      if (inner == 1) {
+        // Few very long rows: cut each row into S equal segments (partials in scratch), then fold the S partials.
+        int64_t S = 1;
+        if (outer < (int64_t)sms * 2 && r >= 65536) {
+          while (S < 1024 && r % (S * 2) == 0 && r / (S * 2) >= 4096 && outer * S < (int64_t)sms * 8) S *= 2;
+        }
+        if (S > 1) {
+          const int64_t off = p->scratch_bytes;
+          p->scratch_bytes += (size_t)RoundUp(outer * S * esize, 256);
+          return row_step(src, Scratch(off), outer * S, r / S, align_in) && row_step(Scratch(off), dst, outer, S, {});
+        }
+        return row_step(src, dst, outer, r, align_in);
+      }
+      const bool vec     = inner % V == 0;
+      const int64_t thr  = (vec ? inner / V : inner) * outer;
+      int64_t splits     = 1;
+      if (thr < (int64_t)sms * 512 && r >= 64 && outer * r * inner * esize >= (4 << 20)) {  // a second launch only pays on large inputs
+        splits = std::min<int64_t>(r / 16, CeilDiv((int64_t)sms * 1024, thr));
+        splits = std::max<int64_t>(1, std::min<int64_t>(splits, 512));
+      }
+      // whole groups of eight rows per split: the kernel keeps eight row loads in flight and takes a remainder one
+      // row (one DRAM latency) at a time
+      const int64_t rps = splits > 1 ? RoundUp(CeilDiv(r, splits), 8) : r;
+      splits            = CeilDiv(r, rps);
+      if (splits == 1) return col_step(src, dst, outer, r, inner, 1, align_in, dst_is_out);
+      const int64_t off = p->scratch_bytes;
+      p->scratch_bytes += (size_t)RoundUp(splits * outer * inner * esize, 256);
+      return col_step(src, Scratch(off), outer, r, inner, splits, align_in, false) &&
+             col_step(Scratch(off), dst, 1, splits, outer * inner, 1, {}, dst_is_out);
+    };
+    int64_t outer, r, inner;
+    if (!ReduceView(x.shape, AttrList(*op, "dim"), &outer, &r, &inner)) {
+      // Any other set of axes: the runs of adjacent reduced axes are folded one at a time, the last run first, each
+      // as an [outer, r, inner] reduction of what the previous step left in scratch memory (see MatchReduce; the
+      // intermediates have the tensor's own type, so a 16-bit sum is rounded to 16 bits between the steps, as the
+      // reference's accumulation in the tensor's type is at every step).
+      std::vector<int64_t> dims = AttrList(*op, "dim");
+      const int nd = (int)x.shape.size();
+      std::vector<bool> red(nd, false);
+      for (auto d : dims) {
+        if (d < 0) d += nd;
+        if (d < 0 || d >= nd) return nullptr;
+        red[d] = true;
+      }
+      std::vector<int64_t> ext;
+      std::vector<bool> is_red;
+      for (int i = 0; i < nd; ++i)
+        if (x.shape[i] != 1) {
+          ext.push_back(x.shape[i]);
+          is_red.push_back(red[i]);
+        }
+      int64_t kept = 1;
+      for (size_t i = 0; i < ext.size(); ++i) kept *= is_red[i] ? 1 : ext[i];
+      if (o.numel() != kept) {
+        Fail("reduce output has " + std::to_string(o.numel()) + " elements, expected " + std::to_string(kept));
+        return nullptr;
+      }
+      p           = NewPlan("multi_axis_reduce");
+      p->elements = x.numel();
+      ArgSpec src = In(0);
+      std::vector<int> align = {0};
+      while (true) {
+        int hi = (int)ext.size() - 1;
+        while (hi >= 0 && !is_red[hi]) --hi;
+        if (hi < 0) break;
+        int lo = hi;
+        while (lo > 0 && is_red[lo - 1]) --lo;
+        int64_t so = 1, sr = 1, si = 1;
+        for (int i = 0; i < lo; ++i) so *= ext[i];
+        for (int i = lo; i <= hi; ++i) sr *= ext[i];
+        for (int i = hi + 1; i < (int)ext.size(); ++i) si *= ext[i];
+        bool last = true;
+        for (int i = 0; i < lo; ++i) last = last && !is_red[i];
+        ArgSpec dst = Out(0);
+        if (!last) {
+          const int64_t off = p->scratch_bytes;
+          p->scratch_bytes += (size_t)RoundUp(so * si * esize, 256);
+          dst = Scratch(off);
+        }
+        if (!plan_one(src, dst, so, sr, si, align, last)) return nullptr;
+        ext.erase(ext.begin() + lo, ext.begin() + hi + 1);
+        is_red.erase(is_red.begin() + lo, is_red.begin() + hi + 1);
+        src = dst;
+        align.clear();
+        if (last) break;
+      }
       return p;
     }
-    const int64_t off = p->scratch_bytes;
-    p->scratch_bytes += (size_t)RoundUp(splits * outer * inner * esize, 256);
-    if (!col_step(In(0), Scratch(off), outer, r, inner, splits, {0}, false)) return nullptr;
-    if (!col_step(Scratch(off), Out(0), 1, splits, outer * inner, 1, {}, true)) return nullptr;
+    if (o.numel() != outer * inner) {
+      Fail("reduce output has " + std::to_string(o.numel()) + " elements, expected " + std::to_string(outer * inner));
+      return nullptr;
+    }
+    p           = NewPlan(inner == 1 ? "row_reduce" : "col_reduce");
+    p->elements = x.numel();
+    if (!plan_one(In(0), Out(0), outer, r, inner, {0}, true)) return nullptr;
     return p;
   }
 

@@ -53,6 +53,7 @@
 namespace cinn_b200 {
 
 int SetLastError(int code, const std::string& message);  // runtime.cc
+int OptPeerReducersPerSm();                                // runtime.cc: option "peer_reducers_per_sm"
 
 CINN_B200_DEFINE_ASYNC_TIMEOUT_COUNTER(g_peer_wait_timeouts);
 
@@ -300,6 +301,9 @@ int PlanLaunch(cinn_b200_peer_ctx* c, int kind, long long rows_local, long long 
   long long comb = std::min<long long>(tiles, std::max<long long>(1, std::min<long long>(c->sms, cap / 4)));
   long long gath = gather ? std::min<long long>(tiles * (c->world - 1), std::max<long long>(1, std::min<long long>(c->sms, cap / 4))) : 0;
   long long red  = std::min<long long>(tiles * c->world, cap - comb - gath);
+  // Fewer reducers than fit finish their items sooner, one round after the other, so that the partials (and with them
+  // the exchange) are spread over the whole reduction instead of arriving in one or two bursts.
+  if (OptPeerReducersPerSm() > 0) red = std::min<long long>(red, (long long)OptPeerReducersPerSm() * c->sms / ranks_in_launch);
   if (red < 1) return SetLastError(CINN_B200_ECUDA, "col_reduce_sharded: the GPU cannot hold one CTA per role");
   // Every reducer gets the same number of items (1024 items on 316 CTAs would leave most of them idle during the
   // fourth round; 256 CTAs with four items each finish together).

@@ -386,7 +386,10 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
   in.row_len   = r;
   __shared__ float part[8][ROWP_SREGS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool per_warp   = FORM == 1 ? true : (FORM == 2 ? false : group == 32);
+  // (FORM 2 keeps the run-time test although its rows always get a CTA: with the test folded away the compiler packs
+  // the CTA form into fewer registers and no longer issues a row's loads together -- measured on B200, rms_norm over
+  // 16384 x 4096 fell from 0.90 to 0.45 of the HBM peak.)
+  const bool per_warp   = FORM == 1 ? true : group == 32;
   const long long first = per_warp ? (long long)blockIdx.x * 8 + warp : blockIdx.x;
   const long long step  = per_warp ? (long long)gridDim.x * 8 : gridDim.x;
   const int t = per_warp ? lane : (int)threadIdx.x, nt = per_warp ? 32 : 256;
@@ -396,7 +399,8 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
   // vectors per lane.
   constexpr int kCacheVecs = FORM == 1 ? 8 : 4;
   constexpr int kStride    = FORM == 1 ? 32 : 256;
-  const bool use_cache = Prog::kStatic && FORM != 0 && vec_ok && npass > 1 && (r >> 2) <= (long long)kCacheVecs * kStride;
+  const bool use_cache = Prog::kStatic && FORM != 0 && (FORM == 1 || !per_warp) && vec_ok && npass > 1 &&
+                         (r >> 2) <= (long long)kCacheVecs * kStride;
   float cache[kCacheVecs][DAG_MAX_IN][4];
   // CTA-per-row: every thread of the CTA walks the same rows, so the barriers below are uniform.
   for (long long row = first; row < rows; row += step) {
@@ -510,7 +514,7 @@ __global__ void __launch_bounds__(256) k_row_program(ROWP_PARAMS) {
 }
 
 template <int FORM, unsigned long long META, unsigned long long COUNTS, uint32_t... SIG>
-__global__ void __launch_bounds__(256, FORM == 1 ? 3 : 1) k_row_program_static(ROWP_PARAMS) {
+__global__ void __launch_bounds__(256, 3) k_row_program_static(ROWP_PARAMS) {
   grid_dependency_sync();
   ROWP_UNPACK;
   const StaticRowProgram<META, COUNTS, SIG...> prog = {steps};

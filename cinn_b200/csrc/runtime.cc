@@ -101,6 +101,7 @@ static int g_opt_ew_stream = 1, g_opt_ew_stream_stages = 0, g_opt_ew_stream_ctas
 static int g_opt_static_chains = 1;
 static int g_opt_fuse_interpreted = 0;
 static int g_opt_pdl = 1;  // programmatic dependent launch for the kernels that support it
+static int g_opt_peer_reducers_per_sm = 0;  // reducer CTAs per SM of the fused reduce + exchange kernel (0: automatic)
 static int g_opt_host_chunks = 0;  // upper limit of the chunks group_run_host cuts a group into (0: up to 16)
 static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1, g_opt_rownorm_simple = -1;
 
@@ -848,10 +849,20 @@ int cinn_b200_device_status(unsigned int* async_wait_timeouts) {
   return CINN_B200_OK;
 }
 
+}  // extern "C"
+namespace cinn_b200 {
+int OptPeerReducersPerSm() { return g_opt_peer_reducers_per_sm; }
+}  // namespace cinn_b200
+extern "C" {
+
 int cinn_b200_set_option(const char* key, long long value) {
   if (!key) return SetError(CINN_B200_EINVAL, "null option key");
   if (!strcmp(key, "sm_count")) {
     g_opt_sm_count = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "peer_reducers_per_sm")) {
+    g_opt_peer_reducers_per_sm = (int)value;
     return CINN_B200_OK;
   }
   if (!strcmp(key, "host_chunks")) {

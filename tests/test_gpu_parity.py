@@ -456,3 +456,41 @@ def test_reduce_over_non_adjacent_axes(oracle, shape, dims, kind, keep):
     else:
         r = int(np.prod([shape[d] for d in dims]))
         assert np.allclose(got, want, rtol=1e-5, atol=2e-6 * np.sqrt(r))
+
+
+@pytest.mark.parametrize("dtype", ["int32", "int64", "float16", "float64", "bool"])
+@pytest.mark.parametrize("shape,dims", [((8, 16, 32, 4), (0, 2)), ((6, 5, 7, 3, 9), (0, 2, 4)), ((64, 3, 128, 8), (1, 3))])
+def test_reduce_over_non_adjacent_axes_other_types(oracle, dtype, shape, dims):
+    """The same plan for the other element types (integers and bool bit-exact; float16 against the exact sum at 1e-2,
+    float64 at 1e-12)."""
+    import torch
+    import cinn_b200
+    rng = np.random.default_rng(9)
+    kind = "all" if dtype == "bool" else "sum"
+    npt = {"int32": np.int32, "int64": np.int64, "float16": np.float16, "float64": np.float64, "bool": np.bool_}[dtype]
+    if dtype == "bool":
+        x = rng.random(shape) > 0.02
+    elif dtype.startswith("int"):
+        x = rng.integers(-1000, 1000, shape).astype(npt)
+    else:
+        x = rng.standard_normal(shape).astype(npt)
+    out_shape = [d for i, d in enumerate(shape) if i not in dims]
+    s = lambda sh: ",".join(str(d) for d in sh)  # noqa: E731
+    desc = ("group fn_multi_axis_%s_%s\ninput X %s %s\nop reduce_%s y = X ; dim=%s keep_dim=false\noutput y %s %s\n"
+            % (kind, dtype, dtype, s(shape), kind, s(dims), dtype, s(out_shape)))
+    g = cinn_b200.FusedGroup(desc)
+    assert g.pattern == "multi_axis_reduce" and g.launches >= 2
+    tt = {"int32": torch.int32, "int64": torch.int64, "float16": torch.float16, "float64": torch.float64, "bool": torch.bool}[dtype]
+    out = torch.empty(out_shape, device="cuda", dtype=tt)
+    g.run([torch.from_numpy(x).cuda(), out])
+    torch.cuda.synchronize()
+    g.release()
+    got = out.cpu().numpy()
+    if dtype == "bool":
+        assert np.array_equal(got, x.all(axis=dims))
+    elif dtype.startswith("int"):
+        assert np.array_equal(got, x.sum(axis=dims, dtype=npt))
+    else:
+        exact = x.astype(np.float64).sum(axis=dims)
+        tol = 1e-2 if dtype == "float16" else 1e-12
+        assert np.allclose(got.astype(np.float64), exact, rtol=tol, atol=tol * np.sqrt(np.prod([shape[d] for d in dims])))
