@@ -316,6 +316,9 @@ int cinn_b200_device_status(unsigned int* async_wait_timeouts);
  * or row-program kernel takes (one launch, but several times slower per byte than the specialised kernels; off, such
  * regions are split into groups the chain and reduction kernels take; a group handed to cinn_b200_compile_group
  * directly is always accepted);
+ * "peer_reducers_per_sm" (default 0 = as many as fit): the most reducer CTAs per SM of the fused reduce + exchange
+ * kernel (fewer reducers take their items in more rounds; measured on 4 GPUs: two to four per SM change nothing, one
+ * per SM is too few to stream the local rows at full bandwidth);
  * "host_chunks" (default 0 = up to 16): the most chunks cinn_b200_group_run_host pipelines a group over (read at the
  * group's first host run);
  * "enable_ew_stream" (default 1),
