@@ -1158,7 +1158,16 @@ std::unique_ptr<CompiledGroup> MatchChainReduce(const GroupDesc& g, const Device
     st.args.push_back(int_arg(inner));
     st.args.push_back(int_arg(rows_per_split));
     p->steps.push_back(st);
-    if (S > 1) {
+    if (S > 1 && (outer * inner) % 4 == 0) {
+      // few columns, S rows of partials: the rows over the warps of a CTA (reduce_generic.cu)
+      LaunchStep f;
+      f.kernel = FindKernel(std::string("reduce_generic_col_fold_") + opname + "_f32");
+      if (!f.kernel) return nullptr;
+      f.block[0] = 256;
+      f.grid[0]  = (unsigned)CeilDiv(outer * inner / 4, 32);
+      f.args     = {scratch_arg(0), out_arg, int_arg(S), int_arg(outer * inner)};
+      p->steps.push_back(f);
+    } else if (S > 1) {
       LaunchStep f;
       f.kernel = FindKernel(std::string("reduce_generic_col_") + opname + "_f32");
       if (!f.kernel) return nullptr;

@@ -12,6 +12,7 @@
 // launch and the result does not depend on which CTA came last.  The DUAL form keeps two accumulations, sum and sum
 // of squares, for the two-output group {reduce_sum(x), reduce_sum(x * x)}.  Squares are rounded products added
 // without fma, as a materialised producer would be.
+#include <type_traits>
 #include "device_math.cuh"
 #include "kernel_registry.h"
 
@@ -70,6 +71,24 @@ __device__ __forceinline__ void walk_vectors(const uint4* __restrict__ px, const
 #pragma unroll
     for (int j = 0; j < U; ++j) {
       if (ok[j]) {
+        if constexpr (sizeof(T) == 2 && DUAL && !GRAD && std::is_same<OpA, SumOp>::value &&
+                      std::is_same<OpB, SumSquareOp>::value) {
+          // sum and sum of squares of 16-bit values with the mixed-precision add / fma of sm_100 (the operand is
+          // widened inside the instruction: no conversion instructions; x * x is exact in fp32, so the fma rounds
+          // exactly where a + x * x does)
+          const unsigned short* h = reinterpret_cast<const unsigned short*>(&r[j]);
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            if constexpr (std::is_same<T, __half>::value) {
+              asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(a0) : "h"(h[i]));
+              asm("fma.rn.f32.f16 %0, %1, %1, %0;" : "+f"(a1) : "h"(h[i]));
+            } else {
+              asm("add.rn.f32.bf16 %0, %1, %0;" : "+f"(a0) : "h"(h[i]));
+              asm("fma.rn.f32.bf16 %0, %1, %1, %0;" : "+f"(a1) : "h"(h[i]));
+            }
+          }
+          continue;
+        }
         float f[V], f2[V];
         Io<T>::unpack(r[j], f);
         if (GRAD) Io<T>::unpack(r2[GRAD ? j : 0], f2);

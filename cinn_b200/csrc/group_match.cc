@@ -879,6 +879,16 @@ struct Matcher {
               Aligned(vec, src_in_for_align, {})};
     p->steps.push_back(s);
     const int64_t oi = outer * inner;
+    if (oi % 4 == 0 && FindKernel(std::string("reduce_generic_col_fold_") + BaseReduceOp(opname) + "_f32")) {
+      // the partials are few columns and `splits` rows: the rows over the warps of a CTA (reduce_generic.cu)
+      LaunchStep f;
+      if (!Kernel(&f, std::string("reduce_generic_col_fold_") + BaseReduceOp(opname) + "_f32")) return false;
+      f.block[0] = 256;
+      f.grid[0]  = (unsigned)CeilDiv(oi / 4, 32);
+      f.args     = {Scratch(scratch_off), dst, I(splits), I(oi)};
+      p->steps.push_back(f);
+      return true;
+    }
     return PlanReduce(p, BaseReduceOp(opname), 1, splits, oi, Scratch(scratch_off), dst, {});
   }
 
@@ -1174,8 +1184,17 @@ struct Matcher {
       if (splits == 1) return col_step(src, dst, outer, r, inner, 1, align_in, dst_is_out);
       const int64_t off = p->scratch_bytes;
       p->scratch_bytes += (size_t)RoundUp(splits * outer * inner * esize, 256);
-      return col_step(src, Scratch(off), outer, r, inner, splits, align_in, false) &&
-             col_step(Scratch(off), dst, 1, splits, outer * inner, 1, {}, dst_is_out);
+      if (!col_step(src, Scratch(off), outer, r, inner, splits, align_in, false)) return false;
+      if ((outer * inner) % V == 0) {  // the partials are few columns and many rows: rows over the warps of a CTA
+        LaunchStep f;
+        if (!Kernel(&f, "reduce_generic_col_fold_" + suffix)) return false;
+        f.block[0] = 256;
+        f.grid[0]  = (unsigned)CeilDiv(outer * inner / V, 32);
+        f.args     = {Scratch(off), dst, I(splits), I(outer * inner)};
+        p->steps.push_back(f);
+        return true;
+      }
+      return col_step(Scratch(off), dst, 1, splits, outer * inner, 1, {}, dst_is_out);
     };
     int64_t outer, r, inner;
     if (!ReduceView(x.shape, AttrList(*op, "dim"), &outer, &r, &inner)) {

@@ -8,6 +8,7 @@
 // Two layouts, as in reduce_kernels.cu: rows (inner == 1: a warp or a CTA per row) and columns (inner > 1: a
 // thread per 16 bytes of columns, eight row loads in flight).  16-byte loads when the buffers allow it.
 #include <cstdint>
+#include <type_traits>
 
 #include "device_math.cuh"
 #include "kernel_registry.h"
@@ -108,12 +109,28 @@ struct GAny {
   __device__ static int32_t apply(int32_t a, int32_t b) { return a || b; }
 };
 
+// acc (+)= v for one stored element.  A sum of 16-bit floats uses the mixed-precision add of sm_100 (add.f32.f16 /
+// add.f32.bf16: the operand is widened inside the instruction), one instruction instead of a conversion on the
+// XU pipe plus an add; the result is the same bit for bit (the widening is exact, the add rounds once).
+template <typename T, class Op>
+__device__ __forceinline__ typename Elem<T>::Acc fold_elem(typename Elem<T>::Acc acc, T v) {
+  if constexpr (std::is_same<Op, GSum>::value && std::is_same<T, __half>::value) {
+    asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc) : "h"(__half_as_ushort(v)));
+    return acc;
+  } else if constexpr (std::is_same<Op, GSum>::value && std::is_same<T, __nv_bfloat16>::value) {
+    asm("add.rn.f32.bf16 %0, %1, %0;" : "+f"(acc) : "h"(__bfloat16_as_ushort(v)));
+    return acc;
+  } else {
+    return Op::apply(acc, Elem<T>::load(v));
+  }
+}
+
 template <typename T, class Op>
 __device__ __forceinline__ void fold16(const uint4& u, typename Elem<T>::Acc& acc) {
   constexpr int V = 16 / sizeof(T);
   const T* e      = reinterpret_cast<const T*>(&u);
 #pragma unroll
-  for (int i = 0; i < V; ++i) acc = Op::apply(acc, Elem<T>::load(e[i]));
+  for (int i = 0; i < V; ++i) acc = fold_elem<T, Op>(acc, e[i]);
 }
 
 template <typename A, class Op>
@@ -155,7 +172,7 @@ __global__ void __launch_bounds__(256)
       for (; v < nv; v += nt) fold16<T, Op>(__ldcs(pv + v), acc);
       done = nv * V;
     }
-    for (long long i = done + t; i < r; i += nt) acc = Op::apply(acc, Elem<T>::load(px[i]));
+    for (long long i = done + t; i < r; i += nt) acc = fold_elem<T, Op>(acc, px[i]);
     acc = warp_fold<A, Op>(acc);
     if (per_warp) {
       if (lane == 0) y[row] = Elem<T>::store(acc);
@@ -203,14 +220,14 @@ __global__ void __launch_bounds__(256)
           for (int q = 0; q < 8; ++q) {
             const T* e = reinterpret_cast<const T*>(&u[q]);
 #pragma unroll
-            for (int i = 0; i < V; ++i) acc[i] = Op::apply(acc[i], Elem<T>::load(e[i]));
+            for (int i = 0; i < V; ++i) acc[i] = fold_elem<T, Op>(acc[i], e[i]);
           }
         }
         for (; k < r; ++k) {
           const uint4 u = __ldcs(pv + k * nv);
           const T* e    = reinterpret_cast<const T*>(&u);
 #pragma unroll
-          for (int i = 0; i < V; ++i) acc[i] = Op::apply(acc[i], Elem<T>::load(e[i]));
+          for (int i = 0; i < V; ++i) acc[i] = fold_elem<T, Op>(acc[i], e[i]);
         }
         uint4 out;
         T* e = reinterpret_cast<T*>(&out);
@@ -223,14 +240,74 @@ __global__ void __launch_bounds__(256)
         A a0 = Op::template identity<T>(), a1 = a0, a2 = a0, a3 = a0;
         long long k = 0;
         for (; k + 4 <= r; k += 4) {
-          a0 = Op::apply(a0, Elem<T>::load(px[(k + 0) * inner + c]));
-          a1 = Op::apply(a1, Elem<T>::load(px[(k + 1) * inner + c]));
-          a2 = Op::apply(a2, Elem<T>::load(px[(k + 2) * inner + c]));
-          a3 = Op::apply(a3, Elem<T>::load(px[(k + 3) * inner + c]));
+          a0 = fold_elem<T, Op>(a0, px[(k + 0) * inner + c]);
+          a1 = fold_elem<T, Op>(a1, px[(k + 1) * inner + c]);
+          a2 = fold_elem<T, Op>(a2, px[(k + 2) * inner + c]);
+          a3 = fold_elem<T, Op>(a3, px[(k + 3) * inner + c]);
         }
-        for (; k < r; ++k) a0 = Op::apply(a0, Elem<T>::load(px[k * inner + c]));
+        for (; k < r; ++k) a0 = fold_elem<T, Op>(a0, px[k * inner + c]);
         py[c] = Elem<T>::store(Op::apply(Op::apply(a0, a1), Op::apply(a2, a3)));
       }
+    }
+  }
+}
+
+// ---- fold of few columns: y[c] = fold over x[0..r, c] with the rows spread over the warps of a CTA ----------------------
+// The second step of a split column reduction has r = number of splits (tens to hundreds) and only inner / V column
+// groups: with a thread per column group it would run on a handful of CTAs, each walking all the rows eight at a
+// time.  Here a CTA takes 32 column groups (a warp reads 512 contiguous bytes of a row) and its 8 warps take the
+// rows k = warp, warp + 8, ... (up to four loads in flight each); the warps' accumulators meet in shared memory and
+// warp 0 folds them in warp order.  Needs inner % V == 0 (the planner checks) and a 16-byte aligned x.
+template <typename T, class Op>
+__global__ void __launch_bounds__(256)
+    k_reduce_generic_col_fold(const T* __restrict__ x, T* __restrict__ y, long long r, long long inner) {
+  using A         = typename Elem<T>::Acc;
+  constexpr int V = 16 / sizeof(T);
+  __shared__ A part[8][32][V + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long nv = inner / V;
+  const long long c  = (long long)blockIdx.x * 32 + lane;
+  A acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = Op::template identity<T>();
+  if (c < nv) {
+    const uint4* pv = reinterpret_cast<const uint4*>(x) + c;
+    long long k     = warp;
+    for (; k + 24 < r; k += 32) {
+      uint4 u[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) u[q] = __ldcs(pv + (k + 8 * q) * nv);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const T* e = reinterpret_cast<const T*>(&u[q]);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fold_elem<T, Op>(acc[i], e[i]);
+      }
+    }
+    for (; k < r; k += 8) {
+      const uint4 u = __ldcs(pv + k * nv);
+      const T* e    = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = fold_elem<T, Op>(acc[i], e[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) part[warp][lane][i] = acc[i];
+  __syncthreads();
+  if (warp == 0 && c < nv) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w)
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = Op::apply(acc[i], part[w][lane][i]);
+    uint4 out;
+    T* e = reinterpret_cast<T*>(&out);
+#pragma unroll
+    for (int i = 0; i < V; ++i) e[i] = Elem<T>::store(acc[i]);
+    if ((reinterpret_cast<uintptr_t>(y) & 15u) == 0) {
+      reinterpret_cast<uint4*>(y)[c] = out;
+    } else {  // the group's output may sit at any address; the partials this kernel reads are always aligned
+#pragma unroll
+      for (int i = 0; i < V; ++i) y[c * V + i] = e[i];
     }
   }
 }
@@ -239,7 +316,8 @@ __global__ void __launch_bounds__(256)
 
 #define REG_GENERIC(OPNAME, OP, TNAME, T)                                                                       \
   CINN_B200_REGISTER_KERNEL("reduce_generic_row_" OPNAME "_" TNAME, 6, 256, k_reduce_generic_row<T, OP>);      \
-  CINN_B200_REGISTER_KERNEL("reduce_generic_col_" OPNAME "_" TNAME, 7, 256, k_reduce_generic_col<T, OP>)
+  CINN_B200_REGISTER_KERNEL("reduce_generic_col_" OPNAME "_" TNAME, 7, 256, k_reduce_generic_col<T, OP>);      \
+  CINN_B200_REGISTER_KERNEL("reduce_generic_col_fold_" OPNAME "_" TNAME, 4, 256, k_reduce_generic_col_fold<T, OP>)
 #define REG_GENERIC_ARITH(TNAME, T)   \
   REG_GENERIC("sum", GSum, TNAME, T);  \
   REG_GENERIC("prod", GProd, TNAME, T); \
