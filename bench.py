@@ -358,6 +358,7 @@ PROFILE_GROUPS = {
     "chain_abs_add_f64": lambda W: W.generic_chain("abs_add_f64", (8192, 4096)),
     "reduce_sum_f16_rows": lambda W: W.generic_reduce("sum", "float16", axis=1),
     "reduce_sum_i32_cols": lambda W: W.generic_reduce("sum", "int32", axis=0),
+    "reduce_sum_f16_cols": lambda W: W.generic_reduce("sum", "float16", axis=0),
     "chain_reduce_rows": lambda W: W.chain_reduce("sum_abs_diff", axis=1),
     "chain_tree": lambda W: W.chain_tree(),
     "bn_train_stats_f16": lambda W: W.bn_train_stats((256, 64, 112, 112), half=True),

@@ -128,6 +128,17 @@ __device__ __forceinline__ typename Elem<T>::Acc fold_elem(typename Elem<T>::Acc
 template <typename T, class Op>
 __device__ __forceinline__ void fold16(const uint4& u, typename Elem<T>::Acc& acc) {
   constexpr int V = 16 / sizeof(T);
+  if constexpr (std::is_same<T, uint8_t>::value && (std::is_same<Op, GAll>::value || std::is_same<Op, GAny>::value)) {
+    // sixteen bools at once: "any" is a non-zero word; "all" is a word without a zero byte
+    // ((w - 0x01010101) & ~w & 0x80808080 is non-zero exactly when some byte of w is zero)
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      if constexpr (std::is_same<Op, GAny>::value) acc = acc | (w[q] != 0u ? 1 : 0);
+      else acc = acc & ((((w[q] - 0x01010101u) & ~w[q] & 0x80808080u) == 0u) ? 1 : 0);
+    }
+    return;
+  }
   const T* e      = reinterpret_cast<const T*>(&u);
 #pragma unroll
   for (int i = 0; i < V; ++i) acc = fold_elem<T, Op>(acc, e[i]);
