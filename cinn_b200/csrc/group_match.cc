@@ -268,6 +268,7 @@ struct Matcher {
     if (!Kernel(&s, std::string("ew_bias_scale_tanh_cast_f32_") + suffix)) return nullptr;
     s.block[0] = 256;
     s.grid[0]  = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(CeilDiv(n, 8), 512), dev.sm_count * 32));
+    if (dev.ew_reg_ctas_per_sm > 0) s.grid[0] = (unsigned)std::min<int64_t>(s.grid[0] * 2, (int64_t)dev.sm_count * dev.ew_reg_ctas_per_sm);
     s.args     = {In(xi), In(bi), Out(0), I(n), I(cols), Aligned(cols % 8 == 0, {0, 1}, {0}),
                   F((float)AttrF(*scale, "scale", 1.0)), F((float)AttrF(*scale, "bias", 0.0))};
     // Large 16-bit-output launches stream x through warp-private shared-memory rings filled by bulk copies

@@ -321,6 +321,8 @@ int cinn_b200_device_status(unsigned int* async_wait_timeouts);
  * per SM is too few to stream the local rows at full bandwidth);
  * "host_chunks" (default 0 = up to 16): the most chunks cinn_b200_group_run_host pipelines a group over (read at the
  * group's first host run);
+ * "ew_reg_ctas_per_sm" (default 0 = by size): grid of the register form of the bias / scale / tanh / cast kernel in
+ * CTAs per SM (measured on an 8.4 M-element shard: 4 to 16 per SM all within 10.7-11.2 us);
  * "enable_ew_stream" (default 1),
  * "ew_stream_stages", "ew_stream_ctas_per_sm": whether large elementwise groups with 16-bit outputs stream their
  * input through shared-memory rings filled by bulk copies, the ring depth and the resident CTAs per SM; "rownorm_rows_per_iter": rows per CTA
