@@ -315,3 +315,30 @@ def test_integer_pow_known_answers():
                (3037000499, 2, int(float(3037000499 ** 2))), (5, -2, 0), (-1, 2 ** 62 + 1, 1), (2 ** 53 + 1, 1, 2 ** 53)]
     a, b, want = zip(*cases64)
     assert orc.pow_int(i64(a), i64(b)).tolist() == list(want)
+
+
+def test_uint8_follows_the_unsigned_instructions():
+    """uint8 tensors: the reference's LLVM code generator picks UDiv / URem, unsigned compares, a logical right shift
+    and zero-extending casts for `uint` types (cinn/backends/llvm/codegen_llvm.cc:205-216, 280-340, 1449-1457); the
+    arithmetic wraps modulo 256.  Known answers through the op-by-op evaluator."""
+    from oracle import x86_graph_eval as ge
+    a = np.array([200, 255, 0, 7, 128, 1], np.uint8)
+    b = np.array([100, 1, 0, 2, 255, 0], np.uint8)
+
+    def run(op, extra=""):
+        desc = ("group g\ninput A uint8 6\ninput B uint8 6\nop %s y = A B ; axis=-1%s\noutput y %s 6\n"
+                % (op, extra, "bool" if op in ("greater_than", "less_equal") else "uint8"))
+        return ge.run(desc, [a, b])
+    assert run("elementwise_add").tolist() == [44, 0, 0, 9, 127, 1]          # modulo 256
+    assert run("subtract").tolist() == [100, 254, 0, 5, 129, 1]
+    assert run("elementwise_mul").tolist() == [32, 255, 0, 14, 128, 0]
+    assert run("divide").tolist() == [2, 255, 0, 3, 0, 0]                     # unsigned; a zero divisor gives 0 here
+    assert run("mod").tolist() == [0, 0, 0, 1, 128, 0]
+    assert run("greater_than").tolist() == [True, True, False, True, False, True]   # 128 > 255 is false: unsigned
+    assert run("right_shift").tolist() == [200 >> 4, 255 >> 1, 0, 7 >> 2, 128 >> 7, 1]   # logical, count modulo 8
+    desc = "group g\ninput A uint8 6\nop cast y = A ; dtype=int32\noutput y int32 6\n"
+    assert ge.run(desc, [a]).tolist() == [200, 255, 0, 7, 128, 1]            # zero-extended
+    desc = "group g\ninput A uint8 6\nop cast y = A ; dtype=float32\noutput y float32 6\n"
+    assert ge.run(desc, [a]).tolist() == [200.0, 255.0, 0.0, 7.0, 128.0, 1.0]
+    desc = "group g\ninput A uint8 6\nop negative y = A\noutput y uint8 6\n"
+    assert ge.run(desc, [a]).tolist() == [56, 1, 0, 249, 128, 255]
