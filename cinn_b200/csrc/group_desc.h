@@ -100,6 +100,7 @@ struct DeviceInfo {
   int enable_ew_stream      = 1;   // elementwise groups streamed through shared-memory rings (0 = register kernels)
   int ew_stream_stages      = 0;
   int ew_stream_ctas_per_sm = 0;
+  int rowp_form = 0;  // row programs: 0 automatic, 32 a warp per row, 128 half a CTA per row, 256 a CTA per row
   int ew_reg_ctas_per_sm = 0;  // grid of the register form of the headline elementwise kernel (0: by size)
   int rownorm_rows_per_iter = 0;  // rows a CTA of the register-resident kernels takes per iteration
   int rownorm_simple        = -1;  // plain softmax by the one-CTA-per-row kernel of softmax_safe.cu: 1 on, 0 off, -1 automatic

@@ -377,7 +377,8 @@ struct StaticRowProgram {
 };
 
 // ---- the kernel body --------------------------------------------------------------------------------------------------
-// FORM 0: warp or CTA per row by `group` at run time (the interpreting kernel); 1: a warp per row; 2: a CTA per row
+// FORM 0: warp or CTA per row by `group` at run time (the interpreting kernel); 1: a warp per row; 2: a CTA per row;
+// 3: half a CTA (four warps) per row, two rows per CTA at a time, each half with a named barrier of its own
 // (the specialised kernels: one instantiation each, so that the register cache below is sized for its form).
 template <class Prog, int FORM>
 __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInputs& inputs, const RowOutputs& out,
@@ -386,20 +387,22 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
   in.row_len   = r;
   __shared__ float part[8][ROWP_SREGS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = FORM == 3 ? (int)(threadIdx.x >> 7) : 0;  // FORM 3: which of the CTA's two rows
   // (FORM 2 keeps the run-time test although its rows always get a CTA: with the test folded away the compiler packs
   // the CTA form into fewer registers and no longer issues a row's loads together -- measured on B200, rms_norm over
   // 16384 x 4096 fell from 0.90 to 0.45 of the HBM peak.)
   const bool per_warp   = FORM == 1 ? true : group == 32;
-  const long long first = per_warp ? (long long)blockIdx.x * 8 + warp : blockIdx.x;
-  const long long step  = per_warp ? (long long)gridDim.x * 8 : gridDim.x;
-  const int t = per_warp ? lane : (int)threadIdx.x, nt = per_warp ? 32 : 256;
+  const long long first = FORM == 3 ? (long long)blockIdx.x * 2 + half : (per_warp ? (long long)blockIdx.x * 8 + warp : blockIdx.x);
+  const long long step  = FORM == 3 ? (long long)gridDim.x * 2 : (per_warp ? (long long)gridDim.x * 8 : gridDim.x);
+  const int t  = FORM == 3 ? (int)(threadIdx.x & 127) : (per_warp ? lane : (int)threadIdx.x);
+  const int nt = FORM == 3 ? 128 : (per_warp ? 32 : 256);
   const int npass = prog.passes();
   // A specialised program of several passes keeps the row in registers between the passes instead of reading it
   // again: a CTA holds a row of up to 4096 elements in four vectors per thread, a warp one of up to 1024 in eight
   // vectors per lane.
-  constexpr int kCacheVecs = FORM == 1 ? 8 : 4;
-  constexpr int kStride    = FORM == 1 ? 32 : 256;
-  const bool use_cache = Prog::kStatic && FORM != 0 && (FORM == 1 || !per_warp) && vec_ok && npass > 1 &&
+  constexpr int kCacheVecs = FORM == 1 || FORM == 3 ? 8 : 4;
+  constexpr int kStride    = FORM == 1 ? 32 : (FORM == 3 ? 128 : 256);
+  const bool use_cache = Prog::kStatic && FORM != 0 && (FORM == 1 || FORM == 3 || !per_warp) && vec_ok && npass > 1 &&
                          (r >> 2) <= (long long)kCacheVecs * kStride;
   float cache[kCacheVecs][DAG_MAX_IN][4];
   // CTA-per-row: every thread of the CTA walks the same rows, so the barriers below are uniform.
@@ -459,7 +462,26 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
         for (int o = 16; o > 0; o >>= 1) v = rp_fold(kind, v, __shfl_xor_sync(0xffffffffu, v, o));
         acc[k] = v;
       }
-      if (!per_warp && mask) {
+      if (FORM == 3 && mask) {
+        // the four warps of this half meet at a barrier of their own (ids 1 and 2): the CTA's two rows never wait
+        // for each other
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+        if (lane == 0) {
+#pragma unroll
+          for (int k = 0; k < ROWP_SREGS; ++k)
+            if (mask & (1u << k)) part[warp][k] = acc[k];
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+#pragma unroll
+        for (int k = 0; k < ROWP_SREGS; ++k) {
+          if (!(mask & (1u << k))) continue;
+          const int kind = (kinds >> (2 * k)) & 3;
+          float v = part[4 * half][k];
+#pragma unroll
+          for (int w2 = 1; w2 < 4; ++w2) v = rp_fold(kind, v, part[4 * half + w2][k]);
+          acc[k] = v;
+        }
+      } else if (!per_warp && mask) {
         __syncthreads();  // the previous pass's reads of `part` are over
         if (lane == 0) {
 #pragma unroll
@@ -532,13 +554,16 @@ StaticChainKey MakeRowKey(const char* base, long long meta, long long counts) {
 
 CINN_B200_REGISTER_KERNEL_PDL("row_program", 70, 256, k_row_program);
 
-// Two kernels per program: a CTA per row (key "row_program") and a warp per row (key "row_program_w").
+// Three kernels per program: a CTA per row (key "row_program"), a warp per row (key "row_program_w") and half a CTA
+// per row (key "row_program_h").
 #define STATIC_ROW_PROGRAM(ID, META, COUNTS, ...)                                                                  \
   CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID, 70, 256, k_row_program_static<2, META##ull, COUNTS##ull, __VA_ARGS__>); \
   CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID "_w", 70, 256, k_row_program_static<1, META##ull, COUNTS##ull, __VA_ARGS__>); \
+  CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID "_h", 70, 256, k_row_program_static<3, META##ull, COUNTS##ull, __VA_ARGS__>); \
   static int cinn_b200_static_row_program_##ID =                                                                     \
       RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program", META##ll, COUNTS##ll), "row_program_static_" #ID) + \
-      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program_w", META##ll, COUNTS##ll), "row_program_static_" #ID "_w")
+      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program_w", META##ll, COUNTS##ll), "row_program_static_" #ID "_w") + \
+      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program_h", META##ll, COUNTS##ll), "row_program_static_" #ID "_h")
 
 #include "row_prog_static_table.inc"
 

@@ -103,6 +103,7 @@ static int g_opt_fuse_interpreted = 0;
 static int g_opt_pdl = 1;  // programmatic dependent launch for the kernels that support it
 static int g_opt_peer_reducers_per_sm = 0;  // reducer CTAs per SM of the fused reduce + exchange kernel (0: automatic)
 static int g_opt_ew_reg_ctas = 0;
+static int g_opt_rowp_form = 0;
 static int g_opt_host_chunks = 0;  // upper limit of the chunks group_run_host cuts a group into (0: up to 16)
 static int g_opt_rownorm_stages = 0, g_opt_rownorm_ctas = 0, g_opt_enable_tma_rownorm = -1, g_opt_rownorm_simple = -1;
 
@@ -133,6 +134,7 @@ DeviceInfo CurrentDeviceInfo() {
   d.ew_stream_stages      = g_opt_ew_stream_stages;
   d.ew_stream_ctas_per_sm = g_opt_ew_stream_ctas;
   d.ew_reg_ctas_per_sm    = g_opt_ew_reg_ctas;
+  d.rowp_form             = g_opt_rowp_form;
   d.rownorm_stages      = g_opt_rownorm_stages;
   d.rownorm_ctas_per_sm = g_opt_rownorm_ctas;
   d.enable_tma_rownorm = g_opt_enable_tma_rownorm;
@@ -889,6 +891,10 @@ int cinn_b200_set_option(const char* key, long long value) {
   }
   if (!strcmp(key, "ew_stream_stages")) {
     g_opt_ew_stream_stages = (int)value;
+    return CINN_B200_OK;
+  }
+  if (!strcmp(key, "rowp_form")) {
+    g_opt_rowp_form = (int)value;
     return CINN_B200_OK;
   }
   if (!strcmp(key, "ew_reg_ctas_per_sm")) {

@@ -321,6 +321,8 @@ int cinn_b200_device_status(unsigned int* async_wait_timeouts);
  * per SM is too few to stream the local rows at full bandwidth);
  * "host_chunks" (default 0 = up to 16): the most chunks cinn_b200_group_run_host pipelines a group over (read at the
  * group's first host run);
+ * "rowp_form" (default 0 = automatic): the form of a row program -- 32 a warp per row, 128 half a CTA per row
+ * (specialised kernels only), 256 a CTA per row;
  * "ew_reg_ctas_per_sm" (default 0 = by size): grid of the register form of the bias / scale / tanh / cast kernel in
  * CTAs per SM (measured on an 8.4 M-element shard: 4 to 16 per SM all within 10.7-11.2 us);
  * "enable_ew_stream" (default 1),

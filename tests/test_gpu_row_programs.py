@@ -132,3 +132,37 @@ def test_reduction_with_a_per_row_epilogue_as_one_group():
     g.release()
     want = ge.run_all(desc, ins)["y"]
     assert np.allclose(out.cpu().numpy(), want, rtol=2e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("form", [32, 128, 256])
+@pytest.mark.parametrize("index", [0, 1, 2, 5])  # rms_norm, standardise, log_softmax, min_max_normalise
+@pytest.mark.parametrize("shape", [(37, 4096), (19, 2052), (41, 1024)], ids=lambda s: "%dx%d" % s)
+def test_specialised_row_program_in_every_form(form, index, shape):
+    """The three forms of a specialised row program -- a warp, half a CTA (two rows per CTA, a named barrier per half)
+    or a CTA per row -- forced through the `rowp_form` option, against the oracle."""
+    rows, r = shape
+    make = _tabled(index)
+    L = cinn_b200.lib()
+    L.cinn_b200_set_option(b"rowp_form", form)
+    try:
+        b = NetBuilder("%s_form%d" % (make.__name__, form))
+        fetch = make(b, rows, r)
+        comp = Computation.build_and_compile(TARGET, b, fetch=[str(f) for f in fetch])
+    finally:
+        L.cinn_b200_set_option(b"rowp_form", 0)
+    kernels = [p.split()[1] for _, p in comp.groups()]
+    want_suffix = {32: "_w", 128: "_h", 256: ""}[form]
+    assert kernels == ["row_program_static_" + make.__name__ + want_suffix], kernels
+    rng = np.random.default_rng(rows * 11 + r + form)
+    feeds = {}
+    for t in comp.get_input_tensors():
+        _, shp, _ = t._info()
+        feeds[t.name] = rng.standard_normal(shp).astype(np.float32)
+        t.from_numpy(feeds[t.name], TARGET)
+    comp.execute()
+    want = oracle_program(comp, feeds)
+    for f in fetch:
+        got, ref = comp.get_tensor(str(f)).numpy(TARGET), np.asarray(want[str(f)])
+        scale = max(1.0, float(np.abs(ref).max()))
+        assert np.allclose(got, ref, rtol=2e-5, atol=2e-6 * np.sqrt(r) * scale), \
+            (str(f), float(np.abs(got - ref).max()), kernels)
