@@ -293,6 +293,7 @@ def side_groups(torch, dev, peak, only=None):
         ("row_program_standardise_16384x4096", lambda: W.row_program("standardise"), 2, "(x - mean) * rsqrt(var + eps), three passes over a row in registers, one kernel"),
         ("row_program_log_softmax_16384x4096", lambda: W.row_program("log_softmax"), 2, "x - max - log(sum(exp(x - max))), one kernel"),
         ("row_program_moments_16384x4096", lambda: W.row_program("moments"), 2, "mean and variance per row from one read"),
+        ("row_program_rms_norm_8192x8192", lambda: W.row_program("rms_norm", (8192, 8192)), 2, "long rows: a CTA per row, eight vectors per thread"),
         ("row_program_rms_norm_65536x1024", lambda: W.row_program("rms_norm", (65536, 1024)), 2, "short rows: a warp per row"),
         ("row_program_standardise_65536x1024", lambda: W.row_program("standardise", (65536, 1024)), 2, "short rows: a warp per row"),
         ("dag_shared_sum_4out_4096x8192", lambda: W.dag_program("shared_sum_4out", (4096, 8192)), 1,
@@ -368,6 +369,7 @@ PROFILE_GROUPS = {
     "row_centre": lambda W: W.row_program("centre"),
     "row_affine_relu": lambda W: W.row_program("affine_relu"),
     "row_rms_norm": lambda W: W.row_program("rms_norm"),
+    "row_standardise": lambda W: W.row_program("standardise"),
     "dag_shared_sum_4out": lambda W: W.dag_program("shared_sum_4out", (4096, 8192)),
 }
 
@@ -721,7 +723,7 @@ def pinned_copy_ceiling(torch, dev, h2d_bytes, d2h_bytes, reps=5):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-side-groups", action="store_true", help="skip the per-group table of the other kernels")

@@ -2149,6 +2149,9 @@ std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceI
     if (half) fixed = FindStaticChain("row_program_h", meta, (int)words.size() + 2, sig);
     if (fixed) {
       st.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(rows, 2), (int64_t)dev.sm_count * 8));
+    } else if (r % 4 == 0 && r > 4096 && r <= 8192 && npass > 1 && group == 256 &&
+               (fixed = FindStaticChain("row_program_c8", meta, (int)words.size() + 2, sig)) != nullptr) {
+      // rows of 4097 to 8192 elements: a CTA per row with eight vectors per thread in registers between the passes
     } else {
       fixed = FindStaticChain(group == 32 ? "row_program_w" : "row_program", meta, (int)words.size() + 2, sig);
     }

@@ -378,7 +378,8 @@ struct StaticRowProgram {
 
 // ---- the kernel body --------------------------------------------------------------------------------------------------
 // FORM 0: warp or CTA per row by `group` at run time (the interpreting kernel); 1: a warp per row; 2: a CTA per row;
-// 3: half a CTA (four warps) per row, two rows per CTA at a time, each half with a named barrier of its own
+// 3: half a CTA (four warps) per row, two rows per CTA at a time, each half with a named barrier of its own; 4: a CTA
+// per row with eight cached vectors per thread (rows of up to 8192 elements)
 // (the specialised kernels: one instantiation each, so that the register cache below is sized for its form).
 template <class Prog, int FORM>
 __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInputs& inputs, const RowOutputs& out,
@@ -400,7 +401,7 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
   // A specialised program of several passes keeps the row in registers between the passes instead of reading it
   // again: a CTA holds a row of up to 4096 elements in four vectors per thread, a warp one of up to 1024 in eight
   // vectors per lane.
-  constexpr int kCacheVecs = FORM == 1 || FORM == 3 ? 8 : 4;
+  constexpr int kCacheVecs = FORM == 1 || FORM == 3 || FORM == 4 ? 8 : 4;
   constexpr int kStride    = FORM == 1 ? 32 : (FORM == 3 ? 128 : 256);
   const bool use_cache = Prog::kStatic && FORM != 0 && (FORM == 1 || FORM == 3 || !per_warp) && vec_ok && npass > 1 &&
                          (r >> 2) <= (long long)kCacheVecs * kStride;
@@ -554,16 +555,18 @@ StaticChainKey MakeRowKey(const char* base, long long meta, long long counts) {
 
 CINN_B200_REGISTER_KERNEL_PDL("row_program", 70, 256, k_row_program);
 
-// Three kernels per program: a CTA per row (key "row_program"), a warp per row (key "row_program_w") and half a CTA
-// per row (key "row_program_h").
+// Four kernels per program: a CTA per row (key "row_program"), a warp per row (key "row_program_w"), half a CTA per
+// row (key "row_program_h") and a CTA per row of up to 8192 elements (key "row_program_c8").
 #define STATIC_ROW_PROGRAM(ID, META, COUNTS, ...)                                                                  \
   CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID, 70, 256, k_row_program_static<2, META##ull, COUNTS##ull, __VA_ARGS__>); \
   CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID "_w", 70, 256, k_row_program_static<1, META##ull, COUNTS##ull, __VA_ARGS__>); \
   CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID "_h", 70, 256, k_row_program_static<3, META##ull, COUNTS##ull, __VA_ARGS__>); \
+  CINN_B200_REGISTER_KERNEL_PDL("row_program_static_" #ID "_c8", 70, 256, k_row_program_static<4, META##ull, COUNTS##ull, __VA_ARGS__>); \
   static int cinn_b200_static_row_program_##ID =                                                                     \
       RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program", META##ll, COUNTS##ll), "row_program_static_" #ID) + \
       RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program_w", META##ll, COUNTS##ll), "row_program_static_" #ID "_w") + \
-      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program_h", META##ll, COUNTS##ll), "row_program_static_" #ID "_h")
+      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program_h", META##ll, COUNTS##ll), "row_program_static_" #ID "_h") + \
+      RegisterStaticChain(MakeRowKey<__VA_ARGS__>("row_program_c8", META##ll, COUNTS##ll), "row_program_static_" #ID "_c8")
 
 #include "row_prog_static_table.inc"
 

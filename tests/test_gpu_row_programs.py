@@ -86,7 +86,7 @@ def _tabled(index):
 
 PROGRAMS = [l2_normalise, centre, shifted_exponentials_with_bias, three_sums, centred_and_its_variance,
             exp_minus_its_maximum] + [_tabled(i) for i in range(6)]
-SHAPES = [(70, 1024), (9, 4096), (33, 1001), (5, 2050), (128, 64)]  # warp / CTA per row, ragged rows, short rows
+SHAPES = [(70, 1024), (9, 4096), (33, 1001), (5, 2050), (128, 64), (7, 8192), (6, 6144)]  # warp / half CTA / CTA per row, ragged, short and long rows
 
 
 @pytest.mark.parametrize("make", PROGRAMS, ids=lambda f: f.__name__)

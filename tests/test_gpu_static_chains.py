@@ -84,13 +84,14 @@ def test_static_kernel_equals_interpreter(name, desc, variant):
     assert all(k.startswith("ew_chain_") for k in k_i), k_i
     if "_static_" not in k_s[0]:
         pytest.skip("no specialised kernel for this entry (%s)" % k_s[0])
-    # A specialised ROW program evaluates exp / tanh / sigmoid through the approximate exponential and reciprocal
-    # (its results are of the reduction class); every other program is the interpreter's bit for bit.
-    approximate = k_i[0] == "row_program" and any(" %s " % t in desc for t in ("exp", "tanh", "sigmoid"))
+    # A specialised ROW program may run in another form than the interpreter (half a CTA or a warp per row: another
+    # summation tree) and evaluates exp / tanh / sigmoid through the approximate exponential and reciprocal; its
+    # results are of the reduction class.  Register programs are the interpreter's bit for bit.
+    approximate = k_i[0] == "row_program"
     for a, b in zip(got_s, got_i):
         if approximate:
             fa, fb = a.view(np.float32), b.view(np.float32)
-            assert np.allclose(fa, fb, rtol=2e-5, atol=2e-6 * float(np.abs(fb).max())), (name, variant, k_s)
+            assert np.allclose(fa, fb, rtol=2e-5, atol=4e-6 * float(np.abs(fb).max())), (name, variant, k_s)
         else:
             assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))
 
@@ -131,8 +132,8 @@ def test_static_chain_reduction_equals_interpreter(name, desc, shape):
 @pytest.mark.parametrize("variant", ["table_shape", "other_size"])
 def test_static_register_and_row_programs_equal_their_interpreters(name, desc, variant):
     """Register programs (several outputs, shared values) and row programs (reductions with elementwise ops around
-    them): the kernel with the program as template arguments against the interpreting kernel, bit for bit (same steps,
-    same accumulation order) except where the specialised form uses the approximate transcendental functions."""
+    them): the kernel with the program as template arguments against the interpreting kernel -- bit for bit for the
+    register programs (same steps), at the reduction tolerance for the row programs."""
     if variant == "other_size":
         desc = (desc.replace("64,4096", "37,1028").replace("shape=64 ", "shape=37 ").replace(" 64\n", " 37\n")
                 .replace("value=4096.0", "value=1028.0").replace("64,1024", "61,1028").replace(" 1024\n", " 1028\n"))
@@ -142,12 +143,13 @@ def test_static_register_and_row_programs_equal_their_interpreters(name, desc, v
         pytest.skip("this entry is a chain (%s): covered by the chain table" % k_i[0])
     if "_static_" not in k_s[0]:
         pytest.skip("no specialised kernel for this entry (%s)" % k_s[0])
-    # A specialised ROW program evaluates exp / tanh / sigmoid through the approximate exponential and reciprocal
-    # (its results are of the reduction class); every other program is the interpreter's bit for bit.
-    approximate = k_i[0] == "row_program" and any(" %s " % t in desc for t in ("exp", "tanh", "sigmoid"))
+    # A specialised ROW program may run in another form than the interpreter (half a CTA or a warp per row: another
+    # summation tree) and evaluates exp / tanh / sigmoid through the approximate exponential and reciprocal; its
+    # results are of the reduction class.  Register programs are the interpreter's bit for bit.
+    approximate = k_i[0] == "row_program"
     for a, b in zip(got_s, got_i):
         if approximate:
             fa, fb = a.view(np.float32), b.view(np.float32)
-            assert np.allclose(fa, fb, rtol=2e-5, atol=2e-6 * float(np.abs(fb).max())), (name, variant, k_s)
+            assert np.allclose(fa, fb, rtol=2e-5, atol=4e-6 * float(np.abs(fb).max())), (name, variant, k_s)
         else:
             assert np.array_equal(a, b), (name, variant, k_s, int((a != b).sum()))

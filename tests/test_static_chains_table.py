@@ -28,9 +28,9 @@ def test_committed_table_is_up_to_date_and_registered():
         for m in re.finditer(r"^STATIC_(CHAIN_REDUCE_ROW|CHAIN_REDUCE_COL|CHAIN|DAG|ROW_PROGRAM|INT_CHAIN|F64_CHAIN)\((\w+),", text, flags=re.M):
             prefix = {"CHAIN": "ew_static_", "DAG": "ew_dag_static_", "ROW_PROGRAM": "row_program_static_", "INT_CHAIN": "ew_int_static_", "F64_CHAIN": "ew_f64_static_"}.get(m.group(1), "chain_reduce_static_")
             assert L.cinn_b200_get_kernel((prefix + m.group(2)).encode()), prefix + m.group(2)
-    # (a row program has three kernels -- a CTA, half a CTA or a warp per row: three registry entries per table line)
+    # (a row program has four kernels -- a CTA (two sizes), half a CTA or a warp per row: four registry entries per table line)
     rows = len(re.findall(r"^STATIC_ROW_PROGRAM\(", open(os.path.join(ROOT, "cinn_b200", "csrc", "row_prog_static_table.inc")).read(), flags=re.M))
-    assert L.cinn_b200_num_static_chains() == total + 2 * rows and total >= 60
+    assert L.cinn_b200_num_static_chains() == total + 3 * rows and total >= 60
 
 
 def test_listed_groups_plan_to_their_static_kernel_and_others_to_the_interpreter():
@@ -88,7 +88,7 @@ def test_builder_row_compositions_fuse_into_one_specialised_kernel():
             kernels = [p.split()[1] for _, p in comp.groups()]
             # (suffix _w: the warp-per-row form, taken for short rows and for single-pass programs)
             # (suffix _h: half a CTA per row, taken for programs of several passes over rows of 1025 to 4096 elements)
-            assert kernels in (["row_program_static_" + make.__name__ + f] for f in ("", "_w", "_h")), \
+            assert kernels in (["row_program_static_" + make.__name__ + f] for f in ("", "_w", "_h", "_c8")), \
                 (shape, make.__name__, kernels)
             if shape[1] <= 1024:
                 assert kernels[0].endswith("_w")
