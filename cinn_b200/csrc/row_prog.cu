@@ -19,7 +19,10 @@
 // The arithmetic per op is that of the chain kernels (chain_step's helpers).  Reductions combine per-thread partials
 // in a tree, as every reduction kernel of this library does (sums differ from the serial order by rounding only).
 // As for the chains there is an interpreting kernel and, for the programs of row_prog_static_table.inc, kernels with
-// the program as template arguments.
+// the program as template arguments.  Those come in four forms (see row_program_body): a warp, half a CTA or a CTA
+// per row, the latter in two sizes; all but the single-pass ones keep the row in registers between the passes
+// instead of reading it again, ask the next row into L2 meanwhile, evaluate exp / tanh / sigmoid through the
+// approximate exponential, and divide by a per-row value through one reciprocal per row.
 #include "ew_chain_body.cuh"
 #include "kernel_registry.h"
 
