@@ -145,3 +145,31 @@ def test_missing_rank_runs_the_waits_out_and_the_context_turns_failed():
         assert op.status() == 0 and all(bool((o == 8.0).all()) for o in outs)
     finally:
         op.close()
+
+
+@pytest.mark.parametrize("reducers_per_sm", [1, 2])
+def test_emulated_world_with_fewer_reducers(reducers_per_sm, oracle):
+    """The `peer_reducers_per_sm` option caps the reducer CTAs (their items then take more rounds): same results."""
+    import cinn_b200
+    from cinn_b200 import sharding
+    from cinn_b200 import workloads as W
+    world, full = 4, (32, 64, 1024)  # inner = 65536: 16 tiles per band, 64 items per rank
+    inner, rows = full[1] * full[2], full[0] // 4
+    L = cinn_b200.lib()
+    L.cinn_b200_set_option(b"peer_reducers_per_sm", reducers_per_sm)
+    op = sharding.EmulatedFusedShardedReduceAxis0("max", full, world, all_gather=True)
+    dev = torch.device("cuda:0")
+    try:
+        for call in range(4):
+            x = W.reduce_input(full, seed=300 + call)
+            xs = [torch.from_numpy(np.ascontiguousarray(x[r * rows:(r + 1) * rows])).to(dev) for r in range(world)]
+            outs = [torch.full(op.out_shape, float("nan"), device=dev) for _ in range(world)]
+            op(xs, outs)
+            torch.cuda.synchronize()
+            want = oracle.reduce("max", x, 1, full[0], inner)
+            for r in range(world):
+                assert np.array_equal(outs[r].cpu().numpy().reshape(-1), want), (call, r)
+        assert op.status() == 0
+    finally:
+        L.cinn_b200_set_option(b"peer_reducers_per_sm", 0)
+        op.close()
