@@ -237,16 +237,18 @@ __global__ void __launch_bounds__(256)
       const int begin = chunk * per;
       const int end   = min(begin + per, nvec);
       const int B     = blockDim.x;
-      for (int v = begin + threadIdx.x; v < end; v += 2 * B) {
-        uint4 rx[2], rd[2];
+      // four predicated vectors of each input per iteration: eight 16-byte loads in flight per thread
+      constexpr int U = 4;
+      for (int v = begin + threadIdx.x; v < end; v += U * B) {
+        uint4 rx[U], rd[U];
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < U; ++j)
           if (v + j * B < end) {
             rx[j] = ld_stream16(xp + (long long)(v + j * B) * V);
             rd[j] = ld_stream16(dp + (long long)(v + j * B) * V);
           }
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < U; ++j) {
           if (v + j * B < end) {
             float fx[V], fd[V];
             Io<T>::unpack(rx[j], fx);
