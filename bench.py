@@ -300,6 +300,8 @@ def side_groups(torch, dev, peak, only=None):
          "g = A + B feeding four sums: six reads, four writes, one kernel"),
         ("dag_bias_relu_mask_3out_8192x8192", lambda: W.dag_program("bias_relu_mask_3out"), 1,
          "x + bias, its relu and its mask: one read, three writes"),
+        ("dag_adam_update_8192x8192", lambda: W.dag_program("adam_update"), 1,
+         "an Adam step: both moments and the parameter, four reads, three writes, one kernel"),
     ]
     if not only or any(o in "add_relu_1x3x224x224" for o in only):
         # config 1 through NetBuilder / Computation, timed by the library's own ExecuteTest loop (no Python per launch)

@@ -137,6 +137,22 @@ GROUPS.append(("bias_pre_and_relu_f32",
                "group fn_static_bias_pre_and_relu_f32\ninput X float32 %s\ninput bias float32 %s\n"
                "op elementwise_add pre = X bias ; axis=-1\nop relu act = pre\n"
                "output pre float32 %s\noutput act float32 %s\n" % (FULL, ROWVEC, FULL, FULL)))
+# swish with its sigmoid kept, a momentum step (velocity and parameter), gelu's tanh form with the tanh kept: chains
+# that store one value on the way
+GROUPS.append(("swish_and_sigmoid_f32",
+               "group fn_static_swish_and_sigmoid_f32\ninput x float32 %s\nop sigmoid s = x\n"
+               "op elementwise_mul y = x s ; axis=-1\noutput s float32 %s\noutput y float32 %s\n" % (FULL, FULL, FULL)))
+GROUPS.append(("momentum_update_f32",
+               "group fn_static_momentum_update_f32\ninput W float32 %s\ninput G float32 %s\ninput V float32 %s\n"
+               "op scale v1 = V ; scale=0.9 bias=0.0 bias_after_scale=true\nop elementwise_add v2 = v1 G ; axis=-1\n"
+               "op scale st = v2 ; scale=-0.01 bias=0.0 bias_after_scale=true\nop elementwise_add w2 = W st ; axis=-1\n"
+               "output v2 float32 %s\noutput w2 float32 %s\n" % (FULL, FULL, FULL, FULL, FULL)))
+GROUPS.append(("gelu_tanh_kept_f32",
+               "group fn_static_gelu_tanh_kept_f32\ninput x float32 %s\nop elementwise_mul x2 = x x ; axis=-1\n"
+               "op elementwise_mul x3 = x2 x ; axis=-1\nop scale c = x3 ; scale=0.044715 bias=0.0 bias_after_scale=true\n"
+               "op elementwise_add u = x c ; axis=-1\nop scale w = u ; scale=0.7978845608 bias=0.0 bias_after_scale=true\n"
+               "op tanh t = w\nop scale h = t ; scale=0.5 bias=0.5 bias_after_scale=true\n"
+               "op elementwise_mul y = x h ; axis=-1\noutput y float32 %s\noutput t float32 %s\n" % (FULL, FULL, FULL)))
 
 
 
@@ -203,13 +219,20 @@ DAG_GROUPS = [
           ["elementwise_add pre = x b ; axis=-1", "relu act = pre",
            "fill_constant z = ; shape=%s value=0.0 dtype=float32" % FULL, "greater_than m = pre z ; axis=-1",
            "cast mf = m ; dtype=float32"], ["pre", "act", "mf"]),
-    # swish and its derivative factor from one read of x
-    multi("swish_and_sigmoid", ["x float32 " + FULL], ["sigmoid s = x", "elementwise_mul y = x s ; axis=-1"], ["s", "y"]),
-    # momentum update: two states from one gradient
-    multi("momentum_update", _f("WGV"), ["scale v1 = V ; scale=0.9 bias=0.0 bias_after_scale=true",
-                                         "elementwise_add v2 = v1 G ; axis=-1",
-                                         "scale st = v2 ; scale=-0.01 bias=0.0 bias_after_scale=true",
-                                         "elementwise_add w2 = W st ; axis=-1"], ["v2", "w2"]),
+    # Adam: both moments and the parameter from one read of the gradient (three outputs)
+    multi("adam_update", _f("PGMV"),
+          ["scale m1 = M ; scale=0.9 bias=0.0 bias_after_scale=true",
+           "scale g1 = G ; scale=0.1 bias=0.0 bias_after_scale=true",
+           "elementwise_add m2 = m1 g1 ; axis=-1",
+           "elementwise_mul gg = G G ; axis=-1",
+           "scale v1 = V ; scale=0.999 bias=0.0 bias_after_scale=true",
+           "scale g2 = gg ; scale=0.001 bias=0.0 bias_after_scale=true",
+           "elementwise_add v2 = v1 g2 ; axis=-1",
+           "sqrt sv = v2",
+           "scale den = sv ; scale=1.0 bias=1e-08 bias_after_scale=true",
+           "divide upd = m2 den ; axis=-1",
+           "scale st = upd ; scale=-0.001 bias=0.0 bias_after_scale=true",
+           "elementwise_add p2 = P st ; axis=-1"], ["m2", "v2", "p2"]),
 ]
 
 # Row programs (row_prog.cu): reductions over the last axis with elementwise ops around them.  Two row lengths per

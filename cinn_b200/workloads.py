@@ -503,7 +503,8 @@ def _row_program_from_builder(kind, shape, seed):
 
 def dag_program(kind="shared_sum_4out", shape=(8192, 8192), seed=13):
     """Elementwise groups that are not chains (ew_dag.cu).  shared_sum_4out: g = A + B feeding four sums with C..F (six
-    reads, four writes); bias_relu_mask_3out: x + bias, its relu and the mask of its positive part."""
+    reads, four writes); bias_relu_mask_3out: x + bias, its relu and the mask of its positive part; adam_update: both
+    moments and the parameter of an Adam step (four reads, three writes; V is made non-negative by the generator)."""
     s = _shape(shape)
     if kind == "shared_sum_4out":
         ins = [f"{n} float32 {s}" for n in "ABCDEF"]
@@ -514,6 +515,15 @@ def dag_program(kind="shared_sum_4out", shape=(8192, 8192), seed=13):
         ops = ["elementwise_add pre = x b ; axis=-1", "relu act = pre", f"fill_constant z = ; shape={s} value=0.0 dtype=float32",
                "greater_than m = pre z ; axis=-1", "cast mf = m ; dtype=float32"]
         outs = ["pre", "act", "mf"]
+    elif kind == "adam_update":
+        ins = [f"{n} float32 {s}" for n in "PGMV"]
+        ops = ["scale m1 = M ; scale=0.9 bias=0.0 bias_after_scale=true", "scale g1 = G ; scale=0.1 bias=0.0 bias_after_scale=true",
+               "elementwise_add m2 = m1 g1 ; axis=-1", "elementwise_mul gg = G G ; axis=-1",
+               "scale v1 = V ; scale=0.999 bias=0.0 bias_after_scale=true", "scale g2 = gg ; scale=0.001 bias=0.0 bias_after_scale=true",
+               "elementwise_add v2 = v1 g2 ; axis=-1", "sqrt sv = v2", "scale den = sv ; scale=1.0 bias=1e-08 bias_after_scale=true",
+               "divide upd = m2 den ; axis=-1", "scale st = upd ; scale=-0.001 bias=0.0 bias_after_scale=true",
+               "elementwise_add p2 = P st ; axis=-1"]
+        outs = ["m2", "v2", "p2"]
     else:
         raise ValueError(kind)
     desc = (f"group fn_dag_{kind}\n" + "".join(f"input {i}\n" for i in ins) + "".join(f"op {o}\n" for o in ops) +
@@ -521,5 +531,8 @@ def dag_program(kind="shared_sum_4out", shape=(8192, 8192), seed=13):
 
     def gen():
         rng = np.random.default_rng(seed)
-        return [rng.standard_normal([int(d) for d in i.split()[2].split(",")], dtype=np.float32) for i in ins]
+        arrays = [rng.standard_normal([int(d) for d in i.split()[2].split(",")], dtype=np.float32) for i in ins]
+        if kind == "adam_update":
+            arrays[3] = np.abs(arrays[3])  # the second moment is a running mean of squares
+        return arrays
     return Workload("dag_" + kind, desc, gen, np.float32, shape, more_outputs=[(np.float32, shape)] * (len(outs) - 1))
