@@ -87,8 +87,18 @@ def _dag_programs():
         e = b.add(v["A"], v["B"])
         return [b.add(e, v["C"]), b.multiply(e, e), b.tanh(e)]
 
+    def adam_step(b):
+        # both moments and the parameter of an Adam step from one read of the gradient (the second moment enters
+        # squared here, so that random test data never puts a negative number under the root)
+        v = inputs(b, P=(96, 512), G=(96, 512), M=(96, 512), V=(96, 512))
+        vv = b.multiply(v["V"], v["V"])
+        m2 = b.add(b.scale(v["M"], 0.9, 0.0), b.scale(v["G"], 0.1, 0.0))
+        v2 = b.add(b.scale(vv, 0.999, 0.0), b.scale(b.multiply(v["G"], v["G"]), 0.001, 0.0))
+        upd = b.divide(m2, b.scale(b.sqrt(v2), 1.0, 1e-8))
+        return [m2, v2, b.add(v["P"], b.scale(upd, -0.001, 0.0))]
+
     return [shared_value_four_outputs, fma_contraction_choice, half_storage, constants_and_select,
-            odd_size_takes_the_scalar_tail]
+            odd_size_takes_the_scalar_tail, adam_step]
 
 
 @pytest.mark.parametrize("make", _dag_programs(), ids=lambda f: f.__name__)
