@@ -293,6 +293,9 @@ def side_groups(torch, dev, peak, only=None):
         ("row_program_standardise_16384x4096", lambda: W.row_program("standardise"), 2, "(x - mean) * rsqrt(var + eps), three passes over a row in registers, one kernel"),
         ("row_program_log_softmax_16384x4096", lambda: W.row_program("log_softmax"), 2, "x - max - log(sum(exp(x - max))), one kernel"),
         ("row_program_moments_16384x4096", lambda: W.row_program("moments"), 2, "mean and variance per row from one read"),
+        ("row_program_scaled_softmax_16384x4096", lambda: W.row_program("scaled_softmax"), 2, "softmax(x * s) with the maximum subtracted, one kernel"),
+        ("row_program_masked_softmax_16384x4096", lambda: W.row_program("masked_softmax"), 2, "softmax(x * s + mask), one kernel"),
+        ("row_program_cosine_similarity_16384x4096", lambda: W.row_program("cosine_similarity"), 2, "three sums of products from one read of two tensors"),
         ("row_program_rms_norm_8192x8192", lambda: W.row_program("rms_norm", (8192, 8192)), 2, "long rows: a CTA per row, eight vectors per thread"),
         ("row_program_rms_norm_65536x1024", lambda: W.row_program("rms_norm", (65536, 1024)), 2, "short rows: a warp per row"),
         ("row_program_standardise_65536x1024", lambda: W.row_program("standardise", (65536, 1024)), 2, "short rows: a warp per row"),

@@ -263,6 +263,20 @@ ROW_GROUPS = [
                "subtract d = X mb ; axis=-1", "exp e = d", "reduce_sum s = e ; dim=1 keep_dim=false",
                "broadcast_to sb = s ; out_shape=%s broadcast_axes=0" % ROWS, "divide p = e sb ; axis=-1",
                "scale y = p ; scale=2.0 bias=0.0 bias_after_scale=true"], ["y float32 " + ROWS]),
+    # attention scores: softmax of the scaled (and masked) scores, maximum subtracted -- the scaling and the mask join
+    # the softmax in one kernel instead of running as a chain kernel in front of the dedicated softmax kernel
+    row_group("scaled_softmax", ["X float32 " + ROWS],
+              ["scale d = X ; bias=0.0 bias_after_scale=true scale=0.125",
+               "reduce_max mx = d ; dim=1 keep_dim=false", "broadcast_to mb = mx ; broadcast_axes=0 out_shape=%s" % ROWS,
+               "subtract z = d mb ; axis=-1", "exp e = z", "reduce_sum s = e ; dim=1 keep_dim=false",
+               "broadcast_to sb = s ; broadcast_axes=0 out_shape=%s" % ROWS, "divide y = e sb ; axis=-1"],
+              ["y float32 " + ROWS]),
+    row_group("masked_softmax", ["X float32 " + ROWS, "M float32 " + ROWS],
+              ["scale d0 = X ; bias=0.0 bias_after_scale=true scale=0.125", "elementwise_add d = d0 M ; axis=-1",
+               "reduce_max mx = d ; dim=1 keep_dim=false", "broadcast_to mb = mx ; broadcast_axes=0 out_shape=%s" % ROWS,
+               "subtract z = d mb ; axis=-1", "exp e = z", "reduce_sum s = e ; dim=1 keep_dim=false",
+               "broadcast_to sb = s ; broadcast_axes=0 out_shape=%s" % ROWS, "divide y = e sb ; axis=-1"],
+              ["y float32 " + ROWS]),
     row_group("three_sums", ["A float32 " + ROWS, "B float32 " + ROWS],
               ["elementwise_add c = A B ; axis=-1", "reduce_sum sa = A ; dim=1 keep_dim=false",
                "reduce_sum sb = B ; dim=1 keep_dim=false", "reduce_sum sc = c ; dim=1 keep_dim=false"],
@@ -435,7 +449,29 @@ def builder_row_programs(R=64, C=4096):
         mn, mx = b.reduce_min(x, [1]), b.reduce_max(x, [1])
         return [b.divide(b.subtract(x, b.broadcast_to(mn, [R, C], [0])), b.broadcast_to(b.subtract(mx, mn), [R, C], [0]))]
 
-    return [rms_norm, standardise, log_softmax, l1_normalise, moments, min_max_normalise]
+    def rms_norm_plain(b):  # without the weight vector
+        x = b.create_input(F32, (R, C), "X")
+        inv = b.rsqrt(b.scale(b.reduce_sum(b.multiply(x, x), [1]), 1.0 / C, 1e-6))
+        return [b.multiply(x, b.broadcast_to(inv, [R, C], [0]))]
+
+    def l2_normalise_eps(b):  # x / max(||x||, eps)
+        x = b.create_input(F32, (R, C), "X")
+        n = b.sqrt(b.reduce_sum(b.multiply(x, x), [1]))
+        return [b.divide(x, b.broadcast_to(b.max(n, b.fill_constant([R], 1e-12)), [R, C], [0]))]
+
+    def cosine_similarity(b):  # three sums from one read of two tensors, one value per row
+        x, y = b.create_input(F32, (R, C), "X"), b.create_input(F32, (R, C), "Y")
+        xy, xx, yy = (b.reduce_sum(b.multiply(p, q), [1]) for p, q in ((x, y), (x, x), (y, y)))
+        return [b.divide(xy, b.sqrt(b.multiply(xx, yy)))]
+
+    def log_sum_exp(b):
+        x = b.create_input(F32, (R, C), "X")
+        mx = b.reduce_max(x, [1])
+        s = b.reduce_sum(b.exp(b.subtract(x, b.broadcast_to(mx, [R, C], [0]))), [1])
+        return [b.add(mx, b.log(s))]
+
+    return [rms_norm, standardise, log_softmax, l1_normalise, moments, min_max_normalise, rms_norm_plain,
+            l2_normalise_eps, cosine_similarity, log_sum_exp]
 
 
 def builder_groups(programs, pattern):

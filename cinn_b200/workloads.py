@@ -452,12 +452,21 @@ def row_program(kind, shape=(16384, 4096), seed=12):
         ins, outs = [f"X float32 {s}", f"a float32 {rows}", f"c float32 {rows}"], [("y", "float32", (rows,))]
         ops = ["reduce_sum s = X ; dim=1 keep_dim=false", "elementwise_mul t = s a ; axis=-1",
                "elementwise_add u = t c ; axis=-1", "relu y = u"]
+    elif kind in ("scaled_softmax", "masked_softmax"):
+        ins = [f"X float32 {s}"] + ([f"M float32 {s}"] if kind == "masked_softmax" else [])
+        outs = [("y", "float32", shape)]
+        ops = ["scale d0 = X ; bias=0.0 bias_after_scale=true scale=0.125"]
+        ops += ["elementwise_add d = d0 M ; axis=-1"] if kind == "masked_softmax" else ["identity d = d0"]
+        ops += ["reduce_max mx = d ; dim=1 keep_dim=false", f"broadcast_to mb = mx ; broadcast_axes=0 out_shape={s}",
+                "subtract z = d mb ; axis=-1", "exp e = z", "reduce_sum sm = e ; dim=1 keep_dim=false",
+                f"broadcast_to sb = sm ; broadcast_axes=0 out_shape={s}", "divide y = e sb ; axis=-1"]
     elif kind == "three_sums":
         ins = [f"A float32 {s}", f"B float32 {s}"]
         outs = [("sa", "float32", (rows,)), ("sb", "float32", (rows,)), ("sc", "float32", (rows,))]
         ops = ["elementwise_add c = A B ; axis=-1", "reduce_sum sa = A ; dim=1 keep_dim=false",
                "reduce_sum sb = B ; dim=1 keep_dim=false", "reduce_sum sc = c ; dim=1 keep_dim=false"]
-    elif kind in ("rms_norm", "standardise", "log_softmax", "l1_normalise", "moments", "min_max_normalise"):
+    elif kind in ("rms_norm", "standardise", "log_softmax", "l1_normalise", "moments", "min_max_normalise",
+                  "rms_norm_plain", "l2_normalise_eps", "cosine_similarity", "log_sum_exp"):
         return _row_program_from_builder(kind, shape, seed)
     else:
         raise ValueError(kind)

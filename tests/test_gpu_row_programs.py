@@ -84,8 +84,23 @@ def _tabled(index):
     return make
 
 
+def scaled_softmax(b, rows, r):
+    # attention scores: the scaling joins the max-subtracted softmax in one kernel
+    x = b.create_input(F32, (rows, r), "X")
+    d = b.scale(x, 0.125, 0.0)
+    e = b.exp(b.subtract(d, b.broadcast_to(b.reduce_max(d, [1]), [rows, r], [0])))
+    return [b.divide(e, b.broadcast_to(b.reduce_sum(e, [1]), [rows, r], [0]))]
+
+
+def masked_softmax(b, rows, r):
+    x, m = b.create_input(F32, (rows, r), "X"), b.create_input(F32, (rows, r), "M")
+    d = b.add(b.scale(x, 0.125, 0.0), m)
+    e = b.exp(b.subtract(d, b.broadcast_to(b.reduce_max(d, [1]), [rows, r], [0])))
+    return [b.divide(e, b.broadcast_to(b.reduce_sum(e, [1]), [rows, r], [0]))]
+
+
 PROGRAMS = [l2_normalise, centre, shifted_exponentials_with_bias, three_sums, centred_and_its_variance,
-            exp_minus_its_maximum] + [_tabled(i) for i in range(6)]
+            exp_minus_its_maximum, scaled_softmax, masked_softmax] + [_tabled(i) for i in range(10)]
 SHAPES = [(70, 1024), (9, 4096), (33, 1001), (5, 2050), (128, 64), (7, 8192), (6, 6144)]  # warp / half CTA / CTA per row, ragged, short and long rows
 
 
