@@ -470,8 +470,18 @@ def builder_row_programs(R=64, C=4096):
         s = b.reduce_sum(b.exp(b.subtract(x, b.broadcast_to(mx, [R, C], [0]))), [1])
         return [b.add(mx, b.log(s))]
 
+    def rms_norm_16bit(T, suffix):  # 16-bit storage of x, the weight and the result, fp32 arithmetic between casts
+        def make(b):
+            x, g = b.create_input(T, (R, C), "X"), b.create_input(T, (C,), "G")
+            xf, gf = b.cast(x, "float32"), b.cast(g, "float32")
+            inv = b.rsqrt(b.scale(b.reduce_sum(b.multiply(xf, xf), [1]), 1.0 / C, 1e-6))
+            return [b.cast(b.multiply(b.multiply(xf, b.broadcast_to(inv, [R, C], [0])), gf), suffix)]
+        make.__name__ = "rms_norm_" + {"float16": "f16", "bfloat16": "bf16"}[suffix]
+        return make
+
     return [rms_norm, standardise, log_softmax, l1_normalise, moments, min_max_normalise, rms_norm_plain,
-            l2_normalise_eps, cosine_similarity, log_sum_exp]
+            l2_normalise_eps, cosine_similarity, log_sum_exp, rms_norm_16bit(common.Float16(), "float16"),
+            rms_norm_16bit(common.BFloat16(), "bfloat16")]
 
 
 def builder_groups(programs, pattern):

@@ -181,3 +181,33 @@ def test_specialised_row_program_in_every_form(form, index, shape):
         scale = max(1.0, float(np.abs(ref).max()))
         assert np.allclose(got, ref, rtol=2e-5, atol=2e-6 * np.sqrt(r) * scale), \
             (str(f), float(np.abs(got - ref).max()), kernels)
+
+
+@pytest.mark.parametrize("dtype", ["float16", "bfloat16"])
+@pytest.mark.parametrize("shape", [(64, 4096), (37, 1024), (5, 8192)], ids=lambda s: "%dx%d" % s)
+def test_rms_norm_with_16_bit_storage_is_one_specialised_kernel(dtype, shape):
+    """x, the weight and the result stored as 16-bit floats, fp32 arithmetic between the casts: one row-program kernel
+    from the table; against a float64 evaluation at the 16-bit tolerance."""
+    import torch
+    rows, r = shape
+    T = common.Float16() if dtype == "float16" else common.BFloat16()
+    b = NetBuilder("rms_norm_" + dtype)
+    x, g = b.create_input(T, (rows, r), "X"), b.create_input(T, (r,), "G")
+    xf, gf = b.cast(x, "float32"), b.cast(g, "float32")
+    inv = b.rsqrt(b.scale(b.reduce_sum(b.multiply(xf, xf), [1]), 1.0 / r, 1e-6))
+    y = b.cast(b.multiply(b.multiply(xf, b.broadcast_to(inv, [rows, r], [0])), gf), dtype)
+    comp = Computation.build_and_compile(TARGET, b, fetch=[str(y)], plan_only=True)
+    groups = comp.groups()
+    assert len(groups) == 1 and groups[0][1].split()[1].startswith("row_program_static_rms_norm_"), groups
+    tt = torch.float16 if dtype == "float16" else torch.bfloat16
+    gen = torch.Generator(device="cuda").manual_seed(rows + r)
+    X = torch.randn((rows, r), device="cuda", generator=gen).to(tt)
+    G = (1.0 + 0.1 * torch.randn((r,), device="cuda", generator=gen)).to(tt)
+    out = torch.empty((rows, r), device="cuda", dtype=tt)
+    fg = cinn_b200.FusedGroup(groups[0][0].replace(groups[0][0].splitlines()[0], "group fn_rms16_%s_%d_%d" % (dtype, rows, r)))
+    fg.run([X, G, out])
+    torch.cuda.synchronize()
+    fg.release()
+    xd = X.double()
+    want = xd * torch.rsqrt((xd * xd).sum(1, keepdim=True) / r + 1e-6) * G.double()
+    assert bool(((out.double() - want).abs() <= 1e-2 * want.abs() + 1e-3).all())
