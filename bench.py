@@ -297,6 +297,7 @@ def side_groups(torch, dev, peak, only=None):
         ("row_program_masked_softmax_16384x4096", lambda: W.row_program("masked_softmax"), 2, "softmax(x * s + mask), one kernel"),
         ("row_program_cosine_similarity_16384x4096", lambda: W.row_program("cosine_similarity"), 2, "three sums of products from one read of two tensors"),
         ("row_program_rms_norm_8192x8192", lambda: W.row_program("rms_norm", (8192, 8192)), 2, "long rows: a CTA per row, eight vectors per thread"),
+        ("row_program_rms_norm_f16_16384x4096", lambda: W.row_program("rms_norm_f16"), 2, "fp16 storage of x, weight and result, one kernel"),
         ("row_program_rms_norm_65536x1024", lambda: W.row_program("rms_norm", (65536, 1024)), 2, "short rows: a warp per row"),
         ("row_program_standardise_65536x1024", lambda: W.row_program("standardise", (65536, 1024)), 2, "short rows: a warp per row"),
         ("dag_shared_sum_4out_4096x8192", lambda: W.dag_program("shared_sum_4out", (4096, 8192)), 1,

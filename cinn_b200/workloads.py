@@ -466,7 +466,7 @@ def row_program(kind, shape=(16384, 4096), seed=12):
         ops = ["elementwise_add c = A B ; axis=-1", "reduce_sum sa = A ; dim=1 keep_dim=false",
                "reduce_sum sb = B ; dim=1 keep_dim=false", "reduce_sum sc = c ; dim=1 keep_dim=false"]
     elif kind in ("rms_norm", "standardise", "log_softmax", "l1_normalise", "moments", "min_max_normalise",
-                  "rms_norm_plain", "l2_normalise_eps", "cosine_similarity", "log_sum_exp"):
+                  "rms_norm_plain", "l2_normalise_eps", "cosine_similarity", "log_sum_exp", "rms_norm_f16"):
         return _row_program_from_builder(kind, shape, seed)
     else:
         raise ValueError(kind)
@@ -505,9 +505,9 @@ def _row_program_from_builder(kind, shape, seed):
 
     def gen_inputs():
         rng = np.random.default_rng(seed)
-        return [rng.standard_normal(dims(w), dtype=np.float32) for w in ins]
-    return Workload("row_" + kind, desc, gen_inputs, np.float32, dims(outs[0]),
-                    more_outputs=[(np.float32, dims(w)) for w in outs[1:]])
+        return [rng.standard_normal(dims(w), dtype=np.float32).astype(_NP[w[2]]) for w in ins]
+    return Workload("row_" + kind, desc, gen_inputs, _NP[outs[0][2]], dims(outs[0]),
+                    more_outputs=[(_NP[w[2]], dims(w)) for w in outs[1:]])
 
 
 def dag_program(kind="shared_sum_4out", shape=(8192, 8192), seed=13):
