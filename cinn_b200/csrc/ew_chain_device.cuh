@@ -187,23 +187,6 @@ __device__ __forceinline__ void load_vec4(const void* p, int dtype, long long id
   }
 }
 
-// Eight consecutive elements starting at idx (idx % 8 == 0 for 16-bit types: one 16-byte load; pointer 16-byte aligned).
-__device__ __forceinline__ void load_vec8(const void* p, int dtype, long long idx, bool stream, float (&f)[8]) {
-  if (dtype == EW_F16 || dtype == EW_BF16) {
-    const uint4* q = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + idx);
-    const uint4 u  = stream ? __ldcs(q) : __ldg(q);
-    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      if (dtype == EW_F16) unpack_h2(w[k], f[2 * k], f[2 * k + 1]);
-      else unpack_bf2(w[k], f[2 * k], f[2 * k + 1]);
-    }
-  } else {
-    load_vec4(p, dtype, idx, stream, *reinterpret_cast<float(*)[4]>(&f[0]));
-    load_vec4(p, dtype, idx + 4, stream, *reinterpret_cast<float(*)[4]>(&f[4]));
-  }
-}
-
 // float -> integer as the x86 conversion instruction does it (cvttss2si): toward zero; NaN and values out of
 // range give the most negative integer.
 __device__ __forceinline__ int32_t x86_f2i32(float x) {
@@ -278,12 +261,7 @@ __device__ __forceinline__ long long side_index(long long i, long long inner, lo
 // (the later passes of a row program), so that it stays in L1.
 template <int VEC>
 __device__ __forceinline__ void load_side(const SideSpec& s, long long i0, float (&f)[VEC], bool stream = true) {
-  if (VEC == 8 && s.mode == EW_SIDE_FULL) {
-    load_vec8(s.ptr, s.dtype, i0, stream, *reinterpret_cast<float(*)[8]>(&f[0]));
-  } else if (VEC == 8 && s.mode == EW_SIDE_PERIODIC_VEC) {  // the caller has checked mid % 8 == 0
-    const long long idx = s.mid == s.row_len ? i0 - s.row_base : side_index(i0, 1, s.mid);
-    load_vec8(s.ptr, s.dtype, idx, false, *reinterpret_cast<float(*)[8]>(&f[0]));
-  } else if (VEC == 4 && s.mode == EW_SIDE_FULL) {
+  if (VEC == 4 && s.mode == EW_SIDE_FULL) {
     load_vec4(s.ptr, s.dtype, i0, stream, *reinterpret_cast<float(*)[4]>(&f[0]));
   } else if (VEC == 4 && s.mode == EW_SIDE_PERIODIC_VEC) {
     const long long idx = s.mid == s.row_len ? i0 - s.row_base : side_index(i0, 1, s.mid);
@@ -310,13 +288,6 @@ struct Store2 {
 template <int VEC>
 __device__ __forceinline__ void store_second(const Store2& st, const float (&a)[VEC]) {
   if constexpr (VEC == 8) {
-    if ((st.dtype == EW_F16 || st.dtype == EW_BF16) && st.i1 == st.i0 + 4 && (st.i0 & 7) == 0) {  // eight adjacent, aligned 16-bit values: one store
-      uint4 u;
-      if (st.dtype == EW_F16) u = make_uint4(pack_h2(a[0], a[1]), pack_h2(a[2], a[3]), pack_h2(a[4], a[5]), pack_h2(a[6], a[7]));
-      else u = make_uint4(pack_bf2(a[0], a[1]), pack_bf2(a[2], a[3]), pack_bf2(a[4], a[5]), pack_bf2(a[6], a[7]));
-      __stcs(reinterpret_cast<uint4*>(static_cast<uint16_t*>(st.ptr) + st.i0), u);
-      return;
-    }
     store_second<4>(Store2{st.ptr, st.dtype, st.i0, 0}, *reinterpret_cast<const float(*)[4]>(&a[0]));
     store_second<4>(Store2{st.ptr, st.dtype, st.i1, 0}, *reinterpret_cast<const float(*)[4]>(&a[4]));
     return;

@@ -72,7 +72,7 @@ template <int VEC, bool FAST = false>
 __device__ __forceinline__ bool rp_element_step(unsigned w, float imm, float imm2, unsigned long long meta,
                                                 const RowInputs& in, const RowOutputs& out, long long i0,
                                                 float (&regs)[DAG_REGS][VEC], const float (&sregs)[ROWP_SREGS],
-                                                float (&acc)[ROWP_SREGS], bool reread, float (*cache)[VEC] = nullptr,
+                                                float (&acc)[ROWP_SREGS], bool reread, float (*cache)[4] = nullptr,
                                                 int cache_mode = 0) {
   const int op = (int)(w & 0xff), dst = (int)((w >> 8) & 15), a = (int)((w >> 12) & 31), b = (int)((w >> 17) & 31),
             c = (int)((w >> 22) & 31);
@@ -80,16 +80,16 @@ __device__ __forceinline__ bool rp_element_step(unsigned w, float imm, float imm
   if (op == DAG_LOAD) {
     const SideSpec s = {in.ptr[a], (int)((meta >> (6 * a)) & 7), (int)((meta >> (6 * a + 3)) & 7), in.mid[a], in.inner[a], in.row_base, in.row_len};
     // cache_mode 2: this full-size input of the row is already in this thread's registers
-    if ((VEC == 4 || VEC == 8) && cache_mode == 2 && s.mode == EW_SIDE_FULL) {
+    if (VEC == 4 && cache_mode == 2 && s.mode == EW_SIDE_FULL) {
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) regs[dst][i] = cache[a][i];
+      for (int i = 0; i < VEC; ++i) regs[dst][i] = cache[a][i & 3];
       return false;
     }
     load_side<VEC>(s, i0, regs[dst], !reread);  // a row that a later pass reads again stays in L1
     return false;
   }
   if (op == DAG_STORE) {
-    const Store2 st = {out.ptr[dst], (int)((meta >> (48 + 3 * dst)) & 7), i0, i0 + 4};
+    const Store2 st = {out.ptr[dst], (int)((meta >> (48 + 3 * dst)) & 7), i0, 0};
     store_second<VEC>(st, regs[a]);
     return false;
   }
@@ -187,11 +187,6 @@ struct DynRowProgram {
                                                      const float (&)[ROWP_SREGS], float (&)[ROWP_SREGS], float (*)[4]) const {}
   __device__ __forceinline__ void preload(const RowInputs&, long long, float (*)[4]) const {}
   __device__ __forceinline__ void prefetch(const RowInputs&, long long) const {}
-  static constexpr bool kWide = false;
-  __device__ __forceinline__ bool wide_sides_ok(const RowInputs&) const { return false; }
-  __device__ __forceinline__ void preload_wide(const RowInputs&, long long, float (*)[8]) const {}
-  __device__ __forceinline__ void run_element_cached_wide(int, const RowInputs&, const RowOutputs&, long long,
-                                                          const float (&)[ROWP_SREGS], float (&)[ROWP_SREGS], float (*)[8]) const {}
   __device__ __forceinline__ int passes() const {
     int p = 0;
     for (int k = 0; k < ROWP_MAX_PASSES; ++k)
@@ -367,73 +362,6 @@ struct StaticRowProgram {
     else if (pass == 1) cached_from<first(1, false), first(1, false) + count(1, false)>(in, out, i0, regs, sregs, acc, cache);
     else cached_from<first(2, false), first(2, false) + count(2, false)>(in, out, i0, regs, sregs, acc, cache);
   }
-  // ---- the wide form: eight elements per vector, for programs whose full-size tensors are all 16-bit floats (a
-  // 16-byte access moves eight of them) -------------------------------------------------------------------------------
-  __host__ __device__ static constexpr bool wide() {
-    bool any = false;
-    for (int p = 0; p < ROWP_MAX_PASSES; ++p)
-      for (int k = first(p, false); k < first(p, false) + count(p, false); k += step_words(k)) {
-        const uint32_t w = word(k);
-        const int op = (int)(w & 0xff);
-        if (op == DAG_LOAD) {
-          const int a = (int)((w >> 12) & 7), dt = (int)((META >> (6 * a)) & 7), mode = (int)((META >> (6 * a + 3)) & 7);
-          if (mode == EW_SIDE_FULL) {
-            if (dt != EW_F16 && dt != EW_BF16) return false;
-            any = true;
-          } else if (mode != EW_SIDE_PERIODIC_VEC && mode != EW_SIDE_SCALAR) {
-            return false;  // one value per four elements, or an index per element: the four-element form
-          }
-        } else if (op == DAG_STORE) {
-          const int dt = (int)((META >> (48 + 3 * ((w >> 8) & 15))) & 7);
-          if (dt != EW_F16 && dt != EW_BF16) return false;
-        }
-      }
-    return any;
-  }
-  static constexpr bool kWide = wide();
-  // vector operands along the row must have a period that eight-element vectors divide
-  __device__ __forceinline__ bool wide_sides_ok(const RowInputs& in) const {
-    bool ok = true;
-#pragma unroll
-    for (int a = 0; a < DAG_MAX_IN; ++a)
-      if (((META >> (6 * a + 3)) & 7) == (unsigned)EW_SIDE_PERIODIC_VEC) ok = ok && in.mid[a] % 8 == 0;
-    return ok;
-  }
-  template <int K, int END>
-  __device__ __forceinline__ void preload_wide_from(const RowInputs& in, long long i0, float (*cache)[8]) const {
-    if constexpr (K < END) {
-      constexpr uint32_t w = word(K);
-      if constexpr ((w & 0xff) == (unsigned)DAG_LOAD) {
-        constexpr int a = (int)((w >> 12) & 7);
-        if constexpr (((META >> (6 * a + 3)) & 7) == (unsigned)EW_SIDE_FULL)
-          load_vec8(in.ptr[a], (int)((META >> (6 * a)) & 7), i0, true, *reinterpret_cast<float(*)[8]>(&cache[a][0]));
-      }
-      preload_wide_from<K + step_words(K), END>(in, i0, cache);
-    }
-  }
-  __device__ __forceinline__ void preload_wide(const RowInputs& in, long long i0, float (*cache)[8]) const {
-    preload_wide_from<first(0, false), first(0, false) + count(0, false)>(in, i0, cache);
-  }
-  template <int K, int END>
-  __device__ __forceinline__ void cached_wide_from(const RowInputs& in, const RowOutputs& out, long long i0,
-                                                   float (&regs)[DAG_REGS][8], const float (&sregs)[ROWP_SREGS],
-                                                   float (&acc)[ROWP_SREGS], float (*cache)[8]) const {
-    if constexpr (K < END) {
-      constexpr uint32_t w = word(K);
-      constexpr int mode = ((w & 0xff) == (unsigned)DAG_LOAD && ((loaded_by_pass0() >> ((w >> 12) & 7)) & 1u)) ? 2 : 0;
-      (void)rp_element_step<8, true>(w, rp_imm(steps[K]), rp_imm(steps[K + 1 < ROWP_MAX_STEPS ? K + 1 : K]), META, in, out, i0,
-                                     regs, sregs, acc, false, cache, mode);
-      cached_wide_from<K + step_words(K), END>(in, out, i0, regs, sregs, acc, cache);
-    }
-  }
-  __device__ __forceinline__ void run_element_cached_wide(int pass, const RowInputs& in, const RowOutputs& out,
-                                                          long long i0, const float (&sregs)[ROWP_SREGS],
-                                                          float (&acc)[ROWP_SREGS], float (*cache)[8]) const {
-    float regs[DAG_REGS][8];
-    if (pass == 0) cached_wide_from<first(0, false), first(0, false) + count(0, false)>(in, out, i0, regs, sregs, acc, cache);
-    else if (pass == 1) cached_wide_from<first(1, false), first(1, false) + count(1, false)>(in, out, i0, regs, sregs, acc, cache);
-    else cached_wide_from<first(2, false), first(2, false) + count(2, false)>(in, out, i0, regs, sregs, acc, cache);
-  }
   template <int VEC>
   __device__ __forceinline__ void run_element(int pass, const RowInputs& in, const RowOutputs& out, long long i0,
                                               const float (&sregs)[ROWP_SREGS], float (&acc)[ROWP_SREGS]) const {
@@ -481,36 +409,11 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
   const bool use_cache = Prog::kStatic && FORM != 0 && (FORM == 1 || FORM == 3 || !per_warp) && vec_ok && npass > 1 &&
                          (r >> 2) <= (long long)kCacheVecs * kStride;
   float cache[kCacheVecs][DAG_MAX_IN][4];
-  // Programs whose full-size tensors are all 16-bit floats move eight elements per vector (16-byte accesses) when the
-  // row length, the vector operands' periods and the cache allow it; else the four-element path below takes them.
-  constexpr int kWideVecs = kCacheVecs / 2;  // half as many vectors of twice the width: the same rows, the same registers
-  bool use_wide = false;
-  if constexpr (Prog::kWide) {
-    use_wide = FORM != 0 && (FORM == 1 || FORM == 3 || !per_warp) && vec_ok && r % 8 == 0 &&
-               (r >> 3) <= (long long)kWideVecs * kStride && prog.wide_sides_ok(in);
-  }
-  float cache_w[Prog::kWide ? kWideVecs : 1][DAG_MAX_IN][8];
   // CTA-per-row: every thread of the CTA walks the same rows, so the barriers below are uniform.
   for (long long row = first; row < rows; row += step) {
     const long long base = row * r;
     in.row_base          = base;
-    if constexpr (Prog::kWide) {
-      if (use_wide) {
-#pragma unroll
-        for (int j = 0; j < kWideVecs; ++j) {
-          const long long v = t + (long long)j * kStride;
-          if (v < (r >> 3)) prog.preload_wide(in, base + (v << 3), cache_w[j]);
-        }
-        if (row + step < rows) {
-#pragma unroll
-          for (int j = 0; j < kWideVecs; ++j) {
-            const long long v = t + (long long)j * kStride;
-            if (v < (r >> 3)) prog.prefetch(in, base + step * r + (v << 3));
-          }
-        }
-      }
-    }
-    if (use_cache && !use_wide) {
+    if (use_cache) {
       // this row's loads, all in flight together; the next row is asked into L2 meanwhile (no registers held for it),
       // so that the next wait is an L2 latency, not a DRAM one
 #pragma unroll
@@ -536,20 +439,7 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
 #pragma unroll
       for (int k = 0; k < ROWP_SREGS; ++k) acc[k] = rp_identity((kinds >> (2 * k)) & 3);
       long long done = 0;
-      bool wide_done = false;
-      if constexpr (Prog::kWide) {
-        if (use_wide) {
-#pragma unroll
-          for (int j = 0; j < kWideVecs; ++j) {
-            const long long v = t + (long long)j * kStride;
-            if (v < (r >> 3)) prog.run_element_cached_wide(pass, in, out, base + (v << 3), sregs, acc, cache_w[j]);
-          }
-          done      = r;
-          wide_done = true;
-        }
-      }
-      if (wide_done) {
-      } else if (use_cache) {
+      if (use_cache) {
         // every thread's vectors of the row were loaded once, all the loads in flight together
 #pragma unroll
         for (int j = 0; j < kCacheVecs; ++j) {
