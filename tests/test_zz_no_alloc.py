@@ -91,5 +91,7 @@ def test_static_scratch_rejects_what_does_not_fit():
     assert rc == 0, L.cinn_b200_last_error()
     torch.cuda.synchronize()
     assert torch.equal(y, x.max(dim=0).values)
-    assert L.cinn_b200_col_reduce_f32_static_scratch(7, None, None, 1, 1, 1, None) == -1
+    # an unknown reduce kind is refused too (real buffers again: no call that could launch gets a pointer it may not use)
+    assert L.cinn_b200_col_reduce_f32_static_scratch(7, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(y.data_ptr()),
+                                                     1, 64, inner, None) == -1
     torch.cuda.synchronize()
