@@ -376,6 +376,8 @@ PROFILE_GROUPS = {
     "row_affine_relu": lambda W: W.row_program("affine_relu"),
     "row_rms_norm": lambda W: W.row_program("rms_norm"),
     "row_standardise": lambda W: W.row_program("standardise"),
+    "row_scaled_softmax": lambda W: W.row_program("scaled_softmax"),
+    "row_log_softmax": lambda W: W.row_program("log_softmax"),
     "dag_shared_sum_4out": lambda W: W.dag_program("shared_sum_4out", (4096, 8192)),
 }
 
