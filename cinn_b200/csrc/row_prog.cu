@@ -409,6 +409,7 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
   const bool use_cache = Prog::kStatic && FORM != 0 && (FORM == 1 || FORM == 3 || !per_warp) && vec_ok && npass > 1 &&
                          (r >> 2) <= (long long)kCacheVecs * kStride;
   float cache[kCacheVecs][DAG_MAX_IN][4];
+  const int nvec_row = use_cache ? (int)(r >> 2) : 0;
   // CTA-per-row: every thread of the CTA walks the same rows, so the barriers below are uniform.
   for (long long row = first; row < rows; row += step) {
     const long long base = row * r;
@@ -418,14 +419,14 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
       // so that the next wait is an L2 latency, not a DRAM one
 #pragma unroll
       for (int j = 0; j < kCacheVecs; ++j) {
-        const long long v = t + (long long)j * kStride;
-        if (v < (r >> 2)) prog.preload(in, base + (v << 2), cache[j]);
+        const int v = t + j * kStride;  // (cached rows have at most 8192 elements)
+        if (v < nvec_row) prog.preload(in, base + (v << 2), cache[j]);
       }
       if (row + step < rows) {
 #pragma unroll
         for (int j = 0; j < kCacheVecs; ++j) {
-          const long long v = t + (long long)j * kStride;
-          if (v < (r >> 2)) prog.prefetch(in, base + step * r + (v << 2));
+          const int v = t + j * kStride;
+          if (v < nvec_row) prog.prefetch(in, base + step * r + (v << 2));
         }
       }
     }
@@ -443,8 +444,8 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
         // every thread's vectors of the row were loaded once, all the loads in flight together
 #pragma unroll
         for (int j = 0; j < kCacheVecs; ++j) {
-          const long long v = t + (long long)j * kStride;
-          if (v < (r >> 2)) prog.run_element_cached(pass, in, out, base + (v << 2), sregs, acc, cache[j]);
+          const int v = t + j * kStride;
+          if (v < nvec_row) prog.run_element_cached(pass, in, out, base + (v << 2), sregs, acc, cache[j]);
         }
         done = r;
       } else if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary
