@@ -265,6 +265,8 @@ def side_groups(torch, dev, peak, only=None):
         ("generic_chain_abs_add_f32_8192x8192", lambda: W.generic_chain("abs_add_f32"), 1, "chain kernel"),
         ("generic_chain_select_f32_8192x8192", lambda: W.generic_chain("select_f32"), 1, "chain kernel"),
         ("generic_chain_greater_than_f32_8192x8192", lambda: W.generic_chain("greater_than_f32"), 1, "chain kernel"),
+        ("generic_chain_gelu_f32_8192x8192", lambda: W.generic_chain("gelu_f32"), 1, "the decomposed gelu (erf form)"),
+        ("generic_chain_sigmoid_grad_f32_8192x8192", lambda: W.generic_chain("sigmoid_grad_f32"), 1, "dy * y * (1 - y)"),
         ("generic_chain_abs_add_i32_8192x8192", lambda: W.generic_chain("abs_add_i32"), 1, "integer chain kernel"),
         ("generic_chain_affine_f64_8192x8192", lambda: W.generic_chain("affine_f64"), 1, "float64 chain kernel"),
         ("generic_chain_abs_add_f64_8192x8192", lambda: W.generic_chain("abs_add_f64"), 1, "float64 chain kernel"),

@@ -155,6 +155,38 @@ GROUPS.append(("gelu_tanh_kept_f32",
                "op elementwise_mul y = x h ; axis=-1\noutput y float32 %s\noutput t float32 %s\n" % (FULL, FULL, FULL)))
 
 
+# What the NetBuilder emits for the activation and backward forms below (the decomposed gelu of
+# cinn/frontend/decomposer/activation.cc, relu_grad, the sigmoid / tanh derivatives written with the primitive ops,
+# softplus, a scaled residual): group texts as the fusion pass prints them, so that users' programs meet the entries.
+def _raw(name, body):
+    return name, "group fn_static_%s\n%s" % (name, body)
+
+
+_GELU = ("op fill_constant h = ; dtype=float32 shape={s} value=0.5\n"
+         "op fill_constant r = ; dtype=float32 shape={s} value=0.7071067811865476\n"
+         "op elementwise_mul u = {x} r ; axis=-1\nop erf e = u\nop elementwise_mul v = h e ; axis=-1\n"
+         "op elementwise_add w = h v ; axis=-1\nop elementwise_mul y = {x} w ; axis=-1\n")
+GROUPS += [
+    _raw("gelu_f32", "input x float32 %s\n" % FULL + _GELU.format(s=FULL, x="x") + "output y float32 %s\n" % FULL),
+    _raw("bias_gelu_f32", "input x float32 %s\ninput b float32 %s\nop elementwise_add t = x b ; axis=-1\n" % (FULL, ROWVEC) +
+         _GELU.format(s=FULL, x="t") + "output y float32 %s\n" % FULL),
+    _raw("gelu_f16", "input x float16 %s\nop cast xf = x ; dtype=float32\n" % FULL + _GELU.format(s=FULL, x="xf") +
+         "op cast z = y ; dtype=float16\noutput z float16 %s\n" % FULL),
+    _raw("relu_grad_f32", "input y float32 {s}\ninput dy float32 {s}\nop fill_constant z = ; dtype=float32 shape={s} value=0.0\n"
+         "op greater_than m = y z ; axis=-1\nop select g = m dy z\noutput g float32 {s}\n".format(s=FULL)),
+    _raw("sigmoid_grad_f32", "input y float32 {s}\ninput dy float32 {s}\n"
+         "op scale c = y ; bias=1.0 bias_after_scale=true scale=-1.0\nop elementwise_mul t = y c ; axis=-1\n"
+         "op elementwise_mul g = dy t ; axis=-1\noutput g float32 {s}\n".format(s=FULL)),
+    _raw("tanh_grad_f32", "input y float32 {s}\ninput dy float32 {s}\nop elementwise_mul q = y y ; axis=-1\n"
+         "op scale c = q ; bias=1.0 bias_after_scale=true scale=-1.0\nop elementwise_mul g = dy c ; axis=-1\n"
+         "output g float32 {s}\n".format(s=FULL)),
+    _raw("softplus_f32", "input x float32 {s}\nop exp e = x\nop scale p = e ; bias=1.0 bias_after_scale=true scale=1.0\n"
+         "op log y = p\noutput y float32 {s}\n".format(s=FULL)),
+    _raw("residual_scale_f32", "input f float32 {s}\ninput x float32 {s}\n"
+         "op scale t = f ; bias=0.0 bias_after_scale=true scale=0.5\nop elementwise_add y = x t ; axis=-1\n"
+         "output y float32 {s}\n".format(s=FULL)),
+]
+
 
 def reduce_group(name, inputs, ops, red, operand, axis, shape=FULL):
     """reduce_<red>(chain) over one axis of a 2-D shape: rows (axis 1) or columns (axis 0)."""

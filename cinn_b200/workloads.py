@@ -234,6 +234,13 @@ def generic_chain(kind, shape=(8192, 8192), seed=5):
         "greater_than_f32": (["A float32", "B float32"], ["op greater_than t0 = A B"], "t0", "bool"),
         "abs_add_i32": (["A int32", "B int32"], ["op elementwise_add t0 = A B", "op abs t1 = t0"], "t1", "int32"),
         "abs_add_f64": (["A float64", "B float64"], ["op elementwise_add t0 = A B", "op abs t1 = t0"], "t1", "float64"),
+        "gelu_f32": (["x float32"], ["op fill_constant h = ; dtype=float32 shape=%s value=0.5" % s,
+                                    "op fill_constant r = ; dtype=float32 shape=%s value=0.7071067811865476" % s,
+                                    "op elementwise_mul u = x r ; axis=-1", "op erf e = u", "op elementwise_mul v = h e ; axis=-1",
+                                    "op elementwise_add w = h v ; axis=-1", "op elementwise_mul y = x w ; axis=-1"], "y", "float32"),
+        "sigmoid_grad_f32": (["y float32", "dy float32"], ["op scale c = y ; bias=1.0 bias_after_scale=true scale=-1.0",
+                                                           "op elementwise_mul t = y c ; axis=-1",
+                                                           "op elementwise_mul g = dy t ; axis=-1"], "g", "float32"),
         "affine_f64": (["A float64"], ["op scale t0 = A ; scale=0.1 bias=1e-05", "op abs t1 = t0"], "t1", "float64"),
     }
     ins, ops, out, out_dtype = table[kind]
