@@ -56,8 +56,15 @@ __device__ __noinline__ float heavy_atan2(float a, float b) {
 // FAST: exp / tanh / sigmoid through the hardware's approximate exponential and reciprocal (relative error about
 // 1e-6).  Only the specialised reductions use it: their result is judged at the reduction tolerance (1e-5 relative),
 // which a sum of such terms keeps with a wide margin, and the full-precision forms make those kernels issue-bound.
-template <int VEC, bool FAST = false>
+// INL: the caller knows `op` at build time, so the error function is expanded in place (the same erff as the
+// out-of-line copy, without a call per element); the interpreter keeps the call to hold its code size down.
+template <int VEC, bool FAST = false, bool INL = false>
 __device__ __forceinline__ void apply_unary(int op, float imm, float (&a)[VEC]) {
+  if (INL && op == EW_ERF) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) a[i] = erff(a[i]);
+    return;
+  }
 #define EW_UNARY_CASE(code, expr) \
   case code:                      \
     _Pragma("unroll") for (int i = 0; i < VEC; ++i) { const float x = a[i]; a[i] = (expr); } \
@@ -353,14 +360,14 @@ __device__ __forceinline__ void pick_operand(int sel, float imm, const float (&s
 // specialised at build time call it with constants, so that both execute the same arithmetic by construction.
 // NT = 2: two temporaries (operand selectors 5 and 6, written by EW_STASH) for expression trees.
 // ST2: the program may hold EW_STORE2 steps (st2 then says where they write).
-template <int VEC, int NS, int NT, bool ST2, bool FAST = false>
+template <int VEC, int NS, int NT, bool ST2, bool FAST = false, bool INL = false>
 __device__ __forceinline__ bool chain_step(int op, int asel, int bsel, int role, float imm, float imm2,
                                            const float (&s1)[VEC], const float (&s2)[VEC], const float (&s3)[VEC],
                                            float (&acc)[VEC], float (&ta)[NT > 0 ? VEC : 1],
                                            float (&tb)[NT > 0 ? VEC : 1], const Store2* st2) {
   if (op == EW_NOP) return false;
   if (op >= EW_FIRST_UNARY) {
-    apply_unary<VEC, FAST>(op, imm, acc);
+    apply_unary<VEC, FAST, INL>(op, imm, acc);
     return false;
   }
   if (ST2 && op == EW_STORE2) {
@@ -451,7 +458,7 @@ __device__ __forceinline__ void run_chain_static_from(const long long* steps, co
     constexpr bool two = ((op == EW_FMA || op == EW_SELECT) && bsel == 0) || op == EW_SCALE_PRE;
     const float imm  = __uint_as_float((uint32_t)(steps[K] >> 32));
     const float imm2 = __uint_as_float((uint32_t)(steps[K + 1 < EW_MAX_STEPS ? K + 1 : K] >> 32));
-    (void)chain_step<VEC, NS, NT, ST2, FAST>(op, asel, bsel, role, imm, imm2, s1, s2, s3, acc, ta, tb, st2);
+    (void)chain_step<VEC, NS, NT, ST2, FAST, true>(op, asel, bsel, role, imm, imm2, s1, s2, s3, acc, ta, tb, st2);
     run_chain_static_from<VEC, NS, NT, ST2, FAST, K + (two ? 2 : 1), SIG...>(steps, s1, s2, s3, acc, ta, tb, st2);
   }
 }
