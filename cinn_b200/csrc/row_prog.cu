@@ -296,6 +296,14 @@ struct StaticRowProgram {
       if ((word(k) & 0xff) == (unsigned)DAG_LOAD) m |= 1u << ((word(k) >> 12) & 7);
     return m;
   }
+  // CTAs per SM the kernel is compiled for: a program of three passes over two or more cached inputs keeps twice the
+  // row state in registers and spills at three CTAs' register budget (80), so it is built for two (128).
+  __host__ __device__ static constexpr int ctas_per_sm() {
+    int full = 0;
+    for (int a = 0; a < DAG_MAX_IN; ++a)
+      if (((loaded_by_pass0() >> a) & 1u) && ((META >> (6 * a + 3)) & 7) == (unsigned)EW_SIDE_FULL) ++full;
+    return (full >= 2 && StaticRowProgram().passes() >= 3) ? 2 : 3;
+  }
   __host__ __device__ static constexpr int step_words(int k) {
     const uint32_t w = word(k);
     const int op = (int)(w & 0xff), a = (int)((w >> 12) & 31), b = (int)((w >> 17) & 31), c = (int)((w >> 22) & 31);
@@ -541,7 +549,8 @@ __global__ void __launch_bounds__(256) k_row_program(ROWP_PARAMS) {
 }
 
 template <int FORM, unsigned long long META, unsigned long long COUNTS, uint32_t... SIG>
-__global__ void __launch_bounds__(256, 3) k_row_program_static(ROWP_PARAMS) {
+__global__ void __launch_bounds__(256, (FORM == 4 ? 2 : StaticRowProgram<META, COUNTS, SIG...>::ctas_per_sm()))
+k_row_program_static(ROWP_PARAMS) {
   grid_dependency_sync();
   ROWP_UNPACK;
   const StaticRowProgram<META, COUNTS, SIG...> prog = {steps};
