@@ -16,6 +16,7 @@
 #include <sstream>
 
 #include "ew_chain.h"
+#include "row_prog_prefix.h"
 #include "group_desc.h"
 
 namespace cinn_b200 {
@@ -2154,6 +2155,16 @@ std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceI
       // rows of 4097 to 8192 elements: a CTA per row with eight vectors per thread in registers between the passes
     } else {
       fixed = FindStaticChain(group == 32 ? "row_program_w" : "row_program", meta, (int)words.size() + 2, sig);
+    }
+    // The specialised kernels evaluate the steps that a pass shares with the passes after it once per row
+    // (row_prog_prefix.h), which is only the same arithmetic when those steps carry the same constants.  The builder
+    // emits them from the same graph nodes, so they do; a program where they differ keeps the interpreting kernel.
+    if (fixed) {
+      const RowPrefixPlan plan = PlanRowPrefixes(sig + 2, counts, (unsigned long long)meta);
+      for (int q = 1; q < npass && fixed; ++q)
+        for (int k = 0; k < plan.start[q] && fixed; ++k)
+          if ((words[row_prefix::ElementFirst(counts, q) + k] >> 32) != (words[row_prefix::ElementFirst(counts, q - 1) + k] >> 32))
+            fixed = nullptr;
     }
     if (fixed) st.kernel = fixed;
   }

@@ -25,6 +25,7 @@
 // approximate exponential, and divide by a per-row value through one reciprocal per row.
 #include "ew_chain_body.cuh"
 #include "kernel_registry.h"
+#include "row_prog_prefix.h"
 
 namespace cinn_b200 {
 namespace {
@@ -360,15 +361,43 @@ struct StaticRowProgram {
       cached_from<K + step_words(K), END>(in, out, i0, regs, sregs, acc, cache);
     }
   }
-  // One vector of a row whose vectors stay in this thread's registers between the passes (`cache` is the slot of
-  // this vector: [input][lane of the vector]).
+  // where the passes share their first steps (row_prog_prefix.h)
+  __host__ __device__ static constexpr RowPrefixPlan prefix_plan() {
+    constexpr uint32_t sig[kN > 0 ? kN : 1] = {SIG...};
+    return PlanRowPrefixes(sig, COUNTS, META);
+  }
+  // One pass over one cached vector.  `cache` is the slot of this vector: [input][lane of the vector] for the inputs
+  // pass 0 loaded.  The value at the end of the steps this pass shares with the later ones takes the place of an
+  // input that nothing loads afterwards (written here after `save` words, read by the later passes, which begin
+  // after those steps): no registers are added to the row's state.
+  template <int PASS>
+  __device__ __forceinline__ void cached_pass(const RowInputs& in, const RowOutputs& out, long long i0,
+                                              const float (&sregs)[ROWP_SREGS], float (&acc)[ROWP_SREGS],
+                                              float (*cache)[4]) const {
+    constexpr RowPrefixPlan plan = prefix_plan();
+    constexpr int b = first(PASS, false), e = b + count(PASS, false);
+    constexpr int start = plan.start[PASS], save = plan.save[PASS];
+    float regs[DAG_REGS][4];
+    if constexpr (start > 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) regs[plan.reg[PASS]][i] = cache[plan.slot][i];
+    }
+    if constexpr (save > start) {
+      cached_from<b + start, b + save>(in, out, i0, regs, sregs, acc, cache);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cache[plan.slot][i] = regs[plan.save_reg[PASS]][i];
+      cached_from<b + save, e>(in, out, i0, regs, sregs, acc, cache);
+    } else {
+      cached_from<b + start, e>(in, out, i0, regs, sregs, acc, cache);
+    }
+  }
+  // One vector of a row whose vectors stay in this thread's registers between the passes.
   __device__ __forceinline__ void run_element_cached(int pass, const RowInputs& in, const RowOutputs& out, long long i0,
                                                      const float (&sregs)[ROWP_SREGS], float (&acc)[ROWP_SREGS],
                                                      float (*cache)[4]) const {
-    float regs[DAG_REGS][4];
-    if (pass == 0) cached_from<first(0, false), first(0, false) + count(0, false)>(in, out, i0, regs, sregs, acc, cache);
-    else if (pass == 1) cached_from<first(1, false), first(1, false) + count(1, false)>(in, out, i0, regs, sregs, acc, cache);
-    else cached_from<first(2, false), first(2, false) + count(2, false)>(in, out, i0, regs, sregs, acc, cache);
+    if (pass == 0) cached_pass<0>(in, out, i0, sregs, acc, cache);
+    else if (pass == 1) cached_pass<1>(in, out, i0, sregs, acc, cache);
+    else cached_pass<2>(in, out, i0, sregs, acc, cache);
   }
   template <int VEC>
   __device__ __forceinline__ void run_element(int pass, const RowInputs& in, const RowOutputs& out, long long i0,

@@ -149,6 +149,29 @@ def test_reduction_with_a_per_row_epilogue_as_one_group():
     assert np.allclose(out.cpu().numpy(), want, rtol=2e-5, atol=1e-4)
 
 
+def test_softmax_with_other_constants_in_the_later_passes():
+    """max(x * 0.125) but exp(x * 0.25 - max): the passes repeat the same step words with other constants, so the
+    value a specialised kernel would keep from the first pass is not the one the later passes need; the matcher
+    gives the program to the interpreting kernel, and the result is the oracle's."""
+    import torch
+    rows, r = 37, 4096
+    desc = ("group fn_two_scales\ninput X float32 %d,%d\n"
+            "op scale d = X ; bias=0.0 bias_after_scale=true scale=0.125\n"
+            "op reduce_max mx = d ; dim=1 keep_dim=false\nop broadcast_to mb = mx ; broadcast_axes=0 out_shape=%d,%d\n"
+            "op scale d2 = X ; bias=0.0 bias_after_scale=true scale=0.25\nop subtract z = d2 mb ; axis=-1\nop exp e = z\n"
+            "op reduce_sum s = e ; dim=1 keep_dim=false\nop broadcast_to sb = s ; broadcast_axes=0 out_shape=%d,%d\n"
+            "op divide y = e sb ; axis=-1\noutput y float32 %d,%d\n" % ((rows, r) * 4))
+    g = cinn_b200.FusedGroup(desc)
+    assert g.pattern == "row_program" and g.kernel_names() == ["row_program"], g.kernel_names()
+    x = np.random.default_rng(3).standard_normal((rows, r)).astype(np.float32)
+    out = torch.empty((rows, r), device="cuda")
+    g.run([torch.from_numpy(x).cuda(), out])
+    torch.cuda.synchronize()
+    g.release()
+    want = ge.run_all(desc, [x])["y"]
+    assert np.allclose(out.cpu().numpy(), want, rtol=2e-5, atol=1e-6)
+
+
 @pytest.mark.parametrize("form", [32, 128, 256])
 @pytest.mark.parametrize("index", [0, 1, 2, 5])  # rms_norm, standardise, log_softmax, min_max_normalise
 @pytest.mark.parametrize("shape", [(37, 4096), (19, 2052), (41, 1024)], ids=lambda s: "%dx%d" % s)

@@ -92,3 +92,20 @@ def test_builder_row_compositions_fuse_into_one_specialised_kernel():
                 (shape, make.__name__, kernels)
             if shape[1] <= 1024:
                 assert kernels[0].endswith("_w")
+
+
+def test_passes_that_repeat_steps_with_other_constants_keep_the_interpreter():
+    """A specialised row program evaluates the steps its passes share once per row, which is only the same arithmetic
+    when those steps carry the same constants: softmax of x * 0.125 is the listed program; with the maximum taken
+    of x * 0.125 but the exponent of x * 0.25 the step words are the same and the constants are not, so the matcher
+    leaves the program to the interpreting kernel."""
+    gen = load_generator()
+    desc = dict(gen.ROW_GROUPS)["scaled_softmax"]
+    g = cinn_b200.FusedGroup(desc.replace("64,4096", "16,2048"))
+    assert g.kernel_names() == ["row_program_static_scaled_softmax_h"], g.kernel_names()
+    g.release()
+    other = desc.replace("op subtract z = d mb", "op scale d2 = X ; bias=0.0 bias_after_scale=true scale=0.25\nop subtract z = d2 mb")
+    assert other != desc
+    g = cinn_b200.FusedGroup(other.replace("fn_static_scaled_softmax", "fn_two_scales"))
+    assert g.pattern == "row_program" and g.kernel_names() == ["row_program"], g.kernel_names()
+    g.release()
