@@ -380,6 +380,7 @@ PROFILE_GROUPS = {
     "row_standardise": lambda W: W.row_program("standardise"),
     "row_scaled_softmax": lambda W: W.row_program("scaled_softmax"),
     "row_log_softmax": lambda W: W.row_program("log_softmax"),
+    "row_masked_softmax": lambda W: W.row_program("masked_softmax"),
     "dag_shared_sum_4out": lambda W: W.dag_program("shared_sum_4out", (4096, 8192)),
 }
 

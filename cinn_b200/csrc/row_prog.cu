@@ -421,7 +421,9 @@ struct StaticRowProgram {
 // 3: half a CTA (four warps) per row, two rows per CTA at a time, each half with a named barrier of its own; 4: a CTA
 // per row with eight cached vectors per thread (rows of up to 8192 elements)
 // (the specialised kernels: one instantiation each, so that the register cache below is sized for its form).
-template <class Prog, int FORM>
+// FULL: the row fills the register cache exactly (r / 4 = vectors per thread x threads per row), so no vector of it
+// needs a bounds test.
+template <class Prog, int FORM, bool FULL = false>
 __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInputs& inputs, const RowOutputs& out,
                                                  long long rows, long long r, long long group, long long vec_ok) {
   RowInputs in = inputs;
@@ -457,13 +459,13 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
 #pragma unroll
       for (int j = 0; j < kCacheVecs; ++j) {
         const int v = t + j * kStride;  // (cached rows have at most 8192 elements)
-        if (v < nvec_row) prog.preload(in, base + (v << 2), cache[j]);
+        if (FULL || v < nvec_row) prog.preload(in, base + (v << 2), cache[j]);
       }
       if (row + step < rows) {
 #pragma unroll
         for (int j = 0; j < kCacheVecs; ++j) {
           const int v = t + j * kStride;
-          if (v < nvec_row) prog.prefetch(in, base + step * r + (v << 2));
+          if (FULL || v < nvec_row) prog.prefetch(in, base + step * r + (v << 2));
         }
       }
     }
@@ -482,7 +484,7 @@ __device__ __forceinline__ void row_program_body(const Prog& prog, const RowInpu
 #pragma unroll
         for (int j = 0; j < kCacheVecs; ++j) {
           const int v = t + j * kStride;
-          if (v < nvec_row) prog.run_element_cached(pass, in, out, base + (v << 2), sregs, acc, cache[j]);
+          if (FULL || v < nvec_row) prog.run_element_cached(pass, in, out, base + (v << 2), sregs, acc, cache[j]);
         }
         done = r;
       } else if (vec_ok) {  // r % 4 == 0 and aligned buffers: every row starts on a vector boundary
@@ -582,8 +584,15 @@ __global__ void __launch_bounds__(256, (FORM == 4 ? 2 : StaticRowProgram<META, C
 k_row_program_static(ROWP_PARAMS) {
   grid_dependency_sync();
   ROWP_UNPACK;
-  const StaticRowProgram<META, COUNTS, SIG...> prog = {steps};
-  row_program_body<StaticRowProgram<META, COUNTS, SIG...>, FORM>(prog, in, out, rows, r, group, vec_ok);
+  using Prog      = StaticRowProgram<META, COUNTS, SIG...>;
+  const Prog prog = {steps};
+  // rows that fill the register cache exactly (1024 elements for a warp, 4096 for half a CTA, 8192 for a CTA) run
+  // the body without per-vector bounds tests
+  constexpr int kFullRow = FORM == 1 ? 1024 : (FORM == 3 ? 4096 : 8192);
+  if (FORM != 2 && Prog().passes() > 1 && vec_ok && r == kFullRow)
+    row_program_body<Prog, FORM, true>(prog, in, out, rows, r, group, vec_ok);
+  else
+    row_program_body<Prog, FORM, false>(prog, in, out, rows, r, group, vec_ok);
 }
 
 template <uint32_t... SIG>
