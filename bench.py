@@ -302,6 +302,10 @@ def side_groups(torch, dev, peak, only=None):
         ("row_program_rms_norm_f16_16384x4096", lambda: W.row_program("rms_norm_f16"), 2, "fp16 storage of x, weight and result, one kernel"),
         ("row_program_rms_norm_65536x1024", lambda: W.row_program("rms_norm", (65536, 1024)), 2, "short rows: a warp per row"),
         ("row_program_standardise_65536x1024", lambda: W.row_program("standardise", (65536, 1024)), 2, "short rows: a warp per row"),
+        ("row_program_rms_norm_32768x2048", lambda: W.row_program("rms_norm", (32768, 2048)), 2, "half a CTA per row, four vectors per thread"),
+        ("row_program_log_softmax_24576x3072", lambda: W.row_program("log_softmax", (24576, 3072)), 2, "half a CTA per row, six vectors per thread"),
+        ("row_program_standardise_16384x5120", lambda: W.row_program("standardise", (16384, 5120)), 2, "a CTA per row, five vectors per thread"),
+        ("row_program_rms_norm_20000x3000", lambda: W.row_program("rms_norm", (20000, 3000)), 2, "half a CTA per row, a row length that needs a bounds test per vector"),
         ("dag_shared_sum_4out_4096x8192", lambda: W.dag_program("shared_sum_4out", (4096, 8192)), 1,
          "g = A + B feeding four sums: six reads, four writes, one kernel"),
         ("dag_bias_relu_mask_3out_8192x8192", lambda: W.dag_program("bias_relu_mask_3out"), 1,

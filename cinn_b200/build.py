@@ -24,7 +24,7 @@ SOURCES = [
     "rownorm_kernels.cu",
     "rownorm_tma.cu",
     "softmax_safe.cu",
-    "ew_chain.cu", "chain_reduce.cu", "ew_static.cu", "ew_dag.cu", "row_prog.cu",
+    "ew_chain.cu", "chain_reduce.cu", "ew_static.cu", "ew_dag.cu", "row_prog.cu", "row_prog_half.cu", "row_prog_half_b.cu",
     "ew_chain_int.cu",
     "ew_chain_f64.cu",
     "ew_stream.cu",

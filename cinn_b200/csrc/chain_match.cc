@@ -2146,15 +2146,24 @@ std::unique_ptr<CompiledGroup> MatchRowProgram(const GroupDesc& g, const DeviceI
     // 0.91 against 0.72, l2_normalise 0.99 against 0.96, rms_norm 0.92 against 0.90.
     const bool half_ok = r % 4 == 0 && r <= 4096 && npass > 1;
     const bool half    = half_ok && (dev.rowp_form == 128 || (dev.rowp_form == 0 && group == 256));
+    // Every form has, besides the kernel for any row, kernels for rows of exactly 2 ... 8 vectors per thread of the
+    // row's group (no bounds tests: see row_program_body; a warp per row: 2 / 4 / 6 / 8 only); they are taken when
+    // the row length is such a multiple.
+    auto find = [&](const std::string& key, int64_t per_vector) -> const KernelEntry* {
+      const KernelEntry* k = nullptr;
+      if (npass > 1 && r % (4 * per_vector) == 0 && r / (4 * per_vector) >= (per_vector == 256 ? 5 : 2) && r / (4 * per_vector) <= 8)
+        k = FindStaticChain((key + std::to_string(r / (4 * per_vector))).c_str(), meta, (int)words.size() + 2, sig);
+      return k ? k : FindStaticChain(key.c_str(), meta, (int)words.size() + 2, sig);
+    };
     const KernelEntry* fixed = nullptr;
-    if (half) fixed = FindStaticChain("row_program_h", meta, (int)words.size() + 2, sig);
+    if (half) fixed = find("row_program_h", 128);
     if (fixed) {
       st.grid[0] = (unsigned)std::max<int64_t>(1, std::min<int64_t>(CeilDiv(rows, 2), (int64_t)dev.sm_count * 8));
     } else if (r % 4 == 0 && r > 4096 && r <= 8192 && npass > 1 && group == 256 &&
-               (fixed = FindStaticChain("row_program_c8", meta, (int)words.size() + 2, sig)) != nullptr) {
+               (fixed = find("row_program_c8", 256)) != nullptr) {
       // rows of 4097 to 8192 elements: a CTA per row with eight vectors per thread in registers between the passes
     } else {
-      fixed = FindStaticChain(group == 32 ? "row_program_w" : "row_program", meta, (int)words.size() + 2, sig);
+      fixed = group == 32 ? find("row_program_w", 32) : FindStaticChain("row_program", meta, (int)words.size() + 2, sig);
     }
     // The specialised kernels evaluate the steps that a pass shares with the passes after it once per row
     // (row_prog_prefix.h), which is only the same arithmetic when those steps carry the same constants.  The builder

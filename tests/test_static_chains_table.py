@@ -28,9 +28,11 @@ def test_committed_table_is_up_to_date_and_registered():
         for m in re.finditer(r"^STATIC_(CHAIN_REDUCE_ROW|CHAIN_REDUCE_COL|CHAIN|DAG|ROW_PROGRAM|INT_CHAIN|F64_CHAIN)\((\w+),", text, flags=re.M):
             prefix = {"CHAIN": "ew_static_", "DAG": "ew_dag_static_", "ROW_PROGRAM": "row_program_static_", "INT_CHAIN": "ew_int_static_", "F64_CHAIN": "ew_f64_static_"}.get(m.group(1), "chain_reduce_static_")
             assert L.cinn_b200_get_kernel((prefix + m.group(2)).encode()), prefix + m.group(2)
-    # (a row program has four kernels -- a CTA (two sizes), half a CTA or a warp per row: four registry entries per table line)
+    # (a row program has 19 kernels -- a CTA per row, and a warp, half a CTA or a CTA with eight vectors per thread for
+    # any row and for rows of exactly 2 / 4 / 6 / 8, 2 ... 8 and 5 ... 8 vectors per thread: 19 registry entries per
+    # table line)
     rows = len(re.findall(r"^STATIC_ROW_PROGRAM\(", open(os.path.join(ROOT, "cinn_b200", "csrc", "row_prog_static_table.inc")).read(), flags=re.M))
-    assert L.cinn_b200_num_static_chains() == total + 3 * rows and total >= 60
+    assert L.cinn_b200_num_static_chains() == total + 18 * rows and total >= 60
 
 
 def test_listed_groups_plan_to_their_static_kernel_and_others_to_the_interpreter():
@@ -88,10 +90,14 @@ def test_builder_row_compositions_fuse_into_one_specialised_kernel():
             kernels = [p.split()[1] for _, p in comp.groups()]
             # (suffix _w: the warp-per-row form, taken for short rows and for single-pass programs)
             # (suffix _h: half a CTA per row, taken for programs of several passes over rows of 1025 to 4096 elements)
-            assert kernels in (["row_program_static_" + make.__name__ + f] for f in ("", "_w", "_h", "_c8")), \
+            # (a digit after the suffix: the kernel for rows of exactly that many vectors per thread)
+            assert len(kernels) == 1 and re.fullmatch("row_program_static_" + make.__name__ + r"(|_w[2-8]?|_h[2-8]?|_c8[5-8]?)", kernels[0]), \
                 (shape, make.__name__, kernels)
             if shape[1] <= 1024:
-                assert kernels[0].endswith("_w")
+                assert "_w" in kernels[0][len("row_program_static_" + make.__name__):]
+            if shape[1] == 4096:
+                single_pass = kernels[0].endswith("_w")  # programs of one pass do not keep the row: a warp per row
+                assert single_pass or kernels[0].endswith("_h8"), kernels
 
 
 def test_passes_that_repeat_steps_with_other_constants_keep_the_interpreter():
@@ -102,7 +108,7 @@ def test_passes_that_repeat_steps_with_other_constants_keep_the_interpreter():
     gen = load_generator()
     desc = dict(gen.ROW_GROUPS)["scaled_softmax"]
     g = cinn_b200.FusedGroup(desc.replace("64,4096", "16,2048"))
-    assert g.kernel_names() == ["row_program_static_scaled_softmax_h"], g.kernel_names()
+    assert g.kernel_names() == ["row_program_static_scaled_softmax_h4"], g.kernel_names()
     g.release()
     other = desc.replace("op subtract z = d mb", "op scale d2 = X ; bias=0.0 bias_after_scale=true scale=0.25\nop subtract z = d2 mb")
     assert other != desc
