@@ -21,11 +21,14 @@ CINN_B200_DEFINE_ASYNC_TIMEOUT_COUNTER(g_rownorm_wait_timeouts);
 
 namespace {
 
-template <typename T, int G, int VPT, bool LAYERNORM>
-__global__ void __launch_bounds__(G)
-    k_rownorm_tma(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
-                  T* __restrict__ y, long long rows, long long cols, long long stages_ll, double eps_d) {
-  grid_dependency_sync();
+// EXACT: a row is exactly VPT vectors per thread -- no test per vector (with the tests every vector is a basic block
+// of its own; without them a thread's shared-memory reads are issued together and its arithmetic interleaves).  A
+// wait that ran out is then not tested per vector either: the thread reads whatever the ring buffer holds (its own
+// shared memory), and the CTA leaves at the barrier of the same row before anything is stored.
+template <typename T, int G, int VPT, bool LAYERNORM, bool EXACT>
+__device__ __forceinline__ void rownorm_tma_body(const T* __restrict__ x, const float* __restrict__ gamma,
+                                                 const float* __restrict__ beta, T* __restrict__ y, long long rows,
+                                                 long long cols, long long stages_ll, double eps_d) {
   constexpr int V      = Io<T>::kVec;
   constexpr int NWARPS = G / 32;
   extern __shared__ __align__(128) unsigned char ring[];
@@ -64,7 +67,7 @@ __global__ void __launch_bounds__(G)
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int v = t + j * G;
-      if (v < nvec) {
+      if (EXACT || v < nvec) {
 #pragma unroll
         for (int q = 0; q < V / 4; ++q) {
           Io<float>::unpack(ld_keep16(gamma + (long long)v * V + 4 * q), &g[j][4 * q]);
@@ -95,7 +98,7 @@ __global__ void __launch_bounds__(G)
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
       const int v = t + j * G;
-      if (v < nvec && ok) {
+      if (EXACT || (v < nvec && ok)) {
         Io<T>::unpack(src[v], f[j]);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
@@ -151,7 +154,7 @@ __global__ void __launch_bounds__(G)
 #pragma unroll
       for (int j = 0; j < VPT; ++j) {
         const int v = t + j * G;
-        if (v < nvec) {
+        if (EXACT || v < nvec) {
 #pragma unroll
           for (int i = 0; i < V; ++i)
             f[j][i] = sizeof(T) == 2 ? fmaf(fmaf(f[j][i], rstd, nmr), g[j][i], b[j][i])
@@ -164,7 +167,7 @@ __global__ void __launch_bounds__(G)
 #pragma unroll
       for (int j = 0; j < VPT; ++j) {
         const int v = t + j * G;
-        if (v < nvec) {
+        if (EXACT || v < nvec) {
 #pragma unroll
           for (int i = 0; i < V; ++i) f[j][i] = f[j][i] * inv_s;
           __stcs(dst + v, Io<T>::pack(f[j]));
@@ -179,6 +182,18 @@ __global__ void __launch_bounds__(G)
     for (long long kk = k + 1; kk < my_rows && kk < k + stages; ++kk)
       (void)mbar_wait_bounded(&full[(int)(kk % stages)], (uint32_t)((kk / stages) & 1));
   }
+}
+
+// (both bodies in one kernel, deliberately: see k_rownorm_reg)
+template <typename T, int G, int VPT, bool LAYERNORM>
+__global__ void __launch_bounds__(G)
+    k_rownorm_tma(const T* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                  T* __restrict__ y, long long rows, long long cols, long long stages_ll, double eps_d) {
+  grid_dependency_sync();
+  if (cols == (long long)G * VPT * Io<T>::kVec)
+    rownorm_tma_body<T, G, VPT, LAYERNORM, true>(x, gamma, beta, y, rows, cols, stages_ll, eps_d);
+  else
+    rownorm_tma_body<T, G, VPT, LAYERNORM, false>(x, gamma, beta, y, rows, cols, stages_ll, eps_d);
 }
 
 }  // namespace
