@@ -40,8 +40,57 @@ __device__ __forceinline__ void walk_vectors(const uint4* __restrict__ px, const
   const IdxT total = (IdxT)my_items * per;
   IdxT k = (IdxT)threadIdx.x / per, v = (IdxT)threadIdx.x - k * per;
   const IdxT step_k = T_ / per, step_v = T_ - step_k * per;  // one stride of T_ vectors
+  // one loaded vector into the accumulators
+  auto fold = [&](const uint4& rv, const uint4& rv2) {
+    if constexpr (sizeof(T) == 2 && DUAL && !GRAD && std::is_same<OpA, SumOp>::value &&
+                  std::is_same<OpB, SumSquareOp>::value) {
+      // sum and sum of squares of 16-bit values with the mixed-precision add / fma of sm_100 (the operand is
+      // widened inside the instruction: no conversion instructions; x * x is exact in fp32, so the fma rounds
+      // exactly where a + x * x does)
+      const unsigned short* h = reinterpret_cast<const unsigned short*>(&rv);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        if constexpr (std::is_same<T, __half>::value) {
+          asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(a0) : "h"(h[i]));
+          asm("fma.rn.f32.f16 %0, %1, %1, %0;" : "+f"(a1) : "h"(h[i]));
+        } else {
+          asm("add.rn.f32.bf16 %0, %1, %0;" : "+f"(a0) : "h"(h[i]));
+          asm("fma.rn.f32.bf16 %0, %1, %1, %0;" : "+f"(a1) : "h"(h[i]));
+        }
+      }
+    } else {
+      float f[V], f2[V];
+      Io<T>::unpack(rv, f);
+      if (GRAD) Io<T>::unpack(rv2, f2);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        a0 = OpA::accum(a0, f[i]);
+        if (GRAD) a1 = a1 + f[i] * (f2[i] - mu);
+        else if (DUAL) a1 = OpB::accum(a1, f[i]);
+      }
+    }
+  };
   for (IdxT idx = threadIdx.x; idx < total; idx += U * T_) {
     uint4 r[U], r2[GRAD ? U : 1];
+    if (chunks == 1 && idx + (IdxT)(U - 1) * T_ < total) {
+      // Whole items (no chunking) and all U vectors in range -- every iteration of a thread but its last: no test
+      // per vector, so the U loads are issued together and the folds run straight through.
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const IdxT at = ((s + k * splits) * B + b) * nvec + v;
+        r[j]          = __ldcs(px + at);
+        if (GRAD) r2[GRAD ? j : 0] = __ldcs(px2 + at);
+        k += step_k;
+        v += step_v;
+        if (v >= per) {
+          v -= per;
+          ++k;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < U; ++j) fold(r[j], r2[GRAD ? j : 0]);
+      continue;
+    }
     bool ok[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
@@ -69,37 +118,8 @@ __device__ __forceinline__ void walk_vectors(const uint4* __restrict__ px, const
       }
     }
 #pragma unroll
-    for (int j = 0; j < U; ++j) {
-      if (ok[j]) {
-        if constexpr (sizeof(T) == 2 && DUAL && !GRAD && std::is_same<OpA, SumOp>::value &&
-                      std::is_same<OpB, SumSquareOp>::value) {
-          // sum and sum of squares of 16-bit values with the mixed-precision add / fma of sm_100 (the operand is
-          // widened inside the instruction: no conversion instructions; x * x is exact in fp32, so the fma rounds
-          // exactly where a + x * x does)
-          const unsigned short* h = reinterpret_cast<const unsigned short*>(&r[j]);
-#pragma unroll
-          for (int i = 0; i < V; ++i) {
-            if constexpr (std::is_same<T, __half>::value) {
-              asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(a0) : "h"(h[i]));
-              asm("fma.rn.f32.f16 %0, %1, %1, %0;" : "+f"(a1) : "h"(h[i]));
-            } else {
-              asm("add.rn.f32.bf16 %0, %1, %0;" : "+f"(a0) : "h"(h[i]));
-              asm("fma.rn.f32.bf16 %0, %1, %1, %0;" : "+f"(a1) : "h"(h[i]));
-            }
-          }
-          continue;
-        }
-        float f[V], f2[V];
-        Io<T>::unpack(r[j], f);
-        if (GRAD) Io<T>::unpack(r2[GRAD ? j : 0], f2);
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-          a0 = OpA::accum(a0, f[i]);
-          if (GRAD) a1 = a1 + f[i] * (f2[i] - mu);
-          else if (DUAL) a1 = OpB::accum(a1, f[i]);
-        }
-      }
-    }
+    for (int j = 0; j < U; ++j)
+      if (ok[j]) fold(r[j], r2[GRAD ? j : 0]);
   }
 }
 
