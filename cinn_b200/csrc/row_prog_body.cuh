@@ -589,8 +589,11 @@ __global__ void __launch_bounds__(256) k_row_program(ROWP_PARAMS) {
 // body.  Holding both bodies is deliberate: compiled alone, the straight-line body is packed into fewer registers
 // (68 against 76-78 for softmax(x * s)) with its loads and arithmetic less interleaved -- measured on B200 over
 // 16384 x 4096, 0.92 of the HBM peak against 0.98, fp16 rms_norm 0.68 against 0.80.
+// (A CTA per row of up to 8192 elements is compiled for two CTAs per SM -- eight cached vectors per thread and the
+// program's own registers do not fit 80 --, its kernels for exactly 5 or 6 vectors per thread for three: standardise
+// over 16384 x 5120, 0.86 -> 0.93 of the HBM peak.)
 template <int FORM, int NV, unsigned long long META, unsigned long long COUNTS, uint32_t... SIG>
-__global__ void __launch_bounds__(256, (FORM == 4 ? 2 : StaticRowProgram<META, COUNTS, SIG...>::ctas_per_sm()))
+__global__ void __launch_bounds__(256, (FORM == 4 && (NV == 0 || NV > 6) ? 2 : StaticRowProgram<META, COUNTS, SIG...>::ctas_per_sm()))
 k_row_program_static(ROWP_PARAMS) {
   grid_dependency_sync();
   ROWP_UNPACK;
